@@ -1,0 +1,304 @@
+// bf16 GEMM on the 5th-generation tensor cores:  C[M,N] = A[M,K] * W[N,K]^T.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: 128x64 A tiles and BNx64 W tiles (128-byte swizzle)
+//               into a STAGES-deep shared-memory ring, completion on mbarriers
+//   warp 1      allocates TMEM and issues tcgen05.mma (128 x BN x 16) from one
+//               thread; tcgen05.commit frees ring slots and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (two accumulator
+//               stages in TMEM, so the next tile's MMAs overlap this store),
+//               optional fused residual add or SwiGLU, bf16 store
+// Every mbarrier wait is bounded; on a time-out the kernel records a status
+// word, drains its copies, frees TMEM and returns.
+//
+// Replaces the reference's cuBLASLt/cuBLAS dispatch
+// (driver/cuda/src/ops/gemm.cpp:326-415, 607-640) and its separate
+// residual-add / SwiGLU passes (driver/cuda/src/kernels/swiglu.cu:180-260).
+#include "tcgen05.cuh"
+
+namespace pie {
+using namespace sm100;
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+enum GemmEpilogue : int {
+    EPI_STORE = 0,     // C = acc
+    EPI_RESIDUAL = 1,  // C = acc + R
+    EPI_SWIGLU = 2,    // C[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]   (C is [M, N/2])
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
+    static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr uint32_t TMEM_COLS = 2 * BN;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 bf16* __restrict__ C, const bf16* __restrict__ R, int M, int N, int K, int ldc,
+                 int ldr, int* status) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_addr(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    uint8_t* tiles_ptr = smem_raw + (tiles - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + STAGES * Cfg::STAGE_BYTES);
+    const uint32_t bar0 = tiles + STAGES * Cfg::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tma_a);
+            tma_prefetch_desc(&tma_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m_blk = t % tiles_m, n_blk = t / tiles_m;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+                    const uint32_t a_dst = tiles + s * Cfg::STAGE_BYTES;
+                    tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
+                    tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, n_blk * BN);
+                }
+            }
+            // no copy of this CTA may still be in flight when it exits
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
+            for (uint32_t j = first; j < it; ++j)
+                mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1u, status, PIE_ERR_WAIT_TMA,
+                          200000000ll);
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tcount) {
+                const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), aph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = tiles + s * Cfg::STAGE_BYTES;
+                    const uint64_t adesc = make_smem_desc_sw128(a_addr);
+                    const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / 16; ++k)
+                        umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0);
+                    umma_commit(empty_bar(s));
+                }
+                if (ok) umma_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        // ----------------------------------------------------------- epilogue
+        const int q = warp & 3;  // TMEM lanes [32q, 32q+32) belong to this warp
+        uint32_t tcount = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tcount) {
+            const int m_blk = t % tiles_m, n_blk = t / tiles_m;
+            const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+            const bool got = mbar_wait(tfull_bar(acc), aph, status, PIE_ERR_WAIT_MMA);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tc_fence_after();
+            const int row = m_blk * GEMM_BM + q * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + c * 32, v);
+                tmem_ld_wait();
+                const int col0 = n_blk * BN + c * 32;
+                if (row < M && col0 < N) {
+                    if (EPI == EPI_SWIGLU) {
+                        bf16* dst = C + (size_t)row * ldc + (col0 >> 1);
+                        float o[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float g = __uint_as_float(v[2 * j]);
+                            const float u = __uint_as_float(v[2 * j + 1]);
+                            o[j] = g / (1.f + __expf(-g)) * u;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            if (col0 + 16 * j < N)
+                                *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o + 8 * j);
+                    } else {
+                        bf16* dst = C + (size_t)row * ldc + col0;
+                        const bf16* res = (EPI == EPI_RESIDUAL) ? R + (size_t)row * ldr + col0 : nullptr;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (col0 + 8 * j >= N) break;
+                            float o[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(v[8 * j + e]);
+                            if (EPI == EPI_RESIDUAL) {
+                                float rr[8];
+                                unpack8(*reinterpret_cast<const bf16x8*>(res + 8 * j), rr);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) o[e] += rr[e];
+                            }
+                            *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace pie
+
+using namespace pie;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with leading dimension ld (elements); box is
+// box_rows x 64 columns with the 128-byte swizzle.
+extern "C" int pie_make_tma_2d_bf16(CUtensorMap* map, const void* ptr, long rows, long cols, long ld,
+                                    int box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return -1;
+    if (((uintptr_t)ptr & 15) || (ld * 2) % 16) return -2;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return (int)r;
+}
+
+template <int BN, int EPI>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M,
+                       int N, int K, int ldc, int ldr, int* status, int num_sms, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    auto kern = gemm_bf16_kernel<BN, EPI>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < num_sms ? tiles : num_sms;
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
+                                                      ldr, status);
+    return (int)cudaGetLastError();
+}
+
+// Column-tile width: the widest tile whose last wave is still reasonably full.
+static int pick_bn(int M, int N, int num_sms) {
+    const int tm = (M + GEMM_BM - 1) / GEMM_BM;
+    int best = 64;
+    double best_cost = 1e30;
+    const int cands[3] = {256, 128, 64};
+    // relative time of one tile per column of output (narrow tiles re-read A more often
+    // and amortise the pipeline fill over less work)
+    const double per_col[3] = {1.0, 1.08, 1.25};
+    for (int i = 0; i < 3; ++i) {
+        const int bn = cands[i];
+        if (bn > 64 && N < bn) continue;
+        const long tiles = (long)tm * ((N + bn - 1) / bn);
+        const long waves = (tiles + num_sms - 1) / num_sms;
+        const double cost = (double)waves * bn * per_col[i];
+        if (cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+// C[M,N] (or [M,N/2] for the SwiGLU epilogue) = A[M,K] * W[N,K]^T.
+// `status` is a device int that stays 0 unless a bounded wait ran out.
+PIE_API int pie_gemm_bf16(const void* A, const void* W, void* C, const void* R, int M, int N, int K,
+                          int lda, int ldw, int ldc, int ldr, int epilogue, int force_bn,
+                          int* status, int num_sms, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || N % 8 || ldc % 8 || (epilogue == EPI_RESIDUAL && ldr % 8))
+        return (int)cudaErrorInvalidValue;
+    if (epilogue == EPI_SWIGLU && N % 32) return (int)cudaErrorInvalidValue;
+    const int bn = force_bn > 0 ? force_bn : pick_bn(M, N, num_sms);
+    CUtensorMap ta, tb;
+    if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
+    if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, bn) != 0) return (int)cudaErrorInvalidValue;
+#define GO(BN_)                                                                                   \
+    switch (epilogue) {                                                                           \
+        case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
+        case EPI_RESIDUAL: return launch_gemm<BN_, EPI_RESIDUAL>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
+        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
+        default: return (int)cudaErrorInvalidValue;                                               \
+    }
+    if (bn == 256) { GO(256) }
+    else if (bn == 128) { GO(128) }
+    else if (bn == 64) { GO(64) }
+#undef GO
+    return (int)cudaErrorInvalidValue;
+}

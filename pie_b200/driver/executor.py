@@ -1,0 +1,458 @@
+"""The model driver: executes batched forward requests on one GPU (or on the CPU for the
+plumbing configuration) and answers with sampled tokens / probe payloads.
+
+Per fire (`TorchDriver.fire_batch`): derive KV lengths and tail-append slots from the CSR
+page tables -> fill ONE pinned host slab with every integer/float input (tokens, positions,
+slots, indptrs, page ids, split-KV work items, sampler parameters) -> one or two H2D copies
+into a fixed-address device slab -> forward (CUDA-graph replay for pure-decode batches padded
+to a bucket of the lattice, eager otherwise) -> sampling kernel -> D2H of the sampled tokens.
+
+Behavioural counterpart of the reference's executor
+(driver/cuda/src/executor/executor.cpp:2133-2800 handle_fire_batch, :1727-1781 graph
+shape decision, executor/persistent_inputs.hpp fixed-address slabs,
+executor/forward_graph.hpp:63-91 bucket lattice, sampling_dispatch.cpp:49-137).
+Differences by design: logit masks are consumed by the GPU sampler (no host override), all
+inputs travel in one slab copy instead of six, and the decode work list is graph-safe
+because its length lives in device memory.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.config import ModelConfig
+from ..models.transformer import ForwardInputs, ParallelContext, Transformer
+from ..models.weights import random_weights, torch_dtype
+from .kv_cache import KVCache
+from .schema import (Capabilities, CopyRequest, ForwardRequest, ForwardResponse, SamplerKind,
+                     SamplerSpec, SlotOutput)
+
+
+def graph_buckets(max_requests: int) -> List[int]:
+    """Request-count lattice for decode graphs: 1,2,4,8 then steps of 8 to 64, 16 to 256, 32 beyond."""
+    out = [b for b in (1, 2, 4, 8) if b <= max_requests]
+    b = 16
+    while b <= max_requests:
+        out.append(b)
+        b += 8 if b < 64 else (16 if b < 256 else 32)
+    if out[-1] != max_requests:
+        out.append(max_requests)
+    return out
+
+
+class _Slab:
+    """Named int32 segments in one pinned host buffer mirrored by one device buffer."""
+
+    def __init__(self, segments: Dict[str, int], device):
+        self.offsets, off = {}, 0
+        for name, n in segments.items():
+            off = (off + 3) & ~3  # 16-byte aligned segments
+            self.offsets[name] = (off, n)
+            off += n
+        self.size = off
+        cuda = torch.device(device).type == "cuda"
+        self.host = torch.zeros(self.size, dtype=torch.int32, pin_memory=cuda)
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=device) if cuda else self.host
+
+    def h(self, name, dtype=np.int32):
+        o, n = self.offsets[name]
+        return self.np[o:o + n].view(dtype)
+
+    def d(self, name, n=None, dtype=torch.int32):
+        o, cap = self.offsets[name]
+        t = self.dev[o:o + (cap if n is None else n * (2 if dtype == torch.int64 else 1))]
+        return t.view(dtype) if dtype != torch.int32 else t
+
+    def upload(self, upto_name: str, extra: Optional[tuple] = None):
+        if self.dev is self.host:
+            return
+        o, n = self.offsets[upto_name]
+        end = o + n
+        self.dev[:end].copy_(self.host[:end], non_blocking=True)
+        if extra is not None:
+            name, used = extra
+            o2, _ = self.offsets[name]
+            if used:
+                self.dev[o2:o2 + used].copy_(self.host[o2:o2 + used], non_blocking=True)
+
+
+@dataclass
+class _Graph:
+    graph: "torch.cuda.CUDAGraph"
+    logits: torch.Tensor
+    bucket: int
+
+
+class TorchDriver:
+    """PyTorch + sm_100a-kernel model driver for one tensor-parallel rank."""
+
+    def __init__(self, cfg: ModelConfig, device="cuda", weights: Optional[dict] = None, num_pages: int = 0,
+                 page_size: int = 16, max_requests: int = 512, max_tokens: int = 8192, seed: int = 0,
+                 par: Optional[ParallelContext] = None, gemm_backend: str = "tcgen05", use_graphs: bool = True,
+                 swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.dtype = torch_dtype(cfg.dtype) if not self.cuda else torch.bfloat16
+        self.par = par or ParallelContext()
+        if self.cuda:
+            torch.cuda.set_device(self.device)
+        if weights is None:
+            weights = random_weights(cfg, self.device, self.dtype, seed, self.par.tp_size, self.par.tp_rank,
+                                     ep=self.par.ep)
+        self.model = Transformer(cfg, weights, self.device, self.dtype, self.par, gemm_backend)
+        self.page_size = page_size
+        hkv = self.model.hkv
+        if num_pages <= 0:
+            num_pages = self._plan_pages(hkv, gpu_mem_utilization)
+        self.kv = KVCache(cfg.num_hidden_layers, num_pages, hkv, page_size, cfg.head_dim, self.dtype,
+                          self.device, swap_pages)
+        self.max_requests, self.max_tokens = max_requests, max_tokens
+        self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
+        self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
+        self.max_items = max_requests + self.num_ctas * 8
+        rows = max(max_requests, 1024)
+        self.max_rows = rows
+        self.slab = _Slab({
+            "tokens": max_tokens, "positions": max_tokens, "slots": max_tokens,
+            "qo_indptr": max_requests + 1, "kv_page_indptr": max_requests + 1, "kv_lens": max_requests,
+            "item_req": self.max_items, "item_start": self.max_items, "item_end": self.max_items,
+            "req_item_indptr": max_requests + 1, "num_items": 4,
+            "logit_rows": rows, "temperature": rows, "top_k": rows, "top_p": rows, "min_p": rows,
+            "mask_row": rows, "seeds": 2 * rows,
+            "tile_req": max_tokens + max_requests, "tile_qstart": max_tokens + max_requests,
+            "page_indices": self.max_page_refs,
+        }, self.device)
+        self.scratch = None
+        if self.cuda:
+            self.scratch = torch.empty(ops.decode_scratch_floats(self.max_items, self.model.hq, cfg.head_dim),
+                                       dtype=torch.float32, device=self.device)
+            self.sampled = torch.zeros(rows, dtype=torch.int32, device=self.device)
+            self.sampled_host = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
+        self.use_graphs = use_graphs and self.cuda
+        self.buckets = graph_buckets(max_requests)
+        self.graphs: Dict[int, _Graph] = {}
+        self.rng = np.random.default_rng(seed + 12345)
+        self.stats = {"fires": 0, "graph_replays": 0, "eager": 0, "kernel_launches": 0}
+
+    # ------------------------------------------------------------------ planning
+    def _plan_pages(self, hkv: int, util: float) -> int:
+        per_page = KVCache.bytes_per_page(self.cfg.num_hidden_layers, hkv, self.page_size, self.cfg.head_dim,
+                                          torch.tensor([], dtype=self.dtype).element_size())
+        if not self.cuda:
+            return 4096
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(total * util) - (total - free) - (6 << 30)  # activations / workspace headroom
+        return max(64, budget // per_page)
+
+    def capabilities(self) -> Capabilities:
+        return Capabilities(
+            total_pages=self.kv.num_pages, kv_page_size=self.page_size, swap_pool_size=self.kv.swap_pages,
+            max_forward_tokens=self.max_tokens, max_forward_requests=self.max_requests,
+            max_page_refs=self.max_page_refs, max_logit_rows=self.max_rows, max_prob_rows=self.max_rows,
+            max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
+            max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
+            tp_size=self.par.tp_size)
+
+    # ------------------------------------------------------------------ request -> slab
+    def _derive(self, req: ForwardRequest):
+        page = self.page_size
+        qo = np.asarray(req.qo_indptr, dtype=np.int64)
+        qlens = np.diff(qo)
+        pptr = np.asarray(req.kv_page_indptr, dtype=np.int64)
+        npages = np.diff(pptr)
+        kv_lens = np.where(npages > 0, (npages - 1) * page + np.asarray(req.kv_last_page_lens, dtype=np.int64), 0)
+        n = int(qo[-1])
+        req_of_tok = np.repeat(np.arange(len(qlens)), qlens)
+        j = np.arange(n) - qo[req_of_tok]
+        kvidx = kv_lens[req_of_tok] - qlens[req_of_tok] + j
+        pages = np.asarray(req.kv_page_indices, dtype=np.int64)
+        if n and (kvidx < 0).any():
+            raise ValueError("KV_INVARIANT_VIOLATION: more input tokens than KV slots")
+        slots = pages[pptr[req_of_tok] + kvidx // page] * page + kvidx % page if n else np.zeros(0, np.int64)
+        return qlens, kv_lens, slots
+
+    def _fill_common(self, req, slots, kv_lens, n_pad_tokens=0, r_pad=0):
+        s = self.slab
+        n, r = req.num_tokens, req.num_requests
+        if n + n_pad_tokens > self.max_tokens or r + r_pad > self.max_requests:
+            raise ValueError("batch exceeds the advertised forward limits")
+        if len(req.kv_page_indices) > self.max_page_refs:
+            raise ValueError("batch exceeds max_page_refs")
+        s.h("tokens")[:n] = req.tokens
+        s.h("positions")[:n] = req.positions
+        s.h("slots")[:n] = slots
+        s.h("qo_indptr")[:r + 1] = req.qo_indptr
+        s.h("kv_page_indptr")[:r + 1] = req.kv_page_indptr
+        s.h("kv_lens")[:r] = kv_lens
+        s.h("page_indices")[:len(req.kv_page_indices)] = req.kv_page_indices
+
+    def _sampler_params(self, req: ForwardRequest, rows_of_slot: np.ndarray):
+        """Fill per-row sampler parameter segments for the token-sampler slots."""
+        s = self.slab
+        token_slots = [i for i, sp in enumerate(req.slot_samplers) if sp.is_token]
+        k = len(token_slots)
+        if k > self.max_rows:
+            raise ValueError("too many sampler rows")
+        t, tk = s.h("temperature", np.float32), s.h("top_k")
+        tp, mp = s.h("top_p", np.float32), s.h("min_p", np.float32)
+        seeds = s.h("seeds", np.int64)
+        for j, i in enumerate(token_slots):
+            sp = req.slot_samplers[i]
+            t[j] = sp.temperature
+            tk[j] = sp.top_k if sp.kind in (SamplerKind.TOP_K, SamplerKind.TOP_K_TOP_P) else 0
+            tp[j] = sp.top_p if sp.kind in (SamplerKind.TOP_P, SamplerKind.TOP_K_TOP_P) else 1.0
+            mp[j] = sp.min_p if sp.kind == SamplerKind.MIN_P else 0.0
+            seeds[j] = sp.seed if sp.seed else int(self.rng.integers(1, 2**62))
+        return token_slots
+
+    # ------------------------------------------------------------------ forward variants
+    def _forward_inputs_decode(self, rb: int) -> ForwardInputs:
+        s = self.slab
+        plan = ops.DecodePlan(
+            page_indices=s.d("page_indices"), kv_page_indptr=s.d("kv_page_indptr"), item_req=s.d("item_req"),
+            item_start=s.d("item_start"), item_end=s.d("item_end"), req_item_indptr=s.d("req_item_indptr"),
+            num_items=s.d("num_items"), scratch=self.scratch, max_items=self.max_items, num_reqs=rb,
+            num_ctas=self.num_ctas, page_size=self.page_size)
+        return ForwardInputs(tokens=s.d("tokens", rb), positions=s.d("positions", rb), slots=s.d("slots", rb),
+                             attn=plan, logit_rows=None, is_decode=True)
+
+    def _capture(self, rb: int) -> _Graph:
+        fi = self._forward_inputs_decode(rb)
+        # warm-up on a side stream (sets kernel attributes, fills allocator pools), then capture
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward(fi, self.kv.data)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            logits = self.model.forward(fi, self.kv.data)
+        return _Graph(g, logits, rb)
+
+    def _bucket(self, r: int) -> int:
+        for b in self.buckets:
+            if b >= r:
+                return b
+        return self.buckets[-1]
+
+    def _run_decode(self, req: ForwardRequest, slots, kv_lens) -> torch.Tensor:
+        s = self.slab
+        r = req.num_requests
+        rb = self._bucket(r) if self.use_graphs else r
+        self._fill_common(req, slots, kv_lens, n_pad_tokens=rb - r, r_pad=rb - r)
+        if rb > r:  # padding requests: token 0 at position 0, no KV write, no attention work
+            s.h("tokens")[r:rb] = 0
+            s.h("positions")[r:rb] = 0
+            s.h("slots")[r:rb] = -1
+            s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
+        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items)
+        ni = len(item_req)
+        s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
+        s.h("req_item_indptr")[:r + 1] = indptr
+        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
+        s.h("num_items")[0] = ni
+        s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
+        if self.use_graphs:
+            if rb not in self.graphs:
+                self.graphs[rb] = self._capture(rb)
+                s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
+            g = self.graphs[rb]
+            g.graph.replay()
+            self.stats["graph_replays"] += 1
+            return g.logits
+        self.stats["eager"] += 1
+        return self.model.forward(self._forward_inputs_decode(rb), self.kv.data)
+
+    def _mask_rows_for_request(self, req: ForwardRequest, r: int, ql: int, kl: int):
+        if req.has_user_mask is not None and req.has_user_mask[r]:
+            a, b = int(req.mask_row_indptr[r]), int(req.mask_row_indptr[r + 1])
+            return req.mask_runs[a:b]
+        return [[0, kl - ql + i + 1] for i in range(ql)]
+
+    def _run_general(self, req: ForwardRequest, qlens, slots, kv_lens) -> torch.Tensor:
+        s = self.slab
+        n, r = req.num_tokens, req.num_requests
+        self._fill_common(req, slots, kv_lens)
+        custom = req.has_user_mask is not None and bool(np.any(req.has_user_mask))
+        rows = np.asarray(req.slot_row, dtype=np.int32) if req.slot_row is not None else np.zeros(0, np.int32)
+        if self.cuda:
+            group = self.model.hq // self.model.hkv
+            tile_req, tile_q = ops.plan_prefill_tiles(np.asarray(req.qo_indptr), group)
+            nt = len(tile_req)
+            s.h("tile_req")[:nt], s.h("tile_qstart")[:nt] = tile_req, tile_q
+            s.h("logit_rows")[:len(rows)] = rows
+            s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
+            mask_bits = mask_indptr = None
+            if custom:
+                parts, indptr = [], [0]
+                for i in range(r):
+                    ql, kl = int(qlens[i]), int(kv_lens[i])
+                    runs = self._mask_rows_for_request(req, i, ql, kl)
+                    bits = ops.brle_expand(runs, kl, self.device) if ql else torch.zeros(0, 1, dtype=torch.int32, device=self.device)
+                    parts.append(bits.reshape(-1))
+                    indptr.append(indptr[-1] + bits.numel())
+                mask_bits = torch.cat(parts) if parts else None
+                mask_indptr = torch.tensor(indptr, dtype=torch.int64, device=self.device)
+            plan = ops.PrefillPlan(s.d("page_indices"), s.d("kv_page_indptr"), s.d("qo_indptr"), s.d("kv_lens"),
+                                   s.d("tile_req"), s.d("tile_qstart"), nt, self.page_size, mask_bits, mask_indptr)
+            fi = ForwardInputs(s.d("tokens", n), s.d("positions", n), s.d("slots", n), plan,
+                               logit_rows=s.d("logit_rows", len(rows)), is_decode=False)
+        else:
+            masks = None
+            if custom:
+                from ..ops.reference import brle_to_bool
+                masks = []
+                for i in range(r):
+                    ql, kl = int(qlens[i]), int(kv_lens[i])
+                    if req.has_user_mask[i]:
+                        runs = self._mask_rows_for_request(req, i, ql, kl)
+                        masks.append(np.stack([brle_to_bool(rr, kl).numpy() for rr in runs]) if ql else None)
+                    else:
+                        masks.append(None)
+            batch = ops.AttnBatch(np.asarray(req.qo_indptr), np.asarray(req.kv_page_indptr),
+                                  np.asarray(req.kv_page_indices), kv_lens, masks)
+            fi = ForwardInputs(torch.from_numpy(np.ascontiguousarray(req.tokens, dtype=np.int32)),
+                               torch.from_numpy(np.ascontiguousarray(req.positions, dtype=np.int32)),
+                               torch.from_numpy(slots.astype(np.int32)), batch,
+                               logit_rows=torch.from_numpy(rows), is_decode=False)
+        self.stats["eager"] += 1
+        hidden = self.model.forward_hidden(fi, self.kv.data)
+        if len(rows) == 0:
+            return None
+        return self.model.logits(hidden, fi)
+
+    # ------------------------------------------------------------------ sampling + response
+    def _respond(self, req: ForwardRequest, logits: Optional[torch.Tensor], slot_logit_row: np.ndarray):
+        nslots = len(req.slot_samplers)
+        if nslots == 0:
+            return ForwardResponse(slots=[], tokens=np.zeros(0, np.int32))
+        token_slots = self._token_slots
+        out_slots: List[Optional[SlotOutput]] = [None] * nslots
+        tokens = None
+        if token_slots:
+            rows = slot_logit_row[token_slots]
+            k = len(token_slots)
+            contiguous = bool((rows == np.arange(k)).all()) and k <= logits.shape[0]
+            lg = logits[:k] if contiguous else logits[torch.from_numpy(rows.astype(np.int64)).to(logits.device)]
+            mask_bits, mask_row = self._logit_mask_rows(req, token_slots)
+            if self.cuda:
+                s = self.slab
+                ops.sample(lg, s.d("temperature", k).view(torch.float32), s.d("top_k", k),
+                           s.d("top_p", k).view(torch.float32), s.d("min_p", k).view(torch.float32),
+                           s.d("seeds", k, torch.int64), mask_bits, mask_row, out=self.sampled)
+                self.sampled_host[:k].copy_(self.sampled[:k], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                tokens = self.sampled_host[:k].numpy().copy()
+            else:
+                tokens = self._sample_cpu(lg, k, mask_bits, mask_row)
+            for j, i in enumerate(token_slots):
+                out_slots[i] = SlotOutput("token", token=int(tokens[j]))
+        probe_slots = [i for i in range(nslots) if out_slots[i] is None]
+        if probe_slots:
+            self._probes(req, logits, slot_logit_row, probe_slots, out_slots)
+        all_tokens = tokens if len(token_slots) == nslots else None
+        return ForwardResponse(slots=out_slots, tokens=all_tokens)
+
+    def _logit_mask_rows(self, req, token_slots):
+        if not req.logit_masks or not any(m is not None for m in req.logit_masks):
+            return None, None
+        reqs = sorted({int(req.slot_req[i]) for i in token_slots if req.logit_masks[int(req.slot_req[i])] is not None})
+        index = {r: j for j, r in enumerate(reqs)}
+        vocab = self.model.vocab_local
+        bits = ops.brle_expand([req.logit_masks[r] for r in reqs], vocab, self.device)
+        mrow = np.array([index.get(int(req.slot_req[i]), -1) for i in token_slots], dtype=np.int32)
+        if self.cuda:
+            self.slab.h("mask_row")[:len(mrow)] = mrow
+            o, _ = self.slab.offsets["mask_row"]
+            self.slab.dev[o:o + len(mrow)].copy_(self.slab.host[o:o + len(mrow)], non_blocking=True)
+            return bits, self.slab.d("mask_row", len(mrow))
+        return bits, torch.from_numpy(mrow)
+
+    def _sample_cpu(self, lg, k, mask_bits, mask_row):
+        from ..ops import reference
+        s = self.slab
+        masks = None
+        if mask_bits is not None:
+            vocab = lg.shape[1]
+            words = mask_bits.numpy().view(np.uint32)
+            unpacked = np.unpackbits(words.view(np.uint8), bitorder="little").reshape(words.shape[0], -1)[:, :vocab].astype(bool)
+            masks = [None if int(mask_row[j]) < 0 else torch.from_numpy(unpacked[int(mask_row[j])]) for j in range(k)]
+        return reference.sample(lg, s.h("temperature", np.float32)[:k], s.h("top_k")[:k], s.h("top_p", np.float32)[:k],
+                                s.h("min_p", np.float32)[:k], s.h("seeds", np.int64)[:k], masks).numpy()
+
+    def _probes(self, req, logits, slot_logit_row, probe_slots, out_slots):
+        rows = torch.from_numpy(slot_logit_row[probe_slots].astype(np.int64)).to(logits.device)
+        lg = logits[rows]
+        stats = ops.row_stats(lg.contiguous()).float().cpu().numpy()
+        for j, i in enumerate(probe_slots):
+            sp = req.slot_samplers[i]
+            row = lg[j].float()
+            mask = req.logit_masks[int(req.slot_req[i])] if req.logit_masks else None
+            if sp.kind == SamplerKind.DIST:
+                t = sp.temperature if sp.temperature > 0 else 1.0
+                p = torch.softmax(row / t, -1)
+                k = min(sp.top_k if sp.top_k > 0 else 32, p.numel())
+                pv, pi = torch.topk(p, k)
+                out_slots[i] = SlotOutput("distribution", ids=pi.cpu().tolist(), probs=pv.cpu().tolist())
+            elif sp.kind == SamplerKind.RAW_LOGITS:
+                out_slots[i] = SlotOutput("logits", logits=row.cpu().numpy().astype(np.float32).tobytes())
+            elif sp.kind in (SamplerKind.LOGPROB, SamplerKind.LOGPROBS):
+                lab = torch.tensor(list(sp.labels), dtype=torch.long, device=row.device)
+                lp = (row[lab] - float(stats[j, 1])).cpu().tolist()
+                out_slots[i] = SlotOutput("logprobs", logprobs=lp)
+            elif sp.kind == SamplerKind.ENTROPY:
+                out_slots[i] = SlotOutput("entropy", entropy=float(stats[j, 2]))
+            elif sp.kind == SamplerKind.EMBEDDING:
+                out_slots[i] = SlotOutput("embedding", logits=b"")
+            else:
+                raise ValueError(f"unsupported sampler kind {sp.kind}")
+            del mask
+
+    # ------------------------------------------------------------------ public entry points
+    def fire_batch(self, req: ForwardRequest) -> ForwardResponse:
+        t0 = time.perf_counter()
+        self.stats["fires"] += 1
+        qlens, kv_lens, slots = self._derive(req)
+        nslots = len(req.slot_samplers)
+        decode = (req.num_requests > 0 and bool((qlens == 1).all())
+                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)))
+        if self.par.tp_size > 1 and self.par.comm is not None:
+            self.par.comm.publish_step(req, decode)
+        self._token_slots = self._sampler_params(req, None) if nslots else []
+        t1 = time.perf_counter()
+        if decode and self.cuda:
+            logits = self._run_decode(req, slots, kv_lens)
+            slot_logit_row = np.asarray(req.slot_req, dtype=np.int64) if nslots else np.zeros(0, np.int64)
+        else:
+            logits = self._run_general(req, qlens, slots, kv_lens)
+            slot_logit_row = np.arange(nslots, dtype=np.int64)
+        t2 = time.perf_counter()
+        resp = self._respond(req, logits, slot_logit_row)
+        if self.cuda and nslots == 0:
+            torch.cuda.current_stream().synchronize()
+        t3 = time.perf_counter()
+        resp.t_build_us = (t1 - t0) * 1e6
+        resp.t_forward_us = (t2 - t1) * 1e6
+        resp.t_sample_us = (t3 - t2) * 1e6
+        resp.t_total_us = (t3 - t0) * 1e6
+        return resp
+
+    def copy(self, req: CopyRequest) -> None:
+        self.kv.copy(req)
+
+    def health(self) -> bool:
+        if self.cuda:
+            ops.check_kernel_status(self.device)
+        return True
+
+    def shutdown(self) -> None:
+        self.graphs.clear()

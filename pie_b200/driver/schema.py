@@ -1,0 +1,157 @@
+"""Runtime <-> driver contract: plain structs in structure-of-arrays / CSR form.
+
+Runtime and driver share one address space, so a request is a set of numpy arrays handed
+over by reference: no serialisation step. Content-wise the structs carry what the
+reference's wire schema carries (driver/bridge/src/schema.rs:83-286 ForwardRequest /
+ForwardResponse, :196-233 Sampler, :293-353 Copy/Adapter requests;
+driver/bridge/src/capabilities.rs:17-78 for the capability handshake).
+"""
+from __future__ import annotations
+
+import enum
+import json
+from dataclasses import dataclass, field, asdict
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+
+class SamplerKind(enum.IntEnum):
+    MULTINOMIAL = 0   # (temperature, seed)
+    TOP_K = 1         # (temperature, k)
+    TOP_P = 2         # (temperature, p)
+    MIN_P = 3         # (temperature, p)
+    TOP_K_TOP_P = 4   # (temperature, k, p)
+    EMBEDDING = 5
+    DIST = 6          # (temperature, k) -> top-k ids + probabilities
+    RAW_LOGITS = 7
+    LOGPROB = 8       # (token)
+    LOGPROBS = 9      # (tokens...)
+    ENTROPY = 10
+
+
+TOKEN_SAMPLERS = {SamplerKind.MULTINOMIAL, SamplerKind.TOP_K, SamplerKind.TOP_P, SamplerKind.MIN_P,
+                  SamplerKind.TOP_K_TOP_P}
+
+
+@dataclass
+class SamplerSpec:
+    kind: SamplerKind = SamplerKind.MULTINOMIAL
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    seed: int = 0                    # 0 = the driver draws a fresh seed for this fire
+    labels: Sequence[int] = ()       # LOGPROB / LOGPROBS candidates
+
+    @property
+    def is_token(self) -> bool:
+        return self.kind in TOKEN_SAMPLERS
+
+    @staticmethod
+    def greedy() -> "SamplerSpec":
+        return SamplerSpec(SamplerKind.MULTINOMIAL, temperature=0.0)
+
+
+@dataclass
+class SlotOutput:
+    """One typed result per sampler slot, in attach order."""
+    kind: str                         # token | distribution | logits | logprobs | entropy | embedding
+    token: int = 0
+    ids: Optional[list] = None
+    probs: Optional[list] = None
+    logits: Optional[bytes] = None
+    logprobs: Optional[list] = None
+    entropy: float = 0.0
+
+
+@dataclass
+class ForwardRequest:
+    """A batch of R requests with N input tokens in total."""
+    tokens: np.ndarray                 # int32 [N]
+    positions: np.ndarray              # int32 [N]
+    qo_indptr: np.ndarray              # int32 [R+1]
+    kv_page_indices: np.ndarray        # int32 [sum pages]  active prefix of each request's pages
+    kv_page_indptr: np.ndarray         # int32 [R+1]
+    kv_last_page_lens: np.ndarray      # int32 [R]   tokens in the last page AFTER this pass
+    # attention masks: BRLE per input token row for requests with has_user_mask, else causal
+    has_user_mask: np.ndarray = None   # bool [R]
+    mask_runs: Optional[list] = None   # list over token rows (only rows of masked requests) of BRLE lists
+    mask_row_indptr: Optional[np.ndarray] = None  # int32 [R+1] rows of mask_runs per request
+    # constrained decoding: one BRLE over the vocabulary per request (None = no mask)
+    logit_masks: Optional[list] = None
+    # sampling slots
+    slot_req: np.ndarray = None        # int32 [S] request of each slot
+    slot_row: np.ndarray = None        # int32 [S] token row (global index into tokens) of each slot
+    slot_samplers: List[SamplerSpec] = field(default_factory=list)
+    # speculative drafts already spliced into tokens: number of draft tokens per request
+    spec_counts: Optional[np.ndarray] = None
+    context_ids: Optional[np.ndarray] = None       # uint64 [R]
+    adapter_ids: Optional[np.ndarray] = None       # int64 [R], -1 = none
+    single_token_mode: bool = False                # every request has exactly one input token
+
+    @property
+    def num_requests(self) -> int:
+        return len(self.qo_indptr) - 1
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.tokens)
+
+
+@dataclass
+class ForwardResponse:
+    slots: List[SlotOutput]
+    # pure token fast path: tokens[i] is the sampled token of slot i when every slot is a token sampler
+    tokens: Optional[np.ndarray] = None
+    # phase timings in microseconds (the reference returns 6 probe fields per response)
+    t_build_us: float = 0.0
+    t_h2d_us: float = 0.0
+    t_forward_us: float = 0.0
+    t_sample_us: float = 0.0
+    t_d2h_us: float = 0.0
+    t_total_us: float = 0.0
+
+
+class CopyDir(enum.IntEnum):
+    D2D = 0
+    D2H = 1
+    H2D = 2
+    H2H = 3
+
+
+@dataclass
+class CopyRequest:
+    direction: CopyDir
+    srcs: np.ndarray   # int32 page ids (device pool for D2*, host pool for H2*)
+    dsts: np.ndarray
+
+
+@dataclass
+class Capabilities:
+    """What a driver advertises at start-up; the runtime batches against these limits."""
+    total_pages: int = 0
+    kv_page_size: int = 16
+    swap_pool_size: int = 0
+    max_forward_tokens: int = 8192
+    max_forward_requests: int = 512
+    max_page_refs: int = 1 << 20
+    max_logit_rows: int = 1024
+    max_prob_rows: int = 1024
+    max_sampler_rows: int = 1024
+    max_logprob_labels: int = 4096
+    max_custom_mask_bytes: int = 1 << 26
+    arch_name: str = ""
+    vocab_size: int = 0
+    max_model_len: int = 0
+    activation_dtype: str = "bfloat16"
+    tp_size: int = 1
+    system_speculation: bool = False
+    rs_cache_slots: int = 0
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self))
+
+    @staticmethod
+    def from_json(s: str) -> "Capabilities":
+        return Capabilities(**json.loads(s))

@@ -1,0 +1,139 @@
+"""Model configuration parsed from a Hugging Face ``config.json``.
+
+Keys consumed mirror the reference's HF config reader
+(driver/cuda/src/loader/hf_config.hpp:145-215).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field, asdict
+from pathlib import Path
+from typing import Optional
+
+LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "olmo2", "phi3"}
+MOE_TYPES = {"qwen3_moe", "mixtral"}
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    max_position_embeddings: int = 131072
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    rope_scaling: Optional[dict] = None
+    tie_word_embeddings: bool = False
+    qk_norm: bool = False           # Qwen3: per-head RMSNorm on q and k
+    attention_bias: bool = False    # Qwen2: bias on q/k/v projections
+    sliding_window: int = -1
+    # mixture of experts
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    # quantisation of the linear weights: None | "fp8_block" (128x128 weight scales)
+    quantization: Optional[str] = None
+    dtype: str = "bfloat16"
+    name: str = ""
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    @staticmethod
+    def from_hf(cfg: dict, name: str = "") -> "ModelConfig":
+        mt = cfg.get("model_type", "llama")
+        heads = cfg["num_attention_heads"]
+        hd = cfg.get("head_dim") or cfg["hidden_size"] // heads
+        q = cfg.get("quantization_config") or {}
+        quant = None
+        if q.get("quant_method") == "fp8" and q.get("weight_block_size"):
+            quant = "fp8_block"
+        return ModelConfig(
+            model_type=mt,
+            hidden_size=cfg["hidden_size"],
+            intermediate_size=cfg.get("intermediate_size", 0),
+            num_hidden_layers=cfg["num_hidden_layers"],
+            num_attention_heads=heads,
+            num_key_value_heads=cfg.get("num_key_value_heads", heads),
+            head_dim=hd,
+            vocab_size=cfg["vocab_size"],
+            max_position_embeddings=cfg.get("max_position_embeddings", 8192),
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-5),
+            rope_theta=cfg.get("rope_theta", 10000.0),
+            rope_scaling=cfg.get("rope_scaling"),
+            tie_word_embeddings=cfg.get("tie_word_embeddings", False),
+            qk_norm=mt in ("qwen3", "qwen3_moe") or cfg.get("use_qk_norm", False),
+            attention_bias=cfg.get("attention_bias", mt == "qwen2"),
+            sliding_window=cfg.get("sliding_window") or -1 if cfg.get("use_sliding_window", False) else -1,
+            num_experts=cfg.get("num_experts", cfg.get("num_local_experts", 0)) or 0,
+            num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=cfg.get("norm_topk_prob", True),
+            quantization=quant,
+            dtype=str(cfg.get("torch_dtype", "bfloat16")),
+            name=name,
+        )
+
+    @staticmethod
+    def from_path(path) -> "ModelConfig":
+        p = Path(path)
+        with open(p / "config.json") as f:
+            return ModelConfig.from_hf(json.load(f), name=p.name)
+
+
+# Architectures named by the benchmark configurations (random-init weights of these shapes).
+PRESETS = {
+    "tiny-llama": dict(model_type="llama", hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000,
+                       rope_theta=10000.0, rms_norm_eps=1e-5, dtype="float32"),
+    "llama-3.1-8b": dict(model_type="llama", hidden_size=4096, intermediate_size=14336,
+                         num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                         head_dim=128, vocab_size=128256, rope_theta=500000.0, rms_norm_eps=1e-5),
+    "qwen3-32b": dict(model_type="qwen3", hidden_size=5120, intermediate_size=25600,
+                      num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                      vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, qk_norm=True),
+    "qwen3-32b-fp8": dict(model_type="qwen3", hidden_size=5120, intermediate_size=25600,
+                          num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                          head_dim=128, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                          qk_norm=True, quantization="fp8_block"),
+    "qwen3-30b-a3b": dict(model_type="qwen3_moe", hidden_size=2048, intermediate_size=6144,
+                          num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4,
+                          head_dim=128, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                          qk_norm=True, num_experts=128, num_experts_per_tok=8,
+                          moe_intermediate_size=768, norm_topk_prob=True),
+    "qwen3-0.6b": dict(model_type="qwen3", hidden_size=1024, intermediate_size=3072,
+                       num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                       vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, qk_norm=True,
+                       tie_word_embeddings=True),
+    "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
+                           num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                           vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,
+                           num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                           dtype="float32"),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    if name not in PRESETS:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
+    kw = dict(PRESETS[name])
+    kw.update(overrides)
+    return ModelConfig(name=name, **kw)

@@ -1,0 +1,174 @@
+"""Decoder-only transformer over paged KV: Llama-2/3, Mistral, Qwen2, Qwen3 (dense) and
+Qwen3-MoE / Mixtral-style mixture-of-experts, tensor-parallel (and expert-parallel) aware.
+
+One forward = embed -> L x [RMSNorm -> fused QKV GEMM -> per-head q/k RMSNorm + RoPE + paged
+KV write -> paged attention -> o_proj GEMM (+residual | +TP reduce) -> RMSNorm -> gate/up GEMM
+with SwiGLU epilogue (or MoE block) -> down GEMM (+residual | +TP reduce)] -> final norm ->
+lm_head on the rows that need logits.
+
+Behavioural counterpart: the reference's `llama_like_forward_paged`
+(driver/cuda/src/model/llama_like.cpp:239-851) and its MoE block
+(driver/cuda/src/model/qwen3_5_moe_forward.cpp:1128-1721). The KV write slot is the tail
+of the context (positions only feed RoPE), as in driver/cuda/src/kernels/kv_paged.cu:52-62.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..ops import reference
+from .config import ModelConfig
+
+
+@dataclass
+class ForwardInputs:
+    """Device-resident inputs of one forward pass (one 'fire')."""
+    tokens: torch.Tensor          # int32 [N]
+    positions: torch.Tensor       # int32 [N]
+    slots: torch.Tensor           # int32 [N]  KV slot (page*page_size+offset) of each new token
+    attn: object                  # ops.DecodePlan | ops.PrefillPlan | ops.AttnBatch (CPU)
+    logit_rows: Optional[torch.Tensor] = None   # int32 rows of the hidden state that need logits
+    is_decode: bool = False
+
+
+class ParallelContext:
+    """Tensor/expert-parallel placement of this rank. Collectives live in pie_b200.parallel."""
+
+    def __init__(self, tp_size: int = 1, tp_rank: int = 0, comm=None, ep: bool = False):
+        self.tp_size, self.tp_rank, self.comm, self.ep = tp_size, tp_rank, comm, ep
+
+
+class Transformer:
+    def __init__(self, cfg: ModelConfig, weights: dict, device, dtype, par: Optional[ParallelContext] = None,
+                 gemm_backend: str = "tcgen05"):
+        self.cfg, self.w, self.device, self.dtype = cfg, weights, torch.device(device), dtype
+        self.par = par or ParallelContext()
+        t = self.par.tp_size
+        self.hq = cfg.num_attention_heads // t
+        self.hkv = max(1, cfg.num_key_value_heads // t)
+        self.d = cfg.head_dim
+        self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.inv_freq = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, self.device)
+        self.gemm_backend = gemm_backend if self.device.type == "cuda" else "torch"
+        self.vocab_local = weights["lm_head"].shape[0]
+
+    # ------------------------------------------------------------------ linear algebra
+    def _gemm(self, x, w, residual=None, swiglu=False):
+        if self.gemm_backend == "tcgen05" and x.dtype == torch.bfloat16:
+            epi = ops.EPI_SWIGLU if swiglu else (ops.EPI_RESIDUAL if residual is not None else ops.EPI_STORE)
+            return ops.gemm(x, w, residual=residual, epilogue=epi)
+        # library path (cuBLAS through torch): the baseline the tcgen05 kernel is measured against
+        y = torch.matmul(x, w.t())
+        if swiglu:
+            return reference.swiglu_interleaved(y) if not y.is_cuda else _swiglu_interleaved_cuda(y)
+        if residual is not None:
+            y = y + residual
+        return y
+
+    # ------------------------------------------------------------------ layers
+    def _attention(self, q, kv_layer, fi: ForwardInputs):
+        if not q.is_cuda:
+            return ops.paged_attention_cpu(q, kv_layer, fi.attn, self.sm_scale)
+        if fi.is_decode:
+            return ops.paged_decode_attention(q, kv_layer, fi.attn, self.sm_scale)
+        return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale)
+
+    def _mlp(self, x, lw, h):
+        act = self._gemm(x, lw["w_gate_up"], swiglu=True)
+        return self._row_parallel(act, lw["w_down"], h)
+
+    def _row_parallel(self, a, w, h):
+        """h + a @ w.T, summed over the tensor-parallel group."""
+        if self.par.tp_size == 1:
+            return self._gemm(a, w, residual=h)
+        y = self.par.comm.gemm_allreduce(a, w, self)
+        return y.add_(h)
+
+    def _moe(self, x, lw, h):
+        from .moe import moe_block
+        return moe_block(self, x, lw, h)
+
+    def forward_hidden(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        page_size = kv_cache.shape[4]
+        if self.par.tp_size > 1 and w.get("embed_sharded", False):
+            h = ops.embed(fi.tokens, w["embed"], vocab_start=w["embed_vocab_start"])
+            h = self.par.comm.all_reduce(h)
+        else:
+            h = ops.embed(fi.tokens, w["embed"])
+        n = h.shape[0]
+        for li in range(cfg.num_hidden_layers):
+            lw = w["layers"][li]
+            x = ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
+            qkv = self._gemm(x, lw["wqkv"])
+            if "bqkv" in lw:
+                qkv = qkv + lw["bqkv"]
+            q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, lw.get("q_norm"),
+                                         lw.get("k_norm"), kv_cache[li], self.hq, self.hkv, self.d,
+                                         page_size, cfg.rms_norm_eps)
+            a = self._attention(q, kv_cache[li], fi)
+            h = self._row_parallel(a.reshape(n, self.hq * self.d), lw["wo"], h)
+            x = ops.rmsnorm(h, lw["ln2"], cfg.rms_norm_eps)
+            if "experts_gate_up" in lw:
+                h = self._moe(x, lw, h)
+            else:
+                h = self._mlp(x, lw, h)
+        return h
+
+    def logits(self, h: torch.Tensor, fi: ForwardInputs) -> torch.Tensor:
+        """lm_head on the requested rows only ('compact logit rows')."""
+        rows = h if fi.logit_rows is None else ops.gather_rows(h, fi.logit_rows)
+        x = ops.rmsnorm(rows, self.w["final_norm"], self.cfg.rms_norm_eps)
+        return self._gemm(x, self.w["lm_head"])
+
+    def forward(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
+        return self.logits(self.forward_hidden(fi, kv_cache), fi)
+
+
+def _swiglu_interleaved_cuda(y):
+    g, u = y[..., 0::2], y[..., 1::2]
+    return torch.nn.functional.silu(g) * u
+
+
+def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> torch.Tensor:
+    """Independent dense (non-paged) fp32 forward of the same weights for one sequence:
+    RMSNorm -> QKV -> rotate-half RoPE -> causal attention -> SwiGLU. Returns logits [T, V].
+    This is the token-for-token oracle of the paged engine path."""
+    x = w["embed"].float()[tokens.long()]
+    t = x.shape[0]
+    pos = torch.arange(t)
+    inv = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+
+    def norm(v, g):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * g.float()
+
+    for lw in w["layers"]:
+        xn = norm(x, lw["ln1"])
+        qkv = xn @ lw["wqkv"].float().t()
+        if "bqkv" in lw:
+            qkv = qkv + lw["bqkv"].float()
+        q = qkv[:, : hq * d].reshape(t, hq, d)
+        k = qkv[:, hq * d:(hq + hkv) * d].reshape(t, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].reshape(t, hkv, d)
+        if "q_norm" in lw:
+            q, k = norm(q, lw["q_norm"]), norm(k, lw["k_norm"])
+        q, k = reference._rope(q, pos, inv), reference._rope(k, pos, inv)
+        k = k.repeat_interleave(hq // hkv, dim=1)
+        v = v.repeat_interleave(hq // hkv, dim=1)
+        s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
+        s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(t, hq * d)
+        x = x + a @ lw["wo"].float().t()
+        xn = norm(x, lw["ln2"])
+        if "experts_gate_up" in lw:
+            from .moe import moe_reference
+            x = x + moe_reference(cfg, xn, lw)
+        else:
+            gu = xn @ lw["w_gate_up"].float().t()
+            x = x + (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t()
+    return norm(x, w["final_norm"]) @ w["lm_head"].float().t()

@@ -1,0 +1,370 @@
+"""Model-forward ops. GPU tensors go to the hand-written sm_100a kernels
+(``csrc/kernels``), CPU tensors to the PyTorch reference in :mod:`.reference`.
+
+There is no silent fallback on a GPU: if the kernel library is missing, a call with CUDA
+tensors raises :class:`pie_b200.ops._lib.KernelLibraryError`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib, reference
+from ._lib import check, fn, ptr, stream_ptr
+
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+
+_NUM_SMS = {}
+
+
+def num_sms(device=None) -> int:
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if dev not in _NUM_SMS:
+        _NUM_SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _NUM_SMS[dev]
+
+
+# --------------------------------------------------------------------------- status word
+_STATUS = {}
+
+
+def kernel_status(device=None) -> torch.Tensor:
+    """Device int32 that kernels with bounded waits set when a wait runs out (0 = healthy)."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if dev not in _STATUS:
+        _STATUS[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+    return _STATUS[dev]
+
+
+def check_kernel_status(device=None) -> None:
+    st = int(kernel_status(device).item())
+    if st != 0:
+        kernel_status(device).zero_()
+        raise _lib.KernelLibraryError(f"a kernel gave up on a bounded wait (status {st})")
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed(tokens, table, vocab_start: int = 0, out=None):
+    if not table.is_cuda:
+        return reference.embed(tokens, table, vocab_start)
+    n, h = tokens.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty(n, h, dtype=table.dtype, device=table.device)
+    check(fn("pie_embed_gather")(ptr(tokens), ptr(table), ptr(out), n, h, vocab_start, table.shape[0],
+                                 stream_ptr()), "embed_gather")
+    return out
+
+
+def rmsnorm(x, w, eps: float, out=None, w_offset: float = 0.0):
+    if not x.is_cuda:
+        return reference.rmsnorm(x, w, eps, w_offset)
+    if out is None:
+        out = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    check(fn("pie_rmsnorm")(ptr(x), None, None, ptr(w), ptr(out), rows, x.shape[-1], eps, w_offset,
+                            stream_ptr()), "rmsnorm")
+    return out
+
+
+def add_rmsnorm(delta, residual, w, eps: float, out=None, w_offset: float = 0.0):
+    """residual += delta in place; returns rmsnorm(residual) * w."""
+    if not residual.is_cuda:
+        return reference.add_rmsnorm(delta, residual, w, eps, w_offset)
+    if out is None:
+        out = torch.empty_like(residual)
+    rows = residual.numel() // residual.shape[-1]
+    check(fn("pie_rmsnorm")(ptr(residual), ptr(delta), ptr(residual), ptr(w), ptr(out), rows,
+                            residual.shape[-1], eps, w_offset, stream_ptr()), "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up, out=None):
+    if not gate_up.is_cuda:
+        return reference.swiglu(gate_up)
+    rows, two_i = gate_up.shape
+    if out is None:
+        out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    check(fn("pie_swiglu")(ptr(gate_up), ptr(out), rows, two_i // 2, stream_ptr()), "swiglu")
+    return out
+
+
+def qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, kv_layer, hq, hkv,
+                         head_dim, page_size, eps, q_out=None):
+    if not qkv.is_cuda:
+        return reference.qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w,
+                                              kv_layer, hq, hkv, head_dim, page_size, eps)
+    n = qkv.shape[0]
+    if q_out is None:
+        q_out = torch.empty(n, hq, head_dim, dtype=qkv.dtype, device=qkv.device)
+    check(fn("pie_qk_norm_rope_kvwrite")(ptr(qkv), ptr(positions), ptr(slots), ptr(inv_freq),
+                                         ptr(q_norm_w), ptr(k_norm_w), ptr(q_out), ptr(kv_layer), n,
+                                         hq, hkv, head_dim, page_size, eps, qkv.stride(0),
+                                         stream_ptr()), "qk_norm_rope_kvwrite")
+    return q_out
+
+
+def gather_rows(x, idx, out=None):
+    if not x.is_cuda:
+        return x[idx.long()]
+    if out is None:
+        out = torch.empty(idx.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+    check(fn("pie_gather_rows")(ptr(x), ptr(idx), ptr(out), idx.numel(), x.shape[1], stream_ptr()),
+          "gather_rows")
+    return out
+
+
+def copy_pages(kv, src, dst):
+    """kv [layers, pages, ...]: copy page src[i] -> dst[i] in every layer."""
+    if not kv.is_cuda:
+        kv[:, dst.long()] = kv[:, src.long()]
+        return
+    layers = kv.shape[0]
+    page_bytes = kv[0, 0].numel() * kv.element_size()
+    layer_bytes = kv[0].numel() * kv.element_size()
+    check(fn("pie_copy_pages")(ptr(kv), ptr(src), ptr(dst), src.numel(), layers, page_bytes,
+                               layer_bytes, stream_ptr()), "copy_pages")
+
+
+def brle_expand(rows_runs, nbits: int, device, tail_value: bool = False):
+    """Expand BRLE rows (lists of run lengths, even index = zeros) to a packed bitmask
+    [rows, ceil(nbits/32)] uint32 (as int32 tensor)."""
+    words = (nbits + 31) // 32
+    nrows = len(rows_runs)
+    if torch.device(device).type != "cuda":
+        out = torch.zeros(nrows, words * 32, dtype=torch.bool)
+        for r, runs in enumerate(rows_runs):
+            out[r, :nbits] = reference.brle_to_bool(runs, nbits, tail_value)
+        w = out.view(nrows, words, 32).to(torch.int64)
+        packed = (w << torch.arange(32, dtype=torch.int64)).sum(-1)
+        return _to_i32(packed)
+    ends = [np.cumsum(np.asarray(r, dtype=np.int64)).clip(max=2**32 - 1).astype(np.uint32) for r in rows_runs]
+    indptr = np.zeros(nrows + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum([len(e) for e in ends])
+    flat = np.concatenate(ends) if ends and indptr[-1] > 0 else np.zeros(1, dtype=np.uint32)
+    d_ends = torch.from_numpy(flat.view(np.int32)).to(device)
+    d_indptr = torch.from_numpy(indptr).to(device)
+    out = torch.empty(nrows, words, dtype=torch.int32, device=device)
+    check(fn("pie_brle_expand")(ptr(d_ends), ptr(d_indptr), ptr(out), nrows, nbits, int(tail_value),
+                                stream_ptr()), "brle_expand")
+    return out
+
+
+def _to_i32(packed_i64):
+    p = packed_i64 & 0xFFFFFFFF
+    p = torch.where(p >= 2**31, p - 2**32, p)
+    return p.to(torch.int32)
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(x, w, residual=None, epilogue: int = EPI_STORE, out=None, force_bn: int = 0):
+    """y = x @ w.T (+ residual | SwiGLU over interleaved gate/up columns). x [M,K], w [N,K]."""
+    if not x.is_cuda:
+        y = reference.gemm(x, w, residual if epilogue == EPI_RESIDUAL else None)
+        return reference.swiglu_interleaved(y) if epilogue == EPI_SWIGLU else y
+    m, k = x.shape
+    n = w.shape[0]
+    n_out = n // 2 if epilogue == EPI_SWIGLU else n
+    if out is None:
+        out = torch.empty(m, n_out, dtype=x.dtype, device=x.device)
+    if m == 0:
+        return out
+    check(fn("pie_gemm_bf16")(ptr(x), ptr(w), ptr(out), ptr(residual), m, n, k, x.stride(0), w.stride(0),
+                              out.stride(0), residual.stride(0) if residual is not None else 0, epilogue,
+                              force_bn, ptr(kernel_status(x.device)), num_sms(x.device), stream_ptr()),
+          "gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------- attention
+@dataclass
+class AttnBatch:
+    """Host description of one fire's attention work (CSR arrays as numpy int32)."""
+    qo_indptr: np.ndarray
+    kv_page_indptr: np.ndarray
+    page_indices: np.ndarray
+    kv_lens: np.ndarray            # total kv length per request, new tokens included
+    masks: Optional[list] = None   # per request: None (causal) or bool [qo_len, kv_len] array
+    window_left: int = -1
+
+    @property
+    def num_requests(self) -> int:
+        return len(self.kv_lens)
+
+    @property
+    def is_decode(self) -> bool:
+        q = np.diff(self.qo_indptr)
+        return bool(len(q) > 0 and (q == 1).all() and self.masks is None)
+
+
+def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items: int = 0,
+                      min_chunk: int = 256):
+    """Split each request's KV range into chunks so that items*hkv fills the machine.
+
+    Returns (item_req, item_start, item_end, req_item_indptr) as int32 arrays.
+    """
+    kv_lens = np.asarray(kv_lens, dtype=np.int64)
+    total = int(kv_lens.sum())
+    chunk = max(min_chunk, -(-total * hkv // max(1, target_ctas * 4)))
+    chunk = -(-chunk // 16) * 16
+    while True:
+        n_items = np.maximum(1, -(-kv_lens // chunk))
+        if max_items <= 0 or int(n_items.sum()) <= max_items:
+            break
+        chunk *= 2
+    indptr = np.zeros(len(kv_lens) + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(n_items)
+    tot = int(indptr[-1])
+    item_req = np.repeat(np.arange(len(kv_lens), dtype=np.int32), n_items)
+    within = np.arange(tot, dtype=np.int64) - np.repeat(indptr[:-1].astype(np.int64), n_items)
+    start = within * chunk
+    end = np.minimum(start + chunk, kv_lens[item_req])
+    return item_req, start.astype(np.int32), end.astype(np.int32), indptr
+
+
+def plan_prefill_tiles(qo_indptr: np.ndarray, group: int):
+    """Tiles of 64/group query tokens per request: (tile_req, tile_qstart)."""
+    tq = max(1, 64 // group)
+    qlens = np.diff(qo_indptr).astype(np.int64)
+    ntiles = -(-qlens // tq)
+    tile_req = np.repeat(np.arange(len(qlens), dtype=np.int32), ntiles)
+    base = np.zeros(len(qlens) + 1, dtype=np.int64)
+    base[1:] = np.cumsum(ntiles)
+    within = np.arange(int(base[-1]), dtype=np.int64) - np.repeat(base[:-1], ntiles)
+    return tile_req, (within * tq).astype(np.int32)
+
+
+@dataclass
+class DecodePlan:
+    """Device-side arguments of the split-KV decode kernel (static addresses: graph safe)."""
+    page_indices: torch.Tensor
+    kv_page_indptr: torch.Tensor
+    item_req: torch.Tensor
+    item_start: torch.Tensor
+    item_end: torch.Tensor
+    req_item_indptr: torch.Tensor
+    num_items: torch.Tensor       # int32[1] on device
+    scratch: torch.Tensor         # fp32 partial outputs + lse
+    max_items: int
+    num_reqs: int
+    num_ctas: int
+    page_size: int
+
+
+def decode_scratch_floats(max_items: int, hq: int, head_dim: int) -> int:
+    return max_items * hq * head_dim + max_items * hq
+
+
+def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=None):
+    """q [R, hq, D] (one token per request) against paged KV; split-KV + merge."""
+    if out is None:
+        out = torch.empty_like(q)
+    r, hq, d = q.shape
+    hkv = kv_layer.shape[2]
+    check(fn("pie_paged_decode_attn")(
+        ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
+        ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),
+        ptr(out), ptr(plan.scratch), plan.max_items, plan.num_reqs, hq, hkv, d, plan.page_size,
+        sm_scale, plan.num_ctas, 1, stream_ptr()), "paged_decode_attn")
+    return out
+
+
+@dataclass
+class PrefillPlan:
+    page_indices: torch.Tensor
+    kv_page_indptr: torch.Tensor
+    qo_indptr: torch.Tensor
+    kv_lens: torch.Tensor
+    tile_req: torch.Tensor
+    tile_qstart: torch.Tensor
+    num_tiles: int
+    page_size: int
+    mask_bits: Optional[torch.Tensor] = None
+    mask_word_indptr: Optional[torch.Tensor] = None
+    window_left: int = -1
+
+
+def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out=None, lse_out=None):
+    if out is None:
+        out = torch.empty_like(q)
+    n, hq, d = q.shape
+    hkv = kv_layer.shape[2]
+    check(fn("pie_paged_prefill_attn")(
+        ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
+        ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
+        ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), hq, hkv, d,
+        plan.page_size, sm_scale, plan.window_left, stream_ptr()), "paged_prefill_attn")
+    return out
+
+
+def pack_masks(masks, kv_lens, device):
+    """Pack per-request bool [qo_len, kv_len] masks into the word layout the prefill kernel
+    reads: request r starts at word mask_word_indptr[r], row stride ceil(kv_len/32) words.
+    Requests without a mask get an all-causal mask synthesised by the caller beforehand."""
+    chunks, indptr = [], [0]
+    for m, kl in zip(masks, kv_lens):
+        words = (int(kl) + 31) // 32
+        mm = np.zeros((m.shape[0], words * 32), dtype=bool)
+        mm[:, : m.shape[1]] = np.asarray(m, dtype=bool)[:, : words * 32]
+        bits = np.packbits(mm.reshape(m.shape[0], words, 32), axis=-1, bitorder="little")
+        chunks.append(bits.reshape(-1).view(np.uint32))
+        indptr.append(indptr[-1] + m.shape[0] * words)
+    flat = np.concatenate(chunks) if chunks else np.zeros(1, dtype=np.uint32)
+    return (torch.from_numpy(flat.view(np.int32)).to(device),
+            torch.from_numpy(np.asarray(indptr, dtype=np.int64)).to(device))
+
+
+def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device) -> PrefillPlan:
+    tile_req, tile_qstart = plan_prefill_tiles(batch.qo_indptr, group)
+    mask_bits = mask_indptr = None
+    if batch.masks is not None:
+        masks = []
+        qlens = np.diff(batch.qo_indptr)
+        for r, m in enumerate(batch.masks):
+            kl, ql = int(batch.kv_lens[r]), int(qlens[r])
+            if m is None:
+                qi = np.arange(ql)[:, None]
+                m = np.arange(kl)[None, :] < (kl - ql + qi + 1)
+            masks.append(np.asarray(m, dtype=bool))
+        mask_bits, mask_indptr = pack_masks(masks, batch.kv_lens, device)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(device)
+    return PrefillPlan(t(batch.page_indices), t(batch.kv_page_indptr), t(batch.qo_indptr),
+                       t(batch.kv_lens), t(tile_req), t(tile_qstart), len(tile_req), page_size,
+                       mask_bits, mask_indptr, batch.window_left)
+
+
+def paged_attention_cpu(q, kv_layer, batch: AttnBatch, sm_scale: float):
+    masks = None
+    if batch.masks is not None:
+        masks = [None if m is None else torch.as_tensor(np.asarray(m, dtype=bool)) for m in batch.masks]
+    return reference.paged_attention(q, kv_layer, batch.qo_indptr, batch.kv_page_indptr,
+                                     torch.as_tensor(batch.page_indices), batch.kv_lens, sm_scale,
+                                     masks=masks, window_left=batch.window_left)
+
+
+# --------------------------------------------------------------------------- sampling
+def sample(logits, temperature, top_k, top_p, min_p, seeds, mask_bits=None, mask_row=None, out=None):
+    """Draw one token per row of bf16 logits on the device. All parameter tensors are per row
+    (float32 / int32 / float32 / float32 / int64 seeds)."""
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    mask_words = mask_bits.shape[1] if mask_bits is not None else 0
+    check(fn("pie_sample")(ptr(logits), logits.stride(0), rows, vocab, ptr(temperature), ptr(top_k),
+                           ptr(top_p), ptr(min_p), ptr(seeds), ptr(mask_bits), ptr(mask_row),
+                           mask_words, ptr(out), stream_ptr()), "sample")
+    return out
+
+
+def row_stats(logits):
+    """[rows, 3] fp32: max, log-sum-exp and entropy of the unscaled next-token distribution."""
+    if not logits.is_cuda:
+        return reference.row_stats(logits)
+    rows, vocab = logits.shape
+    out = torch.empty(rows, 3, dtype=torch.float32, device=logits.device)
+    check(fn("pie_row_stats")(ptr(logits), logits.stride(0), rows, vocab, ptr(out), stream_ptr()),
+          "row_stats")
+    return out

@@ -1,0 +1,110 @@
+"""ctypes binding of ``libpie_kernels.so`` (the sm_100a kernel library).
+
+The library is built in-tree by :mod:`pie_b200._build`. On a machine with a GPU the
+kernels are the only path: if the library is missing or a symbol cannot be resolved the
+ops raise instead of falling back to PyTorch. On a CPU-only machine the ops use their
+PyTorch reference implementations (``pie_b200.ops.reference``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_C" / "libpie_kernels.so"
+
+p = C.c_void_p
+i32 = C.c_int
+i64 = C.c_long
+f32 = C.c_float
+
+_SIGNATURES = {
+    "pie_embed_gather": [p, p, p, i32, i32, i32, i32, p],
+    "pie_rmsnorm": [p, p, p, p, p, i32, i32, f32, f32, p],
+    "pie_swiglu": [p, p, i64, i32, p],
+    "pie_qk_norm_rope_kvwrite": [p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
+    "pie_gather_rows": [p, p, p, i32, i32, p],
+    "pie_copy_pages": [p, p, p, i32, i32, i64, i64, p],
+    "pie_brle_expand": [p, p, p, i32, i32, i32, p],
+    "pie_paged_decode_attn": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, p],
+    "pie_paged_prefill_attn": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, f32, i32, p],
+    "pie_prefill_tile_tokens": [i32],
+    "pie_sample": [p, i64, i32, i32, p, p, p, p, p, p, p, i32, p, p],
+    "pie_row_stats": [p, i64, i32, i32, p, p],
+    "pie_gemm_bf16": [p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, i32, p],
+}
+_RESTYPES = {"pie_decode_attn_scratch_floats": i64}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load(required: bool = True):
+    """Return the loaded kernel library (building nothing). Raises when absent and required."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        if not _LIB_PATH.exists():
+            if required:
+                raise KernelLibraryError(
+                    f"{_LIB_PATH} is missing: run `python -m pie_b200._build` (needs nvcc) first")
+            return None
+        lib = C.CDLL(str(_LIB_PATH))
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name, None)
+            if fn is None:
+                continue  # resolved lazily by `fn()` so that a stale library fails loudly on use
+            fn.argtypes = argtypes
+            fn.restype = i32
+        for name, rt in _RESTYPES.items():
+            f = getattr(lib, name, None)
+            if f is not None:
+                f.restype = rt
+        _LIB = lib
+        return _LIB
+
+
+def fn(name: str):
+    lib = load(required=True)
+    f = getattr(lib, name, None)
+    if f is None:
+        raise KernelLibraryError(f"symbol {name} not found in {_LIB_PATH}; rebuild the kernel library")
+    return f
+
+
+def declare(name: str, argtypes, restype=i32):
+    """Declare the signature of a symbol added after the table above (multi-GPU kernels)."""
+    f = fn(name)
+    f.argtypes = argtypes
+    f.restype = restype
+    return f
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def check(err: int, what: str) -> None:
+    if err != 0:
+        raise KernelLibraryError(f"{what}: CUDA error code {err}")
+
+
+def use_cuda(t: torch.Tensor) -> bool:
+    """True when `t` lives on a GPU, in which case the native kernels must be used."""
+    return t.is_cuda

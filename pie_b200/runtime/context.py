@@ -1,0 +1,452 @@
+"""Context manager: the KV state that inferlets own and manipulate.
+
+A context = a chain of committed pages (immutable, content-hashed, shared through the page
+store) + a tail of working pages (exclusive, partially filled) + the lineage of tokens that
+fills them. Inferlets allocate (reserve), commit, fork, truncate, release, save/snapshot,
+open/take and destroy contexts; forward passes pin a context to read a consistent page list.
+
+States: ACTIVE (resident), PINNED (in a batch), SUSPENDED (evicted: working pages stashed on
+the CPU tier or dropped for replay), plus named snapshots that live outside any process.
+
+Behavioural counterpart of runtime/src/context.rs:311-840 (API), :1549-1981 (create, destroy,
+commit with position-monotonicity check :1752-1763, pin :1834-1940), context/snapshot.rs:37-392
+(fork / save / open / take), context/sched.rs:1084-1176 (suspend with CPU stash) and
+context/restore.rs (restore + replay). Page arithmetic follows runtime/src/api/inference.rs:914-942.
+"""
+from __future__ import annotations
+
+import enum
+import itertools
+import threading
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+
+from ..driver.schema import CopyDir, CopyRequest
+from .pagestore import PageStore, page_hash
+
+
+class ContextError(RuntimeError):
+    pass
+
+
+class State(enum.Enum):
+    ACTIVE = "active"
+    PINNED = "pinned"
+    SUSPENDED = "suspended"
+    DESTROYED = "destroyed"
+
+
+@dataclass
+class Context:
+    id: int
+    model: str
+    owner: str                        # process id ("" for snapshots)
+    driver: int = 0
+    chain: List[int] = field(default_factory=list)           # committed chain hashes
+    working_pages: List[int] = field(default_factory=list)   # physical page ids
+    tokens: List[int] = field(default_factory=list)          # lineage of the working area
+    positions: List[int] = field(default_factory=list)
+    mask_keys: List[bytes] = field(default_factory=list)     # per working token, b"" = causal
+    committed_tokens: List[int] = field(default_factory=list)     # lineage of committed pages (for replay)
+    committed_positions: List[int] = field(default_factory=list)
+    max_committed_position: int = -1
+    adapter_seed: int = 0
+    state: State = State.ACTIVE
+    pins: int = 0
+    bid: float = 1.0
+    stash: Optional[List[int]] = None    # host swap-pool page ids while suspended
+    created_seq: int = 0
+
+    @property
+    def working_token_count(self) -> int:
+        return len(self.tokens)
+
+
+@dataclass
+class PinnedContext:
+    context_id: int
+    pages: List[int]          # physical ids: committed then working
+    kv_len: int               # committed_pages*page + working tokens
+    driver: int
+
+
+class ContextManager:
+    """All contexts of one model. Thread-safe: inferlet host calls and the scheduler share it."""
+
+    def __init__(self, model: str, page_size: int, stores: Sequence[PageStore],
+                 copy_fn: Optional[Callable[[int, CopyRequest], None]] = None,
+                 swap_pages: int = 0):
+        self.model, self.page_size = model, page_size
+        self.stores = list(stores)
+        self.copy_fn = copy_fn or (lambda driver, req: None)
+        self.contexts: Dict[int, Context] = {}
+        self.snapshots: Dict[tuple, int] = {}      # (username, name) -> context id
+        self.by_owner: Dict[str, set] = {}
+        self._ids = itertools.count(1)
+        self._seq = itertools.count(1)
+        self.lock = threading.RLock()
+        self._swap_free = list(range(swap_pages - 1, -1, -1))
+        self.counters = {"created": 0, "forked": 0, "commits": 0, "dedup_pages": 0, "suspended": 0,
+                         "restored": 0, "evictions": 0, "replayed_tokens": 0}
+        self.evict_hook: Optional[Callable[[int, int], bool]] = None   # (driver, pages needed) -> made room
+
+    # ------------------------------------------------------------------ helpers
+    def _get(self, cid: int) -> Context:
+        ctx = self.contexts.get(cid)
+        if ctx is None or ctx.state == State.DESTROYED:
+            raise ContextError(f"context {cid} does not exist")
+        return ctx
+
+    def _store(self, ctx: Context) -> PageStore:
+        return self.stores[ctx.driver]
+
+    def _alloc(self, driver: int, n: int, exclude: Optional[int] = None) -> List[int]:
+        store = self.stores[driver]
+        pages = store.pool.alloc(n)
+        while pages is None:
+            if not self._evict_one(driver, exclude):
+                raise ContextError(f"out of KV pages: need {n}, free {store.pool.free_count}")
+            pages = store.pool.alloc(n)
+        return pages
+
+    def least_loaded_driver(self) -> int:
+        return max(range(len(self.stores)), key=lambda d: self.stores[d].pool.free_count)
+
+    # ------------------------------------------------------------------ lifecycle
+    def create(self, owner: str, driver: Optional[int] = None) -> int:
+        with self.lock:
+            cid = next(self._ids)
+            d = self.least_loaded_driver() if driver is None else driver
+            self.contexts[cid] = Context(id=cid, model=self.model, owner=owner, driver=d,
+                                         created_seq=next(self._seq))
+            self.by_owner.setdefault(owner, set()).add(cid)
+            self.counters["created"] += 1
+            return cid
+
+    def destroy(self, cid: int) -> None:
+        with self.lock:
+            ctx = self.contexts.get(cid)
+            if ctx is None or ctx.state == State.DESTROYED:
+                return
+            store = self._store(ctx)
+            store.release(ctx.chain)
+            store.pool.free(ctx.working_pages)
+            if ctx.stash:
+                self._swap_free.extend(ctx.stash)
+            ctx.chain, ctx.working_pages, ctx.stash = [], [], None
+            ctx.state = State.DESTROYED
+            self.by_owner.get(ctx.owner, set()).discard(cid)
+            del self.contexts[cid]
+
+    def destroy_owner(self, owner: str) -> None:
+        with self.lock:
+            for cid in list(self.by_owner.get(owner, ())):
+                self.destroy(cid)
+            self.by_owner.pop(owner, None)
+
+    # ------------------------------------------------------------------ queries
+    def committed_page_count(self, cid: int) -> int:
+        with self.lock:
+            return len(self._get(cid).chain)
+
+    def working_page_count(self, cid: int) -> int:
+        with self.lock:
+            return len(self._get(cid).working_pages)
+
+    def working_page_token_count(self, cid: int) -> int:
+        with self.lock:
+            return self._get(cid).working_token_count
+
+    def kv_len(self, cid: int) -> int:
+        with self.lock:
+            ctx = self._get(cid)
+            return len(ctx.chain) * self.page_size + len(ctx.tokens)
+
+    # ------------------------------------------------------------------ working pages
+    def reserve_working_pages(self, cid: int, n: int) -> None:
+        with self.lock:
+            ctx = self._get(cid)
+            self._ensure_resident(ctx)
+            ctx.working_pages.extend(self._alloc(ctx.driver, n, exclude=cid))
+
+    def release_working_pages(self, cid: int, n: int) -> None:
+        with self.lock:
+            ctx = self._get(cid)
+            n = min(n, len(ctx.working_pages))
+            keep = len(ctx.working_pages) - n
+            if keep * self.page_size < len(ctx.tokens):
+                # tokens living in released pages are dropped with them
+                self._truncate_to(ctx, keep * self.page_size)
+            freed, ctx.working_pages = ctx.working_pages[keep:], ctx.working_pages[:keep]
+            self._store(ctx).pool.free(freed)
+
+    def truncate_working_page_tokens(self, cid: int, n: int) -> None:
+        with self.lock:
+            ctx = self._get(cid)
+            self._truncate_to(ctx, max(0, len(ctx.tokens) - n))
+
+    def _truncate_to(self, ctx: Context, keep: int) -> None:
+        del ctx.tokens[keep:], ctx.positions[keep:], ctx.mask_keys[keep:]
+
+    def append_working_tokens(self, cid: int, tokens: Sequence[int], positions: Sequence[int],
+                              mask_keys: Optional[Sequence[bytes]] = None) -> None:
+        """Record tokens whose KV a finished forward pass wrote at the tail of the context."""
+        with self.lock:
+            ctx = self._get(cid)
+            if len(ctx.tokens) + len(tokens) > len(ctx.working_pages) * self.page_size:
+                raise ContextError("KV_INVARIANT_VIOLATION: working tokens exceed working pages")
+            ctx.tokens.extend(int(t) for t in tokens)
+            ctx.positions.extend(int(p) for p in positions)
+            ctx.mask_keys.extend(mask_keys if mask_keys is not None else [b""] * len(tokens))
+
+    def commit_working_pages(self, cid: int, n: int) -> None:
+        """Turn the first n (full) working pages into committed, shareable pages."""
+        with self.lock:
+            ctx = self._get(cid)
+            ps = self.page_size
+            if n > len(ctx.working_pages) or n * ps > len(ctx.tokens):
+                raise ContextError("commit needs full working pages")
+            pos = ctx.positions[: n * ps]
+            last = ctx.max_committed_position
+            for p in pos:
+                if p <= last:
+                    raise ContextError("committed positions must be strictly increasing")
+                last = p
+            store = self._store(ctx)
+            prev = ctx.chain[-1] if ctx.chain else 0
+            for i in range(n):
+                tok = ctx.tokens[i * ps:(i + 1) * ps]
+                pp = ctx.positions[i * ps:(i + 1) * ps]
+                mk = b"".join(ctx.mask_keys[i * ps:(i + 1) * ps])
+                h = page_hash(prev, tok, pp, mk, ctx.adapter_seed)
+                page, dedup = store.extend(prev, h, ctx.working_pages[i])
+                if dedup:
+                    store.pool.free([ctx.working_pages[i]])
+                    self.counters["dedup_pages"] += 1
+                ctx.chain.append(h)
+                prev = h
+            ctx.committed_tokens.extend(ctx.tokens[: n * ps])
+            ctx.committed_positions.extend(pos)
+            ctx.max_committed_position = last
+            del ctx.working_pages[:n]
+            self._truncate_front(ctx, n * ps)
+            self.counters["commits"] += 1
+
+    def _truncate_front(self, ctx: Context, n: int) -> None:
+        del ctx.tokens[:n], ctx.positions[:n], ctx.mask_keys[:n]
+
+    # ------------------------------------------------------------------ fork / snapshots
+    def fork(self, cid: int, owner: Optional[str] = None) -> int:
+        """Share the committed chain, physically copy the working pages."""
+        with self.lock:
+            src = self._get(cid)
+            self._ensure_resident(src)
+            store = self._store(src)
+            new_pages = self._alloc(src.driver, len(src.working_pages), exclude=cid)
+            store.acquire(src.chain)
+            if new_pages:
+                self.copy_fn(src.driver, CopyRequest(CopyDir.D2D, np.asarray(src.working_pages, np.int32),
+                                                     np.asarray(new_pages, np.int32)))
+            nid = next(self._ids)
+            own = src.owner if owner is None else owner
+            self.contexts[nid] = Context(
+                id=nid, model=self.model, owner=own, driver=src.driver, chain=list(src.chain),
+                working_pages=new_pages, tokens=list(src.tokens), positions=list(src.positions),
+                mask_keys=list(src.mask_keys), committed_tokens=list(src.committed_tokens),
+                committed_positions=list(src.committed_positions),
+                max_committed_position=src.max_committed_position, adapter_seed=src.adapter_seed,
+                bid=src.bid, created_seq=next(self._seq))
+            self.by_owner.setdefault(own, set()).add(nid)
+            self.counters["forked"] += 1
+            return nid
+
+    def save(self, cid: int, username: str, name: str) -> None:
+        with self.lock:
+            key = (username, name)
+            if key in self.snapshots:
+                self.destroy(self.snapshots.pop(key))
+            snap = self.fork(cid, owner=f"@snapshot:{username}")
+            self.snapshots[key] = snap
+
+    def snapshot(self, cid: int, username: str) -> str:
+        name = f"snap-{next(self._seq):08x}"
+        self.save(cid, username, name)
+        return name
+
+    def open(self, username: str, name: str, owner: str) -> int:
+        with self.lock:
+            snap = self.snapshots.get((username, name))
+            if snap is None:
+                raise ContextError(f"no snapshot named {name!r}")
+            return self.fork(snap, owner=owner)
+
+    def take(self, username: str, name: str, owner: str) -> int:
+        with self.lock:
+            snap = self.snapshots.pop((username, name), None)
+            if snap is None:
+                raise ContextError(f"no snapshot named {name!r}")
+            ctx = self._get(snap)
+            self.by_owner.get(ctx.owner, set()).discard(snap)
+            ctx.owner = owner
+            self.by_owner.setdefault(owner, set()).add(snap)
+            return snap
+
+    def delete_snapshot(self, username: str, name: str) -> None:
+        with self.lock:
+            snap = self.snapshots.pop((username, name), None)
+            if snap is None:
+                raise ContextError(f"no snapshot named {name!r}")
+            self.destroy(snap)
+
+    # ------------------------------------------------------------------ pin / unpin
+    def pin(self, cid: int, n_new_tokens: int) -> PinnedContext:
+        """Freeze the page list for a forward pass that appends n_new_tokens at the tail."""
+        with self.lock:
+            ctx = self._get(cid)
+            self._ensure_resident(ctx)
+            ps = self.page_size
+            kv_len = len(ctx.chain) * ps + len(ctx.tokens)
+            cap = (len(ctx.chain) + len(ctx.working_pages)) * ps
+            if kv_len + n_new_tokens > cap:
+                raise ContextError(
+                    f"KV_INVARIANT_VIOLATION: kv_len {kv_len} + {n_new_tokens} inputs > capacity {cap}")
+            ctx.pins += 1
+            ctx.state = State.PINNED
+            pages = self._store(ctx).physical_ids(ctx.chain) + list(ctx.working_pages)
+            return PinnedContext(cid, pages, kv_len, ctx.driver)
+
+    def unpin(self, cid: int) -> None:
+        with self.lock:
+            ctx = self.contexts.get(cid)
+            if ctx is None:
+                return
+            ctx.pins = max(0, ctx.pins - 1)
+            if ctx.pins == 0 and ctx.state == State.PINNED:
+                ctx.state = State.ACTIVE
+
+    def pinned_count(self) -> int:
+        with self.lock:
+            return sum(1 for c in self.contexts.values() if c.pins > 0)
+
+    def set_bid(self, cid: int, value: float) -> None:
+        with self.lock:
+            self._get(cid).bid = float(value)
+
+    # ------------------------------------------------------------------ suspend / restore
+    def suspend(self, cid: int) -> None:
+        """Evict a context: stash working pages on the CPU tier when there is room (all or
+        nothing), else drop them and remember the lineage for replay; release the chain."""
+        with self.lock:
+            ctx = self._get(cid)
+            if ctx.state == State.SUSPENDED:
+                return
+            if ctx.pins:
+                raise ContextError("cannot suspend a pinned context")
+            store = self._store(ctx)
+            used_working = -(-len(ctx.tokens) // self.page_size)
+            stash = None
+            if used_working and len(self._swap_free) >= used_working:
+                stash = [self._swap_free.pop() for _ in range(used_working)]
+                self.copy_fn(ctx.driver, CopyRequest(CopyDir.D2H, np.asarray(ctx.working_pages[:used_working], np.int32),
+                                                     np.asarray(stash, np.int32)))
+            ctx.stash = stash
+            ctx._n_working = len(ctx.working_pages)
+            store.pool.free(ctx.working_pages)
+            ctx.working_pages = []
+            ctx._chain_resident = store.would_free(ctx.chain) == 0
+            store.release(ctx.chain)
+            ctx.state = State.SUSPENDED
+            self.counters["suspended"] += 1
+
+    def _ensure_resident(self, ctx: Context) -> None:
+        if ctx.state == State.SUSPENDED:
+            self.restore(ctx.id)
+
+    def restore(self, cid: int) -> List[tuple]:
+        """Bring a suspended context back. Returns the (tokens, positions, first_kv_index) spans
+        that must be replayed through forward passes because their KV no longer exists."""
+        with self.lock:
+            ctx = self._get(cid)
+            if ctx.state != State.SUSPENDED:
+                return []
+            store = self._store(ctx)
+            ps = self.page_size
+            # committed prefix still present in the store can simply be re-acquired
+            present = store.prefix_len(ctx.chain)
+            replay: List[tuple] = []
+            if present < len(ctx.chain):
+                missing = len(ctx.chain) - present
+                pages = self._alloc(ctx.driver, missing, exclude=cid)
+                store.acquire(ctx.chain[:present])
+                prev = ctx.chain[present - 1] if present else 0
+                for i, h in enumerate(ctx.chain[present:]):
+                    store.extend(prev, h, pages[i])
+                    prev = h
+                a, b = present * ps, len(ctx.chain) * ps
+                replay.append((ctx.committed_tokens[a:b], ctx.committed_positions[a:b], a))
+                self.counters["replayed_tokens"] += b - a
+            else:
+                store.acquire(ctx.chain)
+            n_working = getattr(ctx, "_n_working", -(-len(ctx.tokens) // ps))
+            ctx.working_pages = self._alloc(ctx.driver, n_working, exclude=cid)
+            if ctx.stash:
+                self.copy_fn(ctx.driver, CopyRequest(CopyDir.H2D, np.asarray(ctx.stash, np.int32),
+                                                     np.asarray(ctx.working_pages[:len(ctx.stash)], np.int32)))
+                self._swap_free.extend(ctx.stash)
+                ctx.stash = None
+            elif ctx.tokens:
+                replay.append((list(ctx.tokens), list(ctx.positions), len(ctx.chain) * ps))
+                self.counters["replayed_tokens"] += len(ctx.tokens)
+            ctx.state = State.ACTIVE
+            self.counters["restored"] += 1
+            ctx._pending_replay = replay
+            return replay
+
+    def take_pending_replay(self, cid: int) -> List[tuple]:
+        with self.lock:
+            ctx = self._get(cid)
+            r = getattr(ctx, "_pending_replay", [])
+            ctx._pending_replay = []
+            return r
+
+    def _evict_one(self, driver: int, exclude: Optional[int]) -> bool:
+        """Pick a victim (lowest bid, newest first) among unpinned resident contexts of the driver."""
+        cands = [c for c in self.contexts.values()
+                 if c.driver == driver and c.state == State.ACTIVE and c.pins == 0 and c.id != exclude
+                 and (c.working_pages or c.chain) and not c.owner.startswith("@snapshot")]
+        if not cands:
+            cands = [c for c in self.contexts.values()
+                     if c.driver == driver and c.state == State.ACTIVE and c.pins == 0 and c.id != exclude
+                     and (c.working_pages or c.chain)]
+        if not cands:
+            return False
+        victim = min(cands, key=lambda c: (c.bid, -c.created_seq))
+        before = self.stores[driver].pool.free_count
+        self.suspend(victim.id)
+        self.counters["evictions"] += 1
+        return self.stores[driver].pool.free_count > before
+
+    # ------------------------------------------------------------------ accounting
+    def pages_used(self, driver: int = 0) -> int:
+        return self.stores[driver].pool.used_count
+
+    def effective_pages(self, cid: int) -> float:
+        with self.lock:
+            ctx = self._get(cid)
+            return self._store(ctx).effective_pages(ctx.chain, len(ctx.working_pages))
+
+    def audit(self) -> None:
+        """Every physical page is free, a working page of exactly one context, or a store node."""
+        with self.lock:
+            for d, store in enumerate(self.stores):
+                owned = [p for c in self.contexts.values() if c.driver == d for p in c.working_pages]
+                nodes = [n.page for n in store.nodes.values()]
+                if len(set(owned)) != len(owned):
+                    raise ContextError("a working page is owned twice")
+                if set(owned) & set(nodes):
+                    raise ContextError("a page is both working and committed")
+                if len(owned) + len(set(nodes)) != store.pool.used_count:
+                    raise ContextError(
+                        f"page leak: {len(owned)} working + {len(set(nodes))} committed != {store.pool.used_count} used")

@@ -1,0 +1,389 @@
+"""Batch scheduler: coalesces forward-pass calls of many inferlets into one ragged batch.
+
+One OS thread per driver drains a queue of pending requests, accumulates them under the
+driver's advertised limits, asks a policy whether to fire or wait, folds the per-request
+arrays into one CSR `ForwardRequest`, runs it synchronously on the driver and scatters the
+per-slot outputs back to the waiting futures. A request larger than `max_forward_tokens` is
+split into sequential prefix chunks (chunked prefill).
+
+Behavioural counterpart of runtime/src/inference/scheduler.rs:311-655 (accumulator and its
+eight limits), :1173-1531 (run loop), :1545-1882 (execute_batch and scatter),
+inference/adaptive_policy.rs:30-274 (policies), inference/scheduler/chunked.rs:48-293
+(chunking) and inference/request.rs:387-540 (fold).
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+
+from ..driver.schema import Capabilities, ForwardRequest, ForwardResponse, SamplerSpec, SlotOutput
+
+
+@dataclass
+class PendingRequest:
+    context_id: int
+    tokens: Sequence[int]
+    positions: Sequence[int]
+    pages: Sequence[int]                  # physical pages: active prefix covering kv_len + len(tokens)
+    kv_len: int                           # tokens already in the context
+    samplers: List[tuple] = field(default_factory=list)   # (index within this request's tokens, SamplerSpec)
+    masks: Optional[list] = None          # per input token BRLE over kv positions, None = causal
+    logit_mask: Optional[list] = None     # BRLE over the vocabulary
+    spec_count: int = 0                   # trailing input tokens that are unverified drafts
+    adapter: int = -1
+    on_done: Optional[Callable] = None    # called with (list[SlotOutput] | Exception)
+    t_submit: float = 0.0
+    chunk_of: Optional["_ChunkState"] = None
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.tokens)
+
+
+@dataclass
+class _ChunkState:
+    parent: PendingRequest
+    offset: int = 0
+    outputs: dict = field(default_factory=dict)   # original slot index -> SlotOutput
+
+
+@dataclass
+class Usage:
+    requests: int = 0
+    tokens: int = 0
+    page_refs: int = 0
+    sampler_rows: int = 0
+    mask_bytes: int = 0
+    logprob_labels: int = 0
+
+
+class BatchAccumulator:
+    """Admits requests while every driver limit holds."""
+
+    def __init__(self, caps: Capabilities, page_size: int):
+        self.caps, self.page_size = caps, page_size
+        self.items: List[PendingRequest] = []
+        self.usage = Usage()
+
+    def cost(self, r: PendingRequest) -> Usage:
+        total = r.kv_len + r.n_tokens
+        pages = -(-total // self.page_size)
+        mask_bytes = 0
+        if r.masks is not None:
+            mask_bytes = r.n_tokens * (-(-total // 8))
+        labels = sum(len(s.labels) for _, s in r.samplers)
+        return Usage(1, r.n_tokens, pages, len(r.samplers), mask_bytes, labels)
+
+    def fits(self, r: PendingRequest) -> bool:
+        c, u, caps = self.cost(r), self.usage, self.caps
+        return (u.requests + c.requests <= caps.max_forward_requests
+                and u.tokens + c.tokens <= caps.max_forward_tokens
+                and u.page_refs + c.page_refs <= caps.max_page_refs
+                and u.sampler_rows + c.sampler_rows <= min(caps.max_sampler_rows, caps.max_logit_rows)
+                and u.mask_bytes + c.mask_bytes <= caps.max_custom_mask_bytes
+                and u.logprob_labels + c.logprob_labels <= caps.max_logprob_labels)
+
+    def push(self, r: PendingRequest) -> None:
+        c, u = self.cost(r), self.usage
+        u.requests += c.requests; u.tokens += c.tokens; u.page_refs += c.page_refs
+        u.sampler_rows += c.sampler_rows; u.mask_bytes += c.mask_bytes; u.logprob_labels += c.logprob_labels
+        self.items.append(r)
+
+    def take(self) -> List[PendingRequest]:
+        items, self.items, self.usage = self.items, [], Usage()
+        return items
+
+    def __len__(self):
+        return len(self.items)
+
+
+def fold(items: Sequence[PendingRequest], page_size: int) -> ForwardRequest:
+    """Per-request arrays -> one batched CSR request (no page trim, decode masks elided)."""
+    r = len(items)
+    qo = np.zeros(r + 1, dtype=np.int32)
+    pptr = np.zeros(r + 1, dtype=np.int32)
+    last = np.zeros(r, dtype=np.int32)
+    has_mask = np.zeros(r, dtype=bool)
+    mask_ptr = np.zeros(r + 1, dtype=np.int32)
+    tokens, positions, pages, mask_runs = [], [], [], []
+    slot_req, slot_row, samplers = [], [], []
+    logit_masks = [None] * r
+    spec = np.zeros(r, dtype=np.int32)
+    ctx_ids = np.zeros(r, dtype=np.uint64)
+    adapters = np.full(r, -1, dtype=np.int64)
+    single = True
+    for i, it in enumerate(items):
+        n = it.n_tokens
+        single &= n == 1
+        total = it.kv_len + n
+        npg = -(-total // page_size)
+        if npg > len(it.pages):
+            raise ValueError("KV_INVARIANT_VIOLATION: request carries too few pages")
+        tokens.append(np.asarray(it.tokens, dtype=np.int32))
+        positions.append(np.asarray(it.positions, dtype=np.int32))
+        pages.append(np.asarray(it.pages[:npg], dtype=np.int32))
+        qo[i + 1] = qo[i] + n
+        pptr[i + 1] = pptr[i] + npg
+        last[i] = total % page_size or (page_size if total else 0)
+        if it.masks is not None:
+            has_mask[i] = True
+            mask_runs.extend(it.masks)
+        mask_ptr[i + 1] = len(mask_runs)
+        for idx, sp in it.samplers:
+            slot_req.append(i)
+            slot_row.append(int(qo[i]) + idx)
+            samplers.append(sp)
+        logit_masks[i] = it.logit_mask
+        spec[i] = it.spec_count
+        ctx_ids[i] = it.context_id
+        adapters[i] = it.adapter
+    cat = lambda xs: np.concatenate(xs) if xs else np.zeros(0, dtype=np.int32)
+    any_mask = bool(has_mask.any())
+    return ForwardRequest(
+        tokens=cat(tokens), positions=cat(positions), qo_indptr=qo, kv_page_indices=cat(pages),
+        kv_page_indptr=pptr, kv_last_page_lens=last,
+        has_user_mask=has_mask if any_mask else None, mask_runs=mask_runs if any_mask else None,
+        mask_row_indptr=mask_ptr if any_mask else None,
+        logit_masks=logit_masks if any(m is not None for m in logit_masks) else None,
+        slot_req=np.asarray(slot_req, dtype=np.int32), slot_row=np.asarray(slot_row, dtype=np.int32),
+        slot_samplers=samplers, spec_counts=spec if spec.any() else None, context_ids=ctx_ids,
+        adapter_ids=adapters, single_token_mode=single)
+
+
+# ------------------------------------------------------------------------------ policies
+class Policy:
+    def decide(self, batch_size: int, waited_s: float, sched: "BatchScheduler") -> float:
+        """Return 0 to fire now, or the number of seconds to keep waiting for more requests."""
+        raise NotImplementedError
+
+    def after_fire(self, batch_size: int, latency_s: float) -> None:
+        pass
+
+
+class GreedyPolicy(Policy):
+    def decide(self, batch_size, waited_s, sched):
+        return 0.0
+
+
+class EagerPolicy(Policy):
+    """Fire when every context that is currently pinned-or-pending has joined the batch."""
+
+    def __init__(self, max_wait_s: float = 0.002):
+        self.max_wait_s = max_wait_s
+
+    def decide(self, batch_size, waited_s, sched):
+        cohort = sched.cohort_size()
+        if batch_size >= cohort or waited_s >= self.max_wait_s:
+            return 0.0
+        return self.max_wait_s - waited_s
+
+
+class AdaptivePolicy(Policy):
+    """Fire at the driver cap, at the recent cohort high-water mark, or when the wait reaches the
+    last batch latency (watchdog). The high-water mark relaxes by one per fire so that a
+    shrinking population of inferlets does not stall on a stale target."""
+
+    def __init__(self, min_wait_s: float = 0.0002, max_wait_s: float = 0.050):
+        self.high_water = 1
+        self.last_latency = 0.001
+        self.min_wait_s, self.max_wait_s = min_wait_s, max_wait_s
+
+    def decide(self, batch_size, waited_s, sched):
+        if batch_size >= sched.caps.max_forward_requests or batch_size >= self.high_water:
+            return 0.0
+        budget = min(self.max_wait_s, max(self.min_wait_s, self.last_latency))
+        if waited_s >= budget:
+            return 0.0
+        return budget - waited_s
+
+    def after_fire(self, batch_size, latency_s):
+        self.last_latency = latency_s
+        self.high_water = max(batch_size, self.high_water - 1, 1)
+
+
+def make_policy(name: str) -> Policy:
+    return {"adaptive": AdaptivePolicy, "eager": EagerPolicy, "greedy": GreedyPolicy}[name]()
+
+
+# ------------------------------------------------------------------------------ scheduler
+class BatchScheduler:
+    def __init__(self, driver, caps: Capabilities, page_size: int, policy: str = "adaptive",
+                 on_batch: Optional[Callable] = None, name: str = "pie-sched-0"):
+        self.driver, self.caps, self.page_size = driver, caps, page_size
+        self.policy = make_policy(policy)
+        self.q: "queue.SimpleQueue[Optional[PendingRequest]]" = queue.SimpleQueue()
+        self.acc = BatchAccumulator(caps, page_size)
+        self.stash: Optional[PendingRequest] = None
+        self.on_batch = on_batch
+        self.post_fire_hooks: List[Callable] = []
+        self.running = True
+        self.aborted: Optional[Exception] = None
+        self.inflight_contexts = 0
+        self.stats = {"total_batches": 0, "total_requests": 0, "total_tokens": 0, "last_latency_us": 0.0,
+                      "cum_latency_us": 0.0, "batch_size_hist": [0] * 8, "chunked_requests": 0,
+                      "failed_batches": 0}
+        self.expected_cohort: Callable[[], int] = lambda: 0
+        self.thread = threading.Thread(target=self.run, name=name, daemon=True)
+        self.thread.start()
+
+    # ---- producer side
+    def submit(self, r: PendingRequest) -> None:
+        if self.aborted is not None:
+            if r.on_done:
+                r.on_done(self.aborted)
+            return
+        r.t_submit = time.perf_counter()
+        self.q.put(r)
+
+    def cohort_size(self) -> int:
+        return max(1, self.expected_cohort())
+
+    def abort(self, exc: Exception) -> None:
+        """Fail everything in flight and everything submitted from now on (driver death)."""
+        self.aborted = exc
+        self.running = False
+        self.q.put(None)
+
+    def shutdown(self) -> None:
+        self.running = False
+        self.q.put(None)
+        self.thread.join(timeout=5)
+
+    # ---- chunked prefill
+    def _prepare(self, r: PendingRequest) -> PendingRequest:
+        cap = self.caps.max_forward_tokens
+        if r.n_tokens <= cap or r.chunk_of is not None:
+            return r
+        self.stats["chunked_requests"] += 1
+        st = _ChunkState(parent=r)
+        return self._next_chunk(st)
+
+    def _next_chunk(self, st: _ChunkState) -> PendingRequest:
+        p, cap = st.parent, self.caps.max_forward_tokens
+        a, b = st.offset, min(st.offset + cap, p.n_tokens)
+        samplers = [(idx - a, sp) for idx, sp in p.samplers if a <= idx < b]
+        st._slot_ids = [k for k, (idx, _) in enumerate(p.samplers) if a <= idx < b]
+        return PendingRequest(
+            context_id=p.context_id, tokens=p.tokens[a:b], positions=p.positions[a:b], pages=p.pages,
+            kv_len=p.kv_len + a, samplers=samplers, masks=None if p.masks is None else p.masks[a:b],
+            logit_mask=p.logit_mask, adapter=p.adapter, chunk_of=st, t_submit=p.t_submit)
+
+    # ---- consumer side
+    def _admit(self, r: PendingRequest) -> bool:
+        r = self._prepare(r)
+        if self.acc.fits(r):
+            self.acc.push(r)
+            return True
+        if len(self.acc) == 0:
+            if r.on_done or r.chunk_of:
+                self._deliver(r, ValueError("request exceeds the driver's forward limits"))
+            return True
+        self.stash = r
+        return False
+
+    def run(self) -> None:
+        while self.running:
+            try:
+                if self.stash is not None:
+                    r, self.stash = self.stash, None
+                else:
+                    r = self.q.get()
+                if r is None:
+                    continue
+                t_first = time.perf_counter()
+                self._admit(r)
+                while self.stash is None:
+                    # drain what is already queued
+                    try:
+                        while self.stash is None:
+                            nxt = self.q.get_nowait()
+                            if nxt is None:
+                                break
+                            self._admit(nxt)
+                    except queue.Empty:
+                        pass
+                    if self.stash is not None or not self.running:
+                        break
+                    wait = self.policy.decide(len(self.acc), time.perf_counter() - t_first, self)
+                    if wait <= 0:
+                        break
+                    try:
+                        nxt = self.q.get(timeout=wait)
+                        if nxt is not None:
+                            self._admit(nxt)
+                    except queue.Empty:
+                        break
+                if len(self.acc):
+                    self.execute_batch(self.acc.take())
+            except Exception as e:  # keep the scheduler alive; fail the batch
+                for it in self.acc.take():
+                    self._deliver(it, e)
+        exc = self.aborted or RuntimeError("scheduler stopped")
+        for it in self.acc.take():
+            self._deliver(it, exc)
+        while True:
+            try:
+                it = self.q.get_nowait()
+            except queue.Empty:
+                break
+            if it is not None:
+                self._deliver(it, exc)
+
+    def execute_batch(self, items: List[PendingRequest]) -> None:
+        t0 = time.perf_counter()
+        try:
+            req = fold(items, self.page_size)
+            resp: ForwardResponse = self.driver.fire_batch(req)
+        except Exception as e:
+            self.stats["failed_batches"] += 1
+            for it in items:
+                self._deliver(it, e)
+            return
+        lat = time.perf_counter() - t0
+        st = self.stats
+        st["total_batches"] += 1
+        st["total_requests"] += len(items)
+        st["total_tokens"] += req.num_tokens
+        st["last_latency_us"] = lat * 1e6
+        st["cum_latency_us"] += lat * 1e6
+        st["batch_size_hist"][min(7, max(0, len(items)).bit_length() - 1 if len(items) else 0)] += 1
+        self.policy.after_fire(len(items), lat)
+        if len(resp.slots) != len(req.slot_samplers):
+            err = RuntimeError(f"driver returned {len(resp.slots)} slots for {len(req.slot_samplers)} samplers")
+            for it in items:
+                self._deliver(it, err)
+            return
+        k = 0
+        for it in items:
+            n = len(it.samplers)
+            self._deliver(it, resp.slots[k:k + n])
+            k += n
+        if self.on_batch:
+            self.on_batch(items, lat)
+
+    def _deliver(self, it: PendingRequest, result) -> None:
+        st = it.chunk_of
+        if st is not None:
+            p = st.parent
+            if isinstance(result, Exception):
+                if p.on_done:
+                    p.on_done(result)
+                return
+            for sid, out in zip(st._slot_ids, result):
+                st.outputs[sid] = out
+            st.offset += it.n_tokens
+            if st.offset < p.n_tokens:
+                nxt = self._next_chunk(st)
+                nxt.t_submit = time.perf_counter()
+                self.q.put(nxt)
+                return
+            if p.on_done:
+                p.on_done([st.outputs[i] for i in range(len(p.samplers))])
+            return
+        if it.on_done:
+            it.on_done(result)
