@@ -42,7 +42,7 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const bf16* 
 // VEC_PER_THREAD 8-element vectors are cached in registers between passes.
 template <int MAXV>
 __global__ void __launch_bounds__(256)
-rmsnorm_kernel(const bf16* __restrict__ x, const bf16* delta, bf16* residual_out,
+rmsnorm_kernel(const bf16* x, const bf16* delta, bf16* residual_out,
                const bf16* __restrict__ w, bf16* out, int hidden, float eps, float w_offset) {
     __shared__ float red[32];
     const int t = blockIdx.x;

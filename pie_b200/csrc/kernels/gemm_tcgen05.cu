@@ -197,6 +197,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();  // lane 0 ran the MMA loop alone: reconverge before the aligned dealloc
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }

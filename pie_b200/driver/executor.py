@@ -87,6 +87,7 @@ class _Graph:
     graph: "torch.cuda.CUDAGraph"
     logits: torch.Tensor
     bucket: int
+    launches: int = 0
 
 
 class TorchDriver:
@@ -233,10 +234,13 @@ class TorchDriver:
                 self.model.forward(fi, self.kv.data)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
+        from ..ops import _lib
         g = torch.cuda.CUDAGraph()
+        before = _lib.LAUNCHES
         with torch.cuda.graph(g):
             logits = self.model.forward(fi, self.kv.data)
-        return _Graph(g, logits, rb)
+        # the decode-attention launcher issues two kernels (split-KV pass + merge) per layer
+        return _Graph(g, logits, rb, _lib.LAUNCHES - before + self.cfg.num_hidden_layers)
 
     def _bucket(self, r: int) -> int:
         for b in self.buckets:
@@ -445,6 +449,57 @@ class TorchDriver:
         resp.t_sample_us = (t3 - t2) * 1e6
         resp.t_total_us = (t3 - t0) * 1e6
         return resp
+
+    # ------------------------------------------------------------------ device-resident decode loop
+    def stage_decode(self, req: ForwardRequest) -> dict:
+        """Prepare one pure-decode step without running it: returns device copies of the slab
+        contents so that `replay_staged` can run the step with no host work in between.
+        Used to time the device path alone (tokens are fed from the previous step's samples)."""
+        qlens, kv_lens, slots = self._derive(req)
+        assert self.cuda and bool((qlens == 1).all())
+        s = self.slab
+        r = req.num_requests
+        rb = self._bucket(r)
+        self._token_slots = self._sampler_params(req, None)
+        self._fill_common(req, slots, kv_lens, n_pad_tokens=rb - r, r_pad=rb - r)
+        if rb > r:
+            s.h("tokens")[r:rb] = 0
+            s.h("positions")[r:rb] = 0
+            s.h("slots")[r:rb] = -1
+            s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
+        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items)
+        ni = len(item_req)
+        s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
+        s.h("req_item_indptr")[:r + 1] = indptr
+        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
+        s.h("num_items")[0] = ni
+        o, n = s.offsets["tile_qstart"]
+        end = o + n
+        po, _ = s.offsets["page_indices"]
+        npg = len(req.kv_page_indices)
+        if rb not in self.graphs:
+            s.upload("tile_qstart", ("page_indices", npg))
+            self.graphs[rb] = self._capture(rb)
+        return {"fixed": s.host[:end].to(self.device), "pages": s.host[po:po + npg].to(self.device),
+                "rb": rb, "r": r, "end": end, "po": po, "npg": npg}
+
+    def replay_staged(self, st: dict, feed_sampled: bool) -> None:
+        s = self.slab
+        s.dev[:st["end"]].copy_(st["fixed"], non_blocking=True)
+        s.dev[st["po"]:st["po"] + st["npg"]].copy_(st["pages"], non_blocking=True)
+        r = st["r"]
+        if feed_sampled:
+            s.d("tokens", r).copy_(self.sampled[:r], non_blocking=True)
+        g = self.graphs[st["rb"]]
+        g.graph.replay()
+        ops.sample(g.logits[:r], s.d("temperature", r).view(torch.float32), s.d("top_k", r),
+                   s.d("top_p", r).view(torch.float32), s.d("min_p", r).view(torch.float32),
+                   s.d("seeds", r, torch.int64), None, None, out=self.sampled)
+
+    def launches_per_decode_step(self, rb: int) -> int:
+        """Kernels of this library launched by one decode step of bucket `rb`: the captured
+        forward (counted at capture time) plus the sampler."""
+        return self.graphs[rb].launches + 1
 
     def copy(self, req: CopyRequest) -> None:
         self.kv.copy(req)

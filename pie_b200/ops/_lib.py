@@ -100,7 +100,12 @@ def ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+LAUNCHES = 0   # native launcher calls made through this module (each is >= 1 kernel launch)
+
+
 def check(err: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if err != 0:
         raise KernelLibraryError(f"{what}: CUDA error code {err}")
 

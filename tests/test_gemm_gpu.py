@@ -1,0 +1,61 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference (and its fused epilogues)."""
+import pytest
+import torch
+
+from pie_b200 import ops
+from pie_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(torch.bfloat16)
+
+
+def check(y, want, k):
+    err = (y.float() - want.float()).abs().max().item()
+    # bf16 output rounding (2^-8 relative) + fp32 accumulation over k terms
+    tol = 2e-2 * want.float().abs().max().item() + 1e-3 * k ** 0.5
+    assert err <= tol, f"max err {err} > {tol}"
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 4096), (1, 6144, 4096),
+                                   (77, 4096, 4096), (512, 6144, 4096), (300, 1000, 328), (2048, 14336, 4096),
+                                   (130, 128256, 256)])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_plain(m, n, k, bn):
+    if bn and (m * n > 4096 * 4096) and bn != 256:
+        pytest.skip("large shape only with the automatic tile choice")
+    x, w = bf(m, k, seed=1), bf(n, k, scale=0.05, seed=2)
+    y = ops.gemm(x, w, force_bn=bn)
+    check(y, x.float() @ w.float().t(), k)
+
+
+def test_gemm_residual():
+    m, n, k = 333, 4096, 1024
+    x, w, r = bf(m, k, seed=3), bf(n, k, scale=0.05, seed=4), bf(m, n, seed=5)
+    y = ops.gemm(x, w, residual=r, epilogue=ops.EPI_RESIDUAL)
+    check(y, x.float() @ w.float().t() + r.float(), k)
+
+
+def test_gemm_swiglu():
+    m, n, k = 200, 2 * 1408, 512
+    x, w = bf(m, k, seed=6), bf(n, k, scale=0.05, seed=7)
+    y = ops.gemm(x, w, epilogue=ops.EPI_SWIGLU)
+    want = ref.swiglu_interleaved((x.float() @ w.float().t()))
+    assert y.shape == (m, n // 2)
+    check(y, want, k)
+
+
+def test_gemm_strided_operands():
+    m, n, k = 96, 512, 256
+    big = bf(m, 3 * k, seed=8)
+    x = big[:, k:2 * k]                      # row stride 3k
+    w = bf(n, k, scale=0.05, seed=9)
+    out = torch.zeros(m, 2 * n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(x, w, out=out[:, n:])
+    check(out[:, n:], x.float() @ w.float().t(), k)
+    assert float(out[:, :n].abs().max()) == 0.0

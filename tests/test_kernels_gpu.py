@@ -1,0 +1,230 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 reference of the same op."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from pie_b200 import ops
+from pie_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(torch.bfloat16)
+
+
+def close(a, b, atol, rtol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (allowed {tol.max().item():.4g})"
+
+
+def test_embed_and_shard():
+    table = bf(1000, 256)
+    tok = torch.randint(0, 1000, (77,), device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.embed(tok, table), ref.embed(tok, table))
+    shard = table[250:500].contiguous()
+    assert torch.equal(ops.embed(tok, shard, vocab_start=250), ref.embed(tok, shard, 250))
+
+
+@pytest.mark.parametrize("hidden", [256, 2048, 4096, 5120, 8192])
+def test_rmsnorm(hidden):
+    x, w = bf(33, hidden, seed=1), bf(hidden, seed=2) + 1
+    close(ops.rmsnorm(x, w, 1e-5), ref.rmsnorm(x, w, 1e-5), 2e-2)
+    res, res2 = bf(33, hidden, seed=3), None
+    res2 = res.clone()
+    y = ops.add_rmsnorm(x, res, w, 1e-5)
+    y2 = ref.add_rmsnorm(x, res2, w, 1e-5)
+    close(res, res2, 1e-2)
+    close(y, y2, 3e-2)
+
+
+def test_swiglu():
+    gu = bf(50, 2 * 1408, seed=4)
+    close(ops.swiglu(gu), ref.swiglu(gu), 2e-2)
+
+
+@pytest.mark.parametrize("d,hq,hkv,norm", [(128, 8, 2, False), (128, 8, 2, True), (64, 4, 2, True)])
+def test_qk_norm_rope_kvwrite(d, hq, hkv, norm):
+    n, page, pages = 41, 16, 12
+    qkv = bf(n, (hq + 2 * hkv) * d, seed=5)
+    pos = torch.randint(0, 5000, (n,), device=DEV, dtype=torch.int32)
+    perm = torch.randperm(pages * page, device=DEV)[:n].to(torch.int32)
+    perm[3] = -1
+    inv = ref.rope_inv_freq(d, 500000.0, None, DEV)
+    qn = (bf(d, seed=6) + 1) if norm else None
+    kn = (bf(d, seed=7) + 1) if norm else None
+    kv1 = torch.zeros(pages, 2, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+    kv2 = kv1.clone()
+    q1 = ops.qk_norm_rope_kvwrite(qkv, pos, perm, inv, qn, kn, kv1, hq, hkv, d, page, 1e-6)
+    q2 = ref.qk_norm_rope_kvwrite(qkv, pos, perm, inv, qn, kn, kv2, hq, hkv, d, page, 1e-6)
+    close(q1, q2, 3e-2)
+    close(kv1, kv2, 3e-2)
+
+
+def test_gather_copy_pages():
+    x = bf(100, 512, seed=8)
+    idx = torch.randint(0, 100, (37,), device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.gather_rows(x, idx), x[idx.long()])
+    kv = bf(3, 10, 2, 2, 16, 64, seed=9)
+    want = kv.clone()
+    src = torch.tensor([1, 4], device=DEV, dtype=torch.int32)
+    dst = torch.tensor([7, 2], device=DEV, dtype=torch.int32)
+    want[:, dst.long()] = want[:, src.long()]
+    ops.copy_pages(kv, src, dst)
+    assert torch.equal(kv, want)
+
+
+def test_brle_expand():
+    rng = np.random.default_rng(0)
+    rows, nbits = [], 1000
+    for _ in range(9):
+        runs, tot = [], 0
+        while tot < nbits:
+            r = int(rng.integers(0, 90))
+            runs.append(r)
+            tot += r
+        rows.append(runs)
+    rows.append([0, nbits])
+    rows.append([nbits])
+    rows.append([5, 3])      # short vector: tail is zeros
+    got = ops.brle_expand(rows, nbits, DEV).cpu()
+    want = ops.brle_expand(rows, nbits, "cpu")
+    assert torch.equal(got, want)
+
+
+def make_paged(nreq, kv_lens, hkv, d, page, seed=0, extra_pages=5):
+    npages = [-(-int(k) // page) for k in kv_lens]
+    total = sum(npages) + extra_pages
+    kv = bf(total, 2, hkv, page, d, seed=seed)
+    perm = torch.randperm(total)[: sum(npages)].numpy().astype(np.int32)
+    indptr = np.zeros(nreq + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(npages)
+    return kv, perm, indptr
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (128, 8, 1), (64, 4, 2), (128, 16, 16), (128, 16, 1)])
+def test_paged_decode_attention(d, hq, hkv):
+    page = 16
+    kv_lens = np.array([1, 15, 16, 17, 300, 1000, 2305, 64], dtype=np.int32)
+    r = len(kv_lens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=11)
+    q = bf(r, hq, d, seed=12)
+    item_req, st, en, iptr = ops.plan_decode_items(kv_lens, hkv, target_ctas=64, min_chunk=256)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    max_items = len(item_req) + 3
+    plan = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
+                          torch.tensor([len(item_req)], dtype=torch.int32, device=DEV),
+                          torch.empty(ops.decode_scratch_floats(max_items, hq, d), device=DEV),
+                          max_items, r, 64, page)
+    scale = 1 / math.sqrt(d)
+    out = ops.paged_decode_attention(q, kv, plan, scale)
+    qo = np.arange(r + 1, dtype=np.int32)
+    want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale)
+    close(out, want, 2e-2)
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (128, 8, 1), (64, 4, 2)])
+@pytest.mark.parametrize("mode", ["causal", "custom", "window"])
+def test_paged_prefill_attention(d, hq, hkv, mode):
+    page = 16
+    qlens = np.array([1, 5, 64, 130, 17], dtype=np.int32)
+    prev = np.array([40, 0, 0, 200, 31], dtype=np.int32)
+    kv_lens = qlens + prev
+    r = len(qlens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=21)
+    qo = np.zeros(r + 1, dtype=np.int32)
+    qo[1:] = np.cumsum(qlens)
+    q = bf(int(qo[-1]), hq, d, seed=22)
+    masks = None
+    window = -1
+    if mode == "custom":
+        rng = np.random.default_rng(5)
+        masks = []
+        for i in range(r):
+            m = rng.random((qlens[i], kv_lens[i])) < 0.6
+            m[:, 0] = True
+            masks.append(m if i != 2 else None)
+    if mode == "window":
+        window = 37
+    batch = ops.AttnBatch(qo, indptr, pages, kv_lens, masks, window)
+    plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV)
+    scale = 1 / math.sqrt(d)
+    lse = torch.empty(int(qo[-1]), hq, device=DEV)
+    out = ops.paged_prefill_attention(q, kv, plan, scale, lse_out=lse)
+    tmasks = None if masks is None else [None if m is None else torch.from_numpy(m) for m in masks]
+    want, want_lse = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
+                                         masks=tmasks, window_left=window, return_lse=True)
+    close(out, want, 2e-2)
+    close(lse, want_lse, 2e-2)
+
+
+def test_row_stats():
+    lg = bf(7, 4096, scale=3.0, seed=30)
+    close(ops.row_stats(lg), ref.row_stats(lg), 2e-3, rtol=1e-3)
+
+
+def _params(rows, t, k, p, mp, seed0=1):
+    return (torch.full((rows,), t, device=DEV), torch.full((rows,), k, dtype=torch.int32, device=DEV),
+            torch.full((rows,), p, device=DEV), torch.full((rows,), mp, device=DEV),
+            torch.arange(seed0, seed0 + rows, dtype=torch.int64, device=DEV))
+
+
+def test_sample_argmax_and_topk1():
+    lg = bf(16, 32000, scale=2.0, seed=31)
+    want = lg.float().argmax(-1).int()
+    got = ops.sample(lg, *_params(16, 0.0, 0, 1.0, 0.0))
+    assert torch.equal(got, want)
+    got = ops.sample(lg, *_params(16, 1.0, 1, 1.0, 0.0))
+    # top-k = 1 keeps every token tied with the maximum (bf16 ties are common)
+    mx = lg.float().amax(-1)
+    assert bool((lg.float()[torch.arange(16), got.long()] == mx).all())
+
+
+@pytest.mark.parametrize("t,k,p,mp", [(1.0, 50, 1.0, 0.0), (0.8, 0, 0.9, 0.0), (1.0, 0, 1.0, 0.05), (0.7, 40, 0.95, 0.0)])
+def test_sample_stays_in_kept_set(t, k, p, mp):
+    rows, vocab = 64, 8192
+    lg = bf(rows, vocab, scale=3.0, seed=32)
+    got = ops.sample(lg, *_params(rows, t, k, p, mp)).cpu()
+    lgc = lg.cpu()
+    for r in range(rows):
+        keep = ref.kept_set(lgc[r], t, k, p, mp)
+        assert bool(keep[got[r]]), f"row {r}: token {int(got[r])} outside the kept set"
+
+
+def test_sample_distribution_matches_softmax():
+    vocab, draws = 64, 20000
+    row = (torch.randn(vocab, generator=torch.Generator().manual_seed(3)) * 1.5).to(torch.bfloat16)
+    lg = row.to(DEV).repeat(draws, 1).contiguous()
+    got = ops.sample(lg, *_params(draws, 1.0, 0, 1.0, 0.0, seed0=1000)).cpu()
+    freq = torch.bincount(got.long(), minlength=vocab).float() / draws
+    p = torch.softmax(row.float(), -1)
+    assert float((freq - p).abs().max()) < 0.02
+    # same seeds -> same tokens (counter-based stream)
+    again = ops.sample(lg, *_params(draws, 1.0, 0, 1.0, 0.0, seed0=1000)).cpu()
+    assert torch.equal(got, again)
+
+
+def test_sample_with_vocab_mask():
+    rows, vocab = 8, 4096
+    lg = bf(rows, vocab, scale=2.0, seed=33)
+    runs = [[100, 50, 1000, 7]]           # allowed: [100,150) and [1150,1157)
+    bits = ops.brle_expand(runs, vocab, DEV)
+    mrow = torch.tensor([0, -1] * 4, dtype=torch.int32, device=DEV)
+    got = ops.sample(lg, *_params(rows, 1.0, 0, 1.0, 0.0), mask_bits=bits, mask_row=mrow).cpu()
+    for r in range(0, rows, 2):
+        t = int(got[r])
+        assert 100 <= t < 150 or 1150 <= t < 1157
+    # greedy under a mask = arg-max over the allowed set
+    got = ops.sample(lg, *_params(rows, 0.0, 0, 1.0, 0.0), mask_bits=bits, mask_row=mrow).cpu()
+    allowed = torch.zeros(vocab, dtype=torch.bool)
+    allowed[100:150] = True
+    allowed[1150:1157] = True
+    for r in range(0, rows, 2):
+        want = int(lg[r].float().cpu().masked_fill(~allowed, float("-inf")).argmax())
+        assert int(got[r]) == want
