@@ -99,6 +99,8 @@ class TorchDriver:
                  swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0):
         self.cfg = cfg
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.cuda = self.device.type == "cuda"
         self.dtype = torch_dtype(cfg.dtype) if not self.cuda else torch.bfloat16
         self.par = par or ParallelContext()
