@@ -176,10 +176,10 @@ def run_engine_workload(engine, model_name: str, prompts, out_tokens: int, sampl
                         window_skip: int, window_steps: int, timeout: float = 1800.0):
     """All inferlets at once through the public API. Returns e2e metrics."""
     entry = engine.model(model_name)
-    fires = []   # (t_end, n_requests, n_tokens)
+    fires = []   # (t_end, n_requests, n_tokens, latency)
 
-    def on_batch(items, lat):
-        fires.append((time.perf_counter(), len(items), sum(it.n_tokens for it in items), lat))
+    def on_batch(n_requests, n_tokens, lat, kind):
+        fires.append((time.perf_counter(), n_requests, n_tokens, lat))
 
     for s in entry.schedulers:
         s.on_batch = on_batch

@@ -330,3 +330,25 @@ PIE_API int pie_brle_expand(const uint32_t* run_ends, const int* indptr, uint32_
     brle_expand_kernel<<<grid, 128, 0, st>>>(run_ends, indptr, out, words, nbits, tail_value);
     return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------- token feed
+// Decode pipelining: the input token of row i is the token sampled for row
+// src_row[i] by the previous step (still on the device), unless src_row[i] < 0,
+// in which case the host-provided token already in `tokens` stays.
+namespace pie {
+__global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src_row,
+                                   const int* __restrict__ prev_sampled, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int s = src_row[i];
+        if (s >= 0) tokens[i] = prev_sampled[s];
+    }
+}
+}  // namespace pie
+
+PIE_API int pie_feed_tokens(int* tokens, const int* src_row, const int* prev_sampled, int n,
+                            cudaStream_t st) {
+    if (n <= 0) return 0;
+    pie::feed_tokens_kernel<<<(n + 255) / 256, 256, 0, st>>>(tokens, src_row, prev_sampled, n);
+    return (int)cudaGetLastError();
+}

@@ -56,9 +56,16 @@ class _Slab:
             off += n
         self.size = off
         cuda = torch.device(device).type == "cuda"
-        self.host = torch.zeros(self.size, dtype=torch.int32, pin_memory=cuda)
+        # two pinned host copies: a pipelined decode step fills one while the H2D copy of the
+        # previous step may still be reading the other
+        self.hosts = [torch.zeros(self.size, dtype=torch.int32, pin_memory=cuda) for _ in range(2 if cuda else 1)]
+        self.host = self.hosts[0]
         self.np = self.host.numpy()
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=device) if cuda else self.host
+
+    def select(self, parity: int) -> None:
+        self.host = self.hosts[parity % len(self.hosts)]
+        self.np = self.host.numpy()
 
     def h(self, name, dtype=np.int32):
         o, n = self.offsets[name]
@@ -80,6 +87,36 @@ class _Slab:
             o2, _ = self.offsets[name]
             if used:
                 self.dev[o2:o2 + used].copy_(self.host[o2:o2 + used], non_blocking=True)
+
+
+@dataclass
+class CohortStep:
+    """One pure-decode step over r rows in array form (no per-request objects)."""
+    r: int
+    host_tokens: np.ndarray     # int32 [r] input token when src_row < 0
+    src_row: np.ndarray         # int32 [r] row of the previous pipelined step that sampled this row's input
+    positions: np.ndarray       # int32 [r]
+    kv_lens: np.ndarray         # int32 [r] KV length including this token
+    page_indptr: np.ndarray     # int32 [r+1]
+    page_indices: np.ndarray    # int32
+    temperature: np.ndarray
+    top_k: np.ndarray
+    top_p: np.ndarray
+    min_p: np.ndarray
+    seeds: np.ndarray           # int64 [r]
+
+
+class AsyncTokens:
+    """Result handle of `decode_async`: wait() blocks until the step's tokens are on the host."""
+
+    def __init__(self, event, host_buf, r: int, ready: Optional[np.ndarray] = None):
+        self.event, self.host_buf, self.r, self.ready = event, host_buf, r, ready
+
+    def wait(self) -> np.ndarray:
+        if self.ready is None:
+            self.event.synchronize()
+            self.ready = self.host_buf[:self.r].numpy().copy()
+        return self.ready
 
 
 @dataclass
@@ -128,7 +165,7 @@ class TorchDriver:
             "item_req": self.max_items, "item_start": self.max_items, "item_end": self.max_items,
             "req_item_indptr": max_requests + 1, "num_items": 4,
             "logit_rows": rows, "temperature": rows, "top_k": rows, "top_p": rows, "min_p": rows,
-            "mask_row": rows, "seeds": 2 * rows,
+            "mask_row": rows, "seeds": 2 * rows, "src_row": rows,
             "tile_req": max_tokens + max_requests, "tile_qstart": max_tokens + max_requests,
             "page_indices": self.max_page_refs,
         }, self.device)
@@ -138,6 +175,8 @@ class TorchDriver:
                                        dtype=torch.float32, device=self.device)
             self.sampled = torch.zeros(rows, dtype=torch.int32, device=self.device)
             self.sampled_host = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
+            self.cohort_sampled = [torch.zeros(rows, dtype=torch.int32, device=self.device) for _ in range(2)]
+            self.cohort_host = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.use_graphs = use_graphs and self.cuda
         self.buckets = graph_buckets(max_requests)
         self.graphs: Dict[int, _Graph] = {}
@@ -451,6 +490,103 @@ class TorchDriver:
         resp.t_sample_us = (t3 - t2) * 1e6
         resp.t_total_us = (t3 - t0) * 1e6
         return resp
+
+    # ------------------------------------------------------------------ pipelined decode
+    def decode_async(self, step: "CohortStep", parity: int) -> "AsyncTokens":
+        """Launch one pure-decode step for the rows of `step` and return at once.
+
+        Rows whose `src_row` is >= 0 take their input token from the tokens sampled by the
+        previous pipelined step (device to device), so the host never has to wait for one step's
+        result before launching the next; it reads each step's tokens one step late.
+        """
+        r = step.r
+        ps = self.page_size
+        if not self.cuda:
+            return self._decode_sync_cpu(step)
+        s = self.slab
+        s.select(parity)
+        rb = self._bucket(r) if self.use_graphs else r
+        if r > self.max_requests or len(step.page_indices) > self.max_page_refs:
+            raise ValueError("decode step exceeds the advertised forward limits")
+        idx = step.kv_lens.astype(np.int64) - 1
+        pg = step.page_indices[step.page_indptr[:-1].astype(np.int64) + idx // ps].astype(np.int64)
+        s.h("tokens")[:r] = step.host_tokens
+        s.h("positions")[:r] = step.positions
+        s.h("slots")[:r] = pg * ps + idx % ps
+        s.h("src_row")[:r] = step.src_row
+        s.h("qo_indptr")[:rb + 1] = np.arange(rb + 1, dtype=np.int32)
+        s.h("kv_page_indptr")[:r + 1] = step.page_indptr
+        s.h("kv_lens")[:r] = step.kv_lens
+        npg = len(step.page_indices)
+        s.h("page_indices")[:npg] = step.page_indices
+        if rb > r:
+            s.h("tokens")[r:rb] = 0
+            s.h("positions")[r:rb] = 0
+            s.h("slots")[r:rb] = -1
+            s.h("src_row")[r:rb] = -1
+            s.h("kv_page_indptr")[r + 1:rb + 1] = step.page_indptr[-1]
+        item_req, st, en, indptr = ops.plan_decode_items(step.kv_lens, self.model.hkv, self.num_ctas, self.max_items)
+        ni = len(item_req)
+        s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
+        s.h("req_item_indptr")[:r + 1] = indptr
+        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
+        s.h("num_items")[0] = ni
+        s.h("temperature", np.float32)[:r] = step.temperature
+        s.h("top_k")[:r] = step.top_k
+        s.h("top_p", np.float32)[:r] = step.top_p
+        s.h("min_p", np.float32)[:r] = step.min_p
+        s.h("seeds", np.int64)[:r] = step.seeds
+        if self.par.tp_size > 1 and self.par.comm is not None:
+            self.par.comm.publish_decode(s, r, rb, npg, parity)
+        if self.use_graphs and rb not in self.graphs:
+            s.upload("tile_qstart", ("page_indices", npg))
+            self.graphs[rb] = self._capture(rb)
+        self._launch_decode(r, rb, npg, parity)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.stats["fires"] += 1
+        return AsyncTokens(ev, self.cohort_host[parity & 1], r)
+
+    def _launch_decode(self, r: int, rb: int, npg: int, parity: int) -> None:
+        """Device side of a pipelined decode step (also what tensor-parallel followers run)."""
+        s = self.slab
+        s.upload("tile_qstart", ("page_indices", npg))
+        cur, prev = self.cohort_sampled[parity & 1], self.cohort_sampled[(parity & 1) ^ 1]
+        ops.feed_tokens(s.d("tokens"), s.d("src_row"), prev, r)
+        if self.use_graphs:
+            g = self.graphs[rb]
+            g.graph.replay()
+            logits = g.logits
+            self.stats["graph_replays"] += 1
+        else:
+            logits = self.model.forward(self._forward_inputs_decode(rb), self.kv.data)
+            self.stats["eager"] += 1
+        ops.sample(logits[:r], s.d("temperature", r).view(torch.float32), s.d("top_k", r),
+                   s.d("top_p", r).view(torch.float32), s.d("min_p", r).view(torch.float32),
+                   s.d("seeds", r, torch.int64), None, None, out=cur)
+        self.cohort_host[parity & 1][:r].copy_(cur[:r], non_blocking=True)
+
+    def _decode_sync_cpu(self, step: "CohortStep") -> "AsyncTokens":
+        """CPU drivers have no stream to pipeline on: resolve the token feed on the host and run
+        the step through the ordinary batch path."""
+        r = step.r
+        toks = np.array(step.host_tokens, dtype=np.int32)
+        prev = getattr(self, "_cpu_prev_tokens", None)
+        sel = step.src_row >= 0
+        if sel.any():
+            toks[sel] = prev[step.src_row[sel]]
+        last = (step.kv_lens - 1) % self.page_size + 1
+        samplers = [SamplerSpec(SamplerKind.TOP_K_TOP_P, float(step.temperature[i]), int(step.top_k[i]),
+                                float(step.top_p[i]), 0.0, int(step.seeds[i])) if step.min_p[i] == 0 else
+                    SamplerSpec(SamplerKind.MIN_P, float(step.temperature[i]), 0, 1.0, float(step.min_p[i]),
+                                int(step.seeds[i])) for i in range(r)]
+        req = ForwardRequest(tokens=toks, positions=step.positions, qo_indptr=np.arange(r + 1, dtype=np.int32),
+                             kv_page_indices=step.page_indices, kv_page_indptr=step.page_indptr,
+                             kv_last_page_lens=last.astype(np.int32), slot_req=np.arange(r, dtype=np.int32),
+                             slot_row=np.arange(r, dtype=np.int32), slot_samplers=samplers, single_token_mode=True)
+        resp = self.fire_batch(req)
+        self._cpu_prev_tokens = np.asarray(resp.tokens, dtype=np.int32)
+        return AsyncTokens(None, None, r, ready=self._cpu_prev_tokens)
 
     # ------------------------------------------------------------------ device-resident decode loop
     def stage_decode(self, req: ForwardRequest) -> dict:

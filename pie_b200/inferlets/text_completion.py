@@ -41,7 +41,13 @@ async def main(args):
     gen = ctx.generate(make_sampler(args), max_tokens=int(args.get("max_tokens", 64)))
     if "stop_tokens" in args:
         gen.stop(args["stop_tokens"])
-    tokens = await gen.collect_tokens()
+    if args.get("per_step"):
+        # inferlet-driven loop (one forward-pass.execute per token) instead of the runtime's cohort
+        async for step in gen:
+            await step.execute()
+        tokens = list(gen._generated)
+    else:
+        tokens = await gen.collect_tokens()
     ctx.release()
     if args.get("return_tokens") or "prompt_tokens" in args:
         return json.dumps({"tokens": tokens})

@@ -22,11 +22,16 @@ async def main(args):
     ctx = Context(model)
     ctx.append(args["prompt_tokens"])
     gen = ctx.generate(make_sampler(args), max_tokens=int(args.get("max_tokens", 256))).stop([])
-    stamps = []
-    n = 0
-    async for step in gen:
-        out = await step.execute()
-        n += len(out.tokens)
-        stamps.append(time.perf_counter())
+    if args.get("per_step"):
+        # inferlet-driven loop: one forward-pass.execute per token
+        stamps, n = [], 0
+        async for step in gen:
+            out = await step.execute()
+            n += len(out.tokens)
+            stamps.append(time.perf_counter())
+    else:
+        # plain generation: the runtime's decode cohort runs the loop and stamps each token
+        stream = await gen.run_offloaded()
+        stamps, n = list(stream.stamps), len(stream.tokens)
     ctx.release()
     return json.dumps({"t0": t0, "stamps": stamps, "n_tokens": n})

@@ -117,6 +117,15 @@ def gather_rows(x, idx, out=None):
     return out
 
 
+def feed_tokens(tokens, src_row, prev_sampled, n: int):
+    """tokens[i] = prev_sampled[src_row[i]] where src_row[i] >= 0 (device-side token feed)."""
+    if not tokens.is_cuda:
+        sel = src_row[:n] >= 0
+        tokens[:n][sel] = prev_sampled[src_row[:n][sel].long()]
+        return
+    check(fn("pie_feed_tokens")(ptr(tokens), ptr(src_row), ptr(prev_sampled), n, stream_ptr()), "feed_tokens")
+
+
 def copy_pages(kv, src, dst):
     """kv [layers, pages, ...]: copy page src[i] -> dst[i] in every layer."""
     if not kv.is_cuda:

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "pie_prefill_tile_tokens": [i32],
     "pie_sample": [p, i64, i32, i32, p, p, p, p, p, p, p, i32, p, p],
     "pie_row_stats": [p, i64, i32, i32, p, p],
+    "pie_feed_tokens": [p, p, p, i32, p],
     "pie_gemm_bf16": [p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, i32, p],
 }
 _RESTYPES = {"pie_decode_attn_scratch_floats": i64}

@@ -24,6 +24,7 @@ from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional
 
 from ..driver.schema import Capabilities, CopyRequest
+from .cohort import DecodeCohort
 from .context import ContextManager
 from .inference import InferenceService
 from .messaging import Messaging
@@ -105,8 +106,12 @@ class Engine:
             sched = BatchScheduler(drv, caps, entry.page_size, self.config.batch_policy,
                                    name=f"pie-sched-{name}-{i}")
             sched.expected_cohort = entry.ctxm.pinned_count
+            sched.cohort = DecodeCohort(entry.ctxm, entry.page_size, caps.max_forward_requests)
             entry.schedulers.append(sched)
         entry.inference = InferenceService(entry.ctxm, entry.schedulers, self.config.speculation_depth)
+        entry.inference.cohorts = [s.cohort for s in entry.schedulers]
+        for s in entry.schedulers:
+            s.cohort.on_finish = lambda st, e=entry: self._charge(e, st.ctx_id, getattr(st, "kept", 0))
         entry.inference.on_tokens = lambda cid, n, e=entry: self._charge(e, cid, n)
         self.models[name] = entry
         return entry

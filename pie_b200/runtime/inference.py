@@ -95,6 +95,7 @@ class InferenceService:
     def __init__(self, ctxm: ContextManager, schedulers: Sequence[BatchScheduler], speculation_depth: int = 1):
         self.ctxm, self.schedulers = ctxm, list(schedulers)
         self.depth = speculation_depth
+        self.cohorts: list = []       # DecodeCohort per driver (set by the engine)
         self.staged: Dict[int, _Staged] = {}
         self.lock = threading.Lock()
         self.stats = {"submits": 0, "bypass_hits": 0, "chain_submits": 0, "chain_drops": 0,
@@ -125,6 +126,29 @@ class InferenceService:
 
     def drop_context(self, cid: int) -> None:
         self._abandon(cid)
+
+    def start_stream(self, cid: int, tokens: Sequence[int], positions: Sequence[int], spec: SamplerSpec,
+                     max_tokens: int, stop: Sequence[int] = ()):
+        """Plain generation offloaded to the runtime: one ordinary pass over `tokens` that samples
+        the first token, then the context decodes inside the driver's cohort (array-form,
+        device-fed tokens) until `max_tokens` or a stop token. Returns a cohort Stream."""
+        from .cohort import Stream
+        stream = Stream(cid, spec, max_tokens, stop, first_position=int(positions[-1]) + 1)
+        driver = self.ctxm.contexts[cid].driver
+        fut = self.submit(cid, tokens, positions, [(len(tokens) - 1, spec)], speculate=False)
+
+        def first(f: Future):
+            try:
+                out = f.result()
+            except BaseException as e:  # noqa: BLE001
+                stream.error = e
+                stream.finished = True
+                stream.done.set(exc=e)
+                return
+            self.cohorts[driver].add(stream, out.slots[0].token)
+
+        fut.add_done_callback(first)
+        return stream
 
     # ------------------------------------------------------------------ staged passes
     def _try_hit(self, cid, tokens, positions, samplers, masks, logit_mask, spec_tokens) -> Optional[Future]:

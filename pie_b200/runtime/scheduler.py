@@ -228,6 +228,9 @@ class BatchScheduler:
                       "cum_latency_us": 0.0, "batch_size_hist": [0] * 8, "chunked_requests": 0,
                       "failed_batches": 0}
         self.expected_cohort: Callable[[], int] = lambda: 0
+        self.cohort = None            # DecodeCohort of this driver (set by the engine)
+        self._inflight = None         # (AsyncTokens, row snapshot) of the pipelined decode step
+        self._parity = 0
         self.thread = threading.Thread(target=self.run, name=name, daemon=True)
         self.thread.start()
 
@@ -286,46 +289,93 @@ class BatchScheduler:
         self.stash = r
         return False
 
+    def _cohort_busy(self) -> bool:
+        return self._inflight is not None or (self.cohort is not None and self.cohort.has_work())
+
+    def _drain_inflight(self) -> None:
+        if self._inflight is not None:
+            handle, snap = self._inflight
+            self._inflight = None
+            self.cohort.absorb(snap, handle.wait())
+
+    def _cohort_step(self) -> None:
+        """Launch decode step s, then absorb step s-1 while s runs on the GPU."""
+        t0 = time.perf_counter()
+        built = self.cohort.build() if self.cohort.has_work() else None
+        handle = None
+        if built is not None:
+            step, snap = built
+            handle = self.driver.decode_async(step, self._parity)
+            self._parity ^= 1
+        self._drain_inflight()
+        if handle is not None:
+            self._inflight = (handle, snap)
+            st = self.stats
+            st["total_batches"] += 1
+            st["total_requests"] += step.r
+            st["total_tokens"] += step.r
+            st["decode_steps"] = st.get("decode_steps", 0) + 1
+            lat = time.perf_counter() - t0
+            st["last_latency_us"] = lat * 1e6
+            st["cum_latency_us"] += lat * 1e6
+            st["batch_size_hist"][min(7, max(1, step.r).bit_length() - 1)] += 1
+            if self.on_batch:
+                self.on_batch(step.r, step.r, lat, "decode")
+
     def run(self) -> None:
         while self.running:
             try:
+                busy = self._cohort_busy()
                 if self.stash is not None:
                     r, self.stash = self.stash, None
+                elif busy:
+                    try:
+                        r = self.q.get_nowait()
+                    except queue.Empty:
+                        r = None
                 else:
                     r = self.q.get()
-                if r is None:
-                    continue
-                t_first = time.perf_counter()
-                self._admit(r)
-                while self.stash is None:
-                    # drain what is already queued
-                    try:
-                        while self.stash is None:
-                            nxt = self.q.get_nowait()
-                            if nxt is None:
-                                break
-                            self._admit(nxt)
-                    except queue.Empty:
-                        pass
-                    if self.stash is not None or not self.running:
-                        break
-                    wait = self.policy.decide(len(self.acc), time.perf_counter() - t_first, self)
-                    if wait <= 0:
-                        break
-                    try:
-                        nxt = self.q.get(timeout=wait)
-                        if nxt is not None:
-                            self._admit(nxt)
-                    except queue.Empty:
-                        break
-                if len(self.acc):
-                    self.execute_batch(self.acc.take())
-            except Exception as e:  # keep the scheduler alive; fail the batch
+                if r is not None:
+                    # an ordinary batch shares the input slab: finish the pipelined step first
+                    self._drain_inflight()
+                    t_first = time.perf_counter()
+                    self._admit(r)
+                    while self.stash is None:
+                        try:
+                            while self.stash is None:
+                                nxt = self.q.get_nowait()
+                                if nxt is None:
+                                    break
+                                self._admit(nxt)
+                        except queue.Empty:
+                            pass
+                        if self.stash is not None or not self.running or busy:
+                            break
+                        wait = self.policy.decide(len(self.acc), time.perf_counter() - t_first, self)
+                        if wait <= 0:
+                            break
+                        try:
+                            nxt = self.q.get(timeout=wait)
+                            if nxt is not None:
+                                self._admit(nxt)
+                        except queue.Empty:
+                            break
+                    if len(self.acc):
+                        self.execute_batch(self.acc.take())
+                if self.cohort is not None and self._cohort_busy():
+                    self._cohort_step()
+            except Exception as e:  # keep the scheduler alive; fail what was in flight
                 for it in self.acc.take():
                     self._deliver(it, e)
+                if self.cohort is not None:
+                    self._inflight = None
+                    self.cohort.abort_all(e)
         exc = self.aborted or RuntimeError("scheduler stopped")
         for it in self.acc.take():
             self._deliver(it, exc)
+        if self.cohort is not None:
+            self._inflight = None
+            self.cohort.abort_all(exc)
         while True:
             try:
                 it = self.q.get_nowait()
@@ -364,7 +414,7 @@ class BatchScheduler:
             self._deliver(it, resp.slots[k:k + n])
             k += n
         if self.on_batch:
-            self.on_batch(items, lat)
+            self.on_batch(len(items), req.num_tokens, lat, "batch")
 
     def _deliver(self, it: PendingRequest, result) -> None:
         st = it.chunk_of

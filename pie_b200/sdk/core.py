@@ -15,6 +15,7 @@ then commit of floor(tokens / page) pages (context.rs:407-455).
 """
 from __future__ import annotations
 
+import asyncio
 import json
 from typing import Any, Iterable, List, Optional, Sequence
 
@@ -515,7 +516,48 @@ class Generator:
             self._pending = None
         return out
 
+    def _offloadable(self) -> bool:
+        """Plain generation (token sampler, no constraints, no inferlet-side speculator, nothing
+        generated yet) can run inside the runtime's decode cohort instead of stepping here."""
+        return (not self._constraints and self.speculator is None and self._pending is None
+                and not self._done and self.sampler.spec.is_token and bool(self.ctx._buffer)
+                and self.ctx._entry.inference.cohorts)
+
+    async def run_offloaded(self, on_tokens=None):
+        """Hand the whole decode loop to the runtime; returns the cohort Stream when it ended."""
+        ctx = self.ctx
+        toks, ctx._buffer = ctx._buffer, []
+        n = self._max if self._max is not None else 1 << 30
+        start = ctx.seq_len
+        ctx._reserve_for(len(toks) + 1)
+        stream = ctx._entry.inference.start_stream(ctx.id, toks, list(range(start, start + len(toks))),
+                                                   self.sampler.spec, n, self._stop)
+        if on_tokens is not None:
+            stream.listeners.append(on_tokens)
+        try:
+            await host.wait(stream.done)
+        except asyncio.CancelledError:
+            stream.cancel()
+            raise
+        kept = getattr(stream, "kept", 0)
+        ctx._seq_len += len(toks) + kept
+        ctx._next_pos = start + len(toks) + kept
+        ctx._buffer = list(stream.tokens[kept:])
+        ctxm = ctx._entry.ctxm
+        full = ctxm.working_page_token_count(ctx.id) // ctx.page_size
+        if full:
+            try:
+                ctxm.commit_working_pages(ctx.id, full)
+            except Exception:
+                pass
+        self._generated = list(stream.tokens)
+        self._done = True
+        return stream
+
     async def collect_tokens(self) -> List[int]:
+        if self._offloadable():
+            await self.run_offloaded()
+            return list(self._generated)
         async for step in self:
             await step.execute()
         return [t for t in self._generated]

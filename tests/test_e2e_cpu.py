@@ -47,8 +47,22 @@ def test_text_completion_matches_dense_oracle():
         want = oracle_greedy(cfg, w, prompt, 64)
         assert got == want
         st = eng.model_status()["models"]["tiny-llama"]
-        assert st["bypass_hits"] > 0          # the staged (speculative) passes were claimed
         assert st["kv_pages_used"] == 0       # everything released with the process
+        assert eng.model("tiny-llama").schedulers[0].stats.get("decode_steps", 0) >= 63   # ran in the cohort
+    finally:
+        eng.shutdown()
+
+
+def test_per_step_inferlet_claims_staged_passes():
+    eng, cfg, w = make_engine()
+    try:
+        prompt = np.random.default_rng(1).integers(0, cfg.vocab_size, 32).tolist()
+        res = eng.run("text-completion", {"prompt_tokens": prompt, "max_tokens": 24, "stop_tokens": [],
+                                          "per_step": True}, timeout=300)
+        assert json.loads(res)["tokens"] == oracle_greedy(cfg, w, prompt, 24)
+        st = eng.model_status()["models"]["tiny-llama"]
+        assert st["bypass_hits"] > 0          # the staged (speculative) passes were claimed
+        assert st["kv_pages_used"] == 0
     finally:
         eng.shutdown()
 
@@ -57,7 +71,8 @@ def test_no_speculation_same_tokens():
     eng, cfg, w = make_engine(policy="greedy", depth=0)
     try:
         prompt = np.random.default_rng(1).integers(0, cfg.vocab_size, 32).tolist()
-        res = eng.run("text-completion", {"prompt_tokens": prompt, "max_tokens": 16, "stop_tokens": []}, timeout=300)
+        res = eng.run("text-completion", {"prompt_tokens": prompt, "max_tokens": 16, "stop_tokens": [],
+                                          "per_step": True}, timeout=300)
         assert json.loads(res)["tokens"] == oracle_greedy(cfg, w, prompt, 16)
     finally:
         eng.shutdown()
