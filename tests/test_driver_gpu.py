@@ -86,7 +86,8 @@ def test_engine_on_gpu_greedy_is_deterministic_and_batched():
         same = sum(x == y for x, y in zip(a, b))
         assert same >= 10    # batch composition may flip a near-tie in bf16, not more
         st = eng.model_status()["models"]["m"]
-        assert st["bypass_hits"] > 0 and st["kv_pages_used"] == 0
+        assert st["kv_pages_used"] == 0
+        assert eng.model("m").schedulers[0].stats.get("decode_steps", 0) > 0   # decoded inside the cohort
         assert drv.stats["graph_replays"] > 0
     finally:
         eng.shutdown()
