@@ -588,3 +588,65 @@ PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const in
 
 // Query tokens covered by one prefill tile for a given GQA group size.
 PIE_API int pie_prefill_tile_tokens(int group) { return PF_ROWS / group; }
+
+// ------------------------------------------------- allocation-free variant
+// See pie_noalloc.h: split-KV decode attention whose scratch lives in this
+// library instead of being passed in, for callers that cannot allocate.
+#include <stdio.h>
+#include <mutex>
+#include "pie_noalloc.h"
+
+// Split-KV partial outputs and log-sum-exps of the allocation-free entry point.
+// Host code must not use this name as an address: it is a host-side stand-in;
+// the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float pie_noalloc_scratch[PIE_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device (looked up once per device).
+int noalloc_scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return PIE_NOALLOC_ERR_SETUP;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, pie_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return PIE_NOALLOC_ERR_SETUP;
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+PIE_API int pie_paged_decode_attn_noalloc(const void* q, const void* kv_layer,
+                                          const int* page_indices, const int* kv_page_indptr,
+                                          const int* item_req, const int* item_start,
+                                          const int* item_end, const int* req_item_indptr,
+                                          const int* num_items_ptr, void* out, int max_items,
+                                          int num_reqs, int hq, int hkv, int head_dim,
+                                          int page_size, float sm_scale, int num_ctas,
+                                          cudaStream_t stream) {
+    if (max_items < 0 || hq <= 0 || head_dim <= 0) return (int)cudaErrorInvalidValue;
+    const long need = pie_decode_attn_scratch_floats(max_items, hq, head_dim);
+    if (need > (long)PIE_NOALLOC_SCRATCH_FLOATS) {
+        fprintf(stderr,
+                "pie_paged_decode_attn_noalloc: max_items=%d, hq=%d, head_dim=%d need %ld floats of "
+                "scratch; the built-in array holds %u. Use fewer work items or pie_paged_decode_attn "
+                "with your own buffer.\n",
+                max_items, hq, head_dim, need, (unsigned)PIE_NOALLOC_SCRATCH_FLOATS);
+        return PIE_NOALLOC_ERR_TOO_LARGE;
+    }
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_for_current_device(&scratch);
+    if (rc != 0) return rc;
+    return pie_paged_decode_attn(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start,
+                                 item_end, req_item_indptr, num_items_ptr, out, scratch, max_items,
+                                 num_reqs, hq, hkv, head_dim, page_size, sm_scale, num_ctas, 1, stream);
+}
