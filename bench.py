@@ -42,6 +42,10 @@ def parse_args():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-device", action="store_true")
     ap.add_argument("--max-tokens", type=int, default=16384)
+    ap.add_argument("--device-loop", default="pipelined", choices=["pipelined", "staged"],
+                    help="pipelined: decode_async with device-fed tokens (all N); staged: inputs pre-staged on the device (N=1)")
+    ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"],
+                    help="fused: GEMM epilogue reduce-scatter + push all-gather over peer memory; nccl: GEMM + all-reduce")
     return ap.parse_args()
 
 
@@ -55,6 +59,7 @@ def main():
             print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
 
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer loads/stores only, no NVLS binding
     import torch
 
     if not torch.cuda.is_available():
@@ -78,7 +83,7 @@ def main():
         import torch.distributed as dist
         from pie_b200.parallel.comm import TPComm
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        comm = TPComm(rank, world, torch.device("cuda", local_rank))
+        comm = TPComm(rank, world, torch.device("cuda", local_rank), fused=args.tp_backend == "fused")
         par = ParallelContext(world, rank, comm)
         barrier = dist.barrier
     if args.gpus != world and rank == 0:
@@ -101,6 +106,7 @@ def main():
 
     if world > 1 and rank != 0:
         comm.follower_loop(driver)      # serves every fire rank 0 publishes, both phases
+        comm.close()
         import torch.distributed as dist
         dist.destroy_process_group()
         return 0
@@ -124,11 +130,15 @@ def main():
     clocks = None
     if not args.skip_device:
         sampler_clk = harness.ClockSampler(local_rank).start()
-        dev = harness.run_device_decode(driver, prompts, args.out_tokens, sampler, args.warmup, args.steps,
-                                        barrier=None)
+        if args.device_loop == "staged" and world == 1:
+            dev = harness.run_device_decode(driver, prompts, args.out_tokens, sampler, args.warmup, args.steps)
+        else:
+            dev = harness.run_pipelined_decode(driver, prompts, args.out_tokens, sampler, args.warmup,
+                                               args.steps, comm=comm)
         clocks = sampler_clk.stop()
     if comm is not None:
         comm.stop_followers()
+        comm.close()
 
     n_req = args.requests
     h2d = d2h = None
@@ -146,7 +156,7 @@ def main():
         "data": "synthetic random-token prompts, random-init N(0,0.02) weights",
         "impl": "ours",
         "config": {"model": cfg.name, "global_batch": n_req, "seq_len": f"prompts U[{args.prompt_min},{args.prompt_max}] + {args.out_tokens} out",
-                   "parallelism": f"tp{world}", "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
+                   "parallelism": f"tp{world}", "tp_backend": args.tp_backend if world > 1 else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
                    "gemm": args.gemm, "layers": cfg.num_hidden_layers,
                    "l2": "working set per step (weights 16 GB + KV > 60 GB) exceeds the 126 MB L2; no flush needed",
                    "valid": not args.layers},

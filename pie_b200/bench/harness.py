@@ -143,6 +143,71 @@ def decode_request(driver, prompts, pages, tokens, step: int, sampler: SamplerSp
     return fold(items, driver.page_size)
 
 
+def run_pipelined_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec, warmup: int, steps: int,
+                         comm=None):
+    """Device-timed decode through `decode_async` (the path the engine's cohort uses): step s is
+    launched with its tokens fed on the device from step s-1, the host only trails one step behind
+    to recycle its input slab. W untimed + K timed steps bracketed by synchronise (+ barrier and
+    max over ranks under tensor parallelism) and CUDA events on the launching stream."""
+    from ..driver.executor import CohortStep
+    ps = driver.page_size
+    pages, first, t_prefill = prefill_contexts(driver, prompts, out_tokens, sampler)
+    r = len(prompts)
+    plen = np.array([len(p) for p in prompts], dtype=np.int64)
+    maxp = max(len(p) for p in pages)
+    table = np.zeros((r, maxp), np.int32)
+    for i, p in enumerate(pages):
+        table[i, :len(p)] = p
+    cols = np.arange(maxp, dtype=np.int32)[None, :]
+    rng = np.random.default_rng(3)
+
+    def make(step: int) -> CohortStep:
+        kv_after = (plen + step + 1).astype(np.int32)
+        used = (kv_after + ps - 1) // ps
+        indptr = np.zeros(r + 1, np.int32)
+        np.cumsum(used, out=indptr[1:])
+        return CohortStep(
+            r=r, host_tokens=np.asarray(first, np.int32),
+            src_row=(np.arange(r, dtype=np.int32) if step > 0 else np.full(r, -1, np.int32)),
+            positions=(plen + step).astype(np.int32), kv_lens=kv_after, page_indptr=indptr,
+            page_indices=table[cols < used[:, None]],
+            temperature=np.full(r, sampler.temperature, np.float32),
+            top_k=np.full(r, sampler.top_k if sampler.kind.name.startswith("TOP_K") else 0, np.int32),
+            top_p=np.full(r, sampler.top_p if "TOP_P" in sampler.kind.name else 1.0, np.float32),
+            min_p=np.zeros(r, np.float32), seeds=rng.integers(1, 2**62, r, dtype=np.int64))
+
+    prev = None
+    ms = None
+    ev0 = ev1 = None
+    for s in range(warmup + steps):
+        if s == warmup:
+            if prev is not None:
+                prev.wait()
+            if comm is not None:
+                comm.mark(False)
+            else:
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+        h = driver.decode_async(make(s), s & 1)
+        if prev is not None:
+            prev.wait()
+        prev = h
+    if comm is not None:
+        ms = comm.mark(True)
+    else:
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+    prev.wait()
+    driver.health()
+    prefill_tokens = sum(t for _, t in t_prefill)
+    prefill_s = sum(d for d, _ in t_prefill)
+    rb = driver._bucket(r) if driver.use_graphs else r
+    return {"ms_total": ms, "ms_per_step": ms / steps, "tokens_per_s": r * steps / (ms / 1e3),
+            "prefill_tokens_per_s": prefill_tokens / max(prefill_s, 1e-9), "rb": rb}
+
+
 def run_device_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec, warmup: int, steps: int,
                       barrier=None):
     """Device-only decode: W untimed + K timed steps, CUDA events on the launching stream."""

@@ -27,6 +27,27 @@ enum GemmEpilogue : int {
     EPI_STORE = 0,     // C = acc
     EPI_RESIDUAL = 1,  // C = acc + R
     EPI_SWIGLU = 2,    // C[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]   (C is [M, N/2])
+    EPI_RS = 3,        // reduce-scatter: rows go to their owner rank's receive buffer (peer stores)
+};
+
+constexpr int TP_MAX_RANKS = 8;
+
+// Tensor-parallel side channel of the fused kernels. All pointers are device addresses valid
+// on THIS GPU; peer_* entries are peer-mapped (NVLink) addresses of the same buffer on rank i.
+//   gated loads : before its first TMA load the producer waits until every rank has pushed its
+//                 rows of the activation (ag_flags[src] >= *ag_epoch, written by peers).
+//   EPI_RS      : the epilogue stores each accumulator row into the receive buffer of the rank
+//                 that owns the row (rows_per_rank consecutive rows per rank, a multiple of 32),
+//                 at [this rank][row within owner][col]; the last epilogue warp of the grid
+//                 bumps the local epoch and writes it into every owner's flag word for this rank.
+struct TpArgs {
+    const int* ag_flags;          // [world] local, written by peers
+    const int* ag_epoch;          // local expected value
+    bf16* peer_recv[TP_MAX_RANKS];
+    int* peer_rs_flags[TP_MAX_RANKS];  // word [rank] of rank i's flag array is at peer_rs_flags[i] + rank
+    int* rs_done;                 // local arrival counter of the epilogue warps
+    int* rs_epoch;                // local count of reduce-scatter ops issued
+    int world, rank, rows_per_rank, gated;
 };
 
 template <int BN>
@@ -43,7 +64,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  bf16* __restrict__ C, const bf16* __restrict__ R, int M, int N, int K, int ldc,
-                 int ldr, int* status) {
+                 int ldr, int* status, const __grid_constant__ TpArgs tp) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -92,6 +113,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             tma_prefetch_desc(&tma_b);
             uint32_t it = 0;
             bool ok = true;
+            if (tp.gated) {
+                // all-gather gate: the A operand is complete once every rank's flag reached the epoch
+                const int e = *reinterpret_cast<const volatile int*>(tp.ag_epoch);
+                const long long t0 = clock64();
+                for (int src = 0; src < tp.world && ok; ++src) {
+                    while (*reinterpret_cast<const volatile int*>(tp.ag_flags + src) < e) {
+                        if (*reinterpret_cast<volatile int*>(status) != 0 || clock64() - t0 > 1500000000ll) {
+                            atomicCAS(status, 0, PIE_ERR_WAIT_PEER);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                __threadfence_system();
+                asm volatile("fence.proxy.async;\n" ::: "memory");
+            }
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const int m_blk = t % tiles_m, n_blk = t / tiles_m;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -155,7 +192,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 tmem_ld_32x32(t_row + c * 32, v);
                 tmem_ld_wait();
                 const int col0 = n_blk * BN + c * 32;
-                if (row < M && col0 < N) {
+                if (EPI == EPI_RS) {
+                    if (row < M && col0 < N) {
+                        const int owner = row / tp.rows_per_rank;
+                        const int local = row - owner * tp.rows_per_rank;
+                        bf16* dst = tp.peer_recv[owner] +
+                                    ((size_t)tp.rank * tp.rows_per_rank + local) * (size_t)N + col0;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (col0 + 8 * j >= N) break;
+                            float o[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(v[8 * j + e]);
+                            *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
+                        }
+                    }
+                } else if (row < M && col0 < N) {
                     if (EPI == EPI_SWIGLU) {
                         bf16* dst = C + (size_t)row * ldc + (col0 >> 1);
                         float o[16];
@@ -192,6 +244,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (EPI == EPI_RS) {
+                // publish: this warp's rows of the tile are in the owners' buffers
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0) {
+                    const int total = num_tiles * 4;
+                    if (atomicAdd(tp.rs_done, 1) + 1 == total) {
+                        *tp.rs_done = 0;
+                        const int e = *reinterpret_cast<volatile int*>(tp.rs_epoch) + 1;
+                        *reinterpret_cast<volatile int*>(tp.rs_epoch) = e;
+                        __threadfence_system();
+                        for (int p = 0; p < tp.world; ++p)
+                            *reinterpret_cast<volatile int*>(tp.peer_rs_flags[p] + tp.rank) = e;
+                    }
+                }
+            }
         }
     }
     tc_fence_before();
@@ -244,7 +312,8 @@ extern "C" int pie_make_tma_2d_bf16(CUtensorMap* map, const void* ptr, long rows
 
 template <int BN, int EPI>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M,
-                       int N, int K, int ldc, int ldr, int* status, int num_sms, cudaStream_t st) {
+                       int N, int K, int ldc, int ldr, int* status, int num_sms, cudaStream_t st,
+                       const TpArgs& tp = TpArgs{}) {
     using Cfg = GemmCfg<BN>;
     auto kern = gemm_bf16_kernel<BN, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -253,7 +322,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, co
     const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
     const int grid = tiles < num_sms ? tiles : num_sms;
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
-                                                      ldr, status);
+                                                      ldr, status, tp);
     return (int)cudaGetLastError();
 }
 
@@ -296,6 +365,54 @@ PIE_API int pie_gemm_bf16(const void* A, const void* W, void* C, const void* R, 
         case EPI_RESIDUAL: return launch_gemm<BN_, EPI_RESIDUAL>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
         case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
         default: return (int)cudaErrorInvalidValue;                                               \
+    }
+    if (bn == 256) { GO(256) }
+    else if (bn == 128) { GO(128) }
+    else if (bn == 64) { GO(64) }
+#undef GO
+    return (int)cudaErrorInvalidValue;
+}
+
+// Tensor-parallel GEMM: `tp_blob` points at a host copy of TpArgs (see pie_tp_args_size).
+//   epilogue EPI_RS  : y = A * W^T is not stored locally; each row goes to its owner's receive buffer
+//   gated (tp.gated) : A is the all-gathered activation; loads wait for every rank's push flag
+PIE_API int pie_tp_args_size() { return (int)sizeof(TpArgs); }
+
+PIE_API int pie_tp_fill_args(void* blob, const int* ag_flags, const int* ag_epoch, void* const* peer_recv,
+                             int* const* peer_rs_flags, int* rs_done, int* rs_epoch, int world, int rank,
+                             int rows_per_rank, int gated) {
+    if (world > TP_MAX_RANKS || world < 1) return (int)cudaErrorInvalidValue;
+    TpArgs a{};
+    a.ag_flags = ag_flags; a.ag_epoch = ag_epoch; a.rs_done = rs_done; a.rs_epoch = rs_epoch;
+    for (int i = 0; i < world; ++i) {
+        a.peer_recv[i] = (bf16*)peer_recv[i];
+        a.peer_rs_flags[i] = peer_rs_flags[i];
+    }
+    a.world = world; a.rank = rank; a.rows_per_rank = rows_per_rank; a.gated = gated;
+    *reinterpret_cast<TpArgs*>(blob) = a;
+    return 0;
+}
+
+PIE_API int pie_gemm_bf16_tp(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
+                             int ldc, int epilogue, const void* tp_blob, int rows_per_rank, int gated,
+                             int force_bn, int* status, int num_sms, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || N % 8) return (int)cudaErrorInvalidValue;
+    if (epilogue == EPI_SWIGLU && N % 32) return (int)cudaErrorInvalidValue;
+    TpArgs tp = *reinterpret_cast<const TpArgs*>(tp_blob);
+    tp.rows_per_rank = rows_per_rank;
+    tp.gated = gated;
+    if (epilogue == EPI_RS && (rows_per_rank % 32 || rows_per_rank <= 0)) return (int)cudaErrorInvalidValue;
+    const int bn = force_bn > 0 ? force_bn : pick_bn(M, N, num_sms);
+    CUtensorMap ta, tb;
+    if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
+    if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, bn) != 0) return (int)cudaErrorInvalidValue;
+#define GO(BN_)                                                                                    \
+    switch (epilogue) {                                                                            \
+        case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, num_sms, st, tp);   \
+        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, num_sms, st, tp); \
+        case EPI_RS: return launch_gemm<BN_, EPI_RS>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, num_sms, st, tp);         \
+        default: return (int)cudaErrorInvalidValue;                                                \
     }
     if (bn == 256) { GO(256) }
     else if (bn == 128) { GO(128) }

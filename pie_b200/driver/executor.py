@@ -151,6 +151,13 @@ class TorchDriver:
         hkv = self.model.hkv
         if num_pages <= 0:
             num_pages = self._plan_pages(hkv, gpu_mem_utilization)
+            if self.par.tp_size > 1:
+                # page ids are global to the replica: every rank must hold the same number of pages
+                import torch.distributed as dist
+                if dist.is_available() and dist.is_initialized():
+                    t = torch.tensor([num_pages], dtype=torch.int64, device=self.device)
+                    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                    num_pages = int(t.item())
         self.kv = KVCache(cfg.num_hidden_layers, num_pages, hkv, page_size, cfg.head_dim, self.dtype,
                           self.device, swap_pages)
         self.max_requests, self.max_tokens = max_requests, max_tokens
@@ -470,7 +477,11 @@ class TorchDriver:
         nslots = len(req.slot_samplers)
         decode = (req.num_requests > 0 and bool((qlens == 1).all())
                   and not (req.has_user_mask is not None and np.any(req.has_user_mask)))
-        if self.par.tp_size > 1 and self.par.comm is not None:
+        if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
+            # followers must draw the same tokens: fix the per-fire seeds before publishing
+            from dataclasses import replace as _replace
+            req.slot_samplers = [_replace(sp, seed=int(self.rng.integers(1, 2**62))) if sp.is_token and not sp.seed
+                                 else sp for sp in req.slot_samplers]
             self.par.comm.publish_step(req, decode)
         self._token_slots = self._sampler_params(req, None) if nslots else []
         t1 = time.perf_counter()
@@ -640,6 +651,8 @@ class TorchDriver:
         return self.graphs[rb].launches + 1
 
     def copy(self, req: CopyRequest) -> None:
+        if self.par.tp_size > 1 and self.par.comm is not None:
+            self.par.comm.publish_copy(req)     # every rank holds a shard of each page
         self.kv.copy(req)
 
     def health(self) -> bool:

@@ -54,7 +54,7 @@ class Transformer:
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.inv_freq = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, self.device)
         self.gemm_backend = gemm_backend if self.device.type == "cuda" else "torch"
-        self.vocab_local = weights["lm_head"].shape[0]
+        self.vocab_local = weights["lm_head"].shape[0] * (self.par.tp_size if self.par.comm is not None else 1)
 
     # ------------------------------------------------------------------ linear algebra
     def _gemm(self, x, w, residual=None, swiglu=False):
@@ -92,7 +92,39 @@ class Transformer:
         from .moe import moe_block
         return moe_block(self, x, lw, h)
 
+    def _fused_tp(self) -> bool:
+        return self.par.tp_size > 1 and self.par.comm is not None and getattr(self.par.comm, "fused", False) \
+            and self.device.type == "cuda"
+
+    def _forward_hidden_tp(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
+        """Tensor-parallel forward over the fused kernels: the residual stream is row-sharded,
+        every row-parallel GEMM scatters its partial rows to their owners from its epilogue, the
+        owner reduces + normalises + pushes, and the next column-parallel GEMM gates its loads
+        on the push flags. Returns the final-normalised hidden states of all rows."""
+        cfg, w, comm = self.cfg, self.w, self.par.comm
+        page_size = kv_cache.shape[4]
+        n = fi.tokens.shape[0]
+        layers = w["layers"]
+        comm.embed_norm_push(fi.tokens, w["embed"], layers[0]["ln1"], cfg.rms_norm_eps, n)
+        for li, lw in enumerate(layers):
+            qkv = comm.gemm_gated(lw["wqkv"], n)
+            if "bqkv" in lw:
+                qkv = qkv + lw["bqkv"]
+            q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, lw.get("q_norm"),
+                                         lw.get("k_norm"), kv_cache[li], self.hq, self.hkv, self.d,
+                                         page_size, cfg.rms_norm_eps)
+            a = self._attention(q, kv_cache[li], fi)
+            comm.gemm_rs(a.reshape(n, self.hq * self.d), lw["wo"], n)
+            comm.reduce_norm_push(lw["ln2"], cfg.rms_norm_eps, n)
+            act = comm.gemm_gated(lw["w_gate_up"], n, swiglu=True)
+            comm.gemm_rs(act, lw["w_down"], n)
+            nxt = layers[li + 1]["ln1"] if li + 1 < len(layers) else w["final_norm"]
+            comm.reduce_norm_push(nxt, cfg.rms_norm_eps, n)
+        return comm.wait_gathered(n)
+
     def forward_hidden(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
+        if self._fused_tp() and "experts_gate_up" not in self.w["layers"][0]:
+            return self._forward_hidden_tp(fi, kv_cache)
         cfg, w = self.cfg, self.w
         page_size = kv_cache.shape[4]
         if self.par.tp_size > 1 and w.get("embed_sharded", False):
@@ -122,8 +154,15 @@ class Transformer:
     def logits(self, h: torch.Tensor, fi: ForwardInputs) -> torch.Tensor:
         """lm_head on the requested rows only ('compact logit rows')."""
         rows = h if fi.logit_rows is None else ops.gather_rows(h, fi.logit_rows)
+        if self._fused_tp() and "experts_gate_up" not in self.w["layers"][0]:
+            # h is already final-normalised and gathered; every rank computes its vocabulary slice
+            local = self.par.comm.gemm_gated(self.w["lm_head"], rows.shape[0], x=rows)
+            return self.par.comm.all_gather_logits(local)
         x = ops.rmsnorm(rows, self.w["final_norm"], self.cfg.rms_norm_eps)
-        return self._gemm(x, self.w["lm_head"])
+        y = self._gemm(x, self.w["lm_head"])
+        if self.par.tp_size > 1 and self.par.comm is not None:
+            y = self.par.comm.all_gather_logits(y)
+        return y
 
     def forward(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
         return self.logits(self.forward_hidden(fi, kv_cache), fi)

@@ -1,0 +1,97 @@
+"""Tensor-parallel parity check, run as one process per GPU:
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
+        -m pie_b200.parallel.tp_check [--backend fused|nccl]
+
+Rank 0 drives a prefill batch and two decode steps through the tensor-parallel driver (followers
+mirror every fire from the control ring) and compares the logits with a single-GPU driver holding
+the unsharded weights of the same seed. Same idea as the reference's tp=1 vs tp=2 parity script
+(driver/cuda/tests/parity_tp.py:1-16: cosine, arg-max, top-5 overlap). Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer loads/stores only, no NVLS binding
+
+import numpy as np
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--backend", default="fused")
+    ap.add_argument("--hidden", type=int, default=512)
+    a = ap.parse_args()
+    import torch.distributed as dist
+    from ..driver.executor import TorchDriver
+    from ..driver.schema import SamplerKind, SamplerSpec
+    from ..models.config import preset
+    from ..models.transformer import ParallelContext
+    from ..runtime.scheduler import PendingRequest, fold
+    from .comm import TPComm
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = preset("tiny-llama", hidden_size=a.hidden, intermediate_size=1408, num_attention_heads=8,
+                 num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16")
+    comm = TPComm(rank, world, dev, fused=a.backend == "fused")
+    drv = TorchDriver(cfg, dev, num_pages=64, page_size=16, max_requests=8, max_tokens=512,
+                      par=ParallelContext(world, rank, comm), seed=0)
+    comm.attach(drv)
+    if rank != 0:
+        comm.follower_loop(drv)
+        comm.close()
+        dist.destroy_process_group()
+        return
+    ref = TorchDriver(cfg, dev, num_pages=64, page_size=16, max_requests=8, max_tokens=512, seed=0)
+    rng = np.random.default_rng(0)
+    lens = [37, 5, 64]
+    prompts = [rng.integers(0, cfg.vocab_size, n).tolist() for n in lens]
+    pages, nxt = [], 0
+    for n in lens:
+        k = -(-(n + 8) // 16)
+        pages.append(list(range(nxt, nxt + k)))
+        nxt += k
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    report = {"backend": a.backend, "world": world, "checks": []}
+
+    def compare(tag, r_tp, r_ref):
+        for i, (x, y) in enumerate(zip(r_tp.slots, r_ref.slots)):
+            g = np.frombuffer(x.logits, dtype=np.float32)
+            w = np.frombuffer(y.logits, dtype=np.float32)
+            cos = float(np.dot(g, w) / (np.linalg.norm(g) * np.linalg.norm(w) + 1e-12))
+            top5 = len(set(np.argsort(g)[-5:]) & set(np.argsort(w)[-5:]))
+            report["checks"].append({"tag": tag, "req": i, "cos": cos, "max_abs": float(np.abs(g - w).max()),
+                                     "argmax_equal": bool(g.argmax() == w.argmax()), "top5_overlap": top5})
+
+    items = lambda: [PendingRequest(i, p, list(range(len(p))), pg, 0, [(len(p) - 1, raw)])
+                     for i, (p, pg) in enumerate(zip(prompts, pages))]
+    r_tp = drv.fire_batch(fold(items(), 16))
+    r_ref = ref.fire_batch(fold(items(), 16))
+    compare("prefill", r_tp, r_ref)
+    toks = [int(np.frombuffer(s.logits, dtype=np.float32).argmax()) for s in r_ref.slots]
+    for step in range(2):
+        mk = lambda: [PendingRequest(i, [t], [len(p) + step], pg, len(p) + step, [(0, raw)])
+                      for i, (t, p, pg) in enumerate(zip(toks, prompts, pages))]
+        r_tp = drv.fire_batch(fold(mk(), 16))
+        r_ref = ref.fire_batch(fold(mk(), 16))
+        compare(f"decode{step}", r_tp, r_ref)
+        toks = [int(np.frombuffer(s.logits, dtype=np.float32).argmax()) for s in r_ref.slots]
+    comm.stop_followers()
+    torch.cuda.synchronize()
+    drv.health()
+    report["ok"] = all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
+    report["graph_replays"] = drv.stats["graph_replays"]
+    print(json.dumps(report))
+    comm.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,27 @@
+"""Tensor parallelism on real GPUs (needs >= 2): fused peer-memory path and NCCL baseline path
+against a single-GPU run of the same weights."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("backend", ["fused", "nccl"])
+def test_tp2_logits_match_single_gpu(backend):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    port = 29511 + (0 if backend == "fused" else 1)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), "-m", "pie_b200.parallel.tp_check", "--backend", backend]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert out.returncode == 0 and lines, out.stdout[-2000:] + out.stderr[-4000:]
+    rep = json.loads(lines[-1])
+    assert rep["ok"], rep
