@@ -107,9 +107,7 @@ def main():
     if world > 1 and rank != 0:
         comm.follower_loop(driver)      # serves every fire rank 0 publishes, both phases
         comm.close()
-        import torch.distributed as dist
-        dist.destroy_process_group()
-        return 0
+        _hard_exit(0)
 
     e2e = None
     if not args.skip_e2e:
@@ -175,9 +173,16 @@ def main():
                        "requests_per_fire": e2e.get("window_requests_per_fire")}
     print(json.dumps(line))
     if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        _hard_exit(0)
     return 0
+
+
+def _hard_exit(code: int) -> None:
+    """Leave without tearing down NCCL communicators that CUDA graphs still reference (that
+    teardown can block); everything this process owns dies with it."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(code)
 
 
 if __name__ == "__main__":

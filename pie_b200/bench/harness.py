@@ -200,7 +200,7 @@ def run_pipelined_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec,
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1)
     prev.wait()
-    driver.health()
+    driver.check_status_host()
     prefill_tokens = sum(t for _, t in t_prefill)
     prefill_s = sum(d for d, _ in t_prefill)
     rb = driver._bucket(r) if driver.use_graphs else r
@@ -229,7 +229,8 @@ def run_device_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec, wa
     torch.cuda.synchronize()
     if barrier:
         barrier()
-    driver.health()
+    from .. import ops
+    ops.check_kernel_status(driver.device)
     ms = ev0.elapsed_time(ev1)
     prefill_tokens = sum(t for _, t in t_prefill)
     prefill_s = sum(d for d, _ in t_prefill)

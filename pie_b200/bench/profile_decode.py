@@ -58,7 +58,8 @@ def main():
         torch.cuda.synchronize()
         toks = [sl.token for sl in resp.slots]
         print(f"decode step {s}: {ev0.elapsed_time(ev1):.3f} ms")
-    drv.health()
+    from .. import ops
+    ops.check_kernel_status(drv.device)
 
 
 if __name__ == "__main__":

@@ -109,13 +109,15 @@ class CohortStep:
 class AsyncTokens:
     """Result handle of `decode_async`: wait() blocks until the step's tokens are on the host."""
 
-    def __init__(self, event, host_buf, r: int, ready: Optional[np.ndarray] = None):
-        self.event, self.host_buf, self.r, self.ready = event, host_buf, r, ready
+    def __init__(self, event, host_buf, r: int, ready: Optional[np.ndarray] = None, driver=None):
+        self.event, self.host_buf, self.r, self.ready, self.driver = event, host_buf, r, ready, driver
 
     def wait(self) -> np.ndarray:
         if self.ready is None:
             self.event.synchronize()
             self.ready = self.host_buf[:self.r].numpy().copy()
+            if self.driver is not None:
+                self.driver.check_status_host()
         return self.ready
 
 
@@ -184,6 +186,8 @@ class TorchDriver:
             self.sampled_host = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
             self.cohort_sampled = [torch.zeros(rows, dtype=torch.int32, device=self.device) for _ in range(2)]
             self.cohort_host = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._failed: Optional[str] = None
         self.use_graphs = use_graphs and self.cuda
         self.buckets = graph_buckets(max_requests)
         self.graphs: Dict[int, _Graph] = {}
@@ -285,7 +289,7 @@ class TorchDriver:
         from ..ops import _lib
         g = torch.cuda.CUDAGraph()
         before = _lib.LAUNCHES
-        with torch.cuda.graph(g):
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             logits = self.model.forward(fi, self.kv.data)
         # the decode-attention launcher issues two kernels (split-KV pass + merge) per layer
         return _Graph(g, logits, rb, _lib.LAUNCHES - before + self.cfg.num_hidden_layers)
@@ -402,8 +406,10 @@ class TorchDriver:
                            s.d("top_p", k).view(torch.float32), s.d("min_p", k).view(torch.float32),
                            s.d("seeds", k, torch.int64), mask_bits, mask_row, out=self.sampled)
                 self.sampled_host[:k].copy_(self.sampled[:k], non_blocking=True)
+                self.status_host.copy_(ops.kernel_status(self.device), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
                 tokens = self.sampled_host[:k].numpy().copy()
+                self.check_status_host()
             else:
                 tokens = self._sample_cpu(lg, k, mask_bits, mask_row)
             for j, i in enumerate(token_slots):
@@ -556,7 +562,7 @@ class TorchDriver:
         ev = torch.cuda.Event()
         ev.record()
         self.stats["fires"] += 1
-        return AsyncTokens(ev, self.cohort_host[parity & 1], r)
+        return AsyncTokens(ev, self.cohort_host[parity & 1], r, driver=self)
 
     def _launch_decode(self, r: int, rb: int, npg: int, parity: int) -> None:
         """Device side of a pipelined decode step (also what tensor-parallel followers run)."""
@@ -576,6 +582,7 @@ class TorchDriver:
                    s.d("top_p", r).view(torch.float32), s.d("min_p", r).view(torch.float32),
                    s.d("seeds", r, torch.int64), None, None, out=cur)
         self.cohort_host[parity & 1][:r].copy_(cur[:r], non_blocking=True)
+        self.status_host.copy_(ops.kernel_status(self.device), non_blocking=True)
 
     def _decode_sync_cpu(self, step: "CohortStep") -> "AsyncTokens":
         """CPU drivers have no stream to pipeline on: resolve the token feed on the host and run
@@ -655,10 +662,21 @@ class TorchDriver:
             self.par.comm.publish_copy(req)     # every rank holds a shard of each page
         self.kv.copy(req)
 
+    def check_status_host(self) -> None:
+        """Raise if a kernel gave up on a bounded wait (reads the pinned copy of the status word
+        that the last fire brought back; call only after that fire's stream work is complete)."""
+        if self.cuda and int(self.status_host[0]) != 0:
+            code = int(self.status_host[0])
+            self._failed = f"a kernel gave up on a bounded wait (status {code})"
+            self.status_host[0] = 0
+            ops.kernel_status(self.device).zero_()
+            from ..ops._lib import KernelLibraryError
+            raise KernelLibraryError(self._failed)
+
     def health(self) -> bool:
-        if self.cuda:
-            ops.check_kernel_status(self.device)
-        return True
+        """Called from the watchdog thread: host state only (a CUDA call here could invalidate a
+        graph capture running on the scheduler thread)."""
+        return self._failed is None
 
     def shutdown(self) -> None:
         self.graphs.clear()

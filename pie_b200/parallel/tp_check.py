@@ -47,8 +47,7 @@ def main():
     if rank != 0:
         comm.follower_loop(drv)
         comm.close()
-        dist.destroy_process_group()
-        return
+        os._exit(0)
     ref = TorchDriver(cfg, dev, num_pages=64, page_size=16, max_requests=8, max_tokens=512, seed=0)
     rng = np.random.default_rng(0)
     lens = [37, 5, 64]
@@ -85,12 +84,13 @@ def main():
         toks = [int(np.frombuffer(s.logits, dtype=np.float32).argmax()) for s in r_ref.slots]
     comm.stop_followers()
     torch.cuda.synchronize()
-    drv.health()
+    from .. import ops
+    ops.check_kernel_status(dev)
     report["ok"] = all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
     report["graph_replays"] = drv.stats["graph_replays"]
-    print(json.dumps(report))
+    print(json.dumps(report), flush=True)
     comm.close()
-    dist.destroy_process_group()
+    os._exit(0)
 
 
 if __name__ == "__main__":

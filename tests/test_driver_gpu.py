@@ -66,7 +66,9 @@ def test_prefill_and_decode_logits_match_oracle(backend):
         got = np.frombuffer(resp2.slots[i].logits, dtype=np.float32)
         want = dense_reference_forward(cfg, wc, torch.tensor(p + [t]))[-1].numpy()
         assert np.abs(got - want).max() < 0.08 * max(1.0, np.abs(want).max())
-    drv.health()
+    from pie_b200 import ops
+    ops.check_kernel_status(drv.device)
+    assert drv.health()
 
 
 def test_engine_on_gpu_greedy_is_deterministic_and_batched():
