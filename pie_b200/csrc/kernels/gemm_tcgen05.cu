@@ -60,11 +60,68 @@ struct GemmCfg {
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+// Stream-K side of the kernel. With `enabled`, the (tile, k-block) units of the whole problem are
+// split evenly over the CTAs instead of whole tiles, so skinny problems (few tiles, long K) keep
+// every SM busy. A CTA whose share covers only part of a tile's K range writes its fp32 partial
+// tile to `ws` and bumps the tile's arrival counter; the last warp to arrive for a 32-row quarter
+// adds the other partials and runs the real epilogue. Nobody waits for anybody.
+//   ws  : [(grid + num_tiles)][128][BN] floats, slot = cta + tile
+//   cnt : [num_tiles][4] ints, zero before the launch; the last arriver resets its counter
+struct StreamKArgs {
+    float* ws;
+    int* cnt;
+    int enabled;
+};
+
+struct Segment {
+    int tile, kb0, kb1;
+};
+
+// Walks the work of one CTA; every role of the CTA walks the same sequence.
+struct SegmentWalk {
+    long long u, u_end;
+    int t, t_step, num_tiles, num_kb;
+    bool sk;
+    __device__ SegmentWalk(bool streamk, int num_tiles_, int num_kb_)
+        : num_tiles(num_tiles_), num_kb(num_kb_), sk(streamk) {
+        if (sk) {
+            const long long total = (long long)num_tiles * num_kb;
+            u = total * blockIdx.x / gridDim.x;
+            u_end = total * (blockIdx.x + 1) / gridDim.x;
+        } else {
+            t = blockIdx.x;
+            t_step = gridDim.x;
+        }
+    }
+    __device__ bool next(Segment& s) {
+        if (sk) {
+            if (u >= u_end) return false;
+            s.tile = (int)(u / num_kb);
+            s.kb0 = (int)(u - (long long)s.tile * num_kb);
+            const long long left = u_end - u;
+            s.kb1 = (int)min((long long)num_kb, s.kb0 + left);
+            u += s.kb1 - s.kb0;
+            return true;
+        }
+        if (t >= num_tiles) return false;
+        s.tile = t;
+        s.kb0 = 0;
+        s.kb1 = num_kb;
+        t += t_step;
+        return true;
+    }
+};
+
+// CTA whose unit range contains unit `unit` (ranges are [c*total/grid, (c+1)*total/grid)).
+__device__ __forceinline__ int streamk_cta_of(long long unit, long long total, int grid) {
+    return (int)(((unit + 1) * grid + total - 1) / total - 1);
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  bf16* __restrict__ C, const bf16* __restrict__ R, int M, int N, int K, int ldc,
-                 int ldr, int* status, const __grid_constant__ TpArgs tp) {
+                 int ldr, int* status, const __grid_constant__ TpArgs tp, const StreamKArgs sk) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -129,9 +186,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 __threadfence_system();
                 asm volatile("fence.proxy.async;\n" ::: "memory");
             }
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int m_blk = t % tiles_m, n_blk = t / tiles_m;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb);
+            Segment seg;
+            while (ok && walk.next(seg)) {
+                const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
@@ -153,12 +212,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tcount) {
+            SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb);
+            Segment seg;
+            for (; ok && walk.next(seg); ++tcount) {
                 const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
@@ -168,7 +229,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
 #pragma unroll
                     for (int k = 0; k < GEMM_BK / 16; ++k)
-                        umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0);
+                        umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(tfull_bar(acc));
@@ -178,19 +239,68 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         // ----------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lanes [32q, 32q+32) belong to this warp
         uint32_t tcount = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tcount) {
-            const int m_blk = t % tiles_m, n_blk = t / tiles_m;
+        SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb);
+        Segment seg;
+        const long long total_units = (long long)num_tiles * num_kb;
+        for (; walk.next(seg); ++tcount) {
+            const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
             const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
             const bool got = mbar_wait(tfull_bar(acc), aph, status, PIE_ERR_WAIT_MMA);
             if (!__all_sync(0xffffffffu, got)) break;
             tc_fence_after();
             const int row = m_blk * GEMM_BM + q * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+            const bool partial = seg.kb0 != 0 || seg.kb1 != num_kb;
+            bool finalise = true;
+            int c_first = 0, c_last = -1;
+            if (partial) {
+                // park this warp's 32 rows of the partial tile, then count the arrival
+                float* mine = sk.ws + ((size_t)(blockIdx.x + seg.tile) * GEMM_BM + q * 32 + lane) * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        reinterpret_cast<uint4*>(mine + c * 32)[j] =
+                            make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+                __threadfence();
+                __syncwarp();
+                c_first = streamk_cta_of((long long)seg.tile * num_kb, total_units, gridDim.x);
+                c_last = streamk_cta_of((long long)(seg.tile + 1) * num_kb - 1, total_units, gridDim.x);
+                int last = 0;
+                if (lane == 0) {
+                    int* ctr = sk.cnt + seg.tile * 4 + q;
+                    last = (atomicAdd(ctr, 1) + 1 == c_last - c_first + 1) ? 1 : 0;
+                    if (last) *ctr = 0;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                finalise = last != 0;
+                if (finalise) __threadfence();
+            }
+            if (finalise) {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32(t_row + c * 32, v);
                 tmem_ld_wait();
+                if (partial) {
+                    for (int cc = c_first; cc <= c_last; ++cc) {
+                        if (cc == (int)blockIdx.x) continue;
+                        const float* other =
+                            sk.ws + ((size_t)(cc + seg.tile) * GEMM_BM + q * 32 + lane) * BN + c * 32;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 o4 = __ldcg(reinterpret_cast<const float4*>(other) + j);
+                            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + o4.x);
+                            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + o4.y);
+                            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + o4.z);
+                            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + o4.w);
+                        }
+                    }
+                }
                 const int col0 = n_blk * BN + c * 32;
                 if (EPI == EPI_RS) {
                     if (row < M && col0 < N) {
@@ -241,10 +351,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     }
                 }
             }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
-            if (EPI == EPI_RS) {
+            if (EPI == EPI_RS && finalise) {
                 // publish: this warp's rows of the tile are in the owners' buffers
                 __threadfence_system();
                 __syncwarp();
@@ -310,40 +421,83 @@ extern "C" int pie_make_tma_2d_bf16(CUtensorMap* map, const void* ptr, long rows
     return (int)r;
 }
 
+// Per-device stream-K workspace, registered once by the caller (pie_gemm_set_workspace).
+struct GemmWorkspace {
+    float* ws = nullptr;
+    long ws_floats = 0;
+    int* cnt = nullptr;
+    int cnt_ints = 0;
+};
+static GemmWorkspace g_gemm_ws[64];
+
+// ws: fp32 scratch for partial tiles; cnt: zero-initialised arrival counters (the kernel leaves
+// them zero). Without a registered workspace every GEMM runs with whole-tile scheduling.
+PIE_API int pie_gemm_set_workspace(int device, float* ws, long ws_floats, int* cnt, int cnt_ints) {
+    if (device < 0 || device >= 64) return (int)cudaErrorInvalidValue;
+    g_gemm_ws[device] = GemmWorkspace{ws, ws_floats, cnt, cnt_ints};
+    return 0;
+}
+
+struct GemmPlan {
+    int bn, grid, streamk;
+};
+
+// Tile width and scheduling. Whole-tile scheduling costs ceil(tiles / SMs) waves of one tile each;
+// stream-K spreads the same k-blocks evenly and pays a fix-up per split tile. Costs are in units
+// of "output columns per CTA" (time is proportional to it for a fixed K).
+static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const GemmWorkspace& w) {
+    const int tm = (M + GEMM_BM - 1) / GEMM_BM;
+    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+    const int cands[3] = {256, 128, 64};
+    // relative time per column: narrow tiles re-read A more often and amortise pipeline fill worse
+    const double per_col[3] = {1.0, 1.08, 1.25};
+    GemmPlan best{64, 1, 0};
+    double best_cost = 1e30;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = cands[i];
+        if (force_bn > 0 ? bn != force_bn : (bn > 64 && N < bn)) continue;
+        const long tiles = (long)tm * ((N + bn - 1) / bn);
+        const long waves = (tiles + num_sms - 1) / num_sms;
+        const double dp = (double)waves * bn * per_col[i];
+        if (dp < best_cost) {
+            best_cost = dp;
+            best = GemmPlan{bn, (int)(tiles < num_sms ? tiles : num_sms), 0};
+        }
+        // stream-K candidate
+        const long units = tiles * num_kb;
+        long grid = units / 4 < num_sms ? units / 4 : num_sms;   // at least 4 k-blocks per CTA
+        if (grid < 1 || !w.ws || tiles > 2L * num_sms || tiles % grid == 0) continue;
+        if ((grid + tiles) * (long)GEMM_BM * bn > w.ws_floats || tiles * 4 > w.cnt_ints) continue;
+        const double sk = (double)tiles * bn * per_col[i] / grid + 0.12 * bn;
+        if (sk < 0.92 * best_cost) {
+            best_cost = sk;
+            best = GemmPlan{bn, (int)grid, 1};
+        }
+    }
+    return best;
+}
+
 template <int BN, int EPI>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M,
-                       int N, int K, int ldc, int ldr, int* status, int num_sms, cudaStream_t st,
-                       const TpArgs& tp = TpArgs{}) {
+                       int N, int K, int ldc, int ldr, int* status, const GemmPlan& plan,
+                       const GemmWorkspace& w, cudaStream_t st, const TpArgs& tp = TpArgs{}) {
     using Cfg = GemmCfg<BN>;
     auto kern = gemm_bf16_kernel<BN, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
-    const int grid = tiles < num_sms ? tiles : num_sms;
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
-                                                      ldr, status, tp);
+    StreamKArgs sk{w.ws, w.cnt, plan.streamk};
+    kern<<<plan.grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
+                                                           ldr, status, tp, sk);
     return (int)cudaGetLastError();
 }
 
-// Column-tile width: the widest tile whose last wave is still reasonably full.
-static int pick_bn(int M, int N, int num_sms) {
-    const int tm = (M + GEMM_BM - 1) / GEMM_BM;
-    int best = 64;
-    double best_cost = 1e30;
-    const int cands[3] = {256, 128, 64};
-    // relative time of one tile per column of output (narrow tiles re-read A more often
-    // and amortise the pipeline fill over less work)
-    const double per_col[3] = {1.0, 1.08, 1.25};
-    for (int i = 0; i < 3; ++i) {
-        const int bn = cands[i];
-        if (bn > 64 && N < bn) continue;
-        const long tiles = (long)tm * ((N + bn - 1) / bn);
-        const long waves = (tiles + num_sms - 1) / num_sms;
-        const double cost = (double)waves * bn * per_col[i];
-        if (cost < best_cost) { best_cost = cost; best = bn; }
-    }
-    return best;
+static int current_workspace(GemmWorkspace* out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    *out = (dev >= 0 && dev < 64) ? g_gemm_ws[dev] : GemmWorkspace{};
+    return 0;
 }
 
 // C[M,N] (or [M,N/2] for the SwiGLU epilogue) = A[M,K] * W[N,K]^T.
@@ -355,15 +509,19 @@ PIE_API int pie_gemm_bf16(const void* A, const void* W, void* C, const void* R, 
     if (K <= 0 || K % 8 || N % 8 || ldc % 8 || (epilogue == EPI_RESIDUAL && ldr % 8))
         return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_SWIGLU && N % 32) return (int)cudaErrorInvalidValue;
-    const int bn = force_bn > 0 ? force_bn : pick_bn(M, N, num_sms);
+    GemmWorkspace w;
+    if (int rc = current_workspace(&w)) return rc;
+    if (force_bn < 0) { w = GemmWorkspace{}; force_bn = -force_bn == 1 ? 0 : -force_bn; }  // negative: whole-tile only
+    const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w);
+    const int bn = plan.bn;
     CUtensorMap ta, tb;
     if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
     if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, bn) != 0) return (int)cudaErrorInvalidValue;
 #define GO(BN_)                                                                                   \
     switch (epilogue) {                                                                           \
-        case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
-        case EPI_RESIDUAL: return launch_gemm<BN_, EPI_RESIDUAL>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
-        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, R, M, N, K, ldc, ldr, status, num_sms, st); \
+        case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, R, M, N, K, ldc, ldr, status, plan, w, st); \
+        case EPI_RESIDUAL: return launch_gemm<BN_, EPI_RESIDUAL>(ta, tb, C, R, M, N, K, ldc, ldr, status, plan, w, st); \
+        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, R, M, N, K, ldc, ldr, status, plan, w, st); \
         default: return (int)cudaErrorInvalidValue;                                               \
     }
     if (bn == 256) { GO(256) }
@@ -403,15 +561,18 @@ PIE_API int pie_gemm_bf16_tp(const void* A, const void* W, void* C, int M, int N
     tp.rows_per_rank = rows_per_rank;
     tp.gated = gated;
     if (epilogue == EPI_RS && (rows_per_rank % 32 || rows_per_rank <= 0)) return (int)cudaErrorInvalidValue;
-    const int bn = force_bn > 0 ? force_bn : pick_bn(M, N, num_sms);
+    GemmWorkspace w;
+    if (int rc = current_workspace(&w)) return rc;
+    const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w);
+    const int bn = plan.bn;
     CUtensorMap ta, tb;
     if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
     if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, bn) != 0) return (int)cudaErrorInvalidValue;
 #define GO(BN_)                                                                                    \
     switch (epilogue) {                                                                            \
-        case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, num_sms, st, tp);   \
-        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, num_sms, st, tp); \
-        case EPI_RS: return launch_gemm<BN_, EPI_RS>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, num_sms, st, tp);         \
+        case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, plan, w, st, tp);   \
+        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, plan, w, st, tp); \
+        case EPI_RS: return launch_gemm<BN_, EPI_RS>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, plan, w, st, tp);         \
         default: return (int)cudaErrorInvalidValue;                                                \
     }
     if (bn == 256) { GO(256) }

@@ -235,7 +235,9 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
     const float x_floor = (MP > 0.f) ? xmax + T * __logf(MP) : -INFINITY;
 
     // ---- pass 4: Gumbel-max over the kept set
-    const unsigned long long seed = seeds[row];
+    // per-row stream keys from the 64-bit seed; per-element noise is one 32-bit mix of the index
+    const unsigned long long seed = splitmix64(seeds[row]);
+    const uint32_t s0 = (uint32_t)seed, s1 = (uint32_t)(seed >> 32);
     unsigned long long pick = 0ull;
     for (int v = threadIdx.x; v < rv.nvec; v += SAMPLE_THREADS) {
         const uint4 pk = rv.vec[v];
@@ -248,7 +250,9 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
             const float x = __bfloat162float(__ushort_as_bfloat16(e[k]));
             if (x < x_floor) continue;
             if (!rv.allowed(idx)) continue;
-            const float u = uniform01(seed, 0u, (uint32_t)idx);
+            uint32_t hsh = ((uint32_t)idx + s0) * 0x9E3779B1u ^ s1;
+            hsh ^= hsh >> 16; hsh *= 0x85EBCA6Bu; hsh ^= hsh >> 13; hsh *= 0xC2B2AE35u; hsh ^= hsh >> 16;
+            const float u = ((float)(hsh >> 8) + 0.5f) * (1.0f / 16777216.0f);
             const float score = (x - xmax) * inv_t - __logf(-__logf(u));
             const unsigned long long cand =
                 ((unsigned long long)f32_key(score) << 32) | (0xffffffffu - (uint32_t)idx);

@@ -169,6 +169,23 @@ def _to_i32(packed_i64):
 
 
 # --------------------------------------------------------------------------- GEMM
+_GEMM_WS = {}
+
+
+def ensure_gemm_workspace(device) -> None:
+    """Register the stream-K scratch of `device` with the kernel library (once per device):
+    fp32 space for the partial tiles of split output tiles and their arrival counters."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx in _GEMM_WS:
+        return
+    sms = num_sms(idx)
+    ws = torch.empty(3 * sms * 128 * 256, dtype=torch.float32, device=f"cuda:{idx}")
+    cnt = torch.zeros(2 * sms * 4, dtype=torch.int32, device=f"cuda:{idx}")
+    check(fn("pie_gemm_set_workspace")(idx, ptr(ws), ws.numel(), ptr(cnt), cnt.numel()), "gemm_set_workspace")
+    _GEMM_WS[idx] = (ws, cnt)
+
+
 def gemm(x, w, residual=None, epilogue: int = EPI_STORE, out=None, force_bn: int = 0):
     """y = x @ w.T (+ residual | SwiGLU over interleaved gate/up columns). x [M,K], w [N,K]."""
     if not x.is_cuda:
@@ -181,6 +198,7 @@ def gemm(x, w, residual=None, epilogue: int = EPI_STORE, out=None, force_bn: int
         out = torch.empty(m, n_out, dtype=x.dtype, device=x.device)
     if m == 0:
         return out
+    ensure_gemm_workspace(x.device)
     check(fn("pie_gemm_bf16")(ptr(x), ptr(w), ptr(out), ptr(residual), m, n, k, x.stride(0), w.stride(0),
                               out.stride(0), residual.stride(0) if residual is not None else 0, epilogue,
                               force_bn, ptr(kernel_status(x.device)), num_sms(x.device), stream_ptr()),

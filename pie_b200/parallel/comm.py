@@ -170,6 +170,7 @@ class TPComm:
         self._wait_ag = _lib.declare("pie_tp_wait_ag", [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p])
         self._status = status
         self._sms = ops.num_sms(self.device)
+        ops.ensure_gemm_workspace(self.device)
         # control ring
         name = [f"pie_b200_ring_{os.getpid()}_{int(time.time() * 1e3) & 0xFFFFFF}"] if self.rank == 0 else [None]
         if self.rank == 0:

@@ -34,6 +34,27 @@ def test_gemm_plain(m, n, k, bn):
     check(y, x.float() @ w.float().t(), k)
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 6144, 4096), (512, 4096, 14336), (512, 768, 4096), (64, 4096, 4096),
+                                   (300, 2048, 8192), (512, 28672, 4096)])
+@pytest.mark.parametrize("epi", ["store", "residual", "swiglu"])
+def test_gemm_stream_k_matches_whole_tile_and_reference(m, n, k, epi):
+    """Skinny shapes take the stream-K schedule (split tiles fixed up through the workspace);
+    force_bn=-1 forces whole-tile scheduling of the same kernel."""
+    x, w = bf(m, k, seed=11), bf(n, k, scale=0.03, seed=12)
+    r = bf(m, n, seed=13) if epi == "residual" else None
+    e = {"store": ops.EPI_STORE, "residual": ops.EPI_RESIDUAL, "swiglu": ops.EPI_SWIGLU}[epi]
+    for rep in range(2):     # twice: the arrival counters must be back at zero
+        y = ops.gemm(x, w, residual=r, epilogue=e)
+    y_dp = ops.gemm(x, w, residual=r, epilogue=e, force_bn=-1)
+    want = x.float() @ w.float().t()
+    if epi == "residual":
+        want = want + r.float()
+    if epi == "swiglu":
+        want = ref.swiglu_interleaved(want)
+    check(y, want, k)
+    check(y_dp, want, k)
+
+
 def test_gemm_residual():
     m, n, k = 333, 4096, 1024
     x, w, r = bf(m, k, seed=3), bf(n, k, scale=0.05, seed=4), bf(m, n, seed=5)
