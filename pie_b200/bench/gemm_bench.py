@@ -1,0 +1,60 @@
+"""GEMM micro-benchmark: the tcgen05 kernels (CTA pairs, single CTA) against cuBLAS (torch.matmul)
+on the model's shapes. CUDA events, warm-up, L2 flushed between timed launches.
+
+    python -m pie_b200.bench.gemm_bench [--shapes decode|prefill|all]
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from .. import ops
+
+DECODE = [(512, 6144, 4096), (512, 4096, 4096), (512, 28672, 4096), (512, 4096, 14336), (512, 128256, 4096),
+          (512, 768, 4096), (512, 4096, 512), (512, 3584, 4096), (512, 4096, 1792), (64, 6144, 4096)]
+PREFILL = [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (16384, 6144, 4096)]
+
+
+def timeit(fn, flush, iters=10):
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="all")
+    a = ap.parse_args()
+    shapes = {"decode": DECODE, "prefill": PREFILL, "all": DECODE + PREFILL}[a.shapes]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    print(f"{'M':>6} {'N':>7} {'K':>6} | {'cuBLAS us':>10} {'TF':>6} | {'pairs us':>9} {'TF':>6} | {'1-CTA us':>9} {'TF':>6} | max err")
+    for m, n, k in shapes:
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+        fl = 2.0 * m * n * k
+        t_cb = timeit(lambda: torch.matmul(x, w.t()), flush)
+        ops.set_gemm_pairs(True)
+        t_p = timeit(lambda: ops.gemm(x, w), flush)
+        y = ops.gemm(x, w)
+        ops.set_gemm_pairs(False)
+        t_1 = timeit(lambda: ops.gemm(x, w), flush)
+        ops.set_gemm_pairs(True)
+        err = (y.float() - torch.matmul(x, w.t()).float()).abs().max().item()
+        print(f"{m:6d} {n:7d} {k:6d} | {t_cb*1e3:10.1f} {fl/t_cb/1e9:6.0f} | {t_p*1e3:9.1f} {fl/t_p/1e9:6.0f} | "
+              f"{t_1*1e3:9.1f} {fl/t_1/1e9:6.0f} | {err:.3f}")
+        ops.check_kernel_status()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,180 @@
+// Definitions shared by the single-CTA and CTA-pair tcgen05 GEMM kernels: epilogue modes, the
+// tensor-parallel side channel, stream-K work walking and the epilogue store.
+#pragma once
+#include "tcgen05.cuh"
+
+namespace pie {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+enum GemmEpilogue : int {
+    EPI_STORE = 0,     // C = acc
+    EPI_RESIDUAL = 1,  // C = acc + R
+    EPI_SWIGLU = 2,    // C[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]   (C is [M, N/2])
+    EPI_RS = 3,        // reduce-scatter: rows go to their owner rank's receive buffer (peer stores)
+};
+
+constexpr int TP_MAX_RANKS = 8;
+
+// Tensor-parallel side channel of the fused kernels. All pointers are device addresses valid
+// on THIS GPU; peer_* entries are peer-mapped (NVLink) addresses of the same buffer on rank i.
+//   gated loads : before its first TMA load the producer waits until every rank has pushed its
+//                 rows of the activation (ag_flags[src] >= *ag_epoch, written by peers).
+//   EPI_RS      : the epilogue stores each accumulator row into the receive buffer of the rank
+//                 that owns the row (rows_per_rank consecutive rows per rank, a multiple of 32),
+//                 at [this rank][row within owner][col]; the last epilogue warp of the grid
+//                 bumps the local epoch and writes it into every owner's flag word for this rank.
+struct TpArgs {
+    const int* ag_flags;          // [world] local, written by peers
+    const int* ag_epoch;          // local expected value
+    bf16* peer_recv[TP_MAX_RANKS];
+    int* peer_rs_flags[TP_MAX_RANKS];  // word [rank] of rank i's flag array is at peer_rs_flags[i] + rank
+    int* rs_done;                 // local arrival counter of the epilogue warps
+    int* rs_epoch;                // local count of reduce-scatter ops issued
+    int world, rank, rows_per_rank, gated;
+};
+
+// Stream-K side of the kernel. With `enabled`, the (tile, k-block) units of the whole problem are
+// split evenly over the CTAs instead of whole tiles, so skinny problems (few tiles, long K) keep
+// every SM busy. A CTA whose share covers only part of a tile's K range writes its fp32 partial
+// tile to `ws` and bumps the tile's arrival counter; the last warp to arrive for a 32-row quarter
+// adds the other partials and runs the real epilogue. Nobody waits for anybody.
+//   ws  : [(grid + num_tiles)][128][BN] floats, slot = cta + tile
+//   cnt : [num_tiles][4] ints, zero before the launch; the last arriver resets its counter
+struct StreamKArgs {
+    float* ws;
+    int* cnt;
+    int enabled;
+};
+
+struct Segment {
+    int tile, kb0, kb1;
+};
+
+// Walks the work of one CTA; every role of the CTA walks the same sequence.
+struct SegmentWalk {
+    long long u, u_end;
+    int t, t_step, num_tiles, num_kb;
+    bool sk;
+    // worker = CTA (or CTA pair) index, workers = how many share the problem
+    __device__ SegmentWalk(bool streamk, int num_tiles_, int num_kb_, int worker, int workers)
+        : num_tiles(num_tiles_), num_kb(num_kb_), sk(streamk) {
+        if (sk) {
+            const long long total = (long long)num_tiles * num_kb;
+            u = total * worker / workers;
+            u_end = total * (worker + 1) / workers;
+        } else {
+            t = worker;
+            t_step = workers;
+        }
+    }
+    __device__ bool next(Segment& s) {
+        if (sk) {
+            if (u >= u_end) return false;
+            s.tile = (int)(u / num_kb);
+            s.kb0 = (int)(u - (long long)s.tile * num_kb);
+            const long long left = u_end - u;
+            s.kb1 = (int)min((long long)num_kb, s.kb0 + left);
+            u += s.kb1 - s.kb0;
+            return true;
+        }
+        if (t >= num_tiles) return false;
+        s.tile = t;
+        s.kb0 = 0;
+        s.kb1 = num_kb;
+        t += t_step;
+        return true;
+    }
+};
+
+// CTA whose unit range contains unit `unit` (ranges are [c*total/grid, (c+1)*total/grid)).
+__device__ __forceinline__ int streamk_cta_of(long long unit, long long total, int grid) {
+    return (int)(((unit + 1) * grid + total - 1) / total - 1);
+}
+
+
+// Final epilogue of 32 accumulator columns [col0, col0+32) of one output row held by a thread.
+template <int EPI>
+__device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&v)[32], int row, int col0, int M, int N,
+                                                     bf16* __restrict__ C, int ldc, const bf16* __restrict__ R,
+                                                     int ldr, const TpArgs& tp) {
+    if (row >= M || col0 >= N) return;
+    if (EPI == EPI_RS) {
+        const int owner = row / tp.rows_per_rank;
+        const int local = row - owner * tp.rows_per_rank;
+        bf16* dst = tp.peer_recv[owner] + ((size_t)tp.rank * tp.rows_per_rank + local) * (size_t)N + col0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (col0 + 8 * j >= N) break;
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(v[8 * j + e]);
+            *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        bf16* dst = C + (size_t)row * ldc + (col0 >> 1);
+        float o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float g = __uint_as_float(v[2 * j]);
+            const float u = __uint_as_float(v[2 * j + 1]);
+            o[j] = g / (1.f + __expf(-g)) * u;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (col0 + 16 * j < N) *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o + 8 * j);
+    } else {
+        bf16* dst = C + (size_t)row * ldc + col0;
+        const bf16* res = (EPI == EPI_RESIDUAL) ? R + (size_t)row * ldr + col0 : nullptr;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (col0 + 8 * j >= N) break;
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(v[8 * j + e]);
+            if (EPI == EPI_RESIDUAL) {
+                float rr[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(res + 8 * j), rr);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] += rr[e];
+            }
+            *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
+        }
+    }
+}
+
+// Reduce-scatter publication: called by lane 0 of an epilogue warp after its rows of a tile
+// reached their owners. The `total`-th arrival bumps the epoch and raises this rank's flag on
+// every owner.
+__device__ __forceinline__ void rs_publish_arrival(const TpArgs& tp, int total) {
+    if (atomicAdd(tp.rs_done, 1) + 1 == total) {
+        *tp.rs_done = 0;
+        const int e = *reinterpret_cast<volatile int*>(tp.rs_epoch) + 1;
+        *reinterpret_cast<volatile int*>(tp.rs_epoch) = e;
+        __threadfence_system();
+        for (int p = 0; p < tp.world; ++p) *reinterpret_cast<volatile int*>(tp.peer_rs_flags[p] + tp.rank) = e;
+    }
+}
+
+// All-gather gate: spin (bounded) until every rank's push flag reached this rank's epoch.
+__device__ __forceinline__ bool ag_gate_wait(const TpArgs& tp, int* status) {
+    const int e = *reinterpret_cast<const volatile int*>(tp.ag_epoch);
+    const long long t0 = clock64();
+    bool ok = true;
+    for (int src = 0; src < tp.world && ok; ++src) {
+        while (*reinterpret_cast<const volatile int*>(tp.ag_flags + src) < e) {
+            if (*reinterpret_cast<volatile int*>(status) != 0 || clock64() - t0 > 1500000000ll) {
+                atomicCAS(status, 0, PIE_ERR_WAIT_PEER);
+                ok = false;
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+    asm volatile("fence.proxy.async;\n" ::: "memory");
+    return ok;
+}
+
+}  // namespace pie

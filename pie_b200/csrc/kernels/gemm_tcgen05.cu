@@ -14,41 +14,10 @@
 // Replaces the reference's cuBLASLt/cuBLAS dispatch
 // (driver/cuda/src/ops/gemm.cpp:326-415, 607-640) and its separate
 // residual-add / SwiGLU passes (driver/cuda/src/kernels/swiglu.cu:180-260).
-#include "tcgen05.cuh"
+#include "gemm_common.cuh"
 
 namespace pie {
 using namespace sm100;
-
-constexpr int GEMM_BM = 128;
-constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 192;
-
-enum GemmEpilogue : int {
-    EPI_STORE = 0,     // C = acc
-    EPI_RESIDUAL = 1,  // C = acc + R
-    EPI_SWIGLU = 2,    // C[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]   (C is [M, N/2])
-    EPI_RS = 3,        // reduce-scatter: rows go to their owner rank's receive buffer (peer stores)
-};
-
-constexpr int TP_MAX_RANKS = 8;
-
-// Tensor-parallel side channel of the fused kernels. All pointers are device addresses valid
-// on THIS GPU; peer_* entries are peer-mapped (NVLink) addresses of the same buffer on rank i.
-//   gated loads : before its first TMA load the producer waits until every rank has pushed its
-//                 rows of the activation (ag_flags[src] >= *ag_epoch, written by peers).
-//   EPI_RS      : the epilogue stores each accumulator row into the receive buffer of the rank
-//                 that owns the row (rows_per_rank consecutive rows per rank, a multiple of 32),
-//                 at [this rank][row within owner][col]; the last epilogue warp of the grid
-//                 bumps the local epoch and writes it into every owner's flag word for this rank.
-struct TpArgs {
-    const int* ag_flags;          // [world] local, written by peers
-    const int* ag_epoch;          // local expected value
-    bf16* peer_recv[TP_MAX_RANKS];
-    int* peer_rs_flags[TP_MAX_RANKS];  // word [rank] of rank i's flag array is at peer_rs_flags[i] + rank
-    int* rs_done;                 // local arrival counter of the epilogue warps
-    int* rs_epoch;                // local count of reduce-scatter ops issued
-    int world, rank, rows_per_rank, gated;
-};
 
 template <int BN>
 struct GemmCfg {
@@ -59,63 +28,6 @@ struct GemmCfg {
     static constexpr uint32_t TMEM_COLS = 2 * BN;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
-
-// Stream-K side of the kernel. With `enabled`, the (tile, k-block) units of the whole problem are
-// split evenly over the CTAs instead of whole tiles, so skinny problems (few tiles, long K) keep
-// every SM busy. A CTA whose share covers only part of a tile's K range writes its fp32 partial
-// tile to `ws` and bumps the tile's arrival counter; the last warp to arrive for a 32-row quarter
-// adds the other partials and runs the real epilogue. Nobody waits for anybody.
-//   ws  : [(grid + num_tiles)][128][BN] floats, slot = cta + tile
-//   cnt : [num_tiles][4] ints, zero before the launch; the last arriver resets its counter
-struct StreamKArgs {
-    float* ws;
-    int* cnt;
-    int enabled;
-};
-
-struct Segment {
-    int tile, kb0, kb1;
-};
-
-// Walks the work of one CTA; every role of the CTA walks the same sequence.
-struct SegmentWalk {
-    long long u, u_end;
-    int t, t_step, num_tiles, num_kb;
-    bool sk;
-    __device__ SegmentWalk(bool streamk, int num_tiles_, int num_kb_)
-        : num_tiles(num_tiles_), num_kb(num_kb_), sk(streamk) {
-        if (sk) {
-            const long long total = (long long)num_tiles * num_kb;
-            u = total * blockIdx.x / gridDim.x;
-            u_end = total * (blockIdx.x + 1) / gridDim.x;
-        } else {
-            t = blockIdx.x;
-            t_step = gridDim.x;
-        }
-    }
-    __device__ bool next(Segment& s) {
-        if (sk) {
-            if (u >= u_end) return false;
-            s.tile = (int)(u / num_kb);
-            s.kb0 = (int)(u - (long long)s.tile * num_kb);
-            const long long left = u_end - u;
-            s.kb1 = (int)min((long long)num_kb, s.kb0 + left);
-            u += s.kb1 - s.kb0;
-            return true;
-        }
-        if (t >= num_tiles) return false;
-        s.tile = t;
-        s.kb0 = 0;
-        s.kb1 = num_kb;
-        t += t_step;
-        return true;
-    }
-};
-
-// CTA whose unit range contains unit `unit` (ranges are [c*total/grid, (c+1)*total/grid)).
-__device__ __forceinline__ int streamk_cta_of(long long unit, long long total, int grid) {
-    return (int)(((unit + 1) * grid + total - 1) / total - 1);
-}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -186,7 +98,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 __threadfence_system();
                 asm volatile("fence.proxy.async;\n" ::: "memory");
             }
-            SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb);
+            SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
             Segment seg;
             while (ok && walk.next(seg)) {
                 const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
@@ -212,7 +124,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb);
+            SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
             Segment seg;
             for (; ok && walk.next(seg); ++tcount) {
                 const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
@@ -239,7 +151,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         // ----------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lanes [32q, 32q+32) belong to this warp
         uint32_t tcount = 0;
-        SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb);
+        SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
         Segment seg;
         const long long total_units = (long long)num_tiles * num_kb;
         for (; walk.next(seg); ++tcount) {
@@ -438,6 +350,14 @@ PIE_API int pie_gemm_set_workspace(int device, float* ws, long ws_floats, int* c
     return 0;
 }
 
+// 0: single-CTA tiles only; 1: CTA pairs (cta_group::2) where the shape allows (default)
+static int g_gemm_pairs = 1;
+PIE_API int pie_gemm_set_pairs(int enabled) { g_gemm_pairs = enabled; return 0; }
+
+int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int M, int N, int K, int lda,
+                       int ldw, int ldc, int ldr, int epilogue, int* status, int num_sms, cudaStream_t st,
+                       const TpArgs* tp_in, float* ws, long ws_floats, int* cnt, int cnt_ints, int* handled);
+
 struct GemmPlan {
     int bn, grid, streamk;
 };
@@ -511,6 +431,12 @@ PIE_API int pie_gemm_bf16(const void* A, const void* W, void* C, const void* R, 
     if (epilogue == EPI_SWIGLU && N % 32) return (int)cudaErrorInvalidValue;
     GemmWorkspace w;
     if (int rc = current_workspace(&w)) return rc;
+    if (g_gemm_pairs && force_bn == 0) {
+        int handled = 0;
+        const int rc = pie_gemm2_dispatch(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, epilogue, status, num_sms, st,
+                                          nullptr, w.ws, w.ws_floats, w.cnt, w.cnt_ints, &handled);
+        if (handled || rc) return rc;
+    }
     if (force_bn < 0) { w = GemmWorkspace{}; force_bn = -force_bn == 1 ? 0 : -force_bn; }  // negative: whole-tile only
     const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w);
     const int bn = plan.bn;
@@ -563,6 +489,12 @@ PIE_API int pie_gemm_bf16_tp(const void* A, const void* W, void* C, int M, int N
     if (epilogue == EPI_RS && (rows_per_rank % 32 || rows_per_rank <= 0)) return (int)cudaErrorInvalidValue;
     GemmWorkspace w;
     if (int rc = current_workspace(&w)) return rc;
+    if (g_gemm_pairs && force_bn == 0) {
+        int handled = 0;
+        const int rc = pie_gemm2_dispatch(A, W, C, nullptr, M, N, K, lda, ldw, ldc, 0, epilogue, status, num_sms,
+                                          st, &tp, w.ws, w.ws_floats, w.cnt, w.cnt_ints, &handled);
+        if (handled || rc) return rc;
+    }
     const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w);
     const int bn = plan.bn;
     CUtensorMap ta, tb;

@@ -184,6 +184,14 @@ def ensure_gemm_workspace(device) -> None:
     cnt = torch.zeros(2 * sms * 4, dtype=torch.int32, device=f"cuda:{idx}")
     check(fn("pie_gemm_set_workspace")(idx, ptr(ws), ws.numel(), ptr(cnt), cnt.numel()), "gemm_set_workspace")
     _GEMM_WS[idx] = (ws, cnt)
+    import os
+    if os.environ.get("PIE_GEMM_PAIRS", "1") == "0":
+        set_gemm_pairs(False)
+
+
+def set_gemm_pairs(enabled: bool) -> None:
+    """Use CTA-pair (cta_group::2, 256-row) tiles where the shape allows, or single-CTA tiles only."""
+    check(fn("pie_gemm_set_pairs")(1 if enabled else 0), "gemm_set_pairs")
 
 
 def gemm(x, w, residual=None, epilogue: int = EPI_STORE, out=None, force_bn: int = 0):
