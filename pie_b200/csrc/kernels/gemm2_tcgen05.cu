@@ -25,7 +25,7 @@ struct Gemm2Cfg {
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = BN == 256 ? 6 : 8;
     static constexpr uint32_t TMEM_COLS = 2 * BN;
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/ + 16384 /*epilogue staging*/;
 };
 
 template <int BN, int EPI>
@@ -52,6 +52,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t crank = cluster_ctarank();
     const bool leader = crank == 0;
+    const bool relay = (sk.dbg & 4) != 0;
     const int pid = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int tiles_m = (M + PAIR_M - 1) / PAIR_M;
     const int tiles_n = (N + BN - 1) / BN;
@@ -89,6 +90,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             uint32_t it = 0;
             bool ok = true;
             if (tp.gated) ok = ag_gate_wait(tp, status);
+            const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
             SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, pid, npairs);
             Segment seg;
             while (ok && walk.next(seg)) {
@@ -97,19 +99,34 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait_cluster(empty_bar(s), ph ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
                     const uint32_t a_dst = tiles + s * Cfg::STAGE_BYTES;
-                    tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * PAIR_M + (int)crank * GEMM_BM);
-                    tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK,
-                                n_blk * BN + (int)crank * (BN / 2));
+                    const int a_row = m_blk * PAIR_M + (int)crank * GEMM_BM;
+                    const int b_row = n_blk * BN + (int)crank * (BN / 2);
+                    if (relay) {
+                        if (sk.dbg & 2) { mbar_arrive(full_bar(s)); continue; }
+                        mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+                        tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, a_row);
+                        tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
+                    } else {
+                        // both CTAs' loads complete on the leader's barrier, armed for the pair's bytes
+                        if (sk.dbg & 2) { if (leader) mbar_arrive(full_bar(s)); continue; }
+                        if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
+                        const uint32_t lbar = leader_full0 + 8u * s;
+                        tma_load_2d_pair(a_dst, &tma_a, lbar, kb * GEMM_BK, a_row);
+                        tma_load_2d_pair(a_dst + Cfg::A_BYTES, &tma_b, lbar, kb * GEMM_BK, b_row);
+                    }
                 }
             }
-            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
-            for (uint32_t j = first; j < it; ++j)
-                mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1u, status, PIE_ERR_WAIT_TMA, 200000000ll);
+            // no copy into this CTA may be in flight when it exits: with direct signalling the
+            // leader's barriers cover the pair and both CTAs meet at the cluster barrier below
+            if (relay || leader) {
+                const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
+                for (uint32_t j = first; j < it; ++j)
+                    mbar_wait_cluster(full_bar(j % STAGES), (j / STAGES) & 1u, status, PIE_ERR_WAIT_TMA, 200000000ll);
+            }
         }
     } else if (warp == 1) {
-        if (lane == 0 && !leader) {
+        if (lane == 0 && !leader && relay) {
             // ---------------------------------------------------- follower: relay "stage landed"
             uint32_t it = 0;
             bool ok = true;
@@ -122,7 +139,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                     mbar_arrive_cluster(map_to_cta(peer_bar(s), 0));
                 }
             }
-        } else if (lane == 0) {
+        } else if (lane == 0 && leader) {
             // ---------------------------------------------------- leader: MMA issuer of the pair
             constexpr uint32_t idesc = make_idesc_bf16(PAIR_M, BN);
             uint32_t it = 0, tcount = 0;
@@ -137,15 +154,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    if (!mbar_wait(full_bar(s), ph, status, PIE_ERR_WAIT_TMA) ||
-                        !mbar_wait_cluster(peer_bar(s), ph, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                    if (!mbar_wait_cluster(full_bar(s), ph, status, PIE_ERR_WAIT_TMA) ||
+                        (relay && !mbar_wait_cluster(peer_bar(s), ph, status, PIE_ERR_WAIT_TMA))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = tiles + s * Cfg::STAGE_BYTES;
                     const uint64_t adesc = make_smem_desc_sw128(a_addr);
                     const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
+                    if (!(sk.dbg & 1)) {
 #pragma unroll
-                    for (int k = 0; k < GEMM_BK / 16; ++k)
-                        umma_bf16_2cta(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
+                        for (int k = 0; k < GEMM_BK / 16; ++k)
+                            umma_bf16_2cta(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
+                    }
                     umma_commit_2cta(empty_bar(s), 3);   // slot s is free in both CTAs
                 }
                 if (ok) umma_commit_2cta(tfull_bar(acc), 3);
@@ -173,7 +192,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             bool finalise = true;
             int c_first = 0, c_last = -1;
             if (partial) {
-                float* mine = sk.ws + ((size_t)(pid + seg.tile) * PAIR_M + row_in_pair) * BN;
+                // workspace layout per (slot, warp): [chunk of 32 columns][float4 j][lane], so that every
+                // store/load instruction of a warp moves 512 contiguous bytes
+                uint4* mine = reinterpret_cast<uint4*>(sk.ws) + (size_t)(pid + seg.tile) * (PAIR_M * BN / 4) +
+                              (size_t)((int)crank * 4 + q) * (32 * BN / 4) + lane;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t v[32];
@@ -181,8 +203,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        reinterpret_cast<uint4*>(mine + c * 32)[j] =
-                            make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        mine[(c * 8 + j) * 32] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
                 __threadfence();
                 __syncwarp();
@@ -199,27 +220,35 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                 if (finalise) __threadfence();
             }
             if (finalise) {
+                uint8_t* stage = tiles_ptr + STAGES * Cfg::STAGE_BYTES + 512 + (warp - 2) * 4096;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(t_row + c * 32, v);
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld_32x32(t_row + c * 64, v0);
+                    tmem_ld_32x32(t_row + c * 64 + 32, v1);
                     tmem_ld_wait();
                     if (partial) {
                         for (int cc = c_first; cc <= c_last; ++cc) {
                             if (cc == pid) continue;
-                            const float* other =
-                                sk.ws + ((size_t)(cc + seg.tile) * PAIR_M + row_in_pair) * BN + c * 32;
+                            const float4* other = reinterpret_cast<const float4*>(sk.ws) +
+                                                  (size_t)(cc + seg.tile) * (PAIR_M * BN / 4) +
+                                                  (size_t)((int)crank * 4 + q) * (32 * BN / 4) + (size_t)c * 16 * 32 + lane;
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                const float4 o4 = __ldcg(reinterpret_cast<const float4*>(other) + j);
-                                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + o4.x);
-                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + o4.y);
-                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + o4.z);
-                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + o4.w);
+                                const float4 a4 = __ldcg(other + j * 32), b4 = __ldcg(other + (8 + j) * 32);
+                                v0[4 * j] = __float_as_uint(__uint_as_float(v0[4 * j]) + a4.x);
+                                v0[4 * j + 1] = __float_as_uint(__uint_as_float(v0[4 * j + 1]) + a4.y);
+                                v0[4 * j + 2] = __float_as_uint(__uint_as_float(v0[4 * j + 2]) + a4.z);
+                                v0[4 * j + 3] = __float_as_uint(__uint_as_float(v0[4 * j + 3]) + a4.w);
+                                v1[4 * j] = __float_as_uint(__uint_as_float(v1[4 * j]) + b4.x);
+                                v1[4 * j + 1] = __float_as_uint(__uint_as_float(v1[4 * j + 1]) + b4.y);
+                                v1[4 * j + 2] = __float_as_uint(__uint_as_float(v1[4 * j + 2]) + b4.z);
+                                v1[4 * j + 3] = __float_as_uint(__uint_as_float(v1[4 * j + 3]) + b4.w);
                             }
                         }
                     }
-                    epilogue_store_chunk<EPI>(v, row, n_blk * BN + c * 32, M, N, C, ldc, R, ldr, tp);
+                    epilogue_store_64<EPI>(v0, v1, stage, m_blk * PAIR_M + (int)crank * GEMM_BM + q * 32,
+                                           n_blk * BN + c * 64, M, N, C, ldc, R, ldr, tp);
                 }
             }
             tc_fence_before();
@@ -251,6 +280,9 @@ using namespace pie;
 
 extern "C" int pie_make_tma_2d_bf16(CUtensorMap* map, const void* ptr, long rows, long cols, long ld, int box_rows);
 
+static int g_pair_dbg = 0;
+extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_debug(int bits) { g_pair_dbg = bits; return 0; }
+
 template <int BN, int EPI>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M, int N,
                         int K, int ldc, int ldr, int* status, int pairs, int streamk, float* ws, int* cnt,
@@ -259,7 +291,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, c
     auto kern = gemm2_bf16_kernel<BN, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    StreamKArgs sk{ws, cnt, streamk};
+    StreamKArgs sk{ws, cnt, streamk, g_pair_dbg};
     kern<<<2 * pairs, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
                                                            status, tp, sk);
     return (int)cudaGetLastError();
@@ -271,7 +303,8 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
                        int ldw, int ldc, int ldr, int epilogue, int* status, int num_sms, cudaStream_t st,
                        const TpArgs* tp_in, float* ws, long ws_floats, int* cnt, int cnt_ints, int* handled) {
     *handled = 0;
-    if (M <= GEMM_BM || N < 128 || num_sms < 2) return 0;
+    // small problems are launch/fix-up bound: the single-CTA kernel's narrower tiles fill the machine better
+    if (M <= GEMM_BM || N < 128 || num_sms < 2 || (double)M * N * K < 1.0e10) return 0;
     const int bn = N >= 256 ? 256 : 128;
     const int pairs_max = num_sms / 2;
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
@@ -281,7 +314,7 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
     {
         const long waves = (tiles + pairs_max - 1) / pairs_max;
         const long units = tiles * num_kb;
-        const long gp = units / 4 < pairs_max ? units / 4 : pairs_max;
+        const long gp = units / 16 < pairs_max ? units / 16 : pairs_max;   // >= 16 k-blocks per pair
         if (ws && gp >= 1 && tiles % gp != 0 && tiles <= 2L * pairs_max &&
             (gp + tiles) * 2L * GEMM_BM * bn <= ws_floats && tiles * 8 <= cnt_ints) {
             const double dp = (double)waves, skc = (double)tiles / gp + 0.12;

@@ -47,6 +47,7 @@ struct StreamKArgs {
     float* ws;
     int* cnt;
     int enabled;
+    int dbg;   // pair kernel diagnostics: 1 skip the MMAs, 2 skip the loads, 4 relay instead of direct signalling
 };
 
 struct Segment {
@@ -143,6 +144,88 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&v)[32], in
             *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
         }
     }
+}
+
+// Epilogue of 64 accumulator columns [col0, col0+64) for the 32 rows of one warp, with coalesced
+// global accesses. Thread `lane` holds row (row0 + lane): v0 = columns col0..+31, v1 = +32..+63.
+// The values go through a per-warp staging tile in shared memory (32 rows x 128 B, 16-byte
+// chunks XOR-swizzled by row) so that one store instruction of the warp covers 4 rows x 128 B
+// (8 rows x 64 B for SwiGLU) instead of 32 rows x 16 B.
+//   stage : this warp's 4 KB staging tile (shared memory)
+template <int EPI>
+__device__ __forceinline__ void epilogue_store_64(const uint32_t (&v0)[32], const uint32_t (&v1)[32],
+                                                  uint8_t* stage, int row0, int col0, int M, int N,
+                                                  bf16* __restrict__ C, int ldc, const bf16* __restrict__ R,
+                                                  int ldr, const TpArgs& tp) {
+    const int lane = threadIdx.x & 31;
+    auto slot = [&](int r, int c) { return reinterpret_cast<bf16x8*>(stage + r * 128 + ((c ^ (r & 7)) << 4)); };
+    if (EPI == EPI_SWIGLU) {
+        // 64 accumulator columns -> 32 outputs (64 B) per row
+        float o[32];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float g0 = __uint_as_float(v0[2 * j]), u0 = __uint_as_float(v0[2 * j + 1]);
+            const float g1 = __uint_as_float(v1[2 * j]), u1 = __uint_as_float(v1[2 * j + 1]);
+            o[j] = g0 / (1.f + __expf(-g0)) * u0;
+            o[16 + j] = g1 / (1.f + __expf(-g1)) * u1;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *slot(lane, c) = pack8(o + 8 * c);
+        __syncwarp();
+        const int oc0 = col0 >> 1;   // first output column
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = i * 8 + (lane >> 2), c = lane & 3;
+            const int row = row0 + r, oc = oc0 + c * 8;
+            if (row < M && 2 * oc < N) *reinterpret_cast<bf16x8*>(C + (size_t)row * ldc + oc) = *slot(r, c);
+        }
+        __syncwarp();
+        return;
+    }
+    if (EPI == EPI_RESIDUAL) {
+        // bring the residual tile in with coalesced loads, add in fp32 on the owning thread
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), c = lane & 7;
+            const int row = row0 + r, col = col0 + c * 8;
+            bf16x8 t;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) t.v[e] = __floats2bfloat162_rn(0.f, 0.f);
+            if (row < M && col < N) t = *reinterpret_cast<const bf16x8*>(R + (size_t)row * ldr + col);
+            *slot(r, c) = t;
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(c < 4 ? v0[8 * c + e] : v1[8 * (c - 4) + e]);
+        if (EPI == EPI_RESIDUAL) {
+            float rr[8];
+            unpack8(*slot(lane, c), rr);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] += rr[e];
+        }
+        *slot(lane, c) = pack8(o);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = i * 4 + (lane >> 3), c = lane & 7;
+        const int row = row0 + r, col = col0 + c * 8;
+        if (row >= M || col >= N) continue;
+        bf16* dst;
+        if (EPI == EPI_RS) {
+            const int owner = row / tp.rows_per_rank;
+            const int local = row - owner * tp.rows_per_rank;
+            dst = tp.peer_recv[owner] + ((size_t)tp.rank * tp.rows_per_rank + local) * (size_t)N + col;
+        } else {
+            dst = C + (size_t)row * ldc + col;
+        }
+        *reinterpret_cast<bf16x8*>(dst) = *slot(r, c);
+    }
+    __syncwarp();
 }
 
 // Reduce-scatter publication: called by lane 0 of an epilogue warp after its rows of a tile

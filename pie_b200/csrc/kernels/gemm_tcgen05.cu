@@ -26,7 +26,7 @@ struct GemmCfg {
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr uint32_t TMEM_COLS = 2 * BN;
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 16384 /*epilogue staging*/;
 };
 
 template <int BN, int EPI>
@@ -167,7 +167,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             int c_first = 0, c_last = -1;
             if (partial) {
                 // park this warp's 32 rows of the partial tile, then count the arrival
-                float* mine = sk.ws + ((size_t)(blockIdx.x + seg.tile) * GEMM_BM + q * 32 + lane) * BN;
+                // workspace layout per (slot, warp): [chunk of 32 columns][float4 j][lane], so that every
+                // store/load instruction of a warp moves 512 contiguous bytes
+                uint4* mine = reinterpret_cast<uint4*>(sk.ws) + (size_t)(blockIdx.x + seg.tile) * (GEMM_BM * BN / 4) +
+                              (size_t)q * (32 * BN / 4) + lane;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t v[32];
@@ -175,8 +178,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        reinterpret_cast<uint4*>(mine + c * 32)[j] =
-                            make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        mine[(c * 8 + j) * 32] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
                 __threadfence();
                 __syncwarp();
@@ -193,76 +195,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (finalise) __threadfence();
             }
             if (finalise) {
+                uint8_t* stage = tiles_ptr + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + c * 32, v);
-                tmem_ld_wait();
-                if (partial) {
-                    for (int cc = c_first; cc <= c_last; ++cc) {
-                        if (cc == (int)blockIdx.x) continue;
-                        const float* other =
-                            sk.ws + ((size_t)(cc + seg.tile) * GEMM_BM + q * 32 + lane) * BN + c * 32;
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld_32x32(t_row + c * 64, v0);
+                    tmem_ld_32x32(t_row + c * 64 + 32, v1);
+                    tmem_ld_wait();
+                    if (partial) {
+                        for (int cc = c_first; cc <= c_last; ++cc) {
+                            if (cc == (int)blockIdx.x) continue;
+                            const float4* other = reinterpret_cast<const float4*>(sk.ws) +
+                                                  (size_t)(cc + seg.tile) * (GEMM_BM * BN / 4) +
+                                                  (size_t)q * (32 * BN / 4) + (size_t)c * 16 * 32 + lane;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 o4 = __ldcg(reinterpret_cast<const float4*>(other) + j);
-                            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + o4.x);
-                            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + o4.y);
-                            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + o4.z);
-                            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + o4.w);
-                        }
-                    }
-                }
-                const int col0 = n_blk * BN + c * 32;
-                if (EPI == EPI_RS) {
-                    if (row < M && col0 < N) {
-                        const int owner = row / tp.rows_per_rank;
-                        const int local = row - owner * tp.rows_per_rank;
-                        bf16* dst = tp.peer_recv[owner] +
-                                    ((size_t)tp.rank * tp.rows_per_rank + local) * (size_t)N + col0;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (col0 + 8 * j >= N) break;
-                            float o[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(v[8 * j + e]);
-                            *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
-                        }
-                    }
-                } else if (row < M && col0 < N) {
-                    if (EPI == EPI_SWIGLU) {
-                        bf16* dst = C + (size_t)row * ldc + (col0 >> 1);
-                        float o[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float g = __uint_as_float(v[2 * j]);
-                            const float u = __uint_as_float(v[2 * j + 1]);
-                            o[j] = g / (1.f + __expf(-g)) * u;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            if (col0 + 16 * j < N)
-                                *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o + 8 * j);
-                    } else {
-                        bf16* dst = C + (size_t)row * ldc + col0;
-                        const bf16* res = (EPI == EPI_RESIDUAL) ? R + (size_t)row * ldr + col0 : nullptr;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (col0 + 8 * j >= N) break;
-                            float o[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(v[8 * j + e]);
-                            if (EPI == EPI_RESIDUAL) {
-                                float rr[8];
-                                unpack8(*reinterpret_cast<const bf16x8*>(res + 8 * j), rr);
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) o[e] += rr[e];
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 a4 = __ldcg(other + j * 32), b4 = __ldcg(other + (8 + j) * 32);
+                                v0[4 * j] = __float_as_uint(__uint_as_float(v0[4 * j]) + a4.x);
+                                v0[4 * j + 1] = __float_as_uint(__uint_as_float(v0[4 * j + 1]) + a4.y);
+                                v0[4 * j + 2] = __float_as_uint(__uint_as_float(v0[4 * j + 2]) + a4.z);
+                                v0[4 * j + 3] = __float_as_uint(__uint_as_float(v0[4 * j + 3]) + a4.w);
+                                v1[4 * j] = __float_as_uint(__uint_as_float(v1[4 * j]) + b4.x);
+                                v1[4 * j + 1] = __float_as_uint(__uint_as_float(v1[4 * j + 1]) + b4.y);
+                                v1[4 * j + 2] = __float_as_uint(__uint_as_float(v1[4 * j + 2]) + b4.z);
+                                v1[4 * j + 3] = __float_as_uint(__uint_as_float(v1[4 * j + 3]) + b4.w);
                             }
-                            *reinterpret_cast<bf16x8*>(dst + 8 * j) = pack8(o);
                         }
                     }
+                    epilogue_store_64<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n_blk * BN + c * 64, M, N, C,
+                                           ldc, R, ldr, tp);
                 }
-            }
             }
             tc_fence_before();
             __syncwarp();
@@ -385,7 +347,7 @@ static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const 
         }
         // stream-K candidate
         const long units = tiles * num_kb;
-        long grid = units / 4 < num_sms ? units / 4 : num_sms;   // at least 4 k-blocks per CTA
+        long grid = units / 16 < num_sms ? units / 16 : num_sms;   // at least 16 k-blocks per CTA
         if (grid < 1 || !w.ws || tiles > 2L * num_sms || tiles % grid == 0) continue;
         if ((grid + tiles) * (long)GEMM_BM * bn > w.ws_floats || tiles * 4 > w.cnt_ints) continue;
         const double sk = (double)tiles * bn * per_col[i] / grid + 0.12 * bn;
@@ -406,7 +368,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, co
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    StreamKArgs sk{w.ws, w.cnt, plan.streamk};
+    StreamKArgs sk{w.ws, w.cnt, plan.streamk, 0};
     kern<<<plan.grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
                                                            ldr, status, tp, sk);
     return (int)cudaGetLastError();
