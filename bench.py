@@ -170,7 +170,8 @@ def main():
                        "workload_tokens_per_s": e2e["workload_tokens_per_s"],
                        "p50_ttft_s": e2e["p50_ttft_s"], "p50_itl_s": e2e["p50_itl_s"],
                        "wall_s": e2e["wall_s"], "fires": e2e["fires"],
-                       "requests_per_fire": e2e.get("window_requests_per_fire")}
+                       "requests_per_fire": e2e.get("window_requests_per_fire"),
+                       "steps_used": e2e.get("window_steps_used")}
     print(json.dumps(line))
     if world > 1:
         _hard_exit(0)

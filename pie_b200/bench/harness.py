@@ -266,15 +266,25 @@ def run_engine_workload(engine, model_name: str, prompts, out_tokens: int, sampl
            "p50_ttft_s": statistics.median(ttft) if ttft else None,
            "p50_itl_s": statistics.median(itl) if itl else None,
            "fires": len(fires), "decode_fires": len(dec)}
-    # skip the fires that overlap prefill, then take `window_steps` consecutive decode fires
+    # steady-state decode window: consecutive pure-decode fires that carry (nearly) all requests,
+    # after skipping `window_skip` of them; shorter than asked when the workload leaves fewer
     full = [i for i, f in enumerate(fires) if f[1] == f[2] and f[1] >= 0.9 * len(prompts)]
-    if len(full) > window_skip + window_steps:
-        a = full[window_skip]
-        b = a + window_steps
-        span = fires[a:b + 1]
-        if all(f[1] == f[2] for f in span):
+    runs, cur = [], []
+    for i in full:
+        if cur and i != cur[-1] + 1:
+            runs.append(cur)
+            cur = []
+        cur.append(i)
+    if cur:
+        runs.append(cur)
+    if runs:
+        best = max(runs, key=len)
+        skip = min(window_skip, max(0, len(best) - 2))
+        span = [fires[i] for i in best[skip:skip + window_steps + 1]]
+        if len(span) >= 2:
             toks = sum(f[2] for f in span[1:])
+            out["window_steps_used"] = len(span) - 1
             out["window_tokens_per_s"] = toks / (span[-1][0] - span[0][0])
-            out["window_ms_per_step"] = (span[-1][0] - span[0][0]) / window_steps * 1e3
+            out["window_ms_per_step"] = (span[-1][0] - span[0][0]) / (len(span) - 1) * 1e3
             out["window_requests_per_fire"] = statistics.mean(f[1] for f in span[1:])
     return out

@@ -1,0 +1,103 @@
+// Python bindings of the native host runtime pieces: BRLE, page pool / content-addressed page
+// store, BPE merge engine. Built in-tree by pie_b200._build into pie_b200/_C/pie_host*.so.
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "bpe.hpp"
+#include "brle.hpp"
+#include "pagestore.hpp"
+
+namespace py = pybind11;
+using namespace pie_host;
+
+PYBIND11_MODULE(pie_host, m) {
+    m.doc() = "native host runtime of pie_b200";
+
+    // ------------------------------------------------------------------ BRLE
+    m.def("brle_encode", [](py::array_t<bool, py::array::c_style | py::array::forcecast> bits) {
+        return brle_encode(reinterpret_cast<const uint8_t*>(bits.data()), (size_t)bits.size());
+    });
+    m.def("brle_decode", [](const Brle& runs, long size, bool tail) {
+        const size_t n = size < 0 ? (size_t)brle_length(runs) : (size_t)size;
+        py::array_t<bool> out(n);
+        brle_decode(runs, reinterpret_cast<uint8_t*>(out.mutable_data()), n, tail);
+        return out;
+    }, py::arg("runs"), py::arg("size") = -1, py::arg("tail") = false);
+    m.def("brle_and", &brle_and);
+    m.def("brle_length", &brle_length);
+    m.def("brle_count_true", &brle_count_true);
+    m.def("brle_to_bitmask", [](const std::vector<Brle>& rows, size_t nbits, bool tail) {
+        const size_t nw = (nbits + 31) / 32;
+        py::array_t<uint32_t> out({rows.size(), nw});
+        for (size_t r = 0; r < rows.size(); ++r) brle_to_bitmask(rows[r], out.mutable_data(r, 0), nbits, tail);
+        return out;
+    }, py::arg("rows"), py::arg("nbits"), py::arg("tail") = false);
+    m.def("brle_droppable_pages", [](const std::vector<Brle>& rows, int page_size, int num_pages) {
+        auto v = brle_droppable_pages(rows, page_size, num_pages);
+        py::array_t<bool> out(v.size());
+        std::copy(v.begin(), v.end(), reinterpret_cast<uint8_t*>(out.mutable_data()));
+        return out;
+    });
+
+    // ------------------------------------------------------------------ pages
+    m.def("page_hash", [](uint64_t prev, const std::vector<uint32_t>& tokens, const std::vector<uint32_t>& positions,
+                          const std::string& mask_key, uint64_t adapter_seed) {
+        return page_hash(prev, tokens.data(), positions.data(), tokens.size(),
+                         reinterpret_cast<const uint8_t*>(mask_key.data()), mask_key.size(), adapter_seed);
+    }, py::arg("prev"), py::arg("tokens"), py::arg("positions"), py::arg("mask_key") = std::string(),
+       py::arg("adapter_seed") = 0);
+
+    py::class_<PagePool>(m, "PagePool")
+        .def(py::init<int>())
+        .def_property_readonly("num_pages", &PagePool::num_pages)
+        .def_property_readonly("free_count", &PagePool::free_count)
+        .def_property_readonly("used_count", &PagePool::used_count)
+        .def_property_readonly("double_free_count", &PagePool::double_free_count)
+        .def("alloc", [](PagePool& p, int n) -> py::object {
+            std::vector<int> out;
+            if (!p.alloc(n, out)) return py::none();
+            return py::cast(out);
+        })
+        .def("free", [](PagePool& p, const std::vector<int>& pages) { p.free(pages); });
+
+    py::class_<PageStore>(m, "PageStore")
+        .def(py::init<int>())
+        .def_readonly("pool", &PageStore::pool)
+        .def("lookup", [](const PageStore& s, uint64_t h) -> py::object {
+            const int p = s.lookup(h);
+            return p < 0 ? py::object(py::none()) : py::object(py::int_(p));
+        })
+        .def("extend", &PageStore::extend)
+        .def("acquire", &PageStore::acquire)
+        .def("release", &PageStore::release)
+        .def("would_free", &PageStore::would_free)
+        .def("prefix_len", &PageStore::prefix_len)
+        .def("physical_ids", &PageStore::physical_ids)
+        .def("effective_pages", &PageStore::effective_pages)
+        .def("node_pages", &PageStore::node_pages)
+        .def_property_readonly("node_count", &PageStore::node_count);
+
+    // ------------------------------------------------------------------ BPE
+    py::class_<BpeCore>(m, "BpeCore")
+        .def(py::init([](const std::vector<py::bytes>& vocab, const std::vector<int>& ids,
+                         const std::vector<std::pair<py::bytes, py::bytes>>& merges, int unk_id, bool byte_fallback) {
+            std::vector<std::string> v;
+            v.reserve(vocab.size());
+            for (auto& b : vocab) v.push_back(std::string(b));
+            std::vector<std::pair<std::string, std::string>> mg;
+            mg.reserve(merges.size());
+            for (auto& p : merges) mg.emplace_back(std::string(p.first), std::string(p.second));
+            return new BpeCore(v, ids, mg, unk_id, byte_fallback);
+        }), py::arg("vocab"), py::arg("ids"), py::arg("merges"), py::arg("unk_id") = 0, py::arg("byte_fallback") = false)
+        .def("encode_piece", [](BpeCore& c, const py::bytes& piece) { return c.encode_piece(std::string(piece)); })
+        .def("encode_pieces", [](BpeCore& c, const std::vector<py::bytes>& pieces) {
+            std::vector<std::string> ps;
+            ps.reserve(pieces.size());
+            for (auto& p : pieces) ps.push_back(std::string(p));
+            return c.encode_pieces(ps);
+        })
+        .def("decode", [](const BpeCore& c, const std::vector<int>& ids) { return py::bytes(c.decode(ids)); })
+        .def("token_bytes", [](const BpeCore& c, int id) { return py::bytes(c.token_bytes(id)); })
+        .def_property_readonly("vocab_size", &BpeCore::vocab_size);
+}

@@ -126,3 +126,23 @@ def droppable_pages(rows: Sequence[Sequence[int]], page_size: int, num_pages: in
         d = decode(r, num_pages * page_size)
         vis |= d
     return ~vis.reshape(num_pages, page_size).any(axis=1)
+
+
+try:  # native implementations (csrc/host/brle.hpp) replace the hot entry points when built
+    from .._C import pie_host as _native
+
+    def encode(bits) -> List[int]:  # noqa: F811
+        return _native.brle_encode(np.ascontiguousarray(bits, dtype=bool))
+
+    def decode(runs, size: int = -1, tail: bool = False) -> np.ndarray:  # noqa: F811
+        return _native.brle_decode(list(runs), size, tail)
+
+    def logical_and(a, b) -> List[int]:  # noqa: F811
+        return _native.brle_and(list(a), list(b))
+
+    def droppable_pages(rows, page_size: int, num_pages: int) -> np.ndarray:  # noqa: F811
+        return _native.brle_droppable_pages([list(r) for r in rows], page_size, num_pages)
+
+    NATIVE = True
+except ImportError:  # pragma: no cover
+    NATIVE = False

@@ -90,7 +90,7 @@ class ContextManager:
         self._swap_free = list(range(swap_pages - 1, -1, -1))
         self.counters = {"created": 0, "forked": 0, "commits": 0, "dedup_pages": 0, "suspended": 0,
                          "restored": 0, "evictions": 0, "replayed_tokens": 0}
-        self.evict_hook: Optional[Callable[[int, int], bool]] = None   # (driver, pages needed) -> made room
+        self.market = None   # optional Market: orders eviction victims (defaulted, lowest bid, newest)
 
     # ------------------------------------------------------------------ helpers
     def _get(self, cid: int) -> Context:
@@ -422,7 +422,10 @@ class ContextManager:
                      and (c.working_pages or c.chain)]
         if not cands:
             return False
-        victim = min(cands, key=lambda c: (c.bid, -c.created_seq))
+        if self.market is not None:
+            victim = min(cands, key=lambda c: self.market.victim_key(c.owner, c.bid, c.created_seq))
+        else:
+            victim = min(cands, key=lambda c: (c.bid, -c.created_seq))
         before = self.stores[driver].pool.free_count
         self.suspend(victim.id)
         self.counters["evictions"] += 1
@@ -442,7 +445,7 @@ class ContextManager:
         with self.lock:
             for d, store in enumerate(self.stores):
                 owned = [p for c in self.contexts.values() if c.driver == d for p in c.working_pages]
-                nodes = [n.page for n in store.nodes.values()]
+                nodes = list(store.node_pages())
                 if len(set(owned)) != len(owned):
                     raise ContextError("a working page is owned twice")
                 if set(owned) & set(nodes):

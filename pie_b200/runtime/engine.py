@@ -27,6 +27,7 @@ from ..driver.schema import Capabilities, CopyRequest
 from .cohort import DecodeCohort
 from .context import ContextManager
 from .inference import InferenceService
+from .market import Market
 from .messaging import Messaging
 from .pagestore import PageStore
 from .process import Process, current_process
@@ -44,6 +45,8 @@ class EngineConfig:
     default_token_budget: Optional[int] = None
     watchdog_interval_s: float = 1.0
     swap_pages: int = 0
+    default_endowment_pages: int = 64
+    admission_oversubscription_factor: float = 4.0
 
 
 class ModelEntry:
@@ -113,8 +116,24 @@ class Engine:
         for s in entry.schedulers:
             s.cohort.on_finish = lambda st, e=entry: self._charge(e, st.ctx_id, getattr(st, "kept", 0))
         entry.inference.on_tokens = lambda cid, n, e=entry: self._charge(e, cid, n)
+        entry.market = Market(sum(c.total_pages for c in entry.caps), self.config.default_endowment_pages,
+                              self.config.admission_oversubscription_factor)
+        entry.ctxm.market = entry.market
+        for i, s in enumerate(entry.schedulers):
+            s.post_fire_hooks.append(lambda ctx_ids, e=entry, d=i: self._market_tick(e, d, ctx_ids))
         self.models[name] = entry
         return entry
+
+    def _market_tick(self, entry: ModelEntry, driver: int, ctx_ids) -> None:
+        batch = []
+        for cid in ctx_ids:
+            ctx = entry.ctxm.contexts.get(int(cid))
+            if ctx is not None:
+                try:
+                    batch.append((ctx.id, ctx.owner, ctx.bid, entry.ctxm.effective_pages(ctx.id)))
+                except Exception:  # noqa: BLE001
+                    pass
+        entry.market.tick(entry.ctxm.pages_used(driver), batch)
 
     def _charge(self, entry: ModelEntry, cid: int, n: int) -> None:
         ctx = entry.ctxm.contexts.get(cid)
@@ -122,6 +141,7 @@ class Engine:
             p = self.processes.get(ctx.owner)
             if p is not None:
                 p.charge_tokens(n)
+                entry.market.debit_tokens(ctx.owner, n)
 
     def model(self, name: Optional[str] = None) -> ModelEntry:
         if name is None:
@@ -155,8 +175,20 @@ class Engine:
         self.call_soon(start)
         return proc
 
+    async def admit_process(self, proc: Process) -> None:
+        """KV admission: wait until the process's page claim fits every model's market."""
+        for entry in self.models.values():
+            loop = asyncio.get_running_loop()
+            fut = loop.create_future()
+            ok = entry.market.try_admit(proc.id, None, proc.token_budget,
+                                        on_admit=lambda f=fut: loop.call_soon_threadsafe(
+                                            lambda: f.done() or f.set_result(True)))
+            if not ok:
+                await fut
+
     def release_process(self, proc: Process) -> None:
         for entry in self.models.values():
+            entry.market.release(proc.id)
             for cid in list(entry.ctxm.by_owner.get(proc.id, ())):
                 entry.inference.drop_context(cid)
             entry.ctxm.destroy_owner(proc.id)
@@ -211,6 +243,8 @@ class Engine:
             m["avg_batch_latency_us"] = m["cum_latency_us"] / max(1, m["total_batches"])
             m["batch_size_hist"] = [sum(s.stats["batch_size_hist"][i] for s in e.schedulers) for i in range(8)]
             m.update(e.inference.stats)
+            m.update({"market_price": e.market.clearing_price, "market_ticks": e.market.ticks,
+                      "market_rent": e.market.total_rent, "market_waiting": len(e.market.waiting)})
             m.update({f"ctx_{k}": v for k, v in e.ctxm.counters.items()})
             out["models"][name] = m
         out["processes"] = len([p for p in self.processes.values() if not p.finished])

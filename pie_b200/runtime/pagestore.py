@@ -78,8 +78,8 @@ class _Node:
     children: int = 0
 
 
-class PageStore:
-    """Per-driver store: pool + committed-page index."""
+class PyPageStore:
+    """Per-driver store: pool + committed-page index (portable implementation)."""
 
     def __init__(self, num_pages: int):
         self.pool = PagePool(num_pages)
@@ -149,6 +149,22 @@ class PageStore:
     def physical_ids(self, chain: Sequence[int]) -> List[int]:
         return [self.nodes[h].page for h in chain]
 
+    def node_pages(self) -> List[int]:
+        return [n.page for n in self.nodes.values()]
+
     def effective_pages(self, chain: Sequence[int], working: int) -> float:
         """Cost share of a context: shared pages are split between their holders."""
         return working + sum(1.0 / max(1, self.nodes[h].refcount) for h in chain if h in self.nodes)
+
+
+py_page_hash = page_hash
+try:  # the native store (csrc/host/pagestore.hpp) is the one used when the host module is built
+    from .._C import pie_host as _native
+    PageStore = _native.PageStore
+    NATIVE = True
+
+    def page_hash(prev: int, tokens, positions, mask_key: bytes = b"", adapter_seed: int = 0) -> int:  # noqa: F811
+        return _native.page_hash(prev, list(tokens), list(positions), mask_key, adapter_seed)
+except ImportError:  # pragma: no cover - exercised only without a compiler
+    PageStore = PyPageStore
+    NATIVE = False

@@ -93,6 +93,7 @@ class Process:
         token = current_process.set(self)
         try:
             async with eng.admission:
+                await eng.admit_process(self)
                 result = await self.entry(self.input)
             if result is not None and not isinstance(result, str):
                 result = json.dumps(result)

@@ -319,6 +319,10 @@ class BatchScheduler:
             st["last_latency_us"] = lat * 1e6
             st["cum_latency_us"] += lat * 1e6
             st["batch_size_hist"][min(7, max(1, step.r).bit_length() - 1)] += 1
+            if self.post_fire_hooks and (st["decode_steps"] & 15) == 0:   # market tick every 16 decode steps
+                ids = [s_.ctx_id for s_ in snap]
+                for hook in self.post_fire_hooks:
+                    hook(ids)
             if self.on_batch:
                 self.on_batch(step.r, step.r, lat, "decode")
 
@@ -413,6 +417,8 @@ class BatchScheduler:
             n = len(it.samplers)
             self._deliver(it, resp.slots[k:k + n])
             k += n
+        for hook in self.post_fire_hooks:
+            hook([it.context_id for it in items])
         if self.on_batch:
             self.on_batch(len(items), req.num_tokens, lat, "batch")
 
