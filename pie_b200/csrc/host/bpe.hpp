@@ -61,9 +61,26 @@ public:
         }
         auto hit = cache_.find(piece);
         if (hit != cache_.end()) return hit->second;
+        // initial symbols: whole UTF-8 characters that are vocabulary entries (sentencepiece-style
+        // vocabularies), single bytes otherwise (byte-level vocabularies, byte fallback)
         std::vector<int> ids;
         ids.reserve(piece.size());
-        for (unsigned char c : piece) ids.push_back(byte_id_[c] >= 0 ? byte_id_[c] : unk_id_);
+        for (size_t i = 0; i < piece.size();) {
+            const unsigned char c = (unsigned char)piece[i];
+            size_t len = c < 0x80 ? 1 : (c >> 5) == 6 ? 2 : (c >> 4) == 14 ? 3 : (c >> 3) == 30 ? 4 : 1;
+            if (i + len > piece.size()) len = 1;
+            if (len > 1) {
+                auto it = tok2id_.find(piece.substr(i, len));
+                if (it != tok2id_.end()) {
+                    ids.push_back(it->second);
+                    i += len;
+                    continue;
+                }
+                len = 1;
+            }
+            ids.push_back(byte_id_[c] >= 0 ? byte_id_[c] : unk_id_);
+            i += 1;
+        }
         while (ids.size() > 1) {
             int best_rank = std::numeric_limits<int>::max(), best_i = -1, best_id = -1;
             for (size_t i = 0; i + 1 < ids.size(); ++i) {

@@ -1,0 +1,245 @@
+"""Weight loading from Hugging Face safetensors through a small storage-program compiler.
+
+`compile_program(cfg, tensor_names, tp_size, tp_rank, ep)` turns checkpoint metadata + the runtime
+layout contract (see models/weights.py) into a typed list of ops; `execute_program` runs it
+against a safetensors reader, producing this rank's weight dict. Ops:
+
+  Read(name)                      checkpoint tensor (lazily sliced)
+  Shard(axis, rank, world)        contiguous shard along an axis
+  Rows(start, count)              explicit row range (KV heads replicated across ranks)
+  Concat(axis)                    join operands (fused QKV)
+  Interleave()                    rows g0,u0,g1,u1,... (gate/up for the SwiGLU GEMM epilogue)
+  Stack()                         expert stacks
+  Cast(dtype) / DequantFp8Block() dtype change / 128x128 block-scaled fp8 -> bf16
+  Attach(path)                    store under a runtime name
+
+The program is serialisable (`program_to_json`), so a per-rank plan can be compiled once and
+cached. Counterpart of the reference's weight-loader compiler (driver/weight_loader/src/
+{frontend,abi,storage_compiler}.rs: fused QKV / gate-up joins, MoE expert stacks, shard axes)
+and its C++ executor (driver/cuda/src/loader/*).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .config import ModelConfig
+from .weights import kv_head_range, torch_dtype
+
+
+@dataclass
+class Op:
+    kind: str
+    args: dict = field(default_factory=dict)
+    inputs: List["Op"] = field(default_factory=list)
+
+    def to_json(self):
+        return {"kind": self.kind, "args": self.args, "inputs": [i.to_json() for i in self.inputs]}
+
+    @staticmethod
+    def from_json(d):
+        return Op(d["kind"], d["args"], [Op.from_json(i) for i in d["inputs"]])
+
+
+def Read(name): return Op("read", {"name": name})
+def Shard(x, axis, rank, world): return x if world == 1 else Op("shard", {"axis": axis, "rank": rank, "world": world}, [x])
+def Rows(x, start, count): return Op("rows", {"start": start, "count": count}, [x])
+def Concat(xs, axis=0): return Op("concat", {"axis": axis}, list(xs))
+def Interleave(a, b): return Op("interleave", {}, [a, b])
+def Stack(xs): return Op("stack", {}, list(xs))
+
+
+@dataclass
+class Program:
+    attach: Dict[str, Op]          # runtime path ("layers.3.wqkv") -> expression
+    dtype: str
+    meta: dict = field(default_factory=dict)
+
+
+def program_to_json(p: Program) -> str:
+    return json.dumps({"dtype": p.dtype, "meta": p.meta, "attach": {k: v.to_json() for k, v in p.attach.items()}})
+
+
+def program_from_json(s: str) -> Program:
+    d = json.loads(s)
+    return Program({k: Op.from_json(v) for k, v in d["attach"].items()}, d["dtype"], d.get("meta", {}))
+
+
+def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp_rank: int = 0,
+                    ep: bool = False, dtype: str = "bfloat16") -> Program:
+    """Layout plan for a Llama/Qwen-family checkpoint (HF names) on rank (tp_rank of tp_size)."""
+    names = set(names)
+    T, r, d = tp_size, tp_rank, cfg.head_dim
+    kv0, kvn = kv_head_range(cfg, r, T)
+    pre = "model." if any(n.startswith("model.") for n in names) else ""
+    att: Dict[str, Op] = {}
+
+    def w(n):
+        if n not in names:
+            raise KeyError(f"checkpoint has no tensor {n}")
+        return Read(n)
+
+    att["embed"] = w(f"{pre}embed_tokens.weight")
+    att["final_norm"] = w(f"{pre}norm.weight")
+    head = w("lm_head.weight") if "lm_head.weight" in names else w(f"{pre}embed_tokens.weight")
+    att["lm_head"] = Shard(head, 0, r, T)
+    for li in range(cfg.num_hidden_layers):
+        L, P = f"{pre}layers.{li}.", f"layers.{li}."
+        att[P + "ln1"] = w(L + "input_layernorm.weight")
+        att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
+        q = Shard(w(L + "self_attn.q_proj.weight"), 0, r, T)
+        k = Rows(w(L + "self_attn.k_proj.weight"), kv0 * d, kvn * d)
+        v = Rows(w(L + "self_attn.v_proj.weight"), kv0 * d, kvn * d)
+        att[P + "wqkv"] = Concat([q, k, v], 0)
+        if L + "self_attn.q_proj.bias" in names:
+            att[P + "bqkv"] = Concat([Shard(w(L + "self_attn.q_proj.bias"), 0, r, T),
+                                      Rows(w(L + "self_attn.k_proj.bias"), kv0 * d, kvn * d),
+                                      Rows(w(L + "self_attn.v_proj.bias"), kv0 * d, kvn * d)], 0)
+        att[P + "wo"] = Shard(w(L + "self_attn.o_proj.weight"), 1, r, T)
+        if L + "self_attn.q_norm.weight" in names:
+            att[P + "q_norm"] = w(L + "self_attn.q_norm.weight")
+            att[P + "k_norm"] = w(L + "self_attn.k_norm.weight")
+        if cfg.is_moe and L + "mlp.gate.weight" in names:
+            att[P + "router"] = w(L + "mlp.gate.weight")
+            E = cfg.num_experts
+            experts = range(r * (E // T), (r + 1) * (E // T)) if (ep and T > 1) else range(E)
+            gus, downs = [], []
+            for e in experts:
+                X = f"{L}mlp.experts.{e}."
+                g, u, dn = w(X + "gate_proj.weight"), w(X + "up_proj.weight"), w(X + "down_proj.weight")
+                if not ep:
+                    g, u, dn = Shard(g, 0, r, T), Shard(u, 0, r, T), Shard(dn, 1, r, T)
+                gus.append(Interleave(g, u))
+                downs.append(dn)
+            att[P + "experts_gate_up"] = Stack(gus)
+            att[P + "experts_down"] = Stack(downs)
+        else:
+            att[P + "w_gate_up"] = Interleave(Shard(w(L + "mlp.gate_proj.weight"), 0, r, T),
+                                              Shard(w(L + "mlp.up_proj.weight"), 0, r, T))
+            att[P + "w_down"] = Shard(w(L + "mlp.down_proj.weight"), 1, r, T)
+    return Program(att, dtype, {"tp_size": T, "tp_rank": r, "ep": ep, "layers": cfg.num_hidden_layers,
+                                "vocab_start": r * (cfg.vocab_size // T) if T > 1 else 0})
+
+
+class SafetensorsReader:
+    """Index over the *.safetensors shards of a checkpoint directory (lazy, sliceable reads)."""
+
+    def __init__(self, path):
+        from safetensors import safe_open
+        self.path = Path(path)
+        files = sorted(self.path.glob("*.safetensors")) if self.path.is_dir() else [self.path]
+        if not files:
+            raise FileNotFoundError(f"no .safetensors under {path}")
+        self.handles = [safe_open(str(f), framework="pt", device="cpu") for f in files]
+        self.where = {}
+        for h in self.handles:
+            for k in h.keys():
+                self.where[k] = h
+
+    def names(self) -> List[str]:
+        return list(self.where)
+
+    def get_slice(self, name):
+        return self.where[name].get_slice(name)
+
+    def get(self, name) -> torch.Tensor:
+        return self.where[name].get_tensor(name)
+
+
+def _eval(op: Op, reader, dtype) -> torch.Tensor:
+    k = op.kind
+    if k == "read":
+        return reader.get(op.args["name"])
+    if k in ("shard", "rows") and op.inputs[0].kind == "read":
+        # slice straight out of the file: only this rank's bytes are read
+        sl = reader.get_slice(op.inputs[0].args["name"])
+        shape = sl.get_shape()
+        if k == "rows":
+            a, n = op.args["start"], op.args["count"]
+            return sl[a:a + n]
+        ax, r, wd = op.args["axis"], op.args["rank"], op.args["world"]
+        n = shape[ax] // wd
+        return sl[r * n:(r + 1) * n] if ax == 0 else sl[:, r * n:(r + 1) * n]
+    xs = [_eval(i, reader, dtype) for i in op.inputs]
+    if k == "shard":
+        ax, r, wd = op.args["axis"], op.args["rank"], op.args["world"]
+        n = xs[0].shape[ax] // wd
+        return xs[0].narrow(ax, r * n, n)
+    if k == "rows":
+        return xs[0][op.args["start"]:op.args["start"] + op.args["count"]]
+    if k == "concat":
+        return torch.cat(xs, dim=op.args["axis"])
+    if k == "interleave":
+        return torch.stack([xs[0], xs[1]], dim=1).reshape(xs[0].shape[0] * 2, *xs[0].shape[1:])
+    if k == "stack":
+        return torch.stack(xs, dim=0)
+    raise ValueError(f"unknown op {k}")
+
+
+def execute_program(prog: Program, reader, device="cpu") -> dict:
+    """Materialise the runtime weight dict of this rank."""
+    dtype = torch_dtype(prog.dtype)
+    out = {"layers": [dict() for _ in range(prog.meta["layers"])]}
+    for path, op in prog.attach.items():
+        t = _eval(op, reader, dtype).to(dtype).contiguous().to(device)
+        if path.startswith("layers."):
+            _, li, key = path.split(".", 2)
+            out["layers"][int(li)][key] = t
+        else:
+            out[path] = t
+    out["lm_head_vocab_start"] = prog.meta.get("vocab_start", 0)
+    return out
+
+
+def load_checkpoint(path, device="cpu", tp_size: int = 1, tp_rank: int = 0, ep: bool = False,
+                    dtype: Optional[str] = None):
+    """config.json + safetensors -> (ModelConfig, weights of this rank)."""
+    cfg = ModelConfig.from_path(path)
+    reader = SafetensorsReader(path)
+    prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)
+    return cfg, execute_program(prog, reader, device)
+
+
+def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
+    """Write unsharded runtime weights back out under Hugging Face names (tests, tooling)."""
+    from safetensors.torch import save_file
+    p = Path(path)
+    p.mkdir(parents=True, exist_ok=True)
+    d, hq, hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    t: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": weights["embed"], "model.norm.weight": weights["final_norm"]}
+    if not cfg.tie_word_embeddings:
+        t["lm_head.weight"] = weights["lm_head"]
+    for li, lw in enumerate(weights["layers"]):
+        L = f"model.layers.{li}."
+        t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
+        q, k, v = lw["wqkv"].split([hq * d, hkv * d, hkv * d], 0)
+        t[L + "self_attn.q_proj.weight"], t[L + "self_attn.k_proj.weight"], t[L + "self_attn.v_proj.weight"] = q, k, v
+        t[L + "self_attn.o_proj.weight"] = lw["wo"]
+        if "bqkv" in lw:
+            bq, bk, bv = lw["bqkv"].split([hq * d, hkv * d, hkv * d], 0)
+            t[L + "self_attn.q_proj.bias"], t[L + "self_attn.k_proj.bias"], t[L + "self_attn.v_proj.bias"] = bq, bk, bv
+        if "q_norm" in lw:
+            t[L + "self_attn.q_norm.weight"], t[L + "self_attn.k_norm.weight"] = lw["q_norm"], lw["k_norm"]
+        if "experts_gate_up" in lw:
+            t[L + "mlp.gate.weight"] = lw["router"]
+            for e in range(lw["experts_gate_up"].shape[0]):
+                gu = lw["experts_gate_up"][e]
+                t[f"{L}mlp.experts.{e}.gate_proj.weight"], t[f"{L}mlp.experts.{e}.up_proj.weight"] = gu[0::2], gu[1::2]
+                t[f"{L}mlp.experts.{e}.down_proj.weight"] = lw["experts_down"][e]
+        else:
+            t[L + "mlp.gate_proj.weight"], t[L + "mlp.up_proj.weight"] = lw["w_gate_up"][0::2], lw["w_gate_up"][1::2]
+            t[L + "mlp.down_proj.weight"] = lw["w_down"]
+    save_file({k: v.contiguous().cpu() for k, v in t.items()}, str(p / "model.safetensors"))
+    hf = {"model_type": cfg.model_type, "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+          "num_hidden_layers": cfg.num_hidden_layers, "num_attention_heads": hq, "num_key_value_heads": hkv,
+          "head_dim": d, "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
+          "tie_word_embeddings": cfg.tie_word_embeddings, "torch_dtype": cfg.dtype, "attention_bias": cfg.attention_bias,
+          "max_position_embeddings": cfg.max_position_embeddings}
+    if cfg.is_moe:
+        hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
+                  moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)
+    (p / "config.json").write_text(json.dumps(hf))

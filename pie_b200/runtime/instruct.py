@@ -1,0 +1,299 @@
+"""Instruct (chat) templates per model family and the streaming decoders built on them.
+
+A template renders a role message into tokens (`render`), emits the assistant cue (`cue`), the
+turn terminator (`seal`), knows the stop tokens, how tool definitions and tool results are
+written (`equip`, `answer`) and how to split reasoning from the answer. Decoders consume
+generated tokens incrementally and emit events (chat text deltas, reasoning segments, tool
+calls). Families: llama3, llama2, qwen (ChatML: Qwen2/Qwen3), mistral, gemma, phi3, olmo,
+deepseek-r1 style reasoning. Counterpart of runtime/src/model/instruct.rs and instruct/*.rs.
+"""
+from __future__ import annotations
+
+import json
+import re
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+
+class Instruct:
+    """Base: plain concatenation, no special tokens."""
+
+    name = "plain"
+    bos = ""
+    stop_strings: Sequence[str] = ()
+    think_open, think_close = "<think>", "</think>"
+    tool_open, tool_close = "<tool_call>", "</tool_call>"
+
+    def format(self, role: str, message: str, first: bool) -> str:
+        return message
+
+    def cue_text(self) -> str:
+        return ""
+
+    def seal_text(self) -> str:
+        return ""
+
+    # ---- token level
+    def render(self, role: str, message: str, tok, first: bool = False) -> List[int]:
+        text = (self.bos if first else "") + self.format(role, message, first)
+        return tok.encode(text)
+
+    def cue(self, tok) -> List[int]:
+        return tok.encode(self.cue_text())
+
+    def seal(self, tok) -> List[int]:
+        return tok.encode(self.seal_text())
+
+    def stop_tokens(self, tok) -> List[int]:
+        out = list(getattr(tok, "eos_tokens", []))
+        for s in self.stop_strings:
+            ids = tok.encode(s)
+            if len(ids) == 1:
+                out.append(ids[0])
+        return sorted(set(out))
+
+    # ---- tools
+    def equip(self, tools: Sequence[dict]) -> str:
+        """System-prompt text that declares the callable tools (JSON schema per tool)."""
+        lines = ["You may call these tools. To call one, answer with "
+                 f"{self.tool_open}{{\"name\": ..., \"arguments\": {{...}}}}{self.tool_close}.", ""]
+        lines += [json.dumps(t) for t in tools]
+        return "\n".join(lines)
+
+    def answer(self, name: str, result: str) -> str:
+        """Text of a tool result fed back to the model."""
+        return json.dumps({"tool": name, "result": result})
+
+    def tool_grammar(self, tools: Sequence[dict]) -> str:
+        """EBNF of one tool call, for constrained decoding of the call body."""
+        names = " | ".join(json.dumps(json.dumps(t["name"])) for t in tools) or '"\\"none\\""'
+        return ('root ::= "{" ws "\\"name\\"" ws ":" ws name ws "," ws "\\"arguments\\"" ws ":" ws object ws "}"\n'
+                f"name ::= {names}\n" + JSON_EBNF_TAIL)
+
+
+JSON_EBNF_TAIL = r'''object ::= "{" ws (pair (ws "," ws pair)*)? ws "}"
+pair ::= string ws ":" ws value
+array ::= "[" ws (value (ws "," ws value)*)? ws "]"
+value ::= object | array | string | number | "true" | "false" | "null"
+string ::= "\"" char* "\""
+char ::= [^"\\] | "\\" ["\\/bfnrt]
+number ::= "-"? [0-9]+ ("." [0-9]+)? ([eE] [+-]? [0-9]+)?
+ws ::= [ \t\n]*
+'''
+
+
+class Llama3(Instruct):
+    name = "llama3"
+    bos = "<|begin_of_text|>"
+    stop_strings = ("<|eot_id|>", "<|end_of_text|>")
+    tool_open, tool_close = "<|python_tag|>", "<|eom_id|>"
+
+    def format(self, role, message, first):
+        return f"<|start_header_id|>{role}<|end_header_id|>\n\n{message}<|eot_id|>"
+
+    def cue_text(self):
+        return "<|start_header_id|>assistant<|end_header_id|>\n\n"
+
+    def seal_text(self):
+        return "<|eot_id|>"
+
+
+class Llama2(Instruct):
+    name = "llama2"
+    bos = "<s>"
+    stop_strings = ("</s>",)
+
+    def __init__(self):
+        self._system = ""
+
+    def format(self, role, message, first):
+        if role == "system":
+            self._system = message
+            return ""
+        if role == "user":
+            sys = f"<<SYS>>\n{self._system}\n<</SYS>>\n\n" if self._system else ""
+            self._system = ""
+            return f"[INST] {sys}{message} [/INST]"
+        return f" {message} </s><s>"
+
+    def seal_text(self):
+        return " </s>"
+
+
+class ChatML(Instruct):
+    """Qwen2 / Qwen3 / OLMo-style ChatML."""
+    name = "qwen"
+    stop_strings = ("<|im_end|>", "<|endoftext|>")
+
+    def format(self, role, message, first):
+        return f"<|im_start|>{role}\n{message}<|im_end|>\n"
+
+    def cue_text(self):
+        return "<|im_start|>assistant\n"
+
+    def seal_text(self):
+        return "<|im_end|>\n"
+
+    def answer(self, name, result):
+        return f"<tool_response>\n{result}\n</tool_response>"
+
+
+class Mistral(Instruct):
+    name = "mistral"
+    bos = "<s>"
+    stop_strings = ("</s>",)
+    tool_open, tool_close = "[TOOL_CALLS]", "</s>"
+
+    def format(self, role, message, first):
+        if role in ("system", "user"):
+            return f"[INST] {message} [/INST]"
+        return f"{message}</s>"
+
+    def seal_text(self):
+        return "</s>"
+
+
+class Gemma(Instruct):
+    name = "gemma"
+    bos = "<bos>"
+    stop_strings = ("<end_of_turn>", "<eos>")
+
+    def format(self, role, message, first):
+        role = "model" if role == "assistant" else "user"
+        return f"<start_of_turn>{role}\n{message}<end_of_turn>\n"
+
+    def cue_text(self):
+        return "<start_of_turn>model\n"
+
+    def seal_text(self):
+        return "<end_of_turn>\n"
+
+
+class Phi3(Instruct):
+    name = "phi3"
+    stop_strings = ("<|end|>", "<|endoftext|>")
+
+    def format(self, role, message, first):
+        return f"<|{role}|>\n{message}<|end|>\n"
+
+    def cue_text(self):
+        return "<|assistant|>\n"
+
+    def seal_text(self):
+        return "<|end|>\n"
+
+
+class R1(ChatML):
+    """DeepSeek-R1 style: the assistant cue opens a reasoning block."""
+    name = "r1"
+
+    def cue_text(self):
+        return "<|im_start|>assistant\n<think>\n"
+
+
+FAMILIES: Dict[str, type] = {"llama3": Llama3, "llama": Llama3, "llama2": Llama2, "qwen": ChatML, "qwen2": ChatML,
+                             "qwen3": ChatML, "qwen3_moe": ChatML, "olmo2": ChatML, "olmo3": ChatML,
+                             "mistral": Mistral, "mistral3": Mistral, "mixtral": Mistral, "gemma": Gemma,
+                             "gemma2": Gemma, "gemma3": Gemma, "phi3": Phi3, "r1": R1, "plain": Instruct}
+
+
+def for_arch(arch: str) -> Instruct:
+    return FAMILIES.get(arch, Instruct)()
+
+
+# ------------------------------------------------------------------------------ streaming decoders
+@dataclass
+class Event:
+    kind: str                  # delta | done | thinking | thinking_done | tool_call
+    text: str = ""
+    call: Optional[dict] = None
+
+
+class ChatDecoder:
+    """Feeds generated tokens, yields printable text deltas; `done` at a stop token. Incomplete
+    UTF-8 sequences are held back until they complete."""
+
+    def __init__(self, tok, instruct: Instruct):
+        self.tok, self.stop = tok, set(instruct.stop_tokens(tok))
+        self.ids: List[int] = []
+        self.emitted = ""
+        self.finished = False
+
+    def feed(self, tokens: Sequence[int]) -> List[Event]:
+        out = []
+        for t in tokens:
+            if self.finished:
+                break
+            if t in self.stop:
+                self.finished = True
+                out.append(Event("done", self.emitted))
+                break
+            self.ids.append(t)
+            text = self.tok.decode(self.ids)
+            if text.endswith("�"):
+                continue
+            if len(text) > len(self.emitted):
+                out.append(Event("delta", text[len(self.emitted):]))
+                self.emitted = text
+        return out
+
+
+class ReasoningDecoder:
+    """Splits `<think>...</think>` from the answer in a text stream."""
+
+    def __init__(self, instruct: Instruct, starts_in_think: bool = False):
+        self.open, self.close = instruct.think_open, instruct.think_close
+        self.in_think = starts_in_think
+        self.buf = ""
+
+    def feed(self, text: str) -> List[Event]:
+        self.buf += text
+        out = []
+        while True:
+            tag = self.close if self.in_think else self.open
+            i = self.buf.find(tag)
+            if i < 0:
+                keep = max(0, len(self.buf) - len(tag) + 1)     # a tag may be split across deltas
+                if keep:
+                    out.append(Event("thinking" if self.in_think else "delta", self.buf[:keep]))
+                    self.buf = self.buf[keep:]
+                break
+            if i:
+                out.append(Event("thinking" if self.in_think else "delta", self.buf[:i]))
+            if self.in_think:
+                out.append(Event("thinking_done"))
+            self.buf = self.buf[i + len(tag):]
+            self.in_think = not self.in_think
+        return out
+
+    def flush(self) -> List[Event]:
+        out = [Event("thinking" if self.in_think else "delta", self.buf)] if self.buf else []
+        self.buf = ""
+        return out
+
+
+class ToolDecoder:
+    """Extracts tool calls (`<tool_call>{json}</tool_call>` or the family's tags) from a text stream."""
+
+    def __init__(self, instruct: Instruct):
+        self.open, self.close = instruct.tool_open, instruct.tool_close
+        self.buf = ""
+
+    def feed(self, text: str) -> List[Event]:
+        self.buf += text
+        out = []
+        while True:
+            i = self.buf.find(self.open)
+            if i < 0:
+                break
+            j = self.buf.find(self.close, i + len(self.open))
+            if j < 0:
+                break
+            body = self.buf[i + len(self.open):j].strip()
+            try:
+                call = json.loads(body)
+                out.append(Event("tool_call", body, call))
+            except json.JSONDecodeError:
+                out.append(Event("delta", self.buf[i:j + len(self.close)]))
+            self.buf = self.buf[:i] + self.buf[j + len(self.close):]
+        return out
