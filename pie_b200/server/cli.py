@@ -1,0 +1,287 @@
+"""`pie` command line (python -m pie_b200 ...). Subcommands follow the reference CLI
+(server/src/cli.rs:50-142): serve, run, config {init,show,set}, auth {add,remove,list,keygen},
+model {list}, inferlet {list}, new, build, doctor, check, smoke.
+
+`pie run <inferlet> [-- --key value ...]` boots a one-shot engine, connects a client over the
+WebSocket like any other client, launches the inferlet with the trailing `--key value` pairs as
+its JSON input, relays its output and shuts down (server/src/cli/run_cmd.rs:26-120).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import sys
+import textwrap
+import time
+from pathlib import Path
+
+from . import config as cfgmod
+
+
+def _trailing_to_json(rest):
+    out, i = {}, 0
+    while i < len(rest):
+        k = rest[i]
+        if not k.startswith("--"):
+            raise SystemExit(f"expected --key, got {k!r}")
+        v = rest[i + 1] if i + 1 < len(rest) and not rest[i + 1].startswith("--") else "true"
+        i += 2 if v != "true" or (i + 1 < len(rest) and rest[i + 1] == "true") else 1
+        try:
+            out[k[2:].replace("-", "_")] = json.loads(v)
+        except json.JSONDecodeError:
+            out[k[2:].replace("-", "_")] = v
+    return out
+
+
+def _load(args) -> cfgmod.Config:
+    if getattr(args, "config", None):
+        return cfgmod.load(args.config)
+    p = cfgmod.default_path()
+    cfg = cfgmod.load(p) if p.exists() else cfgmod.default_config()
+    if getattr(args, "driver", None):
+        for m in cfg.model:
+            m.driver.type = args.driver
+    if getattr(args, "preset", None):
+        cfg.model = [cfgmod.ModelSection(name=args.preset, preset=args.preset, driver=cfg.model[0].driver if cfg.model
+                                         else cfgmod.DriverConfig())]
+    if getattr(args, "model_path", None):
+        cfg.model = [cfgmod.ModelSection(name=Path(args.model_path).name, path=args.model_path,
+                                         driver=cfg.model[0].driver if cfg.model else cfgmod.DriverConfig())]
+    cfgmod.validate(cfg)
+    return cfg
+
+
+def cmd_serve(args) -> int:
+    from .serve import start_engine
+    cfg = _load(args)
+    if args.port is not None:
+        cfg.server.port = args.port
+    if args.no_auth:
+        cfg.auth.enabled = False
+    h = start_engine(cfg)
+    if h is None:
+        return 0
+    print(f"pie_b200 serving on {h.uri}")
+    if cfg.auth.enabled:
+        print(f"internal token: {h.auth.internal_token}")
+    if args.monitor:
+        from .monitor import run_monitor
+        threading = __import__("threading")
+        threading.Thread(target=run_monitor, args=(h.engine,), daemon=True).start()
+    h.wait_then_shutdown()
+    return 0
+
+
+def cmd_run(args) -> int:
+    from ..client.client import PieClient
+    from .serve import start_engine
+    cfg = _load(args)
+    cfg.server.port = 0
+    h = start_engine(cfg)
+    if h is None:
+        return 0
+    rc = 0
+    try:
+        c = PieClient(h.uri)
+        if cfg.auth.enabled:
+            c.auth_by_token(h.auth.internal_token)
+        name = args.inferlet
+        if Path(name).suffix == ".py" and Path(name).exists():
+            src = Path(name).read_bytes()
+            name = Path(name).stem.replace("_", "-")
+            c.install_program(src, f'[package]\nname = "{name}"\nversion = "0.1.0"\n')
+        proc = c.launch_process(name, _trailing_to_json(args.rest))
+        while True:
+            ev, val = proc.recv(timeout=args.timeout)
+            if ev == "stdout":
+                print(val, end="", flush=True)
+            elif ev == "stderr":
+                print(val, end="", file=sys.stderr, flush=True)
+            elif ev == "message":
+                print(f"[message] {val}")
+            elif ev == "return":
+                print(val)
+                break
+            elif ev == "error":
+                print(f"error: {val}", file=sys.stderr)
+                rc = 1
+                break
+        c.close()
+    finally:
+        h.shutdown()
+    return rc
+
+
+def cmd_config(args) -> int:
+    p = Path(args.config).expanduser() if args.config else cfgmod.default_path()
+    if args.action == "init":
+        if p.exists() and not args.force:
+            raise SystemExit(f"{p} exists (use --force)")
+        p.parent.mkdir(parents=True, exist_ok=True)
+        p.write_text(cfgmod.dumps(cfgmod.default_config()))
+        print(f"wrote {p}")
+    elif args.action == "show":
+        print(cfgmod.dumps(cfgmod.load(p) if p.exists() else cfgmod.default_config()))
+    elif args.action == "set":
+        cfg = cfgmod.load(p) if p.exists() else cfgmod.default_config()
+        cfgmod.set_key(cfg, args.key, args.value)
+        p.parent.mkdir(parents=True, exist_ok=True)
+        p.write_text(cfgmod.dumps(cfg))
+        print(f"{args.key} = {args.value}")
+    return 0
+
+
+def cmd_auth(args) -> int:
+    from .auth import UserStore, generate_ed25519
+    cfg = _load(args)
+    store = UserStore(cfg.auth.authorized_users)
+    if args.action == "add":
+        store.add(args.username, Path(args.pubkey).expanduser().read_text() if Path(args.pubkey).expanduser().exists()
+                  else args.pubkey)
+        print(f"added key for {args.username}")
+    elif args.action == "remove":
+        print("removed" if store.remove(args.username) else "no such user")
+    elif args.action == "list":
+        for u, ks in store.users.items():
+            print(f"{u}: {len(ks)} key(s)")
+    elif args.action == "keygen":
+        from cryptography.hazmat.primitives import serialization
+        k, pub = generate_ed25519()
+        out = Path(args.pubkey or "pie_ed25519").expanduser()
+        out.write_bytes(k.private_bytes(serialization.Encoding.PEM, serialization.PrivateFormat.OpenSSH,
+                                        serialization.NoEncryption()))
+        out.with_suffix(".pub").write_text(pub + "\n")
+        print(f"wrote {out} and {out.with_suffix('.pub')}")
+    return 0
+
+
+def cmd_model(args) -> int:
+    from ..models.config import PRESETS
+    for name, kw in PRESETS.items():
+        print(f"{name:18s} {kw['model_type']:10s} layers={kw['num_hidden_layers']:3d} hidden={kw['hidden_size']:5d} "
+              f"heads={kw['num_attention_heads']}/{kw['num_key_value_heads']} vocab={kw['vocab_size']}")
+    return 0
+
+
+def cmd_inferlet(args) -> int:
+    import importlib
+    import pkgutil
+    from .. import inferlets
+    for m in pkgutil.iter_modules(inferlets.__path__):
+        mod = importlib.import_module(f"pie_b200.inferlets.{m.name}")
+        if hasattr(mod, "main"):
+            doc = (mod.__doc__ or "").strip().splitlines()
+            print(f"{getattr(mod, 'NAME', m.name.replace('_', '-')):28s} {doc[0] if doc else ''}")
+    return 0
+
+
+TEMPLATE = '''"""{name}: describe what this inferlet does."""
+from pie_b200.sdk import Context, Model, Sampler, runtime
+
+NAME = "{name}"
+
+
+async def main(args):
+    model = Model.load(runtime.models()[0])
+    ctx = Context(model)
+    ctx.system("You are a helpful assistant.").user(args.get("prompt", "Hello")).cue()
+    text = await ctx.generate(Sampler.top_p(0.6, 0.95), max_tokens=int(args.get("max_tokens", 128))).collect_text()
+    ctx.release()
+    return text
+'''
+
+
+def cmd_new(args) -> int:
+    d = Path(args.name)
+    d.mkdir(parents=True, exist_ok=False)
+    (d / "main.py").write_text(TEMPLATE.format(name=args.name))
+    (d / "Pie.toml").write_text(f'[package]\nname = "{args.name}"\nversion = "0.1.0"\n\n[runtime]\nlanguage = "python"\n')
+    print(f"created {d}/main.py and {d}/Pie.toml")
+    return 0
+
+
+def cmd_build(args) -> int:
+    """Native inferlets need no compilation: check that the program loads and defines main()."""
+    import ast
+    src = (Path(args.path) / "main.py") if Path(args.path).is_dir() else Path(args.path)
+    tree = ast.parse(src.read_text())
+    ok = any(isinstance(n, ast.AsyncFunctionDef) and n.name == "main" for n in tree.body)
+    print("ok" if ok else "missing `async def main(input)`")
+    return 0 if ok else 1
+
+
+def cmd_doctor(args) -> int:
+    import shutil
+    import torch
+    from ..ops import _lib
+    print(f"python        {sys.version.split()[0]}")
+    print(f"torch         {torch.__version__} cuda={torch.cuda.is_available()} devices={torch.cuda.device_count()}")
+    print(f"nvcc          {shutil.which('nvcc') or 'not found'}")
+    print(f"kernel lib    {'present' if _lib.lib_path().exists() else 'missing (python -m pie_b200._build)'}")
+    try:
+        from .._C import pie_host  # noqa: F401
+        print("host module   present")
+    except ImportError:
+        print("host module   missing (python -m pie_b200._build)")
+    for i in range(torch.cuda.device_count()):
+        p = torch.cuda.get_device_properties(i)
+        print(f"gpu {i}         {p.name} sm_{p.major}{p.minor} {p.total_memory >> 30} GiB {p.multi_processor_count} SMs")
+    return 0
+
+
+def cmd_check(args) -> int:
+    try:
+        cfg = cfgmod.load(args.config) if args.config else (
+            cfgmod.load(cfgmod.default_path()) if cfgmod.default_path().exists() else cfgmod.default_config())
+        print(f"config ok: {len(cfg.model)} model(s)")
+        return 0
+    except Exception as e:  # noqa: BLE001
+        print(f"config error: {e}", file=sys.stderr)
+        return 1
+
+
+def cmd_smoke(args) -> int:
+    """Boot a dummy-driver engine, run text-completion through the WebSocket path."""
+    args.config, args.driver, args.preset, args.model_path = None, "dummy", "tiny-llama", None
+    args.inferlet, args.rest, args.timeout = "text-completion", ["--prompt_tokens", "[1,2,3]", "--max_tokens", "4"], 60
+    return cmd_run(args)
+
+
+def main(argv=None) -> int:
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(levelname)s %(message)s")
+    ap = argparse.ArgumentParser(prog="pie", description="pie_b200: programmable LLM serving on B200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def common(p):
+        p.add_argument("--config")
+        p.add_argument("--driver", choices=["cuda_native", "cpu", "dummy"])
+        p.add_argument("--preset")
+        p.add_argument("--model-path")
+
+    p = sub.add_parser("serve"); common(p)
+    p.add_argument("--port", type=int); p.add_argument("--no-auth", action="store_true")
+    p.add_argument("--monitor", action="store_true"); p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("run"); common(p)
+    p.add_argument("inferlet"); p.add_argument("--timeout", type=float, default=600.0)
+    p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_run)
+    p = sub.add_parser("config"); p.add_argument("action", choices=["init", "show", "set"])
+    p.add_argument("key", nargs="?"); p.add_argument("value", nargs="?")
+    p.add_argument("--config"); p.add_argument("--force", action="store_true"); p.set_defaults(fn=cmd_config)
+    p = sub.add_parser("auth"); common(p); p.add_argument("action", choices=["add", "remove", "list", "keygen"])
+    p.add_argument("username", nargs="?"); p.add_argument("pubkey", nargs="?"); p.set_defaults(fn=cmd_auth)
+    p = sub.add_parser("model"); p.add_argument("action", choices=["list"], nargs="?", default="list"); p.set_defaults(fn=cmd_model)
+    p = sub.add_parser("inferlet"); p.add_argument("action", choices=["list"], nargs="?", default="list"); p.set_defaults(fn=cmd_inferlet)
+    p = sub.add_parser("new"); p.add_argument("name"); p.set_defaults(fn=cmd_new)
+    p = sub.add_parser("build"); p.add_argument("path"); p.set_defaults(fn=cmd_build)
+    p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("check"); p.add_argument("--config"); p.set_defaults(fn=cmd_check)
+    p = sub.add_parser("smoke"); p.set_defaults(fn=cmd_smoke)
+    args = ap.parse_args(argv)
+    if getattr(args, "rest", None) and args.rest and args.rest[0] == "--":
+        args.rest = args.rest[1:]
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

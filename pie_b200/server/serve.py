@@ -1,0 +1,158 @@
+"""Engine start-up from a configuration: build the drivers of every [[model]] (one per
+data-parallel group), register tokenizer / instruct template, install the bundled inferlets,
+bind the WebSocket server, supervise. Counterpart of server/src/serve.rs:272-418 (start_engine),
+serve/topology.rs (DP x TP), serve/lifecycle.rs (watchdog) and bootstrap_translate.rs.
+
+Tensor parallelism spans processes: start `pie serve` under
+`python -m torch.distributed.run --nproc-per-node T ...`; rank 0 runs the engine and the server,
+the other ranks serve its fires (`TPComm.follower_loop`).
+"""
+from __future__ import annotations
+
+import logging
+import os
+import signal
+import threading
+from pathlib import Path
+from typing import Optional
+
+from ..inferlets import install_all
+from ..models.config import ModelConfig, preset
+from ..runtime import instruct as instruct_mod
+from ..runtime.engine import Engine, EngineConfig
+from ..runtime.tokenizer import ByteTokenizer, load_hf_tokenizer
+from .auth import Authenticator, UserStore
+from .config import Config, ModelSection, calculate_topology
+from .server import PieServer
+
+log = logging.getLogger("pie_b200")
+
+
+def build_drivers(m: ModelSection):
+    """Drivers of one model: one per data-parallel group. Returns (drivers, cfg, tokenizer, comm)."""
+    d = m.driver
+    tok = None
+    comm = None
+    if d.type == "dummy":
+        from ..driver.mock import DummyDriver
+        cfg = preset(m.preset) if m.preset else ModelConfig(name=m.name)
+        return [DummyDriver(vocab=cfg.vocab_size, page_size=d.kv_page_size, total_pages=4096)], cfg, tok, comm
+    import torch
+    from ..driver.executor import TorchDriver
+    from ..models.transformer import ParallelContext
+    weights = None
+    if m.path:
+        from ..models import loader
+        cfg = ModelConfig.from_path(m.path)
+        cfg.name = m.name
+        if (Path(m.path) / "tokenizer.json").exists():
+            tok = load_hf_tokenizer(m.path)
+    else:
+        cfg = preset(m.preset)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if d.type == "cpu":
+        w = None
+        if m.path:
+            _, w = loader.load_checkpoint(m.path, "cpu", dtype="float32")
+            cfg.dtype = "float32"
+        return [TorchDriver(cfg, "cpu", weights=w, num_pages=4096, page_size=d.kv_page_size)], cfg, tok, comm
+    groups = calculate_topology(d.device, d.tensor_parallel_size)
+    drivers = []
+    if d.tensor_parallel_size > 1:
+        if world != d.tensor_parallel_size:
+            raise RuntimeError(f"tensor_parallel_size={d.tensor_parallel_size} needs that many ranks "
+                               f"(start under torch.distributed.run); WORLD_SIZE is {world}")
+        import torch.distributed as dist
+        from ..parallel.comm import TPComm
+        dev = torch.device("cuda", groups[0][rank])
+        torch.cuda.set_device(dev)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+        comm = TPComm(rank, world, dev, fused=d.tp_backend == "fused")
+        par = ParallelContext(world, rank, comm, ep=d.expert_parallel)
+        if m.path:
+            _, weights = loader.load_checkpoint(m.path, dev, world, rank, ep=d.expert_parallel)
+        drv = TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, par=par, gemm_backend=d.gemm,
+                          use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization)
+        comm.attach(drv)
+        return [drv], cfg, tok, comm
+    for g in groups:
+        dev = torch.device("cuda", g[0])
+        if m.path:
+            _, weights = loader.load_checkpoint(m.path, dev)
+        per_page = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * d.kv_page_size * cfg.head_dim * 2
+        swap = int(d.swap_pool_gb * (1 << 30) // per_page)
+        drivers.append(TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, gemm_backend=d.gemm,
+                                   use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
+                                   swap_pages=swap))
+    return drivers, cfg, tok, comm
+
+
+class EngineHandle:
+    def __init__(self, engine: Engine, server: Optional[PieServer], auth: Authenticator, comms: list):
+        self.engine, self.server, self.auth, self.comms = engine, server, auth, comms
+        self._stop = threading.Event()
+
+    @property
+    def port(self) -> int:
+        return self.server.port if self.server else 0
+
+    @property
+    def uri(self) -> str:
+        return f"ws://{self.server.host}:{self.server.port}"
+
+    def wait_then_shutdown(self) -> None:
+        for s in (signal.SIGINT, signal.SIGTERM):
+            try:
+                signal.signal(s, lambda *_: self._stop.set())
+            except ValueError:      # not on the main thread
+                pass
+        self._stop.wait()
+        self.shutdown()
+
+    def shutdown(self) -> None:
+        self._stop.set()
+        if self.server:
+            self.server.stop()
+        for c in self.comms:
+            c.stop_followers()
+        self.engine.shutdown()
+        for c in self.comms:
+            c.close()
+
+
+def start_engine(cfg: Config, serve: bool = True, port: Optional[int] = None) -> Optional[EngineHandle]:
+    """Returns None on tensor-parallel follower ranks (after they served until STOP)."""
+    rt = cfg.runtime
+    first = cfg.model[0].scheduler if cfg.model else None
+    engine = Engine(EngineConfig(batch_policy=first.batch_policy if first else "adaptive",
+                                 speculation_depth=first.speculation_depth if first else 1,
+                                 max_concurrent_processes=rt.max_concurrent_processes,
+                                 request_timeout_secs=rt.request_timeout_secs,
+                                 default_token_budget=rt.default_token_budget,
+                                 default_endowment_pages=rt.default_endowment_pages,
+                                 admission_oversubscription_factor=rt.admission_oversubscription_factor))
+    comms = []
+    for m in cfg.model:
+        drivers, mcfg, tok, comm = build_drivers(m)
+        if comm is not None:
+            comms.append(comm)
+            if comm.rank != 0:
+                comm.follower_loop(drivers[0])
+                comm.close()
+                engine.shutdown()
+                return None
+        if tok is None:
+            tok = ByteTokenizer(mcfg.vocab_size)
+        ins = instruct_mod.for_arch(m.instruct or (mcfg.model_type if m.path else "plain"))
+        engine.add_model(m.name, drivers, tokenizer=tok, instruct=ins)
+        log.info("model %s: %d driver(s), %d KV pages", m.name, len(drivers),
+                 sum(d.capabilities().total_pages for d in drivers))
+    install_all(engine)
+    auth = Authenticator(cfg.auth.enabled, UserStore(cfg.auth.authorized_users) if cfg.auth.enabled else None)
+    server = None
+    if serve:
+        server = PieServer(engine, cfg.server.host, cfg.server.port if port is None else port, auth,
+                           rt.program_dir, cfg.server.max_message_bytes)
+        server.start()
+    return EngineHandle(engine, server, auth, comms)
