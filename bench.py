@@ -44,6 +44,9 @@ def parse_args():
     ap.add_argument("--max-tokens", type=int, default=16384)
     ap.add_argument("--device-loop", default="pipelined", choices=["pipelined", "staged"],
                     help="pipelined: decode_async with device-fed tokens (all N); staged: inputs pre-staged on the device (N=1)")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="N>1: dp = one replica per GPU, the inferlets spread over them (the serving topology "
+                         "for a model that fits one GPU); tp = one tensor-parallel group")
     ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"],
                     help="fused: GEMM epilogue reduce-scatter + push all-gather over peer memory; nccl: GEMM + all-reduce")
     return ap.parse_args()
@@ -79,13 +82,15 @@ def main():
     par = ParallelContext()
     barrier = None
     comm = None
+    dp = world > 1 and args.parallelism == "dp"
     if world > 1:
         import torch.distributed as dist
-        from pie_b200.parallel.comm import TPComm
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        comm = TPComm(rank, world, torch.device("cuda", local_rank), fused=args.tp_backend == "fused")
-        par = ParallelContext(world, rank, comm)
         barrier = dist.barrier
+        if not dp:
+            from pie_b200.parallel.comm import TPComm
+            comm = TPComm(rank, world, torch.device("cuda", local_rank), fused=args.tp_backend == "fused")
+            par = ParallelContext(world, rank, comm)
     if args.gpus != world and rank == 0:
         print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
 
@@ -101,10 +106,12 @@ def main():
     torch.cuda.synchronize()
     t_init = time.time() - t0
     prompts = harness.make_prompts(args.requests, args.prompt_min, args.prompt_max, cfg.vocab_size, seed=1)
+    if dp:
+        prompts = prompts[rank::world]      # every replica serves its share of the same 512 inferlets
     sampler = SamplerSpec(SamplerKind.TOP_P, temperature=1.0, top_p=0.9)
     sampler_args = {"temperature": 1.0, "top_p": 0.9}
 
-    if world > 1 and rank != 0:
+    if comm is not None and rank != 0:
         comm.follower_loop(driver)      # serves every fire rank 0 publishes, both phases
         comm.close()
         _hard_exit(0)
@@ -132,7 +139,7 @@ def main():
             dev = harness.run_device_decode(driver, prompts, args.out_tokens, sampler, args.warmup, args.steps)
         else:
             dev = harness.run_pipelined_decode(driver, prompts, args.out_tokens, sampler, args.warmup,
-                                               args.steps, comm=comm)
+                                               args.steps, comm=comm, barrier=barrier if dp else None)
         clocks = sampler_clk.stop()
     if comm is not None:
         comm.stop_followers()
@@ -145,7 +152,33 @@ def main():
         o, n = driver.slab.offsets["tile_qstart"]
         avg_pages = sum(-(-(len(p) + args.out_tokens // 2) // 16) for p in prompts)
         h2d = (o + n) * 4 + avg_pages * 4
-        d2h = n_req * 4
+        d2h = len(prompts) * 4
+    launches = (driver.launches_per_decode_step(dev["rb"]) * args.steps) if dev else 0
+    if dp:
+        # whole-job numbers: slowest replica sets the step time, throughputs and bytes add up
+        def reduce(x, op):
+            t = torch.tensor([float(x if x is not None else 0.0)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=op)
+            return float(t.item())
+        MAX, SUM = dist.ReduceOp.MAX, dist.ReduceOp.SUM
+        if dev:
+            dev["ms_per_step"] = reduce(dev["ms_per_step"], MAX)
+            dev["tokens_per_s"] = n_req / (dev["ms_per_step"] / 1e3)
+            dev["prefill_tokens_per_s"] = reduce(dev["prefill_tokens_per_s"], SUM)
+            launches = int(reduce(launches, SUM))
+            if clocks:
+                clocks["sm_mhz"] = -reduce(-(clocks.get("sm_mhz") or 0), MAX)     # slowest GPU's median clock
+        if e2e is not None:
+            e2e["window_ms_per_step"] = reduce(e2e.get("window_ms_per_step"), MAX)
+            e2e["window_tokens_per_s"] = n_req / (e2e["window_ms_per_step"] / 1e3) if e2e["window_ms_per_step"] else None
+            e2e["workload_tokens_per_s"] = reduce(e2e["workload_tokens_per_s"], SUM)
+            e2e["p50_ttft_s"] = reduce(e2e["p50_ttft_s"], MAX)
+            e2e["p50_itl_s"] = reduce(e2e["p50_itl_s"], MAX)
+            e2e["wall_s"] = reduce(e2e["wall_s"], MAX)
+            e2e["fires"] = int(reduce(e2e["fires"], SUM))
+            h2d, d2h = int(reduce(h2d, SUM)), int(reduce(d2h, SUM))
+        if rank != 0:
+            _hard_exit(0)
     value = dev["tokens_per_s"] if dev else None
     line = {
         "metric": "decode output tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -154,12 +187,12 @@ def main():
         "data": "synthetic random-token prompts, random-init N(0,0.02) weights",
         "impl": "ours",
         "config": {"model": cfg.name, "global_batch": n_req, "seq_len": f"prompts U[{args.prompt_min},{args.prompt_max}] + {args.out_tokens} out",
-                   "parallelism": f"tp{world}", "tp_backend": args.tp_backend if world > 1 else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
+                   "parallelism": (f"dp{world}" if dp else f"tp{world}"), "tp_backend": args.tp_backend if (world > 1 and not dp) else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
                    "gemm": args.gemm, "layers": cfg.num_hidden_layers,
                    "l2": "working set per step (weights 16 GB + KV > 60 GB) exceeds the 126 MB L2; no flush needed",
                    "valid": not args.layers},
         "clocks": clocks,
-        "gpu_launches": (driver.launches_per_decode_step(dev["rb"]) * args.steps) if dev else 0,
+        "gpu_launches": launches,
         "prefill_tokens_per_s": dev["prefill_tokens_per_s"] if dev else None,
         "init_s": t_init,
     }

@@ -144,7 +144,7 @@ def decode_request(driver, prompts, pages, tokens, step: int, sampler: SamplerSp
 
 
 def run_pipelined_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec, warmup: int, steps: int,
-                         comm=None):
+                         comm=None, barrier=None):
     """Device-timed decode through `decode_async` (the path the engine's cohort uses): step s is
     launched with its tokens fed on the device from step s-1, the host only trails one step behind
     to recycle its input slab. W untimed + K timed steps bracketed by synchronise (+ barrier and
@@ -187,6 +187,9 @@ def run_pipelined_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec,
                 comm.mark(False)
             else:
                 torch.cuda.synchronize()
+                if barrier is not None:     # data-parallel replicas start the timed region together
+                    barrier()
+                    torch.cuda.synchronize()
                 ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 ev0.record()
         h = driver.decode_async(make(s), s & 1)
@@ -199,6 +202,8 @@ def run_pipelined_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec,
         ev1.record()
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1)
+        if barrier is not None:
+            barrier()
     prev.wait()
     driver.check_status_host()
     prefill_tokens = sum(t for _, t in t_prefill)

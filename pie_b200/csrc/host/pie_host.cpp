@@ -6,6 +6,7 @@
 
 #include "bpe.hpp"
 #include "brle.hpp"
+#include "grammar.hpp"
 #include "pagestore.hpp"
 
 namespace py = pybind11;
@@ -77,6 +78,73 @@ PYBIND11_MODULE(pie_host, m) {
         .def("effective_pages", &PageStore::effective_pages)
         .def("node_pages", &PageStore::node_pages)
         .def_property_readonly("node_count", &PageStore::node_count);
+
+    // ------------------------------------------------------------------ grammar
+    py::class_<Grammar>(m, "Grammar")
+        .def(py::init([](const std::vector<std::vector<std::vector<std::pair<int, py::bytes>>>>& rules, int root) {
+            // symbol = (rule id, b"") for a reference, (-1, 32-byte class bitmap) for a byte class
+            auto g = new Grammar();
+            g->root = root;
+            g->rules.resize(rules.size());
+            for (size_t r = 0; r < rules.size(); ++r) {
+                for (auto& alt : rules[r]) {
+                    std::vector<GSymbol> syms;
+                    for (auto& sym : alt) {
+                        GSymbol gs;
+                        if (sym.first >= 0) {
+                            if (sym.first >= (int)rules.size()) throw std::out_of_range("rule reference out of range");
+                            gs.is_rule = true;
+                            gs.rule = sym.first;
+                        } else {
+                            const std::string bits = sym.second;
+                            if (bits.size() != 32) throw std::invalid_argument("byte class must be 32 bytes");
+                            for (int w = 0; w < 4; ++w) {
+                                uint64_t v = 0;
+                                for (int b = 0; b < 8; ++b) v |= (uint64_t)(unsigned char)bits[w * 8 + b] << (8 * b);
+                                gs.cls[w] = v;
+                            }
+                        }
+                        syms.push_back(gs);
+                    }
+                    g->rules[r].push_back(std::move(syms));
+                }
+            }
+            return g;
+        }))
+        .def_property_readonly("num_rules", [](const Grammar& g) { return g.rules.size(); });
+
+    py::class_<TokenTrie>(m, "TokenTrie")
+        .def(py::init([](const std::vector<int>& ids, const std::vector<py::bytes>& toks) {
+            auto t = new TokenTrie();
+            for (size_t i = 0; i < ids.size(); ++i) t->insert(ids[i], std::string(toks[i]));
+            return t;
+        }))
+        .def_readonly("vocab", &TokenTrie::vocab)
+        .def_property_readonly("num_nodes", [](const TokenTrie& t) { return t.nodes.size(); });
+
+    py::class_<GrammarMatcher>(m, "GrammarMatcher")
+        .def(py::init<const Grammar*, const TokenTrie*>(), py::keep_alive<1, 2>(), py::keep_alive<1, 3>())
+        .def("reset", &GrammarMatcher::reset)
+        .def("accept_bytes", [](GrammarMatcher& mt, const py::bytes& b) { return mt.accept_bytes(std::string(b)); })
+        .def("rollback", &GrammarMatcher::rollback)
+        .def("can_terminate", &GrammarMatcher::can_terminate)
+        .def("is_terminated", &GrammarMatcher::is_terminated)
+        .def_property_readonly("num_states", &GrammarMatcher::num_states)
+        .def("next_token_mask", [](const GrammarMatcher& mt) {
+            std::vector<uint8_t> a;
+            mt.next_token_mask(a);
+            py::array_t<bool> out(a.size());
+            std::copy(a.begin(), a.end(), reinterpret_cast<uint8_t*>(out.mutable_data()));
+            return out;
+        })
+        .def("next_token_mask_brle", [](const GrammarMatcher& mt, int vocab_size, const std::vector<int>& extra) {
+            std::vector<uint8_t> a;
+            mt.next_token_mask(a);
+            a.resize((size_t)std::max<int>(vocab_size, (int)a.size()), 0);
+            for (int id : extra)
+                if (id >= 0 && id < (int)a.size()) a[id] = 1;
+            return brle_encode(a.data(), a.size());
+        }, py::arg("vocab_size"), py::arg("extra") = std::vector<int>());
 
     // ------------------------------------------------------------------ BPE
     py::class_<BpeCore>(m, "BpeCore")

@@ -11,8 +11,10 @@
 from .core import Context, Forward, GenStep, Generator, Model, Output, ProbeHandle, SampleHandle, Tokenizer
 from .sample import Distribution, Entropy, Logits, Logprob, Logprobs, Sampler
 from .spec import NGramSpeculator, Speculator
+from .grammar import AnyJson, Ebnf, Grammar, GrammarConstraint, JsonSchema, Matcher, Regex
 from . import messaging, runtime, scheduling, session
 
 __all__ = ["Context", "Forward", "GenStep", "Generator", "Model", "Output", "ProbeHandle", "SampleHandle",
            "Tokenizer", "Distribution", "Entropy", "Logits", "Logprob", "Logprobs", "Sampler", "Speculator",
-           "NGramSpeculator", "messaging", "runtime", "scheduling", "session"]
+           "NGramSpeculator", "AnyJson", "Ebnf", "Grammar", "GrammarConstraint", "JsonSchema", "Matcher", "Regex",
+           "messaging", "runtime", "scheduling", "session"]

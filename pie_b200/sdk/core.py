@@ -381,12 +381,18 @@ class Context:
         return Forward(self)
 
     def generate(self, sampler: Sampler, max_tokens: Optional[int] = None, stop: Optional[Iterable[int]] = None,
-                 **kw) -> "Generator":
+                 constrain=None, logit_mask: Optional[Sequence[int]] = None, **kw) -> "Generator":
         g = Generator(self, sampler, **kw)
         if max_tokens is not None:
             g.max_tokens(max_tokens)
         if stop is not None:
             g.stop(stop)
+        if constrain is not None:
+            for c in (constrain if isinstance(constrain, (list, tuple)) else [constrain]):
+                g.constrain(c)
+        if logit_mask is not None:
+            from .grammar import StaticMaskConstraint
+            g.constrain(StaticMaskConstraint(logit_mask))
         return g
 
     def set_bid(self, value: float) -> None:
@@ -503,7 +509,7 @@ class Generator:
             out.append(t)
             for c in self._constraints:
                 c.accept([t])
-            if t in self._stop:
+            if t in self._stop or any(getattr(c, "is_terminated", lambda: False)() for c in self._constraints):
                 self._done = True
                 break
         if self.speculator is not None:
@@ -569,5 +575,10 @@ class Generator:
             toks = toks[:-1]
         return self.ctx.model.tokenizer().decode(toks)
 
-    async def collect_json(self) -> Any:
-        return json.loads(await self.collect_text())
+    async def collect_json(self, schema=None, parse=None) -> Any:
+        """Constrain the output to JSON (to `schema` when given), drain, parse."""
+        from .grammar import AnyJson, JsonSchema
+        if not self._constraints:
+            self.constrain(JsonSchema(schema) if schema is not None else AnyJson())
+        value = json.loads(await self.collect_text())
+        return parse(value) if parse is not None else value
