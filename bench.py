@@ -85,7 +85,9 @@ def main():
     dp = world > 1 and args.parallelism == "dp"
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=180))
         barrier = dist.barrier
         if not dp:
             from pie_b200.parallel.comm import TPComm
@@ -155,30 +157,34 @@ def main():
         d2h = len(prompts) * 4
     launches = (driver.launches_per_decode_step(dev["rb"]) * args.steps) if dev else 0
     if dp:
-        # whole-job numbers: slowest replica sets the step time, throughputs and bytes add up
-        def reduce(x, op):
-            t = torch.tensor([float(x if x is not None else 0.0)], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=op)
-            return float(t.item())
-        MAX, SUM = dist.ReduceOp.MAX, dist.ReduceOp.SUM
-        if dev:
-            dev["ms_per_step"] = reduce(dev["ms_per_step"], MAX)
-            dev["tokens_per_s"] = n_req / (dev["ms_per_step"] / 1e3)
-            dev["prefill_tokens_per_s"] = reduce(dev["prefill_tokens_per_s"], SUM)
-            launches = int(reduce(launches, SUM))
-            if clocks:
-                clocks["sm_mhz"] = -reduce(-(clocks.get("sm_mhz") or 0), MAX)     # slowest GPU's median clock
-        if e2e is not None:
-            e2e["window_ms_per_step"] = reduce(e2e.get("window_ms_per_step"), MAX)
-            e2e["window_tokens_per_s"] = n_req / (e2e["window_ms_per_step"] / 1e3) if e2e["window_ms_per_step"] else None
-            e2e["workload_tokens_per_s"] = reduce(e2e["workload_tokens_per_s"], SUM)
-            e2e["p50_ttft_s"] = reduce(e2e["p50_ttft_s"], MAX)
-            e2e["p50_itl_s"] = reduce(e2e["p50_itl_s"], MAX)
-            e2e["wall_s"] = reduce(e2e["wall_s"], MAX)
-            e2e["fires"] = int(reduce(e2e["fires"], SUM))
-            h2d, d2h = int(reduce(h2d, SUM)), int(reduce(d2h, SUM))
+        # whole-job numbers: the slowest replica sets the step time, throughputs and bytes add up.
+        # One fixed-size vector per reduction so that every rank issues the same collectives.
+        def g(d, key):
+            v = (d or {}).get(key)
+            return float(v) if v is not None else 0.0
+        mx = torch.tensor([g(dev, "ms_per_step"), g(e2e, "window_ms_per_step"), g(e2e, "p50_ttft_s"),
+                           g(e2e, "p50_itl_s"), g(e2e, "wall_s"), -g(clocks, "sm_mhz")],
+                          device="cuda", dtype=torch.float64)
+        sm = torch.tensor([g(dev, "prefill_tokens_per_s"), float(launches), g(e2e, "workload_tokens_per_s"),
+                           g(e2e, "fires"), float(h2d or 0), float(d2h or 0)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        mx, sm = mx.tolist(), sm.tolist()
         if rank != 0:
             _hard_exit(0)
+        if dev:
+            dev["ms_per_step"] = mx[0]
+            dev["tokens_per_s"] = n_req / (mx[0] / 1e3) if mx[0] else None
+            dev["prefill_tokens_per_s"] = sm[0]
+            launches = int(sm[1])
+            if clocks:
+                clocks["sm_mhz"] = -mx[5]          # slowest GPU's median clock
+        if e2e is not None:
+            e2e["window_ms_per_step"] = mx[1] or None
+            e2e["window_tokens_per_s"] = n_req / (mx[1] / 1e3) if mx[1] else None
+            e2e["p50_ttft_s"], e2e["p50_itl_s"], e2e["wall_s"] = mx[2], mx[3], mx[4]
+            e2e["workload_tokens_per_s"], e2e["fires"] = sm[2], int(sm[3])
+            h2d, d2h = int(sm[4]), int(sm[5])
     value = dev["tokens_per_s"] if dev else None
     line = {
         "metric": "decode output tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,

@@ -29,11 +29,15 @@ struct GemmCfg {
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 16384 /*epilogue staging*/;
 };
 
-template <int BN, int EPI>
+// GROUPED: mixture-of-experts form. A holds token rows sorted by expert in 128-row tiles,
+// tile_expert[m_tile] names the expert whose weights ([E*N, K] under tma_b) the tile multiplies,
+// or -1 for an unused tile, which every role skips. Whole-tile scheduling only.
+template <int BN, int EPI, bool GROUPED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  bf16* __restrict__ C, const bf16* __restrict__ R, int M, int N, int K, int ldc,
-                 int ldr, int* status, const __grid_constant__ TpArgs tp, const StreamKArgs sk) {
+                 int ldr, int* status, const __grid_constant__ TpArgs tp, const StreamKArgs sk,
+                 const int* __restrict__ tile_expert) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -102,6 +106,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             Segment seg;
             while (ok && walk.next(seg)) {
                 const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
+                int b_row = n_blk * BN;
+                if (GROUPED) {
+                    const int e = tile_expert[m_blk];
+                    if (e < 0) continue;
+                    b_row += e * N;
+                }
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -109,7 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
                     const uint32_t a_dst = tiles + s * Cfg::STAGE_BYTES;
                     tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
-                    tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, n_blk * BN);
+                    tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
                 }
             }
             // no copy of this CTA may still be in flight when it exits
@@ -127,6 +137,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
             Segment seg;
             for (; ok && walk.next(seg); ++tcount) {
+                if (GROUPED && tile_expert[seg.tile % tiles_m] < 0) { --tcount; continue; }
                 const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(acc), aph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) break;
                 tc_fence_after();
@@ -156,6 +167,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const long long total_units = (long long)num_tiles * num_kb;
         for (; walk.next(seg); ++tcount) {
             const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
+            if (GROUPED && tile_expert[m_blk] < 0) { --tcount; continue; }
             const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
             const bool got = mbar_wait(tfull_bar(acc), aph, status, PIE_ERR_WAIT_MMA);
             if (!__all_sync(0xffffffffu, got)) break;
@@ -370,7 +382,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, co
     if (e != cudaSuccess) return (int)e;
     StreamKArgs sk{w.ws, w.cnt, plan.streamk, 0};
     kern<<<plan.grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
-                                                           ldr, status, tp, sk);
+                                                           ldr, status, tp, sk, nullptr);
     return (int)cudaGetLastError();
 }
 
@@ -472,6 +484,44 @@ PIE_API int pie_gemm_bf16_tp(const void* A, const void* W, void* C, int M, int N
     if (bn == 256) { GO(256) }
     else if (bn == 128) { GO(128) }
     else if (bn == 64) { GO(64) }
+#undef GO
+    return (int)cudaErrorInvalidValue;
+}
+
+// Grouped (mixture-of-experts) GEMM: A [max_mtiles*128, K] holds token rows sorted by expert in
+// 128-row tiles; W is [E, N, K] contiguous; tile_expert [max_mtiles] (device) gives each tile's
+// expert or -1. C [max_mtiles*128, N] (or N/2 with the SwiGLU epilogue). Graph-safe: the launch
+// shape depends only on max_mtiles.
+PIE_API int pie_grouped_gemm_bf16(const void* A, const void* W, void* C, const int* tile_expert, int max_mtiles,
+                                  int num_experts, int N, int K, int lda, int ldc, int epilogue, int* status,
+                                  int num_sms, cudaStream_t st) {
+    if (max_mtiles <= 0 || N <= 0 || num_experts <= 0) return 0;
+    if (K <= 0 || K % 8 || N % 8 || ldc % 8) return (int)cudaErrorInvalidValue;
+    if (epilogue == EPI_SWIGLU && N % 32) return (int)cudaErrorInvalidValue;
+    const int M = max_mtiles * GEMM_BM;
+    const int bn = N >= 128 ? 128 : 64;
+    CUtensorMap ta, tb;
+    if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
+    if (pie_make_tma_2d_bf16(&tb, W, (long)num_experts * N, K, K, bn) != 0) return (int)cudaErrorInvalidValue;
+    const long tiles = (long)max_mtiles * ((N + bn - 1) / bn);
+    const int grid = (int)(tiles < num_sms ? tiles : num_sms);
+    StreamKArgs sk{nullptr, nullptr, 0, 0};
+    TpArgs tp{};
+#define GO(BN_, EPI_)                                                                                     \
+    {                                                                                                     \
+        auto kern = gemm_bf16_kernel<BN_, EPI_, true>;                                                    \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                             (int)GemmCfg<BN_>::SMEM_BYTES);                              \
+        if (e != cudaSuccess) return (int)e;                                                              \
+        kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, nullptr, M, N, K, ldc, \
+                                                                   0, status, tp, sk, tile_expert);       \
+        return (int)cudaGetLastError();                                                                   \
+    }
+    if (epilogue == EPI_STORE) {
+        if (bn == 128) GO(128, EPI_STORE) else GO(64, EPI_STORE)
+    } else if (epilogue == EPI_SWIGLU) {
+        if (bn == 128) GO(128, EPI_SWIGLU) else GO(64, EPI_SWIGLU)
+    }
 #undef GO
     return (int)cudaErrorInvalidValue;
 }

@@ -1,0 +1,181 @@
+// Mixture-of-experts plumbing around the grouped tcgen05 GEMM (gemm_tcgen05.cu, GROUPED form):
+//   pie_moe_route    softmax over E router logits, top-k, optional renormalisation; every route
+//                    (token, j) takes a position inside its expert's segment with one atomic
+//   pie_moe_align    per-expert segments padded to 128-row tiles: seg_start[e], tile_expert[tile]
+//   pie_moe_permute  token rows -> expert-sorted rows (local buffer, or a peer rank's buffer
+//                    under expert parallelism)
+//   pie_moe_combine  out[t] = residual[t] + sum_j w[t,j] * y[slot(t,j)]
+// Everything is sized by static upper bounds and reads its counts on the device, so the whole
+// block can sit inside a CUDA graph.
+//
+// Replaces driver/cuda/src/kernels/topk_softmax.cu:19 (router) and the pointer-array / aligned
+// dispatch family of driver/cuda/src/kernels/moe_dispatch.cu:12-760 with its cuBLAS batched GEMMs
+// (driver/cuda/src/model/qwen3_5_moe_forward.cpp:1315-1558).
+#include "common.cuh"
+
+namespace pie {
+
+constexpr int MOE_MAX_E = 512;
+constexpr int MOE_TILE = 128;
+
+// One warp per token. logits [N, E] (bf16 or fp32), E <= 512.
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ logits, int ld, int n, int E, int k, int renorm,
+                                 int* __restrict__ ids, float* __restrict__ w, int* __restrict__ pos,
+                                 int* __restrict__ counts) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n) return;
+    const T* row = logits + (size_t)warp * ld;
+    float v[MOE_MAX_E / 32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_E / 32; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = e < E ? (float)row[e] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_E / 32; ++i) {
+        v[i] = (i * 32 + lane) < E ? __expf(v[i] - mx) : -1.f;   // -1 = excluded
+        if (v[i] > 0.f) sum += v[i];
+    }
+    sum = warp_sum(sum);
+    float picked_sum = 0.f;
+    float my_w = 0.f;
+    int my_id = 0;
+    for (int j = 0; j < k; ++j) {
+        float best = -2.f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_E / 32; ++i) {
+            const int e = i * 32 + lane;
+            if (v[i] > best) { best = v[i]; bi = e; }     // lowest index wins ties within a lane
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if ((bi & 31) == lane) v[bi >> 5] = -1.f;
+        picked_sum += best;
+        if (lane == j) { my_w = best; my_id = bi; }
+    }
+    if (lane < k) {
+        const float denom = renorm ? picked_sum : sum;
+        ids[(size_t)warp * k + lane] = my_id;
+        w[(size_t)warp * k + lane] = my_w / denom;
+        pos[(size_t)warp * k + lane] = atomicAdd(counts + my_id, 1);
+    }
+}
+
+// Single block. counts [E] -> seg_start [E] (row of the expert's first slot), tile_expert
+// [max_mtiles]; counts are copied to counts_out (may be null) and zeroed for the next call.
+__global__ void moe_align_kernel(int* __restrict__ counts, int E, int max_mtiles, int* __restrict__ seg_start,
+                                 int* __restrict__ tile_expert, int* __restrict__ counts_out) {
+    __shared__ int tiles_of[MOE_MAX_E];
+    __shared__ int start_of[MOE_MAX_E + 1];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += blockDim.x) {
+        const int c = counts[e];
+        tiles_of[e] = (c + MOE_TILE - 1) / MOE_TILE;
+        if (counts_out) counts_out[e] = c;
+        counts[e] = 0;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; ++e) {
+            start_of[e] = acc;
+            acc += tiles_of[e];
+        }
+        start_of[E] = acc;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+        seg_start[e] = start_of[e] * MOE_TILE;
+        for (int t = start_of[e]; t < start_of[e + 1] && t < max_mtiles; ++t) tile_expert[t] = e;
+    }
+    for (int t = start_of[E] + tid; t < max_mtiles; t += blockDim.x) tile_expert[t] = -1;
+}
+
+// One block per route: xs[slot] = x[token]. dst_of_expert (optional, expert parallelism): base
+// pointer of the expert-sorted buffer on the rank that owns the expert (peer-mapped), with
+// experts_per_rank local experts each; seg_start is then indexed by the global expert id and holds
+// the slot on the owner.
+__global__ void moe_permute_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__ ids,
+                                   const int* __restrict__ pos, const int* __restrict__ seg_start, int H, int k,
+                                   bf16* __restrict__ xs, int* __restrict__ slot_of) {
+    const int route = blockIdx.x;
+    const int e = ids[route];
+    const int slot = seg_start[e] + pos[route];
+    if (threadIdx.x == 0) slot_of[route] = slot;
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)(route / k) * ldx);
+    bf16x8* dst = reinterpret_cast<bf16x8*>(xs + (size_t)slot * H);
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
+}
+
+// One block per token.
+__global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __restrict__ slot_of,
+                                   const float* __restrict__ w, const bf16* __restrict__ residual, int ldr, int H,
+                                   int k, bf16* __restrict__ out, int ldo) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        float acc[8];
+        if (residual) unpack8(*reinterpret_cast<const bf16x8*>(residual + (size_t)t * ldr + c * 8), acc);
+        else
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int j = 0; j < k; ++j) {
+            const int slot = slot_of[(size_t)t * k + j];
+            const float wj = w[(size_t)t * k + j];
+            float v[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(y + (size_t)slot * H + c * 8), v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += wj * v[i];
+        }
+        *reinterpret_cast<bf16x8*>(out + (size_t)t * ldo + c * 8) = pack8(acc);
+    }
+}
+
+}  // namespace pie
+
+using namespace pie;
+
+// logits_fp32: 0 = bf16 logits, 1 = fp32. counts must be zero on entry (pie_moe_align leaves it so).
+PIE_API int pie_moe_route(const void* logits, int logits_fp32, int ld, int n, int E, int k, int renorm, int* ids,
+                          float* w, int* pos, int* counts, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (E > MOE_MAX_E || k > 32 || k > E || k <= 0) return (int)cudaErrorInvalidValue;
+    const int threads = 128, blocks = (n * 32 + threads - 1) / threads;
+    if (logits_fp32)
+        moe_route_kernel<float><<<blocks, threads, 0, st>>>((const float*)logits, ld, n, E, k, renorm, ids, w, pos, counts);
+    else
+        moe_route_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)logits, ld, n, E, k, renorm, ids, w, pos, counts);
+    return (int)cudaGetLastError();
+}
+
+PIE_API int pie_moe_align(int* counts, int E, int max_mtiles, int* seg_start, int* tile_expert, int* counts_out,
+                          cudaStream_t st) {
+    if (E > MOE_MAX_E || E <= 0) return (int)cudaErrorInvalidValue;
+    moe_align_kernel<<<1, 256, 0, st>>>(counts, E, max_mtiles, seg_start, tile_expert, counts_out);
+    return (int)cudaGetLastError();
+}
+
+PIE_API int pie_moe_permute(const void* x, int ldx, const int* ids, const int* pos, const int* seg_start, int n,
+                            int H, int k, void* xs, int* slot_of, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (H % 8 || ldx % 8) return (int)cudaErrorInvalidValue;
+    moe_permute_kernel<<<n * k, 128, 0, st>>>((const bf16*)x, ldx, ids, pos, seg_start, H, k, (bf16*)xs, slot_of);
+    return (int)cudaGetLastError();
+}
+
+PIE_API int pie_moe_combine(const void* y, const int* slot_of, const float* w, const void* residual, int ldr, int n,
+                            int H, int k, void* out, int ldo, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (H % 8 || ldo % 8 || (residual && ldr % 8)) return (int)cudaErrorInvalidValue;
+    moe_combine_kernel<<<n, 128, 0, st>>>((const bf16*)y, slot_of, w, (const bf16*)residual, ldr, H, k, (bf16*)out, ldo);
+    return (int)cudaGetLastError();
+}

@@ -42,34 +42,53 @@ def moe_reference(cfg: ModelConfig, x: torch.Tensor, lw: dict) -> torch.Tensor:
     return out
 
 
+def _buffers(model, n: int, lw: dict, device) -> "ops.MoeBuffers":
+    """Scratch for up to n tokens, grown in powers of two and kept on the model (fixed addresses
+    let the block be captured in CUDA graphs)."""
+    cap = 1 << max(0, (max(n, 1) - 1).bit_length())
+    buf = getattr(model, "_moe_buf", None)
+    e, n2, hdim = lw["experts_gate_up"].shape
+    if buf is None or buf.n < cap or buf.I != n2 // 2 or buf.E != e:
+        buf = ops.MoeBuffers(cap, hdim, n2 // 2, e, model.cfg.num_experts_per_tok, device)
+        model._moe_buf = buf
+    return buf
+
+
 def moe_block(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torch.Tensor:
-    """h + MoE(x). x is the normalised hidden state [N, H]."""
+    """h + MoE(x). x is the normalised hidden state [N, H].
+
+    GPU: router GEMM -> route/align/permute kernels -> grouped tcgen05 GEMMs (SwiGLU fused into the
+    first) -> weighted combine with the residual; no host synchronisation, graph-safe.
+    Under tensor parallelism without EP the experts are sharded on their intermediate dimension
+    (the reference's scheme) and the partial outputs are summed across ranks."""
     cfg, par = model.cfg, model.par
     if par.tp_size > 1 and par.ep:
         return par.comm.moe_expert_parallel(model, x, lw, h)
-    logits = model._gemm(x, lw["router"]) if x.is_cuda and lw["router"].shape[0] % 8 == 0 \
-        else torch.matmul(x, lw["router"].t())
-    w, ids = route(cfg, logits)
+    if x.is_cuda:
+        logits = model._gemm(x, lw["router"]) if lw["router"].shape[0] % 8 == 0 \
+            else torch.matmul(x, lw["router"].t())
+        buf = _buffers(model, x.shape[0], lw, x.device)
+        if par.tp_size > 1:
+            part = ops.moe_experts(x, logits, lw["experts_gate_up"], lw["experts_down"], cfg.num_experts_per_tok,
+                                   cfg.norm_topk_prob, buf)
+            return h + par.comm.all_reduce(part)
+        return ops.moe_experts(x, logits, lw["experts_gate_up"], lw["experts_down"], cfg.num_experts_per_tok,
+                               cfg.norm_topk_prob, buf, residual=h)
+    w, ids = route(cfg, torch.matmul(x, lw["router"].t()))
     n, k = ids.shape
     flat = ids.reshape(-1)
     order = torch.argsort(flat, stable=True)
-    tok = (order // k).to(torch.int32)
+    tok = order // k
     counts = torch.bincount(flat, minlength=lw["experts_gate_up"].shape[0])
-    xs = ops.gather_rows(x, tok) if x.is_cuda else x[tok.long()]
+    xs = x[tok]
     ys = torch.empty(xs.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
-    if x.is_cuda and hasattr(ops, "grouped_gemm"):
-        ops.grouped_expert_mlp(xs, counts, lw["experts_gate_up"], lw["experts_down"], ys)
-    else:
-        start = 0
-        for e, c in enumerate(counts.tolist()):
-            if c:
-                act = model._gemm(xs[start:start + c], lw["experts_gate_up"][e], swiglu=True)
-                ys[start:start + c] = model._gemm(act, lw["experts_down"][e])
-            start += c
+    start = 0
+    for e, c in enumerate(counts.tolist()):
+        if c:
+            act = model._gemm(xs[start:start + c], lw["experts_gate_up"][e], swiglu=True)
+            ys[start:start + c] = model._gemm(act, lw["experts_down"][e])
+        start += c
     wflat = w.reshape(-1)[order].to(torch.float32)
     out = torch.zeros(n, x.shape[1], dtype=torch.float32, device=x.device)
-    out.index_add_(0, tok.long(), ys.float() * wflat[:, None])
-    out = out.to(x.dtype)
-    if par.tp_size > 1:
-        out = par.comm.all_reduce(out)
-    return h + out
+    out.index_add_(0, tok, ys.float() * wflat[:, None])
+    return h + out.to(x.dtype)

@@ -214,6 +214,86 @@ def gemm(x, w, residual=None, epilogue: int = EPI_STORE, out=None, force_bn: int
     return out
 
 
+# --------------------------------------------------------------------------- mixture of experts
+MOE_TILE = 128
+
+
+def moe_max_mtiles(n_tokens: int, k: int, num_experts: int) -> int:
+    """Upper bound of 128-row tiles after padding every expert's segment."""
+    return (n_tokens * k + MOE_TILE - 1) // MOE_TILE + num_experts
+
+
+class MoeBuffers:
+    """Device scratch of one MoE block evaluation for up to `n` tokens (graph-safe: fixed addresses)."""
+
+    def __init__(self, n: int, hidden: int, inter: int, num_experts: int, k: int, device, dtype=torch.bfloat16):
+        self.n, self.k, self.E, self.H, self.I = n, k, num_experts, hidden, inter
+        self.max_mtiles = moe_max_mtiles(n, k, num_experts)
+        rows = self.max_mtiles * MOE_TILE
+        i32 = dict(dtype=torch.int32, device=device)
+        self.ids = torch.empty(n, k, **i32)
+        self.pos = torch.empty(n, k, **i32)
+        self.slot_of = torch.empty(n, k, **i32)
+        self.w = torch.empty(n, k, dtype=torch.float32, device=device)
+        self.counts = torch.zeros(num_experts, **i32)
+        self.counts_out = torch.zeros(num_experts, **i32)
+        self.seg_start = torch.empty(num_experts, **i32)
+        self.tile_expert = torch.empty(self.max_mtiles, **i32)
+        self.xs = torch.zeros(rows, hidden, dtype=dtype, device=device)
+        self.act = torch.zeros(rows, inter, dtype=dtype, device=device)
+        self.ys = torch.zeros(rows, hidden, dtype=dtype, device=device)
+
+
+def moe_route(logits, k: int, renorm: bool, buf: "MoeBuffers"):
+    n, e = logits.shape
+    check(fn("pie_moe_route")(ptr(logits), 1 if logits.dtype == torch.float32 else 0, logits.stride(0), n, e, k,
+                              1 if renorm else 0, ptr(buf.ids), ptr(buf.w), ptr(buf.pos), ptr(buf.counts),
+                              stream_ptr()), "moe_route")
+    return buf.ids[:n], buf.w[:n]
+
+
+def moe_align(buf: "MoeBuffers", max_mtiles: int = 0):
+    check(fn("pie_moe_align")(ptr(buf.counts), buf.E, max_mtiles or buf.max_mtiles, ptr(buf.seg_start),
+                              ptr(buf.tile_expert), ptr(buf.counts_out), stream_ptr()), "moe_align")
+
+
+def moe_permute(x, buf: "MoeBuffers"):
+    n, h = x.shape
+    check(fn("pie_moe_permute")(ptr(x), x.stride(0), ptr(buf.ids), ptr(buf.pos), ptr(buf.seg_start), n, h, buf.k,
+                                ptr(buf.xs), ptr(buf.slot_of), stream_ptr()), "moe_permute")
+
+
+def grouped_gemm(a, w, tile_expert, out, max_mtiles: int, epilogue: int = EPI_STORE):
+    """out[tile rows] = a[tile rows] @ w[tile_expert[tile]].T for every used 128-row tile. w [E,N,K]."""
+    e, n, k = w.shape
+    assert w.is_contiguous() and a.shape[1] == k and a.shape[0] >= max_mtiles * MOE_TILE
+    check(fn("pie_grouped_gemm_bf16")(ptr(a), ptr(w), ptr(out), ptr(tile_expert), max_mtiles, e, n, k, a.stride(0),
+                                      out.stride(0), epilogue, ptr(kernel_status(a.device)), num_sms(a.device),
+                                      stream_ptr()), "grouped_gemm_bf16")
+    return out
+
+
+def moe_combine(buf: "MoeBuffers", n: int, residual=None, out=None):
+    if out is None:
+        out = torch.empty(n, buf.H, dtype=buf.ys.dtype, device=buf.ys.device)
+    check(fn("pie_moe_combine")(ptr(buf.ys), ptr(buf.slot_of), ptr(buf.w), ptr(residual),
+                                residual.stride(0) if residual is not None else 0, n, buf.H, buf.k, ptr(out),
+                                out.stride(0), stream_ptr()), "moe_combine")
+    return out
+
+
+def moe_experts(x, logits, w_gate_up, w_down, k: int, renorm: bool, buf: "MoeBuffers", residual=None):
+    """residual + sum_j w_j * down_e(swiglu(gate_up_e(x))) over each token's top-k experts e."""
+    n = x.shape[0]
+    mt = moe_max_mtiles(n, k, buf.E)
+    moe_route(logits, k, renorm, buf)
+    moe_align(buf, mt)
+    moe_permute(x, buf)
+    grouped_gemm(buf.xs, w_gate_up, buf.tile_expert, buf.act, mt, EPI_SWIGLU)
+    grouped_gemm(buf.act, w_down, buf.tile_expert, buf.ys, mt, EPI_STORE)
+    return moe_combine(buf, n, residual)
+
+
 # --------------------------------------------------------------------------- attention
 @dataclass
 class AttnBatch:
