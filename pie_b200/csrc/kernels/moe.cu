@@ -2,16 +2,20 @@
 //   pie_moe_route    softmax over E router logits, top-k, optional renormalisation; every route
 //                    (token, j) takes a position inside its expert's segment with one atomic
 //   pie_moe_align    per-expert segments padded to 128-row tiles: seg_start[e], tile_expert[tile]
-//   pie_moe_permute  token rows -> expert-sorted rows (local buffer, or a peer rank's buffer
-//                    under expert parallelism)
-//   pie_moe_combine  out[t] = residual[t] + sum_j w[t,j] * y[slot(t,j)]
+//   pie_moe_permute  token rows -> expert-sorted rows
+//   pie_moe_combine  out[t] = residual[t] + sum_j w[t,j] * y[slot(t,j)]; the _rs form stores this
+//                    rank's partial rows into the row owners' receive buffers (peer stores)
+// Expert parallelism in the row-sharded tensor-parallel design: the all-gather push of the
+// normalised activations already delivers every token to every rank (the dispatch), each rank
+// routes all tokens but gives slots only to its own experts, and the combine is a reduce-scatter
+// by peer stores that the owner's reduce+norm kernel sums.
 // Everything is sized by static upper bounds and reads its counts on the device, so the whole
 // block can sit inside a CUDA graph.
 //
 // Replaces driver/cuda/src/kernels/topk_softmax.cu:19 (router) and the pointer-array / aligned
 // dispatch family of driver/cuda/src/kernels/moe_dispatch.cu:12-760 with its cuBLAS batched GEMMs
 // (driver/cuda/src/model/qwen3_5_moe_forward.cpp:1315-1558).
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace pie {
 
@@ -19,10 +23,12 @@ constexpr int MOE_MAX_E = 512;
 constexpr int MOE_TILE = 128;
 
 // One warp per token. logits [N, E] (bf16 or fp32), E <= 512.
+// ids receives the expert index relative to e_lo, or -1 for an expert outside [e_lo, e_lo+e_cnt)
+// (expert parallelism: those routes belong to another rank and take no slot here).
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ logits, int ld, int n, int E, int k, int renorm,
-                                 int* __restrict__ ids, float* __restrict__ w, int* __restrict__ pos,
-                                 int* __restrict__ counts) {
+                                 int e_lo, int e_cnt, int* __restrict__ ids, float* __restrict__ w,
+                                 int* __restrict__ pos, int* __restrict__ counts) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n) return;
     const T* row = logits + (size_t)warp * ld;
@@ -65,9 +71,11 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, int ld, int n, in
     }
     if (lane < k) {
         const float denom = renorm ? picked_sum : sum;
-        ids[(size_t)warp * k + lane] = my_id;
+        const int local = my_id - e_lo;
+        const bool mine = local >= 0 && local < e_cnt;
+        ids[(size_t)warp * k + lane] = mine ? local : -1;
         w[(size_t)warp * k + lane] = my_w / denom;
-        pos[(size_t)warp * k + lane] = atomicAdd(counts + my_id, 1);
+        pos[(size_t)warp * k + lane] = mine ? atomicAdd(counts + local, 1) : -1;
     }
 }
 
@@ -101,15 +109,17 @@ __global__ void moe_align_kernel(int* __restrict__ counts, int E, int max_mtiles
     for (int t = start_of[E] + tid; t < max_mtiles; t += blockDim.x) tile_expert[t] = -1;
 }
 
-// One block per route: xs[slot] = x[token]. dst_of_expert (optional, expert parallelism): base
-// pointer of the expert-sorted buffer on the rank that owns the expert (peer-mapped), with
-// experts_per_rank local experts each; seg_start is then indexed by the global expert id and holds
-// the slot on the owner.
+// One block per route: xs[slot] = x[token]; routes of experts that are not local (ids < 0) take
+// no slot.
 __global__ void moe_permute_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__ ids,
                                    const int* __restrict__ pos, const int* __restrict__ seg_start, int H, int k,
                                    bf16* __restrict__ xs, int* __restrict__ slot_of) {
     const int route = blockIdx.x;
     const int e = ids[route];
+    if (e < 0) {
+        if (threadIdx.x == 0) slot_of[route] = -1;
+        return;
+    }
     const int slot = seg_start[e] + pos[route];
     if (threadIdx.x == 0) slot_of[route] = slot;
     const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)(route / k) * ldx);
@@ -117,11 +127,21 @@ __global__ void moe_permute_kernel(const bf16* __restrict__ x, int ldx, const in
     for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
 }
 
-// One block per token.
+// One block per token. RS: the (partial) row goes to the receive buffer of the rank that owns
+// token t (reduce-scatter by peer stores, same protocol as the GEMM's EPI_RS epilogue); the last
+// block to finish raises this rank's flag on every owner.
+template <bool RS>
 __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __restrict__ slot_of,
                                    const float* __restrict__ w, const bf16* __restrict__ residual, int ldr, int H,
-                                   int k, bf16* __restrict__ out, int ldo) {
+                                   int k, bf16* __restrict__ out, int ldo, const __grid_constant__ TpArgs tp) {
     const int t = blockIdx.x;
+    bf16* dst_row;
+    if (RS) {
+        const int owner = t / tp.rows_per_rank;
+        dst_row = tp.peer_recv[owner] + ((size_t)tp.rank * tp.rows_per_rank + (t - owner * tp.rows_per_rank)) * (size_t)H;
+    } else {
+        dst_row = out + (size_t)t * ldo;
+    }
     for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
         float acc[8];
         if (residual) unpack8(*reinterpret_cast<const bf16x8*>(residual + (size_t)t * ldr + c * 8), acc);
@@ -130,13 +150,19 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __rest
             for (int i = 0; i < 8; ++i) acc[i] = 0.f;
         for (int j = 0; j < k; ++j) {
             const int slot = slot_of[(size_t)t * k + j];
+            if (slot < 0) continue;
             const float wj = w[(size_t)t * k + j];
             float v[8];
             unpack8(*reinterpret_cast<const bf16x8*>(y + (size_t)slot * H + c * 8), v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] += wj * v[i];
         }
-        *reinterpret_cast<bf16x8*>(out + (size_t)t * ldo + c * 8) = pack8(acc);
+        *reinterpret_cast<bf16x8*>(dst_row + c * 8) = pack8(acc);
+    }
+    if (RS) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) rs_publish_arrival(tp, (int)gridDim.x);
     }
 }
 
@@ -145,15 +171,15 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __rest
 using namespace pie;
 
 // logits_fp32: 0 = bf16 logits, 1 = fp32. counts must be zero on entry (pie_moe_align leaves it so).
-PIE_API int pie_moe_route(const void* logits, int logits_fp32, int ld, int n, int E, int k, int renorm, int* ids,
-                          float* w, int* pos, int* counts, cudaStream_t st) {
+PIE_API int pie_moe_route(const void* logits, int logits_fp32, int ld, int n, int E, int k, int renorm, int e_lo,
+                          int e_cnt, int* ids, float* w, int* pos, int* counts, cudaStream_t st) {
     if (n <= 0) return 0;
     if (E > MOE_MAX_E || k > 32 || k > E || k <= 0) return (int)cudaErrorInvalidValue;
     const int threads = 128, blocks = (n * 32 + threads - 1) / threads;
     if (logits_fp32)
-        moe_route_kernel<float><<<blocks, threads, 0, st>>>((const float*)logits, ld, n, E, k, renorm, ids, w, pos, counts);
+        moe_route_kernel<float><<<blocks, threads, 0, st>>>((const float*)logits, ld, n, E, k, renorm, e_lo, e_cnt, ids, w, pos, counts);
     else
-        moe_route_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)logits, ld, n, E, k, renorm, ids, w, pos, counts);
+        moe_route_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)logits, ld, n, E, k, renorm, e_lo, e_cnt, ids, w, pos, counts);
     return (int)cudaGetLastError();
 }
 
@@ -176,6 +202,20 @@ PIE_API int pie_moe_combine(const void* y, const int* slot_of, const float* w, c
                             int H, int k, void* out, int ldo, cudaStream_t st) {
     if (n <= 0) return 0;
     if (H % 8 || ldo % 8 || (residual && ldr % 8)) return (int)cudaErrorInvalidValue;
-    moe_combine_kernel<<<n, 128, 0, st>>>((const bf16*)y, slot_of, w, (const bf16*)residual, ldr, H, k, (bf16*)out, ldo);
+    moe_combine_kernel<false><<<n, 128, 0, st>>>((const bf16*)y, slot_of, w, (const bf16*)residual, ldr, H, k,
+                                                 (bf16*)out, ldo, TpArgs{});
+    return (int)cudaGetLastError();
+}
+
+// Tensor/expert-parallel combine: this rank's partial sum of every token row (its local experts, or
+// its slice of every expert) is stored into the row owner's receive buffer; `tp_blob` is the TpArgs
+// blob of the communicator. The owner then runs pie_tp_reduce_norm_push as after a row-parallel GEMM.
+PIE_API int pie_moe_combine_rs(const void* y, const int* slot_of, const float* w, int n, int H, int k,
+                               const void* tp_blob, int rows_per_rank, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (H % 8 || rows_per_rank <= 0) return (int)cudaErrorInvalidValue;
+    TpArgs tp = *reinterpret_cast<const TpArgs*>(tp_blob);
+    tp.rows_per_rank = rows_per_rank;
+    moe_combine_kernel<true><<<n, 128, 0, st>>>((const bf16*)y, slot_of, w, nullptr, 0, H, k, nullptr, H, tp);
     return (int)cudaGetLastError();
 }

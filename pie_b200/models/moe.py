@@ -63,7 +63,13 @@ def moe_block(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torch.Tensor
     (the reference's scheme) and the partial outputs are summed across ranks."""
     cfg, par = model.cfg, model.par
     if par.tp_size > 1 and par.ep:
-        return par.comm.moe_expert_parallel(model, x, lw, h)
+        # NCCL baseline of expert parallelism: every rank evaluates its own experts on all tokens
+        logits = model._gemm(x, lw["router"]) if x.is_cuda else torch.matmul(x, lw["router"].t())
+        e_local = lw["experts_gate_up"].shape[0]
+        buf = _buffers(model, x.shape[0], lw, x.device)
+        part = ops.moe_experts(x, logits, lw["experts_gate_up"], lw["experts_down"], cfg.num_experts_per_tok,
+                               cfg.norm_topk_prob, buf, e_lo=par.tp_rank * e_local)
+        return h + par.comm.all_reduce(part)
     if x.is_cuda:
         logits = model._gemm(x, lw["router"]) if lw["router"].shape[0] % 8 == 0 \
             else torch.matmul(x, lw["router"].t())
@@ -92,3 +98,20 @@ def moe_block(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torch.Tensor
     out = torch.zeros(n, x.shape[1], dtype=torch.float32, device=x.device)
     out.index_add_(0, tok, ys.float() * wflat[:, None])
     return h + out.to(x.dtype)
+
+
+def moe_block_tp(model, lw: dict, n: int) -> None:
+    """MoE block of the fused tensor-parallel forward. The normalised activations of all n tokens
+    are already on every rank (the all-gather push is the dispatch); each rank routes all tokens,
+    runs its own experts (expert parallelism) or its intermediate-dimension slice of every expert,
+    and scatters its partial output rows to the row owners by peer stores (the combine), where the
+    following reduce+norm kernel sums them with the residual."""
+    cfg, par = model.cfg, model.par
+    comm = par.comm
+    x = comm.wait_gathered(n)
+    logits = model._gemm(x, lw["router"])
+    buf = _buffers(model, n, lw, x.device)
+    e_local = lw["experts_gate_up"].shape[0]
+    e_lo = par.tp_rank * e_local if par.ep else 0
+    ops.moe_experts(x, logits, lw["experts_gate_up"], lw["experts_down"], cfg.num_experts_per_tok,
+                    cfg.norm_topk_prob, buf, e_lo=e_lo, rs=(comm.tp_blob, comm.rows_per_rank(n)))

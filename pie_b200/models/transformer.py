@@ -116,14 +116,18 @@ class Transformer:
             a = self._attention(q, kv_cache[li], fi)
             comm.gemm_rs(a.reshape(n, self.hq * self.d), lw["wo"], n)
             comm.reduce_norm_push(lw["ln2"], cfg.rms_norm_eps, n)
-            act = comm.gemm_gated(lw["w_gate_up"], n, swiglu=True)
-            comm.gemm_rs(act, lw["w_down"], n)
+            if "experts_gate_up" in lw:
+                from .moe import moe_block_tp
+                moe_block_tp(self, lw, n)
+            else:
+                act = comm.gemm_gated(lw["w_gate_up"], n, swiglu=True)
+                comm.gemm_rs(act, lw["w_down"], n)
             nxt = layers[li + 1]["ln1"] if li + 1 < len(layers) else w["final_norm"]
             comm.reduce_norm_push(nxt, cfg.rms_norm_eps, n)
         return comm.wait_gathered(n)
 
     def forward_hidden(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
-        if self._fused_tp() and "experts_gate_up" not in self.w["layers"][0]:
+        if self._fused_tp():
             return self._forward_hidden_tp(fi, kv_cache)
         cfg, w = self.cfg, self.w
         page_size = kv_cache.shape[4]
@@ -154,7 +158,7 @@ class Transformer:
     def logits(self, h: torch.Tensor, fi: ForwardInputs) -> torch.Tensor:
         """lm_head on the requested rows only ('compact logit rows')."""
         rows = h if fi.logit_rows is None else ops.gather_rows(h, fi.logit_rows)
-        if self._fused_tp() and "experts_gate_up" not in self.w["layers"][0]:
+        if self._fused_tp():
             # h is already final-normalised and gathered; every rank computes its vocabulary slice
             local = self.par.comm.gemm_gated(self.w["lm_head"], rows.shape[0], x=rows)
             return self.par.comm.all_gather_logits(local)

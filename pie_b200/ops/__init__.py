@@ -244,11 +244,12 @@ class MoeBuffers:
         self.ys = torch.zeros(rows, hidden, dtype=dtype, device=device)
 
 
-def moe_route(logits, k: int, renorm: bool, buf: "MoeBuffers"):
+def moe_route(logits, k: int, renorm: bool, buf: "MoeBuffers", e_lo: int = 0):
+    """Top-k routing over all experts; only experts [e_lo, e_lo + buf.E) take slots here."""
     n, e = logits.shape
     check(fn("pie_moe_route")(ptr(logits), 1 if logits.dtype == torch.float32 else 0, logits.stride(0), n, e, k,
-                              1 if renorm else 0, ptr(buf.ids), ptr(buf.w), ptr(buf.pos), ptr(buf.counts),
-                              stream_ptr()), "moe_route")
+                              1 if renorm else 0, e_lo, buf.E, ptr(buf.ids), ptr(buf.w), ptr(buf.pos),
+                              ptr(buf.counts), stream_ptr()), "moe_route")
     return buf.ids[:n], buf.w[:n]
 
 
@@ -282,15 +283,24 @@ def moe_combine(buf: "MoeBuffers", n: int, residual=None, out=None):
     return out
 
 
-def moe_experts(x, logits, w_gate_up, w_down, k: int, renorm: bool, buf: "MoeBuffers", residual=None):
-    """residual + sum_j w_j * down_e(swiglu(gate_up_e(x))) over each token's top-k experts e."""
+def moe_experts(x, logits, w_gate_up, w_down, k: int, renorm: bool, buf: "MoeBuffers", residual=None,
+                e_lo: int = 0, rs=None):
+    """residual + sum_j w_j * down_e(swiglu(gate_up_e(x))) over each token's top-k experts e.
+
+    w_gate_up / w_down hold experts [e_lo, e_lo + E_local) (all of them on one GPU). With
+    rs=(tp_blob, rows_per_rank) the partial sums go to the row owners' receive buffers by peer
+    stores instead of `out` (tensor / expert parallelism)."""
     n = x.shape[0]
     mt = moe_max_mtiles(n, k, buf.E)
-    moe_route(logits, k, renorm, buf)
+    moe_route(logits, k, renorm, buf, e_lo)
     moe_align(buf, mt)
     moe_permute(x, buf)
     grouped_gemm(buf.xs, w_gate_up, buf.tile_expert, buf.act, mt, EPI_SWIGLU)
     grouped_gemm(buf.act, w_down, buf.tile_expert, buf.ys, mt, EPI_STORE)
+    if rs is not None:
+        check(fn("pie_moe_combine_rs")(ptr(buf.ys), ptr(buf.slot_of), ptr(buf.w), n, buf.H, k, rs[0], rs[1],
+                                       stream_ptr()), "moe_combine_rs")
+        return None
     return moe_combine(buf, n, residual)
 
 

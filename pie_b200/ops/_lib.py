@@ -40,7 +40,8 @@ _SIGNATURES = {
     "pie_gemm_set_pairs": [i32],
     "pie_gemm_bf16": [p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, i32, p],
     "pie_grouped_gemm_bf16": [p, p, p, p, i32, i32, i32, i32, i32, i32, i32, p, i32, p],
-    "pie_moe_route": [p, i32, i32, i32, i32, i32, i32, p, p, p, p, p],
+    "pie_moe_route": [p, i32, i32, i32, i32, i32, i32, i32, i32, p, p, p, p, p],
+    "pie_moe_combine_rs": [p, p, p, i32, i32, i32, p, i32, p],
     "pie_moe_align": [p, i32, i32, p, p, p, p],
     "pie_moe_permute": [p, i32, p, p, p, i32, i32, i32, p, p, p],
     "pie_moe_combine": [p, p, p, p, i32, i32, i32, i32, p, i32, p],

@@ -24,6 +24,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="fused")
     ap.add_argument("--hidden", type=int, default=512)
+    ap.add_argument("--model", default="dense", choices=["dense", "moe", "moe-ep"],
+                    help="moe: experts sharded on their intermediate dimension; moe-ep: whole experts per rank")
     a = ap.parse_args()
     import torch.distributed as dist
     from ..driver.executor import TorchDriver
@@ -38,11 +40,16 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    cfg = preset("tiny-llama", hidden_size=a.hidden, intermediate_size=1408, num_attention_heads=8,
-                 num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16")
+    if a.model == "dense":
+        cfg = preset("tiny-llama", hidden_size=a.hidden, intermediate_size=1408, num_attention_heads=8,
+                     num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16")
+    else:
+        cfg = preset("tiny-qwen3-moe", hidden_size=a.hidden, num_attention_heads=8, num_key_value_heads=2,
+                     head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16", num_experts=16,
+                     num_experts_per_tok=4, moe_intermediate_size=256)
     comm = TPComm(rank, world, dev, fused=a.backend == "fused")
     drv = TorchDriver(cfg, dev, num_pages=64, page_size=16, max_requests=8, max_tokens=512,
-                      par=ParallelContext(world, rank, comm), seed=0)
+                      par=ParallelContext(world, rank, comm, ep=a.model == "moe-ep"), seed=0)
     comm.attach(drv)
     if rank != 0:
         comm.follower_loop(drv)
@@ -58,7 +65,7 @@ def main():
         pages.append(list(range(nxt, nxt + k)))
         nxt += k
     raw = SamplerSpec(SamplerKind.RAW_LOGITS)
-    report = {"backend": a.backend, "world": world, "checks": []}
+    report = {"backend": a.backend, "model": a.model, "world": world, "checks": []}
 
     def compare(tag, r_tp, r_ref):
         for i, (x, y) in enumerate(zip(r_tp.slots, r_ref.slots)):

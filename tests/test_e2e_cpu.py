@@ -91,3 +91,19 @@ def test_concurrent_inferlets_batch_together():
         assert st["total_requests"] > st["total_batches"]   # batches held more than one request
     finally:
         eng.shutdown()
+
+
+def test_moe_model_matches_dense_oracle():
+    """Qwen3-MoE style model (8 experts, top-2, qk-norm) through the engine on CPU."""
+    cfg = preset("tiny-qwen3-moe")
+    w = random_weights(cfg, "cpu", torch.float32, seed=0)
+    drv = TorchDriver(cfg, device="cpu", weights=w, num_pages=64, page_size=16, max_requests=16, max_tokens=256)
+    eng = Engine(EngineConfig())
+    eng.add_model(cfg.name, drv)
+    install_all(eng)
+    try:
+        prompt = np.random.default_rng(2).integers(0, cfg.vocab_size, 24).tolist()
+        res = eng.run("text-completion", {"prompt_tokens": prompt, "max_tokens": 12, "stop_tokens": []}, timeout=300)
+        assert json.loads(res)["tokens"] == oracle_greedy(cfg, w, prompt, 12)
+    finally:
+        eng.shutdown()

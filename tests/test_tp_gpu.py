@@ -12,15 +12,17 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("backend", ["fused", "nccl"])
-def test_tp2_logits_match_single_gpu(backend):
+@pytest.mark.parametrize("backend,model", [("fused", "dense"), ("nccl", "dense"), ("fused", "moe"),
+                                           ("fused", "moe-ep"), ("nccl", "moe-ep")])
+def test_tp2_logits_match_single_gpu(backend, model):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
-    port = 29511 + (0 if backend == "fused" else 1)
+    port = 29511 + ["dense", "moe", "moe-ep"].index(model) * 2 + (backend == "nccl")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), "-m", "pie_b200.parallel.tp_check", "--backend", backend]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+           "127.0.0.1", "--master-port", str(port), "-m", "pie_b200.parallel.tp_check", "--backend", backend,
+           "--model", model]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
     assert out.returncode == 0 and lines, out.stdout[-2000:] + out.stderr[-4000:]
     rep = json.loads(lines[-1])
