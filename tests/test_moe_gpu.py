@@ -68,9 +68,19 @@ def test_moe_block_in_cuda_graph_and_model():
     prompts = [np.random.default_rng(i).integers(0, cfg.vocab_size, 20 + 7 * i).tolist() for i in range(4)]
     sampler = SamplerSpec(SamplerKind.MULTINOMIAL, temperature=0.0)
     pages, first, _ = harness.prefill_contexts(drv, prompts, 8, sampler)
-    wf = {k_: (v.float().cpu() if torch.is_tensor(v) else v) for k_, v in w.items()} if isinstance(w, dict) else None
+
+    def to_cpu(x):
+        if torch.is_tensor(x):
+            return x.float().cpu()
+        if isinstance(x, dict):
+            return {k_: to_cpu(v) for k_, v in x.items()}
+        if isinstance(x, list):
+            return [to_cpu(v) for v in x]
+        return x
+
+    wf = to_cpu(w)
     for i, p in enumerate(prompts):
-        logits = dense_reference_forward(cfg, w, torch.tensor(p, device=dev))
+        logits = dense_reference_forward(cfg, wf, torch.tensor(p))
         top2 = torch.topk(logits[-1].float(), 2).values
         if (top2[0] - top2[1]) > 0.05:                   # only compare when the oracle is not at a near tie
             assert int(first[i]) == int(torch.argmax(logits[-1])), i
