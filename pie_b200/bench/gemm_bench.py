@@ -11,12 +11,15 @@ import torch
 
 from .. import ops
 
+ITERS = 0
+
 DECODE = [(512, 6144, 4096), (512, 4096, 4096), (512, 28672, 4096), (512, 4096, 14336), (512, 128256, 4096),
           (512, 768, 4096), (512, 4096, 512), (512, 3584, 4096), (512, 4096, 1792), (64, 6144, 4096)]
 PREFILL = [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (16384, 6144, 4096)]
 
 
 def timeit(fn, flush, iters=10):
+    iters = ITERS or iters
     for _ in range(3):
         fn()
     ts = []
@@ -35,10 +38,20 @@ def timeit(fn, flush, iters=10):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="all")
+    ap.add_argument("--m", type=int, default=0, help="override M of every shape (decode batch sweep)")
+    ap.add_argument("--only", default="", help="N,K: run this weight shape only (profiling)")
+    ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     shapes = {"decode": DECODE, "prefill": PREFILL, "all": DECODE + PREFILL}[a.shapes]
+    if a.m:
+        shapes = sorted({(a.m, n, k) for _, n, k in shapes}, key=lambda t: (t[1], t[2]))
+    if a.only:
+        n0, k0 = (int(v) for v in a.only.split(","))
+        shapes = [(m, n, k) for m, n, k in shapes if (n, k) == (n0, k0)][:1] or [(a.m or 512, n0, k0)]
+    global ITERS
+    ITERS = a.iters
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    print(f"{'M':>6} {'N':>7} {'K':>6} | {'cuBLAS us':>10} {'TF':>6} | {'pairs us':>9} {'TF':>6} | {'1-CTA us':>9} {'TF':>6} | max err")
+    print(f"{'M':>6} {'N':>7} {'K':>6} | {'cuBLAS us':>10} {'TF':>6} | {'pairs us':>9} {'TF':>6} | {'1-CTA us':>9} {'TF':>6} | {'W GB/s':>7} | max err")
     for m, n, k in shapes:
         x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
         w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
@@ -52,7 +65,7 @@ def main():
         ops.set_gemm_pairs(True)
         err = (y.float() - torch.matmul(x, w.t()).float()).abs().max().item()
         print(f"{m:6d} {n:7d} {k:6d} | {t_cb*1e3:10.1f} {fl/t_cb/1e9:6.0f} | {t_p*1e3:9.1f} {fl/t_p/1e9:6.0f} | "
-              f"{t_1*1e3:9.1f} {fl/t_1/1e9:6.0f} | {err:.3f}")
+              f"{t_1*1e3:9.1f} {fl/t_1/1e9:6.0f} | {2.0*n*k/min(t_p, t_1)/1e6:7.0f} | {err:.3f}")
         ops.check_kernel_status()
 
 

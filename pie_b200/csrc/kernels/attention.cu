@@ -192,6 +192,8 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_smem = smem_u32(smem);
     const uint32_t warp_smem = q_smem + TILE_BYTES + warp * DEC_STAGES * 2 * TILE_BYTES;
+    pdl_trigger();
+    pdl_wait();
     const long total = (long)(*num_items_ptr) * hkv;
 
     for (long w = blockIdx.x; w < total; w += gridDim.x) {
@@ -316,6 +318,8 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ o_part,
                                           const int* __restrict__ req_item_indptr,
                                           bf16* __restrict__ out, int hq, int hkv, int group) {
     const int req = blockIdx.x, qh = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     const int a = req_item_indptr[req], b = req_item_indptr[req + 1];
     if (b - a <= 1) return;
     const int kvh = qh / group, row = qh - kvh * group;
@@ -545,7 +549,7 @@ PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int
         constexpr int SM = decode_smem_bytes<D>();
         auto kern = paged_decode_attn_kernel<D, G>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
-        kern<<<num_ctas, DEC_WARPS * 32, SM, st>>>(
+        launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
             (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
             item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
             hkv, page_size, scale_log2);
@@ -554,11 +558,11 @@ PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int
     if (err || !run_merge) return err;
     dim3 grid(num_reqs, hq);
     if (head_dim == 128)
-        paged_decode_merge_kernel<128><<<grid, 128, 0, st>>>(o_part, lse_part, req_item_indptr,
-                                                             (bf16*)out, hq, hkv, group);
+        launch_pdl(paged_decode_merge_kernel<128>, grid, dim3(128), 0, st, (const float*)o_part,
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group);
     else
-        paged_decode_merge_kernel<64><<<grid, 64, 0, st>>>(o_part, lse_part, req_item_indptr,
-                                                           (bf16*)out, hq, hkv, group);
+        launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, (const float*)o_part,
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group);
     return (int)cudaGetLastError();
 }
 

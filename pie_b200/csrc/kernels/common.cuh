@@ -23,7 +23,33 @@ enum PieKernelStatus : int {
     PIE_ERR_BOUNDS = 5,        // index outside its table (debug checks)
 };
 
+// Programmatic dependent launch (off unless pie_set_pdl(1)): a kernel launched through
+// pie::launch_pdl may start while its predecessor in the stream is still draining. It must call
+// pdl_wait() before it reads anything the predecessor wrote or writes anything the predecessor
+// may still read; work that touches only constants (weights) may run before that.
+// pdl_trigger() lets the successor's blocks start as soon as resources free up.
+extern int g_pie_pdl;
+
 namespace pie {
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_pie_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;

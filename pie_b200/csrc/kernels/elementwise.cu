@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const bf16* x, const bf16* delta, bf16* residual_out,
                const bf16* __restrict__ w, bf16* out, int hidden, float eps, float w_offset) {
     __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int nvec = hidden >> 3;
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)t * hidden);
@@ -123,6 +125,8 @@ qk_norm_rope_kvwrite_kernel(const bf16* __restrict__ qkv, const int* __restrict_
                             bf16* __restrict__ q_out, bf16* __restrict__ kv_layer, int n_tokens,
                             int hq, int hkv, int page_size, float eps, int qkv_stride) {
     constexpr int EP = D / 64;  // elements per lane per half
+    pdl_trigger();
+    pdl_wait();
     const int heads = hq + 2 * hkv;
     const long gw = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -263,9 +267,8 @@ PIE_API int pie_rmsnorm(const void* x, const void* delta, void* residual_out, co
     const int nvec = hidden / 8;
     const int per = (nvec + 255) / 256;
 #define LAUNCH(MV)                                                                              \
-    rmsnorm_kernel<MV><<<rows, 256, 0, st>>>((const bf16*)x, (const bf16*)delta,                \
-                                             (bf16*)residual_out, (const bf16*)w, (bf16*)out,   \
-                                             hidden, eps, w_offset)
+    launch_pdl(rmsnorm_kernel<MV>, dim3(rows), dim3(256), 0, st, (const bf16*)x, (const bf16*)delta, \
+               (bf16*)residual_out, (const bf16*)w, (bf16*)out, hidden, eps, w_offset)
     if (per <= 1) LAUNCH(1);
     else if (per <= 2) LAUNCH(2);
     else if (per <= 4) LAUNCH(4);
@@ -292,7 +295,7 @@ PIE_API int pie_qk_norm_rope_kvwrite(const void* qkv, const int* positions, cons
     const long warps = (long)n_tokens * (hq + 2 * hkv);
     const int blocks = (int)((warps + 7) / 8);
 #define LAUNCH(D)                                                                               \
-    qk_norm_rope_kvwrite_kernel<D><<<blocks, 256, 0, st>>>(                                     \
+    launch_pdl(qk_norm_rope_kvwrite_kernel<D>, dim3(blocks), dim3(256), 0, st,                  \
         (const bf16*)qkv, positions, slots, inv_freq, (const bf16*)q_norm_w,                    \
         (const bf16*)k_norm_w, (bf16*)q_out, (bf16*)kv_layer, n_tokens, hq, hkv, page_size, eps, \
         qkv_stride)

@@ -248,7 +248,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                         }
                     }
                     epilogue_store_64<EPI>(v0, v1, stage, m_blk * PAIR_M + (int)crank * GEMM_BM + q * 32,
-                                           n_blk * BN + c * 64, M, N, C, ldc, R, ldr, tp);
+                                           n_blk * BN + c * 64, M, N, C, ldc, R, ldr, tp, N);
                 }
             }
             tc_fence_before();

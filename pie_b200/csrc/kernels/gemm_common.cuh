@@ -48,7 +48,16 @@ struct StreamKArgs {
     int* cnt;
     int enabled;
     int dbg;   // pair kernel diagnostics: 1 skip the MMAs, 2 skip the loads, 4 relay instead of direct signalling
+    unsigned long long* trace;   // optional [grid][8] globaltimer stamps of the kernel's phases (profiling aid)
 };
+
+__device__ __forceinline__ void trace_stamp(unsigned long long* trace, int slot) {
+    if (trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        trace[blockIdx.x * 8 + slot] = t;
+    }
+}
 
 struct Segment {
     int tile, kb0, kb1;
@@ -152,11 +161,13 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&v)[32], in
 // chunks XOR-swizzled by row) so that one store instruction of the warp covers 4 rows x 128 B
 // (8 rows x 64 B for SwiGLU) instead of 32 rows x 16 B.
 //   stage : this warp's 4 KB staging tile (shared memory)
+//   n_end : columns at or past n_end are not stored (end of this tile or of the matrix); N itself
+//           stays the row pitch of the reduce-scatter receive buffers
 template <int EPI>
 __device__ __forceinline__ void epilogue_store_64(const uint32_t (&v0)[32], const uint32_t (&v1)[32],
                                                   uint8_t* stage, int row0, int col0, int M, int N,
                                                   bf16* __restrict__ C, int ldc, const bf16* __restrict__ R,
-                                                  int ldr, const TpArgs& tp) {
+                                                  int ldr, const TpArgs& tp, int n_end) {
     const int lane = threadIdx.x & 31;
     auto slot = [&](int r, int c) { return reinterpret_cast<bf16x8*>(stage + r * 128 + ((c ^ (r & 7)) << 4)); };
     if (EPI == EPI_SWIGLU) {
@@ -177,7 +188,7 @@ __device__ __forceinline__ void epilogue_store_64(const uint32_t (&v0)[32], cons
         for (int i = 0; i < 4; ++i) {
             const int r = i * 8 + (lane >> 2), c = lane & 3;
             const int row = row0 + r, oc = oc0 + c * 8;
-            if (row < M && 2 * oc < N) *reinterpret_cast<bf16x8*>(C + (size_t)row * ldc + oc) = *slot(r, c);
+            if (row < M && 2 * oc < n_end) *reinterpret_cast<bf16x8*>(C + (size_t)row * ldc + oc) = *slot(r, c);
         }
         __syncwarp();
         return;
@@ -191,7 +202,7 @@ __device__ __forceinline__ void epilogue_store_64(const uint32_t (&v0)[32], cons
             bf16x8 t;
 #pragma unroll
             for (int e = 0; e < 4; ++e) t.v[e] = __floats2bfloat162_rn(0.f, 0.f);
-            if (row < M && col < N) t = *reinterpret_cast<const bf16x8*>(R + (size_t)row * ldr + col);
+            if (row < M && col < n_end) t = *reinterpret_cast<const bf16x8*>(R + (size_t)row * ldr + col);
             *slot(r, c) = t;
         }
         __syncwarp();
@@ -214,7 +225,7 @@ __device__ __forceinline__ void epilogue_store_64(const uint32_t (&v0)[32], cons
     for (int i = 0; i < 8; ++i) {
         const int r = i * 4 + (lane >> 3), c = lane & 7;
         const int row = row0 + r, col = col0 + c * 8;
-        if (row >= M || col >= N) continue;
+        if (row >= M || col >= n_end) continue;
         bf16* dst;
         if (EPI == EPI_RS) {
             const int owner = row / tp.rows_per_rank;

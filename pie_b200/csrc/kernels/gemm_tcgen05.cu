@@ -14,31 +14,39 @@
 // Replaces the reference's cuBLASLt/cuBLAS dispatch
 // (driver/cuda/src/ops/gemm.cpp:326-415, 607-640) and its separate
 // residual-add / SwiGLU passes (driver/cuda/src/kernels/swiglu.cu:180-260).
+#include <algorithm>
+
 #include "gemm_common.cuh"
 
 namespace pie {
 using namespace sm100;
 
-template <int BN>
+// OCC = CTAs per SM the instantiation is sized for. Two per SM (half the ring each) lets one
+// CTA's prologue, fix-up and epilogue overlap the other's streaming; it pays for skinny problems
+// where those fixed parts are a large share of a CTA's life.
+template <int BN, int OCC = 1>
 struct GemmCfg {
     static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
     static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int STAGES = (BN == 256 ? 4 : (BN == 128 ? 6 : 8)) / OCC;
     static constexpr uint32_t TMEM_COLS = 2 * BN;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 16384 /*epilogue staging*/;
 };
 
+// BN is the widest tile the instantiation has room for (ring slots, TMEM columns); the launch
+// picks the actual width bn <= BN, a multiple of 16, so that the tile count fills the machine's
+// waves; the W tensor map's box has bn rows.
 // GROUPED: mixture-of-experts form. A holds token rows sorted by expert in 128-row tiles,
 // tile_expert[m_tile] names the expert whose weights ([E*N, K] under tma_b) the tile multiplies,
 // or -1 for an unused tile, which every role skips. Whole-tile scheduling only.
-template <int BN, int EPI, bool GROUPED = false>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int BN, int EPI, bool GROUPED = false, int OCC = 1>
+__global__ void __launch_bounds__(GEMM_THREADS, OCC)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  bf16* __restrict__ C, const bf16* __restrict__ R, int M, int N, int K, int ldc,
                  int ldr, int* status, const __grid_constant__ TpArgs tp, const StreamKArgs sk,
-                 const int* __restrict__ tile_expert) {
-    using Cfg = GemmCfg<BN>;
+                 const int* __restrict__ tile_expert, int bn) {
+    using Cfg = GemmCfg<BN, OCC>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
@@ -54,11 +62,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
-    const int tiles_n = (N + BN - 1) / BN;
+    const int tiles_n = (N + bn - 1) / bn;
     const int num_tiles = tiles_m * tiles_n;
+    const uint32_t stage_tx = Cfg::A_BYTES + (uint32_t)bn * (GEMM_BK * 2);
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
 
     if (threadIdx.x == 0) {
+        trace_stamp(sk.trace, 0);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
@@ -78,6 +88,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) trace_stamp(sk.trace, 1);
+    pdl_trigger();
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
@@ -86,42 +98,63 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             tma_prefetch_desc(&tma_b);
             uint32_t it = 0;
             bool ok = true;
-            if (tp.gated) {
-                // all-gather gate: the A operand is complete once every rank's flag reached the epoch
-                const int e = *reinterpret_cast<const volatile int*>(tp.ag_epoch);
-                const long long t0 = clock64();
-                for (int src = 0; src < tp.world && ok; ++src) {
-                    while (*reinterpret_cast<const volatile int*>(tp.ag_flags + src) < e) {
-                        if (*reinterpret_cast<volatile int*>(status) != 0 || clock64() - t0 > 1500000000ll) {
-                            atomicCAS(status, 0, PIE_ERR_WAIT_PEER);
-                            ok = false;
-                            break;
-                        }
-                    }
-                }
-                __threadfence_system();
-                asm volatile("fence.proxy.async;\n" ::: "memory");
-            }
+            // The weight tiles depend on nothing: they stream into the ring at once. The activation
+            // tiles wait for the producing kernel (grid dependency) and, under tensor parallelism,
+            // for every rank's push of the gathered activation; their loads are parked meanwhile.
+            bool dep_ready = false;
+            int pending = 0;
+            int q_kb[STAGES], q_row[STAGES], q_stage[STAGES];
+            auto resolve = [&]() {
+                pdl_wait();
+                if (tp.gated) ok = ag_gate_wait(tp, status);
+                for (int j = 0; j < pending && ok; ++j)
+                    tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES, &tma_a, full_bar(q_stage[j]), q_kb[j] * GEMM_BK,
+                                q_row[j]);
+                pending = 0;
+                dep_ready = true;
+            };
             SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
             Segment seg;
             while (ok && walk.next(seg)) {
                 const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
-                int b_row = n_blk * BN;
+                int b_row = n_blk * bn;
                 if (GROUPED) {
+                    if (!dep_ready) resolve();       // the tile table itself comes from the previous kernel
                     const int e = tile_expert[m_blk];
                     if (e < 0) continue;
                     b_row += e * N;
                 }
-                for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
+                // Whole tiles walk K from a per-tile offset (the sum does not care about the order):
+                // CTAs that run side by side then fetch different activation lines and weight
+                // columns at any instant instead of all hitting the same L2 lines.
+                const int rot = (seg.kb0 == 0 && seg.kb1 == num_kb) ? (int)(((long long)seg.tile * 11) % num_kb) : 0;
+                for (int kbi = seg.kb0; kbi < seg.kb1 && ok; ++kbi, ++it) {
+                    int kb = kbi + rot;
+                    if (kb >= num_kb) kb -= num_kb;
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
+                    if (!dep_ready && it >= (uint32_t)STAGES) resolve();
+                    if (!ok) break;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
                     const uint32_t a_dst = tiles + s * Cfg::STAGE_BYTES;
-                    tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
+                    if (sk.dbg & 6) {   // diagnostics: 2 = no activation loads, 4 = no weight loads, 6 = neither
+                        const uint32_t tx = ((sk.dbg & 2) ? 0u : Cfg::A_BYTES) + ((sk.dbg & 4) ? 0u : (uint32_t)bn * (GEMM_BK * 2));
+                        mbar_arrive_expect_tx(full_bar(s), tx);
+                        if (!(sk.dbg & 4)) tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
+                        if (!(sk.dbg & 2)) tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
+                        continue;
+                    }
+                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
                     tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
+                    if (dep_ready) {
+                        tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
+                    } else {
+                        q_kb[pending] = kb; q_row[pending] = m_blk * GEMM_BM; q_stage[pending] = s;
+                        ++pending;
+                    }
                 }
             }
+            if (!dep_ready) resolve();
             // no copy of this CTA may still be in flight when it exits
             const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
             for (uint32_t j = first; j < it; ++j)
@@ -131,11 +164,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN);
+            const uint32_t idesc = make_idesc_bf16(GEMM_BM, bn);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
             Segment seg;
+            if (GROUPED) pdl_wait();
             for (; ok && walk.next(seg); ++tcount) {
                 if (GROUPED && tile_expert[seg.tile % tiles_m] < 0) { --tcount; continue; }
                 const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
@@ -146,22 +180,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(full_bar(s), ph, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                    if (it == 0) trace_stamp(sk.trace, 2);
                     tc_fence_after();
                     const uint32_t a_addr = tiles + s * Cfg::STAGE_BYTES;
                     const uint64_t adesc = make_smem_desc_sw128(a_addr);
                     const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
+                    if (!(sk.dbg & 1)) {
 #pragma unroll
-                    for (int k = 0; k < GEMM_BK / 16; ++k)
-                        umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
+                        for (int k = 0; k < GEMM_BK / 16; ++k)
+                            umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
+                    }
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
+            trace_stamp(sk.trace, 3);
         }
     } else {
         // ----------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lanes [32q, 32q+32) belong to this warp
         uint32_t tcount = 0;
+        pdl_wait();   // outputs, residual and the stream-K workspace may still be in use by the previous kernel
         SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, blockIdx.x, gridDim.x);
         Segment seg;
         const long long total_units = (long long)num_tiles * num_kb;
@@ -171,20 +210,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
             const bool got = mbar_wait(tfull_bar(acc), aph, status, PIE_ERR_WAIT_MMA);
             if (!__all_sync(0xffffffffu, got)) break;
+            if (warp == 2 && lane == 0) trace_stamp(sk.trace, tcount == 0 ? 4 : 5);
             tc_fence_after();
             const int row = m_blk * GEMM_BM + q * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             const bool partial = seg.kb0 != 0 || seg.kb1 != num_kb;
-            bool finalise = true;
+            // a 32-row quarter that lies wholly past M has nothing to park, reduce or store
+            const bool rows_valid = m_blk * GEMM_BM + q * 32 < M;
+            bool finalise = rows_valid;
             int c_first = 0, c_last = -1;
-            if (partial) {
+            if (partial && rows_valid) {
                 // park this warp's 32 rows of the partial tile, then count the arrival
                 // workspace layout per (slot, warp): [chunk of 32 columns][float4 j][lane], so that every
                 // store/load instruction of a warp moves 512 contiguous bytes
                 uint4* mine = reinterpret_cast<uint4*>(sk.ws) + (size_t)(blockIdx.x + seg.tile) * (GEMM_BM * BN / 4) +
                               (size_t)q * (32 * BN / 4) + lane;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < (bn + 31) / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32(t_row + c * 32, v);
                     tmem_ld_wait();
@@ -209,7 +251,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             if (finalise) {
                 uint8_t* stage = tiles_ptr + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * 4096;
 #pragma unroll 1
-                for (int c = 0; c < BN / 64; ++c) {
+                for (int c = 0; c < (bn + 63) / 64; ++c) {
                     uint32_t v0[32], v1[32];
                     tmem_ld_32x32(t_row + c * 64, v0);
                     tmem_ld_32x32(t_row + c * 64 + 32, v1);
@@ -234,14 +276,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             }
                         }
                     }
-                    epilogue_store_64<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n_blk * BN + c * 64, M, N, C,
-                                           ldc, R, ldr, tp);
+                    epilogue_store_64<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n_blk * bn + c * 64, M, N, C,
+                                           ldc, R, ldr, tp, min(N, (n_blk + 1) * bn));
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
-            if (EPI == EPI_RS && finalise) {
+            // one arrival per (tile, quarter): the finaliser's for a valid quarter, the owner of the
+            // tile's last k-block for a quarter past M
+            if (EPI == EPI_RS && (rows_valid ? finalise : seg.kb1 == num_kb)) {
                 // publish: this warp's rows of the tile are in the owners' buffers
                 __threadfence_system();
                 __syncwarp();
@@ -259,8 +303,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
         }
     }
+    if (warp == 2 && lane == 0) trace_stamp(sk.trace, 6);
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) trace_stamp(sk.trace, 7);
     if (warp == 1) {
         __syncwarp();  // lane 0 ran the MMA loop alone: reconverge before the aligned dealloc
         tc_fence_after();
@@ -324,6 +370,21 @@ PIE_API int pie_gemm_set_workspace(int device, float* ws, long ws_floats, int* c
     return 0;
 }
 
+// Profiling aid: when set, the single-CTA kernel writes 8 globaltimer stamps per CTA
+// (start, set-up done, first tile landed, last MMA issued, first/last accumulator ready,
+// epilogue done, all roles done) into trace[grid][8].
+static unsigned long long* g_gemm_trace = nullptr;
+static int g_gemm_dbg = 0;
+// Diagnostics of the single-CTA kernel (results are then meaningless): 1 skips the MMAs,
+// 2 the activation loads, 4 the weight loads.
+PIE_API int pie_gemm_set_debug(int bits) { g_gemm_dbg = bits; return 0; }
+PIE_API int pie_gemm_set_trace(unsigned long long* trace) { g_gemm_trace = trace; return 0; }
+
+int g_pie_pdl = 0;
+// 1: launch the library's kernels with programmatic stream serialisation, so that a kernel's
+// prologue and weight prefetch overlap the tail of its predecessor.
+PIE_API int pie_set_pdl(int enabled) { g_pie_pdl = enabled; return 0; }
+
 // 0: single-CTA tiles only; 1: CTA pairs (cta_group::2) where the shape allows (default)
 static int g_gemm_pairs = 1;
 PIE_API int pie_gemm_set_pairs(int enabled) { g_gemm_pairs = enabled; return 0; }
@@ -333,37 +394,54 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
                        const TpArgs* tp_in, float* ws, long ws_floats, int* cnt, int cnt_ints, int* handled);
 
 struct GemmPlan {
-    int bn, grid, streamk;
+    int bn;        // tile width of the launch (multiple of 16)
+    int grid, streamk;
+    int bn_t() const { return bn <= 64 ? 64 : (bn <= 128 ? 128 : 256); }   // instantiation that holds it
 };
 
-// Tile width and scheduling. Whole-tile scheduling costs ceil(tiles / SMs) waves of one tile each;
-// stream-K spreads the same k-blocks evenly and pays a fix-up per split tile. Costs are in units
-// of "output columns per CTA" (time is proportional to it for a fixed K).
-static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const GemmWorkspace& w) {
+// Tile width and scheduling from a small analytical model (times in ns).
+//   A tile of width bn costs per 64-deep k-block the slower of its MMAs (128 x bn x 64) and of
+//   filling its ring slot (the activation rows + bn weight rows of 128 B); whole-tile scheduling
+//   runs ceil(tiles / SMs) waves of such tiles, so the width is chosen to make the tile count
+//   fill its waves. The weights also have to come out of HBM once. Stream-K (even split of all
+//   k-blocks, partial tiles fixed up through the workspace) competes when no width fills the waves.
+//   force_bn > 0 fixes the width; allow_sk = false keeps whole-tile scheduling.
+static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const GemmWorkspace& w,
+                          bool allow_sk = true) {
     const int tm = (M + GEMM_BM - 1) / GEMM_BM;
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
-    const int cands[3] = {256, 128, 64};
-    // relative time per column: narrow tiles re-read A more often and amortise pipeline fill worse
-    const double per_col[3] = {1.0, 1.08, 1.25};
+    const double a_rows = M >= GEMM_BM ? 128.0 : (double)M;      // rows of the activation box that carry data
+    const double mma_ns = 1.08, fill_ns = 0.62;                  // per tile column / per 128-byte operand row
+    const double hbm_ns = (double)N * K * 2.0 / 6.0e3;           // all weights once at ~6 TB/s
+    const double launch_ns = 3000.0, wave_ns = 700.0, fixup_ns = 4500.0;
     GemmPlan best{64, 1, 0};
     double best_cost = 1e30;
-    for (int i = 0; i < 3; ++i) {
-        const int bn = cands[i];
-        if (force_bn > 0 ? bn != force_bn : (bn > 64 && N < bn)) continue;
+    for (int bn = 256; bn >= 16; bn -= 16) {
+        if (force_bn > 0 && bn != force_bn) continue;
+        if (force_bn <= 0 && bn > 16 && bn - 16 >= N) continue;  // wider than the matrix: pure waste
+        const int bt = bn <= 64 ? 64 : (bn <= 128 ? 128 : 256);
         const long tiles = (long)tm * ((N + bn - 1) / bn);
+        const double kb_ns = std::max(mma_ns * bn, fill_ns * (a_rows + bn));
+        const double tile_ns = num_kb * kb_ns + wave_ns;
         const long waves = (tiles + num_sms - 1) / num_sms;
-        const double dp = (double)waves * bn * per_col[i];
+        const double active = (double)std::min<long>(tiles, num_sms);
+        // an SM keeps (stages x bn x 128 B) of weights in flight; ~1.6 us to turn them around
+        const int stages = bt == 256 ? 4 : (bt == 128 ? 6 : 8);
+        const double per_sm_gbs = std::min(90.0, stages * bn * 128.0 / 1600.0);
+        const double hbm_eff = std::max(hbm_ns, (double)N * K * 2.0 / (active * per_sm_gbs));
+        const double dp = std::max(waves * tile_ns, hbm_eff) + launch_ns;
         if (dp < best_cost) {
             best_cost = dp;
-            best = GemmPlan{bn, (int)(tiles < num_sms ? tiles : num_sms), 0};
+            best = GemmPlan{bn, (int)std::min<long>(tiles, num_sms), 0};
         }
-        // stream-K candidate
+        if (!allow_sk || !w.ws || (bn != bt)) continue;          // stream-K at the three native widths only
         const long units = tiles * num_kb;
-        long grid = units / 16 < num_sms ? units / 16 : num_sms;   // at least 16 k-blocks per CTA
-        if (grid < 1 || !w.ws || tiles > 2L * num_sms || tiles % grid == 0) continue;
-        if ((grid + tiles) * (long)GEMM_BM * bn > w.ws_floats || tiles * 4 > w.cnt_ints) continue;
-        const double sk = (double)tiles * bn * per_col[i] / grid + 0.12 * bn;
-        if (sk < 0.92 * best_cost) {
+        const long grid = std::min<long>(units / 16, num_sms);   // at least 16 k-blocks per CTA
+        if (grid < 1 || tiles > 2L * num_sms || tiles % grid == 0) continue;
+        if ((grid + tiles) * (long)GEMM_BM * bt > w.ws_floats || tiles * 4 > w.cnt_ints) continue;
+        const double sk_hbm = std::max(hbm_ns, (double)N * K * 2.0 / (grid * per_sm_gbs));
+        const double sk = std::max((double)units / grid * kb_ns, sk_hbm) + fixup_ns + launch_ns;
+        if (sk < best_cost) {
             best_cost = sk;
             best = GemmPlan{bn, (int)grid, 1};
         }
@@ -380,10 +458,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, co
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    StreamKArgs sk{w.ws, w.cnt, plan.streamk, 0};
-    kern<<<plan.grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, (const bf16*)R, M, N, K, ldc,
-                                                           ldr, status, tp, sk, nullptr);
-    return (int)cudaGetLastError();
+    StreamKArgs sk{w.ws, w.cnt, plan.streamk, g_gemm_dbg, g_gemm_trace};
+    e = launch_pdl(kern, dim3(plan.grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, st, ta, tb, (bf16*)C, (const bf16*)R,
+                   M, N, K, ldc, ldr, status, tp, sk, (const int*)nullptr, plan.bn);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 static int current_workspace(GemmWorkspace* out) {
@@ -411,12 +489,14 @@ PIE_API int pie_gemm_bf16(const void* A, const void* W, void* C, const void* R, 
                                           nullptr, w.ws, w.ws_floats, w.cnt, w.cnt_ints, &handled);
         if (handled || rc) return rc;
     }
-    if (force_bn < 0) { w = GemmWorkspace{}; force_bn = -force_bn == 1 ? 0 : -force_bn; }  // negative: whole-tile only
-    const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w);
-    const int bn = plan.bn;
+    bool allow_sk = true;
+    if (force_bn < 0) { allow_sk = false; force_bn = -force_bn == 1 ? 0 : -force_bn; }  // negative: whole-tile only
+    if (force_bn > 256 || force_bn % 16) return (int)cudaErrorInvalidValue;
+    const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w, allow_sk);
+    const int bn = plan.bn_t();
     CUtensorMap ta, tb;
     if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
-    if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, bn) != 0) return (int)cudaErrorInvalidValue;
+    if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, plan.bn) != 0) return (int)cudaErrorInvalidValue;
 #define GO(BN_)                                                                                   \
     switch (epilogue) {                                                                           \
         case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, R, M, N, K, ldc, ldr, status, plan, w, st); \
@@ -469,11 +549,12 @@ PIE_API int pie_gemm_bf16_tp(const void* A, const void* W, void* C, int M, int N
                                           st, &tp, w.ws, w.ws_floats, w.cnt, w.cnt_ints, &handled);
         if (handled || rc) return rc;
     }
+    if (force_bn < 0 || force_bn > 256 || force_bn % 16) return (int)cudaErrorInvalidValue;
     const GemmPlan plan = plan_gemm(M, N, K, num_sms, force_bn, w);
-    const int bn = plan.bn;
+    const int bn = plan.bn_t();
     CUtensorMap ta, tb;
     if (pie_make_tma_2d_bf16(&ta, A, M, K, lda, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
-    if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, bn) != 0) return (int)cudaErrorInvalidValue;
+    if (pie_make_tma_2d_bf16(&tb, W, N, K, ldw, plan.bn) != 0) return (int)cudaErrorInvalidValue;
 #define GO(BN_)                                                                                    \
     switch (epilogue) {                                                                            \
         case EPI_STORE: return launch_gemm<BN_, EPI_STORE>(ta, tb, C, nullptr, M, N, K, ldc, 0, status, plan, w, st, tp);   \
@@ -505,7 +586,7 @@ PIE_API int pie_grouped_gemm_bf16(const void* A, const void* W, void* C, const i
     if (pie_make_tma_2d_bf16(&tb, W, (long)num_experts * N, K, K, bn) != 0) return (int)cudaErrorInvalidValue;
     const long tiles = (long)max_mtiles * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-    StreamKArgs sk{nullptr, nullptr, 0, 0};
+    StreamKArgs sk{nullptr, nullptr, 0, 0, nullptr};
     TpArgs tp{};
 #define GO(BN_, EPI_)                                                                                     \
     {                                                                                                     \
@@ -513,9 +594,9 @@ PIE_API int pie_grouped_gemm_bf16(const void* A, const void* W, void* C, const i
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                              (int)GemmCfg<BN_>::SMEM_BYTES);                              \
         if (e != cudaSuccess) return (int)e;                                                              \
-        kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, st>>>(ta, tb, (bf16*)C, nullptr, M, N, K, ldc, \
-                                                                   0, status, tp, sk, tile_expert);       \
-        return (int)cudaGetLastError();                                                                   \
+        e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN_>::SMEM_BYTES, st, ta, tb, (bf16*)C, \
+                       (const bf16*)nullptr, M, N, K, ldc, 0, status, tp, sk, tile_expert, bn);               \
+        return (int)(e != cudaSuccess ? e : cudaGetLastError());                                          \
     }
     if (epilogue == EPI_STORE) {
         if (bn == 128) GO(128, EPI_STORE) else GO(64, EPI_STORE)

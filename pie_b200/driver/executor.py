@@ -17,6 +17,7 @@ because its length lives in device memory.
 """
 from __future__ import annotations
 
+import threading
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional
@@ -141,6 +142,7 @@ class TorchDriver:
         if self.device.type == "cuda" and self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
         self.cuda = self.device.type == "cuda"
+        self._bound = threading.local()
         self.dtype = torch_dtype(cfg.dtype) if not self.cuda else torch.bfloat16
         self.par = par or ParallelContext()
         if self.cuda:
@@ -203,6 +205,13 @@ class TorchDriver:
         free, total = torch.cuda.mem_get_info(self.device)
         budget = int(total * util) - (total - free) - (6 << 30)  # activations / workspace headroom
         return max(64, budget // per_page)
+
+    def _bind_thread(self) -> None:
+        """The current CUDA device is per thread; the scheduler thread that calls into the driver
+        starts on device 0, so every entry point selects this driver's device first."""
+        if self.device.type == "cuda" and getattr(self._bound, "idx", None) != self.device.index:
+            torch.cuda.set_device(self.device)
+            self._bound.idx = self.device.index
 
     def capabilities(self) -> Capabilities:
         return Capabilities(
@@ -477,6 +486,7 @@ class TorchDriver:
 
     # ------------------------------------------------------------------ public entry points
     def fire_batch(self, req: ForwardRequest) -> ForwardResponse:
+        self._bind_thread()
         t0 = time.perf_counter()
         self.stats["fires"] += 1
         qlens, kv_lens, slots = self._derive(req)
@@ -516,6 +526,7 @@ class TorchDriver:
         previous pipelined step (device to device), so the host never has to wait for one step's
         result before launching the next; it reads each step's tokens one step late.
         """
+        self._bind_thread()
         r = step.r
         ps = self.page_size
         if not self.cuda:
@@ -611,6 +622,7 @@ class TorchDriver:
         """Prepare one pure-decode step without running it: returns device copies of the slab
         contents so that `replay_staged` can run the step with no host work in between.
         Used to time the device path alone (tokens are fed from the previous step's samples)."""
+        self._bind_thread()
         qlens, kv_lens, slots = self._derive(req)
         assert self.cuda and bool((qlens == 1).all())
         s = self.slab
@@ -640,6 +652,7 @@ class TorchDriver:
                 "rb": rb, "r": r, "end": end, "po": po, "npg": npg}
 
     def replay_staged(self, st: dict, feed_sampled: bool) -> None:
+        self._bind_thread()
         s = self.slab
         s.dev[:st["end"]].copy_(st["fixed"], non_blocking=True)
         s.dev[st["po"]:st["po"] + st["npg"]].copy_(st["pages"], non_blocking=True)
@@ -658,6 +671,7 @@ class TorchDriver:
         return self.graphs[rb].launches + 1
 
     def copy(self, req: CopyRequest) -> None:
+        self._bind_thread()
         if self.par.tp_size > 1 and self.par.comm is not None:
             self.par.comm.publish_copy(req)     # every rank holds a shard of each page
         self.kv.copy(req)

@@ -80,3 +80,25 @@ def test_gemm_strided_operands():
     ops.gemm(x, w, out=out[:, n:])
     check(out[:, n:], x.float() @ w.float().t(), k)
     assert float(out[:, :n].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("bn", [16, 48, 80, 112, 176, 208, 240])
+@pytest.mark.parametrize("epi", ["store", "residual", "swiglu"])
+def test_gemm_odd_tile_widths(bn, epi):
+    """Tile widths between the native 64/128/256 (chosen to fill the machine's waves): the last
+    tile of a row is ragged and the SwiGLU epilogue halves the column index."""
+    m, n, k = 200, 2000 if epi != "swiglu" else 2016, 1024
+    x, w = bf(m, k, seed=21), bf(n, k, scale=0.04, seed=22)
+    r = bf(m, n, seed=23) if epi == "residual" else None
+    e = {"store": ops.EPI_STORE, "residual": ops.EPI_RESIDUAL, "swiglu": ops.EPI_SWIGLU}[epi]
+    ops.set_gemm_pairs(False)
+    try:
+        y = ops.gemm(x, w, residual=r, epilogue=e, force_bn=-bn)
+    finally:
+        ops.set_gemm_pairs(True)
+    want = x.float() @ w.float().t()
+    if epi == "residual":
+        want = want + r.float()
+    if epi == "swiglu":
+        want = ref.swiglu_interleaved(want)
+    check(y, want, k)
