@@ -9,7 +9,7 @@ from ._common import load_model, make_sampler, prompt_context
 NAME = "json-schema-validation"
 
 DEFAULT_SCHEMA = {"type": "object",
-                  "properties": {"name": {"type": "string"}, "age": {"type": "integer"},
+                  "properties": {"name": {"type": "string", "maxLength": 24}, "age": {"type": "integer"},
                                  "member": {"type": "boolean"}},
                   "required": ["name", "age", "member"]}
 

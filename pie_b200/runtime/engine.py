@@ -47,6 +47,9 @@ class EngineConfig:
     swap_pages: int = 0
     default_endowment_pages: int = 64
     admission_oversubscription_factor: float = 4.0
+    fs_policy: str = "scratch"               # "scratch": private directory per process | "none"
+    scratch_root: Optional[str] = None
+    network_allow: tuple = ()                # CIDR[:port] rules inferlets may connect to; empty = no network
 
 
 class ModelEntry:

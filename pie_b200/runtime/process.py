@@ -24,6 +24,8 @@ from collections import deque
 from dataclasses import dataclass
 from typing import Any, Callable, Deque, Dict, List, Optional
 
+from .policy import FsPolicy, NetworkPolicy
+
 EVENT_RING = 4096
 current_process: "contextvars.ContextVar[Process]" = contextvars.ContextVar("pie_process")
 
@@ -58,6 +60,18 @@ class Process:
         self.t_end: Optional[float] = None
         self._done_waiters: List[Callable] = []
         self.scratch_dir: Optional[str] = None
+        self.fs_policy: Optional[FsPolicy] = None
+        self.network_policy: Optional[NetworkPolicy] = None
+
+    def scratch(self) -> str:
+        """This process's private directory (created on first use; removed when it ends)."""
+        if self.scratch_dir is None:
+            pol = self.fs_policy or FsPolicy("none")
+            self.scratch_dir = pol.make_scratch(self.id)
+            if self.scratch_dir is None:
+                from .policy import PolicyError
+                raise PolicyError("this process has no filesystem access")
+        return self.scratch_dir
 
     # ------------------------------------------------------------------ events
     def emit(self, event: str, value: str) -> None:
@@ -94,6 +108,8 @@ class Process:
         try:
             async with eng.admission:
                 await eng.admit_process(self)
+                self.fs_policy = FsPolicy(eng.config.fs_policy, eng.config.scratch_root)
+                self.network_policy = NetworkPolicy(list(eng.config.network_allow))
                 result = await self.entry(self.input)
             if result is not None and not isinstance(result, str):
                 result = json.dumps(result)
@@ -108,6 +124,7 @@ class Process:
             self.emit("error", self.error)
         finally:
             current_process.reset(token)
+            FsPolicy.drop_scratch(self.scratch_dir)
             self.finished = True
             self.t_end = time.time()
             eng.release_process(self)

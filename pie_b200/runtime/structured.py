@@ -285,10 +285,10 @@ array ::= "[" ws ( value ( ws "," ws value )* )? ws "]"
 string ::= "\"" char* "\""
 char ::= [^"\\\x00-\x1f] | "\\" ( ["\\/bfnrt] | "u" hex hex hex hex )
 hex ::= [0-9a-fA-F]
-number ::= integer ( "." [0-9]+ )? ( [eE] [+-]? [0-9]+ )?
-integer ::= "-"? ( "0" | [1-9] [0-9]* )
+number ::= integer ( "." [0-9]{1,18} )? ( [eE] [+-]? [0-9]{1,3} )?
+integer ::= "-"? ( "0" | [1-9] [0-9]{0,17} )
 boolean ::= "true" | "false"
-ws ::= [ \t\n]*
+ws ::= [ \t\n]{0,2}
 '''
 
 
@@ -354,6 +354,12 @@ def json_schema_to_ebnf(schema) -> str:
             body = f'"[" ws {item} {rest} ws "]"'
             return new(body if lo > 0 else f'"[" ws ( {item} {rest} )? ws "]"')
         if t == "string":
+            if "maxLength" in s or "minLength" in s:
+                lo, hi = int(s.get("minLength", 0)), s.get("maxLength")
+                return new('"\\"" char{' + f"{lo},{'' if hi is None else int(hi)}" + '} "\\""')
+            if "pattern" in s:
+                sub = regex_to_ebnf(s["pattern"])[len("root ::= "):]
+                return new('"\\"" ( ' + sub + ' ) "\\""')
             return "string"
         if t == "integer":
             return "integer"

@@ -12,9 +12,9 @@ from .core import Context, Forward, GenStep, Generator, Model, Output, ProbeHand
 from .sample import Distribution, Entropy, Logits, Logprob, Logprobs, Sampler
 from .spec import NGramSpeculator, Speculator
 from .grammar import AnyJson, Ebnf, Grammar, GrammarConstraint, JsonSchema, Matcher, Regex
-from . import messaging, runtime, scheduling, session
+from . import io, messaging, runtime, scheduling, session
 
 __all__ = ["Context", "Forward", "GenStep", "Generator", "Model", "Output", "ProbeHandle", "SampleHandle",
            "Tokenizer", "Distribution", "Entropy", "Logits", "Logprob", "Logprobs", "Sampler", "Speculator",
            "NGramSpeculator", "AnyJson", "Ebnf", "Grammar", "GrammarConstraint", "JsonSchema", "Matcher", "Regex",
-           "messaging", "runtime", "scheduling", "session"]
+           "io", "messaging", "runtime", "scheduling", "session"]

@@ -1,0 +1,149 @@
+"""The example inferlets end to end on CPU: tiny Llama through the engine (or the dummy driver
+where the output content does not matter). One test per API feature family."""
+import json
+import threading
+from http.server import BaseHTTPRequestHandler, HTTPServer
+
+import numpy as np
+import pytest
+import torch
+
+from pie_b200.driver.executor import TorchDriver
+from pie_b200.inferlets import install_all
+from pie_b200.models.config import preset
+from pie_b200.models.weights import random_weights
+from pie_b200.runtime.engine import Engine, EngineConfig
+from pie_b200.runtime.tokenizer import ByteTokenizer
+
+
+@pytest.fixture(scope="module")
+def eng():
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=0)
+    drv = TorchDriver(cfg, device="cpu", weights=w, num_pages=256, page_size=16, max_requests=16, max_tokens=512)
+    e = Engine(EngineConfig(network_allow=("127.0.0.1",)))
+    e.add_model("tiny-llama", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
+    install_all(e)
+    yield e
+    e.shutdown()
+
+
+PROMPT = list(range(100, 130))
+
+
+def run(eng, name, args, timeout=300):
+    return eng.run(name, args, timeout=timeout)
+
+
+def test_all_reference_names_registered(eng):
+    want = {"text-completion", "text-completion-bench", "text-completion-spec", "raw-completion", "helloworld",
+            "parallel-generation", "best-of-n", "prefix-tree", "attention-sink", "windowed-attention",
+            "constrained-decoding", "json-schema-validation", "demo-grammar", "sampler-suite", "watermarking",
+            "raw-logits-demo", "demo-messaging", "launch-caller", "launch-callee", "demo-persistent-kv",
+            "demo-parallel-fork", "demo-custom-spec", "empty-forward-test", "output-validation", "demo-filesystem",
+            "image-fetch"}
+    assert want <= set(eng.programs)
+
+
+def test_helloworld_and_raw_completion(eng):
+    assert "Hello from instance" in run(eng, "helloworld", None)
+    assert isinstance(run(eng, "raw-completion", {"prompt": "abc", "max_tokens": 4}), str)
+
+
+def test_parallel_generation_shares_prefix(eng):
+    out = json.loads(run(eng, "parallel-generation", {"prompt_tokens": PROMPT, "n": 3, "max_tokens": 6,
+                                                      "temperature": 0.0}))
+    assert len(out["tokens"]) == 3 and all(len(t) == 6 for t in out["tokens"])
+    assert out["tokens"][0] == out["tokens"][1] == out["tokens"][2]      # greedy forks agree
+    ref = json.loads(run(eng, "text-completion", {"prompt_tokens": PROMPT, "max_tokens": 6, "stop_tokens": []}))
+    assert out["tokens"][0] == ref["tokens"]                               # and match the unforked run
+    assert eng.model_status()["models"]["tiny-llama"]["kv_pages_used"] == 0
+
+
+def test_best_of_n_scores(eng):
+    out = json.loads(run(eng, "best-of-n", {"prompt_tokens": PROMPT, "n": 3, "max_tokens": 5, "temperature": 1.0}))
+    assert len(out["scores"]) == 3 and all(s <= 0 for s in out["scores"])
+    assert out["best_index"] == int(np.argmax(out["scores"]))
+
+
+def test_prefix_tree(eng):
+    out = json.loads(run(eng, "prefix-tree", {"max_tokens": 4}))
+    assert len(out["results"]) == 4 and out["root_committed_pages"] >= 1
+
+
+def test_attention_sink_and_window(eng):
+    a = json.loads(run(eng, "attention-sink", {"prompt_tokens": PROMPT, "sink": 4, "window": 8, "max_tokens": 6}))
+    assert len(a["tokens"]) == 6
+    full = json.loads(run(eng, "attention-sink", {"prompt_tokens": PROMPT, "sink": 4, "window": 10_000, "max_tokens": 6}))
+    ref = json.loads(run(eng, "text-completion", {"prompt_tokens": PROMPT, "max_tokens": 6, "stop_tokens": []}))
+    assert full["tokens"] == ref["tokens"]          # a window that covers everything is plain causal attention
+    w = json.loads(run(eng, "windowed-attention", {"prompt_tokens": PROMPT, "window": 8, "max_tokens": 5}))
+    assert len(w["tokens"]) == 5
+
+
+def test_grammar_inferlets(eng):
+    doc = json.loads(run(eng, "json-schema-validation", {"prompt_tokens": PROMPT, "max_tokens": 300}))
+    assert doc["valid"] and isinstance(doc["value"]["age"], int)
+    expr = run(eng, "demo-grammar", {"prompt_tokens": PROMPT, "max_tokens": 40})
+    assert expr and set(expr) <= set("0123456789+-*/()")
+
+
+def test_speculation_inferlets_match_plain_greedy(eng):
+    ref = json.loads(run(eng, "text-completion", {"prompt_tokens": PROMPT, "max_tokens": 20, "stop_tokens": []}))["tokens"]
+    spec = json.loads(run(eng, "text-completion-spec", {"prompt_tokens": PROMPT, "max_tokens": 20, "stop_tokens": []}))
+    assert spec["tokens"] == ref
+    custom = json.loads(run(eng, "demo-custom-spec", {"prompt_tokens": PROMPT, "max_tokens": 20}))
+    assert custom["tokens"] == ref and custom["passes"] <= 20
+
+
+def test_probes_and_watermark(eng):
+    s = json.loads(run(eng, "sampler-suite", {"prompt_tokens": PROMPT}))
+    assert s["argmax"] == s["logits_argmax"] == s["dist_top5"][0][0]
+    assert s["logprob_argmax"] <= 0 and abs(s["logprobs"][0] - s["logprob_argmax"]) < 1e-4 and s["entropy"] > 0
+    r = json.loads(run(eng, "raw-logits-demo", {"prompt_tokens": PROMPT, "k": 3}))
+    assert r["vocab"] == 32000 and r["top"][0][0] == s["argmax"]
+    wm = json.loads(run(eng, "watermarking", {"prompt_tokens": PROMPT, "max_tokens": 24, "delta": 8.0}))
+    assert wm["z"] > 2.0                                  # strongly biased towards the green list
+
+
+def test_messaging_launch_and_persistent_kv(eng):
+    assert json.loads(run(eng, "demo-messaging", {"count": 3}))["received"] == ["msg-0", "msg-1", "msg-2"]
+    assert json.loads(run(eng, "launch-caller", {"texts": ["a", "bc"]}))["results"] == ["A", "BC"]
+    first = json.loads(run(eng, "demo-persistent-kv", {"name": "t1", "max_tokens": 4}))
+    second = json.loads(run(eng, "demo-persistent-kv", {"name": "t1", "max_tokens": 4}))
+    assert not first["reused"] and second["reused"] and second["tokens"] == first["tokens"]
+    run(eng, "demo-persistent-kv", {"name": "t1", "delete": True})
+    assert eng.model_status()["models"]["tiny-llama"]["kv_pages_used"] == 0
+
+
+def test_fork_validation_and_empty_forward(eng):
+    out = json.loads(run(eng, "demo-parallel-fork", {"max_tokens": 4}))
+    assert len(out) == 3
+    v = json.loads(run(eng, "output-validation", {"prompt_tokens": PROMPT, "pattern": r"(?s).{1,}", "max_tokens": 4}))
+    assert v["ok"] and v["attempts"] == 1
+    assert json.loads(run(eng, "empty-forward-test", None)) == {"slots": 0, "seq_len": 0}
+
+
+def test_filesystem_and_http_policies(eng):
+    fs = json.loads(run(eng, "demo-filesystem", {"text": "xyz"}))
+    assert fs["text"] == "xyz" and fs["blob_len"] == 16 and fs["escape_refused"] and "blob.bin" in fs["files"]
+
+    class H(BaseHTTPRequestHandler):
+        def do_GET(self):
+            self.send_response(200)
+            self.send_header("Content-Type", "image/png")
+            self.end_headers()
+            self.wfile.write(b"\x89PNG fake")
+
+        def log_message(self, *a):
+            pass
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        ok = json.loads(run(eng, "image-fetch", {"url": f"http://127.0.0.1:{srv.server_port}/x.png"}))
+        assert ok["ok"] and ok["status"] == 200 and ok["bytes"] == 9 and ok["content_type"] == "image/png"
+        denied = json.loads(run(eng, "image-fetch", {"url": "http://10.9.9.9:80/"}))
+        assert not denied["ok"] and "denies" in denied["denied"]
+    finally:
+        srv.shutdown()

@@ -1,0 +1,187 @@
+"""Small runtime components: sandbox policies, program manager, telemetry, recurrent-state slot
+pool, memory planner, parity harness, model path resolution."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from pie_b200.runtime.policy import FsPolicy, NetworkPolicy, PolicyError
+from pie_b200.runtime.program import Manifest, ProgramError, ProgramStore, content_hash
+from pie_b200.runtime.rs_cache import RS_FLAG_RESET, RsCache, RsState
+from pie_b200.runtime.telemetry import Telemetry
+
+
+def test_fs_policy_scratch_and_escape(tmp_path):
+    pol = FsPolicy("scratch", str(tmp_path))
+    s = pol.make_scratch("proc-1")
+    assert os.path.isdir(s)
+    assert FsPolicy.resolve(s, "a/b.txt").startswith(s)
+    with pytest.raises(PolicyError):
+        FsPolicy.resolve(s, "../other")
+    with pytest.raises(PolicyError):
+        FsPolicy.resolve(None, "x")
+    FsPolicy.drop_scratch(s)
+    assert not os.path.exists(s)
+    assert FsPolicy("none").make_scratch("p") is None
+
+
+def test_network_policy_cidr_and_ports():
+    pol = NetworkPolicy(["10.0.0.0/8", "192.168.1.5:443", "[2001:db8::]/32:8080"])
+    assert pol.check("10.1.2.3", 80) == ("10.1.2.3", 80)
+    assert pol.check("192.168.1.5", 443)
+    with pytest.raises(PolicyError):
+        pol.check("192.168.1.5", 80)
+    with pytest.raises(PolicyError):
+        pol.check("8.8.8.8", 53)
+    assert pol.check("2001:db8::1", 8080)
+    with pytest.raises(PolicyError):
+        NetworkPolicy([]).check("127.0.0.1", 1)
+    assert NetworkPolicy.allow_all().check("127.0.0.1", 1)
+
+
+MANIFEST = '''
+[package]
+name = "echo-upper"
+version = "1.2.0"
+description = "upper-cases its input"
+
+[parameters]
+text = { type = "string", default = "hi" }
+times = { type = "int", default = 1 }
+'''
+SOURCE = '''
+async def main(args):
+    return (args["text"].upper() + " ") * args["times"]
+'''
+
+
+def test_program_store_install_resolve_and_run(tmp_path):
+    from pie_b200.runtime.engine import Engine, EngineConfig
+    eng = Engine(EngineConfig())
+    try:
+        store = ProgramStore(eng, str(tmp_path))
+        m = Manifest.parse(MANIFEST)
+        h = store.install(SOURCE, m)
+        assert h == content_hash(SOURCE.encode())
+        with pytest.raises(ProgramError):
+            store.install(SOURCE, m, expected_hash="00")
+        assert eng.run("echo-upper", {"times": "2"}, timeout=30) == "HI HI "
+        assert eng.run("echo-upper@1.2.0", {"text": "a"}, timeout=30) == "A "
+        m2 = Manifest.parse(MANIFEST.replace("1.2.0", "1.10.0"))
+        store.install(SOURCE.replace(".upper()", ".lower()"), m2)
+        assert store.latest("echo-upper") == "1.10.0"
+        assert store.resolve("echo-upper", "^1.2.0").version == "1.10.0"
+        assert store.resolve("echo-upper", "2.0.0") is None
+        assert eng.run("echo-upper", {"text": "ABC"}, timeout=30) == "abc "
+        # a fresh store finds both versions in the disk cache
+        eng2 = Engine(EngineConfig())
+        try:
+            assert ProgramStore(eng2, str(tmp_path)).load_cache() == ["echo-upper@1.2.0", "echo-upper@1.10.0"]
+            assert eng2.run("echo-upper", {"text": "Q"}, timeout=30) == "q "
+        finally:
+            eng2.shutdown()
+        dep = Manifest.parse('[package]\nname = "needs"\nversion = "0.1.0"\n[dependencies]\nmissing = "1.0.0"\n')
+        with pytest.raises(ProgramError):
+            store.install(SOURCE, dep)
+    finally:
+        eng.shutdown()
+
+
+def test_manifest_validation():
+    with pytest.raises(ProgramError):
+        Manifest.parse('[package]\nname = "Bad Name"\nversion = "1.0.0"\n')
+    with pytest.raises(ProgramError):
+        Manifest.parse('[package]\nname = "ok"\nversion = "one"\n')
+    with pytest.raises(ProgramError):
+        Manifest.parse('[package]\nname = "ok"\nversion = "1.0.0"\n[surprise]\nx = 1\n')
+    m = Manifest.parse(MANIFEST)
+    assert Manifest.parse(m.to_toml()).parameters == m.parameters
+    with pytest.raises(ProgramError):
+        m.check_input({"times": "many"})
+
+
+def test_telemetry_prometheus_and_spans(tmp_path):
+    path = tmp_path / "spans.jsonl"
+    t = Telemetry("pie", True, str(path))
+    t.incr("fires")
+    t.incr("fires", 2)
+    t.gauge("kv_pages_used", 12)
+    with t.probe("fold"):
+        pass
+    t.record_probe_us("driver_forward", 1500)
+    with t.span("fire_batch", requests=3):
+        pass
+    with pytest.raises(ValueError):
+        with t.span("bad"):
+            raise ValueError("x")
+    text = t.prometheus()
+    assert "pie_fires_total 3" in text and "pie_kv_pages_used 12" in text and "pie_probe_fold_seconds_count 1" in text
+    snap = t.snapshot()
+    assert abs(snap["probes"]["driver_forward"]["mean_us"] - 1500) < 1e-6
+    t.close()
+    spans = [json.loads(l) for l in path.read_text().splitlines()]
+    assert [s["name"] for s in spans] == ["fire_batch", "bad"]
+    assert spans[0]["status"]["code"] == "OK" and spans[1]["status"]["code"] == "ERROR"
+    off = Telemetry(enabled=False)
+    off.incr("x")
+    assert off.prometheus() == "\n"
+
+
+def test_rs_cache_states():
+    assert RsCache(0).state_of(1) == RsState.UNSUPPORTED
+    c = RsCache(2)
+    assert c.acquire(7) == 0 and c.state_of(7) == RsState.EMPTY
+    assert c.flags_for_pass(7) == RS_FLAG_RESET and c.state_of(7) == RsState.RESIDENT
+    assert c.flags_for_pass(7) == 0
+    assert c.fork(7, 8) == (0, 1) and c.state_of(8) == RsState.RESIDENT
+    assert c.acquire(9) is None                     # pool exhausted
+    c.invalidate(8)
+    assert c.flags_for_pass(8) == RS_FLAG_RESET
+    c.release(7)
+    assert c.state_of(7) == RsState.MISSING and c.acquire(9) == 0
+    c.forget(7)
+    assert c.state_of(7) == RsState.EMPTY
+
+
+def test_memory_planner_profiles():
+    from pie_b200.driver.memory_planner import kv_bytes_per_page, plan
+    from pie_b200.models.config import preset
+    cfg = preset("llama-3.1-8b")
+    assert kv_bytes_per_page(cfg, 16) == 32 * 2 * 8 * 16 * 128 * 2
+    free = 160 << 30
+    auto = plan(cfg, free)
+    assert auto.profile == "throughput" and auto.kv_pages * 16 >= 512 * 2048
+    lat = plan(cfg, free, profile="latency")
+    assert lat.max_requests == 64 and lat.kv_pages > auto.kv_pages * 0.9
+    small = plan(cfg, 24 << 30)
+    assert small.profile in ("balanced", "capacity") and small.kv_bytes + small.arena_bytes <= 0.9 * (24 << 30)
+    tp8 = plan(cfg, free, tp=8)
+    assert tp8.kv_pages > 7 * auto.kv_pages
+    with pytest.raises(ValueError):
+        plan(cfg, free, profile="nope")
+
+
+def test_parity_harness_prefill_vs_decode_after_prefill():
+    from pie_b200 import parity
+    toks = list(range(5, 40))
+    a = parity.run("tiny-llama", toks)
+    b = parity.run("tiny-llama", toks, decode_after_prefill=True)
+    rep = parity.compare(a, b)
+    assert rep["cos"] > 0.9999 and rep["argmax_equal"]
+
+
+def test_hf_resolve(tmp_path, monkeypatch):
+    from pie_b200.server.hf import resolve_model
+    snap = tmp_path / "hub" / "models--org--tiny" / "snapshots" / "abc123"
+    snap.mkdir(parents=True)
+    refs = tmp_path / "hub" / "models--org--tiny" / "refs"
+    refs.mkdir()
+    (refs / "main").write_text("abc123")
+    monkeypatch.setenv("HF_HOME", str(tmp_path))
+    monkeypatch.delenv("HF_HUB_CACHE", raising=False)
+    assert resolve_model("org/tiny") == snap
+    assert resolve_model("org/tiny@main") == snap
+    assert resolve_model(str(tmp_path)) == tmp_path
+    with pytest.raises(FileNotFoundError):
+        resolve_model("org/absent")
