@@ -253,6 +253,21 @@ class Engine:
         out["processes"] = len([p for p in self.processes.values() if not p.finished])
         return out
 
+    def metrics_text(self) -> str:
+        """Prometheus exposition of `model_status` plus the telemetry counters and probes."""
+        from . import telemetry
+        st = self.model_status()
+        lines = [f"pie_b200_uptime_seconds {st['uptime_s']:.3f}", f"pie_b200_processes {st['processes']}"]
+        for name, m in st["models"].items():
+            for k, v in m.items():
+                if isinstance(v, bool):
+                    v = int(v)
+                if isinstance(v, (int, float)):
+                    lines.append(f'pie_b200_model_{k}{{model="{name}"}} {v:g}')
+                elif isinstance(v, list) and all(isinstance(x, (int, float)) for x in v):
+                    lines += [f'pie_b200_model_{k}{{model="{name}",bucket="{i}"}} {x:g}' for i, x in enumerate(v)]
+        return "\n".join(lines) + "\n" + telemetry.get().prometheus()
+
     def shutdown(self) -> None:
         self._watchdog_stop.set()
         for p in list(self.processes.values()):

@@ -21,6 +21,7 @@ from typing import Callable, List, Optional, Sequence
 
 import numpy as np
 
+from . import telemetry
 from ..driver.schema import Capabilities, ForwardRequest, ForwardResponse, SamplerSpec, SlotOutput
 
 
@@ -399,6 +400,13 @@ class BatchScheduler:
                 self._deliver(it, e)
             return
         lat = time.perf_counter() - t0
+        tel = telemetry.get()
+        if tel.enabled:
+            tel.incr("fires")
+            tel.incr("forward_tokens", req.num_tokens)
+            tel.record_probe_us("fire_batch", lat * 1e6)
+            for k, v in (getattr(resp, "probes", None) or {}).items():
+                tel.record_probe_us(f"driver_{k}", v)
         st = self.stats
         st["total_batches"] += 1
         st["total_requests"] += len(items)

@@ -1,6 +1,7 @@
 """Daemons: a long-lived inferlet bound to a TCP port; every HTTP request launches the program with
 {"method", "path", "headers", "body", plus the daemon's static input} and its return value is the
-response body (JSON return `{"status", "headers", "body"}` sets those explicitly).
+response body (JSON return `{"status", "headers", "body"}` sets those explicitly). `GET /metrics`
+is answered by the engine itself with its Prometheus exposition.
 Counterpart of runtime/src/daemon.rs:1-90 (wasi:http incoming-handler served with hyper)."""
 from __future__ import annotations
 
@@ -25,6 +26,12 @@ async def start_daemon(engine, program: str, static_input: str, port: int, usern
             headers = {k.strip().lower(): v.strip() for k, v in (l.split(":", 1) for l in lines[1:] if ":" in l)}
             n = int(headers.get("content-length", "0"))
             body = (await reader.readexactly(n)).decode("utf-8", errors="replace") if n else ""
+            if method == "GET" and path == "/metrics":
+                data = engine.metrics_text().encode("utf-8")
+                writer.write(b"HTTP/1.1 200 OK\r\ncontent-type: text/plain; version=0.0.4\r\ncontent-length: "
+                             + str(len(data)).encode() + b"\r\nconnection: close\r\n\r\n" + data)
+                await writer.drain()
+                return
             req = dict(static, method=method, path=path, headers=headers, body=body)
             proc = engine.launch(program, req, username=username, capture_outputs=False)
             ev = asyncio.Event()

@@ -131,7 +131,15 @@ def start_engine(cfg: Config, serve: bool = True, port: Optional[int] = None) ->
                                  request_timeout_secs=rt.request_timeout_secs,
                                  default_token_budget=rt.default_token_budget,
                                  default_endowment_pages=rt.default_endowment_pages,
-                                 admission_oversubscription_factor=rt.admission_oversubscription_factor))
+                                 admission_oversubscription_factor=rt.admission_oversubscription_factor,
+                                 fs_policy="scratch" if rt.allow_fs else "none",
+                                 network_allow=tuple(rt.allow_network)))
+    if cfg.telemetry.enabled:
+        from ..runtime import telemetry
+        log_dir = Path(cfg.telemetry.log_dir).expanduser() if cfg.telemetry.log_dir else None
+        if log_dir:
+            log_dir.mkdir(parents=True, exist_ok=True)
+        telemetry.configure(True, str(log_dir / "spans.jsonl") if log_dir else None, cfg.telemetry.service_name)
     comms = []
     for m in cfg.model:
         drivers, mcfg, tok, comm = build_drivers(m)

@@ -29,6 +29,7 @@ import websockets
 
 from ..runtime.engine import Engine
 from ..runtime.process import ProcessEvent
+from ..runtime.program import Manifest, ProgramError, ProgramStore
 from ..runtime.workflow import WorkflowExecutor
 from .auth import Authenticator
 
@@ -141,15 +142,18 @@ class Session:
         del self.uploads[key]
         if hashlib.sha256(blob).hexdigest() != key:
             return await self.respond(cid, False, "program hash mismatch")
-        manifest = tomllib.loads(up["manifest"]) if up["manifest"] else {}
-        name = manifest.get("package", {}).get("name")
-        if not name:
-            return await self.respond(cid, False, "manifest lacks package.name")
+        try:
+            manifest = Manifest.parse(up["manifest"] or "")
+        except ProgramError as e:
+            return await self.respond(cid, False, str(e))
+        name = manifest.name
         if name in self.engine.programs and not m.get("force_overwrite"):
             return await self.respond(cid, False, f"program {name} exists")
-        load_program_source(self.engine, name, blob.decode("utf-8"), manifest)
+        try:
+            self.server.store.install(blob.decode("utf-8"), manifest)
+        except (ProgramError, SyntaxError) as e:
+            return await self.respond(cid, False, f"install failed: {e}")
         self.server.program_hashes[name] = key
-        self.server.store_program(name, manifest, blob, up["manifest"])
         await self.respond(cid, True, name)
 
     # ---- processes
@@ -285,33 +289,18 @@ class PieServer:
         self._server = None
         self._thread: Optional[threading.Thread] = None
         self._ready = threading.Event()
+        self.store = ProgramStore(engine, str(self.program_dir) if self.program_dir else None)
         self._load_stored_programs()
 
-    # ---- program cache on disk: programs/<name>/<version>.{py,toml}
-    def store_program(self, name, manifest, blob: bytes, manifest_text: str) -> None:
-        if self.program_dir is None:
-            return
-        ver = manifest.get("package", {}).get("version", "0.1.0")
-        d = self.program_dir / name
-        d.mkdir(parents=True, exist_ok=True)
-        (d / f"{ver}.py").write_bytes(blob)
-        (d / f"{ver}.toml").write_text(manifest_text)
-
     def _load_stored_programs(self) -> None:
-        if self.program_dir is None or not self.program_dir.exists():
-            return
-        for d in self.program_dir.iterdir():
-            srcs = sorted(d.glob("*.py"))
-            if not srcs:
-                continue
-            src = srcs[-1]
-            mf = src.with_suffix(".toml")
-            manifest = tomllib.loads(mf.read_text()) if mf.exists() else {}
-            try:
-                load_program_source(self.engine, d.name, src.read_text(), manifest)
-                self.program_hashes[d.name] = hashlib.sha256(src.read_bytes()).hexdigest()
-            except Exception:  # noqa: BLE001 - a broken cached program must not stop the server
-                pass
+        """Programs installed earlier (disk cache programs/<name>/<version>.{py,toml})."""
+        try:
+            for ref in self.store.load_cache():
+                name, _, ver = ref.partition("@")
+                src = self.program_dir / name / f"{ver}.py"
+                self.program_hashes[name] = hashlib.sha256(src.read_bytes()).hexdigest()
+        except Exception:  # noqa: BLE001 - a broken cached program must not stop the server
+            pass
 
     async def _handler(self, ws):
         await Session(self, ws).run()

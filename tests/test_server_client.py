@@ -154,3 +154,26 @@ def test_cli_smoke_run_and_monitor(capsys):
     run_monitor(eng, period=0.01, out=buf, iterations=2)
     assert "kv 0/" in buf.getvalue()
     eng.shutdown()
+
+
+def test_embedded_server_and_client_cli(tmp_path, capsys):
+    from pie_b200.client import cli as client_cli
+    from pie_b200.server.embed import Server
+    toml = (f'[runtime]\nprogram_dir = "{tmp_path}/programs"\n[telemetry]\nenabled = true\n[auth]\nenabled = false\n'
+            '[[model]]\nname = "dummy"\npreset = "tiny-llama"\n[model.driver]\ntype = "dummy"\n')
+    with Server.from_text(toml) as srv:
+        uri = srv.uri
+        assert client_cli.main(["--uri", uri, "ping"]) == 0
+        assert client_cli.main(["--uri", uri, "submit", "helloworld"]) == 0
+        out = capsys.readouterr().out
+        assert "Hello, world!" in out and "Hello from instance" in out
+        src = tmp_path / "main.py"
+        src.write_text("async def main(a):\n    return 'v=' + str((a or {}).get('x'))\n")
+        man = tmp_path / "Pie.toml"
+        man.write_text('[package]\nname = "cli-demo"\nversion = "0.1.0"\n')
+        assert client_cli.main(["--uri", uri, "install", str(src), str(man)]) == 0
+        assert client_cli.main(["--uri", uri, "submit", "cli-demo", "--x", "5"]) == 0
+        assert "v=5" in capsys.readouterr().out
+        assert client_cli.main(["--uri", uri, "status"]) == 0
+        assert '"models"' in capsys.readouterr().out
+        assert "pie_b200_uptime_seconds" in srv.engine.metrics_text()
