@@ -89,6 +89,7 @@ class ForwardRequest:
     context_ids: Optional[np.ndarray] = None       # uint64 [R]
     adapter_ids: Optional[np.ndarray] = None       # int64 [R], -1 = none
     single_token_mode: bool = False                # every request has exactly one input token
+    trimmed_pages: int = 0                         # pages dropped by the runtime's page trim (statistics)
 
     @property
     def num_requests(self) -> int:

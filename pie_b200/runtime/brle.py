@@ -128,6 +128,15 @@ def droppable_pages(rows: Sequence[Sequence[int]], page_size: int, num_pages: in
     return ~vis.reshape(num_pages, page_size).any(axis=1)
 
 
+def remove_pages(runs: Sequence[int], drop: np.ndarray, page_size: int) -> List[int]:
+    """The vector without the positions of the pages flagged in `drop` (page trim re-indexing)."""
+    n = max(length(runs), len(drop) * page_size)
+    bits = decode(runs, n)
+    keep = np.ones(n, dtype=bool)
+    keep[:len(drop) * page_size] = ~np.repeat(np.asarray(drop, dtype=bool), page_size)
+    return encode(bits[keep])
+
+
 try:  # native implementations (csrc/host/brle.hpp) replace the hot entry points when built
     from .._C import pie_host as _native
 

@@ -21,7 +21,7 @@ from typing import Callable, List, Optional, Sequence
 
 import numpy as np
 
-from . import telemetry
+from . import brle, telemetry
 from ..driver.schema import Capabilities, ForwardRequest, ForwardResponse, SamplerSpec, SlotOutput
 
 
@@ -103,8 +103,25 @@ class BatchAccumulator:
         return len(self.items)
 
 
-def fold(items: Sequence[PendingRequest], page_size: int) -> ForwardRequest:
-    """Per-request arrays -> one batched CSR request (no page trim, decode masks elided)."""
+def trim_plan(it: PendingRequest, page_size: int):
+    """Page trim: pages whose KV positions are masked out in every row of the request's attention
+    mask need not travel to the driver. Only pages before the first page that this pass writes
+    qualify. Returns (kept page ids, re-indexed mask rows, number of dropped pages).
+    Counterpart of runtime/src/inference/request.rs:109-229 (TrimPlan)."""
+    first_writable = it.kv_len // page_size
+    if it.masks is None or first_writable == 0:
+        return None
+    drop = brle.droppable_pages(it.masks, page_size, first_writable)
+    nd = int(drop.sum())
+    if nd == 0:
+        return None
+    pages = [p for i, p in enumerate(it.pages) if i >= first_writable or not drop[i]]
+    masks = [brle.remove_pages(m, drop, page_size) for m in it.masks]
+    return pages, masks, nd
+
+
+def fold(items: Sequence[PendingRequest], page_size: int, trim: bool = True) -> ForwardRequest:
+    """Per-request arrays -> one batched CSR request (page trim applied, decode masks elided)."""
     r = len(items)
     qo = np.zeros(r + 1, dtype=np.int32)
     pptr = np.zeros(r + 1, dtype=np.int32)
@@ -118,6 +135,7 @@ def fold(items: Sequence[PendingRequest], page_size: int) -> ForwardRequest:
     ctx_ids = np.zeros(r, dtype=np.uint64)
     adapters = np.full(r, -1, dtype=np.int64)
     single = True
+    trimmed = 0
     for i, it in enumerate(items):
         n = it.n_tokens
         single &= n == 1
@@ -125,15 +143,22 @@ def fold(items: Sequence[PendingRequest], page_size: int) -> ForwardRequest:
         npg = -(-total // page_size)
         if npg > len(it.pages):
             raise ValueError("KV_INVARIANT_VIOLATION: request carries too few pages")
+        it_pages, it_masks = it.pages, it.masks
+        plan = trim_plan(it, page_size) if trim and it.masks is not None else None
+        if plan is not None:
+            it_pages, it_masks, nd = plan
+            trimmed += nd
+            npg -= nd
+            total -= nd * page_size
         tokens.append(np.asarray(it.tokens, dtype=np.int32))
         positions.append(np.asarray(it.positions, dtype=np.int32))
-        pages.append(np.asarray(it.pages[:npg], dtype=np.int32))
+        pages.append(np.asarray(it_pages[:npg], dtype=np.int32))
         qo[i + 1] = qo[i] + n
         pptr[i + 1] = pptr[i] + npg
         last[i] = total % page_size or (page_size if total else 0)
-        if it.masks is not None:
+        if it_masks is not None:
             has_mask[i] = True
-            mask_runs.extend(it.masks)
+            mask_runs.extend(it_masks)
         mask_ptr[i + 1] = len(mask_runs)
         for idx, sp in it.samplers:
             slot_req.append(i)
@@ -153,7 +178,7 @@ def fold(items: Sequence[PendingRequest], page_size: int) -> ForwardRequest:
         logit_masks=logit_masks if any(m is not None for m in logit_masks) else None,
         slot_req=np.asarray(slot_req, dtype=np.int32), slot_row=np.asarray(slot_row, dtype=np.int32),
         slot_samplers=samplers, spec_counts=spec if spec.any() else None, context_ids=ctx_ids,
-        adapter_ids=adapters, single_token_mode=single)
+        adapter_ids=adapters, single_token_mode=single, trimmed_pages=trimmed)
 
 
 # ------------------------------------------------------------------------------ policies
@@ -411,6 +436,7 @@ class BatchScheduler:
         st["total_batches"] += 1
         st["total_requests"] += len(items)
         st["total_tokens"] += req.num_tokens
+        st["trimmed_pages"] = st.get("trimmed_pages", 0) + req.trimmed_pages
         st["last_latency_us"] = lat * 1e6
         st["cum_latency_us"] += lat * 1e6
         st["batch_size_hist"][min(7, max(0, len(items)).bit_length() - 1 if len(items) else 0)] += 1

@@ -147,3 +147,22 @@ def test_filesystem_and_http_policies(eng):
         assert not denied["ok"] and "denies" in denied["denied"]
     finally:
         srv.shutdown()
+
+
+def test_page_trim_drops_masked_pages_and_keeps_tokens(eng):
+    """A sliding window over a long context masks whole pages out; they are dropped from the
+    request and the result equals the untrimmed evaluation."""
+    from pie_b200.runtime import scheduler as sched_mod
+    long_prompt = list(range(200, 330))                     # 130 tokens = 8 pages
+    args = {"prompt_tokens": long_prompt, "sink": 2, "window": 20, "max_tokens": 6}
+    sched = eng.model("tiny-llama").schedulers[0]
+    before = sched.stats.get("trimmed_pages", 0)
+    with_trim = json.loads(run(eng, "attention-sink", args))
+    assert sched.stats.get("trimmed_pages", 0) > before
+    orig = sched_mod.fold
+    try:
+        sched_mod.fold = lambda items, ps, trim=True: orig(items, ps, trim=False)
+        without = json.loads(run(eng, "attention-sink", args))
+    finally:
+        sched_mod.fold = orig
+    assert with_trim["tokens"] == without["tokens"]
