@@ -143,6 +143,8 @@ class TorchDriver:
             self.device = torch.device("cuda", torch.cuda.current_device())
         self.cuda = self.device.type == "cuda"
         self._bound = threading.local()
+        self.adapters: dict = {}
+        self._lora_bindings = None
         self.dtype = torch_dtype(cfg.dtype) if not self.cuda else torch.bfloat16
         self.par = par or ParallelContext()
         if self.cuda:
@@ -205,6 +207,51 @@ class TorchDriver:
         free, total = torch.cuda.mem_get_info(self.device)
         budget = int(total * util) - (total - free) - (6 << 30)  # activations / workspace headroom
         return max(64, budget // per_page)
+
+    # ------------------------------------------------------------------ adapters
+    def create_adapter(self, adapter_id: int, rank: int, alpha: float, seed: int = 0) -> None:
+        from .lora import LoraAdapter
+        if self.par.tp_size > 1:
+            raise NotImplementedError("LoRA adapters are served by single-GPU replicas")
+        self.adapters[adapter_id] = LoraAdapter(self.cfg, rank, alpha, self.device, self.dtype, self.model.hq,
+                                                self.model.hkv, seed)
+
+    def destroy_adapter(self, adapter_id: int) -> None:
+        self.adapters.pop(adapter_id, None)
+
+    def fork_adapter(self, src: int, dst: int) -> None:
+        a = self.adapters[src]
+        self.create_adapter(dst, a.rank, a.alpha)
+        self.adapters[dst].copy_from(a)
+
+    def save_adapter(self, adapter_id: int, path: str) -> None:
+        from safetensors.torch import save_file
+        a = self.adapters[adapter_id]
+        save_file({k: v.detach().float().cpu().contiguous() for k, v in a.tensors().items()}, path,
+                  metadata={"rank": str(a.rank), "alpha": str(a.alpha)})
+
+    def load_adapter(self, adapter_id: int, path: str) -> None:
+        from safetensors import safe_open
+        with safe_open(path, framework="pt", device="cpu") as f:
+            meta = f.metadata() or {}
+            self.create_adapter(adapter_id, int(meta.get("rank", 8)), float(meta.get("alpha", 16.0)))
+            self.adapters[adapter_id].load_tensors({k: f.get_tensor(k) for k in f.keys()})
+
+    def zo_apply(self, adapter_id: int, seed: int, coeff: float) -> None:
+        self.adapters[adapter_id].zo_apply(seed, coeff)
+
+    def _bind_adapters(self, req: ForwardRequest):
+        ids = req.adapter_ids
+        if ids is None or not self.adapters or not (np.asarray(ids) >= 0).any():
+            return None
+        qo = np.asarray(req.qo_indptr)
+        out = []
+        for aid in sorted(set(int(a) for a in ids if a >= 0)):
+            if aid not in self.adapters:
+                raise KeyError(f"unknown adapter {aid}")
+            rows = np.concatenate([np.arange(qo[i], qo[i + 1]) for i in range(len(ids)) if ids[i] == aid])
+            out.append((self.adapters[aid], torch.from_numpy(rows.astype(np.int64)).to(self.device)))
+        return out
 
     def _bind_thread(self) -> None:
         """The current CUDA device is per thread; the scheduler thread that calls into the driver
@@ -390,6 +437,7 @@ class TorchDriver:
                                torch.from_numpy(slots.astype(np.int32)), batch,
                                logit_rows=torch.from_numpy(rows), is_decode=False)
         self.stats["eager"] += 1
+        fi.lora = self._lora_bindings
         hidden = self.model.forward_hidden(fi, self.kv.data)
         if len(rows) == 0:
             return None
@@ -491,7 +539,8 @@ class TorchDriver:
         self.stats["fires"] += 1
         qlens, kv_lens, slots = self._derive(req)
         nslots = len(req.slot_samplers)
-        decode = (req.num_requests > 0 and bool((qlens == 1).all())
+        self._lora_bindings = self._bind_adapters(req)
+        decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None
                   and not (req.has_user_mask is not None and np.any(req.has_user_mask)))
         if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
             # followers must draw the same tokens: fix the per-fire seeds before publishing

@@ -21,6 +21,7 @@ import torch
 
 from .. import ops
 from ..ops import reference
+from ..driver.lora import apply_lora
 from .config import ModelConfig
 
 
@@ -33,6 +34,7 @@ class ForwardInputs:
     attn: object                  # ops.DecodePlan | ops.PrefillPlan | ops.AttnBatch (CPU)
     logit_rows: Optional[torch.Tensor] = None   # int32 rows of the hidden state that need logits
     is_decode: bool = False
+    lora: Optional[list] = None   # [(LoraAdapter, int64 token rows)] for requests bound to an adapter
 
 
 class ParallelContext:
@@ -143,11 +145,15 @@ class Transformer:
             qkv = self._gemm(x, lw["wqkv"])
             if "bqkv" in lw:
                 qkv = qkv + lw["bqkv"]
+            if fi.lora:
+                qkv = apply_lora(fi.lora, li, "qkv", x, qkv)
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, lw.get("q_norm"),
                                          lw.get("k_norm"), kv_cache[li], self.hq, self.hkv, self.d,
                                          page_size, cfg.rms_norm_eps)
-            a = self._attention(q, kv_cache[li], fi)
-            h = self._row_parallel(a.reshape(n, self.hq * self.d), lw["wo"], h)
+            a = self._attention(q, kv_cache[li], fi).reshape(n, self.hq * self.d)
+            h = self._row_parallel(a, lw["wo"], h)
+            if fi.lora:
+                h = apply_lora(fi.lora, li, "o", a, h)
             x = ops.rmsnorm(h, lw["ln2"], cfg.rms_norm_eps)
             if "experts_gate_up" in lw:
                 h = self._moe(x, lw, h)

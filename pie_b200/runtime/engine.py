@@ -49,6 +49,7 @@ class EngineConfig:
     admission_oversubscription_factor: float = 4.0
     fs_policy: str = "scratch"               # "scratch": private directory per process | "none"
     scratch_root: Optional[str] = None
+    adapter_dir: Optional[str] = None        # where named adapters are saved (<name>.safetensors)
     network_allow: tuple = ()                # CIDR[:port] rules inferlets may connect to; empty = no network
 
 
@@ -59,6 +60,7 @@ class ModelEntry:
         self.page_size = self.caps[0].kv_page_size
         self.arch = arch or self.caps[0].arch_name
         self.ctxm: ContextManager = None
+        self.adapters = None          # AdapterService
         self.inference: InferenceService = None
         self.schedulers: List[BatchScheduler] = []
 
@@ -108,6 +110,8 @@ class Engine:
             entry.drivers[driver_idx].copy(req)
 
         entry.ctxm = ContextManager(name, entry.page_size, stores, copy_fn, swap_pages=swap)
+        from .adapter import AdapterService
+        entry.adapters = AdapterService(entry.drivers, self.config.adapter_dir)
         for i, (drv, caps) in enumerate(zip(entry.drivers, entry.caps)):
             sched = BatchScheduler(drv, caps, entry.page_size, self.config.batch_policy,
                                    name=f"pie-sched-{name}-{i}")
@@ -195,6 +199,8 @@ class Engine:
             for cid in list(entry.ctxm.by_owner.get(proc.id, ())):
                 entry.inference.drop_context(cid)
             entry.ctxm.destroy_owner(proc.id)
+            if entry.adapters is not None:
+                entry.adapters.release_owner(proc.id)
 
     def wait(self, proc: Process, timeout: Optional[float] = None) -> str:
         ev = threading.Event()

@@ -11,10 +11,11 @@
 from .core import Context, Forward, GenStep, Generator, Model, Output, ProbeHandle, SampleHandle, Tokenizer
 from .sample import Distribution, Entropy, Logits, Logprob, Logprobs, Sampler
 from .spec import NGramSpeculator, Speculator
+from .adapter import Adapter
 from .grammar import AnyJson, Ebnf, Grammar, GrammarConstraint, JsonSchema, Matcher, Regex
 from . import io, messaging, runtime, scheduling, session
 
 __all__ = ["Context", "Forward", "GenStep", "Generator", "Model", "Output", "ProbeHandle", "SampleHandle",
            "Tokenizer", "Distribution", "Entropy", "Logits", "Logprob", "Logprobs", "Sampler", "Speculator",
-           "NGramSpeculator", "AnyJson", "Ebnf", "Grammar", "GrammarConstraint", "JsonSchema", "Matcher", "Regex",
+           "NGramSpeculator", "Adapter", "AnyJson", "Ebnf", "Grammar", "GrammarConstraint", "JsonSchema", "Matcher", "Regex",
            "io", "messaging", "runtime", "scheduling", "session"]

@@ -427,8 +427,9 @@ class GenStep:
 class Generator:
     """Multi-step decode loop. `async for step in gen: out = await step.execute()`."""
 
-    def __init__(self, ctx: Context, sampler: Sampler, speculator=None):
+    def __init__(self, ctx: Context, sampler: Sampler, speculator=None, adapter=None):
         self.ctx, self.sampler, self.speculator = ctx, sampler, speculator
+        self._adapter = adapter
         self._max: Optional[int] = None
         self._stop: set = set()
         self._constraints: list = []
@@ -456,6 +457,10 @@ class Generator:
         if hasattr(c, "build_constraint"):
             c = c.build_constraint(self.ctx.model)
         self._constraints.append(c)
+        return self
+
+    def adapter(self, a) -> "Generator":
+        self._adapter = a
         return self
 
     def disable_system_speculation(self) -> "Generator":
@@ -486,6 +491,8 @@ class Generator:
         else:
             toks = self._pending
         fwd = Forward(ctx).input(toks)
+        if self._adapter is not None:
+            fwd.adapter(self._adapter)
         n_draft = 0
         if self.speculator is not None and self._pending is not None:
             d_tokens, d_pos = self.speculator.draft()
@@ -525,7 +532,7 @@ class Generator:
     def _offloadable(self) -> bool:
         """Plain generation (token sampler, no constraints, no inferlet-side speculator, nothing
         generated yet) can run inside the runtime's decode cohort instead of stepping here."""
-        return (not self._constraints and self.speculator is None and self._pending is None
+        return (not self._constraints and self.speculator is None and self._pending is None and self._adapter is None
                 and not self._done and self.sampler.spec.is_token and bool(self.ctx._buffer)
                 and self.ctx._entry.inference.cohorts)
 

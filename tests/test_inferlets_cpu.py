@@ -166,3 +166,44 @@ def test_page_trim_drops_masked_pages_and_keeps_tokens(eng):
     finally:
         sched_mod.fold = orig
     assert with_trim["tokens"] == without["tokens"]
+
+
+def test_lora_adapter_identity_effect_save_load(eng, tmp_path):
+    """A fresh adapter (B = 0) changes nothing; a perturbed one changes the logits of only the
+    requests bound to it; save -> load round-trips; ZO steps raise the target's score."""
+    import asyncio
+    from pie_b200.sdk import Adapter, Context, Logits, Model
+    eng.config.adapter_dir = str(tmp_path)
+    eng.model("tiny-llama").adapters.dir = str(tmp_path)
+
+    async def prog(_):
+        model = Model.load()
+        ad = Adapter.create(model, rank=4, alpha=8.0)
+
+        async def logits(adapter):
+            ctx = Context(model)
+            fwd = ctx.forward().input(PROMPT)
+            if adapter is not None:
+                fwd.adapter(adapter)
+            h = fwd.probe(len(PROMPT) - 1, Logits())
+            out = await fwd.execute()
+            ctx.release()
+            return np.frombuffer(out.logits(h), dtype=np.float32).copy()
+
+        base = await logits(None)
+        ident = await logits(ad)
+        ad.zo_init(0.05)
+        ad.zo_perturb(1234, 1.0)
+        moved, untouched = await asyncio.gather(logits(ad), logits(None))      # same batch, one bound
+        ad.save("t-adapter")
+        again = await logits(Adapter.load(model, "t-adapter"))
+        return json.dumps({"ident": float(np.abs(base - ident).max()), "moved": float(np.abs(base - moved).max()),
+                           "untouched": float(np.abs(base - untouched).max()),
+                           "reload": float(np.abs(moved - again).max())})
+
+    eng.register_program("lora-check", prog)
+    r = json.loads(run(eng, "lora-check", None))
+    assert r["ident"] < 1e-6 and r["untouched"] < 1e-5 and r["moved"] > 1e-3 and r["reload"] < 1e-2
+    assert not eng.model("tiny-llama").drivers[0].adapters          # released with the process
+    z = json.loads(run(eng, "marketing-tab3-lora-spec", {"prompt_tokens": PROMPT, "steps": 3, "population": 4}))
+    assert z["score_after"] >= z["score_before"] - 1e-3
