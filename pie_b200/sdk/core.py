@@ -341,6 +341,22 @@ class Context:
         self._buffer.extend(int(t) for t in tokens)
         return self
 
+    def append_image(self, image) -> "Context":
+        """Splice an image's encoder tokens into the context (needs a driver with a vision encoder)."""
+        from . import media
+        media.require(self._model, "image")
+        raise media.MediaUnsupported("image tokens are produced by the driver's encoder")
+
+    def append_audio(self, audio) -> "Context":
+        from . import media
+        media.require(self._model, "audio")
+        raise media.MediaUnsupported("audio tokens are produced by the driver's encoder")
+
+    def append_video(self, video) -> "Context":
+        from . import media
+        media.require(self._model, "video")
+        raise media.MediaUnsupported("video tokens are produced by the driver's encoder")
+
     # ---- page management
     def _reserve_for(self, n_new: int) -> None:
         ctxm, ps = self._entry.ctxm, self.page_size
