@@ -11,6 +11,8 @@
 //   driver/cuda/src/kernels/gather_rows.cu:11   compact rows
 //   driver/cuda/src/swap_pool.cpp               page copies
 //   driver/cuda/src/brle.cpp                    BRLE decode (host in the reference)
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace pie {
@@ -274,6 +276,42 @@ PIE_API int pie_rmsnorm(const void* x, const void* delta, void* residual_out, co
     else if (per <= 4) LAUNCH(4);
     else LAUNCH(8);
 #undef LAUNCH
+    return (int)cudaGetLastError();
+}
+
+// fp8 (e4m3) weights with one fp32 scale per (row, 128 columns): out = bf16(w8 * scale).
+// 16 weights per thread. Replaces driver/cuda/src/kernels/dequant_fp8.cu:41 (per-group expand).
+__global__ void dequant_fp8_rowblock_kernel(const uint8_t* __restrict__ w8, const float* __restrict__ scale,
+                                            bf16* __restrict__ out, int K, long total_vec) {
+    const int vec_per_row = K >> 4;
+    const int kblocks = (K + 127) >> 7;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
+        const long row = i / vec_per_row;
+        const int c = (int)(i - row * vec_per_row) << 4;
+        const float sc = scale[row * kblocks + (c >> 7)];
+        const uint4 raw = *reinterpret_cast<const uint4*>(w8 + row * (long)K + c);
+        const __nv_fp8x2_storage_t* p2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&raw);
+        float f[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(p2[j], __NV_E4M3);
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            f[2 * j] = v.x * sc;
+            f[2 * j + 1] = v.y * sc;
+        }
+        bf16x8* dst = reinterpret_cast<bf16x8*>(out + row * (long)K + c);
+        dst[0] = pack8(f);
+        dst[1] = pack8(f + 8);
+    }
+}
+
+PIE_API int pie_dequant_fp8_rowblock(const void* w8, const float* scale, void* out, long rows, int K,
+                                     cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (K % 16) return (int)cudaErrorInvalidValue;
+    const long total = rows * (K / 16);
+    const int blocks = (int)min((total + 255) / 256, (long)148 * 32);
+    dequant_fp8_rowblock_kernel<<<blocks, 256, 0, st>>>((const uint8_t*)w8, scale, (bf16*)out, K, total);
     return (int)cudaGetLastError();
 }
 

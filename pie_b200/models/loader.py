@@ -51,6 +51,37 @@ def Rows(x, start, count): return Op("rows", {"start": start, "count": count}, [
 def Concat(xs, axis=0): return Op("concat", {"axis": axis}, list(xs))
 def Interleave(a, b): return Op("interleave", {}, [a, b])
 def Stack(xs): return Op("stack", {}, list(xs))
+def ExpandRows(x, factor, like): return Op("expand_rows", {"factor": factor, "like": like}, [x])
+
+
+class QLin:
+    """A linear weight during planning: the weight expression plus, for block-scaled fp8
+    checkpoints, the expression of its per-row scales ([N, K/128], the 128-row block scales
+    expanded to rows). Row and column operations apply to both."""
+
+    def __init__(self, w: Op, s: Optional[Op] = None):
+        self.w, self.s = w, s
+
+    def shard(self, axis, rank, world):
+        if world == 1:
+            return self
+        return QLin(Shard(self.w, axis, rank, world), Shard(self.s, axis, rank, world) if self.s is not None else None)
+
+    def rows(self, start, count):
+        return QLin(Rows(self.w, start, count), Rows(self.s, start, count) if self.s is not None else None)
+
+    @staticmethod
+    def concat(xs):
+        return QLin(Concat([x.w for x in xs], 0), Concat([x.s for x in xs], 0) if xs[0].s is not None else None)
+
+    @staticmethod
+    def interleave(a, b):
+        return QLin(Interleave(a.w, b.w), Interleave(a.s, b.s) if a.s is not None else None)
+
+    def attach(self, att: dict, path: str) -> None:
+        att[path] = self.w
+        if self.s is not None:
+            att[path + "@scale"] = self.s
 
 
 @dataclass
@@ -83,6 +114,13 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
             raise KeyError(f"checkpoint has no tensor {n}")
         return Read(n)
 
+    def lin(n):
+        """Linear weight `n` (+ its block scales when the checkpoint is fp8)."""
+        sc = n + "_scale_inv"
+        if cfg.quantization == "fp8_block" and sc in names:
+            return QLin(w(n), ExpandRows(Read(sc), 128, n))
+        return QLin(w(n))
+
     att["embed"] = w(f"{pre}embed_tokens.weight")
     att["final_norm"] = w(f"{pre}norm.weight")
     head = w("lm_head.weight") if "lm_head.weight" in names else w(f"{pre}embed_tokens.weight")
@@ -91,15 +129,15 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         L, P = f"{pre}layers.{li}.", f"layers.{li}."
         att[P + "ln1"] = w(L + "input_layernorm.weight")
         att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
-        q = Shard(w(L + "self_attn.q_proj.weight"), 0, r, T)
-        k = Rows(w(L + "self_attn.k_proj.weight"), kv0 * d, kvn * d)
-        v = Rows(w(L + "self_attn.v_proj.weight"), kv0 * d, kvn * d)
-        att[P + "wqkv"] = Concat([q, k, v], 0)
+        q = lin(L + "self_attn.q_proj.weight").shard(0, r, T)
+        k = lin(L + "self_attn.k_proj.weight").rows(kv0 * d, kvn * d)
+        v = lin(L + "self_attn.v_proj.weight").rows(kv0 * d, kvn * d)
+        QLin.concat([q, k, v]).attach(att, P + "wqkv")
         if L + "self_attn.q_proj.bias" in names:
             att[P + "bqkv"] = Concat([Shard(w(L + "self_attn.q_proj.bias"), 0, r, T),
                                       Rows(w(L + "self_attn.k_proj.bias"), kv0 * d, kvn * d),
                                       Rows(w(L + "self_attn.v_proj.bias"), kv0 * d, kvn * d)], 0)
-        att[P + "wo"] = Shard(w(L + "self_attn.o_proj.weight"), 1, r, T)
+        lin(L + "self_attn.o_proj.weight").shard(1, r, T).attach(att, P + "wo")
         if L + "self_attn.q_norm.weight" in names:
             att[P + "q_norm"] = w(L + "self_attn.q_norm.weight")
             att[P + "k_norm"] = w(L + "self_attn.k_norm.weight")
@@ -118,9 +156,9 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
             att[P + "experts_gate_up"] = Stack(gus)
             att[P + "experts_down"] = Stack(downs)
         else:
-            att[P + "w_gate_up"] = Interleave(Shard(w(L + "mlp.gate_proj.weight"), 0, r, T),
-                                              Shard(w(L + "mlp.up_proj.weight"), 0, r, T))
-            att[P + "w_down"] = Shard(w(L + "mlp.down_proj.weight"), 1, r, T)
+            QLin.interleave(lin(L + "mlp.gate_proj.weight").shard(0, r, T),
+                            lin(L + "mlp.up_proj.weight").shard(0, r, T)).attach(att, P + "w_gate_up")
+            lin(L + "mlp.down_proj.weight").shard(1, r, T).attach(att, P + "w_down")
     return Program(att, dtype, {"tp_size": T, "tp_rank": r, "ep": ep, "layers": cfg.num_hidden_layers,
                                 "vocab_start": r * (cfg.vocab_size // T) if T > 1 else 0})
 
@@ -172,11 +210,21 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
     if k == "rows":
         return xs[0][op.args["start"]:op.args["start"] + op.args["count"]]
     if k == "concat":
+        if xs[0].dtype == torch.float8_e4m3fn:
+            return torch.cat([x.view(torch.uint8) for x in xs], dim=op.args["axis"]).view(torch.float8_e4m3fn)
         return torch.cat(xs, dim=op.args["axis"])
     if k == "interleave":
-        return torch.stack([xs[0], xs[1]], dim=1).reshape(xs[0].shape[0] * 2, *xs[0].shape[1:])
+        a, b = xs
+        f8 = a.dtype == torch.float8_e4m3fn
+        if f8:
+            a, b = a.view(torch.uint8), b.view(torch.uint8)
+        y = torch.stack([a, b], dim=1).reshape(a.shape[0] * 2, *a.shape[1:])
+        return y.view(torch.float8_e4m3fn) if f8 else y
     if k == "stack":
         return torch.stack(xs, dim=0)
+    if k == "expand_rows":
+        rows = reader.get_slice(op.args["like"]).get_shape()[0]       # ragged last block: cut to the weight's rows
+        return xs[0].float().repeat_interleave(op.args["factor"], dim=0)[:rows]
     raise ValueError(f"unknown op {k}")
 
 
@@ -184,13 +232,28 @@ def execute_program(prog: Program, reader, device="cpu") -> dict:
     """Materialise the runtime weight dict of this rank."""
     dtype = torch_dtype(prog.dtype)
     out = {"layers": [dict() for _ in range(prog.meta["layers"])]}
+    scales = {}
     for path, op in prog.attach.items():
-        t = _eval(op, reader, dtype).to(dtype).contiguous().to(device)
+        t = _eval(op, reader, dtype)
+        if path.endswith("@scale"):
+            scales[path[:-len("@scale")]] = t.float().contiguous().to(device)
+            continue
+        if t.dtype != torch.float8_e4m3fn:
+            t = t.to(dtype)
+        t = t.contiguous().to(device)
         if path.startswith("layers."):
             _, li, key = path.split(".", 2)
             out["layers"][int(li)][key] = t
         else:
             out[path] = t
+    if scales:
+        from ..ops import Fp8Linear
+        for path, sc in scales.items():
+            _, li, key = path.split(".", 2)
+            lw = out["layers"][int(li)]
+            kb = (lw[key].shape[1] + 127) // 128
+            # a column shard of the weight takes the matching columns of the scale grid
+            lw[key] = Fp8Linear(lw[key], sc[:, :kb] if sc.shape[1] >= kb else sc)
     out["lm_head_vocab_start"] = prog.meta.get("vocab_start", 0)
     return out
 

@@ -60,6 +60,11 @@ class Transformer:
 
     # ------------------------------------------------------------------ linear algebra
     def _gemm(self, x, w, residual=None, swiglu=False):
+        if isinstance(w, ops.Fp8Linear):
+            epi = ops.EPI_SWIGLU if swiglu else (ops.EPI_RESIDUAL if residual is not None else ops.EPI_STORE)
+            if self.gemm_backend == "tcgen05" or not x.is_cuda:
+                return ops.gemm_fp8w(x, w, residual=residual, epilogue=epi)
+            w = w.dequant(x.dtype)      # library path: expand, then cuBLAS (the reference's scheme)
         if self.gemm_backend == "tcgen05" and x.dtype == torch.bfloat16:
             epi = ops.EPI_SWIGLU if swiglu else (ops.EPI_RESIDUAL if residual is not None else ops.EPI_STORE)
             return ops.gemm(x, w, residual=residual, epilogue=epi)

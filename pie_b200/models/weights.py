@@ -125,6 +125,12 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             lw["w_gate_up"] = interleave_rows(gate, up).contiguous()
             del gate, up
             lw["w_down"] = shard_cols(gen.normal(H, I), r, T).contiguous()
+        if cfg.quantization == "fp8_block":
+            from ..ops import quantize_fp8_block
+            for key in ("wqkv", "wo", "w_gate_up", "w_down"):
+                if key in lw:
+                    # interleaved gate/up rows come from two 128-row blocks: scale over 64-row pairs
+                    lw[key] = quantize_fp8_block(lw[key].float(), 128)
         w["layers"].append(lw)
     w["final_norm"] = ones(H)
     if cfg.tie_word_embeddings:
@@ -145,7 +151,10 @@ def weights_nbytes(w) -> int:
 
     def visit(x):
         nonlocal total
-        if isinstance(x, torch.Tensor):
+        if hasattr(x, "w8"):
+            visit(x.w8)
+            visit(x.scale)
+        elif isinstance(x, torch.Tensor):
             if x.data_ptr() not in seen:
                 seen.add(x.data_ptr())
                 total += x.numel() * x.element_size()
@@ -158,3 +167,14 @@ def weights_nbytes(w) -> int:
 
     visit(w)
     return total
+
+
+def dequantized(w):
+    """Copy of a weight dict with every fp8 linear expanded to its float values (oracles, export)."""
+    if hasattr(w, "w8"):
+        return w.dequant(torch.float32)
+    if isinstance(w, dict):
+        return {k: dequantized(v) for k, v in w.items()}
+    if isinstance(w, list):
+        return [dequantized(v) for v in w]
+    return w

@@ -222,6 +222,80 @@ def gemm(x, w, residual=None, epilogue: int = EPI_STORE, out=None, force_bn: int
     return out
 
 
+# --------------------------------------------------------------------------- fp8 weights
+FP8_BLOCK = 128
+
+
+class Fp8Linear:
+    """Weight [N, K] in fp8 e4m3 with one fp32 scale per (row, 128 columns). Checkpoints with
+    128 x 128 block scales expand each block's scale to its rows when loaded, which keeps row
+    permutations (interleaved gate/up) exact."""
+
+    def __init__(self, w8: torch.Tensor, scale: torch.Tensor):
+        assert w8.dtype == torch.float8_e4m3fn and scale.dtype == torch.float32
+        assert scale.shape == (w8.shape[0], (w8.shape[1] + FP8_BLOCK - 1) // FP8_BLOCK)
+        self.w8, self.scale = w8.contiguous(), scale.contiguous()
+
+    @property
+    def shape(self):
+        return self.w8.shape
+
+    @property
+    def device(self):
+        return self.w8.device
+
+    def nbytes(self) -> int:
+        return self.w8.numel() + self.scale.numel() * 4
+
+    def dequant(self, dtype=torch.bfloat16, out=None) -> torch.Tensor:
+        return dequant_fp8(self, dtype, out)
+
+
+def quantize_fp8_block(w: torch.Tensor, block_rows: int = FP8_BLOCK) -> "Fp8Linear":
+    """Block-scaled fp8 quantisation (scale = absmax / 448 per block_rows x 128 block)."""
+    n, k = w.shape
+    wf = w.float()
+    kb = (k + FP8_BLOCK - 1) // FP8_BLOCK
+    nb = (n + block_rows - 1) // block_rows
+    pad = torch.zeros(nb * block_rows, kb * FP8_BLOCK, dtype=torch.float32, device=w.device)
+    pad[:n, :k] = wf
+    blocks = pad.view(nb, block_rows, kb, FP8_BLOCK)
+    scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12) / 448.0          # [nb, kb]
+    q = (blocks / scale[:, None, :, None]).view(nb * block_rows, kb * FP8_BLOCK)[:n, :k]
+    row_scale = scale.repeat_interleave(block_rows, dim=0)[:n].contiguous()
+    return Fp8Linear(q.to(torch.float8_e4m3fn), row_scale)
+
+
+_FP8_SCRATCH = {}
+
+
+def dequant_fp8(q: "Fp8Linear", dtype=torch.bfloat16, out=None) -> torch.Tensor:
+    n, k = q.shape
+    if not q.w8.is_cuda:
+        kb = q.scale.shape[1]
+        s = q.scale.repeat_interleave(FP8_BLOCK, dim=1)[:, :k]
+        return (q.w8.float() * s).to(dtype)
+    if out is None:
+        out = torch.empty(n, k, dtype=torch.bfloat16, device=q.device)
+    check(fn("pie_dequant_fp8_rowblock")(ptr(q.w8), ptr(q.scale), ptr(out), n, k, stream_ptr()), "dequant_fp8")
+    return out
+
+
+def gemm_fp8w(x, q: "Fp8Linear", residual=None, epilogue: int = EPI_STORE):
+    """y = x @ dequant(q).T with the usual epilogues. The weight is expanded to bf16 in a scratch
+    buffer that is reused by every call of the same shape (graph-safe: fixed address)."""
+    if not x.is_cuda:
+        w = dequant_fp8(q, x.dtype)
+        y = reference.gemm(x, w, residual if epilogue == EPI_RESIDUAL else None)
+        return reference.swiglu_interleaved(y) if epilogue == EPI_SWIGLU else y
+    key = (q.device.index, tuple(q.shape))
+    buf = _FP8_SCRATCH.get(key)
+    if buf is None:
+        buf = _FP8_SCRATCH[key] = torch.empty(*q.shape, dtype=torch.bfloat16, device=q.device)
+    dequant_fp8(q, out=buf)
+    return gemm(x, buf, residual=residual, epilogue=epilogue)
+
+
 # --------------------------------------------------------------------------- mixture of experts
 MOE_TILE = 128
 

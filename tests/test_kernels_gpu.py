@@ -228,3 +228,29 @@ def test_sample_with_vocab_mask():
     for r in range(0, rows, 2):
         want = int(lg[r].float().cpu().masked_fill(~allowed, float("-inf")).argmax())
         assert int(got[r]) == want
+
+
+def test_fp8_block_dequant_and_gemm():
+    """fp8 weights with per-row x 128-column scales: the dequant kernel equals the PyTorch
+    expansion, and the fp8-weight GEMM (with each epilogue) equals the bf16 GEMM over it."""
+    from pie_b200 import ops
+    from pie_b200.ops import reference as ref
+    torch.manual_seed(5)
+    n, k, m = 1536, 2048, 200
+    w = (torch.randn(n, k, device="cuda") * 0.05)
+    q = ops.quantize_fp8_block(w)
+    assert q.w8.dtype == torch.float8_e4m3fn and q.scale.shape == (n, k // 128)
+    deq = ops.dequant_fp8(q)
+    want = (q.w8.float() * q.scale.repeat_interleave(128, dim=1)).to(torch.bfloat16)
+    assert torch.equal(deq, want)
+    assert (deq.float() - w).abs().max() / w.abs().max() < 0.07
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    r = (torch.randn(m, n, device="cuda") * 0.5).to(torch.bfloat16)
+    full = x.float() @ deq.float().t()
+    y = ops.gemm_fp8w(x, q)
+    assert (y.float() - full).abs().max() < 0.05 * full.abs().max()
+    y = ops.gemm_fp8w(x, q, residual=r, epilogue=ops.EPI_RESIDUAL)
+    assert (y.float() - (full + r.float())).abs().max() < 0.05 * full.abs().max()
+    y = ops.gemm_fp8w(x, q, epilogue=ops.EPI_SWIGLU)
+    assert (y.float() - ref.swiglu_interleaved(full)).abs().max() < 0.05 * full.abs().max()
+    ops.check_kernel_status()
