@@ -1,0 +1,74 @@
+"""The other benchmark configurations (the headline one is bench.py at the repository root),
+on one GPU:
+
+    python -m pie_b200.bench.configs --config 3   # Qwen3-32B block-fp8, 4096-token prompts, 512 out, greedy
+    python -m pie_b200.bench.configs --config 4   # Qwen3-30B-A3B MoE, prompts U[256,1024], 256 out
+    python -m pie_b200.bench.configs --config 5   # agentic fork: 64 agents x 8-way fork x 4 rounds on Llama-3.1-8B
+
+`--requests` / `--agents` scale the concurrency down to what one GPU's memory holds; a scaled run
+prints "valid": false. One JSON line per run, same timing rules as bench.py (device-timed decode
+steps with CUDA events after warm-up, clocks sampled during the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, required=True, choices=[3, 4, 5])
+    ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--agents", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
+    ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (marks the run invalid)")
+    a = ap.parse_args()
+    import torch
+    from . import harness
+    from ..driver.executor import TorchDriver
+    from ..driver.schema import SamplerKind, SamplerSpec
+    from ..inferlets import install_all
+    from ..models.config import preset
+    from ..runtime.engine import Engine, EngineConfig
+
+    spec = {3: dict(model="qwen3-32b-fp8", requests=256, pmin=4096, pmax=4096, out=512,
+                    sampler=SamplerSpec(SamplerKind.MULTINOMIAL, temperature=0.0), sampler_txt="greedy"),
+            4: dict(model="qwen3-30b-a3b", requests=1024, pmin=256, pmax=1024, out=256,
+                    sampler=SamplerSpec(SamplerKind.TOP_P, temperature=1.0, top_p=0.9), sampler_txt="temperature 1.0, top-p 0.9"),
+            5: dict(model="llama-3.1-8b", requests=64, pmin=2048, pmax=2048, out=128,
+                    sampler=SamplerSpec(SamplerKind.TOP_K, temperature=1.0, top_k=50), sampler_txt="top-k 50, seeded")}[a.config]
+    over = {"num_hidden_layers": a.layers} if a.layers else {}
+    cfg = preset(spec["model"], **over)
+    n_req = a.requests or spec["requests"]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    drv = TorchDriver(cfg, dev, page_size=16, max_requests=max(n_req, a.agents * 8 if a.config == 5 else n_req),
+                      max_tokens=16384, gemm_backend=a.gemm)
+    line = {"config": a.config, "model": cfg.name, "n_gpus": 1, "dtype": "bf16" if cfg.quantization is None else "fp8 weights, bf16 activations",
+            "data": "synthetic random-token prompts, random-init weights", "gemm": a.gemm,
+            "valid": not a.layers and (n_req == spec["requests"] if a.config != 5 else a.agents == 64)}
+    clk = harness.ClockSampler(0).start()
+    if a.config == 5:
+        eng = Engine(EngineConfig())
+        eng.add_model(cfg.name, drv)
+        install_all(eng)
+        r = harness.run_agentic_fork(eng, cfg.name, a.agents, 2048, 8, 128, 4, cfg.vocab_size)
+        eng.shutdown()
+        line.update(metric="decode output tokens/s (whole workload, wall clock incl. prefill)", value=r["tokens_per_s"],
+                    agents=a.agents, branches=8, rounds=4, **{k: v for k, v in r.items() if k != "tokens_per_s"})
+    else:
+        prompts = harness.make_prompts(n_req, spec["pmin"], spec["pmax"], cfg.vocab_size, seed=1)
+        t0 = time.time()
+        d = harness.run_pipelined_decode(drv, prompts, spec["out"], spec["sampler"], a.warmup, a.steps)
+        line.update(metric="decode output tokens/s", value=d["tokens_per_s"], ms_per_step=d["ms_per_step"],
+                    requests=n_req, steps=a.steps, warmup=a.warmup, prefill_tokens_per_s=d["prefill_tokens_per_s"],
+                    sampler=spec["sampler_txt"], wall_s=time.time() - t0)
+    line["clocks"] = clk.stop()
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -293,3 +293,25 @@ def run_engine_workload(engine, model_name: str, prompts, out_tokens: int, sampl
             out["window_ms_per_step"] = (span[-1][0] - span[0][0]) / (len(span) - 1) * 1e3
             out["window_requests_per_fire"] = statistics.mean(f[1] for f in span[1:])
     return out
+
+
+def run_agentic_fork(engine, model_name: str, agents: int, prefix_len: int, branches: int, tokens: int, rounds: int,
+                     vocab: int, timeout: float = 3600.0) -> dict:
+    """`agents` agentic-fork inferlets at once (each: shared prefix, `branches`-way fork, `rounds`
+    rounds of `tokens` tokens per branch). Returns whole-workload metrics."""
+    rng = np.random.default_rng(7)
+    args = [{"prefix_tokens": rng.integers(0, vocab, prefix_len).tolist(), "branches": branches, "tokens": tokens,
+             "rounds": rounds, "seed": 1 + i, "top_k": 50, "temperature": 1.0} for i in range(agents)]
+    entry = engine.model(model_name)
+    t0 = time.perf_counter()
+    procs = [engine.launch("agentic-fork", a) for a in args]
+    results = [json.loads(engine.wait(p, timeout)) for p in procs]
+    wall = time.perf_counter() - t0
+    total = sum(r["tokens"] for r in results)
+    st = engine.model_status()["models"][model_name]
+    sched = entry.schedulers[0].stats
+    return {"wall_s": wall, "output_tokens": total, "tokens_per_s": total / wall,
+            "p50_prefill_s": statistics.median(r["prefill_s"] for r in results),
+            "p50_round_s": statistics.median(r["round_ends_s"][-1] / len(r["round_ends_s"]) for r in results),
+            "prefix_pages_per_agent": results[0]["prefix_pages"], "decode_steps": sched.get("decode_steps", 0),
+            "kv_pages_used_after": st["kv_pages_used"]}

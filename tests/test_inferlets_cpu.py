@@ -207,3 +207,10 @@ def test_lora_adapter_identity_effect_save_load(eng, tmp_path):
     assert not eng.model("tiny-llama").drivers[0].adapters          # released with the process
     z = json.loads(run(eng, "marketing-tab3-lora-spec", {"prompt_tokens": PROMPT, "steps": 3, "population": 4}))
     assert z["score_after"] >= z["score_before"] - 1e-3
+
+
+def test_agentic_fork_workload_shares_prefix(eng):
+    from pie_b200.bench import harness
+    r = harness.run_agentic_fork(eng, "tiny-llama", agents=3, prefix_len=50, branches=3, tokens=5, rounds=2, vocab=32000)
+    assert r["output_tokens"] == 3 * 3 * 5 * 2
+    assert r["prefix_pages_per_agent"] == 49 // 16 and r["kv_pages_used_after"] == 0
