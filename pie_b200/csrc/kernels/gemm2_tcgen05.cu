@@ -228,8 +228,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                     tmem_ld_32x32(t_row + c * 64 + 32, v1);
                     tmem_ld_wait();
                     if (partial) {
+                        // every contributor's parked partial (this pair's own included) in pair
+                        // order, so the sum does not depend on which pair arrived last
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v0[j] = v1[j] = 0u;
                         for (int cc = c_first; cc <= c_last; ++cc) {
-                            if (cc == pid) continue;
                             const float4* other = reinterpret_cast<const float4*>(sk.ws) +
                                                   (size_t)(cc + seg.tile) * (PAIR_M * BN / 4) +
                                                   (size_t)((int)crank * 4 + q) * (32 * BN / 4) + (size_t)c * 16 * 32 + lane;

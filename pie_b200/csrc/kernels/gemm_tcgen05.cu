@@ -257,8 +257,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     tmem_ld_32x32(t_row + c * 64 + 32, v1);
                     tmem_ld_wait();
                     if (partial) {
+                        // Sum every contributor's parked partial (this CTA's own included) in CTA
+                        // order: the result does not depend on which CTA happened to arrive last.
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v0[j] = v1[j] = 0u;
                         for (int cc = c_first; cc <= c_last; ++cc) {
-                            if (cc == (int)blockIdx.x) continue;
                             const float4* other = reinterpret_cast<const float4*>(sk.ws) +
                                                   (size_t)(cc + seg.tile) * (GEMM_BM * BN / 4) +
                                                   (size_t)q * (32 * BN / 4) + (size_t)c * 16 * 32 + lane;
@@ -410,7 +413,10 @@ static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const 
                           bool allow_sk = true) {
     const int tm = (M + GEMM_BM - 1) / GEMM_BM;
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
-    const double a_rows = M >= GEMM_BM ? 128.0 : (double)M;      // rows of the activation box that carry data
+    // The plan depends on M only through the number of 128-row tiles: every batch size within a
+    // tile count takes the same tile width and K split, hence the same summation order, so a
+    // request's numbers do not change with the company it is batched with.
+    const double a_rows = 128.0;
     const double mma_ns = 1.08, fill_ns = 0.62;                  // per tile column / per 128-byte operand row
     const double hbm_ns = (double)N * K * 2.0 / 6.0e3;           // all weights once at ~6 TB/s
     const double launch_ns = 3000.0, wave_ns = 700.0, fixup_ns = 4500.0;
