@@ -306,8 +306,11 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
                        int ldw, int ldc, int ldr, int epilogue, int* status, int num_sms, cudaStream_t st,
                        const TpArgs* tp_in, float* ws, long ws_floats, int* cnt, int cnt_ints, int* handled) {
     *handled = 0;
-    // small problems are launch/fix-up bound: the single-CTA kernel's narrower tiles fill the machine better
-    if (M <= GEMM_BM || N < 128 || num_sms < 2 || (double)M * N * K < 1.0e10) return 0;
+    // small problems are launch/fix-up bound: the single-CTA kernel's narrower tiles fill the machine
+    // better. Measured cross-over on B200 (M = 256 / 512 decode shapes): pairs win from 2e10 MACs,
+    // and from 1e10 when K is long (the 14336-deep down projection).
+    const double macs = (double)M * N * K;
+    if (M <= GEMM_BM || N < 128 || num_sms < 2 || macs < 1.0e10 || (macs < 2.0e10 && K < 8192)) return 0;
     const int bn = N >= 256 ? 256 : 128;
     const int pairs_max = num_sms / 2;
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;

@@ -21,15 +21,23 @@
 namespace pie {
 using namespace sm100;
 
+constexpr int GEMM_KSUB = 1;                       // 64-column sub-tiles per ring slot (2 measured no faster)
+constexpr int GEMM_KSTEP = GEMM_BK * GEMM_KSUB;    // K covered by one ring slot
+
 // OCC = CTAs per SM the instantiation is sized for. Two per SM (half the ring each) lets one
 // CTA's prologue, fix-up and epilogue overlap the other's streaming; it pays for skinny problems
 // where those fixed parts are a large share of a CTA's life.
 template <int BN, int OCC = 1>
 struct GemmCfg {
-    static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
-    static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
+    // one ring slot holds KSUB consecutive 64-column sub-tiles of each operand (one swizzle span
+    // each), so a barrier round trip and a commit cover KSUB * 4 MMAs
+    static constexpr int KSUB = GEMM_KSUB;
+    static constexpr uint32_t A_SUB = GEMM_BM * GEMM_BK * 2;
+    static constexpr uint32_t B_SUB = BN * GEMM_BK * 2;
+    static constexpr uint32_t A_BYTES = KSUB * A_SUB;
+    static constexpr uint32_t B_BYTES = KSUB * B_SUB;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256 ? 4 : (BN == 128 ? 6 : 8)) / OCC;
+    static constexpr int STAGES = (BN == 256 ? 4 : (BN == 128 ? 6 : 8)) / OCC / KSUB;
     static constexpr uint32_t TMEM_COLS = 2 * BN;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 16384 /*epilogue staging*/;
 };
@@ -64,8 +72,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
     const int tiles_n = (N + bn - 1) / bn;
     const int num_tiles = tiles_m * tiles_n;
-    const uint32_t stage_tx = Cfg::A_BYTES + (uint32_t)bn * (GEMM_BK * 2);
-    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+    const uint32_t stage_tx = Cfg::A_BYTES + (uint32_t)bn * (GEMM_KSTEP * 2);
+    const int num_kb = (K + GEMM_KSTEP - 1) / GEMM_KSTEP;
 
     if (threadIdx.x == 0) {
         trace_stamp(sk.trace, 0);
@@ -108,8 +116,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 pdl_wait();
                 if (tp.gated) ok = ag_gate_wait(tp, status);
                 for (int j = 0; j < pending && ok; ++j)
-                    tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES, &tma_a, full_bar(q_stage[j]), q_kb[j] * GEMM_BK,
-                                q_row[j]);
+#pragma unroll
+                    for (int u = 0; u < Cfg::KSUB; ++u)
+                        tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES + u * Cfg::A_SUB, &tma_a, full_bar(q_stage[j]),
+                                    q_kb[j] * GEMM_KSTEP + u * GEMM_BK, q_row[j]);
                 pending = 0;
                 dep_ready = true;
             };
@@ -124,13 +134,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (e < 0) continue;
                     b_row += e * N;
                 }
-                // Whole tiles walk K from a per-tile offset (the sum does not care about the order):
-                // CTAs that run side by side then fetch different activation lines and weight
-                // columns at any instant instead of all hitting the same L2 lines.
-                const int rot = (seg.kb0 == 0 && seg.kb1 == num_kb) ? (int)(((long long)seg.tile * 11) % num_kb) : 0;
-                for (int kbi = seg.kb0; kbi < seg.kb1 && ok; ++kbi, ++it) {
-                    int kb = kbi + rot;
-                    if (kb >= num_kb) kb -= num_kb;
+                // Every tile walks K in ascending order: an output element then sees the same
+                // summation order whatever tile shape the plan picked (rotating the start per tile
+                // was measured and did not help).
+                for (int kb = seg.kb0; kb < seg.kb1 && ok; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!dep_ready && it >= (uint32_t)STAGES) resolve();
@@ -138,16 +145,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
                     const uint32_t a_dst = tiles + s * Cfg::STAGE_BYTES;
                     if (sk.dbg & 6) {   // diagnostics: 2 = no activation loads, 4 = no weight loads, 6 = neither
-                        const uint32_t tx = ((sk.dbg & 2) ? 0u : Cfg::A_BYTES) + ((sk.dbg & 4) ? 0u : (uint32_t)bn * (GEMM_BK * 2));
+                        const uint32_t tx = ((sk.dbg & 2) ? 0u : Cfg::A_BYTES) + ((sk.dbg & 4) ? 0u : (uint32_t)bn * (GEMM_KSTEP * 2));
                         mbar_arrive_expect_tx(full_bar(s), tx);
-                        if (!(sk.dbg & 4)) tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
-                        if (!(sk.dbg & 2)) tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
+                        for (int u = 0; u < Cfg::KSUB; ++u) {
+                            if (!(sk.dbg & 4)) tma_load_2d(a_dst + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, b_row);
+                            if (!(sk.dbg & 2)) tma_load_2d(a_dst + u * Cfg::A_SUB, &tma_a, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, m_blk * GEMM_BM);
+                        }
                         continue;
                     }
                     mbar_arrive_expect_tx(full_bar(s), stage_tx);
-                    tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
+#pragma unroll
+                    for (int u = 0; u < Cfg::KSUB; ++u)
+                        tma_load_2d(a_dst + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, b_row);
                     if (dep_ready) {
-                        tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, m_blk * GEMM_BM);
+#pragma unroll
+                        for (int u = 0; u < Cfg::KSUB; ++u)
+                            tma_load_2d(a_dst + u * Cfg::A_SUB, &tma_a, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, m_blk * GEMM_BM);
                     } else {
                         q_kb[pending] = kb; q_row[pending] = m_blk * GEMM_BM; q_stage[pending] = s;
                         ++pending;
@@ -183,12 +196,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (it == 0) trace_stamp(sk.trace, 2);
                     tc_fence_after();
                     const uint32_t a_addr = tiles + s * Cfg::STAGE_BYTES;
-                    const uint64_t adesc = make_smem_desc_sw128(a_addr);
-                    const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
                     if (!(sk.dbg & 1)) {
 #pragma unroll
-                        for (int k = 0; k < GEMM_BK / 16; ++k)
-                            umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
+                        for (int u = 0; u < Cfg::KSUB; ++u) {
+                            const uint64_t adesc = make_smem_desc_sw128(a_addr + u * Cfg::A_SUB);
+                            const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES + u * Cfg::B_SUB);
+#pragma unroll
+                            for (int k = 0; k < GEMM_BK / 16; ++k)
+                                umma_bf16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | u | k) != 0);
+                        }
                     }
                     umma_commit(empty_bar(s));
                 }
@@ -412,7 +428,7 @@ struct GemmPlan {
 static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const GemmWorkspace& w,
                           bool allow_sk = true) {
     const int tm = (M + GEMM_BM - 1) / GEMM_BM;
-    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+    const int num_kb = (K + GEMM_KSTEP - 1) / GEMM_KSTEP;
     // The plan depends on M only through the number of 128-row tiles: every batch size within a
     // tile count takes the same tile width and K split, hence the same summation order, so a
     // request's numbers do not change with the company it is batched with.
@@ -427,22 +443,24 @@ static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const 
         if (force_bn <= 0 && bn > 16 && bn - 16 >= N) continue;  // wider than the matrix: pure waste
         const int bt = bn <= 64 ? 64 : (bn <= 128 ? 128 : 256);
         const long tiles = (long)tm * ((N + bn - 1) / bn);
-        const double kb_ns = std::max(mma_ns * bn, fill_ns * (a_rows + bn));
+        const double kb_ns = GEMM_KSUB * std::max(mma_ns * bn, fill_ns * (a_rows + bn));
         const double tile_ns = num_kb * kb_ns + wave_ns;
         const long waves = (tiles + num_sms - 1) / num_sms;
         const double active = (double)std::min<long>(tiles, num_sms);
         // an SM keeps (stages x bn x 128 B) of weights in flight; ~1.6 us to turn them around
-        const int stages = bt == 256 ? 4 : (bt == 128 ? 6 : 8);
-        const double per_sm_gbs = std::min(90.0, stages * bn * 128.0 / 1600.0);
+        const int stages = (bt == 256 ? 4 : (bt == 128 ? 6 : 8)) / GEMM_KSUB;
+        const double per_sm_gbs = std::min(90.0, stages * bn * 128.0 * GEMM_KSUB / 1600.0);
         const double hbm_eff = std::max(hbm_ns, (double)N * K * 2.0 / (active * per_sm_gbs));
         const double dp = std::max(waves * tile_ns, hbm_eff) + launch_ns;
         if (dp < best_cost) {
             best_cost = dp;
             best = GemmPlan{bn, (int)std::min<long>(tiles, num_sms), 0};
         }
-        if (!allow_sk || !w.ws || (bn != bt)) continue;          // stream-K at the three native widths only
+        // stream-K at the three native widths only, and only over a K long enough to be worth
+        // splitting (short-K problems keep one summation order whatever the batch size)
+        if (!allow_sk || !w.ws || (bn != bt) || K < 2048) continue;
         const long units = tiles * num_kb;
-        const long grid = std::min<long>(units / 16, num_sms);   // at least 16 k-blocks per CTA
+        const long grid = std::min<long>(units * GEMM_KSUB / 16, num_sms);   // at least 1024 of K per CTA
         if (grid < 1 || tiles > 2L * num_sms || tiles % grid == 0) continue;
         if ((grid + tiles) * (long)GEMM_BM * bt > w.ws_floats || tiles * 4 > w.cnt_ints) continue;
         const double sk_hbm = std::max(hbm_ns, (double)N * K * 2.0 / (grid * per_sm_gbs));
@@ -453,6 +471,19 @@ static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const 
         }
     }
     return best;
+}
+
+// The plan the single-CTA kernel would use (introspection, tests): out = {bn, grid, streamk}.
+PIE_API int pie_gemm_plan(int M, int N, int K, int num_sms, int with_workspace, int* out) {
+    GemmWorkspace w{};
+    if (with_workspace) {
+        w.ws = reinterpret_cast<float*>(16);
+        w.ws_floats = 3L * num_sms * 128 * 256;
+        w.cnt_ints = 2 * num_sms * 4;
+    }
+    const GemmPlan p = plan_gemm(M, N, K, num_sms, 0, w);
+    out[0] = p.bn; out[1] = p.grid; out[2] = p.streamk;
+    return 0;
 }
 
 template <int BN, int EPI>
