@@ -6,6 +6,11 @@
 //                        and PUSHES the normalised rows into every rank's full activation
 //                        buffer (the all-gather half), then raises this rank's flag on every peer.
 //  tp_wait_ag            gate for consumers of the gathered activation that are not the GEMM.
+//  tp_allreduce_small    one-shot all-reduce of a small bf16 tensor: every rank stores its data into
+//                        its slot on every peer, raises a flag, waits for the others' flags and sums
+//                        the slots in rank order (replaces ncclAllReduce for sub-MiB sums; the
+//                        reference's P2P all-reduce, driver/cuda/src/custom_all_reduce.cu:137-199,
+//                        is not built for sm_100).
 //
 // Together with the EPI_RS epilogue and the gated loads of gemm_tcgen05.cu this replaces the
 // reference's GEMM + ncclAllReduce + residual_add_rmsnorm sequence
@@ -137,9 +142,106 @@ __global__ void tp_wait_ag_kernel(const int* ag_flags, const int* ag_epoch, int 
     __threadfence_system();
 }
 
+struct TpArArgs {
+    bf16* peer_slots[TPN_MAX_RANKS];   // [2 parities][world][cap] bf16 on every rank
+    int* peer_flags[TPN_MAX_RANKS];    // [world] on every rank (word [src] written by rank src)
+    const int* flags;                  // local flags
+    int* done;                         // local CTA arrival counter
+    int* epoch;                        // local count of all-reduces issued
+    int* status;
+    int world, rank;
+    long cap;                          // elements per slot
+};
+
+// Cooperative across ranks (each GPU runs its own launch); grid <= number of SMs so that every
+// block is resident while it waits. Waits are bounded.
+__global__ void __launch_bounds__(256)
+tp_allreduce_small_kernel(const __grid_constant__ TpArArgs a, const bf16* __restrict__ in, bf16* __restrict__ out,
+                          long n) {
+    __shared__ int s_epoch, s_ok;
+    const long nvec = n >> 3;
+    const int e_next = *reinterpret_cast<volatile int*>(a.epoch) + 1;     // the same in every block until bumped
+    const int par = e_next & 1;
+    // 1. push this rank's data into slot [par][rank] of every rank (own included)
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+        const bf16x8 v = reinterpret_cast<const bf16x8*>(in)[i];
+        for (int p = 0; p < a.world; ++p)
+            reinterpret_cast<bf16x8*>(a.peer_slots[p] + ((size_t)par * a.world + a.rank) * a.cap)[i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // 2. last block of this rank raises the flag on every peer
+        if (atomicAdd(a.done, 1) + 1 == (int)gridDim.x) {
+            *a.done = 0;
+            __threadfence_system();
+            for (int p = 0; p < a.world; ++p) *reinterpret_cast<volatile int*>(a.peer_flags[p] + a.rank) = e_next;
+            *reinterpret_cast<volatile int*>(a.epoch) = e_next;
+        }
+        // 3. wait for every rank's flag
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int src = 0; src < a.world && ok; ++src) {
+            while (*reinterpret_cast<const volatile int*>(a.flags + src) < e_next) {
+                if (*reinterpret_cast<volatile int*>(a.status) != 0 || clock64() - t0 > 1500000000ll) {
+                    atomicCAS(a.status, 0, PIE_ERR_WAIT_PEER);
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+        s_ok = ok;
+        s_epoch = e_next;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    // 4. sum the slots in rank order
+    const bf16* base = a.peer_slots[a.rank] + (size_t)par * a.world * a.cap;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int src = 0; src < a.world; ++src) {
+            float v[8];
+            unpack8(reinterpret_cast<const bf16x8*>(base + (size_t)src * a.cap)[i], v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        reinterpret_cast<bf16x8*>(out)[i] = pack8(acc);
+    }
+}
+
 }  // namespace pie
 
 using namespace pie;
+
+PIE_API int pie_tp_ar_args_size() { return (int)sizeof(TpArArgs); }
+
+PIE_API int pie_tp_fill_ar_args(void* blob, void* const* peer_slots, int* const* peer_flags, const int* flags,
+                                int* done, int* epoch, int* status, int world, int rank, long cap) {
+    if (world > TPN_MAX_RANKS || world < 1) return (int)cudaErrorInvalidValue;
+    TpArArgs a{};
+    for (int i = 0; i < world; ++i) {
+        a.peer_slots[i] = (bf16*)peer_slots[i];
+        a.peer_flags[i] = peer_flags[i];
+    }
+    a.flags = flags; a.done = done; a.epoch = epoch; a.status = status; a.world = world; a.rank = rank; a.cap = cap;
+    *reinterpret_cast<TpArArgs*>(blob) = a;
+    return 0;
+}
+
+// out = sum over ranks of in (n bf16 elements, n % 8 == 0, n <= cap). Every rank must call it the
+// same number of times; `in` may equal `out`.
+PIE_API int pie_tp_allreduce_small(const void* blob, const void* in, void* out, long n, int num_sms, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const TpArArgs a = *reinterpret_cast<const TpArArgs*>(blob);
+    if (n % 8 || n > a.cap) return (int)cudaErrorInvalidValue;
+    long blocks = (n / 8 + 255) / 256;
+    if (blocks > num_sms) blocks = num_sms;
+    tp_allreduce_small_kernel<<<(int)blocks, 256, 0, st>>>(a, (const bf16*)in, (bf16*)out, n);
+    return (int)cudaGetLastError();
+}
 
 PIE_API int pie_tp_norm_args_size() { return (int)sizeof(TpNormArgs); }
 

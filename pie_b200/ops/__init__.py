@@ -281,13 +281,60 @@ def dequant_fp8(q: "Fp8Linear", dtype=torch.bfloat16, out=None) -> torch.Tensor:
     return out
 
 
-def gemm_fp8w(x, q: "Fp8Linear", residual=None, epilogue: int = EPI_STORE):
-    """y = x @ dequant(q).T with the usual epilogues. The weight is expanded to bf16 in a scratch
-    buffer that is reused by every call of the same shape (graph-safe: fixed address)."""
+def quant_act_fp8(x: torch.Tensor):
+    """1 x 128 activation quantisation: (x8 e4m3 [M, K], scales fp32 [M, ceil(K/128)])."""
+    m, k = x.shape
+    kb = (k + FP8_BLOCK - 1) // FP8_BLOCK
+    if not x.is_cuda:
+        pad = torch.zeros(m, kb * FP8_BLOCK, dtype=torch.float32)
+        pad[:, :k] = x.float()
+        blocks = pad.view(m, kb, FP8_BLOCK)
+        sc = blocks.abs().amax(dim=2).clamp_min(1e-12) / 448.0
+        return (blocks / sc[:, :, None]).view(m, -1)[:, :k].to(torch.float8_e4m3fn), sc
+    x8 = torch.empty(m, k, dtype=torch.float8_e4m3fn, device=x.device)
+    sx = torch.empty(m, kb, dtype=torch.float32, device=x.device)
+    check(fn("pie_quant_act_fp8")(ptr(x), x.stride(0), ptr(x8), ptr(sx), m, k, stream_ptr()), "quant_act_fp8")
+    return x8, sx
+
+
+def gemm_fp8_reference(x8, sx, q: "Fp8Linear") -> torch.Tensor:
+    """fp32 evaluation of the block-scaled product (the oracle of the fused kernel)."""
+    k = x8.shape[1]
+    xs = x8.float() * sx.repeat_interleave(FP8_BLOCK, dim=1)[:, :k]
+    ws = q.w8.float() * q.scale.repeat_interleave(FP8_BLOCK, dim=1)[:, :k]
+    return xs @ ws.t()
+
+
+_FP8_MODE = None
+
+
+def fp8_mode() -> str:
+    """"fused": fp8 x fp8 tcgen05 GEMM with block scales folded per 128-deep K block (activations
+    quantised 1 x 128 on the fly); "dequant": expand the weight to bf16 first (the reference's scheme)."""
+    global _FP8_MODE
+    if _FP8_MODE is None:
+        import os
+        _FP8_MODE = os.environ.get("PIE_FP8_MODE", "fused")
+    return _FP8_MODE
+
+
+def gemm_fp8w(x, q: "Fp8Linear", residual=None, epilogue: int = EPI_STORE, mode: Optional[str] = None):
+    """y = x @ W.T for a block-scaled fp8 weight, with the usual epilogues."""
     if not x.is_cuda:
         w = dequant_fp8(q, x.dtype)
         y = reference.gemm(x, w, residual if epilogue == EPI_RESIDUAL else None)
         return reference.swiglu_interleaved(y) if epilogue == EPI_SWIGLU else y
+    mode = mode or fp8_mode()
+    n, k = q.shape
+    if mode == "fused" and k % 16 == 0 and n % 16 == 0:
+        m = x.shape[0]
+        x8, sx = quant_act_fp8(x)
+        out = torch.empty(m, n // 2 if epilogue == EPI_SWIGLU else n, dtype=torch.bfloat16, device=x.device)
+        check(fn("pie_gemm_fp8_blockscaled")(ptr(x8), ptr(sx), ptr(q.w8), ptr(q.scale), ptr(out), ptr(residual), m, n, k,
+                                             out.stride(0), residual.stride(0) if residual is not None else 0,
+                                             epilogue, ptr(kernel_status(x.device)), num_sms(x.device), stream_ptr()),
+              "gemm_fp8_blockscaled")
+        return out
     key = (q.device.index, tuple(q.shape))
     buf = _FP8_SCRATCH.get(key)
     if buf is None:

@@ -27,6 +27,8 @@ _SIGNATURES = {
     "pie_rmsnorm": [p, p, p, p, p, i32, i32, f32, f32, p],
     "pie_swiglu": [p, p, i64, i32, p],
     "pie_dequant_fp8_rowblock": [p, p, p, i64, i32, p],
+    "pie_quant_act_fp8": [p, i32, p, p, i32, i32, p],
+    "pie_gemm_fp8_blockscaled": [p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, p, i32, p],
     "pie_qk_norm_rope_kvwrite": [p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
     "pie_gather_rows": [p, p, p, i32, i32, p],
     "pie_copy_pages": [p, p, p, i32, i32, i64, i64, p],

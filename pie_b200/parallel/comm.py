@@ -130,7 +130,9 @@ class TPComm:
         rows = self.rpr_max * self.world
         nb_act = rows * self.hidden * 2
         self.off_recv, self.off_xfull, self.off_flags = 0, nb_act, 2 * nb_act
-        total = 2 * nb_act + 4096
+        self.ar_cap = 512 * 1024                       # bf16 elements per one-shot all-reduce slot (1 MiB)
+        self.off_ar = 2 * nb_act + 4096
+        total = self.off_ar + 2 * self.world * self.ar_cap * 2
         self.sym = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.sym.zero_()
         torch.cuda.synchronize(self.device)
@@ -160,6 +162,17 @@ class TPComm:
         check(filln(self.norm_blob, self.local_base + self.off_recv, rs_flags[self.rank], lc + 4,
                     arr_p(*[b + self.off_xfull for b in base]), arr_p(*ag_flags), lc + 8, lc + 12,
                     status.data_ptr(), W, self.rank), "tp_fill_norm_args")
+        # one-shot small all-reduce: slots [2][world][cap] on every rank, flags at +512, counters private
+        self.ar_ctr = torch.zeros(2, dtype=torch.int32, device=self.device)
+        ar_flags = [b + self.off_flags + 512 for b in base]
+        self.ar_blob = C.create_string_buffer(_lib.declare("pie_tp_ar_args_size", [], C.c_int)())
+        fill_ar = _lib.declare("pie_tp_fill_ar_args", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                       C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_long])
+        check(fill_ar(self.ar_blob, arr_p(*[b + self.off_ar for b in base]), arr_p(*ar_flags), ar_flags[self.rank],
+                      self.ar_ctr.data_ptr(), self.ar_ctr.data_ptr() + 4, status.data_ptr(), W, self.rank,
+                      self.ar_cap), "tp_fill_ar_args")
+        self._ar_small = _lib.declare("pie_tp_allreduce_small", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int,
+                                                                 C.c_void_p])
         self._ag_flags_local = ag_flags[self.rank]
         self._ag_epoch_ptr = lc + 12
         self._gemm_tp = _lib.declare("pie_gemm_bf16_tp", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
@@ -224,6 +237,13 @@ class TPComm:
 
     # ------------------------------------------------------------------ NCCL paths
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks, in place. Small bf16 tensors go through the one-shot peer-memory kernel
+        (when the fused data plane is attached), everything else through NCCL."""
+        n = x.numel()
+        if (self.fused and getattr(self, "_ar_small", None) is not None and x.dtype == torch.bfloat16
+                and x.is_contiguous() and n % 8 == 0 and n <= self.ar_cap):
+            check(self._ar_small(self.ar_blob, ptr(x), ptr(x), n, self._sms, stream_ptr()), "tp_allreduce_small")
+            return x
         import torch.distributed as dist
         dist.all_reduce(x)
         return x

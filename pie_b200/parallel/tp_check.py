@@ -51,6 +51,18 @@ def main():
     drv = TorchDriver(cfg, dev, num_pages=64, page_size=16, max_requests=8, max_tokens=512,
                       par=ParallelContext(world, rank, comm, ep=a.model == "moe-ep"), seed=0)
     comm.attach(drv)
+    # one-shot small all-reduce against NCCL, three sizes, twice each (buffer parity)
+    ar_ok = True
+    if comm.fused:
+        for n in (8, 4096, 200 * 1024):
+            for rep in range(2):
+                g = torch.Generator(device="cpu").manual_seed(100 * rank + n + rep)
+                x = torch.randn(n, generator=g).to(torch.bfloat16).to(dev)
+                want = x.float().clone()
+                dist.all_reduce(want)
+                got = comm.all_reduce(x.clone())
+                torch.cuda.synchronize()
+                ar_ok &= bool((got.float() - want).abs().max() <= 0.02 * want.abs().max() + 1e-3)
     if rank != 0:
         comm.follower_loop(drv)
         comm.close()
@@ -93,7 +105,8 @@ def main():
     torch.cuda.synchronize()
     from .. import ops
     ops.check_kernel_status(dev)
-    report["ok"] = all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
+    report["allreduce_small_ok"] = ar_ok
+    report["ok"] = ar_ok and all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
     report["graph_replays"] = drv.stats["graph_replays"]
     print(json.dumps(report), flush=True)
     comm.close()

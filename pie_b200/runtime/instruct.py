@@ -65,10 +65,22 @@ class Instruct:
         return json.dumps({"tool": name, "result": result})
 
     def tool_grammar(self, tools: Sequence[dict]) -> str:
-        """EBNF of one tool call, for constrained decoding of the call body."""
-        names = " | ".join(json.dumps(json.dumps(t["name"])) for t in tools) or '"\\"none\\""'
-        return ('root ::= "{" ws "\\"name\\"" ws ":" ws name ws "," ws "\\"arguments\\"" ws ":" ws object ws "}"\n'
-                f"name ::= {names}\n" + JSON_EBNF_TAIL)
+        """EBNF of one tool call `{"name": <tool>, "arguments": {...}}`; the arguments follow the
+        tool's `parameters` JSON schema when it has one, else any JSON object."""
+        from .structured import JSON_RULES, json_schema_rules
+        alts, rules = [], []
+        for i, t in enumerate(tools):
+            schema = t.get("parameters") or t.get("inputSchema")
+            if isinstance(schema, dict) and schema.get("properties"):
+                root, text = json_schema_rules(schema, f"t{i}x")
+                rules.append(text)
+            else:
+                root = "object"
+            alts.append(f'( {json.dumps(json.dumps(t["name"]))} ws "," ws "\\"arguments\\"" ws ":" ws {root} )')
+        if not alts:
+            alts = ['( "\\"none\\"" ws "," ws "\\"arguments\\"" ws ":" ws object )']
+        return ('root ::= "{" ws "\\"name\\"" ws ":" ws call ws "}"\n' + "call ::= " + " | ".join(alts) + "\n"
+                + "".join(rules) + JSON_RULES)
 
 
 JSON_EBNF_TAIL = r'''object ::= "{" ws (pair (ws "," ws pair)*)? ws "}"

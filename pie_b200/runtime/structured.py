@@ -297,6 +297,13 @@ def _lit(s: str) -> str:
 
 
 def json_schema_to_ebnf(schema) -> str:
+    root, rules = json_schema_rules(schema, "s")
+    return f"root ::= {root}\n" + rules + JSON_RULES
+
+
+def json_schema_rules(schema, prefix: str = "s"):
+    """(name of the rule that matches `schema`, text of the rules it needs) with rule names
+    `<prefix>0`, `<prefix>1`, ...; the shared JSON rules (value, string, ws, ...) are not included."""
     if isinstance(schema, str):
         schema = json.loads(schema)
     rules: List[str] = []
@@ -304,9 +311,9 @@ def json_schema_to_ebnf(schema) -> str:
     memo: Dict[str, str] = {}
 
     def new(body: str) -> str:
-        name = f"s{len(rules)}"
-        rules.append(None)
-        rules[int(name[1:])] = f"{name} ::= {body}"
+        idx = len(rules)
+        name = f"{prefix}{idx}"
+        rules.append(f"{name} ::= {body}")
         return name
 
     def visit(s) -> str:
@@ -315,10 +322,11 @@ def json_schema_to_ebnf(schema) -> str:
         if "$ref" in s:
             key = s["$ref"].split("/")[-1]
             if key not in memo:
-                memo[key] = f"s{len(rules)}"
+                idx = len(rules)
+                memo[key] = f"{prefix}{idx}"
                 rules.append(None)
                 body = visit(defs[key])
-                rules[int(memo[key][1:])] = f"{memo[key]} ::= {body}"
+                rules[idx] = f"{memo[key]} ::= {body}"
             return memo[key]
         if "const" in s:
             return new(_lit(json.dumps(s["const"])))
@@ -372,7 +380,7 @@ def json_schema_to_ebnf(schema) -> str:
         return "value"
 
     root = visit(schema)
-    return f"root ::= {root}\n" + "\n".join(r for r in rules if r) + JSON_RULES
+    return root, "\n".join(r for r in rules if r) + "\n"
 
 
 # ------------------------------------------------------------------------------ public objects

@@ -13,9 +13,9 @@ from .sample import Distribution, Entropy, Logits, Logprob, Logprobs, Sampler
 from .spec import NGramSpeculator, Speculator
 from .adapter import Adapter
 from .grammar import AnyJson, Ebnf, Grammar, GrammarConstraint, JsonSchema, Matcher, Regex
-from . import io, messaging, runtime, scheduling, session
+from . import chat, io, mcp, media, messaging, runtime, scheduling, session
 
 __all__ = ["Context", "Forward", "GenStep", "Generator", "Model", "Output", "ProbeHandle", "SampleHandle",
            "Tokenizer", "Distribution", "Entropy", "Logits", "Logprob", "Logprobs", "Sampler", "Speculator",
            "NGramSpeculator", "Adapter", "AnyJson", "Ebnf", "Grammar", "GrammarConstraint", "JsonSchema", "Matcher", "Regex",
-           "io", "messaging", "runtime", "scheduling", "session"]
+           "chat", "io", "mcp", "media", "messaging", "runtime", "scheduling", "session"]

@@ -214,3 +214,27 @@ def test_agentic_fork_workload_shares_prefix(eng):
     r = harness.run_agentic_fork(eng, "tiny-llama", agents=3, prefix_len=50, branches=3, tokens=5, rounds=2, vocab=32000)
     assert r["output_tokens"] == 3 * 3 * 5 * 2
     assert r["prefix_pages_per_agent"] == 49 // 16 and r["kv_pages_used_after"] == 0
+
+
+def test_mcp_tool_call_is_grammar_constrained_and_executed(eng):
+    calls = []
+
+    def server(method, params_json):
+        p = json.loads(params_json)
+        if method == "tools/list":
+            schema = {"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "integer"}},
+                      "required": ["a", "b"]}
+            return json.dumps({"tools": [{"name": "add", "description": "adds", "parameters": schema},
+                                         {"name": "mul", "description": "multiplies", "parameters": schema}]})
+        if method == "tools/call":
+            calls.append(p)
+            return json.dumps({"ok": True, "name": p["name"]})
+        raise ValueError(method)
+
+    eng.mcp_servers["tools"] = server
+    try:
+        out = json.loads(run(eng, "demo-mcp-tools", {"prompt_tokens": PROMPT, "max_tokens": 300}))
+    finally:
+        eng.mcp_servers.pop("tools")
+    assert out["call"]["name"] in ("add", "mul") and set(out["call"]["arguments"]) == {"a", "b"}
+    assert calls and calls[0]["name"] == out["call"]["name"] and out["result"]["ok"]

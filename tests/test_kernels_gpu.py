@@ -254,3 +254,36 @@ def test_fp8_block_dequant_and_gemm():
     y = ops.gemm_fp8w(x, q, epilogue=ops.EPI_SWIGLU)
     assert (y.float() - ref.swiglu_interleaved(full)).abs().max() < 0.05 * full.abs().max()
     ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 1536, 2048), (200, 1024, 5120), (512, 6400, 5120), (1000, 640, 3200), (130, 2016, 1024)])
+@pytest.mark.parametrize("epi", ["store", "residual", "swiglu"])
+def test_fp8_blockscaled_gemm_fused(m, n, k, epi):
+    """fp8 x fp8 tcgen05 GEMM with 1x128 activation scales and per-row x 128 weight scales against
+    the fp32 evaluation of the same quantised operands; and close to the unquantised product."""
+    from pie_b200 import ops
+    from pie_b200.ops import reference as ref
+    torch.manual_seed(m + n)
+    w = torch.randn(n, k, device="cuda") * 0.05
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    r = (torch.randn(m, n, device="cuda") * 0.5).to(torch.bfloat16) if epi == "residual" else None
+    q = ops.quantize_fp8_block(w)
+    x8, sx = ops.quant_act_fp8(x)
+    # the quantiser itself: dequantised activations within fp8 rounding of the input
+    xd = x8.float() * sx.repeat_interleave(128, dim=1)[:, :k]
+    assert (xd - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+    want = ops.gemm_fp8_reference(x8, sx, q)
+    e = {"store": ops.EPI_STORE, "residual": ops.EPI_RESIDUAL, "swiglu": ops.EPI_SWIGLU}[epi]
+    if epi == "residual":
+        want = want + r.float()
+    if epi == "swiglu":
+        want = ref.swiglu_interleaved(want)
+    y = ops.gemm_fp8w(x, q, residual=r, epilogue=e, mode="fused")
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    tol = 2e-2 * want.abs().max().item() + 1e-3 * k ** 0.5
+    assert (y.float() - want).abs().max().item() <= tol
+    if epi == "store":
+        exact = x.float() @ w.t()
+        rel = (y.float() - exact).norm() / exact.norm()
+        assert rel < 0.06, rel
