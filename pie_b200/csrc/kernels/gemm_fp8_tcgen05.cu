@@ -164,12 +164,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             float acc[BN];
 #pragma unroll
             for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+            // scales of the next K block are fetched one block ahead (global latency hidden behind
+            // the wait for the MMAs and the fold of the current block); lane l keeps the weight
+            // scales of columns l, l+32, ... in registers and hands them to its warp through smem
+            constexpr int SPL = BN / 32;
+            float sw_n[SPL], sa_n;
+            auto fetch = [&](int kb) {
+#pragma unroll
+                for (int u = 0; u < SPL; ++u) {
+                    const int c = u * 32 + lane;
+                    sw_n[u] = (c < bn && n0 + c < N) ? __ldg(sw + (size_t)(n0 + c) * kbs + kb) : 0.f;
+                }
+                sa_n = row < M ? __ldg(sa + (size_t)row * kbs + kb) : 0.f;
+            };
+            fetch(0);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-                // weight scales of this block for the tile's columns -> this warp's shared-memory copy
                 float* sws = sw_w + buf * BN;
-                for (int c = lane; c < bn; c += 32) sws[c] = (n0 + c < N) ? __ldg(sw + (size_t)(n0 + c) * kbs + kb) : 0.f;
-                const float sa_r = row < M ? __ldg(sa + (size_t)row * kbs + kb) : 0.f;
+#pragma unroll
+                for (int u = 0; u < SPL; ++u) sws[u * 32 + lane] = sw_n[u];
+                const float sa_r = sa_n;
+                if (kb + 1 < num_kb) fetch(kb + 1);
                 __syncwarp();
                 const bool got = mbar_wait(tfull_bar(buf), bph, status, PIE_ERR_WAIT_MMA);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }

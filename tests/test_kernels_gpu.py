@@ -247,11 +247,11 @@ def test_fp8_block_dequant_and_gemm():
     x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
     r = (torch.randn(m, n, device="cuda") * 0.5).to(torch.bfloat16)
     full = x.float() @ deq.float().t()
-    y = ops.gemm_fp8w(x, q)
+    y = ops.gemm_fp8w(x, q, mode="dequant")
     assert (y.float() - full).abs().max() < 0.05 * full.abs().max()
-    y = ops.gemm_fp8w(x, q, residual=r, epilogue=ops.EPI_RESIDUAL)
+    y = ops.gemm_fp8w(x, q, residual=r, epilogue=ops.EPI_RESIDUAL, mode="dequant")
     assert (y.float() - (full + r.float())).abs().max() < 0.05 * full.abs().max()
-    y = ops.gemm_fp8w(x, q, epilogue=ops.EPI_SWIGLU)
+    y = ops.gemm_fp8w(x, q, epilogue=ops.EPI_SWIGLU, mode="dequant")
     assert (y.float() - ref.swiglu_interleaved(full)).abs().max() < 0.05 * full.abs().max()
     ops.check_kernel_status()
 
