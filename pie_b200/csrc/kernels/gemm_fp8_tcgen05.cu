@@ -59,7 +59,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const float* __restrict__ sa, const float* __restrict__ sw, bf16* __restrict__ C,
-                const bf16* __restrict__ R, int M, int N, int K, int ldc, int ldr, int* status, int bn) {
+                const bf16* __restrict__ R, int M, int N, int K, int ldc, int ldr, int* status, int bn,
+                const __grid_constant__ TpArgs tp) {
     using Cfg = Fp8Cfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -207,7 +208,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             }
             if (!ok) break;
             uint8_t* stage = stage_base + (warp - 2) * 4096;
-            const TpArgs tp{};
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c) {
                 if (c * 64 < bn) {
@@ -220,6 +220,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     epilogue_store_64<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n0 + c * 64, M, N, C, ldc, R, ldr,
                                            tp, min(N, n0 + bn));
                 }
+            }
+            if (EPI == EPI_RS) {
+                // this warp's rows of the tile are in the owners' receive buffers: count the arrival
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0) rs_publish_arrival(tp, num_tiles * 4);
             }
         }
     }
@@ -302,11 +308,35 @@ PIE_API int pie_quant_act_fp8(const void* x, int ldx, void* x8, float* sx, int M
 }
 
 // C[M,N] (or [M,N/2] with SwiGLU) from fp8 operands and their scales (see the header comment).
+static int gemm_fp8_launch(const void* A8, const float* sa, const void* W8, const float* sw, void* C,
+                           const void* R, int M, int N, int K, int ldc, int ldr, int epilogue, int* status,
+                           int num_sms, cudaStream_t st, const TpArgs& tp);
+
 PIE_API int pie_gemm_fp8_blockscaled(const void* A8, const float* sa, const void* W8, const float* sw, void* C,
                                      const void* R, int M, int N, int K, int ldc, int ldr, int epilogue, int* status,
                                      int num_sms, cudaStream_t st) {
+    if (epilogue == EPI_RS) return (int)cudaErrorInvalidValue;
+    return gemm_fp8_launch(A8, sa, W8, sw, C, R, M, N, K, ldc, ldr, epilogue, status, num_sms, st, TpArgs{});
+}
+
+// Tensor-parallel form: with EPI_RS every output row goes to its owner rank's receive buffer
+// (`tp_blob` = the communicator's TpArgs, rows_per_rank rows per owner), as in pie_gemm_bf16_tp.
+PIE_API int pie_gemm_fp8_blockscaled_tp(const void* A8, const float* sa, const void* W8, const float* sw, void* C,
+                                        int M, int N, int K, int ldc, int epilogue, const void* tp_blob,
+                                        int rows_per_rank, int* status, int num_sms, cudaStream_t st) {
+    TpArgs tp = *reinterpret_cast<const TpArgs*>(tp_blob);
+    tp.rows_per_rank = rows_per_rank;
+    tp.gated = 0;
+    if (epilogue == EPI_RS && (rows_per_rank % 32 || rows_per_rank <= 0)) return (int)cudaErrorInvalidValue;
+    return gemm_fp8_launch(A8, sa, W8, sw, C, nullptr, M, N, K, ldc, 0, epilogue, status, num_sms, st, tp);
+}
+
+static int gemm_fp8_launch(const void* A8, const float* sa, const void* W8, const float* sw, void* C,
+                           const void* R, int M, int N, int K, int ldc, int ldr, int epilogue, int* status,
+                           int num_sms, cudaStream_t st, const TpArgs& tp) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 16 || N % 16 || ldc % 8 || (epilogue == EPI_RESIDUAL && ldr % 8)) return (int)cudaErrorInvalidValue;
+    if (K <= 0 || K % 16 || N % 16 || (epilogue != EPI_RS && ldc % 8) || (epilogue == EPI_RESIDUAL && ldr % 8))
+        return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_SWIGLU && N % 32) return (int)cudaErrorInvalidValue;
     const int tm = (M + GEMM_BM - 1) / GEMM_BM;
     // tile width: the widest of {128, 112, ..., 16} whose tile count fills its waves best
@@ -331,7 +361,7 @@ PIE_API int pie_gemm_fp8_blockscaled(const void* A8, const float* sa, const void
                                              (int)Fp8Cfg<BN_>::SMEM_BYTES);                                   \
         if (e != cudaSuccess) return (int)e;                                                                  \
         kern<<<grid, GEMM_THREADS, Fp8Cfg<BN_>::SMEM_BYTES, st>>>(ta, tb, sa, sw, (bf16*)C, (const bf16*)R, M, N, K, \
-                                                                  ldc, ldr, status, bn);                      \
+                                                                  ldc, ldr, status, bn, tp);                  \
         return (int)cudaGetLastError();                                                                       \
     }
 #define GOE(BN_)                                                  \
@@ -339,6 +369,7 @@ PIE_API int pie_gemm_fp8_blockscaled(const void* A8, const float* sa, const void
         case EPI_STORE: GO(BN_, EPI_STORE)                        \
         case EPI_RESIDUAL: GO(BN_, EPI_RESIDUAL)                  \
         case EPI_SWIGLU: GO(BN_, EPI_SWIGLU)                      \
+        case EPI_RS: GO(BN_, EPI_RS)                              \
         default: return (int)cudaErrorInvalidValue;               \
     }
     if (bt == 128) { GOE(128) } else { GOE(64) }

@@ -178,6 +178,9 @@ class TPComm:
         self._gemm_tp = _lib.declare("pie_gemm_bf16_tp", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                                           C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                                           C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p])
+        self._gemm_fp8_tp = _lib.declare("pie_gemm_fp8_blockscaled_tp",
+                                         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                          C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p])
         self._norm_push = _lib.declare("pie_tp_reduce_norm_push", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                                                   C.c_int, C.c_int, C.c_float, C.c_void_p])
         self._wait_ag = _lib.declare("pie_tp_wait_ag", [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p])
@@ -214,8 +217,23 @@ class TPComm:
         check(self._norm_push(self.norm_blob, ptr(self.residual), ptr(weight), rpr, self.hidden,
                               self._valid_rows(n, rpr), 1, eps, stream_ptr()), "tp_reduce_norm_push")
 
-    def gemm_gated(self, w: torch.Tensor, n: int, swiglu: bool = False, x: Optional[torch.Tensor] = None):
+    def _fp8(self, a: torch.Tensor, q, n: int, epilogue: int, out, rpr: int = 32):
+        """Block-scaled fp8 weight: quantise the (already gathered) activation rows 1x128 and run the
+        fp8 tcgen05 GEMM, with the reduce-scatter epilogue when `epilogue` is EPI_RS."""
+        x8, sx = ops.quant_act_fp8(a)
+        nn, k = q.shape
+        check(self._gemm_fp8_tp(ptr(x8), ptr(sx), ptr(q.w8), ptr(q.scale), ptr(out), n, nn, k,
+                                out.stride(0) if out is not None else 0, epilogue, self.tp_blob, rpr,
+                                ptr(self._status), self._sms, stream_ptr()), "gemm_fp8_tp")
+        return out
+
+    def gemm_gated(self, w, n: int, swiglu: bool = False, x: Optional[torch.Tensor] = None):
         """y = gathered_activation[:n] @ w.T (waits inside the kernel for every rank's push)."""
+        if isinstance(w, ops.Fp8Linear):
+            a = self.wait_gathered(n) if x is None else x
+            nn = w.shape[0]
+            out = torch.empty(n, nn // 2 if swiglu else nn, dtype=torch.bfloat16, device=self.device)
+            return self._fp8(a, w, n, ops.EPI_SWIGLU if swiglu else ops.EPI_STORE, out)
         a = self.xfull[:n] if x is None else x
         nn = w.shape[0]
         out = torch.empty(n, nn // 2 if swiglu else nn, dtype=torch.bfloat16, device=self.device)
@@ -224,9 +242,12 @@ class TPComm:
                             ptr(self._status), self._sms, stream_ptr()), "gemm_gated")
         return out
 
-    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, n: int) -> None:
+    def gemm_rs(self, a: torch.Tensor, w, n: int) -> None:
         """Partial y = a @ w.T scattered row-wise into the owners' receive buffers."""
         rpr = self.rows_per_rank(n)
+        if isinstance(w, ops.Fp8Linear):
+            self._fp8(a, w, n, 3, None, rpr)
+            return
         check(self._gemm_tp(ptr(a), ptr(w), None, n, w.shape[0], a.shape[1], a.stride(0), w.stride(0), 0, 3,
                             self.tp_blob, rpr, 0, 0, ptr(self._status), self._sms, stream_ptr()), "gemm_rs")
 
