@@ -56,6 +56,27 @@ struct RowView {
     }
 };
 
+// Visit every 8-element vector of the row: f(vector index, 8 bf16). Four loads are in flight per
+// thread before the first is consumed (a single dependent load per thread leaves the pass
+// latency-bound on L2).
+template <typename F>
+__device__ __forceinline__ void scan_row(const RowView& rv, F&& f) {
+    constexpr int U = 4;
+    for (int v0 = threadIdx.x; v0 < rv.nvec; v0 += SAMPLE_THREADS * U) {
+        uint4 pk[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int v = v0 + u * SAMPLE_THREADS;
+            if (v < rv.nvec) pk[u] = rv.vec[v];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int v = v0 + u * SAMPLE_THREADS;
+            if (v < rv.nvec) f(v, pk[u]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
@@ -82,8 +103,7 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
 
     // ---- pass 1: arg-max over the allowed entries
     unsigned long long best = 0ull;
-    for (int v = threadIdx.x; v < rv.nvec; v += SAMPLE_THREADS) {
-        const uint4 pk = rv.vec[v];
+    scan_row(rv, [&](int v, const uint4& pk) {
         const uint16_t* e = reinterpret_cast<const uint16_t*>(&pk);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -93,7 +113,7 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
                 ((unsigned long long)(bf16_key(e[k]) + 1u) << 32) | (0xffffffffu - (uint32_t)idx);
             best = cand > best ? cand : best;
         }
-    }
+    });
     best = block_max_u64(best, red64);
     const float T = temperature[row];
     if (best == 0ull) {  // nothing allowed: emit token 0
@@ -118,7 +138,84 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
     const bool need_k = K > 0 && K < vocab;
     const bool need_p = P < 1.f;
     uint32_t thr_key = 0;  // keep entries whose key >= thr_key
+    // min-p: keep p_i >= min_p * p_max  <=>  x_i >= xmax + T * ln(min_p)
+    const float x_floor = (MP > 0.f) ? xmax + T * __logf(MP) : -INFINITY;
+    // per-row stream keys from the 64-bit seed; per-element noise is one 32-bit mix of the index
+    const unsigned long long seed = splitmix64(seeds[row]);
+    const uint32_t s0 = (uint32_t)seed, s1 = (uint32_t)(seed >> 32);
 
+    // Gumbel-max over the entries with key >= lo (and the min-p floor, and the mask); `salt`
+    // separates the noise streams of different rounds. Returns (score key << 32 | ~index) or 0.
+    auto gumbel_pass = [&](uint32_t lo, uint32_t salt) -> unsigned long long {
+        unsigned long long pick = 0ull;
+        scan_row(rv, [&](int v, const uint4& pk) {
+            const uint16_t* e = reinterpret_cast<const uint16_t*>(&pk);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int idx = v * 8 + k;
+                const uint32_t key = bf16_key(e[k]);
+                if (key < lo) continue;
+                const float x = __bfloat162float(__ushort_as_bfloat16(e[k]));
+                if (x < x_floor) continue;
+                if (!rv.allowed(idx)) continue;
+                uint32_t hsh = ((uint32_t)idx + s0 + salt * 0x632BE5ABu) * 0x9E3779B1u ^ s1;
+                hsh ^= hsh >> 16; hsh *= 0x85EBCA6Bu; hsh ^= hsh >> 13; hsh *= 0xC2B2AE35u; hsh ^= hsh >> 16;
+                const float u = ((float)(hsh >> 8) + 0.5f) * (1.0f / 16777216.0f);
+                const float score = (x - xmax) * inv_t - __logf(-__logf(u));
+                const unsigned long long cand =
+                    ((unsigned long long)f32_key(score) << 32) | (0xffffffffu - (uint32_t)idx);
+                pick = cand > pick ? cand : pick;
+            }
+        });
+        return block_max_u64(pick, red64);
+    };
+
+    if (need_k || need_p) {
+        // Rejection rounds (no histogram, no atomics): draw a candidate from the distribution
+        // restricted to keys >= lo, then measure how much probability mass / how many entries lie
+        // strictly above its key. It belongs to the kept set iff that is below top-p * Z and below
+        // top-k (ties at the threshold are kept, as in the radix select below). A rejected candidate
+        // proves that every key <= its key is outside the kept set, so the next round draws above it.
+        // With top-p = 0.9 a round accepts with probability >= 0.9; after three rejections, and for
+        // top-k or a small top-p (where a round rarely accepts), the exact radix select takes over.
+        uint32_t lo = 0;
+        bool accepted = false;
+        // rejection pays when a round is likely to accept: top-p alone with a large nucleus
+        const int rounds = (need_p && !need_k && P >= 0.5f) ? 3 : 0;
+        for (int round = 0; round < rounds && !accepted; ++round) {
+            const unsigned long long pick = gumbel_pass(lo, (uint32_t)round);
+            if (pick == 0ull) {                       // nothing left above lo: fall back to the arg-max
+                if (threadIdx.x == 0) out_tokens[row] = arg;
+                return;
+            }
+            const int cand = (int)(0xffffffffu - (uint32_t)(pick & 0xffffffffu));
+            const uint16_t cb = reinterpret_cast<const uint16_t*>(rv.vec)[cand];
+            const uint32_t ckey = bf16_key(cb);
+            float z = 0.f, above = 0.f, n_above = 0.f;
+            scan_row(rv, [&](int v, const uint4& pk) {
+                const uint16_t* e = reinterpret_cast<const uint16_t*>(&pk);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int idx = v * 8 + k;
+                    if (!rv.allowed(idx)) continue;
+                    const uint32_t key = bf16_key(e[k]);
+                    const float w = __expf((__bfloat162float(__ushort_as_bfloat16(e[k])) - xmax) * inv_t);
+                    z += w;
+                    if (key > ckey) { above += w; n_above += 1.f; }
+                }
+            });
+            z = block_sum(z, redf);
+            above = block_sum(above, redf);
+            n_above = block_sum(n_above, redf);
+            const bool ok_p = !need_p || above < P * z;
+            const bool ok_k = !need_k || n_above < (float)K;
+            if (ok_p && ok_k) {
+                if (threadIdx.x == 0) out_tokens[row] = cand;
+                return;
+            }
+            lo = ckey + 1u;
+        }
+    }
     if (need_k || need_p) {
         // ---- pass 2: histogram of the key's high byte (count and softmax mass)
         for (int i = threadIdx.x; i < SAMPLE_WARPS * 256; i += SAMPLE_THREADS) {
@@ -126,8 +223,7 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
             h_mass[i] = 0.f;
         }
         __syncthreads();
-        for (int v = threadIdx.x; v < rv.nvec; v += SAMPLE_THREADS) {
-            const uint4 pk = rv.vec[v];
+        scan_row(rv, [&](int v, const uint4& pk) {
             const uint16_t* e = reinterpret_cast<const uint16_t*>(&pk);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
@@ -138,7 +234,7 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
                 atomicAdd(&h_cnt[wid * 256 + (key >> 8)], 1);
                 atomicAdd(&h_mass[wid * 256 + (key >> 8)], __expf((x - xmax) * inv_t));
             }
-        }
+        });
         __syncthreads();
         if (threadIdx.x < 256) {
             int c = 0;
@@ -177,8 +273,7 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
                 h_mass[i] = 0.f;
             }
             __syncthreads();
-            for (int v = threadIdx.x; v < rv.nvec; v += SAMPLE_THREADS) {
-                const uint4 pk = rv.vec[v];
+            scan_row(rv, [&](int v, const uint4& pk) {
                 const uint16_t* e = reinterpret_cast<const uint16_t*>(&pk);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
@@ -193,7 +288,7 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
                         atomicAdd(&h_mass[wid * 256 + (key & 255u)], __expf((x - xmax) * inv_t));
                     }
                 }
-            }
+            });
             __syncthreads();
             if (threadIdx.x < 256) {
                 int c = 0;
@@ -231,38 +326,10 @@ sample_kernel(const bf16* __restrict__ logits, long row_stride, int vocab,
             thr_key = (uint32_t)s_sel[3];
         }
     }
-    // min-p: keep p_i >= min_p * p_max  <=>  x_i >= xmax + T * ln(min_p)
-    const float x_floor = (MP > 0.f) ? xmax + T * __logf(MP) : -INFINITY;
-
-    // ---- pass 4: Gumbel-max over the kept set
-    // per-row stream keys from the 64-bit seed; per-element noise is one 32-bit mix of the index
-    const unsigned long long seed = splitmix64(seeds[row]);
-    const uint32_t s0 = (uint32_t)seed, s1 = (uint32_t)(seed >> 32);
-    unsigned long long pick = 0ull;
-    for (int v = threadIdx.x; v < rv.nvec; v += SAMPLE_THREADS) {
-        const uint4 pk = rv.vec[v];
-        const uint16_t* e = reinterpret_cast<const uint16_t*>(&pk);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int idx = v * 8 + k;
-            const uint32_t key = bf16_key(e[k]);
-            if (key < thr_key) continue;
-            const float x = __bfloat162float(__ushort_as_bfloat16(e[k]));
-            if (x < x_floor) continue;
-            if (!rv.allowed(idx)) continue;
-            uint32_t hsh = ((uint32_t)idx + s0) * 0x9E3779B1u ^ s1;
-            hsh ^= hsh >> 16; hsh *= 0x85EBCA6Bu; hsh ^= hsh >> 13; hsh *= 0xC2B2AE35u; hsh ^= hsh >> 16;
-            const float u = ((float)(hsh >> 8) + 0.5f) * (1.0f / 16777216.0f);
-            const float score = (x - xmax) * inv_t - __logf(-__logf(u));
-            const unsigned long long cand =
-                ((unsigned long long)f32_key(score) << 32) | (0xffffffffu - (uint32_t)idx);
-            pick = cand > pick ? cand : pick;
-        }
-    }
-    pick = block_max_u64(pick, red64);
+    // ---- final pass: Gumbel-max over the kept set
+    const unsigned long long pick = gumbel_pass(thr_key, 7u);
     if (threadIdx.x == 0)
         out_tokens[row] = pick ? (int)(0xffffffffu - (uint32_t)(pick & 0xffffffffu)) : arg;
-    (void)redf;
 }
 
 // Per-row max, log-sum-exp and Shannon entropy of the unscaled distribution.

@@ -287,3 +287,19 @@ def test_fp8_blockscaled_gemm_fused(m, n, k, epi):
         exact = x.float() @ w.t()
         rel = (y.float() - exact).norm() / exact.norm()
         assert rel < 0.06, rel
+
+
+@pytest.mark.parametrize("k,p", [(0, 0.6), (5, 1.0), (8, 0.8), (0, 0.05)])
+def test_sample_topk_topp_distribution_is_renormalised_kept_set(k, p):
+    """Draws under top-k / top-p follow the softmax renormalised over the kept set (rejection
+    rounds and the radix fallback for a small top-p must agree with the reference set)."""
+    vocab, draws = 64, 20000
+    row = (torch.randn(vocab, generator=torch.Generator().manual_seed(9)) * 1.5).to(torch.bfloat16)
+    lg = row.to(DEV).repeat(draws, 1).contiguous()
+    got = ops.sample(lg, *_params(draws, 1.0, k, p, 0.0, seed0=77)).cpu()
+    keep = ref.kept_set(row, 1.0, k, p, 0.0)
+    assert bool(keep[got.long()].all())
+    probs = torch.softmax(row.float(), -1) * keep
+    probs = probs / probs.sum()
+    freq = torch.bincount(got.long(), minlength=vocab).float() / draws
+    assert float((freq - probs).abs().max()) < 0.02
