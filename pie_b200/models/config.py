@@ -10,7 +10,7 @@ from dataclasses import dataclass, field, asdict
 from pathlib import Path
 from typing import Optional
 
-LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "olmo2", "phi3"}
+LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 MOE_TYPES = {"qwen3_moe", "mixtral"}
 
 

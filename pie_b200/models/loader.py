@@ -129,9 +129,16 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         L, P = f"{pre}layers.{li}.", f"layers.{li}."
         att[P + "ln1"] = w(L + "input_layernorm.weight")
         att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
-        q = lin(L + "self_attn.q_proj.weight").shard(0, r, T)
-        k = lin(L + "self_attn.k_proj.weight").rows(kv0 * d, kvn * d)
-        v = lin(L + "self_attn.v_proj.weight").rows(kv0 * d, kvn * d)
+        hq_d, hkv_d = cfg.num_attention_heads * d, cfg.num_key_value_heads * d
+        if L + "self_attn.qkv_proj.weight" in names:          # Phi-3: q, k, v rows stored in one tensor
+            fused = lin(L + "self_attn.qkv_proj.weight")
+            q = fused.rows(0, hq_d).shard(0, r, T)
+            k = fused.rows(hq_d + kv0 * d, kvn * d)
+            v = fused.rows(hq_d + hkv_d + kv0 * d, kvn * d)
+        else:
+            q = lin(L + "self_attn.q_proj.weight").shard(0, r, T)
+            k = lin(L + "self_attn.k_proj.weight").rows(kv0 * d, kvn * d)
+            v = lin(L + "self_attn.v_proj.weight").rows(kv0 * d, kvn * d)
         QLin.concat([q, k, v]).attach(att, P + "wqkv")
         if L + "self_attn.q_proj.bias" in names:
             att[P + "bqkv"] = Concat([Shard(w(L + "self_attn.q_proj.bias"), 0, r, T),
@@ -156,8 +163,12 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
             att[P + "experts_gate_up"] = Stack(gus)
             att[P + "experts_down"] = Stack(downs)
         else:
-            QLin.interleave(lin(L + "mlp.gate_proj.weight").shard(0, r, T),
-                            lin(L + "mlp.up_proj.weight").shard(0, r, T)).attach(att, P + "w_gate_up")
+            if L + "mlp.gate_up_proj.weight" in names:        # Phi-3: gate rows then up rows in one tensor
+                gu = lin(L + "mlp.gate_up_proj.weight")
+                gate, up = gu.rows(0, cfg.intermediate_size), gu.rows(cfg.intermediate_size, cfg.intermediate_size)
+            else:
+                gate, up = lin(L + "mlp.gate_proj.weight"), lin(L + "mlp.up_proj.weight")
+            QLin.interleave(gate.shard(0, r, T), up.shard(0, r, T)).attach(att, P + "w_gate_up")
             lin(L + "mlp.down_proj.weight").shard(1, r, T).attach(att, P + "w_down")
     return Program(att, dtype, {"tp_size": T, "tp_rank": r, "ep": ep, "layers": cfg.num_hidden_layers,
                                 "vocab_start": r * (cfg.vocab_size // T) if T > 1 else 0})

@@ -123,3 +123,37 @@ def test_fp8_block_checkpoint_loads_and_matches_dequantised_oracle(tmp_path):
     full, part = w2["layers"][0]["wo"], wr["layers"][0]["wo"]
     assert part.shape == (cfg.hidden_size, full.shape[1] // 2)
     assert torch.equal(part.dequant(torch.float32), full.dequant(torch.float32)[:, full.shape[1] // 2:])
+
+
+def test_phi3_fused_projections_load_like_split_ones(tmp_path):
+    """A checkpoint that stores qkv_proj and gate_up_proj fused (Phi-3 layout) loads into the same
+    runtime weights as the split layout, also for a tensor-parallel rank."""
+    import json as _json
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    from pie_b200.models import loader
+    from pie_b200.models.config import preset
+    from pie_b200.models.weights import random_weights
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=5)
+    split_dir, fused_dir = tmp_path / "split", tmp_path / "fused"
+    loader.export_hf_checkpoint(cfg, w, split_dir)
+    fused_dir.mkdir()
+    tensors = {}
+    with safe_open(str(split_dir / "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            tensors[k] = f.get_tensor(k)
+    out = {k: v for k, v in tensors.items() if "_proj.weight" not in k or "o_proj" in k or "down_proj" in k}
+    for li in range(cfg.num_hidden_layers):
+        L = f"model.layers.{li}."
+        out[L + "self_attn.qkv_proj.weight"] = torch.cat([tensors[L + f"self_attn.{x}_proj.weight"] for x in "qkv"], 0)
+        out[L + "mlp.gate_up_proj.weight"] = torch.cat([tensors[L + "mlp.gate_proj.weight"], tensors[L + "mlp.up_proj.weight"]], 0)
+    save_file(out, str(fused_dir / "model.safetensors"))
+    hf = _json.loads((split_dir / "config.json").read_text())
+    hf["model_type"] = "phi3"
+    (fused_dir / "config.json").write_text(_json.dumps(hf))
+    for tp, rank in [(1, 0), (2, 1)]:
+        _, a = loader.load_checkpoint(split_dir, "cpu", tp, rank, dtype="float32")
+        _, b = loader.load_checkpoint(fused_dir, "cpu", tp, rank, dtype="float32")
+        for la, lb in zip(a["layers"], b["layers"]):
+            assert torch.equal(la["wqkv"], lb["wqkv"]) and torch.equal(la["w_gate_up"], lb["w_gate_up"])
