@@ -85,7 +85,8 @@ class ModelConfig:
             sliding_window=cfg.get("sliding_window") or -1 if cfg.get("use_sliding_window", False) else -1,
             num_experts=cfg.get("num_experts", cfg.get("num_local_experts", 0)) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
-            moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
+            # Mixtral has no separate field: its intermediate_size is the expert FFN width
+            moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mt == "mixtral" else 0),
             norm_topk_prob=cfg.get("norm_topk_prob", True),
             quantization=quant,
             dtype=str(cfg.get("torch_dtype", "bfloat16")),

@@ -148,14 +148,19 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         if L + "self_attn.q_norm.weight" in names:
             att[P + "q_norm"] = w(L + "self_attn.q_norm.weight")
             att[P + "k_norm"] = w(L + "self_attn.k_norm.weight")
-        if cfg.is_moe and L + "mlp.gate.weight" in names:
-            att[P + "router"] = w(L + "mlp.gate.weight")
+        mixtral = L + "block_sparse_moe.gate.weight" in names      # Mixtral names: w1 = gate, w3 = up, w2 = down
+        if cfg.is_moe and (L + "mlp.gate.weight" in names or mixtral):
+            att[P + "router"] = w(L + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight"))
             E = cfg.num_experts
             experts = range(r * (E // T), (r + 1) * (E // T)) if (ep and T > 1) else range(E)
             gus, downs = [], []
             for e in experts:
-                X = f"{L}mlp.experts.{e}."
-                g, u, dn = w(X + "gate_proj.weight"), w(X + "up_proj.weight"), w(X + "down_proj.weight")
+                if mixtral:
+                    X = f"{L}block_sparse_moe.experts.{e}."
+                    g, u, dn = w(X + "w1.weight"), w(X + "w3.weight"), w(X + "w2.weight")
+                else:
+                    X = f"{L}mlp.experts.{e}."
+                    g, u, dn = w(X + "gate_proj.weight"), w(X + "up_proj.weight"), w(X + "down_proj.weight")
                 if not ep:
                     g, u, dn = Shard(g, 0, r, T), Shard(u, 0, r, T), Shard(dn, 1, r, T)
                 gus.append(Interleave(g, u))

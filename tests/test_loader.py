@@ -157,3 +157,36 @@ def test_phi3_fused_projections_load_like_split_ones(tmp_path):
         _, b = loader.load_checkpoint(fused_dir, "cpu", tp, rank, dtype="float32")
         for la, lb in zip(a["layers"], b["layers"]):
             assert torch.equal(la["wqkv"], lb["wqkv"]) and torch.equal(la["w_gate_up"], lb["w_gate_up"])
+
+
+def test_mixtral_tensor_names(tmp_path):
+    """block_sparse_moe.{gate, experts.N.w1/w3/w2} (Mixtral) load like mlp.{gate, experts.N.gate/up/down_proj}."""
+    import json as _json
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    from pie_b200.models import loader
+    from pie_b200.models.config import preset
+    from pie_b200.models.weights import random_weights
+    cfg = preset("tiny-qwen3-moe")
+    w = random_weights(cfg, "cpu", torch.float32, seed=2)
+    a_dir, b_dir = tmp_path / "qwen", tmp_path / "mixtral"
+    loader.export_hf_checkpoint(cfg, w, a_dir)
+    b_dir.mkdir()
+    out = {}
+    with safe_open(str(a_dir / "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            nk = (k.replace("mlp.gate.weight", "block_sparse_moe.gate.weight")
+                   .replace("mlp.experts.", "block_sparse_moe.experts.")
+                   .replace("gate_proj", "w1").replace("up_proj", "w3").replace("down_proj", "w2"))
+            out[nk] = f.get_tensor(k)
+    save_file(out, str(b_dir / "model.safetensors"))
+    hf = _json.loads((a_dir / "config.json").read_text())
+    hf.update(model_type="mixtral", num_local_experts=hf.pop("num_experts"), intermediate_size=hf.pop("moe_intermediate_size"))
+    hf["qk_norm"] = False
+    (b_dir / "config.json").write_text(_json.dumps(hf))
+    cfg_b, wb = loader.load_checkpoint(b_dir, "cpu", dtype="float32")
+    _, wa = loader.load_checkpoint(a_dir, "cpu", dtype="float32")
+    assert cfg_b.num_experts == cfg.num_experts and cfg_b.moe_intermediate_size == cfg.moe_intermediate_size
+    for la, lb in zip(wa["layers"], wb["layers"]):
+        assert torch.equal(la["experts_gate_up"], lb["experts_gate_up"]) and torch.equal(la["router"], lb["router"])
+        assert torch.equal(la["experts_down"], lb["experts_down"])
