@@ -22,7 +22,7 @@ import os
 import sys
 import time
 
-REFERENCE_UNAVAILABLE = ("pip cannot install /root/reference (a Rust/C++ workspace without setup.py or "
+REFERENCE_UNAVAILABLE = ("pip cannot install the reference (a Rust/C++ workspace without setup.py or "
                          "pyproject.toml); cargo/rustc, wasmtime and the CPM-fetched C++ dependencies are absent offline")
 
 
