@@ -23,6 +23,8 @@ namespace pie {
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table,
                                     bf16* __restrict__ out, int hidden, int vocab_start,
                                     int vocab_count) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t] - vocab_start;
     const int nvec = hidden >> 3;
@@ -256,7 +258,7 @@ PIE_API int pie_embed_gather(const int* tokens, const void* table, void* out, in
                              int hidden, int vocab_start, int vocab_count, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hidden % 8) return (int)cudaErrorInvalidValue;
-    embed_gather_kernel<<<n_tokens, 128, 0, st>>>(tokens, (const bf16*)table, (bf16*)out, hidden,
+    launch_pdl(embed_gather_kernel, dim3(n_tokens), dim3(128), 0, st, tokens, (const bf16*)table, (bf16*)out, hidden,
                                                   vocab_start, vocab_count);
     return (int)cudaGetLastError();
 }

@@ -46,8 +46,6 @@ async def main(args):
             history.append(t)
         tokens.extend(new)
         pending = new[-1:]
-        if acc < len(draft):
-            # KV of the rejected drafts is still in the working tail: drop it
-            ctx.truncate(len(draft) - acc)
+        # the runtime appended the accepted prefix only; rejected drafts leave no KV behind
     ctx.release()
     return json.dumps({"tokens": tokens[:max_tokens], "passes": passes, "accepted_drafts": accepted_total})

@@ -238,3 +238,50 @@ def test_mcp_tool_call_is_grammar_constrained_and_executed(eng):
         eng.mcp_servers.pop("tools")
     assert out["call"]["name"] in ("add", "mul") and set(out["call"]["arguments"]) == {"a", "b"}
     assert calls and calls[0]["name"] == out["call"]["name"] and out["result"]["ok"]
+
+
+def test_reasoning_style_inferlets(eng):
+    t = json.loads(run(eng, "tree-of-thought", {"prompt_tokens": PROMPT, "depth": 2, "branching": 2, "beam": 2,
+                                                "thought_tokens": 3}))
+    assert t["levels"] == 2 and len(t["best_path"]) == 2 and t["best_score"] <= 0
+    s = json.loads(run(eng, "skeleton-of-thought", {"prompt_tokens": PROMPT, "points": 2, "skeleton_tokens": 6,
+                                                    "point_tokens": 3}))
+    assert len(s["points"]) == 2
+    c = json.loads(run(eng, "demo-self-correct", {"prompt_tokens": PROMPT, "max_tokens": 4}))
+    assert set(c) == {"draft", "critique", "final"}
+    assert eng.model_status()["models"]["tiny-llama"]["kv_pages_used"] == 0
+
+
+def test_jacobi_decoding_equals_greedy(eng):
+    ref = json.loads(run(eng, "text-completion", {"prompt_tokens": PROMPT, "max_tokens": 16, "stop_tokens": []}))["tokens"]
+    j = json.loads(run(eng, "jacobi-decoding", {"prompt_tokens": PROMPT, "max_tokens": 16, "window": 3}))
+    assert j["tokens"] == ref and j["passes"] <= 16
+
+
+def test_agents_template_microbench_and_trim_bench(eng):
+    def server(method, params_json):
+        p = json.loads(params_json)
+        if method == "tools/list":
+            return json.dumps({"tools": [{"name": "lookup", "parameters": {"type": "object", "properties": {
+                "key": {"enum": ["a", "b"]}}, "required": ["key"]}}]})
+        return json.dumps({"value": p["arguments"]["key"] * 2})
+
+    eng.mcp_servers["tools"] = server
+    try:
+        r = json.loads(run(eng, "agent-react", {"prompt_tokens": PROMPT, "max_turns": 2, "max_tokens": 200}))
+    finally:
+        eng.mcp_servers.pop("tools")
+    assert 1 <= r["turns"] <= 2 and all(("call" in t) or ("finish" in t) for t in r["trace"])
+    sw = json.loads(run(eng, "agent-swarm", {"tasks": ["ab", "cd"]}))
+    assert [x["result"] for x in sw["results"]] == ["ba", "dc"]
+    tg = json.loads(run(eng, "template-generation", {"prompt_tokens": PROMPT}))
+    import re
+    assert re.fullmatch(r"[A-Z][a-z]{2,8}", tg["fields"]["Name"]) and tg["fields"]["Member"] in ("yes", "no")
+    mb = json.loads(run(eng, "wit-microbench", {"iters": 20}))
+    assert mb["context_fork_release_us"] > 0 and mb["empty_forward_us"] > 0
+    pt = json.loads(run(eng, "page-trim-bench", {"prompt_tokens": list(range(300, 430)), "window": 24, "steps": 3}))
+    assert pt["pages_trimmed"] > 0
+    h = json.loads(run(eng, "http-server", {"method": "POST", "path": "/complete",
+                                            "body": json.dumps({"prompt_tokens": PROMPT, "max_tokens": 3})}))
+    assert h["status"] == 200 and "completion" in json.loads(h["body"])
+    assert json.loads(run(eng, "http-server", {"method": "GET", "path": "/"}))["status"] == 200
