@@ -187,13 +187,13 @@ def ensure_gemm_workspace(device) -> None:
     import os
     if os.environ.get("PIE_GEMM_PAIRS", "1") == "0":
         set_gemm_pairs(False)
-    set_pdl(os.environ.get("PIE_PDL", "0") == "1")
+    set_pdl(os.environ.get("PIE_PDL", "1") != "0")
 
 
 def set_pdl(enabled: bool) -> None:
     """Programmatic dependent launch for the library's kernels: a kernel's prologue and weight
     prefetch overlap the tail of its predecessor in the stream (also inside CUDA graphs).
-    Off unless PIE_PDL=1: measured gain is ~4 % of a 64-request decode step and nothing at 512."""
+    On unless PIE_PDL=0: measured 3.5 % of a 64-request decode step, 2 % at 128, neutral at 512."""
     check(fn("pie_set_pdl")(1 if enabled else 0), "set_pdl")
 
 
