@@ -303,3 +303,33 @@ def test_sample_topk_topp_distribution_is_renormalised_kept_set(k, p):
     probs = probs / probs.sum()
     freq = torch.bincount(got.long(), minlength=vocab).float() / draws
     assert float((freq - probs).abs().max()) < 0.02
+
+
+def test_bounded_peer_wait_times_out_and_reports_status():
+    """A wait on a peer flag that nothing sets gives up after its bound, records
+    PIE_ERR_WAIT_PEER (4) in the status word and returns; the context stays usable and
+    `check_kernel_status` raises and clears the word."""
+    import ctypes as C
+    import time
+    from pie_b200.ops import _lib
+    wait = _lib.declare("pie_tp_wait_ag", [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p])
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)          # never raised
+    epoch = torch.ones(1, dtype=torch.int32, device=DEV)           # the kernel expects flags >= 1
+    status = ops.kernel_status(DEV)
+    status.zero_()
+    t0 = time.time()
+    _lib.check(wait(flags.data_ptr(), epoch.data_ptr(), 2, status.data_ptr(), _lib.stream_ptr()), "tp_wait_ag")
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 10.0
+    assert int(status.item()) == 4
+    with pytest.raises(_lib.KernelLibraryError):
+        ops.check_kernel_status(DEV)
+    assert int(status.item()) == 0
+    # the device still works
+    x = torch.ones(1024, device=DEV)
+    assert float(x.sum()) == 1024.0
+    # and a wait whose flags are already up returns at once with a clean status
+    flags.fill_(1)
+    _lib.check(wait(flags.data_ptr(), epoch.data_ptr(), 2, status.data_ptr(), _lib.stream_ptr()), "tp_wait_ag")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
