@@ -398,7 +398,8 @@ class TorchDriver:
         rows = np.asarray(req.slot_row, dtype=np.int32) if req.slot_row is not None else np.zeros(0, np.int32)
         if self.cuda:
             group = self.model.hq // self.model.hkv
-            tile_req, tile_q = ops.plan_prefill_tiles(np.asarray(req.qo_indptr), group)
+            tile_rows = ops.prefill_tile_rows(self.model.hq, self.model.hkv, self.model.cfg.head_dim, self.page_size)
+            tile_req, tile_q = ops.plan_prefill_tiles(np.asarray(req.qo_indptr), group, tile_rows)
             nt = len(tile_req)
             s.h("tile_req")[:nt], s.h("tile_qstart")[:nt] = tile_req, tile_q
             s.h("logit_rows")[:len(rows)] = rows
@@ -415,7 +416,8 @@ class TorchDriver:
                 mask_bits = torch.cat(parts) if parts else None
                 mask_indptr = torch.tensor(indptr, dtype=torch.int64, device=self.device)
             plan = ops.PrefillPlan(s.d("page_indices"), s.d("kv_page_indptr"), s.d("qo_indptr"), s.d("kv_lens"),
-                                   s.d("tile_req"), s.d("tile_qstart"), nt, self.page_size, mask_bits, mask_indptr)
+                                   s.d("tile_req"), s.d("tile_qstart"), nt, self.page_size, mask_bits, mask_indptr,
+                                   tile_rows=tile_rows)
             fi = ForwardInputs(s.d("tokens", n), s.d("positions", n), s.d("slots", n), plan,
                                logit_rows=s.d("logit_rows", len(rows)), is_decode=False)
         else:

@@ -7,6 +7,7 @@ tensors raises :class:`pie_b200.ops._lib.KernelLibraryError`.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -482,9 +483,18 @@ def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items
     return item_req, start.astype(np.int32), end.astype(np.int32), indptr
 
 
-def plan_prefill_tiles(qo_indptr: np.ndarray, group: int):
-    """Tiles of 64/group query tokens per request: (tile_req, tile_qstart)."""
-    tq = max(1, 64 // group)
+def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int) -> int:
+    """Packed (token, head) rows per prefill tile: 128 where the tcgen05 kernel covers the shape
+    (head_dim 128, 16-token pages, group size dividing 128) and ``PIE_PREFILL_TC=1`` asks for it,
+    else the 64 rows of the mma.sync kernel."""
+    if os.environ.get("PIE_PREFILL_TC", "0") != "1":
+        return 64
+    return 128 if fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size) else 64
+
+
+def plan_prefill_tiles(qo_indptr: np.ndarray, group: int, rows: int = 64):
+    """Tiles of rows/group query tokens per request: (tile_req, tile_qstart)."""
+    tq = max(1, rows // group)
     qlens = np.diff(qo_indptr).astype(np.int64)
     ntiles = -(-qlens // tq)
     tile_req = np.repeat(np.arange(len(qlens), dtype=np.int32), ntiles)
@@ -542,6 +552,7 @@ class PrefillPlan:
     mask_bits: Optional[torch.Tensor] = None
     mask_word_indptr: Optional[torch.Tensor] = None
     window_left: int = -1
+    tile_rows: int = 64           # 128: tiles planned for the tcgen05 kernel
 
 
 def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out=None, lse_out=None):
@@ -549,6 +560,15 @@ def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out
         out = torch.empty_like(q)
     n, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    if plan.tile_rows == 128:
+        # kv_layer is [pages + 1, 2, hkv, page, d]; its last page is the zero pad page
+        check(fn("pie_paged_prefill_attn_tc")(
+            ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
+            ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
+            ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), n, hq, hkv,
+            kv_layer.shape[0], sm_scale, plan.window_left, ptr(kernel_status(q.device)), stream_ptr()),
+            "paged_prefill_attn_tc")
+        return out
     check(fn("pie_paged_prefill_attn")(
         ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
         ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
@@ -574,8 +594,8 @@ def pack_masks(masks, kv_lens, device):
             torch.from_numpy(np.asarray(indptr, dtype=np.int64)).to(device))
 
 
-def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device) -> PrefillPlan:
-    tile_req, tile_qstart = plan_prefill_tiles(batch.qo_indptr, group)
+def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device, tile_rows: int = 64) -> PrefillPlan:
+    tile_req, tile_qstart = plan_prefill_tiles(batch.qo_indptr, group, tile_rows)
     mask_bits = mask_indptr = None
     if batch.masks is not None:
         masks = []
@@ -590,7 +610,7 @@ def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device) -> 
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(device)
     return PrefillPlan(t(batch.page_indices), t(batch.kv_page_indptr), t(batch.qo_indptr),
                        t(batch.kv_lens), t(tile_req), t(tile_qstart), len(tile_req), page_size,
-                       mask_bits, mask_indptr, batch.window_left)
+                       mask_bits, mask_indptr, batch.window_left, tile_rows)
 
 
 def paged_attention_cpu(q, kv_layer, batch: AttnBatch, sm_scale: float):

@@ -129,12 +129,17 @@ def test_paged_decode_attention(d, hq, hkv):
     close(out, want, 2e-2)
 
 
-@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (128, 8, 1), (64, 4, 2)])
+@pytest.mark.parametrize("d,hq,hkv,rows", [(128, 32, 8, 64), (128, 8, 1, 64), (64, 4, 2, 64),
+                                           (128, 32, 8, 128), (128, 8, 1, 128), (128, 4, 4, 128),
+                                           (128, 32, 2, 128), (128, 8, 4, 128)])
 @pytest.mark.parametrize("mode", ["causal", "custom", "window"])
-def test_paged_prefill_attention(d, hq, hkv, mode):
+def test_paged_prefill_attention(d, hq, hkv, rows, mode):
+    """rows = 64: the mma.sync kernel; rows = 128: the tcgen05 kernel (head_dim 128, 16-token pages)."""
     page = 16
-    qlens = np.array([1, 5, 64, 130, 17], dtype=np.int32)
-    prev = np.array([40, 0, 0, 200, 31], dtype=np.int32)
+    if rows == 128:
+        assert ops._lib.fn("pie_prefill_attn_tc_supported")(hq, hkv, d, page) == 1
+    qlens = np.array([1, 5, 64, 130, 17, 700], dtype=np.int32)
+    prev = np.array([40, 0, 0, 200, 31, 333], dtype=np.int32)
     kv_lens = qlens + prev
     r = len(qlens)
     kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=21)
@@ -153,10 +158,11 @@ def test_paged_prefill_attention(d, hq, hkv, mode):
     if mode == "window":
         window = 37
     batch = ops.AttnBatch(qo, indptr, pages, kv_lens, masks, window)
-    plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV)
+    plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV, tile_rows=rows)
     scale = 1 / math.sqrt(d)
     lse = torch.empty(int(qo[-1]), hq, device=DEV)
     out = ops.paged_prefill_attention(q, kv, plan, scale, lse_out=lse)
+    ops.check_kernel_status(DEV)
     tmasks = None if masks is None else [None if m is None else torch.from_numpy(m) for m in masks]
     want, want_lse = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
                                          masks=tmasks, window_left=window, return_lse=True)
