@@ -1,18 +1,22 @@
 // Paged prefill attention on the 5th-generation tensor cores (head_dim 128, 16-token pages).
 //
-// One CTA per (tile of 128 packed query rows, KV head); a row is (query token, head within the
-// GQA group), so a tile covers 128 / G tokens of one request. KV is walked in blocks of 64 keys:
-//   warp 0      TMA producer: the Q tile once (3-D box over [tokens, heads, d]); per block the K
+// One CTA per (tile of 128 or 256 packed query rows, KV head); a row is (query token, head within
+// the GQA group), so a CTA covers 128 / G or 256 / G tokens of one request as one or two MMA tiles of
+// 128 rows that share the K/V stages. KV is walked in blocks of 64 keys:
+//   warp 0      TMA producer: the Q tiles once (3-D boxes over [tokens, heads, d]); per block the K
 //               and V rows of its four pages (2-D boxes of 16 rows x 64 columns, 128-byte
 //               swizzle) into a ring of stages; pages past the end come from the cache's pad page
 //   warp 1      tcgen05.mma issuer: S = Q K^T (128 x 64, K-major operands) into one of two TMEM
-//               buffers, then O_blk = P V (128 x 128; P from shared memory, V as an MN-major
-//               operand straight from its [key, d] tile) into one of two more
-//   warps 2-5   softmax, one row per thread: S from TMEM, mask (causal / window / custom bits),
-//               running max and sum, P as bf16 into a swizzled shared-memory tile for the next
-//               MMA, and the running output in registers: O = (O + O_blk) * alpha per block
-// The score and output MMAs of neighbouring blocks overlap the softmax through the double
-// buffers. Every wait is bounded; on a time-out the kernel records a status word and leaves.
+//               buffers per tile, then O += P V (128 x 128; P from shared memory, V as an MN-major
+//               operand straight from its [key, d] tile) into the tile's TMEM accumulator
+//   4 warps per tile: softmax, one row per thread: S from TMEM, mask (causal / window / custom bits;
+//               skipped for blocks fully inside the causal region), exponentials against a
+//               reference maximum, P as bf16 into a swizzled shared-memory tile for the PV MMA.
+//               The reference maximum follows the true one lazily: only when a block maximum
+//               outgrows it by 2^8 does the warp rescale its rows of O in TMEM (tcgen05.ld / st),
+//               so most blocks cost one exp per score and no pass over O.
+// The score MMA of block j + 1 overlaps the softmax of block j through the S double buffer.
+// Every wait is bounded; on a time-out the kernel records a status word and leaves.
 //
 // Replaces the FlashInfer FA2 paged prefill kernel the reference calls
 // (driver/cuda/src/ops/attention_flashinfer.cu:848, plans :612,:1075) and this library's own
@@ -22,17 +26,23 @@
 namespace pie {
 using namespace sm100;
 
-constexpr int AT_ROWS = 128;     // packed query rows per tile
+constexpr int AT_ROWS = 128;     // packed query rows per MMA tile
 constexpr int AT_BK = 64;        // keys per block
 constexpr int AT_D = 128;
 constexpr int AT_STAGES = 3;
-constexpr int AT_THREADS = 192;
 constexpr uint32_t AT_Q_BYTES = AT_ROWS * AT_D * 2;            // two 16 KB halves
 constexpr uint32_t AT_KV_TILE = AT_BK * AT_D * 2;              // 16 KB: two 8 KB halves [64 keys x 64 d]
 constexpr uint32_t AT_STAGE_BYTES = 2 * AT_KV_TILE;            // K then V
 constexpr uint32_t AT_P_BYTES = AT_ROWS * AT_BK * 2;           // 16 KB
-constexpr uint32_t AT_SMEM = AT_Q_BYTES + AT_STAGES * AT_STAGE_BYTES + 2 * AT_P_BYTES + 1024 + 512;
-constexpr uint32_t AT_TMEM_COLS = 512;                          // S[2] x 64 + O_blk[2] x 128 = 384 -> 512
+constexpr int AT_TILE_BARS = 9;                                // s_full[2] s_empty[2] p_full[2] p_empty[2] pv_done
+constexpr float AT_RESCALE_LOG2 = 8.f;                         // the reference maximum may lag the true one by 2^8
+
+template <int NT>
+struct AtCfg {
+    static constexpr int THREADS = 64 + 128 * NT;
+    static constexpr uint32_t SMEM = NT * AT_Q_BYTES + AT_STAGES * AT_STAGE_BYTES + NT * 2 * AT_P_BYTES + 1024 + 512;
+    static constexpr uint32_t TMEM_COLS = 256 * NT;             // per tile: S[2] x 64 columns, O x 128
+};
 
 // K-major SW128 descriptor is make_smem_desc_sw128 (tcgen05.cuh). MN-major SW128: the contiguous
 // dimension is N (64 elements = one 128-byte row), 8 K-rows form a 1024-byte group (stride field),
@@ -57,9 +67,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
         "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
-template <int G>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// G = query heads per KV head; NT = MMA tiles of 128 rows per CTA (they share the K/V stages).
+template <int G, int NT>
+__global__ void __launch_bounds__(AtCfg<NT>::THREADS, 1)
 paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv,
                              const int* __restrict__ page_indices, const int* __restrict__ kv_page_indptr,
                              const int* __restrict__ qo_indptr, const int* __restrict__ kv_lens,
@@ -67,26 +83,26 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                              const uint32_t* __restrict__ mask_bits, const long* __restrict__ mask_word_indptr,
                              bf16* __restrict__ out, float* __restrict__ lse_out, int hq, int hkv, int pad_page,
                              float scale_log2, int window_left, int* status) {
-    constexpr int TQ = AT_ROWS / G;
+    constexpr int TQ = AT_ROWS / G;          // query tokens per MMA tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t q_s = base;
-    const uint32_t kv_s = q_s + AT_Q_BYTES;
+    const uint32_t kv_s = q_s + NT * AT_Q_BYTES;
     const uint32_t p_s = kv_s + AT_STAGES * AT_STAGE_BYTES;
-    const uint32_t bar0 = p_s + 2 * AT_P_BYTES;
-    // barriers: q_full, kv_full[ST], kv_empty[ST], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2]
+    const uint32_t bar0 = p_s + NT * 2 * AT_P_BYTES;
     auto q_full = [&]() { return bar0; };
     auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bar0 + 8u * (1 + AT_STAGES + s); };
-    auto s_full = [&](int b) { return bar0 + 8u * (1 + 2 * AT_STAGES + b); };
-    auto s_empty = [&](int b) { return bar0 + 8u * (3 + 2 * AT_STAGES + b); };
-    auto p_full = [&](int b) { return bar0 + 8u * (5 + 2 * AT_STAGES + b); };
-    auto p_empty = [&](int b) { return bar0 + 8u * (7 + 2 * AT_STAGES + b); };
-    auto o_full = [&](int b) { return bar0 + 8u * (9 + 2 * AT_STAGES + b); };
-    auto o_empty = [&](int b) { return bar0 + 8u * (11 + 2 * AT_STAGES + b); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + (bar0 - base) + 8u * (13 + 2 * AT_STAGES));
+    auto tbar = [&](int t, int i) { return bar0 + 8u * (1 + 2 * AT_STAGES + t * AT_TILE_BARS + i); };
+    auto s_full = [&](int t, int b) { return tbar(t, b); };
+    auto s_empty = [&](int t, int b) { return tbar(t, 2 + b); };
+    auto p_full = [&](int t, int b) { return tbar(t, 4 + b); };
+    auto p_empty = [&](int t, int b) { return tbar(t, 6 + b); };
+    auto pv_done = [&](int t) { return tbar(t, 8); };
+    volatile uint32_t* tmem_slot =
+        reinterpret_cast<volatile uint32_t*>(base_ptr + (bar0 - base) + 8u * (1 + 2 * AT_STAGES + NT * AT_TILE_BARS));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, h = blockIdx.y;
@@ -96,9 +112,21 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
     const int kv_len = kv_lens[req];
     const int* pages = page_indices + kv_page_indptr[req];
     const bool custom = mask_bits != nullptr;
-    const int last_q = min(qstart + TQ, qo_len) - 1;
-    const int kv_hi = custom ? kv_len : max(0, min(kv_len, kv_len - qo_len + last_q + 1));
-    const int nkb = (kv_hi + AT_BK - 1) / AT_BK;
+    // keys visible to MMA tile t: up to the causal limit of its last query token
+    auto tile_kv_hi = [&](int t) {
+        const int first = qstart + t * TQ;
+        if (first >= qo_len) return 0;
+        const int last_q = min(first + TQ, qo_len) - 1;
+        return custom ? kv_len : max(0, min(kv_len, kv_len - qo_len + last_q + 1));
+    };
+    int nkb_t[NT], nkb = 0, kv_hi = 0;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int hi = tile_kv_hi(t);
+        nkb_t[t] = (hi + AT_BK - 1) / AT_BK;
+        nkb = max(nkb, nkb_t[t]);
+        kv_hi = max(kv_hi, hi);
+    }
     const int npages = (kv_hi + 15) >> 4;
 
     if (threadIdx.x == 0) {
@@ -107,51 +135,59 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(s_full(b), 1);
-            mbar_init(s_empty(b), 4);
-            mbar_init(p_full(b), 4);
-            mbar_init(p_empty(b), 1);
-            mbar_init(o_full(b), 1);
-            mbar_init(o_empty(b), 4);
+        for (int t = 0; t < NT; ++t) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(s_full(t, b), 1);
+                mbar_init(s_empty(t, b), 4);
+                mbar_init(p_full(t, b), 4);
+                mbar_init(p_empty(t, b), 1);
+            }
+            mbar_init(pv_done(t), 1);
         }
         fence_barrier_init();
         fence_proxy_async();
     }
     if (warp == 1) {
-        tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_slot)), AT_TMEM_COLS);
+        tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_slot)), AtCfg<NT>::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tm_s = tmem_base;                // S buffers: columns [0, 64) and [64, 128)
-    const uint32_t tm_o = tmem_base + 128;          // O_blk buffers: columns [128, 256) and [256, 384)
 
     if (warp == 0) {
         if (lane == 0 && nkb > 0) {
             tma_prefetch_desc(&tma_q);
             tma_prefetch_desc(&tma_kv);
-            mbar_arrive_expect_tx(q_full(), AT_Q_BYTES);
-            tma_load_3d(q_s, &tma_q, q_full(), 0, h * G, q_base + qstart);
-            tma_load_3d(q_s + AT_Q_BYTES / 2, &tma_q, q_full(), 64, h * G, q_base + qstart);
+            mbar_arrive_expect_tx(q_full(), NT * AT_Q_BYTES);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                tma_load_3d(q_s + t * AT_Q_BYTES, &tma_q, q_full(), 0, h * G, q_base + qstart + t * TQ);
+                tma_load_3d(q_s + t * AT_Q_BYTES + AT_Q_BYTES / 2, &tma_q, q_full(), 64, h * G, q_base + qstart + t * TQ);
+            }
             bool ok = true;
             for (int j = 0; j < nkb && ok; ++j) {
                 const int s = j % AT_STAGES;
                 if (!mbar_wait(kv_empty(s), ((j / AT_STAGES) & 1u) ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
                 mbar_arrive_expect_tx(kv_full(s), AT_STAGE_BYTES);
                 const uint32_t kdst = kv_s + s * AT_STAGE_BYTES;
+                int pg_id[4];
+#pragma unroll
                 for (int pg = 0; pg < 4; ++pg) {
                     const int pi = j * 4 + pg;
-                    const int page = pi < npages ? pages[pi] : pad_page;
-                    const int krow = ((page * 2) * hkv + h) * 16;
-                    const int vrow = ((page * 2 + 1) * hkv + h) * 16;
+                    pg_id[pg] = pi < npages ? pages[pi] : pad_page;
+                }
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
+                for (int pg = 0; pg < 4; ++pg) {
+                    const int krow = ((pg_id[pg] * 2) * hkv + h) * 16;
+                    const int vrow = ((pg_id[pg] * 2 + 1) * hkv + h) * 16;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
                         tma_load_2d(kdst + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, kv_full(s), half * 64, krow);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
                         tma_load_2d(kdst + AT_KV_TILE + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, kv_full(s), half * 64, vrow);
-                    }
                 }
             }
             // no copy may be in flight when the CTA exits
@@ -164,154 +200,189 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
             constexpr uint32_t idesc_s = make_idesc_bf16(AT_ROWS, AT_BK);
             constexpr uint32_t idesc_o = make_idesc_bf16_bmn(AT_ROWS, AT_D);
             bool ok = mbar_wait(q_full(), 0, status, PIE_ERR_WAIT_TMA);
+            // O_t += P_t,j V_j; frees the P buffer, and (after the last tile) the K/V stage of block j
             auto issue_pv = [&](int j) {
                 const int s = j % AT_STAGES;
                 const uint32_t b = j & 1u, ph = (j >> 1) & 1u;
-                if (!mbar_wait(p_full(b), ph, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; return; }
-                if (!mbar_wait(o_empty(b), ph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; return; }
-                tc_fence_after();
                 const uint32_t v_addr = kv_s + s * AT_STAGE_BYTES + AT_KV_TILE;
-                const uint32_t p_addr = p_s + b * AT_P_BYTES;
 #pragma unroll
-                for (int k = 0; k < AT_BK / 16; ++k) {
-                    const uint64_t adesc = make_smem_desc_sw128(p_addr) + 2u * k;                       // 16 keys = 32 bytes along a P row
-                    const uint64_t bdesc = make_smem_desc_sw128_mn(v_addr + k * 2048, AT_KV_TILE / 2);  // 16 keys = two 8-row groups
-                    umma_bf16(tm_o + b * AT_D, adesc, bdesc, idesc_o, k != 0);
+                for (int t = 0; t < NT; ++t) {
+                    if (j >= nkb_t[t] || !ok) continue;
+                    if (!mbar_wait(p_full(t, b), ph, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; continue; }
+                    tc_fence_after();
+                    const uint32_t p_addr = p_s + (t * 2 + b) * AT_P_BYTES;
+#pragma unroll
+                    for (int k = 0; k < AT_BK / 16; ++k) {
+                        const uint64_t adesc = make_smem_desc_sw128(p_addr) + 2u * k;                       // 16 keys = 32 bytes along a P row
+                        const uint64_t bdesc = make_smem_desc_sw128_mn(v_addr + k * 2048, AT_KV_TILE / 2);  // 16 keys = two 8-row groups
+                        umma_bf16(tmem_base + t * 256 + 128, adesc, bdesc, idesc_o, (j | k) != 0);
+                    }
+                    umma_commit(pv_done(t));
+                    umma_commit(p_empty(t, b));
                 }
-                umma_commit(o_full(b));
                 umma_commit(kv_empty(s));
-                umma_commit(p_empty(b));
             };
             for (int j = 0; j < nkb && ok; ++j) {
                 const int s = j % AT_STAGES;
                 const uint32_t b = j & 1u, ph = (j >> 1) & 1u;
                 if (!mbar_wait(kv_full(s), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
-                if (!mbar_wait(s_empty(b), ph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; break; }
-                tc_fence_after();
                 const uint32_t k_addr = kv_s + s * AT_STAGE_BYTES;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const uint64_t adesc = make_smem_desc_sw128(q_s + half * (AT_Q_BYTES / 2));
-                    const uint64_t bdesc = make_smem_desc_sw128(k_addr + half * (AT_KV_TILE / 2));
+                for (int t = 0; t < NT; ++t) {
+                    if (j >= nkb_t[t] || !ok) continue;
+                    if (!mbar_wait(s_empty(t, b), ph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; continue; }
+                    tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(tm_s + b * AT_BK, adesc + 2u * k, bdesc + 2u * k, idesc_s, (half | k) != 0);
+                    for (int half = 0; half < 2; ++half) {
+                        const uint64_t adesc = make_smem_desc_sw128(q_s + t * AT_Q_BYTES + half * (AT_Q_BYTES / 2));
+                        const uint64_t bdesc = make_smem_desc_sw128(k_addr + half * (AT_KV_TILE / 2));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(tmem_base + t * 256 + b * AT_BK, adesc + 2u * k, bdesc + 2u * k, idesc_s, (half | k) != 0);
+                    }
+                    umma_commit(s_full(t, b));
                 }
-                umma_commit(s_full(b));
-                if (j >= 1) issue_pv(j - 1);
+                if (j >= 1 && ok) issue_pv(j - 1);
             }
             if (ok) issue_pv(nkb - 1);
         }
     } else {
-        // ------------------------------------------------------------ softmax + output (thread = row)
-        const int q4 = warp & 3;
+        // ---------------------------------------------- softmax warps: thread = row of MMA tile t
+        const int t = (warp - 2) >> 2;
+        const int q4 = warp & 3;                        // the TMEM lane quarter this warp may access
         const int row = q4 * 32 + lane;
-        const int qtok = qstart + row / G;
+        const int qtok = qstart + t * TQ + row / G;
         const bool valid = qtok < qo_len;
         const int lim = valid ? (custom ? kv_len : kv_len - qo_len + qtok + 1) : 0;
         const int lo = (window_left >= 0 && valid) ? max(0, kv_len - qo_len + qtok - window_left) : 0;
         const int mask_words = (kv_len + 31) >> 5;
         const uint32_t* row_mask = (custom && valid) ? mask_bits + mask_word_indptr[req] + (size_t)qtok * mask_words : nullptr;
-        const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-        float o[AT_D];
-#pragma unroll
-        for (int c = 0; c < AT_D; ++c) o[c] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        const uint32_t tm_t = tmem_base + t * 256 + ((uint32_t)(q4 * 32) << 16);
+        const uint32_t tm_o = tm_t + 128;
+        const float thr_raw = AT_RESCALE_LOG2 / scale_log2;
+        const int my_nkb = NT == 1 ? nkb : (t == 0 ? nkb_t[0] : nkb_t[NT - 1]);
+        float m_ref = -INFINITY, l = 0.f;    // exponents are taken against m_ref (raw score units)
         bool ok = true;
-        auto fold_o = [&](int j, float alpha) {
-            // o = (o + O_blk_j) * alpha
+        for (int j = 0; j < my_nkb && ok; ++j) {
             const uint32_t b = j & 1u, ph = (j >> 1) & 1u;
-            const bool got = mbar_wait(o_full(b), ph, status, PIE_ERR_WAIT_MMA);
-            if (!__all_sync(0xffffffffu, got)) { ok = false; return; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < AT_D / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tm_o + lane_base + b * AT_D + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(v[i])) * alpha;
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty(b));
-        };
-        for (int j = 0; j < nkb && ok; ++j) {
-            const uint32_t b = j & 1u, ph = (j >> 1) & 1u;
-            const bool got = mbar_wait(s_full(b), ph, status, PIE_ERR_WAIT_MMA);
+            const bool got = mbar_wait(s_full(t, b), ph, status, PIE_ERR_WAIT_MMA);
             if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
             tc_fence_after();
             float sv[AT_BK];
 #pragma unroll
             for (int c = 0; c < AT_BK / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld_32x32(tm_s + lane_base + b * AT_BK + c * 32, v);
+                tmem_ld_32x32(tm_t + b * AT_BK + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(v[i]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(b));
-            // mask and running max
+            if (lane == 0) mbar_arrive(s_empty(t, b));
             const int kb0 = j * AT_BK;
-            uint32_t mw0 = 0xffffffffu, mw1 = 0xffffffffu;
-            if (row_mask) {
-                mw0 = row_mask[kb0 >> 5];
-                mw1 = (kb0 + 32 < kv_len) ? row_mask[(kb0 >> 5) + 1] : 0u;
-            }
-            float bm = -INFINITY;
+            const bool inner = !custom && kb0 + AT_BK <= lim && kb0 >= lo;
+            if (!__all_sync(0xffffffffu, inner)) {
+                // 64-bit allow mask of this row for the block
+                const int n = lim - kb0, nl = lo - kb0;
+                unsigned long long allow = n >= 64 ? ~0ull : (n <= 0 ? 0ull : ((1ull << n) - 1ull));
+                if (nl > 0) allow &= nl >= 64 ? 0ull : ~((1ull << nl) - 1ull);
+                if (row_mask && allow) {
+                    const unsigned long long w0 = row_mask[kb0 >> 5];
+                    const unsigned long long w1 = (kb0 + 32 < kv_len) ? row_mask[(kb0 >> 5) + 1] : 0u;
+                    allow &= w0 | (w1 << 32);
+                }
 #pragma unroll
-            for (int i = 0; i < AT_BK; ++i) {
-                const int key = kb0 + i;
-                const bool allow = key < lim && key >= lo && (((i < 32 ? mw0 : mw1) >> (i & 31)) & 1u);
-                sv[i] = allow ? sv[i] * scale_log2 : -INFINITY;
-                bm = fmaxf(bm, sv[i]);
+                for (int i = 0; i < AT_BK; ++i)
+                    if (!((allow >> i) & 1ull)) sv[i] = -INFINITY;
             }
-            const float m_new = fmaxf(m, bm);
-            const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m - m_new);   // m = -inf, m_new finite -> 0
-            float psum = 0.f;
+            float bm0 = sv[0], bm1 = sv[1], bm2 = sv[2], bm3 = sv[3];
+#pragma unroll
+            for (int i = 4; i < AT_BK; i += 4) {
+                bm0 = fmaxf(bm0, sv[i]);
+                bm1 = fmaxf(bm1, sv[i + 1]);
+                bm2 = fmaxf(bm2, sv[i + 2]);
+                bm3 = fmaxf(bm3, sv[i + 3]);
+            }
+            const float bm = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
+            // the reference maximum moves only when a row's block maximum outgrows it by 2^8: the
+            // accumulator in TMEM is then rescaled by the warp (tcgen05.ld/st are warp-wide)
+            const bool grow = bm > m_ref + thr_raw;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_ref, bm);
+                const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_ref - m_new) * scale_log2);
+                m_ref = m_new;
+                l *= alpha;
+                if (j > 0) {
+                    const bool done = mbar_wait(pv_done(t), (j - 1) & 1u, status, PIE_ERR_WAIT_MMA);
+                    if (!__all_sync(0xffffffffu, done)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < AT_D / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tm_o + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st_32x32(tm_o + c * 32, v);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            const float neg = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+            const bool freed = mbar_wait(p_empty(t, b), ph ^ 1u, status, PIE_ERR_WAIT_MMA);
+            if (!__all_sync(0xffffffffu, freed)) { ok = false; break; }
             // P row (64 bf16 = 128 bytes) into the swizzled tile: 16-byte chunk c of row r at r*128 + ((c ^ (r & 7)) << 4)
-            if (!mbar_wait(p_empty(b), ph ^ 1u, status, PIE_ERR_WAIT_MMA)) ok = false;
-            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-            uint8_t* prow = base_ptr + (p_s - base) + b * AT_P_BYTES + row * 128;
+            uint8_t* prow = base_ptr + (p_s - base) + (t * 2 + b) * AT_P_BYTES + row * 128;
+            float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 float pv[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float sx = sv[c * 8 + i];
-                    pv[i] = (sx == -INFINITY) ? 0.f : exp2f(sx - m_new);
-                }
-                // the sum uses the bf16-rounded values the MMA will see
-                bf16x8 pk = pack8(pv);
-                float pr[8];
-                unpack8(pk, pr);
+                for (int i = 0; i < 8; ++i) pv[i] = fast_exp2(__fmaf_rn(sv[c * 8 + i], scale_log2, neg));
 #pragma unroll
-                for (int i = 0; i < 8; ++i) psum += pr[i];
-                *reinterpret_cast<bf16x8*>(prow + ((c ^ (row & 7)) << 4)) = pk;
+                for (int i = 0; i < 8; i += 2) {
+                    ps0 += pv[i];
+                    ps1 += pv[i + 1];
+                }
+                *reinterpret_cast<bf16x8*>(prow + ((c ^ (row & 7)) << 4)) = pack8(pv);
             }
+            l += ps0 + ps1;
             fence_proxy_async();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(b));
-            l = l * alpha + psum;
-            m = m_new;
-            if (j >= 1) fold_o(j - 1, alpha);
+            if (lane == 0) mbar_arrive(p_full(t, b));
         }
-        if (ok && nkb > 0) fold_o(nkb - 1, 1.f);
-        if (valid && ok) {
+        if (ok && my_nkb > 0) {
+            // A parity wait tells apart only neighbouring phases. Having seen S of the last block, the
+            // barrier has passed phase my_nkb - 3 at least: wait for the last two phases in turn.
+            bool done = my_nkb < 2 || mbar_wait(pv_done(t), (my_nkb - 2) & 1u, status, PIE_ERR_WAIT_MMA);
+            done = done && mbar_wait(pv_done(t), (my_nkb - 1) & 1u, status, PIE_ERR_WAIT_MMA);
+            ok = __all_sync(0xffffffffu, done);
+        }
+        if (ok && my_nkb > 0) {
+            tc_fence_after();
             const int head = h * G + row % G;
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = out + ((size_t)(q_base + qtok) * hq + head) * AT_D;
+            bf16* dst = out + ((size_t)(q_base + (valid ? qtok : 0)) * hq + head) * AT_D;
 #pragma unroll
-            for (int c = 0; c < AT_D / 8; ++c) {
-                float t[8];
+            for (int c = 0; c < AT_D / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tm_o + c * 32, v);
+                tmem_ld_wait();
+                if (valid) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) t[i] = o[c * 8 + i] * inv;
-                *reinterpret_cast<bf16x8*>(dst + c * 8) = pack8(t);
+                    for (int i8 = 0; i8 < 4; ++i8) {
+                        float tv[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) tv[i] = __uint_as_float(v[i8 * 8 + i]) * inv;
+                        *reinterpret_cast<bf16x8*>(dst + c * 32 + i8 * 8) = pack8(tv);
+                    }
+                }
             }
-            if (lse_out)
-                lse_out[(size_t)(q_base + qtok) * hq + head] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            if (valid && lse_out)
+                lse_out[(size_t)(q_base + qtok) * hq + head] =
+                    l > 0.f ? (m_ref * scale_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
         }
     }
     tc_fence_before();
@@ -319,7 +390,7 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, AT_TMEM_COLS);
+        tmem_dealloc(tmem_base, AtCfg<NT>::TMEM_COLS);
     }
 }
 
@@ -351,18 +422,17 @@ PIE_API int pie_prefill_attn_tc_supported(int hq, int hkv, int head_dim, int pag
     return head_dim == 128 && page_size == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16) ? 1 : 0;
 }
 
-// Same contract as pie_paged_prefill_attn, with tiles of 128 / group query tokens
-// (pie_prefill_tc_tile_tokens) and `total_pages` = pages of kv_layer including the pad page (last).
-PIE_API int pie_prefill_tc_tile_tokens(int group) { return AT_ROWS / group; }
-
+// Same contract as pie_paged_prefill_attn, with tiles of tile_rows / group query tokens (tile_rows = 128 or
+// 256: one or two MMA tiles per CTA) and `total_pages` = pages of kv_layer including the pad page (last).
 PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const int* page_indices,
                                       const int* kv_page_indptr, const int* qo_indptr, const int* kv_lens,
                                       const int* tile_req, const int* tile_qstart, int num_tiles,
                                       const uint32_t* mask_bits, const long* mask_word_indptr, void* out,
                                       float* lse_out, int n_tokens, int hq, int hkv, int total_pages, float sm_scale,
-                                      int window_left, int* status, cudaStream_t st) {
+                                      int window_left, int tile_rows, int* status, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (!pie_prefill_attn_tc_supported(hq, hkv, AT_D, 16)) return (int)cudaErrorInvalidValue;
+    if (!pie_prefill_attn_tc_supported(hq, hkv, AT_D, 16) || (tile_rows != 128 && tile_rows != 256) || !status)
+        return (int)cudaErrorInvalidValue;
     EncodeTiledFnA enc = at_encoder();
     if (!enc) return (int)cudaErrorNotSupported;
     const int G = hq / hkv;
@@ -389,16 +459,18 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
     }
     const float scale_log2 = sm_scale * 1.4426950408889634f;
     dim3 grid(num_tiles, hkv);
-#define GO(G_)                                                                                                  \
-    {                                                                                                           \
-        auto kern = paged_prefill_attn_tc_kernel<G_>;                                                           \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM);  \
-        if (e != cudaSuccess) return (int)e;                                                                    \
-        kern<<<grid, AT_THREADS, AT_SMEM, st>>>(tq, tkv, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req, \
-                                                tile_qstart, mask_bits, mask_word_indptr, (bf16*)out, lse_out, hq, hkv, \
-                                                total_pages - 1, scale_log2, window_left, status);             \
-        return (int)cudaGetLastError();                                                                         \
+#define GO2(G_, NT_)                                                                                                  \
+    {                                                                                                                 \
+        auto kern = paged_prefill_attn_tc_kernel<G_, NT_>;                                                            \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AtCfg<NT_>::SMEM); \
+        if (e != cudaSuccess) return (int)e;                                                                          \
+        kern<<<grid, AtCfg<NT_>::THREADS, AtCfg<NT_>::SMEM, st>>>(                                                    \
+            tq, tkv, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req, tile_qstart, mask_bits,              \
+            mask_word_indptr, (bf16*)out, lse_out, hq, hkv, total_pages - 1, scale_log2, window_left, status);        \
+        return (int)cudaGetLastError();                                                                               \
     }
+#define GO(G_)                 \
+    if (tile_rows == 128) GO2(G_, 1) else GO2(G_, 2)
     switch (G) {
         case 1: GO(1)
         case 2: GO(2)
@@ -407,5 +479,6 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
         case 16: GO(16)
     }
 #undef GO
+#undef GO2
     return (int)cudaErrorInvalidValue;
 }

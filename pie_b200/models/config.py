@@ -11,6 +11,7 @@ from pathlib import Path
 from typing import Optional
 
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
+POST_NORM = {"olmo2"}       # same block with the norms after attention / MLP and q, k norms over all heads
 MOE_TYPES = {"qwen3_moe", "mixtral"}
 
 
@@ -32,6 +33,7 @@ class ModelConfig:
     qk_norm: bool = False           # Qwen3: per-head RMSNorm on q and k
     attention_bias: bool = False    # Qwen2: bias on q/k/v projections
     sliding_window: int = -1
+    post_norm: bool = False         # OLMo-2: h += norm(attn(h)); h += norm(mlp(h)); q/k RMSNorm over the whole projection
     # mixture of experts
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -80,7 +82,8 @@ class ModelConfig:
             rope_theta=cfg.get("rope_theta", 10000.0),
             rope_scaling=cfg.get("rope_scaling"),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            qk_norm=mt in ("qwen3", "qwen3_moe") or cfg.get("use_qk_norm", False),
+            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2") or cfg.get("use_qk_norm", False),
+            post_norm=mt in POST_NORM,
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
             sliding_window=cfg.get("sliding_window") or -1 if cfg.get("use_sliding_window", False) else -1,
             num_experts=cfg.get("num_experts", cfg.get("num_local_experts", 0)) or 0,
@@ -124,6 +127,12 @@ PRESETS = {
                        num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
                        vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, qk_norm=True,
                        tie_word_embeddings=True),
+    "olmo-2-7b": dict(model_type="olmo2", hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                      num_attention_heads=32, num_key_value_heads=32, head_dim=128, vocab_size=100352,
+                      rope_theta=500000.0, rms_norm_eps=1e-6, qk_norm=True, post_norm=True),
+    "tiny-olmo2": dict(model_type="olmo2", hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000,
+                       rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True, post_norm=True, dtype="float32"),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,

@@ -127,8 +127,14 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
     att["lm_head"] = Shard(head, 0, r, T)
     for li in range(cfg.num_hidden_layers):
         L, P = f"{pre}layers.{li}.", f"layers.{li}."
-        att[P + "ln1"] = w(L + "input_layernorm.weight")
-        att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
+        if cfg.post_norm:       # OLMo-2: norms follow the sub-blocks, there is no input norm
+            att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
+            att[P + "ln3"] = w(L + "post_feedforward_layernorm.weight")
+            if T > 1:
+                raise NotImplementedError("q/k norms over all heads need the full projection: tp_size must be 1")
+        else:
+            att[P + "ln1"] = w(L + "input_layernorm.weight")
+            att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
         hq_d, hkv_d = cfg.num_attention_heads * d, cfg.num_key_value_heads * d
         if L + "self_attn.qkv_proj.weight" in names:          # Phi-3: q, k, v rows stored in one tensor
             fused = lin(L + "self_attn.qkv_proj.weight")
@@ -294,7 +300,10 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
         t["lm_head.weight"] = weights["lm_head"]
     for li, lw in enumerate(weights["layers"]):
         L = f"model.layers.{li}."
-        t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
+        if "ln3" in lw:
+            t[L + "post_attention_layernorm.weight"], t[L + "post_feedforward_layernorm.weight"] = lw["ln2"], lw["ln3"]
+        else:
+            t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
         q, k, v = lw["wqkv"].split([hq * d, hkv * d, hkv * d], 0)
         t[L + "self_attn.q_proj.weight"], t[L + "self_attn.k_proj.weight"], t[L + "self_attn.v_proj.weight"] = q, k, v
         t[L + "self_attn.o_proj.weight"] = lw["wo"]

@@ -89,11 +89,11 @@ class Transformer:
         return self._row_parallel(act, lw["w_down"], h)
 
     def _row_parallel(self, a, w, h):
-        """h + a @ w.T, summed over the tensor-parallel group."""
+        """h + a @ w.T (a @ w.T when h is None), summed over the tensor-parallel group."""
         if self.par.tp_size == 1:
             return self._gemm(a, w, residual=h)
         y = self.par.comm.gemm_allreduce(a, w, self)
-        return y.add_(h)
+        return y if h is None else y.add_(h)
 
     def _moe(self, x, lw, h):
         from .moe import moe_block
@@ -101,7 +101,7 @@ class Transformer:
 
     def _fused_tp(self) -> bool:
         return self.par.tp_size > 1 and self.par.comm is not None and getattr(self.par.comm, "fused", False) \
-            and self.device.type == "cuda"
+            and self.device.type == "cuda" and not self.cfg.post_norm
 
     def _forward_hidden_tp(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
         """Tensor-parallel forward over the fused kernels: the residual stream is row-sharded,
@@ -146,16 +146,33 @@ class Transformer:
         n = h.shape[0]
         for li in range(cfg.num_hidden_layers):
             lw = w["layers"][li]
-            x = ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
+            post = cfg.post_norm
+            x = h if post else ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
             qkv = self._gemm(x, lw["wqkv"])
             if "bqkv" in lw:
                 qkv = qkv + lw["bqkv"]
             if fi.lora:
                 qkv = apply_lora(fi.lora, li, "qkv", x, qkv)
-            q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, lw.get("q_norm"),
-                                         lw.get("k_norm"), kv_cache[li], self.hq, self.hkv, self.d,
-                                         page_size, cfg.rms_norm_eps)
+            qn, kn = lw.get("q_norm"), lw.get("k_norm")
+            if qn is not None and qn.numel() != self.d:
+                # OLMo-2: RMSNorm over the whole q and k projections (all heads together)
+                qs, ks = self.hq * self.d, self.hkv * self.d
+                qkv[:, :qs] = ops.rmsnorm(qkv[:, :qs].contiguous(), qn, cfg.rms_norm_eps)
+                qkv[:, qs:qs + ks] = ops.rmsnorm(qkv[:, qs:qs + ks].contiguous(), kn, cfg.rms_norm_eps)
+                qn = kn = None
+            q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, qn, kn, kv_cache[li],
+                                         self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps)
             a = self._attention(q, kv_cache[li], fi).reshape(n, self.hq * self.d)
+            if post:
+                if "experts_gate_up" in lw:
+                    raise NotImplementedError("post-norm blocks with experts")
+                o = self._row_parallel(a, lw["wo"], None)
+                if fi.lora:
+                    o = apply_lora(fi.lora, li, "o", a, o)
+                h = h + ops.rmsnorm(o, lw["ln2"], cfg.rms_norm_eps)
+                act = self._gemm(h, lw["w_gate_up"], swiglu=True)
+                h = h + ops.rmsnorm(self._row_parallel(act, lw["w_down"], None), lw["ln3"], cfg.rms_norm_eps)
+                continue
             h = self._row_parallel(a, lw["wo"], h)
             if fi.lora:
                 h = apply_lora(fi.lora, li, "o", a, h)
@@ -202,14 +219,17 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * g.float()
 
     for lw in w["layers"]:
-        xn = norm(x, lw["ln1"])
+        xn = x if cfg.post_norm else norm(x, lw["ln1"])
         qkv = xn @ lw["wqkv"].float().t()
         if "bqkv" in lw:
             qkv = qkv + lw["bqkv"].float()
         q = qkv[:, : hq * d].reshape(t, hq, d)
         k = qkv[:, hq * d:(hq + hkv) * d].reshape(t, hkv, d)
         v = qkv[:, (hq + hkv) * d:].reshape(t, hkv, d)
-        if "q_norm" in lw:
+        if "q_norm" in lw and lw["q_norm"].numel() != d:       # over all heads together
+            q = norm(q.reshape(t, hq * d), lw["q_norm"]).reshape(t, hq, d)
+            k = norm(k.reshape(t, hkv * d), lw["k_norm"]).reshape(t, hkv, d)
+        elif "q_norm" in lw:
             q, k = norm(q, lw["q_norm"]), norm(k, lw["k_norm"])
         q, k = reference._rope(q, pos, inv), reference._rope(k, pos, inv)
         k = k.repeat_interleave(hq // hkv, dim=1)
@@ -217,6 +237,11 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
         s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
         a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(t, hq * d)
+        if cfg.post_norm:
+            x = x + norm(a @ lw["wo"].float().t(), lw["ln2"])
+            gu = x @ lw["w_gate_up"].float().t()
+            x = x + norm((torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t(), lw["ln3"])
+            continue
         x = x + a @ lw["wo"].float().t()
         xn = norm(x, lw["ln2"])
         if "experts_gate_up" in lw:

@@ -8,6 +8,7 @@ Runtime layout per layer (this rank's shard under tensor parallelism):
                                      so that the GEMM epilogue can apply SwiGLU on adjacent columns
   w_down     [H, I_local]
   ln1, ln2   [H]; q_norm, k_norm [d] (Qwen3); bqkv (Qwen2)
+  OLMo-2 (post-norm): no ln1; ln2 follows attention, ln3 follows the MLP; q_norm [hq*d], k_norm [hkv*d]
 MoE layers replace w_gate_up / w_down by router [E, H], experts_gate_up [E_local, 2*Im, H]
 (interleaved) and experts_down [E_local, H, Im].
 
@@ -95,7 +96,11 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
     emb = gen.normal(cfg.vocab_size, H)
     w["embed"] = emb
     for _ in range(cfg.num_hidden_layers):
-        lw = {"ln1": ones(H), "ln2": ones(H)}
+        if cfg.post_norm:
+            # norm gains away from 1 so that a misplaced norm shows in the tests
+            lw = {"ln2": 1 + gen.normal(H, std=0.1), "ln3": 1 + gen.normal(H, std=0.1)}
+        else:
+            lw = {"ln1": ones(H), "ln2": ones(H)}
         wq, wk, wv = gen.normal(hq * d, H), gen.normal(hkv * d, H), gen.normal(hkv * d, H)
         lw["wqkv"] = torch.cat([shard_rows(wq, r, T), wk[kv0 * d:(kv0 + kvn) * d], wv[kv0 * d:(kv0 + kvn) * d]], 0).contiguous()
         del wq, wk, wv
@@ -104,7 +109,11 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             bq, bk, bv = b[:hq * d], b[hq * d:(hq + hkv) * d], b[(hq + hkv) * d:]
             lw["bqkv"] = torch.cat([shard_rows(bq, r, T), bk[kv0 * d:(kv0 + kvn) * d], bv[kv0 * d:(kv0 + kvn) * d]]).contiguous()
         lw["wo"] = shard_cols(gen.normal(H, hq * d), r, T).contiguous()
-        if cfg.qk_norm:
+        if cfg.qk_norm and cfg.post_norm:
+            if T > 1:
+                raise NotImplementedError("q/k norms over all heads need the full projection: tp_size must be 1")
+            lw["q_norm"], lw["k_norm"] = 1 + gen.normal(hq * d, std=0.1), 1 + gen.normal(hkv * d, std=0.1)
+        elif cfg.qk_norm:
             lw["q_norm"], lw["k_norm"] = ones(d), ones(d)
         if cfg.is_moe:
             E, Im = cfg.num_experts, cfg.moe_intermediate_size

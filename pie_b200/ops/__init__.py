@@ -484,12 +484,13 @@ def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items
 
 
 def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int) -> int:
-    """Packed (token, head) rows per prefill tile: 128 where the tcgen05 kernel covers the shape
-    (head_dim 128, 16-token pages, group size dividing 128) and ``PIE_PREFILL_TC=1`` asks for it,
-    else the 64 rows of the mma.sync kernel."""
-    if os.environ.get("PIE_PREFILL_TC", "0") != "1":
+    """Packed (token, head) rows per prefill tile: 256 (two MMA tiles per CTA; ``PIE_PREFILL_TC=128``
+    for one) where the tcgen05 kernel covers the shape (head_dim 128, 16-token pages, group size
+    dividing 128), else - or with ``PIE_PREFILL_TC=0`` - the 64 rows of the mma.sync kernel."""
+    want = os.environ.get("PIE_PREFILL_TC", "256")
+    if want == "0" or not fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size):
         return 64
-    return 128 if fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size) else 64
+    return 128 if want == "128" else 256
 
 
 def plan_prefill_tiles(qo_indptr: np.ndarray, group: int, rows: int = 64):
@@ -552,7 +553,7 @@ class PrefillPlan:
     mask_bits: Optional[torch.Tensor] = None
     mask_word_indptr: Optional[torch.Tensor] = None
     window_left: int = -1
-    tile_rows: int = 64           # 128: tiles planned for the tcgen05 kernel
+    tile_rows: int = 64           # 128 / 256: tiles planned for the tcgen05 kernel
 
 
 def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out=None, lse_out=None):
@@ -560,13 +561,14 @@ def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out
         out = torch.empty_like(q)
     n, hq, d = q.shape
     hkv = kv_layer.shape[2]
-    if plan.tile_rows == 128:
+    if plan.tile_rows > 64:
         # kv_layer is [pages + 1, 2, hkv, page, d]; its last page is the zero pad page
         check(fn("pie_paged_prefill_attn_tc")(
             ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
             ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
             ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), n, hq, hkv,
-            kv_layer.shape[0], sm_scale, plan.window_left, ptr(kernel_status(q.device)), stream_ptr()),
+            kv_layer.shape[0], sm_scale, plan.window_left, plan.tile_rows, ptr(kernel_status(q.device)),
+            stream_ptr()),
             "paged_prefill_attn_tc")
         return out
     check(fn("pie_paged_prefill_attn")(

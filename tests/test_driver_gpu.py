@@ -18,14 +18,16 @@ from pie_b200.runtime.scheduler import PendingRequest, fold
 pytestmark = pytest.mark.gpu
 
 
-def small_cfg():
+def small_cfg(family="llama"):
+    extra = dict(model_type="olmo2", qk_norm=True, post_norm=True) if family == "olmo2" else {}
     return preset("tiny-llama", hidden_size=512, intermediate_size=1408, num_attention_heads=8,
-                  num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16")
+                  num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16",
+                  **extra)
 
 
-@pytest.mark.parametrize("backend", ["tcgen05", "cublas"])
-def test_prefill_and_decode_logits_match_oracle(backend):
-    cfg = small_cfg()
+@pytest.mark.parametrize("backend,family", [("tcgen05", "llama"), ("cublas", "llama"), ("tcgen05", "olmo2")])
+def test_prefill_and_decode_logits_match_oracle(backend, family):
+    cfg = small_cfg(family)
     w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)
     drv = TorchDriver(cfg, "cuda", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=512,
                       gemm_backend=backend)

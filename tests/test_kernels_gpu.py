@@ -131,12 +131,14 @@ def test_paged_decode_attention(d, hq, hkv):
 
 @pytest.mark.parametrize("d,hq,hkv,rows", [(128, 32, 8, 64), (128, 8, 1, 64), (64, 4, 2, 64),
                                            (128, 32, 8, 128), (128, 8, 1, 128), (128, 4, 4, 128),
-                                           (128, 32, 2, 128), (128, 8, 4, 128)])
+                                           (128, 32, 2, 128), (128, 8, 4, 128), (128, 32, 8, 256),
+                                           (128, 8, 1, 256), (128, 4, 4, 256), (128, 32, 2, 256)])
 @pytest.mark.parametrize("mode", ["causal", "custom", "window"])
 def test_paged_prefill_attention(d, hq, hkv, rows, mode):
-    """rows = 64: the mma.sync kernel; rows = 128: the tcgen05 kernel (head_dim 128, 16-token pages)."""
+    """rows = 64: the mma.sync kernel; rows = 128 / 256: the tcgen05 kernel with one / two MMA
+    tiles per CTA (head_dim 128, 16-token pages)."""
     page = 16
-    if rows == 128:
+    if rows > 64:
         assert ops._lib.fn("pie_prefill_attn_tc_supported")(hq, hkv, d, page) == 1
     qlens = np.array([1, 5, 64, 130, 17, 700], dtype=np.int32)
     prev = np.array([40, 0, 0, 200, 31, 333], dtype=np.int32)
@@ -168,6 +170,30 @@ def test_paged_prefill_attention(d, hq, hkv, rows, mode):
                                          masks=tmasks, window_left=window, return_lse=True)
     close(out, want, 2e-2)
     close(lse, want_lse, 2e-2)
+
+
+@pytest.mark.parametrize("rows", [128, 256])
+def test_prefill_tc_rescales_accumulator_when_scores_grow(rows):
+    """Large score magnitudes make block maxima outgrow the lazily updated reference maximum, so
+    the kernel's rescale of its TMEM accumulator runs in ordinary causal blocks too."""
+    d, hq, hkv, page = 128, 8, 2, 16
+    qlens = np.array([300, 77], dtype=np.int32)
+    prev = np.array([500, 0], dtype=np.int32)
+    kv_lens = qlens + prev
+    kv, pages, indptr = make_paged(2, kv_lens, hkv, d, page, seed=41)
+    qo = np.zeros(3, dtype=np.int32)
+    qo[1:] = np.cumsum(qlens)
+    q = bf(int(qo[-1]), hq, d, seed=42, scale=8.0)
+    batch = ops.AttnBatch(qo, indptr, pages, kv_lens, None, -1)
+    plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV, tile_rows=rows)
+    scale = 1 / math.sqrt(d)
+    lse = torch.empty(int(qo[-1]), hq, device=DEV)
+    out = ops.paged_prefill_attention(q, kv, plan, scale, lse_out=lse)
+    ops.check_kernel_status(DEV)
+    want, want_lse = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
+                                         return_lse=True)
+    close(out, want, 3e-2)
+    close(lse, want_lse, 5e-2, rtol=1e-2)
 
 
 def test_row_stats():

@@ -190,3 +190,40 @@ def test_mixtral_tensor_names(tmp_path):
     for la, lb in zip(wa["layers"], wb["layers"]):
         assert torch.equal(la["experts_gate_up"], lb["experts_gate_up"]) and torch.equal(la["router"], lb["router"])
         assert torch.equal(la["experts_down"], lb["experts_down"])
+
+
+def test_olmo2_post_norm_family_loads_and_matches_dense_oracle(tmp_path):
+    """OLMo-2: no input norm, norms after attention and after the MLP, q/k RMSNorm over all
+    heads together. A checkpoint under its Hugging Face names loads, and prefill + decode
+    through the paged driver give the dense oracle's logits."""
+    import numpy as np
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models import loader
+    from pie_b200.models.config import preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import random_weights
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+
+    cfg = preset("tiny-olmo2")
+    w = random_weights(cfg, "cpu", torch.float32, seed=5)
+    assert "ln1" not in w["layers"][0] and w["layers"][0]["q_norm"].numel() == cfg.q_size
+    loader.export_hf_checkpoint(cfg, w, tmp_path)
+    cfg2, w2 = loader.load_checkpoint(tmp_path, "cpu", dtype="float32")
+    assert cfg2.post_norm and cfg2.qk_norm and cfg2.model_type == "olmo2"
+    for key in ("ln2", "ln3", "q_norm", "k_norm", "wqkv", "w_gate_up"):
+        assert torch.equal(w2["layers"][1][key], w["layers"][1][key])
+    drv = TorchDriver(cfg2, "cpu", weights=w2, num_pages=16, page_size=16, max_requests=4, max_tokens=128)
+    toks = list(range(100, 137))
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    resp = drv.fire_batch(fold([PendingRequest(0, toks, list(range(len(toks))), list(range(4)), 0, [(len(toks) - 1, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg2, w2, torch.tensor(toks))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3
+    # one decode step on top of the cached prefix
+    resp = drv.fire_batch(fold([PendingRequest(0, [7], [len(toks)], list(range(4)), len(toks), [(0, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg2, w2, torch.tensor(toks + [7]))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3
+    with pytest.raises(NotImplementedError):
+        loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=0, dtype="float32")
