@@ -2,20 +2,24 @@
 //
 // One CTA per (tile of 128 or 256 packed query rows, KV head); a row is (query token, head within
 // the GQA group), so a CTA covers 128 / G or 256 / G tokens of one request as one or two MMA tiles of
-// 128 rows that share the K/V stages. KV is walked in blocks of 64 keys:
+// 128 rows that share the K and V tiles. KV is walked in blocks of 64 keys:
 //   warp 0      TMA producer: the Q tiles once (3-D boxes over [tokens, heads, d]); per block the K
-//               and V rows of its four pages (2-D boxes of 16 rows x 64 columns, 128-byte
-//               swizzle) into a ring of stages; pages past the end come from the cache's pad page
-//   warp 1      tcgen05.mma issuer: S = Q K^T (128 x 64, K-major operands) into one of two TMEM
-//               buffers per tile, then O += P V (128 x 128; P from shared memory, V as an MN-major
-//               operand straight from its [key, d] tile) into the tile's TMEM accumulator
+//               and the V rows of its four pages (2-D boxes of 16 rows x 64 columns, 128-byte
+//               swizzle) into a ring of K tiles and a ring of V tiles (K is needed two blocks
+//               before V); pages past the end come from the cache's pad page
+//   1 warp per tile: tcgen05.mma issuer: S = Q K^T (128 x 64, K-major operands) into one of two TMEM
+//               buffers, issued two blocks ahead; O += P V (128 x 128; P from shared memory, V as
+//               an MN-major operand straight from its [key, d] tile) into the tile's TMEM
+//               accumulator as soon as the softmax warps hand over P, then the next S into the
+//               buffer just freed
 //   4 warps per tile: softmax, one row per thread: S from TMEM, mask (causal / window / custom bits;
 //               skipped for blocks fully inside the causal region), exponentials against a
 //               reference maximum, P as bf16 into a swizzled shared-memory tile for the PV MMA.
 //               The reference maximum follows the true one lazily: only when a block maximum
 //               outgrows it by 2^8 does the warp rescale its rows of O in TMEM (tcgen05.ld / st),
 //               so most blocks cost one exp per score and no pass over O.
-// The score MMA of block j + 1 overlaps the softmax of block j through the S double buffer.
+// The two tiles' softmax and MMA phases interleave on the SM: while one tile's rows are in the
+// exponentials the tensor cores work on the other's.
 // Every wait is bounded; on a time-out the kernel records a status word and leaves.
 //
 // Replaces the FlashInfer FA2 paged prefill kernel the reference calls
@@ -29,18 +33,17 @@ using namespace sm100;
 constexpr int AT_ROWS = 128;     // packed query rows per MMA tile
 constexpr int AT_BK = 64;        // keys per block
 constexpr int AT_D = 128;
-constexpr int AT_STAGES = 3;
+constexpr int AT_STAGES = 3;      // K ring and V ring, each of this many 16 KB tiles
 constexpr uint32_t AT_Q_BYTES = AT_ROWS * AT_D * 2;            // two 16 KB halves
 constexpr uint32_t AT_KV_TILE = AT_BK * AT_D * 2;              // 16 KB: two 8 KB halves [64 keys x 64 d]
-constexpr uint32_t AT_STAGE_BYTES = 2 * AT_KV_TILE;            // K then V
 constexpr uint32_t AT_P_BYTES = AT_ROWS * AT_BK * 2;           // 16 KB
-constexpr int AT_TILE_BARS = 9;                                // s_full[2] s_empty[2] p_full[2] p_empty[2] pv_done
+constexpr int AT_TILE_BARS = 8;                                // s_full[2] p_full[2] p_empty[2] pv_done o_final
 constexpr float AT_RESCALE_LOG2 = 8.f;                         // the reference maximum may lag the true one by 2^8
 
 template <int NT>
 struct AtCfg {
-    static constexpr int THREADS = 64 + 128 * NT;
-    static constexpr uint32_t SMEM = NT * AT_Q_BYTES + AT_STAGES * AT_STAGE_BYTES + NT * 2 * AT_P_BYTES + 1024 + 512;
+    static constexpr int THREADS = 32 * (1 + NT) + 128 * NT;   // producer, one MMA warp per tile, softmax warps
+    static constexpr uint32_t SMEM = NT * AT_Q_BYTES + 2 * AT_STAGES * AT_KV_TILE + NT * 2 * AT_P_BYTES + 1024 + 512;
     static constexpr uint32_t TMEM_COLS = 256 * NT;             // per tile: S[2] x 64 columns, O x 128
 };
 
@@ -89,20 +92,23 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t q_s = base;
-    const uint32_t kv_s = q_s + NT * AT_Q_BYTES;
-    const uint32_t p_s = kv_s + AT_STAGES * AT_STAGE_BYTES;
+    const uint32_t k_s = q_s + NT * AT_Q_BYTES;                  // K ring
+    const uint32_t v_s = k_s + AT_STAGES * AT_KV_TILE;            // V ring
+    const uint32_t p_s = v_s + AT_STAGES * AT_KV_TILE;
     const uint32_t bar0 = p_s + NT * 2 * AT_P_BYTES;
     auto q_full = [&]() { return bar0; };
-    auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
-    auto kv_empty = [&](int s) { return bar0 + 8u * (1 + AT_STAGES + s); };
-    auto tbar = [&](int t, int i) { return bar0 + 8u * (1 + 2 * AT_STAGES + t * AT_TILE_BARS + i); };
+    auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (1 + AT_STAGES + s); };       // one arrival per MMA warp
+    auto v_full = [&](int s) { return bar0 + 8u * (1 + 2 * AT_STAGES + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (1 + 3 * AT_STAGES + s); };   // one arrival per MMA warp
+    auto tbar = [&](int t, int i) { return bar0 + 8u * (1 + 4 * AT_STAGES + t * AT_TILE_BARS + i); };
     auto s_full = [&](int t, int b) { return tbar(t, b); };
-    auto s_empty = [&](int t, int b) { return tbar(t, 2 + b); };
-    auto p_full = [&](int t, int b) { return tbar(t, 4 + b); };
-    auto p_empty = [&](int t, int b) { return tbar(t, 6 + b); };
-    auto pv_done = [&](int t) { return tbar(t, 8); };
+    auto p_full = [&](int t, int b) { return tbar(t, 2 + b); };
+    auto p_empty = [&](int t, int b) { return tbar(t, 4 + b); };
+    auto pv_done = [&](int t) { return tbar(t, 6); };     // one phase per PV MMA of the tile
+    auto o_final = [&](int t) { return tbar(t, 7); };     // the tile's last PV MMA has completed
     volatile uint32_t* tmem_slot =
-        reinterpret_cast<volatile uint32_t*>(base_ptr + (bar0 - base) + 8u * (1 + 2 * AT_STAGES + NT * AT_TILE_BARS));
+        reinterpret_cast<volatile uint32_t*>(base_ptr + (bar0 - base) + 8u * (1 + 4 * AT_STAGES + NT * AT_TILE_BARS));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, h = blockIdx.y;
@@ -132,17 +138,19 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
     if (threadIdx.x == 0) {
         mbar_init(q_full(), 1);
         for (int s = 0; s < AT_STAGES; ++s) {
-            mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), 1);
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), NT);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), NT);
         }
         for (int t = 0; t < NT; ++t) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(s_full(t, b), 1);
-                mbar_init(s_empty(t, b), 4);
                 mbar_init(p_full(t, b), 4);
                 mbar_init(p_empty(t, b), 1);
             }
             mbar_init(pv_done(t), 1);
+            mbar_init(o_final(t), 1);
         }
         fence_barrier_init();
         fence_proxy_async();
@@ -169,86 +177,93 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
             bool ok = true;
             for (int j = 0; j < nkb && ok; ++j) {
                 const int s = j % AT_STAGES;
-                if (!mbar_wait(kv_empty(s), ((j / AT_STAGES) & 1u) ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
-                mbar_arrive_expect_tx(kv_full(s), AT_STAGE_BYTES);
-                const uint32_t kdst = kv_s + s * AT_STAGE_BYTES;
+                const uint32_t par = ((j / AT_STAGES) & 1u) ^ 1u;
                 int pg_id[4];
 #pragma unroll
                 for (int pg = 0; pg < 4; ++pg) {
                     const int pi = j * 4 + pg;
                     pg_id[pg] = pi < npages ? pages[pi] : pad_page;
                 }
+                if (!mbar_wait(k_empty(s), par, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                mbar_arrive_expect_tx(k_full(s), AT_KV_TILE);
 #pragma unroll
                 for (int pg = 0; pg < 4; ++pg) {
                     const int krow = ((pg_id[pg] * 2) * hkv + h) * 16;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        tma_load_2d(k_s + s * AT_KV_TILE + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, k_full(s), half * 64, krow);
+                }
+                if (!mbar_wait(v_empty(s), par, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                mbar_arrive_expect_tx(v_full(s), AT_KV_TILE);
+#pragma unroll
+                for (int pg = 0; pg < 4; ++pg) {
                     const int vrow = ((pg_id[pg] * 2 + 1) * hkv + h) * 16;
 #pragma unroll
                     for (int half = 0; half < 2; ++half)
-                        tma_load_2d(kdst + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, kv_full(s), half * 64, krow);
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        tma_load_2d(kdst + AT_KV_TILE + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, kv_full(s), half * 64, vrow);
+                        tma_load_2d(v_s + s * AT_KV_TILE + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, v_full(s), half * 64, vrow);
                 }
             }
             // no copy may be in flight when the CTA exits
             const int first = nkb > AT_STAGES ? nkb - AT_STAGES : 0;
-            for (int j = first; j < nkb; ++j)
-                mbar_wait(kv_full(j % AT_STAGES), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA, 200000000ll);
+            for (int j = first; j < nkb; ++j) {
+                mbar_wait(k_full(j % AT_STAGES), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA, 200000000ll);
+                mbar_wait(v_full(j % AT_STAGES), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA, 200000000ll);
+            }
         }
-    } else if (warp == 1) {
+    } else if (warp <= NT) {
+        // ------------------------------------------------ MMA warp of tile t: S two blocks ahead of PV
+        const int t = warp - 1;
         if (lane == 0 && nkb > 0) {
             constexpr uint32_t idesc_s = make_idesc_bf16(AT_ROWS, AT_BK);
             constexpr uint32_t idesc_o = make_idesc_bf16_bmn(AT_ROWS, AT_D);
+            const int my = NT == 1 ? nkb : (t == 0 ? nkb_t[0] : nkb_t[NT - 1]);
+            const uint32_t tm_s = tmem_base + t * 256, tm_o = tm_s + 128;
+            const uint64_t q_desc0 = make_smem_desc_sw128(q_s + t * AT_Q_BYTES);
+            const uint64_t q_desc1 = make_smem_desc_sw128(q_s + t * AT_Q_BYTES + AT_Q_BYTES / 2);
             bool ok = mbar_wait(q_full(), 0, status, PIE_ERR_WAIT_TMA);
-            // O_t += P_t,j V_j; frees the P buffer, and (after the last tile) the K/V stage of block j
-            auto issue_pv = [&](int j) {
+            // S_t(j) = Q_t K_j^T into S buffer j & 1. Every MMA warp waits for and releases every K and V
+            // tile, also those its (shorter) tile does not use, so that the rings advance in step.
+            auto issue_s = [&](int j) {
                 const int s = j % AT_STAGES;
-                const uint32_t b = j & 1u, ph = (j >> 1) & 1u;
-                const uint32_t v_addr = kv_s + s * AT_STAGE_BYTES + AT_KV_TILE;
-#pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    if (j >= nkb_t[t] || !ok) continue;
-                    if (!mbar_wait(p_full(t, b), ph, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; continue; }
+                if (!mbar_wait(k_full(s), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; return; }
+                if (j < my) {
                     tc_fence_after();
-                    const uint32_t p_addr = p_s + (t * 2 + b) * AT_P_BYTES;
+                    const uint64_t k_desc0 = make_smem_desc_sw128(k_s + s * AT_KV_TILE);
+                    const uint64_t k_desc1 = make_smem_desc_sw128(k_s + s * AT_KV_TILE + AT_KV_TILE / 2);
 #pragma unroll
-                    for (int k = 0; k < AT_BK / 16; ++k) {
-                        const uint64_t adesc = make_smem_desc_sw128(p_addr) + 2u * k;                       // 16 keys = 32 bytes along a P row
-                        const uint64_t bdesc = make_smem_desc_sw128_mn(v_addr + k * 2048, AT_KV_TILE / 2);  // 16 keys = two 8-row groups
-                        umma_bf16(tmem_base + t * 256 + 128, adesc, bdesc, idesc_o, (j | k) != 0);
-                    }
-                    umma_commit(pv_done(t));
-                    umma_commit(p_empty(t, b));
+                    for (int k = 0; k < 4; ++k) umma_bf16(tm_s + (j & 1) * AT_BK, q_desc0 + 2u * k, k_desc0 + 2u * k, idesc_s, k != 0);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(tm_s + (j & 1) * AT_BK, q_desc1 + 2u * k, k_desc1 + 2u * k, idesc_s, 1);
+                    umma_commit(s_full(t, j & 1));
                 }
-                umma_commit(kv_empty(s));
+                umma_commit(k_empty(s));
             };
+            if (ok) issue_s(0);
+            if (ok && nkb > 1) issue_s(1);
             for (int j = 0; j < nkb && ok; ++j) {
                 const int s = j % AT_STAGES;
                 const uint32_t b = j & 1u, ph = (j >> 1) & 1u;
-                if (!mbar_wait(kv_full(s), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
-                const uint32_t k_addr = kv_s + s * AT_STAGE_BYTES;
-#pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    if (j >= nkb_t[t] || !ok) continue;
-                    if (!mbar_wait(s_empty(t, b), ph ^ 1u, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; continue; }
+                if (!mbar_wait(v_full(s), (j / AT_STAGES) & 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
+                if (j < my) {
+                    // softmax has read S_t(j) and written P_t(j)
+                    if (!mbar_wait(p_full(t, b), ph, status, PIE_ERR_WAIT_EPILOGUE)) { ok = false; break; }
                     tc_fence_after();
+                    const uint64_t p_desc = make_smem_desc_sw128(p_s + (t * 2 + b) * AT_P_BYTES);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const uint64_t adesc = make_smem_desc_sw128(q_s + t * AT_Q_BYTES + half * (AT_Q_BYTES / 2));
-                        const uint64_t bdesc = make_smem_desc_sw128(k_addr + half * (AT_KV_TILE / 2));
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma_bf16(tmem_base + t * 256 + b * AT_BK, adesc + 2u * k, bdesc + 2u * k, idesc_s, (half | k) != 0);
-                    }
-                    umma_commit(s_full(t, b));
+                    for (int k = 0; k < AT_BK / 16; ++k)      // 16 keys: 32 bytes along a P row, two 8-row groups of V
+                        umma_bf16(tm_o, p_desc + 2u * k, make_smem_desc_sw128_mn(v_s + s * AT_KV_TILE + k * 2048, AT_KV_TILE / 2),
+                                  idesc_o, (j | k) != 0);
+                    umma_commit(pv_done(t));
+                    umma_commit(p_empty(t, b));
+                    if (j == my - 1) umma_commit(o_final(t));
                 }
-                if (j >= 1 && ok) issue_pv(j - 1);
+                umma_commit(v_empty(s));
+                if (j + 2 < nkb) issue_s(j + 2);      // overwrites the S buffer that block j has just left
             }
-            if (ok) issue_pv(nkb - 1);
         }
     } else {
         // ---------------------------------------------- softmax warps: thread = row of MMA tile t
-        const int t = (warp - 2) >> 2;
+        const int t = (warp - 1 - NT) >> 2;
         const int q4 = warp & 3;                        // the TMEM lane quarter this warp may access
         const int row = q4 * 32 + lane;
         const int qtok = qstart + t * TQ + row / G;
@@ -277,9 +292,6 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(v[i]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(t, b));
             const int kb0 = j * AT_BK;
             const bool inner = !custom && kb0 + AT_BK <= lim && kb0 >= lo;
             if (!__all_sync(0xffffffffu, inner)) {
@@ -354,10 +366,9 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
             if (lane == 0) mbar_arrive(p_full(t, b));
         }
         if (ok && my_nkb > 0) {
-            // A parity wait tells apart only neighbouring phases. Having seen S of the last block, the
-            // barrier has passed phase my_nkb - 3 at least: wait for the last two phases in turn.
-            bool done = my_nkb < 2 || mbar_wait(pv_done(t), (my_nkb - 2) & 1u, status, PIE_ERR_WAIT_MMA);
-            done = done && mbar_wait(pv_done(t), (my_nkb - 1) & 1u, status, PIE_ERR_WAIT_MMA);
+            // pv_done cannot serve here: a parity wait tells apart only neighbouring phases, and by now
+            // that barrier may be one phase short of the last or already past it
+            const bool done = mbar_wait(o_final(t), 0, status, PIE_ERR_WAIT_MMA);
             ok = __all_sync(0xffffffffu, done);
         }
         if (ok && my_nkb > 0) {
@@ -482,3 +493,4 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
 #undef GO2
     return (int)cudaErrorInvalidValue;
 }
+
