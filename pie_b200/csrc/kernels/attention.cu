@@ -184,7 +184,7 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          const int* __restrict__ req_item_indptr,
                          const int* __restrict__ num_items_ptr, bf16* __restrict__ out,
                          float* __restrict__ o_part, float* __restrict__ lse_part, int hq, int hkv,
-                         int page_size, float scale_log2) {
+                         int page_size, float scale_log2, int window_left) {
     static_assert(G <= 16, "at most 16 query heads per KV head");
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int CH = D / 8;              // 16-byte chunks per row
@@ -200,6 +200,9 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
         const int it = (int)(w / hkv), h = (int)(w - (long)it * hkv);
         const int req = item_req[it];
         const int kv_start = item_start[it], kv_end = item_end[it];
+        // sliding window: the query sits at position kv_len - 1 (kv_len = end of the request's last
+        // item) and sees keys >= kv_len - 1 - window_left; items start on a 16-token boundary below that
+        const int kv_lo = window_left >= 0 ? max(0, item_end[req_item_indptr[req + 1] - 1] - 1 - window_left) : 0;
         __syncthreads();  // previous item's merge reads are done
         // Q tile: rows < G are the heads of this KV head, the rest zeros
         for (int c = threadIdx.x; c < 16 * CH; c += blockDim.x) {
@@ -247,7 +250,8 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
             __syncwarp();
             const int tok0 = kv_start + (warp + DEC_WARPS * i) * 16;
             const int nvalid = kv_end - tok0;
-            const uint32_t allow = nvalid >= 16 ? 0xffffu : ((1u << nvalid) - 1u);
+            uint32_t allow = nvalid >= 16 ? 0xffffu : ((1u << nvalid) - 1u);
+            if (kv_lo > tok0) allow &= kv_lo - tok0 >= 16 ? 0u : ~((1u << (kv_lo - tok0)) - 1u);
             const uint32_t kt = warp_smem + (i % DEC_STAGES) * 2 * TILE_BYTES;
             attn_block16<D>(qf, kt, kt + TILE_BYTES, scale_log2, allow, allow, st);
             __syncwarp();
@@ -532,13 +536,15 @@ PIE_API long pie_decode_attn_scratch_floats(int max_items, int hq, int head_dim)
     return (long)max_items * hq * head_dim + (long)max_items * hq;
 }
 
-PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int* page_indices,
-                                  const int* kv_page_indptr, const int* item_req,
-                                  const int* item_start, const int* item_end,
-                                  const int* req_item_indptr, const int* num_items_ptr,
-                                  void* out, float* scratch, int max_items, int num_reqs, int hq,
-                                  int hkv, int head_dim, int page_size, float sm_scale,
-                                  int num_ctas, int run_merge, cudaStream_t st) {
+// window_left >= 0: each request's single query token sees only the last window_left + 1 keys; the
+// caller's items then start at the 16-token boundary at or below the first visible key.
+PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, const int* page_indices,
+                                         const int* kv_page_indptr, const int* item_req,
+                                         const int* item_start, const int* item_end,
+                                         const int* req_item_indptr, const int* num_items_ptr,
+                                         void* out, float* scratch, int max_items, int num_reqs, int hq,
+                                         int hkv, int head_dim, int page_size, float sm_scale,
+                                         int num_ctas, int run_merge, int window_left, cudaStream_t st) {
     if (num_reqs <= 0) return 0;
     if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
     const int group = hq / hkv;
@@ -552,7 +558,7 @@ PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int
         launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
             (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
             item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
-            hkv, page_size, scale_log2);
+            hkv, page_size, scale_log2, window_left);
     });
     int err = (int)cudaGetLastError();
     if (err || !run_merge) return err;
@@ -564,6 +570,18 @@ PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int
         launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, (const float*)o_part,
                    (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group);
     return (int)cudaGetLastError();
+}
+
+PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int* page_indices,
+                                  const int* kv_page_indptr, const int* item_req,
+                                  const int* item_start, const int* item_end,
+                                  const int* req_item_indptr, const int* num_items_ptr,
+                                  void* out, float* scratch, int max_items, int num_reqs, int hq,
+                                  int hkv, int head_dim, int page_size, float sm_scale,
+                                  int num_ctas, int run_merge, cudaStream_t st) {
+    return pie_paged_decode_attn_window(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start, item_end,
+                                        req_item_indptr, num_items_ptr, out, scratch, max_items, num_reqs, hq, hkv,
+                                        head_dim, page_size, sm_scale, num_ctas, run_merge, -1, st);
 }
 
 PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const int* page_indices,

@@ -169,6 +169,8 @@ class TorchDriver:
         self.max_requests, self.max_tokens = max_requests, max_tokens
         self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
         self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
+        # HF sliding_window = number of keys a query sees, itself included
+        self.window_left = self.cfg.sliding_window - 1 if self.cfg.sliding_window and self.cfg.sliding_window > 0 else -1
         self.max_items = max_requests + self.num_ctas * 8
         rows = max(max_requests, 1024)
         self.max_rows = rows
@@ -328,7 +330,7 @@ class TorchDriver:
             page_indices=s.d("page_indices"), kv_page_indptr=s.d("kv_page_indptr"), item_req=s.d("item_req"),
             item_start=s.d("item_start"), item_end=s.d("item_end"), req_item_indptr=s.d("req_item_indptr"),
             num_items=s.d("num_items"), scratch=self.scratch, max_items=self.max_items, num_reqs=rb,
-            num_ctas=self.num_ctas, page_size=self.page_size)
+            num_ctas=self.num_ctas, page_size=self.page_size, window_left=self.window_left)
         return ForwardInputs(tokens=s.d("tokens", rb), positions=s.d("positions", rb), slots=s.d("slots", rb),
                              attn=plan, logit_rows=None, is_decode=True)
 
@@ -366,7 +368,7 @@ class TorchDriver:
             s.h("positions")[r:rb] = 0
             s.h("slots")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
-        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items)
+        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items, window_left=self.window_left)
         ni = len(item_req)
         s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
         s.h("req_item_indptr")[:r + 1] = indptr
@@ -399,7 +401,7 @@ class TorchDriver:
         if self.cuda:
             group = self.model.hq // self.model.hkv
             tile_rows = ops.prefill_tile_rows(self.model.hq, self.model.hkv, self.model.cfg.head_dim, self.page_size)
-            tile_req, tile_q = ops.plan_prefill_tiles(np.asarray(req.qo_indptr), group, tile_rows)
+            tile_req, tile_q = ops.plan_prefill_tiles(np.asarray(req.qo_indptr), group, tile_rows, kv_lens)
             nt = len(tile_req)
             s.h("tile_req")[:nt], s.h("tile_qstart")[:nt] = tile_req, tile_q
             s.h("logit_rows")[:len(rows)] = rows
@@ -417,7 +419,7 @@ class TorchDriver:
                 mask_indptr = torch.tensor(indptr, dtype=torch.int64, device=self.device)
             plan = ops.PrefillPlan(s.d("page_indices"), s.d("kv_page_indptr"), s.d("qo_indptr"), s.d("kv_lens"),
                                    s.d("tile_req"), s.d("tile_qstart"), nt, self.page_size, mask_bits, mask_indptr,
-                                   tile_rows=tile_rows)
+                                   window_left=self.window_left, tile_rows=tile_rows)
             fi = ForwardInputs(s.d("tokens", n), s.d("positions", n), s.d("slots", n), plan,
                                logit_rows=s.d("logit_rows", len(rows)), is_decode=False)
         else:
@@ -433,7 +435,7 @@ class TorchDriver:
                     else:
                         masks.append(None)
             batch = ops.AttnBatch(np.asarray(req.qo_indptr), np.asarray(req.kv_page_indptr),
-                                  np.asarray(req.kv_page_indices), kv_lens, masks)
+                                  np.asarray(req.kv_page_indices), kv_lens, masks, self.window_left)
             fi = ForwardInputs(torch.from_numpy(np.ascontiguousarray(req.tokens, dtype=np.int32)),
                                torch.from_numpy(np.ascontiguousarray(req.positions, dtype=np.int32)),
                                torch.from_numpy(slots.astype(np.int32)), batch,
@@ -604,7 +606,7 @@ class TorchDriver:
             s.h("slots")[r:rb] = -1
             s.h("src_row")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = step.page_indptr[-1]
-        item_req, st, en, indptr = ops.plan_decode_items(step.kv_lens, self.model.hkv, self.num_ctas, self.max_items)
+        item_req, st, en, indptr = ops.plan_decode_items(step.kv_lens, self.model.hkv, self.num_ctas, self.max_items, window_left=self.window_left)
         ni = len(item_req)
         s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
         s.h("req_item_indptr")[:r + 1] = indptr
@@ -686,7 +688,7 @@ class TorchDriver:
             s.h("positions")[r:rb] = 0
             s.h("slots")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
-        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items)
+        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items, window_left=self.window_left)
         ni = len(item_req)
         s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
         s.h("req_item_indptr")[:r + 1] = indptr

@@ -85,7 +85,8 @@ class ModelConfig:
             qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2") or cfg.get("use_qk_norm", False),
             post_norm=mt in POST_NORM,
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
-            sliding_window=cfg.get("sliding_window") or -1 if cfg.get("use_sliding_window", False) else -1,
+            # Qwen2 gates the window on use_sliding_window; Mistral applies it whenever it is set
+            sliding_window=(cfg.get("sliding_window") or -1) if cfg.get("use_sliding_window", mt == "mistral") else -1,
             num_experts=cfg.get("num_experts", cfg.get("num_local_experts", 0)) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
             # Mixtral has no separate field: its intermediate_size is the expert FFN width

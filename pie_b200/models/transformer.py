@@ -236,6 +236,8 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         v = v.repeat_interleave(hq // hkv, dim=1)
         s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
         s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
+        if cfg.sliding_window and cfg.sliding_window > 0:       # a query sees itself and the sliding_window - 1 keys before it
+            s = s.masked_fill(torch.tril(torch.ones(t, t, dtype=torch.bool), -cfg.sliding_window)[None], float("-inf"))
         a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(t, hq * d)
         if cfg.post_norm:
             x = x + norm(a @ lw["wo"].float().t(), lw["ln2"])

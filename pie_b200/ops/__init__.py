@@ -459,12 +459,18 @@ class AttnBatch:
 
 
 def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items: int = 0,
-                      min_chunk: int = 256):
-    """Split each request's KV range into chunks so that items*hkv fills the machine.
+                      min_chunk: int = 256, window_left: int = -1):
+    """Split each request's KV range into chunks so that items*hkv fills the machine. With a
+    sliding window only the last window_left + 1 keys are covered, from the 16-token boundary
+    at or below the first visible key (the kernel masks the keys below it).
 
     Returns (item_req, item_start, item_end, req_item_indptr) as int32 arrays.
     """
-    kv_lens = np.asarray(kv_lens, dtype=np.int64)
+    full_lens = np.asarray(kv_lens, dtype=np.int64)
+    lo = np.zeros_like(full_lens)
+    if window_left >= 0:
+        lo = np.maximum(0, full_lens - 1 - window_left) // 16 * 16
+    kv_lens = full_lens - lo
     total = int(kv_lens.sum())
     chunk = max(min_chunk, -(-total * hkv // max(1, target_ctas * 4)))
     chunk = -(-chunk // 16) * 16
@@ -480,6 +486,7 @@ def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items
     within = np.arange(tot, dtype=np.int64) - np.repeat(indptr[:-1].astype(np.int64), n_items)
     start = within * chunk
     end = np.minimum(start + chunk, kv_lens[item_req])
+    start, end = start + lo[item_req], end + lo[item_req]
     return item_req, start.astype(np.int32), end.astype(np.int32), indptr
 
 
@@ -493,8 +500,10 @@ def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int) -> int:
     return 128 if want == "128" else 256
 
 
-def plan_prefill_tiles(qo_indptr: np.ndarray, group: int, rows: int = 64):
-    """Tiles of rows/group query tokens per request: (tile_req, tile_qstart)."""
+def plan_prefill_tiles(qo_indptr: np.ndarray, group: int, rows: int = 64, kv_lens=None):
+    """Tiles of rows/group query tokens per request: (tile_req, tile_qstart). With `kv_lens` the
+    tiles are ordered by falling causal work (keys visible to the tile's last token), so that the
+    long tiles start first and the short ones fill the tail of the grid."""
     tq = max(1, rows // group)
     qlens = np.diff(qo_indptr).astype(np.int64)
     ntiles = -(-qlens // tq)
@@ -502,7 +511,13 @@ def plan_prefill_tiles(qo_indptr: np.ndarray, group: int, rows: int = 64):
     base = np.zeros(len(qlens) + 1, dtype=np.int64)
     base[1:] = np.cumsum(ntiles)
     within = np.arange(int(base[-1]), dtype=np.int64) - np.repeat(base[:-1], ntiles)
-    return tile_req, (within * tq).astype(np.int32)
+    qstart = within * tq
+    if kv_lens is not None and len(tile_req) > 1:
+        kl = np.asarray(kv_lens, dtype=np.int64)[tile_req]
+        work = kl - qlens[tile_req] + np.minimum(qstart + tq, qlens[tile_req])
+        order = np.argsort(-work, kind="stable")
+        tile_req, qstart = tile_req[order], qstart[order]
+    return tile_req, qstart.astype(np.int32)
 
 
 @dataclass
@@ -520,6 +535,7 @@ class DecodePlan:
     num_reqs: int
     num_ctas: int
     page_size: int
+    window_left: int = -1
 
 
 def decode_scratch_floats(max_items: int, hq: int, head_dim: int) -> int:
@@ -532,11 +548,11 @@ def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=N
         out = torch.empty_like(q)
     r, hq, d = q.shape
     hkv = kv_layer.shape[2]
-    check(fn("pie_paged_decode_attn")(
+    check(fn("pie_paged_decode_attn_window")(
         ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
         ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),
         ptr(out), ptr(plan.scratch), plan.max_items, plan.num_reqs, hq, hkv, d, plan.page_size,
-        sm_scale, plan.num_ctas, 1, stream_ptr()), "paged_decode_attn")
+        sm_scale, plan.num_ctas, 1, plan.window_left, stream_ptr()), "paged_decode_attn")
     return out
 
 
@@ -597,7 +613,7 @@ def pack_masks(masks, kv_lens, device):
 
 
 def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device, tile_rows: int = 64) -> PrefillPlan:
-    tile_req, tile_qstart = plan_prefill_tiles(batch.qo_indptr, group, tile_rows)
+    tile_req, tile_qstart = plan_prefill_tiles(batch.qo_indptr, group, tile_rows, batch.kv_lens)
     mask_bits = mask_indptr = None
     if batch.masks is not None:
         masks = []

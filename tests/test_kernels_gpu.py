@@ -129,6 +129,30 @@ def test_paged_decode_attention(d, hq, hkv):
     close(out, want, 2e-2)
 
 
+@pytest.mark.parametrize("window", [0, 15, 16, 100, 1000])
+def test_paged_decode_attention_sliding_window(window):
+    """Decode attention over the last window + 1 keys only: the plan starts at the 16-token boundary
+    below the first visible key and the kernel masks the keys under it."""
+    d, hq, hkv, page = 128, 32, 8, 16
+    kv_lens = np.array([1, 15, 16, 17, 300, 1000, 2305, 64], dtype=np.int32)
+    r = len(kv_lens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=13)
+    q = bf(r, hq, d, seed=14)
+    item_req, st, en, iptr = ops.plan_decode_items(kv_lens, hkv, target_ctas=64, min_chunk=256, window_left=window)
+    assert (st % 16 == 0).all() and (en[iptr[1:] - 1] == kv_lens).all()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    max_items = len(item_req) + 3
+    plan = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
+                          torch.tensor([len(item_req)], dtype=torch.int32, device=DEV),
+                          torch.empty(ops.decode_scratch_floats(max_items, hq, d), device=DEV),
+                          max_items, r, 64, page, window_left=window)
+    scale = 1 / math.sqrt(d)
+    out = ops.paged_decode_attention(q, kv, plan, scale)
+    qo = np.arange(r + 1, dtype=np.int32)
+    want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale, window_left=window)
+    close(out, want, 2e-2)
+
+
 @pytest.mark.parametrize("d,hq,hkv,rows", [(128, 32, 8, 64), (128, 8, 1, 64), (64, 4, 2, 64),
                                            (128, 32, 8, 128), (128, 8, 1, 128), (128, 4, 4, 128),
                                            (128, 32, 2, 128), (128, 8, 4, 128), (128, 32, 8, 256),

@@ -227,3 +227,36 @@ def test_olmo2_post_norm_family_loads_and_matches_dense_oracle(tmp_path):
     assert np.abs(got - want).max() < 1e-3
     with pytest.raises(NotImplementedError):
         loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=0, dtype="float32")
+
+
+def test_sliding_window_prefill_and_decode_match_windowed_oracle():
+    """Mistral-style sliding window: prefill and decode through the paged driver see only the
+    last `sliding_window` keys; config.json enables it for Mistral without a separate switch."""
+    import numpy as np
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models.config import ModelConfig, preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import random_weights
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+
+    hf = dict(model_type="mistral", hidden_size=64, num_hidden_layers=1, num_attention_heads=2, vocab_size=100,
+              sliding_window=4096)
+    assert ModelConfig.from_hf(hf).sliding_window == 4096
+    assert ModelConfig.from_hf(dict(hf, model_type="qwen2")).sliding_window == -1
+    assert ModelConfig.from_hf(dict(hf, model_type="qwen2", use_sliding_window=True)).sliding_window == 4096
+
+    cfg = preset("tiny-llama", sliding_window=21)
+    w = random_weights(cfg, "cpu", torch.float32, seed=7, std=0.08)
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=16, page_size=16, max_requests=4, max_tokens=128)
+    toks = list(range(200, 250))
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    resp = drv.fire_batch(fold([PendingRequest(0, toks, list(range(len(toks))), list(range(5)), 0, [(len(toks) - 1, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg, w, torch.tensor(toks))[-1].numpy()
+    full = dense_reference_forward(preset("tiny-llama"), w, torch.tensor(toks))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3 and np.abs(want - full).max() > 1e-2      # the window matters
+    resp = drv.fire_batch(fold([PendingRequest(0, [9], [len(toks)], list(range(5)), len(toks), [(0, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg, w, torch.tensor(toks + [9]))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3
