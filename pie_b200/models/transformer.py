@@ -53,7 +53,7 @@ class Transformer:
         self.hq = cfg.num_attention_heads // t
         self.hkv = max(1, cfg.num_key_value_heads // t)
         self.d = cfg.head_dim
-        self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.sm_scale = reference.rope_attention_factor(cfg.rope_scaling) ** 2 / math.sqrt(cfg.head_dim)
         self.inv_freq = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, self.device)
         self.gemm_backend = gemm_backend if self.device.type == "cuda" else "torch"
         self.vocab_local = weights["lm_head"].shape[0] * (self.par.tp_size if self.par.comm is not None else 1)
@@ -234,7 +234,7 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         q, k = reference._rope(q, pos, inv), reference._rope(k, pos, inv)
         k = k.repeat_interleave(hq // hkv, dim=1)
         v = v.repeat_interleave(hq // hkv, dim=1)
-        s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
+        s = torch.einsum("qhd,khd->hqk", q, k) * (reference.rope_attention_factor(cfg.rope_scaling) ** 2 / math.sqrt(d))
         s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
         if cfg.sliding_window and cfg.sliding_window > 0:       # a query sees itself and the sliding_window - 1 keys before it
             s = s.masked_fill(torch.tril(torch.ones(t, t, dtype=torch.bool), -cfg.sliding_window)[None], float("-inf"))

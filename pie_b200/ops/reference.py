@@ -42,12 +42,29 @@ def swiglu_interleaved(gate_up):
 
 
 def rope_inv_freq(head_dim, theta, scaling=None, device="cpu"):
-    """Inverse frequencies of rotate-half RoPE, with optional Llama-3 frequency scaling.
+    """Inverse frequencies of rotate-half RoPE, with optional Llama-3, linear or YaRN frequency
+    scaling (`rope_scaling` of a Hugging Face config).
 
     Mirrors the frequency tables of the reference (driver/cuda/src/kernels/rope.cu:55-160).
     """
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
-    if scaling and scaling.get("rope_type", scaling.get("type")) == "llama3":
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type"))
+    if kind == "linear":
+        inv = inv / float(scaling.get("factor", 1.0))
+    elif kind == "yarn":
+        factor = float(scaling.get("factor", 1.0))
+        orig = float(scaling.get("original_max_position_embeddings", 4096))
+        fast, slow = float(scaling.get("beta_fast", 32.0)), float(scaling.get("beta_slow", 1.0))
+
+        def corr_dim(rot):      # dimension whose wavelength makes `rot` turns over the original context
+            return head_dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
+
+        low = max(math.floor(corr_dim(fast)), 0)
+        high = min(math.ceil(corr_dim(slow)), head_dim - 1)
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float64) - low) / max(high - low, 1e-3)).clamp(0, 1)
+        keep = 1.0 - ramp       # 1: high-frequency dimensions keep their frequency, 0: interpolated by `factor`
+        inv = inv / factor * (1 - keep) + inv * keep
+    if kind == "llama3":
         factor = scaling.get("factor", 8.0)
         lo = scaling.get("low_freq_factor", 1.0)
         hi = scaling.get("high_freq_factor", 4.0)
@@ -58,6 +75,17 @@ def rope_inv_freq(head_dim, theta, scaling=None, device="cpu"):
         mid = (wavelen <= old / lo) & (wavelen >= old / hi)
         inv = torch.where(mid, (1 - smooth) * inv / factor + smooth * inv, scaled)
     return inv.float().to(device)
+
+
+def rope_attention_factor(scaling=None) -> float:
+    """YaRN scales cos and sin by a factor (0.1 ln(factor) + 1 unless the config names one): the
+    attention logits grow by its square, which callers fold into the softmax scale."""
+    if not scaling or scaling.get("rope_type", scaling.get("type")) != "yarn":
+        return 1.0
+    if scaling.get("attention_factor"):
+        return float(scaling["attention_factor"])
+    f = float(scaling.get("factor", 1.0))
+    return 0.1 * math.log(f) + 1.0 if f > 1 else 1.0
 
 
 def _rope(x, positions, inv_freq):

@@ -260,3 +260,21 @@ def test_sliding_window_prefill_and_decode_match_windowed_oracle():
     got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
     want = dense_reference_forward(cfg, w, torch.tensor(toks + [9]))[-1].numpy()
     assert np.abs(got - want).max() < 1e-3
+
+
+def test_rope_scaling_tables_match_transformers():
+    """Llama-3, linear and YaRN frequency tables (and YaRN's attention factor) against the
+    Hugging Face implementation."""
+    from pie_b200.ops import reference as r
+    tf = pytest.importorskip("transformers")
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    for sc in [dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=32768),
+               dict(rope_type="linear", factor=2.0),
+               dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                    original_max_position_embeddings=8192)]:
+        cfg = tf.LlamaConfig(hidden_size=4096, num_attention_heads=32, rope_theta=1e6, max_position_embeddings=131072,
+                             rope_scaling=dict(sc))
+        inv, att = ROPE_INIT_FUNCTIONS[sc["rope_type"]](cfg, "cpu")
+        mine = r.rope_inv_freq(128, 1e6, sc)
+        assert float((inv - mine).abs().max() / inv.abs().max()) < 1e-6
+        assert abs(att - r.rope_attention_factor(sc)) < 1e-9
