@@ -282,7 +282,17 @@ def execute_program(prog: Program, reader, device="cpu") -> dict:
 
 def load_checkpoint(path, device="cpu", tp_size: int = 1, tp_rank: int = 0, ep: bool = False,
                     dtype: Optional[str] = None):
-    """config.json + safetensors -> (ModelConfig, weights of this rank)."""
+    """config.json + safetensors, or one .gguf file (or a directory holding one and no
+    safetensors) -> (ModelConfig, weights of this rank)."""
+    p = Path(path)
+    ggufs = [p] if p.is_file() and p.suffix == ".gguf" else \
+        (sorted(p.glob("*.gguf")) if p.is_dir() and not list(p.glob("*.safetensors")) else [])
+    if ggufs:
+        from .gguf import GGUFReader
+        reader = GGUFReader(ggufs[0])
+        cfg = reader.config()
+        prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)
+        return cfg, execute_program(prog, reader, device)
     cfg = ModelConfig.from_path(path)
     reader = SafetensorsReader(path)
     prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)

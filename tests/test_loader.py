@@ -278,3 +278,63 @@ def test_rope_scaling_tables_match_transformers():
         mine = r.rope_inv_freq(128, 1e6, sc)
         assert float((inv - mine).abs().max() / inv.abs().max()) < 1e-6
         assert abs(att - r.rope_attention_factor(sc)) < 1e-9
+
+
+def test_gguf_checkpoint_loads_like_safetensors(tmp_path):
+    """A GGUF file (llama architecture: q/k rows in llama.cpp's interleaved order; F16, BF16, F32
+    and Q8_0 tensors) loads through the same storage program as safetensors, also sharded."""
+    import numpy as np
+    from pie_b200.models import gguf, loader
+    from pie_b200.models.config import preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import random_weights
+
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=9, std=0.05)
+    d, hq, hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    tensors = {"token_embd.weight": (w["embed"], gguf.T_F16), "output_norm.weight": (w["final_norm"], gguf.T_F32),
+               "output.weight": (w["lm_head"], gguf.T_BF16)}
+    for li, lw in enumerate(w["layers"]):
+        q, k, v = lw["wqkv"].split([hq * d, hkv * d, hkv * d], 0)
+        B = f"blk.{li}."
+        tensors[B + "attn_norm.weight"] = (lw["ln1"], gguf.T_F32)
+        tensors[B + "ffn_norm.weight"] = (lw["ln2"], gguf.T_F32)
+        tensors[B + "attn_q.weight"] = (gguf.permute_rotary(q, hq), gguf.T_F16)
+        tensors[B + "attn_k.weight"] = (gguf.permute_rotary(k, hkv), gguf.T_F16)
+        tensors[B + "attn_v.weight"] = (v, gguf.T_Q8_0)
+        tensors[B + "attn_output.weight"] = (lw["wo"], gguf.T_F16)
+        tensors[B + "ffn_gate.weight"] = (lw["w_gate_up"][0::2], gguf.T_F16)
+        tensors[B + "ffn_up.weight"] = (lw["w_gate_up"][1::2], gguf.T_F16)
+        tensors[B + "ffn_down.weight"] = (lw["w_down"], gguf.T_Q8_0)
+    meta = {"general.architecture": "llama", "general.name": "tiny", "llama.embedding_length": cfg.hidden_size,
+            "llama.block_count": cfg.num_hidden_layers, "llama.attention.head_count": hq,
+            "llama.attention.head_count_kv": hkv, "llama.feed_forward_length": cfg.intermediate_size,
+            "llama.context_length": 4096, "llama.rope.freq_base": float(cfg.rope_theta),
+            "llama.attention.layer_norm_rms_epsilon": float(cfg.rms_norm_eps), "llama.vocab_size": cfg.vocab_size,
+            "tokenizer.ggml.tokens": ["a", "b", "c"]}
+    path = tmp_path / "tiny.gguf"
+    gguf.write_gguf(path, meta, tensors)
+
+    rd = gguf.GGUFReader(path)
+    assert rd.meta["tokenizer.ggml.tokens"] == ["a", "b", "c"] and rd.version == 3
+    cfg2, w2 = loader.load_checkpoint(path, "cpu", dtype="float32")
+    assert (cfg2.hidden_size, cfg2.num_hidden_layers, cfg2.num_key_value_heads, cfg2.head_dim, cfg2.vocab_size) == \
+        (cfg.hidden_size, cfg.num_hidden_layers, hkv, d, cfg.vocab_size)
+    assert not cfg2.tie_word_embeddings
+    lw, lw2 = w["layers"][1], w2["layers"][1]
+    assert (lw2["wqkv"][: (hq + hkv) * d] - lw["wqkv"][: (hq + hkv) * d]).abs().max() < 1e-3      # fp16 rounding, order restored
+    assert (lw2["w_down"] - lw["w_down"]).abs().max() < 0.05 * lw["w_down"].abs().max() / 2          # Q8_0 steps
+    assert (lw2["w_gate_up"] - lw["w_gate_up"]).abs().max() < 1e-3
+    toks = torch.arange(50, 90)
+    got = dense_reference_forward(cfg2, w2, toks)[-1]
+    want = dense_reference_forward(cfg, w, toks)[-1]
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0) > 0.999
+    # directory form and a tensor-parallel shard
+    _, wr = loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=1, dtype="float32")
+    assert torch.equal(wr["layers"][0]["wo"], w2["layers"][0]["wo"][:, hq * d // 2:])
+    # Q4_0 blocks expand as scale * (nibble - 8)
+    raw = np.zeros(18, dtype=np.uint8)
+    raw[:2] = np.array([0.5], dtype=np.float16).view(np.uint8)
+    raw[2] = 0x1F            # element 0 = 15, element 16 = 1
+    x = gguf.dequantize(raw, gguf.T_Q4_0, 32)
+    assert x[0] == 0.5 * (15 - 8) and x[16] == 0.5 * (1 - 8) and x[1] == 0.5 * (0 - 8)
