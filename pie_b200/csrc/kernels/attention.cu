@@ -184,7 +184,8 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          const int* __restrict__ req_item_indptr,
                          const int* __restrict__ num_items_ptr, bf16* __restrict__ out,
                          float* __restrict__ o_part, float* __restrict__ lse_part, int hq, int hkv,
-                         int page_size, float scale_log2, int window_left) {
+                         int page_size, float scale_log2, int window_left,
+                         const float* __restrict__ sinks_log2) {
     static_assert(G <= 16, "at most 16 query heads per KV head");
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int CH = D / 8;              // 16-byte chunks per row
@@ -303,8 +304,10 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                     O += sm_o[(ww * G + row) * D + dim] * sc;
                 }
             }
-            const float val = L > 0.f ? O / L : 0.f;
+            float val = L > 0.f ? O / L : 0.f;
             if (single) {
+                // attention sink: a per-head logit that takes probability mass but has no value row
+                if (sinks_log2 && L > 0.f) val = O / (L + exp2f(sinks_log2[h * G + row] - M));
                 out[((size_t)req * hq + h * G + row) * D + dim] = __float2bfloat16(val);
             } else {
                 o_part[(((size_t)it * hkv + h) * G + row) * D + dim] = val;
@@ -320,7 +323,8 @@ template <int D>
 __global__ void paged_decode_merge_kernel(const float* __restrict__ o_part,
                                           const float* __restrict__ lse_part,
                                           const int* __restrict__ req_item_indptr,
-                                          bf16* __restrict__ out, int hq, int hkv, int group) {
+                                          bf16* __restrict__ out, int hq, int hkv, int group,
+                                          const float* __restrict__ sinks_log2) {
     const int req = blockIdx.x, qh = blockIdx.y;
     pdl_trigger();
     pdl_wait();
@@ -338,6 +342,7 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ o_part,
                 L += sc;
                 O += o_part[base * D + dim] * sc;
             }
+            if (sinks_log2) L += exp2f(sinks_log2[qh] - M);
         }
         out[((size_t)req * hq + qh) * D + dim] = __float2bfloat16(L > 0.f ? O / L : 0.f);
     }
@@ -362,7 +367,7 @@ paged_prefill_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                           const int* __restrict__ tile_req, const int* __restrict__ tile_qstart,
                           const uint32_t* __restrict__ mask_bits,
                           const long* __restrict__ mask_word_indptr, bf16* __restrict__ out,
-                          float* __restrict__ lse_out, int hq, int hkv, int page_size,
+                          float* __restrict__ lse_out, const float* __restrict__ sinks_log2, int hq, int hkv, int page_size,
                           float scale_log2, int window_left) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int CH = D / 8;
@@ -485,6 +490,7 @@ paged_prefill_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
         if (qtok[hh] >= qo_len) continue;
         const int row = warp * 16 + g + hh * 8;
         const int head = h * G + row % G;
+        if (sinks_log2 && st.l[hh] > 0.f) st.l[hh] += exp2f(sinks_log2[head] - st.m[hh]);
         const float inv = st.l[hh] > 0.f ? 1.f / st.l[hh] : 0.f;
         bf16* dst = out + ((size_t)(q_base + qtok[hh]) * hq + head) * D;
 #pragma unroll
@@ -537,14 +543,16 @@ PIE_API long pie_decode_attn_scratch_floats(int max_items, int hq, int head_dim)
 }
 
 // window_left >= 0: each request's single query token sees only the last window_left + 1 keys; the
-// caller's items then start at the 16-token boundary at or below the first visible key.
+// caller's items then start at the 16-token boundary at or below the first visible key (items that
+// start lower are masked). sinks_log2 (optional, [hq], logit * log2(e)): per-head attention sinks.
 PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, const int* page_indices,
                                          const int* kv_page_indptr, const int* item_req,
                                          const int* item_start, const int* item_end,
                                          const int* req_item_indptr, const int* num_items_ptr,
                                          void* out, float* scratch, int max_items, int num_reqs, int hq,
                                          int hkv, int head_dim, int page_size, float sm_scale,
-                                         int num_ctas, int run_merge, int window_left, cudaStream_t st) {
+                                         int num_ctas, int run_merge, int window_left,
+                                         const float* sinks_log2, cudaStream_t st) {
     if (num_reqs <= 0) return 0;
     if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
     const int group = hq / hkv;
@@ -558,17 +566,17 @@ PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, co
         launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
             (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
             item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
-            hkv, page_size, scale_log2, window_left);
+            hkv, page_size, scale_log2, window_left, sinks_log2);
     });
     int err = (int)cudaGetLastError();
     if (err || !run_merge) return err;
     dim3 grid(num_reqs, hq);
     if (head_dim == 128)
         launch_pdl(paged_decode_merge_kernel<128>, grid, dim3(128), 0, st, (const float*)o_part,
-                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group);
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2);
     else
         launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, (const float*)o_part,
-                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group);
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2);
     return (int)cudaGetLastError();
 }
 
@@ -581,7 +589,7 @@ PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int
                                   int num_ctas, int run_merge, cudaStream_t st) {
     return pie_paged_decode_attn_window(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start, item_end,
                                         req_item_indptr, num_items_ptr, out, scratch, max_items, num_reqs, hq, hkv,
-                                        head_dim, page_size, sm_scale, num_ctas, run_merge, -1, st);
+                                        head_dim, page_size, sm_scale, num_ctas, run_merge, -1, nullptr, st);
 }
 
 PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const int* page_indices,
@@ -590,7 +598,7 @@ PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const in
                                    int num_tiles, const uint32_t* mask_bits,
                                    const long* mask_word_indptr, void* out, float* lse_out, int hq,
                                    int hkv, int head_dim, int page_size, float sm_scale,
-                                   int window_left, cudaStream_t st) {
+                                   int window_left, const float* sinks_log2, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
     if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
     const int group = hq / hkv;
@@ -602,7 +610,7 @@ PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const in
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
         kern<<<grid, PF_WARPS * 32, SM, st>>>(
             (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, qo_indptr, kv_lens,
-            tile_req, tile_qstart, mask_bits, mask_word_indptr, (bf16*)out, lse_out, hq, hkv,
+            tile_req, tile_qstart, mask_bits, mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv,
             page_size, scale_log2, window_left);
     });
     return (int)cudaGetLastError();

@@ -84,8 +84,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                              const int* __restrict__ qo_indptr, const int* __restrict__ kv_lens,
                              const int* __restrict__ tile_req, const int* __restrict__ tile_qstart,
                              const uint32_t* __restrict__ mask_bits, const long* __restrict__ mask_word_indptr,
-                             bf16* __restrict__ out, float* __restrict__ lse_out, int hq, int hkv, int pad_page,
-                             float scale_log2, int window_left, int* status) {
+                             bf16* __restrict__ out, float* __restrict__ lse_out, const float* __restrict__ sinks_log2,
+                             int hq, int hkv, int pad_page, float scale_log2, int window_left, int* status) {
     constexpr int TQ = AT_ROWS / G;          // query tokens per MMA tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
@@ -374,6 +374,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
         if (ok && my_nkb > 0) {
             tc_fence_after();
             const int head = h * G + row % G;
+            // attention sink: a per-head logit in the softmax denominator without a value row
+            if (sinks_log2 && l > 0.f) l += exp2f(sinks_log2[head] - m_ref * scale_log2);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(q_base + (valid ? qtok : 0)) * hq + head) * AT_D;
 #pragma unroll
@@ -440,7 +442,8 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
                                       const int* tile_req, const int* tile_qstart, int num_tiles,
                                       const uint32_t* mask_bits, const long* mask_word_indptr, void* out,
                                       float* lse_out, int n_tokens, int hq, int hkv, int total_pages, float sm_scale,
-                                      int window_left, int tile_rows, int* status, cudaStream_t st) {
+                                      int window_left, int tile_rows, const float* sinks_log2, int* status,
+                                      cudaStream_t st) {
     if (num_tiles <= 0) return 0;
     if (!pie_prefill_attn_tc_supported(hq, hkv, AT_D, 16) || (tile_rows != 128 && tile_rows != 256) || !status)
         return (int)cudaErrorInvalidValue;
@@ -477,7 +480,8 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
         if (e != cudaSuccess) return (int)e;                                                                          \
         kern<<<grid, AtCfg<NT_>::THREADS, AtCfg<NT_>::SMEM, st>>>(                                                    \
             tq, tkv, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req, tile_qstart, mask_bits,              \
-            mask_word_indptr, (bf16*)out, lse_out, hq, hkv, total_pages - 1, scale_log2, window_left, status);        \
+            mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv, total_pages - 1, scale_log2, window_left,     \
+            status);                                                                                                  \
         return (int)cudaGetLastError();                                                                               \
     }
 #define GO(G_)                 \

@@ -169,8 +169,8 @@ class TorchDriver:
         self.max_requests, self.max_tokens = max_requests, max_tokens
         self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
         self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
-        # HF sliding_window = number of keys a query sees, itself included
-        self.window_left = self.cfg.sliding_window - 1 if self.cfg.sliding_window and self.cfg.sliding_window > 0 else -1
+        # the widest window any layer needs (-1: some layer sees everything); layers that differ mask per call
+        self.window_left = self.cfg.plan_window_left
         self.max_items = max_requests + self.num_ctas * 8
         rows = max(max_requests, 1024)
         self.max_rows = rows

@@ -12,7 +12,7 @@ from typing import Optional
 
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 POST_NORM = {"olmo2"}       # same block with the norms after attention / MLP and q, k norms over all heads
-MOE_TYPES = {"qwen3_moe", "mixtral"}
+MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
 
 
 @dataclass
@@ -34,11 +34,16 @@ class ModelConfig:
     attention_bias: bool = False    # Qwen2: bias on q/k/v projections
     sliding_window: int = -1
     post_norm: bool = False         # OLMo-2: h += norm(attn(h)); h += norm(mlp(h)); q/k RMSNorm over the whole projection
+    layer_types: Optional[list] = None   # per layer "sliding_attention" | "full_attention" (GPT-OSS); None: all alike
+    attention_sinks: bool = False   # GPT-OSS: a learned per-head logit in every softmax denominator
+    o_bias: bool = False            # bias on the attention output projection
     # mixture of experts
     num_experts: int = 0
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    moe_style: str = "swiglu"       # "gpt_oss": expert and router biases, clamped (up + 1) * gate * sigmoid(1.702 gate)
+    swiglu_limit: float = 7.0
     # quantisation of the linear weights: None | "fp8_block" (128x128 weight scales)
     quantization: Optional[str] = None
     dtype: str = "bfloat16"
@@ -47,6 +52,20 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    def layer_window_left(self, li: int) -> int:
+        """Keys left of the query that layer `li` sees (-1: all). HF `sliding_window` counts the query itself."""
+        if not self.sliding_window or self.sliding_window <= 0:
+            return -1
+        if self.layer_types is not None and self.layer_types[li] != "sliding_attention":
+            return -1
+        return self.sliding_window - 1
+
+    @property
+    def plan_window_left(self) -> int:
+        """The window attention plans may be cut to: the widest any layer needs."""
+        ws = [self.layer_window_left(li) for li in range(self.num_hidden_layers)]
+        return -1 if any(w < 0 for w in ws) or not ws else max(ws)
 
     @property
     def q_size(self) -> int:
@@ -84,13 +103,20 @@ class ModelConfig:
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
             qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2") or cfg.get("use_qk_norm", False),
             post_norm=mt in POST_NORM,
-            attention_bias=cfg.get("attention_bias", mt == "qwen2"),
+            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "gpt_oss")),
             # Qwen2 gates the window on use_sliding_window; Mistral applies it whenever it is set
-            sliding_window=(cfg.get("sliding_window") or -1) if cfg.get("use_sliding_window", mt == "mistral") else -1,
+            sliding_window=(cfg.get("sliding_window") or -1)
+            if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss")) else -1,
+            layer_types=cfg.get("layer_types") if mt == "gpt_oss" else None,
+            attention_sinks=mt == "gpt_oss",
+            o_bias=mt == "gpt_oss" and cfg.get("attention_bias", True),
+            moe_style="gpt_oss" if mt == "gpt_oss" else "swiglu",
+            swiglu_limit=float(cfg.get("swiglu_limit", 7.0)),
             num_experts=cfg.get("num_experts", cfg.get("num_local_experts", 0)) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
             # Mixtral has no separate field: its intermediate_size is the expert FFN width
-            moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or (cfg.get("intermediate_size", 0) if mt == "mixtral" else 0),
+            moe_intermediate_size=cfg.get("moe_intermediate_size", 0)
+            or (cfg.get("intermediate_size", 0) if mt in ("mixtral", "gpt_oss") else 0),
             norm_topk_prob=cfg.get("norm_topk_prob", True),
             quantization=quant,
             dtype=str(cfg.get("torch_dtype", "bfloat16")),
@@ -134,6 +160,20 @@ PRESETS = {
     "tiny-olmo2": dict(model_type="olmo2", hidden_size=256, intermediate_size=688, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000,
                        rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True, post_norm=True, dtype="float32"),
+    "gpt-oss-20b": dict(model_type="gpt_oss", hidden_size=2880, intermediate_size=2880, num_hidden_layers=24,
+                        num_attention_heads=64, num_key_value_heads=8, head_dim=64, vocab_size=201088,
+                        rope_theta=150000.0, rms_norm_eps=1e-5, attention_bias=True, o_bias=True, attention_sinks=True,
+                        sliding_window=128, layer_types=["sliding_attention", "full_attention"] * 12,
+                        num_experts=32, num_experts_per_tok=4, moe_intermediate_size=2880, moe_style="gpt_oss",
+                        rope_scaling=dict(rope_type="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0,
+                                          original_max_position_embeddings=4096, truncate=False)),
+    "tiny-gpt-oss": dict(model_type="gpt_oss", hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000,
+                         rope_theta=10000.0, rms_norm_eps=1e-5, attention_bias=True, o_bias=True,
+                         attention_sinks=True, sliding_window=20, layer_types=["sliding_attention", "full_attention"],
+                         num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, moe_style="gpt_oss",
+                         rope_scaling=dict(rope_type="yarn", factor=4.0, beta_fast=32.0, beta_slow=1.0,
+                                           original_max_position_embeddings=64, truncate=False), dtype="float32"),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,

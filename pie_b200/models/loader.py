@@ -11,6 +11,8 @@ against a safetensors reader, producing this rank's weight dict. Ops:
   Interleave()                    rows g0,u0,g1,u1,... (gate/up for the SwiGLU GEMM epilogue)
   Stack()                         expert stacks
   Cast(dtype) / DequantFp8Block() dtype change / 128x128 block-scaled fp8 -> bf16
+  Transpose(a, b)                 swap two dimensions (GPT-OSS stores experts as [E, in, out])
+  Mxfp4(blocks, scales)           e2m1 nibbles with one e8m0 scale per 32 -> values [.., rows, cols]
   Attach(path)                    store under a runtime name
 
 The program is serialisable (`program_to_json`), so a per-rank plan can be compiled once and
@@ -52,6 +54,33 @@ def Concat(xs, axis=0): return Op("concat", {"axis": axis}, list(xs))
 def Interleave(a, b): return Op("interleave", {}, [a, b])
 def Stack(xs): return Op("stack", {}, list(xs))
 def ExpandRows(x, factor, like): return Op("expand_rows", {"factor": factor, "like": like}, [x])
+def Transpose(x, a, b): return Op("transpose", {"a": a, "b": b}, [x])
+def Mxfp4(blocks, scales): return Op("mxfp4", {}, [blocks, scales])
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def dequant_mxfp4(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """blocks [..., rows, cols/32, 16] uint8 (two e2m1 values per byte, low nibble first),
+    scales [..., rows, cols/32] uint8 (e8m0: 2^(s - 127)) -> float32 [..., rows, cols]."""
+    lut = torch.tensor(_E2M1, dtype=torch.float32)
+    b = blocks.to(torch.int64)
+    vals = torch.stack([lut[b & 0x0F], lut[b >> 4]], dim=-1).reshape(*blocks.shape[:-1], 32)
+    sc = torch.exp2(scales.to(torch.float32) - 127.0)
+    return (vals * sc[..., None]).reshape(*blocks.shape[:-2], blocks.shape[-2] * 32)
+
+
+def quant_mxfp4(w: torch.Tensor):
+    """Inverse of :func:`dequant_mxfp4` for tests and tooling: nearest e2m1 value under a
+    power-of-two scale per 32 columns. Returns (blocks, scales) as uint8."""
+    g = w.float().reshape(*w.shape[:-1], w.shape[-1] // 32, 32)
+    amax = g.abs().amax(-1).clamp_min(2.0 ** -120)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    q = g / torch.exp2(e)[..., None]
+    lut = torch.tensor(_E2M1, dtype=torch.float32)
+    idx = (q[..., None] - lut).abs().argmin(-1).to(torch.uint8)
+    blocks = (idx[..., 0::2] | (idx[..., 1::2] << 4)).contiguous()
+    return blocks, (e + 127).to(torch.uint8).contiguous()
 
 
 class QLin:
@@ -151,11 +180,28 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
                                       Rows(w(L + "self_attn.k_proj.bias"), kv0 * d, kvn * d),
                                       Rows(w(L + "self_attn.v_proj.bias"), kv0 * d, kvn * d)], 0)
         lin(L + "self_attn.o_proj.weight").shard(1, r, T).attach(att, P + "wo")
+        if L + "self_attn.o_proj.bias" in names:
+            att[P + "bo"] = w(L + "self_attn.o_proj.bias")
+        if L + "self_attn.sinks" in names:
+            att[P + "sinks"] = Shard(w(L + "self_attn.sinks"), 0, r, T)
         if L + "self_attn.q_norm.weight" in names:
             att[P + "q_norm"] = w(L + "self_attn.q_norm.weight")
             att[P + "k_norm"] = w(L + "self_attn.k_norm.weight")
         mixtral = L + "block_sparse_moe.gate.weight" in names      # Mixtral names: w1 = gate, w3 = up, w2 = down
-        if cfg.is_moe and (L + "mlp.gate.weight" in names or mixtral):
+        if cfg.is_moe and L + "mlp.router.weight" in names:
+            # GPT-OSS: experts stacked in one tensor, gate/up columns already interleaved; bf16 checkpoints
+            # hold [E, in, out], MXFP4 ones blocks + scales in [E, out, in/32, ...]
+            if T > 1:
+                raise NotImplementedError("GPT-OSS expert biases are not sharded: tp_size must be 1")
+            X = L + "mlp.experts."
+            att[P + "router"], att[P + "router_bias"] = w(L + "mlp.router.weight"), w(L + "mlp.router.bias")
+            for src, dst in (("gate_up_proj", "experts_gate_up"), ("down_proj", "experts_down")):
+                if X + src + "_blocks" in names:
+                    att[P + dst] = Mxfp4(w(X + src + "_blocks"), w(X + src + "_scales"))
+                else:
+                    att[P + dst] = Transpose(w(X + src), 1, 2)
+                att[P + dst + "_bias"] = w(X + src + "_bias")
+        elif cfg.is_moe and (L + "mlp.gate.weight" in names or mixtral):
             att[P + "router"] = w(L + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight"))
             E = cfg.num_experts
             experts = range(r * (E // T), (r + 1) * (E // T)) if (ep and T > 1) else range(E)
@@ -244,6 +290,10 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
         return y.view(torch.float8_e4m3fn) if f8 else y
     if k == "stack":
         return torch.stack(xs, dim=0)
+    if k == "transpose":
+        return xs[0].transpose(op.args["a"], op.args["b"])
+    if k == "mxfp4":
+        return dequant_mxfp4(xs[0], xs[1])
     if k == "expand_rows":
         rows = reader.get_slice(op.args["like"]).get_shape()[0]       # ragged last block: cut to the weight's rows
         return xs[0].float().repeat_interleave(op.args["factor"], dim=0)[:rows]
@@ -322,7 +372,17 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
             t[L + "self_attn.q_proj.bias"], t[L + "self_attn.k_proj.bias"], t[L + "self_attn.v_proj.bias"] = bq, bk, bv
         if "q_norm" in lw:
             t[L + "self_attn.q_norm.weight"], t[L + "self_attn.k_norm.weight"] = lw["q_norm"], lw["k_norm"]
-        if "experts_gate_up" in lw:
+        if "bo" in lw:
+            t[L + "self_attn.o_proj.bias"] = lw["bo"]
+        if "sinks" in lw:
+            t[L + "self_attn.sinks"] = lw["sinks"]
+        if "experts_gate_up_bias" in lw:
+            t[L + "mlp.router.weight"], t[L + "mlp.router.bias"] = lw["router"], lw["router_bias"]
+            t[L + "mlp.experts.gate_up_proj"] = lw["experts_gate_up"].transpose(1, 2)
+            t[L + "mlp.experts.down_proj"] = lw["experts_down"].transpose(1, 2)
+            t[L + "mlp.experts.gate_up_proj_bias"] = lw["experts_gate_up_bias"]
+            t[L + "mlp.experts.down_proj_bias"] = lw["experts_down_bias"]
+        elif "experts_gate_up" in lw:
             t[L + "mlp.gate.weight"] = lw["router"]
             for e in range(lw["experts_gate_up"].shape[0]):
                 gu = lw["experts_gate_up"][e]
@@ -337,7 +397,11 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
           "head_dim": d, "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
           "tie_word_embeddings": cfg.tie_word_embeddings, "torch_dtype": cfg.dtype, "attention_bias": cfg.attention_bias,
           "max_position_embeddings": cfg.max_position_embeddings}
-    if cfg.is_moe:
+    if cfg.model_type == "gpt_oss":
+        hf.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
+                  sliding_window=cfg.sliding_window, layer_types=cfg.layer_types, swiglu_limit=cfg.swiglu_limit,
+                  rope_scaling=cfg.rope_scaling)
+    elif cfg.is_moe:
         hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)
     (p / "config.json").write_text(json.dumps(hf))

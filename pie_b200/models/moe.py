@@ -16,6 +16,15 @@ from .. import ops
 from .config import ModelConfig
 
 
+def gpt_oss_glu(gu: torch.Tensor, limit: float) -> torch.Tensor:
+    """GPT-OSS expert activation on interleaved (gate, up) columns: gate clamped from above, up
+    clamped to +-limit, (up + 1) * gate * sigmoid(1.702 * gate)
+    (the reference's gpt_oss_glu kernel: driver/cuda/src/kernels/swiglu.cu)."""
+    gate = gu[..., 0::2].float().clamp(max=limit)
+    up = gu[..., 1::2].float().clamp(-limit, limit)
+    return (up + 1.0) * gate * torch.sigmoid(1.702 * gate)
+
+
 def route(cfg: ModelConfig, logits: torch.Tensor):
     """Router: softmax over experts, top-k, renormalise. Returns (weights fp32 [N,k], ids [N,k])."""
     probs = torch.softmax(logits.float(), dim=-1)
@@ -28,7 +37,11 @@ def route(cfg: ModelConfig, logits: torch.Tensor):
 def moe_reference(cfg: ModelConfig, x: torch.Tensor, lw: dict) -> torch.Tensor:
     """Dense fp32 oracle: every token through its top-k experts (full, unsharded experts)."""
     xf = x.float()
-    w, ids = route(cfg, xf @ lw["router"].float().t())
+    logits = xf @ lw["router"].float().t()
+    biased = "experts_gate_up_bias" in lw
+    if "router_bias" in lw:
+        logits = logits + lw["router_bias"].float()
+    w, ids = route(cfg, logits)
     out = torch.zeros_like(xf)
     for e in range(lw["experts_gate_up"].shape[0]):
         sel = (ids == e)
@@ -36,8 +49,12 @@ def moe_reference(cfg: ModelConfig, x: torch.Tensor, lw: dict) -> torch.Tensor:
         if tok.numel() == 0:
             continue
         gu = xf[tok] @ lw["experts_gate_up"][e].float().t()
-        act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
-        y = act @ lw["experts_down"][e].float().t()
+        if biased:
+            act = gpt_oss_glu(gu + lw["experts_gate_up_bias"][e].float(), cfg.swiglu_limit)
+            y = act @ lw["experts_down"][e].float().t() + lw["experts_down_bias"][e].float()
+        else:
+            act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+            y = act @ lw["experts_down"][e].float().t()
         out[tok] += y * (w[tok] * sel[tok]).sum(-1, keepdim=True)
     return out
 
@@ -62,6 +79,8 @@ def moe_block(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torch.Tensor
     Under tensor parallelism without EP the experts are sharded on their intermediate dimension
     (the reference's scheme) and the partial outputs are summed across ranks."""
     cfg, par = model.cfg, model.par
+    if cfg.moe_style == "gpt_oss":
+        return _moe_block_biased(model, x, lw, h)
     if par.tp_size > 1 and par.ep:
         # NCCL baseline of expert parallelism: every rank evaluates its own experts on all tokens
         logits = model._gemm(x, lw["router"]) if x.is_cuda else torch.matmul(x, lw["router"].t())
@@ -98,6 +117,39 @@ def moe_block(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torch.Tensor
     out = torch.zeros(n, x.shape[1], dtype=torch.float32, device=x.device)
     out.index_add_(0, tok, ys.float() * wflat[:, None])
     return h + out.to(x.dtype)
+
+
+def _moe_block_biased(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torch.Tensor:
+    """GPT-OSS experts: router bias, per-expert biases on both projections and the clamped GLU.
+    GPU: the same route / align / permute / grouped tcgen05 GEMM / combine kernels as the SwiGLU
+    block, with the first GEMM storing gate and up unactivated and the biases and the activation
+    applied to the expert-sorted rows in between (row -> expert through the tile table); static
+    shapes, no host synchronisation. CPU: the dense formula."""
+    cfg = model.cfg
+    if model.par.tp_size > 1:
+        raise NotImplementedError("GPT-OSS experts under tensor parallelism")
+    if not x.is_cuda:
+        return h + moe_reference(cfg, x, lw).to(x.dtype)
+    k = cfg.num_experts_per_tok
+    n = x.shape[0]
+    logits = torch.matmul(x, lw["router"].t()) + lw["router_bias"]
+    buf = _buffers(model, n, lw, x.device)
+    mt = ops.moe_max_mtiles(n, k, buf.E)
+    ops.moe_route(logits, k, cfg.norm_topk_prob, buf, 0)
+    ops.moe_align(buf, mt)
+    ops.moe_permute(x, buf)
+    rows = mt * 128
+    gu = getattr(model, "_moe_gu", None)
+    if gu is None or gu.shape[0] < rows or gu.shape[1] != 2 * buf.I:
+        gu = torch.empty(max(rows, buf.xs.shape[0]), 2 * buf.I, dtype=x.dtype, device=x.device)
+        model._moe_gu = gu
+    ops.grouped_gemm(buf.xs, lw["experts_gate_up"], buf.tile_expert, gu, mt, ops.EPI_STORE)
+    row_expert = buf.tile_expert[:mt].clamp(min=0).long().repeat_interleave(128)       # unused tiles: any expert
+    act = gpt_oss_glu(gu[:rows] + lw["experts_gate_up_bias"][row_expert], cfg.swiglu_limit)
+    buf.act[:rows] = act.to(x.dtype)
+    ops.grouped_gemm(buf.act, lw["experts_down"], buf.tile_expert, buf.ys, mt, ops.EPI_STORE)
+    buf.ys[:rows] += lw["experts_down_bias"][row_expert]
+    return ops.moe_combine(buf, n, h)
 
 
 def moe_block_tp(model, lw: dict, n: int) -> None:

@@ -77,12 +77,21 @@ class Transformer:
         return y
 
     # ------------------------------------------------------------------ layers
-    def _attention(self, q, kv_layer, fi: ForwardInputs):
+    def _attention(self, q, kv_layer, fi: ForwardInputs, li: int = 0, lw: Optional[dict] = None):
+        """Layer `li`'s attention: its own sliding window where layers differ (the plan then covers
+        the whole range and the kernels mask), and its attention sinks where the model has them."""
+        wl = self.cfg.layer_window_left(li) if self.cfg.layer_types is not None else None
+        sinks = lw.get("sinks") if lw is not None else None
         if not q.is_cuda:
-            return ops.paged_attention_cpu(q, kv_layer, fi.attn, self.sm_scale)
+            return ops.paged_attention_cpu(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks=sinks)
+        sl2 = None
+        if sinks is not None:
+            sl2 = lw.get("sinks_log2")
+            if sl2 is None:
+                sl2 = lw["sinks_log2"] = (sinks.float() * 1.4426950408889634).contiguous()
         if fi.is_decode:
-            return ops.paged_decode_attention(q, kv_layer, fi.attn, self.sm_scale)
-        return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale)
+            return ops.paged_decode_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2)
+        return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2)
 
     def _mlp(self, x, lw, h):
         act = self._gemm(x, lw["w_gate_up"], swiglu=True)
@@ -101,7 +110,7 @@ class Transformer:
 
     def _fused_tp(self) -> bool:
         return self.par.tp_size > 1 and self.par.comm is not None and getattr(self.par.comm, "fused", False) \
-            and self.device.type == "cuda" and not self.cfg.post_norm
+            and self.device.type == "cuda" and not self.cfg.post_norm and self.cfg.model_type != "gpt_oss"
 
     def _forward_hidden_tp(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
         """Tensor-parallel forward over the fused kernels: the residual stream is row-sharded,
@@ -162,7 +171,7 @@ class Transformer:
                 qn = kn = None
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, qn, kn, kv_cache[li],
                                          self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps)
-            a = self._attention(q, kv_cache[li], fi).reshape(n, self.hq * self.d)
+            a = self._attention(q, kv_cache[li], fi, li, lw).reshape(n, self.hq * self.d)
             if post:
                 if "experts_gate_up" in lw:
                     raise NotImplementedError("post-norm blocks with experts")
@@ -174,6 +183,8 @@ class Transformer:
                 h = h + ops.rmsnorm(self._row_parallel(act, lw["w_down"], None), lw["ln3"], cfg.rms_norm_eps)
                 continue
             h = self._row_parallel(a, lw["wo"], h)
+            if "bo" in lw:
+                h = h + lw["bo"]
             if fi.lora:
                 h = apply_lora(fi.lora, li, "o", a, h)
             x = ops.rmsnorm(h, lw["ln2"], cfg.rms_norm_eps)
@@ -218,7 +229,7 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
     def norm(v, g):
         return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * g.float()
 
-    for lw in w["layers"]:
+    for li, lw in enumerate(w["layers"]):
         xn = x if cfg.post_norm else norm(x, lw["ln1"])
         qkv = xn @ lw["wqkv"].float().t()
         if "bqkv" in lw:
@@ -236,15 +247,21 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         v = v.repeat_interleave(hq // hkv, dim=1)
         s = torch.einsum("qhd,khd->hqk", q, k) * (reference.rope_attention_factor(cfg.rope_scaling) ** 2 / math.sqrt(d))
         s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
-        if cfg.sliding_window and cfg.sliding_window > 0:       # a query sees itself and the sliding_window - 1 keys before it
+        if cfg.layer_window_left(li) >= 0:       # a query sees itself and the sliding_window - 1 keys before it
             s = s.masked_fill(torch.tril(torch.ones(t, t, dtype=torch.bool), -cfg.sliding_window)[None], float("-inf"))
-        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(t, hq * d)
+        if "sinks" in lw:       # a per-head extra logit that only takes probability mass
+            s = torch.cat([s, lw["sinks"].float()[:, None, None].expand(hq, t, 1)], dim=-1)
+            a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1)[..., :t], v).reshape(t, hq * d)
+        else:
+            a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(t, hq * d)
         if cfg.post_norm:
             x = x + norm(a @ lw["wo"].float().t(), lw["ln2"])
             gu = x @ lw["w_gate_up"].float().t()
             x = x + norm((torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t(), lw["ln3"])
             continue
         x = x + a @ lw["wo"].float().t()
+        if "bo" in lw:
+            x = x + lw["bo"].float()
         xn = norm(x, lw["ln2"])
         if "experts_gate_up" in lw:
             from .moe import moe_reference

@@ -109,6 +109,10 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             bq, bk, bv = b[:hq * d], b[hq * d:(hq + hkv) * d], b[(hq + hkv) * d:]
             lw["bqkv"] = torch.cat([shard_rows(bq, r, T), bk[kv0 * d:(kv0 + kvn) * d], bv[kv0 * d:(kv0 + kvn) * d]]).contiguous()
         lw["wo"] = shard_cols(gen.normal(H, hq * d), r, T).contiguous()
+        if cfg.o_bias:
+            lw["bo"] = gen.normal(H)
+        if cfg.attention_sinks:
+            lw["sinks"] = shard_rows(gen.normal(hq, std=1.0), r, T).float().contiguous()
         if cfg.qk_norm and cfg.post_norm:
             if T > 1:
                 raise NotImplementedError("q/k norms over all heads need the full projection: tp_size must be 1")
@@ -128,6 +132,12 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             lw["experts_gate_up"] = torch.stack([gate, up], dim=2).reshape(gate.shape[0], 2 * gate.shape[1], H).contiguous()
             lw["experts_down"] = down.contiguous()
             del gate, up, down
+            if cfg.moe_style == "gpt_oss":
+                if T > 1:
+                    raise NotImplementedError("GPT-OSS expert biases are not sharded: tp_size must be 1")
+                lw["router_bias"] = gen.normal(E, std=0.5)
+                lw["experts_gate_up_bias"] = gen.normal(E, 2 * Im, std=0.2)
+                lw["experts_down_bias"] = gen.normal(E, H, std=0.2)
         else:
             I = cfg.intermediate_size
             gate, up = shard_rows(gen.normal(I, H), r, T), shard_rows(gen.normal(I, H), r, T)

@@ -542,17 +542,21 @@ def decode_scratch_floats(max_items: int, hq: int, head_dim: int) -> int:
     return max_items * hq * head_dim + max_items * hq
 
 
-def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=None):
-    """q [R, hq, D] (one token per request) against paged KV; split-KV + merge."""
+def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=None, window_left=None,
+                           sinks_log2=None):
+    """q [R, hq, D] (one token per request) against paged KV; split-KV + merge. `window_left`
+    overrides the plan's window for this call (a layer with its own window; the plan's items
+    must then cover at least that window), `sinks_log2` [hq] fp32 = sink logits * log2(e)."""
     if out is None:
         out = torch.empty_like(q)
+    wl = plan.window_left if window_left is None else window_left
     r, hq, d = q.shape
     hkv = kv_layer.shape[2]
     check(fn("pie_paged_decode_attn_window")(
         ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
         ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),
         ptr(out), ptr(plan.scratch), plan.max_items, plan.num_reqs, hq, hkv, d, plan.page_size,
-        sm_scale, plan.num_ctas, 1, plan.window_left, stream_ptr()), "paged_decode_attn")
+        sm_scale, plan.num_ctas, 1, wl, ptr(sinks_log2), stream_ptr()), "paged_decode_attn")
     return out
 
 
@@ -572,9 +576,11 @@ class PrefillPlan:
     tile_rows: int = 64           # 128 / 256: tiles planned for the tcgen05 kernel
 
 
-def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out=None, lse_out=None):
+def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out=None, lse_out=None,
+                            window_left=None, sinks_log2=None):
     if out is None:
         out = torch.empty_like(q)
+    wl = plan.window_left if window_left is None else window_left
     n, hq, d = q.shape
     hkv = kv_layer.shape[2]
     if plan.tile_rows > 64:
@@ -583,7 +589,7 @@ def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out
             ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
             ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
             ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), n, hq, hkv,
-            kv_layer.shape[0], sm_scale, plan.window_left, plan.tile_rows, ptr(kernel_status(q.device)),
+            kv_layer.shape[0], sm_scale, wl, plan.tile_rows, ptr(sinks_log2), ptr(kernel_status(q.device)),
             stream_ptr()),
             "paged_prefill_attn_tc")
         return out
@@ -591,7 +597,7 @@ def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out
         ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
         ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
         ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), hq, hkv, d,
-        plan.page_size, sm_scale, plan.window_left, stream_ptr()), "paged_prefill_attn")
+        plan.page_size, sm_scale, wl, ptr(sinks_log2), stream_ptr()), "paged_prefill_attn")
     return out
 
 
@@ -631,13 +637,14 @@ def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device, til
                        mask_bits, mask_indptr, batch.window_left, tile_rows)
 
 
-def paged_attention_cpu(q, kv_layer, batch: AttnBatch, sm_scale: float):
+def paged_attention_cpu(q, kv_layer, batch: AttnBatch, sm_scale: float, window_left=None, sinks=None):
     masks = None
     if batch.masks is not None:
         masks = [None if m is None else torch.as_tensor(np.asarray(m, dtype=bool)) for m in batch.masks]
     return reference.paged_attention(q, kv_layer, batch.qo_indptr, batch.kv_page_indptr,
                                      torch.as_tensor(batch.page_indices), batch.kv_lens, sm_scale,
-                                     masks=masks, window_left=batch.window_left)
+                                     masks=masks, window_left=batch.window_left if window_left is None else window_left,
+                                     sinks=sinks)
 
 
 # --------------------------------------------------------------------------- sampling

@@ -59,8 +59,10 @@ def rope_inv_freq(head_dim, theta, scaling=None, device="cpu"):
         def corr_dim(rot):      # dimension whose wavelength makes `rot` turns over the original context
             return head_dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
 
-        low = max(math.floor(corr_dim(fast)), 0)
-        high = min(math.ceil(corr_dim(slow)), head_dim - 1)
+        low, high = corr_dim(fast), corr_dim(slow)
+        if scaling.get("truncate", True):       # GPT-OSS keeps the fractional bounds
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, head_dim - 1)
         ramp = ((torch.arange(head_dim // 2, dtype=torch.float64) - low) / max(high - low, 1e-3)).clamp(0, 1)
         keep = 1.0 - ramp       # 1: high-frequency dimensions keep their frequency, 0: interpolated by `factor`
         inv = inv / factor * (1 - keep) + inv * keep
@@ -133,9 +135,10 @@ def gather_kv(kv_layer, pages, kv_len):
 
 
 def paged_attention(q, kv_layer, qo_indptr, kv_page_indptr, page_indices, kv_lens, sm_scale,
-                    masks=None, window_left=-1, return_lse=False):
+                    masks=None, window_left=-1, return_lse=False, sinks=None):
     """Ragged paged attention. q [N, hq, D]; masks: optional list (per request) of bool
-    [qo_len, kv_len] tensors or None (causal: query i sees kv < kv_len - qo_len + i + 1)."""
+    [qo_len, kv_len] tensors or None (causal: query i sees kv < kv_len - qo_len + i + 1).
+    sinks [hq]: per-head logits that join the softmax denominator without a value row."""
     n, hq, d = q.shape
     hkv = kv_layer.shape[2]
     g = hq // hkv
@@ -167,6 +170,8 @@ def paged_attention(q, kv_layer, qo_indptr, kv_page_indptr, page_indices, kv_len
         m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
         p = (s - m).exp()
         l = p.sum(-1, keepdim=True)
+        if sinks is not None:
+            l = torch.where(l > 0, l + (sinks.float().to(q.device)[:, None, None] - m).exp(), l)
         o = torch.einsum("hqk,hkd->hqd", p, vf) / l.clamp_min(1e-30)
         o = torch.where(l > 0, o, torch.zeros_like(o))
         out[q0:q1] = o.permute(1, 0, 2).to(q.dtype)

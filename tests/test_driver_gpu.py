@@ -22,12 +22,16 @@ def small_cfg(family="llama"):
     extra = dict(model_type="olmo2", qk_norm=True, post_norm=True) if family == "olmo2" else {}
     if family == "window":
         extra = dict(model_type="mistral", sliding_window=24)
+    if family == "gpt_oss":
+        return preset("tiny-gpt-oss", hidden_size=512, intermediate_size=256, moe_intermediate_size=256,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=4096, num_hidden_layers=2,
+                      sliding_window=24, dtype="bfloat16")
     return preset("tiny-llama", hidden_size=512, intermediate_size=1408, num_attention_heads=8,
                   num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16",
                   **extra)
 
 
-@pytest.mark.parametrize("backend,family", [("tcgen05", "llama"), ("cublas", "llama"), ("tcgen05", "olmo2"), ("tcgen05", "window")])
+@pytest.mark.parametrize("backend,family", [("tcgen05", "llama"), ("cublas", "llama"), ("tcgen05", "olmo2"), ("tcgen05", "window"), ("tcgen05", "gpt_oss")])
 def test_prefill_and_decode_logits_match_oracle(backend, family):
     cfg = small_cfg(family)
     w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)

@@ -129,6 +129,49 @@ def test_paged_decode_attention(d, hq, hkv):
     close(out, want, 2e-2)
 
 
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (64, 16, 2)])
+def test_attention_sinks_and_per_call_window(d, hq, hkv):
+    """Per-head sink logits in the softmax denominator (decode: single-item and merged requests;
+    prefill: both kernels) and a window given per call over a plan that covers the whole range."""
+    page = 16
+    sinks = torch.linspace(-2.0, 3.0, hq, device=DEV)
+    sl2 = (sinks * 1.4426950408889634).float().contiguous()
+    scale = 1 / math.sqrt(d)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    # decode
+    kv_lens = np.array([1, 17, 300, 2305, 64], dtype=np.int32)
+    r = len(kv_lens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=51)
+    q = bf(r, hq, d, seed=52)
+    item_req, st, en, iptr = ops.plan_decode_items(kv_lens, hkv, target_ctas=64, min_chunk=256)
+    max_items = len(item_req) + 3
+    plan = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
+                          torch.tensor([len(item_req)], dtype=torch.int32, device=DEV),
+                          torch.empty(ops.decode_scratch_floats(max_items, hq, d), device=DEV), max_items, r, 64, page)
+    qo = np.arange(r + 1, dtype=np.int32)
+    for window in (-1, 40):
+        out = ops.paged_decode_attention(q, kv, plan, scale, window_left=window, sinks_log2=sl2)
+        want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
+                                   window_left=window, sinks=sinks)
+        close(out, want, 2e-2)
+    # prefill
+    qlens = np.array([5, 130, 300], dtype=np.int32)
+    kv_lens = qlens + np.array([40, 0, 77], dtype=np.int32)
+    kv, pages, indptr = make_paged(3, kv_lens, hkv, d, page, seed=53)
+    qo = np.zeros(4, dtype=np.int32)
+    qo[1:] = np.cumsum(qlens)
+    q = bf(int(qo[-1]), hq, d, seed=54)
+    batch = ops.AttnBatch(qo, indptr, pages, kv_lens, None, -1)
+    for rows in ([64, 128, 256] if d == 128 else [64]):
+        plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV, tile_rows=rows)
+        for window in (-1, 33):
+            out = ops.paged_prefill_attention(q, kv, plan, scale, window_left=window, sinks_log2=sl2)
+            want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
+                                       window_left=window, sinks=sinks)
+            close(out, want, 2e-2)
+    ops.check_kernel_status(DEV)
+
+
 @pytest.mark.parametrize("window", [0, 15, 16, 100, 1000])
 def test_paged_decode_attention_sliding_window(window):
     """Decode attention over the last window + 1 keys only: the plan starts at the 16-token boundary

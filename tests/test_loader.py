@@ -338,3 +338,81 @@ def test_gguf_checkpoint_loads_like_safetensors(tmp_path):
     raw[2] = 0x1F            # element 0 = 15, element 16 = 1
     x = gguf.dequantize(raw, gguf.T_Q4_0, 32)
     assert x[0] == 0.5 * (15 - 8) and x[16] == 0.5 * (1 - 8) and x[1] == 0.5 * (0 - 8)
+
+
+def test_gpt_oss_family_runs_through_the_paged_driver():
+    """GPT-OSS style blocks: alternating sliding / full attention layers, per-head attention sinks,
+    biases on q/k/v/o, router and expert biases, clamped GLU experts, YaRN without truncation.
+    Prefill and decode through the paged driver against the dense oracle."""
+    import numpy as np
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models.config import ModelConfig, preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import random_weights
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+
+    hf = dict(model_type="gpt_oss", hidden_size=2880, intermediate_size=2880, num_hidden_layers=4, num_attention_heads=64,
+              num_key_value_heads=8, head_dim=64, vocab_size=201088, num_local_experts=32, num_experts_per_tok=4,
+              sliding_window=128, layer_types=["sliding_attention", "full_attention"] * 2, swiglu_limit=7.0)
+    c = ModelConfig.from_hf(hf)
+    assert c.is_moe and c.moe_intermediate_size == 2880 and c.attention_sinks and c.o_bias and c.attention_bias
+    assert [c.layer_window_left(i) for i in range(4)] == [127, -1, 127, -1] and c.plan_window_left == -1
+
+    cfg = preset("tiny-gpt-oss")
+    w = random_weights(cfg, "cpu", torch.float32, seed=11, std=0.08)
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=16, page_size=16, max_requests=4, max_tokens=128)
+    toks = list(range(300, 345))
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    resp = drv.fire_batch(fold([PendingRequest(0, toks, list(range(len(toks))), list(range(4)), 0, [(len(toks) - 1, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg, w, torch.tensor(toks))[-1].numpy()
+    assert np.abs(got - want).max() < 2e-3
+    resp = drv.fire_batch(fold([PendingRequest(0, [5], [len(toks)], list(range(4)), len(toks), [(0, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg, w, torch.tensor(toks + [5]))[-1].numpy()
+    assert np.abs(got - want).max() < 2e-3
+    # the sinks and the window both matter in this setup
+    w2 = {**w, "layers": [{k: v for k, v in lw.items() if k != "sinks"} for lw in w["layers"]]}
+    assert np.abs(dense_reference_forward(cfg, w2, torch.tensor(toks + [5]))[-1].numpy() - want).max() > 1e-3
+
+
+def test_gpt_oss_checkpoint_names_and_mxfp4_experts(tmp_path):
+    """GPT-OSS checkpoints: stacked experts as [E, in, out] (bf16) or as MXFP4 blocks + e8m0
+    scales, router / expert / o_proj biases, attention sinks."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    from pie_b200.models import loader
+    from pie_b200.models.config import preset
+    from pie_b200.models.weights import random_weights
+
+    cfg = preset("tiny-gpt-oss")
+    w = random_weights(cfg, "cpu", torch.float32, seed=12, std=0.08)
+    loader.export_hf_checkpoint(cfg, w, tmp_path)
+    cfg2, w2 = loader.load_checkpoint(tmp_path, "cpu", dtype="float32")
+    assert cfg2.model_type == "gpt_oss" and cfg2.layer_types == cfg.layer_types and cfg2.attention_sinks
+    assert cfg2.rope_scaling["truncate"] is False
+    for key in ("wqkv", "bqkv", "wo", "bo", "sinks", "router", "router_bias", "experts_gate_up", "experts_down",
+                "experts_gate_up_bias", "experts_down_bias"):
+        assert torch.equal(w2["layers"][1][key], w["layers"][1][key]), key
+    # the same experts as MXFP4 blocks
+    tensors = {}
+    with safe_open(str(tmp_path / "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            tensors[k] = f.get_tensor(k)
+    for li, lw in enumerate(w["layers"]):
+        for src, dst in (("gate_up_proj", "experts_gate_up"), ("down_proj", "experts_down")):
+            X = f"model.layers.{li}.mlp.experts.{src}"
+            del tensors[X]
+            tensors[X + "_blocks"], tensors[X + "_scales"] = loader.quant_mxfp4(lw[dst])
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / "model.safetensors"))
+    _, w3 = loader.load_checkpoint(tmp_path, "cpu", dtype="float32")
+    got, ref = w3["layers"][0]["experts_down"], w["layers"][0]["experts_down"]
+    assert got.shape == ref.shape
+    assert torch.equal(got, loader.dequant_mxfp4(*loader.quant_mxfp4(ref)))
+    assert (got - ref).abs().max() <= 0.26 * ref.abs().amax()        # e2m1 steps: at most 1 in 6 of the block maximum... plus scale rounding
+    # known values: byte 0x2C = low nibble 12 (-2.0), high nibble 2 (1.0); scale 128 -> 2.0
+    blk = torch.zeros(1, 1, 16, dtype=torch.uint8)
+    blk[0, 0, 0] = 0x2C
+    out = loader.dequant_mxfp4(blk, torch.tensor([[128]], dtype=torch.uint8))
+    assert out[0, 0].item() == -4.0 and out[0, 1].item() == 2.0 and out[0, 2].item() == 0.0
