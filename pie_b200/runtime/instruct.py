@@ -5,7 +5,7 @@ turn terminator (`seal`), knows the stop tokens, how tool definitions and tool r
 written (`equip`, `answer`) and how to split reasoning from the answer. Decoders consume
 generated tokens incrementally and emit events (chat text deltas, reasoning segments, tool
 calls). Families: llama3, llama2, qwen (ChatML: Qwen2/Qwen3), mistral, gemma, phi3, olmo,
-deepseek-r1 style reasoning. Counterpart of runtime/src/model/instruct.rs and instruct/*.rs.
+gpt-oss (harmony), kimi, deepseek-r1 style reasoning. Counterpart of runtime/src/model/instruct.rs and instruct/*.rs.
 """
 from __future__ import annotations
 
@@ -195,6 +195,58 @@ class Phi3(Instruct):
         return "<|end|>\n"
 
 
+class GptOss(Instruct):
+    """Harmony format of GPT-OSS: `<|start|>role<|message|>text<|end|>`; the assistant writes its
+    reasoning on the `analysis` channel, tool calls on `commentary` (ended by `<|call|>`) and the
+    answer on `final` (ended by `<|return|>`)."""
+    name = "gptoss"
+    stop_strings = ("<|return|>", "<|call|>")
+    think_open, think_close = "<|channel|>analysis<|message|>", "<|end|>"
+    tool_open, tool_close = "<|constrain|>json<|message|>", "<|call|>"
+
+    def format(self, role, message, first):
+        if role == "assistant":
+            return f"<|start|>assistant<|channel|>final<|message|>{message}<|end|>"
+        if role == "tool":
+            return f"<|start|>functions<|message|>{message}<|end|>"
+        return f"<|start|>{'developer' if role == 'system' and not first else role}<|message|>{message}<|end|>"
+
+    def cue_text(self):
+        return "<|start|>assistant"
+
+    def seal_text(self):
+        return "<|return|>"
+
+    def equip(self, tools):
+        lines = ["# Tools", "", "## functions", "", "namespace functions {", ""]
+        for t in tools:
+            lines += [f"// {t.get('description', '')}",
+                      f"type {t['name']} = (_: {json.dumps(t.get('parameters') or t.get('inputSchema') or {})}) => any;", ""]
+        lines += ["} // namespace functions", "",
+                  "Call a tool with <|channel|>commentary to=functions.NAME <|constrain|>json<|message|>{...}<|call|>."]
+        return "\n".join(lines)
+
+    def answer(self, name, result):
+        return f"<|start|>functions.{name} to=assistant<|channel|>commentary<|message|>{result}<|end|>"
+
+
+class Kimi(Instruct):
+    """Kimi-K2 turns: `<|im_system|>`, `<|im_user|>`, `<|im_assistant|>` headers closed by `<|im_middle|>`."""
+    name = "kimi"
+    stop_strings = ("<|im_end|>",)
+    tool_open, tool_close = "<|tool_call_argument_begin|>", "<|tool_call_end|>"
+
+    def format(self, role, message, first):
+        tag = {"system": "<|im_system|>", "user": "<|im_user|>", "assistant": "<|im_assistant|>"}.get(role, "<|im_system|>")
+        return f"{tag}{role}<|im_middle|>{message}<|im_end|>"
+
+    def cue_text(self):
+        return "<|im_assistant|>assistant<|im_middle|>"
+
+    def seal_text(self):
+        return "<|im_end|>"
+
+
 class R1(ChatML):
     """DeepSeek-R1 style: the assistant cue opens a reasoning block."""
     name = "r1"
@@ -206,7 +258,8 @@ class R1(ChatML):
 FAMILIES: Dict[str, type] = {"llama3": Llama3, "llama": Llama3, "llama2": Llama2, "qwen": ChatML, "qwen2": ChatML,
                              "qwen3": ChatML, "qwen3_moe": ChatML, "olmo2": ChatML, "olmo3": ChatML,
                              "mistral": Mistral, "mistral3": Mistral, "mixtral": Mistral, "gemma": Gemma,
-                             "gemma2": Gemma, "gemma3": Gemma, "phi3": Phi3, "r1": R1, "plain": Instruct}
+                             "gemma2": Gemma, "gemma3": Gemma, "gemma4": Gemma, "phi3": Phi3, "r1": R1, "gpt_oss": GptOss,
+                             "gptoss": GptOss, "kimi": Kimi, "plain": Instruct}
 
 
 def for_arch(arch: str) -> Instruct:

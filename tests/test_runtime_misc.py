@@ -185,3 +185,18 @@ def test_hf_resolve(tmp_path, monkeypatch):
     assert resolve_model(str(tmp_path)) == tmp_path
     with pytest.raises(FileNotFoundError):
         resolve_model("org/absent")
+
+
+def test_harmony_and_kimi_chat_templates():
+    from pie_b200.runtime import instruct as I
+    g = I.for_arch("gpt_oss")
+    text = g.format("system", "Be brief", True) + g.format("system", "Use tools", False) + g.format("user", "hi", False) + g.cue_text()
+    assert text == ("<|start|>system<|message|>Be brief<|end|><|start|>developer<|message|>Use tools<|end|>"
+                    "<|start|>user<|message|>hi<|end|><|start|>assistant")
+    assert g.format("assistant", "ok", False) == "<|start|>assistant<|channel|>final<|message|>ok<|end|>"
+    assert set(g.stop_strings) == {"<|return|>", "<|call|>"} and g.seal_text() == "<|return|>"
+    decl = g.equip([{"name": "get_weather", "description": "weather", "parameters": {"type": "object"}}])
+    assert "type get_weather = (_: {\"type\": \"object\"}) => any;" in decl and "namespace functions" in decl
+    assert g.answer("get_weather", "{}").startswith("<|start|>functions.get_weather to=assistant")
+    k = I.for_arch("kimi")
+    assert k.format("user", "hi", False) + k.cue_text() == "<|im_user|>user<|im_middle|>hi<|im_end|><|im_assistant|>assistant<|im_middle|>"
