@@ -219,3 +219,69 @@ PIE_API int pie_moe_combine_rs(const void* y, const int* slot_of, const float* w
     moe_combine_kernel<true><<<n, 128, 0, st>>>((const bf16*)y, slot_of, w, nullptr, 0, H, k, nullptr, H, tp);
     return (int)cudaGetLastError();
 }
+
+// ----------------------------------------------------------------------- GPT-OSS expert epilogues
+// The expert-sorted rows of a grouped GEMM carry their expert in the tile table (128 rows per tile).
+// gate/up columns are interleaved: act[r, j] = (clamp(up) + 1) * g * sigmoid(1.702 g), g = min(gate, limit),
+// after adding the expert's bias. Rows of unused tiles (expert < 0) are left alone.
+// Counterpart of gpt_oss_glu in the reference (driver/cuda/src/kernels/swiglu.cu).
+namespace pie {
+__global__ void moe_bias_glu_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ bias,
+                                    const int* __restrict__ tile_expert, bf16* __restrict__ act, int inter,
+                                    float limit) {
+    const int row = blockIdx.x;
+    const int e = tile_expert[row >> 7];
+    if (e < 0) return;
+    const bf16* src = gu + (size_t)row * 2 * inter;
+    const bf16* b = bias + (size_t)e * 2 * inter;
+    bf16* dst = act + (size_t)row * inter;
+    for (int c = threadIdx.x * 4; c < inter; c += blockDim.x * 4) {      // 4 outputs = 8 interleaved inputs
+        float x[8], bb[8], y[4];
+        unpack8(*reinterpret_cast<const bf16x8*>(src + 2 * c), x);
+        unpack8(*reinterpret_cast<const bf16x8*>(b + 2 * c), bb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float g = fminf(x[2 * i] + bb[2 * i], limit);
+            const float u = fminf(fmaxf(x[2 * i + 1] + bb[2 * i + 1], -limit), limit);
+            y[i] = (u + 1.f) * g / (1.f + __expf(-1.702f * g));
+        }
+        bf162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+        *reinterpret_cast<uint2*>(dst + c) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+}
+
+__global__ void moe_row_bias_kernel(bf16* __restrict__ y, const bf16* __restrict__ bias,
+                                    const int* __restrict__ tile_expert, int H) {
+    const int row = blockIdx.x;
+    const int e = tile_expert[row >> 7];
+    if (e < 0) return;
+    bf16* dst = y + (size_t)row * H;
+    const bf16* b = bias + (size_t)e * H;
+    for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+        float x[8], bb[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(dst + c), x);
+        unpack8(*reinterpret_cast<const bf16x8*>(b + c), bb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] += bb[i];
+        *reinterpret_cast<bf16x8*>(dst + c) = pack8(x);
+    }
+}
+}  // namespace pie
+
+// act[rows, inter] from gu[rows, 2 * inter] + bias[E, 2 * inter]; rows = mtiles * 128.
+PIE_API int pie_moe_bias_glu(const void* gu, const void* bias, const int* tile_expert, void* act, int mtiles, int inter,
+                             float limit, cudaStream_t st) {
+    if (mtiles <= 0) return 0;
+    if (inter % 4) return (int)cudaErrorInvalidValue;
+    pie::moe_bias_glu_kernel<<<mtiles * 128, 128, 0, st>>>((const bf16*)gu, (const bf16*)bias, tile_expert, (bf16*)act,
+                                                           inter, limit);
+    return (int)cudaGetLastError();
+}
+
+// y[rows, H] += bias[expert of row, H]
+PIE_API int pie_moe_row_bias(void* y, const void* bias, const int* tile_expert, int mtiles, int H, cudaStream_t st) {
+    if (mtiles <= 0) return 0;
+    if (H % 8) return (int)cudaErrorInvalidValue;
+    pie::moe_row_bias_kernel<<<mtiles * 128, 128, 0, st>>>((bf16*)y, (const bf16*)bias, tile_expert, H);
+    return (int)cudaGetLastError();
+}

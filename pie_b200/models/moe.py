@@ -144,11 +144,16 @@ def _moe_block_biased(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torc
         gu = torch.empty(max(rows, buf.xs.shape[0]), 2 * buf.I, dtype=x.dtype, device=x.device)
         model._moe_gu = gu
     ops.grouped_gemm(buf.xs, lw["experts_gate_up"], buf.tile_expert, gu, mt, ops.EPI_STORE)
-    row_expert = buf.tile_expert[:mt].clamp(min=0).long().repeat_interleave(128)       # unused tiles: any expert
-    act = gpt_oss_glu(gu[:rows] + lw["experts_gate_up_bias"][row_expert], cfg.swiglu_limit)
-    buf.act[:rows] = act.to(x.dtype)
-    ops.grouped_gemm(buf.act, lw["experts_down"], buf.tile_expert, buf.ys, mt, ops.EPI_STORE)
-    buf.ys[:rows] += lw["experts_down_bias"][row_expert]
+    if x.dtype == torch.bfloat16 and gu.is_contiguous() and buf.act.is_contiguous():
+        ops.moe_bias_glu(gu, lw["experts_gate_up_bias"], buf.tile_expert, buf.act, mt, cfg.swiglu_limit)
+        ops.grouped_gemm(buf.act, lw["experts_down"], buf.tile_expert, buf.ys, mt, ops.EPI_STORE)
+        ops.moe_row_bias(buf.ys, lw["experts_down_bias"], buf.tile_expert, mt)
+    else:
+        row_expert = buf.tile_expert[:mt].clamp(min=0).long().repeat_interleave(128)       # unused tiles: any expert
+        act = gpt_oss_glu(gu[:rows] + lw["experts_gate_up_bias"][row_expert], cfg.swiglu_limit)
+        buf.act[:rows] = act.to(x.dtype)
+        ops.grouped_gemm(buf.act, lw["experts_down"], buf.tile_expert, buf.ys, mt, ops.EPI_STORE)
+        buf.ys[:rows] += lw["experts_down_bias"][row_expert]
     return ops.moe_combine(buf, n, h)
 
 

@@ -407,6 +407,19 @@ def grouped_gemm(a, w, tile_expert, out, max_mtiles: int, epilogue: int = EPI_ST
     return out
 
 
+def moe_bias_glu(gu, bias, tile_expert, act, mtiles: int, limit: float):
+    """act = clamped GLU of (gu + bias[expert of row]) on expert-sorted rows (GPT-OSS experts)."""
+    check(fn("pie_moe_bias_glu")(ptr(gu), ptr(bias), ptr(tile_expert), ptr(act), mtiles, act.shape[1], limit,
+                                 stream_ptr()), "moe_bias_glu")
+    return act
+
+
+def moe_row_bias(y, bias, tile_expert, mtiles: int):
+    """y[row] += bias[expert of row] on expert-sorted rows."""
+    check(fn("pie_moe_row_bias")(ptr(y), ptr(bias), ptr(tile_expert), mtiles, y.shape[1], stream_ptr()), "moe_row_bias")
+    return y
+
+
 def moe_combine(buf: "MoeBuffers", n: int, residual=None, out=None):
     if out is None:
         out = torch.empty(n, buf.H, dtype=buf.ys.dtype, device=buf.ys.device)

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "pie_copy_pages": [p, p, p, i32, i32, i64, i64, p],
     "pie_brle_expand": [p, p, p, i32, i32, i32, p],
     "pie_paged_decode_attn": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, p],
+    "pie_moe_bias_glu": [p, p, p, p, i32, i32, f32, p],
+    "pie_moe_row_bias": [p, p, p, i32, i32, p],
     "pie_paged_decode_attn_window": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, p, p],
     "pie_paged_prefill_attn": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, f32, i32, p, p],
     "pie_prefill_tile_tokens": [i32],
