@@ -201,3 +201,48 @@ def load_hf_tokenizer(path) -> BpeTokenizer:
     add_prefix = bool((tj.get("normalizer") or {}).get("type") in ("Prepend", "Sequence")) and metaspace
     return BpeTokenizer(vocab, merges, split if byte_level or split else "", special, byte_fallback, metaspace, eos,
                         unk_id, add_prefix)
+
+
+# split regexes of the byte-level pre-tokenizers that GGUF files name in `tokenizer.ggml.pre`
+_GGUF_PRE = {
+    "llama-bpe": r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+",
+    "qwen2": r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+",
+}
+_GGUF_PRE["llama3"] = _GGUF_PRE["llama-bpe"]
+
+
+def load_gguf_tokenizer(source) -> BpeTokenizer:
+    """Build a BpeTokenizer from the `tokenizer.ggml.*` metadata of a GGUF file (a path or an open
+    `GGUFReader`). Byte-level BPE vocabularies (`tokenizer.ggml.model = gpt2`) are covered; control
+    and user-defined tokens (token types 3 and 4) become special tokens."""
+    if hasattr(source, "meta"):
+        meta = source.meta
+    else:
+        from ..models.gguf import GGUFReader
+        meta = GGUFReader(source).meta
+    kind = meta.get("tokenizer.ggml.model", "gpt2")
+    if kind != "gpt2":
+        raise ValueError(f"GGUF tokenizer model {kind!r} is not byte-level BPE")
+    tokens = meta.get("tokenizer.ggml.tokens") or []
+    types = meta.get("tokenizer.ggml.token_type") or [1] * len(tokens)
+
+    def raw(tok: str) -> bytes:
+        try:
+            return bytes(_U2B[c] for c in tok)
+        except KeyError:
+            return tok.encode("utf-8")
+
+    vocab, special = {}, {}
+    for i, (tok, tt) in enumerate(zip(tokens, types)):
+        if tt in (3, 4):
+            special[tok] = i
+        else:
+            vocab.setdefault(raw(tok), i)
+    merges = []
+    for m in meta.get("tokenizer.ggml.merges") or []:
+        a, b = m.split(" ", 1)
+        merges.append((raw(a), raw(b)))
+    eos = [int(meta[k]) for k in ("tokenizer.ggml.eos_token_id", "tokenizer.ggml.eot_token_id") if k in meta]
+    split = _GGUF_PRE.get(str(meta.get("tokenizer.ggml.pre", "")), GPT2_SPLIT)
+    return BpeTokenizer(vocab, merges, split, special, False, False, sorted(set(eos)),
+                        int(meta.get("tokenizer.ggml.unknown_token_id", 0)), False)
