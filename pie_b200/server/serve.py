@@ -43,9 +43,19 @@ def build_drivers(m: ModelSection):
     weights = None
     if m.path:
         from ..models import loader
-        cfg = ModelConfig.from_path(m.path)
+        mp = Path(m.path)
+        ggufs = [mp] if mp.suffix == ".gguf" else ([] if list(mp.glob("*.safetensors")) else sorted(mp.glob("*.gguf")))
+        if ggufs:       # one file carries configuration, weights and tokenizer
+            from ..models.gguf import GGUFReader
+            from ..runtime.tokenizer import load_gguf_tokenizer
+            rd = GGUFReader(ggufs[0])
+            cfg = rd.config()
+            if rd.meta.get("tokenizer.ggml.tokens") and rd.meta.get("tokenizer.ggml.model", "gpt2") == "gpt2":
+                tok = load_gguf_tokenizer(rd)
+        else:
+            cfg = ModelConfig.from_path(m.path)
         cfg.name = m.name
-        if (Path(m.path) / "tokenizer.json").exists():
+        if tok is None and mp.is_dir() and (mp / "tokenizer.json").exists():
             tok = load_hf_tokenizer(m.path)
     else:
         cfg = preset(m.preset)
