@@ -4,6 +4,7 @@ on one GPU:
     python -m pie_b200.bench.configs --config 3   # Qwen3-32B block-fp8, 4096-token prompts, 512 out, greedy
     python -m pie_b200.bench.configs --config 4   # Qwen3-30B-A3B MoE, prompts U[256,1024], 256 out
     python -m pie_b200.bench.configs --config 5   # agentic fork: 64 agents x 8-way fork x 4 rounds on Llama-3.1-8B
+    python -m pie_b200.bench.configs --config 6   # GPT-OSS-20B shapes (not one of the reference's configs), prompts U[256,1024]
 
 `--requests` / `--agents` scale the concurrency down to what one GPU's memory holds; a scaled run
 prints "valid": false. One JSON line per run, same timing rules as bench.py (device-timed decode
@@ -18,7 +19,7 @@ import time
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=[3, 4, 5])
+    ap.add_argument("--config", type=int, required=True, choices=[3, 4, 5, 6])
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--agents", type=int, default=64)
     ap.add_argument("--steps", type=int, default=32)
@@ -37,6 +38,8 @@ def main():
     spec = {3: dict(model="qwen3-32b-fp8", requests=256, pmin=4096, pmax=4096, out=512,
                     sampler=SamplerSpec(SamplerKind.MULTINOMIAL, temperature=0.0), sampler_txt="greedy"),
             4: dict(model="qwen3-30b-a3b", requests=1024, pmin=256, pmax=1024, out=256,
+                    sampler=SamplerSpec(SamplerKind.TOP_P, temperature=1.0, top_p=0.9), sampler_txt="temperature 1.0, top-p 0.9"),
+            6: dict(model="gpt-oss-20b", requests=256, pmin=256, pmax=1024, out=256,
                     sampler=SamplerSpec(SamplerKind.TOP_P, temperature=1.0, top_p=0.9), sampler_txt="temperature 1.0, top-p 0.9"),
             5: dict(model="llama-3.1-8b", requests=64, pmin=2048, pmax=2048, out=128,
                     sampler=SamplerSpec(SamplerKind.TOP_K, temperature=1.0, top_k=50), sampler_txt="top-k 50, seeded")}[a.config]
