@@ -191,16 +191,20 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         if cfg.is_moe and L + "mlp.router.weight" in names:
             # GPT-OSS: experts stacked in one tensor, gate/up columns already interleaved; bf16 checkpoints
             # hold [E, in, out], MXFP4 ones blocks + scales in [E, out, in/32, ...]
-            if T > 1:
-                raise NotImplementedError("GPT-OSS expert biases are not sharded: tp_size must be 1")
+            if T > 1 and ep:
+                raise NotImplementedError("GPT-OSS experts under expert parallelism")
             X = L + "mlp.experts."
             att[P + "router"], att[P + "router_bias"] = w(L + "mlp.router.weight"), w(L + "mlp.router.bias")
-            for src, dst in (("gate_up_proj", "experts_gate_up"), ("down_proj", "experts_down")):
+            # runtime layout [E, out, in]; under tensor parallelism the intermediate dimension is sharded:
+            # rows of gate_up (interleaved pairs stay together), columns of down
+            for src, dst, ax in (("gate_up_proj", "experts_gate_up", 1), ("down_proj", "experts_down", 2)):
                 if X + src + "_blocks" in names:
-                    att[P + dst] = Mxfp4(w(X + src + "_blocks"), w(X + src + "_scales"))
+                    full = Mxfp4(w(X + src + "_blocks"), w(X + src + "_scales"))
                 else:
-                    att[P + dst] = Transpose(w(X + src), 1, 2)
-                att[P + dst + "_bias"] = w(X + src + "_bias")
+                    full = Transpose(w(X + src), 1, 2)
+                att[P + dst] = Shard(full, ax, r, T)
+            att[P + "experts_gate_up_bias"] = Shard(w(X + "gate_up_proj_bias"), 1, r, T)
+            att[P + "experts_down_bias"] = w(X + "down_proj_bias") if r == 0 else Op("zeros_like", {}, [w(X + "down_proj_bias")])
         elif cfg.is_moe and (L + "mlp.gate.weight" in names or mixtral):
             att[P + "router"] = w(L + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight"))
             E = cfg.num_experts
@@ -290,6 +294,8 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
         return y.view(torch.float8_e4m3fn) if f8 else y
     if k == "stack":
         return torch.stack(xs, dim=0)
+    if k == "zeros_like":
+        return torch.zeros_like(xs[0])
     if k == "transpose":
         return xs[0].transpose(op.args["a"], op.args["b"])
     if k == "mxfp4":

@@ -125,10 +125,12 @@ def _moe_block_biased(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torc
     block, with the first GEMM storing gate and up unactivated and the biases and the activation
     applied to the expert-sorted rows in between (row -> expert through the tile table); static
     shapes, no host synchronisation. CPU: the dense formula."""
-    cfg = model.cfg
-    if model.par.tp_size > 1:
-        raise NotImplementedError("GPT-OSS experts under tensor parallelism")
+    cfg, par = model.cfg, model.par
+    if par.tp_size > 1 and par.ep:
+        raise NotImplementedError("GPT-OSS experts under expert parallelism")
     if not x.is_cuda:
+        if par.tp_size > 1:
+            raise NotImplementedError("GPT-OSS experts under tensor parallelism on the CPU path")
         return h + moe_reference(cfg, x, lw).to(x.dtype)
     k = cfg.num_experts_per_tok
     n = x.shape[0]
@@ -154,6 +156,9 @@ def _moe_block_biased(model, x: torch.Tensor, lw: dict, h: torch.Tensor) -> torc
         buf.act[:rows] = act.to(x.dtype)
         ops.grouped_gemm(buf.act, lw["experts_down"], buf.tile_expert, buf.ys, mt, ops.EPI_STORE)
         buf.ys[:rows] += lw["experts_down_bias"][row_expert]
+    if par.tp_size > 1:
+        # experts sharded on their intermediate dimension: partial sums over ranks, then the residual
+        return h + par.comm.all_reduce(ops.moe_combine(buf, n, None))
     return ops.moe_combine(buf, n, h)
 
 

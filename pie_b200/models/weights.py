@@ -133,11 +133,12 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             lw["experts_down"] = down.contiguous()
             del gate, up, down
             if cfg.moe_style == "gpt_oss":
-                if T > 1:
-                    raise NotImplementedError("GPT-OSS expert biases are not sharded: tp_size must be 1")
                 lw["router_bias"] = gen.normal(E, std=0.5)
-                lw["experts_gate_up_bias"] = gen.normal(E, 2 * Im, std=0.2)
-                lw["experts_down_bias"] = gen.normal(E, H, std=0.2)
+                gub, db = gen.normal(E, 2 * Im, std=0.2), gen.normal(E, H, std=0.2)
+                if T > 1:       # (gate, up) pairs follow their intermediate slice; the output bias lives on rank 0
+                    gub = gub[:, r * 2 * (Im // T):(r + 1) * 2 * (Im // T)]
+                    db = db if r == 0 else torch.zeros_like(db)
+                lw["experts_gate_up_bias"], lw["experts_down_bias"] = gub.contiguous(), db
         else:
             I = cfg.intermediate_size
             gate, up = shard_rows(gen.normal(I, H), r, T), shard_rows(gen.normal(I, H), r, T)

@@ -416,3 +416,26 @@ def test_gpt_oss_checkpoint_names_and_mxfp4_experts(tmp_path):
     blk[0, 0, 0] = 0x2C
     out = loader.dequant_mxfp4(blk, torch.tensor([[128]], dtype=torch.uint8))
     assert out[0, 0].item() == -4.0 and out[0, 1].item() == 2.0 and out[0, 2].item() == 0.0
+
+
+def test_gpt_oss_tensor_parallel_shards(tmp_path):
+    """GPT-OSS under tensor parallelism: experts sharded on their intermediate dimension (gate/up
+    pairs stay together, also in the bias), the output bias on rank 0 only, sinks by head; the loader
+    and the random initialiser agree."""
+    from pie_b200.models import loader
+    from pie_b200.models.config import preset
+    from pie_b200.models.weights import random_weights
+
+    cfg = preset("tiny-gpt-oss")
+    full = random_weights(cfg, "cpu", torch.float32, seed=13)
+    loader.export_hf_checkpoint(cfg, full, tmp_path)
+    Im = cfg.moe_intermediate_size
+    for r in range(2):
+        w = random_weights(cfg, "cpu", torch.float32, seed=13, tp_size=2, tp_rank=r)
+        _, l = loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=r, dtype="float32")
+        for key in ("experts_gate_up", "experts_down", "experts_gate_up_bias", "experts_down_bias", "sinks", "bo", "wo"):
+            assert torch.equal(l["layers"][0][key], w["layers"][0][key]), (r, key)
+        lw = w["layers"][0]
+        assert torch.equal(lw["experts_gate_up"], full["layers"][0]["experts_gate_up"][:, r * Im:(r + 1) * Im])
+        assert torch.equal(lw["experts_down"], full["layers"][0]["experts_down"][:, :, r * Im // 2:(r + 1) * Im // 2])
+        assert (lw["experts_down_bias"].abs().sum() > 0) == (r == 0)
