@@ -14,6 +14,11 @@ enum GemmEpilogue : int {
     EPI_RESIDUAL = 1,  // C = acc + R
     EPI_SWIGLU = 2,    // C[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]   (C is [M, N/2])
     EPI_RS = 3,        // reduce-scatter: rows go to their owner rank's receive buffer (peer stores)
+    // Swapped operands (small batches): the kernel computes C^T = W * A^T, so its rows are output
+    // features and its columns tokens; these epilogues write the tile back transposed.
+    EPI_STORE_T = 4,
+    EPI_RESIDUAL_T = 5,
+    EPI_SWIGLU_T = 6,
 };
 
 constexpr int TP_MAX_RANKS = 8;
@@ -235,6 +240,60 @@ __device__ __forceinline__ void epilogue_store_64(const uint32_t (&v0)[32], cons
             dst = C + (size_t)row * ldc + col;
         }
         *reinterpret_cast<bf16x8*>(dst) = *slot(r, c);
+    }
+    __syncwarp();
+}
+
+// Transposed epilogue of the swapped-operand launch: thread `lane` holds output feature
+// (feat0 + lane), v0 / v1 its values for tokens tok0..+31 / +32..+63. The output is C[token][feature].
+// Values are staged as bf16 in the warp's 4 KB tile as [64 tokens][32 features] (64 B per token; for
+// SwiGLU [64 tokens][16 outputs]) and leave in 16-byte stores, 8 (16) token rows per warp store.
+//   F       : number of output features of the GEMM (rows of the swapped problem)
+//   tok_end : tokens at or past tok_end are not stored
+template <int EPI>
+__device__ __forceinline__ void epilogue_store_64_t(const uint32_t (&v0)[32], const uint32_t (&v1)[32],
+                                                    uint8_t* stage, int feat0, int tok0, int F, int tok_end,
+                                                    bf16* __restrict__ C, int ldc, const bf16* __restrict__ R,
+                                                    int ldr) {
+    const int lane = threadIdx.x & 31;
+    bf16* st = reinterpret_cast<bf16*>(stage);
+    const int feat = feat0 + lane;
+    if (EPI == EPI_SWIGLU_T) {
+        // even lanes hold gate_j, odd lanes up_j of output j = feat / 2
+#pragma unroll
+        for (int t = 0; t < 64; ++t) {
+            const float mine = __uint_as_float(t < 32 ? v0[t] : v1[t - 32]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            if (!(lane & 1)) st[t * 16 + (lane >> 1)] = __float2bfloat16(mine / (1.f + __expf(-mine)) * other);
+        }
+        __syncwarp();
+        const int oc0 = feat0 >> 1;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = i * 16 + (lane >> 1), c = lane & 1;
+            const int tok = tok0 + t;
+            if (tok < tok_end && 2 * (oc0 + c * 8) < F)
+                *reinterpret_cast<bf16x8*>(C + (size_t)tok * ldc + oc0 + c * 8) = *reinterpret_cast<const bf16x8*>(st + t * 16 + c * 8);
+        }
+        __syncwarp();
+        return;
+    }
+#pragma unroll
+    for (int t = 0; t < 64; ++t) {
+        float o = __uint_as_float(t < 32 ? v0[t] : v1[t - 32]);
+        if (EPI == EPI_RESIDUAL_T) {
+            const int tok = tok0 + t;
+            if (tok < tok_end && feat < F) o += __bfloat162float(R[(size_t)tok * ldr + feat]);
+        }
+        st[t * 32 + lane] = __float2bfloat16(o);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int t = i * 8 + (lane >> 2), c = lane & 3;
+        const int tok = tok0 + t;
+        if (tok < tok_end && feat0 + c * 8 < F)
+            *reinterpret_cast<bf16x8*>(C + (size_t)tok * ldc + feat0 + c * 8) = *reinterpret_cast<const bf16x8*>(st + t * 32 + c * 8);
     }
     __syncwarp();
 }

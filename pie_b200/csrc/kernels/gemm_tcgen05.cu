@@ -56,6 +56,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  const int* __restrict__ tile_expert, int bn) {
     using Cfg = GemmCfg<BN, OCC>;
     constexpr int STAGES = Cfg::STAGES;
+    constexpr bool SWAPPED = EPI >= EPI_STORE_T;   // tma_a walks the weights, tma_b the activation
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -117,9 +118,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (tp.gated) ok = ag_gate_wait(tp, status);
                 for (int j = 0; j < pending && ok; ++j)
 #pragma unroll
-                    for (int u = 0; u < Cfg::KSUB; ++u)
-                        tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES + u * Cfg::A_SUB, &tma_a, full_bar(q_stage[j]),
-                                    q_kb[j] * GEMM_KSTEP + u * GEMM_BK, q_row[j]);
+                    for (int u = 0; u < Cfg::KSUB; ++u) {
+                        if (SWAPPED)
+                            tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b,
+                                        full_bar(q_stage[j]), q_kb[j] * GEMM_KSTEP + u * GEMM_BK, q_row[j]);
+                        else
+                            tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES + u * Cfg::A_SUB, &tma_a, full_bar(q_stage[j]),
+                                        q_kb[j] * GEMM_KSTEP + u * GEMM_BK, q_row[j]);
+                    }
                 pending = 0;
                 dep_ready = true;
             };
@@ -154,15 +160,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         continue;
                     }
                     mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    // the operand that holds the weights goes first; the activation operand (tma_a, or
+                    // tma_b of a swapped launch) waits for its producer
+                    if (!SWAPPED || dep_ready) {
 #pragma unroll
-                    for (int u = 0; u < Cfg::KSUB; ++u)
-                        tma_load_2d(a_dst + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, b_row);
-                    if (dep_ready) {
+                        for (int u = 0; u < Cfg::KSUB; ++u)
+                            tma_load_2d(a_dst + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, b_row);
+                    }
+                    if (SWAPPED || dep_ready) {
 #pragma unroll
                         for (int u = 0; u < Cfg::KSUB; ++u)
                             tma_load_2d(a_dst + u * Cfg::A_SUB, &tma_a, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, m_blk * GEMM_BM);
-                    } else {
-                        q_kb[pending] = kb; q_row[pending] = m_blk * GEMM_BM; q_stage[pending] = s;
+                    }
+                    if (!dep_ready) {
+                        q_kb[pending] = kb; q_row[pending] = SWAPPED ? b_row : m_blk * GEMM_BM; q_stage[pending] = s;
                         ++pending;
                     }
                 }
@@ -295,8 +306,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             }
                         }
                     }
-                    epilogue_store_64<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n_blk * bn + c * 64, M, N, C,
-                                           ldc, R, ldr, tp, min(N, (n_blk + 1) * bn));
+                    if constexpr (EPI >= EPI_STORE_T)
+                        epilogue_store_64_t<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n_blk * bn + c * 64, M,
+                                                 min(N, (n_blk + 1) * bn), C, ldc, R, ldr);
+                    else
+                        epilogue_store_64<EPI>(v0, v1, stage, m_blk * GEMM_BM + q * 32, n_blk * bn + c * 64, M, N, C,
+                                               ldc, R, ldr, tp, min(N, (n_blk + 1) * bn));
                 }
             }
             tc_fence_before();
@@ -407,6 +422,13 @@ PIE_API int pie_set_pdl(int enabled) { g_pie_pdl = enabled; return 0; }
 // 0: single-CTA tiles only; 1: CTA pairs (cta_group::2) where the shape allows (default)
 static int g_gemm_pairs = 1;
 PIE_API int pie_gemm_set_pairs(int enabled) { g_gemm_pairs = enabled; return 0; }
+
+// Batches of up to this many rows run with swapped operands (0: never): the weight rows take the
+// 128-row side of the MMA and the batch the narrow side, so each CTA streams a [128 x K-slice]
+// block of the weights against the whole (small) activation instead of re-reading the activation
+// once per narrow weight tile.
+static int g_gemm_swap_max_m = 64;
+PIE_API int pie_gemm_set_swap(int max_m) { g_gemm_swap_max_m = max_m; return 0; }
 
 int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int M, int N, int K, int lda,
                        int ldw, int ldc, int ldr, int epilogue, int* status, int num_sms, cudaStream_t st,
@@ -526,6 +548,32 @@ PIE_API int pie_gemm_bf16(const void* A, const void* W, void* C, const void* R, 
                                           nullptr, w.ws, w.ws_floats, w.cnt, w.cnt_ints, &handled);
         if (handled || rc) return rc;
     }
+    if (force_bn == 0 && M <= (g_gemm_swap_max_m >= 1000 ? 128 : g_gemm_swap_max_m) && M <= 128 && N >= 128 && K >= 512) {
+        // C^T = W * A^T: rows of the launch are output features, its one column tile the batch
+        const int bt = M <= 64 ? 64 : 128;
+        const GemmPlan plan = plan_gemm(N, bt, K, num_sms, bt, w, true);
+        // Measured (Llama-3.1-8B shapes, 8 to 128 rows): the swapped launch wins where its 128-row
+        // feature tiles cannot fill the machine by themselves and K is long enough that each CTA of
+        // the K split keeps 20 or more k-blocks (qkv 31 -> 27 us, down 59 -> 47 us at 64 rows); with
+        // shorter splits the fix-up of the partial tiles costs more than the narrow direct tiles.
+        const long s_tiles = (N + GEMM_BM - 1) / GEMM_BM, s_kb = (K + GEMM_KSTEP - 1) / GEMM_KSTEP;
+        const bool take = g_gemm_swap_max_m >= 1000 ||
+                          (plan.streamk && s_tiles <= num_sms && s_tiles * s_kb >= 20L * plan.grid);
+        CUtensorMap ta, tb;
+        if (!take) goto direct;
+        if (pie_make_tma_2d_bf16(&ta, W, N, K, ldw, GEMM_BM) != 0) return (int)cudaErrorInvalidValue;
+        if (pie_make_tma_2d_bf16(&tb, A, M, K, lda, bt) != 0) return (int)cudaErrorInvalidValue;
+#define GO_T(BN_)                                                                                   \
+    switch (epilogue) {                                                                           \
+        case EPI_STORE: return launch_gemm<BN_, EPI_STORE_T>(ta, tb, C, R, N, M, K, ldc, ldr, status, plan, w, st); \
+        case EPI_RESIDUAL: return launch_gemm<BN_, EPI_RESIDUAL_T>(ta, tb, C, R, N, M, K, ldc, ldr, status, plan, w, st); \
+        case EPI_SWIGLU: return launch_gemm<BN_, EPI_SWIGLU_T>(ta, tb, C, R, N, M, K, ldc, ldr, status, plan, w, st); \
+        default: return (int)cudaErrorInvalidValue;                                               \
+    }
+        if (bt == 64) { GO_T(64) } else { GO_T(128) }
+#undef GO_T
+    }
+direct:
     bool allow_sk = true;
     if (force_bn < 0) { allow_sk = false; force_bn = -force_bn == 1 ? 0 : -force_bn; }  // negative: whole-tile only
     if (force_bn > 256 || force_bn % 16) return (int)cudaErrorInvalidValue;

@@ -189,6 +189,8 @@ def ensure_gemm_workspace(device) -> None:
     if os.environ.get("PIE_GEMM_PAIRS", "1") == "0":
         set_gemm_pairs(False)
     set_pdl(os.environ.get("PIE_PDL", "1") != "0")
+    if "PIE_GEMM_SWAP" in os.environ:
+        set_gemm_swap(int(os.environ["PIE_GEMM_SWAP"]))
 
 
 def set_pdl(enabled: bool) -> None:
@@ -196,6 +198,13 @@ def set_pdl(enabled: bool) -> None:
     prefetch overlap the tail of its predecessor in the stream (also inside CUDA graphs).
     On unless PIE_PDL=0: measured 3.5 % of a 64-request decode step, 2 % at 128, neutral at 512."""
     check(fn("pie_set_pdl")(1 if enabled else 0), "set_pdl")
+
+
+def set_gemm_swap(max_m: int) -> None:
+    """Batches of up to max_m rows (default 64, at most 128) may run the single-CTA GEMM with swapped
+    operands (weights on the 128-row side of the MMA, transposed epilogue) where the launcher's rule
+    expects a gain; 0 turns that off, 1000 swaps every batch of up to 128 rows (tests)."""
+    fn("pie_gemm_set_swap")(int(max_m))
 
 
 def set_gemm_pairs(enabled: bool) -> None:

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "pie_feed_tokens": [p, p, p, i32, p],
     "pie_gemm_set_workspace": [i32, p, i64, p, i32],
     "pie_gemm_set_pairs": [i32],
+    "pie_gemm_set_swap": [i32],
     "pie_set_pdl": [i32],
     "pie_gemm_bf16": [p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, i32, p, i32, p],
     "pie_grouped_gemm_bf16": [p, p, p, p, i32, i32, i32, i32, i32, i32, i32, p, i32, p],

@@ -102,3 +102,31 @@ def test_gemm_odd_tile_widths(bn, epi):
     if epi == "swiglu":
         want = ref.swiglu_interleaved(want)
     check(y, want, k)
+
+
+@pytest.mark.parametrize("m", [1, 7, 64, 65, 100, 128])
+@pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 14336), (1000, 512), (28672, 4096)])
+@pytest.mark.parametrize("epi", ["store", "residual", "swiglu"])
+def test_gemm_swapped_operands_small_batch(m, n, k, epi):
+    """Batches of at most 128 rows run C^T = W A^T (weights on the 128-row side, transposed epilogue):
+    same result as the direct orientation and as the fp32 reference, ragged feature counts included."""
+    if epi == "swiglu" and n % 32:
+        n = 992
+    x, w = bf(m, k, seed=31), bf(n, k, scale=0.03, seed=32)
+    r = bf(m, n, seed=33) if epi == "residual" else None
+    e = {"store": ops.EPI_STORE, "residual": ops.EPI_RESIDUAL, "swiglu": ops.EPI_SWIGLU}[epi]
+    ops.set_gemm_swap(1000)      # every shape, not only those the selection rule picks
+    try:
+        y = ops.gemm(x, w, residual=r, epilogue=e)
+        ops.set_gemm_swap(0)
+        y0 = ops.gemm(x, w, residual=r, epilogue=e)
+    finally:
+        ops.set_gemm_swap(64)
+    ref = x.float() @ w.float().t()
+    if epi == "residual":
+        ref = ref + r.float()
+    if epi == "swiglu":
+        ref = torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
+    check(y, ref, k)
+    check(y0, ref, k)
+    ops.check_kernel_status()
