@@ -105,6 +105,7 @@ def main():
                          max_tokens=args.max_tokens, par=par, gemm_backend=args.gemm)
     if comm is not None:
         comm.attach(driver)
+    driver.precapture_graphs()      # start-up work, as in a serving process: no fire pays for a graph capture
     torch.cuda.synchronize()
     t_init = time.time() - t0
     prompts = harness.make_prompts(args.requests, args.prompt_min, args.prompt_max, cfg.vocab_size, seed=1)

@@ -352,6 +352,31 @@ class TorchDriver:
         # the decode-attention launcher issues two kernels (split-KV pass + merge) per layer
         return _Graph(g, logits, rb, _lib.LAUNCHES - before + self.cfg.num_hidden_layers)
 
+    def precapture_graphs(self, buckets: Optional[List[int]] = None) -> int:
+        """Capture the decode graphs of the bucket lattice ahead of the first request, so that no fire
+        pays for a capture (the reference pre-captures its lattice at start-up too:
+        driver/cuda/src/entry.cpp, executor/forward_graph.hpp:63-91). The capture runs on a plan
+        without attention work or KV writes. Returns the number of graphs captured."""
+        if not self.use_graphs or self.par.tp_size > 1:     # tensor-parallel ranks capture in step, on demand
+            return 0
+        self._bind_thread()
+        s, n = self.slab, 0
+        for rb in (buckets or self.buckets):
+            if rb in self.graphs or rb > self.max_requests:
+                continue
+            s.h("tokens")[:rb] = 0
+            s.h("positions")[:rb] = 0
+            s.h("slots")[:rb] = -1
+            s.h("kv_page_indptr")[:rb + 1] = 0
+            s.h("req_item_indptr")[:rb + 1] = 0
+            s.h("num_items")[0] = 0
+            s.upload("tile_qstart")
+            self.graphs[rb] = self._capture(rb)
+            n += 1
+        torch.cuda.synchronize(self.device)
+        ops.kernel_status(self.device).zero_()
+        return n
+
     def _bucket(self, r: int) -> int:
         for b in self.buckets:
             if b >= r:

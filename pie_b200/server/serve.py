@@ -95,6 +95,9 @@ def build_drivers(m: ModelSection):
         drivers.append(TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, gemm_backend=d.gemm,
                                    use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
                                    swap_pages=swap))
+        if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
+            n = drivers[-1].precapture_graphs()
+            log.info("model %s on %s: %d decode graphs captured ahead of time", m.name, dev, n)
     return drivers, cfg, tok, comm
 
 

@@ -101,3 +101,31 @@ def test_engine_on_gpu_greedy_is_deterministic_and_batched():
         assert drv.stats["graph_replays"] > 0
     finally:
         eng.shutdown()
+
+
+def test_precaptured_graphs_serve_decode_without_new_captures():
+    """Start-up capture of the decode bucket lattice: later decode fires replay those graphs and
+    give the logits of an on-demand capture."""
+    cfg = small_cfg()
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)
+    outs = []
+    for pre in (True, False):
+        drv = TorchDriver(cfg, "cuda", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=512)
+        if pre:
+            assert drv.precapture_graphs() == len(drv.buckets) and drv.precapture_graphs() == 0
+            captured = set(drv.graphs)
+        prompts = [list(range(10, 47)), list(range(100, 105))]
+        pages = [[0, 1, 2], [3]]
+        raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+        drv.fire_batch(fold([PendingRequest(i, p, list(range(len(p))), pg, 0, [(len(p) - 1, raw)])
+                             for i, (p, pg) in enumerate(zip(prompts, pages))], 16))
+        resp = drv.fire_batch(fold([PendingRequest(i, [7 + i], [len(p)], pg, len(p), [(0, raw)])
+                                    for i, (p, pg) in enumerate(zip(prompts, pages))], 16))
+        assert drv.stats["graph_replays"] == 1
+        if pre:
+            assert set(drv.graphs) == captured
+        outs.append([np.frombuffer(s_.logits, dtype=np.float32).copy() for s_ in resp.slots])
+        from pie_b200 import ops
+        ops.check_kernel_status(drv.device)
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
