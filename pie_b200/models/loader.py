@@ -159,8 +159,6 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         if cfg.post_norm:       # OLMo-2: norms follow the sub-blocks, there is no input norm
             att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
             att[P + "ln3"] = w(L + "post_feedforward_layernorm.weight")
-            if T > 1:
-                raise NotImplementedError("q/k norms over all heads need the full projection: tp_size must be 1")
         else:
             att[P + "ln1"] = w(L + "input_layernorm.weight")
             att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
@@ -184,7 +182,12 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
             att[P + "bo"] = w(L + "self_attn.o_proj.bias")
         if L + "self_attn.sinks" in names:
             att[P + "sinks"] = Shard(w(L + "self_attn.sinks"), 0, r, T)
-        if L + "self_attn.q_norm.weight" in names:
+        if L + "self_attn.q_norm.weight" in names and cfg.post_norm:
+            # gains over all heads together (OLMo-2): a rank keeps those of its own heads
+            att[P + "q_norm"] = Shard(w(L + "self_attn.q_norm.weight"), 0, r, T)
+            att[P + "k_norm"] = Rows(w(L + "self_attn.k_norm.weight"), kv0 * d, kvn * d) if T > 1 \
+                else w(L + "self_attn.k_norm.weight")
+        elif L + "self_attn.q_norm.weight" in names:
             att[P + "q_norm"] = w(L + "self_attn.q_norm.weight")
             att[P + "k_norm"] = w(L + "self_attn.k_norm.weight")
         mixtral = L + "block_sparse_moe.gate.weight" in names      # Mixtral names: w1 = gate, w3 = up, w2 = down

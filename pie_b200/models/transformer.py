@@ -166,8 +166,20 @@ class Transformer:
             if qn is not None and qn.numel() != self.d:
                 # OLMo-2: RMSNorm over the whole q and k projections (all heads together)
                 qs, ks = self.hq * self.d, self.hkv * self.d
-                qkv[:, :qs] = ops.rmsnorm(qkv[:, :qs].contiguous(), qn, cfg.rms_norm_eps)
-                qkv[:, qs:qs + ks] = ops.rmsnorm(qkv[:, qs:qs + ks].contiguous(), kn, cfg.rms_norm_eps)
+                if self.par.tp_size > 1:
+                    # a rank holds some of the heads: the mean of squares needs every rank's share
+                    if cfg.num_key_value_heads < self.par.tp_size:
+                        raise NotImplementedError("q/k norms over all heads with replicated KV heads")
+                    qf, kf = qkv[:, :qs].float(), qkv[:, qs:qs + ks].float()
+                    ss = torch.stack([qf.pow(2).sum(-1), kf.pow(2).sum(-1)], dim=1)
+                    ss = self.par.comm.all_reduce(ss)
+                    rq = torch.rsqrt(ss[:, 0:1] / cfg.q_size + cfg.rms_norm_eps)
+                    rk = torch.rsqrt(ss[:, 1:2] / cfg.kv_size + cfg.rms_norm_eps)
+                    qkv[:, :qs] = (qf * rq * qn.float()).to(qkv.dtype)
+                    qkv[:, qs:qs + ks] = (kf * rk * kn.float()).to(qkv.dtype)
+                else:
+                    qkv[:, :qs] = ops.rmsnorm(qkv[:, :qs].contiguous(), qn, cfg.rms_norm_eps)
+                    qkv[:, qs:qs + ks] = ops.rmsnorm(qkv[:, qs:qs + ks].contiguous(), kn, cfg.rms_norm_eps)
                 qn = kn = None
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, qn, kn, kv_cache[li],
                                          self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps)

@@ -114,9 +114,9 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
         if cfg.attention_sinks:
             lw["sinks"] = shard_rows(gen.normal(hq, std=1.0), r, T).float().contiguous()
         if cfg.qk_norm and cfg.post_norm:
-            if T > 1:
-                raise NotImplementedError("q/k norms over all heads need the full projection: tp_size must be 1")
-            lw["q_norm"], lw["k_norm"] = 1 + gen.normal(hq * d, std=0.1), 1 + gen.normal(hkv * d, std=0.1)
+            # norms over all heads together: a rank keeps the gains of its own heads
+            qn, kn = 1 + gen.normal(hq * d, std=0.1), 1 + gen.normal(hkv * d, std=0.1)
+            lw["q_norm"], lw["k_norm"] = shard_rows(qn, r, T).contiguous(), kn[kv0 * d:(kv0 + kvn) * d].contiguous()
         elif cfg.qk_norm:
             lw["q_norm"], lw["k_norm"] = ones(d), ones(d)
         if cfg.is_moe:

@@ -24,7 +24,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="fused")
     ap.add_argument("--hidden", type=int, default=512)
-    ap.add_argument("--model", default="dense", choices=["dense", "dense-fp8", "moe", "moe-ep", "gpt-oss"],
+    ap.add_argument("--model", default="dense", choices=["dense", "dense-fp8", "moe", "moe-ep", "gpt-oss", "olmo2"],
                     help="moe: experts sharded on their intermediate dimension; moe-ep: whole experts per rank")
     a = ap.parse_args()
     import torch.distributed as dist
@@ -44,6 +44,9 @@ def main():
         cfg = preset("tiny-llama", hidden_size=a.hidden, intermediate_size=1536, num_attention_heads=8,
                      num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16",
                      quantization="fp8_block" if a.model == "dense-fp8" else None)
+    elif a.model == "olmo2":
+        cfg = preset("tiny-olmo2", hidden_size=a.hidden, intermediate_size=1536, num_attention_heads=8,
+                     num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16")
     elif a.model == "gpt-oss":
         cfg = preset("tiny-gpt-oss", hidden_size=a.hidden, intermediate_size=256, moe_intermediate_size=256,
                      num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=4096, num_hidden_layers=2,

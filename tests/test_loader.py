@@ -225,8 +225,12 @@ def test_olmo2_post_norm_family_loads_and_matches_dense_oracle(tmp_path):
     got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
     want = dense_reference_forward(cfg2, w2, torch.tensor(toks + [7]))[-1].numpy()
     assert np.abs(got - want).max() < 1e-3
-    with pytest.raises(NotImplementedError):
-        loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=0, dtype="float32")
+    # tensor-parallel shards keep the norm gains of their own heads
+    _, wr = loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=1, dtype="float32")
+    ws = random_weights(cfg, "cpu", torch.float32, seed=5, tp_size=2, tp_rank=1)
+    assert torch.equal(wr["layers"][0]["q_norm"], ws["layers"][0]["q_norm"])
+    assert torch.equal(wr["layers"][0]["k_norm"], ws["layers"][0]["k_norm"])
+    assert torch.equal(wr["layers"][0]["q_norm"], w["layers"][0]["q_norm"][cfg.q_size // 2:])
 
 
 def test_sliding_window_prefill_and_decode_match_windowed_oracle():
