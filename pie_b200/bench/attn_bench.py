@@ -58,11 +58,14 @@ def main():
     ap.add_argument("--rows", default="64,128,256")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
+    ap.add_argument("--heads", default="32,8", help="query heads, KV heads")
     a = ap.parse_args()
+    hq, hkv = (int(v) for v in a.heads.split(","))
     rows = [int(r) for r in a.rows.split(",")]
     shapes = [(a.reqs, a.len)] if a.reqs and a.len else [(64, 512), (16, 2048), (8, 4096), (2, 16384)]
     for reqs, plen in shapes:
-        run(reqs, plen, rows, a.iters, warmup=a.warmup)
+        run(reqs, plen, rows, a.iters, hq=hq, hkv=hkv, d=a.head_dim, warmup=a.warmup)
 
 
 if __name__ == "__main__":

@@ -1,4 +1,4 @@
-// Paged prefill attention on the 5th-generation tensor cores (head_dim 128, 16-token pages).
+// Paged prefill attention on the 5th-generation tensor cores (head_dim 64 or 128, 16-token pages).
 //
 // One CTA per (tile of 128 or 256 packed query rows, KV head); a row is (query token, head within
 // the GQA group), so a CTA covers 128 / G or 256 / G tokens of one request as one or two MMA tiles of
@@ -32,18 +32,21 @@ using namespace sm100;
 
 constexpr int AT_ROWS = 128;     // packed query rows per MMA tile
 constexpr int AT_BK = 64;        // keys per block
-constexpr int AT_D = 128;
+constexpr int AT_D = 128;          // widest head: fixes the TMEM budget (S[2] x 64 + O x D columns per tile)
 constexpr int AT_STAGES = 3;      // K ring and V ring, each of this many 16 KB tiles
-constexpr uint32_t AT_Q_BYTES = AT_ROWS * AT_D * 2;            // two 16 KB halves
-constexpr uint32_t AT_KV_TILE = AT_BK * AT_D * 2;              // 16 KB: two 8 KB halves [64 keys x 64 d]
+constexpr uint32_t AT_Q_HALF = AT_ROWS * 64 * 2;               // 16 KB: [128 rows x 64 d]; a Q tile is D / 64 of them
+constexpr uint32_t AT_KV_HALF = AT_BK * 64 * 2;                // 8 KB: [64 keys x 64 d]; a K or V tile is D / 64 of them
 constexpr uint32_t AT_P_BYTES = AT_ROWS * AT_BK * 2;           // 16 KB
 constexpr int AT_TILE_BARS = 8;                                // s_full[2] p_full[2] p_empty[2] pv_done o_final
 constexpr float AT_RESCALE_LOG2 = 8.f;                         // the reference maximum may lag the true one by 2^8
 
-template <int NT>
+template <int NT, int D = AT_D>
 struct AtCfg {
     static constexpr int THREADS = 32 * (1 + NT) + 128 * NT;   // producer, one MMA warp per tile, softmax warps
-    static constexpr uint32_t SMEM = NT * AT_Q_BYTES + 2 * AT_STAGES * AT_KV_TILE + NT * 2 * AT_P_BYTES + 1024 + 512;
+    static constexpr int HALVES = D / 64;
+    static constexpr uint32_t Q_BYTES = HALVES * AT_Q_HALF;
+    static constexpr uint32_t KV_TILE = HALVES * AT_KV_HALF;
+    static constexpr uint32_t SMEM = NT * Q_BYTES + 2 * AT_STAGES * KV_TILE + NT * 2 * AT_P_BYTES + 1024 + 512;
     static constexpr uint32_t TMEM_COLS = 256 * NT;             // per tile: S[2] x 64 columns, O x 128
 };
 
@@ -76,9 +79,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// G = query heads per KV head; NT = MMA tiles of 128 rows per CTA (they share the K/V stages).
-template <int G, int NT>
-__global__ void __launch_bounds__(AtCfg<NT>::THREADS, 1)
+// G = query heads per KV head; NT = MMA tiles of 128 rows per CTA (they share the K/V stages);
+// D = head dimension (64 or 128).
+template <int G, int NT, int D>
+__global__ void __launch_bounds__(AtCfg<NT, D>::THREADS, 1)
 paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv,
                              const int* __restrict__ page_indices, const int* __restrict__ kv_page_indptr,
                              const int* __restrict__ qo_indptr, const int* __restrict__ kv_lens,
@@ -87,6 +91,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                              bf16* __restrict__ out, float* __restrict__ lse_out, const float* __restrict__ sinks_log2,
                              int hq, int hkv, int pad_page, float scale_log2, int window_left, int* status) {
     constexpr int TQ = AT_ROWS / G;          // query tokens per MMA tile
+    constexpr int HALVES = D / 64;
+    constexpr uint32_t AT_Q_BYTES = AtCfg<NT, D>::Q_BYTES, AT_KV_TILE = AtCfg<NT, D>::KV_TILE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_addr(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -156,7 +162,7 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
         fence_proxy_async();
     }
     if (warp == 1) {
-        tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_slot)), AtCfg<NT>::TMEM_COLS);
+        tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_slot)), AtCfg<NT, D>::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -171,8 +177,10 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
             mbar_arrive_expect_tx(q_full(), NT * AT_Q_BYTES);
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                tma_load_3d(q_s + t * AT_Q_BYTES, &tma_q, q_full(), 0, h * G, q_base + qstart + t * TQ);
-                tma_load_3d(q_s + t * AT_Q_BYTES + AT_Q_BYTES / 2, &tma_q, q_full(), 64, h * G, q_base + qstart + t * TQ);
+#pragma unroll
+                for (int half = 0; half < HALVES; ++half)
+                    tma_load_3d(q_s + t * AT_Q_BYTES + half * AT_Q_HALF, &tma_q, q_full(), half * 64, h * G,
+                                q_base + qstart + t * TQ);
             }
             bool ok = true;
             for (int j = 0; j < nkb && ok; ++j) {
@@ -190,8 +198,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                 for (int pg = 0; pg < 4; ++pg) {
                     const int krow = ((pg_id[pg] * 2) * hkv + h) * 16;
 #pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        tma_load_2d(k_s + s * AT_KV_TILE + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, k_full(s), half * 64, krow);
+                    for (int half = 0; half < HALVES; ++half)
+                        tma_load_2d(k_s + s * AT_KV_TILE + half * AT_KV_HALF + pg * 2048, &tma_kv, k_full(s), half * 64, krow);
                 }
                 if (!mbar_wait(v_empty(s), par, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
                 mbar_arrive_expect_tx(v_full(s), AT_KV_TILE);
@@ -199,8 +207,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                 for (int pg = 0; pg < 4; ++pg) {
                     const int vrow = ((pg_id[pg] * 2 + 1) * hkv + h) * 16;
 #pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        tma_load_2d(v_s + s * AT_KV_TILE + half * (AT_KV_TILE / 2) + pg * 2048, &tma_kv, v_full(s), half * 64, vrow);
+                    for (int half = 0; half < HALVES; ++half)
+                        tma_load_2d(v_s + s * AT_KV_TILE + half * AT_KV_HALF + pg * 2048, &tma_kv, v_full(s), half * 64, vrow);
                 }
             }
             // no copy may be in flight when the CTA exits
@@ -215,11 +223,10 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
         const int t = warp - 1;
         if (lane == 0 && nkb > 0) {
             constexpr uint32_t idesc_s = make_idesc_bf16(AT_ROWS, AT_BK);
-            constexpr uint32_t idesc_o = make_idesc_bf16_bmn(AT_ROWS, AT_D);
+            constexpr uint32_t idesc_o = make_idesc_bf16_bmn(AT_ROWS, D);
             const int my = NT == 1 ? nkb : (t == 0 ? nkb_t[0] : nkb_t[NT - 1]);
             const uint32_t tm_s = tmem_base + t * 256, tm_o = tm_s + 128;
             const uint64_t q_desc0 = make_smem_desc_sw128(q_s + t * AT_Q_BYTES);
-            const uint64_t q_desc1 = make_smem_desc_sw128(q_s + t * AT_Q_BYTES + AT_Q_BYTES / 2);
             bool ok = mbar_wait(q_full(), 0, status, PIE_ERR_WAIT_TMA);
             // S_t(j) = Q_t K_j^T into S buffer j & 1. Every MMA warp waits for and releases every K and V
             // tile, also those its (shorter) tile does not use, so that the rings advance in step.
@@ -229,11 +236,13 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                 if (j < my) {
                     tc_fence_after();
                     const uint64_t k_desc0 = make_smem_desc_sw128(k_s + s * AT_KV_TILE);
-                    const uint64_t k_desc1 = make_smem_desc_sw128(k_s + s * AT_KV_TILE + AT_KV_TILE / 2);
+                    // descriptors count in 16-byte units: the next 64-wide half of d is AT_Q_HALF / AT_KV_HALF further
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) umma_bf16(tm_s + (j & 1) * AT_BK, q_desc0 + 2u * k, k_desc0 + 2u * k, idesc_s, k != 0);
+                    for (int half = 0; half < HALVES; ++half)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) umma_bf16(tm_s + (j & 1) * AT_BK, q_desc1 + 2u * k, k_desc1 + 2u * k, idesc_s, 1);
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(tm_s + (j & 1) * AT_BK, q_desc0 + half * (AT_Q_HALF >> 4) + 2u * k,
+                                      k_desc0 + half * (AT_KV_HALF >> 4) + 2u * k, idesc_s, (half | k) != 0);
                     umma_commit(s_full(t, j & 1));
                 }
                 umma_commit(k_empty(s));
@@ -251,7 +260,7 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                     const uint64_t p_desc = make_smem_desc_sw128(p_s + (t * 2 + b) * AT_P_BYTES);
 #pragma unroll
                     for (int k = 0; k < AT_BK / 16; ++k)      // 16 keys: 32 bytes along a P row, two 8-row groups of V
-                        umma_bf16(tm_o, p_desc + 2u * k, make_smem_desc_sw128_mn(v_s + s * AT_KV_TILE + k * 2048, AT_KV_TILE / 2),
+                        umma_bf16(tm_o, p_desc + 2u * k, make_smem_desc_sw128_mn(v_s + s * AT_KV_TILE + k * 2048, AT_KV_HALF),
                                   idesc_o, (j | k) != 0);
                     umma_commit(pv_done(t));
                     umma_commit(p_empty(t, b));
@@ -330,7 +339,7 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                     if (!__all_sync(0xffffffffu, done)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
-                    for (int c = 0; c < AT_D / 32; ++c) {
+                    for (int c = 0; c < D / 32; ++c) {
                         uint32_t v[32];
                         tmem_ld_32x32(tm_o + c * 32, v);
                         tmem_ld_wait();
@@ -377,9 +386,9 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
             // attention sink: a per-head logit in the softmax denominator without a value row
             if (sinks_log2 && l > 0.f) l += exp2f(sinks_log2[head] - m_ref * scale_log2);
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = out + ((size_t)(q_base + (valid ? qtok : 0)) * hq + head) * AT_D;
+            bf16* dst = out + ((size_t)(q_base + (valid ? qtok : 0)) * hq + head) * D;
 #pragma unroll
-            for (int c = 0; c < AT_D / 32; ++c) {
+            for (int c = 0; c < D / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32(tm_o + c * 32, v);
                 tmem_ld_wait();
@@ -403,7 +412,7 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, AtCfg<NT>::TMEM_COLS);
+        tmem_dealloc(tmem_base, AtCfg<NT, D>::TMEM_COLS);
     }
 }
 
@@ -428,11 +437,11 @@ static EncodeTiledFnA at_encoder() {
     return enc;
 }
 
-// 1 when the tensor-core kernel covers the shape (head_dim 128, 16-token pages, group size dividing 128).
+// 1 when the tensor-core kernel covers the shape (head_dim 64 or 128, 16-token pages, group size dividing 128).
 PIE_API int pie_prefill_attn_tc_supported(int hq, int hkv, int head_dim, int page_size) {
     if (hkv <= 0 || hq % hkv) return 0;
     const int g = hq / hkv;
-    return head_dim == 128 && page_size == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16) ? 1 : 0;
+    return (head_dim == 128 || head_dim == 64) && page_size == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16) ? 1 : 0;
 }
 
 // Same contract as pie_paged_prefill_attn, with tiles of tile_rows / group query tokens (tile_rows = 128 or
@@ -441,19 +450,21 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
                                       const int* kv_page_indptr, const int* qo_indptr, const int* kv_lens,
                                       const int* tile_req, const int* tile_qstart, int num_tiles,
                                       const uint32_t* mask_bits, const long* mask_word_indptr, void* out,
-                                      float* lse_out, int n_tokens, int hq, int hkv, int total_pages, float sm_scale,
+                                      float* lse_out, int n_tokens, int hq, int hkv, int head_dim, int total_pages,
+                                      float sm_scale,
                                       int window_left, int tile_rows, const float* sinks_log2, int* status,
                                       cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (!pie_prefill_attn_tc_supported(hq, hkv, AT_D, 16) || (tile_rows != 128 && tile_rows != 256) || !status)
+    const int D_ = head_dim;
+    if (!pie_prefill_attn_tc_supported(hq, hkv, head_dim, 16) || (tile_rows != 128 && tile_rows != 256) || !status)
         return (int)cudaErrorInvalidValue;
     EncodeTiledFnA enc = at_encoder();
     if (!enc) return (int)cudaErrorNotSupported;
     const int G = hq / hkv;
     CUtensorMap tq, tkv;
     {
-        cuuint64_t dims[3] = {(cuuint64_t)AT_D, (cuuint64_t)hq, (cuuint64_t)n_tokens};
-        cuuint64_t strides[2] = {(cuuint64_t)AT_D * 2, (cuuint64_t)hq * AT_D * 2};
+        cuuint64_t dims[3] = {(cuuint64_t)D_, (cuuint64_t)hq, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)D_ * 2, (cuuint64_t)hq * D_ * 2};
         cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(AT_ROWS / G)};
         cuuint32_t estr[3] = {1, 1, 1};
         if (enc(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
@@ -462,8 +473,8 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
             return (int)cudaErrorInvalidValue;
     }
     {
-        cuuint64_t dims[2] = {(cuuint64_t)AT_D, (cuuint64_t)total_pages * 2 * hkv * 16};
-        cuuint64_t strides[1] = {(cuuint64_t)AT_D * 2};
+        cuuint64_t dims[2] = {(cuuint64_t)D_, (cuuint64_t)total_pages * 2 * hkv * 16};
+        cuuint64_t strides[1] = {(cuuint64_t)D_ * 2};
         cuuint32_t box[2] = {64, 16};
         cuuint32_t estr[2] = {1, 1};
         if (enc(&tkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv_layer), dims, strides, box, estr,
@@ -473,17 +484,20 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
     }
     const float scale_log2 = sm_scale * 1.4426950408889634f;
     dim3 grid(num_tiles, hkv);
-#define GO2(G_, NT_)                                                                                                  \
+#define GO3(G_, NT_, D__)                                                                                             \
     {                                                                                                                 \
-        auto kern = paged_prefill_attn_tc_kernel<G_, NT_>;                                                            \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AtCfg<NT_>::SMEM); \
+        auto kern = paged_prefill_attn_tc_kernel<G_, NT_, D__>;                                                       \
+        using Cfg = AtCfg<NT_, D__>;                                                                                  \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);      \
         if (e != cudaSuccess) return (int)e;                                                                          \
-        kern<<<grid, AtCfg<NT_>::THREADS, AtCfg<NT_>::SMEM, st>>>(                                                    \
+        kern<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(                                                                  \
             tq, tkv, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req, tile_qstart, mask_bits,              \
             mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv, total_pages - 1, scale_log2, window_left,     \
             status);                                                                                                  \
         return (int)cudaGetLastError();                                                                               \
     }
+#define GO2(G_, NT_)           \
+    if (D_ == 128) GO3(G_, NT_, 128) else GO3(G_, NT_, 64)
 #define GO(G_)                 \
     if (tile_rows == 128) GO2(G_, 1) else GO2(G_, 2)
     switch (G) {
@@ -495,6 +509,7 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
     }
 #undef GO
 #undef GO2
+#undef GO3
     return (int)cudaErrorInvalidValue;
 }
 

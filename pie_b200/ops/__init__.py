@@ -514,7 +514,7 @@ def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items
 
 def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int) -> int:
     """Packed (token, head) rows per prefill tile: 256 (two MMA tiles per CTA; ``PIE_PREFILL_TC=128``
-    for one) where the tcgen05 kernel covers the shape (head_dim 128, 16-token pages, group size
+    for one) where the tcgen05 kernel covers the shape (head_dim 64 or 128, 16-token pages, group size
     dividing 128), else - or with ``PIE_PREFILL_TC=0`` - the 64 rows of the mma.sync kernel."""
     want = os.environ.get("PIE_PREFILL_TC", "256")
     if want == "0" or not fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size):
@@ -610,7 +610,7 @@ def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out
         check(fn("pie_paged_prefill_attn_tc")(
             ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
             ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
-            ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), n, hq, hkv,
+            ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), n, hq, hkv, d,
             kv_layer.shape[0], sm_scale, wl, plan.tile_rows, ptr(sinks_log2), ptr(kernel_status(q.device)),
             stream_ptr()),
             "paged_prefill_attn_tc")

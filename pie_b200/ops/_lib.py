@@ -40,7 +40,7 @@ _SIGNATURES = {
     "pie_paged_prefill_attn": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, f32, i32, p, p],
     "pie_prefill_tile_tokens": [i32],
     "pie_prefill_attn_tc_supported": [i32, i32, i32, i32],
-    "pie_paged_prefill_attn_tc": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, f32, i32, i32, p, p, p],
+    "pie_paged_prefill_attn_tc": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, i32, p, p, p],
     "pie_sample": [p, i64, i32, i32, p, p, p, p, p, p, p, i32, p, p],
     "pie_row_stats": [p, i64, i32, i32, p, p],
     "pie_feed_tokens": [p, p, p, i32, p],

@@ -162,7 +162,7 @@ def test_attention_sinks_and_per_call_window(d, hq, hkv):
     qo[1:] = np.cumsum(qlens)
     q = bf(int(qo[-1]), hq, d, seed=54)
     batch = ops.AttnBatch(qo, indptr, pages, kv_lens, None, -1)
-    for rows in ([64, 128, 256] if d == 128 else [64]):
+    for rows in [64, 128, 256]:
         plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV, tile_rows=rows)
         for window in (-1, 33):
             out = ops.paged_prefill_attention(q, kv, plan, scale, window_left=window, sinks_log2=sl2)
@@ -199,7 +199,8 @@ def test_paged_decode_attention_sliding_window(window):
 @pytest.mark.parametrize("d,hq,hkv,rows", [(128, 32, 8, 64), (128, 8, 1, 64), (64, 4, 2, 64),
                                            (128, 32, 8, 128), (128, 8, 1, 128), (128, 4, 4, 128),
                                            (128, 32, 2, 128), (128, 8, 4, 128), (128, 32, 8, 256),
-                                           (128, 8, 1, 256), (128, 4, 4, 256), (128, 32, 2, 256)])
+                                           (128, 8, 1, 256), (128, 4, 4, 256), (128, 32, 2, 256),
+                                           (64, 4, 2, 128), (64, 16, 2, 256), (64, 64, 8, 256), (64, 8, 8, 128)])
 @pytest.mark.parametrize("mode", ["causal", "custom", "window"])
 def test_paged_prefill_attention(d, hq, hkv, rows, mode):
     """rows = 64: the mma.sync kernel; rows = 128 / 256: the tcgen05 kernel with one / two MMA
