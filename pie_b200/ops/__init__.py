@@ -480,6 +480,11 @@ class AttnBatch:
         return bool(len(q) > 0 and (q == 1).all() and self.masks is None)
 
 
+# work units (KV chunk x KV head) each persistent decode-attention CTA should get: more units balance the
+# tail of the launch better, fewer keep the merge pass short
+_DECODE_UNITS_PER_CTA = int(os.environ.get("PIE_DECODE_UNITS", "4"))
+
+
 def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items: int = 0,
                       min_chunk: int = 256, window_left: int = -1):
     """Split each request's KV range into chunks so that items*hkv fills the machine. With a
@@ -494,7 +499,7 @@ def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items
         lo = np.maximum(0, full_lens - 1 - window_left) // 16 * 16
     kv_lens = full_lens - lo
     total = int(kv_lens.sum())
-    chunk = max(min_chunk, -(-total * hkv // max(1, target_ctas * 4)))
+    chunk = max(min_chunk, -(-total * hkv // max(1, target_ctas * _DECODE_UNITS_PER_CTA)))
     chunk = -(-chunk // 16) * 16
     while True:
         n_items = np.maximum(1, -(-kv_lens // chunk))

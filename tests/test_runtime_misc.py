@@ -200,3 +200,30 @@ def test_harmony_and_kimi_chat_templates():
     assert g.answer("get_weather", "{}").startswith("<|start|>functions.get_weather to=assistant")
     k = I.for_arch("kimi")
     assert k.format("user", "hi", False) + k.cue_text() == "<|im_user|>user<|im_middle|>hi<|im_end|><|im_assistant|>assistant<|im_middle|>"
+
+
+def test_attention_plans_on_the_host():
+    """Decode work items cover each request's visible key range exactly once in 16-token aligned
+    chunks (also under a sliding window); prefill tiles come out heaviest first."""
+    import numpy as np
+    from pie_b200 import ops
+    kv = np.array([1, 15, 16, 17, 300, 1000, 2305, 64])
+    for window in (-1, 0, 100):
+        req, st, en, iptr = ops.plan_decode_items(kv, 8, target_ctas=64, min_chunk=256, window_left=window)
+        assert iptr[0] == 0 and iptr[-1] == len(req)
+        for r, kl in enumerate(kv):
+            a, b = iptr[r], iptr[r + 1]
+            assert b > a and (req[a:b] == r).all()
+            lo = 0 if window < 0 else max(0, kl - 1 - window) // 16 * 16
+            assert st[a] == lo and en[b - 1] == kl and (st[a:b] % 16 == 0).all()
+            assert (st[a + 1:b] == en[a:b - 1]).all()        # contiguous, no overlap
+    # a cap on the number of items coarsens the chunks instead of dropping work
+    req, st, en, iptr = ops.plan_decode_items(kv, 8, target_ctas=4096, max_items=10, min_chunk=16)
+    assert len(req) <= 10 and en[iptr[1:] - 1].tolist() == kv.tolist()
+    qo = np.array([0, 5, 300, 1000])
+    lens = np.array([45, 295, 2000])
+    tr, tq = ops.plan_prefill_tiles(qo, 4, 256, lens)
+    work = [lens[r] - (qo[r + 1] - qo[r]) + min(q + 64, qo[r + 1] - qo[r]) for r, q in zip(tr, tq)]
+    assert work == sorted(work, reverse=True) and len(tr) == 1 + 5 + 11
+    tr0, tq0 = ops.plan_prefill_tiles(qo, 4, 256)
+    assert sorted(zip(tr.tolist(), tq.tolist())) == sorted(zip(tr0.tolist(), tq0.tolist()))
