@@ -201,7 +201,7 @@ def set_pdl(enabled: bool) -> None:
 
 
 def set_gemm_swap(max_m: int) -> None:
-    """Batches of up to max_m rows (default 64, at most 128) may run the single-CTA GEMM with swapped
+    """Batches of up to max_m rows (default and at most 128) may run the single-CTA GEMM with swapped
     operands (weights on the 128-row side of the MMA, transposed epilogue) where the launcher's rule
     expects a gain; 0 turns that off, 1000 swaps every batch of up to 128 rows (tests)."""
     fn("pie_gemm_set_swap")(int(max_m))

@@ -121,7 +121,7 @@ def test_gemm_swapped_operands_small_batch(m, n, k, epi):
         ops.set_gemm_swap(0)
         y0 = ops.gemm(x, w, residual=r, epilogue=e)
     finally:
-        ops.set_gemm_swap(64)
+        ops.set_gemm_swap(128)
     ref = x.float() @ w.float().t()
     if epi == "residual":
         ref = ref + r.float()
