@@ -177,3 +177,61 @@ def test_embedded_server_and_client_cli(tmp_path, capsys):
         assert client_cli.main(["--uri", uri, "status"]) == 0
         assert '"models"' in capsys.readouterr().out
         assert "pie_b200_uptime_seconds" in srv.engine.metrics_text()
+
+
+def test_cli_runs_a_gguf_model_with_its_own_tokenizer(tmp_path, capsys):
+    """`pie run --model-path file.gguf --driver cpu`: configuration, weights and the byte-level BPE
+    tokenizer all come from the one GGUF file; text goes in, text comes out."""
+    import json
+    import torch
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    from pie_b200.models import gguf
+    from pie_b200.models.config import preset
+    from pie_b200.models.weights import random_weights
+    from pie_b200.server import cli
+
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(["the quick brown fox jumps over the lazy dog " * 4, "hello world hello pie"],
+                            trainers.BpeTrainer(vocab_size=320, special_tokens=["<|eot|>"],
+                                                initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    tj = json.loads(tok.to_str())
+    vocab = tj["model"]["vocab"]
+    tokens = [None] * len(vocab)
+    for t, i in vocab.items():
+        tokens[i] = t
+    merges = [m if isinstance(m, str) else " ".join(m) for m in tj["model"]["merges"]]
+    cfg = preset("tiny-llama", vocab_size=len(tokens), hidden_size=64, intermediate_size=128, num_attention_heads=2,
+                 num_key_value_heads=1, head_dim=32, num_hidden_layers=1)
+    w = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    d, hq, hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    lw = w["layers"][0]
+    q, k, v = lw["wqkv"].split([hq * d, hkv * d, hkv * d], 0)
+    tensors = {"token_embd.weight": (w["embed"], gguf.T_F32), "output_norm.weight": (w["final_norm"], gguf.T_F32),
+               "output.weight": (w["lm_head"], gguf.T_F32), "blk.0.attn_norm.weight": (lw["ln1"], gguf.T_F32),
+               "blk.0.ffn_norm.weight": (lw["ln2"], gguf.T_F32),
+               "blk.0.attn_q.weight": (gguf.permute_rotary(q, hq), gguf.T_F32),
+               "blk.0.attn_k.weight": (gguf.permute_rotary(k, hkv), gguf.T_F32), "blk.0.attn_v.weight": (v, gguf.T_F32),
+               "blk.0.attn_output.weight": (lw["wo"], gguf.T_F32), "blk.0.ffn_gate.weight": (lw["w_gate_up"][0::2], gguf.T_F32),
+               "blk.0.ffn_up.weight": (lw["w_gate_up"][1::2], gguf.T_F32), "blk.0.ffn_down.weight": (lw["w_down"], gguf.T_F32)}
+    meta = {"general.architecture": "llama", "general.name": "tiny-gguf", "llama.embedding_length": cfg.hidden_size,
+            "llama.block_count": 1, "llama.attention.head_count": hq, "llama.attention.head_count_kv": hkv,
+            "llama.feed_forward_length": cfg.intermediate_size, "llama.context_length": 512,
+            "llama.attention.key_length": d, "llama.rope.freq_base": float(cfg.rope_theta),
+            "llama.attention.layer_norm_rms_epsilon": float(cfg.rms_norm_eps), "tokenizer.ggml.model": "gpt2",
+            "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": merges,
+            "tokenizer.ggml.eos_token_id": vocab["<|eot|>"]}
+    path = tmp_path / "tiny.gguf"
+    gguf.write_gguf(path, meta, tensors)
+    capsys.readouterr()
+    rc = cli.main(["run", "--model-path", str(path), "--driver", "cpu", "text-completion", "--",
+                   "--prompt", "hello world", "--max_tokens", "6", "--temperature", "0", "--return_tokens"])
+    out = capsys.readouterr().out
+    assert rc == 0, out
+    res = json.loads([l for l in out.strip().splitlines() if l.startswith("{")][-1])
+    assert 1 <= len(res["tokens"]) <= 6 and all(0 <= t < len(tokens) for t in res["tokens"])
+    # the prompt was tokenised with the file's vocabulary: the same ids as the source tokenizer gives
+    from pie_b200.runtime.tokenizer import load_gguf_tokenizer
+    assert load_gguf_tokenizer(path).encode("hello world") == tok.encode("hello world").ids
