@@ -23,6 +23,7 @@ class Instruct:
     stop_strings: Sequence[str] = ()
     think_open, think_close = "<think>", "</think>"
     tool_open, tool_close = "<tool_call>", "</tool_call>"
+    drop_strings: Sequence[str] = ()      # framing the model writes around its answer; decoders swallow it
 
     def format(self, role: str, message: str, first: bool) -> str:
         return message
@@ -203,6 +204,7 @@ class GptOss(Instruct):
     stop_strings = ("<|return|>", "<|call|>")
     think_open, think_close = "<|channel|>analysis<|message|>", "<|end|>"
     tool_open, tool_close = "<|constrain|>json<|message|>", "<|call|>"
+    drop_strings = ("<|start|>assistant", "<|channel|>final<|message|>", "<|end|>", "<|return|>")
 
     def format(self, role, message, first):
         if role == "assistant":
@@ -308,6 +310,7 @@ class ReasoningDecoder:
 
     def __init__(self, instruct: Instruct, starts_in_think: bool = False):
         self.open, self.close = instruct.think_open, instruct.think_close
+        self.drops = tuple(instruct.drop_strings)
         self.in_think = starts_in_think
         self.buf = ""
 
@@ -315,20 +318,24 @@ class ReasoningDecoder:
         self.buf += text
         out = []
         while True:
-            tag = self.close if self.in_think else self.open
-            i = self.buf.find(tag)
-            if i < 0:
-                keep = max(0, len(self.buf) - len(tag) + 1)     # a tag may be split across deltas
+            # inside a reasoning block only its end matters; outside, its start and the framing to swallow
+            tags = (self.close,) if self.in_think else (self.open,) + self.drops
+            hits = [(self.buf.find(t), -len(t), t) for t in tags if t and self.buf.find(t) >= 0]
+            if not hits:
+                keep = max(0, len(self.buf) - max(len(t) for t in tags) + 1)     # a tag may be split across deltas
                 if keep:
                     out.append(Event("thinking" if self.in_think else "delta", self.buf[:keep]))
                     self.buf = self.buf[keep:]
                 break
+            i, _, tag = min(hits)        # earliest; the longer tag on a tie
             if i:
                 out.append(Event("thinking" if self.in_think else "delta", self.buf[:i]))
+            self.buf = self.buf[i + len(tag):]
             if self.in_think:
                 out.append(Event("thinking_done"))
-            self.buf = self.buf[i + len(tag):]
-            self.in_think = not self.in_think
+                self.in_think = False
+            elif tag == self.open:
+                self.in_think = True
         return out
 
     def flush(self) -> List[Event]:

@@ -227,3 +227,25 @@ def test_attention_plans_on_the_host():
     assert work == sorted(work, reverse=True) and len(tr) == 1 + 5 + 11
     tr0, tq0 = ops.plan_prefill_tiles(qo, 4, 256)
     assert sorted(zip(tr.tolist(), tq.tolist())) == sorted(zip(tr0.tolist(), tq0.tolist()))
+
+
+def test_reasoning_decoder_splits_harmony_channels():
+    from pie_b200.runtime import instruct as I
+    g = I.for_arch("gpt_oss")
+    stream = ("<|channel|>analysis<|message|>think hard<|end|><|start|>assistant<|channel|>final<|message|>"
+              "The answer is 4.<|return|>")
+    for step in (1, 3, 7, len(stream)):
+        dec = I.ReasoningDecoder(g)
+        ev = []
+        for i in range(0, len(stream), step):
+            ev += dec.feed(stream[i:i + step])
+        ev += dec.flush()
+        think = "".join(e.text for e in ev if e.kind == "thinking")
+        answer = "".join(e.text for e in ev if e.kind == "delta")
+        assert think == "think hard" and answer == "The answer is 4.", (step, think, answer)
+        assert sum(e.kind == "thinking_done" for e in ev) == 1
+    # the plain <think> family is unchanged
+    dec = I.ReasoningDecoder(I.for_arch("qwen3"))
+    ev = dec.feed("<think>a</think>b") + dec.flush()
+    got = [(e.kind, e.text) for e in ev if e.text or e.kind == "thinking_done"]
+    assert got == [("thinking", "a"), ("thinking_done", ""), ("delta", "b")]
