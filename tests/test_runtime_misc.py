@@ -249,3 +249,13 @@ def test_reasoning_decoder_splits_harmony_channels():
     ev = dec.feed("<think>a</think>b") + dec.flush()
     got = [(e.kind, e.text) for e in ev if e.text or e.kind == "thinking_done"]
     assert got == [("thinking", "a"), ("thinking_done", ""), ("delta", "b")]
+
+
+def test_precapture_is_a_no_op_without_cuda_graphs():
+    import torch
+    from pie_b200.driver.executor import TorchDriver, graph_buckets
+    from pie_b200.models.config import preset
+    drv = TorchDriver(preset("tiny-llama"), "cpu", num_pages=8, page_size=16, max_requests=4, max_tokens=64)
+    assert drv.precapture_graphs() == 0 and not drv.graphs
+    b = graph_buckets(512)
+    assert b[:5] == [1, 2, 4, 8, 16] and b[-1] == 512 and b == sorted(set(b)) and 64 in b and 256 in b
