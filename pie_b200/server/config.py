@@ -24,6 +24,9 @@ class ServerConfig:
     host: str = "127.0.0.1"
     port: int = 8080
     max_message_bytes: int = 64 << 20
+    # Uploaded programs are Python source that runs inside the engine process (no sandbox): only
+    # switch this on for clients you would give a shell on the machine.
+    allow_program_upload: bool = False
 
 
 @dataclass

@@ -174,6 +174,7 @@ def start_engine(cfg: Config, serve: bool = True, port: Optional[int] = None) ->
     server = None
     if serve:
         server = PieServer(engine, cfg.server.host, cfg.server.port if port is None else port, auth,
-                           rt.program_dir, cfg.server.max_message_bytes)
+                           rt.program_dir, cfg.server.max_message_bytes,
+                           allow_program_upload=cfg.server.allow_program_upload)
         server.start()
     return EngineHandle(engine, server, auth, comms)

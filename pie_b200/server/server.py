@@ -133,6 +133,9 @@ class Session:
         await self.respond(cid, True, "true" if known else "false")
 
     async def on_add_program(self, m, cid):
+        if not self.server.allow_program_upload:
+            return await self.respond(cid, False, "uploads disabled: set [server] allow_program_upload = true "
+                                                  "(uploaded programs run unsandboxed in the engine process)")
         key = m["program_hash"]
         up = self.uploads.setdefault(key, {"chunks": {}, "manifest": m["manifest"]})
         up["chunks"][m["chunk_index"]] = bytes(m["chunk_data"])
@@ -277,8 +280,12 @@ class Session:
 
 class PieServer:
     def __init__(self, engine: Engine, host: str = "127.0.0.1", port: int = 8080, auth: Optional[Authenticator] = None,
-                 program_dir: Optional[str] = None, max_message_bytes: int = 64 << 20):
+                 program_dir: Optional[str] = None, max_message_bytes: int = 64 << 20,
+                 allow_program_upload: bool = False):
         self.engine, self.host, self.port = engine, host, port
+        # Programs are native Python and run in this process with its privileges; uploads (and the
+        # programs an earlier run cached on disk) are only accepted when the operator opted in.
+        self.allow_program_upload = allow_program_upload
         self.auth = auth or Authenticator(False)
         self.program_dir = Path(program_dir).expanduser() if program_dir else None
         self.program_hashes: Dict[str, str] = {}
@@ -294,6 +301,8 @@ class PieServer:
 
     def _load_stored_programs(self) -> None:
         """Programs installed earlier (disk cache programs/<name>/<version>.{py,toml})."""
+        if not self.allow_program_upload:
+            return
         try:
             for ref in self.store.load_cache():
                 name, _, ver = ref.partition("@")

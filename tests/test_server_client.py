@@ -24,7 +24,7 @@ def stack(tmp_path):
     key, pub = generate_ed25519()
     users.add("alice", pub)
     auth = Authenticator(True, users)
-    srv = PieServer(eng, "127.0.0.1", 0, auth, str(tmp_path / "programs"))
+    srv = PieServer(eng, "127.0.0.1", 0, auth, str(tmp_path / "programs"), allow_program_upload=True)
     srv.bad_token_delay_scale = 0.01
     port = srv.start()
     yield eng, srv, auth, key, f"ws://127.0.0.1:{port}"
@@ -88,6 +88,31 @@ def test_upload_program_signal_file_and_disk_cache(stack, tmp_path):
     assert seen[-1] == ("return", "ping:300000")
     assert (tmp_path / "programs" / "echo-test" / "0.2.0.py").exists()
     c.close()
+
+
+def test_upload_refused_unless_enabled(tmp_path):
+    """Uploaded programs are unsandboxed Python: a server accepts them only with allow_program_upload."""
+    eng = Engine(EngineConfig(watchdog_interval_s=0.1))
+    eng.add_model("mock", MockDriver(CounterBehavior(), total_pages=64))
+    install_all(eng)
+    # a program cached by an earlier (opted-in) run must not be executed by a server that did not opt in
+    cached = tmp_path / "programs" / "evil"
+    cached.mkdir(parents=True)
+    marker = tmp_path / "ran"
+    (cached / "0.1.0.py").write_text(f"open({str(marker)!r}, 'w').write('x')\nasync def main(a):\n    return 1\n")
+    (cached / "0.1.0.toml").write_text('[package]\nname = "evil"\nversion = "0.1.0"\n')
+    srv = PieServer(eng, "127.0.0.1", 0, Authenticator(False), str(tmp_path / "programs"))
+    port = srv.start()
+    try:
+        assert not marker.exists() and "evil" not in eng.programs
+        c = PieClient(f"ws://127.0.0.1:{port}")
+        with pytest.raises(ClientError, match="uploads disabled"):
+            c.install_program(PROGRAM, '[package]\nname = "echo-test"\nversion = "0.2.0"\n')
+        assert not c.program_exists("echo-test")
+        c.close()
+    finally:
+        srv.stop()
+        eng.shutdown()
 
 
 def test_workflow_and_daemon(stack):
@@ -159,7 +184,7 @@ def test_cli_smoke_run_and_monitor(capsys):
 def test_embedded_server_and_client_cli(tmp_path, capsys):
     from pie_b200.client import cli as client_cli
     from pie_b200.server.embed import Server
-    toml = (f'[runtime]\nprogram_dir = "{tmp_path}/programs"\n[telemetry]\nenabled = true\n[auth]\nenabled = false\n'
+    toml = (f'[server]\nallow_program_upload = true\n[runtime]\nprogram_dir = "{tmp_path}/programs"\n[telemetry]\nenabled = true\n[auth]\nenabled = false\n'
             '[[model]]\nname = "dummy"\npreset = "tiny-llama"\n[model.driver]\ntype = "dummy"\n')
     with Server.from_text(toml) as srv:
         uri = srv.uri

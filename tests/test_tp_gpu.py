@@ -21,7 +21,7 @@ def test_tp2_logits_match_single_gpu(backend, model):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     port = 29511 + ["dense", "moe", "moe-ep", "dense-fp8", "gpt-oss", "olmo2"].index(model) * 2 + (backend == "nccl")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), "-m", "pie_b200.parallel.tp_check", "--backend", backend,
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_check.py"), "--backend", backend,
            "--model", model]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     lines = [l for l in out.stdout.splitlines() if l.startswith("{")]

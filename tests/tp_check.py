@@ -1,7 +1,7 @@
 """Tensor-parallel parity check, run as one process per GPU:
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
-        -m pie_b200.parallel.tp_check [--backend fused|nccl]
+        tests/tp_check.py [--backend fused|nccl]
 
 Rank 0 drives a prefill batch and two decode steps through the tensor-parallel driver (followers
 mirror every fire from the control ring) and compares the logits with a single-GPU driver holding
@@ -28,12 +28,12 @@ def main():
                     help="moe: experts sharded on their intermediate dimension; moe-ep: whole experts per rank")
     a = ap.parse_args()
     import torch.distributed as dist
-    from ..driver.executor import TorchDriver
-    from ..driver.schema import SamplerKind, SamplerSpec
-    from ..models.config import preset
-    from ..models.transformer import ParallelContext
-    from ..runtime.scheduler import PendingRequest, fold
-    from .comm import TPComm
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models.config import preset
+    from pie_b200.models.transformer import ParallelContext
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+    from pie_b200.parallel.comm import TPComm
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -111,7 +111,7 @@ def main():
         toks = [int(np.frombuffer(s.logits, dtype=np.float32).argmax()) for s in r_ref.slots]
     comm.stop_followers()
     torch.cuda.synchronize()
-    from .. import ops
+    from pie_b200 import ops
     ops.check_kernel_status(dev)
     report["allreduce_small_ok"] = ar_ok
     report["ok"] = ar_ok and all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
