@@ -185,7 +185,8 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          const int* __restrict__ num_items_ptr, bf16* __restrict__ out,
                          float* __restrict__ o_part, float* __restrict__ lse_part, int hq, int hkv,
                          int page_size, float scale_log2, int window_left,
-                         const float* __restrict__ sinks_log2) {
+                         const float* __restrict__ sinks_log2, int max_items, int num_reqs,
+                         int* __restrict__ status) {
     static_assert(G <= 16, "at most 16 query heads per KV head");
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int CH = D / 8;              // 16-byte chunks per row
@@ -195,11 +196,22 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     const uint32_t warp_smem = q_smem + TILE_BYTES + warp * DEC_STAGES * 2 * TILE_BYTES;
     pdl_trigger();
     pdl_wait();
-    const long total = (long)(*num_items_ptr) * hkv;
+    // The work count lives in device memory (graph replays refresh it): never trust it past the
+    // size of the scratch the launcher was given. Work beyond that is dropped and reported.
+    int n_items = *num_items_ptr;
+    if (n_items > max_items || n_items < 0) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && status) atomicCAS(status, 0, PIE_ERR_BOUNDS);
+        n_items = n_items < 0 ? 0 : max_items;
+    }
+    const long total = (long)n_items * hkv;
 
     for (long w = blockIdx.x; w < total; w += gridDim.x) {
         const int it = (int)(w / hkv), h = (int)(w - (long)it * hkv);
         const int req = item_req[it];
+        if (req < 0 || req >= num_reqs) {      // block-uniform: a corrupt item is skipped, not followed
+            if (threadIdx.x == 0 && status) atomicCAS(status, 0, PIE_ERR_BOUNDS);
+            continue;
+        }
         const int kv_start = item_start[it], kv_end = item_end[it];
         // sliding window: the query sits at position kv_len - 1 (kv_len = end of the request's last
         // item) and sees keys >= kv_len - 1 - window_left; items start on a 16-token boundary below that
@@ -324,11 +336,11 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ o_part,
                                           const float* __restrict__ lse_part,
                                           const int* __restrict__ req_item_indptr,
                                           bf16* __restrict__ out, int hq, int hkv, int group,
-                                          const float* __restrict__ sinks_log2) {
+                                          const float* __restrict__ sinks_log2, int max_items) {
     const int req = blockIdx.x, qh = blockIdx.y;
     pdl_trigger();
     pdl_wait();
-    const int a = req_item_indptr[req], b = req_item_indptr[req + 1];
+    const int a = req_item_indptr[req], b = min(req_item_indptr[req + 1], max_items);
     if (b - a <= 1) return;
     const int kvh = qh / group, row = qh - kvh * group;
     float M = -INFINITY;
@@ -537,6 +549,29 @@ using namespace pie;
         if (!ok_) return (int)cudaErrorInvalidValue;                   \
     } while (0)
 
+// Status word of the current device for the bounds reports of the decode kernel (see
+// pie_set_status_word); null when the embedder registered none: the kernel then only clamps.
+namespace {
+constexpr int kStatusDevices = 64;
+int* g_status_word[kStatusDevices] = {};
+int* status_word() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStatusDevices) return nullptr;
+    return g_status_word[dev];
+}
+}  // namespace
+
+// Register a device int32 (on the current device) that kernels without a status argument set to a
+// PieKernelStatus code when they drop work; pass null to unregister.
+PIE_API int pie_set_status_word(int* word) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kStatusDevices) return (int)cudaErrorInvalidValue;
+    g_status_word[dev] = word;
+    return 0;
+}
+
 // Scratch sizes (in floats) a caller must provide for `max_items` work items.
 PIE_API long pie_decode_attn_scratch_floats(int max_items, int hq, int head_dim) {
     return (long)max_items * hq * head_dim + (long)max_items * hq;
@@ -566,17 +601,17 @@ PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, co
         launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
             (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
             item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
-            hkv, page_size, scale_log2, window_left, sinks_log2);
+            hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word());
     });
     int err = (int)cudaGetLastError();
     if (err || !run_merge) return err;
     dim3 grid(num_reqs, hq);
     if (head_dim == 128)
         launch_pdl(paged_decode_merge_kernel<128>, grid, dim3(128), 0, st, (const float*)o_part,
-                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2);
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2, max_items);
     else
         launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, (const float*)o_part,
-                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2);
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2, max_items);
     return (int)cudaGetLastError();
 }
 

@@ -31,7 +31,7 @@ from ..models.transformer import ForwardInputs, ParallelContext, Transformer
 from ..models.weights import random_weights, torch_dtype
 from .kv_cache import KVCache
 from .schema import (Capabilities, CopyRequest, ForwardRequest, ForwardResponse, SamplerKind,
-                     SamplerSpec, SlotOutput)
+                     SamplerSpec, SlotOutput, position_seed)
 
 
 def graph_buckets(max_requests: int) -> List[int]:
@@ -320,7 +320,15 @@ class TorchDriver:
             tk[j] = sp.top_k if sp.kind in (SamplerKind.TOP_K, SamplerKind.TOP_K_TOP_P) else 0
             tp[j] = sp.top_p if sp.kind in (SamplerKind.TOP_P, SamplerKind.TOP_K_TOP_P) else 1.0
             mp[j] = sp.min_p if sp.kind == SamplerKind.MIN_P else 0.0
-            seeds[j] = sp.seed if sp.seed else int(self.rng.integers(1, 2**62))
+            if sp.seed and sp.seed_final:
+                seeds[j] = sp.seed
+            elif sp.seed:
+                # a user-fixed seed is mixed with the position of the sampled row, as the cohort does
+                row = int(req.slot_row[i]) if req.slot_row is not None else -1
+                pos = int(req.positions[row]) if 0 <= row < len(req.positions) else 0
+                seeds[j] = int(position_seed(sp.seed, pos))
+            else:
+                seeds[j] = int(self.rng.integers(1, 2**62))
         return token_slots
 
     # ------------------------------------------------------------------ forward variants
@@ -684,9 +692,9 @@ class TorchDriver:
             toks[sel] = prev[step.src_row[sel]]
         last = (step.kv_lens - 1) % self.page_size + 1
         samplers = [SamplerSpec(SamplerKind.TOP_K_TOP_P, float(step.temperature[i]), int(step.top_k[i]),
-                                float(step.top_p[i]), 0.0, int(step.seeds[i])) if step.min_p[i] == 0 else
+                                float(step.top_p[i]), 0.0, int(step.seeds[i]), seed_final=True) if step.min_p[i] == 0 else
                     SamplerSpec(SamplerKind.MIN_P, float(step.temperature[i]), 0, 1.0, float(step.min_p[i]),
-                                int(step.seeds[i])) for i in range(r)]
+                                int(step.seeds[i]), seed_final=True) for i in range(r)]
         req = ForwardRequest(tokens=toks, positions=step.positions, qo_indptr=np.arange(r + 1, dtype=np.int32),
                              kv_page_indices=step.page_indices, kv_page_indptr=step.page_indptr,
                              kv_last_page_lens=last.astype(np.int32), slot_req=np.arange(r, dtype=np.int32),

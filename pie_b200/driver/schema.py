@@ -43,6 +43,7 @@ class SamplerSpec:
     min_p: float = 0.0
     seed: int = 0                    # 0 = the driver draws a fresh seed for this fire
     labels: Sequence[int] = ()       # LOGPROB / LOGPROBS candidates
+    seed_final: bool = False         # the seed is already the per-draw seed (set by the cohort's CPU path)
 
     @property
     def is_token(self) -> bool:
@@ -156,3 +157,16 @@ class Capabilities:
     @staticmethod
     def from_json(s: str) -> "Capabilities":
         return Capabilities(**json.loads(s))
+
+
+_SEED_MIX = np.int64(0x9E3779B97F4A7C15 - (1 << 64))
+
+
+def position_seed(seed, position):
+    """Per-draw sampler seed of a request that fixed its own seed: the user's seed mixed with the
+    position of the input token whose row is sampled, so that every decode step draws fresh noise
+    and both scheduler paths (per-request fires and the array-stepped cohort) produce the same
+    stream. Works on scalars and numpy arrays; never returns 0 (0 means "pick a seed per fire")."""
+    with np.errstate(over="ignore"):
+        out = (np.asarray(seed, dtype=np.int64) * _SEED_MIX) ^ (np.asarray(position, dtype=np.int64) * np.int64(0x632BE5AB))
+    return np.where(out == 0, 1, out)

@@ -38,6 +38,8 @@ def kernel_status(device=None) -> torch.Tensor:
     dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
     if dev not in _STATUS:
         _STATUS[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        with torch.cuda.device(dev):       # kernels without a status argument report here too
+            check(fn("pie_set_status_word")(ptr(_STATUS[dev])), "set_status_word")
     return _STATUS[dev]
 
 

@@ -43,11 +43,41 @@ def _round32(x: int) -> int:
     return -(-x // 32) * 32
 
 
-class StepRing:
-    """Single-writer (rank 0), multi-reader shared-memory mailbox with two payload slots."""
+def _pid_alive(pid: int) -> bool:
+    if pid <= 0:
+        return True          # not registered yet
+    try:
+        os.kill(pid, 0)
+    except ProcessLookupError:
+        return False
+    except PermissionError:
+        return True
+    try:        # a process that exited but was not reaped yet still answers signals
+        with open(f"/proc/{pid}/stat") as f:
+            return f.read().rsplit(")", 1)[1].split()[0] != "Z"
+    except (OSError, IndexError):
+        return True
 
-    def __init__(self, name: str, world: int, rank: int, cap: int = 48 << 20, create: bool = False):
+
+class StepRing:
+    """Single-writer (rank 0), multi-reader shared-memory mailbox with two payload slots.
+
+    Memory ordering: the writer stores the payload, then the header words, then the sequence word,
+    all as plain stores through numpy; readers poll the sequence word and then read the rest. That
+    is only ordered on hosts with total store order (x86-64, which is what B200 HGX boxes are); an
+    Arm host (Grace) would need a release store / acquire load of the sequence word.
+
+    Liveness: every rank registers its pid in the header. A writer that waits for a follower's
+    acknowledgement, and a reader that waits for the next step, back off to short sleeps, check that
+    the other side's process still exists, and give up after `ack_timeout_s` / the receive timeout.
+    """
+
+    def __init__(self, name: str, world: int, rank: int, cap: int = 48 << 20, create: bool = False,
+                 ack_timeout_s: Optional[float] = None):
         self.world, self.rank, self.cap = world, rank, cap
+        if ack_timeout_s is None:
+            ack_timeout_s = float(os.environ.get("PIE_TP_ACK_TIMEOUT_S", "120"))
+        self.ack_timeout_s = ack_timeout_s
         size = _HDR_WORDS * 8 * 2 + 2 * cap
         self.shm = shared_memory.SharedMemory(name=name, create=create, size=size)
         self.hdr = np.ndarray((2, _HDR_WORDS), dtype=np.int64, buffer=self.shm.buf)
@@ -56,18 +86,26 @@ class StepRing:
         self.payload = [np.ndarray((cap,), dtype=np.uint8, buffer=self.shm.buf, offset=_HDR_WORDS * 16 + i * cap)
                         for i in range(2)]
         self.seq = 0
+        self.hdr[0, 48 + rank] = os.getpid()
 
-    # header words: 0 seq, 1 kind, 2 nbytes, 3..10 meta, 32.. acks per rank
+    # header words: 0 seq, 1 kind, 2 nbytes, 3..10 meta; slot-0 header also holds 32+r acks and 48+r pids
     def publish(self, kind: int, data: Optional[np.ndarray], meta=()) -> None:
         self.seq += 1
         slot = self.seq & 1
         h = self.hdr[slot]
         # the slot was last used by seq-2: every follower must have consumed it
-        deadline = time.time() + 120
+        deadline = time.time() + self.ack_timeout_s
         for r in range(1, self.world):
+            spins = 0
             while self.hdr[0, 32 + r] < self.seq - 2:
-                if time.time() > deadline:
-                    raise RuntimeError(f"tensor-parallel follower {r} stopped consuming steps")
+                spins += 1
+                if spins > 2000:
+                    time.sleep(0.0001)
+                    if spins % 256 == 0:
+                        if not _pid_alive(int(self.hdr[0, 48 + r])):
+                            raise RuntimeError(f"tensor-parallel follower {r} exited")
+                        if time.time() > deadline:
+                            raise RuntimeError(f"tensor-parallel follower {r} stopped consuming steps")
         n = 0 if data is None else data.nbytes
         if n > self.cap:
             raise ValueError("step payload exceeds the control ring capacity")
@@ -88,8 +126,11 @@ class StepRing:
             spins += 1
             if spins > 2000:
                 time.sleep(0.00005)
-                if time.time() > deadline:
-                    raise TimeoutError("no step from rank 0")
+                if spins % 512 == 0:
+                    if not _pid_alive(int(self.hdr[0, 48])):
+                        raise TimeoutError("rank 0 exited")
+                    if time.time() > deadline:
+                        raise TimeoutError("no step from rank 0")
         self.seq = want
         n = int(h[2])
         return int(h[1]), self.payload[slot][:n], [int(x) for x in h[3:11]]

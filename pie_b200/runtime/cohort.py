@@ -27,11 +27,11 @@ from typing import Callable, Dict, List, Optional, Sequence
 import numpy as np
 
 from ..driver.executor import CohortStep
-from ..driver.schema import SamplerKind, SamplerSpec
+from ..driver.schema import SamplerKind, SamplerSpec, position_seed
 from .context import ContextError, ContextManager
 from .inference import Future
 
-_MIX = np.int64(0x9E3779B97F4A7C15 - (1 << 64))
+
 
 
 class Stream:
@@ -209,10 +209,8 @@ class DecodeCohort:
         np.cumsum(used, out=indptr[1:])
         cols = np.arange(self.maxp, dtype=np.int32)[None, :]
         indices = self.table[:n][cols < used[:, None]]
-        seeds = np.where(self.seed[:n] != 0,
-                         (self.seed[:n] * _MIX) ^ (self.pos[:n].astype(np.int64) * np.int64(0x632BE5AB)),
+        seeds = np.where(self.seed[:n] != 0, position_seed(self.seed[:n], self.pos[:n]),
                          self.rng.integers(1, 2**62, n, dtype=np.int64))
-        seeds = np.where(seeds == 0, 1, seeds)
         step = CohortStep(r=n, host_tokens=self.host_tok[:n].copy(), src_row=self.prev_row[:n].copy(),
                           positions=self.pos[:n].copy(), kv_lens=kv_after.astype(np.int32), page_indptr=indptr,
                           page_indices=indices, temperature=self.temp[:n].copy(), top_k=self.topk[:n].copy(),

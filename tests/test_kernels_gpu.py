@@ -129,6 +129,50 @@ def test_paged_decode_attention(d, hq, hkv):
     close(out, want, 2e-2)
 
 
+def test_paged_decode_attention_clamps_work_count():
+    """A work count in device memory larger than the scratch was sized for (a stale value on a graph
+    replay, an embedder's mistake) must not write past the scratch: the kernel drops the extra items,
+    reports PIE_ERR_BOUNDS and the requests whose items are all covered still come out right."""
+    d, hq, hkv, page = 128, 32, 8, 16
+    kv_lens = np.array([300, 17, 1000, 2305], dtype=np.int32)
+    r = len(kv_lens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=61)
+    q = bf(r, hq, d, seed=62)
+    item_req, st, en, iptr = ops.plan_decode_items(kv_lens, hkv, target_ctas=64, min_chunk=256)
+    covered = int(iptr[2])                       # every item of requests 0 and 1
+    assert covered < len(item_req) and iptr[3] > covered + 1
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    need = ops.decode_scratch_floats(covered, hq, d)
+    big = torch.full((need + 65536,), 777.0, device=DEV)
+    status = ops.kernel_status(DEV)
+    status.zero_()
+    plan = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
+                          torch.tensor([len(item_req)], dtype=torch.int32, device=DEV), big, covered, r, 64, page)
+    scale = 1 / math.sqrt(d)
+    out = ops.paged_decode_attention(q, kv, plan, scale)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5               # PIE_ERR_BOUNDS
+    with pytest.raises(ops._lib.KernelLibraryError):
+        ops.check_kernel_status(DEV)
+    assert int(status.item()) == 0
+    assert bool((big[need:] == 777.0).all())     # nothing written past the scratch
+    qo = np.arange(r + 1, dtype=np.int32)
+    want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale)
+    close(out[:2], want[:2], 2e-2)
+    # an item that names a request outside the batch is skipped and reported as well
+    bad = item_req.copy()
+    bad[-1] = r + 5
+    plan = ops.DecodePlan(t(pages), t(indptr), t(bad), t(st), t(en), t(iptr),
+                          torch.tensor([len(item_req)], dtype=torch.int32, device=DEV),
+                          torch.empty(ops.decode_scratch_floats(len(item_req), hq, d), device=DEV),
+                          len(item_req), r, 64, page)
+    out = ops.paged_decode_attention(q, kv, plan, scale)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5
+    status.zero_()
+    close(out[:3], want[:3], 2e-2)
+
+
 @pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (64, 16, 2)])
 def test_attention_sinks_and_per_call_window(d, hq, hkv):
     """Per-head sink logits in the softmax denominator (decode: single-item and merged requests;
