@@ -2,7 +2,10 @@
 """Headline benchmark: decode output tokens/s of Llama-3.1-8B-architecture serving (bf16,
 random-init weights, synthetic random-token prompts), 512 concurrent text-completion
 inferlets, prompts uniform in [128, 2048], 256 output tokens, temperature 1.0 / top-p 0.9,
-KV page size 16, tensor-parallel over --gpus GPUs of one node.
+KV page size 16. With --gpus N > 1 the model runs as ONE tensor-parallel group over the N GPUs
+(fused peer-memory kernels: GEMM -> reduce-scatter epilogue, owner reduce + norm + push all-gather,
+gated GEMM loads, vocabulary-sharded lm_head with a cross-rank sampler); `--parallelism dp` runs N
+independent replicas instead and is labelled as such in the output.
 
     python bench.py --gpus 1 --steps 64 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -44,9 +47,9 @@ def parse_args():
     ap.add_argument("--max-tokens", type=int, default=16384)
     ap.add_argument("--device-loop", default="pipelined", choices=["pipelined", "staged"],
                     help="pipelined: decode_async with device-fed tokens (all N); staged: inputs pre-staged on the device (N=1)")
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
-                    help="N>1: dp = one replica per GPU, the inferlets spread over them (the serving topology "
-                         "for a model that fits one GPU); tp = one tensor-parallel group")
+    ap.add_argument("--parallelism", default="tp", choices=["dp", "tp"],
+                    help="N>1: tp = one tensor-parallel group over all GPUs (default, the named configuration); "
+                         "dp = one replica per GPU, the inferlets spread over them")
     ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"],
                     help="fused: GEMM epilogue reduce-scatter + push all-gather over peer memory; nccl: GEMM + all-reduce")
     return ap.parse_args()
