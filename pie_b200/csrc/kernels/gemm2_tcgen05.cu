@@ -52,7 +52,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t crank = cluster_ctarank();
     const bool leader = crank == 0;
-    const bool relay = (sk.dbg & 4) != 0;
+    const bool relay = PIE_DIAG(sk.dbg & 4) != 0;
     const int pid = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int tiles_m = (M + PAIR_M - 1) / PAIR_M;
     const int tiles_n = (N + BN - 1) / BN;
@@ -89,12 +89,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             tma_prefetch_desc(&tma_b);
             uint32_t it = 0;
             bool ok = true;
-            if (tp.gated) ok = ag_gate_wait(tp, status);
+            uint32_t seen = 0;
             const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
             SegmentWalk walk(sk.enabled != 0, num_tiles, num_kb, pid, npairs);
             Segment seg;
             while (ok && walk.next(seg)) {
                 const int m_blk = seg.tile % tiles_m, n_blk = seg.tile / tiles_m;
+                if (tp.gated && !ag_gate_wait_rows(tp, status, m_blk * PAIR_M + (int)crank * GEMM_BM, GEMM_BM, seen)) {
+                    ok = false;
+                    break;
+                }
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -103,13 +107,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                     const int a_row = m_blk * PAIR_M + (int)crank * GEMM_BM;
                     const int b_row = n_blk * BN + (int)crank * (BN / 2);
                     if (relay) {
-                        if (sk.dbg & 2) { mbar_arrive(full_bar(s)); continue; }
+                        if (PIE_DIAG(sk.dbg & 2)) { mbar_arrive(full_bar(s)); continue; }
                         mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
                         tma_load_2d(a_dst, &tma_a, full_bar(s), kb * GEMM_BK, a_row);
                         tma_load_2d(a_dst + Cfg::A_BYTES, &tma_b, full_bar(s), kb * GEMM_BK, b_row);
                     } else {
                         // both CTAs' loads complete on the leader's barrier, armed for the pair's bytes
-                        if (sk.dbg & 2) { if (leader) mbar_arrive(full_bar(s)); continue; }
+                        if (PIE_DIAG(sk.dbg & 2)) { if (leader) mbar_arrive(full_bar(s)); continue; }
                         if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
                         const uint32_t lbar = leader_full0 + 8u * s;
                         tma_load_2d_pair(a_dst, &tma_a, lbar, kb * GEMM_BK, a_row);
@@ -160,7 +164,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                     const uint32_t a_addr = tiles + s * Cfg::STAGE_BYTES;
                     const uint64_t adesc = make_smem_desc_sw128(a_addr);
                     const uint64_t bdesc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
-                    if (!(sk.dbg & 1)) {
+                    if (!PIE_DIAG(sk.dbg & 1)) {
 #pragma unroll
                         for (int k = 0; k < GEMM_BK / 16; ++k)
                             umma_bf16_2cta(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, ((kb - seg.kb0) | k) != 0);
@@ -284,7 +288,11 @@ using namespace pie;
 extern "C" int pie_make_tma_2d_bf16(CUtensorMap* map, const void* ptr, long rows, long cols, long ld, int box_rows);
 
 static int g_pair_dbg = 0;
+#ifdef PIE_GEMM_DIAG
 extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_debug(int bits) { g_pair_dbg = bits; return 0; }
+#else
+extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_debug(int) { return (int)cudaErrorNotSupported; }
+#endif
 
 template <int BN, int EPI>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M, int N,

@@ -25,8 +25,9 @@ constexpr int TP_MAX_RANKS = 8;
 
 // Tensor-parallel side channel of the fused kernels. All pointers are device addresses valid
 // on THIS GPU; peer_* entries are peer-mapped (NVLink) addresses of the same buffer on rank i.
-//   gated loads : before its first TMA load the producer waits until every rank has pushed its
-//                 rows of the activation (ag_flags[src] >= *ag_epoch, written by peers).
+//   gated loads : before the TMA load of an activation tile the producer waits until the ranks that
+//                 own the tile's rows have pushed them (ag_flags[src] >= *ag_epoch, written by peers);
+//                 with rows_per_rank == 0 (an activation that is not the gathered buffer) every rank.
 //   EPI_RS      : the epilogue stores each accumulator row into the receive buffer of the rank
 //                 that owns the row (rows_per_rank consecutive rows per rank, a multiple of 32),
 //                 at [this rank][row within owner][col]; the last epilogue warp of the grid
@@ -52,10 +53,13 @@ struct StreamKArgs {
     float* ws;
     int* cnt;
     int enabled;
-    int dbg;   // pair kernel diagnostics: 1 skip the MMAs, 2 skip the loads, 4 relay instead of direct signalling
-    unsigned long long* trace;   // optional [grid][8] globaltimer stamps of the kernel's phases (profiling aid)
+    // Diagnostics, compiled in only with -DPIE_GEMM_DIAG (a production build ignores both fields):
+    int dbg;   // 1 skip the MMAs, 2 skip the loads, 4 relay instead of direct signalling (results are meaningless)
+    unsigned long long* trace;   // [grid][8] globaltimer stamps of the kernel's phases
 };
 
+#ifdef PIE_GEMM_DIAG
+#define PIE_DIAG(expr) (expr)
 __device__ __forceinline__ void trace_stamp(unsigned long long* trace, int slot) {
     if (trace) {
         unsigned long long t;
@@ -63,6 +67,10 @@ __device__ __forceinline__ void trace_stamp(unsigned long long* trace, int slot)
         trace[blockIdx.x * 8 + slot] = t;
     }
 }
+#else
+#define PIE_DIAG(expr) 0
+__device__ __forceinline__ void trace_stamp(unsigned long long*, int) {}
+#endif
 
 struct Segment {
     int tile, kb0, kb1;
@@ -309,6 +317,35 @@ __device__ __forceinline__ void rs_publish_arrival(const TpArgs& tp, int total) 
         __threadfence_system();
         for (int p = 0; p < tp.world; ++p) *reinterpret_cast<volatile int*>(tp.peer_rs_flags[p] + tp.rank) = e;
     }
+}
+
+// All-gather gate for the rows [row0, row0 + nrows) of the gathered activation: spin (bounded) until
+// the ranks that own those rows (rows_per_rank consecutive rows each; every rank when rows_per_rank
+// is 0) have pushed for this rank's epoch. `seen` is the caller's bit set of owners already confirmed,
+// so a tile whose owners were seen costs nothing and rank p's rows are consumed as soon as p pushed.
+__device__ __forceinline__ bool ag_gate_wait_rows(const TpArgs& tp, int* status, int row0, int nrows, uint32_t& seen) {
+    int o0 = 0, o1 = tp.world - 1;
+    if (tp.rows_per_rank > 0) {
+        o0 = min(tp.world - 1, row0 / tp.rows_per_rank);
+        o1 = min(tp.world - 1, (row0 + nrows - 1) / tp.rows_per_rank);
+    }
+    const uint32_t need = ((2u << o1) - 1u) & ~((1u << o0) - 1u);
+    if ((need & ~seen) == 0u) return true;
+    const int e = *reinterpret_cast<const volatile int*>(tp.ag_epoch);
+    const long long t0 = clock64();
+    for (int src = o0; src <= o1; ++src) {
+        if (seen & (1u << src)) continue;
+        while (*reinterpret_cast<const volatile int*>(tp.ag_flags + src) < e) {
+            if (*reinterpret_cast<volatile int*>(status) != 0 || clock64() - t0 > 1500000000ll) {
+                atomicCAS(status, 0, PIE_ERR_WAIT_PEER);
+                return false;
+            }
+        }
+    }
+    seen |= need;
+    __threadfence_system();
+    asm volatile("fence.proxy.async;\n" ::: "memory");
+    return true;
 }
 
 // All-gather gate: spin (bounded) until every rank's push flag reached this rank's epoch.

@@ -113,10 +113,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             bool dep_ready = false;
             int pending = 0;
             int q_kb[STAGES], q_row[STAGES], q_stage[STAGES];
+            uint32_t seen = 0;    // owners whose push this producer has observed
             auto resolve = [&]() {
                 pdl_wait();
-                if (tp.gated) ok = ag_gate_wait(tp, status);
-                for (int j = 0; j < pending && ok; ++j)
+                for (int j = 0; j < pending && ok; ++j) {
+                    if (tp.gated) ok = ag_gate_wait_rows(tp, status, q_row[j], SWAPPED ? bn : GEMM_BM, seen);
+                    if (!ok) break;
 #pragma unroll
                     for (int u = 0; u < Cfg::KSUB; ++u) {
                         if (SWAPPED)
@@ -126,6 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             tma_load_2d(tiles + q_stage[j] * Cfg::STAGE_BYTES + u * Cfg::A_SUB, &tma_a, full_bar(q_stage[j]),
                                         q_kb[j] * GEMM_KSTEP + u * GEMM_BK, q_row[j]);
                     }
+                }
                 pending = 0;
                 dep_ready = true;
             };
@@ -150,7 +153,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (!ok) break;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, status, PIE_ERR_WAIT_TMA)) { ok = false; break; }
                     const uint32_t a_dst = tiles + s * Cfg::STAGE_BYTES;
-                    if (sk.dbg & 6) {   // diagnostics: 2 = no activation loads, 4 = no weight loads, 6 = neither
+                    if (PIE_DIAG(sk.dbg & 6)) {   // diagnostics: 2 = no activation loads, 4 = no weight loads, 6 = neither
                         const uint32_t tx = ((sk.dbg & 2) ? 0u : Cfg::A_BYTES) + ((sk.dbg & 4) ? 0u : (uint32_t)bn * (GEMM_KSTEP * 2));
                         mbar_arrive_expect_tx(full_bar(s), tx);
                         for (int u = 0; u < Cfg::KSUB; ++u) {
@@ -158,6 +161,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             if (!(sk.dbg & 2)) tma_load_2d(a_dst + u * Cfg::A_SUB, &tma_a, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, m_blk * GEMM_BM);
                         }
                         continue;
+                    }
+                    if (dep_ready && tp.gated &&
+                        !ag_gate_wait_rows(tp, status, SWAPPED ? b_row : m_blk * GEMM_BM, SWAPPED ? bn : GEMM_BM, seen)) {
+                        ok = false;
+                        break;
                     }
                     mbar_arrive_expect_tx(full_bar(s), stage_tx);
                     // the operand that holds the weights goes first; the activation operand (tma_a, or
@@ -207,7 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (it == 0) trace_stamp(sk.trace, 2);
                     tc_fence_after();
                     const uint32_t a_addr = tiles + s * Cfg::STAGE_BYTES;
-                    if (!(sk.dbg & 1)) {
+                    if (!PIE_DIAG(sk.dbg & 1)) {
 #pragma unroll
                         for (int u = 0; u < Cfg::KSUB; ++u) {
                             const uint64_t adesc = make_smem_desc_sw128(a_addr + u * Cfg::A_SUB);
@@ -404,15 +412,21 @@ PIE_API int pie_gemm_set_workspace(int device, float* ws, long ws_floats, int* c
     return 0;
 }
 
-// Profiling aid: when set, the single-CTA kernel writes 8 globaltimer stamps per CTA
-// (start, set-up done, first tile landed, last MMA issued, first/last accumulator ready,
-// epilogue done, all roles done) into trace[grid][8].
+// Diagnostics, only in a build with -DPIE_GEMM_DIAG (otherwise both setters answer
+// cudaErrorNotSupported and the kernels carry no diagnostic code).
+// trace: the single-CTA kernel writes 8 globaltimer stamps per CTA (start, set-up done, first tile
+// landed, last MMA issued, first/last accumulator ready, epilogue done, all roles done) into
+// trace[grid][8]. debug bits (results are then meaningless): 1 skips the MMAs, 2 the activation
+// loads, 4 the weight loads.
 static unsigned long long* g_gemm_trace = nullptr;
 static int g_gemm_dbg = 0;
-// Diagnostics of the single-CTA kernel (results are then meaningless): 1 skips the MMAs,
-// 2 the activation loads, 4 the weight loads.
+#ifdef PIE_GEMM_DIAG
 PIE_API int pie_gemm_set_debug(int bits) { g_gemm_dbg = bits; return 0; }
 PIE_API int pie_gemm_set_trace(unsigned long long* trace) { g_gemm_trace = trace; return 0; }
+#else
+PIE_API int pie_gemm_set_debug(int) { return (int)cudaErrorNotSupported; }
+PIE_API int pie_gemm_set_trace(unsigned long long*) { return (int)cudaErrorNotSupported; }
+#endif
 
 int g_pie_pdl = 0;
 // 1: launch the library's kernels with programmatic stream serialisation, so that a kernel's

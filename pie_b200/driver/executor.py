@@ -364,8 +364,11 @@ class TorchDriver:
         """Capture the decode graphs of the bucket lattice ahead of the first request, so that no fire
         pays for a capture (the reference pre-captures its lattice at start-up too:
         driver/cuda/src/entry.cpp, executor/forward_graph.hpp:63-91). The capture runs on a plan
-        without attention work or KV writes. Returns the number of graphs captured."""
-        if not self.use_graphs or self.par.tp_size > 1:     # tensor-parallel ranks capture in step, on demand
+        without attention work or KV writes. Returns the number of graphs captured.
+        Under tensor parallelism EVERY rank must call this at the same point of its start-up (before
+        the followers enter their loop): the warm-up forwards of a capture run the fused kernels,
+        which wait for their peers."""
+        if not self.use_graphs:
             return 0
         self._bind_thread()
         s, n = self.slab, 0
@@ -495,10 +498,7 @@ class TorchDriver:
             lg = logits[:k] if contiguous else logits[torch.from_numpy(rows.astype(np.int64)).to(logits.device)]
             mask_bits, mask_row = self._logit_mask_rows(req, token_slots)
             if self.cuda:
-                s = self.slab
-                ops.sample(lg, s.d("temperature", k).view(torch.float32), s.d("top_k", k),
-                           s.d("top_p", k).view(torch.float32), s.d("min_p", k).view(torch.float32),
-                           s.d("seeds", k, torch.int64), mask_bits, mask_row, out=self.sampled)
+                self._sample(lg, k, mask_bits, mask_row, self.sampled)
                 self.sampled_host[:k].copy_(self.sampled[:k], non_blocking=True)
                 self.status_host.copy_(ops.kernel_status(self.device), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
@@ -513,6 +513,16 @@ class TorchDriver:
             self._probes(req, logits, slot_logit_row, probe_slots, out_slots)
         all_tokens = tokens if len(token_slots) == nslots else None
         return ForwardResponse(slots=out_slots, tokens=all_tokens)
+
+    def _sample(self, lg, k: int, mask_bits, mask_row, out):
+        """Token sampler over `k` logit rows: the single-GPU kernel, or under fused tensor
+        parallelism the vocabulary-sharded one (every rank holds a slice of each row)."""
+        s = self.slab
+        args = (s.d("temperature", k).view(torch.float32), s.d("top_k", k), s.d("top_p", k).view(torch.float32),
+                s.d("min_p", k).view(torch.float32), s.d("seeds", k, torch.int64), mask_bits, mask_row)
+        if self.model.sharded_logits:
+            return self.par.comm.sample_sharded(lg, *args, out=out)
+        return ops.sample(lg, *args, out=out)
 
     def _logit_mask_rows(self, req, token_slots):
         if not req.logit_masks or not any(m is not None for m in req.logit_masks):
@@ -544,6 +554,8 @@ class TorchDriver:
     def _probes(self, req, logits, slot_logit_row, probe_slots, out_slots):
         rows = torch.from_numpy(slot_logit_row[probe_slots].astype(np.int64)).to(logits.device)
         lg = logits[rows]
+        if self.model.sharded_logits:       # probes read whole rows: gather the few rows they name
+            lg = self.par.comm.all_gather_logits(lg)
         stats = ops.row_stats(lg.contiguous()).float().cpu().numpy()
         for j, i in enumerate(probe_slots):
             sp = req.slot_samplers[i]
@@ -675,9 +687,7 @@ class TorchDriver:
         else:
             logits = self.model.forward(self._forward_inputs_decode(rb), self.kv.data)
             self.stats["eager"] += 1
-        ops.sample(logits[:r], s.d("temperature", r).view(torch.float32), s.d("top_k", r),
-                   s.d("top_p", r).view(torch.float32), s.d("min_p", r).view(torch.float32),
-                   s.d("seeds", r, torch.int64), None, None, out=cur)
+        self._sample(logits[:r], r, None, None, cur)
         self.cohort_host[parity & 1][:r].copy_(cur[:r], non_blocking=True)
         self.status_host.copy_(ops.kernel_status(self.device), non_blocking=True)
 
@@ -747,9 +757,7 @@ class TorchDriver:
             s.d("tokens", r).copy_(self.sampled[:r], non_blocking=True)
         g = self.graphs[st["rb"]]
         g.graph.replay()
-        ops.sample(g.logits[:r], s.d("temperature", r).view(torch.float32), s.d("top_k", r),
-                   s.d("top_p", r).view(torch.float32), s.d("min_p", r).view(torch.float32),
-                   s.d("seeds", r, torch.int64), None, None, out=self.sampled)
+        self._sample(g.logits[:r], r, None, None, self.sampled)
 
     def launches_per_decode_step(self, rb: int) -> int:
         """Kernels of this library launched by one decode step of bucket `rb`: the captured

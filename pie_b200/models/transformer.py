@@ -210,14 +210,19 @@ class Transformer:
         """lm_head on the requested rows only ('compact logit rows')."""
         rows = h if fi.logit_rows is None else ops.gather_rows(h, fi.logit_rows)
         if self._fused_tp():
-            # h is already final-normalised and gathered; every rank computes its vocabulary slice
-            local = self.par.comm.gemm_gated(self.w["lm_head"], rows.shape[0], x=rows)
-            return self.par.comm.all_gather_logits(local)
+            # h is already final-normalised and gathered; every rank computes its vocabulary slice and
+            # keeps it: token samplers run sharded (TPComm.sample_sharded), only probes gather
+            return self.par.comm.gemm_gated(self.w["lm_head"], rows.shape[0], x=rows)
         x = ops.rmsnorm(rows, self.w["final_norm"], self.cfg.rms_norm_eps)
         y = self._gemm(x, self.w["lm_head"])
         if self.par.tp_size > 1 and self.par.comm is not None:
             y = self.par.comm.all_gather_logits(y)
         return y
+
+    @property
+    def sharded_logits(self) -> bool:
+        """True when `logits` returns this rank's vocabulary slice [rows, V / tp] instead of [rows, V]."""
+        return self._fused_tp()
 
     def forward(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
         return self.logits(self.forward_hidden(fi, kv_cache), fi)

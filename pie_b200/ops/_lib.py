@@ -43,6 +43,8 @@ _SIGNATURES = {
     "pie_prefill_attn_tc_supported": [i32, i32, i32, i32],
     "pie_paged_prefill_attn_tc": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, i32, p, p, p],
     "pie_sample": [p, i64, i32, i32, p, p, p, p, p, p, p, i32, p, p],
+    "pie_tp_sample_max_grid": [i32],
+    "pie_tp_sample": [p, p, i64, i32, p, p, p, p, p, p, p, i32, p, i32, p],
     "pie_row_stats": [p, i64, i32, i32, p, p],
     "pie_feed_tokens": [p, p, p, i32, p],
     "pie_gemm_set_workspace": [i32, p, i64, p, i32],

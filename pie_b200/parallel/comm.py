@@ -173,7 +173,14 @@ class TPComm:
         self.off_recv, self.off_xfull, self.off_flags = 0, nb_act, 2 * nb_act
         self.ar_cap = 512 * 1024                       # bf16 elements per one-shot all-reduce slot (1 MiB)
         self.off_ar = 2 * nb_act + 4096
-        total = self.off_ar + 2 * self.world * self.ar_cap * 2
+        # mailboxes + flags of the vocabulary-sharded sampler (one mailbox per resident CTA)
+        self.ts_grid = max(1, min(1024, _lib.declare("pie_tp_sample_max_grid", [C.c_int], C.c_int)(
+            ops.num_sms(self.device))))
+        self.off_ts_box = self.off_ar + 2 * self.world * self.ar_cap * 2
+        ts_box = _lib.declare("pie_tp_sample_mailbox_bytes", [C.c_int, C.c_int], C.c_long)(self.ts_grid, self.world)
+        self.off_ts_flag = self.off_ts_box + ts_box
+        total = self.off_ts_flag + _lib.declare("pie_tp_sample_flag_bytes", [C.c_int, C.c_int], C.c_long)(
+            self.ts_grid, self.world)
         self.sym = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.sym.zero_()
         torch.cuda.synchronize(self.device)
@@ -214,6 +221,15 @@ class TPComm:
                       self.ar_cap), "tp_fill_ar_args")
         self._ar_small = _lib.declare("pie_tp_allreduce_small", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int,
                                                                  C.c_void_p])
+        # vocabulary-sharded sampler
+        self.vocab_local = driver.model.w["lm_head"].shape[0]
+        self.ts_seq = torch.zeros(self.ts_grid, dtype=torch.int32, device=self.device)
+        self.ts_blob = C.create_string_buffer(_lib.declare("pie_tp_sample_args_size", [], C.c_int)())
+        fill_ts = _lib.declare("pie_tp_sample_fill_args", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                           C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong])
+        check(fill_ts(self.ts_blob, arr_p(*[b + self.off_ts_box for b in base]),
+                      arr_p(*[b + self.off_ts_flag for b in base]), self.ts_seq.data_ptr(), status.data_ptr(), W,
+                      self.rank, self.vocab_local, self.ts_grid, 0), "tp_sample_fill_args")
         self._ag_flags_local = ag_flags[self.rank]
         self._ag_epoch_ptr = lc + 12
         self._gemm_tp = _lib.declare("pie_gemm_bf16_tp", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
@@ -269,7 +285,8 @@ class TPComm:
         return out
 
     def gemm_gated(self, w, n: int, swiglu: bool = False, x: Optional[torch.Tensor] = None):
-        """y = gathered_activation[:n] @ w.T (waits inside the kernel for every rank's push)."""
+        """y = gathered_activation[:n] @ w.T. The kernel's loads of a row tile wait for the push of the
+        ranks that own those rows (for an explicit `x`, which is not laid out by owner, for every rank)."""
         if isinstance(w, ops.Fp8Linear):
             a = self.wait_gathered(n) if x is None else x
             nn = w.shape[0]
@@ -279,7 +296,8 @@ class TPComm:
         nn = w.shape[0]
         out = torch.empty(n, nn // 2 if swiglu else nn, dtype=torch.bfloat16, device=self.device)
         check(self._gemm_tp(ptr(a), ptr(w), ptr(out), n, nn, a.shape[1], a.stride(0), w.stride(0), out.stride(0),
-                            ops.EPI_SWIGLU if swiglu else ops.EPI_STORE, self.tp_blob, 32, 1, 0,
+                            ops.EPI_SWIGLU if swiglu else ops.EPI_STORE, self.tp_blob,
+                            self.rows_per_rank(n) if x is None else 0, 1, 0,
                             ptr(self._status), self._sms, stream_ptr()), "gemm_gated")
         return out
 
@@ -296,6 +314,19 @@ class TPComm:
         check(self._wait_ag(self._ag_flags_local, self._ag_epoch_ptr, self.world, ptr(self._status), stream_ptr()),
               "tp_wait_ag")
         return self.xfull[:n]
+
+    def sample_sharded(self, local_logits: torch.Tensor, temperature, top_k, top_p, min_p, seeds, mask_bits,
+                       mask_row, out: torch.Tensor) -> torch.Tensor:
+        """One token per row from logits that are sharded over the ranks' vocabulary slices
+        (`local_logits` is this rank's [rows, V / world] slice). Every rank calls it in step with
+        the same parameters and receives the same tokens; a few words per row cross NVLink."""
+        rows, v = local_logits.shape
+        assert v == self.vocab_local and local_logits.stride(1) == 1
+        mask_words = mask_bits.shape[1] if mask_bits is not None else 0
+        check(_lib.fn("pie_tp_sample")(self.ts_blob, ptr(local_logits), local_logits.stride(0), rows, ptr(temperature),
+                                       ptr(top_k), ptr(top_p), ptr(min_p), ptr(seeds), ptr(mask_bits), ptr(mask_row),
+                                       mask_words, ptr(out), self._sms, stream_ptr()), "tp_sample")
+        return out
 
     # ------------------------------------------------------------------ NCCL paths
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:

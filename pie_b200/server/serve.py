@@ -85,6 +85,9 @@ def build_drivers(m: ModelSection):
         drv = TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, par=par, gemm_backend=d.gemm,
                           use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization)
         comm.attach(drv)
+        if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
+            n = drv.precapture_graphs()      # every rank is here: the warm-up forwards run in lock step
+            log.info("model %s rank %d: %d decode graphs captured ahead of time", m.name, rank, n)
         return [drv], cfg, tok, comm
     for g in groups:
         dev = torch.device("cuda", g[0])

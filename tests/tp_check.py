@@ -109,12 +109,40 @@ def main():
         r_ref = ref.fire_batch(fold(mk(), 16))
         compare(f"decode{step}", r_tp, r_ref)
         toks = [int(np.frombuffer(s.logits, dtype=np.float32).argmax()) for s in r_ref.slots]
+    # vocabulary-sharded sampler: one more decode step with a raw-logits probe and five token samplers
+    # per request on the same row; the tokens must equal the single-GPU sampler's on the gathered logits
+    from pie_b200 import ops
+    from pie_b200.driver.schema import position_seed
+    samplers = [SamplerSpec.greedy(), SamplerSpec(SamplerKind.TOP_P, 1.0, 0, 0.9, 0.0, 11),
+                SamplerSpec(SamplerKind.TOP_K, 0.8, 50, 1.0, 0.0, 12), SamplerSpec(SamplerKind.MIN_P, 1.0, 0, 1.0, 0.02, 13),
+                SamplerSpec(SamplerKind.MULTINOMIAL, 1.3, 0, 1.0, 0.0, 14)]
+    step = 2
+    mk = [PendingRequest(i, [t], [len(p) + step], pg, len(p) + step, [(0, raw)] + [(0, sp) for sp in samplers])
+          for i, (t, p, pg) in enumerate(zip(toks, prompts, pages))]
+    r_tp = drv.fire_batch(fold(mk, 16))
+    sample_ok = True
+    per = 1 + len(samplers)
+    for i in range(len(prompts)):
+        lg = torch.from_numpy(np.frombuffer(r_tp.slots[i * per].logits, dtype=np.float32).copy()).to(dev)
+        lg = lg.to(torch.bfloat16).reshape(1, -1).contiguous()
+        for j, sp in enumerate(samplers):
+            f = lambda v, dt: torch.tensor([v], dtype=dt, device=dev)
+            want = ops.sample(lg, f(sp.temperature, torch.float32),
+                              f(sp.top_k if sp.kind == SamplerKind.TOP_K else 0, torch.int32),
+                              f(sp.top_p if sp.kind == SamplerKind.TOP_P else 1.0, torch.float32),
+                              f(sp.min_p if sp.kind == SamplerKind.MIN_P else 0.0, torch.float32),
+                              f(int(position_seed(sp.seed, len(prompts[i]) + step)) if sp.seed else 1, torch.int64))
+            got = r_tp.slots[i * per + 1 + j].token
+            if int(want.item()) != got:
+                sample_ok = False
+                report.setdefault("sample_mismatch", []).append([i, j, int(want.item()), got])
+    report["sharded_sampling"] = bool(drv.model.sharded_logits)
+    report["sample_ok"] = sample_ok
     comm.stop_followers()
     torch.cuda.synchronize()
-    from pie_b200 import ops
     ops.check_kernel_status(dev)
     report["allreduce_small_ok"] = ar_ok
-    report["ok"] = ar_ok and all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
+    report["ok"] = ar_ok and sample_ok and all(c["cos"] > 0.995 and c["top5_overlap"] >= 3 for c in report["checks"])
     report["graph_replays"] = drv.stats["graph_replays"]
     print(json.dumps(report), flush=True)
     comm.close()
