@@ -15,7 +15,11 @@ Rank 0 prints ONE JSON line. `value` is device-timed (CUDA events, max over rank
 exactly --steps decode steps of the whole 512-request batch; `e2e.value` is the same metric
 through the engine's public API (inferlets -> scheduler -> driver) with per-step pinned-host
 H2D of the inputs and D2H of the sampled tokens. `--impl reference` reports why the reference
-cannot run here.
+cannot run here. `--impl library` runs the library comparator alone (cuBLAS GEMMs, FlashInfer paged
+attention / norms / RoPE / sampling, NCCL all-reduce twice per layer with rank-0 logits, CUDA graphs:
+the structure of the reference's CUDA driver, none of this repository's kernels; see
+pie_b200/bench/library_arm.py). The default run times that comparator first, on the same GPUs and
+the same synthetic contexts, and reports `vs_baseline` = ours / library.
 """
 from __future__ import annotations
 
@@ -34,7 +38,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"])
+    ap.add_argument("--no-baseline", action="store_true", help="skip the library comparator (vs_baseline stays null)")
     ap.add_argument("--model", default="llama-3.1-8b")
     ap.add_argument("--requests", type=int, default=512)
     ap.add_argument("--prompt-min", type=int, default=128)
@@ -103,6 +108,27 @@ def main():
     if args.layers:
         overrides["num_hidden_layers"] = args.layers
     cfg = preset(args.model, **overrides)
+
+    # ---- library comparator: first, so that its memory is back before the engine sizes its KV pool
+    baseline = None
+    if args.impl == "library" or not args.no_baseline:
+        baseline = _library_arm(args, cfg, rank, world, local_rank)
+        if args.impl == "library":
+            if rank == 0:
+                ok = "error" not in baseline
+                print(json.dumps({
+                    "metric": "decode output tokens/s", "value": baseline.get("tokens_per_s"), "unit": "tokens/s",
+                    "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": baseline.get("ms_per_step"),
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": 1.0 if ok else None, "dtype": "bf16",
+                    "data": "synthetic random-token contexts (random KV content), random-init N(0,0.02) weights",
+                    "impl": "library", "config": {"model": cfg.name, "global_batch": args.requests,
+                                                  "seq_len": f"prompts U[{args.prompt_min},{args.prompt_max}] + {args.out_tokens} out",
+                                                  "parallelism": f"tp{world}", "kv_page_size": 16,
+                                                  "sampler": "temperature 1.0, top-p 0.9", "valid": not args.layers},
+                    "detail": baseline}))
+            if world > 1:
+                _hard_exit(0)
+            return 0
     t0 = time.time()
     driver = TorchDriver(cfg, torch.device("cuda", local_rank), page_size=16, max_requests=args.requests,
                          max_tokens=args.max_tokens, par=par, gemm_backend=args.gemm)
@@ -190,12 +216,18 @@ def main():
             e2e["workload_tokens_per_s"], e2e["fires"] = sm[2], int(sm[3])
             h2d, d2h = int(sm[4]), int(sm[5])
     value = dev["tokens_per_s"] if dev else None
+    vs = None
+    if baseline and baseline.get("tokens_per_s") and value:
+        vs = value / baseline["tokens_per_s"]
     line = {
         "metric": "decode output tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev["ms_per_step"] if dev else None,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": vs, "dtype": "bf16",
         "data": "synthetic random-token prompts, random-init N(0,0.02) weights",
         "impl": "ours",
+        # what vs_baseline divides by: the library comparator timed in this same run (the reference
+        # itself cannot be built here and publishes no number for this configuration)
+        "baseline": baseline,
         "config": {"model": cfg.name, "global_batch": n_req, "seq_len": f"prompts U[{args.prompt_min},{args.prompt_max}] + {args.out_tokens} out",
                    "parallelism": (f"dp{world}" if dp else f"tp{world}"), "tp_backend": args.tp_backend if (world > 1 and not dp) else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
                    "gemm": args.gemm, "layers": cfg.num_hidden_layers,
@@ -219,6 +251,28 @@ def main():
     if world > 1:
         _hard_exit(0)
     return 0
+
+
+def _library_arm(args, cfg, rank: int, world: int, local_rank: int) -> dict:
+    """Time the library comparator on this run's GPUs and contexts; every rank calls it. Failures are
+    reported, not raised: the headline number does not depend on the comparator."""
+    import gc
+
+    import torch
+    from pie_b200.bench import harness, library_arm
+    cache = library_arm.configure_cache()
+    if not os.path.isdir(os.path.join(cache, ".cache", "flashinfer")) and os.environ.get("PIE_LIBRARY_ARM_JIT") != "1":
+        return {"impl": "library", "error": "FlashInfer kernel cache not prebuilt (python -m pie_b200.bench.library_arm "
+                                            "--prebuild); set PIE_LIBRARY_ARM_JIT=1 to compile during the run"}
+    lens = [len(p) for p in harness.make_prompts(args.requests, args.prompt_min, args.prompt_max, cfg.vocab_size, seed=1)]
+    try:
+        out = library_arm.run(cfg, lens, args.out_tokens, args.warmup, args.steps, rank, world,
+                              torch.device("cuda", local_rank))
+    except Exception as e:  # noqa: BLE001
+        out = {"impl": "library", "error": f"{type(e).__name__}: {e}"[:300]}
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
 
 
 def _hard_exit(code: int) -> None:
