@@ -125,6 +125,11 @@ def main():
         for name, (c, t) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
             print(f"{t / a.steps:10.1f} us/step  {c / a.steps:7.1f} launches/step  {t / c:8.2f} us each  {name[:110]}")
     from .. import ops
+    st = ops.kernel_status(drv.device).cpu().numpy()
+    w = st[2:6].view("uint64")
+    if st[6] or st[7]:
+        print(f"peer waits seen by CTA 0: all-gather flags {w[0] / max(1, st[6]) / 1e3:.1f} us x {st[6]} waits, "
+              f"reduce-scatter flags {w[1] / max(1, st[7]) / 1e3:.1f} us x {st[7]} waits (whole run)")
     ops.check_kernel_status(drv.device)
     if comm is not None:
         comm.stop_followers()

@@ -23,6 +23,14 @@ enum PieKernelStatus : int {
     PIE_ERR_BOUNDS = 5,        // index outside its table (debug checks)
 };
 
+// Layout of the status block (8 int32, 8-byte aligned) that the kernels with peer waits are given:
+//   [0]    first PieKernelStatus error code, 0 while healthy
+//   [2..3] nanoseconds (u64) that CTA 0 of the gated GEMMs spent waiting for all-gather flags, [6] waits counted
+//   [4..5] nanoseconds (u64) that CTA 0 of the reduce + norm + push kernel spent waiting for reduce-scatter
+//          flags, [7] waits counted
+// The wait counters are a profiling aid (one atomic per kernel); nothing reads them on the hot path.
+constexpr int PIE_STATUS_WORDS = 8;
+
 // Programmatic dependent launch (off unless pie_set_pdl(1)): a kernel launched through
 // pie::launch_pdl may start while its predecessor in the stream is still draining. It must call
 // pdl_wait() before it reads anything the predecessor wrote or writes anything the predecessor
@@ -49,6 +57,16 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void status_add_wait(int* status, int slot, unsigned long long t0) {
+    atomicAdd(reinterpret_cast<unsigned long long*>(status + 2 + 2 * slot), global_ns() - t0);
+    atomicAdd(status + 6 + slot, 1);
 }
 
 typedef __nv_bfloat16 bf16;

@@ -333,6 +333,7 @@ __device__ __forceinline__ bool ag_gate_wait_rows(const TpArgs& tp, int* status,
     if ((need & ~seen) == 0u) return true;
     const int e = *reinterpret_cast<const volatile int*>(tp.ag_epoch);
     const long long t0 = clock64();
+    const unsigned long long tg = blockIdx.x == 0 ? global_ns() : 0ull;
     for (int src = o0; src <= o1; ++src) {
         if (seen & (1u << src)) continue;
         while (*reinterpret_cast<const volatile int*>(tp.ag_flags + src) < e) {
@@ -342,6 +343,7 @@ __device__ __forceinline__ bool ag_gate_wait_rows(const TpArgs& tp, int* status,
             }
         }
     }
+    if (blockIdx.x == 0) status_add_wait(status, 0, tg);
     seen |= need;
     __threadfence_system();
     asm volatile("fence.proxy.async;\n" ::: "memory");

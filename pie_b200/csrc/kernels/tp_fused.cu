@@ -52,6 +52,7 @@ tp_reduce_norm_push_kernel(const __grid_constant__ TpNormArgs a) {
         if (a.reduce) {
             const int e = *reinterpret_cast<const volatile int*>(a.rs_epoch);
             const long long t0 = clock64();
+            const unsigned long long tg = row == 0 ? global_ns() : 0ull;
             for (int src = 0; src < a.world && ok; ++src) {
                 while (*reinterpret_cast<const volatile int*>(a.rs_flags + src) < e) {
                     if (*reinterpret_cast<volatile int*>(a.status) != 0 || clock64() - t0 > 1500000000ll) {
@@ -61,6 +62,7 @@ tp_reduce_norm_push_kernel(const __grid_constant__ TpNormArgs a) {
                     }
                 }
             }
+            if (row == 0) status_add_wait(a.status, 1, tg);
             __threadfence_system();
         }
         s_ok = ok;

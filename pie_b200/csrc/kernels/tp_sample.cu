@@ -8,14 +8,15 @@
 // equals the single-GPU sampler's on the concatenated logits.
 //
 // Exchange protocol (plain peer stores / loads over NVLink, no multimem): a CTA owns one row at a
-// time and a mailbox [cta][parity][src rank] on every rank. To exchange, it stores its words into
-// its slot of every rank's mailbox, fences, raises flag[cta][rank] = sequence number on every rank,
-// then waits (bounded) until the flags of all source ranks reached the sequence number and reads
-// the slots. Slots alternate by the parity of the sequence number: a rank can run at most one
-// exchange ahead of a peer, so the slot it overwrites has been read by everybody. All ranks launch
-// the same grid and walk rows in the same order, so CTA c of every rank works on the same row.
-// Every CTA of the grid is resident (the launcher bounds the grid by the occupancy), so no CTA
-// waits for one that cannot run.
+// time and a mailbox [cta][parity][src rank] of 64-bit words on every rank. To exchange, it stores
+// each of its 32-bit words, paired with the exchange's sequence number in the upper half, into its
+// slot of every rank's mailbox, then polls (bounded) the slots of all source ranks in its own mailbox
+// until every word carries the sequence number. An aligned 8-byte store is never torn, so a word
+// that shows the sequence number also shows its data: no fence and no separate flag are needed.
+// Slots alternate by the parity of the sequence number: a rank can run at most one exchange ahead of
+// a peer, so the slot it overwrites has been read by everybody. All ranks launch the same grid and
+// walk rows in the same order, so CTA c of every rank works on the same row. Every CTA of the grid
+// is resident (the launcher bounds the grid by the occupancy), so no CTA waits for one that cannot run.
 //
 // Reference behaviour replaced: under tensor parallelism the reference vocabulary-shards lm_head
 // only for greedy sampling (arg-max pairs + all-gather: driver/cuda/src/model/llama_like.cpp:764-813,
@@ -25,6 +26,12 @@
 
 namespace pie {
 
+#ifndef TS_MIN_BLOCKS
+#define TS_MIN_BLOCKS 4
+#endif
+#ifndef TS_UNROLL
+#define TS_UNROLL 1
+#endif
 constexpr int TS_THREADS = 256;
 constexpr int TS_WARPS = TS_THREADS / 32;
 constexpr int TS_MAX_RANKS = 8;
@@ -37,8 +44,7 @@ struct TpSampleRank {
 };
 
 struct TpSampleArgs {
-    uint32_t* peer_xbuf[TS_MAX_RANKS];   // mailbox of rank i: [grid_max][2][world][TS_SLOT_WORDS]
-    int* peer_xflag[TS_MAX_RANKS];       // flags of rank i: [grid_max][world]
+    unsigned long long* peer_xbuf[TS_MAX_RANKS];   // mailbox of rank i: [grid_max][2][world][TS_SLOT_WORDS]
     TpSampleRank r[TS_MAX_RANKS];        // real launch: r[0] is this rank; emulation: one entry per rank
     int* status;
     int world, rank_base, vocab_local, grid_max;
@@ -80,45 +86,37 @@ struct TsLink {
     int* s_fail;           // shared flag
 };
 
-// Sends `nw` words (shared memory, 16-byte aligned, nw % 4 == 0) to every rank and gathers every rank's
-// words into link.gathered[src * TS_SLOT_WORDS + w]. Returns false when a wait ran out.
+// Sends `nw` words (shared memory) to every rank and gathers every rank's words into
+// link.gathered[src * TS_SLOT_WORDS + w]. Returns false when a wait ran out.
 __device__ __forceinline__ bool ts_exchange(TsLink& L, const uint32_t* mine, int nw) {
     const TpSampleArgs& a = *L.a;
     const int world = a.world;
     L.seq += 1;
-    const int seq = L.seq, par = seq & 1;
-    const size_t slot0 = ((size_t)L.cta * 2 + par) * world;       // slot index of source rank 0
-    const int nv = nw >> 2;
-    for (int i = threadIdx.x; i < world * nv; i += TS_THREADS) {
-        const int p = i / nv, v = i - p * nv;
-        reinterpret_cast<uint4*>(a.peer_xbuf[p] + (slot0 + L.rank) * TS_SLOT_WORDS)[v] =
-            reinterpret_cast<const uint4*>(mine)[v];
+    const uint32_t seq = (uint32_t)L.seq;
+    const size_t slot0 = ((size_t)L.cta * 2 + (seq & 1u)) * world;       // slot index of source rank 0
+    for (int i = threadIdx.x; i < world * nw; i += TS_THREADS) {
+        const int p = i / nw, w = i - p * nw;
+        volatile unsigned long long* dst = a.peer_xbuf[p] + (slot0 + L.rank) * TS_SLOT_WORDS + w;
+        *dst = ((unsigned long long)seq << 32) | mine[w];
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world) {
-        *reinterpret_cast<volatile int*>(a.peer_xflag[threadIdx.x] + (size_t)L.cta * world + L.rank) = seq;
-        const volatile int* f = a.peer_xflag[L.rank] + (size_t)L.cta * world + threadIdx.x;
-        const long long t0 = clock64();
-        while ((int)(*f - seq) < 0) {
+    const volatile unsigned long long* box = a.peer_xbuf[L.rank] + slot0 * TS_SLOT_WORDS;
+    const long long t0 = clock64();
+    for (int i = threadIdx.x; i < world * nw; i += TS_THREADS) {
+        const int p = i / nw, w = i - p * nw;
+        const volatile unsigned long long* src = box + (size_t)p * TS_SLOT_WORDS + w;
+        unsigned long long v = *src;
+        while ((uint32_t)(v >> 32) != seq) {
             if (*reinterpret_cast<volatile int*>(a.status) != 0 || clock64() - t0 > a.wait_cycles) {
                 atomicCAS(a.status, 0, PIE_ERR_WAIT_PEER);
                 *L.s_fail = 1;
                 break;
             }
+            v = *src;
         }
-        __threadfence_system();
+        L.gathered[p * TS_SLOT_WORDS + w] = (uint32_t)v;
     }
     __syncthreads();
-    if (*L.s_fail) return false;
-    const uint32_t* box = a.peer_xbuf[L.rank] + slot0 * TS_SLOT_WORDS;
-    for (int i = threadIdx.x; i < world * nv; i += TS_THREADS) {
-        const int p = i / nv, v = i - p * nv;
-        reinterpret_cast<uint4*>(L.gathered + p * TS_SLOT_WORDS)[v] =
-            __ldcg(reinterpret_cast<const uint4*>(box + (size_t)p * TS_SLOT_WORDS) + v);
-    }
-    __syncthreads();
-    return true;
+    return *L.s_fail == 0;
 }
 
 struct TsRow {
@@ -132,7 +130,7 @@ struct TsRow {
 
 template <typename F>
 __device__ __forceinline__ void ts_scan(const TsRow& rv, F&& f) {
-    constexpr int U = 4;
+    constexpr int U = TS_UNROLL;
     for (int v0 = threadIdx.x; v0 < rv.nvec; v0 += TS_THREADS * U) {
         uint4 pk[U];
 #pragma unroll
@@ -149,7 +147,7 @@ __device__ __forceinline__ void ts_scan(const TsRow& rv, F&& f) {
 }
 
 // four resident CTAs per SM: 592 mailboxes on a 148-SM part, one row per CTA for up to 592 rows
-__global__ void __launch_bounds__(TS_THREADS, 4)
+__global__ void __launch_bounds__(TS_THREADS, TS_MIN_BLOCKS)
 tp_sample_kernel(const __grid_constant__ TpSampleArgs a, long row_stride, int rows,
                  const float* __restrict__ temperature, const int* __restrict__ top_k,
                  const float* __restrict__ top_p, const float* __restrict__ min_p,
@@ -453,11 +451,10 @@ using namespace pie;
 PIE_API int pie_tp_sample_args_size() { return (int)sizeof(TpSampleArgs); }
 PIE_API int pie_tp_sample_slot_words() { return TS_SLOT_WORDS; }
 
-// Bytes of mailbox and of flags every rank must provide (zero-initialised) for `grid_max` CTAs.
+// Bytes of mailbox every rank must provide (zero-initialised, 8-byte aligned) for `grid_max` CTAs.
 PIE_API long pie_tp_sample_mailbox_bytes(int grid_max, int world) {
-    return (long)grid_max * 2 * world * TS_SLOT_WORDS * 4;
+    return (long)grid_max * 2 * world * TS_SLOT_WORDS * 8;
 }
-PIE_API long pie_tp_sample_flag_bytes(int grid_max, int world) { return (long)grid_max * world * 4; }
 
 // Largest grid whose CTAs are all resident on a device with `num_sms` SMs.
 PIE_API int pie_tp_sample_max_grid(int num_sms) {
@@ -467,18 +464,15 @@ PIE_API int pie_tp_sample_max_grid(int num_sms) {
     return per_sm * num_sms;
 }
 
-// peer_xbuf[i] / peer_xflag[i]: rank i's mailbox and flags as mapped on THIS GPU. seq: this rank's
-// [grid_max] int32 counters (zero-initialised once, then owned by the kernel).
-PIE_API int pie_tp_sample_fill_args(void* blob, void* const* peer_xbuf, int* const* peer_xflag, int* seq,
+// peer_xbuf[i]: rank i's mailbox as mapped on THIS GPU. seq: this rank's [grid_max] int32 counters
+// (zero-initialised once, then owned by the kernel).
+PIE_API int pie_tp_sample_fill_args(void* blob, void* const* peer_xbuf, int* seq,
                                     int* status, int world, int rank, int vocab_local, int grid_max,
                                     long long wait_cycles) {
     if (world < 1 || world > TS_MAX_RANKS || rank < 0 || rank >= world || vocab_local % 8 || grid_max < 1)
         return (int)cudaErrorInvalidValue;
     TpSampleArgs a{};
-    for (int i = 0; i < world; ++i) {
-        a.peer_xbuf[i] = (uint32_t*)peer_xbuf[i];
-        a.peer_xflag[i] = peer_xflag[i];
-    }
+    for (int i = 0; i < world; ++i) a.peer_xbuf[i] = (unsigned long long*)peer_xbuf[i];
     a.r[0].seq = seq;
     a.status = status; a.world = world; a.rank_base = rank; a.vocab_local = vocab_local; a.grid_max = grid_max;
     a.wait_cycles = wait_cycles > 0 ? wait_cycles : 1500000000ll;
@@ -507,8 +501,8 @@ PIE_API int pie_tp_sample(const void* blob, const void* logits, long row_stride,
 }
 
 // All `world` ranks in ONE cooperative launch on one GPU (blockIdx.y = rank): the multi-rank path
-// on a machine with fewer GPUs than ranks. xbuf / xflag / seq: [world] local buffers sized as above.
-PIE_API int pie_tp_sample_emulated(void* const* xbuf, int* const* xflag, int* const* seq, int* status,
+// on a machine with fewer GPUs than ranks. xbuf / seq: [world] local buffers sized as above.
+PIE_API int pie_tp_sample_emulated(void* const* xbuf, int* const* seq, int* status,
                                    int world, int vocab_local, int grid_max, long long wait_cycles,
                                    const void* const* logits, long row_stride, int rows,
                                    const float* temperature, const int* top_k, const float* top_p,
@@ -519,8 +513,7 @@ PIE_API int pie_tp_sample_emulated(void* const* xbuf, int* const* xflag, int* co
     if (world < 1 || world > TS_MAX_RANKS || vocab_local % 8 || row_stride % 8) return (int)cudaErrorInvalidValue;
     TpSampleArgs a{};
     for (int i = 0; i < world; ++i) {
-        a.peer_xbuf[i] = (uint32_t*)xbuf[i];
-        a.peer_xflag[i] = xflag[i];
+        a.peer_xbuf[i] = (unsigned long long*)xbuf[i];
         a.r[i].logits = (const bf16*)logits[i];
         a.r[i].out_tokens = out_tokens[i];
         a.r[i].seq = seq[i];

@@ -192,7 +192,7 @@ class TorchDriver:
             self.sampled_host = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
             self.cohort_sampled = [torch.zeros(rows, dtype=torch.int32, device=self.device) for _ in range(2)]
             self.cohort_host = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-            self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+            self.status_host = torch.zeros(8, dtype=torch.int32, pin_memory=True)
         self._failed: Optional[str] = None
         self.use_graphs = use_graphs and self.cuda
         self.buckets = graph_buckets(max_requests)

@@ -37,14 +37,14 @@ def kernel_status(device=None) -> torch.Tensor:
     """Device int32 that kernels with bounded waits set when a wait runs out (0 = healthy)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
     if dev not in _STATUS:
-        _STATUS[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        _STATUS[dev] = torch.zeros(8, dtype=torch.int32, device=f"cuda:{dev}")   # [0] status, [2..7] wait counters
         with torch.cuda.device(dev):       # kernels without a status argument report here too
             check(fn("pie_set_status_word")(ptr(_STATUS[dev])), "set_status_word")
     return _STATUS[dev]
 
 
 def check_kernel_status(device=None) -> None:
-    st = int(kernel_status(device).item())
+    st = int(kernel_status(device)[0].item())
     if st != 0:
         kernel_status(device).zero_()
         raise _lib.KernelLibraryError(f"a kernel gave up on a bounded wait (status {st})")

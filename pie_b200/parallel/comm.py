@@ -178,9 +178,7 @@ class TPComm:
             ops.num_sms(self.device))))
         self.off_ts_box = self.off_ar + 2 * self.world * self.ar_cap * 2
         ts_box = _lib.declare("pie_tp_sample_mailbox_bytes", [C.c_int, C.c_int], C.c_long)(self.ts_grid, self.world)
-        self.off_ts_flag = self.off_ts_box + ts_box
-        total = self.off_ts_flag + _lib.declare("pie_tp_sample_flag_bytes", [C.c_int, C.c_int], C.c_long)(
-            self.ts_grid, self.world)
+        total = self.off_ts_box + ts_box
         self.sym = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.sym.zero_()
         torch.cuda.synchronize(self.device)
@@ -225,10 +223,10 @@ class TPComm:
         self.vocab_local = driver.model.w["lm_head"].shape[0]
         self.ts_seq = torch.zeros(self.ts_grid, dtype=torch.int32, device=self.device)
         self.ts_blob = C.create_string_buffer(_lib.declare("pie_tp_sample_args_size", [], C.c_int)())
-        fill_ts = _lib.declare("pie_tp_sample_fill_args", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+        fill_ts = _lib.declare("pie_tp_sample_fill_args", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                            C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong])
         check(fill_ts(self.ts_blob, arr_p(*[b + self.off_ts_box for b in base]),
-                      arr_p(*[b + self.off_ts_flag for b in base]), self.ts_seq.data_ptr(), status.data_ptr(), W,
+                      self.ts_seq.data_ptr(), status.data_ptr(), W,
                       self.rank, self.vocab_local, self.ts_grid, 0), "tp_sample_fill_args")
         self._ag_flags_local = ag_flags[self.rank]
         self._ag_epoch_ptr = lc + 12

@@ -151,10 +151,10 @@ def test_paged_decode_attention_clamps_work_count():
     scale = 1 / math.sqrt(d)
     out = ops.paged_decode_attention(q, kv, plan, scale)
     torch.cuda.synchronize()
-    assert int(status.item()) == 5               # PIE_ERR_BOUNDS
+    assert int(status[0].item()) == 5               # PIE_ERR_BOUNDS
     with pytest.raises(ops._lib.KernelLibraryError):
         ops.check_kernel_status(DEV)
-    assert int(status.item()) == 0
+    assert int(status[0].item()) == 0
     assert bool((big[need:] == 777.0).all())     # nothing written past the scratch
     qo = np.arange(r + 1, dtype=np.int32)
     want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale)
@@ -168,7 +168,7 @@ def test_paged_decode_attention_clamps_work_count():
                           len(item_req), r, 64, page)
     out = ops.paged_decode_attention(q, kv, plan, scale)
     torch.cuda.synchronize()
-    assert int(status.item()) == 5
+    assert int(status[0].item()) == 5
     status.zero_()
     close(out[:3], want[:3], 2e-2)
 
@@ -465,10 +465,10 @@ def test_bounded_peer_wait_times_out_and_reports_status():
     _lib.check(wait(flags.data_ptr(), epoch.data_ptr(), 2, status.data_ptr(), _lib.stream_ptr()), "tp_wait_ag")
     torch.cuda.synchronize()
     assert time.time() - t0 < 10.0
-    assert int(status.item()) == 4
+    assert int(status[0].item()) == 4
     with pytest.raises(_lib.KernelLibraryError):
         ops.check_kernel_status(DEV)
-    assert int(status.item()) == 0
+    assert int(status[0].item()) == 0
     # the device still works
     x = torch.ones(1024, device=DEV)
     assert float(x.sum()) == 1024.0
@@ -476,4 +476,4 @@ def test_bounded_peer_wait_times_out_and_reports_status():
     flags.fill_(1)
     _lib.check(wait(flags.data_ptr(), epoch.data_ptr(), 2, status.data_ptr(), _lib.stream_ptr()), "tp_wait_ag")
     torch.cuda.synchronize()
-    assert int(status.item()) == 0
+    assert int(status[0].item()) == 0

@@ -21,15 +21,13 @@ class Emu:
         self.world, self.vocab_local, self.grid_max = world, vocab_local, grid_max
         lib = _lib.load(required=True)
         box = _lib.declare("pie_tp_sample_mailbox_bytes", [C.c_int, C.c_int], C.c_long)(grid_max, world)
-        flg = _lib.declare("pie_tp_sample_flag_bytes", [C.c_int, C.c_int], C.c_long)(grid_max, world)
         self.xbuf = [torch.zeros(box, dtype=torch.uint8, device=DEV) for _ in range(world)]
-        self.xflag = [torch.zeros(flg // 4, dtype=torch.int32, device=DEV) for _ in range(world)]
         self.seq = [torch.zeros(grid_max, dtype=torch.int32, device=DEV) for _ in range(world)]
         self.out = [torch.full((rows_max,), -1, dtype=torch.int32, device=DEV) for _ in range(world)]
         self.status = ops.kernel_status(DEV)
         self.fn = lib.pie_tp_sample_emulated
         self.fn.restype = C.c_int
-        self.fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_longlong,
+        self.fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_longlong,
                             C.c_void_p, C.c_long, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                             C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
 
@@ -39,7 +37,7 @@ class Emu:
         w, vl = self.world, self.vocab_local
         shards = [logits[:, r * vl:(r + 1) * vl].contiguous() for r in range(w)]
         arr = lambda ts: (C.c_void_p * w)(*[t.data_ptr() for t in ts])
-        rc = self.fn(arr(self.xbuf), arr(self.xflag), arr(self.seq), self.status.data_ptr(), w, vl, self.grid_max,
+        rc = self.fn(arr(self.xbuf), arr(self.seq), self.status.data_ptr(), w, vl, self.grid_max,
                      wait_cycles, arr(shards), vl, rows, temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
                      min_p.data_ptr(), seeds.data_ptr(), 0 if mask_bits is None else mask_bits.data_ptr(),
                      0 if mask_row is None else mask_row.data_ptr(), 0 if mask_bits is None else mask_bits.shape[1],
@@ -97,7 +95,7 @@ def test_sharded_sampler_equals_single_gpu_sampler(world, vocab_local, kind):
         want = ops.sample(lg, *pr)
         got = emu.sample(lg, *pr)
         torch.cuda.synchronize()
-        assert int(emu.status.item()) == 0
+        assert int(emu.status[0].item()) == 0
         for r in range(world):
             assert torch.equal(got[r], got[0])
         same = (got[0] == want).float().mean().item()
@@ -154,15 +152,14 @@ def test_missing_peer_runs_out_of_time_and_reports():
     lib = _lib.load(required=True)
     box = _lib.declare("pie_tp_sample_mailbox_bytes", [C.c_int, C.c_int], C.c_long)(8, world)
     xbuf = [torch.zeros(box, dtype=torch.uint8, device=DEV) for _ in range(world)]
-    xflag = [torch.zeros(8 * world, dtype=torch.int32, device=DEV) for _ in range(world)]
     seq = torch.zeros(8, dtype=torch.int32, device=DEV)
     status = ops.kernel_status(DEV)
     status.zero_()
     blob = C.create_string_buffer(_lib.declare("pie_tp_sample_args_size", [], C.c_int)())
-    fill = _lib.declare("pie_tp_sample_fill_args", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+    fill = _lib.declare("pie_tp_sample_fill_args", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong])
     arr = lambda ts: (C.c_void_p * world)(*[t.data_ptr() for t in ts])
-    assert fill(blob, arr(xbuf), arr(xflag), seq.data_ptr(), status.data_ptr(), world, 0, vl, 8, 2_000_000) == 0
+    assert fill(blob, arr(xbuf), seq.data_ptr(), status.data_ptr(), world, 0, vl, 8, 2_000_000) == 0
     lg = make_logits(rows, vl, 1, True)
     pr = params(rows, "top_p", 1)
     out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
@@ -171,8 +168,8 @@ def test_missing_peer_runs_out_of_time_and_reports():
                                   ops.num_sms(DEV), torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()                     # returns: the wait is bounded
-    assert int(status.item()) == 4               # PIE_ERR_WAIT_PEER
+    assert int(status[0].item()) == 4               # PIE_ERR_WAIT_PEER
     with pytest.raises(_lib.KernelLibraryError):
         ops.check_kernel_status(DEV)
-    assert int(status.item()) == 0
+    assert int(status[0].item()) == 0
     assert float(torch.ones(4, device=DEV).sum().item()) == 4.0    # the context still works
