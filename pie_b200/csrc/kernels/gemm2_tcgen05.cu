@@ -294,6 +294,22 @@ extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_debug(in
 extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_debug(int) { return (int)cudaErrorNotSupported; }
 #endif
 
+// Problems below these MAC counts go to the single-CTA kernel (second value: when K < 8192).
+static double g_pair_min_macs = 1.0e10, g_pair_min_macs_short_k = 2.0e10;
+// Tuning aid: pair tile width (64 / 128 / 256) and stream-K (-1 auto, 0 off, 1 on) instead of the dispatcher's choice.
+static int g_pair_force_bn = 0, g_pair_force_sk = -1;
+extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_plan(int bn, int streamk) {
+    if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return (int)cudaErrorInvalidValue;
+    g_pair_force_bn = bn;
+    g_pair_force_sk = streamk;
+    return 0;
+}
+extern "C" __attribute__((visibility("default"))) int pie_gemm_set_pair_thresholds(double min_macs, double min_macs_short_k) {
+    g_pair_min_macs = min_macs;
+    g_pair_min_macs_short_k = min_macs_short_k;
+    return 0;
+}
+
 template <int BN, int EPI>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M, int N,
                         int K, int ldc, int ldr, int* status, int pairs, int streamk, float* ws, int* cnt,
@@ -318,8 +334,8 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
     // better. Measured cross-over on B200 (M = 256 / 512 decode shapes): pairs win from 2e10 MACs,
     // and from 1e10 when K is long (the 14336-deep down projection).
     const double macs = (double)M * N * K;
-    if (M <= GEMM_BM || N < 128 || num_sms < 2 || macs < 1.0e10 || (macs < 2.0e10 && K < 8192)) return 0;
-    const int bn = N >= 256 ? 256 : 128;
+    if (M <= GEMM_BM || N < 128 || num_sms < 2 || macs < g_pair_min_macs || (macs < g_pair_min_macs_short_k && K < 8192)) return 0;
+    const int bn = g_pair_force_bn ? g_pair_force_bn : (N >= 256 ? 256 : 128);
     const int pairs_max = num_sms / 2;
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
     const long tiles = (long)((M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * ((N + bn - 1) / bn);
@@ -332,7 +348,7 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
         if (ws && gp >= 1 && tiles % gp != 0 && tiles <= 2L * pairs_max &&
             (gp + tiles) * 2L * GEMM_BM * bn <= ws_floats && tiles * 8 <= cnt_ints) {
             const double dp = (double)waves, skc = (double)tiles / gp + 0.12;
-            if (skc < 0.92 * dp) { streamk = 1; pairs = (int)gp; }
+            if ((skc < 0.92 * dp && g_pair_force_sk != 0) || g_pair_force_sk == 1) { streamk = 1; pairs = (int)gp; }
         }
     }
     CUtensorMap ta, tb;
@@ -348,7 +364,7 @@ int pie_gemm2_dispatch(const void* A, const void* W, void* C, const void* R, int
         case EPI_RS: return launch_gemm2<BN_, EPI_RS>(ta, tb, C, R, M, N, K, ldc, ldr, status, pairs, streamk, ws, cnt, st, tp);             \
         default: *handled = 0; return (int)cudaErrorInvalidValue;                                                   \
     }
-    if (bn == 256) { GO(256) } else { GO(128) }
+    if (bn == 256) { GO(256) } else if (bn == 128) { GO(128) } else { GO(64) }
 #undef GO
     return (int)cudaErrorInvalidValue;
 }

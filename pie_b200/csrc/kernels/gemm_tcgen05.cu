@@ -461,8 +461,25 @@ struct GemmPlan {
 //   fill its waves. The weights also have to come out of HBM once. Stream-K (even split of all
 //   k-blocks, partial tiles fixed up through the workspace) competes when no width fills the waves.
 //   force_bn > 0 fixes the width; allow_sk = false keeps whole-tile scheduling.
+// Tuning aid: a plan (tile width, grid, stream-K) that replaces the planner's choice for every
+// following single-CTA launch until cleared with bn = 0. The caller owns its validity.
+static GemmPlan g_plan_override{0, 0, 0};
+PIE_API int pie_gemm_set_plan_override(int bn, int grid, int streamk) {
+    if (bn < 0 || bn > 256 || bn % 16) return (int)cudaErrorInvalidValue;
+    g_plan_override = GemmPlan{bn, grid, streamk};
+    return 0;
+}
+
 static GemmPlan plan_gemm(int M, int N, int K, int num_sms, int force_bn, const GemmWorkspace& w,
                           bool allow_sk = true) {
+    if (g_plan_override.bn > 0) {
+        GemmPlan p = g_plan_override;
+        const long tiles = (long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + p.bn - 1) / p.bn);
+        if (!p.streamk) p.grid = (int)std::min<long>(tiles, p.grid > 0 ? p.grid : num_sms);
+        else if (!w.ws || (long)(p.grid + tiles) * GEMM_BM * (p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256)) > w.ws_floats ||
+                 tiles * 4 > w.cnt_ints) p.streamk = 0, p.grid = (int)std::min<long>(tiles, num_sms);
+        return p;
+    }
     const int tm = (M + GEMM_BM - 1) / GEMM_BM;
     const int num_kb = (K + GEMM_KSTEP - 1) / GEMM_KSTEP;
     // The plan depends on M only through the number of 128-row tiles: every batch size within a
