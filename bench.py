@@ -38,6 +38,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5, 6],
+                    help="2: the headline configuration (this file); 3 Qwen3-32B block-fp8, 4 Qwen3-30B-A3B MoE with "
+                         "expert parallelism, 5 agentic fork, 6 GPT-OSS shapes: see pie_b200/bench/configs.py")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"])
     ap.add_argument("--no-baseline", action="store_true", help="skip the library comparator (vs_baseline stays null)")
     ap.add_argument("--model", default="llama-3.1-8b")
@@ -69,6 +72,10 @@ def main():
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+    if args.config != 2:
+        from pie_b200.bench import configs
+        return configs.main(["--config", str(args.config), "--steps", str(args.steps), "--warmup", str(args.warmup),
+                             "--gemm", args.gemm] + (["--layers", str(args.layers)] if args.layers else []))
 
     os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer loads/stores only, no NVLS binding
     import torch

@@ -1,5 +1,7 @@
-"""The other benchmark configurations (the headline one is bench.py at the repository root),
-on one GPU:
+"""The other benchmark configurations (the headline one is bench.py at the repository root; `bench.py
+--config N` lands here). On one GPU, or under `python -m torch.distributed.run --nproc-per-node T ...`
+as ONE fused tensor-parallel group over T GPUs (config 4: whole experts per rank, i.e. expert
+parallelism, with tensor-parallel attention), device-timed as the max over ranks:
 
     python -m pie_b200.bench.configs --config 3   # Qwen3-32B block-fp8, 4096-token prompts, 512 out, greedy
     python -m pie_b200.bench.configs --config 4   # Qwen3-30B-A3B MoE, prompts U[256,1024], 256 out
@@ -17,16 +19,21 @@ import json
 import time
 
 
-def main():
+def main(argv=None):
+    import os
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, required=True, choices=[3, 4, 5, 6])
+    ap.add_argument("--gpus", type=int, default=0, help="informational; the launcher's WORLD_SIZE decides")
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--agents", type=int, default=64)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (marks the run invalid)")
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch
     from . import harness
     from ..driver.executor import TorchDriver
@@ -46,14 +53,32 @@ def main():
     over = {"num_hidden_layers": a.layers} if a.layers else {}
     cfg = preset(spec["model"], **over)
     n_req = a.requests or spec["requests"]
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    par, comm = None, None
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        from ..models.transformer import ParallelContext
+        from ..parallel.comm import TPComm
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+        comm = TPComm(rank, world, dev, fused=True)
+        par = ParallelContext(world, rank, comm, ep=a.config == 4)
     drv = TorchDriver(cfg, dev, page_size=16, max_requests=max(n_req, a.agents * 8 if a.config == 5 else n_req),
-                      max_tokens=16384, gemm_backend=a.gemm)
-    line = {"config": a.config, "model": cfg.name, "n_gpus": 1, "dtype": "bf16" if cfg.quantization is None else "fp8 weights, bf16 activations",
+                      max_tokens=16384, gemm_backend=a.gemm, par=par)
+    if comm is not None:
+        comm.attach(drv)
+    drv.precapture_graphs()
+    if comm is not None and rank != 0:
+        comm.follower_loop(drv)
+        comm.close()
+        os._exit(0)
+    parallelism = "tp1" if world == 1 else (f"ep{world} experts + tp{world} attention (fused)" if a.config == 4
+                                             else f"tp{world} (fused)")
+    line = {"config": a.config, "model": cfg.name, "n_gpus": world, "parallelism": parallelism, "dtype": "bf16" if cfg.quantization is None else "fp8 weights, bf16 activations",
             "data": "synthetic random-token prompts, random-init weights", "gemm": a.gemm,
             "valid": not a.layers and (n_req == spec["requests"] if a.config != 5 else a.agents == 64)}
-    clk = harness.ClockSampler(0).start()
+    clk = harness.ClockSampler(local).start()
     if a.config == 5:
         eng = Engine(EngineConfig())
         eng.add_model(cfg.name, drv)
@@ -65,12 +90,16 @@ def main():
     else:
         prompts = harness.make_prompts(n_req, spec["pmin"], spec["pmax"], cfg.vocab_size, seed=1)
         t0 = time.time()
-        d = harness.run_pipelined_decode(drv, prompts, spec["out"], spec["sampler"], a.warmup, a.steps)
+        d = harness.run_pipelined_decode(drv, prompts, spec["out"], spec["sampler"], a.warmup, a.steps, comm=comm)
         line.update(metric="decode output tokens/s", value=d["tokens_per_s"], ms_per_step=d["ms_per_step"],
                     requests=n_req, steps=a.steps, warmup=a.warmup, prefill_tokens_per_s=d["prefill_tokens_per_s"],
                     sampler=spec["sampler_txt"], wall_s=time.time() - t0)
     line["clocks"] = clk.stop()
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.stop_followers()
+        comm.close()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -175,7 +175,18 @@ constexpr int decode_smem_bytes() {
     return 16 * D * 2 + DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2;
 }
 
-template <int D, int G>
+// CASCADE: shared-prefix items. A work item may then cover a KV range that up to 16 / G requests
+// (the "members" of a tile: forks of one context, whose leading pages are the same physical pages)
+// have in common: the Q tile holds the heads of all members (row = member * G + head), the keys and
+// values of the range are read ONCE, and every member gets its own partial result. Partial results go
+// to slots: a request's slots are [req_item_indptr[r], req_item_indptr[r + 1]) and a shared item with
+// chunk index c fills slot req_item_indptr[member] + c of every member; an unshared item names its
+// slot directly. The merge pass combines a request's slots as before.
+//   item_slot  [items]  : chunk index (shared item) or slot (unshared item)
+//   item_tile  [items]  : row of tile_members for a shared item, -1 otherwise
+//   tile_members [tiles][16] : request of each member, -1 for unused rows
+// Without CASCADE the three arrays are unused and slot == item index.
+template <int D, int G, bool CASCADE>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_layer,
                          const int* __restrict__ page_indices,
@@ -186,8 +197,10 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          float* __restrict__ o_part, float* __restrict__ lse_part, int hq, int hkv,
                          int page_size, float scale_log2, int window_left,
                          const float* __restrict__ sinks_log2, int max_items, int num_reqs,
-                         int* __restrict__ status) {
+                         int* __restrict__ status, const int* __restrict__ item_slot,
+                         const int* __restrict__ item_tile, const int* __restrict__ tile_members) {
     static_assert(G <= 16, "at most 16 query heads per KV head");
+    constexpr int ROWS = CASCADE ? (16 / G) * G : G;      // rows of the Q tile in use
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int CH = D / 8;              // 16-byte chunks per row
     constexpr int TILE_BYTES = 16 * D * 2; // one 16-token K or V tile
@@ -213,16 +226,28 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
             continue;
         }
         const int kv_start = item_start[it], kv_end = item_end[it];
+        const int tile = CASCADE ? item_tile[it] : -1;
+        const int* members = (CASCADE && tile >= 0) ? tile_members + (size_t)tile * 16 : nullptr;
         // sliding window: the query sits at position kv_len - 1 (kv_len = end of the request's last
         // item) and sees keys >= kv_len - 1 - window_left; items start on a 16-token boundary below that
-        const int kv_lo = window_left >= 0 ? max(0, item_end[req_item_indptr[req + 1] - 1] - 1 - window_left) : 0;
+        // (plans with shared items carry no window)
+        const int kv_lo = (!CASCADE && window_left >= 0)
+                              ? max(0, item_end[req_item_indptr[req + 1] - 1] - 1 - window_left) : 0;
         __syncthreads();  // previous item's merge reads are done
-        // Q tile: rows < G are the heads of this KV head, the rest zeros
+        // Q tile: rows < G are the heads of this KV head (of member row / G in a shared item), the rest zeros
         for (int c = threadIdx.x; c < 16 * CH; c += blockDim.x) {
             const int row = c / CH, col = c - row * CH;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < G)
-                v = *reinterpret_cast<const uint4*>(q + ((size_t)req * hq + h * G + row) * D + col * 8);
+            if (row < ROWS) {
+                int rq = req;
+                if (CASCADE) {
+                    const int mem = row / G;
+                    rq = members ? members[mem] : (mem == 0 ? req : -1);
+                    if (rq >= num_reqs) rq = -1;
+                }
+                if (rq >= 0)
+                    v = *reinterpret_cast<const uint4*>(q + ((size_t)rq * hq + h * G + (row % G)) * D + col * 8);
+            }
             *reinterpret_cast<uint4*>(smem + swz<D>(row, col)) = v;
         }
         __syncthreads();
@@ -279,7 +304,7 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
         __syncthreads();  // every warp is done with its K/V stages: reuse as merge space
         float* sm_m = reinterpret_cast<float*>(smem + TILE_BYTES);  // [W][16]
         float* sm_l = sm_m + DEC_WARPS * 16;                         // [W][16]
-        float* sm_o = sm_l + DEC_WARPS * 16;                         // [W][G][D]
+        float* sm_o = sm_l + DEC_WARPS * 16;                         // [W][ROWS][D]
         {
             const int g = lane >> 2, t = lane & 3;
             if (t == 0) {
@@ -290,20 +315,37 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
             }
 #pragma unroll
             for (int n = 0; n < D / 8; ++n) {
-                if (g < G) {
-                    sm_o[(warp * G + g) * D + n * 8 + 2 * t] = st.o[n][0];
-                    sm_o[(warp * G + g) * D + n * 8 + 2 * t + 1] = st.o[n][1];
+                if (g < ROWS) {
+                    sm_o[(warp * ROWS + g) * D + n * 8 + 2 * t] = st.o[n][0];
+                    sm_o[(warp * ROWS + g) * D + n * 8 + 2 * t + 1] = st.o[n][1];
                 }
-                if (G > 8 && g + 8 < G) {
-                    sm_o[(warp * G + g + 8) * D + n * 8 + 2 * t] = st.o[n][2];
-                    sm_o[(warp * G + g + 8) * D + n * 8 + 2 * t + 1] = st.o[n][3];
+                if (ROWS > 8 && g + 8 < ROWS) {
+                    sm_o[(warp * ROWS + g + 8) * D + n * 8 + 2 * t] = st.o[n][2];
+                    sm_o[(warp * ROWS + g + 8) * D + n * 8 + 2 * t + 1] = st.o[n][3];
                 }
             }
         }
         __syncthreads();
-        const bool single = (req_item_indptr[req + 1] - req_item_indptr[req]) == 1;
-        for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const bool single = !(CASCADE && members) && (req_item_indptr[req + 1] - req_item_indptr[req]) == 1;
+        const int my_slot = CASCADE ? item_slot[it] : it;
+        for (int idx = threadIdx.x; idx < ROWS * D; idx += blockDim.x) {
             const int row = idx / D, dim = idx - row * D;
+            int rq = req, slot = my_slot, hrow = row;
+            if (CASCADE) {
+                const int mem = row / G;
+                hrow = row - mem * G;
+                if (members) {
+                    rq = members[mem];
+                    if (rq < 0 || rq >= num_reqs) continue;
+                    slot = req_item_indptr[rq] + my_slot;
+                } else if (mem != 0) {
+                    continue;
+                }
+                if (slot < 0 || slot >= max_items) {          // a plan that outgrew the scratch: drop, report
+                    if (status) atomicCAS(status, 0, PIE_ERR_BOUNDS);
+                    continue;
+                }
+            }
             float M = -INFINITY;
 #pragma unroll
             for (int ww = 0; ww < DEC_WARPS; ++ww) M = fmaxf(M, sm_m[ww * 16 + row]);
@@ -313,18 +355,18 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                 for (int ww = 0; ww < DEC_WARPS; ++ww) {
                     const float sc = exp2f(sm_m[ww * 16 + row] - M);
                     L += sm_l[ww * 16 + row] * sc;
-                    O += sm_o[(ww * G + row) * D + dim] * sc;
+                    O += sm_o[(ww * ROWS + row) * D + dim] * sc;
                 }
             }
             float val = L > 0.f ? O / L : 0.f;
             if (single) {
                 // attention sink: a per-head logit that takes probability mass but has no value row
-                if (sinks_log2 && L > 0.f) val = O / (L + exp2f(sinks_log2[h * G + row] - M));
-                out[((size_t)req * hq + h * G + row) * D + dim] = __float2bfloat16(val);
+                if (sinks_log2 && L > 0.f) val = O / (L + exp2f(sinks_log2[h * G + hrow] - M));
+                out[((size_t)rq * hq + h * G + hrow) * D + dim] = __float2bfloat16(val);
             } else {
-                o_part[(((size_t)it * hkv + h) * G + row) * D + dim] = val;
+                o_part[(((size_t)slot * hkv + h) * G + hrow) * D + dim] = val;
                 if (dim == 0)
-                    lse_part[((size_t)it * hkv + h) * G + row] = L > 0.f ? M + log2f(L) : -INFINITY;
+                    lse_part[((size_t)slot * hkv + h) * G + hrow] = L > 0.f ? M + log2f(L) : -INFINITY;
             }
         }
     }
@@ -577,31 +619,40 @@ PIE_API long pie_decode_attn_scratch_floats(int max_items, int hq, int head_dim)
     return (long)max_items * hq * head_dim + (long)max_items * hq;
 }
 
-// window_left >= 0: each request's single query token sees only the last window_left + 1 keys; the
-// caller's items then start at the 16-token boundary at or below the first visible key (items that
-// start lower are masked). sinks_log2 (optional, [hq], logit * log2(e)): per-head attention sinks.
-PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, const int* page_indices,
-                                         const int* kv_page_indptr, const int* item_req,
-                                         const int* item_start, const int* item_end,
-                                         const int* req_item_indptr, const int* num_items_ptr,
-                                         void* out, float* scratch, int max_items, int num_reqs, int hq,
-                                         int hkv, int head_dim, int page_size, float sm_scale,
-                                         int num_ctas, int run_merge, int window_left,
-                                         const float* sinks_log2, cudaStream_t st) {
+static int launch_decode(const void* q, const void* kv_layer, const int* page_indices,
+                         const int* kv_page_indptr, const int* item_req, const int* item_start,
+                         const int* item_end, const int* req_item_indptr, const int* num_items_ptr,
+                         void* out, float* scratch, int max_items, int num_reqs, int hq, int hkv,
+                         int head_dim, int page_size, float sm_scale, int num_ctas, int run_merge,
+                         int window_left, const float* sinks_log2, const int* item_slot,
+                         const int* item_tile, const int* tile_members, cudaStream_t st) {
     if (num_reqs <= 0) return 0;
     if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
+    const bool cascade = item_tile != nullptr;
+    if (cascade && (!item_slot || !tile_members || window_left >= 0)) return (int)cudaErrorInvalidValue;
     const int group = hq / hkv;
     float* o_part = scratch;
     float* lse_part = scratch + (size_t)max_items * hq * head_dim;
     const float scale_log2 = sm_scale * 1.4426950408889634f;
     DISPATCH_DG(head_dim, group, {
         constexpr int SM = decode_smem_bytes<D>();
-        auto kern = paged_decode_attn_kernel<D, G>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
-        launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
-            (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
-            item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
-            hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word());
+        if (cascade) {
+            auto kern = paged_decode_attn_kernel<D, G, true>;
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+            launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
+                (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
+                item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
+                hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word(),
+                item_slot, item_tile, tile_members);
+        } else {
+            auto kern = paged_decode_attn_kernel<D, G, false>;
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+            launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
+                (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
+                item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
+                hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word(),
+                (const int*)nullptr, (const int*)nullptr, (const int*)nullptr);
+        }
     });
     int err = (int)cudaGetLastError();
     if (err || !run_merge) return err;
@@ -613,6 +664,39 @@ PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, co
         launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, (const float*)o_part,
                    (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2, max_items);
     return (int)cudaGetLastError();
+}
+
+// window_left >= 0: each request's single query token sees only the last window_left + 1 keys; the
+// caller's items then start at the 16-token boundary at or below the first visible key (items that
+// start lower are masked). sinks_log2 (optional, [hq], logit * log2(e)): per-head attention sinks.
+PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, const int* page_indices,
+                                         const int* kv_page_indptr, const int* item_req,
+                                         const int* item_start, const int* item_end,
+                                         const int* req_item_indptr, const int* num_items_ptr,
+                                         void* out, float* scratch, int max_items, int num_reqs, int hq,
+                                         int hkv, int head_dim, int page_size, float sm_scale,
+                                         int num_ctas, int run_merge, int window_left,
+                                         const float* sinks_log2, cudaStream_t st) {
+    return launch_decode(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start, item_end, req_item_indptr,
+                         num_items_ptr, out, scratch, max_items, num_reqs, hq, hkv, head_dim, page_size, sm_scale,
+                         num_ctas, run_merge, window_left, sinks_log2, nullptr, nullptr, nullptr, st);
+}
+
+// Decode attention over a plan with shared-prefix items (see the kernel): requests that were forked
+// from one context read their common pages once. item_req of a shared item names the member whose
+// page table addresses the range. req_item_indptr counts partial-result slots, all below max_items.
+PIE_API int pie_paged_decode_attn_cascade(const void* q, const void* kv_layer, const int* page_indices,
+                                          const int* kv_page_indptr, const int* item_req,
+                                          const int* item_start, const int* item_end,
+                                          const int* req_item_indptr, const int* num_items_ptr,
+                                          void* out, float* scratch, int max_items, int num_reqs, int hq,
+                                          int hkv, int head_dim, int page_size, float sm_scale,
+                                          int num_ctas, const float* sinks_log2, const int* item_slot,
+                                          const int* item_tile, const int* tile_members, cudaStream_t st) {
+    if (!item_tile) return (int)cudaErrorInvalidValue;
+    return launch_decode(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start, item_end, req_item_indptr,
+                         num_items_ptr, out, scratch, max_items, num_reqs, hq, hkv, head_dim, page_size, sm_scale,
+                         num_ctas, 1, -1, sinks_log2, item_slot, item_tile, tile_members, st);
 }
 
 PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int* page_indices,

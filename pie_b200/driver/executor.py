@@ -172,6 +172,10 @@ class TorchDriver:
         # the widest window any layer needs (-1: some layer sees everything); layers that differ mask per call
         self.window_left = self.cfg.plan_window_left
         self.max_items = max_requests + self.num_ctas * 8
+        # shared-prefix decode plans: forks of one context read their common pages once per step
+        import os as _os
+        self.cascade = (self.cuda and _os.environ.get("PIE_CASCADE", "1") != "0" and self.window_left < 0
+                        and self.cfg.layer_types is None)
         rows = max(max_requests, 1024)
         self.max_rows = rows
         self.slab = _Slab({
@@ -179,6 +183,7 @@ class TorchDriver:
             "qo_indptr": max_requests + 1, "kv_page_indptr": max_requests + 1, "kv_lens": max_requests,
             "item_req": self.max_items, "item_start": self.max_items, "item_end": self.max_items,
             "req_item_indptr": max_requests + 1, "num_items": 4,
+            "item_slot": self.max_items, "item_tile": self.max_items, "tile_members": 16 * max_requests,
             "logit_rows": rows, "temperature": rows, "top_k": rows, "top_p": rows, "min_p": rows,
             "mask_row": rows, "seeds": 2 * rows, "src_row": rows,
             "tile_req": max_tokens + max_requests, "tile_qstart": max_tokens + max_requests,
@@ -332,18 +337,55 @@ class TorchDriver:
         return token_slots
 
     # ------------------------------------------------------------------ forward variants
-    def _forward_inputs_decode(self, rb: int) -> ForwardInputs:
+    def _forward_inputs_decode(self, rb: int, cascade: bool = False) -> ForwardInputs:
         s = self.slab
         plan = ops.DecodePlan(
             page_indices=s.d("page_indices"), kv_page_indptr=s.d("kv_page_indptr"), item_req=s.d("item_req"),
             item_start=s.d("item_start"), item_end=s.d("item_end"), req_item_indptr=s.d("req_item_indptr"),
             num_items=s.d("num_items"), scratch=self.scratch, max_items=self.max_items, num_reqs=rb,
             num_ctas=self.num_ctas, page_size=self.page_size, window_left=self.window_left)
+        if cascade:
+            plan.item_slot, plan.item_tile, plan.tile_members = s.d("item_slot"), s.d("item_tile"), s.d("tile_members")
         return ForwardInputs(tokens=s.d("tokens", rb), positions=s.d("positions", rb), slots=s.d("slots", rb),
                              attn=plan, logit_rows=None, is_decode=True)
 
-    def _capture(self, rb: int) -> _Graph:
-        fi = self._forward_inputs_decode(rb)
+    def _plan_decode(self, kv_lens, page_indptr, page_indices, r: int, rb: int) -> bool:
+        """Fill the slab's decode work list for `r` requests padded to `rb`. Returns True when the plan
+        has shared-prefix items (forks of one context: their common pages are then read once per
+        tile of members instead of once per request), which selects the cascade graph variant."""
+        s = self.slab
+        plan = None
+        if self.cascade and r >= 2:
+            groups = ops.find_shared_prefixes(kv_lens, page_indptr, page_indices, self.page_size)
+            if groups:
+                plan = ops.plan_decode_cascade(kv_lens, groups, self.model.hkv, self.model.hq // self.model.hkv,
+                                               self.num_ctas, self.max_items)
+        if plan is not None and len(plan.tile_members) <= self.max_requests:
+            ni = len(plan.item_req)
+            s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = plan.item_req, plan.item_start, plan.item_end
+            s.h("item_slot")[:ni], s.h("item_tile")[:ni] = plan.item_slot, plan.item_tile
+            nt = plan.tile_members.size
+            s.h("tile_members")[:nt] = plan.tile_members.reshape(-1)
+            indptr = plan.req_slot_indptr
+            self.stats["cascade_steps"] = self.stats.get("cascade_steps", 0) + 1
+            self.stats["cascade_tokens_saved"] = self.stats.get("cascade_tokens_saved", 0) + plan.shared_tokens
+        else:
+            plan = None
+            item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items,
+                                                             window_left=self.window_left)
+            ni = len(item_req)
+            s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
+        s.h("req_item_indptr")[:r + 1] = indptr
+        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
+        s.h("num_items")[0] = ni
+        return plan is not None
+
+    @staticmethod
+    def _gkey(rb: int, cascade: bool):
+        return (rb, "cascade") if cascade else rb
+
+    def _capture(self, rb: int, cascade: bool = False) -> _Graph:
+        fi = self._forward_inputs_decode(rb, cascade)
         # warm-up on a side stream (sets kernel attributes, fills allocator pools), then capture
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -360,9 +402,10 @@ class TorchDriver:
         # the decode-attention launcher issues two kernels (split-KV pass + merge) per layer
         return _Graph(g, logits, rb, _lib.LAUNCHES - before + self.cfg.num_hidden_layers)
 
-    def precapture_graphs(self, buckets: Optional[List[int]] = None) -> int:
+    def precapture_graphs(self, buckets: Optional[List[int]] = None, cascade: bool = False) -> int:
         """Capture the decode graphs of the bucket lattice ahead of the first request, so that no fire
-        pays for a capture (the reference pre-captures its lattice at start-up too:
+        pays for a capture (`cascade`: the variant for plans with shared-prefix items; it is captured on
+        first use otherwise). The reference pre-captures its lattice at start-up too (
         driver/cuda/src/entry.cpp, executor/forward_graph.hpp:63-91). The capture runs on a plan
         without attention work or KV writes. Returns the number of graphs captured.
         Under tensor parallelism EVERY rank must call this at the same point of its start-up (before
@@ -373,7 +416,8 @@ class TorchDriver:
         self._bind_thread()
         s, n = self.slab, 0
         for rb in (buckets or self.buckets):
-            if rb in self.graphs or rb > self.max_requests:
+            key = self._gkey(rb, cascade)
+            if key in self.graphs or rb > self.max_requests:
                 continue
             s.h("tokens")[:rb] = 0
             s.h("positions")[:rb] = 0
@@ -382,7 +426,7 @@ class TorchDriver:
             s.h("req_item_indptr")[:rb + 1] = 0
             s.h("num_items")[0] = 0
             s.upload("tile_qstart")
-            self.graphs[rb] = self._capture(rb)
+            self.graphs[key] = self._capture(rb, cascade)
             n += 1
         torch.cuda.synchronize(self.device)
         ops.kernel_status(self.device).zero_()
@@ -404,23 +448,19 @@ class TorchDriver:
             s.h("positions")[r:rb] = 0
             s.h("slots")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
-        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items, window_left=self.window_left)
-        ni = len(item_req)
-        s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
-        s.h("req_item_indptr")[:r + 1] = indptr
-        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
-        s.h("num_items")[0] = ni
+        cascade = self._plan_decode(kv_lens, np.asarray(req.kv_page_indptr), np.asarray(req.kv_page_indices), r, rb)
         s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
         if self.use_graphs:
-            if rb not in self.graphs:
-                self.graphs[rb] = self._capture(rb)
+            key = self._gkey(rb, cascade)
+            if key not in self.graphs:
+                self.graphs[key] = self._capture(rb, cascade)
                 s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
-            g = self.graphs[rb]
+            g = self.graphs[key]
             g.graph.replay()
             self.stats["graph_replays"] += 1
             return g.logits
         self.stats["eager"] += 1
-        return self.model.forward(self._forward_inputs_decode(rb), self.kv.data)
+        return self.model.forward(self._forward_inputs_decode(rb, cascade), self.kv.data)
 
     def _mask_rows_for_request(self, req: ForwardRequest, r: int, ql: int, kl: int):
         if req.has_user_mask is not None and req.has_user_mask[r]:
@@ -651,41 +691,36 @@ class TorchDriver:
             s.h("slots")[r:rb] = -1
             s.h("src_row")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = step.page_indptr[-1]
-        item_req, st, en, indptr = ops.plan_decode_items(step.kv_lens, self.model.hkv, self.num_ctas, self.max_items, window_left=self.window_left)
-        ni = len(item_req)
-        s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
-        s.h("req_item_indptr")[:r + 1] = indptr
-        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
-        s.h("num_items")[0] = ni
+        cascade = self._plan_decode(step.kv_lens, step.page_indptr, step.page_indices, r, rb)
         s.h("temperature", np.float32)[:r] = step.temperature
         s.h("top_k")[:r] = step.top_k
         s.h("top_p", np.float32)[:r] = step.top_p
         s.h("min_p", np.float32)[:r] = step.min_p
         s.h("seeds", np.int64)[:r] = step.seeds
         if self.par.tp_size > 1 and self.par.comm is not None:
-            self.par.comm.publish_decode(s, r, rb, npg, parity)
-        if self.use_graphs and rb not in self.graphs:
+            self.par.comm.publish_decode(s, r, rb, npg, parity, cascade)
+        if self.use_graphs and self._gkey(rb, cascade) not in self.graphs:
             s.upload("tile_qstart", ("page_indices", npg))
-            self.graphs[rb] = self._capture(rb)
-        self._launch_decode(r, rb, npg, parity)
+            self.graphs[self._gkey(rb, cascade)] = self._capture(rb, cascade)
+        self._launch_decode(r, rb, npg, parity, cascade)
         ev = torch.cuda.Event()
         ev.record()
         self.stats["fires"] += 1
         return AsyncTokens(ev, self.cohort_host[parity & 1], r, driver=self)
 
-    def _launch_decode(self, r: int, rb: int, npg: int, parity: int) -> None:
+    def _launch_decode(self, r: int, rb: int, npg: int, parity: int, cascade: bool = False) -> None:
         """Device side of a pipelined decode step (also what tensor-parallel followers run)."""
         s = self.slab
         s.upload("tile_qstart", ("page_indices", npg))
         cur, prev = self.cohort_sampled[parity & 1], self.cohort_sampled[(parity & 1) ^ 1]
         ops.feed_tokens(s.d("tokens"), s.d("src_row"), prev, r)
         if self.use_graphs:
-            g = self.graphs[rb]
+            g = self.graphs[self._gkey(rb, cascade)]
             g.graph.replay()
             logits = g.logits
             self.stats["graph_replays"] += 1
         else:
-            logits = self.model.forward(self._forward_inputs_decode(rb), self.kv.data)
+            logits = self.model.forward(self._forward_inputs_decode(rb, cascade), self.kv.data)
             self.stats["eager"] += 1
         self._sample(logits[:r], r, None, None, cur)
         self.cohort_host[parity & 1][:r].copy_(cur[:r], non_blocking=True)
@@ -731,21 +766,17 @@ class TorchDriver:
             s.h("positions")[r:rb] = 0
             s.h("slots")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
-        item_req, st, en, indptr = ops.plan_decode_items(kv_lens, self.model.hkv, self.num_ctas, self.max_items, window_left=self.window_left)
-        ni = len(item_req)
-        s.h("item_req")[:ni], s.h("item_start")[:ni], s.h("item_end")[:ni] = item_req, st, en
-        s.h("req_item_indptr")[:r + 1] = indptr
-        s.h("req_item_indptr")[r + 1:rb + 1] = indptr[-1]
-        s.h("num_items")[0] = ni
+        cascade = self._plan_decode(kv_lens, np.asarray(req.kv_page_indptr), np.asarray(req.kv_page_indices), r, rb)
         o, n = s.offsets["tile_qstart"]
         end = o + n
         po, _ = s.offsets["page_indices"]
         npg = len(req.kv_page_indices)
-        if rb not in self.graphs:
+        key = self._gkey(rb, cascade)
+        if key not in self.graphs:
             s.upload("tile_qstart", ("page_indices", npg))
-            self.graphs[rb] = self._capture(rb)
+            self.graphs[key] = self._capture(rb, cascade)
         return {"fixed": s.host[:end].to(self.device), "pages": s.host[po:po + npg].to(self.device),
-                "rb": rb, "r": r, "end": end, "po": po, "npg": npg}
+                "rb": rb, "r": r, "end": end, "po": po, "npg": npg, "key": key}
 
     def replay_staged(self, st: dict, feed_sampled: bool) -> None:
         self._bind_thread()
@@ -755,7 +786,7 @@ class TorchDriver:
         r = st["r"]
         if feed_sampled:
             s.d("tokens", r).copy_(self.sampled[:r], non_blocking=True)
-        g = self.graphs[st["rb"]]
+        g = self.graphs[st.get("key", st["rb"])]
         g.graph.replay()
         self._sample(g.logits[:r], r, None, None, self.sampled)
 

@@ -519,6 +519,117 @@ def plan_decode_items(kv_lens: np.ndarray, hkv: int, target_ctas: int, max_items
     return item_req, start.astype(np.int32), end.astype(np.int32), indptr
 
 
+@dataclass
+class CascadePlan:
+    """Host side of a decode plan with shared-prefix items (see `plan_decode_cascade`)."""
+    item_req: np.ndarray
+    item_start: np.ndarray
+    item_end: np.ndarray
+    item_slot: np.ndarray
+    item_tile: np.ndarray
+    tile_members: np.ndarray      # [tiles, 16]
+    req_slot_indptr: np.ndarray
+    shared_tokens: int            # KV tokens that are read once instead of once per member
+    groups: int
+
+
+def find_shared_prefixes(kv_lens: np.ndarray, page_indptr: np.ndarray, page_indices: np.ndarray, page_size: int,
+                         min_shared_tokens: int = 256):
+    """Groups of requests whose leading KV pages are the same physical pages (forks of one context).
+    Returns [(members int32 array, shared_tokens)] for groups of two or more requests that share at
+    least `min_shared_tokens`; shared_tokens is a multiple of the page size."""
+    r = len(kv_lens)
+    if r < 2:
+        return []
+    indptr = np.asarray(page_indptr, dtype=np.int64)
+    npages = np.diff(indptr)
+    pages = np.asarray(page_indices)
+    first = np.where(npages > 0, pages[np.minimum(indptr[:-1], max(0, len(pages) - 1))], -1 - np.arange(r))
+    order = np.argsort(first, kind="stable")
+    sf = first[order]
+    cut = np.flatnonzero(np.diff(sf)) + 1
+    out = []
+    for a, b in zip(np.concatenate([[0], cut]), np.concatenate([cut, [r]])):
+        if b - a < 2 or sf[a] < 0:
+            continue
+        mem = order[a:b]
+        n = int(npages[mem].min())
+        if n * page_size < min_shared_tokens:
+            continue
+        lead = pages[indptr[mem[0]]:indptr[mem[0]] + n]
+        lcp = n
+        for m in mem[1:]:
+            diff = np.flatnonzero(pages[indptr[m]:indptr[m] + n] != lead)
+            if diff.size:
+                lcp = min(lcp, int(diff[0]))
+        # the page that receives this step's token is private, and so is everything after it
+        lcp = min(lcp, int(((np.asarray(kv_lens)[mem] - 1) // page_size).min()))
+        if lcp * page_size >= min_shared_tokens:
+            out.append((np.sort(mem).astype(np.int32), lcp * page_size))
+    return out
+
+
+def plan_decode_cascade(kv_lens: np.ndarray, groups, hkv: int, group_size: int, target_ctas: int, max_items: int,
+                        min_chunk: int = 256) -> Optional[CascadePlan]:
+    """Decode plan in which every group of `groups` (from `find_shared_prefixes`) reads its shared
+    prefix once: per group and per tile of 16 // group_size members, shared items over the prefix in
+    chunks; per request, unshared items over the rest. A request's partial results occupy consecutive
+    slots (shared chunks first). Returns None when there is nothing to share or the plan would not
+    fit `max_items` slots / items."""
+    memb = max(1, 16 // group_size)
+    if not groups or memb < 2:        # 16 query heads per KV head fill the tile: nothing to pack
+        return None
+    kv = np.asarray(kv_lens, dtype=np.int64)
+    r = len(kv)
+    shared = np.zeros(r, np.int64)
+    for mem, st in groups:
+        shared[mem] = st
+    own = kv - shared
+    tiles_of = [-(-len(mem) // memb) for mem, _ in groups]
+    work = int(own.sum()) + sum(st * t for (_, st), t in zip(groups, tiles_of))
+    chunk = max(min_chunk, -(-work * hkv // max(1, target_ctas * _DECODE_UNITS_PER_CTA)))
+    chunk = -(-chunk // 16) * 16
+    while True:
+        n_sh = -(-shared // chunk)
+        n_own = np.maximum(1, -(-own // chunk))
+        n_items = int(n_own.sum()) + sum(int(-(-st // chunk)) * t for (_, st), t in zip(groups, tiles_of))
+        if int((n_sh + n_own).sum()) <= max_items and n_items <= max_items:
+            break
+        chunk *= 2
+        if chunk > (1 << 22):
+            return None
+    indptr = np.zeros(r + 1, np.int32)
+    indptr[1:] = np.cumsum(n_sh + n_own)
+    i_req, i_st, i_en, i_slot, i_tile, members = [], [], [], [], [], []
+    for (mem, st), nt in zip(groups, tiles_of):
+        nch = int(-(-st // chunk))
+        for t in range(nt):
+            row = np.full(16, -1, np.int32)
+            part = mem[t * memb:(t + 1) * memb]
+            row[:len(part)] = part
+            tid = len(members)
+            members.append(row)
+            c = np.arange(nch, dtype=np.int64)
+            i_req.append(np.full(nch, part[0], np.int32))
+            i_st.append(c * chunk)
+            i_en.append(np.minimum((c + 1) * chunk, st))
+            i_slot.append(c)
+            i_tile.append(np.full(nch, tid, np.int32))
+    req = np.repeat(np.arange(r, dtype=np.int32), n_own)
+    base = np.zeros(r + 1, np.int64)
+    base[1:] = np.cumsum(n_own)
+    within = np.arange(int(base[-1]), dtype=np.int64) - np.repeat(base[:-1], n_own)
+    st_own = shared[req] + within * chunk
+    i_req.append(req)
+    i_st.append(st_own)
+    i_en.append(np.minimum(st_own + chunk, kv[req]))
+    i_slot.append(indptr[:-1].astype(np.int64)[req] + n_sh[req] + within)
+    i_tile.append(np.full(len(req), -1, np.int32))
+    cat = lambda xs: np.concatenate(xs).astype(np.int32)
+    return CascadePlan(cat(i_req), cat(i_st), cat(i_en), cat(i_slot), cat(i_tile), np.stack(members).astype(np.int32),
+                       indptr, int(sum(st * (len(mem) - t) for (mem, st), t in zip(groups, tiles_of))), len(groups))
+
+
 def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int) -> int:
     """Packed (token, head) rows per prefill tile: 256 (two MMA tiles per CTA; ``PIE_PREFILL_TC=128``
     for one) where the tcgen05 kernel covers the shape (head_dim 64 or 128, 16-token pages, group size
@@ -565,6 +676,10 @@ class DecodePlan:
     num_ctas: int
     page_size: int
     window_left: int = -1
+    # shared-prefix plans (`plan_decode_cascade`): slot / tile of every item and the members of every tile
+    item_slot: Optional[torch.Tensor] = None
+    item_tile: Optional[torch.Tensor] = None
+    tile_members: Optional[torch.Tensor] = None
 
 
 def decode_scratch_floats(max_items: int, hq: int, head_dim: int) -> int:
@@ -581,6 +696,14 @@ def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=N
     wl = plan.window_left if window_left is None else window_left
     r, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    if plan.item_tile is not None:
+        check(fn("pie_paged_decode_attn_cascade")(
+            ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
+            ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),
+            ptr(out), ptr(plan.scratch), plan.max_items, plan.num_reqs, hq, hkv, d, plan.page_size,
+            sm_scale, plan.num_ctas, ptr(sinks_log2), ptr(plan.item_slot), ptr(plan.item_tile),
+            ptr(plan.tile_members), stream_ptr()), "paged_decode_attn_cascade")
+        return out
     check(fn("pie_paged_decode_attn_window")(
         ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
         ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),

@@ -358,14 +358,14 @@ class TPComm:
         data = np.frombuffer(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL), dtype=np.uint8)
         self.ring.publish(KIND_BATCH, data)
 
-    def publish_decode(self, slab, r: int, rb: int, npg: int, parity: int) -> None:
+    def publish_decode(self, slab, r: int, rb: int, npg: int, parity: int, cascade: bool = False) -> None:
         if self.rank != 0 or self.ring is None:
             return
         o, n = slab.offsets["tile_qstart"]
         end = o + n
         po, _ = slab.offsets["page_indices"]
         buf = np.concatenate([slab.np[:end], slab.np[po:po + npg]])
-        self.ring.publish(KIND_DECODE, buf, (r, rb, npg, parity, end))
+        self.ring.publish(KIND_DECODE, buf, (r, rb, npg, parity, end, int(cascade)))
 
     def publish_copy(self, req) -> None:
         if self.rank != 0 or self.ring is None:
@@ -415,6 +415,7 @@ class TPComm:
                 driver.fire_batch(req)
             elif kind == KIND_DECODE:
                 r, rb, npg, parity, end = meta[:5]
+                cascade = bool(meta[5])
                 s = driver.slab
                 s.select(parity)
                 words = payload.view(np.int32)
@@ -422,10 +423,11 @@ class TPComm:
                 po, _ = s.offsets["page_indices"]
                 s.np[po:po + npg] = words[end:end + npg]
                 ring.ack()
-                if driver.use_graphs and rb not in driver.graphs:
+                key = driver._gkey(rb, cascade)
+                if driver.use_graphs and key not in driver.graphs:
                     s.upload("tile_qstart", ("page_indices", npg))
-                    driver.graphs[rb] = driver._capture(rb)
-                driver._launch_decode(r, rb, npg, parity)
+                    driver.graphs[key] = driver._capture(rb, cascade)
+                driver._launch_decode(r, rb, npg, parity, cascade)
             elif kind == KIND_COPY:
                 req = pickle.loads(payload.tobytes())
                 ring.ack()

@@ -129,3 +129,49 @@ def test_precaptured_graphs_serve_decode_without_new_captures():
         ops.check_kernel_status(drv.device)
     for a, b in zip(*outs):
         assert np.array_equal(a, b)
+
+
+def test_forked_contexts_decode_through_the_cascade_plan(monkeypatch):
+    """Eight branches forked from one 300-token prefix (the agentic fork pattern): the driver finds
+    the shared pages, serves the decode steps with the shared-prefix plan (its own graph variant)
+    and gives the logits of the plain plan."""
+    cfg = small_cfg()
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=3, std=0.05)
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    rng = np.random.default_rng(4)
+    prefix = rng.integers(0, cfg.vocab_size, 304).tolist()       # 19 full pages
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("PIE_CASCADE", mode)
+        drv = TorchDriver(cfg, "cuda", weights=w, num_pages=128, page_size=16, max_requests=16, max_tokens=1024)
+        assert drv.cascade == (mode == "1")
+        shared = list(range(19))
+        drv.fire_batch(fold([PendingRequest(0, prefix, list(range(304)), shared, 0, [])], 16))
+        branches = 8
+        pages = [shared + [19 + b] for b in range(branches)] + [[40, 41]]        # plus one unrelated request
+        kv = [304] * branches + [0]
+        toks = [[int(t)] for t in rng.integers(0, cfg.vocab_size, branches)] + [list(range(5, 25))]
+        if mode == "0":
+            toks = outs["toks"]
+        outs["toks"] = toks
+        # the unrelated request needs its own prefill before it can decode
+        drv.fire_batch(fold([PendingRequest(8, toks[8], list(range(20)), pages[8], 0, [])], 16))
+        kv[8], toks8 = 20, [3]
+        logits = []
+        for step in range(3):
+            items = [PendingRequest(i, toks[i] if i < 8 else toks8, [kv[i] + step], pages[i], kv[i] + step, [(0, raw)])
+                     for i in range(branches + 1)]
+            resp = drv.fire_batch(fold(items, 16))
+            logits.append([np.frombuffer(s_.logits, dtype=np.float32).copy() for s_ in resp.slots])
+        from pie_b200 import ops
+        ops.check_kernel_status(drv.device)
+        outs[mode] = logits
+        if mode == "1":
+            assert drv.stats.get("cascade_steps", 0) == 3 and (16, "cascade") in drv.graphs
+            assert drv.stats["cascade_tokens_saved"] == 3 * 304 * (8 - 2)        # two tiles of four members
+        else:
+            assert drv.stats.get("cascade_steps", 0) == 0
+    for a, b in zip(outs["1"], outs["0"]):
+        for x, y in zip(a, b):
+            assert np.abs(x - y).max() < 0.05 * max(1.0, np.abs(y).max())
+            assert int(x.argmax()) == int(y.argmax())

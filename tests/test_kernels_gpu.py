@@ -129,6 +129,66 @@ def test_paged_decode_attention(d, hq, hkv):
     close(out, want, 2e-2)
 
 
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (128, 4, 1), (64, 16, 2), (128, 16, 16), (128, 16, 1)])
+def test_paged_decode_attention_shared_prefix(d, hq, hkv):
+    """Forks of one context share their leading pages: the cascade plan reads those pages once per
+    tile of members and must give what the plain per-request plan gives."""
+    page = 16
+    rng = np.random.default_rng(5)
+    tables, kv_lens = [], []
+    nxt = 0
+    for g, (members, shared_pages) in enumerate([(8, 40), (3, 17), (11, 64)]):
+        shared = list(range(nxt, nxt + shared_pages))
+        nxt += shared_pages
+        for b in range(members):
+            own_n = int(rng.integers(1, 9))
+            tables.append(shared + list(range(nxt, nxt + own_n)))
+            nxt += own_n
+            kv_lens.append(shared_pages * page + (own_n - 1) * page + int(rng.integers(1, page + 1)))
+    for n in (1, 3, 70):                                   # requests that share nothing
+        tables.append(list(range(nxt, nxt + n)))
+        nxt += n
+        kv_lens.append((n - 1) * page + int(rng.integers(1, page + 1)))
+    order = rng.permutation(len(tables))
+    tables, kv_lens = [tables[i] for i in order], np.array([kv_lens[i] for i in order], dtype=np.int32)
+    r = len(tables)
+    phys = rng.permutation(nxt + 7)[:nxt].astype(np.int32)          # logical -> physical page ids
+    indptr = np.zeros(r + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum([len(t) for t in tables])
+    pages = np.concatenate([phys[np.array(t)] for t in tables]).astype(np.int32)
+    kv = bf(nxt + 7, 2, hkv, page, d, seed=71)
+    q = bf(r, hq, d, seed=72)
+    groups = ops.find_shared_prefixes(kv_lens, indptr, pages, page, min_shared_tokens=64)
+    assert sorted(len(m) for m, _ in groups) == [3, 8, 11]
+    assert sorted(st for _, st in groups) == [17 * page, 40 * page, 64 * page]
+    cp = ops.plan_decode_cascade(kv_lens, groups, hkv, hq // hkv, target_ctas=64, max_items=4096, min_chunk=256)
+    if hq // hkv == 16:               # one request's heads fill the 16-row tile: no shared items to make
+        assert cp is None
+        return
+    assert cp is not None and cp.shared_tokens > 0
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    max_items = int(cp.req_slot_indptr[-1]) + 5
+    status = ops.kernel_status(DEV)
+    status.zero_()
+    plan = ops.DecodePlan(t(pages), t(indptr), t(cp.item_req), t(cp.item_start), t(cp.item_end), t(cp.req_slot_indptr),
+                          torch.tensor([len(cp.item_req)], dtype=torch.int32, device=DEV),
+                          torch.empty(ops.decode_scratch_floats(max_items, hq, d), device=DEV), max_items, r, 64, page,
+                          item_slot=t(cp.item_slot), item_tile=t(cp.item_tile), tile_members=t(cp.tile_members))
+    scale = 1 / math.sqrt(d)
+    out = ops.paged_decode_attention(q, kv, plan, scale)
+    torch.cuda.synchronize()
+    assert int(status[0].item()) == 0
+    qo = np.arange(r + 1, dtype=np.int32)
+    want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale)
+    close(out, want, 2e-2)
+    # attention sinks merge the same way over shared and unshared slots
+    sinks = torch.linspace(-1.0, 2.0, hq, device=DEV)
+    sl2 = (sinks * 1.4426950408889634).float().contiguous()
+    out = ops.paged_decode_attention(q, kv, plan, scale, sinks_log2=sl2)
+    want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale, sinks=sinks)
+    close(out, want, 2e-2)
+
+
 def test_paged_decode_attention_clamps_work_count():
     """A work count in device memory larger than the scratch was sized for (a stale value on a graph
     replay, an embedder's mistake) must not write past the scratch: the kernel drops the extra items,
