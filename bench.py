@@ -72,6 +72,8 @@ def main():
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+    from pie_b200.bench import configs as _configs
+    _configs._hang_dump()
     if args.config != 2:
         from pie_b200.bench import configs
         return configs.main(["--config", str(args.config), "--steps", str(args.steps), "--warmup", str(args.warmup),

@@ -19,6 +19,16 @@ import json
 import time
 
 
+def _hang_dump() -> None:
+    """PIE_HANG_DUMP_S=N: every N seconds write every thread's Python stack to stderr (all ranks), to see
+    where a run that stopped making progress is waiting."""
+    import os
+    n = float(os.environ.get("PIE_HANG_DUMP_S", "0") or 0)
+    if n > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(n, repeat=True)
+
+
 def main(argv=None):
     import os
     ap = argparse.ArgumentParser()
@@ -31,6 +41,7 @@ def main(argv=None):
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (marks the run invalid)")
     a = ap.parse_args(argv)
+    _hang_dump()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")

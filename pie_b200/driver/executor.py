@@ -174,6 +174,7 @@ class TorchDriver:
         self.max_items = max_requests + self.num_ctas * 8
         # shared-prefix decode plans: forks of one context read their common pages once per step
         import os as _os
+        self._prefix_cache: dict = {}
         self.cascade = (self.cuda and _os.environ.get("PIE_CASCADE", "1") != "0" and self.window_left < 0
                         and self.cfg.layer_types is None)
         rows = max(max_requests, 1024)
@@ -199,6 +200,11 @@ class TorchDriver:
             self.cohort_host = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
             self.status_host = torch.zeros(8, dtype=torch.int32, pin_memory=True)
         self._failed: Optional[str] = None
+        # Fires come from the scheduler thread, page copies (fork, swap) from the threads of the
+        # inferlets: one lock keeps "publish to the tensor-parallel followers + launch here" atomic, so
+        # that every rank sees the same order of fires and copies and the control ring has one writer
+        # at a time.
+        self._order = threading.RLock()
         self.use_graphs = use_graphs and self.cuda
         self.buckets = graph_buckets(max_requests)
         self.graphs: Dict[int, _Graph] = {}
@@ -356,7 +362,8 @@ class TorchDriver:
         s = self.slab
         plan = None
         if self.cascade and r >= 2:
-            groups = ops.find_shared_prefixes(kv_lens, page_indptr, page_indices, self.page_size)
+            groups = ops.find_shared_prefixes(kv_lens, page_indptr, page_indices, self.page_size,
+                                              cache=self._prefix_cache)
             if groups:
                 plan = ops.plan_decode_cascade(kv_lens, groups, self.model.hkv, self.model.hq // self.model.hkv,
                                                self.num_ctas, self.max_items)
@@ -623,6 +630,10 @@ class TorchDriver:
 
     # ------------------------------------------------------------------ public entry points
     def fire_batch(self, req: ForwardRequest) -> ForwardResponse:
+        with self._order:
+            return self._fire_batch(req)
+
+    def _fire_batch(self, req: ForwardRequest) -> ForwardResponse:
         self._bind_thread()
         t0 = time.perf_counter()
         self.stats["fires"] += 1
@@ -664,6 +675,10 @@ class TorchDriver:
         previous pipelined step (device to device), so the host never has to wait for one step's
         result before launching the next; it reads each step's tokens one step late.
         """
+        with self._order:
+            return self._decode_async(step, parity)
+
+    def _decode_async(self, step: "CohortStep", parity: int) -> "AsyncTokens":
         self._bind_thread()
         r = step.r
         ps = self.page_size
@@ -796,10 +811,11 @@ class TorchDriver:
         return self.graphs[rb].launches + 1
 
     def copy(self, req: CopyRequest) -> None:
-        self._bind_thread()
-        if self.par.tp_size > 1 and self.par.comm is not None:
-            self.par.comm.publish_copy(req)     # every rank holds a shard of each page
-        self.kv.copy(req)
+        with self._order:
+            self._bind_thread()
+            if self.par.tp_size > 1 and self.par.comm is not None:
+                self.par.comm.publish_copy(req)     # every rank holds a shard of each page
+            self.kv.copy(req)
 
     def check_status_host(self) -> None:
         """Raise if a kernel gave up on a bounded wait (reads the pinned copy of the status word

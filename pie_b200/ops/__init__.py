@@ -534,38 +534,55 @@ class CascadePlan:
 
 
 def find_shared_prefixes(kv_lens: np.ndarray, page_indptr: np.ndarray, page_indices: np.ndarray, page_size: int,
-                         min_shared_tokens: int = 256):
+                         min_shared_tokens: int = 256, cache: Optional[dict] = None):
     """Groups of requests whose leading KV pages are the same physical pages (forks of one context).
     Returns [(members int32 array, shared_tokens)] for groups of two or more requests that share at
-    least `min_shared_tokens`; shared_tokens is a multiple of the page size."""
+    least `min_shared_tokens`; shared_tokens is a multiple of the page size.
+
+    `cache` (a dict the caller keeps between steps) remembers the groups and their common page count
+    for a batch with the same rows in the same order: page lists only grow at their private tail from
+    one decode step to the next, so a step then only re-checks the lengths."""
     r = len(kv_lens)
     if r < 2:
         return []
+    kv = np.asarray(kv_lens, dtype=np.int64)
     indptr = np.asarray(page_indptr, dtype=np.int64)
     npages = np.diff(indptr)
     pages = np.asarray(page_indices)
     first = np.where(npages > 0, pages[np.minimum(indptr[:-1], max(0, len(pages) - 1))], -1 - np.arange(r))
-    order = np.argsort(first, kind="stable")
-    sf = first[order]
-    cut = np.flatnonzero(np.diff(sf)) + 1
+    key = (r, first.tobytes())
+    found = cache.get(key) if cache is not None else None
+    if found is not None:
+        # still valid if every member still holds at least the remembered common pages
+        if any(int(npages[mem].min()) < lcp for mem, lcp in found):
+            found = None
+    if found is None:
+        order = np.argsort(first, kind="stable")
+        sf = first[order]
+        cut = np.flatnonzero(np.diff(sf)) + 1
+        found = []
+        for a, b in zip(np.concatenate([[0], cut]), np.concatenate([cut, [r]])):
+            if b - a < 2 or sf[a] < 0:
+                continue
+            mem = order[a:b]
+            n = int(npages[mem].min())
+            if n * page_size < min_shared_tokens:
+                continue
+            block = pages[indptr[mem][:, None] + np.arange(n)[None, :]]          # [members, n]
+            differ = (block != block[0:1]).any(axis=0)
+            lcp = int(np.argmax(differ)) if differ.any() else n
+            if lcp * page_size >= min_shared_tokens:
+                found.append((np.sort(mem).astype(np.int32), lcp))
+        if cache is not None:
+            if len(cache) > 64:
+                cache.clear()
+            cache[key] = found
     out = []
-    for a, b in zip(np.concatenate([[0], cut]), np.concatenate([cut, [r]])):
-        if b - a < 2 or sf[a] < 0:
-            continue
-        mem = order[a:b]
-        n = int(npages[mem].min())
-        if n * page_size < min_shared_tokens:
-            continue
-        lead = pages[indptr[mem[0]]:indptr[mem[0]] + n]
-        lcp = n
-        for m in mem[1:]:
-            diff = np.flatnonzero(pages[indptr[m]:indptr[m] + n] != lead)
-            if diff.size:
-                lcp = min(lcp, int(diff[0]))
+    for mem, lcp in found:
         # the page that receives this step's token is private, and so is everything after it
-        lcp = min(lcp, int(((np.asarray(kv_lens)[mem] - 1) // page_size).min()))
-        if lcp * page_size >= min_shared_tokens:
-            out.append((np.sort(mem).astype(np.int32), lcp * page_size))
+        n = min(lcp, int(((kv[mem] - 1) // page_size).min()))
+        if n * page_size >= min_shared_tokens:
+            out.append((mem, n * page_size))
     return out
 
 
