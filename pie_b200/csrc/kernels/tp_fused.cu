@@ -47,6 +47,11 @@ tp_reduce_norm_push_kernel(const __grid_constant__ TpNormArgs a) {
     __shared__ int s_ok;
     const int row = blockIdx.x;
     const int nvec = a.hidden >> 3;
+    // Launched with programmatic stream serialisation: the block may be resident while the GEMM that
+    // feeds it drains (no launch gap), but the epoch it compares the flags with is bumped by that GEMM,
+    // so nothing is read before the grid dependency resolves.
+    pdl_trigger();
+    pdl_wait();
     if (threadIdx.x == 0) {
         int ok = 1;
         if (a.reduce) {
@@ -273,11 +278,12 @@ PIE_API int pie_tp_reduce_norm_push(const void* blob, void* residual, const void
     a.residual = (bf16*)residual; a.weight = (const bf16*)weight;
     a.rows_per_rank = rows_per_rank; a.hidden = hidden; a.valid_rows = valid_rows; a.reduce = reduce; a.eps = eps;
     const int per = (hidden / 8 + 255) / 256;
-    if (per <= 1) tp_reduce_norm_push_kernel<1><<<rows_per_rank, 256, 0, st>>>(a);
-    else if (per <= 2) tp_reduce_norm_push_kernel<2><<<rows_per_rank, 256, 0, st>>>(a);
-    else if (per <= 4) tp_reduce_norm_push_kernel<4><<<rows_per_rank, 256, 0, st>>>(a);
-    else tp_reduce_norm_push_kernel<8><<<rows_per_rank, 256, 0, st>>>(a);
-    return (int)cudaGetLastError();
+    cudaError_t e;
+    if (per <= 1) e = launch_pdl(tp_reduce_norm_push_kernel<1>, dim3(rows_per_rank), dim3(256), 0, st, a);
+    else if (per <= 2) e = launch_pdl(tp_reduce_norm_push_kernel<2>, dim3(rows_per_rank), dim3(256), 0, st, a);
+    else if (per <= 4) e = launch_pdl(tp_reduce_norm_push_kernel<4>, dim3(rows_per_rank), dim3(256), 0, st, a);
+    else e = launch_pdl(tp_reduce_norm_push_kernel<8>, dim3(rows_per_rank), dim3(256), 0, st, a);
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 PIE_API int pie_tp_wait_ag(const int* ag_flags, const int* ag_epoch, int world, int* status,
