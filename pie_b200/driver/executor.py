@@ -136,7 +136,8 @@ class TorchDriver:
     def __init__(self, cfg: ModelConfig, device="cuda", weights: Optional[dict] = None, num_pages: int = 0,
                  page_size: int = 16, max_requests: int = 512, max_tokens: int = 8192, seed: int = 0,
                  par: Optional[ParallelContext] = None, gemm_backend: str = "tcgen05", use_graphs: bool = True,
-                 swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0):
+                 swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0,
+                 memory_profile: str = ""):
         self.cfg = cfg
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
@@ -155,8 +156,10 @@ class TorchDriver:
         self.model = Transformer(cfg, weights, self.device, self.dtype, self.par, gemm_backend)
         self.page_size = page_size
         hkv = self.model.hkv
+        self.memory_plan = None
         if num_pages <= 0:
-            num_pages = self._plan_pages(hkv, gpu_mem_utilization)
+            num_pages, max_requests, max_tokens = self._plan_memory(gpu_mem_utilization, memory_profile, max_requests,
+                                                                    max_tokens)
             if self.par.tp_size > 1:
                 # page ids are global to the replica: every rank must hold the same number of pages
                 import torch.distributed as dist
@@ -212,14 +215,28 @@ class TorchDriver:
         self.stats = {"fires": 0, "graph_replays": 0, "eager": 0, "kernel_launches": 0}
 
     # ------------------------------------------------------------------ planning
-    def _plan_pages(self, hkv: int, util: float) -> int:
-        per_page = KVCache.bytes_per_page(self.cfg.num_hidden_layers, hkv, self.page_size, self.cfg.head_dim,
-                                          torch.tensor([], dtype=self.dtype).element_size())
+    def _plan_memory(self, util: float, profile: str, max_requests: int, max_tokens: int):
+        """KV pages (and, with a named profile, the forward limits) from what the device has left once
+        the weights are resident: `driver.memory_planner` splits `util` of the device between the
+        activation arena of the largest pass and the page pool. Without a profile the caller's limits
+        stand and only the page count is planned. Returns (pages, max_requests, max_tokens)."""
+        from . import memory_planner as mp
         if not self.cuda:
-            return 4096
+            return 4096, max_requests, max_tokens
         free, total = torch.cuda.mem_get_info(self.device)
-        budget = int(total * util) - (total - free) - (6 << 30)  # activations / workspace headroom
-        return max(64, budget // per_page)
+        usable = int(total * util) - (total - free)          # what `util` of the device leaves beside the weights
+        tp = self.par.tp_size
+        if profile:
+            plan = mp.plan(self.cfg, usable, 1.0, profile, self.page_size, tp)
+            max_requests, max_tokens = plan.max_requests, plan.max_tokens
+        else:
+            arena = mp.arena_bytes(self.cfg, max_tokens, max_requests, tp)
+            per_page = mp.kv_bytes_per_page(self.cfg, self.page_size, tp)
+            pages = max(0, (usable - arena - (4 << 30)) // per_page)     # 4 GiB for the graphs' private pools and workspaces
+            plan = mp.MemoryPlan("explicit", self.page_size, int(pages), max_requests, max_tokens, 0, arena,
+                                 int(pages) * per_page)
+        self.memory_plan = plan
+        return max(64, plan.kv_pages), max_requests, max_tokens
 
     # ------------------------------------------------------------------ adapters
     def create_adapter(self, adapter_id: int, rank: int, alpha: float, seed: int = 0) -> None:

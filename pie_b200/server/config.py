@@ -74,6 +74,7 @@ class DriverConfig:
     cuda_graphs: bool = True
     gemm: str = "tcgen05"
     tp_backend: str = "fused"
+    memory_profile: str = ""              # "" = built-in limits; auto | latency | balanced | throughput | capacity
 
 
 @dataclass

@@ -83,7 +83,8 @@ def build_drivers(m: ModelSection):
         if m.path:
             _, weights = loader.load_checkpoint(m.path, dev, world, rank, ep=d.expert_parallel)
         drv = TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, par=par, gemm_backend=d.gemm,
-                          use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization)
+                          use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
+                          memory_profile=d.memory_profile)
         comm.attach(drv)
         if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
             n = drv.precapture_graphs()      # every rank is here: the warm-up forwards run in lock step
@@ -97,7 +98,7 @@ def build_drivers(m: ModelSection):
         swap = int(d.swap_pool_gb * (1 << 30) // per_page)
         drivers.append(TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, gemm_backend=d.gemm,
                                    use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
-                                   swap_pages=swap))
+                                   swap_pages=swap, memory_profile=d.memory_profile))
         if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
             n = drivers[-1].precapture_graphs()
             log.info("model %s on %s: %d decode graphs captured ahead of time", m.name, dev, n)

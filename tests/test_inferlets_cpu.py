@@ -285,3 +285,82 @@ def test_agents_template_microbench_and_trim_bench(eng):
                                             "body": json.dumps({"prompt_tokens": PROMPT, "max_tokens": 3})}))
     assert h["status"] == 200 and "completion" in json.loads(h["body"])
     assert json.loads(run(eng, "http-server", {"method": "GET", "path": "/"}))["status"] == 200
+
+
+def test_cacheback_decoding_equals_greedy(eng):
+    out = json.loads(run(eng, "cacheback-decoding", {"prompt_tokens": PROMPT, "draft_len": 3, "max_tokens": 12}))
+    ref = json.loads(run(eng, "text-completion", {"prompt_tokens": PROMPT, "max_tokens": 12, "stop_tokens": []}))
+    assert out["tokens"] == ref["tokens"]
+    # the drafter is the same model here: every draft is accepted, so each pass yields draft_len + 1 tokens
+    assert out["passes"] == 3 and out["mean_accepted"] == 3.0
+    assert eng.model_status()["models"]["tiny-llama"]["kv_pages_used"] == 0
+
+
+def test_thought_structure_inferlets(eng):
+    g = json.loads(run(eng, "graph-of-thought", {"prompt_tokens": PROMPT, "proposals": 4, "max_tokens": 4}))
+    assert g["merges"] == 3 and g["levels"] == 2 and len(g["tokens"]) <= 4
+    r = json.loads(run(eng, "recursion-of-thought", {"prompt_tokens": PROMPT, "depth": 1, "max_tokens": 80}))
+    assert r["divide"] >= 1 and r["leaf"] >= 1 and isinstance(r["answer"], str)
+    x = json.loads(run(eng, "reflexion", {"prompt_tokens": PROMPT, "attempts": 3, "max_tokens": 6, "min_len": 4,
+                                          "temperature": 1.0, "forbidden_tokens": list(range(0, 32000, 2))}))
+    assert 1 <= x["attempts"] <= 3 and len(x["lessons"]) == x["attempts"] - (1 if x["solved"] else 0)
+    m = json.loads(run(eng, "mcts", {"prompt_tokens": PROMPT, "iterations": 3, "branching": 2, "step_tokens": 3}))
+    assert m["nodes"] == 7 and m["root_visits"] == 6 and len(m["tokens"]) >= 3
+    assert eng.model_status()["models"]["tiny-llama"]["kv_pages_used"] == 0
+
+
+def test_hierarchical_attention_and_modular_cache(eng):
+    doc = list(range(200, 296))
+    h = json.loads(run(eng, "hierarchical-attention", {"document_tokens": doc, "segment": 32, "summary_tokens": 2,
+                                                       "max_tokens": 4}))
+    assert h["segments"] == 3 and h["summary_tokens"] == 6 and h["visible_positions"] == 6 and len(h["tokens"]) == 4
+    args = {"modules": [list(range(10, 42)), list(range(50, 66))], "question_tokens": [7, 8, 9], "max_tokens": 4}
+    run(eng, "modular-cache", dict(args, clear=True))
+    a = json.loads(run(eng, "modular-cache", args))
+    b = json.loads(run(eng, "modular-cache", args))
+    assert a["modules_reused"] == 0 and a["module_tokens_computed"] == 48
+    assert b["modules_reused"] == 2 and b["module_tokens_computed"] == 0 and a["tokens"] == b["tokens"]
+    c = json.loads(run(eng, "modular-cache", dict(args, modules=[args["modules"][0], list(range(70, 80))])))
+    assert c["modules_reused"] == 1 and c["module_tokens_computed"] == 10
+    run(eng, "modular-cache", dict(args, clear=True))
+
+
+def test_launch_stress_scenarios(eng):
+    f = json.loads(run(eng, "launch-stress", {"scenario": "fanout", "n": 12}))
+    assert f["results"] == [f"echo:{i}" for i in range(12)] and f["distinct_pids"] == 12
+    assert "fail" in json.loads(run(eng, "launch-stress", {"scenario": "failure"}))["error"]
+    assert json.loads(run(eng, "launch-stress", {"scenario": "cancel"}))["cancelled"]
+    assert json.loads(run(eng, "launch-stress", {"scenario": "nested", "depth": 3}))["result"] == "nest(nest(nest(leaf)))"
+    assert json.loads(run(eng, "launch-stress", {"scenario": "unknown-program"}))["error"]
+
+
+def test_codeact_async_lm_knowledge_graph_openresponses(eng):
+    from pie_b200.inferlets.agent_codeact import evaluate
+    assert evaluate("6 * 7") == 42 and evaluate("max(2, 3) ** 2 - abs(-1)") == 8
+    for bad in ("__import__('os')", "a.b", "[1][0]", "2 ** 999"):
+        with pytest.raises(Exception):
+            evaluate(bad)
+    c = json.loads(run(eng, "agent-codeact", {"prompt": "Compute 6*7.", "max_steps": 2, "step_tokens": 120}))
+    assert 1 <= c["turns"] <= 2 and all(("code" in t) or ("finish" in t) or ("error" in t) for t in c["trace"])
+    a = json.loads(run(eng, "async-lm", {"prompt_tokens": PROMPT, "max_tokens": 24, "chunk": 8, "tool_latency_s": 0.0,
+                                         "scripted_calls": ["[CALL] a1 [HEAD] upper(hi) [END]",
+                                                            "[CALL] a2 [HEAD] len(abcd) [END][TRAP][END]"]}))
+    assert a["injected"] == ["[INTR] a1 [HEAD] HI [END]", "[INTR] a2 [HEAD] 4 [END]"] or \
+        sorted(a["injected"]) == sorted(["[INTR] a1 [HEAD] HI [END]", "[INTR] a2 [HEAD] 4 [END]"])
+    assert a["traps"] == 1
+    from pie_b200.inferlets.knowledge_graph import bfs_facts
+    facts = bfs_facts([("ada", "wrote", "notes"), ("notes", "describe", "engines")], "ada", 2)
+    assert "ada wrote notes" in facts and "notes describe engines" in facts
+    k = json.loads(run(eng, "knowledge-graph", {"extract_tokens": 160, "max_tokens": 4}))
+    assert isinstance(k["triples"], list) and isinstance(k["answer"], str)
+    body = json.dumps({"model": "auto", "input": [{"type": "message", "role": "user", "content": "Hello!"}],
+                       "max_output_tokens": 5})
+    r = json.loads(run(eng, "openresponses", {"method": "POST", "path": "/responses", "body": body}))
+    resp = json.loads(r["body"])
+    assert r["status"] == 200 and resp["object"] == "response" and resp["output"][0]["role"] == "assistant"
+    assert resp["usage"]["output_tokens"] <= 5
+    s = json.loads(run(eng, "openresponses", {"method": "POST", "path": "/responses",
+                                              "body": json.dumps({"input": "Hi", "stream": True, "max_output_tokens": 3})}))
+    assert s["headers"]["content-type"] == "text/event-stream"
+    assert s["body"].startswith("event: response.created") and "event: response.completed" in s["body"]
+    assert json.loads(run(eng, "openresponses", {"method": "GET", "path": "/x"}))["status"] == 404

@@ -259,3 +259,17 @@ def test_precapture_is_a_no_op_without_cuda_graphs():
     assert drv.precapture_graphs() == 0 and not drv.graphs
     b = graph_buckets(512)
     assert b[:5] == [1, 2, 4, 8, 16] and b[-1] == 512 and b == sorted(set(b)) and 64 in b and 256 in b
+
+
+def test_driver_config_carries_the_memory_profile():
+    """`[model.driver] memory_profile` reaches the driver, which then takes its forward limits from
+    the planner (on a CPU driver the page count is fixed, the limits still follow the profile's)."""
+    from pie_b200.server import config as cfgmod
+    cfg = cfgmod.parse('[[model]]\nname = "m"\npreset = "tiny-llama"\n[model.driver]\ntype = "cpu"\nmemory_profile = "latency"\n')
+    assert cfg.model[0].driver.memory_profile == "latency"
+    from pie_b200.driver.memory_planner import PROFILES, arena_bytes, plan
+    from pie_b200.models.config import preset
+    c = preset("llama-3.1-8b")
+    p = plan(c, 100 << 30, 1.0, "latency")
+    assert (p.max_requests, p.max_tokens) == (PROFILES["latency"]["max_requests"], PROFILES["latency"]["max_tokens"])
+    assert p.kv_bytes + p.arena_bytes <= (100 << 30) and p.arena_bytes == arena_bytes(c, p.max_tokens, p.max_requests)
