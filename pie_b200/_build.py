@@ -75,7 +75,10 @@ def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda j: _run(*j), jobs))
     if jobs or _newer(objs, KERNEL_LIB):
-        _run([_nvcc(), "-shared", "-o", str(KERNEL_LIB), *map(str, objs), "-Xcompiler", "-fPIC"], "link_kernels")
+        # link beside the target and rename: a reader (or a snapshot of the tree) never sees a half-written library
+        tmp = KERNEL_LIB.with_suffix(".so.tmp")
+        _run([_nvcc(), "-shared", "-o", str(tmp), *map(str, objs), "-Xcompiler", "-fPIC"], "link_kernels")
+        os.replace(tmp, KERNEL_LIB)
     return KERNEL_LIB
 
 
@@ -110,7 +113,9 @@ def build_host(verbose: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda j: _run(*j), jobs))
     if jobs or _newer(objs, target):
-        _run(["g++", "-shared", "-pthread", "-o", str(target), *map(str, objs)], "link_host")
+        tmp = target.with_name(target.name + ".tmp")
+        _run(["g++", "-shared", "-pthread", "-o", str(tmp), *map(str, objs)], "link_host")
+        os.replace(tmp, target)
     return target
 
 

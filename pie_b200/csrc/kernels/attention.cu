@@ -614,6 +614,27 @@ PIE_API int pie_set_status_word(int* word) {
     return 0;
 }
 
+// The status word registered for the current device (null if none): for kernels of other files.
+PIE_API int* pie_status_word_current() { return status_word(); }
+
+// Merge pass of split-KV decode on its own (used by the fp8-KV decode kernel of attention_kv8.cu).
+PIE_API int pie_decode_merge(const float* o_part, const float* lse_part, const int* req_item_indptr, void* out,
+                             int num_reqs, int hq, int hkv, int head_dim, const float* sinks_log2, int max_items,
+                             cudaStream_t st) {
+    if (num_reqs <= 0) return 0;
+    dim3 grid(num_reqs, hq);
+    const int group = hq / hkv;
+    if (head_dim == 128)
+        launch_pdl(paged_decode_merge_kernel<128>, grid, dim3(128), 0, st, o_part, lse_part, req_item_indptr,
+                   (bf16*)out, hq, hkv, group, sinks_log2, max_items);
+    else if (head_dim == 64)
+        launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, o_part, lse_part, req_item_indptr,
+                   (bf16*)out, hq, hkv, group, sinks_log2, max_items);
+    else
+        return (int)cudaErrorInvalidValue;
+    return (int)cudaGetLastError();
+}
+
 // Scratch sizes (in floats) a caller must provide for `max_items` work items.
 PIE_API long pie_decode_attn_scratch_floats(int max_items, int hq, int head_dim) {
     return (long)max_items * hq * head_dim + (long)max_items * hq;

@@ -121,13 +121,16 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
 // the token's KV slot. v heads: copied to the V half.
 // KV layer layout: [pages][2][Hkv][page_size][d]; slot = page*page_size + off.
 // A negative slot skips the KV write (padding tokens of a graph bucket).
-template <int D>
+// KV8: the K and V rows are stored as e4m3 bytes with one fp32 scale per (token, KV head) row,
+// scale = max|x| / 448 (kv_layer then addresses bytes, kv_scale [pages][2][Hkv][page_size] floats).
+template <int D, bool KV8>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kvwrite_kernel(const bf16* __restrict__ qkv, const int* __restrict__ positions,
                             const int* __restrict__ slots, const float* __restrict__ inv_freq,
                             const bf16* __restrict__ qn, const bf16* __restrict__ kn,
                             bf16* __restrict__ q_out, bf16* __restrict__ kv_layer, int n_tokens,
-                            int hq, int hkv, int page_size, float eps, int qkv_stride) {
+                            int hq, int hkv, int page_size, float eps, int qkv_stride,
+                            float* __restrict__ kv_scale) {
     constexpr int EP = D / 64;  // elements per lane per half
     pdl_trigger();
     pdl_wait();
@@ -181,7 +184,24 @@ qk_norm_rope_kvwrite_kernel(const bf16* __restrict__ qkv, const int* __restrict_
         if (slot < 0) return;
         const int page = slot / page_size, off = slot - page * page_size;
         const int kvh = is_k ? (h - hq) : (h - hq - hkv);
-        dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * hkv + kvh) * page_size + off) * D;
+        const size_t row = (((size_t)page * 2 + (is_k ? 0 : 1)) * hkv + kvh) * page_size + off;
+        if (KV8) {
+            float amax = 0.f;
+#pragma unroll
+            for (int e = 0; e < EP; ++e) amax = fmaxf(amax, fmaxf(fabsf(lo[e]), fabsf(hi[e])));
+            amax = warp_max(amax);
+            const float scale = fmaxf(amax, 1e-12f) * (1.0f / 448.0f);
+            const float inv = 1.0f / scale;
+            uint8_t* d8 = reinterpret_cast<uint8_t*>(kv_layer) + row * D;
+#pragma unroll
+            for (int e = 0; e < EP; ++e) {
+                d8[lane * EP + e] = (uint8_t)__nv_cvt_float_to_fp8(lo[e] * inv, __NV_SATFINITE, __NV_E4M3);
+                d8[D / 2 + lane * EP + e] = (uint8_t)__nv_cvt_float_to_fp8(hi[e] * inv, __NV_SATFINITE, __NV_E4M3);
+            }
+            if (lane == 0) kv_scale[row] = scale;
+            return;
+        }
+        dst = kv_layer + row * D;
     }
 #pragma unroll
     for (int e = 0; e < EP; ++e) {
@@ -335,15 +355,37 @@ PIE_API int pie_qk_norm_rope_kvwrite(const void* qkv, const int* positions, cons
     const long warps = (long)n_tokens * (hq + 2 * hkv);
     const int blocks = (int)((warps + 7) / 8);
 #define LAUNCH(D)                                                                               \
-    launch_pdl(qk_norm_rope_kvwrite_kernel<D>, dim3(blocks), dim3(256), 0, st,                  \
+    launch_pdl(qk_norm_rope_kvwrite_kernel<D, false>, dim3(blocks), dim3(256), 0, st,           \
         (const bf16*)qkv, positions, slots, inv_freq, (const bf16*)q_norm_w,                    \
         (const bf16*)k_norm_w, (bf16*)q_out, (bf16*)kv_layer, n_tokens, hq, hkv, page_size, eps, \
-        qkv_stride)
+        qkv_stride, (float*)nullptr)
     if (head_dim == 64) LAUNCH(64);
     else if (head_dim == 128) LAUNCH(128);
     else if (head_dim == 256) LAUNCH(256);
     else return (int)cudaErrorInvalidValue;
 #undef LAUNCH
+    return (int)cudaGetLastError();
+}
+
+// The same with fp8 KV pages: kv_layer holds e4m3 bytes, kv_scale one fp32 per (token, KV head) row.
+PIE_API int pie_qk_norm_rope_kvwrite_kv8(const void* qkv, const int* positions, const int* slots,
+                                         const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
+                                         void* q_out, void* kv_layer, float* kv_scale, int n_tokens, int hq,
+                                         int hkv, int head_dim, int page_size, float eps, int qkv_stride,
+                                         cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (!kv_scale) return (int)cudaErrorInvalidValue;
+    const long warps = (long)n_tokens * (hq + 2 * hkv);
+    const int blocks = (int)((warps + 7) / 8);
+#define LAUNCH8(D)                                                                              \
+    launch_pdl(qk_norm_rope_kvwrite_kernel<D, true>, dim3(blocks), dim3(256), 0, st,            \
+        (const bf16*)qkv, positions, slots, inv_freq, (const bf16*)q_norm_w,                    \
+        (const bf16*)k_norm_w, (bf16*)q_out, (bf16*)kv_layer, n_tokens, hq, hkv, page_size, eps, \
+        qkv_stride, kv_scale)
+    if (head_dim == 64) LAUNCH8(64);
+    else if (head_dim == 128) LAUNCH8(128);
+    else return (int)cudaErrorInvalidValue;
+#undef LAUNCH8
     return (int)cudaGetLastError();
 }
 

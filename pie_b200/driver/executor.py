@@ -137,7 +137,7 @@ class TorchDriver:
                  page_size: int = 16, max_requests: int = 512, max_tokens: int = 8192, seed: int = 0,
                  par: Optional[ParallelContext] = None, gemm_backend: str = "tcgen05", use_graphs: bool = True,
                  swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0,
-                 memory_profile: str = ""):
+                 memory_profile: str = "", kv_dtype: str = "auto"):
         self.cfg = cfg
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
@@ -156,6 +156,7 @@ class TorchDriver:
         self.model = Transformer(cfg, weights, self.device, self.dtype, self.par, gemm_backend)
         self.page_size = page_size
         hkv = self.model.hkv
+        self.kv_dtype = kv_dtype
         self.memory_plan = None
         if num_pages <= 0:
             num_pages, max_requests, max_tokens = self._plan_memory(gpu_mem_utilization, memory_profile, max_requests,
@@ -168,7 +169,8 @@ class TorchDriver:
                     dist.all_reduce(t, op=dist.ReduceOp.MIN)
                     num_pages = int(t.item())
         self.kv = KVCache(cfg.num_hidden_layers, num_pages, hkv, page_size, cfg.head_dim, self.dtype,
-                          self.device, swap_pages)
+                          self.device, swap_pages, kv_dtype=kv_dtype)
+        self.model.kv_scale = self.kv.scale
         self.max_requests, self.max_tokens = max_requests, max_tokens
         self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
         self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
@@ -179,7 +181,7 @@ class TorchDriver:
         import os as _os
         self._prefix_cache: dict = {}
         self.cascade = (self.cuda and _os.environ.get("PIE_CASCADE", "1") != "0" and self.window_left < 0
-                        and self.cfg.layer_types is None)
+                        and self.cfg.layer_types is None and self.kv.scale is None)
         rows = max(max_requests, 1024)
         self.max_rows = rows
         self.slab = _Slab({
@@ -232,6 +234,8 @@ class TorchDriver:
         else:
             arena = mp.arena_bytes(self.cfg, max_tokens, max_requests, tp)
             per_page = mp.kv_bytes_per_page(self.cfg, self.page_size, tp)
+            if self.kv_dtype == "fp8_e4m3":       # one byte per element + an fp32 scale per row
+                per_page = int(per_page * (0.5 + 2.0 / self.cfg.head_dim))
             pages = max(0, (usable - arena - (4 << 30)) // per_page)     # 4 GiB for the graphs' private pools and workspaces
             plan = mp.MemoryPlan("explicit", self.page_size, int(pages), max_requests, max_tokens, 0, arena,
                                  int(pages) * per_page)
@@ -521,7 +525,8 @@ class TorchDriver:
                                    s.d("tile_req"), s.d("tile_qstart"), nt, self.page_size, mask_bits, mask_indptr,
                                    window_left=self.window_left, tile_rows=tile_rows)
             fi = ForwardInputs(s.d("tokens", n), s.d("positions", n), s.d("slots", n), plan,
-                               logit_rows=s.d("logit_rows", len(rows)), is_decode=False)
+                               logit_rows=s.d("logit_rows", len(rows)), is_decode=False,
+                               attn_num_pages=len(req.kv_page_indices))
         else:
             masks = None
             if custom:

@@ -19,9 +19,23 @@ from .schema import CopyDir, CopyRequest
 
 class KVCache:
     def __init__(self, layers: int, num_pages: int, kv_heads: int, page_size: int, head_dim: int,
-                 dtype, device, swap_pages: int = 0):
+                 dtype, device, swap_pages: int = 0, kv_dtype: str = "auto"):
+        """kv_dtype "auto": pages in the activation dtype. "fp8_e4m3": one byte per element plus one
+        fp32 scale per (token, KV head) row in `scale` [layers, pages + 1, 2, kv_heads, page_size]
+        (written by the RoPE + KV-write kernel, read by decode attention; prefill attention works on
+        pages expanded to bf16 for the batch). Counterpart of the reference's per-token-head fp8 format
+        (driver/cuda/src/kv_cache_format.hpp, kernels/kv_paged.cu:188-325)."""
         if page_size % 16:
             raise ValueError("kv page size must be a multiple of 16")
+        if kv_dtype not in ("auto", "bf16", "fp8_e4m3"):
+            raise ValueError(f"unknown kv_dtype {kv_dtype!r} (auto | bf16 | fp8_e4m3)")
+        self.kv_dtype = kv_dtype
+        self.scale = None
+        if kv_dtype == "fp8_e4m3":
+            if torch.device(device).type != "cuda":
+                raise NotImplementedError("fp8 KV pages need the CUDA kernels")
+            dtype = torch.uint8
+            self.scale = torch.zeros(layers, num_pages + 1, 2, kv_heads, page_size, dtype=torch.float32, device=device)
         self.layers, self.num_pages, self.kv_heads = layers, num_pages, kv_heads
         self.page_size, self.head_dim, self.dtype = page_size, head_dim, dtype
         self.device = torch.device(device)
@@ -55,7 +69,11 @@ class KVCache:
             s = torch.from_numpy(src).to(self.device)
             d = torch.from_numpy(dst).to(self.device)
             ops.copy_pages(self.data, s, d)
+            if self.scale is not None:
+                ops.copy_pages(self.scale, s, d)
             return
+        if self.scale is not None:
+            raise NotImplementedError("host swap of fp8 KV pages")
         if self.host is None:
             raise RuntimeError("no swap pool configured")
         if req.direction == CopyDir.H2H:

@@ -32,6 +32,7 @@ class ForwardInputs:
     positions: torch.Tensor       # int32 [N]
     slots: torch.Tensor           # int32 [N]  KV slot (page*page_size+offset) of each new token
     attn: object                  # ops.DecodePlan | ops.PrefillPlan | ops.AttnBatch (CPU)
+    attn_num_pages: Optional[int] = None   # page references of this batch (prefill plans; the slab segment is larger)
     logit_rows: Optional[torch.Tensor] = None   # int32 rows of the hidden state that need logits
     is_decode: bool = False
     lora: Optional[list] = None   # [(LoraAdapter, int64 token rows)] for requests bound to an adapter
@@ -57,6 +58,8 @@ class Transformer:
         self.inv_freq = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, self.device)
         self.gemm_backend = gemm_backend if self.device.type == "cuda" else "torch"
         self.vocab_local = weights["lm_head"].shape[0] * (self.par.tp_size if self.par.comm is not None else 1)
+        # fp8 KV pages: per-(token, head) scales [layers, pages, 2, hkv, page] set by the driver, else None
+        self.kv_scale = None
 
     # ------------------------------------------------------------------ linear algebra
     def _gemm(self, x, w, residual=None, swiglu=False):
@@ -89,8 +92,17 @@ class Transformer:
             sl2 = lw.get("sinks_log2")
             if sl2 is None:
                 sl2 = lw["sinks_log2"] = (sinks.float() * 1.4426950408889634).contiguous()
+        ks = self.kv_scale[li] if self.kv_scale is not None else None
         if fi.is_decode:
-            return ops.paged_decode_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2)
+            return ops.paged_decode_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2,
+                                              kv_scale=ks)
+        if ks is not None:
+            # prefill over fp8 pages: expand the pages this batch reads to bf16 and address them compactly
+            from dataclasses import replace as _replace
+            pages = fi.attn.page_indices[:fi.attn_num_pages] if getattr(fi, "attn_num_pages", None) else fi.attn.page_indices
+            dense = ops.dequant_kv_pages(kv_layer, ks, pages)
+            plan = _replace(fi.attn, page_indices=torch.arange(pages.numel(), dtype=torch.int32, device=pages.device))
+            return ops.paged_prefill_attention(q, dense, plan, self.sm_scale, window_left=wl, sinks_log2=sl2)
         return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2)
 
     def _mlp(self, x, lw, h):
@@ -128,8 +140,9 @@ class Transformer:
                 qkv = qkv + lw["bqkv"]
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, lw.get("q_norm"),
                                          lw.get("k_norm"), kv_cache[li], self.hq, self.hkv, self.d,
-                                         page_size, cfg.rms_norm_eps)
-            a = self._attention(q, kv_cache[li], fi)
+                                         page_size, cfg.rms_norm_eps,
+                                         kv_scale=self.kv_scale[li] if self.kv_scale is not None else None)
+            a = self._attention(q, kv_cache[li], fi, li)
             comm.gemm_rs(a.reshape(n, self.hq * self.d), lw["wo"], n)
             comm.reduce_norm_push(lw["ln2"], cfg.rms_norm_eps, n)
             if "experts_gate_up" in lw:
@@ -182,7 +195,8 @@ class Transformer:
                     qkv[:, qs:qs + ks] = ops.rmsnorm(qkv[:, qs:qs + ks].contiguous(), kn, cfg.rms_norm_eps)
                 qn = kn = None
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, qn, kn, kv_cache[li],
-                                         self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps)
+                                         self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps,
+                                         kv_scale=self.kv_scale[li] if self.kv_scale is not None else None)
             a = self._attention(q, kv_cache[li], fi, li, lw).reshape(n, self.hq * self.d)
             if post:
                 if "experts_gate_up" in lw:

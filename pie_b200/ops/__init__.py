@@ -96,13 +96,24 @@ def swiglu(gate_up, out=None):
 
 
 def qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, kv_layer, hq, hkv,
-                         head_dim, page_size, eps, q_out=None):
+                         head_dim, page_size, eps, q_out=None, kv_scale=None):
+    """Per-head q/k RMSNorm (optional), RoPE, Q out, K/V rows appended into their page slots. With
+    `kv_scale` (fp8 pages: kv_layer is a byte tensor, kv_scale [pages, 2, hkv, page] fp32) the rows are
+    stored as e4m3 with one scale per (token, head)."""
     if not qkv.is_cuda:
+        if kv_scale is not None:
+            raise NotImplementedError("fp8 KV pages need the CUDA kernels")
         return reference.qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w,
                                               kv_layer, hq, hkv, head_dim, page_size, eps)
     n = qkv.shape[0]
     if q_out is None:
         q_out = torch.empty(n, hq, head_dim, dtype=qkv.dtype, device=qkv.device)
+    if kv_scale is not None:
+        check(fn("pie_qk_norm_rope_kvwrite_kv8")(ptr(qkv), ptr(positions), ptr(slots), ptr(inv_freq), ptr(q_norm_w),
+                                                 ptr(k_norm_w), ptr(q_out), ptr(kv_layer), ptr(kv_scale), n, hq, hkv,
+                                                 head_dim, page_size, eps, qkv.stride(0), stream_ptr()),
+              "qk_norm_rope_kvwrite_kv8")
+        return q_out
     check(fn("pie_qk_norm_rope_kvwrite")(ptr(qkv), ptr(positions), ptr(slots), ptr(inv_freq),
                                          ptr(q_norm_w), ptr(k_norm_w), ptr(q_out), ptr(kv_layer), n,
                                          hq, hkv, head_dim, page_size, eps, qkv.stride(0),
@@ -703,8 +714,21 @@ def decode_scratch_floats(max_items: int, hq: int, head_dim: int) -> int:
     return max_items * hq * head_dim + max_items * hq
 
 
+def dequant_kv_pages(kv8_layer, scale_layer, pages: torch.Tensor, pad_zero_page: bool = True) -> torch.Tensor:
+    """fp8 pages `pages` (int32, device) of one layer expanded to a compact bf16 tensor
+    [len(pages) (+ 1 zero page), 2, hkv, page, d]; page j of the result is source page pages[j]."""
+    n = pages.numel()
+    _, two, hkv, page, d = kv8_layer.shape
+    out = torch.empty(n + (1 if pad_zero_page else 0), two, hkv, page, d, dtype=torch.bfloat16, device=kv8_layer.device)
+    if pad_zero_page:
+        out[n].zero_()
+    check(fn("pie_dequant_kv_pages")(ptr(kv8_layer), ptr(scale_layer), ptr(pages), ptr(out), n, hkv, page, d,
+                                     stream_ptr()), "dequant_kv_pages")
+    return out
+
+
 def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=None, window_left=None,
-                           sinks_log2=None):
+                           sinks_log2=None, kv_scale=None):
     """q [R, hq, D] (one token per request) against paged KV; split-KV + merge. `window_left`
     overrides the plan's window for this call (a layer with its own window; the plan's items
     must then cover at least that window), `sinks_log2` [hq] fp32 = sink logits * log2(e)."""
@@ -713,6 +737,15 @@ def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=N
     wl = plan.window_left if window_left is None else window_left
     r, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    if kv_scale is not None:        # fp8 pages with per-(token, head) scales
+        if plan.item_tile is not None:
+            raise NotImplementedError("shared-prefix plans over fp8 KV pages")
+        check(fn("pie_paged_decode_attn_kv8")(
+            ptr(q), ptr(kv_layer), ptr(kv_scale), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
+            ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),
+            ptr(out), ptr(plan.scratch), plan.max_items, plan.num_reqs, hq, hkv, d, plan.page_size,
+            sm_scale, plan.num_ctas, wl, ptr(sinks_log2), stream_ptr()), "paged_decode_attn_kv8")
+        return out
     if plan.item_tile is not None:
         check(fn("pie_paged_decode_attn_cascade")(
             ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),

@@ -30,6 +30,9 @@ _SIGNATURES = {
     "pie_quant_act_fp8": [p, i32, p, p, i32, i32, p],
     "pie_gemm_fp8_blockscaled": [p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, p, i32, p],
     "pie_qk_norm_rope_kvwrite": [p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
+    "pie_qk_norm_rope_kvwrite_kv8": [p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
+    "pie_paged_decode_attn_kv8": [p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, p, p],
+    "pie_dequant_kv_pages": [p, p, p, p, i32, i32, i32, i32, p],
     "pie_gather_rows": [p, p, p, i32, i32, p],
     "pie_copy_pages": [p, p, p, i32, i32, i64, i64, p],
     "pie_brle_expand": [p, p, p, i32, i32, i32, p],
