@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--out-tokens", type=int, default=256)
     ap.add_argument("--gemm", default="tcgen05", choices=["tcgen05", "cublas"])
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--kv-dtype", default="auto", choices=["auto", "fp8_e4m3"],
+                    help="fp8_e4m3: KV pages stored in fp8 with per-(token, head) scales; NOT the named configuration "
+                         "(its KV is bf16): the line is marked valid=false")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-device", action="store_true")
     ap.add_argument("--max-tokens", type=int, default=16384)
@@ -140,7 +143,7 @@ def main():
             return 0
     t0 = time.time()
     driver = TorchDriver(cfg, torch.device("cuda", local_rank), page_size=16, max_requests=args.requests,
-                         max_tokens=args.max_tokens, par=par, gemm_backend=args.gemm)
+                         max_tokens=args.max_tokens, par=par, gemm_backend=args.gemm, kv_dtype=args.kv_dtype)
     if comm is not None:
         comm.attach(driver)
     driver.precapture_graphs()      # start-up work, as in a serving process: no fire pays for a graph capture
@@ -239,9 +242,9 @@ def main():
         "baseline": baseline,
         "config": {"model": cfg.name, "global_batch": n_req, "seq_len": f"prompts U[{args.prompt_min},{args.prompt_max}] + {args.out_tokens} out",
                    "parallelism": (f"dp{world}" if dp else f"tp{world}"), "tp_backend": args.tp_backend if (world > 1 and not dp) else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
-                   "gemm": args.gemm, "layers": cfg.num_hidden_layers,
+                   "gemm": args.gemm, "layers": cfg.num_hidden_layers, "kv_dtype": "bf16" if args.kv_dtype == "auto" else args.kv_dtype,
                    "l2": "working set per step (weights 16 GB + KV > 60 GB) exceeds the 126 MB L2; no flush needed",
-                   "valid": not args.layers},
+                   "valid": not args.layers and args.kv_dtype == "auto"},
         "clocks": clocks,
         "gpu_launches": launches,
         "prefill_tokens_per_s": dev["prefill_tokens_per_s"] if dev else None,

@@ -3,6 +3,11 @@ mma.sync kernel on causal prompts over a paged KV cache. CUDA events, warm-up, L
 timed launches; FLOPs counted for the causal half only.
 
     python -m pie_b200.bench.attn_bench [--reqs 16 --len 2048] [--rows 64,128,256] [--iters 5]
+    python -m pie_b200.bench.attn_bench --decode [--reqs 512 --len 1200] [--heads 32,8]
+
+`--decode`: split-KV decode attention over bf16 pages and over fp8 pages (bytes of KV actually streamed
+per launch over the CUDA-event time, against the measured copy bandwidth), and with `--fork B` over
+groups of B requests that share all but their last page (the shared-prefix plan against the plain one).
 """
 from __future__ import annotations
 
@@ -51,8 +56,77 @@ def run(reqs: int, plen: int, rows_list, iters: int, hq: int = 32, hkv: int = 8,
     return res
 
 
+def run_decode(reqs: int, kv_len: int, iters: int, hq: int, hkv: int, d: int, fork: int = 0, page: int = 16,
+               warmup: int = 3):
+    dev = "cuda:0"
+    npg = -(-kv_len // page)
+    rng = np.random.default_rng(0)
+    if fork > 1:                    # groups of `fork` requests: npg - 1 shared pages + one private page each
+        groups = reqs // fork
+        total = groups * (npg - 1) + reqs
+        perm = rng.permutation(total).astype(np.int32)
+        tables = [list(perm[g * (npg - 1):(g + 1) * (npg - 1)]) + [perm[groups * (npg - 1) + g * fork + b]]
+                  for g in range(groups) for b in range(fork)]
+        reqs = groups * fork
+    else:
+        total = reqs * npg
+        perm = rng.permutation(total).astype(np.int32)
+        tables = [list(perm[i * npg:(i + 1) * npg]) for i in range(reqs)]
+    pages = np.concatenate(tables).astype(np.int32)
+    indptr = (np.arange(reqs + 1) * npg).astype(np.int32)
+    kv_lens = np.full(reqs, kv_len, np.int32)
+    g = torch.Generator(device=dev).manual_seed(1)
+    kv = (torch.randn(total + 1, 2, hkv, page, d, device=dev, generator=g) * 0.5).bfloat16()
+    amax = kv.float().abs().amax(-1).clamp_min(1e-12)
+    sc = (amax / 448.0).contiguous()
+    kv8 = (kv.float() / sc[..., None]).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+    q = (torch.randn(reqs, hq, d, device=dev, generator=g) * 0.5).bfloat16()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    ctas = ops.num_sms(dev) * 2
+    max_items = reqs + ctas * 8
+    scratch = torch.empty(ops.decode_scratch_floats(max_items, hq, d), device=dev)
+    item_req, st, en, iptr = ops.plan_decode_items(kv_lens, hkv, ctas, max_items)
+    plain = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
+                           torch.tensor([len(item_req)], dtype=torch.int32, device=dev), scratch, max_items, reqs, ctas, page)
+    variants = [("bf16 pages", plain, kv, None, 2.0), ("fp8 pages", plain, kv8, sc, 1.0 + 4.0 / d)]
+    if fork > 1:
+        grp = ops.find_shared_prefixes(kv_lens, indptr, pages, page)
+        cp = ops.plan_decode_cascade(kv_lens, grp, hkv, hq // hkv, ctas, max_items)
+        if cp is not None:
+            casc = ops.DecodePlan(t(pages), t(indptr), t(cp.item_req), t(cp.item_start), t(cp.item_end), t(cp.req_slot_indptr),
+                                  torch.tensor([len(cp.item_req)], dtype=torch.int32, device=dev), scratch, max_items, reqs,
+                                  ctas, page, item_slot=t(cp.item_slot), item_tile=t(cp.item_tile),
+                                  tile_members=t(cp.tile_members))
+            variants.append(("bf16 pages, shared-prefix plan", casc, kv, None, 2.0))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(q)
+    ref_out = None
+    for name, plan, cache, scale, bytes_per_elem in variants:
+        for _ in range(warmup):
+            ops.paged_decode_attention(q, cache, plan, 1 / math.sqrt(d), out=out, kv_scale=scale)
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ops.paged_decode_attention(q, cache, plan, 1 / math.sqrt(d), out=out, kv_scale=scale)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ops.check_kernel_status(dev)
+        ms = sorted(ts)[len(ts) // 2]
+        if ref_out is None:
+            ref_out = out.float().clone()
+        err = float((out.float() - ref_out).abs().max())
+        logical = 2.0 * reqs * kv_len * hkv * d * bytes_per_elem          # K and V of every request, as a plain plan reads them
+        print(f"decode {reqs} x {kv_len} hq {hq} hkv {hkv} ({name}): {ms * 1e3:8.1f} us  {logical / ms / 1e6:7.0f} GB/s of "
+              f"per-request KV  (max |diff| vs bf16 plain {err:.3f})", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--decode", action="store_true")
+    ap.add_argument("--fork", type=int, default=0)
     ap.add_argument("--reqs", type=int, default=0)
     ap.add_argument("--len", type=int, default=0)
     ap.add_argument("--rows", default="64,128,256")
@@ -62,6 +136,9 @@ def main():
     ap.add_argument("--heads", default="32,8", help="query heads, KV heads")
     a = ap.parse_args()
     hq, hkv = (int(v) for v in a.heads.split(","))
+    if a.decode:
+        run_decode(a.reqs or 512, a.len or 1200, a.iters, hq, hkv, a.head_dim, fork=a.fork)
+        return
     rows = [int(r) for r in a.rows.split(",")]
     shapes = [(a.reqs, a.len)] if a.reqs and a.len else [(64, 512), (16, 2048), (8, 4096), (2, 16384)]
     for reqs, plen in shapes:
