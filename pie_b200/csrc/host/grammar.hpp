@@ -16,7 +16,11 @@
 #include <algorithm>
 #include <array>
 #include <cstdint>
+#include <list>
+#include <memory>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 #include <unordered_set>
 #include <vector>
 
@@ -29,9 +33,49 @@ struct GSymbol {
     bool has(unsigned char b) const { return (cls[b >> 6] >> (b & 63)) & 1ull; }
 };
 
-struct Grammar {
-    std::vector<std::vector<std::vector<GSymbol>>> rules;   // rule -> alternatives -> symbols
-    int root = 0;
+// Token masks by matcher state, shared by every matcher of one grammar (the state of a pushdown
+// matcher recurs constantly: every character inside a JSON string, every digit of a number, every
+// item of an array leads back to a state seen before). Key: an order-independent 128-bit digest of
+// the set of parse stacks plus the trie the mask was computed against; value: the allowed-token
+// bytes. Least-recently-used entries go first. Counterpart of the adaptive token-mask cache of the
+// reference's compiled grammar (runtime/src/inference/structured/compiled_grammar.rs:21-50).
+struct MaskCache {
+    struct Key {
+        uint64_t a, b;
+        const void* trie;
+        bool operator==(const Key& o) const { return a == o.a && b == o.b && trie == o.trie; }
+    };
+    struct KeyHash {
+        size_t operator()(const Key& k) const { return (size_t)(k.a ^ (k.b * 0x9E3779B97F4A7C15ull) ^ (uintptr_t)k.trie); }
+    };
+    using Entry = std::pair<Key, std::shared_ptr<const std::vector<uint8_t>>>;
+    size_t capacity = 512;
+    mutable std::mutex mu;
+    mutable std::list<Entry> lru;
+    mutable std::unordered_map<Key, std::list<Entry>::iterator, KeyHash> index;
+    mutable uint64_t hits = 0, misses = 0;
+
+    std::shared_ptr<const std::vector<uint8_t>> find(const Key& k) const {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = index.find(k);
+        if (it == index.end()) {
+            ++misses;
+            return nullptr;
+        }
+        ++hits;
+        lru.splice(lru.begin(), lru, it->second);
+        return it->second->second;
+    }
+    void put(const Key& k, std::shared_ptr<const std::vector<uint8_t>> v) const {
+        std::lock_guard<std::mutex> lock(mu);
+        if (index.count(k)) return;
+        lru.emplace_front(k, std::move(v));
+        index[k] = lru.begin();
+        while (lru.size() > capacity) {
+            index.erase(lru.back().first);
+            lru.pop_back();
+        }
+    }
 };
 
 struct GFrame {
@@ -39,6 +83,26 @@ struct GFrame {
     bool operator==(const GFrame& o) const { return rule == o.rule && alt == o.alt && pos == o.pos; }
 };
 using GStack = std::vector<GFrame>;
+
+// Lazily built automaton over matcher states: a state set gets a number the first time it is seen,
+// and the successor of (state, byte) is computed once. The token-trie walk of a mask then moves
+// through table look-ups wherever the grammar has been before. Bounded: past `max_states` the walk
+// falls back to computing successors directly.
+struct StateTable {
+    static constexpr int kUnknown = -2, kDead = -1;
+    size_t max_states = 16384;
+    std::mutex mu;
+    std::unordered_map<uint64_t, std::vector<int>> by_hash;          // digest -> candidate ids
+    std::vector<std::shared_ptr<const std::vector<GStack>>> sets;
+    std::vector<std::array<int, 256>> trans;
+};
+
+struct Grammar {
+    std::vector<std::vector<std::vector<GSymbol>>> rules;   // rule -> alternatives -> symbols
+    int root = 0;
+    MaskCache mask_cache;
+    mutable StateTable table;
+};
 
 inline uint64_t gstack_hash(const GStack& s) {
     uint64_t h = 0x9E3779B97F4A7C15ull ^ s.size();
@@ -127,9 +191,29 @@ public:
     size_t num_states() const { return states_.size(); }
 
     // allowed[id] = 1 for every token whose bytes the grammar accepts from the current state.
+    // Served from the grammar's mask cache when this state set was seen before (by any matcher).
     void next_token_mask(std::vector<uint8_t>& allowed) const {
+        const MaskCache::Key key = state_key();
+        if (auto hit = g_->mask_cache.find(key)) {
+            allowed = *hit;
+            return;
+        }
         allowed.assign((size_t)trie_->vocab, 0);
-        walk(0, states_, allowed);
+        const int id = intern(states_);
+        if (id >= 0) walk_table(0, id, allowed);
+        else walk(0, states_, allowed);
+        g_->mask_cache.put(key, std::make_shared<const std::vector<uint8_t>>(allowed));
+    }
+
+    // Digest of the state set, independent of the order the stacks were produced in.
+    MaskCache::Key state_key() const {
+        uint64_t a = 0x243F6A8885A308D3ull ^ states_.size(), b = 0;
+        for (const GStack& s : states_) {
+            const uint64_t h = gstack_hash(s);
+            a += h * 0xD6E8FEB86659FD93ull;                       // commutative combination: order does not matter
+            b ^= (h ^ (h >> 29)) * 0xBF58476D1CE4E5B9ull + 0x94D049BB133111EBull;
+        }
+        return MaskCache::Key{a, b, (const void*)trie_};
     }
 
 private:
@@ -161,10 +245,18 @@ private:
                 if (!s.empty()) s.back().pos += 1;
                 work.push_back(std::move(s));
             } else if (sym->is_rule) {
-                if (s.size() >= kMaxDepth) continue;
+                // A reference that is the last symbol of its alternative is a tail call: the frame is
+                // replaced, not stacked (when the callee finishes, the frame below advances, which is
+                // what the finished caller would have done). Repetition desugars to right recursion, so
+                // this keeps the stack - and with it the matcher state - the same from one iteration to
+                // the next: long strings do not deepen the stack and their states recur in the mask cache.
+                const GFrame top = s.back();
+                const bool tail = top.pos + 1 == (int)g_->rules[top.rule][top.alt].size();
+                if (!tail && s.size() >= kMaxDepth) continue;
                 for (int a = 0; a < (int)g_->rules[sym->rule].size(); ++a) {
                     GStack t = s;
-                    t.push_back(GFrame{sym->rule, a, 0});
+                    if (tail) t.back() = GFrame{sym->rule, a, 0};
+                    else t.push_back(GFrame{sym->rule, a, 0});
                     work.push_back(std::move(t));
                 }
             } else {
@@ -185,6 +277,71 @@ private:
             }
         }
         closure(work, out);
+    }
+
+    static uint64_t set_digest(const std::vector<GStack>& st) {
+        uint64_t a = 0x243F6A8885A308D3ull ^ st.size();
+        for (const GStack& s : st) a += gstack_hash(s) * 0xD6E8FEB86659FD93ull;
+        return a;
+    }
+    static bool same_set(const std::vector<GStack>& x, const std::vector<GStack>& y) {
+        if (x.size() != y.size()) return false;
+        for (const GStack& s : x)
+            if (std::find(y.begin(), y.end(), s) == y.end()) return false;
+        return true;
+    }
+    // Number of a state set in the grammar's table (-1 when the table is full).
+    int intern(const std::vector<GStack>& st) const {
+        StateTable& t = g_->table;
+        const uint64_t d = set_digest(st);
+        std::lock_guard<std::mutex> lock(t.mu);
+        auto& ids = t.by_hash[d];
+        for (int id : ids)
+            if (same_set(*t.sets[id], st)) return id;
+        if (t.sets.size() >= t.max_states) return -1;
+        const int id = (int)t.sets.size();
+        t.sets.push_back(std::make_shared<const std::vector<GStack>>(st));
+        std::array<int, 256> row;
+        row.fill(StateTable::kUnknown);
+        t.trans.push_back(row);
+        ids.push_back(id);
+        return id;
+    }
+    // Successor of table state `id` on byte c: kDead, a table id, or kUnknown when the table is full
+    // (then *overflow holds the successor set).
+    int next_state(int id, unsigned char c, std::vector<GStack>* overflow) const {
+        StateTable& t = g_->table;
+        std::shared_ptr<const std::vector<GStack>> cur;
+        {
+            std::lock_guard<std::mutex> lock(t.mu);
+            const int known = t.trans[id][c];
+            if (known != StateTable::kUnknown) return known;
+            cur = t.sets[id];
+        }
+        std::vector<GStack> nxt;
+        step(*cur, c, nxt);
+        int to = StateTable::kDead;
+        if (!nxt.empty()) {
+            to = intern(nxt);
+            if (to < 0) {
+                *overflow = std::move(nxt);
+                return StateTable::kUnknown;
+            }
+        }
+        std::lock_guard<std::mutex> lock(t.mu);
+        t.trans[id][c] = to;
+        return to;
+    }
+    void walk_table(int node, int id, std::vector<uint8_t>& allowed) const {
+        const TokenTrie::Node& n = trie_->nodes[node];
+        for (int tok : n.tokens) allowed[tok] = 1;
+        for (int c = 0; c < 256; ++c) {
+            if (n.child[c] < 0) continue;
+            std::vector<GStack> overflow;
+            const int to = next_state(id, (unsigned char)c, &overflow);
+            if (to >= 0) walk_table(n.child[c], to, allowed);
+            else if (to == StateTable::kUnknown) walk(n.child[c], overflow, allowed);
+        }
     }
 
     void walk(int node, const std::vector<GStack>& st, std::vector<uint8_t>& allowed) const {

@@ -111,7 +111,19 @@ PYBIND11_MODULE(pie_host, m) {
             }
             return g;
         }))
-        .def_property_readonly("num_rules", [](const Grammar& g) { return g.rules.size(); });
+        .def_property_readonly("num_rules", [](const Grammar& g) { return g.rules.size(); })
+        .def("mask_cache_stats", [](const Grammar& g) {
+            std::lock_guard<std::mutex> lock(g.mask_cache.mu);
+            return py::make_tuple(g.mask_cache.hits, g.mask_cache.misses, g.mask_cache.lru.size());
+        })
+        .def("set_mask_cache_capacity", [](Grammar& g, size_t n) {
+            std::lock_guard<std::mutex> lock(g.mask_cache.mu);
+            g.mask_cache.capacity = n;
+            while (g.mask_cache.lru.size() > n) {
+                g.mask_cache.index.erase(g.mask_cache.lru.back().first);
+                g.mask_cache.lru.pop_back();
+            }
+        });
 
     py::class_<TokenTrie>(m, "TokenTrie")
         .def(py::init([](const std::vector<int>& ids, const std::vector<py::bytes>& toks) {

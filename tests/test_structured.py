@@ -172,3 +172,36 @@ def test_constrained_greedy_on_tiny_model_cpu():
         assert re.fullmatch(r"[0-9]{4}-[a-f]{2}", out), out
     finally:
         eng.shutdown()
+
+
+def test_token_mask_cache_serves_recurring_states():
+    """The matcher state recurs (every character inside a string, every array item): the per-grammar
+    cache must serve those masks without changing them, for every matcher of the grammar."""
+    from pie_b200.runtime.structured import Grammar, Matcher
+    from pie_b200.runtime.tokenizer import ByteTokenizer
+    tok = ByteTokenizer(512)
+    g = Grammar.from_json_schema({"type": "object", "required": ["name", "tags"], "properties": {
+        "name": {"type": "string"}, "tags": {"type": "array", "items": {"type": "integer"}}}})
+    text = b'{"name":"abcdefgh","tags":[12,345,6789,1]}'
+    h0, m0, _ = g.native.mask_cache_stats()
+
+    def run(capacity):
+        g.native.set_mask_cache_capacity(capacity)
+        m = Matcher(g, tok, stop_tokens=[])
+        masks = []
+        for b in text:
+            masks.append(tuple(m.next_token_logit_mask()))
+            m.accept_tokens([b])
+        assert m.native.can_terminate()
+        return masks
+
+    cold = run(0)                                   # capacity 0: every mask is computed by the trie walk
+    h1, m1, n1 = g.native.mask_cache_stats()
+    assert n1 == 0 and h1 == h0
+    warm = run(512)
+    h2, m2, n2 = g.native.mask_cache_stats()
+    again = run(512)                                # a second matcher of the same grammar: all hits
+    h3, m3, n3 = g.native.mask_cache_stats()
+    assert cold == warm == again
+    assert h2 - h1 >= 8                             # the repeated states inside "abcdefgh" and the digits
+    assert h3 - h2 == len(text) and m3 == m2 and 0 < n3 <= 512
