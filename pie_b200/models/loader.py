@@ -23,9 +23,10 @@ and its C++ executor (driver/cuda/src/loader/*).
 from __future__ import annotations
 
 import json
+import os
 from dataclasses import dataclass, field
 from pathlib import Path
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -339,6 +340,106 @@ def execute_program(prog: Program, reader, device="cpu") -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------- materialised-weight cache
+def _source_fingerprint(path: Path) -> str:
+    """Identity of a checkpoint without reading its tensors: names, sizes and mtimes of its files."""
+    import hashlib
+    files = [path] if path.is_file() else sorted(f for f in path.iterdir()
+                                                  if f.suffix in (".safetensors", ".gguf", ".json"))
+    h = hashlib.blake2b(digest_size=16)
+    for f in files:
+        st = f.stat()
+        h.update(f"{f.name}:{st.st_size}:{int(st.st_mtime_ns)};".encode())
+    return h.hexdigest()
+
+
+def _flatten(weights: dict) -> Tuple[dict, dict]:
+    """Runtime weight dict -> (flat name -> tensor, JSON-able structure notes)."""
+    from ..ops import Fp8Linear
+    flat, notes = {}, {"layers": len(weights["layers"]), "scalars": {}, "fp8": []}
+    def put(name, v):
+        if isinstance(v, Fp8Linear):
+            flat[name + "@w8"], flat[name + "@scale"] = v.w8.view(torch.uint8), v.scale
+            notes["fp8"].append(name)
+        elif torch.is_tensor(v):
+            flat[name] = v
+        else:
+            notes["scalars"][name] = v
+    for k, v in weights.items():
+        if k != "layers":
+            put(k, v)
+    for li, lw in enumerate(weights["layers"]):
+        for k, v in lw.items():
+            put(f"layers.{li}.{k}", v)
+    return flat, notes
+
+
+def _unflatten(flat: dict, notes: dict, device) -> dict:
+    from ..ops import Fp8Linear
+    out = {"layers": [dict() for _ in range(notes["layers"])]}
+    def slot(name):
+        if name.startswith("layers."):
+            _, li, key = name.split(".", 2)
+            return out["layers"][int(li)], key
+        return out, name
+    fp8 = set(notes["fp8"])
+    for name, t in flat.items():
+        base = name.rsplit("@", 1)[0]
+        if base in fp8:
+            continue
+        d, key = slot(name)
+        d[key] = t.to(device)
+    for name in fp8:
+        d, key = slot(name)
+        d[key] = Fp8Linear(flat[name + "@w8"].view(torch.float8_e4m3fn).to(device), flat[name + "@scale"].to(device))
+    for name, v in notes["scalars"].items():
+        d, key = slot(name)
+        d[key] = v
+    return out
+
+
+def weight_cache_dir() -> Optional[Path]:
+    d = os.environ.get("PIE_WEIGHT_CACHE_DIR", "")
+    return Path(d).expanduser() if d else None
+
+
+def _cached_load(path: Path, prog: "Program", reader, device):
+    """`execute_program` through the materialised-weight cache (opt-in: PIE_WEIGHT_CACHE_DIR). The
+    cache key covers the source files (names, sizes, mtimes) and the whole storage program, so a
+    different shard plan, dtype or fusion gets its own entry. Entries are one safetensors file per
+    rank, written to a temporary name and renamed, with the key stored inside and checked on load.
+    Counterpart of the reference's weight artifact cache (driver/cuda/src/model/weight_artifact_cache.hpp:1-24,
+    opt-in through PIE_CUDA_WEIGHT_CACHE_DIR there)."""
+    cdir = weight_cache_dir()
+    if cdir is None:
+        return execute_program(prog, reader, device)
+    import hashlib
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    key = hashlib.blake2b((_source_fingerprint(path) + program_to_json(prog)).encode(), digest_size=16).hexdigest()
+    entry = cdir / f"{key}.safetensors"
+    if entry.exists():
+        try:
+            with safe_open(str(entry), framework="pt", device="cpu") as f:
+                meta = f.metadata() or {}
+                if meta.get("key") == key:
+                    flat = {k: f.get_tensor(k) for k in f.keys()}
+                    return _unflatten(flat, json.loads(meta["notes"]), device)
+        except Exception:  # noqa: BLE001 - a damaged entry is rebuilt
+            pass
+    weights = execute_program(prog, reader, device)
+    try:
+        cdir.mkdir(parents=True, exist_ok=True)
+        flat, notes = _flatten(weights)
+        tmp = entry.with_suffix(f".tmp{os.getpid()}")
+        save_file({k: v.detach().cpu().contiguous() for k, v in flat.items()}, str(tmp),
+                  metadata={"key": key, "notes": json.dumps(notes)})
+        os.replace(tmp, entry)
+    except Exception:  # noqa: BLE001 - the cache is an optimisation: never fail a load over it
+        pass
+    return weights
+
+
 def load_checkpoint(path, device="cpu", tp_size: int = 1, tp_rank: int = 0, ep: bool = False,
                     dtype: Optional[str] = None):
     """config.json + safetensors, or one .gguf file (or a directory holding one and no
@@ -351,11 +452,11 @@ def load_checkpoint(path, device="cpu", tp_size: int = 1, tp_rank: int = 0, ep: 
         reader = GGUFReader(ggufs[0])
         cfg = reader.config()
         prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)
-        return cfg, execute_program(prog, reader, device)
+        return cfg, _cached_load(ggufs[0], prog, reader, device)
     cfg = ModelConfig.from_path(path)
     reader = SafetensorsReader(path)
     prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)
-    return cfg, execute_program(prog, reader, device)
+    return cfg, _cached_load(p, prog, reader, device)
 
 
 def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:

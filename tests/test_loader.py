@@ -443,3 +443,36 @@ def test_gpt_oss_tensor_parallel_shards(tmp_path):
         assert torch.equal(lw["experts_gate_up"], full["layers"][0]["experts_gate_up"][:, r * Im:(r + 1) * Im])
         assert torch.equal(lw["experts_down"], full["layers"][0]["experts_down"][:, :, r * Im // 2:(r + 1) * Im // 2])
         assert (lw["experts_down_bias"].abs().sum() > 0) == (r == 0)
+
+
+def test_weight_artifact_cache_round_trip_and_keying(tmp_path, monkeypatch):
+    """PIE_WEIGHT_CACHE_DIR: the first load materialises and stores this rank's weights, the second
+    reads the entry (equal tensors, no storage program run), another shard plan gets its own entry,
+    a touched checkpoint invalidates, a damaged entry is rebuilt."""
+    import os
+    cfg = preset("tiny-qwen3-moe", vocab_size=512)
+    full = random_weights(cfg, "cpu", torch.float32, seed=5)
+    src = tmp_path / "ckpt"
+    src.mkdir()
+    loader.export_hf_checkpoint(cfg, full, str(src))
+    cache = tmp_path / "cache"
+    monkeypatch.setenv("PIE_WEIGHT_CACHE_DIR", str(cache))
+    _, a = loader.load_checkpoint(str(src), dtype="float32")
+    assert len(list(cache.glob("*.safetensors"))) == 1 and _same(full, a)
+    calls = []
+    real = loader.execute_program
+    monkeypatch.setattr(loader, "execute_program", lambda *x, **k: calls.append(1) or real(*x, **k))
+    _, b = loader.load_checkpoint(str(src), dtype="float32")
+    assert calls == [] and _same(a, b) and b["lm_head_vocab_start"] == 0
+    _, r1 = loader.load_checkpoint(str(src), tp_size=2, tp_rank=1, dtype="float32")
+    assert len(calls) == 1 and len(list(cache.glob("*.safetensors"))) == 2
+    assert _same(random_weights(cfg, "cpu", torch.float32, seed=5, tp_size=2, tp_rank=1), r1)
+    f = next(src.glob("*.safetensors"))
+    os.utime(f, ns=(f.stat().st_atime_ns, f.stat().st_mtime_ns + 10**9))       # the checkpoint changed
+    loader.load_checkpoint(str(src), dtype="float32")
+    assert len(calls) == 2 and len(list(cache.glob("*.safetensors"))) == 3
+    for e in cache.glob("*.safetensors"):
+        e.write_bytes(b"broken")
+    _, c = loader.load_checkpoint(str(src), dtype="float32")
+    assert len(calls) == 3 and _same(full, c)
+    assert not list(cache.glob("*.tmp*"))

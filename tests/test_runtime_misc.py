@@ -273,3 +273,18 @@ def test_driver_config_carries_the_memory_profile():
     p = plan(c, 100 << 30, 1.0, "latency")
     assert (p.max_requests, p.max_tokens) == (PROFILES["latency"]["max_requests"], PROFILES["latency"]["max_tokens"])
     assert p.kv_bytes + p.arena_bytes <= (100 << 30) and p.arena_bytes == arena_bytes(c, p.max_tokens, p.max_requests)
+
+
+def test_determinism_ledger_cases_repeat_and_match_when_asked():
+    """Greedy output is repeatable run to run; with PIE_CHECK_LEDGER=1 it must also equal the
+    committed ledger (exact-token regression guard for refactors on the reference machine)."""
+    import json
+    import os
+    from pie_b200.bench import determinism
+    name, prog, args = determinism.CASES[0]
+    h1, h2 = determinism.run_case(name, prog, args), determinism.run_case(name, prog, args)
+    assert h1 == h2 and len(h1) == 64
+    ledger = json.loads(determinism.LEDGER.read_text())
+    assert set(ledger["cases"]) == {f"{n}/{p}" for n, p, _ in determinism.CASES}
+    if os.environ.get("PIE_CHECK_LEDGER") == "1":
+        assert ledger["cases"][f"{name}/{prog}"] == h1
