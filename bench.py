@@ -54,6 +54,7 @@ def parse_args():
                     help="fp8_e4m3: KV pages stored in fp8 with per-(token, head) scales; NOT the named configuration "
                          "(its KV is bf16): the line is marked valid=false")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-per-step", action="store_true", help="skip the inferlet-driven (per-step) e2e variant")
     ap.add_argument("--skip-device", action="store_true")
     ap.add_argument("--max-tokens", type=int, default=16384)
     ap.add_argument("--device-loop", default="pipelined", choices=["pipelined", "staged"],
@@ -163,12 +164,25 @@ def main():
     e2e = None
     if not args.skip_e2e:
         eng = Engine(EngineConfig(batch_policy="adaptive", speculation_depth=1))
-        eng.add_model(cfg.name, driver)
+        from pie_b200.runtime.tokenizer import ByteTokenizer
+        eng.add_model(cfg.name, driver, tokenizer=ByteTokenizer(cfg.vocab_size))   # byte-level ids for the constrained variant
         install_all(eng)
         before = _lib.LAUNCHES
         e2e = harness.run_engine_workload(eng, cfg.name, prompts, args.out_tokens, sampler_args,
                                           window_skip=args.warmup, window_steps=args.steps)
         e2e["launcher_calls"] = _lib.LAUNCHES - before
+        if not args.skip_per_step:
+            # the programmable path: every inferlet drives its own loop, one forward-pass.execute per
+            # token (what constraints, custom speculators and probes use); one in sixteen of the inferlets also
+            # decode under a JSON-schema grammar whose vocabulary mask is applied on the device
+            schema = {"type": "object", "required": ["a"], "properties": {"a": {"type": "array", "items": {"type": "integer"}}}}
+            n_ps = min(len(prompts), 512)
+            ps = harness.run_engine_workload(
+                eng, cfg.name, prompts[:n_ps], 24, sampler_args, window_skip=3, window_steps=12,
+                extra_args=lambda i: {"per_step": True, **({"json_schema": schema} if i % 16 == 0 else {})})
+            e2e["per_step"] = {"ms_per_step": ps.get("window_ms_per_step"), "value": ps.get("window_tokens_per_s"),
+                               "unit": "tokens/s", "inferlets": n_ps, "constrained_inferlets": (n_ps + 15) // 16,
+                               "out_tokens": 24, "workload_tokens_per_s": ps["workload_tokens_per_s"]}
         # keep the driver alive for the device-only phase
         for s in eng.model(cfg.name).schedulers:
             s.shutdown()
@@ -258,7 +272,9 @@ def main():
                        "p50_ttft_s": e2e["p50_ttft_s"], "p50_itl_s": e2e["p50_itl_s"],
                        "wall_s": e2e["wall_s"], "fires": e2e["fires"],
                        "requests_per_fire": e2e.get("window_requests_per_fire"),
-                       "steps_used": e2e.get("window_steps_used")}
+                       "steps_used": e2e.get("window_steps_used"),
+                       # same metric with every inferlet driving its own decode loop (one execute per token)
+                       "per_step": e2e.get("per_step")}
     print(json.dumps(line))
     if world > 1:
         _hard_exit(0)

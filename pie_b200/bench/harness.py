@@ -244,8 +244,10 @@ def run_device_decode(driver, prompts, out_tokens: int, sampler: SamplerSpec, wa
 
 
 def run_engine_workload(engine, model_name: str, prompts, out_tokens: int, sampler_args: dict,
-                        window_skip: int, window_steps: int, timeout: float = 1800.0):
-    """All inferlets at once through the public API. Returns e2e metrics."""
+                        window_skip: int, window_steps: int, timeout: float = 1800.0, extra_args=None):
+    """All inferlets at once through the public API. Returns e2e metrics. `extra_args`: per-inferlet
+    overrides, a dict for all or a callable index -> dict (e.g. {"per_step": True} for the
+    inferlet-driven loop, or a JSON-schema constraint on some of them)."""
     entry = engine.model(model_name)
     fires = []   # (t_end, n_requests, n_tokens, latency)
 
@@ -255,8 +257,13 @@ def run_engine_workload(engine, model_name: str, prompts, out_tokens: int, sampl
     for s in entry.schedulers:
         s.on_batch = on_batch
     t_launch = time.perf_counter()
+    def extra(i):
+        if extra_args is None:
+            return {}
+        return extra_args(i) if callable(extra_args) else extra_args
     procs = [engine.launch("text-completion-bench",
-                           dict(prompt_tokens=p, max_tokens=out_tokens, **sampler_args)) for p in prompts]
+                           dict(prompt_tokens=p, max_tokens=out_tokens, **sampler_args, **extra(i)))
+             for i, p in enumerate(prompts)]
     results = [json.loads(engine.wait(p, timeout)) for p in procs]
     t_done = time.perf_counter()
     for s in entry.schedulers:

@@ -21,8 +21,12 @@ async def main(args):
     t0 = time.perf_counter()
     ctx = Context(model)
     ctx.append(args["prompt_tokens"])
-    gen = ctx.generate(make_sampler(args), max_tokens=int(args.get("max_tokens", 256))).stop([])
-    if args.get("per_step"):
+    constrain = None
+    if args.get("json_schema") is not None:          # constrained variant: the mask is recomputed every step
+        from pie_b200.sdk import JsonSchema
+        constrain = JsonSchema(args["json_schema"])
+    gen = ctx.generate(make_sampler(args), max_tokens=int(args.get("max_tokens", 256)), constrain=constrain).stop([])
+    if args.get("per_step") or constrain is not None:
         # inferlet-driven loop: one forward-pass.execute per token
         stamps, n = [], 0
         async for step in gen:
