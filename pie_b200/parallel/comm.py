@@ -12,7 +12,7 @@ reduce-scatter + one all-gather per GEMM pair instead of the reference's two all
 (driver/cuda/src/model/llama_like.cpp:633-647, 706-742). NCCL remains for bootstrap, the
 logits all-gather and as the baseline path (`all_reduce`, `gemm_allreduce`).
 
-Control plane (host): rank 0 runs the engine; it publishes every fire (a pickled batch request
+Control plane (host): rank 0 runs the engine; it publishes every fire (a batch request as a flat wire frame, `driver/abi.py`,
 or the raw input slab of a pipelined decode step) into a POSIX shared-memory ring that the
 follower ranks poll - one host memcpy per fire instead of the reference's eight NCCL broadcasts
 (driver/cuda/src/executor/executor.cpp:1305-1360), and page copies reach every rank (the
@@ -22,7 +22,6 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-import pickle
 import time
 from dataclasses import replace
 from multiprocessing import shared_memory
@@ -34,6 +33,7 @@ import torch
 from .. import ops
 from ..ops import _lib
 from ..ops._lib import check, ptr, stream_ptr
+from ..driver import abi
 
 KIND_BATCH, KIND_DECODE, KIND_COPY, KIND_STOP, KIND_MARK = 1, 2, 3, 4, 5
 _HDR_WORDS = 64
@@ -355,7 +355,7 @@ class TPComm:
     def publish_step(self, req, decode: bool) -> None:
         if self.rank != 0 or self.ring is None:
             return
-        data = np.frombuffer(pickle.dumps(req, protocol=pickle.HIGHEST_PROTOCOL), dtype=np.uint8)
+        data = np.frombuffer(abi.pack_forward_request(req), dtype=np.uint8)
         self.ring.publish(KIND_BATCH, data)
 
     def publish_decode(self, slab, r: int, rb: int, npg: int, parity: int, cascade: bool = False) -> None:
@@ -370,7 +370,7 @@ class TPComm:
     def publish_copy(self, req) -> None:
         if self.rank != 0 or self.ring is None:
             return
-        self.ring.publish(KIND_COPY, np.frombuffer(pickle.dumps(req), dtype=np.uint8))
+        self.ring.publish(KIND_COPY, np.frombuffer(abi.pack_copy_request(req), dtype=np.uint8))
 
     def mark(self, end: bool) -> float:
         """Timed-region bracket on every rank: device synchronise + barrier, a CUDA event on each
@@ -410,7 +410,7 @@ class TPComm:
                 ring.ack()
                 break
             if kind == KIND_BATCH:
-                req = pickle.loads(payload.tobytes())
+                req = abi.unpack_forward_request(payload.tobytes())
                 ring.ack()
                 driver.fire_batch(req)
             elif kind == KIND_DECODE:
@@ -429,7 +429,7 @@ class TPComm:
                     driver.graphs[key] = driver._capture(rb, cascade)
                 driver._launch_decode(r, rb, npg, parity, cascade)
             elif kind == KIND_COPY:
-                req = pickle.loads(payload.tobytes())
+                req = abi.unpack_copy_request(payload.tobytes())
                 ring.ack()
                 driver.kv.copy(req)
             elif kind == KIND_MARK:
