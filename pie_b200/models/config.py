@@ -11,6 +11,8 @@ from pathlib import Path
 from typing import Optional
 
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
+# `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "mixtral", "olmo2", "gpt_oss")
 POST_NORM = {"olmo2"}       # same block with the norms after attention / MLP and q, k norms over all heads
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
 

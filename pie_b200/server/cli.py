@@ -1,6 +1,7 @@
 """`pie` command line (python -m pie_b200 ...). Subcommands follow the reference CLI
 (server/src/cli.rs:50-142): serve, run, config {init,show,set}, auth {add,remove,list,keygen},
-model {list}, inferlet {list}, new, build, doctor, check, smoke.
+model {list,download,remove}, inferlet {list}, driver {list, <type> install|doctor|show|set|unset},
+new, build, doctor, check, smoke.
 
 `pie run <inferlet> [-- --key value ...]` boots a one-shot engine, connects a client over the
 WebSocket like any other client, launches the inferlet with the trailing `--key value` pairs as
@@ -156,10 +157,39 @@ def cmd_auth(args) -> int:
     return 0
 
 
+def _human(n: int) -> str:
+    for unit in ("B", "KiB", "MiB", "GiB", "TiB"):
+        if n < 1024 or unit == "TiB":
+            return f"{n:.1f} {unit}" if unit != "B" else f"{n} B"
+        n /= 1024.0
+
+
 def cmd_model(args) -> int:
+    """`pie model list | download <org/name> [--revision R] [--all] | remove <org/name> [--yes]`
+    (server/src/cli/model_cmd.rs:20-254)."""
     from ..models.config import PRESETS
+    from . import hf
+    if args.action == "download":
+        if not args.repo:
+            raise SystemExit("usage: pie model download <org/name>")
+        snap = hf.download(args.repo, args.revision, args.all, progress=hf.progress_bar())
+        print(f"{args.repo} -> {snap}")
+        return 0
+    if args.action == "remove":
+        if not args.repo:
+            raise SystemExit("usage: pie model remove <org/name>")
+        if not args.yes and input(f"remove {args.repo} from {hf.hf_cache_root()}? [y/N] ").strip().lower() != "y":
+            return 1
+        print(f"freed {_human(hf.remove(args.repo))}")
+        return 0
+    cached = hf.list_cached()
+    if cached:
+        print(f"cached under {hf.hf_cache_root()}:")
+        for repo, ok, why, size in cached:
+            print(f"  {'ok ' if ok else '-- '} {repo:44s} {why:28s} {_human(size):>10s}")
+    print("presets (random-init, for benchmarks and tests):")
     for name, kw in PRESETS.items():
-        print(f"{name:18s} {kw['model_type']:10s} layers={kw['num_hidden_layers']:3d} hidden={kw['hidden_size']:5d} "
+        print(f"  {name:18s} {kw['model_type']:10s} layers={kw['num_hidden_layers']:3d} hidden={kw['hidden_size']:5d} "
               f"heads={kw['num_attention_heads']}/{kw['num_key_value_heads']} vocab={kw['vocab_size']}")
     return 0
 
@@ -174,6 +204,94 @@ def cmd_inferlet(args) -> int:
             doc = (mod.__doc__ or "").strip().splitlines()
             print(f"{getattr(mod, 'NAME', m.name.replace('_', '-')):28s} {doc[0] if doc else ''}")
     return 0
+
+
+DRIVER_TYPES = {
+    "cuda_native": "B200 driver: tcgen05 / TMA kernels, CUDA graphs, fused tensor parallelism (in-tree libpie_kernels.so)",
+    "cpu": "plain PyTorch fp32 driver on the host: numerics oracle and tests",
+    "dummy": "no model: uniform random tokens, for control-plane and scheduler tests",
+}
+
+
+def _drivers_toml() -> Path:
+    return cfgmod.default_path().parent / "drivers.toml"
+
+
+def _read_driver_knobs() -> dict:
+    import tomllib
+    p = _drivers_toml()
+    return tomllib.loads(p.read_text()) if p.exists() else {}
+
+
+def _write_driver_knobs(d: dict) -> None:
+    p = _drivers_toml()
+    p.parent.mkdir(parents=True, exist_ok=True)
+    out = []
+    for typ, kv in sorted(d.items()):
+        if kv:
+            out.append(f"[{typ}]")
+            out += [f"{k} = {cfgmod._fmt(v)}" for k, v in sorted(kv.items())]
+            out.append("")
+    p.write_text("\n".join(out))
+
+
+def cmd_driver(args) -> int:
+    """`pie driver list [--config F]` and `pie driver <type> install|doctor|show|set K V|unset K`
+    (server/src/cli/driver_cmd.rs:41-130). The drivers are in-tree, so `install` is the kernel build
+    and the persisted knobs (`drivers.toml` beside the config) are defaults of `[model.driver]` keys."""
+    import dataclasses
+    typ = args.type.replace("-", "_")
+    if typ == "list":
+        used = {}
+        if args.config or cfgmod.default_path().exists():
+            for m in cfgmod.load(args.config).model:
+                used.setdefault(m.driver.type, []).append(m.name)
+        for t, doc in DRIVER_TYPES.items():
+            print(f"{t:12s} {doc}" + (f"   [used by: {', '.join(used[t])}]" if t in used else ""))
+        return 0
+    if typ not in DRIVER_TYPES:
+        raise SystemExit(f"unknown driver {args.type!r}; known: {', '.join(DRIVER_TYPES)}")
+    knobs = _read_driver_knobs()
+    mine = knobs.setdefault(typ, {})
+    valid = {f.name: f for f in dataclasses.fields(cfgmod.DriverConfig) if f.name != "type"}
+    act = args.action or "show"
+    if act == "install":
+        cmd = [sys.executable, "-m", "pie_b200._build"]
+        print(" ".join(cmd) + "    # builds libpie_kernels.so (sm_100a) and the host module in-tree")
+        if args.run and typ == "cuda_native":
+            import subprocess
+            return subprocess.call(cmd)
+        return 0
+    if act == "doctor":
+        if typ == "cuda_native":
+            return cmd_doctor(args)
+        print(f"{typ}: no native dependencies")
+        return 0
+    if act == "show":
+        print(f"[{typ}]  ({_drivers_toml()})")
+        for k, f in valid.items():
+            src = "drivers.toml" if k in mine else "default"
+            v = mine.get(k, f.default if f.default is not dataclasses.MISSING else f.default_factory())
+            print(f"  {k:24s} {cfgmod._fmt(v):16s} {src}")
+        return 0
+    if act in ("set", "unset"):
+        if not args.key or args.key not in valid:
+            raise SystemExit(f"unknown knob {args.key!r}; known: {', '.join(valid)}")
+        if act == "unset":
+            mine.pop(args.key, None)
+        else:
+            if args.value is None:
+                raise SystemExit("usage: pie driver <type> set <key> <value>")
+            try:
+                v = json.loads(args.value)
+            except json.JSONDecodeError:
+                v = args.value
+            probe = cfgmod.DriverConfig(**{**mine, args.key: v, "type": typ})
+            cfgmod.validate(cfgmod.Config(model=[cfgmod.ModelSection(name="probe", preset="tiny-llama", driver=probe)]))
+            mine[args.key] = v
+        _write_driver_knobs(knobs)
+        return 0
+    raise SystemExit(f"unknown action {act!r}")
 
 
 TEMPLATE = '''"""{name}: describe what this inferlet does."""
@@ -270,8 +388,15 @@ def main(argv=None) -> int:
     p.add_argument("--config"); p.add_argument("--force", action="store_true"); p.set_defaults(fn=cmd_config)
     p = sub.add_parser("auth"); common(p); p.add_argument("action", choices=["add", "remove", "list", "keygen"])
     p.add_argument("username", nargs="?"); p.add_argument("pubkey", nargs="?"); p.set_defaults(fn=cmd_auth)
-    p = sub.add_parser("model"); p.add_argument("action", choices=["list"], nargs="?", default="list"); p.set_defaults(fn=cmd_model)
+    p = sub.add_parser("model"); p.add_argument("action", choices=["list", "download", "remove"], nargs="?", default="list")
+    p.add_argument("repo", nargs="?"); p.add_argument("--revision", default="main")
+    p.add_argument("--all", action="store_true", help="every file of the repository, not only what the loader reads")
+    p.add_argument("--yes", action="store_true"); p.set_defaults(fn=cmd_model)
     p = sub.add_parser("inferlet"); p.add_argument("action", choices=["list"], nargs="?", default="list"); p.set_defaults(fn=cmd_inferlet)
+    p = sub.add_parser("driver"); p.add_argument("type", help="list | cuda-native | cpu | dummy")
+    p.add_argument("action", nargs="?", choices=["install", "doctor", "show", "set", "unset"])
+    p.add_argument("key", nargs="?"); p.add_argument("value", nargs="?")
+    p.add_argument("--config"); p.add_argument("--run", action="store_true"); p.set_defaults(fn=cmd_driver)
     p = sub.add_parser("new"); p.add_argument("name"); p.set_defaults(fn=cmd_new)
     p = sub.add_parser("build"); p.add_argument("path"); p.set_defaults(fn=cmd_build)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)

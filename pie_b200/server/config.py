@@ -116,8 +116,14 @@ def _build(cls, data: dict, where: str):
     return cls(**kw)
 
 
-def parse(text: str) -> Config:
+def parse(text: str, driver_defaults: Optional[dict] = None) -> Config:
     raw = tomllib.loads(text)
+    if driver_defaults:
+        models = raw.get("model", [])
+        for m in ([models] if isinstance(models, dict) else models):
+            d = m.setdefault("driver", {}) if isinstance(m, dict) else {}
+            for k, v in driver_defaults.get(d.get("type", DriverConfig.type), {}).items():
+                d.setdefault(k, v)
     sections = {"server": ServerConfig, "auth": AuthConfig, "telemetry": TelemetryConfig, "runtime": RuntimeConfig}
     for k in raw:
         if k not in sections and k != "model":
@@ -202,7 +208,13 @@ def default_path() -> Path:
 
 def load(path=None) -> Config:
     p = Path(path).expanduser() if path else default_path()
-    return parse(p.read_text())
+    return parse(p.read_text(), driver_defaults=_driver_defaults())
+
+
+def _driver_defaults() -> dict:
+    """Knobs persisted by `pie driver <type> set` (drivers.toml beside the default config)."""
+    p = default_path().parent / "drivers.toml"
+    return tomllib.loads(p.read_text()) if p.exists() else {}
 
 
 def default_config() -> Config:
