@@ -29,6 +29,7 @@ from .. import ops
 from ..models.config import ModelConfig
 from ..models.transformer import ForwardInputs, ParallelContext, Transformer
 from ..models.weights import random_weights, torch_dtype
+from . import nvtx
 from .kv_cache import KVCache
 from .schema import (Capabilities, CopyRequest, ForwardRequest, ForwardResponse, SamplerKind,
                      SamplerSpec, SlotOutput, position_seed)
@@ -652,7 +653,7 @@ class TorchDriver:
 
     # ------------------------------------------------------------------ public entry points
     def fire_batch(self, req: ForwardRequest) -> ForwardResponse:
-        with self._order:
+        with self._order, nvtx.range("pie.fire"):
             return self._fire_batch(req)
 
     def _fire_batch(self, req: ForwardRequest) -> ForwardResponse:
@@ -673,13 +674,16 @@ class TorchDriver:
         self._token_slots = self._sampler_params(req, None) if nslots else []
         t1 = time.perf_counter()
         if decode and self.cuda:
-            logits = self._run_decode(req, slots, kv_lens)
+            with nvtx.range("forward.decode"):
+                logits = self._run_decode(req, slots, kv_lens)
             slot_logit_row = np.asarray(req.slot_req, dtype=np.int64) if nslots else np.zeros(0, np.int64)
         else:
-            logits = self._run_general(req, qlens, slots, kv_lens)
+            with nvtx.range("forward.general"):
+                logits = self._run_general(req, qlens, slots, kv_lens)
             slot_logit_row = np.arange(nslots, dtype=np.int64)
         t2 = time.perf_counter()
-        resp = self._respond(req, logits, slot_logit_row)
+        with nvtx.range("respond"):
+            resp = self._respond(req, logits, slot_logit_row)
         if self.cuda and nslots == 0:
             torch.cuda.current_stream().synchronize()
         t3 = time.perf_counter()
@@ -747,6 +751,10 @@ class TorchDriver:
 
     def _launch_decode(self, r: int, rb: int, npg: int, parity: int, cascade: bool = False) -> None:
         """Device side of a pipelined decode step (also what tensor-parallel followers run)."""
+        with nvtx.range("pie.decode.launch"):
+            self._launch_decode_impl(r, rb, npg, parity, cascade)
+
+    def _launch_decode_impl(self, r: int, rb: int, npg: int, parity: int, cascade: bool) -> None:
         s = self.slab
         s.upload("tile_qstart", ("page_indices", npg))
         cur, prev = self.cohort_sampled[parity & 1], self.cohort_sampled[(parity & 1) ^ 1]
@@ -833,7 +841,7 @@ class TorchDriver:
         return self.graphs[rb].launches + 1
 
     def copy(self, req: CopyRequest) -> None:
-        with self._order:
+        with self._order, nvtx.range("pie.copy"):
             self._bind_thread()
             if self.par.tp_size > 1 and self.par.comm is not None:
                 self.par.comm.publish_copy(req)     # every rank holds a shard of each page

@@ -245,6 +245,8 @@ class BatchScheduler:
         self.q: "queue.SimpleQueue[Optional[PendingRequest]]" = queue.SimpleQueue()
         self.acc = BatchAccumulator(caps, page_size)
         self.stash: Optional[PendingRequest] = None
+        self._last_fire_start = 0.0
+        self._last_dispatch_end = 0.0
         self.on_batch = on_batch
         self.post_fire_hooks: List[Callable] = []
         self.running = True
@@ -391,7 +393,7 @@ class BatchScheduler:
                         except queue.Empty:
                             break
                     if len(self.acc):
-                        self.execute_batch(self.acc.take())
+                        self.execute_batch(self.acc.take(), time.perf_counter() - t_first)
                 if self.cohort is not None and self._cohort_busy():
                     self._cohort_step()
             except Exception as e:  # keep the scheduler alive; fail what was in flight
@@ -414,24 +416,39 @@ class BatchScheduler:
             if it is not None:
                 self._deliver(it, exc)
 
-    def execute_batch(self, items: List[PendingRequest]) -> None:
+    def execute_batch(self, items: List[PendingRequest], t_accum: float = 0.0) -> None:
+        """One fire. With telemetry on, records the per-fire probe tree (runtime/src/probe/fire.rs:9-30):
+        fire_inter_fire / fire_post_dispatch_to_fire (gaps between fires, siblings of the rest),
+        fire_accumulate_loop, fire_execute_{batch_build, driver_fire, response_dispatch, total} (the three
+        children sum to the total), fire_post_dispatch_hooks, and the driver's own split of its fire
+        (driver_{build, h2d, forward, sample, d2h, total}; runtime/src/probe/driver_cuda.rs)."""
         t0 = time.perf_counter()
+        tel = telemetry.get()
         try:
             req = fold(items, self.page_size)
+            t_built = time.perf_counter()
             resp: ForwardResponse = self.driver.fire_batch(req)
         except Exception as e:
             self.stats["failed_batches"] += 1
             for it in items:
                 self._deliver(it, e)
             return
-        lat = time.perf_counter() - t0
-        tel = telemetry.get()
+        t_fired = time.perf_counter()
+        lat = t_fired - t0
         if tel.enabled:
             tel.incr("fires")
             tel.incr("forward_tokens", req.num_tokens)
-            tel.record_probe_us("fire_batch", lat * 1e6)
-            for k, v in (getattr(resp, "probes", None) or {}).items():
-                tel.record_probe_us(f"driver_{k}", v)
+            us = tel.record_probe_us
+            us("fire_batch", lat * 1e6)
+            if self._last_fire_start:
+                us("fire_inter_fire", (t0 - self._last_fire_start) * 1e6)
+                us("fire_post_dispatch_to_fire", (t0 - self._last_dispatch_end) * 1e6)
+            self._last_fire_start = t0
+            us("fire_accumulate_loop", t_accum * 1e6)
+            us("fire_execute_batch_build", (t_built - t0) * 1e6)
+            us("fire_execute_driver_fire", (t_fired - t_built) * 1e6)
+            for k in ("build", "h2d", "forward", "sample", "d2h", "total"):
+                us(f"driver_{k}", getattr(resp, f"t_{k}_us", 0.0))
         st = self.stats
         st["total_batches"] += 1
         st["total_requests"] += len(items)
@@ -451,10 +468,16 @@ class BatchScheduler:
             n = len(it.samplers)
             self._deliver(it, resp.slots[k:k + n])
             k += n
+        t_disp = time.perf_counter()
         for hook in self.post_fire_hooks:
             hook([it.context_id for it in items])
         if self.on_batch:
             self.on_batch(len(items), req.num_tokens, lat, "batch")
+        if tel.enabled:
+            self._last_dispatch_end = time.perf_counter()
+            tel.record_probe_us("fire_execute_response_dispatch", (t_disp - t_fired) * 1e6)
+            tel.record_probe_us("fire_execute_total", (t_disp - t0) * 1e6)
+            tel.record_probe_us("fire_post_dispatch_hooks", (self._last_dispatch_end - t_disp) * 1e6)
 
     def _deliver(self, it: PendingRequest, result) -> None:
         st = it.chunk_of

@@ -156,7 +156,8 @@ def start_engine(cfg: Config, serve: bool = True, port: Optional[int] = None) ->
         log_dir = Path(cfg.telemetry.log_dir).expanduser() if cfg.telemetry.log_dir else None
         if log_dir:
             log_dir.mkdir(parents=True, exist_ok=True)
-        telemetry.configure(True, str(log_dir / "spans.jsonl") if log_dir else None, cfg.telemetry.service_name)
+        telemetry.configure(True, str(log_dir / "spans.jsonl") if log_dir else None, cfg.telemetry.service_name,
+                            cfg.telemetry.endpoint or None)
     comms = []
     for m in cfg.model:
         drivers, mcfg, tok, comm = build_drivers(m)
