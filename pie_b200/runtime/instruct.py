@@ -4,7 +4,8 @@ A template renders a role message into tokens (`render`), emits the assistant cu
 turn terminator (`seal`), knows the stop tokens, how tool definitions and tool results are
 written (`equip`, `answer`) and how to split reasoning from the answer. Decoders consume
 generated tokens incrementally and emit events (chat text deltas, reasoning segments, tool
-calls). Families: llama3, llama2, qwen (ChatML: Qwen2/Qwen3), mistral, gemma, phi3, olmo,
+calls). Families: llama3, llama2, qwen (ChatML: Qwen2/Qwen3), mistral, mistral3, gemma 2/3, gemma4,
+phi3, olmo2, olmo3,
 gpt-oss (harmony), kimi, deepseek-r1 style reasoning. Counterpart of runtime/src/model/instruct.rs and instruct/*.rs.
 """
 from __future__ import annotations
@@ -24,6 +25,8 @@ class Instruct:
     think_open, think_close = "<think>", "</think>"
     tool_open, tool_close = "<tool_call>", "</tool_call>"
     drop_strings: Sequence[str] = ()      # framing the model writes around its answer; decoders swallow it
+    fold_system = False                   # no system role: the system text opens the first user turn
+    tool_role = "tool"                    # role under which tool results are rendered
 
     def format(self, role: str, message: str, first: bool) -> str:
         return message
@@ -134,7 +137,7 @@ class Llama2(Instruct):
 
 
 class ChatML(Instruct):
-    """Qwen2 / Qwen3 / OLMo-style ChatML."""
+    """Qwen2 / Qwen3 ChatML."""
     name = "qwen"
     stop_strings = ("<|im_end|>", "<|endoftext|>")
 
@@ -167,9 +170,13 @@ class Mistral(Instruct):
 
 
 class Gemma(Instruct):
+    """Gemma 2 / 3: `<start_of_turn>role\n...<end_of_turn>\n`, roles user / model. There is no system
+    role: a leading system message is written as the head of the first user turn
+    (`<bos><start_of_turn>user\n{system}\n{user}<end_of_turn>\n`; model/instruct/gemma3.rs:1-8)."""
     name = "gemma"
     bos = "<bos>"
     stop_strings = ("<end_of_turn>", "<eos>")
+    fold_system = True
 
     def format(self, role, message, first):
         role = "model" if role == "assistant" else "user"
@@ -180,6 +187,109 @@ class Gemma(Instruct):
 
     def seal_text(self):
         return "<end_of_turn>\n"
+
+
+class Gemma4(Instruct):
+    """Gemma 4: single-token turn delimiters `<|turn>` / `<turn|>` and a native system turn
+    (`<bos><|turn>system\n{system}<turn|>\n<|turn>user\n{user}<turn|>\n<|turn>model\n`;
+    model/instruct/gemma4.rs:1-9)."""
+    name = "gemma4"
+    bos = "<bos>"
+    stop_strings = ("<turn|>", "<eos>")
+
+    def format(self, role, message, first):
+        role = {"assistant": "model", "tool": "user"}.get(role, role)
+        return f"<|turn>{role}\n{message}<turn|>\n"
+
+    def cue_text(self):
+        return "<|turn>model\n"
+
+    def seal_text(self):
+        return "<turn|>\n"
+
+
+class Mistral3(Instruct):
+    """Mistral V3 template: `[SYSTEM_PROMPT]..[/SYSTEM_PROMPT]`, `[INST]..[/INST]`,
+    `[AVAILABLE_TOOLS]..[/AVAILABLE_TOOLS]`, calls as `[TOOL_CALLS]name[ARGS]{json}`, results as
+    `[TOOL_RESULTS]..[/TOOL_RESULTS]` (model/instruct/mistral3.rs:1-10)."""
+    name = "mistral3"
+    bos = "<s>"
+    stop_strings = ("</s>",)
+    tool_open, tool_close = "[TOOL_CALLS]", "</s>"
+
+    def format(self, role, message, first):
+        if role == "system":
+            return f"[SYSTEM_PROMPT]{message}[/SYSTEM_PROMPT]"
+        if role == "user":
+            return f"[INST]{message}[/INST]"
+        if role == "tool":
+            return f"[TOOL_RESULTS]{message}[/TOOL_RESULTS]"
+        return f"{message}</s>"
+
+    def seal_text(self):
+        return "</s>"
+
+    def equip(self, tools):
+        return "[AVAILABLE_TOOLS]" + json.dumps([{"type": "function", "function": t} for t in tools]) + "[/AVAILABLE_TOOLS]"
+
+    def answer(self, name, result):
+        return f"[TOOL_RESULTS]{result}[/TOOL_RESULTS]"
+
+    def parse_tool_call(self, text: str):
+        """`name[ARGS]{json}` (the body after `[TOOL_CALLS]`) -> (name, arguments)."""
+        name, sep, args = text.partition("[ARGS]")
+        if not sep:
+            return None
+        try:
+            return name.strip(), json.loads(args)
+        except json.JSONDecodeError:
+            return None
+
+
+class Olmo2(Instruct):
+    """OLMo 2: `<|endoftext|>` opens the chat and ends an assistant turn; plain `<|system|>` / `<|user|>` /
+    `<|assistant|>` markers on their own line, messages separated by newlines
+    (model/instruct/olmo2.rs:5-16)."""
+    name = "olmo2"
+    bos = "<|endoftext|>"
+    stop_strings = ("<|endoftext|>",)
+
+    def format(self, role, message, first):
+        if role == "assistant":
+            return f"<|assistant|>\n{message}<|endoftext|>"
+        return f"<|{'user' if role == 'tool' else role}|>\n{message}\n"
+
+    def cue_text(self):
+        return "<|assistant|>\n"
+
+    def seal_text(self):
+        return "<|endoftext|>"
+
+
+class Olmo3(Instruct):
+    """OLMo 3: ChatML turns; tool definitions ride in the system turn inside `<functions>..</functions>`,
+    calls come back as `<function_calls>..</function_calls>`, results go in an `environment` turn and the
+    assistant cue opens a `<think>` block (model/instruct/olmo3.rs:4-8)."""
+    name = "olmo3"
+    stop_strings = ("<|im_end|>", "<|endoftext|>")
+    tool_open, tool_close = "<function_calls>", "</function_calls>"
+    tool_role = "environment"
+
+    def format(self, role, message, first):
+        role = "environment" if role == "tool" else role
+        return f"<|im_start|>{role}\n{message}<|im_end|>\n"
+
+    def cue_text(self):
+        return "<|im_start|>assistant\n<think>"
+
+    def seal_text(self):
+        return "<|im_end|>\n"
+
+    def equip(self, tools):
+        return "<functions>" + "\n".join(json.dumps(t) for t in tools) + "</functions>"
+
+    def answer(self, name, result):
+        return result
 
 
 class Phi3(Instruct):
@@ -258,9 +368,9 @@ class R1(ChatML):
 
 
 FAMILIES: Dict[str, type] = {"llama3": Llama3, "llama": Llama3, "llama2": Llama2, "qwen": ChatML, "qwen2": ChatML,
-                             "qwen3": ChatML, "qwen3_moe": ChatML, "olmo2": ChatML, "olmo3": ChatML,
-                             "mistral": Mistral, "mistral3": Mistral, "mixtral": Mistral, "gemma": Gemma,
-                             "gemma2": Gemma, "gemma3": Gemma, "gemma4": Gemma, "phi3": Phi3, "r1": R1, "gpt_oss": GptOss,
+                             "qwen3": ChatML, "qwen3_moe": ChatML, "olmo2": Olmo2, "olmo3": Olmo3,
+                             "mistral": Mistral, "mistral3": Mistral3, "mixtral": Mistral, "gemma": Gemma,
+                             "gemma2": Gemma, "gemma3": Gemma, "gemma3n": Gemma, "gemma4": Gemma4, "phi3": Phi3, "r1": R1, "gpt_oss": GptOss,
                              "gptoss": GptOss, "kimi": Kimi, "plain": Instruct}
 
 

@@ -312,8 +312,15 @@ class Context:
         tok = self._model.tokenizer()
         if ins is None:
             self._buffer.extend(tok.encode(message))
-        else:
-            self._buffer.extend(ins.render(role, message, tok, first=self.seq_len + len(self._buffer) == 0))
+            return self
+        if ins.fold_system:
+            # no system role in this family: hold the text and open the next user turn with it
+            if role == "system":
+                self._held_system = (getattr(self, "_held_system", "") + message + "\n")
+                return self
+            if role == "user" and getattr(self, "_held_system", ""):
+                message, self._held_system = self._held_system + message, ""
+        self._buffer.extend(ins.render(role, message, tok, first=self.seq_len + len(self._buffer) == 0))
         return self
 
     def system(self, message: str) -> "Context":
@@ -328,6 +335,9 @@ class Context:
     def cue(self) -> "Context":
         ins = self._model.instruct
         if ins is not None:
+            if getattr(self, "_held_system", ""):          # a system text with no user turn after it
+                held, self._held_system = self._held_system, ""
+                self._fill("user", held.rstrip("\n"))
             self._buffer.extend(ins.cue(self._model.tokenizer()))
         return self
 
