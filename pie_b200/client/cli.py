@@ -8,14 +8,24 @@
         list
         install <source.py> <Pie.toml> [--no-force]
         status
+        config init [--force] | show | update [--host H] [--port P] [--username U]
+                                              [--private-key-path K] [--enable-auth true|false]
 
-Counterpart of client/python/src/pie_client_cli (submit/attach/abort/list/ping/install).
+Connection settings come from, in order: the command line, the client configuration file
+(`~/.pie_b200/client.toml`, or `$PIE_B200_CLIENT_CONFIG`, or `--config`), the defaults. With
+`enable_auth = true` the client proves its identity with the private key before the command runs.
+
+Counterpart of client/python/src/pie_client_cli (submit/attach/abort/list/ping/install, config.py,
+engine.py).
 """
 from __future__ import annotations
 
 import argparse
+import getpass
 import json
+import os
 import sys
+import tomllib
 from pathlib import Path
 
 from .client import ClientError, PieClient
@@ -36,7 +46,8 @@ def _kv_to_json(rest):
     return out
 
 
-def _stream(handle, out=sys.stdout) -> int:
+def _stream(handle, out=None) -> int:
+    out = out or sys.stdout
     while True:
         ev, val = handle.recv(timeout=3600)
         if ev == "stdout":
@@ -54,10 +65,93 @@ def _stream(handle, out=sys.stdout) -> int:
             return 1
 
 
+CONFIG_KEYS = ("host", "port", "username", "private_key_path", "enable_auth")
+
+
+def config_path(custom=None) -> Path:
+    return Path(custom or os.environ.get("PIE_B200_CLIENT_CONFIG", "~/.pie_b200/client.toml")).expanduser()
+
+
+def load_config(custom=None) -> dict:
+    p = config_path(custom)
+    return {k: v for k, v in tomllib.loads(p.read_text()).items() if k in CONFIG_KEYS} if p.exists() else {}
+
+
+def save_config(cfg: dict, custom=None) -> Path:
+    p = config_path(custom)
+    p.parent.mkdir(parents=True, exist_ok=True)
+    fmt = lambda v: ("true" if v else "false") if isinstance(v, bool) else (str(v) if isinstance(v, int) else json.dumps(v))
+    p.write_text("".join(f"{k} = {fmt(cfg[k])}\n" for k in CONFIG_KEYS if cfg.get(k) is not None))
+    return p
+
+
+def find_ssh_key():
+    for name in ("id_ed25519", "id_rsa", "id_ecdsa"):
+        if (Path.home() / ".ssh" / name).exists():
+            return f"~/.ssh/{name}"
+    return None
+
+
+def _check_key(path: str) -> bool:
+    """Warn (never fail) about a private key that is missing, world-readable or unparsable."""
+    p = Path(path).expanduser()
+    if not p.exists():
+        print(f"warning: private key {p} not found", file=sys.stderr)
+        return False
+    if os.name == "posix" and p.stat().st_mode & 0o077:
+        print(f"warning: private key {p} is readable by others (chmod 600)", file=sys.stderr)
+        return False
+    try:
+        from ..server.auth import load_private_key
+        load_private_key(str(p))
+        return True
+    except Exception as e:  # noqa: BLE001
+        print(f"warning: cannot parse private key {p}: {e}", file=sys.stderr)
+        return False
+
+
+def cmd_config(a) -> int:
+    if a.action == "init":
+        p = config_path(a.config)
+        if p.exists() and not a.force:
+            print(f"{p} exists (use --force to overwrite)", file=sys.stderr)
+            return 1
+        key = find_ssh_key()
+        cfg = {"host": "127.0.0.1", "port": 8080, "username": getpass.getuser(), "private_key_path": key or "",
+               "enable_auth": bool(key)}
+        if key:
+            _check_key(key)
+        print(f"wrote {save_config(cfg, a.config)}")
+        return 0
+    if a.action == "show":
+        p = config_path(a.config)
+        if not p.exists():
+            print(f"no configuration at {p} (run `config init`)", file=sys.stderr)
+            return 1
+        print(f"# {p}\n{p.read_text()}", end="")
+        return 0
+    cfg = load_config(a.config)
+    changed = False
+    for k in CONFIG_KEYS:
+        v = getattr(a, k, None)
+        if v is not None:
+            cfg[k] = v
+            changed = True
+    if not changed:
+        print("nothing to update: give at least one of --host --port --username --private-key-path --enable-auth",
+              file=sys.stderr)
+        return 1
+    if cfg.get("private_key_path") and a.private_key_path is not None:
+        _check_key(cfg["private_key_path"])
+    print(f"updated {save_config(cfg, a.config)}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="pie-client")
-    ap.add_argument("--uri", default="ws://127.0.0.1:8080")
+    ap.add_argument("--uri", default=None)
     ap.add_argument("--token", default="")
+    ap.add_argument("--config", default=None, help="client configuration file")
     sub = ap.add_subparsers(dest="cmd", required=True)
     sub.add_parser("ping")
     sub.add_parser("list")
@@ -74,7 +168,18 @@ def main(argv=None) -> int:
     p.add_argument("source")
     p.add_argument("manifest")
     p.add_argument("--no-force", action="store_true")
+    p = sub.add_parser("config")
+    p.add_argument("action", choices=["init", "show", "update"])
+    p.add_argument("--force", action="store_true")
+    p.add_argument("--host"); p.add_argument("--port", type=int); p.add_argument("--username")
+    p.add_argument("--private-key-path", dest="private_key_path")
+    p.add_argument("--enable-auth", dest="enable_auth", type=lambda v: v.lower() in ("1", "true", "yes"))
     a, rest = ap.parse_known_args(argv)
+    if a.cmd == "config":
+        return cmd_config(a)
+    cfg = load_config(a.config)
+    if a.uri is None:
+        a.uri = f"ws://{cfg.get('host', '127.0.0.1')}:{cfg.get('port', 8080)}"
     try:
         c = PieClient(a.uri)
     except Exception as e:  # noqa: BLE001
@@ -83,6 +188,10 @@ def main(argv=None) -> int:
     try:
         if a.token:
             c.auth_by_token(a.token)
+        elif cfg.get("enable_auth") and cfg.get("private_key_path"):
+            from ..server.auth import load_private_key
+            c.auth_with_key(cfg.get("username") or getpass.getuser(),
+                            load_private_key(str(Path(cfg["private_key_path"]).expanduser())))
         if a.cmd == "ping":
             print(c.ping())
         elif a.cmd == "list":

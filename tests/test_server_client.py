@@ -260,3 +260,36 @@ def test_cli_runs_a_gguf_model_with_its_own_tokenizer(tmp_path, capsys):
     # the prompt was tokenised with the file's vocabulary: the same ids as the source tokenizer gives
     from pie_b200.runtime.tokenizer import load_gguf_tokenizer
     assert load_gguf_tokenizer(path).encode("hello world") == tok.encode("hello world").ids
+
+
+def test_client_cli_config_file_and_key_auth(stack, tmp_path, capsys, monkeypatch):
+    """`pie-client config init | update | show`, and a command that authenticates with the configured key."""
+    from cryptography.hazmat.primitives import serialization
+    from pie_b200.client import cli
+    eng, srv, auth, key, uri = stack
+    monkeypatch.setenv("HOME", str(tmp_path))
+    conf = tmp_path / "client.toml"
+    monkeypatch.setenv("PIE_B200_CLIENT_CONFIG", str(conf))
+    assert cli.main(["config", "show"]) == 1
+    assert cli.main(["config", "init"]) == 0
+    assert cli.main(["config", "init"]) == 1                      # refuses to overwrite without --force
+    assert cli.load_config()["enable_auth"] is False             # no key under ~/.ssh
+    assert cli.main(["config", "update"]) == 1
+    kp = tmp_path / "id_test"
+    kp.write_bytes(key.private_bytes(serialization.Encoding.PEM, serialization.PrivateFormat.OpenSSH,
+                                     serialization.NoEncryption()))
+    kp.chmod(0o600)
+    port = int(uri.rsplit(":", 1)[1])
+    assert cli.main(["config", "update", "--port", str(port), "--username", "alice", "--private-key-path", str(kp),
+                     "--enable-auth", "true"]) == 0
+    assert cli.load_config() == {"host": "127.0.0.1", "port": port, "username": "alice", "private_key_path": str(kp),
+                                 "enable_auth": True}
+    capsys.readouterr()
+    assert cli.main(["config", "show"]) == 0
+    assert 'username = "alice"' in capsys.readouterr().out
+    assert cli.main(["status"]) == 0                               # needs authentication: done with the key
+    assert "mock" in capsys.readouterr().out
+    assert cli.main(["submit", "text-completion", "--prompt_tokens", "[5, 6]", "--max_tokens", "3", "--stop_tokens", "[]"]) == 0
+    assert json.loads(capsys.readouterr().out)["tokens"] == [7, 8, 9]
+    assert cli.main(["config", "update", "--enable-auth", "false"]) == 0
+    assert cli.main(["status"]) == 1                               # the server still wants authentication
