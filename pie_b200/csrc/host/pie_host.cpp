@@ -8,6 +8,8 @@
 #include "brle.hpp"
 #include "grammar.hpp"
 #include "pagestore.hpp"
+#include "poll_ring.hpp"
+#include "shm_channel.hpp"
 
 namespace py = pybind11;
 using namespace pie_host;
@@ -40,6 +42,81 @@ PYBIND11_MODULE(pie_host, m) {
         std::copy(v.begin(), v.end(), reinterpret_cast<uint8_t*>(out.mutable_data()));
         return out;
     });
+
+    // ------------------------------------------------------------------ runtime <-> driver channel
+    py::class_<ShmChannel>(m, "ShmChannel")
+        .def(py::init<const std::string&, bool, uint32_t, uint32_t, uint32_t, uint32_t, uint64_t, uint32_t>(),
+             py::arg("name"), py::arg("create"), py::arg("num_slots") = 64, py::arg("req_capacity") = 1 << 20,
+             py::arg("resp_capacity") = 1 << 20, py::arg("schema_version") = 0, py::arg("schema_hash") = 0,
+             py::arg("spin_iters") = 2000)
+        .def_property_readonly("num_slots", &ShmChannel::num_slots)
+        .def_property_readonly("req_capacity", &ShmChannel::req_capacity)
+        .def_property_readonly("resp_capacity", &ShmChannel::resp_capacity)
+        .def_property_readonly("closed", &ShmChannel::closed)
+        .def("close", &ShmChannel::close_channel)
+        .def("submit", [](ShmChannel& c, py::buffer b) {
+            py::buffer_info info = b.request();
+            return c.submit(info.ptr, (size_t)info.size * (size_t)info.itemsize);
+        })
+        .def("wait_response", [](ShmChannel& c, int slot, double timeout_s) -> py::object {
+            int rc;
+            {
+                py::gil_scoped_release nogil;
+                rc = c.wait_response(slot, (uint64_t)(timeout_s * 1e9));
+            }
+            if (rc == 1) {
+                uint32_t len;
+                const uint8_t* p = c.response(slot, &len);
+                py::bytes out(reinterpret_cast<const char*>(p), len);
+                uint64_t q, sv;
+                c.timings(slot, &q, &sv);
+                c.release(slot);
+                return py::make_tuple(out, (double)q * 1e-3, (double)sv * 1e-3);
+            }
+            if (rc == -2) throw std::runtime_error("driver channel closed");
+            return py::none();
+        }, py::arg("slot"), py::arg("timeout_s"))
+        .def("abort", &ShmChannel::abort_slot)
+        .def("slot_state", &ShmChannel::slot_state)
+        .def("next_request", [](ShmChannel& c, double timeout_s) -> py::object {
+            int slot;
+            {
+                py::gil_scoped_release nogil;
+                slot = c.next_request((uint64_t)(timeout_s * 1e9));
+            }
+            if (slot == -2) throw std::runtime_error("driver channel closed");
+            if (slot < 0) return py::none();
+            uint32_t len;
+            uint64_t id;
+            const uint8_t* p = c.request(slot, &len, &id);
+            return py::make_tuple(slot, id, py::bytes(reinterpret_cast<const char*>(p), len));
+        }, py::arg("timeout_s"))
+        .def("respond", [](ShmChannel& c, int slot, py::buffer b) {
+            py::buffer_info info = b.request();
+            return c.respond(slot, info.ptr, (size_t)info.size * (size_t)info.itemsize);
+        });
+
+    py::class_<PollRing>(m, "PollRing")
+        .def(py::init<uint32_t, int64_t>(), py::arg("slots") = 1024, py::arg("spin_budget") = 20000)
+        .def_property_readonly("slots", &PollRing::slots)
+        .def_property_readonly("parks", &PollRing::parks)
+        .def_property_readonly("closed", &PollRing::closed)
+        .def_property_readonly("head", &PollRing::head)
+        .def_property_readonly("tail", &PollRing::tail)
+        .def("claim", &PollRing::claim)
+        .def("publish", &PollRing::publish)
+        .def("poll", [](PollRing& r, double timeout_s) {
+            py::gil_scoped_release nogil;
+            return r.poll((uint64_t)(timeout_s * 1e9));
+        })
+        .def("complete", &PollRing::complete)
+        .def("wait_done", [](PollRing& r, uint64_t seq, double timeout_s) {
+            py::gil_scoped_release nogil;
+            return r.wait_done(seq, (uint64_t)(timeout_s * 1e9));
+        })
+        .def("is_done", &PollRing::is_done)
+        .def("release", &PollRing::release)
+        .def("close", &PollRing::close_ring);
 
     // ------------------------------------------------------------------ pages
     m.def("page_hash", [](uint64_t prev, const std::vector<uint32_t>& tokens, const std::vector<uint32_t>& positions,

@@ -30,7 +30,8 @@ from .schema import (CopyDir, CopyRequest, ForwardRequest, ForwardResponse, Samp
 
 MAGIC = b"PIE4"
 SCHEMA_VERSION = 2
-KIND_FORWARD_REQUEST, KIND_FORWARD_RESPONSE, KIND_COPY_REQUEST = 1, 2, 3
+KIND_FORWARD_REQUEST, KIND_FORWARD_RESPONSE, KIND_COPY_REQUEST, KIND_DECODE_STEP, KIND_CONTROL = 1, 2, 3, 4, 5
+TOKEN_MAGIC = b"PIETFWD1"      # token-only response: magic, u32 count, f32 forward us, f32 total us, then int32 tokens
 
 # dtype codes of sections
 U8, I32, I64, F32, U64, JSON = 1, 2, 3, 4, 5, 6
@@ -75,6 +76,19 @@ FIELDS: List[Tuple[str, str, int, int]] = [
     ("copy_request", "direction", 60, I32),
     ("copy_request", "srcs", 61, I32),
     ("copy_request", "dsts", 62, I32),
+    ("decode_step", "meta", 80, I32),                     # [rows, parity]
+    ("decode_step", "host_tokens", 81, I32),
+    ("decode_step", "src_row", 82, I32),
+    ("decode_step", "positions", 83, I32),
+    ("decode_step", "kv_lens", 84, I32),
+    ("decode_step", "page_indptr", 85, I32),
+    ("decode_step", "page_indices", 86, I32),
+    ("decode_step", "temperature", 87, F32),
+    ("decode_step", "top_k", 88, I32),
+    ("decode_step", "top_p", 89, F32),
+    ("decode_step", "min_p", 90, F32),
+    ("decode_step", "seeds", 91, I64),
+    ("control", "json", 100, JSON),                       # cold operations: adapters, health, capabilities, shutdown
 ]
 
 _SLOT_KINDS = ["token", "distribution", "logits", "logprobs", "entropy", "embedding"]
@@ -280,6 +294,55 @@ def unpack_copy_request(buf) -> CopyRequest:
     return CopyRequest(CopyDir(int(s["direction"][0])), s.get("srcs", np.zeros(0, np.int32)), s.get("dsts", np.zeros(0, np.int32)))
 
 
+# ----------------------------------------------------------------------------- pipelined decode step
+_STEP_ARRAYS = ("host_tokens", "src_row", "positions", "kv_lens", "page_indptr", "page_indices", "temperature",
+                "top_k", "top_p", "min_p", "seeds")
+
+
+def pack_decode_step(step, parity: int) -> bytes:
+    vals = {"meta": [int(step.r), int(parity)]}
+    vals.update({k: getattr(step, k) for k in _STEP_ARRAYS})
+    return _frame(KIND_DECODE_STEP, "decode_step", vals)
+
+
+def unpack_decode_step(buf):
+    from .executor import CohortStep
+    kind, s = _sections(buf)
+    if kind != KIND_DECODE_STEP:
+        raise ValueError("not a decode step frame")
+    dt = {k: _NP[_ID[("decode_step", k)][1]] for k in _STEP_ARRAYS}
+    return CohortStep(int(s["meta"][0]), *[s.get(k, np.zeros(0, dt[k])) for k in _STEP_ARRAYS]), int(s["meta"][1])
+
+
+def pack_tokens(tokens, forward_us: float = 0.0, total_us: float = 0.0) -> bytes:
+    t = np.ascontiguousarray(tokens, dtype=np.int32)
+    return TOKEN_MAGIC + struct.pack("<Iff", t.size, forward_us, total_us) + t.tobytes()
+
+
+def is_token_frame(buf) -> bool:
+    return bytes(buf[:8]) == TOKEN_MAGIC
+
+
+def unpack_tokens(buf):
+    n, fwd, tot = struct.unpack_from("<Iff", buf, 8)
+    return np.frombuffer(buf, dtype=np.int32, count=n, offset=20).copy(), fwd, tot
+
+
+def pack_control(obj: dict) -> bytes:
+    return _frame(KIND_CONTROL, "control", {"json": obj})
+
+
+def unpack_control(buf) -> dict:
+    kind, s = _sections(buf)
+    if kind != KIND_CONTROL:
+        raise ValueError("not a control frame")
+    return s["json"]
+
+
+def frame_kind(buf) -> int:
+    return _HDR.unpack_from(buf, 0)[3]
+
+
 # ----------------------------------------------------------------------------- C header
 def c_header() -> str:
     """`pie_bridge.h`: the frame layout and the section ids for drivers written in C or C++."""
@@ -290,7 +353,9 @@ def c_header() -> str:
         "#ifndef PIE_BRIDGE_H", "#define PIE_BRIDGE_H", "#include <stdint.h>", "#include <string.h>", "",
         f"#define PIE_BRIDGE_SCHEMA_VERSION {SCHEMA_VERSION}u",
         f"#define PIE_BRIDGE_SCHEMA_HASH64 0x{schema_hash()[:16]}ull", "",
-        "enum PieFrameKind { PIE_FRAME_FORWARD_REQUEST = 1, PIE_FRAME_FORWARD_RESPONSE = 2, PIE_FRAME_COPY_REQUEST = 3 };",
+        "enum PieFrameKind { PIE_FRAME_FORWARD_REQUEST = 1, PIE_FRAME_FORWARD_RESPONSE = 2, PIE_FRAME_COPY_REQUEST = 3,",
+        "                    PIE_FRAME_DECODE_STEP = 4, PIE_FRAME_CONTROL = 5 };",
+        "/* A token-only response skips the frame: \"PIETFWD1\", uint32 count, float forward_us, float total_us, int32[count]. */",
         "enum PieSectionType { PIE_U8 = 1, PIE_I32 = 2, PIE_I64 = 3, PIE_F32 = 4, PIE_U64 = 5, PIE_JSON = 6 };", "",
         "typedef struct PieFrameHeader {", "    char magic[4];            /* \"PIE4\" */", "    uint32_t schema_version;",
         "    uint64_t schema_hash64;", "    uint32_t kind;", "    uint32_t num_sections;", "    uint64_t frame_bytes;",

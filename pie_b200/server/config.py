@@ -75,6 +75,8 @@ class DriverConfig:
     gemm: str = "tcgen05"
     tp_backend: str = "fused"
     memory_profile: str = ""              # "" = built-in limits; auto | latency | balanced | throughput | capacity
+    ipc: str = "direct"                   # runtime -> driver: direct call | inproc (queue + service thread) |
+                                          # latency (polled ring) | shmem (driver in a process of its own)
 
 
 @dataclass

@@ -29,6 +29,48 @@ log = logging.getLogger("pie_b200")
 
 
 def build_drivers(m: ModelSection):
+    """Drivers of one model behind the configured channel (`[model.driver] ipc`): the driver objects
+    themselves (`direct`), each behind a service thread (`inproc`, `latency`), or one in a process of its
+    own reached through shared memory (`shmem`). Returns (drivers, cfg, tokenizer, comm)."""
+    ipc = m.driver.ipc
+    if ipc == "shmem":
+        from dataclasses import asdict
+        from ..driver.channel import spawn_driver_process
+        cfg, tok = _config_and_tokenizer(m)
+        sec = asdict(m)
+        sec["driver"]["ipc"] = "direct"
+        drv, _proc = spawn_driver_process(f"pie_b200_drv_{os.getpid()}_{m.name}".replace("/", "_"), sec)
+        return [drv], cfg, tok, None
+    drivers, cfg, tok, comm = _build_drivers_direct(m)
+    if ipc in ("inproc", "latency") and comm is None:
+        from ..driver.channel import ChannelDriver, make_channel
+        drivers = [ChannelDriver(make_channel(drv, ipc), on_shutdown=getattr(drv, "shutdown", None)) for drv in drivers]
+    return drivers, cfg, tok, comm
+
+
+def _config_and_tokenizer(m: ModelSection):
+    """What the runtime needs to know of a model whose driver lives elsewhere."""
+    tok = None
+    if not m.path:
+        return (preset(m.preset) if m.preset else ModelConfig(name=m.name)), tok
+    mp = Path(m.path)
+    ggufs = [mp] if mp.suffix == ".gguf" else ([] if list(mp.glob("*.safetensors")) else sorted(mp.glob("*.gguf")))
+    if ggufs:
+        from ..models.gguf import GGUFReader
+        from ..runtime.tokenizer import load_gguf_tokenizer
+        rd = GGUFReader(ggufs[0])
+        cfg = rd.config()
+        if rd.meta.get("tokenizer.ggml.tokens") and rd.meta.get("tokenizer.ggml.model", "gpt2") == "gpt2":
+            tok = load_gguf_tokenizer(rd)
+    else:
+        cfg = ModelConfig.from_path(m.path)
+    cfg.name = m.name
+    if tok is None and mp.is_dir() and (mp / "tokenizer.json").exists():
+        tok = load_hf_tokenizer(m.path)
+    return cfg, tok
+
+
+def _build_drivers_direct(m: ModelSection):
     """Drivers of one model: one per data-parallel group. Returns (drivers, cfg, tokenizer, comm)."""
     d = m.driver
     tok = None
