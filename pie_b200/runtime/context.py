@@ -72,8 +72,18 @@ class PinnedContext:
     driver: int
 
 
+class Deferred(ContextError):
+    """The allocation must wait: pages are held back for, or can only come from, contexts that outrank the
+    requester. `ContextManager.when_restorable` calls back when it is worth trying again."""
+
+
 class ContextManager:
-    """All contexts of one model. Thread-safe: inferlet host calls and the scheduler share it."""
+    """All contexts of one model. Thread-safe: inferlet host calls and the scheduler share it.
+
+    Allocation order (`_alloc`; runtime/src/context/sched.rs:717-868): (1) priority gate - free pages
+    that the head of the restore queue needs are not handed to a requester that does not outrank it;
+    (2) the free pool; (3) the eviction loop, victims in market order; (4) defer - the requester's
+    operation fails with `Deferred` and may queue itself with `when_restorable`."""
 
     def __init__(self, model: str, page_size: int, stores: Sequence[PageStore],
                  copy_fn: Optional[Callable[[int, CopyRequest], None]] = None,
@@ -91,6 +101,10 @@ class ContextManager:
         self.counters = {"created": 0, "forked": 0, "commits": 0, "dedup_pages": 0, "suspended": 0,
                          "restored": 0, "evictions": 0, "replayed_tokens": 0}
         self.market = None   # optional Market: orders eviction victims (defaulted, lowest bid, newest)
+        self.restore_pause_at_utilization = 0.85
+        self.restore_queue: Dict[int, list] = {d: [] for d in range(len(self.stores))}   # per driver: waiting contexts
+        self.page_waiters: Dict[int, list] = {d: [] for d in range(len(self.stores))}    # one-shot callbacks
+        self.counters.update({"deferred": 0, "gate_holds": 0, "restore_wakeups": 0})
 
     # ------------------------------------------------------------------ helpers
     def _get(self, cid: int) -> Context:
@@ -102,17 +116,132 @@ class ContextManager:
     def _store(self, ctx: Context) -> PageStore:
         return self.stores[ctx.driver]
 
+    def _rank(self, ctx: Optional[Context]) -> tuple:
+        """Higher outranks lower: (not defaulted, bid, older first)."""
+        if ctx is None:
+            return (0, float("-inf"), 0)
+        defaulted = bool(self.market.defaulted(ctx.owner)) if self.market is not None else False
+        return (0 if defaulted else 1, ctx.bid, -ctx.created_seq)
+
+    def _restore_need(self, ctx: Context) -> int:
+        """Pages a suspended context must be given to come back."""
+        store = self._store(ctx)
+        missing = len(ctx.chain) - store.prefix_len(ctx.chain)
+        return missing + getattr(ctx, "_n_working", -(-len(ctx.tokens) // self.page_size))
+
+    def _queue_head(self, driver: int) -> Optional[Context]:
+        q = self.restore_queue[driver]
+        while q:
+            ctx = self.contexts.get(q[0][0])
+            if ctx is not None and ctx.state == State.SUSPENDED:
+                return ctx
+            q.pop(0)                                   # restored by another path, or destroyed
+        return None
+
     def _alloc(self, driver: int, n: int, exclude: Optional[int] = None) -> List[int]:
         store = self.stores[driver]
+        requester = self.contexts.get(exclude) if exclude is not None else None
+        head = self._queue_head(driver)
+        if head is not None and head is not requester and self._rank(requester)[:2] < self._rank(head)[:2]:
+            if store.pool.free_count - n < self._restore_need(head):
+                self.counters["gate_holds"] += 1
+                raise Deferred(f"KV pages are held for context {head.id}, which outranks the requester")
         pages = store.pool.alloc(n)
         while pages is None:
             if not self._evict_one(driver, exclude):
-                raise ContextError(f"out of KV pages: need {n}, free {store.pool.free_count}")
+                self.counters["deferred"] += 1
+                raise Deferred(f"out of KV pages: need {n}, free {store.pool.free_count}")
             pages = store.pool.alloc(n)
         return pages
 
     def least_loaded_driver(self) -> int:
         return max(range(len(self.stores)), key=lambda d: self.stores[d].pool.free_count)
+
+    def best_driver_for(self, hashes: Sequence[int] = (), n_pages: int = 0) -> int:
+        """Data-parallel placement: the replica where the context is cheapest to build - each page of the
+        chain `hashes` already in a replica's store is a page that need not be computed or moved there;
+        ties and empty chains go to the replica with the most free pages (sched.rs:367-417)."""
+        with self.lock:
+            def cost(d: int):
+                present = self.stores[d].prefix_len(list(hashes)) if hashes else 0
+                need = max(0, max(n_pages, len(hashes)) - present)
+                short = max(0, need - self.stores[d].pool.free_count)      # pages that would need an eviction
+                return (short, need, -self.stores[d].pool.free_count)
+            return min(range(len(self.stores)), key=cost)
+
+    # ------------------------------------------------------------------ restore admission
+    def can_restore(self, cid: int) -> bool:
+        """Whether a suspended context may come back now: its pages fit in what is free plus what contexts
+        it outranks could give up, and - unless it heads the queue of an otherwise idle pool - the pool
+        stays under `restore_pause_at_utilization` afterwards (sched.rs:881-938)."""
+        with self.lock:
+            ctx = self._get(cid)
+            if ctx.state != State.SUSPENDED:
+                return True
+            store = self._store(ctx)
+            need = self._restore_need(ctx)
+            free = store.pool.free_count
+            total = free + store.pool.used_count
+            if need <= free:
+                head = self._queue_head(ctx.driver)
+                if head is None or head is ctx or self._rank(ctx)[:2] >= self._rank(head)[:2]:
+                    return (total - free + need) <= self.restore_pause_at_utilization * total or \
+                        not any(c.pins for c in self.contexts.values() if c.driver == ctx.driver)
+                return free - need >= self._restore_need(head)
+            mine = self._rank(ctx)
+            evictable = sum(len(c.working_pages) + store.would_free(c.chain) for c in self.contexts.values()
+                            if c.driver == ctx.driver and c.state == State.ACTIVE and c.pins == 0 and c is not ctx
+                            and self._rank(c)[:2] <= mine[:2])
+            return need <= free + evictable
+
+    def when_restorable(self, cid: int, callback: Callable[[], None]) -> None:
+        """Queue a suspended context (best rank first, then arrival); `callback` runs once, outside the
+        lock, when pages were freed and `can_restore` holds - or at once if it already does."""
+        with self.lock:
+            ctx = self._get(cid)
+            if ctx.state != State.SUSPENDED or self.can_restore(cid):
+                ready = True
+            else:
+                ready = False
+                q = self.restore_queue[ctx.driver]
+                q.append((cid, callback, next(self._seq)))
+                q.sort(key=lambda e: (tuple(-x for x in self._rank(self.contexts[e[0]])[:2]) if e[0] in self.contexts
+                                      else (0, 0), e[2]))
+        if ready:
+            callback()
+
+    def _waiting(self, driver: int) -> bool:
+        return bool(self.restore_queue[driver] or self.page_waiters[driver])
+
+    def on_pages_freed(self, driver: int, callback: Callable[[], None]) -> None:
+        """One-shot: `callback` runs (outside the lock) the next time pages of `driver` are given back.
+        For requesters that were deferred while resident (growth under contention)."""
+        with self.lock:
+            self.page_waiters[driver].append(callback)
+
+    def _pages_freed(self, driver: int) -> None:
+        """Wake the waiters that can come back now, best rank first, then the deferred growers. Call
+        without the lock held."""
+        ready = []
+        with self.lock:
+            q = self.restore_queue[driver]
+            while q:
+                cid, cb, _ = q[0]
+                ctx = self.contexts.get(cid)
+                if ctx is None or ctx.state != State.SUSPENDED:
+                    q.pop(0)
+                    if ctx is not None:
+                        ready.append(cb)
+                    continue
+                if not self.can_restore(cid):
+                    break
+                q.pop(0)
+                ready.append(cb)
+            self.counters["restore_wakeups"] += len(ready)
+            ready += self.page_waiters[driver]
+            self.page_waiters[driver] = []
+        for cb in ready:
+            cb()
 
     # ------------------------------------------------------------------ lifecycle
     def create(self, owner: str, driver: Optional[int] = None) -> int:
@@ -139,6 +268,9 @@ class ContextManager:
             ctx.state = State.DESTROYED
             self.by_owner.get(ctx.owner, set()).discard(cid)
             del self.contexts[cid]
+            waiting = self._waiting(ctx.driver)
+        if waiting:
+            self._pages_freed(ctx.driver)
 
     def destroy_owner(self, owner: str) -> None:
         with self.lock:
@@ -181,6 +313,9 @@ class ContextManager:
                 self._truncate_to(ctx, keep * self.page_size)
             freed, ctx.working_pages = ctx.working_pages[keep:], ctx.working_pages[:keep]
             self._store(ctx).pool.free(freed)
+            waiting = self._waiting(ctx.driver)
+        if waiting:
+            self._pages_freed(ctx.driver)
 
     def truncate_working_page_tokens(self, cid: int, n: int) -> None:
         with self.lock:
@@ -325,6 +460,9 @@ class ContextManager:
             ctx.pins = max(0, ctx.pins - 1)
             if ctx.pins == 0 and ctx.state == State.PINNED:
                 ctx.state = State.ACTIVE
+            waiting = ctx.pins == 0 and self._waiting(ctx.driver)
+        if waiting:
+            self._pages_freed(ctx.driver)       # an unpinned context is evictable again
 
     def pinned_count(self) -> int:
         with self.lock:
@@ -371,6 +509,9 @@ class ContextManager:
             ctx = self._get(cid)
             if ctx.state != State.SUSPENDED:
                 return []
+            if not self.can_restore(cid):
+                self.counters["deferred"] += 1
+                raise Deferred(f"context {cid} cannot be restored yet: {self._restore_need(ctx)} pages needed")
             store = self._store(ctx)
             ps = self.page_size
             # committed prefix still present in the store can simply be re-acquired
@@ -426,6 +567,9 @@ class ContextManager:
             victim = min(cands, key=lambda c: self.market.victim_key(c.owner, c.bid, c.created_seq))
         else:
             victim = min(cands, key=lambda c: (c.bid, -c.created_seq))
+        requester = self.contexts.get(exclude) if exclude is not None else None
+        if requester is not None and self._rank(victim)[:2] > self._rank(requester)[:2]:
+            return False                 # the cheapest victim outranks the requester: the requester waits
         before = self.stores[driver].pool.free_count
         self.suspend(victim.id)
         self.counters["evictions"] += 1

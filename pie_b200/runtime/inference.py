@@ -22,14 +22,14 @@ from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
 from ..driver.schema import SamplerSpec, SlotOutput
-from .context import ContextError, ContextManager
+from .context import ContextError, ContextManager, Deferred
 from .scheduler import BatchScheduler, PendingRequest
 
 
 class Future:
     """Minimal thread-safe future with completion callbacks (usable from asyncio or threads)."""
 
-    __slots__ = ("_ev", "_result", "_exc", "_cbs", "_lock", "done_flag")
+    __slots__ = ("_ev", "_result", "_exc", "_cbs", "_lock", "done_flag", "_defer_tries")
 
     def __init__(self):
         self._ev = threading.Event()
@@ -98,6 +98,7 @@ class InferenceService:
         self.cohorts: list = []       # DecodeCohort per driver (set by the engine)
         self.staged: Dict[int, _Staged] = {}
         self.lock = threading.Lock()
+        self.max_defers = 8          # times one request may wait in the restore queue before it fails
         self.stats = {"submits": 0, "bypass_hits": 0, "chain_submits": 0, "chain_drops": 0,
                       "tokens_appended": 0}
         self.on_tokens: Optional[Callable[[int, int], None]] = None   # (context id, n tokens) accounting hook
@@ -206,6 +207,21 @@ class InferenceService:
         all_positions = positions + spec_positions
         try:
             pinned = self.ctxm.pin(cid, len(all_tokens))
+        except Deferred as e:
+            # evicted and no room to come back yet: wait in the restore queue, bounded by the deadline
+            tries = getattr(fut, "_defer_tries", 0)
+            if tries >= self.max_defers:
+                fut.set(exc=e)
+                return
+            fut._defer_tries = tries + 1
+            self.stats["deferred_starts"] = self.stats.get("deferred_starts", 0) + 1
+            try:
+                self.ctxm.when_restorable(cid, lambda: self._start(cid, tokens, positions, samplers, masks, logit_mask,
+                                                                   spec_tokens, spec_positions, adapter, speculate,
+                                                                   fut, staged))
+            except ContextError as e2:
+                fut.set(exc=e2)
+            return
         except ContextError as e:
             fut.set(exc=e)
             return

@@ -200,7 +200,7 @@ class Forward:
         if n_in == 0:
             from ..runtime.inference import ForwardOutput
             return Output(ForwardOutput(slots=[]), None)
-        ctx._reserve_for(n_in)
+        await ctx._reserve_async(n_in)
         svc = ctx._entry.inference
         fut = svc.submit(ctx.id, self._tokens, self._positions, self._samplers, self._attn_masks, self._mask,
                          self._spec_tokens, self._spec_positions, self._adapter, self._speculate)
@@ -375,6 +375,28 @@ class Context:
         need = self._seq_len + n_new + 1
         if need > have:
             ctxm.reserve_working_pages(self.id, -(-(need - have) // ps))
+
+    async def _reserve_async(self, n_new: int, timeout_s: float = 120.0) -> None:
+        """`_reserve_for` that waits while the allocation is deferred (pages held for, or only obtainable
+        from, contexts that outrank this one): it retries whenever pages are given back, until the
+        deadline, then fails with the deferral (runtime/src/context/sched.rs:717 `when_allocated`)."""
+        import time as _time
+        from ..runtime.context import Deferred
+        from ..runtime.inference import Future
+        deadline = _time.monotonic() + timeout_s
+        while True:
+            try:
+                return self._reserve_for(n_new)
+            except Deferred:
+                if _time.monotonic() >= deadline:
+                    raise
+                ctxm = self._entry.ctxm
+                fut = Future()
+                ctxm.on_pages_freed(ctxm.contexts[self.id].driver, lambda: fut.done_flag or fut.set(True))
+                try:
+                    await asyncio.wait_for(host.wait(fut), timeout=min(1.0, max(0.01, deadline - _time.monotonic())))
+                except asyncio.TimeoutError:
+                    pass
 
     def _after_pass(self, accepted: int, positions: Sequence[int]) -> None:
         self._seq_len += accepted
@@ -568,7 +590,7 @@ class Generator:
         toks, ctx._buffer = ctx._buffer, []
         n = self._max if self._max is not None else 1 << 30
         start = ctx.seq_len
-        ctx._reserve_for(len(toks) + 1)
+        await ctx._reserve_async(len(toks) + 1)
         stream = ctx._entry.inference.start_stream(ctx.id, toks, list(range(start, start + len(toks))),
                                                    self.sampler.spec, n, self._stop)
         if on_tokens is not None:
