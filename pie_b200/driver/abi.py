@@ -89,6 +89,7 @@ FIELDS: List[Tuple[str, str, int, int]] = [
     ("decode_step", "min_p", 90, F32),
     ("decode_step", "seeds", 91, I64),
     ("control", "json", 100, JSON),                       # cold operations: adapters, health, capabilities, shutdown
+    ("forward_response", "spec_accepted", 45, I32),       # accepted drafts per request
 ]
 
 _SLOT_KINDS = ["token", "distribution", "logits", "logprobs", "entropy", "embedding"]
@@ -260,7 +261,8 @@ def pack_forward_response(r: ForwardResponse) -> bytes:
                             "logits": None if sl.logits is None else base64.b64encode(sl.logits).decode()})
     vals = {"slot_kind": [_SLOT_KINDS.index(sl.kind) for sl in r.slots], "slot_token": [sl.token for sl in r.slots],
             "slot_payload": payload if any(p is not None for p in payload) else None, "tokens": r.tokens,
-            "timings_us": [r.t_build_us, r.t_h2d_us, r.t_forward_us, r.t_sample_us, r.t_d2h_us, r.t_total_us]}
+            "timings_us": [r.t_build_us, r.t_h2d_us, r.t_forward_us, r.t_sample_us, r.t_d2h_us, r.t_total_us],
+            "spec_accepted": r.spec_accepted}
     return _frame(KIND_FORWARD_RESPONSE, "forward_response", vals)
 
 
@@ -279,7 +281,7 @@ def unpack_forward_response(buf) -> ForwardResponse:
             sl.logits = None if p["logits"] is None else base64.b64decode(p["logits"])
         slots.append(sl)
     t = s.get("timings_us", np.zeros(6, np.float32))
-    return ForwardResponse(slots, s.get("tokens"), *[float(x) for x in t])
+    return ForwardResponse(slots, s.get("tokens"), *[float(x) for x in t], spec_accepted=s.get("spec_accepted"))
 
 
 # ----------------------------------------------------------------------------- copy request

@@ -364,7 +364,8 @@ def serve_shm(driver, name: str, idle_timeout_s: float = 0.5, stop: Optional[Cal
             if kind == abi.KIND_FORWARD_REQUEST:
                 resp = driver.fire_batch(abi.unpack_forward_request(buf))
                 out = (abi.pack_tokens(resp.tokens, resp.t_forward_us, resp.t_total_us) if resp.tokens is not None
-                       and all(s.kind == "token" for s in resp.slots) else abi.pack_forward_response(resp))
+                       and resp.spec_accepted is None and all(s.kind == "token" for s in resp.slots)
+                       else abi.pack_forward_response(resp))
             elif kind == abi.KIND_DECODE_STEP:
                 step, parity = abi.unpack_decode_step(buf)
                 out = abi.pack_tokens(driver.decode_async(step, parity).wait())

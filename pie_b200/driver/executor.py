@@ -31,7 +31,7 @@ from ..models.transformer import ForwardInputs, ParallelContext, Transformer
 from ..models.weights import random_weights, torch_dtype
 from . import nvtx
 from .kv_cache import KVCache
-from .schema import (Capabilities, CopyRequest, ForwardRequest, ForwardResponse, SamplerKind,
+from .schema import (Capabilities, CopyRequest, ForwardRequest, ForwardResponse, SamplerKind, verify_drafts,
                      SamplerSpec, SlotOutput, position_seed)
 
 
@@ -503,6 +503,10 @@ class TorchDriver:
         self._fill_common(req, slots, kv_lens)
         custom = req.has_user_mask is not None and bool(np.any(req.has_user_mask))
         rows = np.asarray(req.slot_row, dtype=np.int32) if req.slot_row is not None else np.zeros(0, np.int32)
+        # compact logit rows: slots that read the same token row share one row of the vocabulary projection
+        rows, self._slot_logit_row = np.unique(rows, return_inverse=True)
+        rows = rows.astype(np.int32)
+        self.stats["logit_rows"] = self.stats.get("logit_rows", 0) + len(rows)
         if self.cuda:
             group = self.model.hq // self.model.hkv
             tile_rows = ops.prefill_tile_rows(self.model.hq, self.model.hkv, self.model.cfg.head_dim, self.page_size)
@@ -582,7 +586,11 @@ class TorchDriver:
         if probe_slots:
             self._probes(req, logits, slot_logit_row, probe_slots, out_slots)
         all_tokens = tokens if len(token_slots) == nslots else None
-        return ForwardResponse(slots=out_slots, tokens=all_tokens)
+        resp = ForwardResponse(slots=out_slots, tokens=all_tokens)
+        if req.spec_counts is not None and token_slots and np.any(req.spec_counts):
+            resp.spec_accepted = verify_drafts(req, {int(req.slot_row[i]): int(tokens[j])
+                                                     for j, i in enumerate(token_slots)})
+        return resp
 
     def _sample(self, lg, k: int, mask_bits, mask_row, out):
         """Token sampler over `k` logit rows: the single-GPU kernel, or under fused tensor
@@ -680,7 +688,7 @@ class TorchDriver:
         else:
             with nvtx.range("forward.general"):
                 logits = self._run_general(req, qlens, slots, kv_lens)
-            slot_logit_row = np.arange(nslots, dtype=np.int64)
+            slot_logit_row = np.asarray(self._slot_logit_row, dtype=np.int64)
         t2 = time.perf_counter()
         with nvtx.range("respond"):
             resp = self._respond(req, logits, slot_logit_row)

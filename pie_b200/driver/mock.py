@@ -139,7 +139,12 @@ class MockDriver:
             else:
                 slots.append(SlotOutput("embedding", logits=b""))
         all_tok = all(s.kind == "token" for s in slots)
-        return ForwardResponse(slots=slots, tokens=np.array([s.token for s in slots], np.int32) if all_tok else None)
+        resp = ForwardResponse(slots=slots, tokens=np.array([s.token for s in slots], np.int32) if all_tok else None)
+        if req.spec_counts is not None and np.any(req.spec_counts):
+            from .schema import verify_drafts
+            resp.spec_accepted = verify_drafts(req, {int(req.slot_row[i]): s.token for i, s in enumerate(slots)
+                                                     if s.kind == "token"})
+        return resp
 
     def decode_async(self, step, parity: int):
         """Array-form decode step (the cohort path) on top of the behaviour."""

@@ -113,6 +113,26 @@ class ForwardResponse:
     t_sample_us: float = 0.0
     t_d2h_us: float = 0.0
     t_total_us: float = 0.0
+    # drafts accepted per request (int32 [R]) when the request carried `spec_counts`: the driver verifies
+    # each draft against the token it sampled at the previous row
+    spec_accepted: Optional[np.ndarray] = None
+
+
+def verify_drafts(req: "ForwardRequest", slot_tokens: dict) -> np.ndarray:
+    """Accepted draft count per request. The last `spec_counts[r]` input tokens of request r are drafts;
+    draft j stands while the token sampled at the row before it (`slot_tokens`: row -> sampled token)
+    equals it. Counterpart of the driver-side speculation expansion of the reference
+    (driver/cuda/src/executor/spec_expand.cpp)."""
+    qo = np.asarray(req.qo_indptr)
+    out = np.zeros(len(qo) - 1, np.int32)
+    for r, k in enumerate(np.asarray(req.spec_counts)):
+        end = int(qo[r + 1])
+        for j in range(int(k)):
+            row = end - int(k) + j
+            if slot_tokens.get(row - 1) != int(req.tokens[row]):
+                break
+            out[r] += 1
+    return out
 
 
 class CopyDir(enum.IntEnum):

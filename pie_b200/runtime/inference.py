@@ -268,6 +268,7 @@ class InferenceService:
             fut.set(exc=result)
             return
         out = ForwardOutput(slots=list(result))
+        out.driver_accepted = getattr(result, "spec_accepted", None)
         if staged is not None:
             park = False
             with self.lock:
@@ -311,6 +312,11 @@ class InferenceService:
         at the previous row equals the draft; the response tokens become accepted drafts + bonus."""
         if n_spec == 0:
             return len(tokens)
+        verdict = getattr(out, "driver_accepted", None)
+        if verdict is not None:                 # the driver compared drafts and samples itself
+            out.accepted_drafts = min(int(verdict), n_spec)
+            self.stats["driver_verified"] = self.stats.get("driver_verified", 0) + 1
+            return n_plain + out.accepted_drafts
         # samplers attached at rows n_plain-1 .. n_plain-1+n_spec verify the drafts in order
         by_row = {idx: k for k, (idx, sp) in enumerate(samplers) if sp.is_token}
         accepted = 0

@@ -25,6 +25,11 @@ from . import brle, telemetry
 from ..driver.schema import Capabilities, ForwardRequest, ForwardResponse, SamplerSpec, SlotOutput
 
 
+class SlotList(list):
+    """The slot outputs of one request, with the driver's verdict on its drafts when it gave one."""
+    spec_accepted: Optional[int] = None
+
+
 @dataclass
 class PendingRequest:
     context_id: int
@@ -61,10 +66,26 @@ class Usage:
     sampler_rows: int = 0
     mask_bytes: int = 0
     logprob_labels: int = 0
+    logit_rows: int = 0        # distinct token rows that need the vocabulary projection
+    prob_rows: int = 0         # distinct token rows that need a normalised distribution
+
+
+_PROB_KINDS = None
+
+
+def _needs_probs(spec) -> bool:
+    global _PROB_KINDS
+    if _PROB_KINDS is None:
+        from ..driver.schema import SamplerKind
+        _PROB_KINDS = {SamplerKind.DIST, SamplerKind.LOGPROB, SamplerKind.LOGPROBS, SamplerKind.ENTROPY}
+    return spec.kind in _PROB_KINDS
 
 
 class BatchAccumulator:
-    """Admits requests while every driver limit holds."""
+    """Admits requests while every one of the driver's eight limits holds: requests, tokens, page
+    references, logit rows, probability rows, sampler rows, log-probability labels, custom-mask bytes
+    (runtime/src/inference/scheduler.rs:311-655). Logit and probability rows are counted after the
+    compact projection: samplers that read the same token row share one row."""
 
     def __init__(self, caps: Capabilities, page_size: int):
         self.caps, self.page_size = caps, page_size
@@ -78,14 +99,18 @@ class BatchAccumulator:
         if r.masks is not None:
             mask_bytes = r.n_tokens * (-(-total // 8))
         labels = sum(len(s.labels) for _, s in r.samplers)
-        return Usage(1, r.n_tokens, pages, len(r.samplers), mask_bytes, labels)
+        logit_rows = len({i for i, _ in r.samplers})
+        prob_rows = len({i for i, s in r.samplers if _needs_probs(s)})
+        return Usage(1, r.n_tokens, pages, len(r.samplers), mask_bytes, labels, logit_rows, prob_rows)
 
     def fits(self, r: PendingRequest) -> bool:
         c, u, caps = self.cost(r), self.usage, self.caps
         return (u.requests + c.requests <= caps.max_forward_requests
                 and u.tokens + c.tokens <= caps.max_forward_tokens
                 and u.page_refs + c.page_refs <= caps.max_page_refs
-                and u.sampler_rows + c.sampler_rows <= min(caps.max_sampler_rows, caps.max_logit_rows)
+                and u.sampler_rows + c.sampler_rows <= caps.max_sampler_rows
+                and u.logit_rows + c.logit_rows <= caps.max_logit_rows
+                and u.prob_rows + c.prob_rows <= caps.max_prob_rows
                 and u.mask_bytes + c.mask_bytes <= caps.max_custom_mask_bytes
                 and u.logprob_labels + c.logprob_labels <= caps.max_logprob_labels)
 
@@ -93,6 +118,7 @@ class BatchAccumulator:
         c, u = self.cost(r), self.usage
         u.requests += c.requests; u.tokens += c.tokens; u.page_refs += c.page_refs
         u.sampler_rows += c.sampler_rows; u.mask_bytes += c.mask_bytes; u.logprob_labels += c.logprob_labels
+        u.logit_rows += c.logit_rows; u.prob_rows += c.prob_rows
         self.items.append(r)
 
     def take(self) -> List[PendingRequest]:
@@ -464,9 +490,12 @@ class BatchScheduler:
                 self._deliver(it, err)
             return
         k = 0
-        for it in items:
+        for ri, it in enumerate(items):
             n = len(it.samplers)
-            self._deliver(it, resp.slots[k:k + n])
+            out = SlotList(resp.slots[k:k + n])
+            if resp.spec_accepted is not None:
+                out.spec_accepted = int(resp.spec_accepted[ri])
+            self._deliver(it, out)
             k += n
         t_disp = time.perf_counter()
         for hook in self.post_fire_hooks:

@@ -126,3 +126,26 @@ def test_seeded_sampling_same_stream_on_both_scheduler_paths():
         assert len(set(a)) > 1             # the noise differs from step to step
     finally:
         eng.shutdown()
+
+
+def test_samplers_on_one_row_share_one_logit_row():
+    """Compact logit rows: several probes of the same token row cost one row of the vocabulary projection."""
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import ForwardRequest, SamplerKind, SamplerSpec
+    from pie_b200.models.config import preset
+    drv = TorchDriver(preset("tiny-llama", num_hidden_layers=1), device="cpu", num_pages=8)
+    i32 = lambda *a: np.asarray(a, dtype=np.int32)
+
+    def fire(rows, samplers):
+        return drv.fire_batch(ForwardRequest(
+            tokens=i32(1, 2, 3, 4), positions=i32(0, 1, 2, 3), qo_indptr=i32(0, 4), kv_page_indices=i32(0),
+            kv_page_indptr=i32(0, 1), kv_last_page_lens=i32(4), slot_req=i32(*([0] * len(rows))), slot_row=i32(*rows),
+            slot_samplers=samplers))
+    before = drv.stats.get("logit_rows", 0)
+    r = fire([3, 1, 3, 3], [SamplerSpec.greedy(), SamplerSpec.greedy(), SamplerSpec(SamplerKind.DIST, top_k=3),
+                            SamplerSpec(SamplerKind.ENTROPY)])
+    assert drv.stats["logit_rows"] - before == 2                    # rows {1, 3}
+    a = fire([3], [SamplerSpec.greedy()]).slots[0].token
+    b = fire([1], [SamplerSpec.greedy()]).slots[0].token
+    assert [r.slots[0].token, r.slots[1].token] == [a, b]
+    assert r.slots[2].ids[0] == a and r.slots[3].kind == "entropy"

@@ -92,6 +92,7 @@ def test_speculation_inferlets_match_plain_greedy(eng):
     ref = json.loads(run(eng, "text-completion", {"prompt_tokens": PROMPT, "max_tokens": 20, "stop_tokens": []}))["tokens"]
     spec = json.loads(run(eng, "text-completion-spec", {"prompt_tokens": PROMPT, "max_tokens": 20, "stop_tokens": []}))
     assert spec["tokens"] == ref
+    assert eng.models["tiny-llama"].inference.stats.get("driver_verified", 0) > 0      # drafts checked by the driver
     custom = json.loads(run(eng, "demo-custom-spec", {"prompt_tokens": PROMPT, "max_tokens": 20}))
     assert custom["tokens"] == ref and custom["passes"] <= 20
 

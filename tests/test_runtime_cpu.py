@@ -188,6 +188,34 @@ def test_accumulator_enforces_driver_limits():
     assert not acc.fits(req(6, 1, kv=0, samplers=False))  # page refs 5 + 1 > 5
 
 
+def test_accumulator_counts_logit_and_prob_rows_after_the_compact_projection():
+    """Eight limits: logit rows and probability rows are distinct token rows, not sampler slots, and the
+    label and mask-byte budgets hold too (scheduler.rs:728-980)."""
+    from pie_b200.driver.schema import SamplerKind
+    caps = Capabilities(total_pages=100, kv_page_size=16, max_forward_requests=10, max_forward_tokens=100,
+                        max_sampler_rows=8, max_logit_rows=3, max_prob_rows=1, max_logprob_labels=4,
+                        max_custom_mask_bytes=64)
+    acc = BatchAccumulator(caps, 16)
+    probes = PendingRequest(1, [1, 2, 3, 4], [0, 1, 2, 3], [0], 0,
+                            [(3, SamplerSpec.greedy()), (3, SamplerSpec(SamplerKind.DIST, top_k=5)),
+                             (3, SamplerSpec(SamplerKind.ENTROPY)), (3, SamplerSpec(SamplerKind.LOGPROBS, labels=(1, 2)))])
+    c = acc.cost(probes)
+    assert (c.sampler_rows, c.logit_rows, c.prob_rows, c.logprob_labels) == (4, 1, 1, 2)
+    acc.push(probes)
+    assert acc.fits(req(2, 4))                                            # a second logit row, no probabilities
+    acc.push(req(2, 4))
+    other_row = PendingRequest(3, [1, 2], [0, 1], [0], 0, [(0, SamplerSpec(SamplerKind.ENTROPY))])
+    assert not acc.fits(other_row)                                        # a second probability row
+    assert acc.fits(req(4, 1))
+    acc.push(req(4, 1))
+    assert not acc.fits(req(5, 1))                                        # a fourth logit row
+    acc.take()
+    many = PendingRequest(6, [1], [0], [0], 0, [(0, SamplerSpec(SamplerKind.LOGPROBS, labels=(1, 2, 3, 4, 5)))])
+    assert not acc.fits(many)                                             # labels 5 > 4
+    masked = PendingRequest(7, [1] * 8, list(range(8)), [0, 1, 2, 3, 4], 64, masks=[[0, 72]] * 8)
+    assert acc.cost(masked).mask_bytes == 8 * 9 and not acc.fits(masked)  # 72 bytes of custom mask > 64
+
+
 def test_fold_builds_csr_and_rejects_short_page_lists():
     items = [req(1, 5, kv=20), req(2, 1, kv=15)]
     f = fold(items, 16)
