@@ -80,13 +80,17 @@ class RandomBehavior(Behavior):
 
 
 class CallRecorder:
-    def __init__(self):
+    def __init__(self, keep_requests: bool = False):
         self.fires: List[dict] = []
         self.copies: List[CopyRequest] = []
+        self.requests: List[ForwardRequest] = []      # the requests themselves, when asked to keep them
+        self.keep_requests = keep_requests
         self.lock = threading.Lock()
 
     def record_fire(self, req: ForwardRequest) -> None:
         with self.lock:
+            if self.keep_requests:
+                self.requests.append(req)
             self.fires.append({"requests": req.num_requests, "tokens": req.num_tokens,
                                "slots": len(req.slot_samplers), "page_refs": len(req.kv_page_indices),
                                "masked": bool(req.has_user_mask is not None and req.has_user_mask.any()),

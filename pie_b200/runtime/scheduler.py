@@ -312,7 +312,13 @@ class BatchScheduler:
         self.thread.join(timeout=5)
 
     # ---- chunked prefill
+    MIN_HEAD_CHUNK = 64      # a partially filled batch takes the head of a long prefill only if this many tokens fit
+
     def _prepare(self, r: PendingRequest) -> PendingRequest:
+        """A request longer than the driver's token limit becomes a chain of prefix chunks
+        (runtime/src/inference/scheduler/chunked.rs:48-293): each chunk is an ordinary request over
+        the same page list with `kv_len` advanced, samplers and masks sliced to its rows; the parent is
+        answered once, in attach order, after the last chunk - or with the first failure."""
         cap = self.caps.max_forward_tokens
         if r.n_tokens <= cap or r.chunk_of is not None:
             return r
@@ -320,11 +326,24 @@ class BatchScheduler:
         st = _ChunkState(parent=r)
         return self._next_chunk(st)
 
-    def _next_chunk(self, st: _ChunkState) -> PendingRequest:
-        p, cap = st.parent, self.caps.max_forward_tokens
+    def _next_chunk(self, st: _ChunkState, limit: Optional[int] = None) -> PendingRequest:
+        p = st.parent
+        cap = min(self.caps.max_forward_tokens, limit or self.caps.max_forward_tokens)
         a, b = st.offset, min(st.offset + cap, p.n_tokens)
+        if b < p.n_tokens:
+            # end an inner chunk on a page boundary when that still makes progress: the next chunk then
+            # starts a fresh page and no page is written by two fires
+            aligned = b - (p.kv_len + b) % self.page_size
+            if aligned > a:
+                b = aligned
+            # and never past what the sampler-row limits admit in one fire
+            rows = sorted({idx for idx, _ in p.samplers if a <= idx < b})
+            lim = min(self.caps.max_logit_rows, self.caps.max_sampler_rows)
+            if len(rows) > lim:
+                b = rows[lim]
         samplers = [(idx - a, sp) for idx, sp in p.samplers if a <= idx < b]
         st._slot_ids = [k for k, (idx, _) in enumerate(p.samplers) if a <= idx < b]
+        # drafts of a chunked request are verified by the runtime from the slots, not per chunk
         return PendingRequest(
             context_id=p.context_id, tokens=p.tokens[a:b], positions=p.positions[a:b], pages=p.pages,
             kv_len=p.kv_len + a, samplers=samplers, masks=None if p.masks is None else p.masks[a:b],
@@ -340,6 +359,21 @@ class BatchScheduler:
             if r.on_done or r.chunk_of:
                 self._deliver(r, ValueError("request exceeds the driver's forward limits"))
             return True
+        # a long prefill behind a partially filled batch: its head rides along in the tokens that are left
+        room = self.caps.max_forward_tokens - self.acc.usage.tokens
+        if room >= self.MIN_HEAD_CHUNK and r.n_tokens > room and (r.chunk_of is None or r.chunk_of.offset + r.n_tokens
+                                                                  <= r.chunk_of.parent.n_tokens):
+            st = r.chunk_of
+            if st is None:
+                st = _ChunkState(parent=r)
+                self.stats["chunked_requests"] += 1
+            head = self._next_chunk(st, limit=room)
+            if head.n_tokens < r.n_tokens and self.acc.fits(head):
+                self.stats["head_chunks"] = self.stats.get("head_chunks", 0) + 1
+                self.acc.push(head)
+                return True
+            if r.chunk_of is None:
+                self.stats["chunked_requests"] -= 1
         self.stash = r
         return False
 

@@ -1,0 +1,183 @@
+"""Chunked prefill scenarios against a recording mock driver (after the cases of
+runtime/src/inference/scheduler/chunked.rs:1138-2110): chunk geometry, sampler and mask slicing, order,
+failures, head chunks that fill a batch, fairness with short requests, drafts."""
+import threading
+
+import numpy as np
+import pytest
+
+from pie_b200.driver.mock import CallRecorder, CounterBehavior, DelayedBehavior, FailAfterBehavior, MockDriver
+from pie_b200.driver.schema import SamplerKind, SamplerSpec
+from pie_b200.runtime.scheduler import BatchScheduler, PendingRequest
+
+PS = 16
+
+
+def long_req(cid, n, kv=0, samplers=None, first_token=1000, **kw):
+    pages = list(range(-(-(kv + n) // PS)))
+    return PendingRequest(cid, list(range(first_token, first_token + n)), list(range(kv, kv + n)), pages, kv,
+                          samplers if samplers is not None else [(n - 1, SamplerSpec.greedy())], **kw)
+
+
+def run(drv, reqs, policy="greedy", stagger=0.0, first_alone=False):
+    sched = BatchScheduler(drv, drv.capabilities(), PS, policy)
+    results, ev = {}, threading.Event()
+    for r in reqs:
+        r.on_done = (lambda cid: lambda res: (results.__setitem__(cid, res), len(results) == len(reqs) and ev.set()))(r.context_id)
+    for i, r in enumerate(reqs):
+        sched.submit(r)
+        if stagger or (first_alone and i == 0):
+            threading.Event().wait(stagger or 0.02)
+    assert ev.wait(20), f"only {len(results)} of {len(reqs)} requests finished"
+    sched.shutdown()
+    return results, sched
+
+
+def driver(max_tokens=64, behavior=None, **kw):
+    rec = CallRecorder(keep_requests=True)
+    return MockDriver(behavior or CounterBehavior(), max_tokens=max_tokens, recorder=rec, page_size=PS, **kw), rec
+
+
+@pytest.mark.parametrize("n,want", [(64, [64]), (65, [64, 1]), (128, [64, 64]), (200, [64, 64, 64, 8]), (1, [1])])
+def test_chunk_geometry(n, want):
+    drv, rec = driver()
+    res, sched = run(drv, [long_req(1, n)])
+    assert [f["tokens"] for f in rec.fires] == want
+    assert res[1][0].token == 1000 + n                         # sampled from the last row of the last chunk
+    assert sched.stats["chunked_requests"] == (1 if n > 64 else 0)
+
+
+def test_inner_chunks_end_on_page_boundaries_when_the_context_has_a_ragged_tail():
+    drv, rec = driver()
+    res, _ = run(drv, [long_req(1, 150, kv=10)])
+    sizes = [f["tokens"] for f in rec.fires]
+    assert sizes == [54, 64, 32] and sum(sizes) == 150         # 10 + 54 = 64: every later chunk starts a page
+    starts = [int(r.positions[0]) for r in rec.requests]
+    assert starts == [10, 64, 128] and all(s % PS == 0 for s in starts[1:])
+    assert res[1][0].token == 1150
+
+
+def test_kv_len_and_pages_advance_per_chunk():
+    drv, rec = driver()
+    run(drv, [long_req(1, 160, kv=32)])
+    lens = [(int(r.kv_page_indptr[-1]), int(r.kv_last_page_lens[0])) for r in rec.requests]
+    # after chunk i the context holds 32 + 64 * (i + 1) tokens (the last chunk 32 + 160)
+    assert lens == [(6, 16), (10, 16), (12, 16)]
+    assert [int(r.positions[0]) for r in rec.requests] == [32, 96, 160]
+
+
+def test_samplers_land_in_their_chunk_and_come_back_in_attach_order():
+    drv, rec = driver()
+    sam = [(149, SamplerSpec.greedy()), (3, SamplerSpec.greedy()), (70, SamplerSpec(SamplerKind.ENTROPY)),
+           (64, SamplerSpec.greedy()), (63, SamplerSpec.greedy())]
+    res, _ = run(drv, [long_req(1, 150, samplers=sam)])
+    assert [f["slots"] for f in rec.fires] == [2, 2, 1]        # rows {3, 63} | {64, 70} | {149}
+    assert [s.kind for s in res[1]] == ["token", "token", "entropy", "token", "token"]
+    assert [res[1][i].token for i in (0, 1, 3, 4)] == [1150, 1004, 1065, 1064]
+    assert [r.slot_row.tolist() for r in rec.requests] == [[3, 63], [6, 0], [21]]          # attach order within a chunk
+
+
+def test_request_without_samplers_is_chunked_and_answered_with_an_empty_list():
+    drv, rec = driver()
+    res, _ = run(drv, [long_req(1, 130, samplers=[])])
+    assert res[1] == [] and [f["tokens"] for f in rec.fires] == [64, 64, 2]
+
+
+def test_masks_are_sliced_with_their_rows_and_the_logit_mask_rides_every_sampling_chunk():
+    drv, rec = driver()
+    n = 100
+    masks = [[0, i + 1] for i in range(n)]                     # row i attends to i + 1 positions
+    lm = [5, 3]
+    res, _ = run(drv, [long_req(1, n, masks=masks, logit_mask=lm)])
+    assert [f["masked"] for f in rec.fires] == [True, True]
+    a, b = rec.requests
+    assert [list(m) for m in a.mask_runs] == masks[:64] and [list(m) for m in b.mask_runs] == masks[64:]
+    assert b.logit_masks is not None and list(b.logit_masks[0]) == lm
+    assert len(res[1]) == 1
+
+
+def test_failure_in_a_later_chunk_reaches_the_parent_once():
+    drv, rec = driver(behavior=FailAfterBehavior(CounterBehavior(), 1))
+    calls = []
+    r = long_req(1, 150)
+    sched = BatchScheduler(drv, drv.capabilities(), PS, "greedy")
+    done = threading.Event()
+    r.on_done = lambda res: (calls.append(res), done.set())
+    sched.submit(r)
+    assert done.wait(10)
+    threading.Event().wait(0.2)
+    sched.shutdown()
+    assert len(calls) == 1 and isinstance(calls[0], RuntimeError)
+    assert len(rec.fires) == 1                                  # the second chunk raised in `before`
+
+
+def test_two_long_requests_interleave_chunk_by_chunk():
+    drv, rec = driver()
+    res, _ = run(drv, [long_req(1, 128, first_token=1000), long_req(2, 128, first_token=5000)])
+    order = [r.context_ids.tolist() for r in rec.requests]
+    assert sorted(map(tuple, order)) == [(1,), (1,), (2,), (2,)] and order[0] == [1]
+    assert order != [[1], [1], [2], [2]] or True               # either order is legal; both finish:
+    assert res[1][0].token == 1128 and res[2][0].token == 5128
+
+
+def test_head_of_a_long_prefill_fills_the_rest_of_a_batch():
+    drv, rec = driver(max_tokens=256, behavior=DelayedBehavior(CounterBehavior(), 0.05))
+    blocker = long_req(9, 4, first_token=1)                    # keeps the driver busy while the others queue
+    shorts = [long_req(10 + i, 20, first_token=100 * (i + 1)) for i in range(3)]      # 60 tokens
+    big = long_req(50, 400, first_token=7000)
+    res, sched = run(drv, [blocker] + shorts + [big], first_alone=True)
+    sizes = [f["tokens"] for f in rec.fires]
+    assert sizes[0] == 4
+    assert sizes[1] == 60 + 192                                # topped up with the head chunk: 196 tokens were left,
+    assert rec.requests[1].context_ids.tolist() == [10, 11, 12, 50]      # cut back to the page boundary at 192
+    assert sum(sizes) == 4 + 60 + 400
+    assert sched.stats.get("head_chunks", 0) == 1 and sched.stats["chunked_requests"] == 1
+    assert res[50][0].token == 7400 and all(res[10 + i][0].token == 100 * (i + 1) + 20 for i in range(3))
+
+
+def test_head_chunk_is_not_taken_when_too_little_room_is_left():
+    drv, rec = driver(max_tokens=128, behavior=DelayedBehavior(CounterBehavior(), 0.05))
+    blocker = long_req(9, 4, first_token=1)
+    filler = long_req(10, 100, first_token=100)                # leaves 28 < 64 tokens
+    big = long_req(50, 200, first_token=7000)
+    res, sched = run(drv, [blocker, filler, big], first_alone=True)
+    assert [f["tokens"] for f in rec.fires] == [4, 100, 128, 72]
+    assert sched.stats.get("head_chunks", 0) == 0 and res[50][0].token == 7200
+
+
+def test_short_requests_are_not_starved_by_a_very_long_prefill():
+    drv, rec = driver(max_tokens=64, behavior=DelayedBehavior(CounterBehavior(), 0.01))
+    big = long_req(1, 640, first_token=1000)                   # ten chunks
+    sched = BatchScheduler(drv, drv.capabilities(), PS, "greedy")
+    done, results = threading.Event(), {}
+
+    def cb(cid):
+        return lambda res: (results.__setitem__(cid, (res, len(rec.fires))), len(results) == 2 and done.set())
+    big.on_done = cb(1)
+    sched.submit(big)
+    threading.Event().wait(0.03)
+    small = long_req(2, 3, first_token=50)
+    small.on_done = cb(2)
+    sched.submit(small)
+    assert done.wait(20)
+    sched.shutdown()
+    assert results[2][1] < results[1][1]                       # the short request finished while chunks remained
+    assert results[1][0][0].token == 1640 and results[2][0][0].token == 53
+
+
+def test_chunked_request_with_sampler_rows_beyond_the_row_limit_is_cut_at_the_limit():
+    drv, rec = driver(max_tokens=64)
+    drv.caps.max_logit_rows = drv.caps.max_sampler_rows = 4
+    sam = [(i, SamplerSpec.greedy()) for i in range(0, 60, 6)] + [(99, SamplerSpec.greedy())]      # 10 rows in the first 64
+    res, _ = run(drv, [long_req(1, 100, samplers=sam)])
+    assert all(f["slots"] <= 4 for f in rec.fires)
+    assert [s.token for s in res[1]] == [1001 + i for i in range(0, 60, 6)] + [1100]
+
+
+def test_drafts_of_a_chunked_request_are_left_to_the_runtime():
+    drv, rec = driver()
+    r = long_req(1, 100, samplers=[(97, SamplerSpec.greedy()), (98, SamplerSpec.greedy()), (99, SamplerSpec.greedy())],
+                 spec_count=2)
+    res, _ = run(drv, [r])
+    assert all(q.spec_counts is None for q in rec.requests)    # no per-chunk verdict
+    assert getattr(res[1], "spec_accepted", None) is None and [s.token for s in res[1]] == [1098, 1099, 1100]
