@@ -12,8 +12,9 @@ from typing import Optional
 
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 # `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "mixtral", "olmo2", "gpt_oss")
-POST_NORM = {"olmo2"}       # same block with the norms after attention / MLP and q, k norms over all heads
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3",
+                         "gpt_oss")
+POST_NORM = {"olmo2", "olmo3"}       # same block with the norms after attention / MLP and q, k norms over all heads
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
 
 
@@ -103,13 +104,14 @@ class ModelConfig:
             rope_theta=cfg.get("rope_theta", 10000.0),
             rope_scaling=cfg.get("rope_scaling"),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2") or cfg.get("use_qk_norm", False),
+            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2", "olmo3") or cfg.get("use_qk_norm", False),
             post_norm=mt in POST_NORM,
             attention_bias=cfg.get("attention_bias", mt in ("qwen2", "gpt_oss")),
             # Qwen2 gates the window on use_sliding_window; Mistral applies it whenever it is set
             sliding_window=(cfg.get("sliding_window") or -1)
-            if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss")) else -1,
-            layer_types=cfg.get("layer_types") if mt == "gpt_oss" else None,
+            if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss", "olmo3")) else -1,
+            # OLMo-3 and GPT-OSS alternate sliding-window and full-attention layers
+            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") else None,
             attention_sinks=mt == "gpt_oss",
             o_bias=mt == "gpt_oss" and cfg.get("attention_bias", True),
             moe_style="gpt_oss" if mt == "gpt_oss" else "swiglu",

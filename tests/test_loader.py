@@ -476,3 +476,41 @@ def test_weight_artifact_cache_round_trip_and_keying(tmp_path, monkeypatch):
     _, c = loader.load_checkpoint(str(src), dtype="float32")
     assert len(calls) == 3 and _same(full, c)
     assert not list(cache.glob("*.tmp*"))
+
+
+def test_olmo3_alternating_window_layers_load_and_match_dense_oracle(tmp_path):
+    """OLMo-3 = the OLMo-2 block with sliding-window layers alternating with full-attention ones
+    (`layer_types`). Context longer than the window, so the two kinds of layer differ."""
+    import json
+    import numpy as np
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models import loader
+    from pie_b200.models.config import ModelConfig, preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import random_weights
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+
+    cfg = preset("tiny-olmo2", model_type="olmo3", sliding_window=8, layer_types=["sliding_attention", "full_attention"])
+    w = random_weights(cfg, "cpu", torch.float32, seed=6)
+    loader.export_hf_checkpoint(cfg, w, tmp_path)
+    hf = json.loads((tmp_path / "config.json").read_text())
+    hf.update(model_type="olmo3", sliding_window=8, layer_types=["sliding_attention", "full_attention"])
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    cfg2, w2 = loader.load_checkpoint(tmp_path, "cpu", dtype="float32")
+    assert cfg2.model_type == "olmo3" and cfg2.post_norm and cfg2.qk_norm
+    assert [cfg2.layer_window_left(i) for i in range(2)] == [7, -1] and cfg2.plan_window_left == -1
+    drv = TorchDriver(cfg2, "cpu", weights=w2, num_pages=16, page_size=16, max_requests=4, max_tokens=128)
+    toks = list(range(100, 140))
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    resp = drv.fire_batch(fold([PendingRequest(0, toks, list(range(len(toks))), list(range(4)), 0, [(len(toks) - 1, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg2, w2, torch.tensor(toks))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3
+    full = dense_reference_forward(ModelConfig(**{**cfg2.to_dict(), "sliding_window": -1, "layer_types": None}), w2,
+                                   torch.tensor(toks))[-1].numpy()
+    assert np.abs(full - want).max() > 1e-3                     # the window really changes the result
+    resp = drv.fire_batch(fold([PendingRequest(0, [7], [len(toks)], list(range(4)), len(toks), [(0, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg2, w2, torch.tensor(toks + [7]))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3
