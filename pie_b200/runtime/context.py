@@ -279,17 +279,18 @@ class ContextManager:
             self.by_owner.pop(owner, None)
 
     # ------------------------------------------------------------------ queries
+    # The three counters are read without the lock: each is one dictionary look-up and one list length,
+    # which the interpreter reads atomically, and the only writer that moves pages between the two lists
+    # (commit) runs on the context owner's own thread. An inferlet asks for them on every step; under
+    # the lock each call could wait for a whole batch delivery on the scheduler thread.
     def committed_page_count(self, cid: int) -> int:
-        with self.lock:
-            return len(self._get(cid).chain)
+        return len(self._get(cid).chain)
 
     def working_page_count(self, cid: int) -> int:
-        with self.lock:
-            return len(self._get(cid).working_pages)
+        return len(self._get(cid).working_pages)
 
     def working_page_token_count(self, cid: int) -> int:
-        with self.lock:
-            return self._get(cid).working_token_count
+        return len(self._get(cid).tokens)
 
     def kv_len(self, cid: int) -> int:
         with self.lock:

@@ -116,6 +116,7 @@ class Engine:
             sched = BatchScheduler(drv, caps, entry.page_size, self.config.batch_policy,
                                    name=f"pie-sched-{name}-{i}")
             sched.expected_cohort = entry.ctxm.pinned_count
+            sched.delivery_guard = entry.ctxm.lock
             sched.cohort = DecodeCohort(entry.ctxm, entry.page_size, caps.max_forward_requests)
             entry.schedulers.append(sched)
         entry.inference = InferenceService(entry.ctxm, entry.schedulers, self.config.speculation_depth)
@@ -133,13 +134,14 @@ class Engine:
 
     def _market_tick(self, entry: ModelEntry, driver: int, ctx_ids) -> None:
         batch = []
-        for cid in ctx_ids:
-            ctx = entry.ctxm.contexts.get(int(cid))
-            if ctx is not None:
-                try:
-                    batch.append((ctx.id, ctx.owner, ctx.bid, entry.ctxm.effective_pages(ctx.id)))
-                except Exception:  # noqa: BLE001
-                    pass
+        with entry.ctxm.lock:              # once for the batch, not once per context
+            for cid in ctx_ids:
+                ctx = entry.ctxm.contexts.get(int(cid))
+                if ctx is not None:
+                    try:
+                        batch.append((ctx.id, ctx.owner, ctx.bid, entry.ctxm.effective_pages(ctx.id)))
+                    except Exception:  # noqa: BLE001
+                        pass
         entry.market.tick(entry.ctxm.pages_used(driver), batch)
 
     def _charge(self, entry: ModelEntry, cid: int, n: int) -> None:

@@ -270,16 +270,21 @@ class InferenceService:
         out = ForwardOutput(slots=list(result))
         out.driver_accepted = getattr(result, "spec_accepted", None)
         if staged is not None:
-            park = False
+            # Lock order: the context manager's lock may be held when this lock is taken (the scheduler
+            # scatters a whole fire under it), never the other way round - so no call into the context
+            # manager from inside `with self.lock`.
+            park = abandoned = False
             with self.lock:
                 if staged.abandoned:
-                    self.ctxm.unpin(cid)
-                    fut.set(out)
-                    return
-                if not staged.claimed:
+                    abandoned = True
+                elif not staged.claimed:
                     # finished before anybody asked for it: park the result, keep the pin
                     staged._parked = (tokens, positions, samplers, out)
                     park = True
+            if abandoned:
+                self.ctxm.unpin(cid)
+                fut.set(out)
+                return
             if park:
                 fut.set(out)
                 return
@@ -300,12 +305,13 @@ class InferenceService:
             return
         tokens, positions, samplers, out = parked
         st._parked = None
-        self._append_and_unpin(cid, tokens, positions, None)
-        with self.lock:
-            if self.staged.get(cid) is st:
-                del self.staged[cid]
-        if self.depth > 0:
-            self._maybe_stage(cid, tokens, positions, samplers, None, None, 0, out)
+        with self.ctxm.lock:          # one hold for the append, the unpin and the next stage's pin
+            self._append_and_unpin(cid, tokens, positions, None)
+            with self.lock:
+                if self.staged.get(cid) is st:
+                    del self.staged[cid]
+            if self.depth > 0:
+                self._maybe_stage(cid, tokens, positions, samplers, None, None, 0, out)
 
     def _accept(self, tokens, positions, samplers, n_spec, n_plain, out: ForwardOutput) -> int:
         """Number of input tokens whose KV is kept. Draft tokens are kept while the token sampled
@@ -357,10 +363,12 @@ class InferenceService:
         fut = Future()
         st = _Staged(nxt_tok, nxt_pos, sp, fut)
         with self.lock:
-            if cid in self.staged:
-                self.ctxm.unpin(cid)
-                return
-            self.staged[cid] = st
+            taken = cid in self.staged
+            if not taken:
+                self.staged[cid] = st
+        if taken:
+            self.ctxm.unpin(cid)
+            return
         self.stats["chain_submits"] += 1
         sched = self.schedulers[pinned.driver]
         self._queue(sched, cid, pinned, [nxt_tok], [nxt_pos], [(0, sp)], None, None, 0, -1, True, fut, st, 1)

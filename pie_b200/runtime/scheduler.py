@@ -13,6 +13,7 @@ inference/adaptive_policy.rs:30-274 (policies), inference/scheduler/chunked.rs:4
 """
 from __future__ import annotations
 
+import contextlib
 import queue
 import threading
 import time
@@ -275,6 +276,10 @@ class BatchScheduler:
         self._last_dispatch_end = 0.0
         self.on_batch = on_batch
         self.post_fire_hooks: List[Callable] = []
+        # Held (re-entrantly) while the results of one fire are scattered to their requests: every
+        # delivery takes the context manager's lock a few times, and taking it once around the whole
+        # loop keeps the inferlet thread from interleaving with each of several hundred deliveries.
+        self.delivery_guard = contextlib.nullcontext()
         self.running = True
         self.aborted: Optional[Exception] = None
         self.inflight_contexts = 0
@@ -524,16 +529,17 @@ class BatchScheduler:
                 self._deliver(it, err)
             return
         k = 0
-        for ri, it in enumerate(items):
-            n = len(it.samplers)
-            out = SlotList(resp.slots[k:k + n])
-            if resp.spec_accepted is not None:
-                out.spec_accepted = int(resp.spec_accepted[ri])
-            self._deliver(it, out)
-            k += n
-        t_disp = time.perf_counter()
-        for hook in self.post_fire_hooks:
-            hook([it.context_id for it in items])
+        with self.delivery_guard:
+            for ri, it in enumerate(items):
+                n = len(it.samplers)
+                out = SlotList(resp.slots[k:k + n])
+                if resp.spec_accepted is not None:
+                    out.spec_accepted = int(resp.spec_accepted[ri])
+                self._deliver(it, out)
+                k += n
+            t_disp = time.perf_counter()
+            for hook in self.post_fire_hooks:
+                hook([it.context_id for it in items])
         if self.on_batch:
             self.on_batch(len(items), req.num_tokens, lat, "batch")
         if tel.enabled:

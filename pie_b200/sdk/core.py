@@ -399,16 +399,21 @@ class Context:
                     pass
 
     def _after_pass(self, accepted: int, positions: Sequence[int]) -> None:
+        before = self._seq_len
         self._seq_len += accepted
         if accepted:
             self._next_pos = max(self._next_pos, positions[accepted - 1] + 1)
+        ps = self.page_size
+        if before // ps == self._seq_len // ps and not getattr(self, "_commit_retry", False):
+            return  # committed pages are full ones: a working page fills only when a page boundary is crossed
         ctxm = self._entry.ctxm
-        full = ctxm.working_page_token_count(self.id) // self.page_size
+        full = ctxm.working_page_token_count(self.id) // ps
         if full:
             try:
                 ctxm.commit_working_pages(self.id, full)
+                self._commit_retry = False
             except Exception:
-                pass  # non-monotonic positions (custom layouts) stay in working pages
+                self._commit_retry = True  # non-monotonic positions (custom layouts) stay in working pages
 
     async def flush(self) -> None:
         """Run the pending tokens through the model without sampling."""

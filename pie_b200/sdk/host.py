@@ -23,17 +23,54 @@ def engine():
     return proc().engine
 
 
+class _Mailbox:
+    """Completions from runtime threads to one event loop, delivered in batches: a completion is pushed
+    on a deque and the loop is woken (one write to its self-pipe) only when no drain is pending, so a
+    batch of several hundred futures finished by one fire costs one wake-up instead of one each."""
+
+    def __init__(self, loop):
+        import collections
+        import threading
+        self.loop = loop
+        self.items = collections.deque()
+        self.lock = threading.Lock()
+        self.scheduled = False
+
+    def post(self, afut, f: Future) -> None:
+        with self.lock:
+            self.items.append((afut, f))
+            if self.scheduled:
+                return
+            self.scheduled = True
+        self.loop.call_soon_threadsafe(self.drain)
+
+    def drain(self) -> None:
+        while True:
+            with self.lock:
+                if not self.items:
+                    self.scheduled = False
+                    return
+                batch = list(self.items)
+                self.items.clear()
+            for afut, f in batch:
+                _resolve(afut, f)
+
+
+def _mailbox(loop) -> _Mailbox:
+    mb = getattr(loop, "_pie_mailbox", None)
+    if mb is None:
+        mb = loop._pie_mailbox = _Mailbox(loop)
+    return mb
+
+
 async def wait(fut: Future):
     """Await a runtime future from the inferlet's coroutine."""
     if fut.done():
         return fut.result()
     loop = asyncio.get_running_loop()
     afut = loop.create_future()
-
-    def done(f: Future):
-        loop.call_soon_threadsafe(_resolve, afut, f)
-
-    fut.add_done_callback(done)
+    mb = _mailbox(loop)
+    fut.add_done_callback(lambda f: mb.post(afut, f))
     return await afut
 
 
