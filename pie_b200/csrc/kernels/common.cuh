@@ -25,6 +25,7 @@ enum PieKernelStatus : int {
 
 // Layout of the status block (8 int32, 8-byte aligned) that the kernels with peer waits are given:
 //   [0]    first PieKernelStatus error code, 0 while healthy
+//   [1]    for PIE_ERR_BOUNDS from the index validator: table code << 24 | position of the first bad entry
 //   [2..3] nanoseconds (u64) that CTA 0 of the gated GEMMs spent waiting for all-gather flags, [6] waits counted
 //   [4..5] nanoseconds (u64) that CTA 0 of the reduce + norm + push kernel spent waiting for reduce-scatter
 //          flags, [7] waits counted

@@ -431,6 +431,26 @@ __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restri
 }
 }  // namespace pie
 
+namespace pie {
+// Debug check of an index table before the kernels that trust it run: an entry outside [lo, hi) is
+// recorded (first one wins) and nothing is dereferenced.
+__global__ void validate_indices_kernel(const int* __restrict__ v, int n, int lo, int hi, int table_code,
+                                        int* __restrict__ status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int x = v[i];
+    if (x < lo || x >= hi) {
+        if (atomicCAS(&status[0], 0, PIE_ERR_BOUNDS) == 0) status[1] = (table_code << 24) | min(i, 0xFFFFFF);
+    }
+}
+}  // namespace pie
+
+PIE_API int pie_validate_indices(const int* v, int n, int lo, int hi, int table_code, int* status, cudaStream_t st) {
+    if (n <= 0) return 0;
+    pie::validate_indices_kernel<<<(n + 255) / 256, 256, 0, st>>>(v, n, lo, hi, table_code, status);
+    return (int)cudaGetLastError();
+}
+
 PIE_API int pie_feed_tokens(int* tokens, const int* src_row, const int* prev_sampled, int n,
                             cudaStream_t st) {
     if (n <= 0) return 0;

@@ -17,6 +17,7 @@ because its length lives in device memory.
 """
 from __future__ import annotations
 
+import os
 import threading
 import time
 from dataclasses import dataclass
@@ -211,6 +212,7 @@ class TorchDriver:
         # that every rank sees the same order of fires and copies and the control ring has one writer
         # at a time.
         self._order = threading.RLock()
+        self.bounds_check = os.environ.get("PIE_BOUNDS", "0") == "1"
         self.use_graphs = use_graphs and self.cuda
         self.buckets = graph_buckets(max_requests)
         self.graphs: Dict[int, _Graph] = {}
@@ -336,6 +338,24 @@ class TorchDriver:
         s.h("kv_page_indptr")[:r + 1] = req.kv_page_indptr
         s.h("kv_lens")[:r] = kv_lens
         s.h("page_indices")[:len(req.kv_page_indices)] = req.kv_page_indices
+
+    def _validate_request(self, req: ForwardRequest, slots) -> None:
+        """`PIE_BOUNDS=1`: check every index table of the fire against its range before any kernel that
+        trusts it runs (token ids, page indices, last-page lengths, KV write slots, logit rows). A bad
+        entry fails the fire with the table and position; no kernel reads through it."""
+        dev = self.device
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+        pages = self.kv.num_pages
+        ops.validate_indices(t(req.tokens), 0, self.cfg.vocab_size, "tokens")
+        ops.validate_indices(t(req.positions), 0, 1 << 30, "positions")
+        ops.validate_indices(t(req.kv_page_indices), 0, pages, "kv_page_indices")
+        ops.validate_indices(t(req.kv_last_page_lens), 1, self.page_size + 1, "kv_last_page_lens")
+        ops.validate_indices(t(slots), 0, pages * self.page_size, "kv_slots")
+        if req.slot_row is not None and len(req.slot_row):
+            ops.validate_indices(t(req.slot_row), 0, max(1, req.num_tokens), "logit_rows")
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()
+            ops.check_kernel_status(dev)
 
     def _sampler_params(self, req: ForwardRequest, rows_of_slot: np.ndarray):
         """Fill per-row sampler parameter segments for the token-sampler slots."""
@@ -669,6 +689,8 @@ class TorchDriver:
         t0 = time.perf_counter()
         self.stats["fires"] += 1
         qlens, kv_lens, slots = self._derive(req)
+        if self.bounds_check:
+            self._validate_request(req, slots)
         nslots = len(req.slot_samplers)
         self._lora_bindings = self._bind_adapters(req)
         decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None

@@ -43,11 +43,35 @@ def kernel_status(device=None) -> torch.Tensor:
     return _STATUS[dev]
 
 
+BOUNDS_TABLES = ["tokens", "positions", "kv_page_indices", "kv_last_page_lens", "kv_slots", "logit_rows"]
+
+
 def check_kernel_status(device=None) -> None:
-    st = int(kernel_status(device)[0].item())
+    words = kernel_status(device)[:2].tolist()
+    st = int(words[0])
     if st != 0:
         kernel_status(device).zero_()
+        if st == 5:
+            code, pos = (int(words[1]) >> 24) & 0xFF, int(words[1]) & 0xFFFFFF
+            name = BOUNDS_TABLES[code] if code < len(BOUNDS_TABLES) else f"table {code}"
+            raise _lib.KernelLibraryError(f"index out of bounds: {name}[{pos}] (status 5)")
         raise _lib.KernelLibraryError(f"a kernel gave up on a bounded wait (status {st})")
+
+
+def validate_indices(v, lo: int, hi: int, table: str) -> None:
+    """Debug check (`PIE_BOUNDS=1`): every entry of the int32 table `v` lies in [lo, hi). On the device the
+    first bad entry is recorded in the status block (read back by `check_kernel_status`); on the host it
+    raises at once. Nothing is dereferenced through a bad index either way."""
+    if v.numel() == 0:
+        return
+    if not v.is_cuda:
+        bad = ((v < lo) | (v >= hi)).nonzero()
+        if bad.numel():
+            i = int(bad[0])
+            raise IndexError(f"index out of bounds: {table}[{i}] = {int(v[i])}, not in [{lo}, {hi})")
+        return
+    check(fn("pie_validate_indices")(ptr(v), v.numel(), lo, hi, BOUNDS_TABLES.index(table),
+                                     ptr(kernel_status(v.device)), stream_ptr()), "validate_indices")
 
 
 # --------------------------------------------------------------------------- elementwise

@@ -51,6 +51,7 @@ _SIGNATURES = {
     "pie_tp_sample": [p, p, i64, i32, p, p, p, p, p, p, p, i32, p, i32, p],
     "pie_row_stats": [p, i64, i32, i32, p, p],
     "pie_feed_tokens": [p, p, p, i32, p],
+    "pie_validate_indices": [p, i32, i32, i32, i32, p, p],
     "pie_gemm_set_workspace": [i32, p, i64, p, i32],
     "pie_gemm_set_pairs": [i32],
     "pie_gemm_set_swap": [i32],

@@ -6,6 +6,7 @@ token-for-token against an independent dense fp32 forward."""
 import json
 
 import numpy as np
+import pytest
 import torch
 
 from pie_b200.driver.executor import TorchDriver
@@ -149,3 +150,29 @@ def test_samplers_on_one_row_share_one_logit_row():
     b = fire([1], [SamplerSpec.greedy()]).slots[0].token
     assert [r.slots[0].token, r.slots[1].token] == [a, b]
     assert r.slots[2].ids[0] == a and r.slots[3].kind == "entropy"
+
+
+def test_bounds_check_mode_names_the_bad_table_and_entry(monkeypatch):
+    """`PIE_BOUNDS=1`: a fire whose index tables point outside their ranges fails before any kernel runs."""
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import ForwardRequest, SamplerSpec
+    from pie_b200.models.config import preset
+    monkeypatch.setenv("PIE_BOUNDS", "1")
+    drv = TorchDriver(preset("tiny-llama", num_hidden_layers=1), device="cpu", num_pages=8)
+    assert drv.bounds_check
+    i32 = lambda *a: np.asarray(a, dtype=np.int32)
+
+    def req(**kw):
+        base = dict(tokens=i32(1, 2, 3), positions=i32(0, 1, 2), qo_indptr=i32(0, 3), kv_page_indices=i32(2),
+                    kv_page_indptr=i32(0, 1), kv_last_page_lens=i32(3), slot_req=i32(0), slot_row=i32(2),
+                    slot_samplers=[SamplerSpec()])
+        base.update(kw)
+        return ForwardRequest(**base)
+    assert drv.fire_batch(req()).slots[0].kind == "token"
+    with pytest.raises(IndexError, match=r"kv_page_indices\[0\] = 8"):
+        drv.fire_batch(req(kv_page_indices=i32(8)))                  # pages 0..7 exist
+    with pytest.raises(IndexError, match=r"tokens\[1\]"):
+        drv.fire_batch(req(tokens=i32(1, 1 << 20, 3)))
+    with pytest.raises(IndexError, match=r"logit_rows\[0\] = 3"):
+        drv.fire_batch(req(slot_row=i32(3)))
+    assert drv.fire_batch(req()).slots[0].kind == "token"           # the driver is still usable

@@ -537,3 +537,27 @@ def test_bounded_peer_wait_times_out_and_reports_status():
     _lib.check(wait(flags.data_ptr(), epoch.data_ptr(), 2, status.data_ptr(), _lib.stream_ptr()), "tp_wait_ag")
     torch.cuda.synchronize()
     assert int(status[0].item()) == 0
+
+
+def test_index_validator_records_the_first_bad_entry_and_touches_nothing():
+    """The `PIE_BOUNDS=1` check: entries outside [lo, hi) set PIE_ERR_BOUNDS with table and position; the
+    status check raises with them and clears the block, and a clean table leaves it alone."""
+    from pie_b200.ops import _lib
+    ops.kernel_status(DEV).zero_()
+    good = torch.arange(0, 1000, dtype=torch.int32, device=DEV)
+    ops.validate_indices(good, 0, 1000, "kv_page_indices")
+    torch.cuda.synchronize()
+    ops.check_kernel_status(DEV)
+    bad = good.clone()
+    bad[637] = 1000
+    ops.validate_indices(bad, 0, 1000, "kv_page_indices")
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.KernelLibraryError, match=r"kv_page_indices\[637\]"):
+        ops.check_kernel_status(DEV)
+    ops.check_kernel_status(DEV)                              # cleared
+    neg = good.clone()
+    neg[3] = -1
+    ops.validate_indices(neg, 0, 1000, "tokens")
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.KernelLibraryError, match=r"tokens\[3\]"):
+        ops.check_kernel_status(DEV)
