@@ -90,6 +90,8 @@ FIELDS: List[Tuple[str, str, int, int]] = [
     ("decode_step", "seeds", 91, I64),
     ("control", "json", 100, JSON),                       # cold operations: adapters, health, capabilities, shutdown
     ("forward_response", "spec_accepted", 45, I32),       # accepted drafts per request
+    ("forward_request", "rs_slots", 29, I32),             # recurrent-state slot per request
+    ("forward_request", "rs_reset", 30, I32),             # 1 = the slot starts from zero in this fire
 ]
 
 _SLOT_KINDS = ["token", "distribution", "logits", "logprobs", "entropy", "embedding"]
@@ -215,6 +217,7 @@ def pack_forward_request(r: ForwardRequest) -> bytes:
         "sampler_labels": [int(x) for s in ss for x in s.labels], "sampler_labels_indptr": lab_ptr,
         "sampler_seed_final": [1 if s.seed_final else 0 for s in ss],
         "spec_counts": r.spec_counts, "context_ids": r.context_ids, "adapter_ids": r.adapter_ids,
+        "rs_slots": r.rs_slots, "rs_reset": r.rs_reset,
         "flags": [1 if r.single_token_mode else 0, int(r.trimmed_pages)],
     }
     return _frame(KIND_FORWARD_REQUEST, "forward_request", vals)
@@ -246,6 +249,7 @@ def unpack_forward_request(buf) -> ForwardRequest:
         mask_runs=mask_runs, mask_row_indptr=s.get("mask_row_indptr"), logit_masks=logit_masks,
         slot_req=e("slot_req", np.int32), slot_row=e("slot_row", np.int32), slot_samplers=samplers,
         spec_counts=s.get("spec_counts"), context_ids=s.get("context_ids"), adapter_ids=s.get("adapter_ids"),
+        rs_slots=s.get("rs_slots"), rs_reset=s.get("rs_reset"),
         single_token_mode=bool(flags[0]), trimmed_pages=int(flags[1]))
 
 

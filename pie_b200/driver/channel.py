@@ -86,7 +86,8 @@ def dispatch(driver, op: int, payload):
             if hasattr(driver, "shutdown"):
                 driver.shutdown()
             return True
-        if name in ("create_adapter", "destroy_adapter", "fork_adapter", "save_adapter", "load_adapter", "zo_apply"):
+        if name in ("create_adapter", "destroy_adapter", "fork_adapter", "save_adapter", "load_adapter", "zo_apply",
+                    "copy_rs"):
             return getattr(driver, name)(*payload.get("args", []))
         raise ValueError(f"unknown control operation {name!r}")
     raise ValueError(f"unknown operation {op}")
@@ -445,6 +446,9 @@ class ChannelDriver:
 
     def zo_apply(self, *a):
         return self._control("zo_apply", *a)
+
+    def copy_rs(self, src_slot: int, dst_slot: int):
+        return self._control("copy_rs", int(src_slot), int(dst_slot))
 
     def shutdown(self) -> None:
         if self.alive:

@@ -139,7 +139,7 @@ class TorchDriver:
                  page_size: int = 16, max_requests: int = 512, max_tokens: int = 8192, seed: int = 0,
                  par: Optional[ParallelContext] = None, gemm_backend: str = "tcgen05", use_graphs: bool = True,
                  swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0,
-                 memory_profile: str = "", kv_dtype: str = "auto"):
+                 memory_profile: str = "", kv_dtype: str = "auto", rs_slots: int = 0):
         self.cfg = cfg
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
@@ -173,6 +173,14 @@ class TorchDriver:
         self.kv = KVCache(cfg.num_hidden_layers, num_pages, hkv, page_size, cfg.head_dim, self.dtype,
                           self.device, swap_pages, kv_dtype=kv_dtype)
         self.model.kv_scale = self.kv.scale
+        # Gated DeltaNet layers keep their state in slots of a recurrent-state cache, one per resident context
+        self.rs = None
+        if cfg.linear_layers:
+            if self.par.tp_size > 1:
+                raise NotImplementedError("Gated DeltaNet layers under tensor parallelism")
+            from .recurrent import RecurrentStateCache
+            self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
+            use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet
         self.max_requests, self.max_tokens = max_requests, max_tokens
         self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
         self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
@@ -304,7 +312,7 @@ class TorchDriver:
             max_page_refs=self.max_page_refs, max_logit_rows=self.max_rows, max_prob_rows=self.max_rows,
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
-            tp_size=self.par.tp_size)
+            tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0)
 
     # ------------------------------------------------------------------ request -> slab
     def _derive(self, req: ForwardRequest):
@@ -572,10 +580,23 @@ class TorchDriver:
                                logit_rows=torch.from_numpy(rows), is_decode=False)
         self.stats["eager"] += 1
         fi.lora = self._lora_bindings
+        if self.rs is not None:
+            if req.spec_counts is not None and np.any(req.spec_counts):
+                raise ValueError("draft tokens on a model with recurrent layers: a rejected draft cannot be rolled "
+                                 "out of the recurrent state")
+            fi.rs = self.rs.inputs(req.qo_indptr, req.rs_slots, req.rs_reset)
         hidden = self.model.forward_hidden(fi, self.kv.data)
         if len(rows) == 0:
             return None
         return self.model.logits(hidden, fi)
+
+    def copy_rs(self, src_slot: int, dst_slot: int) -> None:
+        """Recurrent-state slot copy (a forked context starts from its parent's state)."""
+        if self.rs is None:
+            return
+        with self._order:
+            self._bind_thread()
+            self.rs.copy_slot(int(src_slot), int(dst_slot))
 
     # ------------------------------------------------------------------ sampling + response
     def _respond(self, req: ForwardRequest, logits: Optional[torch.Tensor], slot_logit_row: np.ndarray):
@@ -694,7 +715,7 @@ class TorchDriver:
         nslots = len(req.slot_samplers)
         self._lora_bindings = self._bind_adapters(req)
         decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None
-                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)))
+                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None)
         if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
             # followers must draw the same tokens: fix the per-fire seeds before publishing
             from dataclasses import replace as _replace

@@ -172,6 +172,9 @@ class MockDriver:
     def copy(self, req: CopyRequest) -> None:
         self.recorder.copies.append(req)
 
+    def copy_rs(self, src_slot: int, dst_slot: int) -> None:
+        self.recorder.copies.append(("rs", int(src_slot), int(dst_slot)))
+
     def health(self) -> bool:
         return self.alive
 

@@ -86,6 +86,10 @@ class ForwardRequest:
     slot_row: np.ndarray = None        # int32 [S] token row (global index into tokens) of each slot
     slot_samplers: List[SamplerSpec] = field(default_factory=list)
     # speculative drafts already spliced into tokens: number of draft tokens per request
+    # models with recurrent (linear-attention) layers: the state slot of every request, and which slots
+    # must start from zero in this fire (first pass of a context, or a replay after its state was lost)
+    rs_slots: Optional[np.ndarray] = None     # int32 [R]
+    rs_reset: Optional[np.ndarray] = None     # int32 [R]
     spec_counts: Optional[np.ndarray] = None
     context_ids: Optional[np.ndarray] = None       # uint64 [R]
     adapter_ids: Optional[np.ndarray] = None       # int64 [R], -1 = none

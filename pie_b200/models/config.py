@@ -13,7 +13,8 @@ from typing import Optional
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 # `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3",
-                         "gpt_oss")
+                         "gpt_oss", "qwen3_5", "qwen3_next")
+GDN_TYPES = {"qwen3_5", "qwen3_next"}   # hybrids: Gated DeltaNet (linear attention) layers between full-attention layers
 POST_NORM = {"olmo2", "olmo3"}       # same block with the norms after attention / MLP and q, k norms over all heads
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
 
@@ -47,6 +48,12 @@ class ModelConfig:
     norm_topk_prob: bool = True
     moe_style: str = "swiglu"       # "gpt_oss": expert and router biases, clamped (up + 1) * gate * sigmoid(1.702 gate)
     swiglu_limit: float = 7.0
+    # Gated DeltaNet layers (layer_types entry "linear_attention"): heads and head sizes of the linear mixer
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
     # quantisation of the linear weights: None | "fp8_block" (128x128 weight scales)
     quantization: Optional[str] = None
     dtype: str = "bfloat16"
@@ -55,6 +62,24 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    def is_linear_layer(self, li: int) -> bool:
+        return self.layer_types is not None and self.layer_types[li] == "linear_attention"
+
+    @property
+    def linear_layers(self) -> list:
+        """Indices of the Gated DeltaNet layers (empty for pure-attention models)."""
+        return [li for li in range(self.num_hidden_layers) if self.is_linear_layer(li)]
+
+    @property
+    def gdn_conv_channels(self) -> int:
+        """Channels of the short convolution: q and k of the key heads, v of the value heads."""
+        return 2 * self.linear_num_key_heads * self.linear_key_head_dim + self.linear_num_value_heads * self.linear_value_head_dim
+
+    @property
+    def gdn_in_features(self) -> int:
+        """Rows of the fused input projection: q | k | v | z (output gate) | b (beta) | a (decay)."""
+        return self.gdn_conv_channels + self.linear_num_value_heads * self.linear_value_head_dim + 2 * self.linear_num_value_heads
 
     def layer_window_left(self, li: int) -> int:
         """Keys left of the query that layer `li` sees (-1: all). HF `sliding_window` counts the query itself."""
@@ -104,14 +129,17 @@ class ModelConfig:
             rope_theta=cfg.get("rope_theta", 10000.0),
             rope_scaling=cfg.get("rope_scaling"),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2", "olmo3") or cfg.get("use_qk_norm", False),
+            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2", "olmo3") or mt in GDN_TYPES or cfg.get("use_qk_norm", False),
             post_norm=mt in POST_NORM,
             attention_bias=cfg.get("attention_bias", mt in ("qwen2", "gpt_oss")),
             # Qwen2 gates the window on use_sliding_window; Mistral applies it whenever it is set
             sliding_window=(cfg.get("sliding_window") or -1)
             if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss", "olmo3")) else -1,
             # OLMo-3 and GPT-OSS alternate sliding-window and full-attention layers
-            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") else None,
+            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") or mt in GDN_TYPES else None,
+            linear_num_key_heads=cfg.get("linear_num_key_heads", 0), linear_num_value_heads=cfg.get("linear_num_value_heads", 0),
+            linear_key_head_dim=cfg.get("linear_key_head_dim", 0), linear_value_head_dim=cfg.get("linear_value_head_dim", 0),
+            linear_conv_kernel_dim=cfg.get("linear_conv_kernel_dim", 4),
             attention_sinks=mt == "gpt_oss",
             o_bias=mt == "gpt_oss" and cfg.get("attention_bias", True),
             moe_style="gpt_oss" if mt == "gpt_oss" else "swiglu",
@@ -178,6 +206,10 @@ PRESETS = {
                          num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, moe_style="gpt_oss",
                          rope_scaling=dict(rope_type="yarn", factor=4.0, beta_fast=32.0, beta_slow=1.0,
                                            original_max_position_embeddings=64, truncate=False), dtype="float32"),
+    "tiny-qwen3.5": dict(model_type="qwen3_5", hidden_size=256, intermediate_size=512, num_hidden_layers=4,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000, qk_norm=True,
+                         rope_theta=1e6, layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+                         linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,

@@ -34,6 +34,7 @@ class ForwardInputs:
     attn: object                  # ops.DecodePlan | ops.PrefillPlan | ops.AttnBatch (CPU)
     attn_num_pages: Optional[int] = None   # page references of this batch (prefill plans; the slab segment is larger)
     logit_rows: Optional[torch.Tensor] = None   # int32 rows of the hidden state that need logits
+    rs: Optional[object] = None   # driver.recurrent.RecurrentInputs for models with Gated DeltaNet layers
     is_decode: bool = False
     lora: Optional[list] = None   # [(LoraAdapter, int64 token rows)] for requests bound to an adapter
 
@@ -169,6 +170,14 @@ class Transformer:
         for li in range(cfg.num_hidden_layers):
             lw = w["layers"][li]
             post = cfg.post_norm
+            if "w_gdn_in" in lw:
+                # Gated DeltaNet layer: the mixer replaces attention, its state lives in the recurrent-state cache
+                x = ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
+                mix = self._gemm(x, lw["w_gdn_in"])
+                o = ops.gdn_mixer(mix, lw, cfg, fi.rs, fi.rs.layer_index[li])
+                h = self._gemm(o, lw["w_gdn_out"], residual=h)
+                h = self._mlp(ops.rmsnorm(h, lw["ln2"], cfg.rms_norm_eps), lw, h)
+                continue
             x = h if post else ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
             qkv = self._gemm(x, lw["wqkv"])
             if "bqkv" in lw:
@@ -247,6 +256,40 @@ def _swiglu_interleaved_cuda(y):
     return torch.nn.functional.silu(g) * u
 
 
+def _dense_gdn(cfg: ModelConfig, lw: dict, xn: torch.Tensor) -> torch.Tensor:
+    """Gated DeltaNet over one whole sequence from an empty state, written token by token with explicit
+    head loops (independent of the cached, batched implementation it checks)."""
+    hk, hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    kk, c = cfg.linear_conv_kernel_dim, cfg.gdn_conv_channels
+    mix = xn @ lw["w_gdn_in"].float().t()
+    t = mix.shape[0]
+    pad = torch.cat([torch.zeros(kk - 1, c), mix[:, :c]], 0)
+    cw = lw["gdn_conv"].float()
+    conv = torch.stack([(pad[i:i + kk] * cw.t()).sum(0) for i in range(t)])
+    conv = conv * torch.sigmoid(conv)
+    out = torch.zeros(t, hv * dv)
+    for h in range(hv):
+        kh = h // (hv // hk)
+        state = torch.zeros(dk, dv)
+        for i in range(t):
+            q = conv[i, kh * dk:(kh + 1) * dk]
+            k = conv[i, hk * dk + kh * dk:hk * dk + (kh + 1) * dk]
+            v = conv[i, 2 * hk * dk + h * dv:2 * hk * dk + (h + 1) * dv]
+            z = mix[i, c + h * dv:c + (h + 1) * dv]
+            beta = torch.sigmoid(mix[i, c + hv * dv + h])
+            g = -torch.exp(lw["gdn_A_log"].float()[h]) * torch.nn.functional.softplus(
+                mix[i, c + hv * dv + hv + h] + lw["gdn_dt_bias"].float()[h])
+            q = q / torch.sqrt((q * q).sum() + 1e-6) / math.sqrt(dk)
+            k = k / torch.sqrt((k * k).sum() + 1e-6)
+            state = state * torch.exp(g)
+            delta = (v - k @ state) * beta
+            state = state + torch.outer(k, delta)
+            o = q @ state
+            o = o / torch.sqrt((o * o).mean() + cfg.rms_norm_eps) * lw["gdn_norm"].float()
+            out[i, h * dv:(h + 1) * dv] = o * z * torch.sigmoid(z)
+    return out
+
+
 def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> torch.Tensor:
     """Independent dense (non-paged) fp32 forward of the same weights for one sequence:
     RMSNorm -> QKV -> rotate-half RoPE -> causal attention -> SwiGLU. Returns logits [T, V].
@@ -261,6 +304,11 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * g.float()
 
     for li, lw in enumerate(w["layers"]):
+        if "w_gdn_in" in lw:
+            x = x + _dense_gdn(cfg, lw, norm(x, lw["ln1"])) @ lw["w_gdn_out"].float().t()
+            gu = norm(x, lw["ln2"]) @ lw["w_gate_up"].float().t()
+            x = x + (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t()
+            continue
         xn = x if cfg.post_norm else norm(x, lw["ln1"])
         qkv = xn @ lw["wqkv"].float().t()
         if "bqkv" in lw:

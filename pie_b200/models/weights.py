@@ -95,7 +95,23 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
     w = {"layers": []}
     emb = gen.normal(cfg.vocab_size, H)
     w["embed"] = emb
-    for _ in range(cfg.num_hidden_layers):
+    for li in range(cfg.num_hidden_layers):
+        if cfg.is_linear_layer(li):
+            if T > 1:
+                raise NotImplementedError("Gated DeltaNet layers under tensor parallelism")
+            # Gated DeltaNet mixer: fused input projection (q | k | v | z | b | a), depthwise short convolution over
+            # q | k | v, per-value-head decay (A_log, dt_bias), gated RMSNorm over the head dimension, output projection
+            Hv, dv = cfg.linear_num_value_heads, cfg.linear_value_head_dim
+            lw = {"ln1": ones(H), "ln2": ones(H),
+                  "w_gdn_in": gen.normal(cfg.gdn_in_features, H, std=0.05),
+                  "gdn_conv": gen.normal(cfg.gdn_conv_channels, cfg.linear_conv_kernel_dim, std=0.3),
+                  "gdn_A_log": gen.normal(Hv, std=0.5).float(), "gdn_dt_bias": gen.normal(Hv, std=0.5).float(),
+                  "gdn_norm": 1 + gen.normal(dv, std=0.1), "w_gdn_out": gen.normal(H, Hv * dv)}
+            gate, up = gen.normal(cfg.intermediate_size, H), gen.normal(cfg.intermediate_size, H)
+            lw["w_gate_up"] = interleave_rows(gate, up).contiguous()
+            lw["w_down"] = gen.normal(H, cfg.intermediate_size)
+            w["layers"].append(lw)
+            continue
         if cfg.post_norm:
             # norm gains away from 1 so that a misplaced norm shows in the tests
             lw = {"ln2": 1 + gen.normal(H, std=0.1), "ln3": 1 + gen.normal(H, std=0.1)}

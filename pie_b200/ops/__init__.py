@@ -896,3 +896,33 @@ def row_stats(logits):
     check(fn("pie_row_stats")(ptr(logits), logits.stride(0), rows, vocab, ptr(out), stream_ptr()),
           "row_stats")
     return out
+
+
+# --------------------------------------------------------------------------- Gated DeltaNet
+def gdn_mixer(mix, lw: dict, cfg, rs, layer: int):
+    """The linear-attention mixer of one layer over a ragged batch (see `reference.gdn_mixer` for the math).
+    `mix` is the fused input projection [N, q | k | v | z | b | a]; `rs` a `driver.recurrent.RecurrentInputs`;
+    the layer's slot states are advanced in place. Returns [N, Hv * dv]."""
+    hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    if rs is None:
+        raise ValueError("a model with Gated DeltaNet layers needs recurrent-state inputs")
+    conv_state, rec_state = rs.conv_state[layer], rs.rec_state[layer]
+    if not mix.is_cuda:
+        return reference.gdn_mixer(mix, lw["gdn_conv"], lw["gdn_A_log"], lw["gdn_dt_bias"], lw["gdn_norm"],
+                                   cfg.rms_norm_eps, hk, hv, dk, dv, rs.qo_host, conv_state, rec_state,
+                                   rs.slots_host, rs.reset_host)
+    n, r = mix.shape[0], len(rs.slots_host)
+    out = torch.empty(n, hv * dv, dtype=torch.bfloat16, device=mix.device)
+    check(fn("pie_gdn_mixer")(ptr(mix), mix.stride(0), ptr(lw["gdn_conv"]), ptr(lw["gdn_A_log"]), ptr(lw["gdn_dt_bias"]),
+                              ptr(lw["gdn_norm"]), ptr(conv_state), ptr(rec_state), ptr(rs.qo_indptr), ptr(rs.tok_req),
+                              ptr(rs.slots), ptr(rs.reset), ptr(rs.scratch), ptr(out), n, r, hk, hv, dk, dv,
+                              cfg.linear_conv_kernel_dim, cfg.rms_norm_eps, stream_ptr()), "gdn_mixer")
+    return out
+
+
+def gdn_copy_slot(buf, src: int, dst: int) -> None:
+    """buf[:, dst] <- buf[:, src] for a [layers, slots, ...] fp32 state cache on the device."""
+    layers, slots = buf.shape[0], buf.shape[1]
+    slot_elems = buf[0, 0].numel()
+    check(fn("pie_gdn_copy_slot")(ptr(buf), slots * slot_elems, slot_elems, layers, src, dst, stream_ptr()), "gdn_copy_slot")

@@ -250,3 +250,63 @@ def gemm(x, w, residual=None):
     if residual is not None:
         y = y + residual.float()
     return y.to(x.dtype)
+
+
+# ------------------------------------------------------------------ Gated DeltaNet (linear attention)
+def gdn_mixer(mix, conv_w, a_log, dt_bias, norm_w, eps, hk, hv, dk, dv, qo_indptr, conv_state, rec_state, slots, reset):
+    """Gated DeltaNet mixer over a ragged batch, state carried in per-slot caches (updated in place).
+
+    `mix` [N, 2*hk*dk + 2*hv*dv + 2*hv] is the fused input projection q | k | v | z | b | a. Per request
+    (rows qo_indptr[r]:qo_indptr[r+1], cache slot slots[r], state zeroed first when reset[r]):
+      * causal depthwise convolution (kernel K) + SiLU over the q | k | v channels, continuing from the
+        slot's last K-1 inputs (`conv_state` [S, C, K-1]);
+      * per value head: q, k L2-normalised, q scaled by dk^-1/2; beta = sigmoid(b);
+        g = -exp(A_log) * softplus(a + dt_bias); S <- S * exp(g); delta = (v - k^T S) * beta;
+        S <- S + k (x) delta; o = q^T S   (`rec_state` [S, hv, dk, dv], fp32);
+      * out = RMSNorm(o) * norm_w * silu(z) per head.
+    Math of the reference's recurrent step (driver/cuda/src/kernels/gated_delta_net.cu, recurrent_step*).
+    """
+    n = mix.shape[0]
+    c = 2 * hk * dk + hv * dv
+    kk = conv_w.shape[1]
+    x = mix.float()
+    out = torch.zeros(n, hv * dv, dtype=torch.float32, device=mix.device)
+    cw = conv_w.float()
+    decay = -torch.exp(a_log.float())
+    rep = hv // hk
+    for r in range(len(qo_indptr) - 1):
+        a0, a1 = int(qo_indptr[r]), int(qo_indptr[r + 1])
+        if a1 <= a0:
+            continue
+        s = int(slots[r])
+        if reset[r]:
+            conv_state[s].zero_()
+            rec_state[s].zero_()
+        hist = torch.cat([conv_state[s].float().t(), x[a0:a1, :c]], dim=0)          # [K-1 + T, C]
+        t = a1 - a0
+        conv = sum(hist[j:j + t] * cw[:, j] for j in range(kk))                      # causal: taps end at the token
+        conv = torch.nn.functional.silu(conv)
+        conv_state[s].copy_(hist[-(kk - 1):].t().to(conv_state.dtype))
+        q = conv[:, :hk * dk].reshape(t, hk, dk)
+        k = conv[:, hk * dk:2 * hk * dk].reshape(t, hk, dk)
+        v = conv[:, 2 * hk * dk:].reshape(t, hv, dv)
+        z = x[a0:a1, c:c + hv * dv].reshape(t, hv, dv)
+        b = x[a0:a1, c + hv * dv:c + hv * dv + hv]
+        a = x[a0:a1, c + hv * dv + hv:]
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+        q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)      # key heads serve `rep` value heads
+        beta = torch.sigmoid(b)
+        g = decay * torch.nn.functional.softplus(a + dt_bias.float())
+        st = rec_state[s].float()                                                     # [hv, dk, dv]
+        o = torch.zeros(t, hv, dv, device=mix.device)
+        for i in range(t):
+            st = st * torch.exp(g[i])[:, None, None]
+            kv = (st * k[i][:, :, None]).sum(1)
+            delta = (v[i] - kv) * beta[i][:, None]
+            st = st + k[i][:, :, None] * delta[:, None, :]
+            o[i] = (st * q[i][:, :, None]).sum(1)
+        rec_state[s].copy_(st)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+        out[a0:a1] = (o * torch.nn.functional.silu(z)).reshape(t, hv * dv)
+    return out.to(mix.dtype)

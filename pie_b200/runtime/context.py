@@ -70,6 +70,8 @@ class PinnedContext:
     pages: List[int]          # physical ids: committed then working
     kv_len: int               # committed_pages*page + working tokens
     driver: int
+    rs_slot: int = -1         # recurrent-state slot (models with linear-attention layers), else -1
+    rs_reset: int = 0         # 1: the next pass of this context starts its recurrent state from zero
 
 
 class Deferred(ContextError):
@@ -87,7 +89,8 @@ class ContextManager:
 
     def __init__(self, model: str, page_size: int, stores: Sequence[PageStore],
                  copy_fn: Optional[Callable[[int, CopyRequest], None]] = None,
-                 swap_pages: int = 0):
+                 swap_pages: int = 0, rs_slots: Sequence[int] = (),
+                 rs_copy_fn: Optional[Callable[[int, int, int], None]] = None):
         self.model, self.page_size = model, page_size
         self.stores = list(stores)
         self.copy_fn = copy_fn or (lambda driver, req: None)
@@ -101,6 +104,10 @@ class ContextManager:
         self.counters = {"created": 0, "forked": 0, "commits": 0, "dedup_pages": 0, "suspended": 0,
                          "restored": 0, "evictions": 0, "replayed_tokens": 0}
         self.market = None   # optional Market: orders eviction victims (defaulted, lowest bid, newest)
+        # recurrent-state slot pools, one per driver (all empty for pure-attention models)
+        from .rs_cache import RsCache
+        self.rs = [RsCache(int(rs_slots[d]) if d < len(rs_slots) else 0) for d in range(len(self.stores))]
+        self.rs_copy_fn = rs_copy_fn or (lambda driver, src, dst: None)
         self.restore_pause_at_utilization = 0.85
         self.restore_queue: Dict[int, list] = {d: [] for d in range(len(self.stores))}   # per driver: waiting contexts
         self.page_waiters: Dict[int, list] = {d: [] for d in range(len(self.stores))}    # one-shot callbacks
@@ -265,6 +272,7 @@ class ContextManager:
             if ctx.stash:
                 self._swap_free.extend(ctx.stash)
             ctx.chain, ctx.working_pages, ctx.stash = [], [], None
+            self.rs[ctx.driver].forget(cid)
             ctx.state = State.DESTROYED
             self.by_owner.get(ctx.owner, set()).discard(cid)
             del self.contexts[cid]
@@ -324,6 +332,8 @@ class ContextManager:
             self._truncate_to(ctx, max(0, len(ctx.tokens) - n))
 
     def _truncate_to(self, ctx: Context, keep: int) -> None:
+        if keep < len(ctx.tokens):
+            self.rs[ctx.driver].invalidate(ctx.id)     # a recurrent state cannot be rolled back: replay
         del ctx.tokens[keep:], ctx.positions[keep:], ctx.mask_keys[keep:]
 
     def append_working_tokens(self, cid: int, tokens: Sequence[int], positions: Sequence[int],
@@ -396,6 +406,14 @@ class ContextManager:
                 bid=src.bid, created_seq=next(self._seq))
             self.by_owner.setdefault(own, set()).add(nid)
             self.counters["forked"] += 1
+            rs = self.rs[src.driver]
+            if rs.supported:
+                from .rs_cache import RsState
+                pair = rs.fork(cid, nid) if not own.startswith("@snapshot") else None
+                if pair is not None:
+                    self.rs_copy_fn(src.driver, pair[0], pair[1])
+                elif rs.state_of(cid) != RsState.EMPTY or own.startswith("@snapshot"):
+                    rs.state[nid] = RsState.MISSING if (src.chain or src.tokens) else RsState.EMPTY
             return nid
 
     def save(self, cid: int, username: str, name: str) -> None:
@@ -448,10 +466,40 @@ class ContextManager:
             if kv_len + n_new_tokens > cap:
                 raise ContextError(
                     f"KV_INVARIANT_VIOLATION: kv_len {kv_len} + {n_new_tokens} inputs > capacity {cap}")
+            rs_slot, rs_reset = -1, 0
+            rs = self.rs[ctx.driver]
+            if rs.supported:
+                from .rs_cache import RsState
+                rs_slot = rs.acquire(cid)
+                if rs_slot is None:
+                    victim = self._rs_victim(ctx)
+                    if victim is None:
+                        self.counters["deferred"] += 1
+                        raise Deferred("no free recurrent-state slot")
+                    rs.release(victim.id)
+                    rs_slot = rs.acquire(cid)
+                if rs.state_of(cid) == RsState.MISSING and kv_len > 0 and not getattr(ctx, "_pending_replay", None):
+                    # the state was lost (eviction, truncation, opened from a snapshot): rebuild it by running
+                    # the whole lineage again, committed part included
+                    spans = []
+                    if ctx.committed_tokens:
+                        spans.append((list(ctx.committed_tokens), list(ctx.committed_positions), 0))
+                    if ctx.tokens:
+                        spans.append((list(ctx.tokens), list(ctx.positions), len(ctx.chain) * ps))
+                    ctx._pending_replay = spans
+                    self.counters["replayed_tokens"] += sum(len(sp[0]) for sp in spans)
+                rs_reset = 1 if rs.flags_for_pass(cid) else 0
             ctx.pins += 1
             ctx.state = State.PINNED
             pages = self._store(ctx).physical_ids(ctx.chain) + list(ctx.working_pages)
-            return PinnedContext(cid, pages, kv_len, ctx.driver)
+            return PinnedContext(cid, pages, kv_len, ctx.driver, rs_slot if rs_slot is not None else -1, rs_reset)
+
+    def _rs_victim(self, requester: Context) -> Optional[Context]:
+        """An unpinned context whose recurrent-state slot may be taken (lowest rank first)."""
+        rs = self.rs[requester.driver]
+        cands = [c for c in self.contexts.values() if c.driver == requester.driver and c.pins == 0
+                 and c is not requester and c.id in rs.slot_of]
+        return min(cands, key=self._rank) if cands else None
 
     def unpin(self, cid: int) -> None:
         with self.lock:
@@ -497,6 +545,7 @@ class ContextManager:
             ctx._chain_resident = store.would_free(ctx.chain) == 0
             store.release(ctx.chain)
             ctx.state = State.SUSPENDED
+            self.rs[ctx.driver].release(cid)
             self.counters["suspended"] += 1
 
     def _ensure_resident(self, ctx: Context) -> None:
@@ -543,6 +592,9 @@ class ContextManager:
                 self.counters["replayed_tokens"] += len(ctx.tokens)
             ctx.state = State.ACTIVE
             self.counters["restored"] += 1
+            if self.rs[ctx.driver].supported and (ctx.committed_tokens or ctx.tokens):
+                # the recurrent state went with the slot: the next pin plans a replay of the whole lineage
+                replay = []
             ctx._pending_replay = replay
             return replay
 

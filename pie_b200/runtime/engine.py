@@ -109,7 +109,9 @@ class Engine:
         def copy_fn(driver_idx: int, req: CopyRequest) -> None:
             entry.drivers[driver_idx].copy(req)
 
-        entry.ctxm = ContextManager(name, entry.page_size, stores, copy_fn, swap_pages=swap)
+        entry.ctxm = ContextManager(name, entry.page_size, stores, copy_fn, swap_pages=swap,
+                                    rs_slots=[c.rs_cache_slots for c in entry.caps],
+                                    rs_copy_fn=lambda d, src, dst: entry.drivers[d].copy_rs(src, dst))
         from .adapter import AdapterService
         entry.adapters = AdapterService(entry.drivers, self.config.adapter_dir)
         for i, (drv, caps) in enumerate(zip(entry.drivers, entry.caps)):
@@ -117,12 +119,16 @@ class Engine:
                                    name=f"pie-sched-{name}-{i}")
             sched.expected_cohort = entry.ctxm.pinned_count
             sched.delivery_guard = entry.ctxm.lock
-            sched.cohort = DecodeCohort(entry.ctxm, entry.page_size, caps.max_forward_requests)
+            # the array-form decode cohort does not carry recurrent-state slots: such models step per request
+            sched.cohort = (DecodeCohort(entry.ctxm, entry.page_size, caps.max_forward_requests)
+                            if not caps.rs_cache_slots and hasattr(drv, "decode_async") else None)
             entry.schedulers.append(sched)
         entry.inference = InferenceService(entry.ctxm, entry.schedulers, self.config.speculation_depth)
-        entry.inference.cohorts = [s.cohort for s in entry.schedulers]
+        entry.inference.cohorts = [s.cohort for s in entry.schedulers] if all(
+            s.cohort is not None for s in entry.schedulers) else []
         for s in entry.schedulers:
-            s.cohort.on_finish = lambda st, e=entry: self._charge(e, st.ctx_id, getattr(st, "kept", 0))
+            if s.cohort is not None:
+                s.cohort.on_finish = lambda st, e=entry: self._charge(e, st.ctx_id, getattr(st, "kept", 0))
         entry.inference.on_tokens = lambda cid, n, e=entry: self._charge(e, cid, n)
         entry.market = Market(sum(c.total_pages for c in entry.caps), self.config.default_endowment_pages,
                               self.config.admission_oversubscription_factor)

@@ -241,13 +241,18 @@ class InferenceService:
         sched = self.schedulers[pinned.driver]
         spans = list(spans)
 
+        reset = [pinned.rs_reset]        # the first replayed span starts the recurrent state over
+
         def step(_res=None):
             if isinstance(_res, Exception) or not spans:
                 then()
                 return
             toks, poss, first = spans.pop(0)
             sched.submit(PendingRequest(context_id=cid, tokens=toks, positions=poss, pages=pinned.pages,
-                                        kv_len=first, samplers=[], on_done=step))
+                                        kv_len=first, samplers=[], on_done=step, rs_slot=pinned.rs_slot,
+                                        rs_reset=reset[0]))
+            reset[0] = 0
+        pinned.rs_reset = 0                # ... and the pass that follows the replay continues from it
         step()
 
     def _queue(self, sched, cid, pinned, tokens, positions, samplers, masks, logit_mask, n_spec, adapter,
@@ -258,7 +263,8 @@ class InferenceService:
 
         sched.submit(PendingRequest(context_id=cid, tokens=tokens, positions=positions, pages=pinned.pages,
                                     kv_len=pinned.kv_len, samplers=list(samplers), masks=masks,
-                                    logit_mask=logit_mask, spec_count=n_spec, adapter=adapter, on_done=on_done))
+                                    logit_mask=logit_mask, spec_count=n_spec, adapter=adapter, on_done=on_done,
+                                    rs_slot=pinned.rs_slot, rs_reset=pinned.rs_reset))
 
     def _on_done(self, cid, tokens, positions, samplers, masks, logit_mask, n_spec, n_plain, speculate, fut,
                  staged, result) -> None:

@@ -43,6 +43,8 @@ class PendingRequest:
     logit_mask: Optional[list] = None     # BRLE over the vocabulary
     spec_count: int = 0                   # trailing input tokens that are unverified drafts
     adapter: int = -1
+    rs_slot: int = -1                     # recurrent-state slot of the context (models with linear layers)
+    rs_reset: int = 0                     # 1: the slot starts from zero in this pass
     on_done: Optional[Callable] = None    # called with (list[SlotOutput] | Exception)
     t_submit: float = 0.0
     chunk_of: Optional["_ChunkState"] = None
@@ -161,6 +163,8 @@ def fold(items: Sequence[PendingRequest], page_size: int, trim: bool = True) -> 
     spec = np.zeros(r, dtype=np.int32)
     ctx_ids = np.zeros(r, dtype=np.uint64)
     adapters = np.full(r, -1, dtype=np.int64)
+    rs_slots = np.full(r, -1, dtype=np.int32)
+    rs_reset = np.zeros(r, dtype=np.int32)
     single = True
     trimmed = 0
     for i, it in enumerate(items):
@@ -195,6 +199,7 @@ def fold(items: Sequence[PendingRequest], page_size: int, trim: bool = True) -> 
         spec[i] = it.spec_count
         ctx_ids[i] = it.context_id
         adapters[i] = it.adapter
+        rs_slots[i], rs_reset[i] = it.rs_slot, it.rs_reset
     cat = lambda xs: np.concatenate(xs) if xs else np.zeros(0, dtype=np.int32)
     any_mask = bool(has_mask.any())
     return ForwardRequest(
@@ -205,7 +210,8 @@ def fold(items: Sequence[PendingRequest], page_size: int, trim: bool = True) -> 
         logit_masks=logit_masks if any(m is not None for m in logit_masks) else None,
         slot_req=np.asarray(slot_req, dtype=np.int32), slot_row=np.asarray(slot_row, dtype=np.int32),
         slot_samplers=samplers, spec_counts=spec if spec.any() else None, context_ids=ctx_ids,
-        adapter_ids=adapters, single_token_mode=single, trimmed_pages=trimmed)
+        adapter_ids=adapters, single_token_mode=single, trimmed_pages=trimmed,
+        rs_slots=rs_slots if (rs_slots >= 0).any() else None, rs_reset=rs_reset if (rs_slots >= 0).any() else None)
 
 
 # ------------------------------------------------------------------------------ policies
@@ -352,7 +358,8 @@ class BatchScheduler:
         return PendingRequest(
             context_id=p.context_id, tokens=p.tokens[a:b], positions=p.positions[a:b], pages=p.pages,
             kv_len=p.kv_len + a, samplers=samplers, masks=None if p.masks is None else p.masks[a:b],
-            logit_mask=p.logit_mask, adapter=p.adapter, chunk_of=st, t_submit=p.t_submit)
+            logit_mask=p.logit_mask, adapter=p.adapter, chunk_of=st, t_submit=p.t_submit,
+            rs_slot=p.rs_slot, rs_reset=p.rs_reset if a == 0 else 0)
 
     # ---- consumer side
     def _admit(self, r: PendingRequest) -> bool:
