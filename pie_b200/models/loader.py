@@ -157,6 +157,28 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
     att["lm_head"] = Shard(head, 0, r, T)
     for li in range(cfg.num_hidden_layers):
         L, P = f"{pre}layers.{li}.", f"layers.{li}."
+        if cfg.is_linear_layer(li):
+            # Gated DeltaNet layer. The checkpoint groups the fused projections by key head:
+            # in_proj_qkvz rows = per key head [q (dk), k (dk), v (rep * dv), z (rep * dv)], in_proj_ba rows = per
+            # key head [b (rep), a (rep)]; the runtime wants q | k | v | z | b | a, each over all heads.
+            if T > 1:
+                raise NotImplementedError("Gated DeltaNet layers under tensor parallelism")
+            X = L + "linear_attn."
+            hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+            dk, dv, rep = cfg.linear_key_head_dim, cfg.linear_value_head_dim, hv // hk
+            G, qkvz, ba = 2 * dk + 2 * rep * dv, w(X + "in_proj_qkvz.weight"), w(X + "in_proj_ba.weight")
+            parts = ([Rows(qkvz, g * G, dk) for g in range(hk)] + [Rows(qkvz, g * G + dk, dk) for g in range(hk)]
+                     + [Rows(qkvz, g * G + 2 * dk, rep * dv) for g in range(hk)]
+                     + [Rows(qkvz, g * G + 2 * dk + rep * dv, rep * dv) for g in range(hk)]
+                     + [Rows(ba, g * 2 * rep, rep) for g in range(hk)] + [Rows(ba, g * 2 * rep + rep, rep) for g in range(hk)])
+            att[P + "w_gdn_in"] = Concat(parts, 0)
+            att[P + "gdn_conv"] = Op("squeeze", {"dim": 1}, [w(X + "conv1d.weight")])
+            att[P + "gdn_A_log"], att[P + "gdn_dt_bias"] = Op("float", {}, [w(X + "A_log")]), Op("float", {}, [w(X + "dt_bias")])
+            att[P + "gdn_norm"], att[P + "w_gdn_out"] = w(X + "norm.weight"), w(X + "out_proj.weight")
+            att[P + "ln1"], att[P + "ln2"] = w(L + "input_layernorm.weight"), w(L + "post_attention_layernorm.weight")
+            QLin.interleave(lin(L + "mlp.gate_proj.weight"), lin(L + "mlp.up_proj.weight")).attach(att, P + "w_gate_up")
+            lin(L + "mlp.down_proj.weight").attach(att, P + "w_down")
+            continue
         if cfg.post_norm:       # OLMo-2: norms follow the sub-blocks, there is no input norm
             att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
             att[P + "ln3"] = w(L + "post_feedforward_layernorm.weight")
@@ -300,6 +322,10 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
         return torch.stack(xs, dim=0)
     if k == "zeros_like":
         return torch.zeros_like(xs[0])
+    if k == "squeeze":
+        return xs[0].squeeze(op.args["dim"])
+    if k == "float":
+        return xs[0].float()
     if k == "transpose":
         return xs[0].transpose(op.args["a"], op.args["b"])
     if k == "mxfp4":
@@ -470,6 +496,22 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
         t["lm_head.weight"] = weights["lm_head"]
     for li, lw in enumerate(weights["layers"]):
         L = f"model.layers.{li}."
+        if "w_gdn_in" in lw:
+            X = L + "linear_attn."
+            hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+            dk, dv, rep = cfg.linear_key_head_dim, cfg.linear_value_head_dim, hv // hk
+            q, k, v, z, b, a = lw["w_gdn_in"].split([hk * dk, hk * dk, hv * dv, hv * dv, hv, hv], 0)
+            grp = lambda x, n: x.reshape(hk, n, -1)
+            t[X + "in_proj_qkvz.weight"] = torch.cat([grp(q, dk), grp(k, dk), grp(v, rep * dv), grp(z, rep * dv)], 1
+                                                     ).reshape(-1, cfg.hidden_size)
+            t[X + "in_proj_ba.weight"] = torch.cat([grp(b, rep), grp(a, rep)], 1).reshape(-1, cfg.hidden_size)
+            t[X + "conv1d.weight"] = lw["gdn_conv"].unsqueeze(1)
+            t[X + "A_log"], t[X + "dt_bias"] = lw["gdn_A_log"], lw["gdn_dt_bias"]
+            t[X + "norm.weight"], t[X + "out_proj.weight"] = lw["gdn_norm"], lw["w_gdn_out"]
+            t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
+            t[L + "mlp.gate_proj.weight"], t[L + "mlp.up_proj.weight"] = lw["w_gate_up"][0::2], lw["w_gate_up"][1::2]
+            t[L + "mlp.down_proj.weight"] = lw["w_down"]
+            continue
         if "ln3" in lw:
             t[L + "post_attention_layernorm.weight"], t[L + "post_feedforward_layernorm.weight"] = lw["ln2"], lw["ln3"]
         else:
@@ -511,6 +553,10 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
         hf.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   sliding_window=cfg.sliding_window, layer_types=cfg.layer_types, swiglu_limit=cfg.swiglu_limit,
                   rope_scaling=cfg.rope_scaling)
+    elif cfg.linear_layers:
+        hf.update(layer_types=cfg.layer_types, linear_num_key_heads=cfg.linear_num_key_heads,
+                  linear_num_value_heads=cfg.linear_num_value_heads, linear_key_head_dim=cfg.linear_key_head_dim,
+                  linear_value_head_dim=cfg.linear_value_head_dim, linear_conv_kernel_dim=cfg.linear_conv_kernel_dim)
     elif cfg.is_moe:
         hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)

@@ -98,7 +98,7 @@ class InferenceService:
         self.cohorts: list = []       # DecodeCohort per driver (set by the engine)
         self.staged: Dict[int, _Staged] = {}
         self.lock = threading.Lock()
-        self.max_defers = 8          # times one request may wait in the restore queue before it fails
+        self.max_defers = 64         # times one request may wait (restore queue, slot shortage) before it fails
         self.stats = {"submits": 0, "bypass_hits": 0, "chain_submits": 0, "chain_drops": 0,
                       "tokens_appended": 0}
         self.on_tokens: Optional[Callable[[int, int], None]] = None   # (context id, n tokens) accounting hook
@@ -215,10 +215,16 @@ class InferenceService:
                 return
             fut._defer_tries = tries + 1
             self.stats["deferred_starts"] = self.stats.get("deferred_starts", 0) + 1
+            retry = lambda: self._start(cid, tokens, positions, samplers, masks, logit_mask, spec_tokens,
+                                        spec_positions, adapter, speculate, fut, staged)
             try:
-                self.ctxm.when_restorable(cid, lambda: self._start(cid, tokens, positions, samplers, masks, logit_mask,
-                                                                   spec_tokens, spec_positions, adapter, speculate,
-                                                                   fut, staged))
+                ctx = self.ctxm.contexts.get(cid)
+                if ctx is not None and ctx.state.value != "suspended":
+                    # resident but short of something another context holds (a recurrent-state slot, pages):
+                    # try again when a context is unpinned or gives pages back
+                    self.ctxm.on_pages_freed(ctx.driver, retry)
+                else:
+                    self.ctxm.when_restorable(cid, retry)
             except ContextError as e2:
                 fut.set(exc=e2)
             return
@@ -358,6 +364,8 @@ class InferenceService:
         """Eligibility: exactly one token-sampler slot at the last input row, no masks, no drafts."""
         if masks is not None or logit_mask is not None or n_spec or len(samplers) != 1:
             return
+        if any(rs.supported for rs in self.ctxm.rs):
+            return  # a staged pass that is later abandoned would already have advanced the recurrent state
         idx, sp = samplers[0]
         if idx != len(tokens) - 1 or not sp.is_token or out.slots[0].kind != "token":
             return

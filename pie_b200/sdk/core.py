@@ -579,6 +579,10 @@ class Generator:
         # a run of accepted drafts already has KV for all but its last token
         self._pending = out[-1:] if out else None
         if self._done:
+            # the last sampled token has no KV yet: it stays pending in the context, as after a
+            # runtime-driven loop, so that a later fill or generate continues from the full text
+            if self._pending:
+                self.ctx._buffer.extend(self._pending)
             self._pending = None
         return out
 

@@ -175,3 +175,32 @@ def test_forked_contexts_decode_through_the_cascade_plan(monkeypatch):
         for x, y in zip(a, b):
             assert np.abs(x - y).max() < 0.05 * max(1.0, np.abs(y).max())
             assert int(x.argmax()) == int(y.argmax())
+
+
+def test_gdn_hybrid_driver_matches_dense_oracle():
+    """Gated DeltaNet hybrid on the GPU driver: chunked prefill + decode over recurrent-state slots against the
+    dense fp32 oracle of the same (bf16-rounded) weights."""
+    from pie_b200.driver.schema import ForwardRequest, SamplerKind, SamplerSpec
+    from pie_b200.models.transformer import dense_reference_forward
+    cfg = preset("tiny-qwen3.5")
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=4)
+    drv = TorchDriver(cfg, "cuda", weights=w, num_pages=32, page_size=16, max_requests=4, max_tokens=128)
+    wf = {"layers": [{k: v.float().cpu() for k, v in lw.items()} for lw in w["layers"]],
+          **{k: v.float().cpu() for k, v in w.items() if k != "layers"}}
+    toks = list(range(60, 60 + 45))
+    want = dense_reference_forward(cfg, wf, torch.tensor(toks)).numpy()
+    i32 = lambda *a: np.asarray(a, dtype=np.int32)
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+
+    def fire(tk, start, reset):
+        n, kv = len(tk), start + len(tk)
+        req = ForwardRequest(tokens=np.asarray(tk, np.int32), positions=np.arange(start, kv, dtype=np.int32), qo_indptr=i32(0, n),
+                             kv_page_indices=np.arange(-(-kv // 16), dtype=np.int32), kv_page_indptr=i32(0, -(-kv // 16)),
+                             kv_last_page_lens=i32((kv - 1) % 16 + 1), slot_req=i32(0), slot_row=i32(n - 1),
+                             slot_samplers=[raw], rs_slots=i32(1), rs_reset=i32(reset))
+        return np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
+    for a, b, reset in ((0, 20, 1), (20, 44, 0), (44, 45, 0)):
+        got = fire(toks[a:b], a, reset)
+        ref_row = want[b - 1]
+        cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
+        assert cos > 0.995 and int(got.argmax()) == int(ref_row.argmax()), (a, b, cos)

@@ -561,3 +561,37 @@ def test_index_validator_records_the_first_bad_entry_and_touches_nothing():
     torch.cuda.synchronize()
     with pytest.raises(_lib.KernelLibraryError, match=r"tokens\[3\]"):
         ops.check_kernel_status(DEV)
+
+
+@pytest.mark.parametrize("dk,dv,hk,hv", [(32, 32, 2, 4), (64, 64, 2, 2), (128, 128, 2, 4)])
+def test_gdn_mixer_matches_reference_over_chunks(dk, dv, hk, hv):
+    """Gated DeltaNet mixer kernels (short convolution with slot tails, token-serial delta rule, gated norm)
+    against the fp32 reference: a ragged batch, then a second fire that continues from the cached state."""
+    from types import SimpleNamespace
+    from pie_b200.driver.recurrent import RecurrentStateCache
+    from pie_b200.models.config import ModelConfig
+    torch.manual_seed(dk + hv)
+    cfg = ModelConfig(model_type="qwen3_5", num_hidden_layers=1, layer_types=["linear_attention"], linear_num_key_heads=hk,
+                      linear_num_value_heads=hv, linear_key_head_dim=dk, linear_value_head_dim=dv)
+    c, f = cfg.gdn_conv_channels, cfg.gdn_in_features
+    lw_f = {"gdn_conv": torch.randn(c, 4) * 0.3, "gdn_A_log": torch.randn(hv) * 0.5, "gdn_dt_bias": torch.randn(hv) * 0.5,
+            "gdn_norm": 1 + torch.randn(dv) * 0.1}
+    lw_f = {k: v.to(torch.bfloat16).float() if k in ("gdn_conv", "gdn_norm") else v for k, v in lw_f.items()}
+    lw_d = {k: (v.to(DEV).to(torch.bfloat16) if k in ("gdn_conv", "gdn_norm") else v.to(DEV)) for k, v in lw_f.items()}
+    dev_cache, cpu_cache = RecurrentStateCache(cfg, 6, DEV), RecurrentStateCache(cfg, 6, "cpu")
+    for lens, reset in (([5, 1, 37, 2], [1, 1, 1, 1]), ([1, 3, 1, 40], [0, 0, 0, 0]), ([2, 1, 1, 1], [1, 0, 0, 0])):
+        qo = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        slots = np.asarray([4, 0, 2, 5], np.int32)
+        mix = (torch.randn(int(qo[-1]), f) * 1.5).to(torch.bfloat16)
+        want = ref.gdn_mixer(mix.float(), lw_f["gdn_conv"], lw_f["gdn_A_log"], lw_f["gdn_dt_bias"], lw_f["gdn_norm"], 1e-5,
+                             hk, hv, dk, dv, qo.tolist(), cpu_cache.conv_state[0], cpu_cache.rec_state[0],
+                             slots.tolist(), reset)
+        got = ops.gdn_mixer(mix.to(DEV), lw_d, cfg, dev_cache.inputs(qo, slots, np.asarray(reset, np.int32)), 0)
+        torch.cuda.synchronize()
+        close(got, want, 3e-2)
+        assert torch.allclose(dev_cache.rec_state.cpu(), cpu_cache.rec_state, atol=2e-2, rtol=2e-2)
+        assert torch.allclose(dev_cache.conv_state.cpu(), cpu_cache.conv_state, atol=1e-6)
+    dev_cache.copy_slot(4, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(dev_cache.rec_state[:, 1], dev_cache.rec_state[:, 4])
+    assert torch.equal(dev_cache.conv_state[:, 1], dev_cache.conv_state[:, 4])
