@@ -588,7 +588,7 @@ def test_gdn_mixer_matches_reference_over_chunks(dk, dv, hk, hv):
                              slots.tolist(), reset)
         got = ops.gdn_mixer(mix.to(DEV), lw_d, cfg, dev_cache.inputs(qo, slots, np.asarray(reset, np.int32)), 0)
         torch.cuda.synchronize()
-        close(got, want, 3e-2)
+        close(got.cpu(), want, 3e-2)
         assert torch.allclose(dev_cache.rec_state.cpu(), cpu_cache.rec_state, atol=2e-2, rtol=2e-2)
         assert torch.allclose(dev_cache.conv_state.cpu(), cpu_cache.conv_state, atol=1e-6)
     dev_cache.copy_slot(4, 1)
