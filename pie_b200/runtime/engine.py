@@ -71,6 +71,7 @@ class Engine:
         self.log = logging.getLogger("pie_b200")
         self.models: Dict[str, ModelEntry] = {}
         self.programs: Dict[str, Callable] = {}
+        self.confined_programs: set = set()
         self.manifests: Dict[str, dict] = {}
         self.processes: Dict[str, Process] = {}
         self.messaging: Messaging = None
@@ -166,7 +167,14 @@ class Engine:
         return self.models[name]
 
     # ------------------------------------------------------------------ programs / processes
-    def register_program(self, name: str, entry: Callable, manifest: Optional[dict] = None) -> None:
+    def register_program(self, name: str, entry: Callable, manifest: Optional[dict] = None,
+                         confined: bool = False) -> None:
+        """`confined`: the program did not ship with the package (upload, disk cache): its processes run under
+        the audit-hook confinement of `runtime/policy.py`."""
+        if confined:
+            self.confined_programs.add(name)
+        else:
+            self.confined_programs.discard(name)
         self.programs[name] = entry
         self.manifests[name] = manifest or {"package": {"name": name, "version": "0.1.0"}}
 

@@ -110,7 +110,12 @@ class Process:
                 await eng.admit_process(self)
                 self.fs_policy = FsPolicy(eng.config.fs_policy, eng.config.scratch_root)
                 self.network_policy = NetworkPolicy(list(eng.config.network_allow))
-                result = await self.entry(self.input)
+                if self.program in getattr(eng, "confined_programs", ()):
+                    from .policy import Confinement, confine
+                    with confine(Confinement(self.program, network=self.network_policy, process=self)):
+                        result = await self.entry(self.input)
+                else:
+                    result = await self.entry(self.input)
             if result is not None and not isinstance(result, str):
                 result = json.dumps(result)
             self.result = result if result is not None else ""

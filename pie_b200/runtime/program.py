@@ -124,8 +124,11 @@ def content_hash(data: bytes) -> str:
 
 
 def compile_program(name: str, source: str) -> Callable:
+    """Run the module body of an uploaded program (confined: it may import, nothing else) and return `main`."""
+    from .policy import Confinement, confine
     ns: Dict[str, Any] = {"__name__": f"pie_program_{name.replace('-', '_')}"}
-    exec(compile(source, f"<inferlet {name}>", "exec"), ns)   # noqa: S102 - programs are the product's plugins
+    with confine(Confinement(name)):
+        exec(compile(source, f"<inferlet {name}>", "exec"), ns)   # noqa: S102 - programs are the product's plugins
     if "main" not in ns or not asyncio.iscoroutinefunction(ns["main"]):
         raise ProgramError("an inferlet must define `async def main(input)`")
     return ns["main"]
@@ -159,16 +162,18 @@ class ProgramStore:
                 raise ProgramError(f"{manifest.name} needs {dep}@{ver}, which is not installed")
         entry = compile_program(manifest.name, source)
         if self.dir and persist:
-            d = self.dir / manifest.name
-            d.mkdir(parents=True, exist_ok=True)
-            (d / f"{manifest.version}.py").write_bytes(data)
-            (d / f"{manifest.version}.toml").write_text(manifest.to_toml())
+            from .policy import trusted
+            with trusted():                        # an inferlet may install a child program: the store writes for it
+                d = self.dir / manifest.name
+                d.mkdir(parents=True, exist_ok=True)
+                (d / f"{manifest.version}.py").write_bytes(data)
+                (d / f"{manifest.version}.toml").write_text(manifest.to_toml())
         self.installed.setdefault(manifest.name, {})[manifest.version] = manifest
         if self.engine is not None:
             wrapped = self._wrap(entry, manifest)
-            self.engine.register_program(f"{manifest.name}@{manifest.version}", wrapped, manifest)
+            self.engine.register_program(f"{manifest.name}@{manifest.version}", wrapped, manifest, confined=True)
             if manifest.version == self.latest(manifest.name):
-                self.engine.register_program(manifest.name, wrapped, manifest)
+                self.engine.register_program(manifest.name, wrapped, manifest, confined=True)
         return h
 
     @staticmethod

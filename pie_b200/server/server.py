@@ -39,11 +39,12 @@ QUERY_MODEL_STATUS = "model_status"
 
 def load_program_source(engine: Engine, name: str, source: str, manifest: Optional[dict] = None) -> None:
     """Register a native inferlet from Python source (must define `async def main(input)`)."""
-    ns: Dict[str, Any] = {"__name__": f"pie_program_{name.replace('-', '_')}"}
-    exec(compile(source, f"<inferlet {name}>", "exec"), ns)   # noqa: S102 - programs are the product's plugins
-    if "main" not in ns or not asyncio.iscoroutinefunction(ns["main"]):
-        raise ValueError("an inferlet must define `async def main(input)`")
-    engine.register_program(name, ns["main"], manifest)
+    from ..runtime.program import ProgramError, compile_program
+    try:
+        entry = compile_program(name, source)
+    except ProgramError as e:
+        raise ValueError(str(e)) from None
+    engine.register_program(name, entry, manifest, confined=True)
 
 
 class Session:
