@@ -72,6 +72,7 @@ class Engine:
         self.models: Dict[str, ModelEntry] = {}
         self.programs: Dict[str, Callable] = {}
         self.confined_programs: set = set()
+        self.program_resolver: Optional[Callable[[str], bool]] = None   # called for programs that are not registered
         self.manifests: Dict[str, dict] = {}
         self.processes: Dict[str, Process] = {}
         self.messaging: Messaging = None
@@ -181,6 +182,8 @@ class Engine:
     def launch(self, program: str, input_value: Any = None, username: str = "local",
                capture_outputs: bool = True, token_budget: Optional[int] = None,
                parent: Optional[str] = None, listener: Optional[Callable] = None) -> Process:
+        if program not in self.programs and program.split("@")[0] not in self.programs and self.program_resolver:
+            self.program_resolver(program)       # e.g. the program store's registry download
         if program not in self.programs:
             base = program.split("@")[0]
             if base not in self.programs:

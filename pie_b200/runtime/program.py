@@ -1,7 +1,8 @@
 """Program manager: installs inferlet programs (source + manifest), keeps a disk cache
 `<dir>/<name>/<version>.py` + `.toml`, checks content hashes, resolves `name@version`, and
-registers entry points with the engine. A registry URL can be configured but is only used when
-the program is not in the cache (there is no network in most deployments).
+registers entry points with the engine. With a registry URL, a program that is neither registered nor
+in the cache is downloaded on first use (`<registry>/api/v1/inferlets/<name>/<version>/download`: a zip
+of `Pie.toml` and `main.py`, its content hash in the `X-Content-Hash` header when the registry sends one).
 
 Manifest (`Pie.toml`):
     [package]      name, version, description, authors
@@ -184,6 +185,48 @@ class ProgramStore:
         async def main(value):
             return await entry(manifest.check_input(value))
         return main
+
+    def fetch(self, name: str, version: str = "latest", timeout: float = 30.0) -> str:
+        """Download `name@version` from the registry and install it; returns `name@version` as installed."""
+        import io
+        import urllib.error
+        import urllib.request
+        import zipfile
+        if not self.registry_url:
+            raise ProgramError(f"program {name!r} is not installed and no registry is configured")
+        if not re.fullmatch(r"[A-Za-z0-9][A-Za-z0-9_.-]*", name) or not re.fullmatch(r"[A-Za-z0-9_.+^*-]+", version):
+            raise ProgramError(f"bad program reference {name}@{version}")
+        url = f"{self.registry_url.rstrip('/')}/api/v1/inferlets/{name}/{version}/download"
+        from .policy import trusted
+        with trusted():                         # an inferlet may launch a program the engine has to fetch first
+            try:
+                with urllib.request.urlopen(urllib.request.Request(url, headers={"User-Agent": "pie_b200"}),
+                                            timeout=timeout) as r:
+                    blob, want = r.read(), r.headers.get("X-Content-Hash", "")
+            except urllib.error.HTTPError as e:
+                raise ProgramError(f"registry has no {name}@{version} ({e.code})") from None
+            except OSError as e:
+                raise ProgramError(f"registry {self.registry_url} unreachable: {e}") from None
+        try:
+            with zipfile.ZipFile(io.BytesIO(blob)) as z:
+                manifest = Manifest.parse(z.read("Pie.toml").decode("utf-8"))
+                source = z.read("main.py").decode("utf-8")
+        except (zipfile.BadZipFile, KeyError) as e:
+            raise ProgramError(f"registry sent a bad package for {name}@{version}: {e}") from None
+        if manifest.name != name:
+            raise ProgramError(f"registry sent {manifest.name!r} for {name!r}")
+        self.install(source, manifest, expected_hash=want)
+        return f"{manifest.name}@{manifest.version}"
+
+    def ensure(self, ref: str) -> bool:
+        """Make `name[@version]` launchable: already registered, or fetched from the registry now."""
+        name, _, version = ref.partition("@")
+        if self.resolve(name, version) is not None:
+            return True
+        if not self.registry_url:
+            return False
+        self.fetch(name, version or "latest")
+        return True
 
     def install_dir(self, path: str) -> str:
         """Install from a directory holding Pie.toml and main.py (or <name>.py)."""

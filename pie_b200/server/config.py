@@ -52,6 +52,7 @@ class RuntimeConfig:
     admission_oversubscription_factor: float = 4.0
     restore_pause_at_utilization: float = 0.85
     program_dir: str = "~/.pie_b200/programs"
+    registry_url: str = ""                  # programs that are not installed are fetched from here on first use
     allow_network: List[str] = field(default_factory=list)     # CIDR[:port] allow-list for inferlets
     allow_fs: bool = True                                      # per-process scratch directory
 

@@ -221,7 +221,7 @@ def start_engine(cfg: Config, serve: bool = True, port: Optional[int] = None) ->
     server = None
     if serve:
         server = PieServer(engine, cfg.server.host, cfg.server.port if port is None else port, auth,
-                           rt.program_dir, cfg.server.max_message_bytes,
+                           rt.program_dir, cfg.server.max_message_bytes, registry_url=rt.registry_url,
                            allow_program_upload=cfg.server.allow_program_upload)
         server.start()
     return EngineHandle(engine, server, auth, comms)

@@ -281,7 +281,7 @@ class Session:
 
 class PieServer:
     def __init__(self, engine: Engine, host: str = "127.0.0.1", port: int = 8080, auth: Optional[Authenticator] = None,
-                 program_dir: Optional[str] = None, max_message_bytes: int = 64 << 20,
+                 program_dir: Optional[str] = None, max_message_bytes: int = 64 << 20, registry_url: str = "",
                  allow_program_upload: bool = False):
         self.engine, self.host, self.port = engine, host, port
         # Programs are native Python and run in this process with its privileges; uploads (and the
@@ -297,7 +297,9 @@ class PieServer:
         self._server = None
         self._thread: Optional[threading.Thread] = None
         self._ready = threading.Event()
-        self.store = ProgramStore(engine, str(self.program_dir) if self.program_dir else None)
+        self.store = ProgramStore(engine, str(self.program_dir) if self.program_dir else None, registry_url)
+        if registry_url:
+            engine.program_resolver = self.store.ensure
         self._load_stored_programs()
 
     def _load_stored_programs(self) -> None:

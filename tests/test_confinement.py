@@ -137,3 +137,55 @@ return json.dumps({{"kid": p.result, "generated": len(gen["tokens"])}})
     r = run(eng, "parent")
     assert r == {"kid": "child says hi", "generated": 4}
     assert (tmp_path / "programs" / "kid" / "0.1.0.py").exists() and "kid" in eng.confined_programs
+
+
+def test_programs_are_fetched_from_the_registry_on_first_use(tmp_path):
+    """`launch` of a program that is neither registered nor cached downloads it from the registry
+    (runtime/src/program/repository.rs:19-45): zip of Pie.toml + main.py, hash header checked, cached on disk,
+    and the fetched program runs confined like any other upload."""
+    import io
+    import zipfile
+    from pie_b200.runtime.program import ProgramError, content_hash
+    src = "async def main(args):\n    return 'from the registry: ' + str(args.get('x'))\n"
+    buf = io.BytesIO()
+    with zipfile.ZipFile(buf, "w") as z:
+        z.writestr("Pie.toml", '[package]\nname = "remote-hello"\nversion = "1.2.0"\n')
+        z.writestr("main.py", src)
+    hits = []
+
+    class Registry(http.server.BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            hits.append(self.path)
+            if self.path in ("/api/v1/inferlets/remote-hello/latest/download", "/api/v1/inferlets/remote-hello/1.2.0/download"):
+                self.send_response(200)
+                self.send_header("Content-Length", str(len(buf.getvalue())))
+                self.send_header("X-Content-Hash", "bad" if "tampered" in self.headers.get("User-Agent", "") else
+                                 content_hash(src.encode()))
+                self.end_headers()
+                self.wfile.write(buf.getvalue())
+            else:
+                self.send_error(404)
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Registry)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    e = Engine(EngineConfig())
+    e.add_model("mock", MockDriver(CounterBehavior(), total_pages=64))
+    try:
+        store = ProgramStore(e, str(tmp_path / "programs"), f"http://127.0.0.1:{srv.server_address[1]}")
+        e.program_resolver = store.ensure
+        assert e.run("remote-hello", {"x": 7}, 30) == "from the registry: 7"
+        assert e.run("remote-hello@1.2.0", {"x": 8}, 30) == "from the registry: 8"
+        assert hits == ["/api/v1/inferlets/remote-hello/latest/download"]            # fetched once, then local
+        assert (tmp_path / "programs" / "remote-hello" / "1.2.0.py").read_text() == src
+        assert "remote-hello" in e.confined_programs
+        with pytest.raises(ProgramError, match="404"):
+            store.fetch("no-such-program")
+        with pytest.raises(ProgramError, match="bad program reference"):
+            store.fetch("../etc/passwd")
+        with pytest.raises(ProgramError, match="registry has no"):
+            e.launch("no-such-program")
+    finally:
+        e.shutdown()
+        srv.shutdown()
