@@ -119,7 +119,11 @@ def _build_drivers_direct(m: ModelSection):
         dev = torch.device("cuda", groups[0][rank])
         torch.cuda.set_device(dev)
         if not dist.is_initialized():
-            dist.init_process_group("nccl", device_id=dev)
+            # a rank that died ends the others' next collective with an error after this long (the control ring
+            # notices sooner: PIE_TP_ACK_TIMEOUT_S), instead of the library's ten-minute default
+            import datetime
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(
+                seconds=float(os.environ.get("PIE_TP_COLLECTIVE_TIMEOUT_S", "120"))))
         comm = TPComm(rank, world, dev, fused=d.tp_backend == "fused")
         par = ParallelContext(world, rank, comm, ep=d.expert_parallel)
         if m.path:
