@@ -336,6 +336,110 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
     raise ValueError(f"unknown op {k}")
 
 
+# ----------------------------------------------------------------------------- type check
+class LoaderTypeError(ValueError):
+    """The checkpoint's tensor shapes do not give the shapes the architecture needs."""
+
+
+def infer_shape(op: Op, reader) -> Tuple[int, ...]:
+    """Shape of an expression from the checkpoint's header alone (no tensor bytes are read)."""
+    k = op.kind
+    if k == "read":
+        return tuple(reader.get_slice(op.args["name"]).get_shape())
+    xs = [infer_shape(i, reader) for i in op.inputs]
+    x = xs[0] if xs else ()
+    if k == "shard":
+        ax, wd = op.args["axis"], op.args["world"]
+        if x[ax] % wd:
+            raise LoaderTypeError(f"dimension {ax} of size {x[ax]} does not split over {wd} ranks")
+        return x[:ax] + (x[ax] // wd,) + x[ax + 1:]
+    if k == "rows":
+        a, n = op.args["start"], op.args["count"]
+        if a < 0 or a + n > x[0]:
+            raise LoaderTypeError(f"rows {a}:{a + n} of a tensor with {x[0]} rows")
+        return (n,) + x[1:]
+    if k == "concat":
+        ax = op.args["axis"]
+        for y in xs[1:]:
+            if len(y) != len(x) or any(y[d] != x[d] for d in range(len(x)) if d != ax):
+                raise LoaderTypeError(f"concat of shapes {xs} along {ax}")
+        return x[:ax] + (sum(y[ax] for y in xs),) + x[ax + 1:]
+    if k == "interleave":
+        if xs[0] != xs[1]:
+            raise LoaderTypeError(f"interleave of shapes {xs[0]} and {xs[1]}")
+        return (2 * x[0],) + x[1:]
+    if k == "stack":
+        if any(y != x for y in xs):
+            raise LoaderTypeError(f"stack of unequal shapes {sorted(set(xs))}")
+        return (len(xs),) + x
+    if k in ("zeros_like", "float"):
+        return x
+    if k == "squeeze":
+        d = op.args["dim"]
+        if x[d] != 1:
+            raise LoaderTypeError(f"squeeze of dimension {d} with size {x[d]}")
+        return x[:d] + x[d + 1:]
+    if k == "transpose":
+        a, b = op.args["a"], op.args["b"]
+        y = list(x)
+        y[a], y[b] = y[b], y[a]
+        return tuple(y)
+    if k == "mxfp4":                    # blocks [..., G, 16] packed nibbles -> [..., G * 32]
+        return x[:-2] + (x[-2] * x[-1] * 2,)
+    if k == "expand_rows":
+        rows = reader.get_slice(op.args["like"]).get_shape()[0]
+        return (min(x[0] * op.args["factor"], rows),) + x[1:]
+    raise LoaderTypeError(f"unknown op {k}")
+
+
+def expected_shapes(cfg: ModelConfig, tp_size: int = 1, ep: bool = False) -> Dict[str, Tuple[int, ...]]:
+    """Runtime shapes of one rank's weights, per attachment key (layer keys without the `layers.N.` prefix)."""
+    T, H, d = tp_size, cfg.hidden_size, cfg.head_dim
+    hq = cfg.num_attention_heads // T
+    hkv = max(1, cfg.num_key_value_heads // T)
+    I = (cfg.moe_intermediate_size if cfg.is_moe else cfg.intermediate_size)
+    E = cfg.num_experts
+    el, il = (E // T, I) if (ep and T > 1) else (E, I // T)
+    out = {"embed": (cfg.vocab_size, H), "final_norm": (H,), "lm_head": (cfg.vocab_size // T, H),
+           "ln1": (H,), "ln2": (H,), "ln3": (H,), "wqkv": ((hq + 2 * hkv) * d, H), "wo": (H, hq * d),
+           "bqkv": ((hq + 2 * hkv) * d,), "bo": (H,), "sinks": (hq,),
+           "w_gate_up": (2 * cfg.intermediate_size // T, H), "w_down": (H, cfg.intermediate_size // T),
+           "router": (E, H), "router_bias": (E,), "experts_gate_up": (el, 2 * il, H), "experts_down": (el, H, il),
+           "experts_gate_up_bias": (el, 2 * il), "experts_down_bias": (el, H)}
+    if cfg.linear_layers:
+        hv, dv = cfg.linear_num_value_heads, cfg.linear_value_head_dim
+        out.update({"w_gdn_in": (cfg.gdn_in_features, H), "gdn_conv": (cfg.gdn_conv_channels, cfg.linear_conv_kernel_dim),
+                    "gdn_A_log": (hv,), "gdn_dt_bias": (hv,), "gdn_norm": (dv,), "w_gdn_out": (H, hv * dv)})
+    return out
+
+
+def typecheck_program(prog: Program, cfg: ModelConfig, reader) -> Dict[str, Tuple[int, ...]]:
+    """Infer the shape of every attachment from the checkpoint's header and compare it with what the
+    architecture needs on this rank; all mismatches are reported together, before any tensor is read.
+    Returns the inferred shapes. Counterpart of the weight loader's type checker in the reference
+    (driver/weight_loader/src/typecheck.rs)."""
+    want = expected_shapes(cfg, prog.meta.get("tp_size", 1), prog.meta.get("ep", False))
+    shapes, errors = {}, []
+    for path, op in prog.attach.items():
+        try:
+            shapes[path] = infer_shape(op, reader)
+        except LoaderTypeError as e:
+            errors.append(f"{path}: {e}")
+            continue
+        key = path.split(".", 2)[2] if path.startswith("layers.") else path
+        if key.endswith("@scale"):
+            continue
+        exp = want.get(key)
+        if key in ("q_norm", "k_norm"):
+            continue                               # per head or over all heads, by family
+        if exp is not None and tuple(shapes[path]) != tuple(exp):
+            errors.append(f"{path}: checkpoint gives {tuple(shapes[path])}, the architecture needs {tuple(exp)}")
+    if errors:
+        more = f" (and {len(errors) - 8} more)" if len(errors) > 8 else ""
+        raise LoaderTypeError("checkpoint does not fit the configuration:\n  " + "\n  ".join(errors[:8]) + more)
+    return shapes
+
+
 def execute_program(prog: Program, reader, device="cpu") -> dict:
     """Materialise the runtime weight dict of this rank."""
     dtype = torch_dtype(prog.dtype)
@@ -478,10 +582,12 @@ def load_checkpoint(path, device="cpu", tp_size: int = 1, tp_rank: int = 0, ep: 
         reader = GGUFReader(ggufs[0])
         cfg = reader.config()
         prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)
+        typecheck_program(prog, cfg, reader)
         return cfg, _cached_load(ggufs[0], prog, reader, device)
     cfg = ModelConfig.from_path(path)
     reader = SafetensorsReader(path)
     prog = compile_program(cfg, reader.names(), tp_size, tp_rank, ep, dtype or cfg.dtype)
+    typecheck_program(prog, cfg, reader)
     return cfg, _cached_load(p, prog, reader, device)
 
 

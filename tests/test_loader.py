@@ -514,3 +514,35 @@ def test_olmo3_alternating_window_layers_load_and_match_dense_oracle(tmp_path):
     got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
     want = dense_reference_forward(cfg2, w2, torch.tensor(toks + [7]))[-1].numpy()
     assert np.abs(got - want).max() < 1e-3
+
+
+def test_type_check_reports_every_misfit_before_reading_tensors(tmp_path):
+    """The loader infers every runtime shape from the checkpoint's header and compares it with the
+    configuration: a wrong config fails with the list of tensors that do not fit, and no tensor is read."""
+    import json
+    from pie_b200.models import loader
+    from pie_b200.models.config import ModelConfig, preset
+    from pie_b200.models.weights import random_weights
+    cfg = preset("tiny-llama")
+    loader.export_hf_checkpoint(cfg, random_weights(cfg, "cpu", torch.float32, seed=1), tmp_path)
+    rd = loader.SafetensorsReader(tmp_path)
+    prog = loader.compile_program(cfg, rd.names(), 2, 1)
+    shapes = loader.typecheck_program(prog, cfg, rd)
+    assert shapes["layers.0.wqkv"] == ((2 + 2 * 1) * cfg.head_dim, cfg.hidden_size)         # this rank's heads
+    assert shapes["layers.1.w_down"] == (cfg.hidden_size, cfg.intermediate_size // 2)
+    hf = json.loads((tmp_path / "config.json").read_text())
+    hf["intermediate_size"] += 16
+    hf["num_key_value_heads"] = 4
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    reads = []
+    orig = loader.SafetensorsReader.get
+    loader.SafetensorsReader.get = lambda self, name: reads.append(name) or orig(self, name)
+    try:
+        with pytest.raises(loader.LoaderTypeError) as e:
+            loader.load_checkpoint(tmp_path, "cpu")
+    finally:
+        loader.SafetensorsReader.get = orig
+    msg = str(e.value)
+    assert "layers.0.w_gate_up" in msg and "layers.0.w_down" in msg and "rows" in msg and reads == []
+    with pytest.raises(loader.LoaderTypeError, match="does not split over 3 ranks"):
+        loader.infer_shape(loader.Shard(loader.Read("model.layers.0.mlp.down_proj.weight"), 1, 0, 3), rd)
