@@ -4,6 +4,8 @@ implementation or an earlier build.
 
     python -m pie_b200.parity --model tiny-llama --tokens 1,2,3,4 --out logits.npy [--device cpu]
         [--decode-after-prefill] [--compare other.npy]
+    python -m pie_b200.parity --path CKPT --tokens 1,2,3,4 --hf --out hf.npy     # the same row from Hugging Face
+                                                                                    # transformers (fp32, eager attention)
 
 Counterpart of driver/cuda/src/parity_harness.cpp (--parity-tokens / --parity-out /
 --parity-paged / --parity-decode-after-prefill; driver/cuda/src/entry.cpp:123-138).
@@ -43,6 +45,17 @@ def run(model: str, tokens, device: str = "cpu", path: str = "", decode_after_pr
     return np.frombuffer(resp.slots[0].logits, dtype=np.float32).copy()
 
 
+def run_hf(path: str, tokens) -> np.ndarray:
+    """Last-token logits of the checkpoint at `path` from Hugging Face transformers (the HF parity dumper of the
+    reference's `scripts/`): fp32 on the host, eager attention, no cache."""
+    import torch
+    from transformers import AutoModelForCausalLM
+    m = AutoModelForCausalLM.from_pretrained(path, dtype=torch.float32, attn_implementation="eager")
+    m.eval()
+    with torch.no_grad():
+        return m(torch.tensor([list(tokens)])).logits[0, -1].float().numpy().copy()
+
+
 def compare(a: np.ndarray, b: np.ndarray) -> dict:
     cos = float(np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-12))
     return {"cos": cos, "max_abs": float(np.abs(a - b).max()), "argmax_equal": bool(a.argmax() == b.argmax()),
@@ -58,9 +71,10 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--decode-after-prefill", action="store_true")
     ap.add_argument("--compare", default="")
+    ap.add_argument("--hf", action="store_true", help="dump from Hugging Face transformers instead of the driver")
     a = ap.parse_args()
     toks = [int(t) for t in a.tokens.split(",") if t.strip()]
-    logits = run(a.model, toks, a.device, a.path, a.decode_after_prefill)
+    logits = run_hf(a.path, toks) if a.hf else run(a.model, toks, a.device, a.path, a.decode_after_prefill)
     if a.out:
         np.save(a.out, logits)
     rep = {"vocab": int(logits.shape[0]), "argmax": int(logits.argmax()), "max": float(logits.max())}
