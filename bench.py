@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5, 6],
                     help="2: the headline configuration (this file); 3 Qwen3-32B block-fp8, 4 Qwen3-30B-A3B MoE with "
                          "expert parallelism, 5 agentic fork, 6 GPT-OSS shapes: see pie_b200/bench/configs.py")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library", "vllm"])
     ap.add_argument("--no-baseline", action="store_true", help="skip the library comparator (vs_baseline stays null)")
     ap.add_argument("--model", default="llama-3.1-8b")
     ap.add_argument("--requests", type=int, default=512)
@@ -75,6 +75,14 @@ def main():
     if args.impl == "reference":
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.impl == "vllm":
+        # the workload served by vLLM (one process; it starts its own tensor-parallel workers for --gpus N)
+        if rank == 0:
+            from pie_b200.bench import vllm_arm
+            vllm_arm.main(["--model", args.model, "--requests", str(args.requests), "--prompt-min", str(args.prompt_min),
+                           "--prompt-max", str(args.prompt_max), "--out-tokens", str(args.out_tokens),
+                           "--gpus", str(args.gpus)] + (["--layers", str(args.layers)] if args.layers else []))
         return 0
     from pie_b200.bench import configs as _configs
     _configs._hang_dump()
