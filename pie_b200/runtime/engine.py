@@ -31,6 +31,7 @@ from .market import Market
 from .messaging import Messaging
 from .pagestore import PageStore
 from .process import Process, current_process
+from . import telemetry
 from .scheduler import BatchScheduler
 
 VERSION = "0.1.0"
@@ -275,7 +276,18 @@ class Engine:
                       "market_rent": e.market.total_rent, "market_waiting": len(e.market.waiting)})
             m.update({f"ctx_{k}": v for k, v in e.ctxm.counters.items()})
             out["models"][name] = m
-        out["processes"] = len([p for p in self.processes.values() if not p.finished])
+        live = [p for p in self.processes.values() if not p.finished]
+        out["processes"] = len(live)
+        # the busiest live processes and the scheduler's per-fire probe tree (when telemetry is on)
+        out["process_table"] = [
+            {"id": p.id, "program": p.program, "user": p.username, "age_s": round(time.time() - p.t_start, 1),
+             "tokens": p.tokens_used}
+            for p in sorted(live, key=lambda q: -q.tokens_used)[:12]]
+        tel = telemetry.get()
+        if tel.enabled:
+            snap = tel.snapshot()
+            out["fire"] = {k: v for k, v in snap["probes"].items() if k.startswith(("fire_", "driver_"))}
+            out["counters"] = snap["counters"]
         return out
 
     def metrics_text(self) -> str:

@@ -1,7 +1,7 @@
 """`pie` command line (python -m pie_b200 ...). Subcommands follow the reference CLI
 (server/src/cli.rs:50-142): serve, run, config {init,show,set}, auth {add,remove,list,keygen},
 model {list,download,remove}, inferlet {list}, driver {list, <type> install|doctor|show|set|unset},
-new, build, doctor, check, smoke.
+new, build, monitor, doctor, check, smoke.
 
 `pie run <inferlet> [-- --key value ...]` boots a one-shot engine, connects a client over the
 WebSocket like any other client, launches the inferlet with the trailing `--key value` pairs as
@@ -348,6 +348,22 @@ def cmd_doctor(args) -> int:
     return 0
 
 
+def cmd_monitor(args) -> int:
+    """`pie monitor [--uri ws://host:port] [--token T]`: the dashboard of a running engine, over its status query."""
+    from ..client.client import PieClient
+    from .monitor import run_monitor
+    c = PieClient(args.uri)
+    try:
+        if args.token:
+            c.auth_by_token(args.token)
+        run_monitor(c.model_status, period=args.period, iterations=args.iterations)
+    except KeyboardInterrupt:
+        pass
+    finally:
+        c.close()
+    return 0
+
+
 def cmd_check(args) -> int:
     try:
         cfg = cfgmod.load(args.config) if args.config else (
@@ -399,6 +415,9 @@ def main(argv=None) -> int:
     p.add_argument("--config"); p.add_argument("--run", action="store_true"); p.set_defaults(fn=cmd_driver)
     p = sub.add_parser("new"); p.add_argument("name"); p.set_defaults(fn=cmd_new)
     p = sub.add_parser("build"); p.add_argument("path"); p.set_defaults(fn=cmd_build)
+    p = sub.add_parser("monitor"); p.add_argument("--uri", default="ws://127.0.0.1:8080"); p.add_argument("--token", default="")
+    p.add_argument("--period", type=float, default=1.0); p.add_argument("--iterations", type=int, default=-1)
+    p.set_defaults(fn=cmd_monitor)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
     p = sub.add_parser("check"); p.add_argument("--config"); p.set_defaults(fn=cmd_check)
     p = sub.add_parser("smoke"); p.set_defaults(fn=cmd_smoke)

@@ -103,3 +103,38 @@ def test_nvtx_ranges_wrap_the_driver_phases_and_cost_nothing_when_off():
     names = [e[1] for e in events if e[0] == "push"]
     assert names == ["pie.fire", "forward.general", "respond"]
     assert sum(e[0] == "pop" for e in events) == 3 and events[-1] == ("pop",)
+
+
+def test_monitor_renders_status_processes_and_fire_tree_locally_and_over_the_client(tmp_path):
+    import io
+    import json
+    from test_runtime_cpu import CounterBehavior, MockDriver, engine_with
+    from pie_b200.client.client import PieClient
+    from pie_b200.server import cli
+    from pie_b200.server.auth import Authenticator
+    from pie_b200.server.monitor import render, run_monitor
+    from pie_b200.server.server import PieServer
+    tel = telemetry.configure(True)
+    eng = engine_with(MockDriver(CounterBehavior(), total_pages=64))
+    srv = PieServer(eng, "127.0.0.1", 0, Authenticator(False), str(tmp_path / "programs"))
+    port = srv.start()
+    try:
+        eng.run("text-completion-bench", {"prompt_tokens": [1, 2, 3], "max_tokens": 5, "per_step": True}, 30)
+        st = eng.model_status()
+        assert "fire_execute_total" in st["fire"] and st["process_table"] == []
+        text = render(st, {})
+        assert "per-fire probes" in text and "fire_execute_driver_fire" in text and "batch size" in text and "[mock] kv 0/64" in text
+        buf = io.StringIO()
+        run_monitor(eng, period=0.01, out=buf, iterations=2, clear=False)
+        assert buf.getvalue().count("pie_b200 ") == 2
+        c = PieClient(f"ws://127.0.0.1:{port}")
+        remote = io.StringIO()
+        run_monitor(c.model_status, period=0.01, out=remote, iterations=1, clear=False)
+        c.close()
+        assert "[mock] kv" in remote.getvalue() and "per-fire probes" in remote.getvalue()
+        assert cli.main(["monitor", "--uri", f"ws://127.0.0.1:{port}", "--iterations", "1", "--period", "0.01"]) == 0
+        json.dumps(st)                                   # the status stays JSON-serialisable for the query
+    finally:
+        srv.stop()
+        eng.shutdown()
+        telemetry.configure(False)
