@@ -67,8 +67,9 @@ def render(status: dict, history: dict) -> str:
     return "\n".join(lines)
 
 
-def run_monitor(source, period: float = 1.0, out=sys.stdout, iterations: int = -1, clear: bool = True) -> None:
+def run_monitor(source, period: float = 1.0, out=None, iterations: int = -1, clear: bool = True) -> None:
     """`source`: an Engine, or any callable returning the status dictionary (a client's `model_status`)."""
+    out = out or sys.stdout
     fetch: Callable[[], dict] = source if callable(source) else source.model_status
     history: dict = {}
     n = 0
