@@ -1,7 +1,7 @@
 """`pie` command line (python -m pie_b200 ...). Subcommands follow the reference CLI
 (server/src/cli.rs:50-142): serve, run, config {init,show,set}, auth {add,remove,list,keygen},
 model {list,download,remove}, inferlet {list}, driver {list, <type> install|doctor|show|set|unset},
-new, build, monitor, doctor, check, smoke.
+new, build, publish, monitor, doctor, check, smoke.
 
 `pie run <inferlet> [-- --key value ...]` boots a one-shot engine, connects a client over the
 WebSocket like any other client, launches the inferlet with the trailing `--key value` pairs as
@@ -319,14 +319,64 @@ def cmd_new(args) -> int:
     return 0
 
 
-def cmd_build(args) -> int:
-    """Native inferlets need no compilation: check that the program loads and defines main()."""
+def _package(path: str):
+    """(manifest, main.py source, zip bytes) of an inferlet directory (or a single source file beside a Pie.toml)."""
     import ast
-    src = (Path(args.path) / "main.py") if Path(args.path).is_dir() else Path(args.path)
-    tree = ast.parse(src.read_text())
-    ok = any(isinstance(n, ast.AsyncFunctionDef) and n.name == "main" for n in tree.body)
-    print("ok" if ok else "missing `async def main(input)`")
-    return 0 if ok else 1
+    import io
+    import zipfile
+    from ..runtime.program import Manifest
+    p = Path(path)
+    d = p if p.is_dir() else p.parent
+    src = (d / "main.py") if p.is_dir() else p
+    toml = d / "Pie.toml"
+    if not src.exists() or not toml.exists():
+        raise SystemExit(f"{d}: need main.py and Pie.toml")
+    source = src.read_text()
+    tree = ast.parse(source)
+    if not any(isinstance(n, ast.AsyncFunctionDef) and n.name == "main" for n in tree.body):
+        raise SystemExit("missing `async def main(input)`")
+    manifest = Manifest.parse(toml.read_text())
+    manifest.validate()
+    buf = io.BytesIO()
+    with zipfile.ZipFile(buf, "w", zipfile.ZIP_DEFLATED) as z:
+        z.writestr("Pie.toml", toml.read_text())
+        z.writestr("main.py", source)
+    return manifest, source, buf.getvalue()
+
+
+def cmd_build(args) -> int:
+    """`pie build <dir> [--out DIR]`: check the program (it parses, defines `async def main`, the manifest is valid)
+    and write the package the registry serves: `<out>/<name>-<version>.zip` holding Pie.toml and main.py
+    (the role of the reference's `bakery build`, sdk/tools/bakery/src/bakery/build.py)."""
+    from ..runtime.program import content_hash
+    manifest, source, blob = _package(args.path)
+    out = Path(args.out or (Path(args.path) if Path(args.path).is_dir() else Path(args.path).parent) / "dist")
+    out.mkdir(parents=True, exist_ok=True)
+    target = out / f"{manifest.name}-{manifest.version}.zip"
+    target.write_bytes(blob)
+    print(f"ok: {target} ({len(blob)} bytes, content hash {content_hash(source.encode())})")
+    return 0
+
+
+def cmd_publish(args) -> int:
+    """`pie publish <dir> --registry URL [--token T]`: upload the package to a registry
+    (`PUT <registry>/api/v1/inferlets/<name>/<version>`; `bakery publish` in the reference)."""
+    import urllib.error
+    import urllib.request
+    from ..runtime.program import content_hash
+    manifest, source, blob = _package(args.path)
+    url = f"{args.registry.rstrip('/')}/api/v1/inferlets/{manifest.name}/{manifest.version}"
+    req = urllib.request.Request(url, data=blob, method="PUT", headers={
+        "Content-Type": "application/zip", "X-Content-Hash": content_hash(source.encode())})
+    if args.token:
+        req.add_header("Authorization", f"Bearer {args.token}")
+    try:
+        with urllib.request.urlopen(req, timeout=60) as r:
+            print(f"published {manifest.name}@{manifest.version} ({r.status})")
+    except urllib.error.HTTPError as e:
+        print(f"registry refused {manifest.name}@{manifest.version}: {e.code} {e.reason}", file=sys.stderr)
+        return 1
+    return 0
 
 
 def cmd_doctor(args) -> int:
@@ -414,7 +464,9 @@ def main(argv=None) -> int:
     p.add_argument("key", nargs="?"); p.add_argument("value", nargs="?")
     p.add_argument("--config"); p.add_argument("--run", action="store_true"); p.set_defaults(fn=cmd_driver)
     p = sub.add_parser("new"); p.add_argument("name"); p.set_defaults(fn=cmd_new)
-    p = sub.add_parser("build"); p.add_argument("path"); p.set_defaults(fn=cmd_build)
+    p = sub.add_parser("build"); p.add_argument("path"); p.add_argument("--out"); p.set_defaults(fn=cmd_build)
+    p = sub.add_parser("publish"); p.add_argument("path"); p.add_argument("--registry", required=True)
+    p.add_argument("--token", default=""); p.set_defaults(fn=cmd_publish)
     p = sub.add_parser("monitor"); p.add_argument("--uri", default="ws://127.0.0.1:8080"); p.add_argument("--token", default="")
     p.add_argument("--period", type=float, default=1.0); p.add_argument("--iterations", type=int, default=-1)
     p.set_defaults(fn=cmd_monitor)

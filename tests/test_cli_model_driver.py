@@ -89,3 +89,59 @@ def test_driver_knobs_persist_and_become_defaults(monkeypatch, tmp_path, capsys)
     assert "used by: m" in capsys.readouterr().out
     assert cli.main(["driver", "cuda-native", "install"]) == 0
     assert "pie_b200._build" in capsys.readouterr().out
+
+
+def test_new_build_publish_and_fetch_round_trip(tmp_path, monkeypatch, capsys):
+    """`pie new` -> `pie build` (package zip) -> `pie publish` to a registry -> an engine fetches it on first launch."""
+    import json as _json
+    from pie_b200.driver.mock import CounterBehavior, MockDriver
+    from pie_b200.runtime.engine import Engine, EngineConfig
+    from pie_b200.runtime.program import ProgramStore
+    store = {}
+
+    class Registry(http.server.BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_PUT(self):
+            store[self.path] = (self.rfile.read(int(self.headers["Content-Length"])), self.headers.get("X-Content-Hash"))
+            self.send_response(201)
+            self.send_header("Content-Length", "0")
+            self.end_headers()
+
+        def do_GET(self):
+            key = self.path[:-len("/download")]
+            if key.endswith("/latest"):
+                key = sorted(k for k in store if k.startswith(key[:-len("latest")]))[-1] if store else key
+            if key not in store:
+                self.send_error(404)
+                return
+            blob, h = store[key]
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(blob)))
+            self.send_header("X-Content-Hash", h)
+            self.end_headers()
+            self.wfile.write(blob)
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Registry)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{srv.server_address[1]}"
+    monkeypatch.chdir(tmp_path)
+    assert cli.main(["new", "my-bot"]) == 0
+    (tmp_path / "my-bot" / "main.py").write_text("async def main(args):\n    return 'bot:' + str(args.get('q'))\n")
+    assert cli.main(["build", "my-bot"]) == 0
+    assert (tmp_path / "my-bot" / "dist" / "my-bot-0.1.0.zip").exists() and "content hash" in capsys.readouterr().out
+    (tmp_path / "broken").mkdir()
+    (tmp_path / "broken" / "main.py").write_text("def main(x):\n    return 1\n")
+    (tmp_path / "broken" / "Pie.toml").write_text('[package]\nname = "broken"\nversion = "0.1.0"\n')
+    with pytest.raises(SystemExit, match="async def main"):
+        cli.main(["build", "broken"])
+    assert cli.main(["publish", "my-bot", "--registry", url]) == 0
+    assert list(store) == ["/api/v1/inferlets/my-bot/0.1.0"]
+    eng = Engine(EngineConfig())
+    eng.add_model("mock", MockDriver(CounterBehavior(), total_pages=16))
+    try:
+        eng.program_resolver = ProgramStore(eng, str(tmp_path / "cache"), url).ensure
+        assert eng.run("my-bot", {"q": 3}, 30) == "bot:3"
+    finally:
+        eng.shutdown()
+        srv.shutdown()
