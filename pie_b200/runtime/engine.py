@@ -41,6 +41,7 @@ VERSION = "0.1.0"
 class EngineConfig:
     batch_policy: str = "adaptive"
     speculation_depth: int = 1
+    system_spec_tokens: int = 0               # > 0: runtime-side prompt-look-up drafts per generator step (replaces the chain)
     max_concurrent_processes: int = 4096
     request_timeout_secs: float = 120.0
     default_token_budget: Optional[int] = None
@@ -126,7 +127,9 @@ class Engine:
             sched.cohort = (DecodeCohort(entry.ctxm, entry.page_size, caps.max_forward_requests)
                             if not caps.rs_cache_slots and hasattr(drv, "decode_async") else None)
             entry.schedulers.append(sched)
-        entry.inference = InferenceService(entry.ctxm, entry.schedulers, self.config.speculation_depth)
+        entry.inference = InferenceService(entry.ctxm, entry.schedulers,
+                                           0 if self.config.system_spec_tokens > 0 else self.config.speculation_depth)
+        entry.inference.system_spec_tokens = self.config.system_spec_tokens
         entry.inference.cohorts = [s.cohort for s in entry.schedulers] if all(
             s.cohort is not None for s in entry.schedulers) else []
         for s in entry.schedulers:

@@ -98,8 +98,10 @@ class InferenceService:
         self.cohorts: list = []       # DecodeCohort per driver (set by the engine)
         self.staged: Dict[int, _Staged] = {}
         self.lock = threading.Lock()
+        self.system_spec_tokens = 0  # > 0: the runtime drafts up to this many tokens per generator step (n-gram look-up)
+        self.system_spec_ngram = 2
         self.max_defers = 64         # times one request may wait (restore queue, slot shortage) before it fails
-        self.stats = {"submits": 0, "bypass_hits": 0, "chain_submits": 0, "chain_drops": 0,
+        self.stats = {"system_spec_proposed": 0, "system_spec_accepted": 0, "submits": 0, "bypass_hits": 0, "chain_submits": 0, "chain_drops": 0,
                       "tokens_appended": 0}
         self.on_tokens: Optional[Callable[[int, int], None]] = None   # (context id, n tokens) accounting hook
 
@@ -107,10 +109,48 @@ class InferenceService:
     def submit(self, cid: int, tokens: Sequence[int], positions: Sequence[int],
                samplers: Sequence[tuple], masks: Optional[list] = None, logit_mask: Optional[list] = None,
                spec_tokens: Sequence[int] = (), spec_positions: Sequence[int] = (), adapter: int = -1,
-               speculate: bool = True) -> Future:
-        """Queue one forward pass of context `cid`; resolves to a ForwardOutput."""
+               speculate: bool = True, spec_budget: Optional[int] = None) -> Future:
+        """Queue one forward pass of context `cid`; resolves to a ForwardOutput.
+
+        `spec_budget`: the caller can take up to this many extra tokens from this pass (a generator step; None:
+        it cannot). With system speculation on, the runtime then drafts continuation tokens itself, verifies
+        them in the same pass and returns the accepted ones in `ForwardOutput.spec_tokens`."""
         self.stats["submits"] += 1
         tokens, positions = list(tokens), list(positions)
+        if (self.system_spec_tokens > 0 and spec_budget and len(tokens) == 1 and len(samplers) == 1 and not spec_tokens
+                and masks is None and logit_mask is None and adapter < 0 and samplers[0][0] == 0
+                and samplers[0][1].is_token and speculate):
+            drafted = self._system_draft(cid, tokens[0], positions[0], min(self.system_spec_tokens, spec_budget))
+            if drafted:
+                d_tokens, d_positions = drafted
+                fut = Future()
+                sp = samplers[0][1]
+                inner = Future()
+
+                def finish(f: Future, n=len(d_tokens)):
+                    try:
+                        out = f.result()
+                    except BaseException as e:  # noqa: BLE001
+                        fut.set(exc=e)
+                        return
+                    k = out.accepted_drafts
+                    # slot i holds the successor of input row i: rows 1..k are the successors of accepted drafts
+                    out.spec_tokens = [s.token for s in out.slots[1:k + 1]]
+                    out.spec_positions = d_positions[:k]
+                    out.system_drafts = n
+                    out.slots = out.slots[:1]
+                    self.stats["system_spec_proposed"] += n
+                    self.stats["system_spec_accepted"] += k
+                    fut.set(out)
+                inner.add_done_callback(finish)
+                prev = self._abandon(cid)
+                args = (cid, tokens, positions, [(i, sp) for i in range(len(d_tokens) + 1)], None, None, d_tokens,
+                        d_positions, -1, False, inner)
+                if prev is not None and not prev.future.done():
+                    prev.future.add_done_callback(lambda _f: self._start(*args))
+                else:
+                    self._start(*args)
+                return fut
         hit = self._try_hit(cid, tokens, positions, samplers, masks, logit_mask, spec_tokens)
         if hit is not None:
             return hit
@@ -127,6 +167,38 @@ class InferenceService:
 
     def drop_context(self, cid: int) -> None:
         self._abandon(cid)
+
+    def _system_draft(self, cid: int, token: int, position: int, k: int):
+        """Prompt-look-up drafter: find the most recent earlier occurrence of the context's last `n` tokens
+        (ending with the token about to be fed) and propose what followed it. Returns (tokens, positions) or
+        None; also makes sure the context has page capacity for the drafts (else no draft)."""
+        ctx = self.ctxm.contexts.get(cid)
+        if ctx is None or k <= 0 or self.ctxm.rs[ctx.driver].supported:
+            return None
+        hist = list(ctx.committed_tokens) + list(ctx.tokens) + [token]
+        n = self.system_spec_ngram
+        if len(hist) <= n:
+            return None
+        key = hist[-n:]
+        found = -1
+        for i in range(len(hist) - n - 1, -1, -1):           # newest match first
+            if hist[i:i + n] == key:
+                found = i + n
+                break
+        if found < 0 or found >= len(hist):
+            return None
+        drafts = hist[found:found + k]
+        if not drafts:
+            return None
+        ps = self.ctxm.page_size
+        need = self.ctxm.kv_len(cid) + 1 + len(drafts) + 1
+        have = (len(ctx.chain) + len(ctx.working_pages)) * ps
+        if need > have:
+            try:
+                self.ctxm.reserve_working_pages(cid, -(-(need - have) // ps))
+            except ContextError:
+                return None
+        return drafts, [position + 1 + i for i in range(len(drafts))]
 
     def start_stream(self, cid: int, tokens: Sequence[int], positions: Sequence[int], spec: SamplerSpec,
                      max_tokens: int, stop: Sequence[int] = ()):

@@ -203,10 +203,12 @@ class Forward:
         await ctx._reserve_async(n_in)
         svc = ctx._entry.inference
         fut = svc.submit(ctx.id, self._tokens, self._positions, self._samplers, self._attn_masks, self._mask,
-                         self._spec_tokens, self._spec_positions, self._adapter, self._speculate)
+                         self._spec_tokens, self._spec_positions, self._adapter, self._speculate,
+                         spec_budget=getattr(self, "_spec_budget", None))
         raw = await host.wait(fut)
         accepted = len(self._tokens) + getattr(raw, "accepted_drafts", 0)
-        ctx._after_pass(accepted, self._positions + self._spec_positions)
+        drafted = self._spec_positions if self._spec_positions else list(getattr(raw, "spec_positions", ()))
+        ctx._after_pass(accepted, self._positions + drafted)
         return Output(raw, None)
 
 
@@ -472,8 +474,15 @@ class GenStep:
             k = out.accepted_drafts
             accepted = sampled[: k + 1]        # accepted drafts' successors + bonus token
         else:
-            accepted = sampled[:1]
+            # the runtime may have drafted and verified a continuation itself (system speculation)
+            accepted = sampled[:1] + list(getattr(out.raw, "spec_tokens", ()) or [])
         out.tokens = self.gen.accept(accepted)
+        extra = len(accepted) - len(out.tokens)
+        if extra > 0 and not self.n_draft:
+            try:                               # the generator stopped inside the accepted run: drop the KV beyond it
+                self.gen.ctx.truncate(extra)
+            except Exception:  # noqa: BLE001
+                pass
         return out
 
 
@@ -553,6 +562,10 @@ class Generator:
                 fwd.speculative(d_tokens, d_pos or None)
                 n_draft = len(d_tokens)
         last = len(toks) - 1
+        if n_draft == 0 and not self._constraints and self._max is not None:
+            fwd._spec_budget = max(0, self._max - len(self._generated) - 1)     # extra tokens this step may deliver
+        elif n_draft == 0 and not self._constraints:
+            fwd._spec_budget = 1 << 20
         handle = fwd.sample(list(range(last, last + 1 + n_draft)), self.sampler)
         for c in self._constraints:
             fwd.mask(c.step([]))

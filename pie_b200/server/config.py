@@ -61,6 +61,7 @@ class RuntimeConfig:
 class SchedulerConfig:
     batch_policy: str = "adaptive"        # adaptive | eager | greedy
     speculation_depth: int = 1
+    system_spec_tokens: int = 0           # > 0: the runtime drafts this many tokens per generator step (prompt look-up)
 
 
 @dataclass

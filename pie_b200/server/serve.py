@@ -190,6 +190,7 @@ def start_engine(cfg: Config, serve: bool = True, port: Optional[int] = None) ->
     first = cfg.model[0].scheduler if cfg.model else None
     engine = Engine(EngineConfig(batch_policy=first.batch_policy if first else "adaptive",
                                  speculation_depth=first.speculation_depth if first else 1,
+                                 system_spec_tokens=first.system_spec_tokens if first else 0,
                                  max_concurrent_processes=rt.max_concurrent_processes,
                                  request_timeout_secs=rt.request_timeout_secs,
                                  default_token_budget=rt.default_token_budget,

@@ -176,3 +176,44 @@ def test_bounds_check_mode_names_the_bad_table_and_entry(monkeypatch):
     with pytest.raises(IndexError, match=r"logit_rows\[0\] = 3"):
         drv.fire_batch(req(slot_row=i32(3)))
     assert drv.fire_batch(req()).slots[0].kind == "token"           # the driver is still usable
+
+
+def test_system_speculation_gives_the_same_greedy_tokens_in_fewer_passes():
+    """Runtime-side prompt-look-up drafting: a repetitive context lets the runtime propose the continuation,
+    verify it in one pass and hand several tokens to the generator step; the output is the plain greedy output."""
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=0)
+    prompt = [11, 12, 13, 14, 15, 16] * 6
+
+    def run(k):
+        drv = TorchDriver(cfg, device="cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=256)
+        eng = Engine(EngineConfig(system_spec_tokens=k))
+        eng.add_model("m", drv)
+        install_all(eng)
+        try:
+            out = json.loads(eng.run("text-completion-bench", {"prompt_tokens": prompt, "max_tokens": 24, "per_step": True,
+                                                               "temperature": 0.0}, 300))
+            st = dict(eng.models["m"].inference.stats)
+            fires = drv.stats["fires"]
+            eng.models["m"].ctxm.audit()
+        finally:
+            eng.shutdown()
+        return out, st, fires
+    base, st0, fires0 = run(0)
+    spec, st4, fires4 = run(4)
+    assert st0["system_spec_proposed"] == 0 and st4["system_spec_proposed"] > 0
+    assert spec["n_tokens"] == base["n_tokens"] == 24
+    # token-level equality through the text-completion inferlet (it returns the tokens)
+    def toks(k):
+        drv = TorchDriver(cfg, device="cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=256)
+        eng = Engine(EngineConfig(system_spec_tokens=k))
+        eng.add_model("m", drv)
+        install_all(eng)
+        try:
+            return json.loads(eng.run("text-completion", {"prompt_tokens": prompt, "max_tokens": 24, "temperature": 0.0,
+                                                          "stop_tokens": [], "per_step": True}, 300))["tokens"]
+        finally:
+            eng.shutdown()
+    assert toks(4) == toks(0)
+    if st4["system_spec_accepted"] > 0:
+        assert fires4 < fires0                     # accepted drafts save forward passes
