@@ -1,4 +1,5 @@
-// Gated DeltaNet (linear attention) mixer of the hybrid models: the short causal convolution over the
+// Recurrent mixers of the hybrid models. Mamba-2 (state-space) is at the end of the file; first the
+// Gated DeltaNet (linear attention) mixer: the short causal convolution over the
 // q | k | v channels with its per-slot tail state, and the gated delta-rule recurrence with the gated
 // RMSNorm on its output. One launch serves a ragged batch (prefill chunks and decode rows alike): the
 // state of every request lives in its slot of the recurrent-state cache and is carried from fire to fire.
@@ -26,7 +27,8 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // x: [N, F] fused projection (first C columns are the convolved channels); state: [S, C, K-1] fp32.
 template <int K>
 __global__ void gdn_conv_kernel(const bf16* __restrict__ x, int x_stride, const bf16* __restrict__ w,
-                                const float* __restrict__ state, const int* __restrict__ qo_indptr,
+                                const bf16* __restrict__ bias, const float* __restrict__ state,
+                                const int* __restrict__ qo_indptr,
                                 const int* __restrict__ tok_req, const int* __restrict__ slots,
                                 const int* __restrict__ reset, float* __restrict__ y, int n, int c) {
     const int ch = blockIdx.x * blockDim.x + threadIdx.x;
@@ -37,7 +39,7 @@ __global__ void gdn_conv_kernel(const bf16* __restrict__ x, int x_stride, const 
     const int i = t - first;
     const bool fresh = reset[r] != 0;
     const float* st = state + ((size_t)slots[r] * c + ch) * (K - 1);
-    float acc = 0.f;
+    float acc = bias ? __bfloat162float(bias[ch]) : 0.f;
 #pragma unroll
     for (int j = 0; j < K; ++j) {
         const int idx = i - (K - 1) + j;
@@ -158,6 +160,55 @@ gdn_recurrent_kernel(const float* __restrict__ conv, const bf16* __restrict__ x,
     for (int i = 0; i < ROWS; ++i) sp[(size_t)i * dv] = S[i];
 }
 
+// Mamba-2 state update: grid (requests, heads), block = head_dim threads; thread p holds S[p, :] (NS values)
+// in registers. conv: [N, inner + 2 * groups * NS] (x | B | C after the convolution); x: the projection
+// [N, z | x B C | dt] for dt; y: [N, inner] fp32 (gate and norm follow outside: they span all heads).
+template <int NS>
+__global__ void __launch_bounds__(256)
+mamba2_ssm_kernel(const float* __restrict__ conv, const bf16* __restrict__ x, int x_stride,
+                  const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ d_skip,
+                  float* __restrict__ rec_state, const int* __restrict__ qo_indptr, const int* __restrict__ slots,
+                  const int* __restrict__ reset, float* __restrict__ y, int heads, int head_dim, int groups) {
+    __shared__ float sb[NS], scv[NS], sc[1];
+    const int r = blockIdx.x, h = blockIdx.y, p = threadIdx.x;
+    const int first = qo_indptr[r], len = qo_indptr[r + 1] - first;
+    if (len <= 0) return;
+    const int inner = heads * head_dim, c = inner + 2 * groups * NS;
+    const int g = h / (heads / groups);
+    float* sp = rec_state + (((size_t)slots[r] * heads + h) * head_dim + p) * NS;
+    float S[NS];
+    if (reset[r]) {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) S[i] = 0.f;
+    } else {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) S[i] = sp[i];
+    }
+    const float a = -__expf(a_log[h]), bias = dt_bias[h], dsk = d_skip[h];
+    for (int t = 0; t < len; ++t) {
+        const size_t row = (size_t)(first + t);
+        const float* cr = conv + row * c;
+        for (int i = p; i < NS; i += blockDim.x) {
+            sb[i] = cr[inner + g * NS + i];
+            scv[i] = cr[inner + groups * NS + g * NS + i];
+        }
+        if (p == 0) sc[0] = softplus_f(__bfloat162float(x[row * x_stride + inner + c + h]) + bias);
+        __syncthreads();
+        const float dt = sc[0], xv = cr[h * head_dim + p];
+        const float decay = __expf(dt * a), dx = dt * xv;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            S[i] = S[i] * decay + dx * sb[i];
+            acc += S[i] * scv[i];
+        }
+        y[row * inner + h * head_dim + p] = acc + dsk * xv;
+        __syncthreads();                                   // sb / scv / sc are rewritten by the next token
+    }
+#pragma unroll
+    for (int i = 0; i < NS; ++i) sp[i] = S[i];
+}
+
 // dst slot <- src slot in both caches of every linear layer (fork of a context).
 __global__ void gdn_copy_slot_kernel(float* __restrict__ buf, size_t layer_stride, size_t slot_elems, int layers,
                                      int src, int dst) {
@@ -182,8 +233,8 @@ PIE_API int pie_gdn_mixer(const void* x, int x_stride, const void* conv_w, const
     const int c = 2 * hk * dk + hv * dv;
     const bf16* xb = static_cast<const bf16*>(x);
     dim3 cg((c + 127) / 128, n);
-    gdn_conv_kernel<4><<<cg, 128, 0, st>>>(xb, x_stride, static_cast<const bf16*>(conv_w), conv_state, qo_indptr,
-                                           tok_req, slots, reset, conv_scratch, n, c);
+    gdn_conv_kernel<4><<<cg, 128, 0, st>>>(xb, x_stride, static_cast<const bf16*>(conv_w), nullptr, conv_state,
+                                           qo_indptr, tok_req, slots, reset, conv_scratch, n, c);
     dim3 sg((c + 127) / 128, r);
     gdn_conv_state_kernel<4><<<sg, 128, 0, st>>>(xb, x_stride, conv_state, qo_indptr, slots, reset, c);
     dim3 rg(r, hv);
@@ -196,6 +247,34 @@ PIE_API int pie_gdn_mixer(const void* x, int x_stride, const void* conv_w, const
     else if (dk == 128) PIE_GDN_LAUNCH(128, 2);
     else return (int)cudaErrorInvalidValue;
 #undef PIE_GDN_LAUNCH
+    return (int)cudaGetLastError();
+}
+
+PIE_API int pie_mamba2_mixer(const void* x, int x_stride, const void* conv_w, const void* conv_b, const float* a_log,
+                             const float* dt_bias, const float* d_skip, float* conv_state, float* rec_state,
+                             const int* qo_indptr, const int* tok_req, const int* slots, const int* reset,
+                             float* conv_scratch, float* y, int n, int r, int heads, int head_dim, int state, int groups,
+                             cudaStream_t st) {
+    using namespace pie;
+    if (n <= 0 || r <= 0) return 0;
+    if (head_dim > 256 || heads % groups != 0) return (int)cudaErrorInvalidValue;
+    const int inner = heads * head_dim, c = inner + 2 * groups * state;
+    const bf16* xb = static_cast<const bf16*>(x) + inner;          // the convolved channels follow the gate
+    dim3 cg((c + 127) / 128, n);
+    gdn_conv_kernel<4><<<cg, 128, 0, st>>>(xb, x_stride, static_cast<const bf16*>(conv_w), static_cast<const bf16*>(conv_b),
+                                           conv_state, qo_indptr, tok_req, slots, reset, conv_scratch, n, c);
+    dim3 sg((c + 127) / 128, r);
+    gdn_conv_state_kernel<4><<<sg, 128, 0, st>>>(xb, x_stride, conv_state, qo_indptr, slots, reset, c);
+    dim3 rg(r, heads);
+    const bf16* x0 = static_cast<const bf16*>(x);
+#define PIE_MAMBA_LAUNCH(NSV)                                                                                   \
+    mamba2_ssm_kernel<NSV><<<rg, head_dim, 0, st>>>(conv_scratch, x0, x_stride, a_log, dt_bias, d_skip, rec_state, \
+                                                    qo_indptr, slots, reset, y, heads, head_dim, groups)
+    if (state == 16) PIE_MAMBA_LAUNCH(16);
+    else if (state == 64) PIE_MAMBA_LAUNCH(64);
+    else if (state == 128) PIE_MAMBA_LAUNCH(128);
+    else return (int)cudaErrorInvalidValue;
+#undef PIE_MAMBA_LAUNCH
     return (int)cudaGetLastError();
 }
 

@@ -175,9 +175,9 @@ class TorchDriver:
         self.model.kv_scale = self.kv.scale
         # Gated DeltaNet layers keep their state in slots of a recurrent-state cache, one per resident context
         self.rs = None
-        if cfg.linear_layers:
+        if cfg.recurrent_layers:
             if self.par.tp_size > 1:
-                raise NotImplementedError("Gated DeltaNet layers under tensor parallelism")
+                raise NotImplementedError("recurrent (Gated DeltaNet / Mamba-2) layers under tensor parallelism")
             from .recurrent import RecurrentStateCache
             self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
             use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet

@@ -1,5 +1,6 @@
-"""Recurrent-state cache of the Gated DeltaNet layers: per (linear layer, slot) the tail of the short
-convolution's inputs and the fp32 delta-rule state. A slot belongs to one resident context; the runtime's
+"""Recurrent-state cache of the Gated DeltaNet and Mamba-2 layers: per (recurrent layer, slot) the tail of the
+short convolution's inputs and the fp32 state (delta-rule state [heads, dk, dv], or state-space state
+[heads, head_dim, state]). A slot belongs to one resident context; the runtime's
 slot pool (`runtime/rs_cache.py`) hands slots out, tells the driver when a slot must start from zero
 (`rs_reset`) and asks for a slot copy when a context forks.
 
@@ -35,10 +36,17 @@ class RecurrentInputs:
 class RecurrentStateCache:
     def __init__(self, cfg: ModelConfig, num_slots: int, device):
         self.cfg, self.num_slots, self.device = cfg, num_slots, torch.device(device)
-        lin = cfg.linear_layers
+        lin = cfg.recurrent_layers
+        if cfg.linear_layers and cfg.mamba_layers:
+            raise NotImplementedError("Gated DeltaNet and Mamba-2 layers in one model")
         self.layer_index = {li: i for i, li in enumerate(lin)}
-        c, k = cfg.gdn_conv_channels, cfg.linear_conv_kernel_dim
-        hv, dk, dv = cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        if cfg.mamba_layers:       # [heads, head_dim, state] per slot, convolution over x | B | C
+            c, k = cfg.mamba_conv_channels, 4
+            hv, dk, dv = cfg.mamba_num_heads, cfg.mamba_head_dim, cfg.ssm_state_size
+        else:
+            c, k = cfg.gdn_conv_channels, cfg.linear_conv_kernel_dim
+            hv, dk, dv = cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.conv_channels = c
         self.conv_state = torch.zeros(len(lin), num_slots, c, k - 1, dtype=torch.float32, device=self.device)
         self.rec_state = torch.zeros(len(lin), num_slots, hv, dk, dv, dtype=torch.float32, device=self.device)
 
@@ -61,7 +69,7 @@ class RecurrentStateCache:
         dev = self.device
         t = lambda a: torch.from_numpy(a).to(dev)
         n = int(qo[-1])
-        scratch = (torch.empty(max(n, 1), self.cfg.gdn_conv_channels, dtype=torch.float32, device=dev)
+        scratch = (torch.empty(max(n, 1), self.conv_channels, dtype=torch.float32, device=dev)
                    if dev.type == "cuda" else None)
         return RecurrentInputs(t(qo), t(tok_req), t(slots), t(reset), qo.tolist(), slots.tolist(), reset.tolist(),
                                self.conv_state, self.rec_state, self.layer_index, scratch)

@@ -13,7 +13,8 @@ from typing import Optional
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 # `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3",
-                         "gpt_oss", "qwen3_5", "qwen3_next")
+                         "gpt_oss", "qwen3_5", "qwen3_next", "mamba2_hybrid")
+MAMBA_TYPES = {"mamba2_hybrid"}         # Mamba-2 (state-space) mixers in llama-like blocks, between full-attention layers
 GDN_TYPES = {"qwen3_5", "qwen3_next"}   # hybrids: Gated DeltaNet (linear attention) layers between full-attention layers
 POST_NORM = {"olmo2", "olmo3"}       # same block with the norms after attention / MLP and q, k norms over all heads
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
@@ -54,6 +55,12 @@ class ModelConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel_dim: int = 4
+    # Mamba-2 layers (layer_types entry "mamba2"): heads, head size, state size, B / C groups
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 0
+    ssm_state_size: int = 0
+    mamba_n_groups: int = 1
+    mamba_norm_grouped: bool = False   # gated RMSNorm per B / C group (Nemotron-H) instead of over the whole inner width (Mamba-2)
     # quantisation of the linear weights: None | "fp8_block" (128x128 weight scales)
     quantization: Optional[str] = None
     dtype: str = "bfloat16"
@@ -70,6 +77,32 @@ class ModelConfig:
     def linear_layers(self) -> list:
         """Indices of the Gated DeltaNet layers (empty for pure-attention models)."""
         return [li for li in range(self.num_hidden_layers) if self.is_linear_layer(li)]
+
+    def is_mamba_layer(self, li: int) -> bool:
+        return self.layer_types is not None and self.layer_types[li] == "mamba2"
+
+    @property
+    def mamba_layers(self) -> list:
+        return [li for li in range(self.num_hidden_layers) if self.is_mamba_layer(li)]
+
+    @property
+    def recurrent_layers(self) -> list:
+        """Layers whose state lives in the recurrent-state cache (Gated DeltaNet or Mamba-2)."""
+        return [li for li in range(self.num_hidden_layers) if self.is_linear_layer(li) or self.is_mamba_layer(li)]
+
+    @property
+    def mamba_inner(self) -> int:
+        return self.mamba_num_heads * self.mamba_head_dim
+
+    @property
+    def mamba_conv_channels(self) -> int:
+        """Channels of the short convolution: x, then B and C of every group."""
+        return self.mamba_inner + 2 * self.mamba_n_groups * self.ssm_state_size
+
+    @property
+    def mamba_in_features(self) -> int:
+        """Rows of the input projection: z (gate) | x B C | dt."""
+        return self.mamba_inner + self.mamba_conv_channels + self.mamba_num_heads
 
     @property
     def gdn_conv_channels(self) -> int:
@@ -136,7 +169,10 @@ class ModelConfig:
             sliding_window=(cfg.get("sliding_window") or -1)
             if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss", "olmo3")) else -1,
             # OLMo-3 and GPT-OSS alternate sliding-window and full-attention layers
-            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") or mt in GDN_TYPES else None,
+            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") or mt in GDN_TYPES or mt in MAMBA_TYPES else None,
+            mamba_num_heads=cfg.get("mamba_num_heads", 0), mamba_head_dim=cfg.get("mamba_head_dim", 0),
+            ssm_state_size=cfg.get("ssm_state_size", 0), mamba_n_groups=cfg.get("mamba_n_groups", 1),
+            mamba_norm_grouped=bool(cfg.get("mamba_norm_grouped", False)),
             linear_num_key_heads=cfg.get("linear_num_key_heads", 0), linear_num_value_heads=cfg.get("linear_num_value_heads", 0),
             linear_key_head_dim=cfg.get("linear_key_head_dim", 0), linear_value_head_dim=cfg.get("linear_value_head_dim", 0),
             linear_conv_kernel_dim=cfg.get("linear_conv_kernel_dim", 4),
@@ -210,6 +246,10 @@ PRESETS = {
                          num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000, qk_norm=True,
                          rope_theta=1e6, layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
                          linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32),
+    "tiny-mamba2": dict(model_type="mamba2_hybrid", hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000,
+                        layer_types=["mamba2", "mamba2", "full_attention"], mamba_num_heads=8, mamba_head_dim=32,
+                        ssm_state_size=16, mamba_n_groups=2),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,

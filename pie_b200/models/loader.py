@@ -157,6 +157,21 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
     att["lm_head"] = Shard(head, 0, r, T)
     for li in range(cfg.num_hidden_layers):
         L, P = f"{pre}layers.{li}.", f"layers.{li}."
+        if cfg.is_mamba_layer(li):
+            # Mamba-2 layer under the names of the Mamba-2 checkpoints (`mixer.*`); in_proj rows are already z | x B C | dt
+            if T > 1:
+                raise NotImplementedError("Mamba-2 layers under tensor parallelism")
+            X = L + "mixer."
+            att[P + "w_mamba_in"] = w(X + "in_proj.weight")
+            att[P + "mamba_conv"] = Op("squeeze", {"dim": 1}, [w(X + "conv1d.weight")])
+            att[P + "mamba_conv_bias"] = w(X + "conv1d.bias")
+            for src, dst in (("A_log", "mamba_A_log"), ("dt_bias", "mamba_dt_bias"), ("D", "mamba_D")):
+                att[P + dst] = Op("float", {}, [w(X + src)])
+            att[P + "mamba_norm"], att[P + "w_mamba_out"] = w(X + "norm.weight"), w(X + "out_proj.weight")
+            att[P + "ln1"], att[P + "ln2"] = w(L + "input_layernorm.weight"), w(L + "post_attention_layernorm.weight")
+            QLin.interleave(lin(L + "mlp.gate_proj.weight"), lin(L + "mlp.up_proj.weight")).attach(att, P + "w_gate_up")
+            lin(L + "mlp.down_proj.weight").attach(att, P + "w_down")
+            continue
         if cfg.is_linear_layer(li):
             # Gated DeltaNet layer. The checkpoint groups the fused projections by key head:
             # in_proj_qkvz rows = per key head [q (dk), k (dk), v (rep * dv), z (rep * dv)], in_proj_ba rows = per
@@ -406,6 +421,11 @@ def expected_shapes(cfg: ModelConfig, tp_size: int = 1, ep: bool = False) -> Dic
            "w_gate_up": (2 * cfg.intermediate_size // T, H), "w_down": (H, cfg.intermediate_size // T),
            "router": (E, H), "router_bias": (E,), "experts_gate_up": (el, 2 * il, H), "experts_down": (el, H, il),
            "experts_gate_up_bias": (el, 2 * il), "experts_down_bias": (el, H)}
+    if cfg.mamba_layers:
+        hm = cfg.mamba_num_heads
+        out.update({"w_mamba_in": (cfg.mamba_in_features, H), "mamba_conv": (cfg.mamba_conv_channels, 4),
+                    "mamba_conv_bias": (cfg.mamba_conv_channels,), "mamba_A_log": (hm,), "mamba_dt_bias": (hm,),
+                    "mamba_D": (hm,), "mamba_norm": (cfg.mamba_inner,), "w_mamba_out": (H, cfg.mamba_inner)})
     if cfg.linear_layers:
         hv, dv = cfg.linear_num_value_heads, cfg.linear_value_head_dim
         out.update({"w_gdn_in": (cfg.gdn_in_features, H), "gdn_conv": (cfg.gdn_conv_channels, cfg.linear_conv_kernel_dim),
@@ -602,6 +622,16 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
         t["lm_head.weight"] = weights["lm_head"]
     for li, lw in enumerate(weights["layers"]):
         L = f"model.layers.{li}."
+        if "w_mamba_in" in lw:
+            X = L + "mixer."
+            t[X + "in_proj.weight"], t[X + "conv1d.weight"] = lw["w_mamba_in"], lw["mamba_conv"].unsqueeze(1)
+            t[X + "conv1d.bias"], t[X + "A_log"], t[X + "dt_bias"], t[X + "D"] = (
+                lw["mamba_conv_bias"], lw["mamba_A_log"], lw["mamba_dt_bias"], lw["mamba_D"])
+            t[X + "norm.weight"], t[X + "out_proj.weight"] = lw["mamba_norm"], lw["w_mamba_out"]
+            t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
+            t[L + "mlp.gate_proj.weight"], t[L + "mlp.up_proj.weight"] = lw["w_gate_up"][0::2], lw["w_gate_up"][1::2]
+            t[L + "mlp.down_proj.weight"] = lw["w_down"]
+            continue
         if "w_gdn_in" in lw:
             X = L + "linear_attn."
             hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
@@ -659,6 +689,10 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
         hf.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   sliding_window=cfg.sliding_window, layer_types=cfg.layer_types, swiglu_limit=cfg.swiglu_limit,
                   rope_scaling=cfg.rope_scaling)
+    elif cfg.mamba_layers:
+        hf.update(layer_types=cfg.layer_types, mamba_num_heads=cfg.mamba_num_heads, mamba_head_dim=cfg.mamba_head_dim,
+                  ssm_state_size=cfg.ssm_state_size, mamba_n_groups=cfg.mamba_n_groups,
+                  mamba_norm_grouped=cfg.mamba_norm_grouped)
     elif cfg.linear_layers:
         hf.update(layer_types=cfg.layer_types, linear_num_key_heads=cfg.linear_num_key_heads,
                   linear_num_value_heads=cfg.linear_num_value_heads, linear_key_head_dim=cfg.linear_key_head_dim,

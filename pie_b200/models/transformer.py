@@ -170,6 +170,14 @@ class Transformer:
         for li in range(cfg.num_hidden_layers):
             lw = w["layers"][li]
             post = cfg.post_norm
+            if "w_mamba_in" in lw:
+                # Mamba-2 layer: state-space mixer, state in the recurrent-state cache
+                x = ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
+                mix = self._gemm(x, lw["w_mamba_in"])
+                o = ops.mamba2_mixer(mix, lw, cfg, fi.rs, fi.rs.layer_index[li])
+                h = self._gemm(o, lw["w_mamba_out"], residual=h)
+                h = self._mlp(ops.rmsnorm(h, lw["ln2"], cfg.rms_norm_eps), lw, h)
+                continue
             if "w_gdn_in" in lw:
                 # Gated DeltaNet layer: the mixer replaces attention, its state lives in the recurrent-state cache
                 x = ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
@@ -256,6 +264,37 @@ def _swiglu_interleaved_cuda(y):
     return torch.nn.functional.silu(g) * u
 
 
+def _dense_mamba2(cfg: ModelConfig, lw: dict, xn: torch.Tensor) -> torch.Tensor:
+    """Mamba-2 mixer over one whole sequence from an empty state, head by head and token by token
+    (independent of the cached, batched implementation it checks)."""
+    hm, p, ns, g = cfg.mamba_num_heads, cfg.mamba_head_dim, cfg.ssm_state_size, cfg.mamba_n_groups
+    inner, c = cfg.mamba_inner, cfg.mamba_conv_channels
+    mix = xn @ lw["w_mamba_in"].float().t()
+    t = mix.shape[0]
+    pad = torch.cat([torch.zeros(3, c), mix[:, inner:inner + c]], 0)
+    cw = lw["mamba_conv"].float()
+    conv = torch.stack([(pad[i:i + 4] * cw.t()).sum(0) for i in range(t)]) + lw["mamba_conv_bias"].float()
+    conv = conv * torch.sigmoid(conv)
+    y = torch.zeros(t, inner)
+    for h in range(hm):
+        grp = h // (hm // g)
+        a = -torch.exp(lw["mamba_A_log"].float()[h])
+        state = torch.zeros(p, ns)
+        for i in range(t):
+            xv = conv[i, h * p:(h + 1) * p]
+            bv = conv[i, inner + grp * ns:inner + (grp + 1) * ns]
+            cv = conv[i, inner + g * ns + grp * ns:inner + g * ns + (grp + 1) * ns]
+            dt = torch.nn.functional.softplus(mix[i, inner + c + h] + lw["mamba_dt_bias"].float()[h])
+            state = state * torch.exp(dt * a) + dt * torch.outer(xv, bv)
+            y[i, h * p:(h + 1) * p] = state @ cv + lw["mamba_D"].float()[h] * xv
+    z = mix[:, :inner]
+    y = y * (z * torch.sigmoid(z))
+    ng = g if cfg.mamba_norm_grouped else 1
+    yg = y.reshape(t, ng, inner // ng)
+    yg = yg / torch.sqrt((yg * yg).mean(-1, keepdim=True) + cfg.rms_norm_eps)
+    return yg.reshape(t, inner) * lw["mamba_norm"].float()
+
+
 def _dense_gdn(cfg: ModelConfig, lw: dict, xn: torch.Tensor) -> torch.Tensor:
     """Gated DeltaNet over one whole sequence from an empty state, written token by token with explicit
     head loops (independent of the cached, batched implementation it checks)."""
@@ -304,6 +343,11 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
         return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * g.float()
 
     for li, lw in enumerate(w["layers"]):
+        if "w_mamba_in" in lw:
+            x = x + _dense_mamba2(cfg, lw, norm(x, lw["ln1"])) @ lw["w_mamba_out"].float().t()
+            gu = norm(x, lw["ln2"]) @ lw["w_gate_up"].float().t()
+            x = x + (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t()
+            continue
         if "w_gdn_in" in lw:
             x = x + _dense_gdn(cfg, lw, norm(x, lw["ln1"])) @ lw["w_gdn_out"].float().t()
             gu = norm(x, lw["ln2"]) @ lw["w_gate_up"].float().t()

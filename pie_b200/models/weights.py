@@ -96,6 +96,23 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
     emb = gen.normal(cfg.vocab_size, H)
     w["embed"] = emb
     for li in range(cfg.num_hidden_layers):
+        if cfg.is_mamba_layer(li):
+            if T > 1:
+                raise NotImplementedError("Mamba-2 layers under tensor parallelism")
+            # Mamba-2 mixer: input projection (z | x B C | dt), depthwise short convolution with bias over x B C,
+            # per-head decay (A_log), step bias (dt_bias) and skip (D), gated RMSNorm over the inner width, output projection
+            Hm, C = cfg.mamba_num_heads, cfg.mamba_conv_channels
+            lw = {"ln1": ones(H), "ln2": ones(H),
+                  "w_mamba_in": gen.normal(cfg.mamba_in_features, H, std=0.05),
+                  "mamba_conv": gen.normal(C, 4, std=0.3), "mamba_conv_bias": gen.normal(C, std=0.1),
+                  "mamba_A_log": gen.normal(Hm, std=0.5).float(), "mamba_dt_bias": gen.normal(Hm, std=0.5).float(),
+                  "mamba_D": (1 + gen.normal(Hm, std=0.2)).float(), "mamba_norm": 1 + gen.normal(cfg.mamba_inner, std=0.1),
+                  "w_mamba_out": gen.normal(H, cfg.mamba_inner)}
+            gate, up = gen.normal(cfg.intermediate_size, H), gen.normal(cfg.intermediate_size, H)
+            lw["w_gate_up"] = interleave_rows(gate, up).contiguous()
+            lw["w_down"] = gen.normal(H, cfg.intermediate_size)
+            w["layers"].append(lw)
+            continue
         if cfg.is_linear_layer(li):
             if T > 1:
                 raise NotImplementedError("Gated DeltaNet layers under tensor parallelism")

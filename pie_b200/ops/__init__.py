@@ -926,3 +926,31 @@ def gdn_copy_slot(buf, src: int, dst: int) -> None:
     layers, slots = buf.shape[0], buf.shape[1]
     slot_elems = buf[0, 0].numel()
     check(fn("pie_gdn_copy_slot")(ptr(buf), slots * slot_elems, slot_elems, layers, src, dst, stream_ptr()), "gdn_copy_slot")
+
+
+# --------------------------------------------------------------------------- Mamba-2
+def mamba2_mixer(mix, lw: dict, cfg, rs, layer: int):
+    """The Mamba-2 mixer of one layer over a ragged batch (see `reference.mamba2_mixer`). `mix` is the input
+    projection [N, z | x B C | dt]; the layer's slot states are advanced in place. Returns [N, heads * head_dim]."""
+    hm, p, ns, g = cfg.mamba_num_heads, cfg.mamba_head_dim, cfg.ssm_state_size, cfg.mamba_n_groups
+    if rs is None:
+        raise ValueError("a model with Mamba-2 layers needs recurrent-state inputs")
+    conv_state, rec_state = rs.conv_state[layer], rs.rec_state[layer]
+    if not mix.is_cuda:
+        return reference.mamba2_mixer(mix, lw["mamba_conv"], lw["mamba_conv_bias"], lw["mamba_A_log"], lw["mamba_dt_bias"],
+                                      lw["mamba_D"], lw["mamba_norm"], cfg.rms_norm_eps, hm, p, ns, g, rs.qo_host,
+                                      conv_state, rec_state, rs.slots_host, rs.reset_host,
+                                      norm_groups=g if cfg.mamba_norm_grouped else 1)
+    n, r, inner = mix.shape[0], len(rs.slots_host), hm * p
+    y = torch.empty(n, inner, dtype=torch.float32, device=mix.device)
+    check(fn("pie_mamba2_mixer")(ptr(mix), mix.stride(0), ptr(lw["mamba_conv"]), ptr(lw["mamba_conv_bias"]),
+                                 ptr(lw["mamba_A_log"]), ptr(lw["mamba_dt_bias"]), ptr(lw["mamba_D"]), ptr(conv_state),
+                                 ptr(rec_state), ptr(rs.qo_indptr), ptr(rs.tok_req), ptr(rs.slots), ptr(rs.reset),
+                                 ptr(rs.scratch), ptr(y), n, r, hm, p, ns, g, stream_ptr()), "mamba2_mixer")
+    # gate and per-group RMSNorm over the inner width (one pass over [N, inner]; the state update above is the cost)
+    z = mix[:, :inner].float()
+    y = y * torch.nn.functional.silu(z)
+    ng = g if cfg.mamba_norm_grouped else 1
+    yg = y.view(n, ng, inner // ng)
+    yg = yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps)
+    return (yg.view(n, inner) * lw["mamba_norm"].float()).to(torch.bfloat16)

@@ -54,6 +54,7 @@ _SIGNATURES = {
     "pie_validate_indices": [p, i32, i32, i32, i32, p, p],
     "pie_gdn_mixer": [p, i32, p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, f32, p],
     "pie_gdn_copy_slot": [p, i64, i64, i32, i32, i32, p],
+    "pie_mamba2_mixer": [p, i32, p, p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, p],
     "pie_gemm_set_workspace": [i32, p, i64, p, i32],
     "pie_gemm_set_pairs": [i32],
     "pie_gemm_set_swap": [i32],

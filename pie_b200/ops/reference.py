@@ -310,3 +310,53 @@ def gdn_mixer(mix, conv_w, a_log, dt_bias, norm_w, eps, hk, hv, dk, dv, qo_indpt
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
         out[a0:a1] = (o * torch.nn.functional.silu(z)).reshape(t, hv * dv)
     return out.to(mix.dtype)
+
+
+# ------------------------------------------------------------------ Mamba-2 (state-space duality) mixer
+def mamba2_mixer(mix, conv_w, conv_b, a_log, dt_bias, d_skip, norm_w, eps, heads, head_dim, state, groups,
+                 qo_indptr, conv_state, rec_state, slots, reset, norm_groups: int = 1):
+    """Mamba-2 mixer over a ragged batch with per-slot state (updated in place).
+
+    `mix` [N, z | x B C | dt]: z [heads*head_dim] gates the output, x B C go through the causal depthwise
+    convolution (kernel K, bias, SiLU) continuing from the slot's last K-1 inputs, dt [heads].
+    Per head h (group g = h // (heads / groups)), state S in R^{head_dim x state} (fp32):
+        dt' = softplus(dt + dt_bias);  S <- S * exp(dt' * -exp(A_log)) + dt' * x (x) B_g;  y = S C_g + D * x
+    out = RMSNorm(y * silu(z)) * norm_w, the norm over the whole inner width or per `norm_groups` slices of it.
+    Math of the reference's Mamba-2 step kernels (driver/cuda/src/kernels/nemotron_h.cu, selective state update)."""
+    n = mix.shape[0]
+    inner, c = heads * head_dim, heads * head_dim + 2 * groups * state
+    kk = conv_w.shape[1]
+    x_all = mix.float()
+    out = torch.zeros(n, inner, dtype=torch.float32, device=mix.device)
+    cw, cb = conv_w.float(), conv_b.float()
+    a = -torch.exp(a_log.float())
+    hpg = heads // groups
+    for r in range(len(qo_indptr) - 1):
+        a0, a1 = int(qo_indptr[r]), int(qo_indptr[r + 1])
+        if a1 <= a0:
+            continue
+        s = int(slots[r])
+        if reset[r]:
+            conv_state[s].zero_()
+            rec_state[s].zero_()
+        t = a1 - a0
+        z = x_all[a0:a1, :inner]
+        hist = torch.cat([conv_state[s].float().t(), x_all[a0:a1, inner:inner + c]], dim=0)
+        conv = sum(hist[j:j + t] * cw[:, j] for j in range(kk)) + cb
+        conv = torch.nn.functional.silu(conv)
+        conv_state[s].copy_(hist[-(kk - 1):].t().to(conv_state.dtype))
+        x = conv[:, :inner].reshape(t, heads, head_dim)
+        bmat = conv[:, inner:inner + groups * state].reshape(t, groups, state).repeat_interleave(hpg, dim=1)
+        cmat = conv[:, inner + groups * state:].reshape(t, groups, state).repeat_interleave(hpg, dim=1)
+        dt = torch.nn.functional.softplus(x_all[a0:a1, inner + c:] + dt_bias.float())      # [t, heads]
+        st = rec_state[s].float()                                                           # [heads, head_dim, state]
+        y = torch.zeros(t, heads, head_dim, device=mix.device)
+        for i in range(t):
+            st = st * torch.exp(dt[i] * a)[:, None, None] + (dt[i][:, None] * x[i])[:, :, None] * bmat[i][:, None, :]
+            y[i] = (st * cmat[i][:, None, :]).sum(-1) + d_skip.float()[:, None] * x[i]
+        rec_state[s].copy_(st)
+        y = y.reshape(t, inner) * torch.nn.functional.silu(z)
+        yg = y.reshape(t, norm_groups, inner // norm_groups)
+        yg = yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + eps)
+        out[a0:a1] = yg.reshape(t, inner) * norm_w.float()
+    return out.to(mix.dtype)

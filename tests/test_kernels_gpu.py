@@ -595,3 +595,34 @@ def test_gdn_mixer_matches_reference_over_chunks(dk, dv, hk, hv):
     torch.cuda.synchronize()
     assert torch.equal(dev_cache.rec_state[:, 1], dev_cache.rec_state[:, 4])
     assert torch.equal(dev_cache.conv_state[:, 1], dev_cache.conv_state[:, 4])
+
+
+@pytest.mark.parametrize("heads,head_dim,state,groups", [(8, 32, 16, 2), (4, 64, 128, 1), (8, 64, 64, 4)])
+def test_mamba2_mixer_matches_reference_over_chunks(heads, head_dim, state, groups):
+    """Mamba-2 mixer (convolution with bias and slot tails, state-space update, gate + norm) against the fp32
+    reference: a ragged batch, a second fire continuing from the cached state, and a reset."""
+    from pie_b200.driver.recurrent import RecurrentStateCache
+    from pie_b200.models.config import ModelConfig
+    torch.manual_seed(heads + state)
+    cfg = ModelConfig(model_type="mamba2_hybrid", num_hidden_layers=1, layer_types=["mamba2"], mamba_num_heads=heads,
+                      mamba_head_dim=head_dim, ssm_state_size=state, mamba_n_groups=groups)
+    c, f, inner = cfg.mamba_conv_channels, cfg.mamba_in_features, cfg.mamba_inner
+    rb = lambda t: t.to(torch.bfloat16).float()
+    lw_f = {"mamba_conv": rb(torch.randn(c, 4) * 0.3), "mamba_conv_bias": rb(torch.randn(c) * 0.1),
+            "mamba_A_log": torch.randn(heads) * 0.5, "mamba_dt_bias": torch.randn(heads) * 0.5,
+            "mamba_D": 1 + torch.randn(heads) * 0.2, "mamba_norm": rb(1 + torch.randn(inner) * 0.1)}
+    bf = ("mamba_conv", "mamba_conv_bias", "mamba_norm")
+    lw_d = {k: (v.to(DEV).to(torch.bfloat16) if k in bf else v.to(DEV)) for k, v in lw_f.items()}
+    dev_cache, cpu_cache = RecurrentStateCache(cfg, 6, DEV), RecurrentStateCache(cfg, 6, "cpu")
+    for lens, reset in (([5, 1, 37, 2], [1, 1, 1, 1]), ([1, 3, 1, 40], [0, 0, 0, 0]), ([2, 1, 1, 1], [1, 0, 0, 0])):
+        qo = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        slots = np.asarray([4, 0, 2, 5], np.int32)
+        mix = (torch.randn(int(qo[-1]), f) * 1.0).to(torch.bfloat16)
+        want = ref.mamba2_mixer(mix.float(), lw_f["mamba_conv"], lw_f["mamba_conv_bias"], lw_f["mamba_A_log"],
+                                lw_f["mamba_dt_bias"], lw_f["mamba_D"], lw_f["mamba_norm"], 1e-5, heads, head_dim, state,
+                                groups, qo.tolist(), cpu_cache.conv_state[0], cpu_cache.rec_state[0], slots.tolist(), reset)
+        got = ops.mamba2_mixer(mix.to(DEV), lw_d, cfg, dev_cache.inputs(qo, slots, np.asarray(reset, np.int32)), 0)
+        torch.cuda.synchronize()
+        close(got.cpu(), want, 3e-2)
+        assert torch.allclose(dev_cache.rec_state.cpu(), cpu_cache.rec_state, atol=2e-2, rtol=2e-2)
+        assert torch.allclose(dev_cache.conv_state.cpu(), cpu_cache.conv_state, atol=1e-6)
