@@ -32,6 +32,8 @@ def main():
     ap.add_argument("--gemm", default="tcgen05")
     ap.add_argument("--graphs", action="store_true")
     ap.add_argument("--prefill", type=int, default=0, help="also run one prefill batch of this many tokens per request")
+    ap.add_argument("--prefill-timeline", action="store_true",
+                    help="per-kernel device time of the prefill batch (one warm-up prefill first; one GPU)")
     ap.add_argument("--timeline", action="store_true", help="per-kernel device time of the decode steps (implies --graphs)")
     ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"])
     a = ap.parse_args()
@@ -87,12 +89,30 @@ def main():
         items = [PendingRequest(i, rng.integers(0, cfg.vocab_size, a.prefill).tolist(),
                                 list(range(kv, kv + a.prefill)), pages[i], kv, [(a.prefill - 1, sp)])
                  for i in range(a.requests)]
+        pprof = None
+        if a.prefill_timeline:
+            from torch.profiler import ProfilerActivity, profile
+            drv.fire_batch(fold(items, ps))                      # warm-up: same pages are written again below
+            torch.cuda.synchronize()
+            pprof = profile(activities=[ProfilerActivity.CUDA])
+            pprof.start()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         drv.fire_batch(fold(items, ps))
         ev1.record()
         torch.cuda.synchronize()
         print(f"prefill {a.requests}x{a.prefill} tokens: {ev0.elapsed_time(ev1):.3f} ms")
+        if pprof is not None:
+            pprof.stop()
+            rows = {}
+            for e in pprof.events():
+                if e.device_type is not None and "cuda" in str(e.device_type).lower():
+                    c, t = rows.get(e.name, (0, 0.0))
+                    rows[e.name] = (c + 1, t + e.device_time)
+            total = sum(t for _, t in rows.values())
+            print(f"prefill kernel timeline ({total / 1e3:.3f} ms of kernels)")
+            for name, (c, t) in sorted(rows.items(), key=lambda kv: -kv[1][1])[:24]:
+                print(f"{t:10.1f} us  {c:5d} launches  {t / c:9.2f} us each  {name[:110]}")
         kv += a.prefill
     toks = rng.integers(0, cfg.vocab_size, a.requests).tolist()
     warm = 2 if a.timeline else 0
