@@ -491,7 +491,12 @@ class ContextManager:
                 rs_reset = 1 if rs.flags_for_pass(cid) else 0
             ctx.pins += 1
             ctx.state = State.PINNED
-            pages = self._store(ctx).physical_ids(ctx.chain) + list(ctx.working_pages)
+            # physical ids of the committed chain: looked up once per chain length (a resident chain's pages
+            # do not move; suspend / restore drop the cache), not once per forward pass
+            cached = ctx.__dict__.get("_phys")
+            if cached is None or cached[0] != len(ctx.chain):
+                cached = ctx.__dict__["_phys"] = (len(ctx.chain), self._store(ctx).physical_ids(ctx.chain))
+            pages = cached[1] + ctx.working_pages
             return PinnedContext(cid, pages, kv_len, ctx.driver, rs_slot if rs_slot is not None else -1, rs_reset)
 
     def _rs_victim(self, requester: Context) -> Optional[Context]:
@@ -545,6 +550,7 @@ class ContextManager:
             ctx._chain_resident = store.would_free(ctx.chain) == 0
             store.release(ctx.chain)
             ctx.state = State.SUSPENDED
+            ctx.__dict__.pop("_phys", None)
             self.rs[ctx.driver].release(cid)
             self.counters["suspended"] += 1
 

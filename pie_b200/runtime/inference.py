@@ -26,33 +26,44 @@ from .context import ContextError, ContextManager, Deferred
 from .scheduler import BatchScheduler, PendingRequest
 
 
-class Future:
-    """Minimal thread-safe future with completion callbacks (usable from asyncio or threads)."""
+_FUTURE_LOCK = threading.Lock()       # guards the rare slow paths of every Future (a waiter's event, late callbacks)
 
-    __slots__ = ("_ev", "_result", "_exc", "_cbs", "_lock", "done_flag", "_defer_tries")
+
+class Future:
+    """Minimal thread-safe future with completion callbacks (usable from asyncio or threads). The
+    event a blocking waiter needs is created only when somebody waits: most futures here are consumed
+    through callbacks, hundreds per fire, and an Event with its condition and lock costs more than the
+    rest of the object."""
+
+    __slots__ = ("_ev", "_result", "_exc", "_cbs", "done_flag", "_defer_tries")
 
     def __init__(self):
-        self._ev = threading.Event()
+        self._ev = None
         self._result = None
         self._exc = None
-        self._cbs: List[Callable] = []
-        self._lock = threading.Lock()
+        self._cbs: Optional[List[Callable]] = None
         self.done_flag = False
 
     def set(self, result=None, exc: Optional[BaseException] = None) -> None:
-        with self._lock:
+        with _FUTURE_LOCK:
             if self.done_flag:
                 return
             self._result, self._exc, self.done_flag = result, exc, True
-            cbs, self._cbs = self._cbs, []
-        self._ev.set()
-        for cb in cbs:
-            cb(self)
+            cbs, self._cbs = self._cbs, None
+            ev = self._ev
+        if ev is not None:
+            ev.set()
+        if cbs:
+            for cb in cbs:
+                cb(self)
 
     def add_done_callback(self, cb: Callable) -> None:
-        with self._lock:
+        with _FUTURE_LOCK:
             if not self.done_flag:
-                self._cbs.append(cb)
+                if self._cbs is None:
+                    self._cbs = [cb]
+                else:
+                    self._cbs.append(cb)
                 return
         cb(self)
 
@@ -60,8 +71,13 @@ class Future:
         return self.done_flag
 
     def result(self, timeout: Optional[float] = None):
-        if not self._ev.wait(timeout):
-            raise TimeoutError("forward pass did not complete in time")
+        if not self.done_flag:
+            with _FUTURE_LOCK:
+                if not self.done_flag and self._ev is None:
+                    self._ev = threading.Event()
+                ev = self._ev
+            if not self.done_flag and not ev.wait(timeout):
+                raise TimeoutError("forward pass did not complete in time")
         if self._exc is not None:
             raise self._exc
         return self._result

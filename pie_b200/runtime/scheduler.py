@@ -73,15 +73,16 @@ class Usage:
     prob_rows: int = 0         # distinct token rows that need a normalised distribution
 
 
-_PROB_KINDS = None
+_PROB_VALUES = None
 
 
 def _needs_probs(spec) -> bool:
-    global _PROB_KINDS
-    if _PROB_KINDS is None:
+    global _PROB_VALUES
+    if _PROB_VALUES is None:
         from ..driver.schema import SamplerKind
-        _PROB_KINDS = {SamplerKind.DIST, SamplerKind.LOGPROB, SamplerKind.LOGPROBS, SamplerKind.ENTROPY}
-    return spec.kind in _PROB_KINDS
+        _PROB_VALUES = frozenset(int(k) for k in (SamplerKind.DIST, SamplerKind.LOGPROB, SamplerKind.LOGPROBS,
+                                                  SamplerKind.ENTROPY))
+    return spec.kind.value in _PROB_VALUES          # plain ints: hashing an enum member runs Python code
 
 
 class BatchAccumulator:
@@ -101,13 +102,23 @@ class BatchAccumulator:
         mask_bytes = 0
         if r.masks is not None:
             mask_bytes = r.n_tokens * (-(-total // 8))
-        labels = sum(len(s.labels) for _, s in r.samplers)
-        logit_rows = len({i for i, _ in r.samplers})
-        prob_rows = len({i for i, s in r.samplers if _needs_probs(s)})
+        if len(r.samplers) == 1:                     # the common case: one sampler on one row
+            sp = r.samplers[0][1]
+            labels, logit_rows, prob_rows = len(sp.labels), 1, 1 if _needs_probs(sp) else 0
+        else:
+            labels = sum(len(s.labels) for _, s in r.samplers)
+            logit_rows = len({i for i, _ in r.samplers})
+            prob_rows = len({i for i, s in r.samplers if _needs_probs(s)})
         return Usage(1, r.n_tokens, pages, len(r.samplers), mask_bytes, labels, logit_rows, prob_rows)
 
+    def _cost(self, r: PendingRequest) -> Usage:
+        c = r.__dict__.get("_usage")          # a request is costed by `fits` and again by `push`
+        if c is None:
+            c = r.__dict__["_usage"] = self.cost(r)
+        return c
+
     def fits(self, r: PendingRequest) -> bool:
-        c, u, caps = self.cost(r), self.usage, self.caps
+        c, u, caps = self._cost(r), self.usage, self.caps
         return (u.requests + c.requests <= caps.max_forward_requests
                 and u.tokens + c.tokens <= caps.max_forward_tokens
                 and u.page_refs + c.page_refs <= caps.max_page_refs
@@ -118,7 +129,7 @@ class BatchAccumulator:
                 and u.logprob_labels + c.logprob_labels <= caps.max_logprob_labels)
 
     def push(self, r: PendingRequest) -> None:
-        c, u = self.cost(r), self.usage
+        c, u = self._cost(r), self.usage
         u.requests += c.requests; u.tokens += c.tokens; u.page_refs += c.page_refs
         u.sampler_rows += c.sampler_rows; u.mask_bytes += c.mask_bytes; u.logprob_labels += c.logprob_labels
         u.logit_rows += c.logit_rows; u.prob_rows += c.prob_rows
