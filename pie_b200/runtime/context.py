@@ -343,6 +343,11 @@ class ContextManager:
             ctx = self._get(cid)
             if len(ctx.tokens) + len(tokens) > len(ctx.working_pages) * self.page_size:
                 raise ContextError("KV_INVARIANT_VIOLATION: working tokens exceed working pages")
+            if len(tokens) == 1 and mask_keys is None:           # a decode step: one token, no generator objects
+                ctx.tokens.append(int(tokens[0]))
+                ctx.positions.append(int(positions[0]))
+                ctx.mask_keys.append(b"")
+                return
             ctx.tokens.extend(int(t) for t in tokens)
             ctx.positions.extend(int(p) for p in positions)
             ctx.mask_keys.extend(mask_keys if mask_keys is not None else [b""] * len(tokens))

@@ -21,6 +21,7 @@ from typing import Any, Iterable, List, Optional, Sequence
 
 from ..driver.schema import SamplerSpec
 from ..runtime import brle
+from ..runtime.context import Deferred as _Deferred
 from . import host
 from .sample import Distribution, Entropy, Logits, Logprob, Logprobs, Sampler
 
@@ -200,7 +201,10 @@ class Forward:
         if n_in == 0:
             from ..runtime.inference import ForwardOutput
             return Output(ForwardOutput(slots=[]), None)
-        await ctx._reserve_async(n_in)
+        try:
+            ctx._reserve_for(n_in)                       # the common case needs no waiting (and no coroutine)
+        except _Deferred:
+            await ctx._reserve_async(n_in)
         svc = ctx._entry.inference
         fut = svc.submit(ctx.id, self._tokens, self._positions, self._samplers, self._attn_masks, self._mask,
                          self._spec_tokens, self._spec_positions, self._adapter, self._speculate,
