@@ -114,6 +114,7 @@ class InferenceService:
         self.cohorts: list = []       # DecodeCohort per driver (set by the engine)
         self.staged: Dict[int, _Staged] = {}
         self.lock = threading.Lock()
+        self._recurrent: Optional[bool] = None      # the model has recurrent layers (set on first use)
         self.system_spec_tokens = 0  # > 0: the runtime drafts up to this many tokens per generator step (n-gram look-up)
         self.system_spec_ngram = 2
         self.max_defers = 64         # times one request may wait (restore queue, slot shortage) before it fails
@@ -452,7 +453,9 @@ class InferenceService:
         """Eligibility: exactly one token-sampler slot at the last input row, no masks, no drafts."""
         if masks is not None or logit_mask is not None or n_spec or len(samplers) != 1:
             return
-        if any(rs.supported for rs in self.ctxm.rs):
+        if self._recurrent is None:
+            self._recurrent = any(rs.supported for rs in self.ctxm.rs)
+        if self._recurrent:
             return  # a staged pass that is later abandoned would already have advanced the recurrent state
         idx, sp = samplers[0]
         if idx != len(tokens) - 1 or not sp.is_token or out.slots[0].kind != "token":
