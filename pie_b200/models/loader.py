@@ -653,7 +653,10 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
         else:
             t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
         q, k, v = lw["wqkv"].split([hq * d, hkv * d, hkv * d], 0)
-        t[L + "self_attn.q_proj.weight"], t[L + "self_attn.k_proj.weight"], t[L + "self_attn.v_proj.weight"] = q, k, v
+        if cfg.model_type == "phi3":          # Phi-3 checkpoints store q, k, v rows in one tensor
+            t[L + "self_attn.qkv_proj.weight"] = lw["wqkv"]
+        else:
+            t[L + "self_attn.q_proj.weight"], t[L + "self_attn.k_proj.weight"], t[L + "self_attn.v_proj.weight"] = q, k, v
         t[L + "self_attn.o_proj.weight"] = lw["wo"]
         if "bqkv" in lw:
             bq, bk, bv = lw["bqkv"].split([hq * d, hkv * d, hkv * d], 0)
@@ -670,12 +673,21 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
             t[L + "mlp.experts.down_proj"] = lw["experts_down"].transpose(1, 2)
             t[L + "mlp.experts.gate_up_proj_bias"] = lw["experts_gate_up_bias"]
             t[L + "mlp.experts.down_proj_bias"] = lw["experts_down_bias"]
+        elif "experts_gate_up" in lw and cfg.model_type == "mixtral":
+            # Mixtral's names: block_sparse_moe.gate, experts.N.w1 (gate) / w3 (up) / w2 (down)
+            t[L + "block_sparse_moe.gate.weight"] = lw["router"]
+            for e in range(lw["experts_gate_up"].shape[0]):
+                gu, X = lw["experts_gate_up"][e], f"{L}block_sparse_moe.experts.{e}."
+                t[X + "w1.weight"], t[X + "w3.weight"], t[X + "w2.weight"] = gu[0::2], gu[1::2], lw["experts_down"][e]
         elif "experts_gate_up" in lw:
             t[L + "mlp.gate.weight"] = lw["router"]
             for e in range(lw["experts_gate_up"].shape[0]):
                 gu = lw["experts_gate_up"][e]
                 t[f"{L}mlp.experts.{e}.gate_proj.weight"], t[f"{L}mlp.experts.{e}.up_proj.weight"] = gu[0::2], gu[1::2]
                 t[f"{L}mlp.experts.{e}.down_proj.weight"] = lw["experts_down"][e]
+        elif cfg.model_type == "phi3":        # gate rows then up rows in one tensor
+            t[L + "mlp.gate_up_proj.weight"] = torch.cat([lw["w_gate_up"][0::2], lw["w_gate_up"][1::2]], 0)
+            t[L + "mlp.down_proj.weight"] = lw["w_down"]
         else:
             t[L + "mlp.gate_proj.weight"], t[L + "mlp.up_proj.weight"] = lw["w_gate_up"][0::2], lw["w_gate_up"][1::2]
             t[L + "mlp.down_proj.weight"] = lw["w_down"]
@@ -685,7 +697,12 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
           "head_dim": d, "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
           "tie_word_embeddings": cfg.tie_word_embeddings, "torch_dtype": cfg.dtype, "attention_bias": cfg.attention_bias,
           "max_position_embeddings": cfg.max_position_embeddings}
-    if cfg.model_type == "gpt_oss":
+    if cfg.model_type == "phi3":
+        hf.update(pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    if cfg.model_type == "mixtral":
+        hf.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
+                  intermediate_size=cfg.moe_intermediate_size)
+    elif cfg.model_type == "gpt_oss":
         hf.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   sliding_window=cfg.sliding_window, layer_types=cfg.layer_types, swiglu_limit=cfg.swiglu_limit,
                   rope_scaling=cfg.rope_scaling)

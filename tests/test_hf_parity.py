@@ -25,6 +25,8 @@ FAMILIES = [
     ("olmo3", "tiny-olmo2", dict(model_type="olmo3", sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     ("qwen3_moe", "tiny-qwen3-moe", {}),
     ("gpt_oss", "tiny-gpt-oss", {}),
+    ("mixtral", "tiny-qwen3-moe", dict(model_type="mixtral", qk_norm=False)),
+    ("phi3", "tiny-llama", dict(model_type="phi3")),
 ]
 
 
