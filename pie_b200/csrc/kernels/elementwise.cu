@@ -114,6 +114,29 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
     }
 }
 
+// GLU over INTERLEAVED columns (gate_0, up_0, gate_1, up_1, ...), the layout of the fused gate / up weights:
+// out[r, j] = act(gu[r, 2j]) * gu[r, 2j + 1]. ACT 0: SiLU, 1: tanh-approximated GELU (Gemma's GeGLU).
+template <int ACT>
+__global__ void glu_interleaved_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long total_vec) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
+        const bf16x8* src = reinterpret_cast<const bf16x8*>(gu) + 2 * i;
+        float a[8], b[8], o[8];
+        unpack8(src[0], a);
+        unpack8(src[1], b);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float g = k < 4 ? a[2 * k] : b[2 * k - 8], u = k < 4 ? a[2 * k + 1] : b[2 * k - 7];
+            if (ACT == 0) {
+                o[k] = g / (1.f + __expf(-g)) * u;
+            } else {
+                const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+                o[k] = 0.5f * g * (1.f + t) * u;
+            }
+        }
+        reinterpret_cast<bf16x8*>(out)[i] = pack8(o);
+    }
+}
+
 // -------------------------------------------- q/k norm + rope + paged KV write
 // One warp per (token, head) of the packed qkv row [Hq*d | Hkv*d | Hkv*d].
 // q heads: optional RMSNorm over the head (weight qn[d]) then rotate-half RoPE,
@@ -343,6 +366,18 @@ PIE_API int pie_swiglu(const void* gate_up, void* out, long rows, int inter, cud
     const long total = rows * (inter / 8);
     const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
     swiglu_kernel<<<blocks, 256, 0, st>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+    return (int)cudaGetLastError();
+}
+
+PIE_API int pie_glu_interleaved(const void* gate_up, void* out, long rows, int inter, int act, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (inter % 8 || act < 0 || act > 1) return (int)cudaErrorInvalidValue;
+    const long total = rows * (inter / 8);
+    const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
+    if (act == 0)
+        glu_interleaved_kernel<0><<<blocks, 256, 0, st>>>((const bf16*)gate_up, (bf16*)out, total);
+    else
+        glu_interleaved_kernel<1><<<blocks, 256, 0, st>>>((const bf16*)gate_up, (bf16*)out, total);
     return (int)cudaGetLastError();
 }
 

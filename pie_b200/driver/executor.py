@@ -181,6 +181,12 @@ class TorchDriver:
             from .recurrent import RecurrentStateCache
             self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
             use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet
+        # soft-capped attention scores (Gemma-2) run as torch ops over a host plan: no decode kernel, no graphs
+        self.host_attention = bool(cfg.attn_softcap)
+        if self.host_attention:
+            use_graphs = False
+            if kv_dtype == "fp8_e4m3":
+                raise NotImplementedError("fp8 KV pages with soft-capped attention scores")
         self.max_requests, self.max_tokens = max_requests, max_tokens
         self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
         self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
@@ -312,7 +318,8 @@ class TorchDriver:
             max_page_refs=self.max_page_refs, max_logit_rows=self.max_rows, max_prob_rows=self.max_rows,
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
-            tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0)
+            tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0,
+            cohort_decode=self.rs is None and not self.host_attention)
 
     # ------------------------------------------------------------------ request -> slab
     def _derive(self, req: ForwardRequest):
@@ -525,6 +532,22 @@ class TorchDriver:
             return req.mask_runs[a:b]
         return [[0, kl - ql + i + 1] for i in range(ql)]
 
+    def _host_batch(self, req: ForwardRequest, qlens, kv_lens, custom: bool):
+        """The fire's attention work as host arrays (and boolean masks): the form the torch statement of the op takes."""
+        masks = None
+        if custom:
+            from ..ops.reference import brle_to_bool
+            masks = []
+            for i in range(req.num_requests):
+                ql, kl = int(qlens[i]), int(kv_lens[i])
+                if req.has_user_mask[i]:
+                    runs = self._mask_rows_for_request(req, i, ql, kl)
+                    masks.append(np.stack([brle_to_bool(rr, kl).numpy() for rr in runs]) if ql else None)
+                else:
+                    masks.append(None)
+        return ops.AttnBatch(np.asarray(req.qo_indptr), np.asarray(req.kv_page_indptr),
+                             np.asarray(req.kv_page_indices), kv_lens, masks, self.window_left)
+
     def _run_general(self, req: ForwardRequest, qlens, slots, kv_lens) -> torch.Tensor:
         s = self.slab
         n, r = req.num_tokens, req.num_requests
@@ -560,20 +583,10 @@ class TorchDriver:
             fi = ForwardInputs(s.d("tokens", n), s.d("positions", n), s.d("slots", n), plan,
                                logit_rows=s.d("logit_rows", len(rows)), is_decode=False,
                                attn_num_pages=len(req.kv_page_indices))
+            if self.host_attention:
+                fi.attn_host = self._host_batch(req, qlens, kv_lens, custom)
         else:
-            masks = None
-            if custom:
-                from ..ops.reference import brle_to_bool
-                masks = []
-                for i in range(r):
-                    ql, kl = int(qlens[i]), int(kv_lens[i])
-                    if req.has_user_mask[i]:
-                        runs = self._mask_rows_for_request(req, i, ql, kl)
-                        masks.append(np.stack([brle_to_bool(rr, kl).numpy() for rr in runs]) if ql else None)
-                    else:
-                        masks.append(None)
-            batch = ops.AttnBatch(np.asarray(req.qo_indptr), np.asarray(req.kv_page_indptr),
-                                  np.asarray(req.kv_page_indices), kv_lens, masks, self.window_left)
+            batch = self._host_batch(req, qlens, kv_lens, custom)
             fi = ForwardInputs(torch.from_numpy(np.ascontiguousarray(req.tokens, dtype=np.int32)),
                                torch.from_numpy(np.ascontiguousarray(req.positions, dtype=np.int32)),
                                torch.from_numpy(slots.astype(np.int32)), batch,
@@ -715,7 +728,8 @@ class TorchDriver:
         nslots = len(req.slot_samplers)
         self._lora_bindings = self._bind_adapters(req)
         decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None
-                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None)
+                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None
+                  and not self.host_attention)
         if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
             # followers must draw the same tokens: fix the per-fire seeds before publishing
             from dataclasses import replace as _replace

@@ -174,6 +174,7 @@ class Capabilities:
     tp_size: int = 1
     system_speculation: bool = False
     rs_cache_slots: int = 0
+    cohort_decode: bool = True      # False: no array-form decode step (`decode_async`); the runtime steps per request
 
     def to_json(self) -> str:
         return json.dumps(asdict(self))

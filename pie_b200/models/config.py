@@ -13,11 +13,14 @@ from typing import Optional
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 # `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3",
-                         "gpt_oss", "qwen3_5", "qwen3_next", "mamba2_hybrid")
+                         "gpt_oss", "qwen3_5", "qwen3_next", "mamba2_hybrid", "gemma2", "gemma3_text", "gemma3")
 MAMBA_TYPES = {"mamba2_hybrid"}         # Mamba-2 (state-space) mixers in llama-like blocks, between full-attention layers
 GDN_TYPES = {"qwen3_5", "qwen3_next"}   # hybrids: Gated DeltaNet (linear attention) layers between full-attention layers
 POST_NORM = {"olmo2", "olmo3"}       # same block with the norms after attention / MLP and q, k norms over all heads
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
+# Gemma-2 / Gemma-3: norms before AND after attention and MLP, gains stored as (w - 1), GeGLU, scaled embeddings,
+# alternating local / global layers (Gemma-3: a RoPE base of their own for the local ones; Gemma-2: soft-capped logits)
+GEMMA_TYPES = {"gemma2", "gemma3_text", "gemma3"}
 
 
 @dataclass
@@ -42,6 +45,14 @@ class ModelConfig:
     layer_types: Optional[list] = None   # per layer "sliding_attention" | "full_attention" (GPT-OSS); None: all alike
     attention_sinks: bool = False   # GPT-OSS: a learned per-head logit in every softmax denominator
     o_bias: bool = False            # bias on the attention output projection
+    sandwich_norm: bool = False     # Gemma-2/3: h += norm(attn(norm(h))); h += norm(mlp(norm(h)))
+    norm_plus_one: bool = False     # checkpoints store RMSNorm gains as (w - 1); the loader adds the 1
+    hidden_act: str = "silu"        # gate activation of the GLU: "silu" | "gelu_tanh"
+    embed_scale: float = 1.0        # embeddings are multiplied by this (Gemma: sqrt(hidden_size))
+    query_pre_attn_scalar: float = 0.0   # attention scale is this ** -0.5 (0: head_dim)
+    attn_softcap: float = 0.0       # scores pass through cap * tanh(s / cap) before the softmax (0: off)
+    final_softcap: float = 0.0      # same for the output logits
+    rope_local_theta: float = 0.0   # RoPE base of the sliding-window layers, unscaled (0: same table as the others)
     # mixture of experts
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -142,6 +153,20 @@ class ModelConfig:
     @staticmethod
     def from_hf(cfg: dict, name: str = "") -> "ModelConfig":
         mt = cfg.get("model_type", "llama")
+        if mt == "gemma3" and "text_config" in cfg:       # multimodal wrapper: the language model's own section
+            cfg = dict(cfg["text_config"], model_type="gemma3_text")
+            mt = "gemma3_text"
+        cfg = _flatten_rope_parameters(dict(cfg))
+        gemma = mt in GEMMA_TYPES
+        if gemma:
+            cfg.setdefault("head_dim", 256)
+            cfg.setdefault("tie_word_embeddings", True)
+            cfg.setdefault("rms_norm_eps", 1e-6)
+            if cfg.get("layer_types") is None:
+                # Gemma-2 alternates local / global; Gemma-3 runs `sliding_window_pattern - 1` local layers per global one
+                pat = int(cfg.get("sliding_window_pattern") or cfg.get("_sliding_window_pattern") or (2 if mt == "gemma2" else 6))
+                cfg["layer_types"] = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention"
+                                      for i in range(cfg["num_hidden_layers"])]
         heads = cfg["num_attention_heads"]
         hd = cfg.get("head_dim") or cfg["hidden_size"] // heads
         q = cfg.get("quantization_config") or {}
@@ -162,14 +187,20 @@ class ModelConfig:
             rope_theta=cfg.get("rope_theta", 10000.0),
             rope_scaling=cfg.get("rope_scaling"),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2", "olmo3") or mt in GDN_TYPES or cfg.get("use_qk_norm", False),
+            qk_norm=mt in ("qwen3", "qwen3_moe", "olmo2", "olmo3", "gemma3_text") or mt in GDN_TYPES or cfg.get("use_qk_norm", False),
+            sandwich_norm=gemma, norm_plus_one=gemma,
+            hidden_act="gelu_tanh" if gemma or "gelu" in str(cfg.get("hidden_act", "")) else "silu",
+            embed_scale=float(cfg["hidden_size"]) ** 0.5 if gemma else 1.0,
+            query_pre_attn_scalar=float(cfg.get("query_pre_attn_scalar") or 0.0) if gemma else 0.0,
+            attn_softcap=float(cfg.get("attn_logit_softcapping") or 0.0), final_softcap=float(cfg.get("final_logit_softcapping") or 0.0),
+            rope_local_theta=float(cfg.get("rope_local_base_freq") or 0.0) if mt == "gemma3_text" else 0.0,
             post_norm=mt in POST_NORM,
             attention_bias=cfg.get("attention_bias", mt in ("qwen2", "gpt_oss")),
             # Qwen2 gates the window on use_sliding_window; Mistral applies it whenever it is set
             sliding_window=(cfg.get("sliding_window") or -1)
-            if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss", "olmo3")) else -1,
+            if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss", "olmo3") or gemma) else -1,
             # OLMo-3 and GPT-OSS alternate sliding-window and full-attention layers
-            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") or mt in GDN_TYPES or mt in MAMBA_TYPES else None,
+            layer_types=cfg.get("layer_types") if mt in ("gpt_oss", "olmo3") or gemma or mt in GDN_TYPES or mt in MAMBA_TYPES else None,
             mamba_num_heads=cfg.get("mamba_num_heads", 0), mamba_head_dim=cfg.get("mamba_head_dim", 0),
             ssm_state_size=cfg.get("ssm_state_size", 0), mamba_n_groups=cfg.get("mamba_n_groups", 1),
             mamba_norm_grouped=bool(cfg.get("mamba_norm_grouped", False)),
@@ -196,6 +227,26 @@ class ModelConfig:
         p = Path(path)
         with open(p / "config.json") as f:
             return ModelConfig.from_hf(json.load(f), name=p.name)
+
+
+def _flatten_rope_parameters(cfg: dict) -> dict:
+    """Newer `config.json` files carry RoPE settings as `rope_parameters`: one dict (`rope_theta`, `rope_type`,
+    scaling fields), or one such dict per layer type. Rewrites them as the older `rope_theta` / `rope_scaling` /
+    `rope_local_base_freq` keys, which win when both are present."""
+    rp = cfg.get("rope_parameters")
+    if not isinstance(rp, dict):
+        return cfg
+    local = None
+    if "full_attention" in rp or "sliding_attention" in rp:
+        local = rp.get("sliding_attention")
+        rp = rp.get("full_attention") or local or {}
+    if "rope_theta" in rp:
+        cfg.setdefault("rope_theta", rp["rope_theta"])
+    if rp.get("rope_type", "default") != "default" and not cfg.get("rope_scaling"):
+        cfg["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+    if local and "rope_theta" in local:
+        cfg.setdefault("rope_local_base_freq", local["rope_theta"])
+    return cfg
 
 
 # Architectures named by the benchmark configurations (random-init weights of these shapes).
@@ -250,6 +301,23 @@ PRESETS = {
                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000,
                         layer_types=["mamba2", "mamba2", "full_attention"], mamba_num_heads=8, mamba_head_dim=32,
                         ssm_state_size=16, mamba_n_groups=2),
+    "gemma-3-27b": dict(model_type="gemma3_text", hidden_size=5376, intermediate_size=21504, num_hidden_layers=62,
+                        num_attention_heads=32, num_key_value_heads=16, head_dim=128, vocab_size=262208,
+                        rope_theta=1e6, rope_scaling=dict(rope_type="linear", factor=8.0), rope_local_theta=10000.0,
+                        rms_norm_eps=1e-6, qk_norm=True, sandwich_norm=True, norm_plus_one=True, hidden_act="gelu_tanh",
+                        embed_scale=5376 ** 0.5, query_pre_attn_scalar=168.0, sliding_window=1024, tie_word_embeddings=True,
+                        layer_types=(["sliding_attention"] * 5 + ["full_attention"]) * 10 + ["sliding_attention"] * 2),
+    "tiny-gemma3": dict(model_type="gemma3_text", hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000, rope_theta=1e6,
+                        rope_scaling=dict(rope_type="linear", factor=8.0), rope_local_theta=10000.0, rms_norm_eps=1e-6,
+                        qk_norm=True, sandwich_norm=True, norm_plus_one=True, hidden_act="gelu_tanh", embed_scale=16.0,
+                        query_pre_attn_scalar=48.0, sliding_window=8, tie_word_embeddings=True,
+                        layer_types=["sliding_attention", "sliding_attention", "full_attention"], dtype="float32"),
+    "tiny-gemma2": dict(model_type="gemma2", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000, rope_theta=10000.0,
+                        rms_norm_eps=1e-6, sandwich_norm=True, norm_plus_one=True, hidden_act="gelu_tanh", embed_scale=16.0,
+                        query_pre_attn_scalar=48.0, sliding_window=8, tie_word_embeddings=True, attn_softcap=50.0,
+                        final_softcap=30.0, layer_types=["sliding_attention", "full_attention"], dtype="float32"),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,

@@ -56,6 +56,7 @@ def Interleave(a, b): return Op("interleave", {}, [a, b])
 def Stack(xs): return Op("stack", {}, list(xs))
 def ExpandRows(x, factor, like): return Op("expand_rows", {"factor": factor, "like": like}, [x])
 def Transpose(x, a, b): return Op("transpose", {"a": a, "b": b}, [x])
+def AddScalar(x, value): return Op("add_scalar", {"value": value}, [x])
 def Mxfp4(blocks, scales): return Op("mxfp4", {}, [blocks, scales])
 
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
@@ -136,8 +137,13 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
     names = set(names)
     T, r, d = tp_size, tp_rank, cfg.head_dim
     kv0, kvn = kv_head_range(cfg, r, T)
-    pre = "model." if any(n.startswith("model.") for n in names) else ""
+    # the language model's tensors may sit under a prefix ("model.", or a multimodal wrapper's "model.language_model.")
+    pre = min((n[:-len("embed_tokens.weight")] for n in names if n.endswith("embed_tokens.weight")), key=len, default="")
     att: Dict[str, Op] = {}
+
+    def gain(n):
+        """RMSNorm gain; Gemma checkpoints store (gain - 1)."""
+        return AddScalar(Op("float", {}, [w(n)]), 1.0) if cfg.norm_plus_one else w(n)
 
     def w(n):
         if n not in names:
@@ -152,7 +158,7 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         return QLin(w(n))
 
     att["embed"] = w(f"{pre}embed_tokens.weight")
-    att["final_norm"] = w(f"{pre}norm.weight")
+    att["final_norm"] = gain(f"{pre}norm.weight")
     head = w("lm_head.weight") if "lm_head.weight" in names else w(f"{pre}embed_tokens.weight")
     att["lm_head"] = Shard(head, 0, r, T)
     for li in range(cfg.num_hidden_layers):
@@ -194,7 +200,10 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
             QLin.interleave(lin(L + "mlp.gate_proj.weight"), lin(L + "mlp.up_proj.weight")).attach(att, P + "w_gate_up")
             lin(L + "mlp.down_proj.weight").attach(att, P + "w_down")
             continue
-        if cfg.post_norm:       # OLMo-2: norms follow the sub-blocks, there is no input norm
+        if cfg.sandwich_norm:   # Gemma-2/3: a norm on the way into and out of each sub-block
+            att[P + "ln1"], att[P + "ln_pa"] = gain(L + "input_layernorm.weight"), gain(L + "post_attention_layernorm.weight")
+            att[P + "ln2"], att[P + "ln_pf"] = gain(L + "pre_feedforward_layernorm.weight"), gain(L + "post_feedforward_layernorm.weight")
+        elif cfg.post_norm:     # OLMo-2: norms follow the sub-blocks, there is no input norm
             att[P + "ln2"] = w(L + "post_attention_layernorm.weight")
             att[P + "ln3"] = w(L + "post_feedforward_layernorm.weight")
         else:
@@ -226,8 +235,8 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
             att[P + "k_norm"] = Rows(w(L + "self_attn.k_norm.weight"), kv0 * d, kvn * d) if T > 1 \
                 else w(L + "self_attn.k_norm.weight")
         elif L + "self_attn.q_norm.weight" in names:
-            att[P + "q_norm"] = w(L + "self_attn.q_norm.weight")
-            att[P + "k_norm"] = w(L + "self_attn.k_norm.weight")
+            att[P + "q_norm"] = gain(L + "self_attn.q_norm.weight")
+            att[P + "k_norm"] = gain(L + "self_attn.k_norm.weight")
         mixtral = L + "block_sparse_moe.gate.weight" in names      # Mixtral names: w1 = gate, w3 = up, w2 = down
         if cfg.is_moe and L + "mlp.router.weight" in names:
             # GPT-OSS: experts stacked in one tensor, gate/up columns already interleaved; bf16 checkpoints
@@ -341,6 +350,8 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
         return xs[0].squeeze(op.args["dim"])
     if k == "float":
         return xs[0].float()
+    if k == "add_scalar":
+        return xs[0] + op.args["value"]
     if k == "transpose":
         return xs[0].transpose(op.args["a"], op.args["b"])
     if k == "mxfp4":
@@ -387,7 +398,7 @@ def infer_shape(op: Op, reader) -> Tuple[int, ...]:
         if any(y != x for y in xs):
             raise LoaderTypeError(f"stack of unequal shapes {sorted(set(xs))}")
         return (len(xs),) + x
-    if k in ("zeros_like", "float"):
+    if k in ("zeros_like", "float", "add_scalar"):
         return x
     if k == "squeeze":
         d = op.args["dim"]
@@ -416,7 +427,7 @@ def expected_shapes(cfg: ModelConfig, tp_size: int = 1, ep: bool = False) -> Dic
     E = cfg.num_experts
     el, il = (E // T, I) if (ep and T > 1) else (E, I // T)
     out = {"embed": (cfg.vocab_size, H), "final_norm": (H,), "lm_head": (cfg.vocab_size // T, H),
-           "ln1": (H,), "ln2": (H,), "ln3": (H,), "wqkv": ((hq + 2 * hkv) * d, H), "wo": (H, hq * d),
+           "ln1": (H,), "ln2": (H,), "ln3": (H,), "ln_pa": (H,), "ln_pf": (H,), "wqkv": ((hq + 2 * hkv) * d, H), "wo": (H, hq * d),
            "bqkv": ((hq + 2 * hkv) * d,), "bo": (H,), "sinks": (hq,),
            "w_gate_up": (2 * cfg.intermediate_size // T, H), "w_down": (H, cfg.intermediate_size // T),
            "router": (E, H), "router_bias": (E,), "experts_gate_up": (el, 2 * il, H), "experts_down": (el, H, il),
@@ -617,7 +628,8 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
     p = Path(path)
     p.mkdir(parents=True, exist_ok=True)
     d, hq, hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
-    t: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": weights["embed"], "model.norm.weight": weights["final_norm"]}
+    ungain = (lambda g: g.float() - 1.0) if cfg.norm_plus_one else (lambda g: g)      # Gemma stores (gain - 1)
+    t: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": weights["embed"], "model.norm.weight": ungain(weights["final_norm"])}
     if not cfg.tie_word_embeddings:
         t["lm_head.weight"] = weights["lm_head"]
     for li, lw in enumerate(weights["layers"]):
@@ -648,7 +660,10 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
             t[L + "mlp.gate_proj.weight"], t[L + "mlp.up_proj.weight"] = lw["w_gate_up"][0::2], lw["w_gate_up"][1::2]
             t[L + "mlp.down_proj.weight"] = lw["w_down"]
             continue
-        if "ln3" in lw:
+        if "ln_pa" in lw:
+            t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = ungain(lw["ln1"]), ungain(lw["ln_pa"])
+            t[L + "pre_feedforward_layernorm.weight"], t[L + "post_feedforward_layernorm.weight"] = ungain(lw["ln2"]), ungain(lw["ln_pf"])
+        elif "ln3" in lw:
             t[L + "post_attention_layernorm.weight"], t[L + "post_feedforward_layernorm.weight"] = lw["ln2"], lw["ln3"]
         else:
             t[L + "input_layernorm.weight"], t[L + "post_attention_layernorm.weight"] = lw["ln1"], lw["ln2"]
@@ -662,7 +677,7 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
             bq, bk, bv = lw["bqkv"].split([hq * d, hkv * d, hkv * d], 0)
             t[L + "self_attn.q_proj.bias"], t[L + "self_attn.k_proj.bias"], t[L + "self_attn.v_proj.bias"] = bq, bk, bv
         if "q_norm" in lw:
-            t[L + "self_attn.q_norm.weight"], t[L + "self_attn.k_norm.weight"] = lw["q_norm"], lw["k_norm"]
+            t[L + "self_attn.q_norm.weight"], t[L + "self_attn.k_norm.weight"] = ungain(lw["q_norm"]), ungain(lw["k_norm"])
         if "bo" in lw:
             t[L + "self_attn.o_proj.bias"] = lw["bo"]
         if "sinks" in lw:
@@ -699,6 +714,12 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
           "max_position_embeddings": cfg.max_position_embeddings}
     if cfg.model_type == "phi3":
         hf.update(pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    if cfg.sandwich_norm:
+        hf.update(layer_types=cfg.layer_types, sliding_window=cfg.sliding_window, query_pre_attn_scalar=int(cfg.query_pre_attn_scalar or cfg.head_dim),
+                  hidden_activation="gelu_pytorch_tanh", attn_logit_softcapping=cfg.attn_softcap or None,
+                  final_logit_softcapping=cfg.final_softcap or None, rope_scaling=cfg.rope_scaling)
+        if cfg.rope_local_theta:
+            hf.update(rope_local_base_freq=cfg.rope_local_theta)
     if cfg.model_type == "mixtral":
         hf.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   intermediate_size=cfg.moe_intermediate_size)

@@ -32,6 +32,7 @@ class ForwardInputs:
     positions: torch.Tensor       # int32 [N]
     slots: torch.Tensor           # int32 [N]  KV slot (page*page_size+offset) of each new token
     attn: object                  # ops.DecodePlan | ops.PrefillPlan | ops.AttnBatch (CPU)
+    attn_host: Optional[object] = None     # ops.AttnBatch of the same work, for attention variants that run as torch ops
     attn_num_pages: Optional[int] = None   # page references of this batch (prefill plans; the slab segment is larger)
     logit_rows: Optional[torch.Tensor] = None   # int32 rows of the hidden state that need logits
     rs: Optional[object] = None   # driver.recurrent.RecurrentInputs for models with Gated DeltaNet layers
@@ -55,8 +56,11 @@ class Transformer:
         self.hq = cfg.num_attention_heads // t
         self.hkv = max(1, cfg.num_key_value_heads // t)
         self.d = cfg.head_dim
-        self.sm_scale = reference.rope_attention_factor(cfg.rope_scaling) ** 2 / math.sqrt(cfg.head_dim)
+        self.sm_scale = reference.rope_attention_factor(cfg.rope_scaling) ** 2 / math.sqrt(cfg.query_pre_attn_scalar or cfg.head_dim)
         self.inv_freq = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, self.device)
+        # Gemma-3: sliding-window layers rotate with their own, unscaled base
+        self.inv_freq_local = reference.rope_inv_freq(cfg.head_dim, cfg.rope_local_theta, None, self.device) \
+            if cfg.rope_local_theta else None
         self.gemm_backend = gemm_backend if self.device.type == "cuda" else "torch"
         self.vocab_local = weights["lm_head"].shape[0] * (self.par.tp_size if self.par.comm is not None else 1)
         # fp8 KV pages: per-(token, head) scales [layers, pages, 2, hkv, page] set by the driver, else None
@@ -86,8 +90,10 @@ class Transformer:
         the whole range and the kernels mask), and its attention sinks where the model has them."""
         wl = self.cfg.layer_window_left(li) if self.cfg.layer_types is not None else None
         sinks = lw.get("sinks") if lw is not None else None
-        if not q.is_cuda:
-            return ops.paged_attention_cpu(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks=sinks)
+        if not q.is_cuda or self.cfg.attn_softcap:
+            # soft-capped scores (Gemma-2) have no CUDA kernel here: the torch statement of the op runs on either device
+            return ops.paged_attention_cpu(q, kv_layer, fi.attn_host or fi.attn, self.sm_scale, window_left=wl, sinks=sinks,
+                                           softcap=self.cfg.attn_softcap)
         sl2 = None
         if sinks is not None:
             sl2 = lw.get("sinks_log2")
@@ -106,9 +112,19 @@ class Transformer:
             return ops.paged_prefill_attention(q, dense, plan, self.sm_scale, window_left=wl, sinks_log2=sl2)
         return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2)
 
+    def _glu(self, x, lw):
+        """act(gate) * up of the fused, interleaved gate / up projection: SiLU in the GEMM's epilogue, GELU after it."""
+        if self.cfg.hidden_act == "silu":
+            return self._gemm(x, lw["w_gate_up"], swiglu=True)
+        return ops.glu_interleaved(self._gemm(x, lw["w_gate_up"]), self.cfg.hidden_act)
+
     def _mlp(self, x, lw, h):
-        act = self._gemm(x, lw["w_gate_up"], swiglu=True)
-        return self._row_parallel(act, lw["w_down"], h)
+        return self._row_parallel(self._glu(x, lw), lw["w_down"], h)
+
+    def _rope_table(self, li: int):
+        if self.inv_freq_local is not None and self.cfg.layer_window_left(li) >= 0:
+            return self.inv_freq_local
+        return self.inv_freq
 
     def _row_parallel(self, a, w, h):
         """h + a @ w.T (a @ w.T when h is None), summed over the tensor-parallel group."""
@@ -123,7 +139,8 @@ class Transformer:
 
     def _fused_tp(self) -> bool:
         return self.par.tp_size > 1 and self.par.comm is not None and getattr(self.par.comm, "fused", False) \
-            and self.device.type == "cuda" and not self.cfg.post_norm and self.cfg.model_type != "gpt_oss"
+            and self.device.type == "cuda" and not self.cfg.post_norm and not self.cfg.sandwich_norm \
+            and self.cfg.model_type != "gpt_oss"
 
     def _forward_hidden_tp(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
         """Tensor-parallel forward over the fused kernels: the residual stream is row-sharded,
@@ -166,6 +183,9 @@ class Transformer:
             h = self.par.comm.all_reduce(h)
         else:
             h = ops.embed(fi.tokens, w["embed"])
+        if cfg.embed_scale != 1.0:
+            # the factor is rounded to the activation dtype first, as the checkpoints' own code does
+            h = h * torch.tensor(cfg.embed_scale, dtype=h.dtype).item()
         n = h.shape[0]
         for li in range(cfg.num_hidden_layers):
             lw = w["layers"][li]
@@ -211,10 +231,19 @@ class Transformer:
                     qkv[:, :qs] = ops.rmsnorm(qkv[:, :qs].contiguous(), qn, cfg.rms_norm_eps)
                     qkv[:, qs:qs + ks] = ops.rmsnorm(qkv[:, qs:qs + ks].contiguous(), kn, cfg.rms_norm_eps)
                 qn = kn = None
-            q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, qn, kn, kv_cache[li],
+            q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self._rope_table(li), qn, kn, kv_cache[li],
                                          self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps,
                                          kv_scale=self.kv_scale[li] if self.kv_scale is not None else None)
             a = self._attention(q, kv_cache[li], fi, li, lw).reshape(n, self.hq * self.d)
+            if cfg.sandwich_norm:
+                # Gemma-2/3: both sublayers are normalised on the way in and on the way out
+                o = self._row_parallel(a, lw["wo"], None)
+                if fi.lora:
+                    o = apply_lora(fi.lora, li, "o", a, o)
+                h = h + ops.rmsnorm(o, lw["ln_pa"], cfg.rms_norm_eps)
+                m = self._row_parallel(self._glu(ops.rmsnorm(h, lw["ln2"], cfg.rms_norm_eps), lw), lw["w_down"], None)
+                h = h + ops.rmsnorm(m, lw["ln_pf"], cfg.rms_norm_eps)
+                continue
             if post:
                 if "experts_gate_up" in lw:
                     raise NotImplementedError("post-norm blocks with experts")
@@ -222,8 +251,7 @@ class Transformer:
                 if fi.lora:
                     o = apply_lora(fi.lora, li, "o", a, o)
                 h = h + ops.rmsnorm(o, lw["ln2"], cfg.rms_norm_eps)
-                act = self._gemm(h, lw["w_gate_up"], swiglu=True)
-                h = h + ops.rmsnorm(self._row_parallel(act, lw["w_down"], None), lw["ln3"], cfg.rms_norm_eps)
+                h = h + ops.rmsnorm(self._row_parallel(self._glu(h, lw), lw["w_down"], None), lw["ln3"], cfg.rms_norm_eps)
                 continue
             h = self._row_parallel(a, lw["wo"], h)
             if "bo" in lw:
@@ -248,6 +276,8 @@ class Transformer:
         y = self._gemm(x, self.w["lm_head"])
         if self.par.tp_size > 1 and self.par.comm is not None:
             y = self.par.comm.all_gather_logits(y)
+        if self.cfg.final_softcap:
+            y = (torch.tanh(y.float() / self.cfg.final_softcap) * self.cfg.final_softcap).to(y.dtype)
         return y
 
     @property
@@ -333,10 +363,12 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
     """Independent dense (non-paged) fp32 forward of the same weights for one sequence:
     RMSNorm -> QKV -> rotate-half RoPE -> causal attention -> SwiGLU. Returns logits [T, V].
     This is the token-for-token oracle of the paged engine path."""
-    x = w["embed"].float()[tokens.long()]
+    x = w["embed"].float()[tokens.long()] * cfg.embed_scale
     t = x.shape[0]
     pos = torch.arange(t)
-    inv = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
+    inv_global = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
+    inv_local = reference.rope_inv_freq(cfg.head_dim, cfg.rope_local_theta, None) if cfg.rope_local_theta else inv_global
+    act = (lambda g: torch.nn.functional.gelu(g, approximate="tanh")) if cfg.hidden_act == "gelu_tanh" else torch.nn.functional.silu
     hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
 
     def norm(v, g):
@@ -365,10 +397,14 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
             k = norm(k.reshape(t, hkv * d), lw["k_norm"]).reshape(t, hkv, d)
         elif "q_norm" in lw:
             q, k = norm(q, lw["q_norm"]), norm(k, lw["k_norm"])
+        inv = inv_local if cfg.layer_window_left(li) >= 0 else inv_global
         q, k = reference._rope(q, pos, inv), reference._rope(k, pos, inv)
         k = k.repeat_interleave(hq // hkv, dim=1)
         v = v.repeat_interleave(hq // hkv, dim=1)
-        s = torch.einsum("qhd,khd->hqk", q, k) * (reference.rope_attention_factor(cfg.rope_scaling) ** 2 / math.sqrt(d))
+        s = torch.einsum("qhd,khd->hqk", q, k) * (reference.rope_attention_factor(cfg.rope_scaling) ** 2
+                                                  / math.sqrt(cfg.query_pre_attn_scalar or d))
+        if cfg.attn_softcap:
+            s = torch.tanh(s / cfg.attn_softcap) * cfg.attn_softcap
         s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
         if cfg.layer_window_left(li) >= 0:       # a query sees itself and the sliding_window - 1 keys before it
             s = s.masked_fill(torch.tril(torch.ones(t, t, dtype=torch.bool), -cfg.sliding_window)[None], float("-inf"))
@@ -377,10 +413,15 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
             a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1)[..., :t], v).reshape(t, hq * d)
         else:
             a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(t, hq * d)
+        if cfg.sandwich_norm:
+            x = x + norm(a @ lw["wo"].float().t(), lw["ln_pa"])
+            gu = norm(x, lw["ln2"]) @ lw["w_gate_up"].float().t()
+            x = x + norm((act(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t(), lw["ln_pf"])
+            continue
         if cfg.post_norm:
             x = x + norm(a @ lw["wo"].float().t(), lw["ln2"])
             gu = x @ lw["w_gate_up"].float().t()
-            x = x + norm((torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t(), lw["ln3"])
+            x = x + norm((act(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t(), lw["ln3"])
             continue
         x = x + a @ lw["wo"].float().t()
         if "bo" in lw:
@@ -391,5 +432,6 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> 
             x = x + moe_reference(cfg, xn, lw)
         else:
             gu = xn @ lw["w_gate_up"].float().t()
-            x = x + (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t()
-    return norm(x, w["final_norm"]) @ w["lm_head"].float().t()
+            x = x + (act(gu[:, 0::2]) * gu[:, 1::2]) @ lw["w_down"].float().t()
+    y = norm(x, w["final_norm"]) @ w["lm_head"].float().t()
+    return torch.tanh(y / cfg.final_softcap) * cfg.final_softcap if cfg.final_softcap else y

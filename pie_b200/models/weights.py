@@ -9,6 +9,8 @@ Runtime layout per layer (this rank's shard under tensor parallelism):
   w_down     [H, I_local]
   ln1, ln2   [H]; q_norm, k_norm [d] (Qwen3); bqkv (Qwen2)
   OLMo-2 (post-norm): no ln1; ln2 follows attention, ln3 follows the MLP; q_norm [hq*d], k_norm [hkv*d]
+  Gemma-2/3 (sandwich norms): ln1 / ln2 before attention / MLP, ln_pa / ln_pf on their outputs before the
+  residual add; gains hold the full multiplier (the loader adds the checkpoint's implicit 1)
 MoE layers replace w_gate_up / w_down by router [E, H], experts_gate_up [E_local, 2*Im, H]
 (interleaved) and experts_down [E_local, H, Im].
 
@@ -132,6 +134,8 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
         if cfg.post_norm:
             # norm gains away from 1 so that a misplaced norm shows in the tests
             lw = {"ln2": 1 + gen.normal(H, std=0.1), "ln3": 1 + gen.normal(H, std=0.1)}
+        elif cfg.sandwich_norm:
+            lw = {k: 1 + gen.normal(H, std=0.1) for k in ("ln1", "ln_pa", "ln2", "ln_pf")}
         else:
             lw = {"ln1": ones(H), "ln2": ones(H)}
         wq, wk, wv = gen.normal(hq * d, H), gen.normal(hkv * d, H), gen.normal(hkv * d, H)
@@ -150,6 +154,8 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             # norms over all heads together: a rank keeps the gains of its own heads
             qn, kn = 1 + gen.normal(hq * d, std=0.1), 1 + gen.normal(hkv * d, std=0.1)
             lw["q_norm"], lw["k_norm"] = shard_rows(qn, r, T).contiguous(), kn[kv0 * d:(kv0 + kvn) * d].contiguous()
+        elif cfg.qk_norm and cfg.sandwich_norm:
+            lw["q_norm"], lw["k_norm"] = 1 + gen.normal(d, std=0.1), 1 + gen.normal(d, std=0.1)
         elif cfg.qk_norm:
             lw["q_norm"], lw["k_norm"] = ones(d), ones(d)
         if cfg.is_moe:

@@ -119,6 +119,22 @@ def swiglu(gate_up, out=None):
     return out
 
 
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def glu_interleaved(gate_up, act: str = "silu", out=None):
+    """act(gate) * up over interleaved columns (gate_0, up_0, gate_1, ...): the layout the fused gate / up
+    projection produces. `act`: "silu" or "gelu_tanh" (Gemma's GeGLU)."""
+    if not gate_up.is_cuda or gate_up.dtype != torch.bfloat16:
+        return reference.glu_interleaved(gate_up, act)
+    rows, two_i = gate_up.shape
+    gate_up = gate_up.contiguous()
+    if out is None:
+        out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    check(fn("pie_glu_interleaved")(ptr(gate_up), ptr(out), rows, two_i // 2, GLU_ACTS[act], stream_ptr()), "glu_interleaved")
+    return out
+
+
 def qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, kv_layer, hq, hkv,
                          head_dim, page_size, eps, q_out=None, kv_scale=None):
     """Per-head q/k RMSNorm (optional), RoPE, Q out, K/V rows appended into their page slots. With
@@ -863,14 +879,14 @@ def build_prefill_plan(batch: AttnBatch, group: int, page_size: int, device, til
                        mask_bits, mask_indptr, batch.window_left, tile_rows)
 
 
-def paged_attention_cpu(q, kv_layer, batch: AttnBatch, sm_scale: float, window_left=None, sinks=None):
+def paged_attention_cpu(q, kv_layer, batch: AttnBatch, sm_scale: float, window_left=None, sinks=None, softcap=0.0):
     masks = None
     if batch.masks is not None:
         masks = [None if m is None else torch.as_tensor(np.asarray(m, dtype=bool)) for m in batch.masks]
     return reference.paged_attention(q, kv_layer, batch.qo_indptr, batch.kv_page_indptr,
                                      torch.as_tensor(batch.page_indices), batch.kv_lens, sm_scale,
                                      masks=masks, window_left=batch.window_left if window_left is None else window_left,
-                                     sinks=sinks)
+                                     sinks=sinks, softcap=softcap)
 
 
 # --------------------------------------------------------------------------- sampling

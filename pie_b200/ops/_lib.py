@@ -26,6 +26,7 @@ _SIGNATURES = {
     "pie_embed_gather": [p, p, p, i32, i32, i32, i32, p],
     "pie_rmsnorm": [p, p, p, p, p, i32, i32, f32, f32, p],
     "pie_swiglu": [p, p, i64, i32, p],
+    "pie_glu_interleaved": [p, p, i64, i32, i32, p],
     "pie_dequant_fp8_rowblock": [p, p, p, i64, i32, p],
     "pie_quant_act_fp8": [p, i32, p, p, i32, i32, p],
     "pie_gemm_fp8_blockscaled": [p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, p, i32, p],

@@ -41,6 +41,12 @@ def swiglu_interleaved(gate_up):
     return (torch.nn.functional.silu(g) * u).to(gate_up.dtype)
 
 
+def glu_interleaved(gate_up, act: str = "silu"):
+    g, u = gate_up[..., 0::2].float(), gate_up[..., 1::2].float()
+    a = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
+    return (a * u).to(gate_up.dtype)
+
+
 def rope_inv_freq(head_dim, theta, scaling=None, device="cpu"):
     """Inverse frequencies of rotate-half RoPE, with optional Llama-3, linear or YaRN frequency
     scaling (`rope_scaling` of a Hugging Face config).
@@ -135,7 +141,7 @@ def gather_kv(kv_layer, pages, kv_len):
 
 
 def paged_attention(q, kv_layer, qo_indptr, kv_page_indptr, page_indices, kv_lens, sm_scale,
-                    masks=None, window_left=-1, return_lse=False, sinks=None):
+                    masks=None, window_left=-1, return_lse=False, sinks=None, softcap=0.0):
     """Ragged paged attention. q [N, hq, D]; masks: optional list (per request) of bool
     [qo_len, kv_len] tensors or None (causal: query i sees kv < kv_len - qo_len + i + 1).
     sinks [hq]: per-head logits that join the softmax denominator without a value row."""
@@ -157,6 +163,8 @@ def paged_attention(q, kv_layer, qo_indptr, kv_page_indptr, page_indices, kv_len
         vf = v.float().repeat_interleave(g, dim=0)
         qf = q[q0:q1].float().permute(1, 0, 2)      # [hq, ql, D]
         s = torch.einsum("hqd,hkd->hqk", qf, kf) * sm_scale
+        if softcap:         # Gemma-2: scores squashed into (-cap, cap) before masking
+            s = torch.tanh(s / softcap) * softcap
         if masks is not None and masks[r] is not None:
             allow = masks[r].to(q.device)[:, :kl]
         else:

@@ -125,7 +125,7 @@ class Engine:
             sched.delivery_guard = entry.ctxm.lock
             # the array-form decode cohort does not carry recurrent-state slots: such models step per request
             sched.cohort = (DecodeCohort(entry.ctxm, entry.page_size, caps.max_forward_requests)
-                            if not caps.rs_cache_slots and hasattr(drv, "decode_async") else None)
+                            if not caps.rs_cache_slots and getattr(caps, "cohort_decode", True) and hasattr(drv, "decode_async") else None)
             entry.schedulers.append(sched)
         entry.inference = InferenceService(entry.ctxm, entry.schedulers,
                                            0 if self.config.system_spec_tokens > 0 else self.config.speculation_depth)

@@ -205,3 +205,35 @@ def test_gdn_hybrid_driver_matches_dense_oracle():
         cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
         # random-init logits are nearly flat: ask for the oracle's best token among the driver's best five
         assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (a, b, cos)
+
+
+@pytest.mark.parametrize("name", ["tiny-gemma3", "tiny-gemma2"])
+def test_gemma_driver_matches_dense_oracle(name):
+    """Gemma-3 (sandwich norms, GeGLU kernel, local RoPE table, windowed layers) over the CUDA kernels, prefill chunks then
+    graph decode; Gemma-2 (soft-capped scores) with its attention as torch ops on the device. Oracle: the dense fp32
+    forward of the same bf16-rounded weights."""
+    from pie_b200.driver.schema import ForwardRequest, SamplerKind, SamplerSpec
+    from pie_b200.models.transformer import dense_reference_forward
+    cfg = preset(name, dtype="bfloat16")
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=4)
+    drv = TorchDriver(cfg, "cuda", weights=w, num_pages=32, page_size=16, max_requests=4, max_tokens=128)
+    assert drv.use_graphs is (name == "tiny-gemma3")
+    wf = {"layers": [{k: v.float().cpu() for k, v in lw.items()} for lw in w["layers"]],
+          **{k: v.float().cpu() for k, v in w.items() if torch.is_tensor(v)}}
+    toks = list(range(60, 60 + 47))
+    want = dense_reference_forward(cfg, wf, torch.tensor(toks)).numpy()
+    i32 = lambda *a: np.asarray(a, dtype=np.int32)
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+
+    def fire(tk, start):
+        n, kv = len(tk), start + len(tk)
+        req = ForwardRequest(tokens=np.asarray(tk, np.int32), positions=np.arange(start, kv, dtype=np.int32), qo_indptr=i32(0, n),
+                             kv_page_indices=np.arange(-(-kv // 16), dtype=np.int32), kv_page_indptr=i32(0, -(-kv // 16)),
+                             kv_last_page_lens=i32((kv - 1) % 16 + 1), slot_req=i32(0), slot_row=i32(n - 1),
+                             slot_samplers=[raw])
+        return np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
+    for a, b in ((0, 20), (20, 44), (44, 45), (45, 46), (46, 47)):
+        got = fire(toks[a:b], a)
+        ref_row = want[b - 1]
+        cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
+        assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (name, a, b, cos)

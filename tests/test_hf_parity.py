@@ -27,6 +27,8 @@ FAMILIES = [
     ("gpt_oss", "tiny-gpt-oss", {}),
     ("mixtral", "tiny-qwen3-moe", dict(model_type="mixtral", qk_norm=False)),
     ("phi3", "tiny-llama", dict(model_type="phi3")),
+    ("gemma3_text", "tiny-gemma3", {}),
+    ("gemma2", "tiny-gemma2", {}),
 ]
 
 

@@ -49,6 +49,13 @@ def test_swiglu():
     close(ops.swiglu(gu), ref.swiglu(gu), 2e-2)
 
 
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+def test_glu_interleaved(act):
+    gu = bf(50, 2 * 1408, seed=4) * 3
+    close(ops.glu_interleaved(gu, act), ref.glu_interleaved(gu.float(), act).to(gu.dtype), 2e-2)
+    assert ops.glu_interleaved(gu[:0], act).shape == (0, 1408)
+
+
 @pytest.mark.parametrize("d,hq,hkv,norm", [(128, 8, 2, False), (128, 8, 2, True), (64, 4, 2, True)])
 def test_qk_norm_rope_kvwrite(d, hq, hkv, norm):
     n, page, pages = 41, 16, 12
