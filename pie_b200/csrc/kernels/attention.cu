@@ -75,10 +75,18 @@ struct AttnState {
 // One warp: S = Q(16 x D) K(16 tokens)^T, online softmax, O += P V.
 // allow0/allow1: bit c set when token c of the block is visible to row g /
 // row g+8 of the warp's tile (g = lane/4).
-template <int D>
+// CAP (Gemma-2's soft-capped scores): the scores pass through cap * tanh(s * sm_scale / cap) before the softmax;
+// scale_log2 then carries sm_scale / cap and cap_log2 = cap * log2(e).
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D, bool CAP = false>
 __device__ __forceinline__ void attn_block16(const uint32_t (&qf)[D / 16][4], uint32_t k_smem,
                                              uint32_t v_smem, float scale_log2, uint32_t allow0,
-                                             uint32_t allow1, AttnState<D>& st) {
+                                             uint32_t allow1, AttnState<D>& st, float cap_log2 = 0.f) {
     const int lane = threadIdx.x & 31;
     const int mi = lane >> 3, r = lane & 7;
     float s[2][2][4];
@@ -106,6 +114,7 @@ __device__ __forceinline__ void attn_block16(const uint32_t (&qf)[D / 16][4], ui
             const int tok = j * 8 + 2 * t + (e & 1);
             const uint32_t allow = (e >> 1) ? allow1 : allow0;
             float v = (s[j][0][e] + s[j][1][e]) * scale_log2;
+            if (CAP) v = cap_log2 * tanh_approx(v);
             v = ((allow >> tok) & 1u) ? v : -INFINITY;
             p[j][e] = v;
             mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -186,7 +195,7 @@ constexpr int decode_smem_bytes() {
 //   item_tile  [items]  : row of tile_members for a shared item, -1 otherwise
 //   tile_members [tiles][16] : request of each member, -1 for unused rows
 // Without CASCADE the three arrays are unused and slot == item index.
-template <int D, int G, bool CASCADE>
+template <int D, int G, bool CASCADE, bool CAP = false>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_layer,
                          const int* __restrict__ page_indices,
@@ -198,7 +207,8 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          int page_size, float scale_log2, int window_left,
                          const float* __restrict__ sinks_log2, int max_items, int num_reqs,
                          int* __restrict__ status, const int* __restrict__ item_slot,
-                         const int* __restrict__ item_tile, const int* __restrict__ tile_members) {
+                         const int* __restrict__ item_tile, const int* __restrict__ tile_members,
+                         float cap_log2) {
     static_assert(G <= 16, "at most 16 query heads per KV head");
     constexpr int ROWS = CASCADE ? (16 / G) * G : G;      // rows of the Q tile in use
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -291,7 +301,7 @@ paged_decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
             uint32_t allow = nvalid >= 16 ? 0xffffu : ((1u << nvalid) - 1u);
             if (kv_lo > tok0) allow &= kv_lo - tok0 >= 16 ? 0u : ~((1u << (kv_lo - tok0)) - 1u);
             const uint32_t kt = warp_smem + (i % DEC_STAGES) * 2 * TILE_BYTES;
-            attn_block16<D>(qf, kt, kt + TILE_BYTES, scale_log2, allow, allow, st);
+            attn_block16<D, CAP>(qf, kt, kt + TILE_BYTES, scale_log2, allow, allow, st, cap_log2);
             __syncwarp();
         }
         cp_async_wait<0>();
@@ -412,7 +422,7 @@ constexpr int prefill_smem_bytes() {
     return PF_ROWS * D * 2 + 2 * 2 * PF_KV * D * 2;
 }
 
-template <int D, int G>
+template <int D, int G, bool CAP = false>
 __global__ void __launch_bounds__(PF_WARPS * 32)
 paged_prefill_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_layer,
                           const int* __restrict__ page_indices,
@@ -422,7 +432,7 @@ paged_prefill_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                           const uint32_t* __restrict__ mask_bits,
                           const long* __restrict__ mask_word_indptr, bf16* __restrict__ out,
                           float* __restrict__ lse_out, const float* __restrict__ sinks_log2, int hq, int hkv, int page_size,
-                          float scale_log2, int window_left) {
+                          float scale_log2, int window_left, float cap_log2) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int CH = D / 8;
     constexpr int TQ = PF_ROWS / G;  // query tokens per tile
@@ -527,8 +537,8 @@ paged_prefill_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                 }
                 allow[hh] = a;
             }
-            attn_block16<D>(qf, kt + sb * 16 * D * 2, kt + KV_TILE + sb * 16 * D * 2, scale_log2,
-                            allow[0], allow[1], st);
+            attn_block16<D, CAP>(qf, kt + sb * 16 * D * 2, kt + KV_TILE + sb * 16 * D * 2, scale_log2,
+                                 allow[0], allow[1], st, cap_log2);
         }
         __syncthreads();
     }
@@ -573,6 +583,15 @@ using namespace pie;
                 case 4: { constexpr int G = 4; __VA_ARGS__; } break;          \
                 case 8: { constexpr int G = 8; __VA_ARGS__; } break;          \
                 case 16: { constexpr int G = 16; __VA_ARGS__; } break;        \
+                default: ok_ = false;                                  \
+            }                                                          \
+        } else if (D_ == 256) {                                        \
+            constexpr int D = 256;                                     \
+            switch (G_) {                                              \
+                case 1: { constexpr int G = 1; __VA_ARGS__; } break;          \
+                case 2: { constexpr int G = 2; __VA_ARGS__; } break;          \
+                case 4: { constexpr int G = 4; __VA_ARGS__; } break;          \
+                case 8: { constexpr int G = 8; __VA_ARGS__; } break;          \
                 default: ok_ = false;                                  \
             }                                                          \
         } else if (D_ == 64) {                                         \
@@ -627,6 +646,9 @@ PIE_API int pie_decode_merge(const float* o_part, const float* lse_part, const i
     if (head_dim == 128)
         launch_pdl(paged_decode_merge_kernel<128>, grid, dim3(128), 0, st, o_part, lse_part, req_item_indptr,
                    (bf16*)out, hq, hkv, group, sinks_log2, max_items);
+    else if (head_dim == 256)
+        launch_pdl(paged_decode_merge_kernel<256>, grid, dim3(256), 0, st, o_part, lse_part, req_item_indptr,
+                   (bf16*)out, hq, hkv, group, sinks_log2, max_items);
     else if (head_dim == 64)
         launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, o_part, lse_part, req_item_indptr,
                    (bf16*)out, hq, hkv, group, sinks_log2, max_items);
@@ -646,25 +668,34 @@ static int launch_decode(const void* q, const void* kv_layer, const int* page_in
                          void* out, float* scratch, int max_items, int num_reqs, int hq, int hkv,
                          int head_dim, int page_size, float sm_scale, int num_ctas, int run_merge,
                          int window_left, const float* sinks_log2, const int* item_slot,
-                         const int* item_tile, const int* tile_members, cudaStream_t st) {
+                         const int* item_tile, const int* tile_members, cudaStream_t st, float softcap = 0.f) {
     if (num_reqs <= 0) return 0;
     if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
     const bool cascade = item_tile != nullptr;
-    if (cascade && (!item_slot || !tile_members || window_left >= 0)) return (int)cudaErrorInvalidValue;
+    if (cascade && (!item_slot || !tile_members || window_left >= 0 || softcap > 0.f)) return (int)cudaErrorInvalidValue;
     const int group = hq / hkv;
     float* o_part = scratch;
     float* lse_part = scratch + (size_t)max_items * hq * head_dim;
-    const float scale_log2 = sm_scale * 1.4426950408889634f;
+    const float scale_log2 = softcap > 0.f ? sm_scale / softcap : sm_scale * 1.4426950408889634f;
+    const float cap_log2 = softcap * 1.4426950408889634f;
     DISPATCH_DG(head_dim, group, {
         constexpr int SM = decode_smem_bytes<D>();
-        if (cascade) {
+        if (softcap > 0.f) {
+            auto kern = paged_decode_attn_kernel<D, G, false, true>;
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+            launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
+                (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
+                item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
+                hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word(),
+                (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, cap_log2);
+        } else if (cascade) {
             auto kern = paged_decode_attn_kernel<D, G, true>;
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
             launch_pdl(kern, dim3(num_ctas), dim3(DEC_WARPS * 32), SM, st,
                 (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
                 item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
                 hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word(),
-                item_slot, item_tile, tile_members);
+                item_slot, item_tile, tile_members, 0.f);
         } else {
             auto kern = paged_decode_attn_kernel<D, G, false>;
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
@@ -672,7 +703,7 @@ static int launch_decode(const void* q, const void* kv_layer, const int* page_in
                 (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, item_req,
                 item_start, item_end, req_item_indptr, num_items_ptr, (bf16*)out, o_part, lse_part, hq,
                 hkv, page_size, scale_log2, window_left, sinks_log2, max_items, num_reqs, status_word(),
-                (const int*)nullptr, (const int*)nullptr, (const int*)nullptr);
+                (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, 0.f);
         }
     });
     int err = (int)cudaGetLastError();
@@ -680,6 +711,9 @@ static int launch_decode(const void* q, const void* kv_layer, const int* page_in
     dim3 grid(num_reqs, hq);
     if (head_dim == 128)
         launch_pdl(paged_decode_merge_kernel<128>, grid, dim3(128), 0, st, (const float*)o_part,
+                   (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2, max_items);
+    else if (head_dim == 256)
+        launch_pdl(paged_decode_merge_kernel<256>, grid, dim3(256), 0, st, (const float*)o_part,
                    (const float*)lse_part, req_item_indptr, (bf16*)out, hq, hkv, group, sinks_log2, max_items);
     else
         launch_pdl(paged_decode_merge_kernel<64>, grid, dim3(64), 0, st, (const float*)o_part,
@@ -701,6 +735,20 @@ PIE_API int pie_paged_decode_attn_window(const void* q, const void* kv_layer, co
     return launch_decode(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start, item_end, req_item_indptr,
                          num_items_ptr, out, scratch, max_items, num_reqs, hq, hkv, head_dim, page_size, sm_scale,
                          num_ctas, run_merge, window_left, sinks_log2, nullptr, nullptr, nullptr, st);
+}
+
+// The same with soft-capped scores (softcap > 0): softmax over softcap * tanh(q.k * sm_scale / softcap).
+PIE_API int pie_paged_decode_attn_softcap(const void* q, const void* kv_layer, const int* page_indices,
+                                          const int* kv_page_indptr, const int* item_req,
+                                          const int* item_start, const int* item_end,
+                                          const int* req_item_indptr, const int* num_items_ptr,
+                                          void* out, float* scratch, int max_items, int num_reqs, int hq,
+                                          int hkv, int head_dim, int page_size, float sm_scale,
+                                          int num_ctas, int run_merge, int window_left,
+                                          const float* sinks_log2, float softcap, cudaStream_t st) {
+    return launch_decode(q, kv_layer, page_indices, kv_page_indptr, item_req, item_start, item_end, req_item_indptr,
+                         num_items_ptr, out, scratch, max_items, num_reqs, hq, hkv, head_dim, page_size, sm_scale,
+                         num_ctas, run_merge, window_left, sinks_log2, nullptr, nullptr, nullptr, st, softcap);
 }
 
 // Decode attention over a plan with shared-prefix items (see the kernel): requests that were forked
@@ -732,6 +780,42 @@ PIE_API int pie_paged_decode_attn(const void* q, const void* kv_layer, const int
                                         head_dim, page_size, sm_scale, num_ctas, run_merge, -1, nullptr, st);
 }
 
+// softcap > 0: softmax over softcap * tanh(q.k * sm_scale / softcap) (Gemma-2).
+PIE_API int pie_paged_prefill_attn_softcap(const void* q, const void* kv_layer, const int* page_indices,
+                                           const int* kv_page_indptr, const int* qo_indptr,
+                                           const int* kv_lens, const int* tile_req, const int* tile_qstart,
+                                           int num_tiles, const uint32_t* mask_bits,
+                                           const long* mask_word_indptr, void* out, float* lse_out, int hq,
+                                           int hkv, int head_dim, int page_size, float sm_scale,
+                                           int window_left, const float* sinks_log2, float softcap,
+                                           cudaStream_t st) {
+    if (num_tiles <= 0) return 0;
+    if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
+    const int group = hq / hkv;
+    const float scale_log2 = softcap > 0.f ? sm_scale / softcap : sm_scale * 1.4426950408889634f;
+    const float cap_log2 = softcap * 1.4426950408889634f;
+    dim3 grid(num_tiles, hkv);
+    DISPATCH_DG(head_dim, group, {
+        constexpr int SM = prefill_smem_bytes<D>();
+        if (softcap > 0.f) {
+            auto kern = paged_prefill_attn_kernel<D, G, true>;
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+            kern<<<grid, PF_WARPS * 32, SM, st>>>(
+                (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, qo_indptr, kv_lens,
+                tile_req, tile_qstart, mask_bits, mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv,
+                page_size, scale_log2, window_left, cap_log2);
+        } else {
+            auto kern = paged_prefill_attn_kernel<D, G, false>;
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
+            kern<<<grid, PF_WARPS * 32, SM, st>>>(
+                (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, qo_indptr, kv_lens,
+                tile_req, tile_qstart, mask_bits, mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv,
+                page_size, scale_log2, window_left, 0.f);
+        }
+    });
+    return (int)cudaGetLastError();
+}
+
 PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const int* page_indices,
                                    const int* kv_page_indptr, const int* qo_indptr,
                                    const int* kv_lens, const int* tile_req, const int* tile_qstart,
@@ -739,21 +823,9 @@ PIE_API int pie_paged_prefill_attn(const void* q, const void* kv_layer, const in
                                    const long* mask_word_indptr, void* out, float* lse_out, int hq,
                                    int hkv, int head_dim, int page_size, float sm_scale,
                                    int window_left, const float* sinks_log2, cudaStream_t st) {
-    if (num_tiles <= 0) return 0;
-    if (hkv <= 0 || hq % hkv || page_size % 16) return (int)cudaErrorInvalidValue;
-    const int group = hq / hkv;
-    const float scale_log2 = sm_scale * 1.4426950408889634f;
-    dim3 grid(num_tiles, hkv);
-    DISPATCH_DG(head_dim, group, {
-        constexpr int SM = prefill_smem_bytes<D>();
-        auto kern = paged_prefill_attn_kernel<D, G>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM);
-        kern<<<grid, PF_WARPS * 32, SM, st>>>(
-            (const bf16*)q, (const bf16*)kv_layer, page_indices, kv_page_indptr, qo_indptr, kv_lens,
-            tile_req, tile_qstart, mask_bits, mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv,
-            page_size, scale_log2, window_left);
-    });
-    return (int)cudaGetLastError();
+    return pie_paged_prefill_attn_softcap(q, kv_layer, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req,
+                                          tile_qstart, num_tiles, mask_bits, mask_word_indptr, out, lse_out, hq, hkv,
+                                          head_dim, page_size, sm_scale, window_left, sinks_log2, 0.f, st);
 }
 
 // Query tokens covered by one prefill tile for a given GQA group size.

@@ -181,12 +181,10 @@ class TorchDriver:
             from .recurrent import RecurrentStateCache
             self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
             use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet
-        # soft-capped attention scores (Gemma-2) run as torch ops over a host plan: no decode kernel, no graphs
-        self.host_attention = bool(cfg.attn_softcap)
-        if self.host_attention:
-            use_graphs = False
-            if kv_dtype == "fp8_e4m3":
-                raise NotImplementedError("fp8 KV pages with soft-capped attention scores")
+        # soft-capped attention scores (Gemma-2): bf16 pages, the 64-row prefill kernel, no shared-prefix decode plans
+        self.softcap = bool(cfg.attn_softcap)
+        if self.softcap and kv_dtype == "fp8_e4m3":
+            raise NotImplementedError("fp8 KV pages with soft-capped attention scores")
         self.max_requests, self.max_tokens = max_requests, max_tokens
         self.max_page_refs = max(4096, min(num_pages * 2, 1 << 22))
         self.num_ctas = ops.num_sms(self.device) * 2 if self.cuda else 1
@@ -197,7 +195,7 @@ class TorchDriver:
         import os as _os
         self._prefix_cache: dict = {}
         self.cascade = (self.cuda and _os.environ.get("PIE_CASCADE", "1") != "0" and self.window_left < 0
-                        and self.cfg.layer_types is None and self.kv.scale is None)
+                        and self.cfg.layer_types is None and self.kv.scale is None and not self.softcap)
         rows = max(max_requests, 1024)
         self.max_rows = rows
         self.slab = _Slab({
@@ -319,7 +317,7 @@ class TorchDriver:
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
             tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0,
-            cohort_decode=self.rs is None and not self.host_attention)
+            cohort_decode=self.rs is None)
 
     # ------------------------------------------------------------------ request -> slab
     def _derive(self, req: ForwardRequest):
@@ -560,7 +558,8 @@ class TorchDriver:
         self.stats["logit_rows"] = self.stats.get("logit_rows", 0) + len(rows)
         if self.cuda:
             group = self.model.hq // self.model.hkv
-            tile_rows = ops.prefill_tile_rows(self.model.hq, self.model.hkv, self.model.cfg.head_dim, self.page_size)
+            tile_rows = ops.prefill_tile_rows(self.model.hq, self.model.hkv, self.model.cfg.head_dim, self.page_size,
+                                              softcap=self.softcap)
             tile_req, tile_q = ops.plan_prefill_tiles(np.asarray(req.qo_indptr), group, tile_rows, kv_lens)
             nt = len(tile_req)
             s.h("tile_req")[:nt], s.h("tile_qstart")[:nt] = tile_req, tile_q
@@ -583,8 +582,6 @@ class TorchDriver:
             fi = ForwardInputs(s.d("tokens", n), s.d("positions", n), s.d("slots", n), plan,
                                logit_rows=s.d("logit_rows", len(rows)), is_decode=False,
                                attn_num_pages=len(req.kv_page_indices))
-            if self.host_attention:
-                fi.attn_host = self._host_batch(req, qlens, kv_lens, custom)
         else:
             batch = self._host_batch(req, qlens, kv_lens, custom)
             fi = ForwardInputs(torch.from_numpy(np.ascontiguousarray(req.tokens, dtype=np.int32)),
@@ -728,8 +725,7 @@ class TorchDriver:
         nslots = len(req.slot_samplers)
         self._lora_bindings = self._bind_adapters(req)
         decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None
-                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None
-                  and not self.host_attention)
+                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None)
         if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
             # followers must draw the same tokens: fix the per-fire seeds before publishing
             from dataclasses import replace as _replace

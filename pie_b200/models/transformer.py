@@ -32,7 +32,6 @@ class ForwardInputs:
     positions: torch.Tensor       # int32 [N]
     slots: torch.Tensor           # int32 [N]  KV slot (page*page_size+offset) of each new token
     attn: object                  # ops.DecodePlan | ops.PrefillPlan | ops.AttnBatch (CPU)
-    attn_host: Optional[object] = None     # ops.AttnBatch of the same work, for attention variants that run as torch ops
     attn_num_pages: Optional[int] = None   # page references of this batch (prefill plans; the slab segment is larger)
     logit_rows: Optional[torch.Tensor] = None   # int32 rows of the hidden state that need logits
     rs: Optional[object] = None   # driver.recurrent.RecurrentInputs for models with Gated DeltaNet layers
@@ -90,10 +89,9 @@ class Transformer:
         the whole range and the kernels mask), and its attention sinks where the model has them."""
         wl = self.cfg.layer_window_left(li) if self.cfg.layer_types is not None else None
         sinks = lw.get("sinks") if lw is not None else None
-        if not q.is_cuda or self.cfg.attn_softcap:
-            # soft-capped scores (Gemma-2) have no CUDA kernel here: the torch statement of the op runs on either device
-            return ops.paged_attention_cpu(q, kv_layer, fi.attn_host or fi.attn, self.sm_scale, window_left=wl, sinks=sinks,
-                                           softcap=self.cfg.attn_softcap)
+        cap = self.cfg.attn_softcap
+        if not q.is_cuda:
+            return ops.paged_attention_cpu(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks=sinks, softcap=cap)
         sl2 = None
         if sinks is not None:
             sl2 = lw.get("sinks_log2")
@@ -102,7 +100,7 @@ class Transformer:
         ks = self.kv_scale[li] if self.kv_scale is not None else None
         if fi.is_decode:
             return ops.paged_decode_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2,
-                                              kv_scale=ks)
+                                              kv_scale=ks, softcap=cap)
         if ks is not None:
             # prefill over fp8 pages: expand the pages this batch reads to bf16 and address them compactly
             from dataclasses import replace as _replace
@@ -110,7 +108,7 @@ class Transformer:
             dense = ops.dequant_kv_pages(kv_layer, ks, pages)
             plan = _replace(fi.attn, page_indices=torch.arange(pages.numel(), dtype=torch.int32, device=pages.device))
             return ops.paged_prefill_attention(q, dense, plan, self.sm_scale, window_left=wl, sinks_log2=sl2)
-        return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2)
+        return ops.paged_prefill_attention(q, kv_layer, fi.attn, self.sm_scale, window_left=wl, sinks_log2=sl2, softcap=cap)
 
     def _glu(self, x, lw):
         """act(gate) * up of the fused, interleaved gate / up projection: SiLU in the GEMM's epilogue, GELU after it."""

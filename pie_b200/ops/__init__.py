@@ -698,12 +698,12 @@ def plan_decode_cascade(kv_lens: np.ndarray, groups, hkv: int, group_size: int, 
                        indptr, int(sum(st * (len(mem) - t) for (mem, st), t in zip(groups, tiles_of))), len(groups))
 
 
-def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int) -> int:
+def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int, softcap: bool = False) -> int:
     """Packed (token, head) rows per prefill tile: 256 (two MMA tiles per CTA; ``PIE_PREFILL_TC=128``
     for one) where the tcgen05 kernel covers the shape (head_dim 64 or 128, 16-token pages, group size
-    dividing 128), else - or with ``PIE_PREFILL_TC=0`` - the 64 rows of the mma.sync kernel."""
+    dividing 128, no soft cap on the scores), else - or with ``PIE_PREFILL_TC=0`` - the 64 rows of the mma.sync kernel."""
     want = os.environ.get("PIE_PREFILL_TC", "256")
-    if want == "0" or not fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size):
+    if want == "0" or softcap or not fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size):
         return 64
     return 128 if want == "128" else 256
 
@@ -768,7 +768,7 @@ def dequant_kv_pages(kv8_layer, scale_layer, pages: torch.Tensor, pad_zero_page:
 
 
 def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=None, window_left=None,
-                           sinks_log2=None, kv_scale=None):
+                           sinks_log2=None, kv_scale=None, softcap: float = 0.0):
     """q [R, hq, D] (one token per request) against paged KV; split-KV + merge. `window_left`
     overrides the plan's window for this call (a layer with its own window; the plan's items
     must then cover at least that window), `sinks_log2` [hq] fp32 = sink logits * log2(e)."""
@@ -777,6 +777,15 @@ def paged_decode_attention(q, kv_layer, plan: DecodePlan, sm_scale: float, out=N
     wl = plan.window_left if window_left is None else window_left
     r, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    if softcap:                     # softmax over softcap * tanh(score / softcap) (Gemma-2)
+        if kv_scale is not None or plan.item_tile is not None:
+            raise NotImplementedError("soft-capped scores over fp8 KV pages or shared-prefix plans")
+        check(fn("pie_paged_decode_attn_softcap")(
+            ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.item_req),
+            ptr(plan.item_start), ptr(plan.item_end), ptr(plan.req_item_indptr), ptr(plan.num_items),
+            ptr(out), ptr(plan.scratch), plan.max_items, plan.num_reqs, hq, hkv, d, plan.page_size,
+            sm_scale, plan.num_ctas, 1, wl, ptr(sinks_log2), float(softcap), stream_ptr()), "paged_decode_attn_softcap")
+        return out
     if kv_scale is not None:        # fp8 pages with per-(token, head) scales
         if plan.item_tile is not None:
             raise NotImplementedError("shared-prefix plans over fp8 KV pages")
@@ -819,12 +828,21 @@ class PrefillPlan:
 
 
 def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out=None, lse_out=None,
-                            window_left=None, sinks_log2=None):
+                            window_left=None, sinks_log2=None, softcap: float = 0.0):
     if out is None:
         out = torch.empty_like(q)
     wl = plan.window_left if window_left is None else window_left
     n, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    if softcap:
+        if plan.tile_rows != 64:
+            raise ValueError("soft-capped scores run on the 64-row prefill kernel: plan with prefill_tile_rows(..., softcap=True)")
+        check(fn("pie_paged_prefill_attn_softcap")(
+            ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
+            ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
+            ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), hq, hkv, d,
+            plan.page_size, sm_scale, wl, ptr(sinks_log2), float(softcap), stream_ptr()), "paged_prefill_attn_softcap")
+        return out
     if plan.tile_rows > 64:
         # kv_layer is [pages + 1, 2, hkv, page, d]; its last page is the zero pad page
         check(fn("pie_paged_prefill_attn_tc")(

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "pie_moe_bias_glu": [p, p, p, p, i32, i32, f32, p],
     "pie_moe_row_bias": [p, p, p, i32, i32, p],
     "pie_paged_decode_attn_window": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, p, p],
+    "pie_paged_decode_attn_softcap": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, p, f32, p],
+    "pie_paged_prefill_attn_softcap": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, f32, i32, p, f32, p],
     "pie_paged_decode_attn_cascade": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, p, p, p, p, p],
     "pie_paged_prefill_attn": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, f32, i32, p, p],
     "pie_prefill_tile_tokens": [i32],

@@ -207,17 +207,19 @@ def test_gdn_hybrid_driver_matches_dense_oracle():
         assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (a, b, cos)
 
 
-@pytest.mark.parametrize("name", ["tiny-gemma3", "tiny-gemma2"])
-def test_gemma_driver_matches_dense_oracle(name):
-    """Gemma-3 (sandwich norms, GeGLU kernel, local RoPE table, windowed layers) over the CUDA kernels, prefill chunks then
-    graph decode; Gemma-2 (soft-capped scores) with its attention as torch ops on the device. Oracle: the dense fp32
-    forward of the same bf16-rounded weights."""
+@pytest.mark.parametrize("name,over", [("tiny-gemma3", {}), ("tiny-gemma2", {}), ("tiny-gemma3", dict(head_dim=256)),
+                                       ("tiny-gemma2", dict(head_dim=256, num_key_value_heads=1))])
+def test_gemma_driver_matches_dense_oracle(name, over):
+    """Gemma-3 (sandwich norms, GeGLU kernel, local RoPE table, windowed layers) and Gemma-2 (soft-capped scores in the
+    decode and 64-row prefill kernels, soft-capped logits) on the CUDA driver, at head_dim 64 and 256: prefill chunks, then
+    graph decode.
+    Oracle: the dense fp32 forward of the same bf16-rounded weights."""
     from pie_b200.driver.schema import ForwardRequest, SamplerKind, SamplerSpec
     from pie_b200.models.transformer import dense_reference_forward
-    cfg = preset(name, dtype="bfloat16")
+    cfg = preset(name, dtype="bfloat16", **over)
     w = random_weights(cfg, "cuda", torch.bfloat16, seed=4)
     drv = TorchDriver(cfg, "cuda", weights=w, num_pages=32, page_size=16, max_requests=4, max_tokens=128)
-    assert drv.use_graphs is (name == "tiny-gemma3")
+    assert drv.use_graphs
     wf = {"layers": [{k: v.float().cpu() for k, v in lw.items()} for lw in w["layers"]],
           **{k: v.float().cpu() for k, v in w.items() if torch.is_tensor(v)}}
     toks = list(range(60, 60 + 47))

@@ -136,6 +136,68 @@ def test_paged_decode_attention(d, hq, hkv):
     close(out, want, 2e-2)
 
 
+@pytest.mark.parametrize("d,hq,hkv,softcap,window", [(256, 8, 4, 0.0, -1), (256, 8, 1, 0.0, 100), (256, 16, 16, 0.0, -1), (256, 8, 2, 1.5, -1),
+                                                     (128, 32, 8, 1.5, -1), (128, 16, 8, 2.0, 100), (64, 4, 2, 1.5, -1)])
+def test_paged_decode_attention_head_dim_256_and_softcap(d, hq, hkv, softcap, window):
+    """head_dim 256 (Gemma sizes) and soft-capped scores (softmax over cap * tanh(s / cap), Gemma-2), alone and together."""
+    page = 16
+    kv_lens = np.array([1, 15, 16, 17, 300, 1000, 2305, 64], dtype=np.int32)
+    r = len(kv_lens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=11)
+    q = bf(r, hq, d, seed=12)
+    item_req, st, en, iptr = ops.plan_decode_items(kv_lens, hkv, target_ctas=64, min_chunk=256, window_left=window)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    max_items = len(item_req) + 3
+    plan = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
+                          torch.tensor([len(item_req)], dtype=torch.int32, device=DEV),
+                          torch.empty(ops.decode_scratch_floats(max_items, hq, d), device=DEV),
+                          max_items, r, 64, page, window_left=window)
+    scale = 1 / math.sqrt(d)
+    out = ops.paged_decode_attention(q, kv, plan, scale, softcap=softcap)
+    qo = np.arange(r + 1, dtype=np.int32)
+    want = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale, window_left=window,
+                               softcap=softcap)
+    close(out, want, 2e-2)
+    if softcap:     # the cap changes the result: the test would not pass without it
+        plain = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale, window_left=window)
+        assert (plain.float() - want.float()).abs().max() > 0.05
+
+
+@pytest.mark.parametrize("d,hq,hkv,softcap", [(256, 8, 4, 0.0), (256, 4, 4, 0.0), (256, 8, 1, 1.5), (128, 32, 8, 1.5), (64, 4, 2, 2.0)])
+@pytest.mark.parametrize("mode", ["causal", "custom", "window"])
+def test_paged_prefill_attention_head_dim_256_and_softcap(d, hq, hkv, softcap, mode):
+    """The 64-row kernel at head_dim 256 and with soft-capped scores (the tcgen05 kernel covers neither)."""
+    page = 16
+    assert ops.prefill_tile_rows(hq, hkv, d, page, softcap=bool(softcap)) == (64 if softcap or d == 256 else 256)
+    qlens = np.array([1, 5, 64, 130, 17, 700], dtype=np.int32)
+    prev = np.array([40, 0, 0, 200, 31, 333], dtype=np.int32)
+    kv_lens = qlens + prev
+    r = len(qlens)
+    kv, pages, indptr = make_paged(r, kv_lens, hkv, d, page, seed=21)
+    qo = np.zeros(r + 1, dtype=np.int32)
+    qo[1:] = np.cumsum(qlens)
+    q = bf(int(qo[-1]), hq, d, seed=22)
+    masks, window = None, -1
+    if mode == "custom":
+        rng = np.random.default_rng(5)
+        masks = []
+        for i in range(r):
+            m = rng.random((qlens[i], kv_lens[i])) < 0.6
+            m[:, 0] = True
+            masks.append(m if i != 2 else None)
+    if mode == "window":
+        window = 37
+    plan = ops.build_prefill_plan(ops.AttnBatch(qo, indptr, pages, kv_lens, masks, window), hq // hkv, page, DEV, tile_rows=64)
+    scale = 1 / math.sqrt(d)
+    lse = torch.empty(int(qo[-1]), hq, device=DEV)
+    out = ops.paged_prefill_attention(q, kv, plan, scale, lse_out=lse, softcap=softcap)
+    tmasks = None if masks is None else [None if m is None else torch.from_numpy(m) for m in masks]
+    want, want_lse = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
+                                         masks=tmasks, window_left=window, return_lse=True, softcap=softcap)
+    close(out, want, 2e-2)
+    close(lse, want_lse, 2e-2)
+
+
 @pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (128, 4, 1), (64, 16, 2), (128, 16, 16), (128, 16, 1)])
 def test_paged_decode_attention_shared_prefix(d, hq, hkv):
     """Forks of one context share their leading pages: the cascade plan reads those pages once per
