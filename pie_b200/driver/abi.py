@@ -92,6 +92,10 @@ FIELDS: List[Tuple[str, str, int, int]] = [
     ("forward_response", "spec_accepted", 45, I32),       # accepted drafts per request
     ("forward_request", "rs_slots", 29, I32),             # recurrent-state slot per request
     ("forward_request", "rs_reset", 30, I32),             # 1 = the slot starts from zero in this fire
+    ("forward_request", "media_slot", 31, I32),           # media spans: the driver-held clip of each span,
+    ("forward_request", "media_src", 32, I32),            # its first encoder-output row,
+    ("forward_request", "media_dst", 33, I32),            # the first token row of the batch that takes it,
+    ("forward_request", "media_count", 34, I32),          # and the number of rows
 ]
 
 _SLOT_KINDS = ["token", "distribution", "logits", "logprobs", "entropy", "embedding"]
@@ -218,6 +222,7 @@ def pack_forward_request(r: ForwardRequest) -> bytes:
         "sampler_seed_final": [1 if s.seed_final else 0 for s in ss],
         "spec_counts": r.spec_counts, "context_ids": r.context_ids, "adapter_ids": r.adapter_ids,
         "rs_slots": r.rs_slots, "rs_reset": r.rs_reset,
+        "media_slot": r.media_slot, "media_src": r.media_src, "media_dst": r.media_dst, "media_count": r.media_count,
         "flags": [1 if r.single_token_mode else 0, int(r.trimmed_pages)],
     }
     return _frame(KIND_FORWARD_REQUEST, "forward_request", vals)
@@ -250,6 +255,8 @@ def unpack_forward_request(buf) -> ForwardRequest:
         slot_req=e("slot_req", np.int32), slot_row=e("slot_row", np.int32), slot_samplers=samplers,
         spec_counts=s.get("spec_counts"), context_ids=s.get("context_ids"), adapter_ids=s.get("adapter_ids"),
         rs_slots=s.get("rs_slots"), rs_reset=s.get("rs_reset"),
+        media_slot=s.get("media_slot"), media_src=s.get("media_src"), media_dst=s.get("media_dst"),
+        media_count=s.get("media_count"),
         single_token_mode=bool(flags[0]), trimmed_pages=int(flags[1]))
 
 

@@ -19,6 +19,7 @@ runs it in a process of its own (service/inproc_service.cpp:31-191 is the refere
 from __future__ import annotations
 
 import heapq
+import base64
 import itertools
 import os
 import threading
@@ -87,8 +88,13 @@ def dispatch(driver, op: int, payload):
                 driver.shutdown()
             return True
         if name in ("create_adapter", "destroy_adapter", "fork_adapter", "save_adapter", "load_adapter", "zo_apply",
-                    "copy_rs"):
+                    "copy_rs", "release_media"):
             return getattr(driver, name)(*payload.get("args", []))
+        if name == "put_media":
+            # patch rows cross the control plane as base64 float16 (a cold path: once per image)
+            slot, kind, b64, shape, grids = payload["args"]
+            patches = np.frombuffer(base64.b64decode(b64), dtype=np.float16).reshape(shape).astype(np.float32)
+            return driver.put_media(slot, kind, patches, grids)
         raise ValueError(f"unknown control operation {name!r}")
     raise ValueError(f"unknown operation {op}")
 
@@ -449,6 +455,14 @@ class ChannelDriver:
 
     def copy_rs(self, src_slot: int, dst_slot: int):
         return self._control("copy_rs", int(src_slot), int(dst_slot))
+
+    def put_media(self, slot: int, kind: str, patches, grids) -> int:
+        p = np.ascontiguousarray(patches, dtype=np.float16)
+        return self._control("put_media", int(slot), kind, base64.b64encode(p.tobytes()).decode(), list(p.shape),
+                             [[int(x) for x in g] for g in grids])
+
+    def release_media(self, slot: int):
+        return self._control("release_media", int(slot))
 
     def shutdown(self) -> None:
         if self.alive:

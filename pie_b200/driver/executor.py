@@ -139,7 +139,7 @@ class TorchDriver:
                  page_size: int = 16, max_requests: int = 512, max_tokens: int = 8192, seed: int = 0,
                  par: Optional[ParallelContext] = None, gemm_backend: str = "tcgen05", use_graphs: bool = True,
                  swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0,
-                 memory_profile: str = "", kv_dtype: str = "auto", rs_slots: int = 0):
+                 memory_profile: str = "", kv_dtype: str = "auto", rs_slots: int = 0, vision=None):
         self.cfg = cfg
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
@@ -181,6 +181,11 @@ class TorchDriver:
             from .recurrent import RecurrentStateCache
             self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
             use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet
+        # media: a vision encoder (models.vision.VisionEncoder) and the clips it has encoded, by the runtime's slot
+        self.vision = vision
+        self.media: Dict[int, torch.Tensor] = {}
+        if vision is not None and vision.cfg.hidden_size != cfg.hidden_size:
+            raise ValueError(f"vision encoder output width {vision.cfg.hidden_size} != model width {cfg.hidden_size}")
         # soft-capped attention scores (Gemma-2): bf16 pages, the 64-row prefill kernel, no shared-prefix decode plans
         self.softcap = bool(cfg.attn_softcap)
         if self.softcap and kv_dtype == "fp8_e4m3":
@@ -317,7 +322,7 @@ class TorchDriver:
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
             tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0,
-            cohort_decode=self.rs is None)
+            cohort_decode=self.rs is None, media=("image", "video") if self.vision is not None else ())
 
     # ------------------------------------------------------------------ request -> slab
     def _derive(self, req: ForwardRequest):
@@ -590,6 +595,8 @@ class TorchDriver:
                                logit_rows=torch.from_numpy(rows), is_decode=False)
         self.stats["eager"] += 1
         fi.lora = self._lora_bindings
+        if req.media_slot is not None and len(req.media_slot):
+            fi.media = self._media_inputs(req)
         if self.rs is not None:
             if req.spec_counts is not None and np.any(req.spec_counts):
                 raise ValueError("draft tokens on a model with recurrent layers: a rejected draft cannot be rolled "
@@ -599,6 +606,32 @@ class TorchDriver:
         if len(rows) == 0:
             return None
         return self.model.logits(hidden, fi)
+
+    def put_media(self, slot: int, kind: str, patches, grids) -> int:
+        """Encode an image / video (patch rows + their (t, h, w) grids, see `runtime.multimodal.patchify`) and keep
+        the encoder's output on the device under `slot`; forward requests then name it in their media spans.
+        Returns the number of rows (placeholder tokens). Counterpart of the image side channel of the
+        reference's forward request (driver/bridge/src/schema.rs, driver/cuda/src/model/qwen3_vl_vision.cpp)."""
+        if self.vision is None or kind not in ("image", "video"):
+            raise ValueError(f"this driver has no encoder for {kind}")
+        with self._order:
+            self._bind_thread()
+            feats = self.vision(np.asarray(patches, dtype=np.float32), [tuple(int(x) for x in g) for g in grids])
+            self.media[int(slot)] = feats.to(self.dtype).contiguous()
+            return int(feats.shape[0])
+
+    def release_media(self, slot: int) -> None:
+        with self._order:
+            self.media.pop(int(slot), None)
+
+    def _media_inputs(self, req: ForwardRequest):
+        out = []
+        for sl, src, dst, cnt in zip(req.media_slot, req.media_src, req.media_dst, req.media_count):
+            feats = self.media.get(int(sl))
+            if feats is None or int(src) + int(cnt) > feats.shape[0]:
+                raise ValueError(f"media slot {int(sl)} rows {int(src)}+{int(cnt)}: no such encoded clip on this driver")
+            out.append((feats, int(src), int(dst), int(cnt)))
+        return out
 
     def copy_rs(self, src_slot: int, dst_slot: int) -> None:
         """Recurrent-state slot copy (a forked context starts from its parent's state)."""
@@ -725,7 +758,8 @@ class TorchDriver:
         nslots = len(req.slot_samplers)
         self._lora_bindings = self._bind_adapters(req)
         decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None
-                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None)
+                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None
+                  and req.media_slot is None)
         if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
             # followers must draw the same tokens: fix the per-fire seeds before publishing
             from dataclasses import replace as _replace

@@ -91,6 +91,13 @@ class ForwardRequest:
     rs_slots: Optional[np.ndarray] = None     # int32 [R]
     rs_reset: Optional[np.ndarray] = None     # int32 [R]
     spec_counts: Optional[np.ndarray] = None
+    # media side channel: spans of token rows whose embeddings come from an encoded image / video / audio clip that
+    # the driver holds under `media_slot` (see `put_media`): rows media_dst[i] .. +media_count[i] of this batch take
+    # rows media_src[i] .. of that clip's encoder output instead of the token embedding
+    media_slot: Optional[np.ndarray] = None        # int32 [M]
+    media_src: Optional[np.ndarray] = None         # int32 [M]
+    media_dst: Optional[np.ndarray] = None         # int32 [M]
+    media_count: Optional[np.ndarray] = None       # int32 [M]
     context_ids: Optional[np.ndarray] = None       # uint64 [R]
     adapter_ids: Optional[np.ndarray] = None       # int64 [R], -1 = none
     single_token_mode: bool = False                # every request has exactly one input token
@@ -103,6 +110,38 @@ class ForwardRequest:
     @property
     def num_tokens(self) -> int:
         return len(self.tokens)
+
+
+# Placeholder tokens of media rows: a context's lineage stores MEDIA_TOKEN_BASE + slot * MEDIA_ROWS + row for row
+# `row` of the clip in media slot `slot`. They hash and replay like any token (the same clip gives the same
+# placeholders, so its pages are shared); the request builder turns them into media spans and sends token 0.
+MEDIA_TOKEN_BASE = 1 << 30
+MEDIA_ROWS = 1 << 16
+MEDIA_SLOTS = (1 << 30) // MEDIA_ROWS
+
+
+def media_tokens(slot: int, count: int, start: int = 0) -> List[int]:
+    if not 0 <= slot < MEDIA_SLOTS or start + count > MEDIA_ROWS:
+        raise ValueError(f"media slot {slot} / rows {start}+{count} outside the placeholder range")
+    base = MEDIA_TOKEN_BASE + slot * MEDIA_ROWS + start
+    return list(range(base, base + count))
+
+
+def split_media_spans(tokens: np.ndarray):
+    """(tokens with placeholders replaced by 0, slot, src, dst, count) - the four arrays are None when no token
+    is a media placeholder. Consecutive rows of one clip form one span."""
+    tokens = np.asarray(tokens, dtype=np.int32)
+    if tokens.size == 0 or int(tokens.max()) < MEDIA_TOKEN_BASE:
+        return tokens, None, None, None, None
+    dst = np.flatnonzero(tokens >= MEDIA_TOKEN_BASE).astype(np.int32)
+    code = tokens[dst] - MEDIA_TOKEN_BASE
+    slot, row = code // MEDIA_ROWS, code % MEDIA_ROWS
+    brk = np.flatnonzero((np.diff(dst) != 1) | (np.diff(slot) != 0) | (np.diff(row) != 1)) + 1
+    starts = np.concatenate([[0], brk])
+    counts = np.diff(np.concatenate([starts, [len(dst)]]))
+    out = tokens.copy()
+    out[dst] = 0
+    return out, slot[starts].astype(np.int32), row[starts].astype(np.int32), dst[starts], counts.astype(np.int32)
 
 
 @dataclass
@@ -175,13 +214,16 @@ class Capabilities:
     system_speculation: bool = False
     rs_cache_slots: int = 0
     cohort_decode: bool = True      # False: no array-form decode step (`decode_async`); the runtime steps per request
+    media: tuple = ()               # media kinds the driver can encode ("image", "video"); empty for text-only models
 
     def to_json(self) -> str:
         return json.dumps(asdict(self))
 
     @staticmethod
     def from_json(s: str) -> "Capabilities":
-        return Capabilities(**json.loads(s))
+        d = json.loads(s)
+        d["media"] = tuple(d.get("media") or ())
+        return Capabilities(**d)
 
 
 _SEED_MIX = np.int64(0x9E3779B97F4A7C15 - (1 << 64))

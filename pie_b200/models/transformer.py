@@ -37,6 +37,7 @@ class ForwardInputs:
     rs: Optional[object] = None   # driver.recurrent.RecurrentInputs for models with Gated DeltaNet layers
     is_decode: bool = False
     lora: Optional[list] = None   # [(LoraAdapter, int64 token rows)] for requests bound to an adapter
+    media: Optional[list] = None  # [(encoder output [rows, H], first source row, first token row, count)]
 
 
 class ParallelContext:
@@ -172,6 +173,8 @@ class Transformer:
         return comm.wait_gathered(n)
 
     def forward_hidden(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
+        if fi.media and self.par.tp_size > 1:
+            raise NotImplementedError("media inputs under tensor parallelism")
         if self._fused_tp():
             return self._forward_hidden_tp(fi, kv_cache)
         cfg, w = self.cfg, self.w
@@ -184,6 +187,9 @@ class Transformer:
         if cfg.embed_scale != 1.0:
             # the factor is rounded to the activation dtype first, as the checkpoints' own code does
             h = h * torch.tensor(cfg.embed_scale, dtype=h.dtype).item()
+        for feats, src, dst, cnt in fi.media or ():
+            # rows of an encoded image / video take the place of their placeholder tokens' embeddings
+            h[dst:dst + cnt] = feats[src:src + cnt].to(h.dtype)
         n = h.shape[0]
         for li in range(cfg.num_hidden_layers):
             lw = w["layers"][li]
@@ -357,11 +363,13 @@ def _dense_gdn(cfg: ModelConfig, lw: dict, xn: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor) -> torch.Tensor:
+def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor, embeds: Optional[dict] = None) -> torch.Tensor:
     """Independent dense (non-paged) fp32 forward of the same weights for one sequence:
     RMSNorm -> QKV -> rotate-half RoPE -> causal attention -> SwiGLU. Returns logits [T, V].
     This is the token-for-token oracle of the paged engine path."""
     x = w["embed"].float()[tokens.long()] * cfg.embed_scale
+    for row, vec in (embeds or {}).items():        # {token row: embedding} of media rows
+        x[row] = vec.float()
     t = x.shape[0]
     pos = torch.arange(t)
     inv_global = reference.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)

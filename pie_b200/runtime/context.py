@@ -104,6 +104,7 @@ class ContextManager:
         self.counters = {"created": 0, "forked": 0, "commits": 0, "dedup_pages": 0, "suspended": 0,
                          "restored": 0, "evictions": 0, "replayed_tokens": 0}
         self.market = None   # optional Market: orders eviction victims (defaulted, lowest bid, newest)
+        self.media = None    # optional runtime.media.MediaRegistry: encoded clips held by the contexts' lineages
         # recurrent-state slot pools, one per driver (all empty for pure-attention models)
         from .rs_cache import RsCache
         self.rs = [RsCache(int(rs_slots[d]) if d < len(rs_slots) else 0) for d in range(len(self.stores))]
@@ -273,6 +274,8 @@ class ContextManager:
                 self._swap_free.extend(ctx.stash)
             ctx.chain, ctx.working_pages, ctx.stash = [], [], None
             self.rs[ctx.driver].forget(cid)
+            if self.media is not None:
+                self.media.drop(cid)
             ctx.state = State.DESTROYED
             self.by_owner.get(ctx.owner, set()).discard(cid)
             del self.contexts[cid]
@@ -411,6 +414,8 @@ class ContextManager:
                 bid=src.bid, created_seq=next(self._seq))
             self.by_owner.setdefault(own, set()).add(nid)
             self.counters["forked"] += 1
+            if self.media is not None:
+                self.media.fork(cid, nid)       # the child's lineage holds the parent's clips
             rs = self.rs[src.driver]
             if rs.supported:
                 from .rs_cache import RsState

@@ -63,6 +63,7 @@ class ModelEntry:
         self.arch = arch or self.caps[0].arch_name
         self.ctxm: ContextManager = None
         self.adapters = None          # AdapterService
+        self.media = None             # MediaRegistry when every driver declares an encoder
         self.inference: InferenceService = None
         self.schedulers: List[BatchScheduler] = []
 
@@ -116,6 +117,9 @@ class Engine:
         entry.ctxm = ContextManager(name, entry.page_size, stores, copy_fn, swap_pages=swap,
                                     rs_slots=[c.rs_cache_slots for c in entry.caps],
                                     rs_copy_fn=lambda d, src, dst: entry.drivers[d].copy_rs(src, dst))
+        if all(getattr(c, "media", ()) for c in entry.caps):
+            from .media import MediaRegistry
+            entry.media = entry.ctxm.media = MediaRegistry(entry.drivers)
         from .adapter import AdapterService
         entry.adapters = AdapterService(entry.drivers, self.config.adapter_dir)
         for i, (drv, caps) in enumerate(zip(entry.drivers, entry.caps)):

@@ -21,7 +21,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
-from ..driver.schema import SamplerSpec, SlotOutput
+from ..driver.schema import MEDIA_TOKEN_BASE, SamplerSpec, SlotOutput
 from .context import ContextError, ContextManager, Deferred
 from .scheduler import BatchScheduler, PendingRequest
 
@@ -205,6 +205,10 @@ class InferenceService:
         if found < 0 or found >= len(hist):
             return None
         drafts = hist[found:found + k]
+        for j, t in enumerate(drafts):          # a media placeholder is never a sampled token: the draft ends before it
+            if t >= MEDIA_TOKEN_BASE:
+                drafts = drafts[:j]
+                break
         if not drafts:
             return None
         ps = self.ctxm.page_size

@@ -23,7 +23,7 @@ from typing import Callable, List, Optional, Sequence
 import numpy as np
 
 from . import brle, telemetry
-from ..driver.schema import Capabilities, ForwardRequest, ForwardResponse, SamplerSpec, SlotOutput
+from ..driver.schema import Capabilities, ForwardRequest, ForwardResponse, SamplerSpec, SlotOutput, split_media_spans
 
 
 class SlotList(list):
@@ -213,8 +213,11 @@ def fold(items: Sequence[PendingRequest], page_size: int, trim: bool = True) -> 
         rs_slots[i], rs_reset[i] = it.rs_slot, it.rs_reset
     cat = lambda xs: np.concatenate(xs) if xs else np.zeros(0, dtype=np.int32)
     any_mask = bool(has_mask.any())
+    # media placeholders in the lineage become spans of the side channel; the driver sees token 0 there
+    toks, m_slot, m_src, m_dst, m_cnt = split_media_spans(cat(tokens))
     return ForwardRequest(
-        tokens=cat(tokens), positions=cat(positions), qo_indptr=qo, kv_page_indices=cat(pages),
+        tokens=toks, positions=cat(positions), qo_indptr=qo, kv_page_indices=cat(pages),
+        media_slot=m_slot, media_src=m_src, media_dst=m_dst, media_count=m_cnt,
         kv_page_indptr=pptr, kv_last_page_lens=last,
         has_user_mask=has_mask if any_mask else None, mask_runs=mask_runs if any_mask else None,
         mask_row_indptr=mask_ptr if any_mask else None,

@@ -357,11 +357,19 @@ class Context:
         self._buffer.extend(int(t) for t in tokens)
         return self
 
-    def append_image(self, image) -> "Context":
-        """Splice an image's encoder tokens into the context (needs a driver with a vision encoder)."""
+    def _append_clip(self, kind: str, features) -> "Context":
         from . import media
-        media.require(self._model, "image")
-        raise media.MediaUnsupported("image tokens are produced by the driver's encoder")
+        media.require(self._model, kind)
+        reg = self._entry.media
+        # the driver encodes the clip (once per distinct content) and keeps the result on the device; the context
+        # takes one placeholder token per encoder row, which the request builder turns into media spans
+        self._buffer.extend(reg.put(self.id, kind, features.patches, [features.grid]))
+        return self
+
+    def append_image(self, image) -> "Context":
+        """Splice an image into the context: one placeholder token per row of the vision encoder's output
+        (needs a driver with a vision encoder). Chat markers around the image are the template's business."""
+        return self._append_clip("image", image.features)
 
     def append_audio(self, audio) -> "Context":
         from . import media
@@ -369,9 +377,7 @@ class Context:
         raise media.MediaUnsupported("audio tokens are produced by the driver's encoder")
 
     def append_video(self, video) -> "Context":
-        from . import media
-        media.require(self._model, "video")
-        raise media.MediaUnsupported("video tokens are produced by the driver's encoder")
+        return self._append_clip("video", video.features)
 
     # ---- page management
     def _reserve_for(self, n_new: int) -> None:

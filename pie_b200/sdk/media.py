@@ -1,9 +1,11 @@
 """Media inputs and audio output for inferlets (WIT `pie:core/media`, `pie:core/audio-out`).
 
 Preprocessing runs on the host (`pie_b200.runtime.multimodal`); whether a model can consume the
-result depends on its driver declaring an encoder (`Capabilities.media`). The text-only model
-families of this build declare none, so `Context.append_image` and friends raise
-`MediaUnsupported` there; the preprocessing itself is usable on its own.
+result depends on its driver declaring an encoder (`Capabilities.media`). A driver built with a vision
+encoder (`models.vision`) declares "image" and "video": `Context.append_image` / `append_video` then hand
+the patch rows to the driver and splice one placeholder token per encoder row into the context. Text-only
+models declare nothing and those calls raise `MediaUnsupported`; there is no audio encoder, so
+`append_audio` always does. The preprocessing itself is usable on its own.
 Counterpart of sdk/python/src/inferlet/media.py and audio.py.
 """
 from __future__ import annotations

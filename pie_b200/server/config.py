@@ -77,6 +77,8 @@ class DriverConfig:
     gemm: str = "tcgen05"
     tp_backend: str = "fused"
     memory_profile: str = ""              # "" = built-in limits; auto | latency | balanced | throughput | capacity
+    vision: str = ""                      # "" = text only | "checkpoint" (the `visual.*` tower of [model] path) |
+                                          # a preset of models.vision with random weights (e.g. "tiny-vit")
     ipc: str = "direct"                   # runtime -> driver: direct call | inproc (queue + service thread) |
                                           # latency (polled ring) | shmem (driver in a process of its own)
 

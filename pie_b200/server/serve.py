@@ -70,6 +70,22 @@ def _config_and_tokenizer(m: ModelSection):
     return cfg, tok
 
 
+def _vision_encoder(m: ModelSection, cfg, device, dtype):
+    """The model's vision encoder per `[model.driver] vision`, or None for a text-only model."""
+    kind = m.driver.vision
+    if not kind:
+        return None
+    import json as _json
+    from ..models import vision as V
+    if kind == "checkpoint":
+        from ..models.loader import SafetensorsReader
+        hf = _json.loads((Path(m.path) / "config.json").read_text())
+        vcfg = V.VisionConfig.from_hf(hf.get("vision_config") or {}, llm_hidden=cfg.hidden_size)
+        return V.VisionEncoder(vcfg, V.load_vision_weights(SafetensorsReader(m.path), device, dtype))
+    vcfg = V.vision_preset(kind, hidden_size=cfg.hidden_size)
+    return V.VisionEncoder(vcfg, V.random_vision_weights(vcfg, device, dtype))
+
+
 def _build_drivers_direct(m: ModelSection):
     """Drivers of one model: one per data-parallel group. Returns (drivers, cfg, tokenizer, comm)."""
     d = m.driver
@@ -107,7 +123,8 @@ def _build_drivers_direct(m: ModelSection):
         if m.path:
             _, w = loader.load_checkpoint(m.path, "cpu", dtype="float32")
             cfg.dtype = "float32"
-        return [TorchDriver(cfg, "cpu", weights=w, num_pages=4096, page_size=d.kv_page_size)], cfg, tok, comm
+        return [TorchDriver(cfg, "cpu", weights=w, num_pages=4096, page_size=d.kv_page_size,
+                            vision=_vision_encoder(m, cfg, "cpu", torch.float32))], cfg, tok, comm
     groups = calculate_topology(d.device, d.tensor_parallel_size)
     drivers = []
     if d.tensor_parallel_size > 1:
@@ -144,7 +161,8 @@ def _build_drivers_direct(m: ModelSection):
         swap = int(d.swap_pool_gb * (1 << 30) // per_page)
         drivers.append(TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, gemm_backend=d.gemm,
                                    use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
-                                   swap_pages=swap, memory_profile=d.memory_profile))
+                                   swap_pages=swap, memory_profile=d.memory_profile,
+                                   vision=_vision_encoder(m, cfg, dev, torch.bfloat16)))
         if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
             n = drivers[-1].precapture_graphs()
             log.info("model %s on %s: %d decode graphs captured ahead of time", m.name, dev, n)

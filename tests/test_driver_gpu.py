@@ -239,3 +239,37 @@ def test_gemma_driver_matches_dense_oracle(name, over):
         ref_row = want[b - 1]
         cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
         assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (name, a, b, cos)
+
+
+def test_media_rows_replace_embeddings_on_the_gpu_driver():
+    """A vision encoder on the device: `put_media` keeps the encoder's rows on the GPU, a prefill whose tokens are media
+    placeholders reads them in place of the embeddings (chunked in the middle of the image), decode follows in a graph."""
+    from pie_b200.driver.schema import media_tokens
+    from pie_b200.models.vision import VisionEncoder, random_vision_weights, vision_preset
+    cfg = preset("tiny-llama", dtype="bfloat16")
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=4)
+    vcfg = vision_preset("tiny-vit", hidden_size=cfg.hidden_size)
+    enc = VisionEncoder(vcfg, random_vision_weights(vcfg, "cuda", torch.bfloat16, seed=5))
+    drv = TorchDriver(cfg, "cuda", weights=w, num_pages=32, page_size=16, max_requests=4, max_tokens=128, vision=enc)
+    rng = np.random.default_rng(0)
+    grid = (1, 6, 8)
+    patches = rng.standard_normal((48, vcfg.patch_features)).astype(np.float32)
+    n_img = drv.put_media(5, "image", patches, [grid])
+    assert n_img == 12 and drv.media[5].is_cuda and drv.capabilities().media == ("image", "video")
+    seq = [70, 71, 72] + media_tokens(5, n_img) + [73, 74]
+    rows = drv.media[5].float().cpu()
+    wf = {"layers": [{k: v.float().cpu() for k, v in lw.items()} for lw in w["layers"]],
+          **{k: v.float().cpu() for k, v in w.items() if torch.is_tensor(v)}}
+    plain = [t if t < (1 << 30) else 0 for t in seq]
+    want = dense_reference_forward(cfg, wf, torch.tensor(plain), embeds={3 + i: rows[i] for i in range(n_img)}).numpy()
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    pages = list(range(2))
+    for a, b in ((0, 8), (8, 16), (16, 17)):                # the first chunk ends inside the image
+        req = fold([PendingRequest(0, seq[a:b], list(range(a, b)), pages, a, [(b - a - 1, raw)])], 16)
+        assert (req.media_slot is not None) == (a < 15)
+        got = np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
+        ref_row = want[b - 1]
+        cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
+        assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (a, b, cos)
+    drv.release_media(5)
+    assert drv.media == {}

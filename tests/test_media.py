@@ -1,0 +1,195 @@
+"""Media inputs end to end on the CPU driver: vision tower against transformers' Qwen2-VL tower; placeholder
+tokens -> media spans -> embedding override in the driver; generation over an image equals the dense oracle fed
+with the encoder's rows; chunked prefill through an image; content-addressed sharing of clips and of their KV
+pages; slot release with the last context; replay after eviction; the wire format; the example inferlets."""
+import base64
+import io
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from pie_b200.driver import abi
+from pie_b200.driver.executor import TorchDriver
+from pie_b200.driver.schema import MEDIA_TOKEN_BASE, ForwardRequest, media_tokens, split_media_spans
+from pie_b200.inferlets import install_all
+from pie_b200.models.config import preset
+from pie_b200.models.transformer import dense_reference_forward
+from pie_b200.models.vision import VisionEncoder, random_vision_weights, vision_preset
+from pie_b200.models.weights import random_weights
+from pie_b200.runtime import multimodal as mm
+from pie_b200.runtime.engine import Engine, EngineConfig
+from pie_b200.runtime.scheduler import PendingRequest, fold
+from pie_b200.runtime.tokenizer import ByteTokenizer
+
+
+def png_bytes(seed: int, h: int = 60, w: int = 90) -> bytes:
+    from PIL import Image
+    rng = np.random.default_rng(seed)
+    buf = io.BytesIO()
+    Image.fromarray(rng.integers(0, 255, (h, w, 3), dtype=np.uint8)).save(buf, format="PNG")
+    return buf.getvalue()
+
+
+def gif_bytes(frames: int = 4) -> bytes:
+    from PIL import Image
+    rng = np.random.default_rng(9)
+    ims = [Image.fromarray(rng.integers(0, 255, (56, 56, 3), dtype=np.uint8)) for _ in range(frames)]
+    buf = io.BytesIO()
+    ims[0].save(buf, format="GIF", save_all=True, append_images=ims[1:])
+    return buf.getvalue()
+
+
+def test_vision_tower_equals_transformers_qwen2_vl():
+    from transformers.models.qwen2_vl import modeling_qwen2_vl as m
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
+    cfg = vision_preset("tiny-vit", hidden_size=128)
+    w = random_vision_weights(cfg, seed=1)
+    c = Qwen2VLVisionConfig(depth=cfg.depth, embed_dim=cfg.embed_dim, hidden_size=cfg.hidden_size, num_heads=cfg.num_heads,
+                            mlp_ratio=int(cfg.mlp_ratio), patch_size=14, spatial_merge_size=2, temporal_patch_size=2, in_channels=3)
+    c._attn_implementation = "eager"
+    tower = m.Qwen2VisionTransformerPretrainedModel(c).float().eval()
+    sd = dict(w)
+    sd["patch_embed.proj.weight"] = w["patch_embed.proj.weight"].reshape(cfg.embed_dim, 3, 2, 14, 14)
+    tower.load_state_dict(sd, strict=True)
+    # a real preprocessing result (row order and feature order of `patchify`) and a two-frame-group clip
+    f1 = mm.patchify([mm.decode_image(png_bytes(1))], min_pixels=28 * 28, max_pixels=28 * 28 * 12)
+    f2 = mm.patchify(mm.decode_frames(gif_bytes(4)), min_pixels=28 * 28, max_pixels=28 * 28 * 4)
+    assert f2.grid[0] == 2
+    x = torch.from_numpy(np.concatenate([f1.patches, f2.patches]))
+    with torch.no_grad():
+        want = tower(x, torch.tensor([f1.grid, f2.grid]))
+    want = want if torch.is_tensor(want) else want.pooler_output
+    got = VisionEncoder(cfg, w)(x, [f1.grid, f2.grid])
+    assert got.shape == (f1.num_tokens + f2.num_tokens, 128) and (got - want).abs().max() < 1e-5
+
+
+def test_placeholders_become_spans_and_cross_the_wire():
+    t = [5, 6] + media_tokens(3, 4) + [7] + media_tokens(3, 2, 4) + media_tokens(9, 3)
+    toks, slot, src, dst, cnt = split_media_spans(np.array(t))
+    assert toks.tolist() == [5, 6, 0, 0, 0, 0, 7, 0, 0, 0, 0, 0]
+    assert (slot.tolist(), src.tolist(), dst.tolist(), cnt.tolist()) == ([3, 3, 9], [0, 4, 0], [2, 7, 9], [4, 2, 3])
+    assert split_media_spans(np.array([1, 2, 3]))[1] is None
+    a = PendingRequest(0, [11] + media_tokens(2, 5), list(range(6)), [0], 0, [])
+    b = PendingRequest(1, media_tokens(2, 3, 5) + [12], list(range(6, 10)), [1], 6, [])
+    req = fold([a, b], 16)
+    assert req.tokens.tolist() == [11, 0, 0, 0, 0, 0, 0, 0, 0, 12]
+    # the two requests carry consecutive rows of one clip at consecutive batch rows: one span covers both
+    assert (req.media_slot.tolist(), req.media_src.tolist(), req.media_dst.tolist(), req.media_count.tolist()) == \
+        ([2], [0], [1], [8])
+    back = abi.unpack_forward_request(abi.pack_forward_request(req))
+    for k in ("media_slot", "media_src", "media_dst", "media_count", "tokens"):
+        assert np.array_equal(getattr(back, k), getattr(req, k)), k
+    plain = abi.unpack_forward_request(abi.pack_forward_request(fold([PendingRequest(0, [1, 2], [0, 1], [0], 0, [])], 16)))
+    assert plain.media_slot is None
+
+
+@pytest.fixture()
+def eng():
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=3)
+    vcfg = vision_preset("tiny-vit", hidden_size=cfg.hidden_size)
+    enc = VisionEncoder(vcfg, random_vision_weights(vcfg, seed=5))
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=48, vision=enc)
+    e = Engine(EngineConfig())
+    e.add_model("vlm", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
+    install_all(e)
+    yield e, cfg, w, enc, drv
+    e.shutdown()
+
+
+def oracle(cfg, w, enc, feats, pre, post, n):
+    """Greedy continuation of pre + image + post by the dense model, the image rows replaced by the encoder's output."""
+    rows = enc(feats.patches, [feats.grid])
+    toks = list(pre) + [0] * rows.shape[0] + list(post)
+    emb = {len(pre) + i: rows[i] for i in range(rows.shape[0])}
+    out = []
+    for _ in range(n):
+        nxt = int(dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+def test_generation_over_an_image_equals_the_oracle_and_shares_work(eng):
+    e, cfg, w, enc, drv = eng
+    assert drv.capabilities().media == ("image", "video") and e.models["vlm"].media is not None
+    data = png_bytes(2, 280, 420)
+    resize = dict(min_pixels=28 * 28, max_pixels=28 * 28 * 80)
+    feats = mm.patchify([mm.decode_image(data)], **resize)
+    assert feats.num_tokens > 48                 # more image rows than one fire takes: the prefill is chunked inside the image
+    q = "What is this?"
+    args = {"image_b64": base64.b64encode(data).decode(), "question": q, "max_tokens": 5, "temperature": 0.0, "resize": resize}
+    out = json.loads(e.run("image-qa", args, 300))
+    assert out["ok"] and out["image_tokens"] == feats.num_tokens and out["grid"] == list(feats.grid)
+    assert out["tokens"] == oracle(cfg, w, enc, feats, [], ByteTokenizer(cfg.vocab_size).encode(q), 5)
+    entry = e.models["vlm"]
+    assert entry.schedulers[0].stats["chunked_requests"] >= 1
+    # the context is gone: so is the clip, on the registry and on the driver
+    assert entry.media.stats()["resident"] == 0 and drv.media == {}
+    # the same image twice in a row inside one program: encoded once; the second context reuses the first one's pages
+    before = entry.ctxm.counters["dedup_pages"]
+    out2 = json.loads(e.run("multi-image-test", {"images_b64": [args["image_b64"], base64.b64encode(png_bytes(7)).decode()],
+                                                 "rounds": 2, "max_tokens": 3, "resize": resize}, 300))
+    assert out2["ok"] and out2["same_output"] and out2["image_tokens"][0] == feats.num_tokens
+    assert out2["media"]["encoded"] - 1 == 2 and out2["media"]["shared"] == 2     # (one clip was encoded by image-qa above)
+    assert out2["media"]["resident"] == 2 and entry.ctxm.counters["dedup_pages"] - before >= feats.num_tokens // 16
+    assert entry.media.stats()["resident"] == 0
+
+
+def test_fork_keeps_the_clip_and_eviction_replays_it(eng):
+    e, cfg, w, enc, drv = eng
+    from pie_b200.sdk import Context, Model, Sampler, media
+
+    async def prog(args):
+        model = Model.load("vlm")
+        im = media.Image.from_bytes(png_bytes(4), min_pixels=28 * 28, max_pixels=28 * 28 * 12)
+        ctx = Context(model)
+        ctx.append([10, 11]).append_image(im).append([12])
+        await ctx.flush()
+        child = ctx.fork()
+        ctx.release()                                   # the child still holds the clip
+        assert model._entry.media.stats()["resident"] == 1
+        child.suspend()                                 # KV goes away; the lineage (placeholders included) is replayed
+        toks = await child.append([13]).generate(Sampler.argmax(), max_tokens=4).collect_tokens()
+        child.release()
+        return json.dumps({"tokens": toks, "image_tokens": im.num_tokens})
+    e.register_program("fork-evict", prog)
+    out = json.loads(e.run("fork-evict", {}, 300))
+    feats = mm.patchify([mm.decode_image(png_bytes(4))], min_pixels=28 * 28, max_pixels=28 * 28 * 12)
+    assert out["tokens"] == oracle(cfg, w, enc, feats, [10, 11], [12, 13], 4)
+    assert e.models["vlm"].media.stats()["resident"] == 0 and drv.media == {}
+
+
+def test_video_clip_and_text_only_models(eng):
+    e, cfg, w, enc, drv = eng
+    out = json.loads(e.run("video-qa", {"video_b64": base64.b64encode(gif_bytes(4)).decode(), "max_tokens": 3,
+                                        "resize": dict(min_pixels=28 * 28, max_pixels=28 * 28 * 4)}, 300))
+    assert out["ok"] and out["grid"][0] == 2 and len(out["tokens"]) == 3
+    # a driver without an encoder declares nothing; the SDK refuses, the driver rejects spans it cannot serve
+    plain = TorchDriver(cfg, "cpu", weights=w, num_pages=8, page_size=16, max_requests=2, max_tokens=32)
+    assert plain.capabilities().media == ()
+    with pytest.raises(ValueError, match="no encoder"):
+        plain.put_media(0, "image", np.zeros((4, 1176), np.float32), [(1, 2, 2)])
+    req = fold([PendingRequest(0, media_tokens(0, 4), [0, 1, 2, 3], [0], 0, [])], 16)
+    with pytest.raises(ValueError, match="no such encoded clip"):
+        plain.fire_batch(req)
+    assert MEDIA_TOKEN_BASE > cfg.vocab_size
+
+
+def test_media_crosses_the_driver_channel(eng):
+    from pie_b200.driver.channel import ChannelDriver, InProcChannel
+    e, cfg, w, enc, drv = eng
+    ch = ChannelDriver(InProcChannel(drv))
+    try:
+        feats = mm.patchify([mm.decode_image(png_bytes(5))], min_pixels=28 * 28, max_pixels=28 * 28 * 4)
+        n = ch.put_media(7, "image", feats.patches, [feats.grid])
+        assert n == feats.num_tokens and 7 in drv.media and tuple(ch.capabilities().media) == ("image", "video")
+        # patch rows travel as float16: the stored rows match the direct path to that rounding
+        direct = enc(feats.patches.astype(np.float16).astype(np.float32), [feats.grid])
+        assert (drv.media[7] - direct).abs().max() < 1e-5
+        ch.release_media(7)
+        assert 7 not in drv.media
+    finally:
+        ch.channel.close()
