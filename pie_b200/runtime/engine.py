@@ -320,6 +320,8 @@ class Engine:
         for e in self.models.values():
             for s in e.schedulers:
                 s.shutdown()
+            if e.media is not None:
+                e.media.close()
             for d in e.drivers:
                 try:
                     d.shutdown()

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import hashlib
 import threading
+from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
 from typing import Dict, List, Sequence, Set, Tuple
 
@@ -29,6 +30,7 @@ class MediaEntry:
     kind: str
     rows: int
     refs: int = 0
+    ready: object = None      # runtime.inference.Future: set when every driver holds the encoded rows (or with the error)
 
 
 class MediaRegistry:
@@ -41,6 +43,9 @@ class MediaRegistry:
         self._next = 0
         self._free: List[int] = []
         self.counters = {"encoded": 0, "shared": 0, "released": 0}
+        # encoders run off the caller's thread: an inferlet's coroutine appends the placeholders at once and only its
+        # next forward pass waits for the rows (`MediaEntry.ready`)
+        self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="pie-media")
 
     @staticmethod
     def content_key(kind: str, patches: np.ndarray, grids) -> bytes:
@@ -50,8 +55,13 @@ class MediaRegistry:
         h.update(np.ascontiguousarray(patches, dtype=np.float32).tobytes())
         return h.digest()
 
-    def put(self, ctx_id: int, kind: str, patches: np.ndarray, grids: Sequence[Tuple[int, int, int]]) -> List[int]:
-        """Encode a clip (or find it encoded already), tie it to the context, return its placeholder tokens."""
+    def put(self, ctx_id: int, kind: str, patches: np.ndarray, grids: Sequence[Tuple[int, int, int]], rows: int):
+        """Tie a clip of `rows` encoder rows to the context and return (its placeholder tokens, its entry). A clip
+        that is not resident yet is handed to the drivers on the registry's worker thread; `entry.ready` completes
+        when they hold it. Nothing here waits for an encoder."""
+        from .inference import Future
+        if not 0 < rows <= MEDIA_ROWS:
+            raise ValueError(f"a clip of {rows} rows is outside the placeholder range")
         key = self.content_key(kind, patches, grids)
         with self.lock:
             e = self.by_key.get(key)
@@ -62,18 +72,24 @@ class MediaRegistry:
                     slot, self._next = self._next, self._next + 1
                 else:
                     raise RuntimeError("out of media slots")
-                rows = {int(d.put_media(slot, kind, patches, grids)) for d in self.drivers}
-                if len(rows) != 1 or not 0 < next(iter(rows)) <= MEDIA_ROWS:
-                    for d in self.drivers:
-                        d.release_media(slot)
-                    self._free.append(slot)
-                    raise RuntimeError(f"drivers disagree on the clip's size, or it is out of range: {sorted(rows)} rows")
-                e = self.by_key[key] = self.by_slot[slot] = MediaEntry(slot, key, kind, rows.pop())
+                e = self.by_key[key] = self.by_slot[slot] = MediaEntry(slot, key, kind, rows, ready=Future())
                 self.counters["encoded"] += 1
+                self._pool.submit(self._encode, e, np.ascontiguousarray(patches, dtype=np.float32), [tuple(g) for g in grids])
             else:
+                if e.rows != rows:
+                    raise RuntimeError(f"clip is resident with {e.rows} rows, caller expects {rows}")
                 self.counters["shared"] += 1
-            self._attach(ctx_id, e)
-            return media_tokens(e.slot, e.rows)
+            self._attach(ctx_id, e)          # the reference is taken before the encoder runs: nobody frees the slot meanwhile
+            return media_tokens(e.slot, e.rows), e
+
+    def _encode(self, e: MediaEntry, patches: np.ndarray, grids) -> None:
+        try:
+            got = {int(d.put_media(e.slot, e.kind, patches, grids)) for d in self.drivers}
+            if got != {e.rows}:
+                raise RuntimeError(f"encoder gave {sorted(got)} rows for a clip planned with {e.rows}")
+            e.ready.set(True)
+        except BaseException as exc:  # noqa: BLE001 - the waiting forward pass gets the error
+            e.ready.set(None, exc)
 
     def _attach(self, ctx_id: int, e: MediaEntry) -> None:
         held = self.of_context.setdefault(ctx_id, set())
@@ -95,11 +111,25 @@ class MediaRegistry:
                     del self.by_slot[slot], self.by_key[e.key]
                     self._free.append(slot)
                     self.counters["released"] += 1
-                    for d in self.drivers:
-                        try:
-                            d.release_media(slot)
-                        except Exception:  # noqa: BLE001 - a dead driver has nothing left to release
-                            pass
+                    # after the encoder (same single worker): a clip dropped while it was being encoded is released too
+                    self._pool.submit(self._release, slot)
+
+    def _release(self, slot: int) -> None:
+        with self.lock:
+            if slot in self.by_slot:        # taken again meanwhile: that clip's rows now live there
+                return
+        for d in self.drivers:
+            try:
+                d.release_media(slot)
+            except Exception:  # noqa: BLE001 - a dead driver has nothing left to release
+                pass
+
+    def drain(self, timeout: float = 30.0) -> None:
+        """Wait until the worker has run everything queued so far (tests, shutdown)."""
+        self._pool.submit(lambda: None).result(timeout)
+
+    def close(self) -> None:
+        self._pool.shutdown(wait=False, cancel_futures=True)
 
     def stats(self) -> dict:
         with self.lock:

@@ -205,6 +205,10 @@ class Forward:
             ctx._reserve_for(n_in)                       # the common case needs no waiting (and no coroutine)
         except _Deferred:
             await ctx._reserve_async(n_in)
+        pending = ctx.__dict__.get("_pending_media")
+        if pending:                                      # clips appended since the last pass: their encoder must be done
+            while pending:
+                await host.wait(pending.pop().ready)
         svc = ctx._entry.inference
         fut = svc.submit(ctx.id, self._tokens, self._positions, self._samplers, self._attn_masks, self._mask,
                          self._spec_tokens, self._spec_positions, self._adapter, self._speculate,
@@ -263,6 +267,8 @@ class Context:
         cid = self._entry.ctxm.fork(self.id)
         c = Context(self._model, _id=cid, _seq_len=self._seq_len, _next_pos=self._next_pos)
         c._buffer = list(self._buffer)
+        if self.__dict__.get("_pending_media"):
+            c._pending_media = list(self._pending_media)
         return c
 
     def save(self, name: str) -> None:
@@ -361,9 +367,15 @@ class Context:
         from . import media
         media.require(self._model, kind)
         reg = self._entry.media
-        # the driver encodes the clip (once per distinct content) and keeps the result on the device; the context
-        # takes one placeholder token per encoder row, which the request builder turns into media spans
-        self._buffer.extend(reg.put(self.id, kind, features.patches, [features.grid]))
+        # the driver encodes the clip (once per distinct content, on the registry's worker thread) and keeps the result
+        # on the device; the context takes one placeholder token per encoder row at once, which the request builder
+        # turns into media spans, and its next forward pass waits for the encoder
+        toks, entry = reg.put(self.id, kind, features.patches, [features.grid], features.num_tokens)
+        self._buffer.extend(toks)
+        if not entry.ready.done():
+            self.__dict__.setdefault("_pending_media", []).append(entry)
+        else:
+            entry.ready.result()            # an encoder error of an earlier caller is this caller's too
         return self
 
     def append_image(self, image) -> "Context":

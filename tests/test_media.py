@@ -126,7 +126,8 @@ def test_generation_over_an_image_equals_the_oracle_and_shares_work(eng):
     assert out["tokens"] == oracle(cfg, w, enc, feats, [], ByteTokenizer(cfg.vocab_size).encode(q), 5)
     entry = e.models["vlm"]
     assert entry.schedulers[0].stats["chunked_requests"] >= 1
-    # the context is gone: so is the clip, on the registry and on the driver
+    # the context is gone: so is the clip, on the registry and (once its worker has run) on the driver
+    entry.media.drain()
     assert entry.media.stats()["resident"] == 0 and drv.media == {}
     # the same image twice in a row inside one program: encoded once; the second context reuses the first one's pages
     before = entry.ctxm.counters["dedup_pages"]
@@ -159,6 +160,7 @@ def test_fork_keeps_the_clip_and_eviction_replays_it(eng):
     out = json.loads(e.run("fork-evict", {}, 300))
     feats = mm.patchify([mm.decode_image(png_bytes(4))], min_pixels=28 * 28, max_pixels=28 * 28 * 12)
     assert out["tokens"] == oracle(cfg, w, enc, feats, [10, 11], [12, 13], 4)
+    e.models["vlm"].media.drain()
     assert e.models["vlm"].media.stats()["resident"] == 0 and drv.media == {}
 
 
@@ -193,3 +195,53 @@ def test_media_crosses_the_driver_channel(eng):
         assert 7 not in drv.media
     finally:
         ch.channel.close()
+
+
+def test_registry_encodes_off_thread_shares_by_content_and_reports_errors():
+    import threading
+    import time
+    from pie_b200.runtime.media import MediaRegistry
+
+    class FakeDriver:
+        def __init__(self):
+            self.gate, self.held, self.calls = threading.Event(), {}, []
+
+        def put_media(self, slot, kind, patches, grids):
+            self.gate.wait(5)
+            self.calls.append(("put", slot))
+            if patches[0, 0] < 0:
+                raise ValueError("bad clip")
+            self.held[slot] = len(patches) // 4
+            return len(patches) // 4
+
+        def release_media(self, slot):
+            self.calls.append(("release", slot))
+            self.held.pop(slot, None)
+    d = FakeDriver()
+    reg = MediaRegistry([d])
+    a = np.ones((8, 4), np.float32)
+    t0 = time.monotonic()
+    toks, e1 = reg.put(1, "image", a, [(1, 2, 4)], 2)
+    assert time.monotonic() - t0 < 1.0 and not e1.ready.done()          # the caller did not wait for the encoder
+    toks2, e2 = reg.put(2, "image", a.copy(), [(1, 2, 4)], 2)            # same content: same entry, same placeholders
+    assert e2 is e1 and toks2 == toks and reg.stats()["encoded"] == 1 and reg.stats()["shared"] == 1
+    reg.drop(1)
+    assert reg.stats()["resident"] == 1                                  # context 2 still holds it
+    d.gate.set()
+    assert e1.ready.result(5) is True and d.held == {e1.slot: 2}
+    reg.drop(2)
+    reg.drain()
+    assert d.held == {} and reg.stats()["resident"] == 0 and ("release", e1.slot) in d.calls
+    # the freed slot is taken again; an encoder error reaches whoever waits, and a wrong row count is an error too
+    _, bad = reg.put(3, "image", -a, [(1, 2, 4)], 2)
+    with pytest.raises(ValueError, match="bad clip"):
+        bad.ready.result(5)
+    _, short = reg.put(3, "image", a * 2, [(1, 2, 4)], 3)
+    with pytest.raises(RuntimeError, match="planned with 3"):
+        short.ready.result(5)
+    with pytest.raises(ValueError, match="outside the placeholder range"):
+        reg.put(3, "image", a, [(1, 2, 4)], 0)
+    reg.drop(3)
+    reg.drain()
+    assert reg.stats()["resident"] == 0
+    reg.close()
