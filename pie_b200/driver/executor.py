@@ -139,7 +139,7 @@ class TorchDriver:
                  page_size: int = 16, max_requests: int = 512, max_tokens: int = 8192, seed: int = 0,
                  par: Optional[ParallelContext] = None, gemm_backend: str = "tcgen05", use_graphs: bool = True,
                  swap_pages: int = 0, gpu_mem_utilization: float = 0.9, max_kv_tokens_per_request: int = 0,
-                 memory_profile: str = "", kv_dtype: str = "auto", rs_slots: int = 0, vision=None):
+                 memory_profile: str = "", kv_dtype: str = "auto", rs_slots: int = 0, vision=None, audio=None):
         self.cfg = cfg
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
@@ -182,10 +182,11 @@ class TorchDriver:
             self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
             use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet
         # media: a vision encoder (models.vision.VisionEncoder) and the clips it has encoded, by the runtime's slot
-        self.vision = vision
+        self.vision, self.audio = vision, audio
         self.media: Dict[int, torch.Tensor] = {}
-        if vision is not None and vision.cfg.hidden_size != cfg.hidden_size:
-            raise ValueError(f"vision encoder output width {vision.cfg.hidden_size} != model width {cfg.hidden_size}")
+        for enc in (vision, audio):
+            if enc is not None and enc.cfg.hidden_size != cfg.hidden_size:
+                raise ValueError(f"media encoder output width {enc.cfg.hidden_size} != model width {cfg.hidden_size}")
         # soft-capped attention scores (Gemma-2): bf16 pages, the 64-row prefill kernel, no shared-prefix decode plans
         self.softcap = bool(cfg.attn_softcap)
         if self.softcap and kv_dtype == "fp8_e4m3":
@@ -322,7 +323,7 @@ class TorchDriver:
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
             tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0,
-            cohort_decode=self.rs is None, media=("image", "video") if self.vision is not None else ())
+            cohort_decode=self.rs is None, media=(("image", "video") if self.vision is not None else ()) + (("audio",) if self.audio is not None else ()))
 
     # ------------------------------------------------------------------ request -> slab
     def _derive(self, req: ForwardRequest):
@@ -608,15 +609,17 @@ class TorchDriver:
         return self.model.logits(hidden, fi)
 
     def put_media(self, slot: int, kind: str, patches, grids) -> int:
-        """Encode an image / video (patch rows + their (t, h, w) grids, see `runtime.multimodal.patchify`) and keep
-        the encoder's output on the device under `slot`; forward requests then name it in their media spans.
-        Returns the number of rows (placeholder tokens). Counterpart of the image side channel of the
-        reference's forward request (driver/bridge/src/schema.rs, driver/cuda/src/model/qwen3_vl_vision.cpp)."""
-        if self.vision is None or kind not in ("image", "video"):
+        """Encode a clip and keep the encoder's output on the device under `slot`; forward requests then name it in
+        their media spans. Images and video: patch rows + their (t, h, w) grids (`runtime.multimodal.patchify`);
+        audio: the log-mel spectrogram [n_mels, frames] (`grids` unused). Returns the number of rows (placeholder
+        tokens). Counterpart of the image / audio side channels of the reference's forward request
+        (driver/bridge/src/schema.rs, driver/cuda/src/model/qwen3_vl_vision.cpp)."""
+        enc = self.audio if kind == "audio" else self.vision if kind in ("image", "video") else None
+        if enc is None:
             raise ValueError(f"this driver has no encoder for {kind}")
         with self._order:
             self._bind_thread()
-            feats = self.vision(np.asarray(patches, dtype=np.float32), [tuple(int(x) for x in g) for g in grids])
+            feats = enc(np.asarray(patches, dtype=np.float32), [tuple(int(x) for x in g) for g in grids])
             self.media[int(slot)] = feats.to(self.dtype).contiguous()
             return int(feats.shape[0])
 

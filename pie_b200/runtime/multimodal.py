@@ -8,8 +8,8 @@ vision / audio encoder consumes:
   audio   WAV decode -> mono -> resample to 16 kHz -> log-mel spectrogram (Whisper-style)
 
 Counterpart of runtime/src/multimodal.rs:1-24 (overview), :239 (smart resize), :369 (M-RoPE
-positions), :670+ (audio front end). The encoders that consume these tensors are not part of
-this build; the media API hands the features to drivers that declare an encoder.
+positions), :670+ (audio front end). The encoders that consume these tensors are `models.vision` and
+`models.audio`; the media API hands the features to drivers that declare one.
 """
 from __future__ import annotations
 

@@ -384,9 +384,8 @@ class Context:
         return self._append_clip("image", image.features)
 
     def append_audio(self, audio) -> "Context":
-        from . import media
-        media.require(self._model, "audio")
-        raise media.MediaUnsupported("audio tokens are produced by the driver's encoder")
+        """Splice an audio clip into the context: one placeholder token per 40 ms (needs a driver with an audio encoder)."""
+        return self._append_clip("audio", audio)
 
     def append_video(self, video) -> "Context":
         return self._append_clip("video", video.features)

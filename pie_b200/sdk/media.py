@@ -2,10 +2,10 @@
 
 Preprocessing runs on the host (`pie_b200.runtime.multimodal`); whether a model can consume the
 result depends on its driver declaring an encoder (`Capabilities.media`). A driver built with a vision
-encoder (`models.vision`) declares "image" and "video": `Context.append_image` / `append_video` then hand
-the patch rows to the driver and splice one placeholder token per encoder row into the context. Text-only
-models declare nothing and those calls raise `MediaUnsupported`; there is no audio encoder, so
-`append_audio` always does. The preprocessing itself is usable on its own.
+encoder (`models.vision`) declares "image" and "video", one with an audio encoder (`models.audio`) "audio":
+`Context.append_image` / `append_video` / `append_audio` then hand the patch rows or the spectrogram to the
+driver and splice one placeholder token per encoder row into the context. Text-only models declare nothing
+and those calls raise `MediaUnsupported`. The preprocessing itself is usable on its own.
 Counterpart of sdk/python/src/inferlet/media.py and audio.py.
 """
 from __future__ import annotations
@@ -50,11 +50,26 @@ class Video:
 
 @dataclass
 class Audio:
-    mel: np.ndarray       # [n_mels, frames]
+    mel: np.ndarray       # [n_mels, frames], 10 ms per frame
 
     @classmethod
     def from_wav(cls, data: bytes, n_mels: int = 80) -> "Audio":
         return cls(mm.audio_features(data, n_mels=n_mels))
+
+    @property
+    def num_tokens(self) -> int:
+        """Rows of the audio encoder's output (one per 40 ms: a stride-2 convolution, then a stride-2 pool)."""
+        f = self.mel.shape[1]
+        return ((f - 1) // 2 + 1) // 2 if f > 0 else 0
+
+    # the shape `Context._append_clip` takes: the array that goes to the encoder and its grid
+    @property
+    def patches(self) -> np.ndarray:
+        return self.mel
+
+    @property
+    def grid(self):
+        return (int(self.mel.shape[1]),)
 
 
 def supported(model) -> List[str]:

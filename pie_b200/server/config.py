@@ -79,6 +79,7 @@ class DriverConfig:
     memory_profile: str = ""              # "" = built-in limits; auto | latency | balanced | throughput | capacity
     vision: str = ""                      # "" = text only | "checkpoint" (the `visual.*` tower of [model] path) |
                                           # a preset of models.vision with random weights (e.g. "tiny-vit")
+    audio: str = ""                       # the same for the audio encoder (`audio_tower.*`; preset e.g. "tiny-audio")
     ipc: str = "direct"                   # runtime -> driver: direct call | inproc (queue + service thread) |
                                           # latency (polled ring) | shmem (driver in a process of its own)
 

@@ -86,6 +86,22 @@ def _vision_encoder(m: ModelSection, cfg, device, dtype):
     return V.VisionEncoder(vcfg, V.random_vision_weights(vcfg, device, dtype))
 
 
+def _audio_encoder(m: ModelSection, cfg, device, dtype):
+    """The model's audio encoder per `[model.driver] audio`, or None."""
+    kind = m.driver.audio
+    if not kind:
+        return None
+    import json as _json
+    from ..models import audio as A
+    if kind == "checkpoint":
+        from ..models.loader import SafetensorsReader
+        hf = _json.loads((Path(m.path) / "config.json").read_text())
+        acfg = A.AudioConfig.from_hf(hf.get("audio_config") or {}, llm_hidden=cfg.hidden_size)
+        return A.AudioEncoder(acfg, A.load_audio_weights(SafetensorsReader(m.path), device, dtype))
+    acfg = A.audio_preset(kind, hidden_size=cfg.hidden_size)
+    return A.AudioEncoder(acfg, A.random_audio_weights(acfg, device, dtype))
+
+
 def _build_drivers_direct(m: ModelSection):
     """Drivers of one model: one per data-parallel group. Returns (drivers, cfg, tokenizer, comm)."""
     d = m.driver
@@ -124,7 +140,8 @@ def _build_drivers_direct(m: ModelSection):
             _, w = loader.load_checkpoint(m.path, "cpu", dtype="float32")
             cfg.dtype = "float32"
         return [TorchDriver(cfg, "cpu", weights=w, num_pages=4096, page_size=d.kv_page_size,
-                            vision=_vision_encoder(m, cfg, "cpu", torch.float32))], cfg, tok, comm
+                            vision=_vision_encoder(m, cfg, "cpu", torch.float32),
+                            audio=_audio_encoder(m, cfg, "cpu", torch.float32))], cfg, tok, comm
     groups = calculate_topology(d.device, d.tensor_parallel_size)
     drivers = []
     if d.tensor_parallel_size > 1:
@@ -162,7 +179,8 @@ def _build_drivers_direct(m: ModelSection):
         drivers.append(TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, gemm_backend=d.gemm,
                                    use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
                                    swap_pages=swap, memory_profile=d.memory_profile,
-                                   vision=_vision_encoder(m, cfg, dev, torch.bfloat16)))
+                                   vision=_vision_encoder(m, cfg, dev, torch.bfloat16),
+                                   audio=_audio_encoder(m, cfg, dev, torch.bfloat16)))
         if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
             n = drivers[-1].precapture_graphs()
             log.info("model %s on %s: %d decode graphs captured ahead of time", m.name, dev, n)

@@ -245,3 +245,65 @@ def test_registry_encodes_off_thread_shares_by_content_and_reports_errors():
     reg.drain()
     assert reg.stats()["resident"] == 0
     reg.close()
+
+
+def wav_bytes_of(seconds: float, freq: float, sr: int = 8000) -> bytes:
+    t = np.arange(int(seconds * sr)) / sr
+    return mm.encode_wav((0.5 * np.sin(2 * np.pi * freq * t)).astype(np.float32), sr)
+
+
+def test_audio_tower_equals_transformers_qwen2_audio():
+    from transformers.models.qwen2_audio import modeling_qwen2_audio as m
+    from transformers.models.qwen2_audio.configuration_qwen2_audio import Qwen2AudioEncoderConfig
+    from pie_b200.models.audio import AudioEncoder, audio_preset, audio_rows, random_audio_weights
+    cfg = audio_preset("tiny-audio", num_mel_bins=16, max_source_positions=50, hidden_size=96)
+    w = random_audio_weights(cfg, seed=2)
+    c = Qwen2AudioEncoderConfig(num_mel_bins=16, encoder_layers=cfg.layers, encoder_attention_heads=cfg.heads,
+                                encoder_ffn_dim=cfg.ffn_dim, d_model=cfg.d_model, max_source_positions=50)
+    c._attn_implementation = "eager"
+    tower = m.Qwen2AudioEncoder(c).float().eval()
+    tower.load_state_dict({k: v for k, v in w.items() if not k.startswith("projector.")}, strict=True)
+    mel = torch.randn(16, 100)                       # the full window of this tower: 2 * max_source_positions frames
+    with torch.no_grad():
+        want = tower(mel[None]).last_hidden_state[0] @ w["projector.linear.weight"].t() + w["projector.linear.bias"]
+    got = AudioEncoder(cfg, w)(mel)
+    assert got.shape == (audio_rows(100), 96) and (got - want).abs().max() < 1e-5
+    assert AudioEncoder(cfg, w)(torch.randn(16, 37)).shape[0] == audio_rows(37) == 9       # shorter clips are not padded
+    with pytest.raises(ValueError, match="longer than"):
+        AudioEncoder(cfg, w)(torch.randn(16, 203))
+
+
+def test_audio_clips_through_the_engine():
+    from pie_b200.models.audio import AudioEncoder, audio_preset, random_audio_weights
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=3)
+    acfg = audio_preset("tiny-audio", hidden_size=cfg.hidden_size)
+    enc = AudioEncoder(acfg, random_audio_weights(acfg, seed=6))
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=48, audio=enc)
+    assert drv.capabilities().media == ("audio",)
+    e = Engine(EngineConfig())
+    try:
+        e.add_model("alm", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
+        install_all(e)
+        wav = wav_bytes_of(2.5, 440.0)
+        q = "What do you hear?"
+        out = json.loads(e.run("audio-qa", {"audio_b64": base64.b64encode(wav).decode(), "question": q, "max_tokens": 4,
+                                            "temperature": 0.0}, 300))
+        mel = mm.audio_features(wav)
+        rows = enc(mel)
+        assert out["ok"] and out["audio_tokens"] == rows.shape[0] > 48 and out["frames"] == mel.shape[1]
+        toks = [0] * rows.shape[0] + ByteTokenizer(cfg.vocab_size).encode(q)
+        emb = {i: rows[i] for i in range(rows.shape[0])}
+        want = []
+        for _ in range(4):
+            want.append(int(dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].argmax()))
+            toks.append(want[-1])
+        assert out["tokens"] == want
+        two = json.loads(e.run("multi-audio-test", {"audios_b64": [base64.b64encode(wav).decode(), base64.b64encode(wav_bytes_of(1.0, 880.0)).decode(),
+                                                                   base64.b64encode(wav).decode()], "max_tokens": 2}, 300))
+        assert two["ok"] and two["audio_tokens"][0] == two["audio_tokens"][2] and two["media"]["resident"] == 2
+        # an image on this model is refused by the SDK: the driver declares audio only
+        out = json.loads(e.run("image-qa", {"image_b64": base64.b64encode(png_bytes(1)).decode()}, 60))
+        assert not out["ok"] and "no image encoder" in out["error"]
+    finally:
+        e.shutdown()
