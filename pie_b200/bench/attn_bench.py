@@ -3,7 +3,7 @@ mma.sync kernel on causal prompts over a paged KV cache. CUDA events, warm-up, L
 timed launches; FLOPs counted for the causal half only.
 
     python -m pie_b200.bench.attn_bench [--reqs 16 --len 2048] [--rows 64,128,256] [--iters 5]
-    python -m pie_b200.bench.attn_bench --decode [--reqs 512 --len 1200] [--heads 32,8]
+    python -m pie_b200.bench.attn_bench --decode [--reqs 512 --len 1200] [--heads 32,8] [--head-dim 256] [--softcap 50]
 
 `--decode`: split-KV decode attention over bf16 pages and over fp8 pages (bytes of KV actually streamed
 per launch over the CUDA-event time, against the measured copy bandwidth), and with `--fork B` over
@@ -21,7 +21,7 @@ from .. import ops
 
 
 def run(reqs: int, plen: int, rows_list, iters: int, hq: int = 32, hkv: int = 8, d: int = 128, page: int = 16,
-        warmup: int = 2):
+        warmup: int = 2, softcap: float = 0.0):
     dev = "cuda:0"
     npg = plen // page
     g = torch.Generator(device=dev).manual_seed(1)
@@ -35,16 +35,20 @@ def run(reqs: int, plen: int, rows_list, iters: int, hq: int = 32, hkv: int = 8,
     flops = 4.0 * plen * plen / 2 * hq * d * reqs
     out = torch.empty_like(q)
     res = {}
+    if d == 256:                        # only the 64-row kernel covers it
+        rows_list = [64]
+    elif softcap:                       # the tcgen05 kernel takes a soft cap in its two-tile form
+        rows_list = [r for r in rows_list if r in (64, 256)]
     for rows in rows_list:
         plan = ops.build_prefill_plan(batch, hq // hkv, page, dev, tile_rows=rows)
         for _ in range(warmup):
-            ops.paged_prefill_attention(q, kv, plan, 1 / math.sqrt(d), out=out)
+            ops.paged_prefill_attention(q, kv, plan, 1 / math.sqrt(d), out=out, softcap=softcap)
         ts = []
         for _ in range(iters):
             flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            ops.paged_prefill_attention(q, kv, plan, 1 / math.sqrt(d), out=out)
+            ops.paged_prefill_attention(q, kv, plan, 1 / math.sqrt(d), out=out, softcap=softcap)
             e1.record()
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
@@ -52,12 +56,13 @@ def run(reqs: int, plen: int, rows_list, iters: int, hq: int = 32, hkv: int = 8,
         ms = sorted(ts)[len(ts) // 2]
         res[rows] = ms
         kind = "mma.sync" if rows == 64 else f"tcgen05 x{rows // 128}"
-        print(f"{reqs} x {plen} ({kind:10s}): {ms:7.3f} ms  {flops / ms / 1e9:6.0f} TFLOP/s", flush=True)
+        print(f"{reqs} x {plen} hq {hq} hkv {hkv} d {d}{' softcap' if softcap else ''} ({kind:10s}): {ms:7.3f} ms  "
+              f"{flops / ms / 1e9:6.0f} TFLOP/s", flush=True)
     return res
 
 
 def run_decode(reqs: int, kv_len: int, iters: int, hq: int, hkv: int, d: int, fork: int = 0, page: int = 16,
-               warmup: int = 3):
+               warmup: int = 3, softcap: float = 0.0):
     dev = "cuda:0"
     npg = -(-kv_len // page)
     rng = np.random.default_rng(0)
@@ -89,7 +94,9 @@ def run_decode(reqs: int, kv_len: int, iters: int, hq: int, hkv: int, d: int, fo
     plain = ops.DecodePlan(t(pages), t(indptr), t(item_req), t(st), t(en), t(iptr),
                            torch.tensor([len(item_req)], dtype=torch.int32, device=dev), scratch, max_items, reqs, ctas, page)
     variants = [("bf16 pages", plain, kv, None, 2.0), ("fp8 pages", plain, kv8, sc, 1.0 + 4.0 / d)]
-    if fork > 1:
+    if softcap or d == 256:             # the fp8-page kernel covers neither
+        variants = [("bf16 pages" + (f", softcap {softcap:g}" if softcap else ""), plain, kv, None, 2.0)]
+    if fork > 1 and not softcap:
         grp = ops.find_shared_prefixes(kv_lens, indptr, pages, page)
         cp = ops.plan_decode_cascade(kv_lens, grp, hkv, hq // hkv, ctas, max_items)
         if cp is not None:
@@ -103,13 +110,13 @@ def run_decode(reqs: int, kv_len: int, iters: int, hq: int, hkv: int, d: int, fo
     ref_out = None
     for name, plan, cache, scale, bytes_per_elem in variants:
         for _ in range(warmup):
-            ops.paged_decode_attention(q, cache, plan, 1 / math.sqrt(d), out=out, kv_scale=scale)
+            ops.paged_decode_attention(q, cache, plan, 1 / math.sqrt(d), out=out, kv_scale=scale, softcap=softcap)
         ts = []
         for _ in range(iters):
             flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            ops.paged_decode_attention(q, cache, plan, 1 / math.sqrt(d), out=out, kv_scale=scale)
+            ops.paged_decode_attention(q, cache, plan, 1 / math.sqrt(d), out=out, kv_scale=scale, softcap=softcap)
             e1.record()
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
@@ -119,7 +126,7 @@ def run_decode(reqs: int, kv_len: int, iters: int, hq: int, hkv: int, d: int, fo
             ref_out = out.float().clone()
         err = float((out.float() - ref_out).abs().max())
         logical = 2.0 * reqs * kv_len * hkv * d * bytes_per_elem          # K and V of every request, as a plain plan reads them
-        print(f"decode {reqs} x {kv_len} hq {hq} hkv {hkv} ({name}): {ms * 1e3:8.1f} us  {logical / ms / 1e6:7.0f} GB/s of "
+        print(f"decode {reqs} x {kv_len} hq {hq} hkv {hkv} d {d} ({name}): {ms * 1e3:8.1f} us  {logical / ms / 1e6:7.0f} GB/s of "
               f"per-request KV  (max |diff| vs bf16 plain {err:.3f})", flush=True)
 
 
@@ -132,17 +139,18 @@ def main():
     ap.add_argument("--rows", default="64,128,256")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
-    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128, 256])
+    ap.add_argument("--softcap", type=float, default=0.0, help="soft cap on the scores (Gemma-2: 50)")
     ap.add_argument("--heads", default="32,8", help="query heads, KV heads")
     a = ap.parse_args()
     hq, hkv = (int(v) for v in a.heads.split(","))
     if a.decode:
-        run_decode(a.reqs or 512, a.len or 1200, a.iters, hq, hkv, a.head_dim, fork=a.fork)
+        run_decode(a.reqs or 512, a.len or 1200, a.iters, hq, hkv, a.head_dim, fork=a.fork, softcap=a.softcap)
         return
     rows = [int(r) for r in a.rows.split(",")]
     shapes = [(a.reqs, a.len)] if a.reqs and a.len else [(64, 512), (16, 2048), (8, 4096), (2, 16384)]
     for reqs, plen in shapes:
-        run(reqs, plen, rows, a.iters, hq=hq, hkv=hkv, d=a.head_dim, warmup=a.warmup)
+        run(reqs, plen, rows, a.iters, hq=hq, hkv=hkv, d=a.head_dim, warmup=a.warmup, softcap=a.softcap)
 
 
 if __name__ == "__main__":

@@ -79,9 +79,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float fast_tanh(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// CAP: soft-capped scores (Gemma-2). A raw score s becomes cap_post * tanh(s * cap_pre) with cap_pre = sm_scale / cap
+// and cap_post = cap / sm_scale, so that the unchanged scale by sm_scale * log2(e) gives cap * tanh(s * sm_scale / cap).
 // G = query heads per KV head; NT = MMA tiles of 128 rows per CTA (they share the K/V stages);
 // D = head dimension (64 or 128).
-template <int G, int NT, int D>
+template <int G, int NT, int D, bool CAP = false>
 __global__ void __launch_bounds__(AtCfg<NT, D>::THREADS, 1)
 paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_kv,
                              const int* __restrict__ page_indices, const int* __restrict__ kv_page_indptr,
@@ -89,7 +97,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                              const int* __restrict__ tile_req, const int* __restrict__ tile_qstart,
                              const uint32_t* __restrict__ mask_bits, const long* __restrict__ mask_word_indptr,
                              bf16* __restrict__ out, float* __restrict__ lse_out, const float* __restrict__ sinks_log2,
-                             int hq, int hkv, int pad_page, float scale_log2, int window_left, int* status) {
+                             int hq, int hkv, int pad_page, float scale_log2, int window_left, int* status,
+                             float cap_pre, float cap_post) {
     constexpr int TQ = AT_ROWS / G;          // query tokens per MMA tile
     constexpr int HALVES = D / 64;
     constexpr uint32_t AT_Q_BYTES = AtCfg<NT, D>::Q_BYTES, AT_KV_TILE = AtCfg<NT, D>::KV_TILE;
@@ -299,7 +308,8 @@ paged_prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __
                 tmem_ld_32x32(tm_t + b * AT_BK + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(v[i]);
+                for (int i = 0; i < 32; ++i)
+                    sv[c * 32 + i] = CAP ? cap_post * fast_tanh(__uint_as_float(v[i]) * cap_pre) : __uint_as_float(v[i]);
             }
             const int kb0 = j * AT_BK;
             const bool inner = !custom && kb0 + AT_BK <= lim && kb0 >= lo;
@@ -446,18 +456,19 @@ PIE_API int pie_prefill_attn_tc_supported(int hq, int hkv, int head_dim, int pag
 
 // Same contract as pie_paged_prefill_attn, with tiles of tile_rows / group query tokens (tile_rows = 128 or
 // 256: one or two MMA tiles per CTA) and `total_pages` = pages of kv_layer including the pad page (last).
-PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const int* page_indices,
-                                      const int* kv_page_indptr, const int* qo_indptr, const int* kv_lens,
-                                      const int* tile_req, const int* tile_qstart, int num_tiles,
-                                      const uint32_t* mask_bits, const long* mask_word_indptr, void* out,
-                                      float* lse_out, int n_tokens, int hq, int hkv, int head_dim, int total_pages,
-                                      float sm_scale,
-                                      int window_left, int tile_rows, const float* sinks_log2, int* status,
-                                      cudaStream_t st) {
+// softcap > 0 (tile_rows 256 only): softmax over softcap * tanh(q.k * sm_scale / softcap).
+PIE_API int pie_paged_prefill_attn_tc_softcap(const void* q, const void* kv_layer, const int* page_indices,
+                                              const int* kv_page_indptr, const int* qo_indptr, const int* kv_lens,
+                                              const int* tile_req, const int* tile_qstart, int num_tiles,
+                                              const uint32_t* mask_bits, const long* mask_word_indptr, void* out,
+                                              float* lse_out, int n_tokens, int hq, int hkv, int head_dim, int total_pages,
+                                              float sm_scale, int window_left, int tile_rows, const float* sinks_log2,
+                                              int* status, float softcap, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
     const int D_ = head_dim;
     if (!pie_prefill_attn_tc_supported(hq, hkv, head_dim, 16) || (tile_rows != 128 && tile_rows != 256) || !status)
         return (int)cudaErrorInvalidValue;
+    if (softcap > 0.f && tile_rows != 256) return (int)cudaErrorInvalidValue;
     EncodeTiledFnA enc = at_encoder();
     if (!enc) return (int)cudaErrorNotSupported;
     const int G = hq / hkv;
@@ -484,22 +495,24 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
     }
     const float scale_log2 = sm_scale * 1.4426950408889634f;
     dim3 grid(num_tiles, hkv);
-#define GO3(G_, NT_, D__)                                                                                             \
+    const float cap_pre = softcap > 0.f ? sm_scale / softcap : 0.f, cap_post = softcap > 0.f ? softcap / sm_scale : 0.f;
+#define GO4(G_, NT_, D__, CAP_)                                                                                       \
     {                                                                                                                 \
-        auto kern = paged_prefill_attn_tc_kernel<G_, NT_, D__>;                                                       \
+        auto kern = paged_prefill_attn_tc_kernel<G_, NT_, D__, CAP_>;                                                 \
         using Cfg = AtCfg<NT_, D__>;                                                                                  \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);      \
         if (e != cudaSuccess) return (int)e;                                                                          \
         kern<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(                                                                  \
             tq, tkv, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req, tile_qstart, mask_bits,              \
             mask_word_indptr, (bf16*)out, lse_out, sinks_log2, hq, hkv, total_pages - 1, scale_log2, window_left,     \
-            status);                                                                                                  \
+            status, cap_pre, cap_post);                                                                               \
         return (int)cudaGetLastError();                                                                               \
     }
 #define GO2(G_, NT_)           \
-    if (D_ == 128) GO3(G_, NT_, 128) else GO3(G_, NT_, 64)
+    if (D_ == 128) GO4(G_, NT_, 128, false) else GO4(G_, NT_, 64, false)
 #define GO(G_)                 \
-    if (tile_rows == 128) GO2(G_, 1) else GO2(G_, 2)
+    if (softcap > 0.f) { if (D_ == 128) GO4(G_, 2, 128, true) else GO4(G_, 2, 64, true) } \
+    else if (tile_rows == 128) GO2(G_, 1) else GO2(G_, 2)
     switch (G) {
         case 1: GO(1)
         case 2: GO(2)
@@ -509,7 +522,21 @@ PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const
     }
 #undef GO
 #undef GO2
-#undef GO3
+#undef GO4
     return (int)cudaErrorInvalidValue;
+}
+
+PIE_API int pie_paged_prefill_attn_tc(const void* q, const void* kv_layer, const int* page_indices,
+                                      const int* kv_page_indptr, const int* qo_indptr, const int* kv_lens,
+                                      const int* tile_req, const int* tile_qstart, int num_tiles,
+                                      const uint32_t* mask_bits, const long* mask_word_indptr, void* out,
+                                      float* lse_out, int n_tokens, int hq, int hkv, int head_dim, int total_pages,
+                                      float sm_scale,
+                                      int window_left, int tile_rows, const float* sinks_log2, int* status,
+                                      cudaStream_t st) {
+    return pie_paged_prefill_attn_tc_softcap(q, kv_layer, page_indices, kv_page_indptr, qo_indptr, kv_lens, tile_req,
+                                             tile_qstart, num_tiles, mask_bits, mask_word_indptr, out, lse_out, n_tokens,
+                                             hq, hkv, head_dim, total_pages, sm_scale, window_left, tile_rows, sinks_log2,
+                                             status, 0.f, st);
 }
 

@@ -701,11 +701,11 @@ def plan_decode_cascade(kv_lens: np.ndarray, groups, hkv: int, group_size: int, 
 def prefill_tile_rows(hq: int, hkv: int, head_dim: int, page_size: int, softcap: bool = False) -> int:
     """Packed (token, head) rows per prefill tile: 256 (two MMA tiles per CTA; ``PIE_PREFILL_TC=128``
     for one) where the tcgen05 kernel covers the shape (head_dim 64 or 128, 16-token pages, group size
-    dividing 128, no soft cap on the scores), else - or with ``PIE_PREFILL_TC=0`` - the 64 rows of the mma.sync kernel."""
+    dividing 128), else - or with ``PIE_PREFILL_TC=0`` - the 64 rows of the mma.sync kernel."""
     want = os.environ.get("PIE_PREFILL_TC", "256")
-    if want == "0" or softcap or not fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size):
+    if want == "0" or not fn("pie_prefill_attn_tc_supported")(hq, hkv, head_dim, page_size):
         return 64
-    return 128 if want == "128" else 256
+    return 128 if want == "128" and not softcap else 256          # a soft cap is built for the two-tile variant only
 
 
 def plan_prefill_tiles(qo_indptr: np.ndarray, group: int, rows: int = 64, kv_lens=None):
@@ -834,9 +834,17 @@ def paged_prefill_attention(q, kv_layer, plan: PrefillPlan, sm_scale: float, out
     wl = plan.window_left if window_left is None else window_left
     n, hq, d = q.shape
     hkv = kv_layer.shape[2]
+    if softcap and plan.tile_rows > 64:
+        if plan.tile_rows != 256:
+            raise ValueError("soft-capped scores on the tcgen05 kernel need 256-row tiles: plan with prefill_tile_rows(..., softcap=True)")
+        check(fn("pie_paged_prefill_attn_tc_softcap")(
+            ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
+            ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,
+            ptr(plan.mask_bits), ptr(plan.mask_word_indptr), ptr(out), ptr(lse_out), n, hq, hkv, d,
+            kv_layer.shape[0], sm_scale, wl, plan.tile_rows, ptr(sinks_log2), ptr(kernel_status(q.device)),
+            float(softcap), stream_ptr()), "paged_prefill_attn_tc_softcap")
+        return out
     if softcap:
-        if plan.tile_rows != 64:
-            raise ValueError("soft-capped scores run on the 64-row prefill kernel: plan with prefill_tile_rows(..., softcap=True)")
         check(fn("pie_paged_prefill_attn_softcap")(
             ptr(q), ptr(kv_layer), ptr(plan.page_indices), ptr(plan.kv_page_indptr), ptr(plan.qo_indptr),
             ptr(plan.kv_lens), ptr(plan.tile_req), ptr(plan.tile_qstart), plan.num_tiles,

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "pie_prefill_tile_tokens": [i32],
     "pie_prefill_attn_tc_supported": [i32, i32, i32, i32],
     "pie_paged_prefill_attn_tc": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, i32, p, p, p],
+    "pie_paged_prefill_attn_tc_softcap": [p, p, p, p, p, p, p, p, i32, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, i32, p, p, f32, p],
     "pie_sample": [p, i64, i32, i32, p, p, p, p, p, p, p, i32, p, p],
     "pie_tp_sample_max_grid": [i32],
     "pie_tp_sample": [p, p, i64, i32, p, p, p, p, p, p, p, i32, p, i32, p],

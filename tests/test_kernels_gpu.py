@@ -163,12 +163,15 @@ def test_paged_decode_attention_head_dim_256_and_softcap(d, hq, hkv, softcap, wi
         assert (plain.float() - want.float()).abs().max() > 0.05
 
 
-@pytest.mark.parametrize("d,hq,hkv,softcap", [(256, 8, 4, 0.0), (256, 4, 4, 0.0), (256, 8, 1, 1.5), (128, 32, 8, 1.5), (64, 4, 2, 2.0)])
+@pytest.mark.parametrize("d,hq,hkv,softcap,rows", [(256, 8, 4, 0.0, 64), (256, 4, 4, 0.0, 64), (256, 8, 1, 1.5, 64), (128, 32, 8, 1.5, 64),
+                                                   (64, 4, 2, 2.0, 64), (128, 32, 8, 1.5, 256), (128, 32, 16, 2.0, 256), (128, 8, 1, 1.5, 256),
+                                                   (64, 16, 2, 2.0, 256)])
 @pytest.mark.parametrize("mode", ["causal", "custom", "window"])
-def test_paged_prefill_attention_head_dim_256_and_softcap(d, hq, hkv, softcap, mode):
-    """The 64-row kernel at head_dim 256 and with soft-capped scores (the tcgen05 kernel covers neither)."""
+def test_paged_prefill_attention_head_dim_256_and_softcap(d, hq, hkv, softcap, rows, mode):
+    """head_dim 256 on the 64-row kernel (the tcgen05 kernel stops at 128); soft-capped scores on both kernels (the
+    tcgen05 one in its two-tile form)."""
     page = 16
-    assert ops.prefill_tile_rows(hq, hkv, d, page, softcap=bool(softcap)) == (64 if softcap or d == 256 else 256)
+    assert ops.prefill_tile_rows(hq, hkv, d, page, softcap=bool(softcap)) == (64 if d == 256 else 256)
     qlens = np.array([1, 5, 64, 130, 17, 700], dtype=np.int32)
     prev = np.array([40, 0, 0, 200, 31, 333], dtype=np.int32)
     kv_lens = qlens + prev
@@ -187,10 +190,11 @@ def test_paged_prefill_attention_head_dim_256_and_softcap(d, hq, hkv, softcap, m
             masks.append(m if i != 2 else None)
     if mode == "window":
         window = 37
-    plan = ops.build_prefill_plan(ops.AttnBatch(qo, indptr, pages, kv_lens, masks, window), hq // hkv, page, DEV, tile_rows=64)
+    plan = ops.build_prefill_plan(ops.AttnBatch(qo, indptr, pages, kv_lens, masks, window), hq // hkv, page, DEV, tile_rows=rows)
     scale = 1 / math.sqrt(d)
     lse = torch.empty(int(qo[-1]), hq, device=DEV)
     out = ops.paged_prefill_attention(q, kv, plan, scale, lse_out=lse, softcap=softcap)
+    ops.check_kernel_status(DEV)
     tmasks = None if masks is None else [None if m is None else torch.from_numpy(m) for m in masks]
     want, want_lse = ref.paged_attention(q, kv, qo, indptr, torch.from_numpy(pages).to(DEV), kv_lens, scale,
                                          masks=tmasks, window_left=window, return_lse=True, softcap=softcap)
