@@ -24,7 +24,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="fused")
     ap.add_argument("--hidden", type=int, default=512)
-    ap.add_argument("--model", default="dense", choices=["dense", "dense-fp8", "moe", "moe-ep", "gpt-oss", "olmo2"],
+    ap.add_argument("--model", default="dense", choices=["dense", "dense-fp8", "moe", "moe-ep", "gpt-oss", "olmo2", "gemma3", "gemma2"],
                     help="moe: experts sharded on their intermediate dimension; moe-ep: whole experts per rank")
     a = ap.parse_args()
     import torch.distributed as dist
@@ -47,6 +47,12 @@ def main():
     elif a.model == "olmo2":
         cfg = preset("tiny-olmo2", hidden_size=a.hidden, intermediate_size=1536, num_attention_heads=8,
                      num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16")
+    elif a.model in ("gemma3", "gemma2"):
+        # sandwich norms, GeGLU, scaled embeddings, alternating local / global layers (gemma2: soft-capped scores and logits)
+        cfg = preset("tiny-" + a.model, hidden_size=a.hidden, intermediate_size=1536, num_attention_heads=8,
+                     num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16",
+                     sliding_window=24, layer_types=["sliding_attention", "full_attention", "sliding_attention"],
+                     embed_scale=float(a.hidden) ** 0.5, query_pre_attn_scalar=128.0)
     elif a.model == "gpt-oss":
         cfg = preset("tiny-gpt-oss", hidden_size=a.hidden, intermediate_size=256, moe_intermediate_size=256,
                      num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=4096, num_hidden_layers=2,
