@@ -263,7 +263,8 @@ def main():
         # itself cannot be built here and publishes no number for this configuration)
         "baseline": baseline,
         "config": {"model": cfg.name, "global_batch": n_req, "seq_len": f"prompts U[{args.prompt_min},{args.prompt_max}] + {args.out_tokens} out",
-                   "parallelism": (f"dp{world}" if dp else f"tp{world}"), "tp_backend": args.tp_backend if (world > 1 and not dp) else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
+                   "parallelism": (f"dp{world}" if dp else f"tp{world}"),
+                   "tp_backend": args.tp_backend if (world > 1 and not dp) else None, "kv_page_size": 16, "sampler": "temperature 1.0, top-p 0.9",
                    "gemm": args.gemm, "layers": cfg.num_hidden_layers, "kv_dtype": "bf16" if args.kv_dtype == "auto" else args.kv_dtype,
                    "l2": "working set per step (weights 16 GB + KV > 60 GB) exceeds the 126 MB L2; no flush needed",
                    "valid": not args.layers and args.kv_dtype == "auto"},

@@ -86,7 +86,8 @@ def main(argv=None):
         os._exit(0)
     parallelism = "tp1" if world == 1 else (f"ep{world} experts + tp{world} attention (fused)" if a.config == 4
                                              else f"tp{world} (fused)")
-    line = {"config": a.config, "model": cfg.name, "n_gpus": world, "parallelism": parallelism, "dtype": "bf16" if cfg.quantization is None else "fp8 weights, bf16 activations",
+    line = {"config": a.config, "model": cfg.name, "n_gpus": world, "parallelism": parallelism,
+            "dtype": "bf16" if cfg.quantization is None else "fp8 weights, bf16 activations",
             "data": "synthetic random-token prompts, random-init weights", "gemm": a.gemm,
             "valid": not a.layers and (n_req == spec["requests"] if a.config != 5 else a.agents == 64)}
     clk = harness.ClockSampler(local).start()

@@ -57,7 +57,8 @@ def main():
     import ctypes as C
     from ..ops import _lib
     thresholds = _lib.declare("pie_gemm_set_pair_thresholds", [C.c_double, C.c_double])
-    print(f"{'M':>6} {'N':>7} {'K':>6} | {'cuBLAS us':>10} {'TF':>6} | {'default us':>9} {'TF':>6} | {'1-CTA us':>9} {'TF':>6} | {'pairs us':>9} {'TF':>6} | max err")
+    print(f"{'M':>6} {'N':>7} {'K':>6} | {'cuBLAS us':>10} {'TF':>6} | {'default us':>9} {'TF':>6} | {'1-CTA us':>9} {'TF':>6} | "
+          f"{'pairs us':>9} {'TF':>6} | max err")
     for m, n, k in shapes:
         x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
         w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)

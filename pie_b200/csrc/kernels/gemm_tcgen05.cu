@@ -157,8 +157,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         const uint32_t tx = ((sk.dbg & 2) ? 0u : Cfg::A_BYTES) + ((sk.dbg & 4) ? 0u : (uint32_t)bn * (GEMM_KSTEP * 2));
                         mbar_arrive_expect_tx(full_bar(s), tx);
                         for (int u = 0; u < Cfg::KSUB; ++u) {
-                            if (!(sk.dbg & 4)) tma_load_2d(a_dst + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, b_row);
-                            if (!(sk.dbg & 2)) tma_load_2d(a_dst + u * Cfg::A_SUB, &tma_a, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, m_blk * GEMM_BM);
+                            if (!(sk.dbg & 4))
+                                tma_load_2d(a_dst + Cfg::A_BYTES + u * Cfg::B_SUB, &tma_b, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, b_row);
+                            if (!(sk.dbg & 2))
+                                tma_load_2d(a_dst + u * Cfg::A_SUB, &tma_a, full_bar(s), kb * GEMM_KSTEP + u * GEMM_BK, m_blk * GEMM_BM);
                         }
                         continue;
                     }

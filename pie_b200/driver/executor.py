@@ -323,7 +323,8 @@ class TorchDriver:
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
             tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0,
-            cohort_decode=self.rs is None, media=(("image", "video") if self.vision is not None else ()) + (("audio",) if self.audio is not None else ()))
+            cohort_decode=self.rs is None,
+            media=(("image", "video") if self.vision is not None else ()) + (("audio",) if self.audio is not None else ()))
 
     # ------------------------------------------------------------------ request -> slab
     def _derive(self, req: ForwardRequest):

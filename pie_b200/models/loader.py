@@ -715,7 +715,8 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
     if cfg.model_type == "phi3":
         hf.update(pad_token_id=0, bos_token_id=1, eos_token_id=2)
     if cfg.sandwich_norm:
-        hf.update(layer_types=cfg.layer_types, sliding_window=cfg.sliding_window, query_pre_attn_scalar=int(cfg.query_pre_attn_scalar or cfg.head_dim),
+        hf.update(layer_types=cfg.layer_types, sliding_window=cfg.sliding_window,
+                  query_pre_attn_scalar=int(cfg.query_pre_attn_scalar or cfg.head_dim),
                   hidden_activation="gelu_pytorch_tanh", attn_logit_softcapping=cfg.attn_softcap or None,
                   final_logit_softcapping=cfg.final_softcap or None, rope_scaling=cfg.rope_scaling)
         if cfg.rope_local_theta:

@@ -31,7 +31,8 @@ def small_cfg(family="llama"):
                   **extra)
 
 
-@pytest.mark.parametrize("backend,family", [("tcgen05", "llama"), ("cublas", "llama"), ("tcgen05", "olmo2"), ("tcgen05", "window"), ("tcgen05", "gpt_oss")])
+@pytest.mark.parametrize("backend,family", [("tcgen05", "llama"), ("cublas", "llama"), ("tcgen05", "olmo2"), ("tcgen05", "window"),
+                                            ("tcgen05", "gpt_oss")])
 def test_prefill_and_decode_logits_match_oracle(backend, family):
     cfg = small_cfg(family)
     w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)

@@ -299,8 +299,8 @@ def test_audio_clips_through_the_engine():
             want.append(int(dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].argmax()))
             toks.append(want[-1])
         assert out["tokens"] == want
-        two = json.loads(e.run("multi-audio-test", {"audios_b64": [base64.b64encode(wav).decode(), base64.b64encode(wav_bytes_of(1.0, 880.0)).decode(),
-                                                                   base64.b64encode(wav).decode()], "max_tokens": 2}, 300))
+        b64 = lambda x: base64.b64encode(x).decode()
+        two = json.loads(e.run("multi-audio-test", {"audios_b64": [b64(wav), b64(wav_bytes_of(1.0, 880.0)), b64(wav)], "max_tokens": 2}, 300))
         assert two["ok"] and two["audio_tokens"][0] == two["audio_tokens"][2] and two["media"]["resident"] == 2
         # an image on this model is refused by the SDK: the driver declares audio only
         out = json.loads(e.run("image-qa", {"image_b64": base64.b64encode(png_bytes(1)).decode()}, 60))

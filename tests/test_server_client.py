@@ -184,7 +184,8 @@ def test_cli_smoke_run_and_monitor(capsys):
 def test_embedded_server_and_client_cli(tmp_path, capsys):
     from pie_b200.client import cli as client_cli
     from pie_b200.server.embed import Server
-    toml = (f'[server]\nallow_program_upload = true\n[runtime]\nprogram_dir = "{tmp_path}/programs"\n[telemetry]\nenabled = true\n[auth]\nenabled = false\n'
+    toml = (f'[server]\nallow_program_upload = true\n[runtime]\nprogram_dir = "{tmp_path}/programs"\n'
+            f'[telemetry]\nenabled = true\n[auth]\nenabled = false\n'
             '[[model]]\nname = "dummy"\npreset = "tiny-llama"\n[model.driver]\ntype = "dummy"\n')
     with Server.from_text(toml) as srv:
         uri = srv.uri
