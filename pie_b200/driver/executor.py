@@ -323,7 +323,7 @@ class TorchDriver:
             max_sampler_rows=self.max_rows, arch_name=self.cfg.model_type, vocab_size=self.cfg.vocab_size,
             max_model_len=self.cfg.max_position_embeddings, activation_dtype=str(self.dtype).replace("torch.", ""),
             tp_size=self.par.tp_size, rs_cache_slots=self.rs.num_slots if self.rs is not None else 0,
-            cohort_decode=self.rs is None,
+            cohort_decode=self.rs is None, media_spec=self._media_spec(),
             media=(("image", "video") if self.vision is not None else ()) + (("audio",) if self.audio is not None else ()))
 
     # ------------------------------------------------------------------ request -> slab
@@ -609,6 +609,15 @@ class TorchDriver:
             return None
         return self.model.logits(hidden, fi)
 
+    def _media_spec(self) -> dict:
+        v = self.vision
+        if v is None:
+            return {}
+        c = v.cfg
+        if hasattr(c, "mm_tokens_per_image"):          # fixed-resolution SigLIP tower (Gemma-3)
+            return {"style": "siglip", "image_size": c.image_size, "patch": c.patch_size, "pool": c.pool}
+        return {"style": "qwen", "patch": c.patch_size, "merge": c.spatial_merge_size, "temporal": c.temporal_patch_size}
+
     def put_media(self, slot: int, kind: str, patches, grids) -> int:
         """Encode a clip and keep the encoder's output on the device under `slot`; forward requests then name it in
         their media spans. Images and video: patch rows + their (t, h, w) grids (`runtime.multimodal.patchify`);
@@ -620,7 +629,10 @@ class TorchDriver:
             raise ValueError(f"this driver has no encoder for {kind}")
         with self._order:
             self._bind_thread()
-            feats = enc(np.asarray(patches, dtype=np.float32), [tuple(int(x) for x in g) for g in grids])
+            grids = [tuple(int(x) for x in g) for g in grids]
+            if enc is self.vision and hasattr(enc.cfg, "mm_tokens_per_image"):
+                grids = [(1, h, w) for t, h, w in grids for _ in range(t)]      # every frame is an image of its own
+            feats = enc(np.asarray(patches, dtype=np.float32), grids)
             self.media[int(slot)] = feats.to(self.dtype).contiguous()
             return int(feats.shape[0])
 

@@ -214,7 +214,9 @@ class Capabilities:
     system_speculation: bool = False
     rs_cache_slots: int = 0
     cohort_decode: bool = True      # False: no array-form decode step (`decode_async`); the runtime steps per request
-    media: tuple = ()               # media kinds the driver can encode ("image", "video"); empty for text-only models
+    media: tuple = ()               # media kinds the driver can encode ("image", "video", "audio"); empty for text-only models
+    media_spec: dict = field(default_factory=dict)   # what the host's preprocessing must produce for the model's vision tower:
+                                    # {"style": "qwen", "patch", "merge", "temporal"} or {"style": "siglip", "image_size", "patch", "pool"}
 
     def to_json(self) -> str:
         return json.dumps(asdict(self))

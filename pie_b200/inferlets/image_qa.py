@@ -30,7 +30,7 @@ async def main(args):
     model = Model.load(args.get("model") or runtime.models()[0])
     if "image" not in media.supported(model):
         return json.dumps({"ok": False, "error": f"model {model.name} has no image encoder"})
-    image = media.Image.from_bytes(await load_image_bytes(args), **(args.get("resize") or {}))
+    image = media.Image.for_model(model, await load_image_bytes(args), **(args.get("resize") or {}))
     ctx = Context(model)
     if model.instruct is not None:
         ctx.system(args.get("system", "You are a helpful visual assistant.")).user("Here is an image:")

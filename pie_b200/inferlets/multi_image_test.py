@@ -19,7 +19,7 @@ async def main(args):
     model = Model.load(args.get("model") or runtime.models()[0])
     if "image" not in media.supported(model):
         return json.dumps({"ok": False, "error": f"model {model.name} has no image encoder"})
-    images = [media.Image.from_bytes(base64.b64decode(b), **(args.get("resize") or {})) for b in args.get("images_b64", [])]
+    images = [media.Image.for_model(model, base64.b64decode(b), **(args.get("resize") or {})) for b in args.get("images_b64", [])]
     if not images:
         return json.dumps({"ok": False, "error": "images_b64 is empty"})
     sep = model.tokenizer().encode(args.get("separator", "\n"))

@@ -18,7 +18,7 @@ async def main(args):
     model = Model.load(args.get("model") or runtime.models()[0])
     if "video" not in media.supported(model):
         return json.dumps({"ok": False, "error": f"model {model.name} has no video encoder"})
-    clip = media.Video.from_bytes(base64.b64decode(args["video_b64"]), max_frames=int(args.get("max_frames", 8)),
+    clip = media.Video.for_model(model, base64.b64decode(args["video_b64"]), max_frames=int(args.get("max_frames", 8)),
                                   **(args.get("resize") or {}))
     ctx = Context(model)
     ctx.append_video(clip)

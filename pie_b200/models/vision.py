@@ -180,3 +180,143 @@ class VisionEncoder:
     def num_tokens(self, grid: Tuple[int, int, int]) -> int:
         t, h, w = grid
         return t * h * w // self.cfg.merge_unit
+
+
+# ----------------------------------------------------------------------------- SigLIP tower + Gemma-3 projector
+@dataclass
+class SiglipConfig:
+    """The fixed-resolution vision tower of Gemma-3: `image_size / patch_size` patches a side with learned position
+    rows, plain pre-LayerNorm blocks (biased projections, tanh-GELU MLP), a final LayerNorm; the projector averages
+    the patch grid down to `mm_tokens_per_image` rows, applies a (1 + w) RMSNorm and one matrix into the language
+    model's width."""
+    image_size: int = 896
+    patch_size: int = 14
+    embed_dim: int = 1152
+    intermediate_size: int = 4304
+    depth: int = 27
+    num_heads: int = 16
+    mm_tokens_per_image: int = 256
+    layer_norm_eps: float = 1e-6
+    in_channels: int = 3
+    hidden_size: int = 2560            # the language model's width
+
+    @property
+    def side(self) -> int:
+        return self.image_size // self.patch_size
+
+    @property
+    def pool(self) -> int:
+        return self.side // int(self.mm_tokens_per_image ** 0.5)
+
+    @property
+    def patch_features(self) -> int:
+        return self.in_channels * self.patch_size * self.patch_size
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    @staticmethod
+    def from_hf(cfg: dict, llm_hidden: int = 0) -> "SiglipConfig":
+        """From a Gemma-3 `config.json` (`vision_config` section + `mm_tokens_per_image`)."""
+        v = cfg.get("vision_config") or {}
+        return SiglipConfig(image_size=v.get("image_size", 896), patch_size=v.get("patch_size", 14), embed_dim=v.get("hidden_size", 1152),
+                            intermediate_size=v.get("intermediate_size", 4304), depth=v.get("num_hidden_layers", 27),
+                            num_heads=v.get("num_attention_heads", 16), mm_tokens_per_image=cfg.get("mm_tokens_per_image", 256),
+                            layer_norm_eps=v.get("layer_norm_eps", 1e-6), in_channels=v.get("num_channels", 3), hidden_size=llm_hidden)
+
+
+SIGLIP_PRESETS = {
+    "tiny-siglip": dict(image_size=112, patch_size=14, embed_dim=64, intermediate_size=128, depth=2, num_heads=4,
+                        mm_tokens_per_image=16, hidden_size=256),
+    "gemma3-siglip": dict(hidden_size=2560),
+}
+
+
+def siglip_preset(name: str, **over) -> SiglipConfig:
+    kw = dict(SIGLIP_PRESETS[name])
+    kw.update(over)
+    return SiglipConfig(**kw)
+
+
+def random_siglip_weights(cfg: SiglipConfig, device="cpu", dtype=torch.float32, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """N(0, 0.05) weights under the checkpoint's names below `vision_tower.vision_model.` (patch embedding flattened to
+    [E, C*p*p]) plus the projector's two tensors as `projector.*`; the projector's norm gain holds the full multiplier."""
+    g = torch.Generator().manual_seed(seed)
+    E, M = cfg.embed_dim, cfg.intermediate_size
+
+    def n(*shape, std=0.05):
+        return (torch.randn(*shape, generator=g) * std).to(dtype).to(device)
+
+    w = {"embeddings.patch_embedding.weight": n(E, cfg.patch_features), "embeddings.patch_embedding.bias": n(E),
+         "embeddings.position_embedding.weight": n(cfg.side * cfg.side, E), "post_layernorm.weight": 1 + n(E, std=0.1),
+         "post_layernorm.bias": n(E), "projector.mm_soft_emb_norm.weight": 1 + n(E, std=0.1),
+         "projector.mm_input_projection_weight": n(E, cfg.hidden_size)}
+    for i in range(cfg.depth):
+        L = f"encoder.layers.{i}."
+        for nm in ("layer_norm1", "layer_norm2"):
+            w[L + nm + ".weight"], w[L + nm + ".bias"] = 1 + n(E, std=0.1), n(E)
+        for p in ("q_proj", "k_proj", "v_proj", "out_proj"):
+            w[L + f"self_attn.{p}.weight"], w[L + f"self_attn.{p}.bias"] = n(E, E), n(E)
+        w[L + "mlp.fc1.weight"], w[L + "mlp.fc1.bias"], w[L + "mlp.fc2.weight"], w[L + "mlp.fc2.bias"] = n(M, E), n(M), n(E, M), n(E)
+    return w
+
+
+def load_siglip_weights(reader, device="cpu", dtype=torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """`vision_tower.vision_model.*` and `multi_modal_projector.*` of a Gemma-3 checkpoint (with or without the leading
+    `model.`); the projector's RMSNorm gain is stored as (w - 1) like the language model's and gets its 1 here."""
+    out = {}
+    for name in reader.names():
+        key = name[len("model."):] if name.startswith("model.") else name
+        if key.startswith("vision_tower.vision_model."):
+            k = key[len("vision_tower.vision_model."):]
+            t = reader.get(name)
+            out[k] = (t.reshape(t.shape[0], -1) if k == "embeddings.patch_embedding.weight" else t).to(dtype).to(device)
+        elif key.startswith("multi_modal_projector."):
+            k = key[len("multi_modal_projector."):]
+            t = reader.get(name)
+            out["projector." + k] = ((t.float() + 1.0) if k == "mm_soft_emb_norm.weight" else t).to(dtype).to(device)
+    if "embeddings.patch_embedding.weight" not in out:
+        raise KeyError("checkpoint has no SigLIP tower (no vision_tower.vision_model.embeddings.patch_embedding.weight)")
+    return out
+
+
+class SiglipEncoder:
+    """forward(patches, grids): patches [images * side^2, C*p*p] in row-major patch order (`multimodal.patchify_fixed`),
+    grids [(1, side, side)] per image -> [images * mm_tokens_per_image, hidden_size]."""
+
+    def __init__(self, cfg: SiglipConfig, weights: Dict[str, torch.Tensor]):
+        self.cfg, self.w = cfg, weights
+        first = weights["embeddings.patch_embedding.weight"]
+        self.device, self.dtype = first.device, first.dtype
+
+    def _lin(self, x, name):
+        return F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
+
+    def _ln(self, x, name):
+        return F.layer_norm(x, (x.shape[-1],), self.w[name + ".weight"], self.w[name + ".bias"], self.cfg.layer_norm_eps)
+
+    @torch.no_grad()
+    def forward(self, patches, grids) -> torch.Tensor:
+        cfg = self.cfg
+        S, E, H = cfg.side * cfg.side, cfg.embed_dim, cfg.num_heads
+        x = torch.as_tensor(patches).to(self.device, self.dtype)
+        if any(tuple(g) != (1, cfg.side, cfg.side) for g in grids) or x.shape != (len(grids) * S, cfg.patch_features):
+            raise ValueError(f"this tower takes images of {cfg.side} x {cfg.side} patches with {cfg.patch_features} features; "
+                             f"got rows {tuple(x.shape)} for grids {list(grids)}")
+        B, hd = len(grids), E // H
+        x = self._lin(x, "embeddings.patch_embedding").reshape(B, S, E) + self.w["embeddings.position_embedding.weight"]
+        for i in range(cfg.depth):
+            L = f"encoder.layers.{i}."
+            y = self._ln(x, L + "layer_norm1")
+            q, k, v = (self._lin(y, L + "self_attn." + p).reshape(B, S, H, hd).transpose(1, 2) for p in ("q_proj", "k_proj", "v_proj"))
+            a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, S, E)
+            x = x + self._lin(a, L + "self_attn.out_proj")
+            x = x + self._lin(F.gelu(self._lin(self._ln(x, L + "layer_norm2"), L + "mlp.fc1"), approximate="tanh"), L + "mlp.fc2")
+        x = self._ln(x, "post_layernorm")
+        # projector: average the patch grid down, RMSNorm, one matrix into the language model's width
+        x = F.avg_pool2d(x.transpose(1, 2).reshape(B, E, cfg.side, cfg.side), cfg.pool, cfg.pool).flatten(2).transpose(1, 2)
+        xf = x.float()
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + cfg.layer_norm_eps) * self.w["projector.mm_soft_emb_norm.weight"].float()
+        return (xf.to(self.dtype) @ self.w["projector.mm_input_projection_weight"]).reshape(B * cfg.mm_tokens_per_image, cfg.hidden_size)
+
+    __call__ = forward

@@ -1,6 +1,7 @@
 """Host-side preprocessing of media inputs, producing the tensors and position ids that a
 vision / audio encoder consumes:
 
+  images  (SigLIP towers) decode -> fixed square resize -> [-1, 1] -> row-major patch rows (`patchify_fixed`)
   images  decode (PIL) -> smart resize (both sides multiples of patch*merge, pixel budget) ->
           normalise -> patchify into [grid_h*grid_w, C*patch*patch] rows (+ temporal duplication)
   M-RoPE  3-axis (t, h, w) position ids for a text + image token sequence
@@ -97,6 +98,20 @@ def patchify(frames: Sequence[np.ndarray], patch: int = 14, merge: int = 2, temp
     # rows ordered (t, h-block, w-block, h-in-block, w-in-block) so that merged neighbours are adjacent
     x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)
     return ImageFeatures(np.ascontiguousarray(x.reshape(gt * gh * gw, 3 * temporal * patch * patch)), (gt, gh, gw), merge)
+
+
+def patchify_fixed(frames: Sequence[np.ndarray], image_size: int = 896, patch: int = 14, pool: int = 4,
+                   mean: float = 0.5, std: float = 0.5) -> ImageFeatures:
+    """SigLIP-style patch rows (Gemma-3): every frame is resized to `image_size` squared whatever its aspect ratio,
+    normalised to [-1, 1], and cut into `patch`-sized squares in row-major order; a row holds (channel, patch row,
+    patch column). `pool` is the side of the average pool of the model's projector: tokens = patches / pool^2."""
+    side = image_size // patch
+    rows = []
+    for f in frames:
+        x = (_resize(f, image_size, image_size).astype(np.float32) / 255.0 - mean) / std          # [H, W, C]
+        x = x.transpose(2, 0, 1).reshape(3, side, patch, side, patch).transpose(1, 3, 0, 2, 4)
+        rows.append(x.reshape(side * side, 3 * patch * patch))
+    return ImageFeatures(np.ascontiguousarray(np.concatenate(rows)), (len(rows), side, side), pool)
 
 
 def mrope_positions(segments: Sequence[tuple], merge: int = 2) -> np.ndarray:

@@ -205,10 +205,8 @@ class Forward:
             ctx._reserve_for(n_in)                       # the common case needs no waiting (and no coroutine)
         except _Deferred:
             await ctx._reserve_async(n_in)
-        pending = ctx.__dict__.get("_pending_media")
-        if pending:                                      # clips appended since the last pass: their encoder must be done
-            while pending:
-                await host.wait(pending.pop().ready)
+        if ctx.__dict__.get("_pending_media"):
+            await ctx._await_media()
         svc = ctx._entry.inference
         fut = svc.submit(ctx.id, self._tokens, self._positions, self._samplers, self._attn_masks, self._mask,
                          self._spec_tokens, self._spec_positions, self._adapter, self._speculate,
@@ -377,6 +375,13 @@ class Context:
         else:
             entry.ready.result()            # an encoder error of an earlier caller is this caller's too
         return self
+
+    async def _await_media(self) -> None:
+        """Clips appended since the last pass: every path that submits this context's tokens waits here until their
+        encoders are done (and gets an encoder's error)."""
+        pending = self.__dict__.get("_pending_media")
+        while pending:
+            await host.wait(pending.pop().ready)
 
     def append_image(self, image) -> "Context":
         """Splice an image into the context: one placeholder token per row of the vision encoder's output
@@ -634,6 +639,8 @@ class Generator:
         n = self._max if self._max is not None else 1 << 30
         start = ctx.seq_len
         await ctx._reserve_async(len(toks) + 1)
+        if ctx.__dict__.get("_pending_media"):
+            await ctx._await_media()
         stream = ctx._entry.inference.start_stream(ctx.id, toks, list(range(start, start + len(toks))),
                                                    self.sampler.spec, n, self._stop)
         if on_tokens is not None:

@@ -28,7 +28,14 @@ class Image:
 
     @classmethod
     def from_bytes(cls, data: bytes, **kw) -> "Image":
+        """Qwen-VL style preprocessing (smart resize, merge-block patch order)."""
         return cls(mm.patchify([mm.decode_image(data)], **kw))
+
+    @classmethod
+    def for_model(cls, model, data: bytes, **kw) -> "Image":
+        """Preprocess the way the model's vision tower wants it (`Capabilities.media_spec`): an inferlet written with
+        this call serves any vision model unchanged. `kw` overrides single settings (e.g. `max_pixels`)."""
+        return cls(_features_for(model, [mm.decode_image(data)], kw))
 
     @property
     def num_tokens(self) -> int:
@@ -42,6 +49,10 @@ class Video:
     @classmethod
     def from_bytes(cls, data: bytes, max_frames: int = 16, **kw) -> "Video":
         return cls(mm.patchify(mm.decode_frames(data, max_frames), **kw))
+
+    @classmethod
+    def for_model(cls, model, data: bytes, max_frames: int = 16, **kw) -> "Video":
+        return cls(_features_for(model, mm.decode_frames(data, max_frames), kw))
 
     @property
     def num_tokens(self) -> int:
@@ -70,6 +81,17 @@ class Audio:
     @property
     def grid(self):
         return (int(self.mel.shape[1]),)
+
+
+def _features_for(model, frames, kw: dict):
+    spec = dict(getattr(model._entry.caps[0], "media_spec", None) or {})
+    if spec.get("style") == "siglip":
+        args = dict(image_size=spec["image_size"], patch=spec["patch"], pool=spec["pool"])
+        args.update({k: v for k, v in kw.items() if k in ("mean", "std")})
+        return mm.patchify_fixed(frames, **args)
+    args = {k: spec[k] for k in ("patch", "merge", "temporal") if k in spec}
+    args.update(kw)
+    return mm.patchify(frames, **args)
 
 
 def supported(model) -> List[str]:

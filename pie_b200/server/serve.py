@@ -80,8 +80,14 @@ def _vision_encoder(m: ModelSection, cfg, device, dtype):
     if kind == "checkpoint":
         from ..models.loader import SafetensorsReader
         hf = _json.loads((Path(m.path) / "config.json").read_text())
+        if (hf.get("vision_config") or {}).get("model_type") == "siglip_vision_model":      # Gemma-3: SigLIP tower + pooling projector
+            scfg = V.SiglipConfig.from_hf(hf, llm_hidden=cfg.hidden_size)
+            return V.SiglipEncoder(scfg, V.load_siglip_weights(SafetensorsReader(m.path), device, dtype))
         vcfg = V.VisionConfig.from_hf(hf.get("vision_config") or {}, llm_hidden=cfg.hidden_size)
         return V.VisionEncoder(vcfg, V.load_vision_weights(SafetensorsReader(m.path), device, dtype))
+    if kind in V.SIGLIP_PRESETS:
+        scfg = V.siglip_preset(kind, hidden_size=cfg.hidden_size)
+        return V.SiglipEncoder(scfg, V.random_siglip_weights(scfg, device, dtype))
     vcfg = V.vision_preset(kind, hidden_size=cfg.hidden_size)
     return V.VisionEncoder(vcfg, V.random_vision_weights(vcfg, device, dtype))
 

@@ -307,3 +307,71 @@ def test_audio_clips_through_the_engine():
         assert not out["ok"] and "no image encoder" in out["error"]
     finally:
         e.shutdown()
+
+
+def test_siglip_tower_and_gemma3_projector_equal_transformers():
+    from transformers import Gemma3Config, Gemma3TextConfig
+    from transformers.models.gemma3 import modeling_gemma3 as g
+    from transformers.models.siglip import modeling_siglip as m
+    from transformers.models.siglip.configuration_siglip import SiglipVisionConfig
+    from pie_b200.models.vision import SiglipEncoder, random_siglip_weights, siglip_preset
+    cfg = siglip_preset("tiny-siglip", hidden_size=96)
+    w = random_siglip_weights(cfg, seed=3)
+    vc = SiglipVisionConfig(hidden_size=cfg.embed_dim, intermediate_size=cfg.intermediate_size, num_hidden_layers=cfg.depth,
+                            num_attention_heads=cfg.num_heads, image_size=cfg.image_size, patch_size=cfg.patch_size, vision_use_head=False)
+    vc._attn_implementation = "eager"
+    tower = m.SiglipVisionModel(vc).float().eval()
+    sd = {"vision_model." + k: v for k, v in w.items() if not k.startswith("projector.")}
+    sd["vision_model.embeddings.patch_embedding.weight"] = sd["vision_model.embeddings.patch_embedding.weight"].reshape(cfg.embed_dim, 3, 14, 14)
+    tower.load_state_dict(sd, strict=True)
+    gc = Gemma3Config(text_config=Gemma3TextConfig(hidden_size=96, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                                                   head_dim=16, intermediate_size=64, vocab_size=100).to_dict(),
+                      vision_config=vc.to_dict(), mm_tokens_per_image=cfg.mm_tokens_per_image)
+    proj = g.Gemma3MultiModalProjector(gc).float().eval()
+    proj.load_state_dict({"mm_input_projection_weight": w["projector.mm_input_projection_weight"],
+                          "mm_soft_emb_norm.weight": w["projector.mm_soft_emb_norm.weight"] - 1})
+    # the host's own preprocessing on two real images: pixel tensors for transformers, patch rows for the encoder
+    frames = [mm.decode_image(png_bytes(1, 80, 130)), mm.decode_image(png_bytes(2, 200, 90))]
+    feats = mm.patchify_fixed(frames, image_size=cfg.image_size, patch=cfg.patch_size, pool=cfg.pool)
+    assert feats.grid == (2, cfg.side, cfg.side) and feats.num_tokens == 2 * cfg.mm_tokens_per_image
+    pix = torch.from_numpy(feats.patches).reshape(2, cfg.side, cfg.side, 3, 14, 14).permute(0, 3, 1, 4, 2, 5).reshape(2, 3, 112, 112)
+    assert float(pix.min()) >= -1.0 and float(pix.max()) <= 1.0
+    with torch.no_grad():
+        want = proj(tower(pixel_values=pix).last_hidden_state).reshape(-1, 96)
+    got = SiglipEncoder(cfg, w)(feats.patches, [(1, cfg.side, cfg.side)] * 2)
+    assert got.shape == want.shape == (32, 96) and (got - want).abs().max() < 1e-5
+
+
+def test_gemma3_with_a_siglip_tower_answers_over_an_image():
+    from pie_b200.models.vision import SiglipEncoder, random_siglip_weights, siglip_preset
+    cfg = preset("tiny-gemma3")
+    w = random_weights(cfg, "cpu", torch.float32, seed=3)
+    scfg = siglip_preset("tiny-siglip", hidden_size=cfg.hidden_size)
+    enc = SiglipEncoder(scfg, random_siglip_weights(scfg, seed=8))
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=48, vision=enc)
+    spec = drv.capabilities().media_spec
+    assert spec == {"style": "siglip", "image_size": 112, "patch": 14, "pool": 2}
+    e = Engine(EngineConfig())
+    try:
+        e.add_model("gemma-vlm", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
+        install_all(e)
+        data = png_bytes(3, 300, 200)
+        q = "Describe."
+        out = json.loads(e.run("image-qa", {"image_b64": base64.b64encode(data).decode(), "question": q, "max_tokens": 4,
+                                            "temperature": 0.0}, 300))
+        # the inferlet asked for the model's own preprocessing: one 112 x 112 image, 16 soft tokens
+        feats = mm.patchify_fixed([mm.decode_image(data)], image_size=112, patch=14, pool=2)
+        assert out["ok"] and out["image_tokens"] == 16 and out["grid"] == [1, 8, 8]
+        rows = enc(feats.patches, [(1, 8, 8)])
+        toks = [0] * 16 + ByteTokenizer(cfg.vocab_size).encode(q)
+        emb = {i: rows[i] for i in range(16)}          # image rows are not scaled by the embedding factor
+        want = []
+        for _ in range(4):
+            want.append(int(dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].argmax()))
+            toks.append(want[-1])
+        assert out["tokens"] == want
+        # a clip of several frames is a batch of images for this tower
+        vid = json.loads(e.run("video-qa", {"video_b64": base64.b64encode(gif_bytes(3)).decode(), "max_tokens": 2}, 300))
+        assert vid["ok"] and vid["video_tokens"] == 3 * 16
+    finally:
+        e.shutdown()
