@@ -173,6 +173,10 @@ class ModelConfig:
         quant = None
         if q.get("quant_method") == "fp8" and q.get("weight_block_size"):
             quant = "fp8_block"
+        elif _is_fp8_weight_config(q):
+            # per-tensor / per-channel fp8 checkpoints (`weight_scale` next to each weight): the loader spreads the scale
+            # over the row blocks of the same runtime format; activations are quantised per call, a stored input scale is unused
+            quant = "fp8_block"
         return ModelConfig(
             model_type=mt,
             hidden_size=cfg["hidden_size"],
@@ -227,6 +231,20 @@ class ModelConfig:
         p = Path(path)
         with open(p / "config.json") as f:
             return ModelConfig.from_hf(json.load(f), name=p.name)
+
+
+def _is_fp8_weight_config(q: dict) -> bool:
+    """`quantization_config` of an 8-bit float weight checkpoint without block scales: `fp8` / `fbgemm_fp8`, or
+    compressed-tensors groups whose weights are 8-bit floats with a tensor or channel strategy."""
+    method = q.get("quant_method")
+    if method in ("fp8", "fbgemm_fp8"):
+        return True
+    if method == "compressed-tensors":
+        groups = (q.get("config_groups") or {}).values()
+        ws = [g.get("weights") or {} for g in groups]
+        return bool(ws) and all(w.get("type") == "float" and w.get("num_bits") == 8 and w.get("strategy") in ("tensor", "channel")
+                                for w in ws)
+    return False
 
 
 def _flatten_rope_parameters(cfg: dict) -> dict:

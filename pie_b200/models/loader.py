@@ -57,6 +57,7 @@ def Stack(xs): return Op("stack", {}, list(xs))
 def ExpandRows(x, factor, like): return Op("expand_rows", {"factor": factor, "like": like}, [x])
 def Transpose(x, a, b): return Op("transpose", {"a": a, "b": b}, [x])
 def AddScalar(x, value): return Op("add_scalar", {"value": value}, [x])
+def RowScales(scale, like): return Op("row_scales", {"like": like}, [scale])
 def Mxfp4(blocks, scales): return Op("mxfp4", {}, [blocks, scales])
 
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
@@ -155,6 +156,10 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
         sc = n + "_scale_inv"
         if cfg.quantization == "fp8_block" and sc in names:
             return QLin(w(n), ExpandRows(Read(sc), 128, n))
+        sc = n + "_scale"
+        if cfg.quantization == "fp8_block" and sc in names:
+            # per-tensor (scalar) or per-output-channel ([N] / [N, 1]) scales: the same number for every 128-wide block of a row
+            return QLin(w(n), RowScales(Read(sc), n))
         return QLin(w(n))
 
     att["embed"] = w(f"{pre}embed_tokens.weight")
@@ -359,6 +364,12 @@ def _eval(op: Op, reader, dtype) -> torch.Tensor:
     if k == "expand_rows":
         rows = reader.get_slice(op.args["like"]).get_shape()[0]       # ragged last block: cut to the weight's rows
         return xs[0].float().repeat_interleave(op.args["factor"], dim=0)[:rows]
+    if k == "row_scales":
+        n, kk = reader.get_slice(op.args["like"]).get_shape()
+        sc = xs[0].float().reshape(-1)
+        if sc.numel() not in (1, n):
+            raise ValueError(f"weight scale of {sc.numel()} values for a weight of {n} rows")
+        return sc.reshape(-1, 1).expand(n, -(-kk // 128)).contiguous()
     raise ValueError(f"unknown op {k}")
 
 
@@ -415,6 +426,14 @@ def infer_shape(op: Op, reader) -> Tuple[int, ...]:
     if k == "expand_rows":
         rows = reader.get_slice(op.args["like"]).get_shape()[0]
         return (min(x[0] * op.args["factor"], rows),) + x[1:]
+    if k == "row_scales":
+        n, kk = reader.get_slice(op.args["like"]).get_shape()
+        cnt = 1
+        for d in x:
+            cnt *= d
+        if cnt not in (1, n):
+            raise LoaderTypeError(f"weight scale of shape {x} for a weight of {n} rows")
+        return (n, -(-kk // 128))
     raise LoaderTypeError(f"unknown op {k}")
 
 

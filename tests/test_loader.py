@@ -546,3 +546,64 @@ def test_type_check_reports_every_misfit_before_reading_tensors(tmp_path):
     assert "layers.0.w_gate_up" in msg and "layers.0.w_down" in msg and "rows" in msg and reads == []
     with pytest.raises(loader.LoaderTypeError, match="does not split over 3 ranks"):
         loader.infer_shape(loader.Shard(loader.Read("model.layers.0.mlp.down_proj.weight"), 1, 0, 3), rd)
+
+
+@pytest.mark.parametrize("strategy", ["tensor", "channel"])
+def test_fp8_per_tensor_and_per_channel_checkpoints_load(tmp_path, strategy):
+    """fp8 checkpoints with one scale per weight tensor or per output channel (`weight_scale` beside each weight, the
+    compressed-tensors / fbgemm layout) load into the block-scaled runtime format: the scale is spread over a row's
+    blocks, also through the fused QKV join, the gate / up interleave and a tensor-parallel shard."""
+    import json as _json
+    import numpy as np
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    from pie_b200 import ops
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models import loader
+    from pie_b200.models.config import ModelConfig, preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import dequantized, random_weights
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=3)
+    loader.export_hf_checkpoint(cfg, w, tmp_path)
+    out = {}
+    with safe_open(str(tmp_path / "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            t = f.get_tensor(k)
+            if k.endswith("_proj.weight"):
+                amax = t.abs().amax() if strategy == "tensor" else t.abs().amax(dim=1, keepdim=True)
+                sc = (amax.clamp_min(1e-12) / 448.0).float()
+                out[k] = (t / sc).to(torch.float8_e4m3fn)
+                out[k + "_scale"] = sc.reshape(1) if strategy == "tensor" else sc          # [1] or [N, 1]
+                out[k[:-len("weight")] + "input_scale"] = torch.ones(1)                       # a static activation scale: unused
+            else:
+                out[k] = t
+    save_file(out, str(tmp_path / "model.safetensors"))
+    hf = _json.loads((tmp_path / "config.json").read_text())
+    hf["quantization_config"] = {"quant_method": "compressed-tensors", "config_groups": {"group_0": {
+        "weights": {"num_bits": 8, "type": "float", "strategy": strategy}, "input_activations": {"num_bits": 8, "type": "float"}}}}
+    (tmp_path / "config.json").write_text(_json.dumps(hf))
+    assert ModelConfig.from_hf({**hf, "quantization_config": {"quant_method": "fbgemm_fp8"}}).quantization == "fp8_block"
+    assert ModelConfig.from_hf({**hf, "quantization_config": {"quant_method": "compressed-tensors", "config_groups": {"g": {
+        "weights": {"num_bits": 4, "type": "int", "strategy": "group"}}}}}).quantization is None
+    cfg2, w2 = loader.load_checkpoint(tmp_path, "cpu", dtype="float32")
+    lw = w2["layers"][0]
+    assert cfg2.quantization == "fp8_block" and isinstance(lw["wqkv"], ops.Fp8Linear) and isinstance(lw["w_down"], ops.Fp8Linear)
+    assert lw["w_gate_up"].scale.shape == (2 * cfg.intermediate_size, cfg.hidden_size // 128)
+    if strategy == "tensor":        # q, k and v keep their own scales inside the fused tensor
+        q_rows = cfg.num_attention_heads * cfg.head_dim
+        assert lw["wqkv"].scale[:q_rows].unique().numel() == 1 and lw["wqkv"].scale.unique().numel() == 3
+    err = (lw["wo"].dequant(torch.float32) - w["layers"][0]["wo"]).abs().max() / w["layers"][0]["wo"].abs().max()
+    assert err < 0.07
+    drv = TorchDriver(cfg2, "cpu", weights=w2, num_pages=16, page_size=16, max_requests=4, max_tokens=128)
+    toks = list(range(40, 70))
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    resp = drv.fire_batch(fold([PendingRequest(0, toks, list(range(len(toks))), list(range(4)), 0, [(len(toks) - 1, raw)])], 16))
+    got = np.frombuffer(resp.slots[0].logits, dtype=np.float32)
+    want = dense_reference_forward(cfg2, dequantized(w2), torch.tensor(toks))[-1].numpy()
+    assert np.abs(got - want).max() < 1e-3
+    _, wr = loader.load_checkpoint(tmp_path, "cpu", tp_size=2, tp_rank=1, dtype="float32")
+    full, part = w2["layers"][0]["w_gate_up"], wr["layers"][0]["w_gate_up"]
+    assert torch.equal(part.dequant(torch.float32), full.dequant(torch.float32)[full.shape[0] // 2:])
