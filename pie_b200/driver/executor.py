@@ -730,34 +730,49 @@ class TorchDriver:
                                 s.h("min_p", np.float32)[:k], s.h("seeds", np.int64)[:k], masks).numpy()
 
     def _probes(self, req, logits, slot_logit_row, probe_slots, out_slots):
+        """Probe slots (distribution, raw logits, log-probabilities of labels, entropy) of one fire, batched per kind:
+        one pass of device work and one device-to-host copy per kind, whatever the number of slots."""
         rows = torch.from_numpy(slot_logit_row[probe_slots].astype(np.int64)).to(logits.device)
         lg = logits[rows]
         if self.model.sharded_logits:       # probes read whole rows: gather the few rows they name
             lg = self.par.comm.all_gather_logits(lg)
-        stats = ops.row_stats(lg.contiguous()).float().cpu().numpy()
+        lg = lg.contiguous()
+        stats = ops.row_stats(lg).float().cpu().numpy()            # max, log-sum-exp, entropy per row
+        by_kind: Dict[int, list] = {}
         for j, i in enumerate(probe_slots):
-            sp = req.slot_samplers[i]
-            row = lg[j].float()
-            mask = req.logit_masks[int(req.slot_req[i])] if req.logit_masks else None
-            if sp.kind == SamplerKind.DIST:
-                t = sp.temperature if sp.temperature > 0 else 1.0
-                p = torch.softmax(row / t, -1)
-                k = min(sp.top_k if sp.top_k > 0 else 32, p.numel())
-                pv, pi = torch.topk(p, k)
-                out_slots[i] = SlotOutput("distribution", ids=pi.cpu().tolist(), probs=pv.cpu().tolist())
-            elif sp.kind == SamplerKind.RAW_LOGITS:
-                out_slots[i] = SlotOutput("logits", logits=row.cpu().numpy().astype(np.float32).tobytes())
-            elif sp.kind in (SamplerKind.LOGPROB, SamplerKind.LOGPROBS):
-                lab = torch.tensor(list(sp.labels), dtype=torch.long, device=row.device)
-                lp = (row[lab] - float(stats[j, 1])).cpu().tolist()
-                out_slots[i] = SlotOutput("logprobs", logprobs=lp)
-            elif sp.kind == SamplerKind.ENTROPY:
-                out_slots[i] = SlotOutput("entropy", entropy=float(stats[j, 2]))
-            elif sp.kind == SamplerKind.EMBEDDING:
-                out_slots[i] = SlotOutput("embedding", logits=b"")
+            by_kind.setdefault(int(req.slot_samplers[i].kind), []).append((j, i))
+        dev = lg.device
+        for kind, members in by_kind.items():
+            js = torch.tensor([j for j, _ in members], dtype=torch.long, device=dev)
+            sps = [req.slot_samplers[i] for _, i in members]
+            if kind == SamplerKind.DIST:
+                temp = torch.tensor([sp.temperature if sp.temperature > 0 else 1.0 for sp in sps], dtype=torch.float32, device=dev)
+                ks = [min(sp.top_k if sp.top_k > 0 else 32, lg.shape[1]) for sp in sps]
+                pv, pi = torch.topk(torch.softmax(lg[js].float() / temp[:, None], -1), max(ks))
+                pv, pi = pv.cpu().numpy(), pi.cpu().numpy()
+                for n, (_, i) in enumerate(members):
+                    out_slots[i] = SlotOutput("distribution", ids=pi[n, :ks[n]].tolist(), probs=pv[n, :ks[n]].tolist())
+            elif kind == SamplerKind.RAW_LOGITS:
+                raw = lg[js].float().cpu().numpy()
+                for n, (_, i) in enumerate(members):
+                    out_slots[i] = SlotOutput("logits", logits=raw[n].tobytes())
+            elif kind in (SamplerKind.LOGPROB, SamplerKind.LOGPROBS):
+                counts = [len(sp.labels) for sp in sps]
+                row_of = torch.tensor([j for (j, _), c in zip(members, counts) for _ in range(c)], dtype=torch.long, device=dev)
+                labs = torch.tensor([int(x) for sp in sps for x in sp.labels], dtype=torch.long, device=dev)
+                vals = lg[row_of, labs].float().cpu().numpy() if labs.numel() else np.zeros(0, np.float32)
+                a = 0
+                for (j, i), c in zip(members, counts):
+                    out_slots[i] = SlotOutput("logprobs", logprobs=(vals[a:a + c] - float(stats[j, 1])).tolist())
+                    a += c
+            elif kind == SamplerKind.ENTROPY:
+                for j, i in members:
+                    out_slots[i] = SlotOutput("entropy", entropy=float(stats[j, 2]))
+            elif kind == SamplerKind.EMBEDDING:
+                for _, i in members:
+                    out_slots[i] = SlotOutput("embedding", logits=b"")
             else:
-                raise ValueError(f"unsupported sampler kind {sp.kind}")
-            del mask
+                raise ValueError(f"unsupported sampler kind {kind}")
 
     # ------------------------------------------------------------------ public entry points
     def fire_batch(self, req: ForwardRequest) -> ForwardResponse:

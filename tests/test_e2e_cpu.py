@@ -217,3 +217,36 @@ def test_system_speculation_gives_the_same_greedy_tokens_in_fewer_passes():
     assert toks(4) == toks(0)
     if st4["system_spec_accepted"] > 0:
         assert fires4 < fires0                     # accepted drafts save forward passes
+
+
+def test_probe_slots_of_every_kind_in_one_fire_are_batched_correctly():
+    """Two distributions with different temperatures and widths, two label sets of different sizes, raw logits and an
+    entropy in one fire: each slot's payload equals the plain computation on its own row."""
+    import numpy as np
+    import torch
+    from pie_b200.driver.executor import TorchDriver
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.models.config import preset
+    from pie_b200.models.transformer import dense_reference_forward
+    from pie_b200.models.weights import random_weights
+    from pie_b200.runtime.scheduler import PendingRequest, fold
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=1)
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=16, page_size=16, max_requests=4, max_tokens=64)
+    toks = list(range(10, 30))
+    specs = [(3, SamplerSpec(SamplerKind.DIST, temperature=0.7, top_k=5)), (19, SamplerSpec(SamplerKind.DIST, temperature=0.0, top_k=0)),
+             (7, SamplerSpec(SamplerKind.LOGPROBS, labels=(1, 2, 3))), (19, SamplerSpec(SamplerKind.LOGPROBS, labels=(31999,))),
+             (12, SamplerSpec(SamplerKind.RAW_LOGITS)), (19, SamplerSpec(SamplerKind.ENTROPY)), (3, SamplerSpec(SamplerKind.ENTROPY))]
+    resp = drv.fire_batch(fold([PendingRequest(0, toks, list(range(20)), [0, 1], 0, specs)], 16))
+    want = dense_reference_forward(cfg, w, torch.tensor(toks))
+    s = resp.slots
+    p = torch.softmax(want[3] / 0.7, -1)
+    pv, pi = torch.topk(p, 5)
+    assert s[0].ids == pi.tolist() and np.allclose(s[0].probs, pv.numpy(), atol=1e-5)
+    pv, pi = torch.topk(torch.softmax(want[19], -1), 32)
+    assert s[1].ids == pi.tolist() and np.allclose(s[1].probs, pv.numpy(), atol=1e-5)
+    assert np.allclose(s[2].logprobs, torch.log_softmax(want[7], -1)[[1, 2, 3]].numpy(), atol=1e-4)
+    assert np.allclose(s[3].logprobs, torch.log_softmax(want[19], -1)[[31999]].numpy(), atol=1e-4)
+    assert np.allclose(np.frombuffer(s[4].logits, dtype=np.float32), want[12].numpy(), atol=1e-4)
+    ent = lambda r: float(-(torch.softmax(r, -1) * torch.log_softmax(r, -1)).sum())
+    assert abs(s[5].entropy - ent(want[19])) < 1e-3 and abs(s[6].entropy - ent(want[3])) < 1e-3
