@@ -293,6 +293,43 @@ __global__ void brle_expand_kernel(const uint32_t* __restrict__ run_ends,
     }
 }
 
+// The same for rows of different lengths in one launch: row r has row_nbits[r] bits and its words start at
+// out + row_word_offset[r] (rows of one request back to back: the layout the prefill kernels read custom masks in).
+__global__ void brle_expand_ragged_kernel(const uint32_t* __restrict__ run_ends, const int* __restrict__ indptr,
+                                          uint32_t* __restrict__ out, const long* __restrict__ row_word_offset,
+                                          const int* __restrict__ row_nbits, int tail_value) {
+    const int r = blockIdx.y;
+    const uint32_t* ends = run_ends + indptr[r];
+    const int nr = indptr[r + 1] - indptr[r];
+    const int nbits = row_nbits[r];
+    const int words = (nbits + 31) >> 5;
+    uint32_t* dst = out + row_word_offset[r];
+    for (int w = blockIdx.x * blockDim.x + threadIdx.x; w < words; w += gridDim.x * blockDim.x) {
+        const uint32_t base = (uint32_t)w * 32u;
+        int lo = 0, hi = nr;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (ends[mid] > base) hi = mid; else lo = mid + 1;
+        }
+        uint32_t word = 0, bit = base;
+        int run = lo;
+        const uint32_t limit = min(base + 32u, (uint32_t)nbits);
+        while (bit < limit) {
+            uint32_t end;
+            int val;
+            if (run < nr) { end = min(ends[run], limit); val = run & 1; }
+            else { end = limit; val = tail_value; }
+            if (val && end > bit) {
+                const uint32_t n = end - bit;
+                word |= ((n >= 32u) ? 0xffffffffu : ((1u << n) - 1u)) << (bit - base);
+            }
+            bit = max(end, bit);
+            if (++run > nr + 1) break;
+        }
+        dst[w] = word;
+    }
+}
+
 }  // namespace pie
 
 using namespace pie;
@@ -448,6 +485,14 @@ PIE_API int pie_brle_expand(const uint32_t* run_ends, const int* indptr, uint32_
     const int words = (nbits + 31) / 32;
     dim3 grid(min((words + 127) / 128, 1024), rows);
     brle_expand_kernel<<<grid, 128, 0, st>>>(run_ends, indptr, out, words, nbits, tail_value);
+    return (int)cudaGetLastError();
+}
+
+PIE_API int pie_brle_expand_ragged(const uint32_t* run_ends, const int* indptr, uint32_t* out, const long* row_word_offset,
+                                   const int* row_nbits, int rows, int max_words, int tail_value, cudaStream_t st) {
+    if (rows <= 0 || max_words <= 0) return 0;
+    dim3 grid(min((max_words + 127) / 128, 64), rows);
+    brle_expand_ragged_kernel<<<grid, 128, 0, st>>>(run_ends, indptr, out, row_word_offset, row_nbits, tail_value);
     return (int)cudaGetLastError();
 }
 

@@ -574,14 +574,15 @@ class TorchDriver:
             s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
             mask_bits = mask_indptr = None
             if custom:
-                parts, indptr = [], [0]
+                # every mask row of the fire in one expansion: rows of a request back to back, each ceil(kv_len / 32) words
+                all_rows, row_bits, indptr = [], [], [0]
                 for i in range(r):
                     ql, kl = int(qlens[i]), int(kv_lens[i])
-                    runs = self._mask_rows_for_request(req, i, ql, kl)
-                    bits = ops.brle_expand(runs, kl, self.device) if ql else torch.zeros(0, 1, dtype=torch.int32, device=self.device)
-                    parts.append(bits.reshape(-1))
-                    indptr.append(indptr[-1] + bits.numel())
-                mask_bits = torch.cat(parts) if parts else None
+                    if ql:
+                        all_rows.extend(self._mask_rows_for_request(req, i, ql, kl))
+                        row_bits.extend([kl] * ql)
+                    indptr.append(indptr[-1] + ql * ((kl + 31) // 32))
+                mask_bits, _ = ops.brle_expand_ragged(all_rows, row_bits, self.device)
                 mask_indptr = torch.tensor(indptr, dtype=torch.int64, device=self.device)
             plan = ops.PrefillPlan(s.d("page_indices"), s.d("kv_page_indptr"), s.d("qo_indptr"), s.d("kv_lens"),
                                    s.d("tile_req"), s.d("tile_qstart"), nt, self.page_size, mask_bits, mask_indptr,

@@ -216,6 +216,30 @@ def brle_expand(rows_runs, nbits: int, device, tail_value: bool = False):
     return out
 
 
+def brle_expand_ragged(rows_runs, row_nbits, device, tail_value: bool = False):
+    """BRLE rows of different lengths in one launch: row r expands to ceil(row_nbits[r] / 32) words. Returns the words
+    of all rows back to back (int32 tensor) and the word offset of every row (int64 numpy [rows + 1])."""
+    nrows = len(rows_runs)
+    nbits = np.asarray(row_nbits, dtype=np.int32)
+    words = (nbits.astype(np.int64) + 31) // 32
+    offs = np.zeros(nrows + 1, dtype=np.int64)
+    offs[1:] = np.cumsum(words)
+    if torch.device(device).type != "cuda":
+        parts = [brle_expand([r], int(n), device, tail_value).reshape(-1) for r, n in zip(rows_runs, nbits)]
+        return (torch.cat(parts) if parts else torch.zeros(0, dtype=torch.int32)), offs
+    ends = [np.cumsum(np.asarray(r, dtype=np.int64)).clip(max=2**32 - 1).astype(np.uint32) for r in rows_runs]
+    indptr = np.zeros(nrows + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum([len(e) for e in ends])
+    flat = np.concatenate(ends) if ends and indptr[-1] > 0 else np.zeros(1, dtype=np.uint32)
+    out = torch.empty(max(1, int(offs[-1])), dtype=torch.int32, device=device)
+    if nrows:
+        d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        d_ends, d_indptr, d_offs, d_bits = d(flat.view(np.int32)), d(indptr), d(offs[:-1]), d(nbits)
+        check(fn("pie_brle_expand_ragged")(ptr(d_ends), ptr(d_indptr), ptr(out), ptr(d_offs), ptr(d_bits), nrows,
+                                           int(words.max()) if nrows else 0, int(tail_value), stream_ptr()), "brle_expand_ragged")
+    return out[:int(offs[-1])], offs
+
+
 def _to_i32(packed_i64):
     p = packed_i64 & 0xFFFFFFFF
     p = torch.where(p >= 2**31, p - 2**32, p)

@@ -37,6 +37,7 @@ _SIGNATURES = {
     "pie_gather_rows": [p, p, p, i32, i32, p],
     "pie_copy_pages": [p, p, p, i32, i32, i64, i64, p],
     "pie_brle_expand": [p, p, p, i32, i32, i32, p],
+    "pie_brle_expand_ragged": [p, p, p, p, p, i32, i32, i32, p],
     "pie_set_status_word": [p],
     "pie_paged_decode_attn": [p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, p],
     "pie_moe_bias_glu": [p, p, p, p, i32, i32, f32, p],

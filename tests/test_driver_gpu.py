@@ -274,3 +274,44 @@ def test_media_rows_replace_embeddings_on_the_gpu_driver():
         assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (a, b, cos)
     drv.release_media(5)
     assert drv.media == {}
+
+
+def test_custom_attention_masks_of_several_requests_in_one_fire():
+    """Requests with and without custom (BRLE) masks and of different lengths in one prefill: all mask rows are expanded in
+    one launch into the layout the attention kernel reads; the logits equal the CPU driver's on the same weights."""
+    cfg = preset("tiny-llama", dtype="bfloat16")
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=7)
+    wf = {"layers": [{k: v.float().cpu() for k, v in lw.items()} for lw in w["layers"]],
+          **{k: (v.float().cpu() if torch.is_tensor(v) else v) for k, v in w.items() if k != "layers"}}
+    gpu = TorchDriver(cfg, "cuda", weights=w, num_pages=32, page_size=16, max_requests=4, max_tokens=256)
+    cfg32 = preset("tiny-llama", dtype="float32")
+    cpu = TorchDriver(cfg32, "cpu", weights=wf, num_pages=32, page_size=16, max_requests=4, max_tokens=256)
+    raw = SamplerSpec(SamplerKind.RAW_LOGITS)
+    rng = np.random.default_rng(3)
+
+    def mask_rows(n):
+        rows = []
+        for i in range(n):          # row i sees a random subset of keys 0..i, always itself: BRLE of zeros / ones runs
+            allow = rng.random(i + 1) < 0.6
+            allow[i] = True
+            runs, cur, cnt = [], False, 0
+            for a in allow:
+                if a == cur:
+                    cnt += 1
+                else:
+                    runs.append(cnt)
+                    cur, cnt = a, 1
+            runs.append(cnt)
+            rows.append(runs)
+        return rows
+    lens = [37, 5, 70]
+    reqs = [PendingRequest(0, list(range(100, 137)), list(range(37)), [0, 1, 2], 0, [(36, raw)], masks=mask_rows(37)),
+            PendingRequest(1, list(range(200, 205)), list(range(5)), [3], 0, [(4, raw)]),
+            PendingRequest(2, list(range(300, 370)), list(range(70)), [4, 5, 6, 7, 8], 0, [(69, raw), (10, raw)], masks=mask_rows(70))]
+    a = gpu.fire_batch(fold(reqs, 16))
+    b = cpu.fire_batch(fold(reqs, 16))
+    assert len(a.slots) == len(b.slots) == 4 and lens
+    for sa, sb in zip(a.slots, b.slots):
+        x, y = np.frombuffer(sa.logits, dtype=np.float32), np.frombuffer(sb.logits, dtype=np.float32)
+        cos = float(np.dot(x, y) / (np.linalg.norm(x) * np.linalg.norm(y)))
+        assert cos > 0.995 and int(y.argmax()) in np.argsort(x)[-5:].tolist(), cos

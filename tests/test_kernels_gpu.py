@@ -105,6 +105,29 @@ def test_brle_expand():
     assert torch.equal(got, want)
 
 
+def test_brle_expand_ragged_equals_row_by_row():
+    rng = np.random.default_rng(1)
+    rows, bits = [], []
+    for nbits in (1, 31, 32, 33, 700, 64, 5000, 17):
+        for _ in range(3):
+            runs, tot = [], 0
+            while tot < nbits:
+                r = int(rng.integers(0, 90))
+                runs.append(r)
+                tot += r
+            rows.append(runs)
+            bits.append(nbits)
+    rows.append([4, 2])          # short row: the tail is zeros
+    bits.append(100)
+    got, offs = ops.brle_expand_ragged(rows, bits, DEV)
+    assert offs[-1] == got.numel() == sum((b + 31) // 32 for b in bits)
+    for i, (r, b) in enumerate(zip(rows, bits)):
+        want = ops.brle_expand([r], b, "cpu").reshape(-1)
+        assert torch.equal(got[offs[i]:offs[i + 1]].cpu(), want), (i, b)
+    cpu, offs2 = ops.brle_expand_ragged(rows, bits, "cpu")
+    assert torch.equal(cpu, got.cpu()) and np.array_equal(offs, offs2)
+
+
 def make_paged(nreq, kv_lens, hkv, d, page, seed=0, extra_pages=5):
     npages = [-(-int(k) // page) for k in kv_lens]
     total = sum(npages) + extra_pages
