@@ -35,6 +35,7 @@ __global__ void gdn_conv_kernel(const bf16* __restrict__ x, int x_stride, const 
     const int t = blockIdx.y;
     if (ch >= c || t >= n) return;
     const int r = tok_req[t];
+    if (slots[r] < 0) return;          // a padding request of a decode graph's bucket: no state, no output
     const int first = qo_indptr[r];
     const int i = t - first;
     const bool fresh = reset[r] != 0;
@@ -60,7 +61,7 @@ __global__ void gdn_conv_state_kernel(const bf16* __restrict__ x, int x_stride, 
     const int r = blockIdx.y;
     if (ch >= c) return;
     const int first = qo_indptr[r], len = qo_indptr[r + 1] - first;
-    if (len <= 0) return;
+    if (len <= 0 || slots[r] < 0) return;
     float* st = state + ((size_t)slots[r] * c + ch) * (K - 1);
     const bool fresh = reset[r] != 0;
     float nv[K - 1];
@@ -91,7 +92,7 @@ gdn_recurrent_kernel(const float* __restrict__ conv, const bf16* __restrict__ x,
     const int r = blockIdx.x, h = blockIdx.y;
     const int j = threadIdx.x / SPLIT, part = threadIdx.x % SPLIT;
     const int first = qo_indptr[r], len = qo_indptr[r + 1] - first;
-    if (len <= 0) return;
+    if (len <= 0 || slots[r] < 0) return;
     const int kh = h / (hv / hk);
     const int c = 2 * hk * DK + hv * dv;
     float* sp = rec_state + (((size_t)slots[r] * hv + h) * DK + (size_t)part * ROWS) * dv + j;
@@ -172,7 +173,7 @@ mamba2_ssm_kernel(const float* __restrict__ conv, const bf16* __restrict__ x, in
     __shared__ float sb[NS], scv[NS], sc[1];
     const int r = blockIdx.x, h = blockIdx.y, p = threadIdx.x;
     const int first = qo_indptr[r], len = qo_indptr[r + 1] - first;
-    if (len <= 0) return;
+    if (len <= 0 || slots[r] < 0) return;
     const int inner = heads * head_dim, c = inner + 2 * groups * NS;
     const int g = h / (heads / groups);
     float* sp = rec_state + (((size_t)slots[r] * heads + h) * head_dim + p) * NS;

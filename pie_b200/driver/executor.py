@@ -180,7 +180,6 @@ class TorchDriver:
                 raise NotImplementedError("recurrent (Gated DeltaNet / Mamba-2) layers under tensor parallelism")
             from .recurrent import RecurrentStateCache
             self.rs = RecurrentStateCache(cfg, rs_slots or max(2 * max_requests, 16), self.device)
-            use_graphs = False           # the mixer's ragged inputs are built per fire; no decode graphs yet
         # media: a vision encoder (models.vision.VisionEncoder) and the clips it has encoded, by the runtime's slot
         self.vision, self.audio = vision, audio
         self.media: Dict[int, torch.Tensor] = {}
@@ -211,7 +210,7 @@ class TorchDriver:
             "req_item_indptr": max_requests + 1, "num_items": 4,
             "item_slot": self.max_items, "item_tile": self.max_items, "tile_members": 16 * max_requests,
             "logit_rows": rows, "temperature": rows, "top_k": rows, "top_p": rows, "min_p": rows,
-            "mask_row": rows, "seeds": 2 * rows, "src_row": rows,
+            "mask_row": rows, "seeds": 2 * rows, "src_row": rows, "rs_slots": max_requests, "rs_reset": max_requests,
             "tile_req": max_tokens + max_requests, "tile_qstart": max_tokens + max_requests,
             "page_indices": self.max_page_refs,
         }, self.device)
@@ -415,7 +414,36 @@ class TorchDriver:
         if cascade:
             plan.item_slot, plan.item_tile, plan.tile_members = s.d("item_slot"), s.d("item_tile"), s.d("tile_members")
         return ForwardInputs(tokens=s.d("tokens", rb), positions=s.d("positions", rb), slots=s.d("slots", rb),
-                             attn=plan, logit_rows=None, is_decode=True)
+                             attn=plan, logit_rows=None, is_decode=True,
+                             rs=self._rs_inputs_decode(rb) if self.rs is not None else None)
+
+    def _rs_inputs_decode(self, rb: int):
+        """Recurrent-state inputs of a decode step over `rb` rows at fixed addresses (a graph replays them): one token
+        per request, slots and reset flags in the slab; a row whose slot is -1 is padding and the mixers skip it."""
+        cache = self.__dict__.setdefault("_rs_decode", {})
+        if rb not in cache:
+            from .recurrent import RecurrentInputs
+            s, dev = self.slab, self.device
+            scratch = torch.empty(rb, self.rs.conv_channels, dtype=torch.float32, device=dev) if self.cuda else None
+            cache[rb] = RecurrentInputs(
+                torch.arange(rb + 1, dtype=torch.int32, device=dev), torch.arange(rb, dtype=torch.int32, device=dev),
+                s.d("rs_slots", rb), s.d("rs_reset", rb), list(range(rb + 1)), [-1] * rb, [0] * rb,
+                self.rs.conv_state, self.rs.rec_state, self.rs.layer_index, scratch)
+        return cache[rb]
+
+    def _fill_rs_decode(self, req: ForwardRequest, r: int, rb: int) -> None:
+        s = self.slab
+        if req.rs_slots is None or len(req.rs_slots) != r:
+            raise ValueError("this model has recurrent layers: every request needs a recurrent-state slot")
+        slots = np.asarray(req.rs_slots, dtype=np.int32)
+        if len(slots) and (slots.min() < 0 or slots.max() >= self.rs.num_slots):
+            raise ValueError(f"recurrent-state slot outside 0..{self.rs.num_slots - 1}")
+        if len(np.unique(slots)) != len(slots):
+            raise ValueError("two requests of one fire share a recurrent-state slot")
+        s.h("rs_slots")[:r] = slots
+        s.h("rs_slots")[r:rb] = -1
+        s.h("rs_reset")[:r] = req.rs_reset if req.rs_reset is not None else 0
+        s.h("rs_reset")[r:rb] = 0
 
     def _plan_decode(self, kv_lens, page_indptr, page_indices, r: int, rb: int) -> bool:
         """Fill the slab's decode work list for `r` requests padded to `rb`. Returns True when the plan
@@ -491,6 +519,7 @@ class TorchDriver:
             s.h("tokens")[:rb] = 0
             s.h("positions")[:rb] = 0
             s.h("slots")[:rb] = -1
+            s.h("rs_slots")[:rb] = -1          # every row is padding: the capture's forwards touch no recurrent state
             s.h("kv_page_indptr")[:rb + 1] = 0
             s.h("req_item_indptr")[:rb + 1] = 0
             s.h("num_items")[0] = 0
@@ -518,11 +547,20 @@ class TorchDriver:
             s.h("slots")[r:rb] = -1
             s.h("kv_page_indptr")[r + 1:rb + 1] = req.kv_page_indptr[-1]
         cascade = self._plan_decode(kv_lens, np.asarray(req.kv_page_indptr), np.asarray(req.kv_page_indices), r, rb)
+        if self.rs is not None:
+            self._fill_rs_decode(req, r, rb)
         s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
         if self.use_graphs:
             key = self._gkey(rb, cascade)
             if key not in self.graphs:
+                if self.rs is not None:
+                    # the capture runs the forward for real (twice to warm up): attention KV writes repeat harmlessly,
+                    # a recurrent state would advance, so the rows are padding while it runs
+                    s.h("rs_slots")[:rb] = -1
+                    s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
                 self.graphs[key] = self._capture(rb, cascade)
+                if self.rs is not None:
+                    self._fill_rs_decode(req, r, rb)
                 s.upload("tile_qstart", ("page_indices", len(req.kv_page_indices)))
             g = self.graphs[key]
             g.graph.replay()
@@ -790,8 +828,7 @@ class TorchDriver:
         nslots = len(req.slot_samplers)
         self._lora_bindings = self._bind_adapters(req)
         decode = (req.num_requests > 0 and bool((qlens == 1).all()) and self._lora_bindings is None
-                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and self.rs is None
-                  and req.media_slot is None)
+                  and not (req.has_user_mask is not None and np.any(req.has_user_mask)) and req.media_slot is None)
         if self.par.tp_size > 1 and self.par.comm is not None and self.par.tp_rank == 0:
             # followers must draw the same tokens: fix the per-fire seeds before publishing
             from dataclasses import replace as _replace

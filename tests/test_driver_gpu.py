@@ -178,17 +178,20 @@ def test_forked_contexts_decode_through_the_cascade_plan(monkeypatch):
             assert int(x.argmax()) == int(y.argmax())
 
 
-def test_gdn_hybrid_driver_matches_dense_oracle():
-    """Gated DeltaNet hybrid on the GPU driver: chunked prefill + decode over recurrent-state slots against the
-    dense fp32 oracle of the same (bf16-rounded) weights."""
+@pytest.mark.parametrize("name", ["tiny-qwen3.5", "tiny-mamba2"])
+def test_gdn_hybrid_driver_matches_dense_oracle(name):
+    """Gated DeltaNet and Mamba-2 hybrids on the GPU driver: chunked prefill, then decode steps through a graph (the first
+    one captures it: the capture's own forwards must leave the recurrent state alone; the bucket is wider than the one
+    request, so padding rows run too) against the dense fp32 oracle of the same (bf16-rounded) weights."""
     from pie_b200.driver.schema import ForwardRequest, SamplerKind, SamplerSpec
     from pie_b200.models.transformer import dense_reference_forward
-    cfg = preset("tiny-qwen3.5")
+    cfg = preset(name)
     w = random_weights(cfg, "cuda", torch.bfloat16, seed=4)
     drv = TorchDriver(cfg, "cuda", weights=w, num_pages=32, page_size=16, max_requests=4, max_tokens=128)
     wf = {"layers": [{k: v.float().cpu() for k, v in lw.items()} for lw in w["layers"]],
           **{k: v.float().cpu() for k, v in w.items() if torch.is_tensor(v)}}
-    toks = list(range(60, 60 + 45))
+    assert drv.use_graphs
+    toks = list(range(60, 60 + 50))
     want = dense_reference_forward(cfg, wf, torch.tensor(toks)).numpy()
     i32 = lambda *a: np.asarray(a, dtype=np.int32)
     raw = SamplerSpec(SamplerKind.RAW_LOGITS)
@@ -200,12 +203,33 @@ def test_gdn_hybrid_driver_matches_dense_oracle():
                              kv_last_page_lens=i32((kv - 1) % 16 + 1), slot_req=i32(0), slot_row=i32(n - 1),
                              slot_samplers=[raw], rs_slots=i32(1), rs_reset=i32(reset))
         return np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
-    for a, b, reset in ((0, 20, 1), (20, 44, 0), (44, 45, 0)):
+    for a, b, reset in ((0, 20, 1), (20, 44, 0), (44, 45, 0), (45, 46, 0), (46, 47, 0), (47, 48, 0), (48, 50, 0)):
         got = fire(toks[a:b], a, reset)
         ref_row = want[b - 1]
         cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
         # random-init logits are nearly flat: ask for the oracle's best token among the driver's best five
         assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (a, b, cos)
+    assert drv.stats["graph_replays"] == 4
+    # two more contexts start from zero and decode in the same fires as the first: three real rows and one padding row in a
+    # graph of four
+    seqs = {3: [7, 8, 9], 0: [20, 21, 22]}
+    wants = {sl: dense_reference_forward(cfg, wf, torch.tensor(sq)).numpy() for sl, sq in seqs.items()}
+    want1 = dense_reference_forward(cfg, wf, torch.tensor(toks + seqs[3])).numpy()
+    for j in range(3):
+        kv1, kv2 = 50 + j + 1, j + 1
+        p1, p2 = -(-kv1 // 16), -(-kv2 // 16)
+        first = 1 if j == 0 else 0
+        req = ForwardRequest(tokens=i32(seqs[3][j], seqs[3][j], seqs[0][j]), positions=i32(50 + j, j, j), qo_indptr=i32(0, 1, 2, 3),
+                             kv_page_indices=np.concatenate([np.arange(p1), 16 + np.arange(p2), 24 + np.arange(p2)]).astype(np.int32),
+                             kv_page_indptr=i32(0, p1, p1 + p2, p1 + 2 * p2),
+                             kv_last_page_lens=i32((kv1 - 1) % 16 + 1, (kv2 - 1) % 16 + 1, (kv2 - 1) % 16 + 1),
+                             slot_req=i32(0, 1, 2), slot_row=i32(0, 1, 2), slot_samplers=[raw] * 3, rs_slots=i32(1, 3, 0),
+                             rs_reset=i32(0, first, first))
+        outs = [np.frombuffer(sl.logits, dtype=np.float32) for sl in drv.fire_batch(req).slots]
+        for got, ref_row in zip(outs, (want1[50 + j], wants[3][j], wants[0][j])):
+            cos = float(np.dot(got, ref_row) / (np.linalg.norm(got) * np.linalg.norm(ref_row)))
+            assert cos > 0.995 and int(ref_row.argmax()) in np.argsort(got)[-5:].tolist(), (j, cos)
+    assert drv.stats["graph_replays"] == 7
 
 
 @pytest.mark.parametrize("name,over", [("tiny-gemma3", {}), ("tiny-gemma2", {}), ("tiny-gemma3", dict(head_dim=256)),
