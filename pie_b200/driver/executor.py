@@ -654,7 +654,8 @@ class TorchDriver:
             return {}
         c = v.cfg
         if hasattr(c, "mm_tokens_per_image"):          # fixed-resolution SigLIP tower (Gemma-3)
-            return {"style": "siglip", "image_size": c.image_size, "patch": c.patch_size, "pool": c.pool}
+            # the rows of one image attend to each other in both directions (Gemma-3)
+            return {"style": "siglip", "image_size": c.image_size, "patch": c.patch_size, "pool": c.pool, "bidirectional": True}
         return {"style": "qwen", "patch": c.patch_size, "merge": c.spatial_merge_size, "temporal": c.temporal_patch_size}
 
     def put_media(self, slot: int, kind: str, patches, grids) -> int:

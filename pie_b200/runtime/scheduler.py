@@ -59,6 +59,26 @@ class _ChunkState:
     parent: PendingRequest
     offset: int = 0
     outputs: dict = field(default_factory=dict)   # original slot index -> SlotOutput
+    reach: Optional[np.ndarray] = None            # with custom masks: running maximum of the last key each row may see
+
+
+def mask_reach(masks: Sequence, kv_len: int) -> np.ndarray:
+    """reach[i] = the largest key position that any of rows 0..i of the pass may attend (BRLE rows: even runs are
+    zeros), never less than the row's own position. A row that looks past itself (bidirectional spans: image rows in
+    Gemma-3, tree drafts) needs those keys written by the same fire, so a chunk may end after row i only if
+    reach[i] <= kv_len + i."""
+    out = np.empty(len(masks), dtype=np.int64)
+    best = -1
+    for i, runs in enumerate(masks):
+        last, pos = kv_len + i, 0
+        if runs is not None:
+            for j, n in enumerate(runs):
+                pos += n
+                if j & 1 and n:
+                    last = max(last, pos - 1)
+        best = max(best, last)
+        out[i] = best
+    return out
 
 
 @dataclass
@@ -366,6 +386,18 @@ class BatchScheduler:
             lim = min(self.caps.max_logit_rows, self.caps.max_sampler_rows)
             if len(rows) > lim:
                 b = rows[lim]
+            if p.masks is not None:
+                # rows that look ahead of themselves keep the keys they look at in their own fire
+                if st.reach is None:
+                    st.reach = mask_reach(p.masks, p.kv_len)
+                c = b
+                while c > a and st.reach[c - 1] > p.kv_len + c - 1:
+                    c -= 1
+                if c == a:          # no cut point inside the budget: take the whole look-ahead span, or fail on the limits
+                    c = b
+                    while c < p.n_tokens and st.reach[c - 1] > p.kv_len + c - 1:
+                        c += 1
+                b = c
         samplers = [(idx - a, sp) for idx, sp in p.samplers if a <= idx < b]
         st._slot_ids = [k for k, (idx, _) in enumerate(p.samplers) if a <= idx < b]
         # drafts of a chunked request are verified by the runtime from the slots, not per chunk

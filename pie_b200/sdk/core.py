@@ -267,6 +267,8 @@ class Context:
         c._buffer = list(self._buffer)
         if self.__dict__.get("_pending_media"):
             c._pending_media = list(self._pending_media)
+        if self.__dict__.get("_bidir_spans"):
+            c._bidir_spans = list(self._bidir_spans)
         return c
 
     def save(self, name: str) -> None:
@@ -369,12 +371,39 @@ class Context:
         # on the device; the context takes one placeholder token per encoder row at once, which the request builder
         # turns into media spans, and its next forward pass waits for the encoder
         toks, entry = reg.put(self.id, kind, features.patches, [features.grid], features.num_tokens)
+        spec = getattr(self._entry.caps[0], "media_spec", None) or {}
+        if spec.get("bidirectional") and kind in ("image", "video"):
+            # the rows of one image see each other in both directions: remembered as spans of the pending buffer, and
+            # run with attention masks before anything else consumes the buffer (`_flush_media_spans`)
+            frames = max(1, int(features.grid[0]))
+            per = len(toks) // frames
+            spans = self.__dict__.setdefault("_bidir_spans", [])
+            spans.extend((len(self._buffer) + f * per, per) for f in range(frames))
         self._buffer.extend(toks)
         if not entry.ready.done():
             self.__dict__.setdefault("_pending_media", []).append(entry)
         else:
             entry.ready.result()            # an encoder error of an earlier caller is this caller's too
         return self
+
+    async def _flush_media_spans(self) -> None:
+        """Run the pending buffer up to the end of its last bidirectional span through the model with attention masks: a
+        row inside a span sees every key up to the span's end, every other row is causal. The scheduler keeps a span in
+        one fire. What follows the last span stays pending."""
+        spans = self.__dict__.get("_bidir_spans")
+        if not spans:
+            return
+        end = max(s + n for s, n in spans)
+        toks, self._buffer = self._buffer[:end], self._buffer[end:]
+        base, masks = self._seq_len, []
+        for i in range(end):
+            hi = base + i + 1
+            for s, n in spans:
+                if s <= i < s + n:
+                    hi = base + s + n
+            masks.append([0, hi])
+        self._bidir_spans = []
+        await Forward(self).input(toks).attention_mask(masks).execute()
 
     async def _await_media(self) -> None:
         """Clips appended since the last pass: every path that submits this context's tokens waits here until their
@@ -445,6 +474,8 @@ class Context:
 
     async def flush(self) -> None:
         """Run the pending tokens through the model without sampling."""
+        if self.__dict__.get("_bidir_spans"):
+            await self._flush_media_spans()
         if not self._buffer:
             return
         toks, self._buffer = self._buffer, []
@@ -573,6 +604,8 @@ class Generator:
             raise StopAsyncIteration
         ctx = self.ctx
         if self._pending is None:
+            if ctx.__dict__.get("_bidir_spans"):
+                await ctx._flush_media_spans()
             toks, ctx._buffer = ctx._buffer, []
             if not toks:
                 raise RuntimeError("generate() needs at least one pending token in the context")
@@ -635,6 +668,8 @@ class Generator:
     async def run_offloaded(self, on_tokens=None):
         """Hand the whole decode loop to the runtime; returns the cohort Stream when it ended."""
         ctx = self.ctx
+        if ctx.__dict__.get("_bidir_spans"):
+            await ctx._flush_media_spans()
         toks, ctx._buffer = ctx._buffer, []
         n = self._max if self._max is not None else 1 << 30
         start = ctx.seq_len

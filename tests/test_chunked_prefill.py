@@ -181,3 +181,22 @@ def test_drafts_of_a_chunked_request_are_left_to_the_runtime():
     res, _ = run(drv, [r])
     assert all(q.spec_counts is None for q in rec.requests)    # no per-chunk verdict
     assert getattr(res[1], "spec_accepted", None) is None and [s.token for s in res[1]] == [1098, 1099, 1100]
+
+
+def test_rows_that_look_ahead_stay_in_one_fire_with_the_keys_they_see():
+    """Custom masks with a bidirectional span (rows 50..79 all see keys 0..79, as the rows of an image do in Gemma-3): no
+    chunk may end inside the span, although the 64-token budget falls there."""
+    from pie_b200.runtime.scheduler import mask_reach
+    n = 150
+    masks = [[0, 80] if 50 <= i < 80 else [0, i + 1] for i in range(n)]
+    assert mask_reach(masks, 0)[49] == 49 and mask_reach(masks, 0)[50] == 79 and mask_reach(masks, 0)[149] == 149
+    drv, rec = driver()
+    res, _ = run(drv, [long_req(1, n, masks=masks)])
+    sizes = [f["tokens"] for f in rec.fires]
+    # the first chunk stops before the span, the second takes it whole and ends on a page boundary, then the rest
+    assert sizes == [50, 62, 38] and res[1][0].token == 1000 + n
+    # the span alone is wider than the budget: it is taken whole and the driver's limit refuses it, instead of a wrong answer
+    wide = [[0, 100] if i < 100 else [0, i + 1] for i in range(120)]
+    drv, rec = driver()
+    res, _ = run(drv, [long_req(2, 120, masks=wide)])
+    assert isinstance(res[2], Exception) and "forward limits" in str(res[2])

@@ -375,3 +375,86 @@ def test_gemma3_with_a_siglip_tower_answers_over_an_image():
         assert vid["ok"] and vid["video_tokens"] == 3 * 16
     finally:
         e.shutdown()
+
+
+def test_gemma3_multimodal_equals_transformers_end_to_end(tmp_path):
+    """A whole Gemma-3 vision-language model (SigLIP tower, pooling projector, Gemma-3 text with local / global layers)
+    assembled in transformers from this build's weights: text + image + text through the engine - preprocessing,
+    encoder on the driver, placeholder rows, embedding override without the embedding factor, rows of the image attending
+    to each other in both directions - gives transformers' next-token logits."""
+    from transformers import Gemma3Config, Gemma3ForConditionalGeneration, Gemma3TextConfig
+    from transformers.models.siglip.configuration_siglip import SiglipVisionConfig
+    from pie_b200.models import loader
+    from pie_b200.models.vision import SiglipEncoder, random_siglip_weights, siglip_preset
+    from pie_b200.sdk import Context, Model, media, sample as sm
+    cfg = preset("tiny-gemma3", sliding_window=64)
+    w = random_weights(cfg, "cpu", torch.float32, seed=11)
+    scfg = siglip_preset("tiny-siglip", hidden_size=cfg.hidden_size)
+    sw = random_siglip_weights(scfg, seed=12)
+    # transformers' model from the same tensors
+    loader.export_hf_checkpoint(cfg, w, tmp_path)
+    from safetensors.torch import load_file
+    text_sd = load_file(str(tmp_path / "model.safetensors"))
+    tcfg = json.loads((tmp_path / "config.json").read_text())
+    tcfg.pop("model_type")
+    vc = SiglipVisionConfig(hidden_size=scfg.embed_dim, intermediate_size=scfg.intermediate_size, num_hidden_layers=scfg.depth,
+                            num_attention_heads=scfg.num_heads, image_size=scfg.image_size, patch_size=scfg.patch_size, vision_use_head=False)
+    IMG = 31999
+    gc = Gemma3Config(text_config=Gemma3TextConfig(**tcfg).to_dict(), vision_config=vc.to_dict(), mm_tokens_per_image=16,
+                      image_token_index=IMG, boi_token_index=31998, eoi_token_index=31997)
+    gc._attn_implementation = "eager"
+    hf = Gemma3ForConditionalGeneration(gc).float().eval()
+    sd = {}
+    for k, v in text_sd.items():
+        sd["model.language_model." + k[len("model."):]] = v
+    sd["lm_head.weight"] = text_sd["model.embed_tokens.weight"]
+    for k, v in sw.items():
+        if k.startswith("projector."):
+            name = k[len("projector."):]
+            sd["model.multi_modal_projector." + name] = (v - 1) if name == "mm_soft_emb_norm.weight" else v
+        else:
+            sd["model.vision_tower.vision_model." + k] = v.reshape(scfg.embed_dim, 3, 14, 14) if k == "embeddings.patch_embedding.weight" else v
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not unexpected and all("rotary" in m or "inv_freq" in m for m in missing), (missing, unexpected)
+    pre, post = [5, 6, 7], [40, 41, 42, 43]
+    data = png_bytes(21, 90, 160)
+    feats = mm.patchify_fixed([mm.decode_image(data)], image_size=112, patch=14, pool=2)
+    pix = torch.from_numpy(feats.patches).reshape(1, 8, 8, 3, 14, 14).permute(0, 3, 1, 4, 2, 5).reshape(1, 3, 112, 112)
+    ids = torch.tensor([pre + [IMG] * 16 + post])
+    tt = torch.tensor([[0] * 3 + [1] * 16 + [0] * 4])
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pix, token_type_ids=tt, attention_mask=torch.ones_like(ids)).logits[0, -1]
+
+    enc = SiglipEncoder(scfg, sw)
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=48, vision=enc)
+    assert drv.capabilities().media_spec["bidirectional"]
+    e = Engine(EngineConfig())
+    try:
+        e.add_model("g3", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
+
+        async def prog(args):
+            model = Model.load("g3")
+            ctx = Context(model)
+            ctx.append(pre).append_image(media.Image.for_model(model, data)).append(post)
+            await ctx.flush()                       # image rows run with their masks; nothing is left pending
+            assert ctx.seq_len == 23
+            # read the logits of the last row again through a one-token pass over a fork that re-feeds it
+            probe = Context(model)
+            probe.append(pre).append_image(media.Image.for_model(model, data)).append(post[:-1])
+            await probe.flush()
+            f = probe.forward().input([post[-1]])
+            h = f.probe(0, sm.Logits())
+            out = await f.execute()
+            raw = out.logits(h)
+            ctx.release()
+            probe.release()
+            return base64.b64encode(raw).decode()
+        e.register_program("g3-probe", prog)
+        got = np.frombuffer(base64.b64decode(e.run("g3-probe", {}, 300)), dtype=np.float32)
+    finally:
+        e.shutdown()
+    assert np.abs(got - want.numpy()).max() < 2e-4 and int(got.argmax()) == int(want.argmax())
+    # without the look-both-ways masks the answer differs: the masks were in force
+    emb = {3 + i: enc(feats.patches, [(1, 8, 8)])[i] for i in range(16)}
+    causal = dense_reference_forward(cfg, w, torch.tensor(pre + [0] * 16 + post), embeds=emb)[-1]
+    assert (causal - want).abs().max() > 1e-3
