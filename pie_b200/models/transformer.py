@@ -363,7 +363,8 @@ def _dense_gdn(cfg: ModelConfig, lw: dict, xn: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor, embeds: Optional[dict] = None) -> torch.Tensor:
+def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor, embeds: Optional[dict] = None,
+                            spans: Optional[list] = None) -> torch.Tensor:
     """Independent dense (non-paged) fp32 forward of the same weights for one sequence:
     RMSNorm -> QKV -> rotate-half RoPE -> causal attention -> SwiGLU. Returns logits [T, V].
     This is the token-for-token oracle of the paged engine path."""
@@ -411,7 +412,10 @@ def dense_reference_forward(cfg: ModelConfig, w: dict, tokens: torch.Tensor, emb
                                                   / math.sqrt(cfg.query_pre_attn_scalar or d))
         if cfg.attn_softcap:
             s = torch.tanh(s / cfg.attn_softcap) * cfg.attn_softcap
-        s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1)[None], float("-inf"))
+        future = torch.triu(torch.ones(t, t, dtype=torch.bool), 1)
+        for a0, n0 in spans or ():          # [(first row, rows)]: rows of a span see every key up to the span's end
+            future[a0:a0 + n0, :a0 + n0] = False
+        s = s.masked_fill(future[None], float("-inf"))
         if cfg.layer_window_left(li) >= 0:       # a query sees itself and the sliding_window - 1 keys before it
             s = s.masked_fill(torch.tril(torch.ones(t, t, dtype=torch.bool), -cfg.sliding_window)[None], float("-inf"))
         if "sinks" in lw:       # a per-head extra logit that only takes probability mass

@@ -165,14 +165,14 @@ def paged_attention(q, kv_layer, qo_indptr, kv_page_indptr, page_indices, kv_len
         s = torch.einsum("hqd,hkd->hqk", qf, kf) * sm_scale
         if softcap:         # Gemma-2: scores squashed into (-cap, cap) before masking
             s = torch.tanh(s / softcap) * softcap
+        qi = torch.arange(ql, device=q.device)[:, None]
+        kj = torch.arange(kl, device=q.device)[None, :]
         if masks is not None and masks[r] is not None:
             allow = masks[r].to(q.device)[:, :kl]
         else:
-            qi = torch.arange(ql, device=q.device)[:, None]
-            kj = torch.arange(kl, device=q.device)[None, :]
             allow = kj < (kl - ql + qi + 1)
-            if window_left >= 0:
-                allow = allow & (kj >= (kl - ql + qi - window_left))
+        if window_left >= 0:        # a layer's window bounds the keys on the left under a custom mask too, as in the kernels
+            allow = allow & (kj >= (kl - ql + qi - window_left))
         s = s.masked_fill(~allow[None], float("-inf"))
         m = s.amax(-1, keepdim=True)
         m = torch.where(torch.isinf(m), torch.zeros_like(m), m)

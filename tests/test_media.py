@@ -350,7 +350,7 @@ def test_gemma3_with_a_siglip_tower_answers_over_an_image():
     enc = SiglipEncoder(scfg, random_siglip_weights(scfg, seed=8))
     drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=48, vision=enc)
     spec = drv.capabilities().media_spec
-    assert spec == {"style": "siglip", "image_size": 112, "patch": 14, "pool": 2}
+    assert spec == {"style": "siglip", "image_size": 112, "patch": 14, "pool": 2, "bidirectional": True}
     e = Engine(EngineConfig())
     try:
         e.add_model("gemma-vlm", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
@@ -367,7 +367,7 @@ def test_gemma3_with_a_siglip_tower_answers_over_an_image():
         emb = {i: rows[i] for i in range(16)}          # image rows are not scaled by the embedding factor
         want = []
         for _ in range(4):
-            want.append(int(dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].argmax()))
+            want.append(int(dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb, spans=[(0, 16)])[-1].argmax()))
             toks.append(want[-1])
         assert out["tokens"] == want
         # a clip of several frames is a batch of images for this tower
