@@ -401,7 +401,7 @@ def test_paged_decode_attention_sliding_window(window):
                                            (128, 32, 2, 128), (128, 8, 4, 128), (128, 32, 8, 256),
                                            (128, 8, 1, 256), (128, 4, 4, 256), (128, 32, 2, 256),
                                            (64, 4, 2, 128), (64, 16, 2, 256), (64, 64, 8, 256), (64, 8, 8, 128)])
-@pytest.mark.parametrize("mode", ["causal", "custom", "window"])
+@pytest.mark.parametrize("mode", ["causal", "custom", "window", "custom_window"])
 def test_paged_prefill_attention(d, hq, hkv, rows, mode):
     """rows = 64: the mma.sync kernel; rows = 128 / 256: the tcgen05 kernel with one / two MMA
     tiles per CTA (head_dim 128, 16-token pages)."""
@@ -418,14 +418,14 @@ def test_paged_prefill_attention(d, hq, hkv, rows, mode):
     q = bf(int(qo[-1]), hq, d, seed=22)
     masks = None
     window = -1
-    if mode == "custom":
+    if mode in ("custom", "custom_window"):      # custom_window: a layer's window bounds the left side under a custom mask too
         rng = np.random.default_rng(5)
         masks = []
         for i in range(r):
             m = rng.random((qlens[i], kv_lens[i])) < 0.6
             m[:, 0] = True
             masks.append(m if i != 2 else None)
-    if mode == "window":
+    if mode in ("window", "custom_window"):
         window = 37
     batch = ops.AttnBatch(qo, indptr, pages, kv_lens, masks, window)
     plan = ops.build_prefill_plan(batch, hq // hkv, page, DEV, tile_rows=rows)
