@@ -153,7 +153,7 @@ qk_norm_rope_kvwrite_kernel(const bf16* __restrict__ qkv, const int* __restrict_
                             const bf16* __restrict__ qn, const bf16* __restrict__ kn,
                             bf16* __restrict__ q_out, bf16* __restrict__ kv_layer, int n_tokens,
                             int hq, int hkv, int page_size, float eps, int qkv_stride,
-                            float* __restrict__ kv_scale) {
+                            float* __restrict__ kv_scale, const bf16* __restrict__ bias) {
     constexpr int EP = D / 64;  // elements per lane per half
     pdl_trigger();
     pdl_wait();
@@ -169,6 +169,14 @@ qk_norm_rope_kvwrite_kernel(const bf16* __restrict__ qkv, const int* __restrict_
     for (int e = 0; e < EP; ++e) {
         lo[e] = __bfloat162float(src[lane * EP + e]);
         hi[e] = __bfloat162float(src[D / 2 + lane * EP + e]);
+    }
+    if (bias) {     // projection bias (Qwen2): added here instead of by a pass of its own over the packed rows, rounded as that pass would
+        const bf16* bp = bias + (size_t)h * D;
+#pragma unroll
+        for (int e = 0; e < EP; ++e) {
+            lo[e] = __bfloat162float(__float2bfloat16(lo[e] + __bfloat162float(bp[lane * EP + e])));
+            hi[e] = __bfloat162float(__float2bfloat16(hi[e] + __bfloat162float(bp[D / 2 + lane * EP + e])));
+        }
     }
     const bool is_q = h < hq;
     const bool is_k = !is_q && h < hq + hkv;
@@ -418,25 +426,19 @@ PIE_API int pie_glu_interleaved(const void* gate_up, void* out, long rows, int i
     return (int)cudaGetLastError();
 }
 
+PIE_API int pie_qk_bias_norm_rope_kvwrite(const void* qkv, const void* qkv_bias, const int* positions, const int* slots,
+                                          const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
+                                          void* q_out, void* kv_layer, float* kv_scale, int n_tokens, int hq,
+                                          int hkv, int head_dim, int page_size, float eps, int qkv_stride,
+                                          cudaStream_t st);
+
 PIE_API int pie_qk_norm_rope_kvwrite(const void* qkv, const int* positions, const int* slots,
                                      const float* inv_freq, const void* q_norm_w,
                                      const void* k_norm_w, void* q_out, void* kv_layer,
                                      int n_tokens, int hq, int hkv, int head_dim, int page_size,
                                      float eps, int qkv_stride, cudaStream_t st) {
-    if (n_tokens <= 0) return 0;
-    const long warps = (long)n_tokens * (hq + 2 * hkv);
-    const int blocks = (int)((warps + 7) / 8);
-#define LAUNCH(D)                                                                               \
-    launch_pdl(qk_norm_rope_kvwrite_kernel<D, false>, dim3(blocks), dim3(256), 0, st,           \
-        (const bf16*)qkv, positions, slots, inv_freq, (const bf16*)q_norm_w,                    \
-        (const bf16*)k_norm_w, (bf16*)q_out, (bf16*)kv_layer, n_tokens, hq, hkv, page_size, eps, \
-        qkv_stride, (float*)nullptr)
-    if (head_dim == 64) LAUNCH(64);
-    else if (head_dim == 128) LAUNCH(128);
-    else if (head_dim == 256) LAUNCH(256);
-    else return (int)cudaErrorInvalidValue;
-#undef LAUNCH
-    return (int)cudaGetLastError();
+    return pie_qk_bias_norm_rope_kvwrite(qkv, nullptr, positions, slots, inv_freq, q_norm_w, k_norm_w, q_out, kv_layer,
+                                         nullptr, n_tokens, hq, hkv, head_dim, page_size, eps, qkv_stride, st);
 }
 
 // The same with fp8 KV pages: kv_layer holds e4m3 bytes, kv_scale one fp32 per (token, KV head) row.
@@ -445,19 +447,37 @@ PIE_API int pie_qk_norm_rope_kvwrite_kv8(const void* qkv, const int* positions, 
                                          void* q_out, void* kv_layer, float* kv_scale, int n_tokens, int hq,
                                          int hkv, int head_dim, int page_size, float eps, int qkv_stride,
                                          cudaStream_t st) {
-    if (n_tokens <= 0) return 0;
     if (!kv_scale) return (int)cudaErrorInvalidValue;
+    return pie_qk_bias_norm_rope_kvwrite(qkv, nullptr, positions, slots, inv_freq, q_norm_w, k_norm_w, q_out, kv_layer,
+                                         kv_scale, n_tokens, hq, hkv, head_dim, page_size, eps, qkv_stride, st);
+}
+
+// The general form: optional projection bias [(hq + 2 hkv) * head_dim] added to the packed rows first; kv_scale non-null
+// selects fp8 KV pages (head_dim 64 / 128).
+PIE_API int pie_qk_bias_norm_rope_kvwrite(const void* qkv, const void* qkv_bias, const int* positions, const int* slots,
+                                          const float* inv_freq, const void* q_norm_w, const void* k_norm_w,
+                                          void* q_out, void* kv_layer, float* kv_scale, int n_tokens, int hq,
+                                          int hkv, int head_dim, int page_size, float eps, int qkv_stride,
+                                          cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
     const long warps = (long)n_tokens * (hq + 2 * hkv);
     const int blocks = (int)((warps + 7) / 8);
-#define LAUNCH8(D)                                                                              \
-    launch_pdl(qk_norm_rope_kvwrite_kernel<D, true>, dim3(blocks), dim3(256), 0, st,            \
+#define LAUNCH(D, KV8)                                                                           \
+    launch_pdl(qk_norm_rope_kvwrite_kernel<D, KV8>, dim3(blocks), dim3(256), 0, st,             \
         (const bf16*)qkv, positions, slots, inv_freq, (const bf16*)q_norm_w,                    \
         (const bf16*)k_norm_w, (bf16*)q_out, (bf16*)kv_layer, n_tokens, hq, hkv, page_size, eps, \
-        qkv_stride, kv_scale)
-    if (head_dim == 64) LAUNCH8(64);
-    else if (head_dim == 128) LAUNCH8(128);
-    else return (int)cudaErrorInvalidValue;
-#undef LAUNCH8
+        qkv_stride, kv_scale, (const bf16*)qkv_bias)
+    if (kv_scale) {
+        if (head_dim == 64) LAUNCH(64, true);
+        else if (head_dim == 128) LAUNCH(128, true);
+        else return (int)cudaErrorInvalidValue;
+    } else {
+        if (head_dim == 64) LAUNCH(64, false);
+        else if (head_dim == 128) LAUNCH(128, false);
+        else if (head_dim == 256) LAUNCH(256, false);
+        else return (int)cudaErrorInvalidValue;
+    }
+#undef LAUNCH
     return (int)cudaGetLastError();
 }
 

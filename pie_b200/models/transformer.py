@@ -153,12 +153,11 @@ class Transformer:
         comm.embed_norm_push(fi.tokens, w["embed"], layers[0]["ln1"], cfg.rms_norm_eps, n)
         for li, lw in enumerate(layers):
             qkv = comm.gemm_gated(lw["wqkv"], n)
-            if "bqkv" in lw:
-                qkv = qkv + lw["bqkv"]
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self.inv_freq, lw.get("q_norm"),
                                          lw.get("k_norm"), kv_cache[li], self.hq, self.hkv, self.d,
                                          page_size, cfg.rms_norm_eps,
-                                         kv_scale=self.kv_scale[li] if self.kv_scale is not None else None)
+                                         kv_scale=self.kv_scale[li] if self.kv_scale is not None else None,
+                                         bias=lw.get("bqkv"))
             a = self._attention(q, kv_cache[li], fi, li)
             comm.gemm_rs(a.reshape(n, self.hq * self.d), lw["wo"], n)
             comm.reduce_norm_push(lw["ln2"], cfg.rms_norm_eps, n)
@@ -212,11 +211,13 @@ class Transformer:
                 continue
             x = h if post else ops.rmsnorm(h, lw["ln1"], cfg.rms_norm_eps)
             qkv = self._gemm(x, lw["wqkv"])
-            if "bqkv" in lw:
-                qkv = qkv + lw["bqkv"]
+            qn, kn = lw.get("q_norm"), lw.get("k_norm")
+            # the projection's bias rides in the RoPE / KV-write kernel unless something reads the packed rows before it
+            bias = lw.get("bqkv")
+            if bias is not None and (fi.lora or (qn is not None and qn.numel() != self.d)):
+                qkv, bias = qkv + bias, None
             if fi.lora:
                 qkv = apply_lora(fi.lora, li, "qkv", x, qkv)
-            qn, kn = lw.get("q_norm"), lw.get("k_norm")
             if qn is not None and qn.numel() != self.d:
                 # OLMo-2: RMSNorm over the whole q and k projections (all heads together)
                 qs, ks = self.hq * self.d, self.hkv * self.d
@@ -237,7 +238,7 @@ class Transformer:
                 qn = kn = None
             q = ops.qk_norm_rope_kvwrite(qkv, fi.positions, fi.slots, self._rope_table(li), qn, kn, kv_cache[li],
                                          self.hq, self.hkv, self.d, page_size, cfg.rms_norm_eps,
-                                         kv_scale=self.kv_scale[li] if self.kv_scale is not None else None)
+                                         kv_scale=self.kv_scale[li] if self.kv_scale is not None else None, bias=bias)
             a = self._attention(q, kv_cache[li], fi, li, lw).reshape(n, self.hq * self.d)
             if cfg.sandwich_norm:
                 # Gemma-2/3: both sublayers are normalised on the way in and on the way out

@@ -136,18 +136,27 @@ def glu_interleaved(gate_up, act: str = "silu", out=None):
 
 
 def qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w, kv_layer, hq, hkv,
-                         head_dim, page_size, eps, q_out=None, kv_scale=None):
+                         head_dim, page_size, eps, q_out=None, kv_scale=None, bias=None):
     """Per-head q/k RMSNorm (optional), RoPE, Q out, K/V rows appended into their page slots. With
     `kv_scale` (fp8 pages: kv_layer is a byte tensor, kv_scale [pages, 2, hkv, page] fp32) the rows are
-    stored as e4m3 with one scale per (token, head)."""
+    stored as e4m3 with one scale per (token, head). `bias` [(hq + 2 hkv) * head_dim]: the projection's bias,
+    added to the packed rows first (in the kernel, instead of a pass of its own)."""
     if not qkv.is_cuda:
         if kv_scale is not None:
             raise NotImplementedError("fp8 KV pages need the CUDA kernels")
+        if bias is not None:
+            qkv = qkv + bias
         return reference.qk_norm_rope_kvwrite(qkv, positions, slots, inv_freq, q_norm_w, k_norm_w,
                                               kv_layer, hq, hkv, head_dim, page_size, eps)
     n = qkv.shape[0]
     if q_out is None:
         q_out = torch.empty(n, hq, head_dim, dtype=qkv.dtype, device=qkv.device)
+    if bias is not None:
+        check(fn("pie_qk_bias_norm_rope_kvwrite")(ptr(qkv), ptr(bias), ptr(positions), ptr(slots), ptr(inv_freq), ptr(q_norm_w),
+                                                  ptr(k_norm_w), ptr(q_out), ptr(kv_layer), ptr(kv_scale), n, hq, hkv,
+                                                  head_dim, page_size, eps, qkv.stride(0), stream_ptr()),
+              "qk_bias_norm_rope_kvwrite")
+        return q_out
     if kv_scale is not None:
         check(fn("pie_qk_norm_rope_kvwrite_kv8")(ptr(qkv), ptr(positions), ptr(slots), ptr(inv_freq), ptr(q_norm_w),
                                                  ptr(k_norm_w), ptr(q_out), ptr(kv_layer), ptr(kv_scale), n, hq, hkv,

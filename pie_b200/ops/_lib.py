@@ -31,6 +31,7 @@ _SIGNATURES = {
     "pie_quant_act_fp8": [p, i32, p, p, i32, i32, p],
     "pie_gemm_fp8_blockscaled": [p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, p, i32, p],
     "pie_qk_norm_rope_kvwrite": [p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
+    "pie_qk_bias_norm_rope_kvwrite": [p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
     "pie_qk_norm_rope_kvwrite_kv8": [p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
     "pie_paged_decode_attn_kv8": [p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, p, p],
     "pie_dequant_kv_pages": [p, p, p, p, i32, i32, i32, i32, p],

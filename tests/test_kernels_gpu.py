@@ -56,6 +56,24 @@ def test_glu_interleaved(act):
     assert ops.glu_interleaved(gu[:0], act).shape == (0, 1408)
 
 
+@pytest.mark.parametrize("d,hq,hkv,norm", [(128, 8, 2, False), (64, 4, 2, True), (256, 4, 1, False)])
+def test_qk_norm_rope_kvwrite_with_projection_bias(d, hq, hkv, norm):
+    """The projection bias added inside the kernel equals adding it to the packed rows first."""
+    n, page, pages = 33, 16, 8
+    qkv = bf(n, (hq + 2 * hkv) * d, seed=5)
+    bias = bf((hq + 2 * hkv) * d, seed=9)
+    pos = torch.randint(0, 5000, (n,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV)[:n].to(torch.int32)
+    inv = ref.rope_inv_freq(d, 500000.0, None, DEV)
+    qn = (bf(d, seed=6) + 1) if norm else None
+    kn = (bf(d, seed=7) + 1) if norm else None
+    kv_a = torch.zeros(pages, 2, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+    kv_b = torch.zeros_like(kv_a)
+    qa = ops.qk_norm_rope_kvwrite(qkv, pos, slots, inv, qn, kn, kv_a, hq, hkv, d, page, 1e-6, bias=bias)
+    qb = ops.qk_norm_rope_kvwrite(qkv + bias, pos, slots, inv, qn, kn, kv_b, hq, hkv, d, page, 1e-6)
+    assert torch.equal(qa, qb) and torch.equal(kv_a, kv_b)
+
+
 @pytest.mark.parametrize("d,hq,hkv,norm", [(128, 8, 2, False), (128, 8, 2, True), (64, 4, 2, True)])
 def test_qk_norm_rope_kvwrite(d, hq, hkv, norm):
     n, page, pages = 41, 16, 12
