@@ -458,3 +458,18 @@ def test_gemma3_multimodal_equals_transformers_end_to_end(tmp_path):
     emb = {3 + i: enc(feats.patches, [(1, 8, 8)])[i] for i in range(16)}
     causal = dense_reference_forward(cfg, w, torch.tensor(pre + [0] * 16 + post), embeds=emb)[-1]
     assert (causal - want).abs().max() > 1e-3
+
+
+def test_image_qa_bench_batch_mode_counts_tokens(eng):
+    e, cfg, w, enc, drv = eng
+    resize = dict(min_pixels=28 * 28, max_pixels=28 * 28 * 8)
+    imgs = [base64.b64encode(png_bytes(s)).decode() for s in (31, 32, 31)]
+    out = json.loads(e.run("image-qa-bench", {"images_b64": imgs, "questions": ["One?", "Two?"], "question": "Rest?", "max_tokens": 5,
+                                              "temperature": 0.0, "resize": resize}, 300))
+    assert out["ok"] and len(out["results"]) == 3
+    tok = ByteTokenizer(cfg.vocab_size)
+    for r, q in zip(out["results"], ["One?", "Two?", "Rest?"]):
+        assert r["num_output_tokens"] == 5 and len(r["stamps"]) == 5
+        assert r["num_prompt_tokens"] == r["num_image_tokens"] + len(tok.encode(q))
+    e.models["vlm"].media.drain()
+    assert e.models["vlm"].media.stats()["resident"] == 0 and e.models["vlm"].media.stats()["shared"] >= 1
