@@ -13,11 +13,11 @@ from typing import Optional
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 # `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
 SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3",
-                         "gpt_oss", "qwen3_5", "qwen3_next", "mamba2_hybrid", "gemma2", "gemma3_text", "gemma3")
+                         "gpt_oss", "qwen3_5", "qwen3_next", "mamba2_hybrid", "gemma2", "gemma3_text", "gemma3", "qwen2_moe")
 MAMBA_TYPES = {"mamba2_hybrid"}         # Mamba-2 (state-space) mixers in llama-like blocks, between full-attention layers
 GDN_TYPES = {"qwen3_5", "qwen3_next"}   # hybrids: Gated DeltaNet (linear attention) layers between full-attention layers
 POST_NORM = {"olmo2", "olmo3"}       # same block with the norms after attention / MLP and q, k norms over all heads
-MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss"}
+MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "qwen2_moe"}
 # Gemma-2 / Gemma-3: norms before AND after attention and MLP, gains stored as (w - 1), GeGLU, scaled embeddings,
 # alternating local / global layers (Gemma-3: a RoPE base of their own for the local ones; Gemma-2: soft-capped logits)
 GEMMA_TYPES = {"gemma2", "gemma3_text", "gemma3"}
@@ -58,6 +58,8 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    # a dense expert that every token also passes through, scaled by sigmoid(x . shared_gate) (Qwen2-MoE, Qwen3-Next); 0: none
+    shared_expert_intermediate_size: int = 0
     moe_style: str = "swiglu"       # "gpt_oss": expert and router biases, clamped (up + 1) * gate * sigmoid(1.702 gate)
     swiglu_limit: float = 7.0
     # Gated DeltaNet layers (layer_types entry "linear_attention"): heads and head sizes of the linear mixer
@@ -199,7 +201,7 @@ class ModelConfig:
             attn_softcap=float(cfg.get("attn_logit_softcapping") or 0.0), final_softcap=float(cfg.get("final_logit_softcapping") or 0.0),
             rope_local_theta=float(cfg.get("rope_local_base_freq") or 0.0) if mt == "gemma3_text" else 0.0,
             post_norm=mt in POST_NORM,
-            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "gpt_oss")),
+            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "gpt_oss", "qwen2_moe")),
             # Qwen2 gates the window on use_sliding_window; Mistral applies it whenever it is set
             sliding_window=(cfg.get("sliding_window") or -1)
             if cfg.get("use_sliding_window", mt in ("mistral", "gpt_oss", "olmo3") or gemma) else -1,
@@ -220,7 +222,8 @@ class ModelConfig:
             # Mixtral has no separate field: its intermediate_size is the expert FFN width
             moe_intermediate_size=cfg.get("moe_intermediate_size", 0)
             or (cfg.get("intermediate_size", 0) if mt in ("mixtral", "gpt_oss") else 0),
-            norm_topk_prob=cfg.get("norm_topk_prob", True),
+            norm_topk_prob=cfg.get("norm_topk_prob", mt != "qwen2_moe"),
+            shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0) or 0,
             quantization=quant,
             dtype=str(cfg.get("torch_dtype", "bfloat16")),
             name=name,
@@ -336,6 +339,10 @@ PRESETS = {
                         rms_norm_eps=1e-6, sandwich_norm=True, norm_plus_one=True, hidden_act="gelu_tanh", embed_scale=16.0,
                         query_pre_attn_scalar=48.0, sliding_window=8, tie_word_embeddings=True, attn_softcap=50.0,
                         final_softcap=30.0, layer_types=["sliding_attention", "full_attention"], dtype="float32"),
+    "tiny-qwen2-moe": dict(model_type="qwen2_moe", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=32000, rope_theta=10000.0,
+                           rms_norm_eps=1e-6, attention_bias=True, num_experts=8, num_experts_per_tok=2,
+                           moe_intermediate_size=128, norm_topk_prob=False, shared_expert_intermediate_size=192, dtype="float32"),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            vocab_size=32000, rope_theta=10000.0, rms_norm_eps=1e-6, qk_norm=True,

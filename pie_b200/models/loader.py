@@ -278,6 +278,13 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
                 downs.append(dn)
             att[P + "experts_gate_up"] = Stack(gus)
             att[P + "experts_down"] = Stack(downs)
+            if L + "mlp.shared_expert.gate_proj.weight" in names:
+                # the shared expert (Qwen2-MoE): a dense MLP, sharded like one; its per-token gate is replicated
+                S = L + "mlp.shared_expert."
+                QLin.interleave(lin(S + "gate_proj.weight").shard(0, r, T), lin(S + "up_proj.weight").shard(0, r, T)).attach(
+                    att, P + "shared_gate_up")
+                lin(S + "down_proj.weight").shard(1, r, T).attach(att, P + "shared_down")
+                att[P + "shared_gate"] = w(L + "mlp.shared_expert_gate.weight")
         else:
             if L + "mlp.gate_up_proj.weight" in names:        # Phi-3: gate rows then up rows in one tensor
                 gu = lin(L + "mlp.gate_up_proj.weight")
@@ -450,7 +457,9 @@ def expected_shapes(cfg: ModelConfig, tp_size: int = 1, ep: bool = False) -> Dic
            "bqkv": ((hq + 2 * hkv) * d,), "bo": (H,), "sinks": (hq,),
            "w_gate_up": (2 * cfg.intermediate_size // T, H), "w_down": (H, cfg.intermediate_size // T),
            "router": (E, H), "router_bias": (E,), "experts_gate_up": (el, 2 * il, H), "experts_down": (el, H, il),
-           "experts_gate_up_bias": (el, 2 * il), "experts_down_bias": (el, H)}
+           "experts_gate_up_bias": (el, 2 * il), "experts_down_bias": (el, H),
+           "shared_gate_up": (2 * cfg.shared_expert_intermediate_size // T, H),
+           "shared_down": (H, cfg.shared_expert_intermediate_size // T), "shared_gate": (1, H)}
     if cfg.mamba_layers:
         hm = cfg.mamba_num_heads
         out.update({"w_mamba_in": (cfg.mamba_in_features, H), "mamba_conv": (cfg.mamba_conv_channels, 4),
@@ -714,6 +723,10 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
                 gu, X = lw["experts_gate_up"][e], f"{L}block_sparse_moe.experts.{e}."
                 t[X + "w1.weight"], t[X + "w3.weight"], t[X + "w2.weight"] = gu[0::2], gu[1::2], lw["experts_down"][e]
         elif "experts_gate_up" in lw:
+            if "shared_gate_up" in lw:
+                S = L + "mlp.shared_expert."
+                t[S + "gate_proj.weight"], t[S + "up_proj.weight"] = lw["shared_gate_up"][0::2], lw["shared_gate_up"][1::2]
+                t[S + "down_proj.weight"], t[L + "mlp.shared_expert_gate.weight"] = lw["shared_down"], lw["shared_gate"]
             t[L + "mlp.gate.weight"] = lw["router"]
             for e in range(lw["experts_gate_up"].shape[0]):
                 gu = lw["experts_gate_up"][e]
@@ -758,4 +771,6 @@ def export_hf_checkpoint(cfg: ModelConfig, weights: dict, path) -> None:
     elif cfg.is_moe:
         hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.num_experts_per_tok,
                   moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)
+        if cfg.shared_expert_intermediate_size:
+            hf.update(shared_expert_intermediate_size=cfg.shared_expert_intermediate_size, decoder_sparse_step=1, mlp_only_layers=[])
     (p / "config.json").write_text(json.dumps(hf))

@@ -56,6 +56,10 @@ def moe_reference(cfg: ModelConfig, x: torch.Tensor, lw: dict) -> torch.Tensor:
             act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
             y = act @ lw["experts_down"][e].float().t()
         out[tok] += y * (w[tok] * sel[tok]).sum(-1, keepdim=True)
+    if "shared_gate_up" in lw:
+        gu = xf @ lw["shared_gate_up"].float().t()
+        sh = (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ lw["shared_down"].float().t()
+        out = out + torch.sigmoid(xf @ lw["shared_gate"].float().t()) * sh
     return out
 
 

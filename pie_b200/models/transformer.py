@@ -134,12 +134,18 @@ class Transformer:
 
     def _moe(self, x, lw, h):
         from .moe import moe_block
-        return moe_block(self, x, lw, h)
+        h = moe_block(self, x, lw, h)
+        if "shared_gate_up" in lw:
+            # shared expert: a dense SwiGLU MLP for every token, scaled per token by sigmoid(x . shared_gate)
+            sh = self._row_parallel(self._gemm(x, lw["shared_gate_up"], swiglu=True), lw["shared_down"], None)
+            gate = torch.sigmoid(torch.matmul(x, lw["shared_gate"].t()).float())
+            h = h + (sh.float() * gate).to(h.dtype)
+        return h
 
     def _fused_tp(self) -> bool:
         return self.par.tp_size > 1 and self.par.comm is not None and getattr(self.par.comm, "fused", False) \
             and self.device.type == "cuda" and not self.cfg.post_norm and not self.cfg.sandwich_norm \
-            and self.cfg.model_type != "gpt_oss"
+            and self.cfg.model_type != "gpt_oss" and not self.cfg.shared_expert_intermediate_size
 
     def _forward_hidden_tp(self, fi: ForwardInputs, kv_cache) -> torch.Tensor:
         """Tensor-parallel forward over the fused kernels: the residual stream is row-sharded,

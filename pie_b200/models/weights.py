@@ -171,6 +171,13 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=None, seed: int = 0, tp
             lw["experts_gate_up"] = torch.stack([gate, up], dim=2).reshape(gate.shape[0], 2 * gate.shape[1], H).contiguous()
             lw["experts_down"] = down.contiguous()
             del gate, up, down
+            if cfg.shared_expert_intermediate_size:
+                # the shared expert is a dense MLP: sharded like one under tensor parallelism (also with expert parallelism)
+                Is = cfg.shared_expert_intermediate_size
+                sg, su = shard_rows(gen.normal(Is, H), r, T), shard_rows(gen.normal(Is, H), r, T)
+                lw["shared_gate_up"] = interleave_rows(sg, su).contiguous()
+                lw["shared_down"] = shard_cols(gen.normal(H, Is), r, T).contiguous()
+                lw["shared_gate"] = gen.normal(1, H, std=0.1)
             if cfg.moe_style == "gpt_oss":
                 lw["router_bias"] = gen.normal(E, std=0.5)
                 gub, db = gen.normal(E, 2 * Im, std=0.2), gen.normal(E, H, std=0.2)

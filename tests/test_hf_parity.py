@@ -29,6 +29,7 @@ FAMILIES = [
     ("phi3", "tiny-llama", dict(model_type="phi3")),
     ("gemma3_text", "tiny-gemma3", {}),
     ("gemma2", "tiny-gemma2", {}),
+    ("qwen2_moe", "tiny-qwen2-moe", {}),
 ]
 
 

@@ -15,12 +15,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 @pytest.mark.parametrize("backend,model", [("fused", "dense"), ("nccl", "dense"), ("fused", "moe"),
                                            ("fused", "moe-ep"), ("nccl", "moe-ep"), ("fused", "dense-fp8"),
                                            ("nccl", "gpt-oss"), ("fused", "gpt-oss"), ("nccl", "olmo2"),
-                                           ("nccl", "gemma3"), ("fused", "gemma2")])
+                                           ("nccl", "gemma3"), ("fused", "gemma2"), ("nccl", "qwen2-moe")])
 def test_tp2_logits_match_single_gpu(backend, model):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
-    port = 29511 + ["dense", "moe", "moe-ep", "dense-fp8", "gpt-oss", "olmo2", "gemma3", "gemma2"].index(model) * 2 + (backend == "nccl")
+    port = 29511 + ["dense", "moe", "moe-ep", "dense-fp8", "gpt-oss", "olmo2", "gemma3", "gemma2", "qwen2-moe"].index(model) * 2 + (backend == "nccl")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_check.py"), "--backend", backend,
            "--model", model]

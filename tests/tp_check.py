@@ -24,7 +24,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="fused")
     ap.add_argument("--hidden", type=int, default=512)
-    ap.add_argument("--model", default="dense", choices=["dense", "dense-fp8", "moe", "moe-ep", "gpt-oss", "olmo2", "gemma3", "gemma2"],
+    ap.add_argument("--model", default="dense", choices=["dense", "dense-fp8", "moe", "moe-ep", "gpt-oss", "olmo2", "gemma3", "gemma2", "qwen2-moe"],
                     help="moe: experts sharded on their intermediate dimension; moe-ep: whole experts per rank")
     a = ap.parse_args()
     import torch.distributed as dist
@@ -53,6 +53,11 @@ def main():
                      num_key_value_heads=2, head_dim=128, vocab_size=4096, num_hidden_layers=3, dtype="bfloat16",
                      sliding_window=24, layer_types=["sliding_attention", "full_attention", "sliding_attention"],
                      embed_scale=float(a.hidden) ** 0.5, query_pre_attn_scalar=128.0)
+    elif a.model == "qwen2-moe":
+        # routed experts plus a shared expert gated per token; attention biases
+        cfg = preset("tiny-qwen2-moe", hidden_size=a.hidden, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                     vocab_size=4096, num_hidden_layers=3, dtype="bfloat16", num_experts=16, num_experts_per_tok=4,
+                     moe_intermediate_size=256, shared_expert_intermediate_size=512)
     elif a.model == "gpt-oss":
         cfg = preset("tiny-gpt-oss", hidden_size=a.hidden, intermediate_size=256, moe_intermediate_size=256,
                      num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=4096, num_hidden_layers=2,
