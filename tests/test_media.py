@@ -473,3 +473,25 @@ def test_image_qa_bench_batch_mode_counts_tokens(eng):
         assert r["num_prompt_tokens"] == r["num_image_tokens"] + len(tok.encode(q))
     e.models["vlm"].media.drain()
     assert e.models["vlm"].media.stats()["resident"] == 0 and e.models["vlm"].media.stats()["shared"] >= 1
+
+
+def test_server_config_builds_a_multimodal_model(tmp_path):
+    """`[model.driver] vision` / `audio` in the server configuration: the CPU driver comes up with both encoders, declares
+    the media kinds and the preprocessing the tower wants, and answers image and audio programs through the embedded server."""
+    from pie_b200.server.embed import Server
+    toml = ('[auth]\nenabled = false\n[[model]]\nname = "mm"\npreset = "tiny-llama"\n'
+            '[model.driver]\ntype = "cpu"\nvision = "tiny-vit"\naudio = "tiny-audio"\n')
+    with Server.from_text(toml) as srv:
+        entry = srv.engine.models["mm"]
+        caps = entry.caps[0]
+        assert tuple(caps.media) == ("image", "video", "audio") and caps.media_spec["style"] == "qwen"
+        img = json.loads(srv.engine.run("image-qa", {"image_b64": base64.b64encode(png_bytes(41)).decode(), "max_tokens": 3,
+                                                     "resize": dict(min_pixels=28 * 28, max_pixels=28 * 28 * 6)}, 300))
+        assert img["ok"] and len(img["tokens"]) == 3
+        aud = json.loads(srv.engine.run("audio-qa", {"audio_b64": base64.b64encode(wav_bytes_of(0.6, 300.0)).decode(),
+                                                     "max_tokens": 2}, 300))
+        assert aud["ok"] and aud["audio_tokens"] > 0 and len(aud["tokens"]) == 2
+    sig = ('[auth]\nenabled = false\n[[model]]\nname = "g"\npreset = "tiny-gemma3"\n[model.driver]\ntype = "cpu"\nvision = "tiny-siglip"\n')
+    with Server.from_text(sig) as srv:
+        assert srv.engine.models["g"].caps[0].media_spec == {"style": "siglip", "image_size": 112, "patch": 14, "pool": 2,
+                                                             "bidirectional": True}
