@@ -301,17 +301,53 @@ class inference:
         def execute(self) -> "inference.future_output":
             if self._ctx is None:
                 raise WitError("forward-pass.execute: no context attached")
+            waits = []
             if self._media:
-                kinds = getattr(self._ctx._entry.caps[0], "media", ()) or ()
-                for kind, _, _ in self._media:
-                    if kind not in kinds:
+                # a spliced clip: the driver encodes it (once per distinct content) and the rows of this pass at positions
+                # anchor .. anchor + token-count take the encoder's rows instead of their tokens' embeddings
+                entry = self._ctx._entry
+                kinds = getattr(entry.caps[0], "media", ()) or ()
+                for kind, clip, anchor in self._media:
+                    if kind not in kinds or entry.media is None:
                         raise WitError(f"model has no {kind} encoder")
+                    rows = clip.token_count()
+                    try:
+                        at = self._positions.index(anchor)
+                    except ValueError:
+                        raise WitError(f"input-{kind}: no input token at position {anchor}") from None
+                    if self._positions[at:at + rows] != list(range(anchor, anchor + rows)):
+                        raise WitError(f"input-{kind}: the pass must carry {rows} consecutive positions from {anchor} for the clip")
+                    toks, e = _guard(entry.media.put, self._ctx.id, kind, clip._array(), clip._grids(), rows)
+                    self._tokens[at:at + rows] = toks
+                    if not e.ready.done():
+                        waits.append(e.ready)
             flat = [(i, spec) for idx, spec in self._samplers for i in idx]
             groups = [len(idx) for idx, _ in self._samplers]
             svc = self._ctx._entry.inference
-            fut = _guard(svc.submit, self._ctx.id, self._tokens, self._positions, flat, self._attn, self._mask,
-                         self._spec_tokens, self._spec_positions, self._adapter, self._pass_spec)
-            return inference.future_output(fut, groups)
+            args = (self._ctx.id, self._tokens, self._positions, flat, self._attn, self._mask,
+                    self._spec_tokens, self._spec_positions, self._adapter, self._pass_spec)
+            if not waits:
+                return inference.future_output(_guard(svc.submit, *args), groups)
+            # the pass goes to the scheduler once every encoder has finished; an encoder's error is the pass's error
+            from ..runtime.inference import Future
+            out, left, loop = Future(), [len(waits)], asyncio.get_running_loop()
+
+            def go():
+                try:
+                    svc.submit(*args).add_done_callback(lambda g: out.set(g._result, g._exc))
+                except Exception as exc:  # noqa: BLE001
+                    out.set(None, exc)
+
+            def ready(f):
+                if f._exc is not None:
+                    out.set(None, f._exc)
+                    return
+                left[0] -= 1
+                if left[0] == 0:
+                    loop.call_soon_threadsafe(go)
+            for f in waits:
+                f.add_done_callback(ready)
+            return inference.future_output(out, groups)
 
     class future_output:
         def __init__(self, fut, groups: List[int]):
@@ -575,14 +611,15 @@ class media:
         @staticmethod
         def from_bytes(mdl: "model.model", bytes: bytes) -> "media.image":  # noqa: A002
             from . import media as md
-            return media.image(_guard(md.Image.from_bytes, bytes).features)
+            return media.image(_guard(md.Image.for_model, mdl._m, bytes).features)
 
         def token_count(self) -> int:
             return int(self._f.num_tokens)
 
         def position_span(self) -> int:
-            g = self.grid()
-            return int(max(g[1], g[2]))
+            """Positions the clip advances the sequence by: its rows (the language models here use one-dimensional
+            positions for image rows)."""
+            return self.token_count()
 
         def grid(self) -> Tuple[int, int, int]:
             g = self._f.grid
@@ -594,23 +631,29 @@ class media:
         def suffix_tokens(self) -> List[int]:
             return []
 
+        def _array(self):
+            return self._f.patches
+
+        def _grids(self):
+            return [self._f.grid]
+
     class video:
-        def __init__(self, frames):
-            self._frames = frames
+        def __init__(self, mdl, frames):
+            self._m, self._frames = mdl, frames
 
         @staticmethod
         def from_bytes(mdl: "model.model", bytes: bytes, max_frames: int) -> "media.video":  # noqa: A002
             from ..runtime import multimodal as mm
-            return media.video(_guard(mm.decode_frames, bytes, max_frames))
+            return media.video(mdl, _guard(mm.decode_frames, bytes, max_frames))
 
         def frame_count(self) -> int:
             return len(self._frames)
 
         def frame(self, index: int) -> "media.image":
-            from ..runtime import multimodal as mm
+            from . import media as md
             if not 0 <= index < len(self._frames):
                 raise WitError("frame index out of range")
-            return media.image(mm.patchify([self._frames[index]]))
+            return media.image(md._features_for(self._m._m, [self._frames[index]], {}))
 
         def timestamp(self, index: int) -> float:
             return float(index)
@@ -625,7 +668,8 @@ class media:
             return media.audio(_guard(mm.audio_features, bytes))
 
         def token_count(self) -> int:
-            return int(-(-self._mel.shape[1] // 4))       # four mel frames per soft token
+            f = int(self._mel.shape[1])
+            return ((f - 1) // 2 + 1) // 2 if f > 0 else 0       # a stride-2 convolution, then a stride-2 pool: one row per 40 ms
 
         def position_span(self) -> int:
             return self.token_count()
@@ -635,6 +679,12 @@ class media:
 
         def suffix_tokens(self) -> List[int]:
             return []
+
+        def _array(self):
+            return self._mel
+
+        def _grids(self):
+            return [(int(self._mel.shape[1]),)]
 
 
 # ----------------------------------------------------------------------------- pie:core/audio-out

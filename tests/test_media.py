@@ -495,3 +495,65 @@ def test_server_config_builds_a_multimodal_model(tmp_path):
     with Server.from_text(sig) as srv:
         assert srv.engine.models["g"].caps[0].media_spec == {"style": "siglip", "image_size": 112, "patch": 14, "pool": 2,
                                                              "bidirectional": True}
+
+
+def test_wit_level_forward_pass_splices_an_image_and_an_audio_clip():
+    """The contract-level API (`forward-pass.input-image` / `input-audio` with an anchor position): the pass carries
+    ordinary tokens at the clip's positions, the host swaps in the clip's placeholders, waits for the encoders and the
+    logits equal the SDK path's (same oracle)."""
+    from pie_b200.models.audio import AudioEncoder, audio_preset, random_audio_weights
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=3)
+    vcfg = vision_preset("tiny-vit", hidden_size=cfg.hidden_size)
+    acfg = audio_preset("tiny-audio", hidden_size=cfg.hidden_size)
+    venc, aenc = VisionEncoder(vcfg, random_vision_weights(vcfg, seed=5)), AudioEncoder(acfg, random_audio_weights(acfg, seed=6))
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=128, vision=venc, audio=aenc)
+    img, wav = png_bytes(51, 56, 84), wav_bytes_of(0.5, 500.0)
+
+    async def prog(args):
+        from pie_b200.sdk import wit
+        m = wit.model.model.load(wit.runtime.models()[0])
+        image = wit.media.image.from_bytes(m, img)
+        clip = wit.media.audio.from_bytes(m, wav)
+        ni, na = image.token_count(), clip.token_count()
+        n = 2 + ni + 1 + na + 2
+        ctx = wit.context.context.create(m)
+        ctx.reserve_working_pages(-(-(n + 1) // ctx.tokens_per_page()))
+        fp = wit.inference.forward_pass(m)
+        fp.context(ctx)
+        toks = [10, 11] + [0] * ni + [12] + [0] * na + [13, 14]
+        fp.input_tokens(toks, list(range(n)))
+        fp.input_image(image, 2)
+        fp.input_audio(clip, 2 + ni + 1)
+        fp.sampler([n - 1], "raw-logits")
+        fut = fp.execute()
+        await fut.pollable().block()
+        out = fut.get()
+        bad = wit.inference.forward_pass(m)
+        bad.context(ctx)
+        bad.input_tokens([1, 2], [n, n + 1])
+        bad.input_image(image, n)            # the pass does not carry the clip's rows
+        try:
+            bad.execute()
+            err = ""
+        except wit.WitError as e:
+            err = str(e)
+        ctx.destroy()
+        return json.dumps({"ni": ni, "na": na, "logits": base64.b64encode(out["slots"][0][1]).decode(), "err": err})
+    e = Engine(EngineConfig())
+    try:
+        e.add_model("mm", drv, tokenizer=ByteTokenizer(cfg.vocab_size))
+        e.register_program("wit-media", prog)
+        out = json.loads(e.run("wit-media", {}, 300))
+    finally:
+        e.shutdown()
+    feats = mm.patchify([mm.decode_image(img)])
+    vrows, arows = venc(feats.patches, [feats.grid]), aenc(mm.audio_features(wav))
+    ni, na = out["ni"], out["na"]
+    assert (ni, na) == (vrows.shape[0], arows.shape[0]) and "consecutive positions" in out["err"]
+    toks = [10, 11] + [0] * ni + [12] + [0] * na + [13, 14]
+    emb = {2 + i: vrows[i] for i in range(ni)}
+    emb.update({2 + ni + 1 + i: arows[i] for i in range(na)})
+    want = dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].numpy()
+    got = np.frombuffer(base64.b64decode(out["logits"]), dtype=np.float32)
+    assert np.abs(got - want).max() < 1e-4
