@@ -557,3 +557,40 @@ def test_wit_level_forward_pass_splices_an_image_and_an_audio_clip():
     want = dense_reference_forward(cfg, w, torch.tensor(toks), embeds=emb)[-1].numpy()
     got = np.frombuffer(base64.b64decode(out["logits"]), dtype=np.float32)
     assert np.abs(got - want).max() < 1e-4
+
+
+def test_a_saved_context_keeps_its_clip_for_the_next_program(eng):
+    e, cfg, w, enc, drv = eng
+    from pie_b200.sdk import Context, Model, Sampler, media
+    data = png_bytes(61)
+    resize = dict(min_pixels=28 * 28, max_pixels=28 * 28 * 6)
+
+    async def writer(args):
+        model = Model.load("vlm")
+        ctx = Context(model)
+        ctx.append([3, 4]).append_image(media.Image.for_model(model, data, **resize)).append([5])
+        await ctx.flush()
+        ctx.save("with-image")
+        ctx.release()
+        return "saved"
+
+    async def reader(args):
+        model = Model.load("vlm")
+        ctx = Context.open(model, "with-image")
+        toks = await ctx.append([6]).generate(Sampler.argmax(), max_tokens=3).collect_tokens()
+        ctx.release()
+        if args.get("delete"):
+            Context.delete(model, "with-image")
+        return json.dumps(toks)
+    e.register_program("mm-writer", writer)
+    e.register_program("mm-reader", reader)
+    assert e.run("mm-writer", {}, 120) == "saved"
+    reg = e.models["vlm"].media
+    reg.drain()
+    assert reg.stats()["resident"] == 1 and len(drv.media) == 1      # the writer is gone, the snapshot holds the clip
+    feats = mm.patchify([mm.decode_image(data)], **resize)
+    want = oracle(cfg, w, enc, feats, [3, 4], [5, 6], 3)
+    assert json.loads(e.run("mm-reader", {}, 120)) == want
+    assert json.loads(e.run("mm-reader", {"delete": True}, 120)) == want      # opened twice: the snapshot is not consumed
+    reg.drain()
+    assert reg.stats()["resident"] == 0 and drv.media == {}
