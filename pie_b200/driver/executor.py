@@ -649,14 +649,24 @@ class TorchDriver:
         return self.model.logits(hidden, fi)
 
     def _media_spec(self) -> dict:
+        spec: dict = {}
         v = self.vision
-        if v is None:
-            return {}
-        c = v.cfg
-        if hasattr(c, "mm_tokens_per_image"):          # fixed-resolution SigLIP tower (Gemma-3)
-            # the rows of one image attend to each other in both directions (Gemma-3)
-            return {"style": "siglip", "image_size": c.image_size, "patch": c.patch_size, "pool": c.pool, "bidirectional": True}
-        return {"style": "qwen", "patch": c.patch_size, "merge": c.spatial_merge_size, "temporal": c.temporal_patch_size}
+        if v is not None:
+            c = v.cfg
+            if hasattr(c, "mm_tokens_per_image"):          # fixed-resolution SigLIP tower (Gemma-3)
+                # the rows of one image attend to each other in both directions (Gemma-3)
+                spec = {"style": "siglip", "image_size": c.image_size, "patch": c.patch_size, "pool": c.pool, "bidirectional": True}
+            else:
+                spec = {"style": "qwen", "patch": c.patch_size, "merge": c.spatial_merge_size, "temporal": c.temporal_patch_size}
+        # the text a clip is wrapped in (the model's own span markers), per kind: {"image": [before, after], ...}
+        marks = {}
+        for kinds, enc in ((("image", "video"), v), (("audio",), self.audio)):
+            d = getattr(enc, "delimiters", None)
+            if d and (d[0] or d[1]):
+                marks.update({k: [d[0], d[1]] for k in kinds})
+        if marks:
+            spec["delimiters"] = marks
+        return spec
 
     def put_media(self, slot: int, kind: str, patches, grids) -> int:
         """Encode a clip and keep the encoder's output on the device under `slot`; forward requests then name it in

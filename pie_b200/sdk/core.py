@@ -372,6 +372,9 @@ class Context:
         # turns into media spans, and its next forward pass waits for the encoder
         toks, entry = reg.put(self.id, kind, features.patches, [features.grid], features.num_tokens)
         spec = getattr(self._entry.caps[0], "media_spec", None) or {}
+        before, after = (spec.get("delimiters") or {}).get(kind, ("", ""))
+        if before:          # the model's own span markers go around the clip
+            self._buffer.extend(self._model.tokenizer().encode(before))
         if spec.get("bidirectional") and kind in ("image", "video"):
             # the rows of one image see each other in both directions: remembered as spans of the pending buffer, and
             # run with attention masks before anything else consumes the buffer (`_flush_media_spans`)
@@ -380,6 +383,8 @@ class Context:
             spans = self.__dict__.setdefault("_bidir_spans", [])
             spans.extend((len(self._buffer) + f * per, per) for f in range(frames))
         self._buffer.extend(toks)
+        if after:
+            self._buffer.extend(self._model.tokenizer().encode(after))
         if not entry.ready.done():
             self.__dict__.setdefault("_pending_media", []).append(entry)
         else:

@@ -603,15 +603,24 @@ class adapter:
 
 
 # ----------------------------------------------------------------------------- pie:core/media
+def _marker_tokens(mdl, kind: str, side: int) -> List[int]:
+    """The model's own span marker before (0) or after (1) a clip of `kind`, tokenised; [] where it has none."""
+    if mdl is None:
+        return []
+    spec = getattr(mdl._m._entry.caps[0], "media_spec", None) or {}
+    text = ((spec.get("delimiters") or {}).get(kind) or ("", ""))[side]
+    return list(mdl._m.tokenizer().encode(text)) if text else []
+
+
 class media:
     class image:
-        def __init__(self, feats):
-            self._f = feats
+        def __init__(self, feats, mdl=None):
+            self._f, self._mdl = feats, mdl
 
         @staticmethod
         def from_bytes(mdl: "model.model", bytes: bytes) -> "media.image":  # noqa: A002
             from . import media as md
-            return media.image(_guard(md.Image.for_model, mdl._m, bytes).features)
+            return media.image(_guard(md.Image.for_model, mdl._m, bytes).features, mdl)
 
         def token_count(self) -> int:
             return int(self._f.num_tokens)
@@ -626,10 +635,10 @@ class media:
             return (int(g[0]), int(g[1]), int(g[2]))
 
         def prefix_tokens(self) -> List[int]:
-            return []
+            return _marker_tokens(self._mdl, "image", 0)
 
         def suffix_tokens(self) -> List[int]:
-            return []
+            return _marker_tokens(self._mdl, "image", 1)
 
         def _array(self):
             return self._f.patches
@@ -653,19 +662,19 @@ class media:
             from . import media as md
             if not 0 <= index < len(self._frames):
                 raise WitError("frame index out of range")
-            return media.image(md._features_for(self._m._m, [self._frames[index]], {}))
+            return media.image(md._features_for(self._m._m, [self._frames[index]], {}), self._m)
 
         def timestamp(self, index: int) -> float:
             return float(index)
 
     class audio:
-        def __init__(self, mel):
-            self._mel = mel
+        def __init__(self, mel, mdl=None):
+            self._mel, self._mdl = mel, mdl
 
         @staticmethod
         def from_bytes(mdl: "model.model", bytes: bytes) -> "media.audio":  # noqa: A002
             from ..runtime import multimodal as mm
-            return media.audio(_guard(mm.audio_features, bytes))
+            return media.audio(_guard(mm.audio_features, bytes), mdl)
 
         def token_count(self) -> int:
             f = int(self._mel.shape[1])
@@ -675,10 +684,10 @@ class media:
             return self.token_count()
 
         def prefix_tokens(self) -> List[int]:
-            return []
+            return _marker_tokens(self._mdl, "audio", 0)
 
         def suffix_tokens(self) -> List[int]:
-            return []
+            return _marker_tokens(self._mdl, "audio", 1)
 
         def _array(self):
             return self._mel

@@ -82,9 +82,13 @@ def _vision_encoder(m: ModelSection, cfg, device, dtype):
         hf = _json.loads((Path(m.path) / "config.json").read_text())
         if (hf.get("vision_config") or {}).get("model_type") == "siglip_vision_model":      # Gemma-3: SigLIP tower + pooling projector
             scfg = V.SiglipConfig.from_hf(hf, llm_hidden=cfg.hidden_size)
-            return V.SiglipEncoder(scfg, V.load_siglip_weights(SafetensorsReader(m.path), device, dtype))
+            enc = V.SiglipEncoder(scfg, V.load_siglip_weights(SafetensorsReader(m.path), device, dtype))
+            enc.delimiters = ("\n\n<start_of_image>", "<end_of_image>\n\n")        # Gemma-3's image span markers
+            return enc
         vcfg = V.VisionConfig.from_hf(hf.get("vision_config") or {}, llm_hidden=cfg.hidden_size)
-        return V.VisionEncoder(vcfg, V.load_vision_weights(SafetensorsReader(m.path), device, dtype))
+        enc = V.VisionEncoder(vcfg, V.load_vision_weights(SafetensorsReader(m.path), device, dtype))
+        enc.delimiters = ("<|vision_start|>", "<|vision_end|>")                        # Qwen-VL's
+        return enc
     if kind in V.SIGLIP_PRESETS:
         scfg = V.siglip_preset(kind, hidden_size=cfg.hidden_size)
         return V.SiglipEncoder(scfg, V.random_siglip_weights(scfg, device, dtype))
@@ -103,7 +107,9 @@ def _audio_encoder(m: ModelSection, cfg, device, dtype):
         from ..models.loader import SafetensorsReader
         hf = _json.loads((Path(m.path) / "config.json").read_text())
         acfg = A.AudioConfig.from_hf(hf.get("audio_config") or {}, llm_hidden=cfg.hidden_size)
-        return A.AudioEncoder(acfg, A.load_audio_weights(SafetensorsReader(m.path), device, dtype))
+        enc = A.AudioEncoder(acfg, A.load_audio_weights(SafetensorsReader(m.path), device, dtype))
+        enc.delimiters = ("<|audio_bos|>", "<|audio_eos|>")                            # Qwen2-Audio's clip markers
+        return enc
     acfg = A.audio_preset(kind, hidden_size=cfg.hidden_size)
     return A.AudioEncoder(acfg, A.random_audio_weights(acfg, device, dtype))
 

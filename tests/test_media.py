@@ -594,3 +594,37 @@ def test_a_saved_context_keeps_its_clip_for_the_next_program(eng):
     assert json.loads(e.run("mm-reader", {"delete": True}, 120)) == want      # opened twice: the snapshot is not consumed
     reg.drain()
     assert reg.stats()["resident"] == 0 and drv.media == {}
+
+
+def test_span_markers_of_the_model_go_around_a_clip():
+    cfg = preset("tiny-llama")
+    w = random_weights(cfg, "cpu", torch.float32, seed=3)
+    vcfg = vision_preset("tiny-vit", hidden_size=cfg.hidden_size)
+    enc = VisionEncoder(vcfg, random_vision_weights(vcfg, seed=5))
+    enc.delimiters = ("<img>", "</img>")
+    drv = TorchDriver(cfg, "cpu", weights=w, num_pages=64, page_size=16, max_requests=8, max_tokens=128, vision=enc)
+    assert drv.capabilities().media_spec["delimiters"] == {"image": ["<img>", "</img>"], "video": ["<img>", "</img>"]}
+    tok = ByteTokenizer(cfg.vocab_size)
+
+    async def prog(args):
+        from pie_b200.sdk import Context, Model, media, wit
+        model = Model.load("vlm")
+        im = media.Image.for_model(model, png_bytes(71), min_pixels=28 * 28, max_pixels=28 * 28 * 4)
+        ctx = Context(model)
+        ctx.append([9]).append_image(im)
+        buf = list(ctx.buffer)
+        ctx.release()
+        wm = wit.model.model.load("vlm")
+        wi = wit.media.image.from_bytes(wm, png_bytes(71))
+        return json.dumps({"buf": buf, "n": im.num_tokens, "pre": wi.prefix_tokens(), "suf": wi.suffix_tokens()})
+    e = Engine(EngineConfig())
+    try:
+        e.add_model("vlm", drv, tokenizer=tok)
+        e.register_program("marks", prog)
+        out = json.loads(e.run("marks", {}, 120))
+    finally:
+        e.shutdown()
+    pre, suf, n = tok.encode("<img>"), tok.encode("</img>"), out["n"]
+    assert out["buf"][:1 + len(pre)] == [9] + pre and out["buf"][-len(suf):] == suf
+    assert len(out["buf"]) == 1 + len(pre) + n + len(suf) and all(t >= MEDIA_TOKEN_BASE for t in out["buf"][1 + len(pre):-len(suf)])
+    assert out["pre"] == pre and out["suf"] == suf
