@@ -282,6 +282,8 @@ class Engine:
             m.update({"market_price": e.market.clearing_price, "market_ticks": e.market.ticks,
                       "market_rent": e.market.total_rent, "market_waiting": len(e.market.waiting)})
             m.update({f"ctx_{k}": v for k, v in e.ctxm.counters.items()})
+            if e.media is not None:          # encoded clips: encoder runs, content hits, slots in use, encoder rows held
+                m.update({f"media_{k}": v for k, v in e.media.stats().items()})
             out["models"][name] = m
         live = [p for p in self.processes.values() if not p.finished]
         out["processes"] = len(live)

@@ -488,6 +488,8 @@ def test_server_config_builds_a_multimodal_model(tmp_path):
         img = json.loads(srv.engine.run("image-qa", {"image_b64": base64.b64encode(png_bytes(41)).decode(), "max_tokens": 3,
                                                      "resize": dict(min_pixels=28 * 28, max_pixels=28 * 28 * 6)}, 300))
         assert img["ok"] and len(img["tokens"]) == 3
+        st = srv.engine.model_status()["models"]["mm"]
+        assert st["media_encoded"] == 1 and 'pie_b200_model_media_encoded{model="mm"} 1' in srv.engine.metrics_text()
         aud = json.loads(srv.engine.run("audio-qa", {"audio_b64": base64.b64encode(wav_bytes_of(0.6, 300.0)).decode(),
                                                      "max_tokens": 2}, 300))
         assert aud["ok"] and aud["audio_tokens"] > 0 and len(aud["tokens"]) == 2
