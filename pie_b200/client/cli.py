@@ -46,10 +46,22 @@ def _kv_to_json(rest):
     return out
 
 
-def _stream(handle, out=None) -> int:
+def _stream(handle, out=None, owner: bool = True) -> int:
+    """Print a process' events until it returns. Ctrl-C ends the process when this client launched it (`owner`) and only
+    stops listening when it attached to somebody's; either way the exit code is 130."""
     out = out or sys.stdout
     while True:
-        ev, val = handle.recv(timeout=3600)
+        try:
+            ev, val = handle.recv(timeout=3600)
+        except KeyboardInterrupt:
+            if owner:
+                try:
+                    sys.stderr.write("interrupted: process terminated\n" if handle.terminate() else "interrupted\n")
+                except Exception:  # noqa: BLE001 - the connection may be the thing that broke
+                    sys.stderr.write("interrupted\n")
+            else:
+                sys.stderr.write("detached\n")
+            return 130
         if ev == "stdout":
             out.write(val)
             out.flush()
@@ -207,7 +219,7 @@ def main(argv=None) -> int:
                 return 0
             return _stream(h)
         elif a.cmd == "attach":
-            return _stream(c.attach_process(a.pid))
+            return _stream(c.attach_process(a.pid), owner=False)
         elif a.cmd == "abort":
             h = c.attach_process(a.pid)
             print("terminated" if h.terminate() else "not running")

@@ -294,3 +294,21 @@ def test_client_cli_config_file_and_key_auth(stack, tmp_path, capsys, monkeypatc
     assert json.loads(capsys.readouterr().out)["tokens"] == [7, 8, 9]
     assert cli.main(["config", "update", "--enable-auth", "false"]) == 0
     assert cli.main(["status"]) == 1                               # the server still wants authentication
+
+
+def test_client_cli_interrupt_terminates_its_own_process_and_only_detaches_from_others():
+    from pie_b200.client import cli as client_cli
+
+    class Handle:
+        def __init__(self):
+            self.terminated = 0
+
+        def recv(self, timeout=None):
+            raise KeyboardInterrupt
+
+        def terminate(self):
+            self.terminated += 1
+            return True
+    own, other = Handle(), Handle()
+    assert client_cli._stream(own) == 130 and own.terminated == 1
+    assert client_cli._stream(other, owner=False) == 130 and other.terminated == 0
