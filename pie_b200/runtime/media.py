@@ -89,6 +89,9 @@ class MediaRegistry:
                 raise RuntimeError(f"encoder gave {sorted(got)} rows for a clip planned with {e.rows}")
             e.ready.set(True)
         except BaseException as exc:  # noqa: BLE001 - the waiting forward pass gets the error
+            with self.lock:         # the same content may be tried again; the contexts that hold this entry keep its slot until they go
+                if self.by_key.get(e.key) is e:
+                    del self.by_key[e.key]
             e.ready.set(None, exc)
 
     def _attach(self, ctx_id: int, e: MediaEntry) -> None:
@@ -108,7 +111,9 @@ class MediaRegistry:
                 e = self.by_slot[slot]
                 e.refs -= 1
                 if e.refs <= 0:
-                    del self.by_slot[slot], self.by_key[e.key]
+                    del self.by_slot[slot]
+                    if self.by_key.get(e.key) is e:
+                        del self.by_key[e.key]
                     self._free.append(slot)
                     self.counters["released"] += 1
                     # after the encoder (same single worker): a clip dropped while it was being encoded is released too

@@ -236,6 +236,11 @@ def test_registry_encodes_off_thread_shares_by_content_and_reports_errors():
     _, bad = reg.put(3, "image", -a, [(1, 2, 4)], 2)
     with pytest.raises(ValueError, match="bad clip"):
         bad.ready.result(5)
+    _, again = reg.put(4, "image", -a, [(1, 2, 4)], 2)           # a failed clip is not remembered: the same content is tried again
+    assert again is not bad and again.slot != bad.slot
+    with pytest.raises(ValueError, match="bad clip"):
+        again.ready.result(5)
+    reg.drop(4)
     _, short = reg.put(3, "image", a * 2, [(1, 2, 4)], 3)
     with pytest.raises(RuntimeError, match="planned with 3"):
         short.ready.result(5)
