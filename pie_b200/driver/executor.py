@@ -677,14 +677,24 @@ class TorchDriver:
         enc = self.audio if kind == "audio" else self.vision if kind in ("image", "video") else None
         if enc is None:
             raise ValueError(f"this driver has no encoder for {kind}")
+        grids = [tuple(int(x) for x in g) for g in grids]
+        if enc is self.vision and hasattr(enc.cfg, "mm_tokens_per_image"):
+            grids = [(1, h, w) for t, h, w in grids for _ in range(t)]      # every frame is an image of its own
+        self._bind_thread()
+        if self.cuda:
+            # the encoder runs on a stream of its own, outside the lock that orders fires: decode steps of other requests
+            # go on while a clip is encoded; the rows are published once they are complete
+            stream = self.__dict__.get("_media_stream")
+            if stream is None:
+                stream = self._media_stream = torch.cuda.Stream(self.device)
+            with torch.cuda.stream(stream):
+                feats = enc(np.asarray(patches, dtype=np.float32), grids).to(self.dtype).contiguous()
+            stream.synchronize()
+        else:
+            feats = enc(np.asarray(patches, dtype=np.float32), grids).to(self.dtype).contiguous()
         with self._order:
-            self._bind_thread()
-            grids = [tuple(int(x) for x in g) for g in grids]
-            if enc is self.vision and hasattr(enc.cfg, "mm_tokens_per_image"):
-                grids = [(1, h, w) for t, h, w in grids for _ in range(t)]      # every frame is an image of its own
-            feats = enc(np.asarray(patches, dtype=np.float32), grids)
-            self.media[int(slot)] = feats.to(self.dtype).contiguous()
-            return int(feats.shape[0])
+            self.media[int(slot)] = feats
+        return int(feats.shape[0])
 
     def release_media(self, slot: int) -> None:
         with self._order:
