@@ -77,6 +77,7 @@ class DriverConfig:
     gemm: str = "tcgen05"
     tp_backend: str = "fused"
     memory_profile: str = ""              # "" = built-in limits; auto | latency | balanced | throughput | capacity
+    kv_dtype: str = "auto"                # KV pages: auto / bf16 | fp8_e4m3 (one byte per element + a scale per token and head)
     vision: str = ""                      # "" = text only | "checkpoint" (the `visual.*` tower of [model] path) |
                                           # a preset of models.vision with random weights (e.g. "tiny-vit")
     audio: str = ""                       # the same for the audio encoder (`audio_tower.*`; preset e.g. "tiny-audio")
@@ -158,6 +159,10 @@ def validate(cfg: Config) -> None:
             raise ConfigError(f"model {m.name}: unknown driver type {d.type!r}")
         if d.kv_page_size % 16:
             raise ConfigError(f"model {m.name}: kv_page_size must be a multiple of 16")
+        if d.kv_dtype not in ("auto", "bf16", "fp8_e4m3"):
+            raise ConfigError(f"model {m.name}: unknown kv_dtype {d.kv_dtype!r} (auto | bf16 | fp8_e4m3)")
+        if d.kv_dtype == "fp8_e4m3" and d.type != "cuda_native":
+            raise ConfigError(f"model {m.name}: fp8 KV pages need the cuda_native driver")
         if not 0.05 <= d.gpu_mem_utilization <= 0.98:
             raise ConfigError(f"model {m.name}: gpu_mem_utilization out of range")
         if d.type == "cuda_native":

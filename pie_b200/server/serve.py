@@ -176,7 +176,7 @@ def _build_drivers_direct(m: ModelSection):
             _, weights = loader.load_checkpoint(m.path, dev, world, rank, ep=d.expert_parallel)
         drv = TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, par=par, gemm_backend=d.gemm,
                           use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
-                          memory_profile=d.memory_profile)
+                          memory_profile=d.memory_profile, kv_dtype=d.kv_dtype)
         comm.attach(drv)
         if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":
             n = drv.precapture_graphs()      # every rank is here: the warm-up forwards run in lock step
@@ -190,7 +190,7 @@ def _build_drivers_direct(m: ModelSection):
         swap = int(d.swap_pool_gb * (1 << 30) // per_page)
         drivers.append(TorchDriver(cfg, dev, weights=weights, page_size=d.kv_page_size, gemm_backend=d.gemm,
                                    use_graphs=d.cuda_graphs, gpu_mem_utilization=d.gpu_mem_utilization,
-                                   swap_pages=swap, memory_profile=d.memory_profile,
+                                   swap_pages=swap, memory_profile=d.memory_profile, kv_dtype=d.kv_dtype,
                                    vision=_vision_encoder(m, cfg, dev, torch.bfloat16),
                                    audio=_audio_encoder(m, cfg, dev, torch.bfloat16)))
         if d.cuda_graphs and os.environ.get("PIE_PRECAPTURE_GRAPHS", "1") != "0":

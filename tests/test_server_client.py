@@ -164,6 +164,13 @@ type = "dummy"
         cfgmod.parse(text.replace('type = "dummy"', 'device = [3]'))       # device 3 claimed twice
     cfgmod.set_key(cfg, "model.1.driver.kv_page_size", "32")
     assert cfg.model[1].driver.kv_page_size == 32
+    # KV page format and media encoders are driver keys
+    fp8 = cfgmod.parse(text.replace("tensor_parallel_size = 2", 'tensor_parallel_size = 2\nkv_dtype = "fp8_e4m3"\nvision = "tiny-vit"'))
+    assert fp8.model[0].driver.kv_dtype == "fp8_e4m3" and fp8.model[0].driver.vision == "tiny-vit" and fp8.model[1].driver.kv_dtype == "auto"
+    with pytest.raises(cfgmod.ConfigError, match="kv_dtype"):
+        cfgmod.parse(text.replace("tensor_parallel_size = 2", 'tensor_parallel_size = 2\nkv_dtype = "int4"'))
+    with pytest.raises(cfgmod.ConfigError, match="cuda_native"):
+        cfgmod.parse(text.replace('type = "dummy"', 'type = "dummy"\nkv_dtype = "fp8_e4m3"'))
 
 
 def test_cli_smoke_run_and_monitor(capsys):
