@@ -225,7 +225,7 @@ class ModelConfig:
             norm_topk_prob=cfg.get("norm_topk_prob", mt != "qwen2_moe"),
             shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0) or 0,
             quantization=quant,
-            dtype=str(cfg.get("torch_dtype", "bfloat16")),
+            dtype=str(cfg.get("torch_dtype") or cfg.get("dtype") or "bfloat16"),      # newer files say `dtype`
             name=name,
         )
 

@@ -373,6 +373,8 @@ class Context:
         toks, entry = reg.put(self.id, kind, features.patches, [features.grid], features.num_tokens)
         spec = getattr(self._entry.caps[0], "media_spec", None) or {}
         before, after = (spec.get("delimiters") or {}).get(kind, ("", ""))
+        if self._entry.tokenizer is None:       # token-level use without a tokenizer: the caller places any markers itself
+            before = after = ""
         if before:          # the model's own span markers go around the clip
             self._buffer.extend(self._model.tokenizer().encode(before))
         if spec.get("bidirectional") and kind in ("image", "video"):

@@ -635,3 +635,61 @@ def test_span_markers_of_the_model_go_around_a_clip():
     assert out["buf"][:1 + len(pre)] == [9] + pre and out["buf"][-len(suf):] == suf
     assert len(out["buf"]) == 1 + len(pre) + n + len(suf) and all(t >= MEDIA_TOKEN_BASE for t in out["buf"][1 + len(pre):-len(suf)])
     assert out["pre"] == pre and out["suf"] == suf
+
+
+def test_server_loads_a_gemma3_vision_language_checkpoint(tmp_path):
+    """A Gemma-3 vision-language checkpoint as transformers writes it (nested configuration, `model.language_model.*`,
+    `model.vision_tower.*`, `model.multi_modal_projector.*`): `pie serve` with `vision = "checkpoint"` loads all three parts
+    and the engine's logits over text + image + text equal transformers'."""
+    from transformers import Gemma3Config, Gemma3ForConditionalGeneration, Gemma3TextConfig
+    from transformers.models.siglip.configuration_siglip import SiglipVisionConfig
+    from pie_b200.sdk import Context, Model, media, sample as sm
+    from pie_b200.server.embed import Server
+    torch.manual_seed(0)
+    tcfg = Gemma3TextConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                            head_dim=64, vocab_size=2048, sliding_window=64, query_pre_attn_scalar=64,
+                            layer_types=["sliding_attention", "sliding_attention", "full_attention"], max_position_embeddings=512)
+    vc = SiglipVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=112,
+                            patch_size=14, vision_use_head=False)
+    IMG = 2047
+    gc = Gemma3Config(text_config=tcfg.to_dict(), vision_config=vc.to_dict(), mm_tokens_per_image=16, image_token_index=IMG,
+                      boi_token_index=2046, eoi_token_index=2045)
+    gc._attn_implementation = "eager"
+    hf = Gemma3ForConditionalGeneration(gc).float().eval()
+    for p in hf.parameters():           # norm gains away from zero so that a missed (w + 1) would show
+        if p.dim() == 1:
+            torch.nn.init.normal_(p, 0.0, 0.1)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    pre, post = [5, 6, 7], [40, 41, 42, 43]
+    data = png_bytes(81, 70, 120)
+    feats = mm.patchify_fixed([mm.decode_image(data)], image_size=112, patch=14, pool=2)
+    pix = torch.from_numpy(feats.patches).reshape(1, 8, 8, 3, 14, 14).permute(0, 3, 1, 4, 2, 5).reshape(1, 3, 112, 112)
+
+    toml = (f'[auth]\nenabled = false\n[[model]]\nname = "g3"\npath = "{tmp_path}"\n[model.driver]\ntype = "cpu"\nvision = "checkpoint"\n')
+    with Server.from_text(toml) as srv:
+        caps = srv.engine.models["g3"].caps[0]
+        assert caps.arch_name == "gemma3_text" and caps.media_spec["style"] == "siglip" and caps.media_spec["pool"] == 2
+        assert caps.media_spec["delimiters"]["image"] == ["\n\n<start_of_image>", "<end_of_image>\n\n"]
+
+        async def prog(args):
+            model = Model.load("g3")
+            ctx = Context(model)
+            ctx.append(pre).append_image(media.Image.for_model(model, data)).append(post[:-1])
+            await ctx.flush()
+            f = ctx.forward().input([post[-1]])
+            h = f.probe(0, sm.Logits())
+            raw = (await f.execute()).logits(h)
+            ctx.release()
+            tok = model.tokenizer()         # the server gave the model a byte-level tokenizer: the span markers are real tokens
+            return json.dumps({"logits": base64.b64encode(raw).decode(), "before": tok.encode("\n\n<start_of_image>"),
+                               "after": tok.encode("<end_of_image>\n\n")})
+        srv.engine.register_program("probe", prog)
+        out = json.loads(srv.engine.run("probe", {}, 300))
+    got = np.frombuffer(base64.b64decode(out["logits"]), dtype=np.float32)
+    m0, m1 = out["before"], out["after"]
+    assert m0 and m1 and max(m0 + m1) < IMG
+    ids = torch.tensor([pre + m0 + [IMG] * 16 + m1 + post])
+    tt = torch.tensor([[0] * (3 + len(m0)) + [1] * 16 + [0] * (len(m1) + 4)])
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pix, token_type_ids=tt, attention_mask=torch.ones_like(ids)).logits[0, -1].numpy()
+    assert np.abs(got - want).max() < 2e-4 and int(got.argmax()) == int(want.argmax())
