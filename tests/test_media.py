@@ -693,3 +693,41 @@ def test_server_loads_a_gemma3_vision_language_checkpoint(tmp_path):
     with torch.no_grad():
         want = hf(input_ids=ids, pixel_values=pix, token_type_ids=tt, attention_mask=torch.ones_like(ids)).logits[0, -1].numpy()
     assert np.abs(got - want).max() < 2e-4 and int(got.argmax()) == int(want.argmax())
+
+
+def test_server_loads_a_qwen2_vl_checkpoint(tmp_path):
+    """A Qwen2-VL checkpoint as transformers writes it: the language model loads as the Qwen2 block (text-only logits equal
+    transformers': with equal components the three-axis rotary positions are the ordinary ones), the `visual.*` tower loads
+    next to it and its rows equal transformers' image features; the clip's span markers come from the family."""
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    from pie_b200.server.embed import Server
+    torch.manual_seed(1)
+    c = Qwen2VLConfig(text_config=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                       num_key_value_heads=2, vocab_size=2048, max_position_embeddings=512,
+                                       rope_parameters={"rope_type": "default", "mrope_section": [4, 6, 6], "rope_theta": 10000.0}),
+                      vision_config=dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, patch_size=14,
+                                         spatial_merge_size=2, temporal_patch_size=2, in_channels=3))
+    c._attn_implementation = "eager"
+    hf = Qwen2VLForConditionalGeneration(c).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    toks = list(range(30, 60))
+    feats = mm.patchify([mm.decode_image(png_bytes(91))], min_pixels=28 * 28, max_pixels=28 * 28 * 6)
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([toks])).logits[0, -1].numpy()
+        rows = hf.get_image_features(torch.from_numpy(feats.patches), torch.tensor([feats.grid]))
+    rows = rows if torch.is_tensor(rows) else (rows.pooler_output if hasattr(rows, "pooler_output") else rows[0])
+    rows = torch.cat(list(rows)) if isinstance(rows, (list, tuple)) else rows
+    toml = f'[auth]\nenabled = false\n[[model]]\nname = "q"\npath = "{tmp_path}"\n[model.driver]\ntype = "cpu"\nvision = "checkpoint"\n'
+    with Server.from_text(toml) as srv:
+        entry = srv.engine.models["q"]
+        caps = entry.caps[0]
+        assert caps.arch_name == "qwen2" and caps.media_spec["style"] == "qwen" and tuple(caps.media) == ("image", "video")
+        assert caps.media_spec["delimiters"]["image"] == ["<|vision_start|>", "<|vision_end|>"]
+        drv = entry.drivers[0]
+        assert drv.put_media(3, "image", feats.patches, [feats.grid]) == feats.num_tokens
+        assert (drv.media[3] - rows.reshape(-1, 128)).abs().max() < 1e-5
+        drv.release_media(3)
+        from pie_b200.driver.schema import SamplerKind, SamplerSpec
+        req = fold([PendingRequest(0, toks, list(range(30)), [0, 1], 0, [(29, SamplerSpec(SamplerKind.RAW_LOGITS))])], 16)
+        got = np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
+    assert np.abs(got - want).max() < 2e-4
