@@ -12,8 +12,9 @@ from typing import Optional
 
 LLAMA_LIKE = {"llama", "qwen2", "qwen3", "mistral", "phi3"}   # pre-norm decoder blocks with SwiGLU and rotate-half RoPE
 # `model_type` strings of checkpoints this build loads (the architecture registry of the loader)
-SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3",
-                         "gpt_oss", "qwen3_5", "qwen3_next", "mamba2_hybrid", "gemma2", "gemma3_text", "gemma3", "qwen2_moe", "qwen2_vl")
+SUPPORTED_MODEL_TYPES = ("llama", "mistral", "qwen2", "qwen3", "phi3", "qwen3_moe", "mixtral", "olmo2", "olmo3", "gpt_oss",
+                         "qwen3_5", "qwen3_next", "mamba2_hybrid", "gemma2", "gemma3_text", "gemma3", "qwen2_moe", "qwen2_vl",
+                         "qwen2_audio")
 MAMBA_TYPES = {"mamba2_hybrid"}         # Mamba-2 (state-space) mixers in llama-like blocks, between full-attention layers
 GDN_TYPES = {"qwen3_5", "qwen3_next"}   # hybrids: Gated DeltaNet (linear attention) layers between full-attention layers
 POST_NORM = {"olmo2", "olmo3"}       # same block with the norms after attention / MLP and q, k norms over all heads
@@ -158,6 +159,10 @@ class ModelConfig:
         if mt == "gemma3" and "text_config" in cfg:       # multimodal wrapper: the language model's own section
             cfg = dict(cfg["text_config"], model_type="gemma3_text")
             mt = "gemma3_text"
+        if mt == "qwen2_audio" and "text_config" in cfg:       # the language model of Qwen2-Audio is a plain Qwen2
+            tc = dict(cfg["text_config"])
+            tc.setdefault("tie_word_embeddings", cfg.get("tie_word_embeddings", False))
+            cfg, mt = dict(tc, model_type="qwen2"), "qwen2"
         if mt in ("qwen2_vl", "qwen2_vl_text"):
             # the language model of Qwen2-VL is the Qwen2 block; its three-axis rotary positions are not built: tokens
             # take one-dimensional positions (the same thing for text; image rows then differ from the checkpoint's own code)

@@ -164,7 +164,9 @@ def compile_program(cfg: ModelConfig, names: Sequence[str], tp_size: int = 1, tp
 
     att["embed"] = w(f"{pre}embed_tokens.weight")
     att["final_norm"] = gain(f"{pre}norm.weight")
-    head = w("lm_head.weight") if "lm_head.weight" in names else w(f"{pre}embed_tokens.weight")
+    # an untied output projection sits beside the language model's `model.` subtree (under a wrapper's prefix too)
+    head_names = ["lm_head.weight"] + ([pre[:-len("model.")] + "lm_head.weight"] if pre.endswith("model.") else [])
+    head = next((w(n) for n in head_names if n in names), None) or w(f"{pre}embed_tokens.weight")
     att["lm_head"] = Shard(head, 0, r, T)
     for li in range(cfg.num_hidden_layers):
         L, P = f"{pre}layers.{li}.", f"layers.{li}."

@@ -731,3 +731,35 @@ def test_server_loads_a_qwen2_vl_checkpoint(tmp_path):
         req = fold([PendingRequest(0, toks, list(range(30)), [0, 1], 0, [(29, SamplerSpec(SamplerKind.RAW_LOGITS))])], 16)
         got = np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
     assert np.abs(got - want).max() < 2e-4
+
+
+def test_server_loads_a_qwen2_audio_checkpoint(tmp_path):
+    """A Qwen2-Audio checkpoint as transformers writes it (`language_model.*` with an untied head, `audio_tower.*`,
+    `multi_modal_projector.*`): text logits equal transformers', the audio tower's projected rows equal transformers'."""
+    from transformers import Qwen2AudioConfig, Qwen2AudioForConditionalGeneration
+    from pie_b200.driver.schema import SamplerKind, SamplerSpec
+    from pie_b200.server.embed import Server
+    torch.manual_seed(2)
+    c = Qwen2AudioConfig(text_config=dict(model_type="qwen2", hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                          num_attention_heads=4, num_key_value_heads=2, vocab_size=2048, max_position_embeddings=512),
+                         audio_config=dict(num_mel_bins=80, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, d_model=64,
+                                           max_source_positions=50), audio_token_index=2047)
+    c._attn_implementation = "eager"
+    hf = Qwen2AudioForConditionalGeneration(c).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    toks = list(range(30, 60))
+    mel = torch.randn(80, 100)
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([toks])).logits[0, -1].numpy()
+        rows = hf.multi_modal_projector(hf.audio_tower(mel[None]).last_hidden_state)[0]
+    toml = f'[auth]\nenabled = false\n[[model]]\nname = "a"\npath = "{tmp_path}"\n[model.driver]\ntype = "cpu"\naudio = "checkpoint"\n'
+    with Server.from_text(toml) as srv:
+        entry = srv.engine.models["a"]
+        caps, drv = entry.caps[0], entry.drivers[0]
+        assert caps.arch_name == "qwen2" and tuple(caps.media) == ("audio",)
+        assert caps.media_spec["delimiters"] == {"audio": ["<|audio_bos|>", "<|audio_eos|>"]}
+        assert drv.put_media(0, "audio", mel.numpy(), [(100,)]) == 25
+        assert (drv.media[0] - rows).abs().max() < 1e-5
+        req = fold([PendingRequest(0, toks, list(range(30)), [0, 1], 0, [(29, SamplerSpec(SamplerKind.RAW_LOGITS))])], 16)
+        got = np.frombuffer(drv.fire_batch(req).slots[0].logits, dtype=np.float32)
+    assert np.abs(got - want).max() < 2e-4
