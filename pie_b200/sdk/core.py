@@ -394,23 +394,21 @@ class Context:
         return self
 
     async def _flush_media_spans(self) -> None:
-        """Run the pending buffer up to the end of its last bidirectional span through the model with attention masks: a
-        row inside a span sees every key up to the span's end, every other row is causal. The scheduler keeps a span in
-        one fire. What follows the last span stays pending."""
-        spans = self.__dict__.get("_bidir_spans")
+        """Run the pending buffer up to the end of its last bidirectional span through the model: the text before and
+        between spans in ordinary causal passes, every span in a pass of its own whose rows see every key up to the span's
+        end (attention masks; the scheduler keeps such a pass in one fire). What follows the last span stays pending."""
+        spans = sorted(self.__dict__.get("_bidir_spans") or ())
         if not spans:
             return
-        end = max(s + n for s, n in spans)
-        toks, self._buffer = self._buffer[:end], self._buffer[end:]
-        base, masks = self._seq_len, []
-        for i in range(end):
-            hi = base + i + 1
-            for s, n in spans:
-                if s <= i < s + n:
-                    hi = base + s + n
-            masks.append([0, hi])
         self._bidir_spans = []
-        await Forward(self).input(toks).attention_mask(masks).execute()
+        buf, pos = self._buffer, 0
+        self._buffer = buf[spans[-1][0] + spans[-1][1]:]
+        for s, n in spans:
+            if s > pos:
+                await Forward(self).input(buf[pos:s]).execute()
+            hi = self._seq_len + n
+            await Forward(self).input(buf[s:s + n]).attention_mask([[0, hi]] * n).execute()
+            pos = s + n
 
     async def _await_media(self) -> None:
         """Clips appended since the last pass: every path that submits this context's tokens waits here until their
