@@ -387,11 +387,83 @@ def json_schema_rules(schema, prefix: str = "s"):
 _CACHE: "OrderedDict[str, Grammar]" = OrderedDict()
 
 
+def optimise_rules(rules: List[List[List[tuple]]], root: int, inline_limit: int = 12):
+    """Shrink a grammar without changing its language: (1) a rule with one alternative that does not call itself is
+    substituted where it is referenced when it is short or referenced once (the matcher then keeps one frame less on
+    its stacks for every such level: literals and sequences that the front ends wrap in helper rules); (2) rules with
+    identical bodies become one; (3) rules the root no longer reaches are dropped and the rest renumbered. Returns
+    (rules, root). Counterpart of the grammar optimiser of the reference
+    (runtime/src/inference/structured/optimizer.rs)."""
+    rules = [[list(alt) for alt in r] for r in rules]
+    for _ in range(8):
+        changed = False
+        refs: Dict[int, int] = {}
+        for r in rules:
+            for alt in r:
+                for sym in alt:
+                    if sym[0] >= 0:
+                        refs[sym[0]] = refs.get(sym[0], 0) + 1
+        inlinable = {i for i, r in enumerate(rules)
+                     if i != root and len(r) == 1 and all(sym[0] != i for sym in r[0])
+                     and (len(r[0]) <= inline_limit or refs.get(i, 0) <= 1)}
+        # never substitute a rule into a body through a cycle of inlinable rules: take those that call no inlinable rule
+        leaf = {i for i in inlinable if all(sym[0] not in inlinable for sym in rules[i][0])}
+        if leaf:
+            for r in rules:
+                for k, alt in enumerate(r):
+                    if any(sym[0] in leaf for sym in alt):
+                        out: List[tuple] = []
+                        for sym in alt:
+                            out.extend(rules[sym[0]][0] if sym[0] in leaf else [sym])
+                        r[k] = out
+                        changed = True
+        # identical bodies (compared by value; a self-reference keeps a rule apart from its twins)
+        seen: Dict[tuple, int] = {}
+        alias: Dict[int, int] = {}
+        for i, r in enumerate(rules):
+            if any(sym[0] == i for alt in r for sym in alt):
+                continue
+            key = tuple(tuple(alt) for alt in r)
+            if key in seen and i != root:
+                alias[i] = seen[key]
+            else:
+                seen.setdefault(key, i)
+        if alias:
+            for r in rules:
+                for alt in r:
+                    for j, sym in enumerate(alt):
+                        if sym[0] in alias:
+                            alt[j] = (alias[sym[0]], sym[1])
+            changed = True
+        if not changed:
+            break
+    # reachable rules, renumbered in first-visit order
+    order: List[int] = []
+    index: Dict[int, int] = {}
+    stack = [root]
+    while stack:
+        i = stack.pop()
+        if i in index:
+            continue
+        index[i] = len(order)
+        order.append(i)
+        for alt in rules[i]:
+            for sym in reversed(alt):
+                if sym[0] >= 0 and sym[0] not in index:
+                    stack.append(sym[0])
+    out_rules = [[[(index[sym[0]], sym[1]) if sym[0] >= 0 else sym for sym in alt] for alt in rules[i]] for i in order]
+    return out_rules, index[root]
+
+
 class Grammar:
-    def __init__(self, ebnf: str):
+    def __init__(self, ebnf: str, optimise: bool = True):
         from .._C import pie_host
         self.source = ebnf
         rules, root = _Ebnf(ebnf).parse()
+        self.rules_parsed = len(rules)
+        if optimise:
+            rules, root = optimise_rules(rules, root)
+        self.rules_compiled = len(rules)
         self.native = pie_host.Grammar(rules, root)
 
     @staticmethod

@@ -205,3 +205,46 @@ def test_token_mask_cache_serves_recurring_states():
     assert cold == warm == again
     assert h2 - h1 >= 8                             # the repeated states inside "abcdefgh" and the digits
     assert h3 - h2 == len(text) and m3 == m2 and 0 < n3 <= 512
+
+
+def test_grammar_optimiser_keeps_the_language_and_shrinks_the_rule_set():
+    """Helper rules of the front ends (literals, sequences, groups) are inlined, identical rules merged, unreachable ones
+    dropped: fewer rules, and every vocabulary mask along valid inputs - and the step at which an invalid input dies - is
+    the same as without the pass."""
+    from pie_b200.runtime.structured import JSON_RULES, optimise_rules
+    tok = ByteTokenizer(512)
+    schema = {"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"},
+                                               "tags": {"type": "array", "items": {"enum": ["a", "b"]}},
+                                               "addr": {"type": "object", "properties": {"city": {"type": "string"}}, "required": ["city"]}},
+              "required": ["name", "age"]}
+    cases = [
+        (json_schema_to_ebnf(schema), ['{"name": "Ada", "age": 36, "tags": ["a", "b"], "addr": {"city": "X"}}', '{"name": "", "age": -1}'],
+         ['{"age": 1}', '{"name": "x", "age": "1"}']),
+        ("root ::= value\n" + JSON_RULES, ['[1, {"k": [true, null]}, "s\\n"]', "-1.5e3"], ["[1,, 2]", "{'a': 1}"]),
+        (regex_to_ebnf(r"(ab|cd)+[0-9]{2,4}x?"), ["abcd12", "cd9999x"], ["ab1", "abab12345"]),
+        ('root ::= expr\nexpr ::= term (("+" | "-") term)*\nterm ::= [0-9]+ | "(" expr ")"\n', ["(1+2)-(3)", "42"], ["(1+", "1++2"]),
+    ]
+    for n, (ebnf, good, bad) in enumerate(cases):
+        plain, opt = Grammar(ebnf, optimise=False), Grammar(ebnf, optimise=True)
+        assert opt.rules_compiled <= plain.rules_compiled == plain.rules_parsed, ebnf[:40]
+        if n < 2:           # the JSON grammars are full of helper rules: a third or more of the rules go
+            assert opt.rules_compiled * 3 <= plain.rules_compiled * 2, (opt.rules_compiled, plain.rules_compiled)
+        for text, valid in [(t, True) for t in good] + [(t, False) for t in bad]:
+            a, b = Matcher(plain, tok), Matcher(opt, tok)
+            died = None
+            for i, ch in enumerate(tok.encode(text)):
+                ma, mb = a.next_token_logit_mask(), b.next_token_logit_mask()
+                assert ma == mb, (text, i)
+                if not bool(brle.decode(ma, 512)[ch]):
+                    died = i
+                    break
+                a.accept_tokens([ch])
+                b.accept_tokens([ch])
+            assert a.native.can_terminate() == b.native.can_terminate() and a.is_terminated() == b.is_terminated()
+            # a bad text dies at some byte or ends before the grammar may end
+            assert (died is None and a.native.can_terminate()) == valid, text
+    # the pass alone: a chain of single-use wrappers collapses into the root; a recursive rule stays a rule
+    cls = lambda c: (-1, bytes(bytearray([(1 << (ord(c) & 7)) if i == ord(c) >> 3 else 0 for i in range(32)])))
+    rules = [[[(1, b"")]], [[(2, b""), (3, b"")]], [[cls("a")]], [[cls("b"), (3, b"")], []], [[cls("z")]]]
+    out, root = optimise_rules(rules, 0)
+    assert root == 0 and len(out) == 2 and out[0] == [[cls("a"), (1, b"")]] and out[1] == [[cls("b"), (1, b"")], []]
