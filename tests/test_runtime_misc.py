@@ -288,3 +288,18 @@ def test_determinism_ledger_cases_repeat_and_match_when_asked():
     assert set(ledger["cases"]) == {f"{n}/{p}" for n, p, _ in determinism.CASES}
     if os.environ.get("PIE_CHECK_LEDGER") == "1":
         assert ledger["cases"][f"{name}/{prog}"] == h1
+
+
+def test_ragged_brle_expansion_on_the_cpu_path():
+    """Rows of different lengths expand back to back, each to ceil(bits / 32) words, with zeros past the last run."""
+    import numpy as np
+    from pie_b200 import ops
+    from pie_b200.runtime import brle
+    rows, bits = [[3, 2, 1], [0, 40], [10], [0, 5, 2, 7], []], [6, 40, 10, 70, 33]
+    words, offs = ops.brle_expand_ragged(rows, bits, "cpu")
+    assert offs.tolist() == [0, 1, 3, 4, 7, 9] and words.numel() == 9
+    for i, (r, n) in enumerate(zip(rows, bits)):
+        got = np.unpackbits(words[offs[i]:offs[i + 1]].numpy().view(np.uint8), bitorder="little")[:n].astype(bool)
+        assert np.array_equal(got, brle.decode(r, n)), i
+    empty, offs0 = ops.brle_expand_ragged([], [], "cpu")
+    assert empty.numel() == 0 and offs0.tolist() == [0]
