@@ -49,6 +49,10 @@ def _load(args) -> cfgmod.Config:
     if getattr(args, "model_path", None):
         cfg.model = [cfgmod.ModelSection(name=Path(args.model_path).name, path=args.model_path,
                                          driver=cfg.model[0].driver if cfg.model else cfgmod.DriverConfig())]
+    for key in ("vision", "audio"):
+        if getattr(args, key, None):
+            for m in cfg.model:
+                setattr(m.driver, key, getattr(args, key))
     cfgmod.validate(cfg)
     return cfg
 
@@ -442,6 +446,8 @@ def main(argv=None) -> int:
         p.add_argument("--driver", choices=["cuda_native", "cpu", "dummy"])
         p.add_argument("--preset")
         p.add_argument("--model-path")
+        p.add_argument("--vision", help='vision encoder: "checkpoint" (the tower of --model-path) or a preset such as tiny-vit')
+        p.add_argument("--audio", help='audio encoder: "checkpoint" or a preset such as tiny-audio')
 
     p = sub.add_parser("serve"); common(p)
     p.add_argument("--port", type=int); p.add_argument("--no-auth", action="store_true")
