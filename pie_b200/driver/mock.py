@@ -45,6 +45,21 @@ class CounterBehavior(Behavior):
         return (np.asarray(req.tokens)[rows] + 1) % self.vocab
 
 
+class ScriptedBehavior(Behavior):
+    """Answers the sampled rows with the next tokens of a fixed script, one per row in call order (the script's last
+    token repeats when it runs out): lets a test make the "model" say a chosen reply."""
+
+    def __init__(self, script):
+        self.script, self.i = [int(t) for t in script], 0
+
+    def tokens(self, req, rows):
+        out = np.empty(len(rows), dtype=np.int64)
+        for k in range(len(rows)):
+            out[k] = self.script[min(self.i, len(self.script) - 1)]
+            self.i += 1
+        return out
+
+
 class DelayedBehavior(Behavior):
     def __init__(self, inner: Behavior, seconds: float):
         self.inner, self.seconds = inner, seconds

@@ -74,3 +74,23 @@ def test_gemma3_folds_system_into_first_user_turn_through_the_context():
         eng.shutdown()
     assert a == "<bos><start_of_turn>user\nS\nU<end_of_turn>\n<start_of_turn>model\n"
     assert b == "<bos><start_of_turn>user\nonly<end_of_turn>\n<start_of_turn>model\n"
+
+
+def test_python_example_inferlet_streams_answer_and_keeps_reasoning_apart():
+    """The walk-through inferlet on a chat model: tokens go through the chat decoder and the reasoning decoder; what is inside
+    the think tags does not reach the answer. The scripted driver speaks a reply with a reasoning block."""
+    from test_runtime_cpu import MockDriver, engine_with
+    from pie_b200.driver.mock import ScriptedBehavior
+    from pie_b200.inferlets import install_all
+    ins = I.for_arch("qwen3")
+    reply = TOK.encode("<think>hm</think>Paris.")
+    eng = engine_with(MockDriver(ScriptedBehavior(reply + TOK.encode("!")), total_pages=64))
+    try:
+        entry = eng.models["mock"]
+        entry.tokenizer, entry.instruct = TOK, ins
+        entry.inference.cohorts = []
+        install_all(eng)
+        out = eng.run("python-example", {"max_tokens": len(reply) + 3}, 60)
+    finally:
+        eng.shutdown()
+    assert out.startswith("Paris.") and out.rstrip("!") == "Paris." and "hm" not in out and "think" not in out
